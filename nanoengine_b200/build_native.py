@@ -1,0 +1,137 @@
+"""In-tree build of the native parts.
+
+Three artefacts land in ``nanoengine_b200/_native``:
+
+* ``_core*.so``      C++20 + pybind11: scheduler, block manager, wire codec, metrics.
+* ``libne_kernels.so`` CUDA sm_100a kernels with a plain C ABI (loaded with ctypes, so
+  building needs neither torch headers nor a GPU; nvcc cross-compiles).
+* ``ne-gateway``     C++ HTTP gateway binary.
+
+The reference builds its native side with maturin/cargo (pyproject.toml:1-3,66-76) and
+JIT-compiles CUDA through tvm_ffi (dlengine/runtime/kernel/jit/sgl/utils.py:76-123); here
+everything is ahead-of-time so the shared objects travel with the source tree.
+
+Run ``python -m nanoengine_b200.build_native`` (add ``--force`` to rebuild everything).
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+OUT = PKG / "_native"
+OBJ = OUT / "obj"
+REPO = PKG.parent
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+              "-Xptxas", "-v", "-DNDEBUG"] + GENCODE
+
+
+def _stamp(paths, extra=""):
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        h.update(str(p).encode())
+        h.update(Path(p).read_bytes())
+    return h.hexdigest()
+
+
+def _needs(target: Path, stamp: str, force: bool) -> bool:
+    sf = target.with_suffix(target.suffix + ".stamp")
+    if force or not target.exists() or not sf.exists() or sf.read_text() != stamp:
+        return True
+    return False
+
+
+def _mark(target: Path, stamp: str):
+    target.with_suffix(target.suffix + ".stamp").write_text(stamp)
+
+
+def _run(cmd, log: Path | None = None):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if log is not None:
+        log.write_text(" ".join(map(str, cmd)) + "\n" + r.stdout + r.stderr)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError(f"build failed: {' '.join(map(str, cmd))}")
+    return r
+
+
+def build_core(force=False) -> Path:
+    import pybind11
+    suffix = sysconfig.get_config_var("EXT_SUFFIX")
+    target = OUT / f"_core{suffix}"
+    srcs = list((CSRC / "core").glob("*.cpp")) + list((CSRC / "core").glob("*.h"))
+    stamp = _stamp(srcs)
+    if _needs(target, stamp, force):
+        cmd = [CXX, "-O2", "-std=c++20", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
+               f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}",
+               str(CSRC / "core" / "bindings.cpp"), "-o", str(target)]
+        _run(cmd)
+        _mark(target, stamp)
+    return target
+
+
+def build_kernels(force=False) -> Path:
+    target = OUT / "libne_kernels.so"
+    kdir = CSRC / "kernels"
+    cus = sorted(kdir.glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu"))
+    hdrs = sorted(kdir.glob("*.cuh")) + sorted(kdir.glob("*.h")) + sorted((CSRC / "comm").glob("*.cuh")) + sorted((CSRC / "comm").glob("*.h"))
+    if not cus:
+        return target
+    OBJ.mkdir(parents=True, exist_ok=True)
+    hstamp = _stamp(hdrs, " ".join(NVCC_FLAGS))
+    objs, jobs = [], []
+    for cu in cus:
+        obj = OBJ / (cu.stem + ".o")
+        objs.append(obj)
+        st = _stamp([cu], hstamp)
+        if _needs(obj, st, force):
+            jobs.append((cu, obj, st))
+
+    def one(job):
+        cu, obj, st = job
+        _run([NVCC, *NVCC_FLAGS, f"-I{kdir}", f"-I{CSRC / 'comm'}", "-c", str(cu), "-o", str(obj)],
+             log=OBJ / (cu.stem + ".ptxas.log"))
+        _mark(obj, st)
+
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
+        list(ex.map(one, jobs))
+    lstamp = _stamp(objs)
+    if _needs(target, lstamp, force or bool(jobs)):
+        _run([NVCC, "-shared", *GENCODE, "-o", str(target), *map(str, objs), "-lcudart"])
+        _mark(target, lstamp)
+    return target
+
+
+def build_gateway(force=False) -> Path:
+    target = OUT / "ne-gateway"
+    gdir = REPO / "gateway"
+    srcs = sorted(gdir.glob("*.cpp")) + sorted(gdir.glob("*.h"))
+    if not srcs:
+        return target
+    stamp = _stamp(srcs)
+    if _needs(target, stamp, force):
+        _run([CXX, "-O2", "-std=c++20", "-pthread", "-Wall", *map(str, sorted(gdir.glob("*.cpp"))), "-o", str(target)])
+        _mark(target, stamp)
+    return target
+
+
+def build_all(force=False):
+    OUT.mkdir(parents=True, exist_ok=True)
+    (OUT / "__init__.py").touch()
+    return {"core": build_core(force), "kernels": build_kernels(force), "gateway": build_gateway(force)}
+
+
+if __name__ == "__main__":
+    res = build_all(force="--force" in sys.argv)
+    for k, v in res.items():
+        print(f"{k}: {v} ({'ok' if Path(v).exists() else 'absent'})")
