@@ -1,0 +1,176 @@
+"""Engine configuration: one object, consumed as Python kwargs, from a YAML/JSON file, or from CLI flags.
+
+Parity: reference dlengine/config.py:17-271 (fields) and :273-884 (validator: architecture detection, MLA
+forces block size 64 and attention_tp == 1, MTP / PP / HiSparse constraints), :886-897 (world sizes).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass, field, fields
+from typing import Any, Dict, List, Optional
+
+from .models.config import PRESETS, ModelConfig
+from .parallel.dist import ParallelSpec
+
+
+@dataclass
+class Config:
+    model: str = "tiny-deepseek-v3"          # checkpoint directory, or a preset name with dummy_weight
+    hf_overrides: Dict[str, Any] = field(default_factory=dict)
+    model_config: Optional[ModelConfig] = None
+    dtype: str = "bfloat16"
+    device: str = "auto"                     # "auto" | "cuda" | "cpu"
+    seed: int = 0
+    dummy_weight: bool = False               # random-init weights in the HF layout
+    dummy_prefill: bool = False              # decode engine fabricates KV for arriving prompts (no prefill peer)
+    # scheduling
+    max_num_batched_tokens: int = 16384
+    max_num_seqs: int = 16
+    max_model_len: Optional[int] = None
+    enable_prefix_caching: bool = True
+    enable_chunked_prefill: bool = True
+    routing_strategy: str = "round_robin"    # round_robin | least_batch | least_cache | affinity
+    mode: str = "hybrid"                     # hybrid | prefill | decode
+    # parallel layout
+    attention_dp: int = 1
+    attention_sp: int = 1
+    attention_tp: int = 1
+    ffn_dp: int = 1
+    ffn_ep: int = 1
+    ffn_tp: int = 1
+    pp: int = 1
+    # cache
+    kv_cache_dtype: str = "auto"             # auto | bfloat16 | fp8
+    kvcache_block_size: int = 256
+    num_kvcache_blocks: Optional[int] = None  # None = size from free memory
+    gpu_memory_utilization: float = 0.9
+    num_host_kvcache_blocks: int = 0
+    l3_dir: Optional[str] = None
+    l3_capacity_blocks: int = 0
+    # speculative decoding
+    num_speculative_tokens: int = 0
+    # sparse attention
+    disable_nsa: bool = False
+    enable_hisparse: bool = False
+    # execution
+    enforce_eager: bool = False
+    cuda_graph_max_bs: int = 256
+    executor_backend: str = "auto"           # auto | inproc | mp
+    use_fused_comm: bool = True              # fused compute+collective kernels when peers are reachable
+    dummy_eplb: bool = False
+    # observability
+    log_level: str = "INFO"
+    step_timing: bool = False
+    profiler_dir: Optional[str] = None
+    # serving / PD
+    engine_id: str = "engine-0"
+    ctrl_address: Optional[str] = None
+    host: str = "127.0.0.1"
+    port: int = 8000
+
+    def __post_init__(self):
+        self.validate()
+
+    # ---- validation ------------------------------------------------------------------------
+    def validate(self) -> None:
+        if self.model_config is None:
+            if self.model in PRESETS:
+                self.model_config = PRESETS[self.model]()
+                self.dummy_weight = True
+            elif os.path.isdir(self.model):
+                self.model_config = ModelConfig.from_pretrained(self.model)
+            else:
+                raise ValueError(f"model '{self.model}' is neither a checkpoint directory nor a preset {sorted(PRESETS)}")
+        for k, v in self.hf_overrides.items():
+            if not hasattr(self.model_config, k):
+                raise ValueError(f"unknown model field in hf_overrides: {k}")
+            setattr(self.model_config, k, v)
+        mc = self.model_config
+        if self.mode not in ("hybrid", "prefill", "decode"):
+            raise ValueError("mode must be hybrid, prefill or decode")
+        if self.routing_strategy not in ("round_robin", "least_batch", "least_cache", "affinity"):
+            raise ValueError(f"unknown routing_strategy {self.routing_strategy}")
+        if self.kv_cache_dtype not in ("auto", "bfloat16", "float32", "fp8"):
+            raise ValueError("kv_cache_dtype must be auto, bfloat16, float32 or fp8")
+        if self.dtype not in ("bfloat16", "float16", "float32"):
+            raise ValueError("dtype must be bfloat16, float16 or float32")
+        if mc.is_mla:
+            # the latent-cache kernels page in units of 64 rows; latent KV is shared by all heads, so head-sharding it buys nothing
+            if self.kvcache_block_size == 256:
+                self.kvcache_block_size = 64
+            if self.attention_tp != 1:
+                raise ValueError("MLA architectures run attention data-parallel: attention_tp must be 1")
+        elif self.kvcache_block_size == 256:
+            self.kvcache_block_size = 64
+        if self.attention_sp != 1:
+            raise ValueError("attention_sp > 1 is not supported by the runner")
+        spec = self.parallel_spec()
+        spec.validate()
+        if mc.n_routed_experts and mc.n_routed_experts % self.ffn_ep:
+            raise ValueError("n_routed_experts must be divisible by ffn_ep")
+        if not mc.is_mla and mc.num_key_value_heads % self.attention_tp and self.attention_tp % mc.num_key_value_heads:
+            raise ValueError("attention_tp must divide (or be a multiple of) num_key_value_heads")
+        if self.num_speculative_tokens < 0:
+            raise ValueError("num_speculative_tokens must be >= 0")
+        if self.num_speculative_tokens > 0:
+            if mc.num_nextn_predict_layers < 1:
+                raise ValueError("speculative decoding needs a model with MTP layers (num_nextn_predict_layers >= 1)")
+            if self.pp > 1:
+                raise ValueError("speculative decoding is not available with pipeline parallelism")
+        if self.pp > 1:
+            if self.mode != "prefill":
+                raise ValueError("pipeline parallelism is a prefill-only pipeline: set mode='prefill'")
+            self.enforce_eager = True
+        if self.enable_hisparse and not mc.has_indexer:
+            raise ValueError("enable_hisparse needs a DSA model (lightning indexer)")
+        if self.max_model_len is None:
+            self.max_model_len = mc.max_position_embeddings
+        if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1:
+            raise ValueError("max_num_seqs and max_num_batched_tokens must be positive")
+        if not (0.0 < self.gpu_memory_utilization <= 1.0):
+            raise ValueError("gpu_memory_utilization must be in (0, 1]")
+
+    # ---- projections -----------------------------------------------------------------------
+    def parallel_spec(self) -> ParallelSpec:
+        return ParallelSpec(self.attention_dp, self.attention_sp, self.attention_tp, self.ffn_dp, self.ffn_ep, self.ffn_tp, self.pp)
+
+    @property
+    def world_size(self) -> int:
+        return self.parallel_spec().world_size
+
+    def resolved_kv_dtype(self) -> str:
+        if self.kv_cache_dtype != "auto":
+            return self.kv_cache_dtype
+        return self.dtype
+
+    def use_nsa(self) -> bool:
+        return self.model_config.has_indexer and not self.disable_nsa
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = {f.name: getattr(self, f.name) for f in fields(self) if f.name != "model_config"}
+        d["model_config"] = self.model_config.to_dict()
+        return d
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "Config":
+        d = dict(d)
+        mc = d.pop("model_config", None)
+        known = {f.name for f in fields(cls)}
+        bad = set(d) - known
+        if bad:
+            raise ValueError(f"unknown config fields: {sorted(bad)}")
+        if mc is not None:
+            d["model_config"] = ModelConfig.from_dict(mc) if isinstance(mc, dict) else mc
+        return cls(**d)
+
+    @classmethod
+    def from_file(cls, path: str, **overrides) -> "Config":
+        with open(path) as f:
+            if path.endswith((".yaml", ".yml")):
+                import yaml
+                d = yaml.safe_load(f) or {}
+            else:
+                d = json.load(f)
+        d.update(overrides)
+        return cls.from_dict(d)

@@ -1,0 +1,170 @@
+"""Executors: launch one worker per GPU and fan calls out to them.
+
+* ``InprocExecutor``  - the single worker lives in the controller process (world size 1).
+* ``MultiprocExecutor`` - one spawned process per rank; each joins ``torch.distributed`` (NCCL for device
+  collectives + gloo for host control, or gloo only on CPU) and serves calls over a pipe.  A watchdog
+  notices a dead worker and fails the pending call instead of hanging the controller.
+
+Parity: reference executor/ray_executor.py:100-482 (collective_rpc :311, run_batch_bytes_async :407,
+KV-block count = min over workers :443); the Ray / RDMA-RPC transports are replaced by pipes on one box.
+"""
+from __future__ import annotations
+
+import os
+import socket
+import traceback
+from typing import Any, List, Optional, Sequence
+
+import torch
+
+from ..config import Config
+
+
+class ExecutorError(RuntimeError):
+    pass
+
+
+class InprocExecutor:
+    def __init__(self, config: Config):
+        from ..runtime.model_runner import ModelRunner
+        self.config = config
+        self.world_size = 1
+        self.runner = ModelRunner(config, 0, 1)
+
+    def collective_rpc(self, method: str, *args, **kw) -> List[Any]:
+        return [getattr(self.runner, method)(*args, **kw)]
+
+    def run_batches(self, blobs: Sequence[bytes]) -> List[bytes]:
+        return [self.runner.run_from_bytes(blobs[0])]
+
+    def shutdown(self):
+        self.runner = None
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker_main(rank: int, world_size: int, config_dict: dict, port: int, conn, use_cuda: bool):
+    try:
+        import torch.distributed as dist
+        from ..config import Config as _Config
+        from ..runtime.model_runner import ModelRunner
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ["RANK"], os.environ["WORLD_SIZE"], os.environ["LOCAL_RANK"] = str(rank), str(world_size), str(rank)
+        cfg = _Config.from_dict(config_dict)
+        if use_cuda:
+            torch.cuda.set_device(rank)
+            dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world_size, device_id=torch.device(f"cuda:{rank}"))
+        else:
+            torch.set_num_threads(max(1, (os.cpu_count() or 2) // world_size))
+            dist.init_process_group("gloo", rank=rank, world_size=world_size)
+        runner = ModelRunner(cfg, rank, world_size, device=f"cuda:{rank}" if use_cuda else "cpu")
+        conn.send(("ready", None))
+        while True:
+            msg = conn.recv()
+            if msg is None:
+                break
+            method, args, kw = msg
+            try:
+                conn.send(("ok", getattr(runner, method)(*args, **kw)))
+            except Exception as e:  # report and keep serving: the controller decides what to do
+                conn.send(("err", f"{type(e).__name__}: {e}\n{traceback.format_exc()}"))
+        dist.destroy_process_group()
+    except Exception as e:
+        try:
+            conn.send(("err", f"worker {rank} failed to start: {e}\n{traceback.format_exc()}"))
+        except Exception:
+            pass
+
+
+class MultiprocExecutor:
+    def __init__(self, config: Config, timeout_s: float = 600.0):
+        import torch.multiprocessing as mp
+        self.config = config
+        self.world_size = config.world_size
+        self.timeout_s = timeout_s
+        use_cuda = config.device == "cuda" or (config.device == "auto" and torch.cuda.is_available())
+        if use_cuda and torch.cuda.device_count() < self.world_size:
+            raise ExecutorError(f"layout needs {self.world_size} GPUs, {torch.cuda.device_count()} visible")
+        ctx = mp.get_context("spawn")
+        port = _free_port()
+        self.procs, self.conns = [], []
+        cd = config.to_dict()
+        for r in range(self.world_size):
+            parent, child = ctx.Pipe()
+            p = ctx.Process(target=_worker_main, args=(r, self.world_size, cd, port, child, use_cuda), daemon=True)
+            p.start()
+            self.procs.append(p)
+            self.conns.append(parent)
+        for r in range(self.world_size):
+            self._recv(r)
+
+    def _recv(self, r: int):
+        conn, p = self.conns[r], self.procs[r]
+        waited = 0.0
+        while not conn.poll(0.5):
+            waited += 0.5
+            if not p.is_alive():
+                raise ExecutorError(f"worker {r} died (exit code {p.exitcode})")
+            if waited > self.timeout_s:
+                raise ExecutorError(f"worker {r} did not answer within {self.timeout_s}s")
+        try:
+            status, val = conn.recv()
+        except EOFError:
+            raise ExecutorError(f"worker {r} closed its pipe")
+        if status == "err":
+            raise ExecutorError(val)
+        return val
+
+    def collective_rpc(self, method: str, *args, **kw) -> List[Any]:
+        for c in self.conns:
+            c.send((method, args, kw))
+        return [self._recv(r) for r in range(self.world_size)]
+
+    def _batch_index(self, rank: int) -> int:
+        s = self.config.parallel_spec()
+        return (rank // (s.attention_sp * s.attention_tp)) % s.attention_dp
+
+    def run_batches(self, blobs: Sequence[bytes]) -> List[bytes]:
+        """blobs: one per attention-DP rank.  Returns one result per DP rank (from attention-TP rank 0)."""
+        s = self.config.parallel_spec()
+        for r, c in enumerate(self.conns):
+            c.send(("run_from_bytes", (blobs[self._batch_index(r)],), {}))
+        outs = [self._recv(r) for r in range(self.world_size)]
+        tp = s.attention_sp * s.attention_tp
+        per_stage = self.world_size // s.pp
+        last_stage = (s.pp - 1) * per_stage
+        return [outs[last_stage + d * tp] for d in range(s.attention_dp)]
+
+    def alive(self) -> List[bool]:
+        return [p.is_alive() for p in self.procs]
+
+    def shutdown(self):
+        for c, p in zip(self.conns, self.procs):
+            try:
+                if p.is_alive():
+                    c.send(None)
+            except Exception:
+                pass
+        for p in self.procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.terminate()
+        self.procs, self.conns = [], []
+
+
+def build_executor(config: Config):
+    backend = config.executor_backend
+    if backend == "auto":
+        backend = "inproc" if config.world_size == 1 else "mp"
+    if backend == "inproc":
+        if config.world_size != 1:
+            raise ValueError("the in-process executor runs exactly one worker")
+        return InprocExecutor(config)
+    if backend == "mp":
+        return MultiprocExecutor(config)
+    raise ValueError(f"unknown executor_backend {backend}")

@@ -1,0 +1,142 @@
+"""The engine controller: native scheduler + executor + the step loop.
+
+Parity: reference engine/llm_engine.py - _build_executor :16-25, __init__ :29-59, step :386-406,
+_run_scheduled_step :175-222, profiler fan-out :95-122, update_weights :124-148; engine/scheduler.py:19-143
+(SchedulerConfig from Config and the model's cache plan, token budget).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, Iterable, List, Optional
+
+from .._native import _core as C
+from ..config import Config
+from .executor import build_executor
+
+_ROUTING = {"round_robin": C.ROUND_ROBIN, "least_batch": C.LEAST_BATCH, "least_cache": C.LEAST_CACHE, "affinity": C.AFFINITY}
+_MODE = {"hybrid": C.MODE_HYBRID, "prefill": C.MODE_PREFILL, "decode": C.MODE_DECODE}
+
+
+def scheduler_token_budget(config: Config) -> int:
+    """Per-step prefill token budget; a prefill pipeline keeps `pp` micro-batches in flight."""
+    return config.max_num_batched_tokens * max(1, config.pp)
+
+
+def build_scheduler_config(config: Config, num_blocks: int, plan_bits: int) -> "C.SchedulerConfig":
+    sc = C.SchedulerConfig()
+    sc.num_blocks = num_blocks
+    sc.num_host_blocks = config.num_host_kvcache_blocks
+    sc.block_size = config.kvcache_block_size
+    sc.max_num_seqs = config.max_num_seqs
+    sc.max_num_batched_tokens = scheduler_token_budget(config)
+    sc.max_model_len = config.max_model_len
+    sc.attention_dp = config.attention_dp
+    sc.mode = _MODE[config.mode]
+    sc.num_speculative_tokens = config.num_speculative_tokens
+    sc.enable_prefix_caching = config.enable_prefix_caching
+    sc.enable_chunked_prefill = config.enable_chunked_prefill
+    sc.routing = _ROUTING[config.routing_strategy]
+    sc.cache_plan = plan_bits
+    sc.num_handoff_slots = config.max_num_seqs if config.num_speculative_tokens > 0 else 0
+    sc.num_hisparse_slots = config.max_num_seqs if config.enable_hisparse else 0
+    sc.eos_token_ids = config.model_config.eos_ids()
+    sc.engine_id = config.engine_id
+    return sc
+
+
+class LLMEngine:
+    def __init__(self, config: Config, executor=None):
+        self.config = config
+        self.executor = executor or build_executor(config)
+        self.executor.collective_rpc("init_model")
+        counts = self.executor.collective_rpc("profile_num_blocks")
+        self.num_blocks = int(min(counts))
+        if self.num_blocks < 1:
+            raise RuntimeError("no memory left for the KV cache; lower gpu_memory_utilization or the model size")
+        from ..runtime.cache import make_cache_plan
+        plan = make_cache_plan(config.model_config, config.resolved_kv_dtype(), config.kvcache_block_size, config.attention_tp,
+                               use_indexer=config.use_nsa())
+        self.scheduler = C.Scheduler(build_scheduler_config(config, self.num_blocks, plan.plan_bits()))
+        self.executor.collective_rpc("allocate_kvcache", self.num_blocks)
+        self._next_seq_id = 1
+        self.migrator = None   # set by the PD layer (disagg.KVMigrator)
+
+    # ---- requests ----------------------------------------------------------------------------
+    def add_request_payload(self, payload: bytes) -> int:
+        return self.scheduler.add_request_bytes(payload)
+
+    def add_request(self, prompt_token_ids: List[int], sampling_params=None, seq_id: Optional[int] = None, affinity_key: int = 0) -> int:
+        if seq_id is None:
+            seq_id = self._next_seq_id
+        self._next_seq_id = max(self._next_seq_id, seq_id) + 1
+        sp = sampling_params or C.SamplingParams()
+        return self.scheduler.add_request(C.RequestIn(seq_id, list(prompt_token_ids), sp, affinity_key))
+
+    def abort(self, seq_id: int) -> bool:
+        return self.scheduler.abort(seq_id)
+
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished()
+
+    # ---- the step ------------------------------------------------------------------------------
+    def step(self) -> List["C.StepOut"]:
+        res = self.scheduler.schedule()
+        if res.migrations:
+            self._run_migrations(res)
+        if not res.has_work:
+            return []
+        t0 = time.perf_counter()
+        blobs = self.scheduler.serialize_run_batches()
+        outs = self.executor.run_batches(blobs)
+        ms = (time.perf_counter() - t0) * 1e3
+        return self.scheduler.postprocess_runner_out_bytes(outs, ms)
+
+    def _run_migrations(self, res) -> None:
+        if self.migrator is None:
+            raise RuntimeError("received a migrated request but no KV migrator is attached to this engine")
+        blobs = self.scheduler.serialize_migrate_batches()
+        t0 = time.perf_counter()
+        ok_ids, bad_ids, nbytes = self.migrator.pull(blobs)
+        self.scheduler.record_transfer((time.perf_counter() - t0) * 1e3, nbytes)
+        if ok_ids:
+            self.scheduler.complete_migration(ok_ids, True)
+        if bad_ids:
+            self.scheduler.complete_migration(bad_ids, False)
+
+    # ---- PD ------------------------------------------------------------------------------------
+    def export_to_be_migrated(self):
+        return self.scheduler.export_to_be_migrated()
+
+    def free_to_be_migrated_ids(self, ids: Iterable[int]) -> int:
+        return self.scheduler.free_to_be_migrated(list(ids))
+
+    # ---- control -------------------------------------------------------------------------------
+    def start_profiler(self, trace_name: str = "trace") -> bool:
+        if not trace_name or any(c in trace_name for c in "/\\") or ".." in trace_name:
+            raise ValueError("trace name must be a plain file stem")
+        return all(self.executor.collective_rpc("start_profiler", trace_name))
+
+    def stop_profiler(self) -> List[Optional[str]]:
+        return self.executor.collective_rpc("stop_profiler")
+
+    def update_weights(self, named_tensors_or_path) -> int:
+        """Swap weights in place (live update).  Accepts a checkpoint directory or an iterable of (name, tensor)."""
+        return min(self.executor.collective_rpc("update_weights", named_tensors_or_path))
+
+    def metrics_prometheus(self) -> str:
+        return self.scheduler.metrics_prometheus()
+
+    def metrics_summary(self) -> Dict:
+        return self.scheduler.metrics_summary()
+
+    def engine_info(self) -> Dict:
+        c = self.config
+        return {"id": c.engine_id, "role": c.mode, "world_size": c.world_size, "num_blocks": self.num_blocks,
+                "host": c.host, "port": c.port, "max_num_seqs": c.max_num_seqs, "attention_dp": c.attention_dp,
+                "attention_sp": c.attention_sp, "attention_tp": c.attention_tp, "pp": c.pp,
+                "num_hidden_layers": c.model_config.num_hidden_layers, "block_size": c.kvcache_block_size,
+                "architecture": c.model_config.architecture, "kv_cache_dtype": c.resolved_kv_dtype(),
+                "mtp_num_kv_layers": max(1, c.model_config.num_nextn_predict_layers) if c.num_speculative_tokens else 0}
+
+    def shutdown(self):
+        self.executor.shutdown()

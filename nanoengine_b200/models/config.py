@@ -1,0 +1,176 @@
+"""Model architecture description shared by every model family, plus shape presets.
+
+The fields follow the HF ``config.json`` names of the DeepSeek-V3 / Qwen3-MoE families so a
+checkpoint directory can be read directly (the reference resolves the same fields through
+``transformers.AutoConfig`` in dlengine/config.py:273-884).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field, fields
+from typing import Any, Dict, List, Optional
+
+
+@dataclass
+class ModelConfig:
+    architecture: str = "DeepseekV3ForCausalLM"
+    vocab_size: int = 129280
+    hidden_size: int = 7168
+    num_hidden_layers: int = 61
+    num_attention_heads: int = 128
+    num_key_value_heads: int = 128
+    head_dim: int = 128                      # GQA families
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[Dict[str, Any]] = None
+    max_position_embeddings: int = 163840
+    tie_word_embeddings: bool = False
+    # dense MLP
+    intermediate_size: int = 18432
+    # MLA
+    q_lora_rank: Optional[int] = 1536
+    kv_lora_rank: int = 512
+    qk_nope_head_dim: int = 128
+    qk_rope_head_dim: int = 64
+    v_head_dim: int = 128
+    # MoE
+    n_routed_experts: int = 256
+    n_shared_experts: int = 1
+    num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 2048
+    first_k_dense_replace: int = 3
+    moe_layer_freq: int = 1
+    n_group: int = 8
+    topk_group: int = 4
+    norm_topk_prob: bool = True
+    routed_scaling_factor: float = 2.5
+    scoring_func: str = "sigmoid"            # "sigmoid" (DeepSeek-V3) or "softmax" (Qwen3-MoE, V2)
+    topk_method: str = "noaux_tc"
+    # GQA extras (Qwen3)
+    qk_norm: bool = False
+    attention_bias: bool = False
+    # DSA lightning indexer (DeepSeek-V3.2)
+    index_n_heads: int = 0
+    index_head_dim: int = 128
+    index_topk: int = 2048
+    # MTP
+    num_nextn_predict_layers: int = 0
+    # quantisation of linear / expert weights: None (use dtype) or "fp8" (e4m3, 128x128 block scales)
+    quant: Optional[str] = None
+    weight_block_size: List[int] = field(default_factory=lambda: [128, 128])
+    eos_token_id: Any = None
+    bos_token_id: Any = None
+
+    # ---- derived ---------------------------------------------------------------------------
+    @property
+    def is_mla(self) -> bool:
+        return self.architecture in ("DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM",
+                                     "GlmMoeDsaForCausalLM", "KimiK2ForCausalLM")
+
+    @property
+    def has_indexer(self) -> bool:
+        return self.index_n_heads > 0
+
+    @property
+    def qk_head_dim(self) -> int:
+        return self.qk_nope_head_dim + self.qk_rope_head_dim
+
+    @property
+    def mla_cache_dim(self) -> int:
+        return self.kv_lora_rank + self.qk_rope_head_dim
+
+    def is_moe_layer(self, layer_idx: int) -> bool:
+        if self.n_routed_experts <= 0:
+            return False
+        return layer_idx >= self.first_k_dense_replace and layer_idx % self.moe_layer_freq == 0
+
+    def eos_ids(self) -> List[int]:
+        e = self.eos_token_id
+        if e is None:
+            return []
+        return list(e) if isinstance(e, (list, tuple)) else [int(e)]
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "ModelConfig":
+        d = dict(d)
+        archs = d.pop("architectures", None)
+        if archs and "architecture" not in d:
+            d["architecture"] = archs[0]
+        q = d.pop("quantization_config", None)
+        if q and q.get("quant_method") == "fp8":
+            d["quant"] = "fp8"
+            d["weight_block_size"] = list(q.get("weight_block_size", [128, 128]))
+        # Qwen3-MoE spellings
+        if "num_experts" in d:
+            d["n_routed_experts"] = d.pop("num_experts")
+            d.setdefault("n_shared_experts", 0)
+            d.setdefault("first_k_dense_replace", 0)
+            d.setdefault("scoring_func", "softmax")
+            d.setdefault("n_group", 1)
+            d.setdefault("topk_group", 1)
+            d.setdefault("routed_scaling_factor", 1.0)
+            d.setdefault("qk_norm", True)
+        if d.get("architecture", "").startswith("Qwen3") and "n_routed_experts" not in d:
+            d.setdefault("n_routed_experts", 0)
+            d.setdefault("qk_norm", True)
+        known = {f.name for f in fields(cls)}
+        return cls(**{k: v for k, v in d.items() if k in known})
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = {f.name: getattr(self, f.name) for f in fields(self)}
+        d["architectures"] = [d.pop("architecture")]
+        if d.pop("quant") == "fp8":
+            d["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": d["weight_block_size"]}
+        d.pop("weight_block_size")
+        return d
+
+
+def tiny_deepseek_v3(**over) -> ModelConfig:
+    """The CPU plumbing shape: 2 layers (dense then MoE), hidden 256, 8 MLA heads, 8 experts top-2."""
+    c = ModelConfig(architecture="DeepseekV3ForCausalLM", vocab_size=1024, hidden_size=256, num_hidden_layers=2,
+                    num_attention_heads=8, num_key_value_heads=8, rms_norm_eps=1e-6, rope_theta=10000.0,
+                    max_position_embeddings=4096, intermediate_size=512, q_lora_rank=128, kv_lora_rank=64,
+                    qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=8, n_shared_experts=1,
+                    num_experts_per_tok=2, moe_intermediate_size=128, first_k_dense_replace=1, n_group=1, topk_group=1,
+                    norm_topk_prob=True, routed_scaling_factor=1.0, scoring_func="sigmoid", eos_token_id=None)
+    for k, v in over.items():
+        setattr(c, k, v)
+    return c
+
+
+def deepseek_v3(**over) -> ModelConfig:
+    """DeepSeek-V3 / R1 shape: 61 layers, 256 experts top-8 (8 groups / top-4), fp8 block-scaled weights."""
+    c = ModelConfig(quant="fp8", eos_token_id=1, num_nextn_predict_layers=1,
+                    rope_scaling={"type": "yarn", "factor": 40, "original_max_position_embeddings": 4096,
+                                  "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0})
+    for k, v in over.items():
+        setattr(c, k, v)
+    return c
+
+
+def deepseek_v32(**over) -> ModelConfig:
+    """DeepSeek-V3.2 shape: the V3 body plus a lightning indexer (64 heads x 128, top-2048) per layer."""
+    return deepseek_v3(architecture="DeepseekV32ForCausalLM", index_n_heads=64, index_head_dim=128, index_topk=2048, **over)
+
+
+def qwen3_235b(**over) -> ModelConfig:
+    """Qwen3-235B-A22B shape: 94 layers, GQA 64/4 heads with q/k norm, 128 experts top-8 softmax routing."""
+    c = ModelConfig(architecture="Qwen3MoeForCausalLM", vocab_size=151936, hidden_size=4096, num_hidden_layers=94,
+                    num_attention_heads=64, num_key_value_heads=4, head_dim=128, rope_theta=1e6,
+                    max_position_embeddings=40960, intermediate_size=12288, n_routed_experts=128, n_shared_experts=0,
+                    num_experts_per_tok=8, moe_intermediate_size=1536, first_k_dense_replace=0, n_group=1, topk_group=1,
+                    norm_topk_prob=True, routed_scaling_factor=1.0, scoring_func="softmax", qk_norm=True,
+                    q_lora_rank=None, eos_token_id=151645)
+    for k, v in over.items():
+        setattr(c, k, v)
+    return c
+
+
+PRESETS = {"tiny-deepseek-v3": tiny_deepseek_v3, "deepseek-v3": deepseek_v3, "deepseek-v3.2": deepseek_v32,
+           "qwen3-235b-a22b": qwen3_235b}

@@ -1,0 +1,149 @@
+"""Building blocks shared by the model families: quantisable linears, norms, SwiGLU MLP, routed experts.
+
+Parity: reference runtime/layers/base_backend.py:91-211 (linear / experts factories),
+layers/backends/linear/deep_gemm.py (fp8 block-scaled linears), layers/backends/experts/deep_gemm.py:138-175
+(stacked expert weights ``gate_up_proj [E_local, 2I, H]``, ``down_proj [E_local, H, I]``, scales per 128x128
+block), layers/layernorm.py:16-108, layers/activation.py:29-112.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..ops import reference as ref
+from ..parallel.dist import get_dist_context
+
+
+def _ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+class QLinear(nn.Module):
+    """y = x W^T with W [out, in] in the activation dtype or in fp8 e4m3 with 128x128 block scales."""
+
+    def __init__(self, in_features: int, out_features: int, dtype, device, quant: Optional[str] = None, bias: bool = False):
+        super().__init__()
+        self.in_features, self.out_features, self.quant = in_features, out_features, quant
+        if quant == "fp8":
+            self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=torch.float8_e4m3fn, device=device), requires_grad=False)
+            self.weight_scale_inv = nn.Parameter(torch.ones(_ceil_div(out_features, 128), _ceil_div(in_features, 128),
+                                                            dtype=torch.float32, device=device), requires_grad=False)
+        else:
+            self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device), requires_grad=False)
+            self.weight_scale_inv = None
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device), requires_grad=False) if bias else None
+
+    def forward(self, x):
+        return ops.linear(x, self.weight, self.weight_scale_inv, self.bias)
+
+    @torch.no_grad()
+    def init_random(self, gen: torch.Generator, std: float = 0.02):
+        w = torch.empty(self.out_features, self.in_features, dtype=torch.float32, device=self.weight.device)
+        w.normal_(0.0, std, generator=gen)
+        self.set_weight(w)
+
+    @torch.no_grad()
+    def set_weight(self, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None):
+        """Accepts a high-precision weight (quantised here if needed) or an fp8 weight with its scales."""
+        if self.quant == "fp8":
+            if w.dtype == torch.float8_e4m3fn:
+                self.weight.copy_(w)
+                self.weight_scale_inv.copy_(scale_inv)
+            else:
+                q, s = ref.quant_fp8_block(w.to(self.weight.device))
+                self.weight.copy_(q)
+                self.weight_scale_inv.copy_(s)
+        else:
+            if w.dtype == torch.float8_e4m3fn:
+                w = ref.dequant_fp8_block(w, scale_inv)
+            self.weight.copy_(w.to(self.weight.dtype))
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, dtype, device):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x, residual=None):
+        """Without residual: y.  With residual: (y, x + residual) - the fused add + norm used between blocks."""
+        if residual is None:
+            return ops.rmsnorm(x, self.weight, self.eps)
+        return ops.add_rmsnorm(x, residual, self.weight, self.eps)
+
+
+class SwiGLUMLP(nn.Module):
+    """Dense SwiGLU MLP with gate and up projections merged into one GEMM."""
+
+    def __init__(self, hidden: int, inter: int, dtype, device, quant=None):
+        super().__init__()
+        self.gate_up_proj = QLinear(hidden, 2 * inter, dtype, device, quant)
+        self.down_proj = QLinear(inter, hidden, dtype, device, quant)
+
+    def forward(self, x):
+        return self.down_proj(ops.silu_and_mul(self.gate_up_proj(x)))
+
+    def init_random(self, gen):
+        self.gate_up_proj.init_random(gen)
+        self.down_proj.init_random(gen)
+
+
+class RoutedExperts(nn.Module):
+    """The experts this rank owns: ids [ep_rank*E_local, (ep_rank+1)*E_local), stacked for grouped GEMMs."""
+
+    def __init__(self, num_experts: int, hidden: int, inter: int, dtype, device, quant=None):
+        super().__init__()
+        d = get_dist_context()
+        assert num_experts % d.ep_size == 0, "experts must divide evenly over the EP group"
+        self.num_experts, self.hidden, self.inter, self.quant = num_experts, hidden, inter, quant
+        self.num_local = num_experts // d.ep_size
+        self.expert_offset = d.ep_rank * self.num_local
+        wdt = torch.float8_e4m3fn if quant == "fp8" else dtype
+        E = self.num_local
+        self.gate_up_proj = nn.Parameter(torch.empty(E, 2 * inter, hidden, dtype=wdt, device=device), requires_grad=False)
+        self.down_proj = nn.Parameter(torch.empty(E, hidden, inter, dtype=wdt, device=device), requires_grad=False)
+        if quant == "fp8":
+            self.gate_up_scale = nn.Parameter(torch.ones(E, _ceil_div(2 * inter, 128), _ceil_div(hidden, 128), dtype=torch.float32, device=device), requires_grad=False)
+            self.down_scale = nn.Parameter(torch.ones(E, _ceil_div(hidden, 128), _ceil_div(inter, 128), dtype=torch.float32, device=device), requires_grad=False)
+        else:
+            self.gate_up_scale = self.down_scale = None
+
+    def owns(self, expert_id: int) -> bool:
+        return self.expert_offset <= expert_id < self.expert_offset + self.num_local
+
+    def forward(self, x, topk_idx, topk_w):
+        """Local part of the routed output for the tokens given (weights applied, zero rows where no expert is local)."""
+        return ops.moe_experts(x, topk_idx, topk_w, self.gate_up_proj, self.down_proj, self.gate_up_scale, self.down_scale,
+                               self.expert_offset)
+
+    @torch.no_grad()
+    def set_expert(self, local_idx: int, which: str, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None):
+        """which in {gate, up, down}; w is one expert's HF-layout matrix (fp8 + scales, or high precision)."""
+        I = self.inter
+        tgt, tscale, rows = {
+            "gate": (self.gate_up_proj, self.gate_up_scale, slice(0, I)),
+            "up": (self.gate_up_proj, self.gate_up_scale, slice(I, 2 * I)),
+            "down": (self.down_proj, self.down_scale, slice(0, self.hidden)),
+        }[which]
+        if self.quant == "fp8":
+            if w.dtype != torch.float8_e4m3fn:
+                w, scale_inv = ref.quant_fp8_block(w.to(tgt.device))
+            tgt[local_idx, rows].copy_(w)
+            srows = slice(rows.start // 128, _ceil_div(rows.stop, 128))
+            tscale[local_idx, srows].copy_(scale_inv)
+        else:
+            if w.dtype == torch.float8_e4m3fn:
+                w = ref.dequant_fp8_block(w, scale_inv)
+            tgt[local_idx, rows].copy_(w.to(tgt.dtype))
+
+    @torch.no_grad()
+    def init_random(self, gen, std: float = 0.02):
+        dev = self.gate_up_proj.device
+        for e in range(self.num_local):
+            for which, shape in (("gate", (self.inter, self.hidden)), ("up", (self.inter, self.hidden)), ("down", (self.hidden, self.inter))):
+                w = torch.empty(*shape, dtype=torch.float32, device=dev).normal_(0.0, std, generator=gen)
+                self.set_expert(e, which, w)

@@ -1,0 +1,43 @@
+"""Architecture name -> model class.  Parity: reference runtime/models/registry.py:78-100."""
+from __future__ import annotations
+
+from typing import Callable, Dict
+
+_REGISTRY: Dict[str, Callable] = {}
+
+
+def register(*names):
+    def deco(fn):
+        for n in names:
+            _REGISTRY[n] = fn
+        return fn
+    return deco
+
+
+def _deepseek():
+    from .deepseek import DeepseekV3ForCausalLM
+    return DeepseekV3ForCausalLM
+
+
+def _qwen3_moe():
+    from .qwen3 import Qwen3MoeForCausalLM
+    return Qwen3MoeForCausalLM
+
+
+_LAZY = {
+    "DeepseekV2ForCausalLM": _deepseek, "DeepseekV3ForCausalLM": _deepseek, "DeepseekV32ForCausalLM": _deepseek,
+    "GlmMoeDsaForCausalLM": _deepseek, "KimiK2ForCausalLM": _deepseek,
+    "Qwen3MoeForCausalLM": _qwen3_moe, "Qwen3ForCausalLM": _qwen3_moe,
+}
+
+
+def supported_architectures():
+    return sorted(set(_LAZY) | set(_REGISTRY))
+
+
+def get_model_class(architecture: str):
+    if architecture in _REGISTRY:
+        return _REGISTRY[architecture]
+    if architecture in _LAZY:
+        return _LAZY[architecture]()
+    raise ValueError(f"unsupported architecture {architecture}; supported: {supported_architectures()}")

@@ -1,0 +1,336 @@
+"""HF-layout weight handling: name mapping into the fused/stacked parameters of the models, a random
+generator that emits tensors under the same names (so synthetic benchmarks exercise the real loading
+path), safetensors shard iteration with expert-parallel pre-filtering, and a tiny checkpoint writer.
+
+Parity: reference runtime/runner/loader.py:212-250 (iterate_weights), :34-53 (EP filter before the tensor
+is read), :362-494 (per-expert -> stacked tensors), :90-119 (fp8 block dequant);
+models/deepseek_v2/deepseek_v2_loader.py:36-121 (kv_b_proj -> kc/vc), :124-270.
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+import re
+import zlib
+from typing import Callable, Dict, Iterable, Iterator, Optional, Tuple
+
+import torch
+
+from ..parallel.dist import get_dist_context
+from .config import ModelConfig
+
+_EXPERT_RE = re.compile(r"\.mlp\.experts\.(\d+)\.")
+_LAYER_RE = re.compile(r"^model\.layers\.(\d+)\.")
+
+
+def expert_owner_filter(cfg: ModelConfig, ep_size: int, ep_rank: int, layer_range=None) -> Callable[[str], bool]:
+    """True for tensors this rank must read: its own experts and (with PP) its own layers."""
+    per = max(1, cfg.n_routed_experts // max(1, ep_size)) if cfg.n_routed_experts else 1
+
+    def keep(name: str) -> bool:
+        m = _LAYER_RE.match(name)
+        if m and layer_range is not None:
+            li = int(m.group(1))
+            if li < cfg.num_hidden_layers and not (layer_range[0] <= li < layer_range[1]):
+                return False
+        e = _EXPERT_RE.search(name)
+        if e is not None:
+            return int(e.group(1)) // per == ep_rank
+        return True
+
+    return keep
+
+
+def iterate_safetensors(path: str, keep: Optional[Callable[[str], bool]] = None, device="cpu") -> Iterator[Tuple[str, torch.Tensor]]:
+    """Yield (name, tensor) from every *.safetensors shard; `keep` is consulted before a tensor is read."""
+    from safetensors import safe_open
+    for f in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
+        with safe_open(f, framework="pt", device=str(device)) as sf:
+            for name in sf.keys():
+                if keep is None or keep(name):
+                    yield name, sf.get_tensor(name)
+
+
+def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tuple[int, ...]]:
+    """Every tensor name of an HF-layout checkpoint of this architecture with its (high-precision) shape."""
+    H, V = cfg.hidden_size, cfg.vocab_size
+    out: Dict[str, Tuple[int, ...]] = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,), "lm_head.weight": (V, H)}
+
+    def attn(p):
+        if cfg.is_mla:
+            nh, R, rope, nope, v = cfg.num_attention_heads, cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.qk_nope_head_dim, cfg.v_head_dim
+            if cfg.q_lora_rank:
+                out[p + "q_a_proj.weight"] = (cfg.q_lora_rank, H)
+                out[p + "q_a_layernorm.weight"] = (cfg.q_lora_rank,)
+                out[p + "q_b_proj.weight"] = (nh * (nope + rope), cfg.q_lora_rank)
+            else:
+                out[p + "q_proj.weight"] = (nh * (nope + rope), H)
+            out[p + "kv_a_proj_with_mqa.weight"] = (R + rope, H)
+            out[p + "kv_a_layernorm.weight"] = (R,)
+            out[p + "kv_b_proj.weight"] = (nh * (nope + v), R)
+            out[p + "o_proj.weight"] = (H, nh * v)
+            if cfg.has_indexer:
+                out[p + "indexer.wq_b.weight"] = (cfg.index_n_heads * cfg.index_head_dim, cfg.q_lora_rank or H)
+                out[p + "indexer.wk.weight"] = (cfg.index_head_dim, H)
+                out[p + "indexer.k_norm.weight"] = (cfg.index_head_dim,)
+                out[p + "indexer.k_norm.bias"] = (cfg.index_head_dim,)
+                out[p + "indexer.weights_proj.weight"] = (cfg.index_n_heads, H)
+        else:
+            hd = cfg.head_dim
+            out[p + "q_proj.weight"] = (cfg.num_attention_heads * hd, H)
+            out[p + "k_proj.weight"] = (cfg.num_key_value_heads * hd, H)
+            out[p + "v_proj.weight"] = (cfg.num_key_value_heads * hd, H)
+            out[p + "o_proj.weight"] = (H, cfg.num_attention_heads * hd)
+            if cfg.qk_norm:
+                out[p + "q_norm.weight"] = (hd,)
+                out[p + "k_norm.weight"] = (hd,)
+
+    def layer(i, moe):
+        p = f"model.layers.{i}."
+        out[p + "input_layernorm.weight"] = (H,)
+        out[p + "post_attention_layernorm.weight"] = (H,)
+        attn(p + "self_attn.")
+        if moe:
+            I = cfg.moe_intermediate_size
+            out[p + "mlp.gate.weight"] = (cfg.n_routed_experts, H)
+            if cfg.topk_method == "noaux_tc" and cfg.scoring_func == "sigmoid":
+                out[p + "mlp.gate.e_score_correction_bias"] = (cfg.n_routed_experts,)
+            for e in range(cfg.n_routed_experts):
+                out[p + f"mlp.experts.{e}.gate_proj.weight"] = (I, H)
+                out[p + f"mlp.experts.{e}.up_proj.weight"] = (I, H)
+                out[p + f"mlp.experts.{e}.down_proj.weight"] = (H, I)
+            if cfg.n_shared_experts:
+                Is = I * cfg.n_shared_experts
+                out[p + "mlp.shared_experts.gate_proj.weight"] = (Is, H)
+                out[p + "mlp.shared_experts.up_proj.weight"] = (Is, H)
+                out[p + "mlp.shared_experts.down_proj.weight"] = (H, Is)
+        else:
+            I = cfg.intermediate_size
+            out[p + "mlp.gate_proj.weight"] = (I, H)
+            out[p + "mlp.up_proj.weight"] = (I, H)
+            out[p + "mlp.down_proj.weight"] = (H, I)
+
+    for i in range(cfg.num_hidden_layers):
+        layer(i, cfg.is_moe_layer(i))
+    if include_mtp:
+        for k in range(cfg.num_nextn_predict_layers):
+            i = cfg.num_hidden_layers + k
+            layer(i, cfg.n_routed_experts > 0)
+            p = f"model.layers.{i}."
+            out[p + "enorm.weight"] = (H,)
+            out[p + "hnorm.weight"] = (H,)
+            out[p + "eh_proj.weight"] = (H, 2 * H)
+            out[p + "shared_head.norm.weight"] = (H,)
+    return out
+
+
+def random_hf_weights(cfg: ModelConfig, seed: int = 0, device="cpu", keep: Optional[Callable[[str], bool]] = None,
+                      include_mtp: bool = False, std: float = 0.02) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Random-init tensors under HF names.  Each tensor draws from its own generator seeded by (seed, name),
+    so the values do not depend on which rank generates them or on the parallel layout."""
+    dev = torch.device(device)
+    for name, shape in hf_param_shapes(cfg, include_mtp).items():
+        if keep is not None and not keep(name):
+            continue
+        g = torch.Generator(device=dev)
+        g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFF)
+        if name.endswith("norm.weight") and "k_norm" not in name or name.endswith("layernorm.weight"):
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        elif name.endswith("e_score_correction_bias") or name.endswith(".bias"):
+            t = 0.01 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        elif name.endswith("k_norm.weight"):
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        else:
+            t = std * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        yield name, t
+
+
+def _mlp_target(mod, leaf: str):
+    return {"gate_proj": ("gate_up", 0), "up_proj": ("gate_up", 1), "down_proj": ("down", 0)}[leaf]
+
+
+class _Pending:
+    """Collects (weight, weight_scale_inv) pairs and halves of merged matrices until they are complete."""
+
+    def __init__(self):
+        self.w: Dict[str, torch.Tensor] = {}
+        self.s: Dict[str, torch.Tensor] = {}
+
+    def take(self, key):
+        return self.w.pop(key), self.s.pop(key, None)
+
+
+def _deq(w, s):
+    from ..ops import reference as ref
+    return ref.dequant_fp8_block(w, s) if w.dtype == torch.float8_e4m3fn else w.float()
+
+
+def load_deepseek_weights(model, weights: Iterable[Tuple[str, torch.Tensor]], mtp=None) -> int:
+    """Feed HF-named tensors into a DeepseekV3ForCausalLM (and optionally its MTP head).  Returns tensors consumed.
+
+    fp8 checkpoints deliver ``<name>.weight`` (e4m3) and ``<name>.weight_scale_inv``; both orders are accepted.
+    Merged parameters (gate_up, qkv_a) are assembled from their parts; parts that arrive in fp8 for a merged
+    fp8 target are copied block-wise with their scales, anything else goes through fp32.
+    """
+    cfg: ModelConfig = model.cfg
+    n = 0
+    fp8 = torch.float8_e4m3fn
+    wbuf: Dict[str, torch.Tensor] = {}
+    sbuf: Dict[str, torch.Tensor] = {}
+    groups: Dict[str, Dict[str, Tuple[torch.Tensor, Optional[torch.Tensor]]]] = {}
+    quant_names = set()
+
+    def layer_of(i):
+        if i < cfg.num_hidden_layers:
+            return model.model.layers[str(i)] if str(i) in model.model.layers else None
+        return mtp.blocks[i - cfg.num_hidden_layers] if mtp is not None else None
+
+    def merged_set(lin, parts):
+        """parts: list of (w, s) in row order -> one QLinear."""
+        if lin.quant == "fp8" and all(w.dtype == fp8 for w, _ in parts) and all(w.shape[0] % 128 == 0 for w, _ in parts[:-1]):
+            lin.set_weight(torch.cat([w for w, _ in parts], 0), torch.cat([s for _, s in parts], 0))
+        else:
+            lin.set_weight(torch.cat([_deq(w, s) for w, s in parts], 0))
+
+    def place(base: str, w: torch.Tensor, s: Optional[torch.Tensor]):
+        nonlocal n
+        n += 1
+        if base == "model.embed_tokens":
+            if model.model.embed_tokens is not None:
+                model.model.embed_tokens.weight.copy_(w.to(model.model.embed_tokens.weight.dtype))
+            return
+        if base == "lm_head":
+            model.lm_head.weight.copy_(w.to(model.lm_head.weight.dtype)); return
+        if base == "model.norm":
+            if model.model.norm is not None:
+                model.model.norm.weight.copy_(w.to(model.model.norm.weight.dtype))
+            return
+        m = _LAYER_RE.match(base + ".")
+        if not m:
+            return
+        li = int(m.group(1))
+        L = layer_of(li)
+        if L is None:
+            n -= 1
+            return
+        rest = base[m.end():]
+        if li >= cfg.num_hidden_layers and mtp is not None:
+            k = li - cfg.num_hidden_layers
+            if rest in ("enorm", "hnorm"):
+                getattr(mtp, rest)[k].weight.copy_(w.to(mtp.enorm[k].weight.dtype)); return
+            if rest == "eh_proj":
+                mtp.eh_proj[k].set_weight(_deq(w, s)); return
+            if rest == "shared_head.norm":
+                mtp.final_norm[k].weight.copy_(w.to(mtp.final_norm[k].weight.dtype)); return
+            if rest.startswith("shared_head.") or rest == "embed_tokens":
+                return  # shared with the target model
+        if rest in ("input_layernorm", "post_attention_layernorm"):
+            getattr(L, rest).weight.copy_(w.to(getattr(L, rest).weight.dtype)); return
+        if rest.startswith("self_attn."):
+            A = L.self_attn
+            leaf = rest[len("self_attn."):]
+            if leaf in ("q_a_layernorm", "kv_a_layernorm"):
+                getattr(A, leaf).weight.copy_(w.to(getattr(A, leaf).weight.dtype)); return
+            if leaf == "kv_b_proj":
+                A.set_kv_b(w, s); return
+            if leaf in ("q_b_proj", "o_proj", "q_proj") or (leaf == "kv_a_proj_with_mqa" and not A.q_lora):
+                getattr(A, leaf).set_weight(w, s); return
+            if leaf in ("q_a_proj", "kv_a_proj_with_mqa"):
+                g = groups.setdefault(f"{li}.qkv_a", {})
+                g[leaf] = (w, s)
+                if len(g) == 2:
+                    merged_set(A.qkv_a_proj, [g["q_a_proj"], g["kv_a_proj_with_mqa"]]); groups.pop(f"{li}.qkv_a")
+                return
+            if leaf.startswith("indexer.") and A.indexer is not None:
+                A.indexer.load(leaf[len("indexer."):], w, s); return
+            return
+        if rest.startswith("mlp."):
+            leaf = rest[len("mlp."):]
+            M = L.mlp
+            if leaf == "gate":
+                M.gate.weight.copy_(w.float()); return
+            e = re.match(r"experts\.(\d+)\.(gate_proj|up_proj|down_proj)$", leaf)
+            if e:
+                eid, which = int(e.group(1)), e.group(2)[:-5]
+                ex = M.experts
+                if ex.owns(eid):
+                    ex.set_expert(eid - ex.expert_offset, which, w, s)
+                else:
+                    n -= 1
+                return
+            tgt = M.shared_experts if leaf.startswith("shared_experts.") else M
+            leaf2 = leaf.split(".")[-1]
+            if leaf2 == "down_proj":
+                tgt.down_proj.set_weight(w, s); return
+            g = groups.setdefault(f"{li}.{'s' if tgt is not M else 'd'}.gate_up", {})
+            g[leaf2] = (w, s)
+            if len(g) == 2:
+                merged_set(tgt.gate_up_proj, [g["gate_proj"], g["up_proj"]]); groups.pop(f"{li}.{'s' if tgt is not M else 'd'}.gate_up")
+            return
+
+    with torch.no_grad():
+        for name, t in weights:
+            if name.endswith(".e_score_correction_bias"):
+                li = int(_LAYER_RE.match(name).group(1))
+                L = layer_of(li)
+                if L is not None and getattr(L.mlp, "gate", None) is not None and L.mlp.gate.e_score_correction_bias is not None:
+                    L.mlp.gate.e_score_correction_bias.copy_(t.float()); n += 1
+                continue
+            if name.endswith("k_norm.bias"):
+                li = int(_LAYER_RE.match(name).group(1))
+                L = layer_of(li)
+                if L is not None and L.self_attn.indexer is not None:
+                    L.self_attn.indexer.load("k_norm.bias", t, None); n += 1
+                continue
+            if name.endswith(".weight_scale_inv"):
+                base = name[: -len(".weight_scale_inv")]
+                if base in wbuf:
+                    place(base, wbuf.pop(base), t)
+                else:
+                    sbuf[base] = t
+                continue
+            if not name.endswith(".weight"):
+                continue
+            base = name[: -len(".weight")]
+            if t.dtype == fp8:
+                if base in sbuf:
+                    place(base, t, sbuf.pop(base))
+                else:
+                    wbuf[base] = t
+            else:
+                place(base, t, None)
+    if wbuf or groups:
+        raise ValueError(f"incomplete checkpoint: {list(wbuf)[:3]} {list(groups)[:3]}")
+    return n
+
+
+def save_hf_checkpoint(path: str, cfg: ModelConfig, weights: Iterable[Tuple[str, torch.Tensor]], quantize_fp8: bool = False,
+                       shard_bytes: int = 1 << 30) -> None:
+    """Write a small HF-layout checkpoint (config.json + safetensors shards); used by tests and examples."""
+    from safetensors.torch import save_file
+    from ..ops import reference as ref
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f, indent=1)
+    shard, size, idx = {}, 0, 0
+
+    def flush():
+        nonlocal shard, size, idx
+        if shard:
+            save_file(shard, os.path.join(path, f"model-{idx:05d}.safetensors"))
+            shard, size, idx = {}, 0, idx + 1
+
+    for name, t in weights:
+        t = t.detach().cpu()
+        big = t.dim() == 2 and name.endswith("proj.weight") and "indexer" not in name and "eh_proj" not in name
+        if quantize_fp8 and big:
+            q, s = ref.quant_fp8_block(t)
+            shard[name] = q.contiguous(); shard[name + "_scale_inv"] = s.contiguous()
+            size += q.numel() + s.numel() * 4
+        else:
+            shard[name] = t.to(torch.bfloat16).contiguous() if t.dim() >= 1 else t
+            size += t.numel() * 2
+        if size >= shard_bytes:
+            flush()
+    flush()

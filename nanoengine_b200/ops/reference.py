@@ -1,0 +1,368 @@
+"""Plain-PyTorch statements of every operator.
+
+These are the numerical oracles for the CUDA kernels (tests compare each kernel against the
+fp32 form here) and the execution path on CPU, where the engine runs its plumbing tests.
+They play the role of the reference's generic back-ends (layers/backends/linear/generic.py,
+experts/generic.py:237-273, attention/base.py:451-525 SDPA reference, layers/sampler.py:18-52).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+FP8_MAX = 448.0
+FP8 = torch.float8_e4m3fn
+
+
+# ---- norms -------------------------------------------------------------------------------------
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y * w.float()).to(x.dtype)
+
+
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float):
+    """residual_out = x + residual (in the activation dtype); y = rmsnorm(residual_out)."""
+    if residual is not None:
+        x = (x.float() + residual.float()).to(x.dtype)
+    return rmsnorm(x, w, eps), x
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    return F.layer_norm(x.float(), (x.shape[-1],), w.float(), None if b is None else b.float(), eps).to(x.dtype)
+
+
+# ---- fp8 block quantisation ----------------------------------------------------------------------
+def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row, per-128-column groups: q = x / s (e4m3), s = amax/448 (optionally rounded up to 2^k)."""
+    T, K = x.shape
+    assert K % 128 == 0
+    g = x.float().view(T, K // 128, 128)
+    amax = g.abs().amax(-1).clamp_min(1e-10)
+    s = amax / FP8_MAX
+    if ue8m0:
+        s = torch.exp2(torch.ceil(torch.log2(s)))
+    q = (g / s.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(FP8).view(T, K)
+    return q, s
+
+
+def dequant_fp8_1x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    T, K = q.shape
+    return (q.float().view(T, K // 128, 128) * s.unsqueeze(-1)).view(T, K)
+
+
+def quant_fp8_block(w: torch.Tensor, block: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """128x128 weight blocks: returns (w_fp8, weight_scale_inv) with w ~= w_fp8 * scale_inv."""
+    *lead, N, K = w.shape
+    pn, pk = (-N) % block, (-K) % block
+    wf = F.pad(w.float(), (0, pk, 0, pn))
+    Np, Kp = N + pn, K + pk
+    g = wf.view(*lead, Np // block, block, Kp // block, block)
+    amax = g.abs().amax(dim=(-3, -1)).clamp_min(1e-10)
+    s = amax / FP8_MAX
+    q = (g / s.unsqueeze(-1).unsqueeze(-3)).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    q = q.view(*lead, Np, Kp)[..., :N, :K].contiguous()
+    return q, s
+
+
+def dequant_fp8_block(q: torch.Tensor, s: torch.Tensor, block: int = 128) -> torch.Tensor:
+    *lead, N, K = q.shape
+    se = s.repeat_interleave(block, -2).repeat_interleave(block, -1)[..., :N, :K]
+    return q.float() * se
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, bias=None) -> torch.Tensor:
+    """y = x @ w^T.  fp8 weights follow the DeepSeek recipe: activations quantised 1x128, fp32 accumulate."""
+    if w.dtype == FP8:
+        xq, xs = quant_fp8_1x128(x.reshape(-1, x.shape[-1]))
+        y = dequant_fp8_1x128(xq, xs) @ dequant_fp8_block(w, w_scale).t()
+        y = y.view(*x.shape[:-1], w.shape[0]).to(x.dtype)
+    else:
+        y = F.linear(x, w)
+    if bias is not None:
+        y = y + bias
+    return y
+
+
+# ---- rotary ------------------------------------------------------------------------------------
+def yarn_mscale(scale: float, mscale: float) -> float:
+    return 1.0 if scale <= 1 else 0.1 * mscale * math.log(scale) + 1.0
+
+
+def rope_inv_freq(dim: int, theta: float, scaling: Optional[dict]) -> Tuple[torch.Tensor, float]:
+    """Inverse frequencies (+ attention-magnitude factor) for plain RoPE and YaRN."""
+    inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    if not scaling or scaling.get("type", scaling.get("rope_type")) != "yarn":
+        return inv, 1.0
+    factor = float(scaling["factor"])
+    orig = int(scaling["original_max_position_embeddings"])
+    beta_fast, beta_slow = float(scaling.get("beta_fast", 32)), float(scaling.get("beta_slow", 1))
+
+    def corr_dim(n_rot):
+        return dim * math.log(orig / (n_rot * 2 * math.pi)) / (2 * math.log(theta))
+
+    low = max(math.floor(corr_dim(beta_fast)), 0)
+    high = min(math.ceil(corr_dim(beta_slow)), dim - 1)
+    ramp = ((torch.arange(dim // 2, dtype=torch.float32) - low) / max(high - low, 1e-3)).clamp(0, 1)
+    inv_mask = 1.0 - ramp
+    inv = inv / factor * (1 - inv_mask) + inv * inv_mask
+    m = yarn_mscale(factor, float(scaling.get("mscale", 1.0))) / yarn_mscale(factor, float(scaling.get("mscale_all_dim", 0.0)))
+    return inv, m
+
+
+def rope_cos_sin_cache(dim: int, max_pos: int, theta: float, scaling: Optional[dict] = None) -> torch.Tensor:
+    """[max_pos, dim] fp32: first half cos, second half sin (already multiplied by the YaRN magnitude)."""
+    inv, m = rope_inv_freq(dim, theta, scaling)
+    f = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
+    return torch.cat([f.cos() * m, f.sin() * m], -1)
+
+
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """x [T, ..., D].  interleaved=True rotates pairs (2i, 2i+1) (DeepSeek MLA); False rotates (i, i+D/2) (Qwen)."""
+    D = x.shape[-1]
+    cs = cache[positions.long()]
+    cos, sin = cs[:, : D // 2], cs[:, D // 2:]
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [D // 2]
+    cos, sin = cos.view(shape), sin.view(shape)
+    xf = x.float()
+    if interleaved:
+        a, b = xf[..., 0::2], xf[..., 1::2]
+        out = torch.stack([a * cos - b * sin, b * cos + a * sin], -1).flatten(-2)
+    else:
+        a, b = xf[..., : D // 2], xf[..., D // 2:]
+        out = torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+    return out.to(x.dtype)
+
+
+# ---- KV cache ------------------------------------------------------------------------------------
+def mla_kv_store(cache: torch.Tensor, slot_mapping: torch.Tensor, ckv: torch.Tensor, k_pe: torch.Tensor) -> None:
+    """cache [blocks, block_size, R+rope]; row = [normed latent | rotated rope key].
+    An fp8 cache stores the clamped e4m3 cast of all R+rope values with no scale
+    (reference triton/hopper/fp8_utils.py:275-281)."""
+    row = torch.cat([ckv, k_pe], -1)
+    flat = cache.view(-1, cache.shape[-1])
+    if cache.dtype == FP8:
+        row = row.float().clamp(-FP8_MAX, FP8_MAX).to(FP8)
+        flat.view(torch.uint8)[slot_mapping.long()] = row.view(torch.uint8)
+    else:
+        flat[slot_mapping.long()] = row.to(cache.dtype)
+
+
+def gqa_kv_store(k_cache, v_cache, slot_mapping, k, v) -> None:
+    """k_cache/v_cache [blocks, block_size, kv_heads, head_dim]."""
+    k_cache.view(-1, *k_cache.shape[2:])[slot_mapping.long()] = k.to(k_cache.dtype)
+    v_cache.view(-1, *v_cache.shape[2:])[slot_mapping.long()] = v.to(v_cache.dtype)
+
+
+def _gather_rows(cache: torch.Tensor, block_table: torch.Tensor, n: int) -> torch.Tensor:
+    bs = cache.shape[1]
+    nb = (n + bs - 1) // bs
+    rows = cache[block_table[:nb].long()].reshape(nb * bs, *cache.shape[2:])[:n]
+    return rows.float() if rows.dtype != FP8 else rows.float()
+
+
+# ---- attention -----------------------------------------------------------------------------------
+def mla_attention_paged(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                        context_lens: torch.Tensor, scale: float, kv_lora_rank: int,
+                        sparse_indices: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Absorbed MLA over the paged latent cache, causal within each sequence.
+
+    q [T, H, R+rope] (already absorbed with W_UK and rotated); returns the latent output [T, H, R].
+    Query token t of sequence i sits at absolute position context_len_i - q_len_i + (t - cu_q[i]).
+    ``sparse_indices`` [T, topk] (physical token slots, -1 = none) restricts the keys (DSA).
+    With an fp8 cache the query is clamped and cast to e4m3 too (reference mla/trtllm.py:93-204).
+    """
+    T, H, D = q.shape
+    out = torch.zeros(T, H, kv_lora_rank, dtype=torch.float32, device=q.device)
+    qf = q.float()
+    if cache.dtype == FP8:
+        qf = qf.clamp(-FP8_MAX, FP8_MAX).to(FP8).float()
+    flat = cache.view(-1, cache.shape[-1])
+    B = cu_seqlens_q.numel() - 1
+    for i in range(B):
+        lo, hi = int(cu_seqlens_q[i]), int(cu_seqlens_q[i + 1])
+        if hi == lo:
+            continue
+        n = int(context_lens[i])
+        ql = hi - lo
+        if sparse_indices is None:
+            kv = _gather_rows(cache, block_tables[i], n)                      # [n, D]
+            s = torch.einsum("thd,nd->thn", qf[lo:hi], kv) * scale
+            pos = torch.arange(n - ql, n, device=q.device).view(ql, 1, 1)
+            mask = torch.arange(n, device=q.device).view(1, 1, n) > pos
+            s = s.masked_fill(mask, float("-inf"))
+            p = torch.softmax(s, -1)
+            out[lo:hi] = torch.einsum("thn,nr->thr", p, kv[:, :kv_lora_rank])
+        else:
+            for t in range(lo, hi):
+                idx = sparse_indices[t]
+                idx = idx[idx >= 0].long()
+                kv = flat[idx].float()
+                s = torch.einsum("hd,nd->hn", qf[t], kv) * scale
+                p = torch.softmax(s, -1)
+                out[t] = torch.einsum("hn,nr->hr", p, kv[:, :kv_lora_rank])
+    return out.to(q.dtype)
+
+
+def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale) -> torch.Tensor:
+    """q [T, Hq, D]; caches [blocks, block_size, Hkv, D]; causal; returns [T, Hq, D]."""
+    T, Hq, D = q.shape
+    Hkv = k_cache.shape[2]
+    out = torch.zeros(T, Hq, D, dtype=torch.float32, device=q.device)
+    B = cu_seqlens_q.numel() - 1
+    for i in range(B):
+        lo, hi = int(cu_seqlens_q[i]), int(cu_seqlens_q[i + 1])
+        if hi == lo:
+            continue
+        n, ql = int(context_lens[i]), hi - lo
+        k = _gather_rows(k_cache, block_tables[i], n).repeat_interleave(Hq // Hkv, 1)   # [n, Hq, D]
+        v = _gather_rows(v_cache, block_tables[i], n).repeat_interleave(Hq // Hkv, 1)
+        s = torch.einsum("thd,nhd->thn", q[lo:hi].float(), k) * scale
+        pos = torch.arange(n - ql, n, device=q.device).view(ql, 1, 1)
+        s = s.masked_fill(torch.arange(n, device=q.device).view(1, 1, n) > pos, float("-inf"))
+        out[lo:hi] = torch.einsum("thn,nhd->thd", torch.softmax(s, -1), v)
+    return out.to(q.dtype)
+
+
+def merge_attention_states(o1, lse1, o2, lse2):
+    """Combine two partial attention results over disjoint key sets (LSE-weighted)."""
+    m = torch.maximum(lse1, lse2)
+    w1, w2 = torch.exp(lse1 - m), torch.exp(lse2 - m)
+    o = (o1.float() * w1.unsqueeze(-1) + o2.float() * w2.unsqueeze(-1)) / (w1 + w2).unsqueeze(-1)
+    return o.to(o1.dtype), m + torch.log(w1 + w2)
+
+
+# ---- MoE -----------------------------------------------------------------------------------------
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_group: int = 1, topk_group: int = 1,
+              norm_topk_prob: bool = True, routed_scaling_factor: float = 1.0, scoring: str = "sigmoid"):
+    """DeepSeek ``noaux_tc`` routing and Qwen3 softmax routing.
+
+    scores = sigmoid|softmax(logits fp32); choice = scores + bias; with n_group > 1 only the
+    topk_group groups with the largest sum of their top-2 choices stay eligible; idx = top_k of
+    choice; weights are the un-biased scores, renormalised and scaled
+    (reference models/deepseek_v2/deepseek_v2.py:478-543, models/qwen3_moe/qwen3_moe.py:283-297).
+    """
+    lf = logits.float()
+    scores = torch.sigmoid(lf) if scoring == "sigmoid" else torch.softmax(lf, -1)
+    choice = scores + bias.float() if bias is not None else scores
+    T, E = choice.shape
+    if n_group > 1:
+        g = choice.view(T, n_group, E // n_group)
+        gs = g.topk(2, -1).values.sum(-1)
+        keep = gs.topk(topk_group, -1).indices
+        gmask = torch.zeros(T, n_group, dtype=torch.bool, device=logits.device).scatter_(1, keep, True)
+        choice = choice.masked_fill(~gmask.unsqueeze(-1).expand(T, n_group, E // n_group).reshape(T, E), float("-inf"))
+    idx = choice.topk(top_k, -1).indices
+    w = scores.gather(1, idx)
+    if norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return idx.to(torch.int32), (w * routed_scaling_factor).float()
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    a, b = x.float().chunk(2, -1)
+    return (F.silu(a) * b).to(x.dtype)
+
+
+def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0) -> torch.Tensor:
+    """Routed experts held locally: ids [expert_offset, expert_offset + E_local).  w13 [E, 2I, H], w2 [E, H, I].
+    Returns the weighted sum over the local experts of each token (zeros where none is local)."""
+    T, H = x.shape
+    E = w13.shape[0]
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for e in range(E):
+        sel = (topk_idx == e + expert_offset)
+        tok, slot = sel.nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        xe = x[tok]
+        h = linear(xe, w13[e], None if w13_scale is None else w13_scale[e])
+        h = silu_and_mul(h)
+        y = linear(h, w2[e], None if w2_scale is None else w2_scale[e])
+        out.index_add_(0, tok, y.float() * topk_w[tok, slot].unsqueeze(-1))
+    return out.to(x.dtype)
+
+
+# ---- sampling ------------------------------------------------------------------------------------
+def sample(logits: torch.Tensor, temperatures: torch.Tensor, generator: Optional[torch.Generator] = None,
+           return_logprobs: bool = False):
+    """Gumbel-max in log space with per-row temperature; rows with temperature < 1e-5 are greedy."""
+    lf = logits.float()
+    greedy = temperatures < 1e-5
+    if bool(greedy.all()):
+        tok = lf.argmax(-1)
+    else:
+        t = torch.where(greedy, torch.ones_like(temperatures), temperatures).unsqueeze(-1)
+        u = torch.rand(lf.shape, generator=generator, device=lf.device, dtype=torch.float32).clamp_min(1e-20)
+        g = -torch.log(-torch.log(u))
+        tok = torch.where(greedy, lf.argmax(-1), (lf / t + g).argmax(-1))
+    if not return_logprobs:
+        return tok, None
+    lp = torch.log_softmax(lf, -1).gather(1, tok.unsqueeze(-1)).squeeze(-1)
+    return tok, lp
+
+
+# ---- DSA lightning indexer -------------------------------------------------------------------------
+def hadamard(x: torch.Tensor) -> torch.Tensor:
+    """Normalised fast Walsh-Hadamard transform over the last dim (a power of two)."""
+    n = x.shape[-1]
+    y = x.float().reshape(-1, n)
+    h = 1
+    while h < n:
+        y = y.view(-1, n // (2 * h), 2, h)
+        y = torch.stack([y[:, :, 0] + y[:, :, 1], y[:, :, 0] - y[:, :, 1]], 2).reshape(-1, n)
+        h *= 2
+    return (y * n ** -0.5).view(x.shape).to(x.dtype)
+
+
+def quant_fp8_per_token_pow2(x: torch.Tensor):
+    """One power-of-two scale per row (indexer keys / queries)."""
+    amax = x.float().abs().amax(-1, keepdim=True).clamp_min(1e-4)
+    s = torch.exp2(torch.ceil(torch.log2(amax / FP8_MAX)))
+    return (x.float() / s).clamp(-FP8_MAX, FP8_MAX).to(FP8), s.squeeze(-1)
+
+
+def indexer_logits(q_fp8, q_scale, head_w, k_fp8, k_scale) -> torch.Tensor:
+    """score(i, j) = sum_h w[i,h] * relu(q[i,h] . k[j]) (reference dsa/indexer/lightning.py:116-162).
+    q_fp8 [T, Hi, D], q_scale [T, Hi], head_w [T, Hi], k_fp8 [N, D], k_scale [N] -> [T, N] fp32."""
+    s = torch.einsum("thd,nd->thn", q_fp8.float(), k_fp8.float())
+    s = torch.relu(s) * (q_scale.float() * head_w.float()).unsqueeze(-1)
+    return s.sum(1) * k_scale.float().unsqueeze(0)
+
+
+def indexer_topk(logits: torch.Tensor, valid_len: torch.Tensor, topk: int) -> torch.Tensor:
+    """Row-wise top-k of the first valid_len[i] entries; -1 pads.  Returns int32 [T, topk] (logical positions)."""
+    T, N = logits.shape
+    masked = logits.masked_fill(torch.arange(N, device=logits.device).unsqueeze(0) >= valid_len.unsqueeze(1), float("-inf"))
+    k = min(topk, N)
+    v, idx = masked.topk(k, -1)
+    idx = idx.masked_fill(torch.isinf(v), -1).to(torch.int32)
+    if k < topk:
+        idx = F.pad(idx, (0, topk - k), value=-1)
+    return idx
+
+
+def logical_to_physical(idx: torch.Tensor, block_table_rows: torch.Tensor, block_size: int) -> torch.Tensor:
+    """block_table[idx // bs] * bs + idx % bs, -1 stays -1 (reference topk.cuh:250-430)."""
+    safe = idx.clamp_min(0).long()
+    phys = block_table_rows.gather(1, safe // block_size).long() * block_size + safe % block_size
+    return torch.where(idx >= 0, phys, torch.full_like(phys, -1)).to(torch.int32)
+
+
+# ---- small GEMM-shaped helpers -------------------------------------------------------------------
+def bmm_absorb(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Per-head matmul of MLA weight absorption: x [T, H, A], w [H, A, B] -> [T, H, B]."""
+    return torch.einsum("tha,hab->thb", x.float(), w.float()).to(x.dtype)
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """MoE router GEMM in fp32: x [T, H] (any dtype), w [E, H] fp32 -> [T, E] fp32."""
+    return F.linear(x.float(), w.float())
+
+
+def lm_head(hidden: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Vocabulary projection; logits are returned in fp32."""
+    return F.linear(hidden, w).float()

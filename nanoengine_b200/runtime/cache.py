@@ -1,0 +1,120 @@
+"""KV-cache families, byte accounting and allocation.
+
+MLA latent cache   [L, blocks, block_size, R + rope]   bf16/fp32, or fp8 e4m3 raw rows (576 B per token per layer
+                                                        for DeepSeek-V3: clamped cast, no scales)
+indexer key cache  [L, blocks, block_size * (D + 4)] u8 per page: block_size fp8 keys, then block_size fp32 scales
+GQA cache          [2, L, blocks, block_size, kv_heads_local, head_dim]
+
+One extra block past the scheduler-visible range is reserved as the scratch page that dummy batches of idle
+DP ranks write into.
+
+Parity: reference runtime/context/cache/__init__.py:153-472 (budget :366-372, blocks :431-432),
+cache/mla.py:45-199 (formats and shapes), cache/indexer.py:45-77, cache/gqa.py:56-71.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..models.config import ModelConfig
+
+
+def torch_dtype(name: str):
+    return {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32, "fp8": torch.float8_e4m3fn}[name]
+
+
+@dataclass
+class CachePlan:
+    mla: bool
+    gqa: bool
+    indexer: bool
+    num_layers: int            # target layers + MTP layers held on this rank
+    block_size: int
+    kv_dtype: torch.dtype
+    row_dim: int               # MLA: R + rope ; GQA: head_dim
+    kv_heads_local: int = 1
+    index_dim: int = 0
+
+    @property
+    def kv_block_bytes(self) -> int:
+        e = torch.empty(0, dtype=self.kv_dtype).element_size()
+        if self.mla:
+            return self.num_layers * self.block_size * self.row_dim * e
+        return 2 * self.num_layers * self.block_size * self.kv_heads_local * self.row_dim * e
+
+    @property
+    def indexer_block_bytes(self) -> int:
+        return self.num_layers * self.block_size * (self.index_dim + 4) if self.indexer else 0
+
+    @property
+    def block_bytes(self) -> int:
+        return self.kv_block_bytes + self.indexer_block_bytes
+
+    def plan_bits(self) -> int:
+        from .._native import _core as C
+        bits = C.PLAN_MLA if self.mla else C.PLAN_GQA
+        if self.indexer:
+            bits |= C.PLAN_INDEXER
+        return bits
+
+
+def make_cache_plan(mc: ModelConfig, kv_dtype_name: str, block_size: int, attn_tp: int = 1, num_mtp_layers: int = 0,
+                    use_indexer: bool = True, num_layers: Optional[int] = None) -> CachePlan:
+    L = (num_layers if num_layers is not None else mc.num_hidden_layers) + num_mtp_layers
+    dt = torch_dtype(kv_dtype_name)
+    if mc.is_mla:
+        return CachePlan(True, False, mc.has_indexer and use_indexer, L, block_size, dt, mc.mla_cache_dim,
+                         index_dim=mc.index_head_dim)
+    return CachePlan(False, True, False, L, block_size, dt, mc.head_dim, kv_heads_local=max(1, mc.num_key_value_heads // attn_tp))
+
+
+def kv_budget_blocks(plan: CachePlan, total: int, utilization: float, used: int, peak: int, current: int, reserved: int = 0) -> int:
+    """blocks = (total*util - used - peak + current - reserved) // bytes_per_block."""
+    budget = int(total * utilization) - used - peak + current - reserved
+    return max(0, budget // plan.block_bytes)
+
+
+class KVCache:
+    def __init__(self, plan: CachePlan, num_blocks: int, device):
+        self.plan, self.num_blocks, self.device = plan, num_blocks, torch.device(device)
+        nb = num_blocks + 1   # + scratch page
+        self.scratch_block = num_blocks
+        if plan.mla:
+            self.kv = torch.zeros(plan.num_layers, nb, plan.block_size, plan.row_dim, dtype=torch.uint8 if plan.kv_dtype == torch.float8_e4m3fn else plan.kv_dtype, device=device)
+            if plan.kv_dtype == torch.float8_e4m3fn:
+                self.kv = self.kv.view(torch.float8_e4m3fn)
+            self.layers: List = [self.kv[l] for l in range(plan.num_layers)]
+        else:
+            self.kv = torch.zeros(2, plan.num_layers, nb, plan.block_size, plan.kv_heads_local, plan.row_dim, dtype=plan.kv_dtype, device=device)
+            self.layers = [(self.kv[0, l], self.kv[1, l]) for l in range(plan.num_layers)]
+        self.indexer = None
+        self.indexer_layers = None
+        if plan.indexer:
+            self.indexer = torch.zeros(plan.num_layers, nb, plan.block_size * (plan.index_dim + 4), dtype=torch.uint8, device=device)
+            self.indexer_layers = [self.indexer[l] for l in range(plan.num_layers)]
+        self.host_kv = None
+
+    def allocate_host(self, num_host_blocks: int):
+        """Pinned host tier used by preemption swap."""
+        if num_host_blocks <= 0:
+            return
+        shape = list(self.kv.shape)
+        bdim = 1 if self.plan.mla else 2
+        shape[bdim] = num_host_blocks
+        self.host_kv = torch.zeros(shape, dtype=self.kv.dtype if self.kv.dtype != torch.float8_e4m3fn else torch.uint8,
+                                   pin_memory=self.device.type == "cuda")
+
+    def swap(self, src: List[int], dst: List[int], to_host: bool):
+        """Copy whole blocks (all layers) between the device cache and the host tier."""
+        if not src:
+            return
+        bdim = 1 if self.plan.mla else 2
+        dev = self.kv.view(torch.uint8) if self.kv.dtype == torch.float8_e4m3fn else self.kv
+        s = torch.as_tensor(src, dtype=torch.long)
+        d = torch.as_tensor(dst, dtype=torch.long)
+        if to_host:
+            self.host_kv.index_copy_(bdim, d, dev.index_select(bdim, s.to(dev.device)).to("cpu"))
+        else:
+            dev.index_copy_(bdim, d.to(dev.device), self.host_kv.index_select(bdim, s).to(dev.device, non_blocking=True))

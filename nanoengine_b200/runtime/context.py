@@ -1,0 +1,35 @@
+"""Per-step attention metadata handed to every layer of a forward pass.
+
+Parity: reference runtime/context/batch.py:11-43 (BatchContext fields: cu_seqlens_q/k,
+slot_mapping, context_lens, block_tables, sampling indices).  Here it is an explicit argument of
+``model.forward`` instead of a process-global singleton, which keeps CUDA-graph capture and
+multi-engine processes (prefill + decode engines in one test) free of hidden state.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import torch
+
+
+@dataclass
+class ForwardContext:
+    is_prefill: bool
+    num_seqs: int
+    num_tokens: int
+    cu_seqlens_q: torch.Tensor            # int32 [B+1]
+    context_lens: torch.Tensor            # int32 [B]  context length of each sequence after this step
+    slot_mapping: torch.Tensor            # int64 [T]  cache row of every new token
+    block_tables: torch.Tensor            # int32 [B, max_blocks]
+    max_seqlen_q: int = 1
+    max_seqlen_k: int = 1
+    last_token_indices: Optional[torch.Tensor] = None   # int32 [B] row of each sequence's last new token
+    q_len_uniform: int = 0                # > 0 when every sequence contributes exactly this many rows (decode / verify)
+    is_dummy: bool = False
+    kv_caches: Optional[List[Any]] = None  # per-layer cache tensors (MLA: [blocks, bs, D]; GQA: (k, v))
+    indexer_caches: Optional[List[Any]] = None
+    extras: Dict[str, Any] = field(default_factory=dict)   # per-forward scratch shared by layers (e.g. DSA top-k reuse)
+    # host copies for the CPU reference path and for planning
+    cu_seqlens_q_host: Optional[List[int]] = None
+    context_lens_host: Optional[List[int]] = None

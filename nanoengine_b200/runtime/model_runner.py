@@ -1,0 +1,289 @@
+"""Worker runtime: one ModelRunner per GPU (or per CPU rank in tests).
+
+Owns the model shard, the KV cache, input preparation, CUDA-graph replay for decode, sampling and the
+host<->device block swap.  All traffic with the controller is bytes of the native wire format.
+
+Parity: reference runtime/runner/model_runner.py:223 (ModelRunner) - dist init :351-559, allocate_kvcache
+:685-917, run_model :1539-1621 (eager for prefill, graphs for decode), _standard_sample :1743-1826,
+prepare_from_bytes :1829-1948, run_prepared :1984-2132, step timers :84-197; runtime/runner/input_preparer.py:36-393.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .._native import _core as C
+from ..config import Config
+from ..models.registry import get_model_class
+from ..models.weights import expert_owner_filter, iterate_safetensors, random_hf_weights
+from ..parallel.dist import DistContext, ParallelSpec, get_dist_context, init_dist_context
+from .cache import KVCache, kv_budget_blocks, make_cache_plan, torch_dtype
+from .context import ForwardContext
+from .sampler import Sampler
+
+
+class StepTimer:
+    """CPU phase timer plus optional CUDA-event forward timing (enabled by Config.step_timing)."""
+
+    def __init__(self, enabled: bool, cuda: bool):
+        self.enabled, self.cuda = enabled, cuda
+        self.phases: Dict[str, float] = {}
+        self._t0 = None
+        self._ev = None
+        self.last_forward_ms = 0.0
+
+    def start(self, name):
+        if self.enabled:
+            self._t0 = (name, time.perf_counter())
+
+    def stop(self):
+        if self.enabled and self._t0:
+            n, t = self._t0
+            self.phases[n] = self.phases.get(n, 0.0) + (time.perf_counter() - t) * 1e3
+            self._t0 = None
+
+    def forward_begin(self):
+        if self.enabled and self.cuda:
+            self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self._ev[0].record()
+
+    def forward_end(self):
+        if self.enabled and self.cuda and self._ev:
+            self._ev[1].record()
+            self._ev[1].synchronize()
+            self.last_forward_ms = self._ev[0].elapsed_time(self._ev[1])
+
+
+class ModelRunner:
+    def __init__(self, config: Config, rank: int = 0, world_size: int = 1, device: Optional[str] = None,
+                 dist_ctx: Optional[DistContext] = None):
+        self.config = config
+        self.rank, self.world_size = rank, world_size
+        if device is None:
+            use_cuda = config.device == "cuda" or (config.device == "auto" and torch.cuda.is_available())
+            device = f"cuda:{int(os.environ.get('LOCAL_RANK', rank)) % max(1, torch.cuda.device_count())}" if use_cuda else "cpu"
+        self.device = torch.device(device)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        self.dtype = torch_dtype(config.dtype)
+        self.dist = dist_ctx or init_dist_context(config.parallel_spec(), rank, world_size, self.device)
+        self.mc = config.model_config
+        self.model = None
+        self.mtp = None
+        self.cache: Optional[KVCache] = None
+        self.sampler = Sampler(config.seed + 1000 * self.dist.attn_dp_rank, self.device)
+        self.timer = StepTimer(config.step_timing, self.device.type == "cuda")
+        self.graphs = None
+        self.mtp_runner = None
+        self._profiler = None
+        self.plan = make_cache_plan(self.mc, config.resolved_kv_dtype(), config.kvcache_block_size, config.attention_tp,
+                                    num_mtp_layers=self._num_mtp_layers(), use_indexer=config.use_nsa())
+
+    def _num_mtp_layers(self) -> int:
+        return max(1, self.mc.num_nextn_predict_layers) if self.config.num_speculative_tokens > 0 else 0
+
+    # ---- model -------------------------------------------------------------------------------
+    def layer_range(self):
+        L, pp = self.mc.num_hidden_layers, self.config.pp
+        if pp == 1:
+            return (0, L)
+        from ..models.pp import pp_layer_partition
+        return pp_layer_partition(L, pp)[self.dist.pp_rank]
+
+    def init_model(self) -> None:
+        cls = get_model_class(self.mc.architecture)
+        torch.manual_seed(self.config.seed)
+        lr = self.layer_range()
+        self.model = cls(self.mc, dtype=self.dtype, device=self.device, layer_range=lr if self.config.pp > 1 else None)
+        keep = expert_owner_filter(self.mc, self.dist.ep_size, self.dist.ep_rank, lr if self.config.pp > 1 else None)
+        want_mtp = self.config.num_speculative_tokens > 0
+        if want_mtp:
+            from ..models.deepseek import DeepseekMTP
+            self.mtp = DeepseekMTP(self.mc, self.dtype, self.device, self.model.model.embed_tokens, self.model.lm_head)
+        if self.config.dummy_weight:
+            it = random_hf_weights(self.mc, self.config.seed, self.device, keep, include_mtp=want_mtp)
+        else:
+            it = iterate_safetensors(self.config.model, keep, self.device)
+        self.load_weights(it)
+        self.model.eval()
+
+    def load_weights(self, it) -> int:
+        if self.mtp is not None:
+            from ..models.weights import load_deepseek_weights
+            return load_deepseek_weights(self.model, it, mtp=self.mtp)
+        return self.model.load_weights(it)
+
+    # ---- cache -------------------------------------------------------------------------------
+    def profile_num_blocks(self) -> int:
+        """How many KV blocks fit: run a worst-case prefill to find peak activation memory, then apply the budget formula."""
+        if self.config.num_kvcache_blocks is not None:
+            return self.config.num_kvcache_blocks
+        if self.device.type != "cuda":
+            return 256
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        free, total = torch.cuda.mem_get_info()
+        current = torch.cuda.memory_allocated()
+        # activation peak estimate from a synthetic prefill of the configured token budget
+        try:
+            self._warmup_prefill(min(self.config.max_num_batched_tokens, 8192))
+        finally:
+            torch.cuda.synchronize()
+        peak = torch.cuda.max_memory_allocated()
+        used = total - free
+        torch.cuda.empty_cache()
+        return kv_budget_blocks(self.plan, total, self.config.gpu_memory_utilization, used, peak, current)
+
+    def _warmup_prefill(self, tokens: int) -> None:
+        bs = self.plan.block_size
+        nb = (tokens + bs - 1) // bs
+        tmp = KVCache(self.plan, nb, self.device)
+        b = C.RunnerIn()
+        b.is_prefill = True
+        b.seq_ids = [0]
+        b.input_ids = [1] * tokens
+        b.positions = list(range(tokens))
+        b.q_lens, b.seq_lens = [tokens], [tokens]
+        b.block_tables, b.block_offsets = list(range(nb)), [0, nb]
+        b.temperatures, b.sample_mask = [0.0], [1]
+        b.state_slots = b.handoff_slots = b.hisparse_slots = [-1]
+        saved, self.cache = self.cache, tmp
+        try:
+            self.run_batch(b)
+        finally:
+            self.cache = saved
+            del tmp
+
+    def allocate_kvcache(self, num_blocks: int) -> None:
+        self.cache = KVCache(self.plan, num_blocks, self.device)
+        self.cache.allocate_host(self.config.num_host_kvcache_blocks)
+        if self.config.num_speculative_tokens > 0:
+            from .mtp_runner import MTPRunner
+            self.mtp_runner = MTPRunner(self)
+        if self.device.type == "cuda" and not self.config.enforce_eager:
+            from .graph_runner import DecodeGraphRunner
+            self.graphs = DecodeGraphRunner(self)
+
+    # ---- input preparation ---------------------------------------------------------------------
+    def _to_dev(self, arr: np.ndarray, dtype=None) -> torch.Tensor:
+        t = torch.from_numpy(arr)
+        if dtype is not None:
+            t = t.to(dtype)
+        if self.device.type == "cuda":
+            return t.pin_memory().to(self.device, non_blocking=True)
+        return t
+
+    def prepare(self, b) -> ForwardContext:
+        bs = self.plan.block_size
+        if b.is_dummy or b.num_seqs == 0:
+            return self._dummy_context(b.is_prefill)
+        d = b.prepare(bs, 0)
+        q_lens = b.q_lens
+        uniform = q_lens[0] if all(q == q_lens[0] for q in q_lens) else 0
+        ctx = ForwardContext(
+            is_prefill=b.is_prefill, num_seqs=b.num_seqs, num_tokens=len(b.input_ids),
+            cu_seqlens_q=self._to_dev(d["cu_seqlens_q"]), context_lens=self._to_dev(d["context_lens"]),
+            slot_mapping=self._to_dev(d["slot_mapping"]), block_tables=self._to_dev(d["block_tables"]).view(b.num_seqs, -1),
+            max_seqlen_q=int(d["max_seqlen_q"]), max_seqlen_k=int(d["max_seqlen_k"]),
+            last_token_indices=self._to_dev(d["last_token_indices"]), q_len_uniform=uniform,
+            kv_caches=self.cache.layers, indexer_caches=self.cache.indexer_layers,
+            cu_seqlens_q_host=d["cu_seqlens_q"].tolist(), context_lens_host=d["context_lens"].tolist())
+        ctx.extras["input_ids"] = self._to_dev(d["input_ids"]).long()
+        ctx.extras["positions"] = self._to_dev(d["positions"]).long()
+        return ctx
+
+    def _dummy_context(self, is_prefill: bool) -> ForwardContext:
+        """One token on the scratch page so an idle DP rank still joins every EP collective of the step."""
+        dev = self.device
+        sb = self.cache.scratch_block
+        ctx = ForwardContext(
+            is_prefill=is_prefill, num_seqs=1, num_tokens=1,
+            cu_seqlens_q=torch.tensor([0, 1], dtype=torch.int32, device=dev), context_lens=torch.tensor([1], dtype=torch.int32, device=dev),
+            slot_mapping=torch.tensor([sb * self.plan.block_size], dtype=torch.int64, device=dev),
+            block_tables=torch.tensor([[sb]], dtype=torch.int32, device=dev), max_seqlen_q=1, max_seqlen_k=1,
+            last_token_indices=torch.tensor([0], dtype=torch.int32, device=dev), q_len_uniform=1, is_dummy=True,
+            kv_caches=self.cache.layers, indexer_caches=self.cache.indexer_layers, cu_seqlens_q_host=[0, 1], context_lens_host=[1])
+        ctx.extras["input_ids"] = torch.zeros(1, dtype=torch.long, device=dev)
+        ctx.extras["positions"] = torch.zeros(1, dtype=torch.long, device=dev)
+        return ctx
+
+    # ---- execution -----------------------------------------------------------------------------
+    @torch.inference_mode()
+    def forward(self, ctx: ForwardContext) -> torch.Tensor:
+        ids, pos = ctx.extras["input_ids"], ctx.extras["positions"]
+        if self.graphs is not None and not ctx.is_prefill and ctx.q_len_uniform == 1 and self.graphs.can_run(ctx):
+            return self.graphs.run(ids, pos, ctx)
+        return self.model(ids, pos, ctx)
+
+    @torch.inference_mode()
+    def run_batch(self, b) -> "C.RunnerOut":
+        self.timer.start("swap")
+        if b.swap_out_src:
+            self.cache.swap(list(b.swap_out_src), list(b.swap_out_dst), to_host=True)
+        if b.swap_in_src:
+            self.cache.swap(list(b.swap_in_src), list(b.swap_in_dst), to_host=False)
+        self.timer.stop()
+        self.timer.start("prepare")
+        ctx = self.prepare(b)
+        self.timer.stop()
+        if self.mtp_runner is not None and not ctx.is_dummy:
+            return self.mtp_runner.run(b, ctx)
+        self.timer.forward_begin()
+        hidden = self.forward(ctx)
+        if ctx.is_dummy:
+            if self.mtp_runner is not None:
+                self.mtp_runner.run_dummy(ctx)
+            self.timer.forward_end()
+            return C.RunnerOut([], [])
+        mask = np.asarray(b.sample_mask, dtype=bool)
+        if not mask.any():
+            self.timer.forward_end()
+            return C.RunnerOut([], [])
+        rows = ctx.last_token_indices.long()
+        if not mask.all():
+            rows = rows[torch.from_numpy(mask).to(rows.device)]
+        logits = self.model.compute_logits(hidden[rows])
+        temps = torch.tensor([t for t, m in zip(b.temperatures, mask) if m], dtype=torch.float32, device=self.device)
+        tok, lp = self.sampler(logits, temps, b.any_return_logprobs)
+        self.timer.forward_end()
+        self.timer.start("d2h")
+        toks = tok.tolist()
+        lps = lp.tolist() if lp is not None else None
+        self.timer.stop()
+        ids = [s for s, m in zip(b.seq_ids, mask) if m]
+        return C.RunnerOut(ids, [[t] for t in toks], None if lps is None else [[x] for x in lps])
+
+    def run_from_bytes(self, blob: bytes) -> bytes:
+        return self.run_batch(C.RunnerIn.from_bytes(blob)).to_bytes()
+
+    # ---- profiler control ----------------------------------------------------------------------
+    def start_profiler(self, trace_name: str = "trace") -> bool:
+        if self._profiler is not None or not self.config.profiler_dir:
+            return False
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if self.device.type == "cuda":
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        self._profiler = (torch.profiler.profile(activities=acts), trace_name)
+        self._profiler[0].start()
+        return True
+
+    def stop_profiler(self) -> Optional[str]:
+        if self._profiler is None:
+            return None
+        prof, name = self._profiler
+        prof.stop()
+        os.makedirs(self.config.profiler_dir, exist_ok=True)
+        path = os.path.join(self.config.profiler_dir, f"{name}.rank{self.rank}.json")
+        prof.export_chrome_trace(path)
+        self._profiler = None
+        return path
+
+    def get_step_timing(self) -> Dict[str, float]:
+        out = dict(self.timer.phases)
+        out["forward_ms_last"] = self.timer.last_forward_ms
+        return out
