@@ -33,7 +33,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 CXX = os.environ.get("CXX", "g++")
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
-              "-Xptxas", "-v", "-DNDEBUG"] + GENCODE
+              "-Xptxas", "-v", "-DNDEBUG", "-rdc=true"] + GENCODE
 
 
 def _stamp(paths, extra=""):
@@ -107,7 +107,7 @@ def build_kernels(force=False) -> Path:
         list(ex.map(one, jobs))
     lstamp = _stamp(objs)
     if _needs(target, lstamp, force or bool(jobs)):
-        _run([NVCC, "-shared", *GENCODE, "-o", str(target), *map(str, objs), "-lcudart"])
+        _run([NVCC, "-shared", "-rdc=true", *GENCODE, "-o", str(target), *map(str, objs), "-lcudart"])
         _mark(target, lstamp)
     return target
 

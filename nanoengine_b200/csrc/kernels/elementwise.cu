@@ -1,0 +1,252 @@
+// Memory-bound operators of the decoder layer, each fused as far as its neighbours allow:
+//   * (residual add +) RMSNorm (+ 1x128 fp8 quantisation with the scale layout the block-scaled GEMM reads)
+//   * 1x128 fp8 quantisation of bf16 activations
+//   * SwiGLU (+ 1x128 fp8 requantisation), flat or over the masked [E, max_m, *] expert layout
+//   * RoPE in place on a strided sub-range of each head (MLA q_pe / k_pe, GQA q / k)
+//   * MLA latent KV row store into the paged cache (bf16 rows or raw 576-byte e4m3 rows)
+// Replaces in the reference: triton/generic/rmsnorm.py, triton/hopper/rmsnorm_quant_fp8.py:27-108, triton/hopper/fp8.py:9-187,
+// jit/sgl/csrc/deepseek_v4/silu_and_mul_masked_post_quant.cuh, triton/hopper/mla_rope.py:17, triton/generic/kv_store.py,
+// triton/hopper/fp8_utils.py:203-305.
+#include "ptx.cuh"
+
+namespace ne {
+
+constexpr float kFp8Max = 448.f;
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) { t = warp_sum(t); if (l == 0) red[0] = t; }
+  __syncthreads();
+  float r = red[0];
+  __syncthreads();
+  return r;
+}
+
+// One CTA per row.  x may be a strided view (row stride x_ld).  Optional residual add (res_in -> res_out, bf16),
+// optional bf16 output, optional fp8 output with scales written to sc[(col/128) * sc_ld + row].
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, const __nv_bfloat16* __restrict__ res_in,
+                                                     const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long out_ld,
+                                                     __nv_bfloat16* __restrict__ res_out, uint8_t* __restrict__ q, float* __restrict__ sc, int sc_ld,
+                                                     int H, float eps) {
+  extern __shared__ float srow[];            // H floats
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* xr = x + (long long)row * x_ld;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; j++) { float2 t = unpack_bf16x2(u[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+    if (res_in) {
+      uint4 rv = *reinterpret_cast<const uint4*>(res_in + (long long)row * H + i);
+      uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float2 t = unpack_bf16x2(ru[j]);
+        o[j] = pack_bf16x2(f[2 * j] + t.x, f[2 * j + 1] + t.y);
+        float2 b = unpack_bf16x2(o[j]);      // the sum is rounded to bf16 first, as the unfused form does
+        f[2 * j] = b.x; f[2 * j + 1] = b.y;
+      }
+      *reinterpret_cast<uint4*>(res_out + (long long)row * H + i) = make_uint4(o[0], o[1], o[2], o[3]);
+    } else if (res_out) {
+      *reinterpret_cast<uint4*>(res_out + (long long)row * H + i) = v;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) { srow[i + j] = f[j]; ss += f[j] * f[j]; }
+  }
+  float tot = block_sum(ss, red);
+  float inv = rsqrtf(tot / (float)H + eps);
+  if (out) {
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+      uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float2 t = unpack_bf16x2(wu[j]);
+        o[j] = pack_bf16x2(srow[i + 2 * j] * inv * t.x, srow[i + 2 * j + 1] * inv * t.y);
+      }
+      *reinterpret_cast<uint4*>(out + (long long)row * out_ld + i) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  if (q) {
+    // one warp per 128-column group; values are rounded to bf16 first so the result matches quantising the bf16 output
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int g = warp; g < H / 128; g += nw) {
+      int c = g * 128 + lane * 4;
+      float v[4];
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        v[j] = __bfloat162float(__float2bfloat16(srow[c + j] * inv * __bfloat162float(w[c + j])));
+        amax = fmaxf(amax, fabsf(v[j]));
+      }
+      amax = fmaxf(warp_max(amax), 1e-10f);
+      float s = amax / kFp8Max, is = kFp8Max / amax;
+      *reinterpret_cast<uint32_t*>(q + (long long)row * H + c) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
+      if (lane == 0) sc[(long long)g * sc_ld + row] = s;
+    }
+  }
+}
+
+// bf16 [T, K] (row stride x_ld) -> e4m3 [T, K] + scales sc[(k/128) * sc_ld + t].  One warp per (row, group).
+__global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, uint8_t* __restrict__ q, float* __restrict__ sc,
+                                   int sc_ld, int T, int K) {
+  const int groups = K / 128;
+  long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (long long)T * groups) return;
+  int row = (int)(gw / groups), g = (int)(gw % groups), lane = threadIdx.x & 31;
+  uint2 v = *reinterpret_cast<const uint2*>(x + (long long)row * x_ld + g * 128 + lane * 4);
+  float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+  amax = fmaxf(warp_max(amax), 1e-10f);
+  float is = kFp8Max / amax;
+  *reinterpret_cast<uint32_t*>(q + (long long)row * K + g * 128 + lane * 4) = pack_e4m3x4(a.x * is, a.y * is, b.x * is, b.y * is);
+  if (lane == 0) sc[(long long)g * sc_ld + row] = amax / kFp8Max;
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+// x [groups, rows, 2I] -> y.  One warp per (row, 128 output columns).  rows_valid[g] masks rows (nullptr = all).
+// Output bf16 (q == nullptr) or e4m3 + scales sc[g][(col/128) * sc_ld + row].
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ sc,
+                                int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, int groups, int rows, int I) {
+  const int cg = I / 128;
+  long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (long long)groups * rows * cg) return;
+  int c = (int)(gw % cg); long long t = gw / cg; int row = (int)(t % rows), g = (int)(t / rows), lane = threadIdx.x & 31;
+  if (rows_valid && row >= rows_valid[g]) return;
+  const __nv_bfloat16* xr = x + ((long long)g * rows + row) * 2 * I + c * 128 + lane * 4;
+  uint2 gv = *reinterpret_cast<const uint2*>(xr), uv = *reinterpret_cast<const uint2*>(xr + I);
+  float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), u0 = unpack_bf16x2(uv.x), u1 = unpack_bf16x2(uv.y);
+  float v[4] = {silu(g0.x) * u0.x, silu(g0.y) * u0.y, silu(g1.x) * u1.x, silu(g1.y) * u1.y};
+  long long o = ((long long)g * rows + row) * I + c * 128 + lane * 4;
+  if (!q) {
+    *reinterpret_cast<uint2*>(y + o) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+    return;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; j++) { v[j] = __bfloat162float(__float2bfloat16(v[j])); amax = fmaxf(amax, fabsf(v[j])); }
+  amax = fmaxf(warp_max(amax), 1e-10f);
+  float is = kFp8Max / amax;
+  *reinterpret_cast<uint32_t*>(q + o) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
+  if (lane == 0) sc[(long long)g * sc_gs + (long long)c * sc_ld + row] = amax / kFp8Max;
+}
+
+// In-place rotary embedding on dims [off, off+D) of each of `heads` heads of every row.
+// cache [max_pos, D] fp32 (cos | sin).  interleaved: pairs (2i, 2i+1); otherwise pairs (i, i + D/2).
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long row_stride, int head_stride, int heads, int off, int D,
+                            const long long* __restrict__ positions, const float* __restrict__ cache, int interleaved, int T) {
+  int half = D / 2;
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long total = (long long)T * heads * half;
+  if (idx >= total) return;
+  int i = (int)(idx % half); long long r = idx / half; int h = (int)(r % heads); int t = (int)(r / heads);
+  const float* cs = cache + positions[t] * D;
+  float c = cs[i], s = cs[half + i];
+  __nv_bfloat16* p = x + (long long)t * row_stride + (long long)h * head_stride + off;
+  int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+  float a = __bfloat162float(p[ia]), b = __bfloat162float(p[ib]);
+  p[ia] = __float2bfloat16(a * c - b * s);
+  p[ib] = __float2bfloat16(b * c + a * s);
+}
+
+// cache row = [ckv (R) | k_pe (rope)], bf16 or e4m3 (clamped cast, no scale).  One warp per token.
+__global__ void mla_kv_store_kernel(const __nv_bfloat16* __restrict__ ckv, long long ckv_ld, const __nv_bfloat16* __restrict__ kpe, long long kpe_ld,
+                                    void* __restrict__ cache, const long long* __restrict__ slots, int T, int R, int rope, int fp8) {
+  int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  long long slot = slots[t];
+  if (slot < 0) return;
+  int D = R + rope;
+  for (int c = lane * 2; c < D; c += 64) {
+    uint32_t v = c < R ? *reinterpret_cast<const uint32_t*>(ckv + (long long)t * ckv_ld + c)
+                       : *reinterpret_cast<const uint32_t*>(kpe + (long long)t * kpe_ld + (c - R));
+    if (fp8) {
+      float2 f = unpack_bf16x2(v);
+      uint16_t o = (uint16_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(cache) + slot * D + c) = o;
+    } else {
+      *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(cache) + slot * D + c) = v;
+    }
+  }
+}
+
+// y[t, :] = a[t, :] + b[t, :] (bf16), used where a fused epilogue is not available
+__global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* y, long long n) {
+  long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  uint4 av = *reinterpret_cast<const uint4*>(a + i), bv = *reinterpret_cast<const uint4*>(b + i);
+  uint32_t au[4] = {av.x, av.y, av.z, av.w}, bu[4] = {bv.x, bv.y, bv.z, bv.w}, o[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) { float2 p = unpack_bf16x2(au[j]), r = unpack_bf16x2(bu[j]); o[j] = pack_bf16x2(p.x + r.x, p.y + r.y); }
+  *reinterpret_cast<uint4*>(y + i) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+}  // namespace ne
+
+using namespace ne;
+
+extern "C" int ne_rmsnorm(const void* x, long long x_ld, const void* res_in, const void* w, void* out, long long out_ld, void* res_out,
+                          void* q, float* sc, int sc_ld, int T, int H, float eps, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || (q && H % 128 != 0) || x_ld % 8 != 0) return 1001;
+  size_t smem = (size_t)H * sizeof(float);
+  if (smem > 48 * 1024) {
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); done = true; }
+  }
+  rmsnorm_kernel<<<T, 256, smem, st>>>((const __nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)res_in, (const __nv_bfloat16*)w,
+                                       (__nv_bfloat16*)out, out_ld, (__nv_bfloat16*)res_out, (uint8_t*)q, sc, sc_ld, H, eps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_quant_1x128(const void* x, long long x_ld, void* q, float* sc, int sc_ld, int T, int K, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (K % 128 != 0 || x_ld % 4 != 0) return 1001;
+  long long warps = (long long)T * (K / 128);
+  int blocks = (int)((warps + 7) / 8);
+  quant_1x128_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, x_ld, (uint8_t*)q, sc, sc_ld, T, K);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, int groups,
+                           int rows, int I, cudaStream_t st) {
+  if (groups <= 0 || rows <= 0) return 0;
+  if (I % 128 != 0) return 1001;
+  long long warps = (long long)groups * rows * (I / 128);
+  int blocks = (int)((warps + 7) / 8);
+  silu_mul_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, groups, rows, I);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_rope(void* x, long long row_stride, int head_stride, int heads, int off, int D, const long long* positions,
+                       const float* cache, int interleaved, int T, cudaStream_t st) {
+  if (T <= 0) return 0;
+  long long total = (long long)T * heads * (D / 2);
+  rope_kernel<<<(int)((total + 255) / 256), 256, 0, st>>>((__nv_bfloat16*)x, row_stride, head_stride, heads, off, D, positions, cache, interleaved, T);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_mla_kv_store(const void* ckv, long long ckv_ld, const void* kpe, long long kpe_ld, void* cache, const long long* slots,
+                               int T, int R, int rope, int fp8, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (R % 2 || rope % 2) return 1001;
+  mla_kv_store_kernel<<<(T + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)ckv, ckv_ld, (const __nv_bfloat16*)kpe, kpe_ld, cache, slots, T, R, rope, fp8);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_add(const void* a, const void* b, void* y, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return 1001;
+  add_kernel<<<(int)((n / 8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n);
+  return (int)cudaGetLastError();
+}

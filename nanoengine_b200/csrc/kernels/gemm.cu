@@ -1,0 +1,391 @@
+// tcgen05 GEMM family for sm_100a:  D[g, m, n] = sum_k A[g, m, k] * B[g, n, k]   (both operands K-major).
+//
+//  * bf16 x bf16 -> fp32 accumulation in TMEM, bf16 or fp32 output
+//  * fp8 e4m3 x e4m3 with DeepSeek block scales (activations 1x128, weights 128x128): each 128-deep K block is
+//    multiplied on the tensor cores into a fresh TMEM accumulator and promoted into fp32 registers with
+//    scale_a[m, kb] * scale_b[n/128, kb] by the epilogue warps while the next K block is being multiplied
+//  * dense (one group, M rows) or grouped-masked (E groups of up to max_m rows, masked_m[e] valid), the layout
+//    the MoE path uses for prefill and decode alike
+//
+// Structure (one CTA per SM, persistent over tiles): warp 0 issues TMA loads into a multi-stage 128B-swizzled
+// shared-memory ring, warp 1 issues tcgen05.mma from one elected thread and owns the TMEM allocation, warps 2-5
+// drain TMEM (tcgen05.ld), apply scales, convert and store.  Two TMEM accumulators let the epilogue of one tile
+// (or K block) overlap the MMAs of the next.  All mbarrier waits are bounded.
+//
+// Replaces in the reference: deep_gemm.fp8_gemm_nt / m_grouped_fp8_gemm_nt_masked call sites
+// (layers/backends/linear/deep_gemm.py, layers/backends/experts/deep_gemm.py:498-837), the CuTe-DSL small-M bf16
+// GEMM (kernel/cutedsl_bf16_gemm.py) and cuBLAS F.linear (layers/backends/linear/generic.py:103-315).
+#include <mutex>
+#include <unordered_map>
+
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace ne {
+
+__device__ int g_status[8];
+
+constexpr int kBlockM = 128;
+constexpr int kKBytes = 128;            // bytes of K per stage row: one 128B swizzle atom
+constexpr int kGemmThreads = 192;
+constexpr int kKernelGemm = 1;
+
+struct GemmArgs {
+  int M, N, K, groups;
+  const int* masked_m;                  // [groups] valid rows per group, or nullptr (all M rows valid)
+  const int* row_start;                 // contiguous mode: group g owns rows [row_start[g], row_start[g] + masked_m[g]) of one
+                                        // flat [M, K] activation matrix (starts are multiples of 128); nullptr = [groups, M, K]
+  int a_group_inner;                    // A is stored [rows, groups, K]: TMA coordinates are (k, group, row)
+  void* D; long long ldd; long long d_group_stride;   // in elements
+  const float* sa; int sa_ld; long long sa_group_stride;   // activation scales [groups][K/128][sa_ld]
+  const float* sb; long long sb_group_stride;              // weight scales [groups][ceil(N/128)][K/128]
+  int out_fp32;
+};
+
+template <int BLOCK_N> struct Smem {
+  static constexpr int kABytes = kBlockM * kKBytes;
+  static constexpr int kBBytes = BLOCK_N * kKBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (200 * 1024 / kStageBytes) > 10 ? 10 : (200 * 1024 / kStageBytes);
+  static constexpr int kBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct TileSched {
+  int groups, M, n_blocks;
+  const int* masked_m;
+  const int* row_start;
+  int g = 0, base = 0;
+  __device__ TileSched(int groups_, int M_, int nb, const int* mm, const int* rs) : groups(groups_), M(M_), n_blocks(nb), masked_m(mm), row_start(rs) {}
+  __device__ int row0(int grp) const { return row_start ? row_start[grp] : 0; }
+  __device__ int rows(int grp) const {
+    int r = masked_m ? masked_m[grp] : M;
+    int cap = row_start ? M - row_start[grp] : M;      // never step outside the buffer, whatever the counts say
+    return r < cap ? r : (cap > 0 ? cap : 0);
+  }
+  __device__ bool get(int tile, int& grp, int& mb, int& nb) {
+    while (g < groups) {
+      int cnt = ((rows(g) + kBlockM - 1) / kBlockM) * n_blocks;
+      if (tile < base + cnt) { int l = tile - base; grp = g; mb = l / n_blocks; nb = l % n_blocks; return true; }
+      base += cnt; g++;
+    }
+    return false;
+  }
+};
+
+template <int BLOCK_N, bool kFP8, bool kBlockScaled>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
+  using S = Smem<BLOCK_N>;
+  constexpr int kStages = S::kStages;
+  constexpr int kElemsPerStageK = kFP8 ? 128 : 64;
+  constexpr int kUmmaK = kFP8 ? 32 : 16;
+  constexpr int kMmasPerStage = kElemsPerStageK / kUmmaK;     // 4
+  constexpr uint32_t kTmemCols = (2 * BLOCK_N) < 32 ? 32 : 2 * BLOCK_N;
+  constexpr uint32_t kIdesc = make_idesc(kFP8 ? FMT_E4M3 : FMT_BF16, kFP8 ? FMT_E4M3 : FMT_BF16, kBlockM, BLOCK_N);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  // bars: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
+  const uint32_t tfull0 = smem_u32(bars + 2 * kStages), tempty0 = smem_u32(bars + 2 * kStages + 2);
+  const uint32_t smem_base = smem_u32(smem);
+
+  const int warp = threadIdx.x >> 5;
+  const int num_kb = (args.K + kElemsPerStageK - 1) / kElemsPerStageK;
+  const int n_blocks = (args.N + BLOCK_N - 1) / BLOCK_N;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
+    for (int i = 0; i < 2; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (elect_one()) {
+      TileSched sched(args.groups, args.M, n_blocks, args.masked_m, args.row_start);
+      int stage = 0; uint32_t phase = 0; int grp, mb, nb;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && sched.get(tile, grp, mb, nb); tile += gridDim.x) {
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, kKernelGemm, 100 + stage)) { ok = false; break; }
+          uint32_t a_dst = smem_base + stage * S::kStageBytes, b_dst = a_dst + S::kABytes;
+          mbar_expect_tx(full0 + 8 * stage, S::kStageBytes);
+          if (args.a_group_inner) tma_load_3d(a_dst, &tmap_a, full0 + 8 * stage, kb * kElemsPerStageK, grp, mb * kBlockM);
+          else tma_load_3d(a_dst, &tmap_a, full0 + 8 * stage, kb * kElemsPerStageK, sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp);
+          tma_load_3d(b_dst, &tmap_b, full0 + 8 * stage, kb * kElemsPerStageK, nb * BLOCK_N, grp);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one()) {
+      TileSched sched(args.groups, args.M, n_blocks, args.masked_m, args.row_start);
+      int stage = 0; uint32_t phase = 0; int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && sched.get(tile, grp, mb, nb); tile += gridDim.x) {
+        if (!kBlockScaled) {
+          if (!mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 200 + buf)) { ok = false; break; }
+          tc_fence_after();
+        }
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (kBlockScaled) {
+            if (!mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 210 + buf)) { ok = false; break; }
+          }
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, kKernelGemm, 300 + stage)) { ok = false; break; }
+          tc_fence_after();
+          uint32_t a_addr = smem_base + stage * S::kStageBytes, b_addr = a_addr + S::kABytes;
+          uint64_t adesc = make_smem_desc(a_addr, 16, 1024, SW_128B);
+          uint64_t bdesc = make_smem_desc(b_addr, 16, 1024, SW_128B);
+          uint32_t d = tmem_base + buf * BLOCK_N;
+#pragma unroll
+          for (int k = 0; k < kMmasPerStage; k++) {
+            uint32_t acc = kBlockScaled ? (k != 0) : ((kb | k) != 0);
+            // advancing 32 bytes along K inside the 128B swizzle atom = +2 in the descriptor's 16-byte address units
+            if (kFP8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            else umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+          }
+          tc_commit(empty0 + 8 * stage);                // smem slot reusable once these MMAs retire
+          if (kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == 2) { buf = 0; bphase ^= 1; } }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        if (!kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == 2) { buf = 0; bphase ^= 1; } }
+      }
+    }
+  } else {
+    // ---------------- epilogue: 4 warps, warp w may touch TMEM lanes [32*(w%4), +32) ----------------
+    const int wq = warp & 3;
+    const int row_in_tile = wq * 32 + (int)lane_id();
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    TileSched sched(args.groups, args.M, n_blocks, args.masked_m, args.row_start);
+    int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && sched.get(tile, grp, mb, nb); tile += gridDim.x) {
+      const bool row_ok = mb * kBlockM + row_in_tile < sched.rows(grp);
+      const int row = sched.row0(grp) + mb * kBlockM + row_in_tile;      // row inside the group's (or the flat) matrix
+      const int n0 = nb * BLOCK_N;
+      if (kBlockScaled) {
+        float acc[BLOCK_N];
+#pragma unroll
+        for (int j = 0; j < BLOCK_N; j++) acc[j] = 0.f;
+        const float* sa = args.sa + (long long)grp * args.sa_group_stride + (row_ok ? row : 0);
+        const float* sb = args.sb + (long long)grp * args.sb_group_stride + (long long)(n0 / 128) * num_kb;
+        for (int kb = 0; kb < num_kb; kb++) {
+          float s = __ldg(sa + (long long)kb * args.sa_ld) * __ldg(sb + kb);
+          if (!mbar_wait(tfull0 + 8 * buf, bphase, abort_flag, kKernelGemm, 400 + buf)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < BLOCK_N / 32; c++) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + c * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j++) acc[c * 32 + j] = fmaf(s, __uint_as_float(r[j]), acc[c * 32 + j]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane_id() == 0) mbar_arrive(tempty0 + 8 * buf);
+          if (++buf == 2) { buf = 0; bphase ^= 1; }
+        }
+        if (!ok) break;
+        if (row_ok) {
+          long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0;
+#pragma unroll
+          for (int c = 0; c < BLOCK_N / 8; c++) {
+            if (n0 + c * 8 < args.N) {
+              if (args.out_fp32) {
+                float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.D) + off + c * 8);
+                p[0] = make_float4(acc[c * 8], acc[c * 8 + 1], acc[c * 8 + 2], acc[c * 8 + 3]);
+                p[1] = make_float4(acc[c * 8 + 4], acc[c * 8 + 5], acc[c * 8 + 6], acc[c * 8 + 7]);
+              } else {
+                uint4 v = make_uint4(pack_bf16x2(acc[c * 8], acc[c * 8 + 1]), pack_bf16x2(acc[c * 8 + 2], acc[c * 8 + 3]),
+                                     pack_bf16x2(acc[c * 8 + 4], acc[c * 8 + 5]), pack_bf16x2(acc[c * 8 + 6], acc[c * 8 + 7]));
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.D) + off + c * 8) = v;
+              }
+            }
+          }
+        }
+      } else {
+        if (!mbar_wait(tfull0 + 8 * buf, bphase, abort_flag, kKernelGemm, 410 + buf)) { ok = false; break; }
+        tc_fence_after();
+        long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0;
+#pragma unroll
+        for (int c = 0; c < BLOCK_N / 32; c++) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + c * 32, r);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              int col = n0 + c * 32 + q * 8;
+              if (col < args.N) {
+                if (args.out_fp32) {
+                  float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.D) + off + c * 32 + q * 8);
+                  p[0] = make_float4(__uint_as_float(r[q * 8]), __uint_as_float(r[q * 8 + 1]), __uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
+                  p[1] = make_float4(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]), __uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
+                } else {
+                  uint4 v = make_uint4(pack_bf16x2(__uint_as_float(r[q * 8]), __uint_as_float(r[q * 8 + 1])),
+                                       pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
+                                       pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
+                                       pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.D) + off + c * 32 + q * 8) = v;
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane_id() == 0) mbar_arrive(tempty0 + 8 * buf);
+        if (++buf == 2) { buf = 0; bphase ^= 1; }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // give copies still in flight time to land before the shared memory is handed back
+    for (int i = 0; i < 2000; i++) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+struct TmapKey {
+  const void* p; uint64_t d0, d1, d2, s1, s2; uint32_t b0, b1; int dt;
+  bool operator==(const TmapKey& o) const {
+    return p == o.p && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && s1 == o.s1 && s2 == o.s2 && b0 == o.b0 && b1 == o.b1 && dt == o.dt;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = (size_t)k.p;
+    for (uint64_t v : {k.d0, k.d1, k.d2, k.s1, k.s2, (uint64_t)k.b0, (uint64_t)k.b1, (uint64_t)k.dt}) h = h * 1000003u ^ (size_t)v;
+    return h;
+  }
+};
+
+// [groups][rows][K] K-major tensor -> 3-D map, box {128 bytes of K, box_rows, 1}, 128B swizzle.
+static int get_tmap_kmajor(CUtensorMap* out, const void* base, bool fp8, uint64_t K, uint64_t rows, uint64_t groups,
+                           uint64_t row_stride_elems, uint64_t group_stride_elems, uint32_t box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  const uint64_t es = fp8 ? 1 : 2;
+  TmapKey key{base, K, rows, groups, row_stride_elems * es, group_stride_elems * es, (uint32_t)(kKBytes / es), box_rows, fp8 ? TMA_U8 : TMA_BF16};
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  uint64_t dims[3] = {K, rows, groups};
+  uint64_t strides[2] = {row_stride_elems * es, group_stride_elems * es};
+  uint32_t box[3] = {(uint32_t)(kKBytes / es), box_rows, 1};
+  if (groups > 1 && group_stride_elems < row_stride_elems) {
+    // heads interleaved inside a row ([rows, groups, K] memory order): keep strides ascending, the kernel swaps coordinates
+    dims[1] = groups; dims[2] = rows; strides[0] = group_stride_elems * es; strides[1] = row_stride_elems * es;
+    box[1] = 1; box[2] = box_rows;
+  }
+  int rc = make_tmap(out, base, fp8 ? TMA_U8 : TMA_BF16, 3, dims, strides, box, TMA_SW_128);
+  if (rc == 0) { if (cache.size() > 8192) cache.clear(); cache.emplace(key, *out); }
+  return rc;
+}
+
+static int num_sms() {
+  static int n = 0;
+  if (!n) { int dev; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev); }
+  return n;
+}
+
+template <int BLOCK_N, bool kFP8, bool kBS>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int grid, cudaStream_t st) {
+  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BLOCK_N>::kBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, Smem<BLOCK_N>::kBytes, st>>>(ta, tb, a);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace ne
+
+using namespace ne;
+
+// dtype: 0 = bf16 operands, 1 = fp8 e4m3 operands with block scales (sa/sb required).
+// A [groups, M, K] (row stride lda, group stride a_gs), B [groups, N, K] (contiguous), D [groups, M, N] (row stride ldd).
+// masked_m: device int32 [groups] or null.  row_start: device int32 [groups] for the contiguous grouped layout (A and D
+// are then flat [M, *] matrices and masked_m holds the per-group row counts) or null.
+// Returns 0 or a CUDA / argument error code.
+extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void* B, void* D, long long ldd, long long d_gs,
+                       int M, int N, int K, int groups, const int* masked_m, const int* row_start, int dtype, const float* sa, int sa_ld,
+                       long long sa_gs, const float* sb, int out_fp32, int block_n_hint, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
+  const bool fp8 = dtype == 1;
+  if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % 16 != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
+  if (fp8 && (K % 128 != 0 || !sa || !sb)) return 1002;
+  if ((ldd * (out_fp32 ? 4 : 2)) % 16 != 0) return 1003;
+  const int m_blocks = (M + kBlockM - 1) / kBlockM;
+  // pick the widest N tile that still yields about one tile per SM; fp8 promotion keeps BLOCK_N accumulators in registers
+  int bn = block_n_hint;
+  if (bn == 0) {
+    const int cands[4] = {256, 128, 64, 32};
+    bn = 32;
+    for (int c : cands) {
+      if (fp8 && c > 128) continue;
+      long long tiles = (long long)groups * m_blocks * ((N + c - 1) / c);
+      if (tiles >= num_sms() || c == 32) { bn = c; break; }
+    }
+    if (!fp8 && bn == 256 && N % 256 != 0 && N < 2048) bn = 128;
+  }
+  if (fp8 && bn > 128) bn = 128;
+  CUtensorMap ta, tb;
+  if (row_start || groups == 1) a_gs = (long long)M * lda;
+  int rc = get_tmap_kmajor(&ta, A, fp8, (uint64_t)K, (uint64_t)M, (uint64_t)(row_start ? 1 : groups), (uint64_t)lda, (uint64_t)a_gs, kBlockM);
+  if (rc) return 2000 + rc;
+  rc = get_tmap_kmajor(&tb, B, fp8, (uint64_t)K, (uint64_t)N, (uint64_t)groups, (uint64_t)K, (uint64_t)N * K, (uint32_t)bn);
+  if (rc) return 3000 + rc;
+  GemmArgs a;
+  a.a_group_inner = (!row_start && groups > 1 && a_gs < lda) ? 1 : 0;
+  a.M = M; a.N = N; a.K = K; a.groups = groups; a.masked_m = masked_m; a.row_start = row_start; a.D = D; a.ldd = ldd; a.d_group_stride = d_gs;
+  if (row_start) { a.d_group_stride = 0; sa_gs = 0; if (!masked_m) return 1004; }
+  a.sa = sa; a.sa_ld = sa_ld; a.sa_group_stride = sa_gs; a.sb = sb;
+  a.sb_group_stride = (long long)((N + 127) / 128) * (K / 128); a.out_fp32 = out_fp32;
+  long long tiles = (long long)groups * m_blocks * ((N + bn - 1) / bn);
+  int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+  if (fp8) {
+    switch (bn) {
+      case 128: return launch<128, true, true>(ta, tb, a, grid, stream);
+      case 64: return launch<64, true, true>(ta, tb, a, grid, stream);
+      default: return launch<32, true, true>(ta, tb, a, grid, stream);
+    }
+  }
+  switch (bn) {
+    case 256: return launch<256, false, false>(ta, tb, a, grid, stream);
+    case 128: return launch<128, false, false>(ta, tb, a, grid, stream);
+    case 64: return launch<64, false, false>(ta, tb, a, grid, stream);
+    default: return launch<32, false, false>(ta, tb, a, grid, stream);
+  }
+}
+
+extern "C" int ne_get_status(int* out8) {
+  return (int)cudaMemcpyFromSymbol(out8, g_status, sizeof(int) * 8);
+}
+extern "C" int ne_clear_status() {
+  int z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  return (int)cudaMemcpyToSymbol(g_status, z, sizeof(z));
+}

@@ -1,0 +1,195 @@
+// MoE routing and the token <-> expert-major layout transforms around the grouped GEMMs.
+//
+//   route    : sigmoid (+ correction bias, group-limited) or softmax top-k with renormalisation and scaling
+//   count    : per-expert token counts and each (token, k) pair's slot inside its expert
+//   scan     : 128-aligned exclusive prefix over the counts -> row_start[e] (every expert's rows start a GEMM tile)
+//   scatter  : write each routed token row into the expert-major buffer, quantising to e4m3 1x128 on the way
+//   combine  : out[t] = sum_k w[t,k] * Y[pos[t,k]] (+ shared-expert output), fixed k order -> deterministic
+// Everything data-dependent stays on the device, so the whole sequence is CUDA-graph capturable.
+//
+// Replaces in the reference: jit/sgl/csrc/moe/moe_fused_gate.cuh, triton/generic/fused_topk.py:26-129,
+// triton/hopper/fused_moe_v3.py:214-453 (ep_scatter / ep_gather), triton/generic/local_dispatch.py:25-84.
+#include "ptx.cuh"
+
+namespace ne {
+
+constexpr int kMaxExperts = 1024;
+
+// one warp per token
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx_out,
+                                                       float* __restrict__ w_out, int T, int E, int top_k, int n_group, int topk_group,
+                                                       int norm, float scale, int softmax) {
+  __shared__ float s_choice[4][kMaxExperts];
+  __shared__ float s_score[4][kMaxExperts];
+  __shared__ float s_group[4][64];
+  const int wl = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + wl;
+  if (t >= T) return;
+  float* choice = s_choice[wl]; float* score = s_score[wl]; float* gsc = s_group[wl];
+  const float* lr = logits + (long long)t * E;
+  if (softmax) {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, lr[e]);
+    m = warp_max(m);
+    float s = 0.f;
+    for (int e = lane; e < E; e += 32) { float v = __expf(lr[e] - m); score[e] = v; s += v; }
+    s = warp_sum(s);
+    float inv = 1.f / s;
+    for (int e = lane; e < E; e += 32) { score[e] *= inv; choice[e] = score[e] + (bias ? bias[e] : 0.f); }
+  } else {
+    for (int e = lane; e < E; e += 32) { float v = 1.f / (1.f + __expf(-lr[e])); score[e] = v; choice[e] = v + (bias ? bias[e] : 0.f); }
+  }
+  __syncwarp();
+  if (n_group > 1) {
+    const int gs = E / n_group;
+    for (int g = lane; g < n_group; g += 32) {
+      float a = -INFINITY, b = -INFINITY;      // two largest of the group
+      for (int j = 0; j < gs; j++) { float v = choice[g * gs + j]; if (v > a) { b = a; a = v; } else if (v > b) b = v; }
+      gsc[g] = a + b;
+    }
+    __syncwarp();
+    // keep the topk_group best groups (lowest index wins ties); lane g decides for group g
+    for (int g = lane; g < n_group; g += 32) {
+      int better = 0;
+      for (int h = 0; h < n_group; h++) better += (gsc[h] > gsc[g]) || (gsc[h] == gsc[g] && h < g);
+      if (better >= topk_group) for (int j = 0; j < gs; j++) choice[g * gs + j] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float wsum = 0.f;
+  for (int k = 0; k < top_k; k++) {
+    float best = -INFINITY; int bi = E;
+    for (int e = lane; e < E; e += 32) { float v = choice[e]; if (v > best) { best = v; bi = e; } }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (bi >= E) bi = 0;   // every remaining choice is -inf (cannot happen with valid arguments)
+    float sv = score[bi];
+    wsum += sv;
+    if (lane == 0) { idx_out[(long long)t * top_k + k] = bi; w_out[(long long)t * top_k + k] = sv; choice[bi] = -INFINITY; }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    float f = (norm ? 1.f / (wsum + 1e-20f) : 1.f) * scale;
+    for (int k = 0; k < top_k; k++) w_out[(long long)t * top_k + k] *= f;
+  }
+}
+
+// slot[t,k] = running index of the pair inside its (local) expert, counts[e] = pairs per expert
+__global__ void moe_count_kernel(const int* __restrict__ idx, int* __restrict__ counts, int* __restrict__ slot, int n_pairs, int expert_offset, int E_local) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs) return;
+  int e = idx[i] - expert_offset;
+  slot[i] = (e >= 0 && e < E_local) ? atomicAdd(&counts[e], 1) : -1;
+}
+
+// single CTA: row_start[e] = sum_{e' < e} align(counts[e'], align); row_start[E] = total
+__global__ void moe_scan_kernel(const int* __restrict__ counts, int* __restrict__ row_start, int E, int align) {
+  __shared__ int s[kMaxExperts + 1];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s[e] = (counts[e] + align - 1) / align * align;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; e++) { int c = s[e]; s[e] = acc; acc += c; }
+    s[E] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) row_start[e] = s[e];
+}
+
+// one warp per (token, k) pair; writes pos[t,k] (row in the expert-major buffer, -1 if not local / overflow)
+__global__ void moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx, const int* __restrict__ slot,
+                                   const int* __restrict__ row_start, int* __restrict__ pos, __nv_bfloat16* __restrict__ a_bf16,
+                                   uint8_t* __restrict__ a_q, float* __restrict__ a_s, int s_ld, int n_pairs, int top_k, int H,
+                                   int expert_offset, int E_local, int max_rows) {
+  int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (i >= n_pairs) return;
+  int e = idx[i] - expert_offset, sl = slot[i];
+  int row = -1;
+  if (e >= 0 && e < E_local && sl >= 0) { row = row_start[e] + sl; if (row >= max_rows) row = -1; }
+  if (lane == 0) pos[i] = row;
+  if (row < 0) return;
+  const __nv_bfloat16* xr = x + (long long)(i / top_k) * H;
+  if (a_q) {
+    for (int g = 0; g < H / 128; g++) {
+      uint2 v = *reinterpret_cast<const uint2*>(xr + g * 128 + lane * 4);
+      float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
+      float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+      amax = fmaxf(warp_max(amax), 1e-10f);
+      float is = 448.f / amax;
+      *reinterpret_cast<uint32_t*>(a_q + (long long)row * H + g * 128 + lane * 4) = pack_e4m3x4(a.x * is, a.y * is, b.x * is, b.y * is);
+      if (lane == 0) a_s[(long long)g * s_ld + row] = amax / 448.f;
+    }
+  } else {
+    for (int c = lane * 8; c < H; c += 256) *reinterpret_cast<uint4*>(a_bf16 + (long long)row * H + c) = *reinterpret_cast<const uint4*>(xr + c);
+  }
+}
+
+// one CTA per token
+__global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ w,
+                                                         const __nv_bfloat16* __restrict__ add_in, __nv_bfloat16* __restrict__ out, int top_k, int H) {
+  const int t = blockIdx.x;
+  __shared__ int s_pos[64]; __shared__ float s_w[64];
+  if (threadIdx.x < top_k) { s_pos[threadIdx.x] = pos[(long long)t * top_k + threadIdx.x]; s_w[threadIdx.x] = w[(long long)t * top_k + threadIdx.x]; }
+  __syncthreads();
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < top_k; k++) {
+      int r = s_pos[k];
+      if (r < 0) continue;
+      uint4 v = *reinterpret_cast<const uint4*>(y + (long long)r * H + c);
+      uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) { float2 f = unpack_bf16x2(u[j]); acc[2 * j] += s_w[k] * f.x; acc[2 * j + 1] += s_w[k] * f.y; }
+    }
+    if (add_in) {
+      // the routed sum is rounded to bf16 before the shared-expert output is added, as in the unfused form
+      uint4 v = *reinterpret_cast<const uint4*>(add_in + (long long)t * H + c);
+      uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float2 f = unpack_bf16x2(u[j]); float2 r = unpack_bf16x2(pack_bf16x2(acc[2 * j], acc[2 * j + 1]));
+        acc[2 * j] = r.x + f.x; acc[2 * j + 1] = r.y + f.y;
+      }
+    }
+    *reinterpret_cast<uint4*>(out + (long long)t * H + c) =
+        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
+}  // namespace ne
+
+using namespace ne;
+
+extern "C" int ne_moe_route(const float* logits, const float* bias, int* idx, float* w, int T, int E, int top_k, int n_group,
+                            int topk_group, int norm, float scale, int softmax, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (E > kMaxExperts || top_k > 64 || n_group > 64 || (n_group > 1 && E % n_group)) return 1001;
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, bias, idx, w, T, E, top_k, n_group, topk_group, norm, scale, softmax);
+  return (int)cudaGetLastError();
+}
+
+// counts [E_local] must be zero on entry.  Outputs: slot [T*K] (scratch), row_start [E_local+1], pos [T*K], and the
+// expert-major activations (bf16, or e4m3 + scales with leading dimension s_ld >= max_rows).
+extern "C" int ne_moe_dispatch_local(const void* x, const int* idx, int* counts, int* slot, int* row_start, int* pos, void* a_bf16,
+                                     void* a_q, float* a_s, int s_ld, int T, int top_k, int H, int expert_offset, int E_local,
+                                     int max_rows, int align, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (E_local > kMaxExperts || H % 128) return 1001;
+  int n = T * top_k;
+  moe_count_kernel<<<(n + 255) / 256, 256, 0, st>>>(idx, counts, slot, n, expert_offset, E_local);
+  moe_scan_kernel<<<1, 256, 0, st>>>(counts, row_start, E_local, align);
+  moe_scatter_kernel<<<(n + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, idx, slot, row_start, pos, (__nv_bfloat16*)a_bf16, (uint8_t*)a_q,
+                                                  a_s, s_ld, n, top_k, H, expert_offset, E_local, max_rows);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_moe_combine_local(const void* y, const int* pos, const float* w, const void* add_in, void* out, int T, int top_k, int H,
+                                    cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 || top_k > 64) return 1001;
+  moe_combine_kernel<<<T, 256, 0, st>>>((const __nv_bfloat16*)y, pos, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, top_k, H);
+  return (int)cudaGetLastError();
+}

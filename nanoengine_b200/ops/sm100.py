@@ -1,0 +1,299 @@
+"""CUDA (sm_100a) bodies of the operators: ctypes calls into ``_native/libne_kernels.so``.
+
+Every function mirrors the signature of its namesake in ``ops.reference``.  The library is loaded on first
+use and its absence is an error: on a GPU there is no silent PyTorch fallback.  Kernels run on the current
+torch stream; scratch buffers come from torch's caching allocator, which keeps the sequence capturable in
+CUDA graphs.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+from . import reference as ref
+
+FP8 = torch.float8_e4m3fn
+_LIB = None
+_c = ctypes
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_native", "libne_kernels.so")
+        if not os.path.exists(path):
+            raise RuntimeError(f"CUDA kernel library missing: {path}; run `python -m nanoengine_b200.build_native`")
+        _LIB = ctypes.CDLL(path)
+        for name in dir(_LIB):
+            pass
+    return _LIB
+
+
+def _p(t: Optional[torch.Tensor]):
+    return _c.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _st():
+    return _c.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ck(rc: int, name: str):
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+
+
+def kernel_status():
+    """Status words written by a kernel whose bounded wait ran out (all zero = healthy)."""
+    buf = (_c.c_int * 8)()
+    _ck(lib().ne_get_status(buf), "ne_get_status")
+    return list(buf)
+
+
+def clear_kernel_status():
+    _ck(lib().ne_clear_status(), "ne_clear_status")
+
+
+# ---- GEMM ----------------------------------------------------------------------------------------
+def _gemm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, row_start, fp8, sa, sa_ld, sa_gs, sb, out_fp32, bn=0):
+    rc = lib().ne_gemm(_p(A), _c.c_longlong(lda), _c.c_longlong(a_gs), _p(B), _p(D), _c.c_longlong(ldd), _c.c_longlong(d_gs),
+                       _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), _p(masked_m), _p(row_start), _c.c_int(1 if fp8 else 0),
+                       _p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(1 if out_fp32 else 0), _c.c_int(bn), _st())
+    _ck(rc, "ne_gemm")
+
+
+def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False):
+    """bf16 [T, K] -> (e4m3 [T, K], scales [T, K/128]).  The kernel writes scales column-major ([K/128, T]);
+    the returned view presents them in the reference's [T, K/128] orientation."""
+    assert not ue8m0, "UE8M0 scales are not produced by the CUDA path"
+    T, K = x.shape
+    x = x if x.stride(-1) == 1 else x.contiguous()
+    q = torch.empty(T, K, dtype=FP8, device=x.device)
+    s = torch.empty(K // 128, T, dtype=torch.float32, device=x.device)
+    _ck(lib().ne_quant_1x128(_p(x), _c.c_longlong(x.stride(0)), _p(q), _p(s), _c.c_int(T), _c.c_int(T), _c.c_int(K), _st()), "ne_quant_1x128")
+    return q, s.t()
+
+
+def _as_bf16_2d(x):
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.dtype != torch.bfloat16:
+        x2 = x2.to(torch.bfloat16)
+    if x2.stride(-1) != 1 or (x2.stride(0) * 2) % 16 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    return x2
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, bias=None, out_fp32: bool = False) -> torch.Tensor:
+    N, K = w.shape
+    x2 = _as_bf16_2d(x)
+    T = x2.shape[0]
+    out = torch.empty(T, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+    if T > 0:
+        if w.dtype == FP8:
+            q = torch.empty(T, K, dtype=FP8, device=x.device)
+            s = torch.empty(K // 128, T, dtype=torch.float32, device=x.device)
+            _ck(lib().ne_quant_1x128(_p(x2), _c.c_longlong(x2.stride(0)), _p(q), _p(s), _c.c_int(T), _c.c_int(T), _c.c_int(K), _st()), "ne_quant_1x128")
+            _gemm(q, K, 0, w, out, N, 0, T, N, K, 1, None, None, True, s, T, 0, w_scale, out_fp32)
+        else:
+            assert w.dtype == torch.bfloat16, "CUDA linears take bf16 or fp8 weights"
+            _gemm(x2, x2.stride(0), 0, w, out, N, 0, T, N, K, 1, None, None, False, None, 0, 0, None, out_fp32)
+    if bias is not None:
+        out = out + bias
+    return out.view(*x.shape[:-1], N)
+
+
+_BF16_CACHE = {}
+
+
+def _cached(key_t: torch.Tensor, tag: str, fn):
+    key = (key_t.data_ptr(), tuple(key_t.shape), tag)
+    v = _BF16_CACHE.get(key)
+    if v is None:
+        v = fn(key_t)
+        _BF16_CACHE[key] = v
+    return v
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    wb = _cached(w, "bf16", lambda t: t.to(torch.bfloat16).contiguous())
+    return linear(x, wb, out_fp32=True)
+
+
+def lm_head(hidden: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return linear(hidden, w, out_fp32=True)
+
+
+def bmm_absorb(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [T, H, A] (any row/head strides, unit inner stride), w [H, A, B] -> [T, H, B]: a grouped GEMM with one group per head."""
+    T, H, A = x.shape
+    Bd = w.shape[2]
+    wt = _cached(w, "t", lambda t: t.to(torch.bfloat16).transpose(1, 2).contiguous())      # [H, B, A], K-major
+    if x.dtype != torch.bfloat16 or x.stride(2) != 1 or (x.stride(0) * 2) % 16 or (x.stride(1) * 2) % 16 or x.data_ptr() % 16:
+        x = x.to(torch.bfloat16).contiguous()
+    out = torch.empty(T, H, Bd, dtype=torch.bfloat16, device=x.device)
+    if T > 0:
+        _gemm(x, x.stride(0), x.stride(1), wt, out, H * Bd, Bd, T, Bd, A, H, None, None, False, None, 0, 0, None, False)
+    return out
+
+
+# ---- norms / activation ----------------------------------------------------------------------------
+def _rmsnorm(x, res_in, w, eps, want_res):
+    T, H = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    res_out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if want_res else None
+    if res_in is not None:
+        res_in = res_in.contiguous()
+    _ck(lib().ne_rmsnorm(_p(x), _c.c_longlong(x.stride(0)), _p(res_in), _p(w), _p(out), _c.c_longlong(H), _p(res_out), _p(None), _p(None),
+                         _c.c_int(0), _c.c_int(T), _c.c_int(H), _c.c_float(eps), _st()), "ne_rmsnorm")
+    return out, res_out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    if x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    return _rmsnorm(x, None, w, eps, False)[0]
+
+
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float):
+    if x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    if residual is None:
+        return _rmsnorm(x, None, w, eps, False)[0], x
+    return _rmsnorm(x, residual, w, eps, True)
+
+
+def layernorm(x, w, b, eps):
+    return ref.layernorm(x, w, b, eps)
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    T, I2 = x.shape
+    I = I2 // 2
+    x = x.contiguous()
+    y = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
+    _ck(lib().ne_silu_mul(_p(x), _p(y), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I), _st()), "ne_silu_mul")
+    return y
+
+
+# ---- rotary / KV ----------------------------------------------------------------------------------
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """Rotates `x` in place (x may be a strided view of the projection output) and returns it."""
+    assert x.dtype == torch.bfloat16 and x.stride(-1) == 1
+    T, D = x.shape[0], x.shape[-1]
+    heads, hs = (x.shape[1], x.stride(1)) if x.dim() == 3 else (1, 0)
+    pos = positions if positions.dtype == torch.int64 else positions.long()
+    _ck(lib().ne_rope(_p(x), _c.c_longlong(x.stride(0)), _c.c_int(hs), _c.c_int(heads), _c.c_int(0), _c.c_int(D), _p(pos), _p(cache),
+                      _c.c_int(1 if interleaved else 0), _c.c_int(T), _st()), "ne_rope")
+    return x
+
+
+def mla_kv_store(cache: torch.Tensor, slot_mapping: torch.Tensor, ckv: torch.Tensor, k_pe: torch.Tensor) -> None:
+    T, R = ckv.shape
+    rope = k_pe.shape[1]
+    assert ckv.stride(1) == 1 and k_pe.stride(1) == 1
+    fp8 = cache.dtype == FP8
+    assert fp8 or cache.dtype == torch.bfloat16
+    _ck(lib().ne_mla_kv_store(_p(ckv), _c.c_longlong(ckv.stride(0)), _p(k_pe), _c.c_longlong(k_pe.stride(0)), _p(cache), _p(slot_mapping),
+                              _c.c_int(T), _c.c_int(R), _c.c_int(rope), _c.c_int(1 if fp8 else 0), _st()), "ne_mla_kv_store")
+
+
+def gqa_kv_store(k_cache, v_cache, slot_mapping, k, v):
+    return ref.gqa_kv_store(k_cache, v_cache, slot_mapping, k, v)
+
+
+# ---- MoE -----------------------------------------------------------------------------------------
+def moe_route(logits, bias, top_k, n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=1.0, scoring="sigmoid"):
+    T, E = logits.shape
+    logits = logits.float().contiguous()
+    idx = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    _ck(lib().ne_moe_route(_p(logits), _p(bias), _p(idx), _p(w), _c.c_int(T), _c.c_int(E), _c.c_int(top_k), _c.c_int(n_group), _c.c_int(topk_group),
+                           _c.c_int(1 if norm_topk_prob else 0), _c.c_float(routed_scaling_factor), _c.c_int(0 if scoring == "sigmoid" else 1), _st()),
+        "ne_moe_route")
+    return idx, w
+
+
+def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0, add_in=None) -> torch.Tensor:
+    """Local routed experts over an expert-major, 128-row-aligned layout: scatter (+fp8 quant) -> grouped GEMM ->
+    SwiGLU (+requant) -> grouped GEMM -> weighted gather.  `add_in` (e.g. the shared-expert output) is summed in the gather."""
+    T, H = x.shape
+    E, I2, _ = w13.shape
+    I = I2 // 2
+    K = topk_idx.shape[1]
+    dev = x.device
+    fp8 = w13.dtype == FP8
+    x = _as_bf16_2d(x)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    if T == 0:
+        return out
+    R = T * K + E * 127
+    R = (R + 127) // 128 * 128
+    meta = torch.zeros(E + (E + 1) + 2 * T * K, dtype=torch.int32, device=dev)
+    counts, row_start = meta[:E], meta[E:2 * E + 1]
+    slot, pos = meta[2 * E + 1:2 * E + 1 + T * K], meta[2 * E + 1 + T * K:]
+    idx = topk_idx.to(torch.int32).contiguous()
+    w = topk_w.float().contiguous()
+    if fp8:
+        a_q = torch.empty(R, H, dtype=FP8, device=dev)
+        a_s = torch.empty(H // 128, R, dtype=torch.float32, device=dev)
+        a_b = None
+    else:
+        a_b = torch.empty(R, H, dtype=torch.bfloat16, device=dev)
+        a_q = a_s = None
+    _ck(lib().ne_moe_dispatch_local(_p(x), _p(idx), _p(counts), _p(slot), _p(row_start), _p(pos), _p(a_b), _p(a_q), _p(a_s), _c.c_int(R),
+                                    _c.c_int(T), _c.c_int(K), _c.c_int(H), _c.c_int(expert_offset), _c.c_int(E), _c.c_int(R), _c.c_int(128), _st()),
+        "ne_moe_dispatch_local")
+    g = torch.empty(R, I2, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(R, H, dtype=torch.bfloat16, device=dev)
+    if fp8:
+        _gemm(a_q, H, 0, w13, g, I2, 0, R, I2, H, E, counts, row_start, True, a_s, R, 0, w13_scale, False)
+        h_q = torch.empty(R, I, dtype=FP8, device=dev)
+        h_s = torch.empty(I // 128, R, dtype=torch.float32, device=dev)
+        _ck(lib().ne_silu_mul(_p(g), _p(None), _p(h_q), _p(h_s), _c.c_int(R), _c.c_longlong(0), _p(None), _c.c_int(1), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
+        _gemm(h_q, I, 0, w2, y, H, 0, R, H, I, E, counts, row_start, True, h_s, R, 0, w2_scale, False)
+    else:
+        _gemm(a_b, H, 0, w13, g, I2, 0, R, I2, H, E, counts, row_start, False, None, 0, 0, None, False)
+        h = torch.empty(R, I, dtype=torch.bfloat16, device=dev)
+        _ck(lib().ne_silu_mul(_p(g), _p(h), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(None), _c.c_int(1), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
+        _gemm(h, I, 0, w2, y, H, 0, R, H, I, E, counts, row_start, False, None, 0, 0, None, False)
+    _ck(lib().ne_moe_combine_local(_p(y), _p(pos), _p(w), _p(add_in), _p(out), _c.c_int(T), _c.c_int(K), _c.c_int(H), _st()), "ne_moe_combine_local")
+    return out
+
+
+# ---- attention / sampling: filled in by the dedicated kernel modules ---------------------------------
+def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scale, kv_lora_rank, sparse_indices=None):
+    from . import sm100_attn
+    return sm100_attn.mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scale, kv_lora_rank, sparse_indices)
+
+
+def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale):
+    from . import sm100_attn
+    return sm100_attn.gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale)
+
+
+def sample(logits, temperatures, generator=None, return_logprobs=False):
+    from . import sm100_attn
+    return sm100_attn.sample(logits, temperatures, generator, return_logprobs)
+
+
+def dequant_fp8_block(q, s, block=128):
+    return ref.dequant_fp8_block(q, s, block)
+
+
+def quant_fp8_block(w, block=128):
+    return ref.quant_fp8_block(w, block)
+
+
+def merge_attention_states(o1, lse1, o2, lse2):
+    return ref.merge_attention_states(o1, lse1, o2, lse2)
+
+
+hadamard = ref.hadamard
+quant_fp8_per_token_pow2 = ref.quant_fp8_per_token_pow2
+indexer_logits = ref.indexer_logits
+indexer_topk = ref.indexer_topk
+logical_to_physical = ref.logical_to_physical
+dequant_fp8_1x128 = ref.dequant_fp8_1x128

@@ -1,0 +1,171 @@
+"""Numerics of every sm_100a kernel against the plain PyTorch fp32 statement of the same operator."""
+import pytest
+import torch
+
+from nanoengine_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+@pytest.fixture(scope="module")
+def k():
+    from nanoengine_b200.ops import sm100
+    sm100.lib()
+    sm100.clear_kernel_status()
+    yield sm100
+    assert sm100.kernel_status()[0] == 0, f"a kernel reported a timed-out wait: {sm100.kernel_status()}"
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (7, 576, 512), (128, 2112, 7168), (300, 7168, 2048), (1000, 1536, 1536), (4096, 4096, 4096)])
+def test_gemm_bf16(k, M, N, K):
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    got = k.linear(x, w)
+    want = x.float() @ w.float().t()
+    assert got.shape == (M, N) and _rel(got, want) < 5e-3
+    got32 = k.linear(x, w, out_fp32=True)
+    assert got32.dtype == torch.float32 and _rel(got32, want) < 1e-3
+
+
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+def test_gemm_bf16_every_tile_width(k, bn):
+    torch.manual_seed(1)
+    M, N, K = 200, 768, 1024
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    k._gemm(x, K, 0, w, out, N, 0, M, N, K, 1, None, None, False, None, 0, 0, None, False, bn)
+    assert _rel(out, x.float() @ w.float().t()) < 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (33, 2112, 7168), (128, 4096, 7168), (500, 7168, 2048), (2048, 2048, 2048)])
+def test_gemm_fp8_blockscaled(k, M, N, K):
+    torch.manual_seed(2)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda") * 0.05
+    wq, ws = ref.quant_fp8_block(w)
+    got = k.linear(x, wq, ws)
+    want = ref.linear(x, wq, ws)          # same quantisation recipe in fp32
+    assert _rel(got, want) < 5e-3
+    assert _rel(got, x.float() @ w.t()) < 6e-2   # and close to the unquantised product
+
+
+def test_quant_1x128_matches_reference(k):
+    torch.manual_seed(3)
+    x = torch.randn(77, 1024, device="cuda", dtype=torch.bfloat16) * 3
+    q, s = k.quant_fp8_1x128(x)
+    rq, rs = ref.quant_fp8_1x128(x)
+    assert torch.allclose(s, rs, rtol=1e-6)
+    assert _rel(ref.dequant_fp8_1x128(q, s.contiguous()), ref.dequant_fp8_1x128(rq, rs)) < 2e-2
+    assert (q.view(torch.uint8) != rq.view(torch.uint8)).float().mean() < 0.02   # rounding-mode ties only
+
+
+@pytest.mark.parametrize("T,H", [(1, 128), (5, 512), (64, 7168), (300, 1536)])
+def test_rmsnorm_and_fused_add(k, T, H):
+    torch.manual_seed(4)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+    assert _rel(k.rmsnorm(x, w, 1e-6), ref.rmsnorm(x, w, 1e-6)) < 4e-3
+    y, ro = k.add_rmsnorm(x, r, w, 1e-6)
+    ry, rro = ref.add_rmsnorm(x, r, w, 1e-6)
+    assert torch.equal(ro, rro) and _rel(y, ry) < 4e-3
+    # strided input view (a column slice of a wider projection output)
+    big = torch.randn(T, H + 64, device="cuda", dtype=torch.bfloat16)
+    assert _rel(k.rmsnorm(big[:, :H], w, 1e-6), ref.rmsnorm(big[:, :H], w, 1e-6)) < 4e-3
+
+
+def test_silu_and_mul(k):
+    torch.manual_seed(5)
+    x = torch.randn(37, 2 * 2048, device="cuda", dtype=torch.bfloat16)
+    assert _rel(k.silu_and_mul(x), ref.silu_and_mul(x)) < 4e-3
+
+
+def test_rope_in_place_on_strided_heads(k):
+    torch.manual_seed(6)
+    T, H, nope, rope = 19, 16, 128, 64
+    cache = ref.rope_cos_sin_cache(rope, 4096, 10000.0).cuda()
+    pos = torch.randint(0, 4096, (T,), device="cuda")
+    q = torch.randn(T, H, nope + rope, device="cuda", dtype=torch.bfloat16)
+    want = ref.apply_rope(q[..., nope:].clone(), pos, cache, True)
+    keep = q[..., :nope].clone()
+    got = k.apply_rope(q[..., nope:], pos, cache, True)
+    assert _rel(got, want) < 4e-3 and torch.equal(q[..., :nope], keep)
+    kp = torch.randn(T, 512 + rope, device="cuda", dtype=torch.bfloat16)
+    want = ref.apply_rope(kp[:, 512:].clone(), pos, cache, False)
+    assert _rel(k.apply_rope(kp[:, 512:], pos, cache, False), want) < 4e-3
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_mla_kv_store(k, fp8):
+    torch.manual_seed(7)
+    T, R, rope, nb, bs = 50, 512, 64, 8, 64
+    ckv = torch.randn(T, R, device="cuda", dtype=torch.bfloat16)
+    kpe = torch.randn(T, R + rope, device="cuda", dtype=torch.bfloat16)[:, R:]
+    slots = torch.randperm(nb * bs, device="cuda")[:T]
+    dt = FP8 if fp8 else torch.bfloat16
+    c1 = torch.zeros(nb, bs, R + rope, device="cuda", dtype=torch.uint8 if fp8 else dt)
+    c1 = c1.view(FP8) if fp8 else c1
+    c2 = c1.clone()
+    k.mla_kv_store(c1, slots, ckv, kpe)
+    ref.mla_kv_store(c2, slots, ckv, kpe)
+    assert torch.equal(c1.view(torch.uint8), c2.view(torch.uint8))
+
+
+@pytest.mark.parametrize("E,topk,ng,tg,scoring", [(256, 8, 8, 4, "sigmoid"), (128, 8, 1, 1, "softmax"), (8, 2, 1, 1, "sigmoid"), (64, 6, 4, 2, "sigmoid")])
+@pytest.mark.parametrize("T", [1, 16, 513])
+def test_moe_route(k, T, E, topk, ng, tg, scoring):
+    torch.manual_seed(8)
+    logits = torch.randn(T, E, device="cuda")
+    bias = torch.randn(E, device="cuda") * 0.1 if scoring == "sigmoid" else None
+    idx, w = k.moe_route(logits, bias, topk, ng, tg, True, 2.5, scoring)
+    ridx, rw = ref.moe_route(logits, bias, topk, ng, tg, True, 2.5, scoring)
+    assert torch.equal(idx.sort(-1).values, ridx.sort(-1).values)
+    assert torch.allclose(w.sum(-1), rw.sum(-1), rtol=1e-4)
+    o, ro = idx.argsort(-1), ridx.argsort(-1)
+    assert torch.allclose(w.gather(1, o), rw.gather(1, ro), rtol=1e-4, atol=1e-6)
+
+
+def test_bmm_absorb_on_strided_heads(k):
+    torch.manual_seed(9)
+    T, H = 40, 16
+    q = torch.randn(T, H, 192, device="cuda", dtype=torch.bfloat16)
+    kc = (torch.randn(H, 128, 512, device="cuda") * 0.05).to(torch.bfloat16)
+    got = k.bmm_absorb(q[..., :128], kc)
+    assert _rel(got, ref.bmm_absorb(q[..., :128], kc)) < 5e-3
+    o = torch.randn(T, H, 512, device="cuda", dtype=torch.bfloat16)
+    vc = (torch.randn(H, 512, 128, device="cuda") * 0.05).to(torch.bfloat16)
+    assert _rel(k.bmm_absorb(o, vc), ref.bmm_absorb(o, vc)) < 5e-3
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("T,E,topk", [(1, 8, 2), (64, 32, 8), (700, 16, 4)])
+def test_moe_experts_local(k, T, E, topk, fp8):
+    torch.manual_seed(10)
+    H, I = 512, 256
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w13 = torch.randn(E, 2 * I, H, device="cuda") * 0.05
+    w2 = torch.randn(E, H, I, device="cuda") * 0.05
+    logits = torch.randn(T, E, device="cuda")
+    idx, w = ref.moe_route(logits, None, topk, 1, 1, True, 1.0, "softmax")
+    if fp8:
+        w13q, s13 = ref.quant_fp8_block(w13)
+        w2q, s2 = ref.quant_fp8_block(w2)
+        got = k.moe_experts(x, idx, w, w13q, w2q, s13, s2, 0)
+        want = ref.moe_experts(x, idx, w, w13q, w2q, s13, s2, 0)
+    else:
+        got = k.moe_experts(x, idx, w, w13.bfloat16(), w2.bfloat16(), None, None, 0)
+        want = ref.moe_experts(x, idx, w, w13.bfloat16(), w2.bfloat16(), None, None, 0)
+    assert _rel(got, want) < 2e-2
+    # experts [E/2, E) only, as an EP rank would hold them
+    half = E // 2
+    if fp8:
+        got2 = k.moe_experts(x, idx, w, w13q[half:].contiguous(), w2q[half:].contiguous(), s13[half:].contiguous(), s2[half:].contiguous(), half)
+        want2 = ref.moe_experts(x, idx, w, w13q[half:], w2q[half:], s13[half:], s2[half:], half)
+        assert _rel(got2, want2) < 2e-2
