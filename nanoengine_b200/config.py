@@ -56,7 +56,7 @@ class Config:
     # execution
     enforce_eager: bool = False
     cuda_graph_max_bs: int = 256
-    executor_backend: str = "auto"           # auto | inproc | mp
+    executor_backend: str = "auto"           # auto | inproc | mp | spmd (one engine per torchrun rank)
     use_fused_comm: bool = True              # fused compute+collective kernels when peers are reachable
     dummy_eplb: bool = False
     # observability

@@ -1,0 +1,320 @@
+// Absorbed MLA attention over the paged fp8 latent cache on tcgen05 tensor cores (DeepSeek-V3 geometry: 576-value
+// rows = 512 latent + 64 rope, 512-value output, 64-token pages).  Serves decode (q_len 1..N+1) and absorbed prefill
+// alike: one CTA handles the heads (<= 128) of ONE query token, one half (256 values) of the output width and one
+// slice of the key pages; keys are causal-limited per token, so a prefix-cache hit or a chunked prefill needs no
+// separate gather/merge pass.
+//
+// Per 64-token page:  S = Q K^T   (18 x tcgen05.mma kind::f8f6f4, M=128 N=64 K=32, both operands K-major in smem)
+//                     online softmax by 128 threads (one per head) reading S from TMEM; P -> e4m3 -> smem
+//                     O += P V    (2 x tcgen05.mma, V is the same page tile read MN-major, N=256)
+// TMEM: S double-buffered (2 x 64 columns) + O (256 columns).  Shared memory: Q 72 KB, 4-page ring 144 KB, P 8 KB.
+// Warp 0: TMA producer; warp 1: MMA issuer; warps 2-5: softmax / rescale / epilogue.  All waits are bounded.
+// With more than one key slice the CTA writes a normalised partial result and its log2-sum-exp; ne_attn_merge folds them.
+//
+// fp8 contract (reference layers/backends/mla/trtllm.py:93-204): the query is clamped to +-448 and cast to e4m3 without
+// a scale, cache rows are clamped-cast e4m3, softmax scale is applied to the fp32 logits.
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace ne {
+
+constexpr int kMlaThreads = 192;
+constexpr int kKernelMla = 2;
+constexpr int kPage = 64, kDk = 576, kDv = 512, kVHalf = 256;
+constexpr int kQNope = 4 * 128 * 128;          // four 128-byte-wide panels of 128 rows
+constexpr int kQBytes = kQNope + 128 * 64;     // + rope panel (64 bytes wide)
+constexpr int kPgNope = 4 * kPage * 128;
+constexpr int kPgBytes = kPgNope + kPage * 64;
+constexpr int kPgStages = 4;
+constexpr int kPBytes = 128 * 64;
+constexpr int kMlaSmem = kQBytes + kPgStages * kPgBytes + kPBytes + 1024 + 256;
+
+struct MlaArgs {
+  const int* block_tables; int bt_stride;
+  const int* cu_seqlens_q; const int* context_lens; int num_seqs;
+  int T, H, splits;
+  float scale_log2;                  // softmax scale * log2(e)
+  __nv_bfloat16* out;                // [T, H, 512] (splits == 1)
+  float* part; float* lse2;          // [splits, T, H, 512], [splits, T, H] (splits > 1)
+};
+
+__global__ void __launch_bounds__(kMlaThreads, 1)
+mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant__ CUtensorMap tq64,
+               const __grid_constant__ CUtensorMap tk128, const __grid_constant__ CUtensorMap tk64, const MlaArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sPg = sQ + kQBytes;
+  uint8_t* sP = sPg + kPgStages * kPgBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
+  // q_full | pg_full[4] | pg_empty[4] | s_full[2] | s_empty[2] | p_full | p_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t b_qfull = smem_u32(bars), b_pgfull = smem_u32(bars + 1), b_pgempty = smem_u32(bars + 5);
+  const uint32_t b_sfull = smem_u32(bars + 9), b_sempty = smem_u32(bars + 11), b_pfull = smem_u32(bars + 13), b_pempty = smem_u32(bars + 14);
+
+  const int warp = threadIdx.x >> 5;
+  const int t = blockIdx.x, split = blockIdx.y, vhalf = blockIdx.z;
+
+  // sequence of this token, causal limit, page range of this split (uniform over the CTA)
+  int lo = 0, hi = a.num_seqs;
+  while (lo + 1 < hi) { int mid = (lo + hi) >> 1; if (a.cu_seqlens_q[mid] <= t) lo = mid; else hi = mid; }
+  const int seq = lo;
+  const int q_len = a.cu_seqlens_q[seq + 1] - a.cu_seqlens_q[seq];
+  const int limit = a.context_lens[seq] - q_len + (t - a.cu_seqlens_q[seq]);     // last visible key position
+  const int total_pages = limit >= 0 ? limit / kPage + 1 : 0;
+  const int per_split = (total_pages + a.splits - 1) / a.splits;
+  const int pg_begin = split * per_split;
+  const int pg_end = min(total_pages, pg_begin + per_split);
+  const int n_tiles = max(0, pg_end - pg_begin);
+  const int* bt = a.block_tables + (long long)seq * a.bt_stride;
+
+  if (threadIdx.x == 0) {
+    mbar_init(b_qfull, 1);
+    for (int i = 0; i < kPgStages; i++) { mbar_init(b_pgfull + 8 * i, 1); mbar_init(b_pgempty + 8 * i, 1); }
+    for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 4); }
+    mbar_init(b_pfull, 4); mbar_init(b_pempty, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 128;
+
+  if (warp == 0) {
+    if (n_tiles > 0 && elect_one()) {
+      const int qrow = t * a.H;
+      mbar_expect_tx(b_qfull, kQBytes);
+      for (int p = 0; p < 4; p++) tma_load_2d(smem_u32(sQ + p * 128 * 128), &tq128, b_qfull, p * 128, qrow);
+      tma_load_2d(smem_u32(sQ + kQNope), &tq64, b_qfull, 512, qrow);
+      for (int i = 0; i < n_tiles; i++) {
+        const int s = i % kPgStages;
+        if (!mbar_wait(b_pgempty + 8 * s, ((i / kPgStages) & 1) ^ 1, abort_flag, kKernelMla, 100 + s)) break;
+        const int block = bt[pg_begin + i];
+        uint8_t* dst = sPg + s * kPgBytes;
+        mbar_expect_tx(b_pgfull + 8 * s, kPgBytes);
+        for (int p = 0; p < 4; p++) tma_load_3d(smem_u32(dst + p * kPage * 128), &tk128, b_pgfull + 8 * s, p * 128, 0, block);
+        tma_load_3d(smem_u32(dst + kPgNope), &tk64, b_pgfull + 8 * s, 512, 0, block);
+      }
+    }
+  } else if (warp == 1) {
+    if (n_tiles > 0 && elect_one()) {
+      constexpr uint32_t kIdescQK = make_idesc(FMT_E4M3, FMT_E4M3, 128, kPage);
+      constexpr uint32_t kIdescPV = make_idesc(FMT_E4M3, FMT_E4M3, 128, kVHalf, 0, 1);   // B (= V) is MN-major
+      bool ok = mbar_wait(b_qfull, 0, abort_flag, kKernelMla, 200);
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      auto pv = [&](int j) -> bool {
+        if (!mbar_wait(b_pfull, j & 1, abort_flag, kKernelMla, 230)) return false;
+        tc_fence_after();
+        const int s = j % kPgStages;
+        const uint32_t pg = smem_u32(sPg + s * kPgBytes);
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+          uint64_t adesc = make_smem_desc(p_addr + ks * 32, 16, 512, SW_64B);
+          uint64_t bdesc = make_smem_desc(pg + (vhalf * 2) * kPage * 128 + ks * 32 * 128, 8192, 1024, SW_128B);
+          umma_f8(tmem_o, adesc, bdesc, kIdescPV, (j | ks) != 0);
+        }
+        tc_commit(b_pgempty + 8 * s);
+        tc_commit(b_pempty);
+        return true;
+      };
+      for (int i = 0; ok && i < n_tiles; i++) {
+        const int sb = i & 1, s = i % kPgStages;
+        if (!mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelMla, 210 + sb)) { ok = false; break; }
+        if (!mbar_wait(b_pgfull + 8 * s, (i / kPgStages) & 1, abort_flag, kKernelMla, 220 + s)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t pg = smem_u32(sPg + s * kPgBytes);
+        const uint32_t d = tmem_base + sb * kPage;
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ks++) {
+            uint64_t adesc = make_smem_desc(q_addr + p * 128 * 128 + ks * 32, 16, 1024, SW_128B);
+            uint64_t bdesc = make_smem_desc(pg + p * kPage * 128 + ks * 32, 16, 1024, SW_128B);
+            umma_f8(d, adesc, bdesc, kIdescQK, (p | ks) != 0);
+          }
+        }
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+          uint64_t adesc = make_smem_desc(q_addr + kQNope + ks * 32, 16, 512, SW_64B);
+          uint64_t bdesc = make_smem_desc(pg + kPgNope + ks * 32, 16, 512, SW_64B);
+          umma_f8(d, adesc, bdesc, kIdescQK, 1);
+        }
+        tc_commit(b_sfull + 8 * sb);
+        if (i > 0 && !pv(i - 1)) { ok = false; break; }
+      }
+      if (ok) pv(n_tiles - 1);
+    }
+  } else {
+    const int wq = warp & 3;
+    const int row = wq * 32 + (int)lane_id();
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const bool row_ok = row < a.H;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int i = 0; ok && i < n_tiles; i++) {
+      const int sb = i & 1;
+      if (!mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelMla, 300 + sb)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * kPage, r0);
+      tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * kPage + 32, r1);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane_id() == 0) mbar_arrive(b_sempty + 8 * sb);
+      const int key0 = (pg_begin + i) * kPage;
+      float tl[64];
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 64; j++) {
+        float s = __uint_as_float(j < 32 ? r0[j] : r1[j - 32]) * a.scale_log2;
+        tl[j] = (row_ok && key0 + j <= limit) ? s : -INFINITY;
+        m_tile = fmaxf(m_tile, tl[j]);
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
+      float psum = 0.f;
+      uint32_t pk[16];
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        float p0 = (m_new == -INFINITY) ? 0.f : exp2f(tl[4 * j] - m_new), p1 = (m_new == -INFINITY) ? 0.f : exp2f(tl[4 * j + 1] - m_new);
+        float p2 = (m_new == -INFINITY) ? 0.f : exp2f(tl[4 * j + 2] - m_new), p3 = (m_new == -INFINITY) ? 0.f : exp2f(tl[4 * j + 3] - m_new);
+        psum += (p0 + p1) + (p2 + p3);
+        pk[j] = pack_e4m3x4(p0, p1, p2, p3);
+      }
+      l_run = l_run * alpha + psum;
+      m_run = m_new;
+      if (i > 0) {
+        // P buffer and O are free once the previous page's P V product has retired
+        if (!mbar_wait(b_pempty, (i - 1) & 1, abort_flag, kKernelMla, 310)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha < 1.f)) {
+#pragma unroll 1
+          for (int cblk = 0; cblk < kVHalf / 16; cblk++) {
+            uint32_t o[16];
+            tmem_ld_32x32b_x16(tmem_o + lane_addr + cblk * 16, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st_32x32b_x16(tmem_o + lane_addr + cblk * 16, o);
+          }
+          tc_wait_st();
+        }
+      }
+      // P row (64 e4m3 = 4 chunks of 16 bytes) into the 64B-swizzled K-major layout the MMA reads
+      {
+        uint8_t* prow = sP + row * 64;
+        const int sw = (row >> 1) & 3;
+#pragma unroll
+        for (int cch = 0; cch < 4; cch++)
+          *reinterpret_cast<uint4*>(prow + ((cch ^ sw) << 4)) = make_uint4(pk[4 * cch], pk[4 * cch + 1], pk[4 * cch + 2], pk[4 * cch + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane_id() == 0) mbar_arrive(b_pfull);
+    }
+    if (ok && n_tiles > 0) ok = mbar_wait(b_pempty, (n_tiles - 1) & 1, abort_flag, kKernelMla, 320);
+    if (ok && n_tiles > 0) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const long long orow = (long long)t * a.H + row;
+#pragma unroll 1
+      for (int cblk = 0; cblk < kVHalf / 32; cblk++) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tmem_o + lane_addr + cblk * 32, o);
+        tc_wait_ld();
+        if (row_ok) {
+          if (a.splits == 1) {
+            __nv_bfloat16* dst = a.out + orow * kDv + vhalf * kVHalf + cblk * 32;
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+              *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(
+                  pack_bf16x2(__uint_as_float(o[v * 8]) * inv, __uint_as_float(o[v * 8 + 1]) * inv),
+                  pack_bf16x2(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv),
+                  pack_bf16x2(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv),
+                  pack_bf16x2(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv));
+            }
+          } else {
+            float* dst = a.part + ((long long)split * a.T * a.H + orow) * kDv + vhalf * kVHalf + cblk * 32;
+#pragma unroll
+            for (int v = 0; v < 8; v++)
+              *reinterpret_cast<float4*>(dst + v * 4) = make_float4(__uint_as_float(o[v * 4]) * inv, __uint_as_float(o[v * 4 + 1]) * inv,
+                                                                    __uint_as_float(o[v * 4 + 2]) * inv, __uint_as_float(o[v * 4 + 3]) * inv);
+          }
+        }
+      }
+    }
+    if (a.splits > 1 && vhalf == 0 && row_ok)
+      a.lse2[(long long)split * a.T * a.H + (long long)t * a.H + row] = (ok && l_run > 0.f) ? m_run + log2f(l_run) : -INFINITY;
+    if (a.splits == 1 && n_tiles == 0 && row_ok) {
+      // a token that sees no key (cannot happen for causal self-attention, kept for safety): zero output
+      __nv_bfloat16* dst = a.out + ((long long)t * a.H + row) * kDv + vhalf * kVHalf;
+      for (int cidx = 0; cidx < kVHalf; cidx += 8) *reinterpret_cast<uint4*>(dst + cidx) = make_uint4(0, 0, 0, 0);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) for (int i = 0; i < 2000; i++) __nanosleep(1000);
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// bf16 -> e4m3 with clamp, no scale (queries of the fp8 attention path)
+__global__ void cast_e4m3_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, long long n) {
+  long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  uint4 v = *reinterpret_cast<const uint4*>(x + i);
+  float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+  *reinterpret_cast<uint2*>(y + i) = make_uint2(pack_e4m3x4(a.x, a.y, b.x, b.y), pack_e4m3x4(c.x, c.y, d.x, d.y));
+}
+
+}  // namespace ne
+
+using namespace ne;
+
+extern "C" int ne_cast_e4m3(const void* x, void* y, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 8) return 1001;
+  cast_e4m3_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)y, n);
+  return (int)cudaGetLastError();
+}
+
+// q8 [T*H, 576] e4m3 (contiguous), cache [num_blocks, 64, 576] e4m3.  out bf16 [T, H, 512] when splits == 1, otherwise
+// part fp32 [splits, T, H, 512] + lse2 fp32 [splits, T, H] for ne_attn_merge.
+extern "C" int ne_mla_fp8(const void* q8, const void* cache, int num_blocks, const int* block_tables, int bt_stride,
+                          const int* cu_seqlens_q, const int* context_lens, int num_seqs, int T, int H, int splits, float scale,
+                          void* out, float* part, float* lse2, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H > 128 || H < 1 || splits < 1 || (splits > 1 && (!part || !lse2))) return 1001;
+  CUtensorMap tq128, tq64, tk128, tk64;
+  {
+    uint64_t dims[2] = {(uint64_t)kDk, (uint64_t)T * H}; uint64_t strides[1] = {(uint64_t)kDk};
+    uint32_t b128[2] = {128, 128}, b64[2] = {64, 128};
+    int rc = make_tmap(&tq128, q8, TMA_U8, 2, dims, strides, b128, TMA_SW_128); if (rc) return 2000 + rc;
+    rc = make_tmap(&tq64, q8, TMA_U8, 2, dims, strides, b64, TMA_SW_64); if (rc) return 2100 + rc;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)kDk, (uint64_t)kPage, (uint64_t)num_blocks}; uint64_t strides[2] = {(uint64_t)kDk, (uint64_t)kDk * kPage};
+    uint32_t b128[3] = {128, kPage, 1}, b64[3] = {64, kPage, 1};
+    int rc = make_tmap(&tk128, cache, TMA_U8, 3, dims, strides, b128, TMA_SW_128); if (rc) return 2200 + rc;
+    rc = make_tmap(&tk64, cache, TMA_U8, 3, dims, strides, b64, TMA_SW_64); if (rc) return 2300 + rc;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mla_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  MlaArgs a;
+  a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs;
+  a.T = T; a.H = H; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f; a.out = (__nv_bfloat16*)out; a.part = part; a.lse2 = lse2;
+  dim3 grid(T, splits, 2);
+  mla_fp8_kernel<<<grid, kMlaThreads, kMlaSmem, st>>>(tq128, tq64, tk128, tk64, a);
+  return (int)cudaGetLastError();
+}

@@ -157,8 +157,64 @@ class MultiprocExecutor:
         self.procs, self.conns = [], []
 
 
+class SpmdExecutor:
+    """One engine per rank, launched by torchrun (one process per GPU).  Every rank schedules the requests of its own
+    attention-DP shard; ranks only meet inside the model's collectives, so before each step they agree (one tiny host
+    all-reduce) whether anybody has work - a rank without work then runs a dummy batch to keep the collectives matched."""
+
+    def __init__(self, config: Config):
+        import torch.distributed as dist
+        from ..runtime.model_runner import ModelRunner
+        self.config = config
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world_size = int(os.environ.get("WORLD_SIZE", "1"))
+        if self.world_size != config.world_size:
+            raise ExecutorError(f"layout needs {config.world_size} ranks, launched with {self.world_size}")
+        use_cuda = config.device == "cuda" or (config.device == "auto" and torch.cuda.is_available())
+        local = int(os.environ.get("LOCAL_RANK", self.rank))
+        if self.world_size > 1 and not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            if use_cuda:
+                torch.cuda.set_device(local)
+                dist.init_process_group("cpu:gloo,cuda:nccl", rank=self.rank, world_size=self.world_size, device_id=torch.device(f"cuda:{local}"))
+            else:
+                dist.init_process_group("gloo", rank=self.rank, world_size=self.world_size)
+        self.runner = ModelRunner(config, self.rank, self.world_size, device=f"cuda:{local}" if use_cuda else "cpu")
+        self._host_group = None
+        if self.world_size > 1:
+            self._host_group = dist.new_group(list(range(self.world_size)), backend="gloo")
+
+    def collective_rpc(self, method: str, *args, **kw) -> List[Any]:
+        return [getattr(self.runner, method)(*args, **kw)]
+
+    def agree(self, has_work: bool, is_prefill: bool):
+        """(anybody has work, anybody prefills) across all ranks."""
+        if self.world_size == 1:
+            return has_work, is_prefill
+        import torch.distributed as dist
+        t = torch.tensor([int(has_work), int(is_prefill)], dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self._host_group)
+        return bool(t[0]), bool(t[1])
+
+    def min_over_ranks(self, v: int) -> int:
+        if self.world_size == 1:
+            return v
+        import torch.distributed as dist
+        t = torch.tensor([v], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self._host_group)
+        return int(t[0])
+
+    def run_batches(self, blobs: Sequence[bytes]) -> List[bytes]:
+        return [self.runner.run_from_bytes(blobs[0])]
+
+    def shutdown(self):
+        self.runner = None
+
+
 def build_executor(config: Config):
     backend = config.executor_backend
+    if backend == "spmd":
+        return SpmdExecutor(config)
     if backend == "auto":
         backend = "inproc" if config.world_size == 1 else "mp"
     if backend == "inproc":

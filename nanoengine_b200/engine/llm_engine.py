@@ -30,7 +30,7 @@ def build_scheduler_config(config: Config, num_blocks: int, plan_bits: int) -> "
     sc.max_num_seqs = config.max_num_seqs
     sc.max_num_batched_tokens = scheduler_token_budget(config)
     sc.max_model_len = config.max_model_len
-    sc.attention_dp = config.attention_dp
+    sc.attention_dp = 1 if config.executor_backend == "spmd" else config.attention_dp
     sc.mode = _MODE[config.mode]
     sc.num_speculative_tokens = config.num_speculative_tokens
     sc.enable_prefix_caching = config.enable_prefix_caching
@@ -51,6 +51,9 @@ class LLMEngine:
         self.executor.collective_rpc("init_model")
         counts = self.executor.collective_rpc("profile_num_blocks")
         self.num_blocks = int(min(counts))
+        self.spmd = config.executor_backend == "spmd"
+        if self.spmd:
+            self.num_blocks = self.executor.min_over_ranks(self.num_blocks)
         if self.num_blocks < 1:
             raise RuntimeError("no memory left for the KV cache; lower gpu_memory_utilization or the model size")
         from ..runtime.cache import make_cache_plan
@@ -83,6 +86,13 @@ class LLMEngine:
         res = self.scheduler.schedule()
         if res.migrations:
             self._run_migrations(res)
+        if self.spmd:
+            any_work, any_prefill = self.executor.agree(res.has_work, res.has_work and res.is_prefill)
+            if any_work and not res.has_work:
+                dummy = C.RunnerIn()
+                dummy.is_dummy, dummy.is_prefill = True, any_prefill
+                self.executor.run_batches([dummy.to_bytes()])
+                return []
         if not res.has_work:
             return []
         t0 = time.perf_counter()

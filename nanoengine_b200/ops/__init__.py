@@ -14,16 +14,16 @@ from . import reference
 _sm100 = None
 
 
-def sm100():
+def _get_sm100():
     global _sm100
     if _sm100 is None:
-        from . import sm100 as m
-        _sm100 = m
+        import importlib
+        _sm100 = importlib.import_module(__name__ + ".sm100")
     return _sm100
 
 
 def impl(t: torch.Tensor):
-    return sm100() if t.is_cuda else reference
+    return _get_sm100() if t.is_cuda else reference
 
 
 def __getattr__(name):

@@ -1,0 +1,111 @@
+"""CUDA-graph replay of the decode forward pass.
+
+One graph per batch-size bucket (1, 2, 4, 8, then multiples of 16 up to ``cuda_graph_max_bs``), captured lazily
+after an eager warm-up of the same shape, all sharing one memory pool and one set of persistent input buffers.
+Rows beyond the live batch point at the scratch page with context length 1, so a padded replay is valid work
+that touches no live sequence.
+
+Parity: reference runtime/runner/graph_runner.py:55 (_make_bs_list), :65-540 (DecodeGraphRunner: persistent
+buffers, shared pool, capture per size, run).
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .context import ForwardContext
+
+
+def make_bs_list(max_bs: int) -> List[int]:
+    out = [b for b in (1, 2, 4, 8) if b <= max_bs]
+    out += list(range(16, max_bs + 1, 16))
+    if max_bs not in out:
+        out.append(max_bs)
+    return sorted(set(out))
+
+
+class DecodeGraphRunner:
+    def __init__(self, runner, q_len: int = 1):
+        self.r = runner
+        self.q_len = q_len
+        cfg = runner.config
+        self.max_bs = min(cfg.cuda_graph_max_bs, cfg.max_num_seqs)
+        self.bs_list = make_bs_list(self.max_bs)
+        bs = runner.plan.block_size
+        self.max_blocks = (cfg.max_model_len + bs - 1) // bs + 1
+        dev = runner.device
+        n = self.max_bs * q_len
+        self.input_ids = torch.zeros(n, dtype=torch.long, device=dev)
+        self.positions = torch.zeros(n, dtype=torch.long, device=dev)
+        self.slot_mapping = torch.zeros(n, dtype=torch.long, device=dev)
+        self.context_lens = torch.ones(self.max_bs, dtype=torch.int32, device=dev)
+        self.block_tables = torch.zeros(self.max_bs, self.max_blocks, dtype=torch.int32, device=dev)
+        self.cu_seqlens_q = (torch.arange(self.max_bs + 1, dtype=torch.int32, device=dev) * q_len)
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.outputs: Dict[int, torch.Tensor] = {}
+        self.pool = None
+
+    def bucket(self, n: int) -> int:
+        for b in self.bs_list:
+            if b >= n:
+                return b
+        return -1
+
+    def can_run(self, ctx: ForwardContext) -> bool:
+        return (ctx.q_len_uniform == self.q_len and ctx.num_seqs <= self.max_bs and ctx.block_tables.shape[1] <= self.max_blocks
+                and self.bucket(ctx.num_seqs) > 0)
+
+    def _static_ctx(self, b: int) -> ForwardContext:
+        q = self.q_len
+        return ForwardContext(
+            is_prefill=False, num_seqs=b, num_tokens=b * q, cu_seqlens_q=self.cu_seqlens_q[: b + 1], context_lens=self.context_lens[:b],
+            slot_mapping=self.slot_mapping[: b * q], block_tables=self.block_tables[:b], max_seqlen_q=q,
+            max_seqlen_k=self.r.config.max_model_len, last_token_indices=None, q_len_uniform=q,
+            kv_caches=self.r.cache.layers, indexer_caches=self.r.cache.indexer_layers)
+
+    def _fill(self, ids, pos, ctx: ForwardContext, b: int):
+        n, q = ctx.num_seqs, self.q_len
+        sb = self.r.cache.scratch_block
+        self.input_ids[: n * q].copy_(ids)
+        self.positions[: n * q].copy_(pos)
+        self.slot_mapping[: n * q].copy_(ctx.slot_mapping)
+        self.context_lens[:n].copy_(ctx.context_lens)
+        w = ctx.block_tables.shape[1]
+        self.block_tables[:n, :w].copy_(ctx.block_tables)
+        if n < b:
+            # padding rows: q_len tokens of a one-page sequence on the scratch page
+            self.input_ids[n * q: b * q].zero_()
+            self.positions[n * q: b * q].copy_(torch.arange(q, device=ids.device).repeat(b - n))
+            self.slot_mapping[n * q: b * q].copy_(sb * self.r.plan.block_size + torch.arange(q, device=ids.device).repeat(b - n))
+            self.context_lens[n:b].fill_(q)
+            self.block_tables[n:b].fill_(sb)
+
+    def _capture(self, b: int):
+        sctx = self._static_ctx(b)
+        q = self.q_len
+        ids, pos = self.input_ids[: b * q], self.positions[: b * q]
+        # eager warm-up on the side stream: sets kernel attributes, fills caches of derived weights, sizes the allocator
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self.r.model(ids, pos, sctx)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self.pool):
+            out = self.r.model(ids, pos, sctx)
+        if self.pool is None:
+            self.pool = g.pool()
+        self.graphs[b], self.outputs[b] = g, out
+
+    def run(self, ids, pos, ctx: ForwardContext) -> torch.Tensor:
+        b = self.bucket(ctx.num_seqs)
+        # the padding rows must be in place before a capture too: the warm-up runs on them
+        self._fill(ids, pos, ctx, b)
+        if b not in self.graphs:
+            self._capture(b)
+            self._fill(ids, pos, ctx, b)
+        self.graphs[b].replay()
+        return self.outputs[b][: ctx.num_seqs * self.q_len]
