@@ -40,9 +40,14 @@ def _st():
     return _c.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+LAUNCHES = [0]          # kernels of this library launched so far (a call that launches several counts them all)
+_KERNELS_PER_CALL = {"ne_moe_dispatch_local": 3}
+
+
 def _ck(rc: int, name: str):
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")
+    LAUNCHES[0] += _KERNELS_PER_CALL.get(name, 1)
 
 
 def kernel_status():

@@ -81,6 +81,9 @@ class ModelRunner:
         self.graphs = None
         self.mtp_runner = None
         self._profiler = None
+        self.h2d_bytes = 0          # bytes copied host -> device for step inputs (benchmark bookkeeping)
+        self.d2h_bytes = 0          # bytes read back (sampled tokens, log-probabilities)
+        self._last_decode = None
         self.plan = make_cache_plan(self.mc, config.resolved_kv_dtype(), config.kvcache_block_size, config.attention_tp,
                                     num_mtp_layers=self._num_mtp_layers(), use_indexer=config.use_nsa())
 
@@ -175,6 +178,7 @@ class ModelRunner:
         if dtype is not None:
             t = t.to(dtype)
         if self.device.type == "cuda":
+            self.h2d_bytes += t.numel() * t.element_size()
             return t.pin_memory().to(self.device, non_blocking=True)
         return t
 
@@ -248,15 +252,50 @@ class ModelRunner:
         if not mask.all():
             rows = rows[torch.from_numpy(mask).to(rows.device)]
         logits = self.model.compute_logits(hidden[rows])
-        temps = torch.tensor([t for t, m in zip(b.temperatures, mask) if m], dtype=torch.float32, device=self.device)
+        temps = self._to_dev(np.asarray([t for t, m in zip(b.temperatures, mask) if m], dtype=np.float32))
         tok, lp = self.sampler(logits, temps, b.any_return_logprobs)
         self.timer.forward_end()
         self.timer.start("d2h")
         toks = tok.tolist()
         lps = lp.tolist() if lp is not None else None
+        self.d2h_bytes += tok.numel() * tok.element_size() + (lp.numel() * 4 if lp is not None else 0)
         self.timer.stop()
+        if not ctx.is_prefill:
+            self._last_decode = (ctx, temps)
         ids = [s for s, m in zip(b.seq_ids, mask) if m]
         return C.RunnerOut(ids, [[t] for t in toks], None if lps is None else [[x] for x in lps])
+
+    # ---- benchmark helpers ----------------------------------------------------------------------
+    @torch.inference_mode()
+    def make_resident_decode_step(self):
+        """A closure that repeats the most recent decode step (forward + lm_head + sampling) on inputs already on the device."""
+        if self._last_decode is None:
+            raise RuntimeError("run a decode step first")
+        ctx, temps = self._last_decode
+        ids, pos = ctx.extras["input_ids"], ctx.extras["positions"]
+        rows = ctx.last_token_indices.long()
+
+        @torch.inference_mode()
+        def step():
+            hidden = self.forward(ctx)
+            logits = self.model.compute_logits(hidden[rows])
+            return self.sampler(logits, temps, False)[0]
+
+        return step
+
+    @torch.inference_mode()
+    def count_step_launches(self) -> int:
+        """Kernels of this library launched by one decode step, counted on an eager (non-graph) run of the last step."""
+        from ..ops import sm100
+        if self._last_decode is None:
+            raise RuntimeError("run a decode step first")
+        ctx, temps = self._last_decode
+        before = sm100.LAUNCHES[0]
+        hidden = self.model(ctx.extras["input_ids"], ctx.extras["positions"], ctx)
+        logits = self.model.compute_logits(hidden[ctx.last_token_indices.long()])
+        self.sampler(logits, temps, False)
+        torch.cuda.synchronize()
+        return sm100.LAUNCHES[0] - before
 
     def run_from_bytes(self, blob: bytes) -> bytes:
         return self.run_batch(C.RunnerIn.from_bytes(blob)).to_bytes()
