@@ -141,9 +141,11 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
   if (lane == 0) sc[(long long)g * sc_gs + (long long)c * sc_ld + row] = amax / kFp8Max;
 }
 
-// In-place rotary embedding on dims [off, off+D) of each of `heads` heads of every row.
+// Rotary embedding on dims [off, off+D) of each of `heads` heads of every row; the result goes to `y` (which may be `x`
+// itself for the in-place form, or a differently strided buffer such as the rope tail of the absorbed-query tensor).
 // cache [max_pos, D] fp32 (cos | sin).  interleaved: pairs (2i, 2i+1); otherwise pairs (i, i + D/2).
-__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long row_stride, int head_stride, int heads, int off, int D,
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, long long row_stride, int head_stride, __nv_bfloat16* __restrict__ y,
+                            long long y_row_stride, int y_head_stride, int heads, int off, int D,
                             const long long* __restrict__ positions, const float* __restrict__ cache, int interleaved, int T) {
   int half = D / 2;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -152,11 +154,12 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long row_stride,
   int i = (int)(idx % half); long long r = idx / half; int h = (int)(r % heads); int t = (int)(r / heads);
   const float* cs = cache + positions[t] * D;
   float c = cs[i], s = cs[half + i];
-  __nv_bfloat16* p = x + (long long)t * row_stride + (long long)h * head_stride + off;
+  const __nv_bfloat16* p = x + (long long)t * row_stride + (long long)h * head_stride + off;
+  __nv_bfloat16* q = y + (long long)t * y_row_stride + (long long)h * y_head_stride;
   int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
   float a = __bfloat162float(p[ia]), b = __bfloat162float(p[ib]);
-  p[ia] = __float2bfloat16(a * c - b * s);
-  p[ib] = __float2bfloat16(b * c + a * s);
+  q[ia] = __float2bfloat16(a * c - b * s);
+  q[ib] = __float2bfloat16(b * c + a * s);
 }
 
 // cache row = [ckv (R) | k_pe (rope)], bf16 or e4m3 (clamped cast, no scale).  One warp per token.
@@ -228,11 +231,12 @@ extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld
   return (int)cudaGetLastError();
 }
 
-extern "C" int ne_rope(void* x, long long row_stride, int head_stride, int heads, int off, int D, const long long* positions,
-                       const float* cache, int interleaved, int T, cudaStream_t st) {
+extern "C" int ne_rope(const void* x, long long row_stride, int head_stride, void* y, long long y_row_stride, int y_head_stride, int heads,
+                       int off, int D, const long long* positions, const float* cache, int interleaved, int T, cudaStream_t st) {
   if (T <= 0) return 0;
   long long total = (long long)T * heads * (D / 2);
-  rope_kernel<<<(int)((total + 255) / 256), 256, 0, st>>>((__nv_bfloat16*)x, row_stride, head_stride, heads, off, D, positions, cache, interleaved, T);
+  rope_kernel<<<(int)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, row_stride, head_stride, (__nv_bfloat16*)y, y_row_stride,
+                                                          y_head_stride, heads, off, D, positions, cache, interleaved, T);
   return (int)cudaGetLastError();
 }
 

@@ -80,17 +80,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   constexpr int kElemsPerStageK = kFP8 ? 128 : 64;
   constexpr int kUmmaK = kFP8 ? 32 : 16;
   constexpr int kMmasPerStage = kElemsPerStageK / kUmmaK;     // 4
-  constexpr uint32_t kTmemCols = (2 * BLOCK_N) < 32 ? 32 : 2 * BLOCK_N;
+  // TMEM accumulator ring: block-scaled GEMMs hand one accumulator per K block to the epilogue, so they use the
+  // deepest ring 512 columns allow (up to 4); plain GEMMs hand over one per tile and need two.
+  constexpr int kAcc = kBlockScaled ? ((512 / BLOCK_N) > 4 ? 4 : (512 / BLOCK_N)) : 2;
+  constexpr uint32_t kTmemCols = (kAcc * BLOCK_N) < 32 ? 32 : kAcc * BLOCK_N;
   constexpr uint32_t kIdesc = make_idesc(kFP8 ? FMT_E4M3 : FMT_BF16, kFP8 ? FMT_E4M3 : FMT_BF16, kBlockM, BLOCK_N);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
-  // bars: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  // bars: full[kStages], empty[kStages], tmem_full[kAcc], tmem_empty[kAcc]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAcc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
-  const uint32_t tfull0 = smem_u32(bars + 2 * kStages), tempty0 = smem_u32(bars + 2 * kStages + 2);
+  const uint32_t tfull0 = smem_u32(bars + 2 * kStages), tempty0 = smem_u32(bars + 2 * kStages + kAcc);
   const uint32_t smem_base = smem_u32(smem);
 
   const int warp = threadIdx.x >> 5;
@@ -99,7 +102,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4); }
+    for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_b);
@@ -157,11 +160,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             else umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
           }
           tc_commit(empty0 + 8 * stage);                // smem slot reusable once these MMAs retire
-          if (kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == 2) { buf = 0; bphase ^= 1; } }
+          if (kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == kAcc) { buf = 0; bphase ^= 1; } }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        if (!kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == 2) { buf = 0; bphase ^= 1; } }
+        if (!kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == kAcc) { buf = 0; bphase ^= 1; } }
       }
     }
   } else {
@@ -187,17 +190,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (!mbar_wait(tfull0 + 8 * buf, bphase, abort_flag, kKernelGemm, 400 + buf)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < BLOCK_N / 32; c++) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + c * 32, r);
+          for (int c = 0; c < BLOCK_N / 32; c += 2) {
+            // two TMEM loads in flight per wait
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + c * 32, r0);
+            if (c + 1 < BLOCK_N / 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + (c + 1) * 32, r1);
             tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; j++) acc[c * 32 + j] = fmaf(s, __uint_as_float(r[j]), acc[c * 32 + j]);
+            for (int j = 0; j < 32; j++) acc[c * 32 + j] = fmaf(s, __uint_as_float(r0[j]), acc[c * 32 + j]);
+            if (c + 1 < BLOCK_N / 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) acc[(c + 1) * 32 + j] = fmaf(s, __uint_as_float(r1[j]), acc[(c + 1) * 32 + j]);
+            }
           }
           tc_fence_before();
           __syncwarp();
           if (lane_id() == 0) mbar_arrive(tempty0 + 8 * buf);
-          if (++buf == 2) { buf = 0; bphase ^= 1; }
+          if (++buf == kAcc) { buf = 0; bphase ^= 1; }
         }
         if (!ok) break;
         if (row_ok) {
@@ -249,7 +258,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         tc_fence_before();
         __syncwarp();
         if (lane_id() == 0) mbar_arrive(tempty0 + 8 * buf);
-        if (++buf == 2) { buf = 0; bphase ^= 1; }
+        if (++buf == kAcc) { buf = 0; bphase ^= 1; }
       }
     }
   }
@@ -343,14 +352,26 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
   // pick the widest N tile that still yields about one tile per SM; fp8 promotion keeps BLOCK_N accumulators in registers
   int bn = block_n_hint;
   if (bn == 0) {
-    const int cands[4] = {256, 128, 64, 32};
-    bn = 32;
-    for (int c : cands) {
-      if (fp8 && c > 128) continue;
-      long long tiles = (long long)groups * m_blocks * ((N + c - 1) / c);
-      if (tiles >= num_sms() || c == 32) { bn = c; break; }
+    if (fp8 && !row_start && !masked_m) {
+      // dense block-scaled GEMM: the serial K loop of a tile dominates at small M, so take the fewest waves of
+      // tiles and, among equals, the narrowest tile (more SMs pulling weights at the same time)
+      long long best_waves = 1ll << 60;
+      bn = 128;
+      for (int c : {128, 64, 32}) {
+        long long tiles = (long long)groups * m_blocks * ((N + c - 1) / c);
+        long long waves = (tiles + num_sms() - 1) / num_sms();
+        if (waves <= best_waves) { best_waves = waves; bn = c; }
+      }
+    } else {
+      const int cands[4] = {256, 128, 64, 32};
+      bn = 32;
+      for (int c : cands) {
+        if (fp8 && c > 128) continue;
+        long long tiles = (long long)groups * m_blocks * ((N + c - 1) / c);
+        if (tiles >= num_sms() || c == 32) { bn = c; break; }
+      }
+      if (!fp8 && bn == 256 && N % 256 != 0 && N < 2048) bn = 128;
     }
-    if (!fp8 && bn == 256 && N % 256 != 0 && N < 2048) bn = 128;
   }
   if (fp8 && bn > 128) bn = 128;
   CUtensorMap ta, tb;

@@ -79,15 +79,13 @@ class MLAAttention(nn.Module):
             kv_a = self.kv_a_proj_with_mqa(x)
         q = q.view(T, H, nope + rope)
         ckv = self.kv_a_layernorm(kv_a[:, :R])
-        q_pe = ops.apply_rope(q[..., nope:], positions, rope_cache, True)
         k_pe = ops.apply_rope(kv_a[:, R:], positions, rope_cache, True)
         cache = ctx.kv_caches[self.layer_idx]
         ops.mla_kv_store(cache, ctx.slot_mapping, ckv, k_pe)
         sparse = None
         if self.indexer is not None:
             sparse = self.indexer(x, q_c if q_c is not None else x, positions, ctx, rope_cache)
-        q_abs = ops.bmm_absorb(q[..., :nope], self.kc)                       # [T, H, R]
-        q_full = torch.cat([q_abs, q_pe], -1)
+        q_full = ops.mla_absorb_rope(q, self.kc, positions, rope_cache, nope)   # [T, H, R + rope]
         o_lat = ops.mla_attention_paged(q_full, cache, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale, R,
                                         sparse_indices=sparse)
         o = ops.bmm_absorb(o_lat, self.vc)                                   # [T, H, v]
@@ -123,10 +121,8 @@ class DeepseekMoE(nn.Module):
     def forward(self, x, ctx: ForwardContext):
         from ..parallel.ep import ep_moe_forward
         idx, w = self.gate(x)
-        routed = ep_moe_forward(self.experts, x, idx, w, ctx)
-        if self.shared_experts is not None:
-            routed = routed + self.shared_experts(x)
-        return routed
+        shared = self.shared_experts(x) if self.shared_experts is not None else None
+        return ep_moe_forward(self.experts, x, idx, w, ctx, add_in=shared)
 
 
 class DeepseekDecoderLayer(nn.Module):

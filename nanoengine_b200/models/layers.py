@@ -115,10 +115,11 @@ class RoutedExperts(nn.Module):
     def owns(self, expert_id: int) -> bool:
         return self.expert_offset <= expert_id < self.expert_offset + self.num_local
 
-    def forward(self, x, topk_idx, topk_w):
-        """Local part of the routed output for the tokens given (weights applied, zero rows where no expert is local)."""
+    def forward(self, x, topk_idx, topk_w, add_in=None):
+        """Local part of the routed output for the tokens given (weights applied, zero rows where no expert is local);
+        `add_in` (the shared-expert output) is summed in by the same gather pass."""
         return ops.moe_experts(x, topk_idx, topk_w, self.gate_up_proj, self.down_proj, self.gate_up_scale, self.down_scale,
-                               self.expert_offset)
+                               self.expert_offset, add_in)
 
     @torch.no_grad()
     def set_expert(self, local_idx: int, which: str, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None):

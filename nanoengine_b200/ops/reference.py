@@ -267,7 +267,7 @@ def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
     return (F.silu(a) * b).to(x.dtype)
 
 
-def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0) -> torch.Tensor:
+def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0, add_in=None) -> torch.Tensor:
     """Routed experts held locally: ids [expert_offset, expert_offset + E_local).  w13 [E, 2I, H], w2 [E, H, I].
     Returns the weighted sum over the local experts of each token (zeros where none is local)."""
     T, H = x.shape
@@ -283,7 +283,8 @@ def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, exp
         h = silu_and_mul(h)
         y = linear(h, w2[e], None if w2_scale is None else w2_scale[e])
         out.index_add_(0, tok, y.float() * topk_w[tok, slot].unsqueeze(-1))
-    return out.to(x.dtype)
+    out = out.to(x.dtype)
+    return out if add_in is None else out + add_in
 
 
 # ---- sampling ------------------------------------------------------------------------------------
@@ -356,6 +357,11 @@ def logical_to_physical(idx: torch.Tensor, block_table_rows: torch.Tensor, block
 def bmm_absorb(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """Per-head matmul of MLA weight absorption: x [T, H, A], w [H, A, B] -> [T, H, B]."""
     return torch.einsum("tha,hab->thb", x.float(), w.float()).to(x.dtype)
+
+
+def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, nope: int) -> torch.Tensor:
+    """Absorbed MLA query [q_nope @ W_UK | rope(q_pe)]: q [T, H, nope + rope], kc [H, nope, R] -> [T, H, R + rope]."""
+    return torch.cat([bmm_absorb(q[..., :nope], kc), apply_rope(q[..., nope:], positions, cache, True)], -1)
 
 
 def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

@@ -130,16 +130,18 @@ def lm_head(hidden: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return linear(hidden, w, out_fp32=True)
 
 
-def bmm_absorb(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [T, H, A] (any row/head strides, unit inner stride), w [H, A, B] -> [T, H, B]: a grouped GEMM with one group per head."""
     T, H, A = x.shape
     Bd = w.shape[2]
     wt = _cached(w, "t", lambda t: t.to(torch.bfloat16).transpose(1, 2).contiguous())      # [H, B, A], K-major
     if x.dtype != torch.bfloat16 or x.stride(2) != 1 or (x.stride(0) * 2) % 16 or (x.stride(1) * 2) % 16 or x.data_ptr() % 16:
         x = x.to(torch.bfloat16).contiguous()
-    out = torch.empty(T, H, Bd, dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty(T, H, Bd, dtype=torch.bfloat16, device=x.device)
+    assert out.stride(2) == 1 and (out.stride(0) * 2) % 16 == 0 and (out.stride(1) * 2) % 16 == 0 and out.data_ptr() % 16 == 0
     if T > 0:
-        _gemm(x, x.stride(0), x.stride(1), wt, out, H * Bd, Bd, T, Bd, A, H, None, None, False, None, 0, 0, None, False)
+        _gemm(x, x.stride(0), x.stride(1), wt, out, out.stride(0), out.stride(1), T, Bd, A, H, None, None, False, None, 0, 0, None, False)
     return out
 
 
@@ -184,15 +186,30 @@ def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
 
 
 # ---- rotary / KV ----------------------------------------------------------------------------------
-def apply_rope(x: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, interleaved: bool) -> torch.Tensor:
-    """Rotates `x` in place (x may be a strided view of the projection output) and returns it."""
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, interleaved: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rotates `x` (which may be a strided view of a projection output) in place, or into `out` when given."""
     assert x.dtype == torch.bfloat16 and x.stride(-1) == 1
+    y = x if out is None else out
+    assert y.dtype == torch.bfloat16 and y.stride(-1) == 1 and y.shape == x.shape
     T, D = x.shape[0], x.shape[-1]
-    heads, hs = (x.shape[1], x.stride(1)) if x.dim() == 3 else (1, 0)
+    heads, hs, yhs = (x.shape[1], x.stride(1), y.stride(1)) if x.dim() == 3 else (1, 0, 0)
     pos = positions if positions.dtype == torch.int64 else positions.long()
-    _ck(lib().ne_rope(_p(x), _c.c_longlong(x.stride(0)), _c.c_int(hs), _c.c_int(heads), _c.c_int(0), _c.c_int(D), _p(pos), _p(cache),
-                      _c.c_int(1 if interleaved else 0), _c.c_int(T), _st()), "ne_rope")
-    return x
+    _ck(lib().ne_rope(_p(x), _c.c_longlong(x.stride(0)), _c.c_int(hs), _p(y), _c.c_longlong(y.stride(0)), _c.c_int(yhs), _c.c_int(heads),
+                      _c.c_int(0), _c.c_int(D), _p(pos), _p(cache), _c.c_int(1 if interleaved else 0), _c.c_int(T), _st()), "ne_rope")
+    return y
+
+
+def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, nope: int) -> torch.Tensor:
+    """Absorbed query of MLA in one buffer: [q_nope @ W_UK | rope(q_pe)] -> [T, H, R + rope], no concatenation pass."""
+    T, H, _ = q.shape
+    R = kc.shape[2]
+    rope = q.shape[2] - nope
+    out = torch.empty(T, H, R + rope, dtype=torch.bfloat16, device=q.device)
+    if T == 0:
+        return out
+    bmm_absorb(q[..., :nope], kc, out=out[..., :R])
+    apply_rope(q[..., nope:], positions, cache, True, out=out[..., R:])
+    return out
 
 
 def mla_kv_store(cache: torch.Tensor, slot_mapping: torch.Tensor, ckv: torch.Tensor, k_pe: torch.Tensor) -> None:

@@ -57,10 +57,12 @@ def ep_moe_allgather(experts, x, topk_idx, topk_w, group, ep_size: int, ep_rank:
     return part[ep_rank * m: ep_rank * m + T].to(x.dtype)
 
 
-def ep_moe_forward(experts, x, topk_idx, topk_w, ctx=None):
+def ep_moe_forward(experts, x, topk_idx, topk_w, ctx=None, add_in=None):
+    """Routed-expert output for this rank's tokens; `add_in` (shared-expert output) is added to it."""
     d = get_dist_context()
     if d.ep_size == 1:
-        return experts(x, topk_idx, topk_w)
+        return experts(x, topk_idx, topk_w, add_in)
     if x.is_cuda and _FUSED is not None:
-        return _FUSED.forward(experts, x, topk_idx, topk_w, ctx)
-    return ep_moe_allgather(experts, x, topk_idx, topk_w, d.group("ffn_ep"), d.ep_size, d.ep_rank)
+        return _FUSED.forward(experts, x, topk_idx, topk_w, ctx, add_in)
+    out = ep_moe_allgather(experts, x, topk_idx, topk_w, d.group("ffn_ep"), d.ep_size, d.ep_rank)
+    return out if add_in is None else out + add_in

@@ -168,7 +168,10 @@ class ModelRunner:
         if self.config.num_speculative_tokens > 0:
             from .mtp_runner import MTPRunner
             self.mtp_runner = MTPRunner(self)
-        if self.device.type == "cuda" and not self.config.enforce_eager:
+        from ..parallel.ep import get_fused_backend
+        # the NCCL all-gather EP path sizes its buffers from a host read-back and cannot be captured; the fused path can
+        ep_capturable = self.dist.ep_size == 1 or get_fused_backend() is not None
+        if self.device.type == "cuda" and not self.config.enforce_eager and ep_capturable:
             from .graph_runner import DecodeGraphRunner
             self.graphs = DecodeGraphRunner(self)
 
