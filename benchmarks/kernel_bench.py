@@ -1,0 +1,172 @@
+"""Per-kernel timings at the shapes the DeepSeek-V3 decode and prefill steps use, with roofline fractions.
+
+    python benchmarks/kernel_bench.py                       # all cases, table on stdout
+    python benchmarks/kernel_bench.py --case moe_gemm1 --experts 8 --iters 3   # one small case (what the ncu captures run)
+
+Timing: CUDA events on the launching stream, 3 warm-up runs, a buffer larger than L2 is rewritten between timed
+runs, the median of `--iters` runs is reported.  Fractions are against MEASURED_PEAKS.json (copy bandwidth and cuBLAS
+bf16 throughput of this pool's B200s) when that file exists, otherwise against the documented fallback figures.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+from nanoengine_b200.ops import reference as ref
+from nanoengine_b200.ops import sm100, sm100_attn
+
+FP8 = torch.float8_e4m3fn
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.fill_(1)
+
+
+def timeit(fn, iters):
+    for _ in range(3):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def rand_fp8(*shape):
+    return (torch.randn(*shape, device="cuda") * 0.5).to(FP8)
+
+
+def case_dense_fp8(M, N, K):
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w, s = rand_fp8(N, K), torch.rand((N + 127) // 128, K // 128, device="cuda") + 0.5
+    q = torch.empty(M, K, dtype=FP8, device="cuda")
+    sc = torch.empty(K // 128, M, dtype=torch.float32, device="cuda")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    q.copy_(rand_fp8(M, K)); sc.fill_(1.0)
+    fn = lambda: sm100._gemm(q, K, 0, w, out, N, 0, M, N, K, 1, None, None, True, sc, M, 0, s, False)
+    return fn, N * K + M * K + M * N * 2, 2.0 * M * N * K
+
+
+def case_dense_bf16(M, N, K, out_fp32=False):
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    fn = lambda: sm100.linear(x, w, out_fp32=out_fp32)
+    return fn, (N * K + M * K) * 2 + M * N * (4 if out_fp32 else 2), 2.0 * M * N * K
+
+
+def case_moe_gemm(E, rows_per_expert, N, K):
+    """Contiguous grouped fp8 GEMM as the local MoE path runs it (every expert gets the same number of rows)."""
+    pad = (rows_per_expert + 127) // 128 * 128
+    R = E * pad
+    a = rand_fp8(R, K)
+    sa = torch.ones(K // 128, R, device="cuda")
+    w = rand_fp8(E, N, K)
+    sb = torch.rand(E, (N + 127) // 128, K // 128, device="cuda") + 0.5
+    counts = torch.full((E,), rows_per_expert, dtype=torch.int32, device="cuda")
+    row_start = (torch.arange(E + 1, device="cuda") * pad).to(torch.int32)
+    out = torch.empty(R, N, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: sm100._gemm(a, K, 0, w, out, N, 0, R, N, K, E, counts, row_start, True, sa, R, 0, sb, False)
+    return fn, E * N * K + E * rows_per_expert * (K + 2 * N), 2.0 * E * rows_per_expert * N * K
+
+
+def case_mla(B, ctx, H=128, q_len=1):
+    bs = 64
+    nb = (ctx + bs - 1) // bs
+    cache = rand_fp8(B * nb + 1, bs, 576)
+    bt = torch.arange(B * nb, device="cuda", dtype=torch.int32).view(B, nb)
+    q = (torch.randn(B * q_len, H, 576, device="cuda") * 0.3).to(torch.bfloat16)
+    cu = (torch.arange(B + 1, device="cuda") * q_len).to(torch.int32)
+    cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    fn = lambda: sm100_attn.mla_attention_paged(q, cache, bt, cu, cl, 0.07, 512)
+    return fn, B * ctx * 576 + B * q_len * H * (576 + 512) * 2, 2.0 * B * q_len * H * ctx * (576 + 512)
+
+
+def case_moe_layer(T, E, topk=8, H=7168, I=2048):
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w13, w2 = rand_fp8(E, 2 * I, H), rand_fp8(E, H, I)
+    s13 = torch.rand(E, 2 * I // 128, H // 128, device="cuda") * 0.01
+    s2 = torch.rand(E, H // 128, I // 128, device="cuda") * 0.01
+    idx = torch.stack([torch.randperm(E, device="cuda")[:topk] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, topk, device="cuda")
+    fn = lambda: sm100.moe_experts(x, idx, w, w13, w2, s13, s2, 0)
+    return fn, E * 3 * I * H, 2.0 * T * topk * 3 * I * H
+
+
+def build_cases(args):
+    E = args.experts
+    c = {
+        # decode, 128 tokens per GPU
+        "qkv_a_decode": lambda: case_dense_fp8(128, 2112, 7168),
+        "q_b_decode": lambda: case_dense_fp8(128, 24576, 1536),
+        "o_proj_decode": lambda: case_dense_fp8(128, 7168, 16384),
+        "shared_up_decode": lambda: case_dense_fp8(128, 4096, 7168),
+        "shared_down_decode": lambda: case_dense_fp8(128, 7168, 2048),
+        "lm_head_decode": lambda: case_dense_bf16(128, 129280, 7168, True),
+        "moe_gemm1": lambda: case_moe_gemm(E, args.rows, 4096, 7168),
+        "moe_gemm2": lambda: case_moe_gemm(E, args.rows, 7168, 2048),
+        "moe_layer_decode": lambda: case_moe_layer(128, E),
+        "mla_decode": lambda: case_mla(128, args.ctx),
+        "mla_decode_small_batch": lambda: case_mla(8, 8192),
+        # prefill, 16384 tokens
+        "qkv_a_prefill": lambda: case_dense_fp8(args.prefill_tokens, 2112, 7168),
+        "o_proj_prefill": lambda: case_dense_fp8(args.prefill_tokens, 7168, 16384),
+        "moe_gemm1_prefill": lambda: case_moe_gemm(E, args.prefill_tokens * 8 // 32, 4096, 7168),
+        "bf16_square": lambda: case_dense_bf16(8192, 8192, 8192),
+    }
+    return c
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="all")
+    ap.add_argument("--iters", type=int, default=7)
+    ap.add_argument("--experts", type=int, default=32)
+    ap.add_argument("--rows", type=int, default=32, help="rows per expert for the grouped GEMM cases")
+    ap.add_argument("--ctx", type=int, default=2560)
+    ap.add_argument("--prefill-tokens", type=int, default=16384)
+    args = ap.parse_args()
+    sm100.lib()
+    bw, fl, src = peaks()
+    cases = build_cases(args)
+    names = list(cases) if args.case == "all" else args.case.split(",")
+    print(f"{'case':26s} {'time_us':>10s} {'GB/s':>9s} {'frac_bw':>8s} {'TFLOP/s':>9s} {'frac_bf16':>9s}   (fractions of {src} peaks)")
+    for n in names:
+        fn, nbytes, flops = cases[n]()
+        t = timeit(fn, args.iters)
+        print(f"{n:26s} {t * 1e6:10.1f} {nbytes / t / 1e9:9.0f} {nbytes / t / bw:8.2f} {flops / t / 1e12:9.1f} {flops / t / fl:9.2f}")
+        del fn
+        torch.cuda.empty_cache()
+    st = sm100.kernel_status()
+    if st[0] != 0:
+        print("kernel status:", st)
+
+
+if __name__ == "__main__":
+    main()

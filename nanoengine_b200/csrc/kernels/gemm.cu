@@ -40,6 +40,8 @@ struct GemmArgs {
   const float* sa; int sa_ld; long long sa_group_stride;   // activation scales [groups][K/128][sa_ld]
   const float* sb; long long sb_group_stride;              // weight scales [groups][ceil(N/128)][K/128]
   int out_fp32;
+  const long long* row_dst;             // optional scatter epilogue: absolute address of every output row (bf16, may be peer memory),
+  long long rd_group_stride;            // indexed [group * rd_group_stride + row]; used by the MoE combine
 };
 
 template <int BLOCK_N> struct Smem {
@@ -72,8 +74,15 @@ struct TileSched {
   }
 };
 
+// Block-scaled tiles at least 64 wide use two epilogue warpgroups that split the tile's columns, halving the
+// promotion work per thread and per K block.
+template <int BLOCK_N, bool kBlockScaled> struct EpiCfg {
+  static constexpr int kGroups = (kBlockScaled && BLOCK_N >= 64) ? 2 : 1;
+  static constexpr int kThreads = 64 + 128 * kGroups;
+};
+
 template <int BLOCK_N, bool kFP8, bool kBlockScaled>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__((EpiCfg<BLOCK_N, kBlockScaled>::kThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
   using S = Smem<BLOCK_N>;
   constexpr int kStages = S::kStages;
@@ -85,6 +94,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   constexpr int kAcc = kBlockScaled ? ((512 / BLOCK_N) > 4 ? 4 : (512 / BLOCK_N)) : 2;
   constexpr uint32_t kTmemCols = (kAcc * BLOCK_N) < 32 ? 32 : kAcc * BLOCK_N;
   constexpr uint32_t kIdesc = make_idesc(kFP8 ? FMT_E4M3 : FMT_BF16, kFP8 ? FMT_E4M3 : FMT_BF16, kBlockM, BLOCK_N);
+  constexpr int kEpi = EpiCfg<BLOCK_N, kBlockScaled>::kGroups;
+  constexpr int kCols = BLOCK_N / kEpi;          // columns of the tile each epilogue thread owns
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -102,7 +113,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
-    for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4); }
+    for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4 * kEpi); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_b);
@@ -168,8 +179,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
     }
   } else {
-    // ---------------- epilogue: 4 warps, warp w may touch TMEM lanes [32*(w%4), +32) ----------------
+    // ---------------- epilogue: 4 warps per group, warp w may touch TMEM lanes [32*(w%4), +32) ----------------
     const int wq = warp & 3;
+    const int cbase = ((warp - 2) >> 2) * kCols;   // column offset of this warp's group inside the tile
     const int row_in_tile = wq * 32 + (int)lane_id();
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     TileSched sched(args.groups, args.M, n_blocks, args.masked_m, args.row_start);
@@ -180,25 +192,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int row = sched.row0(grp) + mb * kBlockM + row_in_tile;      // row inside the group's (or the flat) matrix
       const int n0 = nb * BLOCK_N;
       if (kBlockScaled) {
-        float acc[BLOCK_N];
+        float acc[kCols];
 #pragma unroll
-        for (int j = 0; j < BLOCK_N; j++) acc[j] = 0.f;
+        for (int j = 0; j < kCols; j++) acc[j] = 0.f;
         const float* sa = args.sa + (long long)grp * args.sa_group_stride + (row_ok ? row : 0);
         const float* sb = args.sb + (long long)grp * args.sb_group_stride + (long long)(n0 / 128) * num_kb;
-        for (int kb = 0; kb < num_kb; kb++) {
-          float s = __ldg(sa + (long long)kb * args.sa_ld) * __ldg(sb + kb);
+        // scale factors are fetched four K blocks ahead so their L2 latency hides behind the promotion work
+        constexpr int kPf = 4;
+        float nxt[kPf];
+#pragma unroll
+        for (int j = 0; j < kPf; j++) nxt[j] = j < num_kb ? __ldg(sa + (long long)j * args.sa_ld) * __ldg(sb + j) : 0.f;
+        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kPf) {
+          float cur[kPf];
+#pragma unroll
+          for (int j = 0; j < kPf; j++) {
+            cur[j] = nxt[j];
+            const int kn = kb0 + kPf + j;
+            nxt[j] = kn < num_kb ? __ldg(sa + (long long)kn * args.sa_ld) * __ldg(sb + kn) : 0.f;
+          }
+#pragma unroll
+        for (int jj = 0; jj < kPf; jj++) {
+          if (kb0 + jj >= num_kb || !ok) break;
+          const float s = cur[jj];
           if (!mbar_wait(tfull0 + 8 * buf, bphase, abort_flag, kKernelGemm, 400 + buf)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < BLOCK_N / 32; c += 2) {
+          for (int c = 0; c < kCols / 32; c += 2) {
             // two TMEM loads in flight per wait
             uint32_t r0[32], r1[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + c * 32, r0);
-            if (c + 1 < BLOCK_N / 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + (c + 1) * 32, r1);
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + cbase + c * 32, r0);
+            if (c + 1 < kCols / 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + cbase + (c + 1) * 32, r1);
             tc_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; j++) acc[c * 32 + j] = fmaf(s, __uint_as_float(r0[j]), acc[c * 32 + j]);
-            if (c + 1 < BLOCK_N / 32) {
+            if (c + 1 < kCols / 32) {
 #pragma unroll
               for (int j = 0; j < 32; j++) acc[(c + 1) * 32 + j] = fmaf(s, __uint_as_float(r1[j]), acc[(c + 1) * 32 + j]);
             }
@@ -208,12 +235,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (lane_id() == 0) mbar_arrive(tempty0 + 8 * buf);
           if (++buf == kAcc) { buf = 0; bphase ^= 1; }
         }
+        }
         if (!ok) break;
         if (row_ok) {
-          long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0;
+          long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0 + cbase;
+          __nv_bfloat16* dbf = args.row_dst ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0 + cbase
+                                            : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
 #pragma unroll
-          for (int c = 0; c < BLOCK_N / 8; c++) {
-            if (n0 + c * 8 < args.N) {
+          for (int c = 0; c < kCols / 8; c++) {
+            if (n0 + cbase + c * 8 < args.N) {
               if (args.out_fp32) {
                 float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.D) + off + c * 8);
                 p[0] = make_float4(acc[c * 8], acc[c * 8 + 1], acc[c * 8 + 2], acc[c * 8 + 3]);
@@ -221,7 +251,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               } else {
                 uint4 v = make_uint4(pack_bf16x2(acc[c * 8], acc[c * 8 + 1]), pack_bf16x2(acc[c * 8 + 2], acc[c * 8 + 3]),
                                      pack_bf16x2(acc[c * 8 + 4], acc[c * 8 + 5]), pack_bf16x2(acc[c * 8 + 6], acc[c * 8 + 7]));
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.D) + off + c * 8) = v;
+                *reinterpret_cast<uint4*>(dbf + c * 8) = v;
               }
             }
           }
@@ -230,6 +260,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (!mbar_wait(tfull0 + 8 * buf, bphase, abort_flag, kKernelGemm, 410 + buf)) { ok = false; break; }
         tc_fence_after();
         long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0;
+        __nv_bfloat16* dbf = (args.row_dst && row_ok) ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0
+                                                      : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
 #pragma unroll
         for (int c = 0; c < BLOCK_N / 32; c++) {
           uint32_t r[32];
@@ -249,7 +281,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                        pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
                                        pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
                                        pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.D) + off + c * 32 + q * 8) = v;
+                  *reinterpret_cast<uint4*>(dbf + c * 32 + q * 8) = v;
                 }
               }
             }
@@ -327,7 +359,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, kGemmThreads, Smem<BLOCK_N>::kBytes, st>>>(ta, tb, a);
+  kern<<<grid, EpiCfg<BLOCK_N, kBS>::kThreads, Smem<BLOCK_N>::kBytes, st>>>(ta, tb, a);
   return (int)cudaGetLastError();
 }
 
@@ -342,7 +374,7 @@ using namespace ne;
 // Returns 0 or a CUDA / argument error code.
 extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void* B, void* D, long long ldd, long long d_gs,
                        int M, int N, int K, int groups, const int* masked_m, const int* row_start, int dtype, const float* sa, int sa_ld,
-                       long long sa_gs, const float* sb, int out_fp32, int block_n_hint, cudaStream_t stream) {
+                       long long sa_gs, const float* sb, int out_fp32, int block_n_hint, const long long* row_dst, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
   const bool fp8 = dtype == 1;
   if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % 16 != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
@@ -386,6 +418,8 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
   if (row_start) { a.d_group_stride = 0; sa_gs = 0; if (!masked_m) return 1004; }
   a.sa = sa; a.sa_ld = sa_ld; a.sa_group_stride = sa_gs; a.sb = sb;
   a.sb_group_stride = (long long)((N + 127) / 128) * (K / 128); a.out_fp32 = out_fp32;
+  a.row_dst = row_dst; a.rd_group_stride = row_start ? 0 : M;
+  if (row_dst && out_fp32) return 1005;
   long long tiles = (long long)groups * m_blocks * ((N + bn - 1) / bn);
   int grid = (int)(tiles < num_sms() ? tiles : num_sms());
   if (fp8) {

@@ -62,10 +62,10 @@ def clear_kernel_status():
 
 
 # ---- GEMM ----------------------------------------------------------------------------------------
-def _gemm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, row_start, fp8, sa, sa_ld, sa_gs, sb, out_fp32, bn=0):
+def _gemm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, row_start, fp8, sa, sa_ld, sa_gs, sb, out_fp32, bn=0, row_dst=None):
     rc = lib().ne_gemm(_p(A), _c.c_longlong(lda), _c.c_longlong(a_gs), _p(B), _p(D), _c.c_longlong(ldd), _c.c_longlong(d_gs),
                        _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), _p(masked_m), _p(row_start), _c.c_int(1 if fp8 else 0),
-                       _p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(1 if out_fp32 else 0), _c.c_int(bn), _st())
+                       _p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(1 if out_fp32 else 0), _c.c_int(bn), _p(row_dst), _st())
     _ck(rc, "ne_gemm")
 
 

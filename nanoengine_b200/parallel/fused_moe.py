@@ -1,0 +1,142 @@
+"""Fused expert-parallel MoE: dispatch, grouped GEMMs and combine over NVLink peer memory (kernels in csrc/comm/ep.cu).
+
+``FusedEP`` owns the symmetric receive buffers of one EP group and runs one MoE layer as a fixed kernel sequence with
+no host synchronisation, so it can be captured in the decode CUDA graph.  Capacity per local expert (`cap`) bounds the
+rows an expert can receive in one layer; a pair that finds its expert full is dropped and reported through the kernel
+status words (size `cap` from the token budget: the default is four times the balanced load, never less than 256).
+
+Parity: reference runtime/context/expert.py:42-224 (buffer sizing, low-latency mode with at most 128 dispatch tokens
+per rank) and layers/backends/experts/deep_gemm.py:611-837 (dispatch -> grouped GEMMs -> combine data flow).
+"""
+from __future__ import annotations
+
+import ctypes as _c
+from typing import Optional
+
+import torch
+
+from ..ops import sm100 as _k
+from .symm import MAX_PEERS, SymmetricHeap
+
+FP8 = torch.float8_e4m3fn
+
+
+class EpLayout(_c.Structure):
+    _fields_ = [("peer_base", _c.c_ulonglong * MAX_PEERS),
+                ("off_cnt", _c.c_longlong), ("off_aq", _c.c_longlong), ("off_as", _c.c_longlong), ("off_abf", _c.c_longlong),
+                ("off_info", _c.c_longlong), ("off_ret", _c.c_longlong), ("off_arrive", _c.c_longlong), ("off_done", _c.c_longlong),
+                ("rank", _c.c_int), ("world", _c.c_int), ("E_local", _c.c_int), ("cap", _c.c_int), ("H", _c.c_int), ("top_k", _c.c_int),
+                ("fp8", _c.c_int)]
+
+
+def ep_heap_bytes(E_local: int, cap: int, H: int, max_tokens: int, top_k: int, fp8: bool) -> int:
+    rows = E_local * cap
+    act = rows * H + rows * (H // 128) * 4 if fp8 else rows * H * 2
+    return act + rows * 8 + max_tokens * top_k * H * 2 + E_local * 4 + 64 * 1024
+
+
+class FusedEP:
+    def __init__(self, group, ep_rank: int, ep_size: int, num_experts: int, hidden: int, inter: int, top_k: int, max_tokens: int,
+                 fp8: bool, cap: Optional[int] = None, spin_limit: int = 1 << 22):
+        lib = _k.lib()
+        assert lib.ne_ep_layout_size() == _c.sizeof(EpLayout), "EpLayout mismatch between Python and the kernel library"
+        self.E_local = num_experts // ep_size
+        self.H, self.I, self.K, self.fp8 = hidden, inter, top_k, fp8
+        self.max_tokens = max_tokens
+        balanced = -(-ep_size * max_tokens * top_k // num_experts)
+        self.cap = cap if cap is not None else max(256, min(ep_size * max_tokens, 4 * balanced))
+        self.cap = (self.cap + 127) // 128 * 128
+        self.spin_limit = spin_limit
+        E, C, H = self.E_local, self.cap, hidden
+        self.heap = SymmetricHeap(ep_heap_bytes(E, C, H, max_tokens, top_k, fp8), group)
+        assert self.heap.rank == ep_rank and self.heap.world_size == ep_size
+        hp = self.heap
+        self.b_cnt = hp.alloc(E * 4)
+        self.b_arrive = hp.alloc(MAX_PEERS * 4)
+        self.b_done = hp.alloc(MAX_PEERS * 4)
+        self.b_info = hp.alloc(E * C * 8)
+        self.b_ret = hp.alloc(max_tokens * top_k * H * 2)
+        if fp8:
+            self.b_aq = hp.alloc(E * C * H)
+            self.b_as = hp.alloc(E * (H // 128) * C * 4)
+            self.b_abf = None
+        else:
+            self.b_abf = hp.alloc(E * C * H * 2)
+            self.b_aq = self.b_as = None
+        L = EpLayout()
+        for r in range(ep_size):
+            L.peer_base[r] = hp.peer_ptrs[r]
+        L.off_cnt, L.off_arrive, L.off_done, L.off_info, L.off_ret = (self.b_cnt.offset, self.b_arrive.offset, self.b_done.offset,
+                                                                     self.b_info.offset, self.b_ret.offset)
+        L.off_aq = self.b_aq.offset if fp8 else 0
+        L.off_as = self.b_as.offset if fp8 else 0
+        L.off_abf = 0 if fp8 else self.b_abf.offset
+        L.rank, L.world, L.E_local, L.cap, L.H, L.top_k, L.fp8 = ep_rank, ep_size, E, C, H, top_k, int(fp8)
+        self.layout = L
+        dev = hp.device
+        self.state = torch.zeros(4, dtype=torch.int32, device=dev)       # [epoch, dispatch CTA counter, -, -]
+        self.counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        self.row_dst = torch.zeros(E * C, dtype=torch.int64, device=dev)
+        self.g = torch.empty(E, C, 2 * inter, dtype=torch.bfloat16, device=dev)
+        if fp8:
+            self.h_q = torch.empty(E, C, inter, dtype=FP8, device=dev)
+            self.h_s = torch.empty(E, inter // 128, C, dtype=torch.float32, device=dev)
+        else:
+            self.h = torch.empty(E, C, inter, dtype=torch.bfloat16, device=dev)
+        self.pair_ok = torch.zeros(max_tokens * top_k, dtype=torch.int32, device=dev)
+        hp.barrier()
+
+    def forward(self, experts, x, topk_idx, topk_w, ctx=None, add_in=None):
+        lib = _k.lib()
+        T, H = x.shape
+        K, E, C, I = self.K, self.E_local, self.cap, self.I
+        if T > self.max_tokens:
+            raise ValueError(f"{T} tokens exceed the EP buffer size {self.max_tokens}")
+        x = _k._as_bf16_2d(x)
+        idx = topk_idx.to(torch.int32).contiguous()
+        w = topk_w.float().contiguous()
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+        L = _c.byref(self.layout)
+        epoch, ctr = _k._p(self.state), _c.c_void_p(self.state.data_ptr() + 4)
+        st = _k._st()
+        _k._ck(lib.ne_ep_dispatch(L, _k._p(x), _k._p(idx), _k._p(self.pair_ok), _c.c_int(T * K), epoch, ctr, st), "ne_ep_dispatch")
+        _k._ck(lib.ne_ep_wait_build(L, _k._p(self.counts), _k._p(self.row_dst), epoch, _c.c_int(self.spin_limit), st), "ne_ep_wait_build")
+        ret_dummy = self.g          # D pointer is unused when every row has an explicit destination
+        if self.fp8:
+            aq = self.b_aq.view(FP8, (E, C, H))
+            a_s = self.b_as.view(torch.float32, (E, H // 128, C))
+            _k._gemm(aq, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, self.counts, None, True, a_s, C,
+                     (H // 128) * C, experts.gate_up_scale, False)
+            _k._ck(lib.ne_silu_mul(_k._p(self.g), _k._p(None), _k._p(self.h_q), _k._p(self.h_s), _c.c_int(C), _c.c_longlong((I // 128) * C),
+                                   _k._p(self.counts), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
+            _k._gemm(self.h_q, I, C * I, experts.down_proj, ret_dummy, H, 0, C, H, I, E, self.counts, None, True, self.h_s, C,
+                     (I // 128) * C, experts.down_scale, False, row_dst=self.row_dst)
+        else:
+            ab = self.b_abf.view(torch.bfloat16, (E, C, H))
+            _k._gemm(ab, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, self.counts, None, False, None, 0, 0, None, False)
+            _k._ck(lib.ne_silu_mul(_k._p(self.g), _k._p(self.h), _k._p(None), _k._p(None), _c.c_int(0), _c.c_longlong(0),
+                                   _k._p(self.counts), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
+            _k._gemm(self.h, I, C * I, experts.down_proj, ret_dummy, H, 0, C, H, I, E, self.counts, None, False, None, 0, 0, None, False,
+                     row_dst=self.row_dst)
+        _k._ck(lib.ne_ep_signal(L, epoch, st), "ne_ep_signal")
+        _k._ck(lib.ne_ep_reduce(L, _k._p(self.pair_ok), _k._p(w), _k._p(add_in), _k._p(out), _c.c_int(T), epoch, _c.c_int(self.spin_limit), st),
+               "ne_ep_reduce")
+        _k._ck(lib.ne_ep_advance(epoch, st), "ne_ep_advance")
+        return out
+
+
+def install(config, dist_ctx) -> Optional[FusedEP]:
+    """Create the fused backend for this rank's EP group when peers are reachable; returns None otherwise."""
+    from . import ep
+    from .symm import peers_reachable
+    mc = config.model_config
+    if dist_ctx.ep_size == 1 or not config.use_fused_comm or not torch.cuda.is_available():
+        return None
+    group = dist_ctx.group("ffn_ep")
+    if not peers_reachable(group):
+        return None
+    max_tokens = max(config.max_num_batched_tokens, config.max_num_seqs * (1 + config.num_speculative_tokens))
+    be = FusedEP(group, dist_ctx.ep_rank, dist_ctx.ep_size, mc.n_routed_experts, mc.hidden_size, mc.moe_intermediate_size,
+                 mc.num_experts_per_tok, max_tokens, mc.quant == "fp8")
+    ep.set_fused_backend(be)
+    return be

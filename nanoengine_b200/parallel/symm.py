@@ -46,7 +46,10 @@ class SymmetricHeap:
         if self.world_size > MAX_PEERS:
             raise ValueError(f"at most {MAX_PEERS} peers per heap")
         self.peer_ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
-        self.multicast_ptr: int = int(self.handle.multicast_ptr) if self.handle.has_multicast_support(self.device.type, self.device.index) else 0
+        try:        # 0 when the fabric offers no NVLS multicast object for this group
+            self.multicast_ptr: int = int(self.handle.multicast_ptr)
+        except Exception:
+            self.multicast_ptr = 0
         self.buf.zero_()
         self._cursor = 0
         self._named: Dict[str, SymmBuffer] = {}

@@ -114,6 +114,9 @@ class ModelRunner:
             it = iterate_safetensors(self.config.model, keep, self.device)
         self.load_weights(it)
         self.model.eval()
+        if self.device.type == "cuda" and self.dist.ep_size > 1:
+            from ..parallel import fused_moe
+            fused_moe.install(self.config, self.dist)
 
     def load_weights(self, it) -> int:
         if self.mtp is not None:

@@ -1,0 +1,81 @@
+"""Fused expert-parallel MoE (peer-memory dispatch + grouped GEMMs + epilogue combine) against the NCCL all-gather oracle,
+on 2 GPUs of one box, eagerly, repeatedly (epoch reuse of the receive buffers) and from a captured CUDA graph."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, fp8, q):
+    try:
+        import torch.distributed as dist
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+        from nanoengine_b200.models.layers import RoutedExperts
+        from nanoengine_b200.ops import reference as ref, sm100
+        from nanoengine_b200.parallel.dist import ParallelSpec, init_dist_context
+        from nanoengine_b200.parallel.ep import ep_moe_allgather
+        from nanoengine_b200.parallel.fused_moe import FusedEP
+        d = init_dist_context(ParallelSpec(attention_dp=world, ffn_ep=world), rank, world, f"cuda:{rank}")
+        H, I, E, K = 1024, 256, 16, 4
+        ex = RoutedExperts(E, H, I, torch.bfloat16, f"cuda:{rank}", "fp8" if fp8 else None)
+        g = torch.Generator(device=f"cuda:{rank}").manual_seed(100 + rank)
+        ex.init_random(g, std=0.05)
+        be = FusedEP(d.group("ffn_ep"), d.ep_rank, world, E, H, I, K, max_tokens=64, fp8=fp8)
+        worst = 0.0
+        for it, T in enumerate([37 if rank == 0 else 5, 1, 64]):
+            x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+            logits = torch.randn(T, E, device="cuda", generator=g)
+            idx, w = ref.moe_route(logits, None, K, 1, 1, True, 1.0, "softmax")
+            add = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+            want = ep_moe_allgather(ex, x, idx, w, d.group("ffn_ep"), world, rank) + add
+            got = be.forward(ex, x, idx, w, None, add)
+            torch.cuda.synchronize()
+            worst = max(worst, ((got.float() - want.float()).norm() / want.float().norm()).item())
+        # graph capture and two replays with fresh inputs in the same buffers
+        T = 16
+        xs = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+        lg = torch.randn(T, E, device="cuda", generator=g)
+        idx, w = ref.moe_route(lg, None, K, 1, 1, True, 1.0, "softmax")
+        be.forward(ex, xs, idx, w)            # warm-up outside capture
+        torch.cuda.synchronize(); dist.barrier()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            yg = be.forward(ex, xs, idx, w)
+        for rep in range(2):
+            xs.copy_(torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16))
+            want = ep_moe_allgather(ex, xs, idx, w, d.group("ffn_ep"), world, rank)
+            gr.replay()
+            torch.cuda.synchronize()
+            worst = max(worst, ((yg.float() - want.float()).norm() / want.float().norm()).item())
+        st = sm100.kernel_status()
+        dist.barrier()
+        q.put((rank, worst, st[0]))
+        dist.destroy_process_group()
+    except Exception as e:  # surface the failure to the parent instead of hanging it
+        import traceback
+        q.put((rank, f"{e}\n{traceback.format_exc()}", -1))
+
+
+@pytest.mark.parametrize("fp8", [True, False])
+def test_fused_ep_matches_allgather_oracle(fp8):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_worker, args=(r, 2, port, fp8, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = [q.get(timeout=300) for _ in ps]
+    for p in ps:
+        p.join(timeout=60)
+    for rank, worst, status in res:
+        assert status == 0, f"rank {rank}: {worst}"
+        assert worst < 2e-2, f"rank {rank}: relative error {worst}"
