@@ -118,27 +118,34 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); 
 // Output bf16 (q == nullptr) or e4m3 + scales sc[g][(col/128) * sc_ld + row].
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ sc,
                                 int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, int groups, int rows, int I) {
-  const int cg = I / 128;
-  long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (gw >= (long long)groups * rows * cg) return;
-  int c = (int)(gw % cg); long long t = gw / cg; int row = (int)(t % rows), g = (int)(t / rows), lane = threadIdx.x & 31;
-  if (rows_valid && row >= rows_valid[g]) return;
-  const __nv_bfloat16* xr = x + ((long long)g * rows + row) * 2 * I + c * 128 + lane * 4;
-  uint2 gv = *reinterpret_cast<const uint2*>(xr), uv = *reinterpret_cast<const uint2*>(xr + I);
-  float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), u0 = unpack_bf16x2(uv.x), u1 = unpack_bf16x2(uv.y);
-  float v[4] = {silu(g0.x) * u0.x, silu(g0.y) * u0.y, silu(g1.x) * u1.x, silu(g1.y) * u1.y};
-  long long o = ((long long)g * rows + row) * I + c * 128 + lane * 4;
-  if (!q) {
-    *reinterpret_cast<uint2*>(y + o) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
-    return;
-  }
-  float amax = 0.f;
+  // grid-stride over (group, valid row, 128-column block): a sparsely filled masked layout costs only its valid rows
+  const int cg = I / 128, lane = threadIdx.x & 31;
+  const long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nw = (long long)gridDim.x * (blockDim.x >> 5);
+  for (int g = 0; g < groups; g++) {
+    int nrows = rows_valid ? rows_valid[g] : rows;
+    nrows = nrows < rows ? nrows : rows;
+    const long long items = (long long)nrows * cg;
+    for (long long it = w0; it < items; it += nw) {
+      const int row = (int)(it / cg), c = (int)(it % cg);
+      const __nv_bfloat16* xr = x + ((long long)g * rows + row) * 2 * I + c * 128 + lane * 4;
+      uint2 gv = *reinterpret_cast<const uint2*>(xr), uv = *reinterpret_cast<const uint2*>(xr + I);
+      float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), u0 = unpack_bf16x2(uv.x), u1 = unpack_bf16x2(uv.y);
+      float v[4] = {silu(g0.x) * u0.x, silu(g0.y) * u0.y, silu(g1.x) * u1.x, silu(g1.y) * u1.y};
+      const long long o = ((long long)g * rows + row) * I + c * 128 + lane * 4;
+      if (!q) {
+        *reinterpret_cast<uint2*>(y + o) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+        continue;
+      }
+      float amax = 0.f;
 #pragma unroll
-  for (int j = 0; j < 4; j++) { v[j] = __bfloat162float(__float2bfloat16(v[j])); amax = fmaxf(amax, fabsf(v[j])); }
-  amax = fmaxf(warp_max(amax), 1e-10f);
-  float is = kFp8Max / amax;
-  *reinterpret_cast<uint32_t*>(q + o) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
-  if (lane == 0) sc[(long long)g * sc_gs + (long long)c * sc_ld + row] = amax / kFp8Max;
+      for (int j = 0; j < 4; j++) { v[j] = __bfloat162float(__float2bfloat16(v[j])); amax = fmaxf(amax, fabsf(v[j])); }
+      amax = fmaxf(warp_max(amax), 1e-10f);
+      const float is = kFp8Max / amax;
+      *reinterpret_cast<uint32_t*>(q + o) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
+      if (lane == 0) sc[(long long)g * sc_gs + (long long)c * sc_ld + row] = amax / kFp8Max;
+    }
+  }
 }
 
 // Rotary embedding on dims [off, off+D) of each of `heads` heads of every row; the result goes to `y` (which may be `x`
@@ -226,7 +233,8 @@ extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld
   if (groups <= 0 || rows <= 0) return 0;
   if (I % 128 != 0) return 1001;
   long long warps = (long long)groups * rows * (I / 128);
-  int blocks = (int)((warps + 7) / 8);
+  long long want = (warps + 7) / 8;
+  int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
   silu_mul_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, groups, rows, I);
   return (int)cudaGetLastError();
 }

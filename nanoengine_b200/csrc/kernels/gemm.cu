@@ -48,8 +48,10 @@ template <int BLOCK_N> struct Smem {
   static constexpr int kABytes = kBlockM * kKBytes;
   static constexpr int kBBytes = BLOCK_N * kKBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (200 * 1024 / kStageBytes) > 10 ? 10 : (200 * 1024 / kStageBytes);
-  static constexpr int kBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kStaging = 8 * 32 * 80;      // per-warp epilogue staging for up to 8 epilogue warps
+  static constexpr int kBudget = 232448 - 1024 - 256 - kStaging;
+  static constexpr int kStages = (kBudget / kStageBytes) > 10 ? 10 : (kBudget / kStageBytes);
+  static constexpr int kBytes = kStages * kStageBytes + kStaging + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct TileSched {
@@ -73,6 +75,32 @@ struct TileSched {
     return false;
   }
 };
+
+// bf16 output goes through a small per-warp staging buffer: each thread parks 32 columns of its row (64 bytes), then the
+// warp writes eight rows per instruction with four lanes covering each row's 64 contiguous bytes.  Compared with every
+// thread writing 16 bytes of a different row this quadruples the contiguous run per row - what matters most when the rows
+// are scattered to peer GPUs by the MoE combine.
+constexpr int kStgPitch = 80;                       // 64 bytes of data + 16 of padding: conflict-free for 16-byte accesses
+constexpr int kStgWarpBytes = 32 * kStgPitch;
+__device__ __forceinline__ void epi_store32_bf16(uint8_t* stg, const float (&v)[32], bool row_ok, __nv_bfloat16* drow, int ncols_left) {
+  const int lane = (int)lane_id();
+  uint8_t* mine = stg + lane * kStgPitch;
+#pragma unroll
+  for (int q = 0; q < 4; q++)
+    *reinterpret_cast<uint4*>(mine + q * 16) = make_uint4(pack_bf16x2(v[q * 8], v[q * 8 + 1]), pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]),
+                                                          pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]));
+  __syncwarp();
+  const int ch = lane & 3;
+#pragma unroll
+  for (int r0 = 0; r0 < 32; r0 += 8) {
+    const int rr = r0 + (lane >> 2);
+    const bool okr = __shfl_sync(0xffffffffu, (int)row_ok, rr) != 0;
+    const unsigned long long dp = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(drow), rr);
+    if (okr && ch * 8 < ncols_left)
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dp) + ch * 8) = *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + ch * 16);
+  }
+  __syncwarp();
+}
 
 // Block-scaled tiles at least 64 wide use two epilogue warpgroups that split the tile's columns, halving the
 // promotion work per thread and per K block.
@@ -99,7 +127,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  uint8_t* staging = smem + kStages * S::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + S::kStaging);
   // bars: full[kStages], empty[kStages], tmem_full[kAcc], tmem_empty[kAcc]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAcc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -237,22 +266,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         }
         if (!ok) break;
-        if (row_ok) {
-          long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0 + cbase;
-          __nv_bfloat16* dbf = args.row_dst ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0 + cbase
-                                            : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
+        {
+          const long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0 + cbase;
+          if (args.out_fp32) {
+            if (row_ok) {
 #pragma unroll
-          for (int c = 0; c < kCols / 8; c++) {
-            if (n0 + cbase + c * 8 < args.N) {
-              if (args.out_fp32) {
-                float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.D) + off + c * 8);
-                p[0] = make_float4(acc[c * 8], acc[c * 8 + 1], acc[c * 8 + 2], acc[c * 8 + 3]);
-                p[1] = make_float4(acc[c * 8 + 4], acc[c * 8 + 5], acc[c * 8 + 6], acc[c * 8 + 7]);
-              } else {
-                uint4 v = make_uint4(pack_bf16x2(acc[c * 8], acc[c * 8 + 1]), pack_bf16x2(acc[c * 8 + 2], acc[c * 8 + 3]),
-                                     pack_bf16x2(acc[c * 8 + 4], acc[c * 8 + 5]), pack_bf16x2(acc[c * 8 + 6], acc[c * 8 + 7]));
-                *reinterpret_cast<uint4*>(dbf + c * 8) = v;
+              for (int c = 0; c < kCols / 8; c++) {
+                if (n0 + cbase + c * 8 < args.N) {
+                  float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.D) + off + c * 8);
+                  p[0] = make_float4(acc[c * 8], acc[c * 8 + 1], acc[c * 8 + 2], acc[c * 8 + 3]);
+                  p[1] = make_float4(acc[c * 8 + 4], acc[c * 8 + 5], acc[c * 8 + 6], acc[c * 8 + 7]);
+                }
               }
+            }
+          } else {
+            __nv_bfloat16* dbf = (args.row_dst && row_ok)
+                ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0 + cbase
+                : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
+            uint8_t* stg = staging + (warp - 2) * kStgWarpBytes;
+#pragma unroll
+            for (int cc = 0; cc < kCols / 32; cc++) {
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] = acc[cc * 32 + j];
+              epi_store32_bf16(stg, v, row_ok, dbf + cc * 32, args.N - (n0 + cbase + cc * 32));
             }
           }
         }
@@ -267,24 +304,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + c * 32, r);
           tc_wait_ld();
-          if (row_ok) {
+          if (args.out_fp32) {
+            if (row_ok) {
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-              int col = n0 + c * 32 + q * 8;
-              if (col < args.N) {
-                if (args.out_fp32) {
+              for (int q = 0; q < 4; q++) {
+                if (n0 + c * 32 + q * 8 < args.N) {
                   float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.D) + off + c * 32 + q * 8);
                   p[0] = make_float4(__uint_as_float(r[q * 8]), __uint_as_float(r[q * 8 + 1]), __uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
                   p[1] = make_float4(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]), __uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
-                } else {
-                  uint4 v = make_uint4(pack_bf16x2(__uint_as_float(r[q * 8]), __uint_as_float(r[q * 8 + 1])),
-                                       pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
-                                       pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
-                                       pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
-                  *reinterpret_cast<uint4*>(dbf + c * 32 + q * 8) = v;
                 }
               }
             }
+          } else {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+            epi_store32_bf16(staging + (warp - 2) * kStgWarpBytes, v, row_ok, dbf + c * 32, args.N - (n0 + c * 32));
           }
         }
         tc_fence_before();

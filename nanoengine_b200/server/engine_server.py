@@ -152,6 +152,22 @@ class EngineClient:
             t.cancel()
         self.sock.close(0)
 
+    def destroy(self):
+        """Drop the socket and the ZMQ context without lingering (safe to call from any thread at shutdown)."""
+        for t in self._tasks:
+            try:
+                t.cancel()
+            except Exception:
+                pass
+        try:
+            self.sock.close(0)
+        except Exception:
+            pass
+        try:
+            self.ctx.destroy(linger=0)
+        except Exception:
+            pass
+
     def next_seq_id(self) -> int:
         self._next += 1
         return self._next

@@ -18,6 +18,9 @@ import time
 import uuid
 from typing import Any, Dict, List, Optional
 
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
 from .._native import _core as C
 from .tokenizer import load_tokenizer
 from .tool_parser import StreamingToolParser, parse as parse_tools
@@ -81,9 +84,6 @@ def anthropic_to_chat(body: Dict[str, Any]) -> Dict[str, Any]:
 
 
 def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", mode: str = "hybrid", default_max_tokens: int = 256):
-    from fastapi import FastAPI, Request
-    from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
-
     app = FastAPI(title="nanoengine_b200")
     t_start = time.time()
 
