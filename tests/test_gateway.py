@@ -1,0 +1,171 @@
+"""The C++ gateway against fake engines: hybrid proxying with SSE pass-through, the two-phase PD forward with
+/pd/free, the finished-in-prefill shortcut, 502 on upstream failure, model aliases, and control-plane discovery."""
+import json
+import os
+import socket
+import subprocess
+import threading
+import time
+import urllib.request
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GATEWAY = os.path.join(ROOT, "nanoengine_b200", "_native", "ne-gateway")
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class FakeEngine:
+    def __init__(self, role, finish_in_prefill=False):
+        self.role, self.finish_in_prefill = role, finish_in_prefill
+        self.requests, self.freed = [], []
+        eng = self
+
+        class H(BaseHTTPRequestHandler):
+            def log_message(self, *a):
+                pass
+
+            def do_POST(self):
+                body = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0))) or b"{}")
+                eng.requests.append((self.path, body))
+                if self.path == "/pd/free":
+                    eng.freed.append(body.get("seq_id"))
+                    return self._json({"freed": 1})
+                if self.path == "/list_entities":
+                    return self._json({"entities": eng.entities})
+                kv = body.get("kv_transfer_params") or {}
+                if eng.role == "prefill" and kv.get("do_remote_decode"):
+                    assert body.get("stream") is False
+                    if eng.finish_in_prefill:
+                        return self._json({"id": "x", "choices": [{"index": 0, "message": {"role": "assistant", "content": "done"}}]})
+                    return self._json({"id": "x", "choices": [], "kv_transfer_params": {"migration": "beef", "seq_id": 41, "first_token": 7}})
+                if body.get("stream"):
+                    self.send_response(200)
+                    self.send_header("Content-Type", "text/event-stream")
+                    self.end_headers()
+                    for i in range(3):
+                        self.wfile.write(f"data: {json.dumps({'tok': i, 'role': eng.role, 'first': kv.get('first_token')})}\n\n".encode())
+                        self.wfile.flush()
+                    self.wfile.write(b"data: [DONE]\n\n")
+                    return
+                return self._json({"id": "y", "role": eng.role, "model": body.get("model"), "got_migration": kv.get("migration")})
+
+            def _json(self, obj):
+                b = json.dumps(obj).encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "application/json")
+                self.send_header("Content-Length", str(len(b)))
+                self.end_headers()
+                self.wfile.write(b)
+
+        self.entities = []
+        self.port = _port()
+        self.srv = ThreadingHTTPServer(("127.0.0.1", self.port), H)
+        threading.Thread(target=self.srv.serve_forever, daemon=True).start()
+        self.url = f"http://127.0.0.1:{self.port}"
+
+    def stop(self):
+        self.srv.shutdown()
+
+
+def _gateway(*args):
+    port = _port()
+    p = subprocess.Popen([GATEWAY, "--port", str(port), "--host", "127.0.0.1", *args], stderr=subprocess.DEVNULL)
+    for _ in range(100):
+        try:
+            socket.create_connection(("127.0.0.1", port), timeout=0.2).close()
+            break
+        except OSError:
+            time.sleep(0.05)
+    return p, f"http://127.0.0.1:{port}"
+
+
+def _post(url, body, timeout=10):
+    req = urllib.request.Request(url, json.dumps(body).encode(), {"Content-Type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=timeout) as r:
+            return r.status, r.read()
+    except urllib.error.HTTPError as e:
+        return e.code, e.read()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_hybrid_proxy_stream_and_alias():
+    e = FakeEngine("hybrid")
+    p, gw = _gateway("--hybrid", e.url, "--model-alias", "short=long-model-name")
+    try:
+        st, body = _post(gw + "/v1/chat/completions", {"model": "short", "messages": []})
+        assert st == 200 and json.loads(body)["model"] == "long-model-name"
+        st, body = _post(gw + "/v1/completions", {"prompt": "x", "stream": True})
+        assert st == 200 and body.count(b"data: ") == 4 and body.rstrip().endswith(b"[DONE]")
+        assert json.loads(urllib.request.urlopen(gw + "/health").read())["engines"] == 1
+        assert _post(gw + "/nope", {})[0] == 404
+    finally:
+        p.terminate(); e.stop()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_pd_forward_frees_prefill_and_passes_first_token():
+    pf, dc = FakeEngine("prefill"), FakeEngine("decode")
+    p, gw = _gateway("--prefill", pf.url, "--decode", dc.url)
+    try:
+        st, body = _post(gw + "/v1/chat/completions", {"messages": [], "stream": True, "max_tokens": 5})
+        assert st == 200 and b'"first": 7' in body and b'"role": "decode"' in body
+        path, dbody = dc.requests[-1]
+        assert dbody["kv_transfer_params"] == {"migration": "beef", "seq_id": 41, "first_token": 7} and dbody["stream"] is True
+        for _ in range(50):
+            if pf.freed:
+                break
+            time.sleep(0.05)
+        assert pf.freed == [41]
+        st, body = _post(gw + "/v1/completions", {"prompt": "x"})
+        assert json.loads(body)["got_migration"] == "beef"
+    finally:
+        p.terminate(); pf.stop(); dc.stop()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_pd_request_finished_in_prefill_and_upstream_failure():
+    pf, dc = FakeEngine("prefill", finish_in_prefill=True), FakeEngine("decode")
+    p, gw = _gateway("--prefill", pf.url, "--decode", dc.url)
+    try:
+        st, body = _post(gw + "/v1/chat/completions", {"messages": [], "stream": True})
+        assert st == 200 and body.startswith(b"data: ") and b"done" in body and not dc.requests
+        st, body = _post(gw + "/v1/chat/completions", {"messages": []})
+        assert json.loads(body)["choices"][0]["message"]["content"] == "done"
+    finally:
+        p.terminate(); pf.stop(); dc.stop()
+    dead = f"http://127.0.0.1:{_port()}"
+    p, gw = _gateway("--hybrid", dead)
+    try:
+        st, body = _post(gw + "/v1/completions", {"prompt": "x"})
+        assert st == 502 and b"gateway_error" in body
+    finally:
+        p.terminate()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_discovery_adds_and_removes_engines():
+    ctrl, e = FakeEngine("ctrl"), FakeEngine("hybrid")
+    ctrl.entities = [{"id": "e0", "role": "hybrid", "host": "127.0.0.1", "port": e.port, "model": "m"}]
+    p, gw = _gateway("--ctrl-address", ctrl.url)
+    try:
+        for _ in range(40):
+            if json.loads(urllib.request.urlopen(gw + "/engines").read()):
+                break
+            time.sleep(0.1)
+        assert _post(gw + "/v1/completions", {"prompt": "x"})[0] == 200
+        ctrl.entities = []
+        for _ in range(80):
+            if not json.loads(urllib.request.urlopen(gw + "/engines").read()):
+                break
+            time.sleep(0.1)
+        assert _post(gw + "/v1/completions", {"prompt": "x"})[0] == 503
+    finally:
+        p.terminate(); ctrl.stop(); e.stop()
