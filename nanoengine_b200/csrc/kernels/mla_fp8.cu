@@ -318,3 +318,55 @@ extern "C" int ne_mla_fp8(const void* q8, const void* cache, int num_blocks, con
   mla_fp8_kernel<<<grid, kMlaThreads, kMlaSmem, st>>>(tq128, tq64, tk128, tk64, a);
   return (int)cudaGetLastError();
 }
+
+// ---- allocation-free entry point ----------------------------------------------------------------------
+// (declared in ne_noalloc.h; this entry point has no counterpart in the reference)
+//
+// Split-KV decode needs scratch for the per-slice partial outputs and their log-sum-exp values.  The regular entry point
+// takes that scratch from its caller.  Some callers have nowhere to get it: a C host program that links this library
+// without a tensor allocator, or code that runs where cudaMalloc is not allowed (inside a stream capture, or in a process
+// whose memory was carved up front).  For them the scratch lives in a file-scope device array of fixed size, so every GPU
+// that loads the library carries kNoAllocScratchBytes of it until the process exits.
+namespace ne {
+constexpr long long kNoAllocMaxSliceRows = 4096;                                  // splits * T * H may not exceed this
+constexpr long long kNoAllocScratchBytes = kNoAllocMaxSliceRows * (kDv + 1) * 4;  // partial outputs + log-sum-exp, fp32
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+}  // namespace ne
+
+extern "C" int ne_attn_merge(const float* part, const float* lse2, void* out, int splits, long long rows, int D, int out_row_stride, cudaStream_t st);
+
+// Same contract as ne_mla_fp8 with splits >= 1, but the caller passes inputs and the output only.
+// * The first call on a device resolves the device address of the scratch array (cudaGetSymbolAddress) for that device;
+//   make that first call outside any stream capture.  The address is cached per device.
+// * Nothing in the scratch has to start at zero: every (slice, row) the merge reads is written by the attention kernel of
+//   the same call, and slices that saw no key are marked by an infinite log-sum-exp and skipped.
+// * All calls on a device share the one array.  Calls that may overlap on the GPU (different streams without an ordering
+//   between them) race on it; issue them on one stream or order them with events.
+// * Returns 1101 when splits * T * H exceeds kNoAllocMaxSliceRows (4096); no cudaMalloc / cudaFree is made on any path.
+extern "C" int ne_mla_fp8_noalloc(const void* q8, const void* cache, int num_blocks, const int* block_tables, int bt_stride,
+                                  const int* cu_seqlens_q, const int* context_lens, int num_seqs, int T, int H, int splits, float scale,
+                                  void* out, cudaStream_t st) {
+  static unsigned char* scratch_of_device[64] = {nullptr};
+  if (T <= 0) return 0;
+  if (splits < 1 || H < 1 || H > 128) return 1001;
+  const long long slice_rows = (long long)splits * T * H;
+  if (slice_rows > kNoAllocMaxSliceRows) return 1101;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return 1102;
+  if (!scratch_of_device[dev]) {
+    // in host code the array's name is only a handle; the kernels need its address in this device's memory
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    scratch_of_device[dev] = static_cast<unsigned char*>(p);
+  }
+  if (splits == 1)
+    return ne_mla_fp8(q8, cache, num_blocks, block_tables, bt_stride, cu_seqlens_q, context_lens, num_seqs, T, H, 1, scale, out, nullptr, nullptr, st);
+  float* part = reinterpret_cast<float*>(scratch_of_device[dev]);
+  float* lse2 = part + slice_rows * kDv;
+  int rc = ne_mla_fp8(q8, cache, num_blocks, block_tables, bt_stride, cu_seqlens_q, context_lens, num_seqs, T, H, splits, scale, out, part, lse2, st);
+  if (rc) return rc;
+  return ne_attn_merge(part, lse2, out, splits, (long long)T * H, kDv, kDv, st);
+}

@@ -1,0 +1,59 @@
+"""The allocation-free attention entry point (for hosts without an allocator or code that may not call cudaMalloc) must
+give what the regular entry point gives.  Called through its exported C symbol, twice in a row so the second call runs on
+a scratch array that still holds the first call's contents."""
+import ctypes as c
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+def _case(seed, ctx_lens, H):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    B, bs = len(ctx_lens), 64
+    nb = [(n + bs - 1) // bs for n in ctx_lens]
+    total = sum(nb) + 2
+    perm = torch.randperm(total, device="cuda", generator=g).to(torch.int32)
+    bt = torch.zeros(B, max(nb) + 1, dtype=torch.int32, device="cuda")
+    o = 0
+    for i, n in enumerate(nb):
+        bt[i, :n] = perm[o:o + n]; o += n
+    cache = (torch.randn(total, bs, 576, device="cuda", generator=g) * 0.5).to(FP8)
+    q = (torch.randn(B, H, 576, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+    cl = torch.tensor(ctx_lens, dtype=torch.int32, device="cuda")
+    return q, cache, bt, cu, cl
+
+
+def test_noalloc_entry_matches_regular_entry_twice():
+    from nanoengine_b200.ops import sm100, sm100_attn
+    lib = sm100.lib()
+    fn = lib.ne_mla_fp8_noalloc
+    fn.restype = c.c_int
+    st = c.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for seed, ctx, H, splits in [(1, [700, 65, 300], 128, 3), (2, [1, 513], 64, 4)]:
+        q, cache, bt, cu, cl = _case(seed, ctx, H)
+        T = q.shape[0]
+        want = sm100_attn.mla_attention_paged(q, cache, bt, cu, cl, 0.0722, 512, splits=splits)
+        q8 = torch.empty(T * H, 576, dtype=torch.uint8, device="cuda")
+        assert lib.ne_cast_e4m3(c.c_void_p(q.data_ptr()), c.c_void_p(q8.data_ptr()), c.c_longlong(q.numel()), st) == 0
+        out = torch.empty(T, H, 512, dtype=torch.bfloat16, device="cuda")
+        before = torch.cuda.memory_allocated()
+        rc = fn(c.c_void_p(q8.data_ptr()), c.c_void_p(cache.data_ptr()), c.c_int(cache.shape[0]), c.c_void_p(bt.data_ptr()),
+                c.c_int(bt.stride(0)), c.c_void_p(cu.data_ptr()), c.c_void_p(cl.data_ptr()), c.c_int(cl.numel()), c.c_int(T), c.c_int(H),
+                c.c_int(splits), c.c_float(0.0722), c.c_void_p(out.data_ptr()), st)
+        torch.cuda.synchronize()
+        assert rc == 0 and torch.cuda.memory_allocated() == before
+        rel = ((out.float() - want.float()).norm() / want.float().norm()).item()
+        assert rel < 1e-3, rel       # same kernels, same split count: only the scratch location differs
+    # beyond the fixed scratch: refused with a clear code, nothing launched
+    q, cache, bt, cu, cl = _case(3, [64] * 40, 128)
+    q8 = torch.zeros(40 * 128, 576, dtype=torch.uint8, device="cuda")
+    out = torch.empty(40, 128, 512, dtype=torch.bfloat16, device="cuda")
+    rc = fn(c.c_void_p(q8.data_ptr()), c.c_void_p(cache.data_ptr()), c.c_int(cache.shape[0]), c.c_void_p(bt.data_ptr()), c.c_int(bt.stride(0)),
+            c.c_void_p(cu.data_ptr()), c.c_void_p(cl.data_ptr()), c.c_int(40), c.c_int(40), c.c_int(128), c.c_int(2), c.c_float(0.07),
+            c.c_void_p(out.data_ptr()), st)
+    assert rc == 1101
+    assert sm100.kernel_status()[0] == 0
