@@ -25,9 +25,9 @@ constexpr int kQNope = 4 * 128 * 128;          // four 128-byte-wide panels of 1
 constexpr int kQBytes = kQNope + 128 * 64;     // + rope panel (64 bytes wide)
 constexpr int kPgNope = 4 * kPage * 128;
 constexpr int kPgBytes = kPgNope + kPage * 64;
-constexpr int kPgStages = 4;
-constexpr int kPBytes = 128 * 64;
-constexpr int kMlaSmem = kQBytes + kPgStages * kPgBytes + kPBytes + 1024 + 256;
+constexpr int kPgStages = 3;
+constexpr int kPBytes = 128 * 64;      // one P buffer; two are kept so softmax of page i+1 overlaps P V of page i
+constexpr int kMlaSmem = kQBytes + kPgStages * kPgBytes + 2 * kPBytes + 1024 + 256;
 
 struct MlaArgs {
   const int* block_tables; int bt_stride;
@@ -46,15 +46,16 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
   uint8_t* sQ = smem;
   uint8_t* sPg = sQ + kQBytes;
   uint8_t* sP = sPg + kPgStages * kPgBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
-  // q_full | pg_full[4] | pg_empty[4] | s_full[2] | s_empty[2] | p_full | p_empty
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kPBytes);
+  // q_full | pg_full[3] | pg_empty[3] | s_full[2] | s_empty[2] | p_full[2] | p_empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  const uint32_t b_qfull = smem_u32(bars), b_pgfull = smem_u32(bars + 1), b_pgempty = smem_u32(bars + 5);
-  const uint32_t b_sfull = smem_u32(bars + 9), b_sempty = smem_u32(bars + 11), b_pfull = smem_u32(bars + 13), b_pempty = smem_u32(bars + 14);
+  const uint32_t b_qfull = smem_u32(bars), b_pgfull = smem_u32(bars + 1), b_pgempty = smem_u32(bars + 4);
+  const uint32_t b_sfull = smem_u32(bars + 7), b_sempty = smem_u32(bars + 9), b_pfull = smem_u32(bars + 11), b_pempty = smem_u32(bars + 13);
 
   const int warp = threadIdx.x >> 5;
-  const int t = blockIdx.x, split = blockIdx.y, vhalf = blockIdx.z;
+  // the two output halves of a token sit in adjacent CTAs so the second reader of every KV page hits L2
+  const int t = blockIdx.x >> 1, vhalf = blockIdx.x & 1, split = blockIdx.y;
 
   // sequence of this token, causal limit, page range of this split (uniform over the CTA)
   int lo = 0, hi = a.num_seqs;
@@ -73,7 +74,7 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
     mbar_init(b_qfull, 1);
     for (int i = 0; i < kPgStages; i++) { mbar_init(b_pgfull + 8 * i, 1); mbar_init(b_pgempty + 8 * i, 1); }
     for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 4); }
-    mbar_init(b_pfull, 4); mbar_init(b_pempty, 1);
+    for (int i = 0; i < 2; i++) { mbar_init(b_pfull + 8 * i, 4); mbar_init(b_pempty + 8 * i, 1); }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -107,18 +108,18 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
       bool ok = mbar_wait(b_qfull, 0, abort_flag, kKernelMla, 200);
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       auto pv = [&](int j) -> bool {
-        if (!mbar_wait(b_pfull, j & 1, abort_flag, kKernelMla, 230)) return false;
+        if (!mbar_wait(b_pfull + 8 * (j & 1), (j >> 1) & 1, abort_flag, kKernelMla, 230)) return false;
         tc_fence_after();
         const int s = j % kPgStages;
         const uint32_t pg = smem_u32(sPg + s * kPgBytes);
 #pragma unroll
         for (int ks = 0; ks < 2; ks++) {
-          uint64_t adesc = make_smem_desc(p_addr + ks * 32, 16, 512, SW_64B);
+          uint64_t adesc = make_smem_desc(p_addr + (j & 1) * kPBytes + ks * 32, 16, 512, SW_64B);
           uint64_t bdesc = make_smem_desc(pg + (vhalf * 2) * kPage * 128 + ks * 32 * 128, 8192, 1024, SW_128B);
           umma_f8(tmem_o, adesc, bdesc, kIdescPV, (j | ks) != 0);
         }
         tc_commit(b_pgempty + 8 * s);
-        tc_commit(b_pempty);
+        tc_commit(b_pempty + 8 * (j & 1));
         return true;
       };
       for (int i = 0; ok && i < n_tiles; i++) {
@@ -175,8 +176,12 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
         tl[j] = (row_ok && key0 + j <= limit) ? s : -INFINITY;
         m_tile = fmaxf(m_tile, tl[j]);
       }
-      const float m_new = fmaxf(m_run, m_tile);
-      const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
+      // Lazy rescaling: the reference maximum only moves when the page's maximum exceeds it by more than 2^8.  Until then
+      // probabilities may be as large as 256 (inside e4m3's range, same relative precision) and O needs no correction;
+      // the result is exact because l_run is accumulated against the same reference.
+      const bool first_valid = (m_run == -INFINITY);
+      const float m_new = (first_valid || m_tile > m_run + 8.f) ? fmaxf(m_run, m_tile) : m_run;
+      const float alpha = (m_new == -INFINITY || first_valid) ? 1.f : exp2f(m_run - m_new);
       float psum = 0.f;
       uint32_t pk[16];
 #pragma unroll
@@ -188,26 +193,26 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
       }
       l_run = l_run * alpha + psum;
       m_run = m_new;
-      if (i > 0) {
-        // P buffer and O are free once the previous page's P V product has retired
-        if (!mbar_wait(b_pempty, (i - 1) & 1, abort_flag, kKernelMla, 310)) { ok = false; break; }
+      // O may only be rescaled once the previous page's P V product has retired; that is rare with lazy rescaling
+      if (i > 0 && __any_sync(0xffffffffu, alpha < 1.f)) {
+        if (!mbar_wait(b_pempty + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, kKernelMla, 310)) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha < 1.f)) {
 #pragma unroll 1
-          for (int cblk = 0; cblk < kVHalf / 16; cblk++) {
-            uint32_t o[16];
-            tmem_ld_32x32b_x16(tmem_o + lane_addr + cblk * 16, o);
-            tc_wait_ld();
+        for (int cblk = 0; cblk < kVHalf / 16; cblk++) {
+          uint32_t o[16];
+          tmem_ld_32x32b_x16(tmem_o + lane_addr + cblk * 16, o);
+          tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st_32x32b_x16(tmem_o + lane_addr + cblk * 16, o);
-          }
-          tc_wait_st();
+          for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_st_32x32b_x16(tmem_o + lane_addr + cblk * 16, o);
         }
+        tc_wait_st();
       }
+      // this page's P buffer was last read by the P V product of page i-2
+      if (i > 1 && !mbar_wait(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1, abort_flag, kKernelMla, 311)) { ok = false; break; }
       // P row (64 e4m3 = 4 chunks of 16 bytes) into the 64B-swizzled K-major layout the MMA reads
       {
-        uint8_t* prow = sP + row * 64;
+        uint8_t* prow = sP + (i & 1) * kPBytes + row * 64;
         const int sw = (row >> 1) & 3;
 #pragma unroll
         for (int cch = 0; cch < 4; cch++)
@@ -216,9 +221,9 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane_id() == 0) mbar_arrive(b_pfull);
+      if (lane_id() == 0) mbar_arrive(b_pfull + 8 * (i & 1));
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(b_pempty, (n_tiles - 1) & 1, abort_flag, kKernelMla, 320);
+    if (ok && n_tiles > 0) ok = mbar_wait(b_pempty + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag, kKernelMla, 320);
     if (ok && n_tiles > 0) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -314,7 +319,7 @@ extern "C" int ne_mla_fp8(const void* q8, const void* cache, int num_blocks, con
   MlaArgs a;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs;
   a.T = T; a.H = H; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f; a.out = (__nv_bfloat16*)out; a.part = part; a.lse2 = lse2;
-  dim3 grid(T, splits, 2);
+  dim3 grid(2 * T, splits, 1);
   mla_fp8_kernel<<<grid, kMlaThreads, kMlaSmem, st>>>(tq128, tq64, tk128, tk64, a);
   return (int)cudaGetLastError();
 }

@@ -120,9 +120,15 @@ class MultiprocExecutor:
             raise ExecutorError(val)
         return val
 
+    def _send(self, r: int, msg) -> None:
+        try:
+            self.conns[r].send(msg)
+        except (BrokenPipeError, OSError) as e:
+            raise ExecutorError(f"worker {r} is gone (exit code {self.procs[r].exitcode}): {e}")
+
     def collective_rpc(self, method: str, *args, **kw) -> List[Any]:
-        for c in self.conns:
-            c.send((method, args, kw))
+        for r in range(self.world_size):
+            self._send(r, (method, args, kw))
         return [self._recv(r) for r in range(self.world_size)]
 
     def _batch_index(self, rank: int) -> int:
@@ -132,8 +138,8 @@ class MultiprocExecutor:
     def run_batches(self, blobs: Sequence[bytes]) -> List[bytes]:
         """blobs: one per attention-DP rank.  Returns one result per DP rank (from attention-TP rank 0)."""
         s = self.config.parallel_spec()
-        for r, c in enumerate(self.conns):
-            c.send(("run_from_bytes", (blobs[self._batch_index(r)],), {}))
+        for r in range(self.world_size):
+            self._send(r, ("run_from_bytes", (blobs[self._batch_index(r)],), {}))
         outs = [self._recv(r) for r in range(self.world_size)]
         tp = s.attention_sp * s.attention_tp
         per_stage = self.world_size // s.pp

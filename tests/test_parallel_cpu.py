@@ -1,0 +1,62 @@
+"""Multi-rank layouts on CPU (gloo) ranks: the outputs must equal the single-rank run.
+
+* attention-DP 2 + expert-parallel 2 (DeepSeek-V3 style): the all-gather EP oracle path, dummy batches for the idle rank
+* attention-TP 2 + expert-parallel 2 (Qwen3-MoE style): token-sliced residual stream, head-sharded qkv, reduce-scatter
+* a worker that dies is noticed by the executor instead of hanging the controller
+"""
+import pytest
+import torch
+
+from nanoengine_b200 import Config, LLM, SamplingParams
+from nanoengine_b200.models.config import ModelConfig
+
+
+def _prompts(n, length, seed, vocab):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def _run(cfg, prompts, sp):
+    llm = LLM(cfg)
+    try:
+        return {o["seq_id"]: o["token_ids"] for o in llm.generate(prompts, sp)}
+    finally:
+        llm.shutdown()
+
+
+def test_dp2_ep2_matches_single_rank():
+    base = dict(model="tiny-deepseek-v3", dtype="float32", device="cpu", kvcache_block_size=16, max_num_seqs=8, num_kvcache_blocks=64)
+    prompts = _prompts(3, 24, 1, 1024)       # odd count: one DP rank runs a dummy batch on some steps
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    want = _run(Config(**base), prompts, sp)
+    got = _run(Config(**base, attention_dp=2, ffn_ep=2), prompts, sp)
+    assert got == want
+
+
+def _qwen_cfg():
+    return ModelConfig(architecture="Qwen3MoeForCausalLM", vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=8,
+                       num_key_value_heads=2, head_dim=16, rope_theta=1e6, max_position_embeddings=1024, intermediate_size=256,
+                       n_routed_experts=8, n_shared_experts=0, num_experts_per_tok=2, moe_intermediate_size=64, first_k_dense_replace=0,
+                       n_group=1, topk_group=1, scoring_func="softmax", qk_norm=True, q_lora_rank=None, routed_scaling_factor=1.0)
+
+
+def test_tp2_ep2_qwen3_moe_matches_single_rank():
+    base = dict(model="qwen3-tiny", dummy_weight=True, dtype="float32", device="cpu", kvcache_block_size=16, max_num_seqs=8, num_kvcache_blocks=64)
+    prompts = _prompts(3, 21, 2, 512)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = _run(Config(**base, model_config=_qwen_cfg()), prompts, sp)
+    got = _run(Config(**base, model_config=_qwen_cfg(), attention_tp=2, ffn_ep=2), prompts, sp)
+    assert got == want
+
+
+def test_dead_worker_is_reported():
+    from nanoengine_b200.engine.executor import ExecutorError, MultiprocExecutor
+    cfg = Config(model="tiny-deepseek-v3", dtype="float32", device="cpu", kvcache_block_size=16, num_kvcache_blocks=32, attention_dp=2, ffn_ep=2)
+    ex = MultiprocExecutor(cfg, timeout_s=30)
+    try:
+        ex.procs[1].terminate()
+        ex.procs[1].join(timeout=10)
+        with pytest.raises(ExecutorError):
+            ex.collective_rpc("get_step_timing")
+    finally:
+        ex.shutdown()
