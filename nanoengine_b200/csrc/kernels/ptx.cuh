@@ -50,16 +50,24 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait (about a second at most).  `abort_flag` is a shared-memory word all roles of a CTA watch: once
-// one of them gives up, the others stop waiting too.
-constexpr uint32_t kSpinLimit = 1u << 22;
+// Hardware-suspended wait: the thread sleeps inside the barrier unit until the phase completes or `hint_ns` elapses.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+  return ok != 0;
+}
+// Bounded wait (a couple of seconds at most): a short poll for the common case, then hardware-suspended waits of 20 us
+// each.  `abort_flag` is a shared-memory word all roles of a CTA watch: once one of them gives up, the others stop too.
+constexpr uint32_t kSpinLimit = 1u << 22;          // iteration budget of flag polls on global memory
+constexpr uint32_t kMbarTries = 100000;            // x 20 us
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int kernel_id, int where) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) {
-      __nanosleep(i > 4096 ? 256 : 32);
-      if ((i & 255) == 0 && *abort_flag) return false;
-    }
+#pragma unroll 1
+  for (int i = 0; i < 16; ++i) if (mbar_test(bar, parity)) return true;
+#pragma unroll 1
+  for (uint32_t i = 0; i < kMbarTries; ++i) {
+    if (mbar_try_wait(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
   }
   *abort_flag = 1;
   report(ST_MBAR_TIMEOUT, kernel_id, where, (int)parity);
