@@ -1,0 +1,66 @@
+// PD disaggregation data path: the prefill GPU pushes the KV pages of finished prompts straight into the decode GPU's
+// paged pool with peer stores, translating page ids on the way (prefill page ids differ from decode page ids), then raises
+// a per-request completion flag the decode side polls.  One CTA copies one (layer, page) pair; the last CTA to finish
+// publishes the flags after a system-scope fence, so a flag never overtakes its data.
+//
+// Replaces in the reference: the decode-side pull of runtime/disagg/p2p/cache_transfer.py:648-1142 (coalesced one-sided
+// reads followed by a device synchronise) and the byte-stride bookkeeping of disagg/p2p/cache_layout.py:14-240.
+#include "ptx.cuh"
+
+namespace ne {
+
+struct KvPushArgs {
+  const uint8_t* src; uint8_t* dst;                 // cache bases: [layers, blocks, page_bytes] on each side
+  long long src_layer_stride, dst_layer_stride;     // bytes
+  int page_bytes;                                   // bytes of one page of one layer (multiple of 16)
+  const int* src_blocks; const int* dst_blocks;     // [n_pairs]
+  int n_pairs, layers;
+  int* flags; const int* flag_index; int n_flags; int flag_value;   // dst-side flag words (peer memory), one per request
+  int* cta_counter;
+};
+
+__global__ void __launch_bounds__(256) kv_push_kernel(const KvPushArgs a) {
+  const int pair = blockIdx.x, layer = blockIdx.y;
+  const uint4* s = reinterpret_cast<const uint4*>(a.src + (long long)layer * a.src_layer_stride + (long long)a.src_blocks[pair] * a.page_bytes);
+  uint4* d = reinterpret_cast<uint4*>(a.dst + (long long)layer * a.dst_layer_stride + (long long)a.dst_blocks[pair] * a.page_bytes);
+  const int n = a.page_bytes / 16;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) d[i] = s[i];
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.cta_counter, 1) == (int)(gridDim.x * gridDim.y) - 1);
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) *a.cta_counter = 0;
+    __threadfence_system();
+    for (int f = threadIdx.x; f < a.n_flags; f += blockDim.x) st_release_sys(a.flags + a.flag_index[f], a.flag_value);
+  }
+}
+
+// Bounded wait for completion flags (decode side): out[i] = 1 if flags[idx[i]] >= want within the budget, else 0.
+__global__ void kv_wait_kernel(const int* flags, const int* idx, int n, int want, int* out, int spin_limit) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  out[i] = wait_flag_ge(flags + idx[i], want, 4, i, (uint32_t)spin_limit) ? 1 : 0;
+}
+
+}  // namespace ne
+
+using namespace ne;
+
+extern "C" int ne_kv_push(const void* src, void* dst, long long src_layer_stride, long long dst_layer_stride, int page_bytes,
+                          const int* src_blocks, const int* dst_blocks, int n_pairs, int layers, int* flags, const int* flag_index,
+                          int n_flags, int flag_value, int* cta_counter, cudaStream_t st) {
+  if (n_pairs <= 0 || layers <= 0) return 0;
+  if (page_bytes % 16) return 1001;
+  KvPushArgs a{(const uint8_t*)src, (uint8_t*)dst, src_layer_stride, dst_layer_stride, page_bytes, src_blocks, dst_blocks, n_pairs, layers,
+               flags, flag_index, n_flags, flag_value, cta_counter};
+  kv_push_kernel<<<dim3(n_pairs, layers), 256, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_kv_wait(const int* flags, const int* idx, int n, int want, int* out, int spin_limit, cudaStream_t st) {
+  if (n <= 0) return 0;
+  kv_wait_kernel<<<(n + 127) / 128, 128, 0, st>>>(flags, idx, n, want, out, spin_limit);
+  return (int)cudaGetLastError();
+}

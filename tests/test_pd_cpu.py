@@ -1,0 +1,74 @@
+"""Prefill/decode disaggregation on CPU engines in one process: a prompt prefilled on one engine and decoded on another
+yields exactly the tokens of a hybrid engine; incompatible engines are refused; a vanished peer fails only that request."""
+import pytest
+import torch
+
+from nanoengine_b200 import Config, LLM, RequestMigrate, SamplingParams
+from nanoengine_b200.parallel.kv_transfer import KVMigrator, LocalTransport, check_compatible
+
+
+def _cfg(mode, **kw):
+    base = dict(model="tiny-deepseek-v3", dtype="float32", device="cpu", kvcache_block_size=16, max_num_seqs=8, num_kvcache_blocks=64, mode=mode)
+    base.update(kw)
+    return Config(**base)
+
+
+def _prompts():
+    g = torch.Generator().manual_seed(21)
+    return [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (30, 17, 45)]
+
+
+def _pair(**kw):
+    prefill, decode = LLM(_cfg("prefill", engine_id="p0", **kw)), LLM(_cfg("decode", engine_id="d0", **kw))
+    tr = LocalTransport([prefill.engine.executor.runner], [decode.engine.executor.runner])
+    decode.engine.migrator = KVMigrator(tr, decode.engine.engine_info(), prefill.engine.engine_info())
+    return prefill, decode
+
+
+def test_pd_pipeline_equals_hybrid():
+    sp = SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True)
+    want = {o["seq_id"]: o["token_ids"] for o in LLM(_cfg("hybrid")).generate(_prompts(), sp)}
+    prefill, decode = _pair()
+    blobs = prefill.generate(_prompts(), sp, return_serialized=True)
+    assert len(blobs) == 3
+    firsts = {}
+    for b in blobs:
+        m = RequestMigrate.from_bytes(b)
+        sid, first = m.metadata
+        firsts[sid] = first
+        decode.add_request_payload(b)
+    outs = {o["seq_id"]: o["token_ids"] for o in decode.generate()}
+    got = {sid: [firsts[sid]] + toks for sid, toks in outs.items()}
+    assert got == want
+    assert prefill.free_to_be_migrated_ids(list(firsts)) == 3
+    assert prefill.engine.scheduler.num_free_blocks() == 64
+
+
+def test_pd_with_mtp_hands_the_drafts_over():
+    kw = dict(hf_overrides={"num_nextn_predict_layers": 1}, num_speculative_tokens=2)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    want = {o["seq_id"]: o["token_ids"] for o in LLM(_cfg("hybrid", **kw)).generate(_prompts()[:2], sp)}
+    prefill, decode = _pair(**kw)
+    blobs = prefill.generate(_prompts()[:2], sp, return_serialized=True)
+    firsts = {}
+    for b in blobs:
+        sid, first = RequestMigrate.from_bytes(b).metadata
+        firsts[sid] = first
+        decode.add_request_payload(b)
+    outs = {o["seq_id"]: [firsts[o["seq_id"]]] + o["token_ids"] for o in decode.generate()}
+    assert outs == want
+
+
+def test_incompatible_engines_and_vanished_peer():
+    a = {"architecture": "X", "block_size": 64, "kv_cache_dtype": "fp8", "num_hidden_layers": 4, "mtp_num_kv_layers": 0, "num_blocks": 8}
+    with pytest.raises(ValueError):
+        check_compatible(a, dict(a, block_size=16))
+    prefill, decode = _pair()
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    blobs = prefill.generate(_prompts()[:2], sp, return_serialized=True)
+    decode.engine.migrator.fail_next = True          # the first transfer fails on the host; no GPU fault involved
+    for b in blobs:
+        decode.add_request_payload(b)
+    outs = decode.generate()
+    assert len(outs) == 1                              # the failed request was dropped, the other one decoded
+    assert decode.engine.scheduler.num_free_blocks() == 64
