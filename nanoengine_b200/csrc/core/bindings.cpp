@@ -266,6 +266,7 @@ PYBIND11_MODULE(_core, m) {
       .def(py::init<const SchedulerConfig&>())
       .def_property_readonly("config", &Scheduler::config)
       .def("update_num_blocks", &Scheduler::update_num_blocks)
+      .def("reset_prefix_cache", &Scheduler::reset_prefix_cache)
       .def("add_request", &Scheduler::add_request)
       .def("add_migration", &Scheduler::add_migration)
       .def("add_request_bytes", [](Scheduler& s, const std::string& b) { return s.add_request_bytes(b); })

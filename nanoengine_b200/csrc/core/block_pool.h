@@ -127,6 +127,15 @@ class BlockPool {
 
   uint64_t evictions() const { return evictions_; }
 
+  // Forget every cached prefix (the KV it describes is stale, e.g. after a weight update).  Blocks in use stay allocated
+  // but lose their hash, so they return to the free list when released.
+  void clear_cache() {
+    for (int id : lru_) { Block& b = blocks_[id]; b.in_lru = false; b.hash = 0; b.state = BLOCK_EMPTY; free_.push_back(id); }
+    lru_.clear();
+    for (auto& b : blocks_) b.hash = 0;
+    by_hash_.clear();
+  }
+
  private:
   struct Block {
     int32_t ref = 0;

@@ -97,6 +97,11 @@ class Scheduler {
     throw WireError("add_request_bytes: not a request packet");
   }
 
+  void reset_prefix_cache() {
+    for (auto& p : pools_) p.clear_cache();
+    for (auto& kv : seqs_) { kv.second->commit_cursor = (int)kv.second->block_table.size(); }   // live sequences publish nothing stale
+  }
+
   // ---- scheduling ------------------------------------------------------------------------
   const ScheduleResult& schedule() {
     step_++;

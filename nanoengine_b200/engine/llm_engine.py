@@ -131,7 +131,9 @@ class LLMEngine:
 
     def update_weights(self, named_tensors_or_path) -> int:
         """Swap weights in place (live update).  Accepts a checkpoint directory or an iterable of (name, tensor)."""
-        return min(self.executor.collective_rpc("update_weights", named_tensors_or_path))
+        n = min(self.executor.collective_rpc("update_weights", named_tensors_or_path))
+        self.scheduler.reset_prefix_cache()      # cached KV was computed with the old weights
+        return n
 
     def metrics_prometheus(self) -> str:
         return self.scheduler.metrics_prometheus()

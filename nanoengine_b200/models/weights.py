@@ -311,8 +311,11 @@ def save_hf_checkpoint(path: str, cfg: ModelConfig, weights: Iterable[Tuple[str,
     from safetensors.torch import save_file
     from ..ops import reference as ref
     os.makedirs(path, exist_ok=True)
+    cd = cfg.to_dict()
+    if quantize_fp8:
+        cd["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128]}
     with open(os.path.join(path, "config.json"), "w") as f:
-        json.dump(cfg.to_dict(), f, indent=1)
+        json.dump(cd, f, indent=1)
     shard, size, idx = {}, 0, 0
 
     def flush():

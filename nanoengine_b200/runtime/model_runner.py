@@ -124,6 +124,18 @@ class ModelRunner:
             return load_deepseek_weights(self.model, it, mtp=self.mtp)
         return self.model.load_weights(it)
 
+    def update_weights(self, src) -> int:
+        """Replace the weights in place from a checkpoint directory or an iterable of (name, tensor).  Derived copies that
+        kernels cache (transposed / bf16 forms) are dropped so they are rebuilt from the new values."""
+        keep = expert_owner_filter(self.mc, self.dist.ep_size, self.dist.ep_rank, None)
+        it = iterate_safetensors(src, keep, self.device) if isinstance(src, str) else ((n, t) for n, t in src if keep(n))
+        n = self.load_weights(it)
+        if self.device.type == "cuda":
+            from ..ops import sm100
+            sm100._BF16_CACHE.clear()
+            self.graphs = None if self.graphs is None else type(self.graphs)(self)
+        return n
+
     # ---- cache -------------------------------------------------------------------------------
     def profile_num_blocks(self) -> int:
         """How many KV blocks fit: run a worst-case prefill to find peak activation memory, then apply the budget formula."""
