@@ -117,7 +117,8 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); 
 // x [groups, rows, 2I] -> y.  One warp per (row, 128 output columns).  rows_valid[g] masks rows (nullptr = all).
 // Output bf16 (q == nullptr) or e4m3 + scales sc[g][(col/128) * sc_ld + row].
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ sc,
-                                int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, int groups, int rows, int I) {
+                                int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, const int* __restrict__ row_start, int groups,
+                                int rows, int I) {
   // grid-stride over (group, valid row, 128-column block): a sparsely filled masked layout costs only its valid rows
   const int cg = I / 128, lane = threadIdx.x & 31;
   const long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -125,14 +126,18 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
   for (int g = 0; g < groups; g++) {
     int nrows = rows_valid ? rows_valid[g] : rows;
     nrows = nrows < rows ? nrows : rows;
+    // contiguous grouped layout: group g owns rows [row_start[g], +rows_valid[g]) of one flat matrix; otherwise [groups, rows, *]
+    const long long gbase = row_start ? 0 : (long long)g * rows;
+    const int r0 = row_start ? row_start[g] : 0;
     const long long items = (long long)nrows * cg;
     for (long long it = w0; it < items; it += nw) {
-      const int row = (int)(it / cg), c = (int)(it % cg);
-      const __nv_bfloat16* xr = x + ((long long)g * rows + row) * 2 * I + c * 128 + lane * 4;
+      const int row = r0 + (int)(it / cg), c = (int)(it % cg);
+      if (row >= rows && row_start) continue;
+      const __nv_bfloat16* xr = x + (gbase + row) * 2 * I + c * 128 + lane * 4;
       uint2 gv = *reinterpret_cast<const uint2*>(xr), uv = *reinterpret_cast<const uint2*>(xr + I);
       float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), u0 = unpack_bf16x2(uv.x), u1 = unpack_bf16x2(uv.y);
       float v[4] = {silu(g0.x) * u0.x, silu(g0.y) * u0.y, silu(g1.x) * u1.x, silu(g1.y) * u1.y};
-      const long long o = ((long long)g * rows + row) * I + c * 128 + lane * 4;
+      const long long o = (gbase + row) * I + c * 128 + lane * 4;
       if (!q) {
         *reinterpret_cast<uint2*>(y + o) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
         continue;
@@ -143,7 +148,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
       amax = fmaxf(warp_max(amax), 1e-10f);
       const float is = kFp8Max / amax;
       *reinterpret_cast<uint32_t*>(q + o) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
-      if (lane == 0) sc[(long long)g * sc_gs + (long long)c * sc_ld + row] = amax / kFp8Max;
+      if (lane == 0) sc[(row_start ? 0 : (long long)g * sc_gs) + (long long)c * sc_ld + row] = amax / kFp8Max;
     }
   }
 }
@@ -228,14 +233,14 @@ extern "C" int ne_quant_1x128(const void* x, long long x_ld, void* q, float* sc,
   return (int)cudaGetLastError();
 }
 
-extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, int groups,
-                           int rows, int I, cudaStream_t st) {
+extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, const int* row_start,
+                           int groups, int rows, int I, cudaStream_t st) {
   if (groups <= 0 || rows <= 0) return 0;
   if (I % 128 != 0) return 1001;
   long long warps = (long long)groups * rows * (I / 128);
   long long want = (warps + 7) / 8;
   int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
-  silu_mul_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, groups, rows, I);
+  silu_mul_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, row_start, groups, rows, I);
   return (int)cudaGetLastError();
 }
 

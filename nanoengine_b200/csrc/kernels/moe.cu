@@ -99,31 +99,81 @@ __global__ void moe_scan_kernel(const int* __restrict__ counts, int* __restrict_
   for (int e = threadIdx.x; e <= E; e += blockDim.x) row_start[e] = s[e];
 }
 
-// one warp per (token, k) pair; writes pos[t,k] (row in the expert-major buffer, -1 if not local / overflow)
-__global__ void moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx, const int* __restrict__ slot,
+// One CTA per token: the row is quantised to e4m3 1x128 once (kept in shared memory) and then copied to each of the
+// token's local experts; writes pos[t,k] (row in the expert-major buffer, -1 if not local / overflow).
+__global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx, const int* __restrict__ slot,
                                    const int* __restrict__ row_start, int* __restrict__ pos, __nv_bfloat16* __restrict__ a_bf16,
-                                   uint8_t* __restrict__ a_q, float* __restrict__ a_s, int s_ld, int n_pairs, int top_k, int H,
+                                   uint8_t* __restrict__ a_q, float* __restrict__ a_s, int s_ld, int top_k, int H,
                                    int expert_offset, int E_local, int max_rows) {
-  int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (i >= n_pairs) return;
-  int e = idx[i] - expert_offset, sl = slot[i];
-  int row = -1;
-  if (e >= 0 && e < E_local && sl >= 0) { row = row_start[e] + sl; if (row >= max_rows) row = -1; }
-  if (lane == 0) pos[i] = row;
-  if (row < 0) return;
-  const __nv_bfloat16* xr = x + (long long)(i / top_k) * H;
+  extern __shared__ uint8_t s_raw[];
+  uint32_t* s_q = reinterpret_cast<uint32_t*>(s_raw);                 // H bytes of e4m3
+  float* s_sc = reinterpret_cast<float*>(s_raw + H);                  // H/128 scales
+  __shared__ int s_row[64];
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if ((int)threadIdx.x < top_k) {
+    const int i = t * top_k + threadIdx.x;
+    const int e = idx[i] - expert_offset, sl = slot[i];
+    int row = -1;
+    if (e >= 0 && e < E_local && sl >= 0) { row = row_start[e] + sl; if (row >= max_rows) row = -1; }
+    pos[i] = row; s_row[threadIdx.x] = row;
+  }
+  const __nv_bfloat16* xr = x + (long long)t * H;
   if (a_q) {
-    for (int g = 0; g < H / 128; g++) {
+    for (int g = warp; g < H / 128; g += nw) {
       uint2 v = *reinterpret_cast<const uint2*>(xr + g * 128 + lane * 4);
       float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
       float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
       amax = fmaxf(warp_max(amax), 1e-10f);
-      float is = 448.f / amax;
-      *reinterpret_cast<uint32_t*>(a_q + (long long)row * H + g * 128 + lane * 4) = pack_e4m3x4(a.x * is, a.y * is, b.x * is, b.y * is);
-      if (lane == 0) a_s[(long long)g * s_ld + row] = amax / 448.f;
+      const float is = 448.f / amax;
+      s_q[g * 32 + lane] = pack_e4m3x4(a.x * is, a.y * is, b.x * is, b.y * is);
+      if (lane == 0) s_sc[g] = amax / 448.f;
     }
-  } else {
-    for (int c = lane * 8; c < H; c += 256) *reinterpret_cast<uint4*>(a_bf16 + (long long)row * H + c) = *reinterpret_cast<const uint4*>(xr + c);
+  }
+  __syncthreads();
+  for (int k = 0; k < top_k; k++) {
+    const int row = s_row[k];
+    if (row < 0) continue;
+    if (a_q) {
+      uint4* dst = reinterpret_cast<uint4*>(a_q + (long long)row * H);
+      const uint4* src = reinterpret_cast<const uint4*>(s_q);
+      for (int c = threadIdx.x; c < H / 16; c += blockDim.x) dst[c] = src[c];
+      for (int g = threadIdx.x; g < H / 128; g += blockDim.x) a_s[(long long)g * s_ld + row] = s_sc[g];
+    } else {
+      for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) *reinterpret_cast<uint4*>(a_bf16 + (long long)row * H + c) = *reinterpret_cast<const uint4*>(xr + c);
+    }
+  }
+}
+
+// Router logits on CUDA cores with the fp32 gate weight: logits[t, e] = x[t, :] . w[e, :].  One CTA = 8 tokens x 32 experts;
+// the tokens' rows sit in shared memory, each warp streams the rows of 4 experts once and keeps 8 running sums per row.
+__global__ void __launch_bounds__(256) router_gemv_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
+                                                         int T, int E, int H) {
+  extern __shared__ __nv_bfloat16 s_x[];                                // [8][H]
+  const int t0 = blockIdx.x * 8, e0 = blockIdx.y * 32, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x * 8; i < 8 * H; i += blockDim.x * 8) {
+    const int tt = t0 + i / H;
+    *reinterpret_cast<uint4*>(s_x + i) = tt < T ? *reinterpret_cast<const uint4*>(x + (long long)tt * H + (i % H)) : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  for (int ee = warp; ee < 32; ee += 8) {
+    const int e = e0 + ee;
+    if (e >= E) break;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const float* wr = w + (long long)e * H;
+    for (int c = lane * 4; c < H; c += 128) {
+      const float4 wv = *reinterpret_cast<const float4*>(wr + c);
+#pragma unroll
+      for (int tt = 0; tt < 8; tt++) {
+        const uint2 xv = *reinterpret_cast<const uint2*>(s_x + tt * H + c);
+        const float2 a = unpack_bf16x2(xv.x), b = unpack_bf16x2(xv.y);
+        acc[tt] = fmaf(wv.x, a.x, fmaf(wv.y, a.y, fmaf(wv.z, b.x, fmaf(wv.w, b.y, acc[tt]))));
+      }
+    }
+#pragma unroll
+    for (int tt = 0; tt < 8; tt++) {
+      const float v = warp_sum(acc[tt]);
+      if (lane == 0 && t0 + tt < T) logits[(long long)(t0 + tt) * E + e] = v;
+    }
   }
 }
 
@@ -181,8 +231,9 @@ extern "C" int ne_moe_dispatch_local(const void* x, const int* idx, int* counts,
   int n = T * top_k;
   moe_count_kernel<<<(n + 255) / 256, 256, 0, st>>>(idx, counts, slot, n, expert_offset, E_local);
   moe_scan_kernel<<<1, 256, 0, st>>>(counts, row_start, E_local, align);
-  moe_scatter_kernel<<<(n + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, idx, slot, row_start, pos, (__nv_bfloat16*)a_bf16, (uint8_t*)a_q,
-                                                  a_s, s_ld, n, top_k, H, expert_offset, E_local, max_rows);
+  if (top_k > 64) return 1001;
+  moe_scatter_kernel<<<T, 256, (size_t)H + (H / 128) * 4, st>>>((const __nv_bfloat16*)x, idx, slot, row_start, pos, (__nv_bfloat16*)a_bf16,
+                                                                (uint8_t*)a_q, a_s, s_ld, top_k, H, expert_offset, E_local, max_rows);
   return (int)cudaGetLastError();
 }
 
@@ -191,5 +242,20 @@ extern "C" int ne_moe_combine_local(const void* y, const int* pos, const float* 
   if (T <= 0) return 0;
   if (H % 8 || top_k > 64) return 1001;
   moe_combine_kernel<<<T, 256, 0, st>>>((const __nv_bfloat16*)y, pos, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, top_k, H);
+  return (int)cudaGetLastError();
+}
+
+// x bf16 [T, H], w fp32 [E, H] -> logits fp32 [T, E]
+extern "C" int ne_router_gemv(const void* x, const float* w, float* logits, int T, int E, int H, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 128) return 1001;
+  size_t smem = (size_t)8 * H * 2;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(router_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  router_gemv_kernel<<<dim3((T + 7) / 8, (E + 31) / 32), 256, smem, st>>>((const __nv_bfloat16*)x, w, logits, T, E, H);
   return (int)cudaGetLastError();
 }

@@ -37,6 +37,9 @@ class InprocExecutor:
     def run_batches(self, blobs: Sequence[bytes]) -> List[bytes]:
         return [self.runner.run_from_bytes(blobs[0])]
 
+    def run_batches_pipelined(self, waves):
+        return [self.run_batches(w) for w in waves]
+
     def shutdown(self):
         self.runner = None
 
@@ -145,6 +148,20 @@ class MultiprocExecutor:
         per_stage = self.world_size // s.pp
         last_stage = (s.pp - 1) * per_stage
         return [outs[last_stage + d * tp] for d in range(s.attention_dp)]
+
+    def run_batches_pipelined(self, waves: Sequence[Sequence[bytes]]) -> List[List[bytes]]:
+        """Submit every wave of micro-batches before collecting any result, so pipeline stages overlap."""
+        s = self.config.parallel_spec()
+        for wave in waves:
+            for r in range(self.world_size):
+                self._send(r, ("run_from_bytes", (wave[self._batch_index(r)],), {}))
+        tp = s.attention_sp * s.attention_tp
+        last_stage = (s.pp - 1) * (self.world_size // s.pp)
+        out = []
+        for _ in waves:
+            outs = [self._recv(r) for r in range(self.world_size)]
+            out.append([outs[last_stage + d * tp] for d in range(s.attention_dp)])
+        return out
 
     def alive(self) -> List[bool]:
         return [p.is_alive() for p in self.procs]

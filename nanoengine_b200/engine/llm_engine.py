@@ -96,10 +96,40 @@ class LLMEngine:
         if not res.has_work:
             return []
         t0 = time.perf_counter()
-        blobs = self.scheduler.serialize_run_batches()
-        outs = self.executor.run_batches(blobs)
+        if self.config.pp > 1 and res.is_prefill:
+            outs = self._run_static_pp_prefill_pipeline(res)
+        else:
+            outs = self.executor.run_batches(self.scheduler.serialize_run_batches())
         ms = (time.perf_counter() - t0) * 1e3
         return self.scheduler.postprocess_runner_out_bytes(outs, ms)
+
+    def _run_static_pp_prefill_pipeline(self, res) -> List[bytes]:
+        """Split each DP rank's prefill batch into `pp` micro-batches and keep them all in flight: every worker receives
+        the micro-batches in order, so stage s works on micro-batch m while stage s+1 works on m-1."""
+        from ..models.pp import split_batch
+        depth = self.config.pp
+        per_dp = [split_batch(C.RunnerIn.from_bytes(b), depth) for b in self.scheduler.serialize_run_batches()]
+        rounds = max(len(m) for m in per_dp)
+        waves = []
+        for r in range(rounds):
+            wave = []
+            for mbs in per_dp:
+                if r < len(mbs):
+                    wave.append(mbs[r].to_bytes())
+                else:
+                    dummy = C.RunnerIn()
+                    dummy.is_dummy, dummy.is_prefill = True, True
+                    wave.append(dummy.to_bytes())
+            waves.append(wave)
+        results = self.executor.run_batches_pipelined(waves)
+        merged = []
+        for d in range(len(per_dp)):
+            ids, toks, lps = [], [], []
+            for r in range(rounds):
+                o = C.RunnerOut.from_bytes(results[r][d])
+                ids.extend(o.seq_ids); toks.extend(o.token_ids)
+            merged.append(C.RunnerOut(ids, toks).to_bytes())
+        return merged
 
     def _run_migrations(self, res) -> None:
         if self.migrator is None:

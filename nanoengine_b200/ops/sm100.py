@@ -92,14 +92,18 @@ def _as_bf16_2d(x):
 
 def linear(x: torch.Tensor, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, bias=None, out_fp32: bool = False) -> torch.Tensor:
     N, K = w.shape
+    pre = getattr(x, "_ne_q", None)          # (e4m3 [T, K], scales [K/128, T]) left by a fused norm + quant kernel
     x2 = _as_bf16_2d(x)
     T = x2.shape[0]
     out = torch.empty(T, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
     if T > 0:
         if w.dtype == FP8:
-            q = torch.empty(T, K, dtype=FP8, device=x.device)
-            s = torch.empty(K // 128, T, dtype=torch.float32, device=x.device)
-            _ck(lib().ne_quant_1x128(_p(x2), _c.c_longlong(x2.stride(0)), _p(q), _p(s), _c.c_int(T), _c.c_int(T), _c.c_int(K), _st()), "ne_quant_1x128")
+            if pre is not None and pre[0].shape == (T, K):
+                q, s = pre
+            else:
+                q = torch.empty(T, K, dtype=FP8, device=x.device)
+                s = torch.empty(K // 128, T, dtype=torch.float32, device=x.device)
+                _ck(lib().ne_quant_1x128(_p(x2), _c.c_longlong(x2.stride(0)), _p(q), _p(s), _c.c_int(T), _c.c_int(T), _c.c_int(K), _st()), "ne_quant_1x128")
             _gemm(q, K, 0, w, out, N, 0, T, N, K, 1, None, None, True, s, T, 0, w_scale, out_fp32)
         else:
             assert w.dtype == torch.bfloat16, "CUDA linears take bf16 or fp8 weights"
@@ -122,8 +126,14 @@ def _cached(key_t: torch.Tensor, tag: str, fn):
 
 
 def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    wb = _cached(w, "bf16", lambda t: t.to(torch.bfloat16).contiguous())
-    return linear(x, wb, out_fp32=True)
+    """x bf16 [T, H] against the fp32 gate weight [E, H] on CUDA cores (N is far too small for a tensor-core tile)."""
+    x2 = _as_bf16_2d(x)
+    T, H = x2.shape
+    E = w.shape[0]
+    assert w.dtype == torch.float32 and w.is_contiguous() and x2.stride(0) == H
+    out = torch.empty(T, E, dtype=torch.float32, device=x.device)
+    _ck(lib().ne_router_gemv(_p(x2), _p(w), _p(out), _c.c_int(T), _c.c_int(E), _c.c_int(H), _st()), "ne_router_gemv")
+    return out
 
 
 def lm_head(hidden: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -146,15 +156,24 @@ def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = N
 
 
 # ---- norms / activation ----------------------------------------------------------------------------
-def _rmsnorm(x, res_in, w, eps, want_res):
+QUANT_AFTER_NORM = True      # block-level norms also emit the e4m3 1x128 copy their fp8 consumers need
+
+
+def _rmsnorm(x, res_in, w, eps, want_res, quant=False):
     T, H = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1
     out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
     res_out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device) if want_res else None
     if res_in is not None:
         res_in = res_in.contiguous()
-    _ck(lib().ne_rmsnorm(_p(x), _c.c_longlong(x.stride(0)), _p(res_in), _p(w), _p(out), _c.c_longlong(H), _p(res_out), _p(None), _p(None),
-                         _c.c_int(0), _c.c_int(T), _c.c_int(H), _c.c_float(eps), _st()), "ne_rmsnorm")
+    q = sc = None
+    if quant and H % 128 == 0 and T > 0:
+        q = torch.empty(T, H, dtype=FP8, device=x.device)
+        sc = torch.empty(H // 128, T, dtype=torch.float32, device=x.device)
+    _ck(lib().ne_rmsnorm(_p(x), _c.c_longlong(x.stride(0)), _p(res_in), _p(w), _p(out), _c.c_longlong(H), _p(res_out), _p(q), _p(sc),
+                         _c.c_int(T), _c.c_int(T), _c.c_int(H), _c.c_float(eps), _st()), "ne_rmsnorm")
+    if q is not None:
+        out._ne_q = (q, sc)
     return out, res_out
 
 
@@ -168,8 +187,8 @@ def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tens
     if x.stride(0) % 8 or x.data_ptr() % 16:
         x = x.contiguous()
     if residual is None:
-        return _rmsnorm(x, None, w, eps, False)[0], x
-    return _rmsnorm(x, residual, w, eps, True)
+        return _rmsnorm(x, None, w, eps, False, QUANT_AFTER_NORM)[0], x
+    return _rmsnorm(x, residual, w, eps, True, QUANT_AFTER_NORM)
 
 
 def layernorm(x, w, b, eps):
@@ -181,7 +200,7 @@ def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
     I = I2 // 2
     x = x.contiguous()
     y = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
-    _ck(lib().ne_silu_mul(_p(x), _p(y), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I), _st()), "ne_silu_mul")
+    _ck(lib().ne_silu_mul(_p(x), _p(y), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(None), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I), _st()), "ne_silu_mul")
     return y
 
 
@@ -274,12 +293,12 @@ def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, exp
         _gemm(a_q, H, 0, w13, g, I2, 0, R, I2, H, E, counts, row_start, True, a_s, R, 0, w13_scale, False)
         h_q = torch.empty(R, I, dtype=FP8, device=dev)
         h_s = torch.empty(I // 128, R, dtype=torch.float32, device=dev)
-        _ck(lib().ne_silu_mul(_p(g), _p(None), _p(h_q), _p(h_s), _c.c_int(R), _c.c_longlong(0), _p(None), _c.c_int(1), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
+        _ck(lib().ne_silu_mul(_p(g), _p(None), _p(h_q), _p(h_s), _c.c_int(R), _c.c_longlong(0), _p(counts), _p(row_start), _c.c_int(E), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
         _gemm(h_q, I, 0, w2, y, H, 0, R, H, I, E, counts, row_start, True, h_s, R, 0, w2_scale, False)
     else:
         _gemm(a_b, H, 0, w13, g, I2, 0, R, I2, H, E, counts, row_start, False, None, 0, 0, None, False)
         h = torch.empty(R, I, dtype=torch.bfloat16, device=dev)
-        _ck(lib().ne_silu_mul(_p(g), _p(h), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(None), _c.c_int(1), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
+        _ck(lib().ne_silu_mul(_p(g), _p(h), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(counts), _p(row_start), _c.c_int(E), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
         _gemm(h, I, 0, w2, y, H, 0, R, H, I, E, counts, row_start, False, None, 0, 0, None, False)
     _ck(lib().ne_moe_combine_local(_p(y), _p(pos), _p(w), _p(add_in), _p(out), _c.c_int(T), _c.c_int(K), _c.c_int(H), _st()), "ne_moe_combine_local")
     return out

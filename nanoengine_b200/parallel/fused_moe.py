@@ -108,14 +108,14 @@ class FusedEP:
             _k._gemm(aq, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, self.counts, None, True, a_s, C,
                      (H // 128) * C, experts.gate_up_scale, False)
             _k._ck(lib.ne_silu_mul(_k._p(self.g), _k._p(None), _k._p(self.h_q), _k._p(self.h_s), _c.c_int(C), _c.c_longlong((I // 128) * C),
-                                   _k._p(self.counts), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
+                                   _k._p(self.counts), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
             _k._gemm(self.h_q, I, C * I, experts.down_proj, ret_dummy, H, 0, C, H, I, E, self.counts, None, True, self.h_s, C,
                      (I // 128) * C, experts.down_scale, False, row_dst=self.row_dst)
         else:
             ab = self.b_abf.view(torch.bfloat16, (E, C, H))
             _k._gemm(ab, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, self.counts, None, False, None, 0, 0, None, False)
             _k._ck(lib.ne_silu_mul(_k._p(self.g), _k._p(self.h), _k._p(None), _k._p(None), _c.c_int(0), _c.c_longlong(0),
-                                   _k._p(self.counts), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
+                                   _k._p(self.counts), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
             _k._gemm(self.h, I, C * I, experts.down_proj, ret_dummy, H, 0, C, H, I, E, self.counts, None, False, None, 0, 0, None, False,
                      row_dst=self.row_dst)
         _k._ck(lib.ne_ep_signal(L, epoch, st), "ne_ep_signal")

@@ -240,7 +240,26 @@ class ModelRunner:
         ids, pos = ctx.extras["input_ids"], ctx.extras["positions"]
         if self.graphs is not None and not ctx.is_prefill and ctx.q_len_uniform == 1 and self.graphs.can_run(ctx):
             return self.graphs.run(ids, pos, ctx)
+        if self.config.pp > 1:
+            return self._forward_pp_stage(ids, pos, ctx)
         return self.model(ids, pos, ctx)
+
+    def _forward_pp_stage(self, ids, pos, ctx: ForwardContext):
+        """One stage of the prefill pipeline: receive (hidden, residual) from the previous stage, run this stage's layers,
+        pass the pair on.  Only the last stage returns hidden states; the others return None."""
+        from ..models.pp import pp_recv, pp_send
+        d = self.dist
+        inner = self.model.model
+        if d.is_first_pp:
+            out = inner(ids, pos, ctx)
+        else:
+            h, res = pp_recv(ids.numel(), self.mc.hidden_size, self.dtype, self.device, d.pp_neighbor(-1))
+            out = inner(None, pos, ctx, inputs_embeds=h, residual=res)
+        if d.is_last_pp:
+            return out
+        h, res = out
+        pp_send(h, res, d.pp_neighbor(+1))
+        return None
 
     @torch.inference_mode()
     def run_batch(self, b) -> "C.RunnerOut":
@@ -257,6 +276,9 @@ class ModelRunner:
             return self.mtp_runner.run(b, ctx)
         self.timer.forward_begin()
         hidden = self.forward(ctx)
+        if hidden is None:                      # an inner pipeline stage: nothing to sample here
+            self.timer.forward_end()
+            return C.RunnerOut([], [])
         if ctx.is_dummy:
             if self.mtp_runner is not None:
                 self.mtp_runner.run_dummy(ctx)

@@ -60,3 +60,23 @@ def test_dead_worker_is_reported():
             ex.collective_rpc("get_step_timing")
     finally:
         ex.shutdown()
+
+
+def test_pp2_prefill_pipeline_matches_single_stage():
+    """Static prefill pipeline over 2 stages (prefill mode): same first tokens as the single-stage prefill engine."""
+    from nanoengine_b200 import RequestMigrate
+    from nanoengine_b200.models.pp import pp_layer_partition, split_batch
+    assert pp_layer_partition(61, 8)[0] == (0, 8) and pp_layer_partition(61, 8)[-1] == (54, 61)
+    base = dict(model="tiny-deepseek-v3", dtype="float32", device="cpu", kvcache_block_size=16, max_num_seqs=8, num_kvcache_blocks=64, mode="prefill")
+    prompts = _prompts(5, 19, 7, 1024)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+
+    def firsts(cfg):
+        llm = LLM(cfg)
+        try:
+            blobs = llm.generate(prompts, sp, return_serialized=True)
+            return sorted(RequestMigrate.from_bytes(b).metadata for b in blobs)
+        finally:
+            llm.shutdown()
+
+    assert firsts(Config(**base, pp=2)) == firsts(Config(**base))
