@@ -267,6 +267,11 @@ PYBIND11_MODULE(_core, m) {
       .def_property_readonly("config", &Scheduler::config)
       .def("update_num_blocks", &Scheduler::update_num_blocks)
       .def("reset_prefix_cache", &Scheduler::reset_prefix_cache)
+      .def("set_commit_log", &Scheduler::set_commit_log)
+      .def("take_committed", &Scheduler::take_committed, py::arg("dp") = 0)
+      .def("begin_import", &Scheduler::begin_import, py::arg("dp"), py::arg("hashes"))
+      .def("finish_import", &Scheduler::finish_import, py::arg("dp"), py::arg("hashes"), py::arg("ids"), py::arg("ok") = true)
+      .def("has_cached_hash", &Scheduler::has_cached_hash, py::arg("dp"), py::arg("hash"))
       .def("add_request", &Scheduler::add_request)
       .def("add_migration", &Scheduler::add_migration)
       .def("add_request_bytes", [](Scheduler& s, const std::string& b) { return s.add_request_bytes(b); })

@@ -107,7 +107,38 @@ class BlockPool {
     Block& b = blocks_.at(id);
     b.state = BLOCK_READY;
     if (!prefix_cache_ || b.hash) return;
-    if (by_hash_.emplace(hash, id).second) b.hash = hash;
+    if (by_hash_.emplace(hash, id).second) { b.hash = hash; if (log_commits_) commit_log_.emplace_back(hash, id); }
+  }
+
+  // ---- third-tier hooks ---------------------------------------------------------------
+  // With the log on, every newly published (hash, block) pair is remembered until take_committed() drains it, so
+  // a lower tier can persist fresh blocks.
+  void set_commit_log(bool on) { log_commits_ = on; if (!on) commit_log_.clear(); }
+  std::vector<std::pair<uint64_t, int32_t>> take_committed() { auto out = std::move(commit_log_); commit_log_.clear(); return out; }
+  bool has_hash(uint64_t h) const { return by_hash_.count(h) != 0; }
+
+  // Reserve one block per hash that is not cached yet (in order; stops when the pool runs dry).  Entry i of the result is
+  // the reserved block id, or -1 when hashes[i] is already cached.  The caller fills the blocks and hands the same two
+  // lists to finish_import(), which publishes them as cached, unreferenced blocks.
+  std::vector<int32_t> begin_import(const std::vector<uint64_t>& hashes) {
+    std::vector<int32_t> out;
+    for (uint64_t h : hashes) {
+      if (by_hash_.count(h)) { out.push_back(-1); continue; }
+      std::vector<int32_t> one;
+      if (!allocate(1, &one)) break;
+      out.push_back(one[0]);
+    }
+    return out;
+  }
+  void finish_import(const std::vector<uint64_t>& hashes, const std::vector<int32_t>& ids, bool ok) {
+    const bool was = log_commits_;
+    log_commits_ = false;                       // imported blocks came from the lower tier: nothing to persist again
+    for (size_t i = 0; i < ids.size() && i < hashes.size(); i++) {
+      if (ids[i] < 0) continue;
+      if (ok) commit(ids[i], hashes[i]);
+      release_one(ids[i]);
+    }
+    log_commits_ = was;
   }
 
   void mark_ready(int id) { blocks_.at(id).state = BLOCK_READY; }
@@ -156,6 +187,8 @@ class BlockPool {
   std::list<int32_t> lru_;
   std::unordered_map<uint64_t, int32_t> by_hash_;
   uint64_t lookups_ = 0, hit_tokens_ = 0, lookup_tokens_ = 0, evictions_ = 0;
+  bool log_commits_ = false;
+  std::vector<std::pair<uint64_t, int32_t>> commit_log_;
 };
 
 // Fixed set of integer slots (recurrent state rows, MTP hand-off rows, HiSparse hot buffers).

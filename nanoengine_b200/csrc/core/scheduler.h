@@ -97,6 +97,15 @@ class Scheduler {
     throw WireError("add_request_bytes: not a request packet");
   }
 
+  // Third KV tier: see BlockPool::begin_import / finish_import / take_committed.
+  void set_commit_log(bool on) { for (auto& p : pools_) p.set_commit_log(on); }
+  std::vector<std::pair<uint64_t, int32_t>> take_committed(int dp) { return pools_.at(dp).take_committed(); }
+  std::vector<int32_t> begin_import(int dp, const std::vector<uint64_t>& hashes) { return pools_.at(dp).begin_import(hashes); }
+  void finish_import(int dp, const std::vector<uint64_t>& hashes, const std::vector<int32_t>& ids, bool ok) {
+    pools_.at(dp).finish_import(hashes, ids, ok);
+  }
+  bool has_cached_hash(int dp, uint64_t h) const { return pools_.at(dp).has_hash(h); }
+
   void reset_prefix_cache() {
     for (auto& p : pools_) p.clear_cache();
     for (auto& kv : seqs_) { kv.second->commit_cursor = (int)kv.second->block_table.size(); }   // live sequences publish nothing stale

@@ -11,7 +11,10 @@ from typing import Dict, Iterable, List, Optional
 
 from .._native import _core as C
 from ..config import Config
+from ..utils.logging import get_logger
 from .executor import build_executor
+
+logger = get_logger("nanoengine.engine")
 
 _ROUTING = {"round_robin": C.ROUND_ROBIN, "least_batch": C.LEAST_BATCH, "least_cache": C.LEAST_CACHE, "affinity": C.AFFINITY}
 _MODE = {"hybrid": C.MODE_HYBRID, "prefill": C.MODE_PREFILL, "decode": C.MODE_DECODE}
@@ -63,6 +66,15 @@ class LLMEngine:
         self.executor.collective_rpc("allocate_kvcache", self.num_blocks)
         self._next_seq_id = 1
         self.migrator = None   # set by the PD layer (disagg.KVMigrator)
+        # file-backed third KV tier: needs the prefix cache (blocks are found by their chained hash) and one block pool
+        self.l3_enabled = False
+        if config.l3_dir and config.enable_prefix_caching:
+            if config.attention_dp > 1 and not self.spmd:
+                logger.warning("l3_dir is ignored: the file-backed KV tier needs one scheduler per attention-DP rank (executor_backend=spmd)")
+            else:
+                self.executor.collective_rpc("l3_open", config.l3_dir, config.l3_capacity_blocks)
+                self.scheduler.set_commit_log(True)
+                self.l3_enabled = True
 
     # ---- requests ----------------------------------------------------------------------------
     def add_request_payload(self, payload: bytes) -> int:
@@ -73,7 +85,43 @@ class LLMEngine:
             seq_id = self._next_seq_id
         self._next_seq_id = max(self._next_seq_id, seq_id) + 1
         sp = sampling_params or C.SamplingParams()
+        if self.l3_enabled:
+            self._l3_import(prompt_token_ids)
         return self.scheduler.add_request(C.RequestIn(seq_id, list(prompt_token_ids), sp, affinity_key))
+
+    # ---- file-backed KV tier ------------------------------------------------------------------
+    def _l3_import(self, prompt_token_ids: List[int]) -> int:
+        """Bring the prompt's leading blocks that only the file tier still holds back into the device prefix cache."""
+        from ..runtime.l3_store import prompt_block_hashes
+        hashes = prompt_block_hashes(prompt_token_ids, self.config.kvcache_block_size)
+        if not hashes:
+            return 0
+        stored = None
+        for got in self.executor.collective_rpc("l3_exists", hashes):       # a block counts only if every worker has its shard
+            stored = set(got) if stored is None else stored & set(got)
+        run = []
+        for h in hashes:
+            if not (self.scheduler.has_cached_hash(0, h) or h in stored):
+                break
+            run.append(h)
+        if not any(h in stored and not self.scheduler.has_cached_hash(0, h) for h in run):
+            return 0
+        ids = self.scheduler.begin_import(0, run)
+        run = run[:len(ids)]
+        pairs = [(h, b) for h, b in zip(run, ids) if b >= 0]
+        ok = True
+        try:
+            self.executor.collective_rpc("l3_load", pairs)
+        except Exception as e:                                              # a vanished file: the blocks stay unpublished
+            logger.warning("L3 import failed, recomputing instead: %s", e)
+            ok = False
+        self.scheduler.finish_import(0, run, ids, ok)
+        return len(pairs) if ok else 0
+
+    def _l3_persist(self) -> None:
+        pairs = self.scheduler.take_committed(0)
+        if pairs:
+            self.executor.collective_rpc("l3_store", pairs)
 
     def abort(self, seq_id: int) -> bool:
         return self.scheduler.abort(seq_id)
@@ -101,7 +149,10 @@ class LLMEngine:
         else:
             outs = self.executor.run_batches(self.scheduler.serialize_run_batches())
         ms = (time.perf_counter() - t0) * 1e3
-        return self.scheduler.postprocess_runner_out_bytes(outs, ms)
+        step_outs = self.scheduler.postprocess_runner_out_bytes(outs, ms)
+        if self.l3_enabled:
+            self._l3_persist()
+        return step_outs
 
     def _run_static_pp_prefill_pipeline(self, res) -> List[bytes]:
         """Split each DP rank's prefill batch into `pp` micro-batches and keep them all in flight: every worker receives

@@ -106,6 +106,14 @@ class KVCache:
         self.host_kv = torch.zeros(shape, dtype=self.kv.dtype if self.kv.dtype != torch.float8_e4m3fn else torch.uint8,
                                    pin_memory=self.device.type == "cuda")
 
+    def block_views(self, bid: int) -> List[torch.Tensor]:
+        """Byte views of everything block `bid` holds (all layers of every cache family), for the file-backed tier."""
+        kv = self.kv.view(torch.uint8) if self.kv.dtype == torch.float8_e4m3fn else self.kv
+        out = [kv[:, bid] if self.plan.mla else kv[:, :, bid]]
+        if self.indexer is not None:
+            out.append(self.indexer[:, bid])
+        return out
+
     def swap(self, src: List[int], dst: List[int], to_host: bool):
         """Copy whole blocks (all layers) between the device cache and the host tier."""
         if not src:

@@ -261,6 +261,24 @@ class ModelRunner:
         pp_send(h, res, d.pp_neighbor(+1))
         return None
 
+    # ---- file-backed KV tier (one store per worker: every rank persists its own shard of a block) ----
+    def l3_open(self, root: str, capacity_blocks: int = 0) -> int:
+        from .l3_store import L3Store
+        self.l3 = L3Store(self.cache, root, rank=self.dist.rank if self.dist is not None else 0, capacity_blocks=capacity_blocks)
+        return len(self.l3)
+
+    def l3_exists(self, hashes: List[int]) -> List[int]:
+        return self.l3.exists(hashes)
+
+    def l3_store(self, pairs) -> int:
+        return len(self.l3.store(pairs))
+
+    def l3_load(self, pairs) -> int:
+        return self.l3.load(pairs)
+
+    def l3_stats(self) -> dict:
+        return self.l3.stats()
+
     @torch.inference_mode()
     def run_batch(self, b) -> "C.RunnerOut":
         self.timer.start("swap")
