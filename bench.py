@@ -72,6 +72,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=61, help="debug only: anything but 61 marks the result invalid")
     ap.add_argument("--experts-per-gpu", type=int, default=32)
+    ap.add_argument("--profile-range", action="store_true",
+                    help="bracket the device-timed decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -165,11 +167,15 @@ def main():
     for _ in range(3):
         step_fn()
     sync()
+    if args.profile_range:
+        torch.cuda.profiler.start()
     e0.record()
     for _ in range(args.steps):
         step_fn()
     e1.record()
     e1.synchronize()
+    if args.profile_range:
+        torch.cuda.profiler.stop()
     sync()
     dev_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
     stop.set()

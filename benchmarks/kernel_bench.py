@@ -108,6 +108,19 @@ def case_mla(B, ctx, H=128, q_len=1):
     return fn, B * ctx * 576 + B * q_len * H * (576 + 512) * 2, 2.0 * B * q_len * H * ctx * (576 + 512)
 
 
+def case_silu_masked(E=32, rows=32, cap=512, I=2048):
+    g = torch.randn(E, cap, 2 * I, device="cuda", dtype=torch.bfloat16)
+    counts = torch.full((E,), rows, dtype=torch.int32, device="cuda")
+    q = torch.empty(E, cap, I, dtype=FP8, device="cuda")
+    sc = torch.empty(E, I // 128, cap, dtype=torch.float32, device="cuda")
+    import ctypes as _c
+    lib = sm100.lib()
+    def fn():
+        sm100._ck(lib.ne_silu_mul(sm100._p(g), sm100._p(None), sm100._p(q), sm100._p(sc), _c.c_int(cap), _c.c_longlong((I // 128) * cap),
+                                  sm100._p(counts), sm100._p(None), _c.c_int(E), _c.c_int(cap), _c.c_int(I), sm100._st()), "ne_silu_mul")
+    return fn, E * rows * I * 5, 0.0
+
+
 def case_moe_layer(T, E, topk=8, H=7168, I=2048):
     x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
     w13, w2 = rand_fp8(E, 2 * I, H), rand_fp8(E, H, I)
@@ -119,6 +132,31 @@ def case_moe_layer(T, E, topk=8, H=7168, I=2048):
     return fn, E * 3 * I * H, 2.0 * T * topk * 3 * I * H
 
 
+def case_small(kind, T=128, H=7168, E=32, K=8, I=2048):
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    if kind == "router":
+        w = torch.randn(E, H, device="cuda")
+        def fn():
+            sm100.moe_route(sm100.router_logits(x, w), None, 8, 1, 1, True, 2.5, "sigmoid")
+        return fn, E * H * 4 + T * H * 2, 2.0 * T * E * H
+    if kind == "add_rmsnorm_quant":
+        r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16); w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+        return (lambda: sm100.add_rmsnorm(x, r, w, 1e-6)), T * H * (2 + 2 + 2 + 2 + 1), 0.0
+    if kind == "rmsnorm_then_quant":
+        r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16); w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+        def fn():
+            y, _ = sm100._rmsnorm(x, r, w, 1e-6, True, False)
+            sm100.quant_fp8_1x128(y)
+        return fn, T * H * (2 + 2 + 2 + 2 + 2 + 1), 0.0
+    if kind == "moe_route":
+        lg = torch.randn(T, 256, device="cuda"); b = torch.zeros(256, device="cuda")
+        return (lambda: sm100.moe_route(lg, b, 8, 8, 4, True, 2.5, "sigmoid")), T * 256 * 4, 0.0
+    if kind == "sample":
+        lg = torch.randn(T, 129280, device="cuda"); tm = torch.zeros(T, device="cuda")
+        return (lambda: sm100_attn.sample(lg, tm)), T * 129280 * 4, 0.0
+    raise ValueError(kind)
+
+
 def build_cases(args):
     E = args.experts
     c = {
@@ -128,10 +166,19 @@ def build_cases(args):
         "o_proj_decode": lambda: case_dense_fp8(128, 7168, 16384),
         "shared_up_decode": lambda: case_dense_fp8(128, 4096, 7168),
         "shared_down_decode": lambda: case_dense_fp8(128, 7168, 2048),
+        # same bytes and K steps as the fp8 cases above, without the per-K-block promotion (isolates the memory path)
+        "qkv_a_like_bf16": lambda: case_dense_bf16(128, 2112, 3584),
+        "o_proj_like_bf16": lambda: case_dense_bf16(128, 7168, 8192),
         "lm_head_decode": lambda: case_dense_bf16(128, 129280, 7168, True),
         "moe_gemm1": lambda: case_moe_gemm(E, args.rows, 4096, 7168),
         "moe_gemm2": lambda: case_moe_gemm(E, args.rows, 7168, 2048),
         "moe_layer_decode": lambda: case_moe_layer(128, E),
+        "router": lambda: case_small("router"),
+        "silu_masked": lambda: case_silu_masked(),
+        "add_rmsnorm_quant": lambda: case_small("add_rmsnorm_quant"),
+        "rmsnorm_then_quant": lambda: case_small("rmsnorm_then_quant"),
+        "moe_route": lambda: case_small("moe_route"),
+        "sample": lambda: case_small("sample"),
         "mla_decode": lambda: case_mla(128, args.ctx),
         "mla_decode_small_batch": lambda: case_mla(8, 8192),
         # prefill, 16384 tokens

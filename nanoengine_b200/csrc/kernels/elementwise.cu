@@ -119,10 +119,12 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); 
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ sc,
                                 int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, const int* __restrict__ row_start, int groups,
                                 int rows, int I) {
-  // grid-stride over (group, valid row, 128-column block): a sparsely filled masked layout costs only its valid rows
+  // warps stride over the concatenation of all groups' (valid row, 128-column block) items, so a sparsely filled masked
+  // layout costs only its valid rows and every warp gets an equal share whatever the split between groups
   const int cg = I / 128, lane = threadIdx.x & 31;
   const long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nw = (long long)gridDim.x * (blockDim.x >> 5);
+  long long base = 0;                      // items of the groups before g, modulo nw
   for (int g = 0; g < groups; g++) {
     int nrows = rows_valid ? rows_valid[g] : rows;
     nrows = nrows < rows ? nrows : rows;
@@ -130,7 +132,10 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
     const long long gbase = row_start ? 0 : (long long)g * rows;
     const int r0 = row_start ? row_start[g] : 0;
     const long long items = (long long)nrows * cg;
-    for (long long it = w0; it < items; it += nw) {
+    long long first = w0 - base;
+    if (first < 0) first += nw;
+    base = (base + items) % nw;
+    for (long long it = first; it < items; it += nw) {
       const int row = r0 + (int)(it / cg), c = (int)(it % cg);
       if (row >= rows && row_start) continue;
       const __nv_bfloat16* xr = x + (gbase + row) * 2 * I + c * 128 + lane * 4;

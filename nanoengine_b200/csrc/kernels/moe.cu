@@ -18,7 +18,7 @@ constexpr int kMaxExperts = 1024;
 // one warp per token
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx_out,
                                                        float* __restrict__ w_out, int T, int E, int top_k, int n_group, int topk_group,
-                                                       int norm, float scale, int softmax) {
+                                                       int norm, float scale, int softmax, int planes) {
   __shared__ float s_choice[4][kMaxExperts];
   __shared__ float s_score[4][kMaxExperts];
   __shared__ float s_group[4][64];
@@ -26,7 +26,13 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   const int t = blockIdx.x * 4 + wl;
   if (t >= T) return;
   float* choice = s_choice[wl]; float* score = s_score[wl]; float* gsc = s_group[wl];
-  const float* lr = logits + (long long)t * E;
+  // the logits may arrive as `planes` partial sums [planes, T, E] (split-K router product)
+  for (int e = lane; e < E; e += 32) {
+    float v = 0.f;
+    for (int p = 0; p < planes; p++) v += logits[((long long)p * T + t) * E + e];
+    choice[e] = v;
+  }
+  const float* lr = choice;
   if (softmax) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, lr[e]);
@@ -144,35 +150,49 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* _
   }
 }
 
-// Router logits on CUDA cores with the fp32 gate weight: logits[t, e] = x[t, :] . w[e, :].  One CTA = 8 tokens x 32 experts;
-// the tokens' rows sit in shared memory, each warp streams the rows of 4 experts once and keeps 8 running sums per row.
-__global__ void __launch_bounds__(256) router_gemv_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
+// Router logits on CUDA cores with the fp32 gate weight: logits[t, e] = x[t, :] . w[e, :], split along the hidden
+// dimension into planes of kRouterCols columns that the routing kernel adds up.  One CTA = 8 tokens x 32 experts x one
+// column slice: the tokens' slice sits in shared memory, each warp takes 4 experts, streams each expert's slice with
+// eight 16-byte loads in flight per lane and keeps 8 running sums.
+constexpr int kRouterCols = 1024;
+__global__ void __launch_bounds__(256) router_gemv_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, float* __restrict__ planes,
                                                          int T, int E, int H) {
-  extern __shared__ __nv_bfloat16 s_x[];                                // [8][H]
-  const int t0 = blockIdx.x * 8, e0 = blockIdx.y * 32, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x * 8; i < 8 * H; i += blockDim.x * 8) {
-    const int tt = t0 + i / H;
-    *reinterpret_cast<uint4*>(s_x + i) = tt < T ? *reinterpret_cast<const uint4*>(x + (long long)tt * H + (i % H)) : make_uint4(0, 0, 0, 0);
+  __shared__ __align__(16) __nv_bfloat16 s_x[8][kRouterCols];
+  const int t0 = blockIdx.x * 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h0 = blockIdx.z * kRouterCols;
+  const int hc = min(kRouterCols, H - h0);                                // multiple of 128
+  for (int i = threadIdx.x * 8; i < 8 * kRouterCols; i += 256 * 8) {
+    const int tt = i / kRouterCols, c = i % kRouterCols;
+    *reinterpret_cast<uint4*>(&s_x[tt][c]) = (t0 + tt < T && c < hc) ? *reinterpret_cast<const uint4*>(x + (long long)(t0 + tt) * H + h0 + c)
+                                                                    : make_uint4(0, 0, 0, 0);
   }
   __syncthreads();
-  for (int ee = warp; ee < 32; ee += 8) {
-    const int e = e0 + ee;
+  float* out = planes + (long long)blockIdx.z * T * E;
+#pragma unroll 1
+  for (int ee = 0; ee < 4; ee++) {
+    const int e = blockIdx.y * 32 + warp * 4 + ee;
     if (e >= E) break;
+    const float* wr = w + (long long)e * H + h0;
+    float4 wv[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int c = u * 128 + lane * 4;
+      wv[u] = c < hc ? *reinterpret_cast<const float4*>(wr + c) : make_float4(0, 0, 0, 0);
+    }
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const float* wr = w + (long long)e * H;
-    for (int c = lane * 4; c < H; c += 128) {
-      const float4 wv = *reinterpret_cast<const float4*>(wr + c);
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
 #pragma unroll
       for (int tt = 0; tt < 8; tt++) {
-        const uint2 xv = *reinterpret_cast<const uint2*>(s_x + tt * H + c);
+        const uint2 xv = *reinterpret_cast<const uint2*>(&s_x[tt][u * 128 + lane * 4]);
         const float2 a = unpack_bf16x2(xv.x), b = unpack_bf16x2(xv.y);
-        acc[tt] = fmaf(wv.x, a.x, fmaf(wv.y, a.y, fmaf(wv.z, b.x, fmaf(wv.w, b.y, acc[tt]))));
+        acc[tt] = fmaf(wv[u].x, a.x, fmaf(wv[u].y, a.y, fmaf(wv[u].z, b.x, fmaf(wv[u].w, b.y, acc[tt]))));
       }
     }
 #pragma unroll
     for (int tt = 0; tt < 8; tt++) {
       const float v = warp_sum(acc[tt]);
-      if (lane == 0 && t0 + tt < T) logits[(long long)(t0 + tt) * E + e] = v;
+      if (lane == 0 && t0 + tt < T) out[(long long)(t0 + tt) * E + e] = v;
     }
   }
 }
@@ -214,10 +234,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
 using namespace ne;
 
 extern "C" int ne_moe_route(const float* logits, const float* bias, int* idx, float* w, int T, int E, int top_k, int n_group,
-                            int topk_group, int norm, float scale, int softmax, cudaStream_t st) {
+                            int topk_group, int norm, float scale, int softmax, int planes, cudaStream_t st) {
   if (T <= 0) return 0;
-  if (E > kMaxExperts || top_k > 64 || n_group > 64 || (n_group > 1 && E % n_group)) return 1001;
-  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, bias, idx, w, T, E, top_k, n_group, topk_group, norm, scale, softmax);
+  if (E > kMaxExperts || top_k > 64 || n_group > 64 || (n_group > 1 && E % n_group) || planes < 1) return 1001;
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, bias, idx, w, T, E, top_k, n_group, topk_group, norm, scale, softmax, planes);
   return (int)cudaGetLastError();
 }
 
@@ -245,17 +265,11 @@ extern "C" int ne_moe_combine_local(const void* y, const int* pos, const float* 
   return (int)cudaGetLastError();
 }
 
-// x bf16 [T, H], w fp32 [E, H] -> logits fp32 [T, E]
-extern "C" int ne_router_gemv(const void* x, const float* w, float* logits, int T, int E, int H, cudaStream_t st) {
+// x bf16 [T, H], w fp32 [E, H] -> partial logits fp32 [ne_router_planes(H), T, E]; their sum over the first axis is x . w^T
+extern "C" int ne_router_planes(int H) { return (H + kRouterCols - 1) / kRouterCols; }
+extern "C" int ne_router_gemv(const void* x, const float* w, float* planes, int T, int E, int H, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 128) return 1001;
-  size_t smem = (size_t)8 * H * 2;
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(router_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
-  router_gemv_kernel<<<dim3((T + 7) / 8, (E + 31) / 32), 256, smem, st>>>((const __nv_bfloat16*)x, w, logits, T, E, H);
+  router_gemv_kernel<<<dim3((T + 7) / 8, (E + 31) / 32, ne_router_planes(H)), 256, 0, st>>>((const __nv_bfloat16*)x, w, planes, T, E, H);
   return (int)cudaGetLastError();
 }

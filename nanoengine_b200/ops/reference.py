@@ -246,6 +246,8 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_
     (reference models/deepseek_v2/deepseek_v2.py:478-543, models/qwen3_moe/qwen3_moe.py:283-297).
     """
     lf = logits.float()
+    if lf.dim() == 3:          # partial sums of a split-K router product
+        lf = lf.sum(0)
     scores = torch.sigmoid(lf) if scoring == "sigmoid" else torch.softmax(lf, -1)
     choice = scores + bias.float() if bias is not None else scores
     T, E = choice.shape

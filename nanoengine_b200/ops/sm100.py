@@ -126,12 +126,15 @@ def _cached(key_t: torch.Tensor, tag: str, fn):
 
 
 def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """x bf16 [T, H] against the fp32 gate weight [E, H] on CUDA cores (N is far too small for a tensor-core tile)."""
+    """x bf16 [T, H] against the fp32 gate weight [E, H] on CUDA cores (N is far too small for a tensor-core tile).
+
+    Returns partial logits [P, T, E] (the hidden dimension is split into P slices so enough CTAs pull the weight at
+    once); `moe_route` adds the planes up, any other consumer calls `.sum(0)`."""
     x2 = _as_bf16_2d(x)
     T, H = x2.shape
     E = w.shape[0]
     assert w.dtype == torch.float32 and w.is_contiguous() and x2.stride(0) == H
-    out = torch.empty(T, E, dtype=torch.float32, device=x.device)
+    out = torch.empty(lib().ne_router_planes(_c.c_int(H)), T, E, dtype=torch.float32, device=x.device)
     _ck(lib().ne_router_gemv(_p(x2), _p(w), _p(out), _c.c_int(T), _c.c_int(E), _c.c_int(H), _st()), "ne_router_gemv")
     return out
 
@@ -247,12 +250,14 @@ def gqa_kv_store(k_cache, v_cache, slot_mapping, k, v):
 
 # ---- MoE -----------------------------------------------------------------------------------------
 def moe_route(logits, bias, top_k, n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=1.0, scoring="sigmoid"):
-    T, E = logits.shape
+    planes = logits.shape[0] if logits.dim() == 3 else 1
+    T, E = logits.shape[-2:]
     logits = logits.float().contiguous()
     idx = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
     w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
     _ck(lib().ne_moe_route(_p(logits), _p(bias), _p(idx), _p(w), _c.c_int(T), _c.c_int(E), _c.c_int(top_k), _c.c_int(n_group), _c.c_int(topk_group),
-                           _c.c_int(1 if norm_topk_prob else 0), _c.c_float(routed_scaling_factor), _c.c_int(0 if scoring == "sigmoid" else 1), _st()),
+                           _c.c_int(1 if norm_topk_prob else 0), _c.c_float(routed_scaling_factor), _c.c_int(0 if scoring == "sigmoid" else 1),
+                           _c.c_int(planes), _st()),
         "ne_moe_route")
     return idx, w
 
