@@ -26,7 +26,12 @@ namespace ne {
 __device__ int g_status[8];
 
 constexpr int kBlockM = 128;
-constexpr int kKBytes = 128;            // bytes of K per stage row: one 128B swizzle atom
+constexpr int kKBytes = 128;            // bytes of K per K block row: one 128B swizzle atom
+// One pipeline stage holds kG consecutive K blocks of both operands, fetched by ONE TMA instruction per operand: the
+// tensor maps carry the 128-byte K chunk index as their outermost dimension, so a box {128 B, rows, ..., kG} lands as kG
+// consecutive swizzled [rows x 128 B] tiles.  An SM retires roughly one TMA instruction per 0.2 us whatever its size, so
+// two instructions per K block cap a 128-wide tile well below both the tensor pipe and HBM; two per kG blocks do not.
+template <int BLOCK_N> struct KGroup { static constexpr int value = BLOCK_N >= 256 ? 1 : 2; };   // the 256-wide tile keeps 4 single-block stages
 constexpr int kGemmThreads = 192;
 constexpr int kKernelGemm = 1;
 
@@ -47,16 +52,19 @@ struct GemmArgs {
 template <int BLOCK_N> struct Smem {
   static constexpr int kABytes = kBlockM * kKBytes;
   static constexpr int kBBytes = BLOCK_N * kKBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kG = KGroup<BLOCK_N>::value;
+  static constexpr int kStageBytes = kG * (kABytes + kBBytes);
   static constexpr int kStaging = 8 * 32 * 80;      // per-warp epilogue staging for up to 8 epilogue warps
   static constexpr int kBudget = 232448 - 1024 - 256 - kStaging;
   static constexpr int kStages = (kBudget / kStageBytes) > 10 ? 10 : (kBudget / kStageBytes);
   static constexpr int kBytes = kStages * kStageBytes + kStaging + 1024 /*align*/ + 256 /*barriers*/;
 };
 
+constexpr int kSchedCache = 512;        // group tables up to this many groups are staged in shared memory
+
 struct TileSched {
   int groups, M, n_blocks;
-  const int* masked_m;
+  const int* masked_m;                  // global or shared memory
   const int* row_start;
   int g = 0, base = 0;
   __device__ TileSched(int groups_, int M_, int nb, const int* mm, const int* rs) : groups(groups_), M(M_), n_blocks(nb), masked_m(mm), row_start(rs) {}
@@ -109,11 +117,19 @@ template <int BLOCK_N, bool kBlockScaled> struct EpiCfg {
   static constexpr int kThreads = 64 + 128 * kGroups;
 };
 
-template <int BLOCK_N, bool kFP8, bool kBlockScaled>
+// kSplit: split-K across a thread-block cluster.  The CTAs of a cluster work on the same output tile, each over its own
+// slice of K; every CTA parks its fp32 partial tile in its shared memory and, after a cluster barrier, CTA r adds up rows
+// [r * R, (r + 1) * R) of all partials through distributed shared memory and writes them out.  This is what lets a
+// 128-token decode GEMM keep every SM pulling weights while using the 128-wide tile (a narrow tile re-reads the
+// activation operand once per tile and is bound by the SM's L2 read rate instead of HBM).  One tile per cluster,
+// dense operands only (groups = 1, no row tables).
+template <int BLOCK_N, bool kFP8, bool kBlockScaled, bool kSplit>
 __global__ void __launch_bounds__((EpiCfg<BLOCK_N, kBlockScaled>::kThreads), 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64, const __grid_constant__ CUtensorMap tmap_a32,
+            const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
   using S = Smem<BLOCK_N>;
   constexpr int kStages = S::kStages;
+  constexpr int kG = S::kG;
   constexpr int kElemsPerStageK = kFP8 ? 128 : 64;
   constexpr int kUmmaK = kFP8 ? 32 : 16;
   constexpr int kMmasPerStage = kElemsPerStageK / kUmmaK;     // 4
@@ -137,15 +153,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t smem_base = smem_u32(smem);
 
   const int warp = threadIdx.x >> 5;
-  const int num_kb = (args.K + kElemsPerStageK - 1) / kElemsPerStageK;
+  const int total_kb = (args.K + kElemsPerStageK - 1) / kElemsPerStageK;
   const int n_blocks = (args.N + BLOCK_N - 1) / BLOCK_N;
+  const int split = kSplit ? (int)cluster_nctarank() : 1;
+  const int srank = kSplit ? (int)cluster_ctarank() : 0;
+  const int num_kb = total_kb / split;                 // the host picks a split that divides the K blocks
+  const int num_st = (num_kb + kG - 1) / kG;           // pipeline stages' worth of K blocks per tile
+  const int kb_begin = srank * num_kb;
+  const int tile0 = kSplit ? (int)blockIdx.x / split : (int)blockIdx.x;
+  const int tile_stride = kSplit ? (int)gridDim.x / split : (int)gridDim.x;
 
+  // the per-group row tables are read once per tile by three roles: keep them in shared memory, a global load per
+  // lookup sits on the producer's critical path at every tile switch
+  __shared__ int s_mm[kSchedCache], s_rs[kSchedCache];
+  const bool cache_tables = args.groups <= kSchedCache;
+  if (cache_tables) {
+    for (int i = threadIdx.x; i < args.groups; i += blockDim.x) {
+      if (args.masked_m) s_mm[i] = args.masked_m[i];
+      if (args.row_start) s_rs[i] = args.row_start[i];
+    }
+  }
+  const int* mm_tab = args.masked_m ? (cache_tables ? s_mm : args.masked_m) : nullptr;
+  const int* rs_tab = args.row_start ? (cache_tables ? s_rs : args.row_start) : nullptr;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
     for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4 * kEpi); }
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_a64); tma_prefetch_desc(&tmap_a32); tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
   tc_fence_before();
@@ -156,17 +191,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (elect_one()) {
-      TileSched sched(args.groups, args.M, n_blocks, args.masked_m, args.row_start);
+      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab);
       int stage = 0; uint32_t phase = 0; int grp, mb, nb;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && sched.get(tile, grp, mb, nb); tile += gridDim.x) {
-        for (int kb = 0; kb < num_kb; kb++) {
+      for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
+        // a tile with few valid rows (decode: a handful of tokens per expert) fetches only the first 32 or 64 rows of
+        // the activation block; the MMA still spans 128 rows, whose stale remainder lands in output rows nobody stores
+        const int rows_here = sched.rows(grp) - mb * kBlockM;
+        const CUtensorMap* ta = rows_here <= 32 ? &tmap_a32 : (rows_here <= 64 ? &tmap_a64 : &tmap_a);
+        const uint32_t a_bytes = rows_here <= 32 ? 32 * kKBytes : (rows_here <= 64 ? 64 * kKBytes : S::kABytes);
+        for (int st = 0; st < num_st; st++) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, kKernelGemm, 100 + stage)) { ok = false; break; }
-          uint32_t a_dst = smem_base + stage * S::kStageBytes, b_dst = a_dst + S::kABytes;
-          mbar_expect_tx(full0 + 8 * stage, S::kStageBytes);
-          if (args.a_group_inner) tma_load_3d(a_dst, &tmap_a, full0 + 8 * stage, kb * kElemsPerStageK, grp, mb * kBlockM);
-          else tma_load_3d(a_dst, &tmap_a, full0 + 8 * stage, kb * kElemsPerStageK, sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp);
-          tma_load_3d(b_dst, &tmap_b, full0 + 8 * stage, kb * kElemsPerStageK, nb * BLOCK_N, grp);
+          uint32_t a_dst = smem_base + stage * S::kStageBytes, b_dst = a_dst + kG * S::kABytes;
+          mbar_expect_tx(full0 + 8 * stage, kG * (a_bytes + S::kBBytes));      // chunks past the end of K arrive as zeros
+          const int kc = kb_begin + st * kG;
+          if (args.a_group_inner) tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, grp, mb * kBlockM, kc);
+          else tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, kc);
+          tma_load_4d(b_dst, &tmap_b, full0 + 8 * stage, 0, nb * BLOCK_N, grp, kc);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -174,33 +215,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      TileSched sched(args.groups, args.M, n_blocks, args.masked_m, args.row_start);
+      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab);
       int stage = 0; uint32_t phase = 0; int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && sched.get(tile, grp, mb, nb); tile += gridDim.x) {
+      for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
         if (!kBlockScaled) {
           if (!mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 200 + buf)) { ok = false; break; }
           tc_fence_after();
         }
-        for (int kb = 0; kb < num_kb; kb++) {
-          if (kBlockScaled) {
-            if (!mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 210 + buf)) { ok = false; break; }
-          }
+        // the activation box of this tile (see the producer): its K blocks sit a_kstride apart inside the stage
+        const int rows_here = sched.rows(grp) - mb * kBlockM;
+        const uint32_t a_kstride = rows_here <= 32 ? 32 * kKBytes : (rows_here <= 64 ? 64 * kKBytes : S::kABytes);
+        for (int st = 0; st < num_st && ok; st++) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, kKernelGemm, 300 + stage)) { ok = false; break; }
           tc_fence_after();
-          uint32_t a_addr = smem_base + stage * S::kStageBytes, b_addr = a_addr + S::kABytes;
-          uint64_t adesc = make_smem_desc(a_addr, 16, 1024, SW_128B);
-          uint64_t bdesc = make_smem_desc(b_addr, 16, 1024, SW_128B);
-          uint32_t d = tmem_base + buf * BLOCK_N;
+          const uint32_t a_base = smem_base + stage * S::kStageBytes, b_base = a_base + kG * S::kABytes;
 #pragma unroll
-          for (int k = 0; k < kMmasPerStage; k++) {
-            uint32_t acc = kBlockScaled ? (k != 0) : ((kb | k) != 0);
-            // advancing 32 bytes along K inside the 128B swizzle atom = +2 in the descriptor's 16-byte address units
-            if (kFP8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
-            else umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+          for (int g = 0; g < kG; g++) {
+            const int kb = st * kG + g;
+            if (kb >= num_kb) break;
+            if (kBlockScaled) {
+              if (!mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 210 + buf)) { ok = false; break; }
+              tc_fence_after();
+            }
+            uint64_t adesc = make_smem_desc(a_base + g * a_kstride, 16, 1024, SW_128B);
+            uint64_t bdesc = make_smem_desc(b_base + g * S::kBBytes, 16, 1024, SW_128B);
+            uint32_t d = tmem_base + buf * BLOCK_N;
+#pragma unroll
+            for (int k = 0; k < kMmasPerStage; k++) {
+              uint32_t acc = kBlockScaled ? (k != 0) : ((kb | k) != 0);
+              // advancing 32 bytes along K inside the 128B swizzle atom = +2 in the descriptor's 16-byte address units
+              if (kFP8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              else umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            }
+            if (kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == kAcc) { buf = 0; bphase ^= 1; } }
           }
           tc_commit(empty0 + 8 * stage);                // smem slot reusable once these MMAs retire
-          if (kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == kAcc) { buf = 0; bphase ^= 1; } }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
@@ -213,10 +263,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int cbase = ((warp - 2) >> 2) * kCols;   // column offset of this warp's group inside the tile
     const int row_in_tile = wq * 32 + (int)lane_id();
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    TileSched sched(args.groups, args.M, n_blocks, args.masked_m, args.row_start);
+    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab);
     int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && sched.get(tile, grp, mb, nb); tile += gridDim.x) {
+    for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
       const bool row_ok = mb * kBlockM + row_in_tile < sched.rows(grp);
       const int row = sched.row0(grp) + mb * kBlockM + row_in_tile;      // row inside the group's (or the flat) matrix
       const int n0 = nb * BLOCK_N;
@@ -224,8 +274,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         float acc[kCols];
 #pragma unroll
         for (int j = 0; j < kCols; j++) acc[j] = 0.f;
-        const float* sa = args.sa + (long long)grp * args.sa_group_stride + (row_ok ? row : 0);
-        const float* sb = args.sb + (long long)grp * args.sb_group_stride + (long long)(n0 / 128) * num_kb;
+        const float* sa = args.sa + (long long)grp * args.sa_group_stride + (row_ok ? row : 0) + (long long)kb_begin * args.sa_ld;
+        const float* sb = args.sb + (long long)grp * args.sb_group_stride + (long long)(n0 / 128) * total_kb + kb_begin;
         // scale factors are fetched four K blocks ahead so their L2 latency hides behind the promotion work
         constexpr int kPf = 4;
         float nxt[kPf];
@@ -266,7 +316,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         }
         if (!ok) break;
-        {
+        if (kSplit) {
+          // park the partial tile: [128 rows][BLOCK_N / 4 chunks of 16 bytes], chunk index xor-ed with the row so the
+          // 32 rows a warp writes at once land in different banks
+          float4* P = reinterpret_cast<float4*>(smem);
+#pragma unroll
+          for (int c4 = 0; c4 < kCols / 4; c4++) {
+            const int chunk = cbase / 4 + c4;
+            P[row_in_tile * (BLOCK_N / 4) + (chunk ^ (row_in_tile & 7))] = make_float4(acc[c4 * 4], acc[c4 * 4 + 1], acc[c4 * 4 + 2], acc[c4 * 4 + 3]);
+          }
+        } else {
           const long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0 + cbase;
           if (args.out_fp32) {
             if (row_ok) {
@@ -304,7 +363,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + c * 32, r);
           tc_wait_ld();
-          if (args.out_fp32) {
+          if (kSplit) {
+            float4* P = reinterpret_cast<float4*>(smem);
+#pragma unroll
+            for (int q = 0; q < 8; q++)
+              P[row_in_tile * (BLOCK_N / 4) + ((c * 8 + q) ^ (row_in_tile & 7))] =
+                  make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
+          } else if (args.out_fp32) {
             if (row_ok) {
 #pragma unroll
               for (int q = 0; q < 4; q++) {
@@ -328,6 +393,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (++buf == kAcc) { buf = 0; bphase ^= 1; }
       }
     }
+  }
+
+  if (kSplit) {
+    // ---------------- cross-CTA reduction of the partial tiles ----------------
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int mb = tile0 / n_blocks, nb = tile0 % n_blocks;
+      const int R = (kBlockM + split - 1) / split;
+      constexpr int kChunks = BLOCK_N / 4;
+      const int nthr = 128 * kEpi, te = (int)threadIdx.x - 64;
+      for (int item = te; item < R * kChunks; item += nthr) {
+        const int r = srank * R + item / kChunks, chunk = item % kChunks;
+        const int grow = mb * kBlockM + r, n = nb * BLOCK_N + chunk * 4;
+        if (r >= kBlockM || grow >= args.M || n >= args.N) continue;
+        const uint32_t local = smem_base + (uint32_t)(r * kChunks + (chunk ^ (r & 7))) * 16u;
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int pr = 0; pr < split; pr++) {
+          const float4 v = ld_dsmem_f4(mapa_shared(local, (uint32_t)pr));
+          s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+        }
+        const long long off = (long long)grow * args.ldd + n;
+        if (args.out_fp32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(args.D) + off) = s4;
+        else *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(args.D) + off) = make_uint2(pack_bf16x2(s4.x, s4.y), pack_bf16x2(s4.z, s4.w));
+      }
+    }
+    cluster_sync_all();           // nobody leaves while a peer may still read its partial tile
   }
 
   // ---------------- teardown ----------------
@@ -356,28 +447,33 @@ struct TmapKeyHash {
   }
 };
 
-// [groups][rows][K] K-major tensor -> 3-D map, box {128 bytes of K, box_rows, 1}, 128B swizzle.
+// [groups][rows][K] K-major tensor -> 4-D map {128 bytes of K, rows, groups, K chunk} with box {128 B, box_rows, 1, kG}
+// (kG = K blocks per pipeline stage of the kernel that will use the map) and 128B swizzle; K in bytes must be a multiple of 128.  The chunk dimension's stride (128 B) is smaller than the row
+// stride, which the encoder accepts.
 static int get_tmap_kmajor(CUtensorMap* out, const void* base, bool fp8, uint64_t K, uint64_t rows, uint64_t groups,
-                           uint64_t row_stride_elems, uint64_t group_stride_elems, uint32_t box_rows) {
+                           uint64_t row_stride_elems, uint64_t group_stride_elems, uint32_t box_rows, int kg) {
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   const uint64_t es = fp8 ? 1 : 2;
-  TmapKey key{base, K, rows, groups, row_stride_elems * es, group_stride_elems * es, (uint32_t)(kKBytes / es), box_rows, fp8 ? TMA_U8 : TMA_BF16};
+  TmapKey key{base, K, rows, groups, row_stride_elems * es, group_stride_elems * es, (uint32_t)(kKBytes / es), box_rows | ((uint32_t)kg << 16), fp8 ? TMA_U8 : TMA_BF16};
   std::lock_guard<std::mutex> lk(mu);
   auto it = cache.find(key);
   if (it != cache.end()) { *out = it->second; return 0; }
-  uint64_t dims[3] = {K, rows, groups};
-  uint64_t strides[2] = {row_stride_elems * es, group_stride_elems * es};
-  uint32_t box[3] = {(uint32_t)(kKBytes / es), box_rows, 1};
+  uint64_t dims[4] = {kKBytes / es, rows, groups, K * es / kKBytes};
+  uint64_t strides[3] = {row_stride_elems * es, group_stride_elems * es, (uint64_t)kKBytes};
+  uint32_t box[4] = {(uint32_t)(kKBytes / es), box_rows, 1, (uint32_t)kg};
   if (groups > 1 && group_stride_elems < row_stride_elems) {
-    // heads interleaved inside a row ([rows, groups, K] memory order): keep strides ascending, the kernel swaps coordinates
+    // heads interleaved inside a row ([rows, groups, K] memory order): groups become the faster dimension, the kernel swaps coordinates
     dims[1] = groups; dims[2] = rows; strides[0] = group_stride_elems * es; strides[1] = row_stride_elems * es;
     box[1] = 1; box[2] = box_rows;
   }
-  int rc = make_tmap(out, base, fp8 ? TMA_U8 : TMA_BF16, 3, dims, strides, box, TMA_SW_128);
+  if (groups == 1) strides[1] = rows * row_stride_elems * es;      // unused, but must be a legal stride
+  int rc = make_tmap(out, base, fp8 ? TMA_U8 : TMA_BF16, 4, dims, strides, box, TMA_SW_128);
   if (rc == 0) { if (cache.size() > 8192) cache.clear(); cache.emplace(key, *out); }
   return rc;
 }
+
+static bool g_split_k_enabled = true;
 
 static int num_sms() {
   static int n = 0;
@@ -386,16 +482,60 @@ static int num_sms() {
 }
 
 template <int BLOCK_N, bool kFP8, bool kBS>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int grid, cudaStream_t st) {
-  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS>;
+static int launch(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs& a, int grid, cudaStream_t st) {
+  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, false>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BLOCK_N>::kBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, EpiCfg<BLOCK_N, kBS>::kThreads, Smem<BLOCK_N>::kBytes, st>>>(ta, tb, a);
+  kern<<<grid, EpiCfg<BLOCK_N, kBS>::kThreads, Smem<BLOCK_N>::kBytes, st>>>(tas[0], tas[1], tas[2], tb, a);
   return (int)cudaGetLastError();
+}
+
+// split-K form: `tiles` clusters of `split` CTAs
+template <int BLOCK_N, bool kFP8, bool kBS>
+static int launch_split(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs& a, int tiles, int split, cudaStream_t st) {
+  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, true>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BLOCK_N>::kBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles * split), 1, 1);
+  cfg.blockDim = dim3(EpiCfg<BLOCK_N, kBS>::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Smem<BLOCK_N>::kBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, tas[0], tas[1], tas[2], tb, a);
+}
+
+// Split-K plan for a dense GEMM with at most 128 rows.  The cost of a candidate is the bytes one CTA pulls through its
+// L2 port (activation + weight slices of every tile it runs) plus a fixed charge per wave and for the reduction; the
+// 128-wide tile halves the activation re-reads of the 64-wide one, and the split brings the idle SMs back.
+static void plan_small_m(int N, int num_kb, bool fp8, int* bn_out, int* split_out) {
+  double best = 1e30;
+  *bn_out = 128; *split_out = 1;
+  for (int bn : {256, 128, 64, 32}) {
+    for (int sp = 1; sp <= 8; sp++) {
+      if (bn == 256 && (fp8 || sp > 1 || N % 256 != 0)) continue;       // the widest tile exists for plain bf16 only
+      if (num_kb % sp || (sp > 1 && num_kb / sp < 4)) continue;
+      const long long tiles = (N + bn - 1) / bn;
+      const long long ctas = tiles * sp;
+      const int cap = sp > 1 ? (num_sms() / 8 / sp) * sp * 8 : num_sms();      // clusters do not straddle the 8 GPCs
+      if (cap <= 0) continue;
+      const long long waves = (ctas + cap - 1) / cap;
+      const double unit_kb = (double)(kBlockM + bn) * kKBytes * (num_kb / sp) / 1024.0;
+      const double cost = (double)waves * (unit_kb / 64.0 + 1.0) + (sp > 1 ? 2.0 : 0.0);    // ~64 KB/us per SM
+      if (cost < best - 1e-9) { best = cost; *bn_out = bn; *split_out = sp; }
+    }
+  }
 }
 
 }  // namespace ne
@@ -412,13 +552,19 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
                        long long sa_gs, const float* sb, int out_fp32, int block_n_hint, const long long* row_dst, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
   const bool fp8 = dtype == 1;
-  if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % 16 != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
+  if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % kKBytes != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
   if (fp8 && (K % 128 != 0 || !sa || !sb)) return 1002;
   if ((ldd * (out_fp32 ? 4 : 2)) % 16 != 0) return 1003;
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
   // pick the widest N tile that still yields about one tile per SM; fp8 promotion keeps BLOCK_N accumulators in registers
   int bn = block_n_hint;
-  if (bn == 0) {
+  int split = 1;
+  const int num_kb_host = (K * (fp8 ? 1 : 2) + kKBytes - 1) / kKBytes;
+  const bool can_split = groups == 1 && !row_start && !masked_m && !row_dst && m_blocks == 1 && N % 4 == 0 &&
+                         (K * (fp8 ? 1 : 2)) % kKBytes == 0 && g_split_k_enabled;
+  if (bn == 0 && can_split) {
+    plan_small_m(N, num_kb_host, fp8, &bn, &split);
+  } else if (bn == 0) {
     if (fp8 && !row_start && !masked_m) {
       // dense block-scaled GEMM: the serial K loop of a tile dominates at small M, so take the fewest waves of
       // tiles and, among equals, the narrowest tile (more SMs pulling weights at the same time)
@@ -441,11 +587,14 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
     }
   }
   if (fp8 && bn > 128) bn = 128;
-  CUtensorMap ta, tb;
+  const int kg = bn >= 256 ? 1 : 2;      // KGroup<bn>::value
+  CUtensorMap ta[3], tb;       // activation maps with 128-, 64- and 32-row boxes
   if (row_start || groups == 1) a_gs = (long long)M * lda;
-  int rc = get_tmap_kmajor(&ta, A, fp8, (uint64_t)K, (uint64_t)M, (uint64_t)(row_start ? 1 : groups), (uint64_t)lda, (uint64_t)a_gs, kBlockM);
+  int rc = 0;
+  for (int i = 0; i < 3 && !rc; i++)
+    rc = get_tmap_kmajor(&ta[i], A, fp8, (uint64_t)K, (uint64_t)M, (uint64_t)(row_start ? 1 : groups), (uint64_t)lda, (uint64_t)a_gs, kBlockM >> i, kg);
   if (rc) return 2000 + rc;
-  rc = get_tmap_kmajor(&tb, B, fp8, (uint64_t)K, (uint64_t)N, (uint64_t)groups, (uint64_t)K, (uint64_t)N * K, (uint32_t)bn);
+  rc = get_tmap_kmajor(&tb, B, fp8, (uint64_t)K, (uint64_t)N, (uint64_t)groups, (uint64_t)K, (uint64_t)N * K, (uint32_t)bn, kg);
   if (rc) return 3000 + rc;
   GemmArgs a;
   a.a_group_inner = (!row_start && groups > 1 && a_gs < lda) ? 1 : 0;
@@ -457,6 +606,20 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
   if (row_dst && out_fp32) return 1005;
   long long tiles = (long long)groups * m_blocks * ((N + bn - 1) / bn);
   int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+  if (split > 1) {
+    if (fp8) {
+      switch (bn) {
+        case 128: return launch_split<128, true, true>(ta, tb, a, (int)tiles, split, stream);
+        case 64: return launch_split<64, true, true>(ta, tb, a, (int)tiles, split, stream);
+        default: return launch_split<32, true, true>(ta, tb, a, (int)tiles, split, stream);
+      }
+    }
+    switch (bn) {
+      case 128: return launch_split<128, false, false>(ta, tb, a, (int)tiles, split, stream);
+      case 64: return launch_split<64, false, false>(ta, tb, a, (int)tiles, split, stream);
+      default: return launch_split<32, false, false>(ta, tb, a, (int)tiles, split, stream);
+    }
+  }
   if (fp8) {
     switch (bn) {
       case 128: return launch<128, true, true>(ta, tb, a, grid, stream);
@@ -471,6 +634,9 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
     default: return launch<32, false, false>(ta, tb, a, grid, stream);
   }
 }
+
+// Turn the cluster split-K plan of small-M dense GEMMs on or off (on by default); returns the previous setting.
+extern "C" int ne_gemm_set_split_k(int on) { int was = g_split_k_enabled ? 1 : 0; g_split_k_enabled = on != 0; return was; }
 
 extern "C" int ne_get_status(int* out8) {
   return (int)cudaMemcpyFromSymbol(out8, g_status, sizeof(int) * 8);

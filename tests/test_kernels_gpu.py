@@ -56,6 +56,36 @@ def test_gemm_fp8_blockscaled(k, M, N, K):
     assert _rel(got, x.float() @ w.t()) < 6e-2   # and close to the unquantised product
 
 
+@pytest.mark.parametrize("fp8", [True, False])
+@pytest.mark.parametrize("M,N,K", [(128, 2112, 7168), (5, 4096, 7168), (128, 7168, 16384), (77, 7168, 2048), (128, 1536, 1536), (16, 520, 1024)])
+def test_gemm_cluster_split_k_equals_single_cta(k, fp8, M, N, K):
+    """Small-M dense GEMMs run split-K over a thread-block cluster (partials reduced through distributed shared memory);
+    the result must match the same GEMM run by one CTA per tile, and the fp32 reference."""
+    torch.manual_seed(21)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda") * 0.05
+    if fp8:
+        wq, ws = ref.quant_fp8_block(w)
+        run = lambda **kw: k.linear(x, wq, ws, **kw)
+        want = ref.linear(x, wq, ws)
+    else:
+        wb = w.to(torch.bfloat16)
+        run = lambda **kw: k.linear(x, wb, **kw)
+        want = x.float() @ wb.float().t()
+    lib = k.lib()
+    was = lib.ne_gemm_set_split_k(0)
+    try:
+        single = run()
+        single32 = run(out_fp32=True) if not fp8 else None
+    finally:
+        lib.ne_gemm_set_split_k(was)
+    split = run()
+    assert _rel(split, want) < 5e-3
+    assert _rel(split, single) < 4e-3            # bf16 rounding of differently ordered fp32 sums
+    if not fp8:
+        assert _rel(run(out_fp32=True), single32) < 2e-4     # fp32 sums taken in a different order
+
+
 def test_quant_1x128_matches_reference(k):
     torch.manual_seed(3)
     x = torch.randn(77, 1024, device="cuda", dtype=torch.bfloat16) * 3
@@ -130,6 +160,23 @@ def test_moe_route(k, T, E, topk, ng, tg, scoring):
     assert torch.allclose(w.sum(-1), rw.sum(-1), rtol=1e-4)
     o, ro = idx.argsort(-1), ridx.argsort(-1)
     assert torch.allclose(w.gather(1, o), rw.gather(1, ro), rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("T,E,H", [(1, 8, 256), (128, 32, 7168), (37, 256, 7168), (9, 128, 2048)])
+def test_router_logits_planes(k, T, E, H):
+    """Split-K router product: the planes add up to x . w^T, and routing on the planes equals routing on their sum."""
+    torch.manual_seed(9)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(E, H, device="cuda") * 0.05
+    planes = k.router_logits(x, w)
+    assert planes.dim() == 3 and planes.shape[1:] == (T, E)
+    want = x.float() @ w.t()
+    assert torch.allclose(planes.sum(0), want, rtol=1e-3, atol=1e-3)
+    topk = min(8, E)
+    idx, wt = k.moe_route(planes, None, topk, 1, 1, True, 1.0, "sigmoid")
+    ridx, rw = ref.moe_route(planes.sum(0), None, topk, 1, 1, True, 1.0, "sigmoid")
+    assert torch.allclose(wt.sum(-1), rw.sum(-1), rtol=1e-4)
+    assert torch.allclose(wt.sort(-1).values, rw.sort(-1).values, rtol=1e-3, atol=1e-5)
 
 
 def test_bmm_absorb_on_strided_heads(k):
