@@ -179,6 +179,80 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, long long row_s
   q[ib] = __float2bfloat16(b * c + a * s);
 }
 
+// MLA key path in one pass, one warp per token: RMSNorm of the compressed KV (R values, rounded to bf16 as the separate
+// norm kernel would), interleaved RoPE of the R..R+rope tail, and the store of both into the token's cache row (bf16, or
+// e4m3 with a clamped cast and no scale).  kv [T, >= R + rope] bf16 with row stride kv_ld.
+__global__ void __launch_bounds__(256) mla_kv_prepare_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_ld, const __nv_bfloat16* __restrict__ w,
+                                                            float eps, const long long* __restrict__ positions, const float* __restrict__ rope_cache,
+                                                            void* __restrict__ cache, const long long* __restrict__ slots, int T, int R, int rope, int fp8) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const long long slot = slots[t];
+  const __nv_bfloat16* row = kv + (long long)t * kv_ld;
+  float ss = 0.f;
+  for (int c = lane * 2; c < R; c += 64) {
+    const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(row + c));
+    ss += f.x * f.x + f.y * f.y;
+  }
+  ss = warp_sum(ss);
+  if (slot < 0) return;
+  const float inv = rsqrtf(ss / (float)R + eps);
+  const int D = R + rope;
+  for (int c = lane * 2; c < R; c += 64) {
+    const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(row + c));
+    const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(w + c));
+    const uint32_t o = pack_bf16x2(f.x * inv * g.x, f.y * inv * g.y);
+    if (fp8) {
+      const float2 r = unpack_bf16x2(o);
+      *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(cache) + slot * D + c) = (uint16_t)__nv_cvt_float2_to_fp8x2(r, __NV_SATFINITE, __NV_E4M3);
+    } else {
+      *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(cache) + slot * D + c) = o;
+    }
+  }
+  const float* cs = rope_cache + positions[t] * rope;
+  const int half = rope / 2;
+  for (int i = lane; i < half; i += 32) {
+    const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(row + R + 2 * i));
+    const float c = cs[i], sn = cs[half + i];
+    const uint32_t o = pack_bf16x2(f.x * c - f.y * sn, f.y * c + f.x * sn);
+    if (fp8) {
+      const float2 r = unpack_bf16x2(o);
+      *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(cache) + slot * D + R + 2 * i) = (uint16_t)__nv_cvt_float2_to_fp8x2(r, __NV_SATFINITE, __NV_E4M3);
+    } else {
+      *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(cache) + slot * D + R + 2 * i) = o;
+    }
+  }
+}
+
+// Absorbed MLA query for the fp8 attention kernel: q8[t, h, :] = e4m3([q_lat[t, h, :R] | rope(q_pe[t, h, :])]) with a
+// clamped cast and no scale; q_pe is the interleaved rope tail of the query projection (a strided view).  One warp per
+// (token, head).
+__global__ void __launch_bounds__(256) mla_q_finalize_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q_pe,
+                                                            long long pe_row_stride, int pe_head_stride, const long long* __restrict__ positions,
+                                                            const float* __restrict__ rope_cache, uint8_t* __restrict__ q8, int T, int H, int R, int rope) {
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)T * H) return;
+  const int t = (int)(wid / H), h = (int)(wid % H);
+  const int D = R + rope;
+  const __nv_bfloat16* src = q_lat + wid * R;
+  uint8_t* dst = q8 + wid * D;
+  for (int c = lane * 8; c < R; c += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src + c);
+    const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c2 = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+    *reinterpret_cast<uint2*>(dst + c) = make_uint2(pack_e4m3x4(a.x, a.y, b.x, b.y), pack_e4m3x4(c2.x, c2.y, d.x, d.y));
+  }
+  const float* cs = rope_cache + positions[t] * rope;
+  const int half = rope / 2;
+  const __nv_bfloat16* pe = q_pe + (long long)t * pe_row_stride + (long long)h * pe_head_stride;
+  for (int i = lane; i < half; i += 32) {
+    const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pe + 2 * i));
+    const float c = cs[i], sn = cs[half + i];
+    const float2 r = unpack_bf16x2(pack_bf16x2(f.x * c - f.y * sn, f.y * c + f.x * sn));     // bf16 rounding as the unfused rope
+    *reinterpret_cast<uint16_t*>(dst + R + 2 * i) = (uint16_t)__nv_cvt_float2_to_fp8x2(r, __NV_SATFINITE, __NV_E4M3);
+  }
+}
+
 // cache row = [ckv (R) | k_pe (rope)], bf16 or e4m3 (clamped cast, no scale).  One warp per token.
 __global__ void mla_kv_store_kernel(const __nv_bfloat16* __restrict__ ckv, long long ckv_ld, const __nv_bfloat16* __restrict__ kpe, long long kpe_ld,
                                     void* __restrict__ cache, const long long* __restrict__ slots, int T, int R, int rope, int fp8) {
@@ -263,6 +337,25 @@ extern "C" int ne_mla_kv_store(const void* ckv, long long ckv_ld, const void* kp
   if (T <= 0) return 0;
   if (R % 2 || rope % 2) return 1001;
   mla_kv_store_kernel<<<(T + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)ckv, ckv_ld, (const __nv_bfloat16*)kpe, kpe_ld, cache, slots, T, R, rope, fp8);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_mla_kv_prepare(const void* kv, long long kv_ld, const void* w, float eps, const long long* positions, const float* rope_cache,
+                                 void* cache, const long long* slots, int T, int R, int rope, int fp8, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (R % 2 || rope % 2 || kv_ld % 2) return 1001;
+  mla_kv_prepare_kernel<<<(T + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)kv, kv_ld, (const __nv_bfloat16*)w, eps, positions, rope_cache, cache, slots,
+                                                     T, R, rope, fp8);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_mla_q_finalize(const void* q_lat, const void* q_pe, long long pe_row_stride, int pe_head_stride, const long long* positions,
+                                 const float* rope_cache, void* q8, int T, int H, int R, int rope, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (R % 8 || rope % 2 || pe_row_stride % 2 || pe_head_stride % 2) return 1001;
+  long long warps = (long long)T * H;
+  mla_q_finalize_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)q_lat, (const __nv_bfloat16*)q_pe, pe_row_stride, pe_head_stride,
+                                                                     positions, rope_cache, (uint8_t*)q8, T, H, R, rope);
   return (int)cudaGetLastError();
 }
 

@@ -105,6 +105,37 @@ __global__ void moe_scan_kernel(const int* __restrict__ counts, int* __restrict_
   for (int e = threadIdx.x; e <= E; e += blockDim.x) row_start[e] = s[e];
 }
 
+// The two kernels above in one CTA (no zeroed input needed): counts are taken with shared-memory atomics, the aligned
+// prefix sums follow, and both tables are written out.  One CTA walks all T * top_k pairs; at 16K tokens that is a few tens
+// of microseconds, a small cost against saving two launches and a memset per MoE layer in every decode step.
+__global__ void __launch_bounds__(1024) moe_count_scan_kernel(const int* __restrict__ idx, int* __restrict__ counts, int* __restrict__ slot,
+                                                             int* __restrict__ row_start, int n_pairs, int expert_offset, int E, int align) {
+  __shared__ int s_cnt[kMaxExperts + 1];
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) s_cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = idx[i] - expert_offset;
+    slot[i] = (e >= 0 && e < E) ? atomicAdd(&s_cnt[e], 1) : -1;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = s_cnt[e];
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // warp scan over the aligned counts, 32 experts per round
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + (int)threadIdx.x;
+      const int c = e < E ? (s_cnt[e] + align - 1) / align * align : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if ((int)threadIdx.x >= o) incl += v; }
+      if (e < E) row_start[e] = carry + incl - c;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (threadIdx.x == 0) row_start[E] = carry;
+  }
+}
+
 // One CTA per token: the row is quantised to e4m3 1x128 once (kept in shared memory) and then copied to each of the
 // token's local experts; writes pos[t,k] (row in the expert-major buffer, -1 if not local / overflow).
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx, const int* __restrict__ slot,
@@ -241,7 +272,7 @@ extern "C" int ne_moe_route(const float* logits, const float* bias, int* idx, fl
   return (int)cudaGetLastError();
 }
 
-// counts [E_local] must be zero on entry.  Outputs: slot [T*K] (scratch), row_start [E_local+1], pos [T*K], and the
+// Outputs: counts [E_local], slot [T*K] (scratch), row_start [E_local+1], pos [T*K], and the
 // expert-major activations (bf16, or e4m3 + scales with leading dimension s_ld >= max_rows).
 extern "C" int ne_moe_dispatch_local(const void* x, const int* idx, int* counts, int* slot, int* row_start, int* pos, void* a_bf16,
                                      void* a_q, float* a_s, int s_ld, int T, int top_k, int H, int expert_offset, int E_local,
@@ -249,9 +280,8 @@ extern "C" int ne_moe_dispatch_local(const void* x, const int* idx, int* counts,
   if (T <= 0) return 0;
   if (E_local > kMaxExperts || H % 128) return 1001;
   int n = T * top_k;
-  moe_count_kernel<<<(n + 255) / 256, 256, 0, st>>>(idx, counts, slot, n, expert_offset, E_local);
-  moe_scan_kernel<<<1, 256, 0, st>>>(counts, row_start, E_local, align);
   if (top_k > 64) return 1001;
+  moe_count_scan_kernel<<<1, 1024, 0, st>>>(idx, counts, slot, row_start, n, expert_offset, E_local, align);
   moe_scatter_kernel<<<T, 256, (size_t)H + (H / 128) * 4, st>>>((const __nv_bfloat16*)x, idx, slot, row_start, pos, (__nv_bfloat16*)a_bf16,
                                                                 (uint8_t*)a_q, a_s, s_ld, top_k, H, expert_offset, E_local, max_rows);
   return (int)cudaGetLastError();

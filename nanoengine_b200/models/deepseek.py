@@ -37,7 +37,7 @@ class MLAAttention(nn.Module):
         if self.q_lora:
             # fused [q_a_proj ; kv_a_proj_with_mqa]
             self.qkv_a_proj = QLinear(cfg.hidden_size, self.q_lora + R + rope, dtype, device, q)
-            self.q_a_layernorm = RMSNorm(self.q_lora, cfg.rms_norm_eps, dtype, device)
+            self.q_a_layernorm = RMSNorm(self.q_lora, cfg.rms_norm_eps, dtype, device, quant_out=(q == "fp8"))
             self.q_b_proj = QLinear(self.q_lora, H * (nope + rope), dtype, device, q)
         else:
             self.q_proj = QLinear(cfg.hidden_size, H * (nope + rope), dtype, device, q)
@@ -78,14 +78,12 @@ class MLAAttention(nn.Module):
             q = self.q_proj(x)
             kv_a = self.kv_a_proj_with_mqa(x)
         q = q.view(T, H, nope + rope)
-        ckv = self.kv_a_layernorm(kv_a[:, :R])
-        k_pe = ops.apply_rope(kv_a[:, R:], positions, rope_cache, True)
         cache = ctx.kv_caches[self.layer_idx]
-        ops.mla_kv_store(cache, ctx.slot_mapping, ckv, k_pe)
+        ops.mla_kv_prepare(kv_a, self.kv_a_layernorm.weight, self.kv_a_layernorm.eps, positions, rope_cache, cache, ctx.slot_mapping, R)
         sparse = None
         if self.indexer is not None:
             sparse = self.indexer(x, q_c if q_c is not None else x, positions, ctx, rope_cache)
-        q_full = ops.mla_absorb_rope(q, self.kc, positions, rope_cache, nope)   # [T, H, R + rope]
+        q_full = ops.mla_query(q, self.kc, positions, rope_cache, nope, cache, sparse is None)   # [T, H, R + rope]
         o_lat = ops.mla_attention_paged(q_full, cache, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale, R,
                                         sparse_indices=sparse)
         o = ops.bmm_absorb(o_lat, self.vc)                                   # [T, H, v]

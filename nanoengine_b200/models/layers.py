@@ -64,15 +64,16 @@ class QLinear(nn.Module):
 
 
 class RMSNorm(nn.Module):
-    def __init__(self, dim: int, eps: float, dtype, device):
+    def __init__(self, dim: int, eps: float, dtype, device, quant_out: bool = False):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device), requires_grad=False)
         self.eps = eps
+        self.quant_out = quant_out      # the only consumer is an fp8 linear: let the kernel emit its quantised input too
 
     def forward(self, x, residual=None):
         """Without residual: y.  With residual: (y, x + residual) - the fused add + norm used between blocks."""
         if residual is None:
-            return ops.rmsnorm(x, self.weight, self.eps)
+            return ops.rmsnorm(x, self.weight, self.eps, self.quant_out)
         return ops.add_rmsnorm(x, residual, self.weight, self.eps)
 
 
@@ -85,7 +86,7 @@ class SwiGLUMLP(nn.Module):
         self.down_proj = QLinear(inter, hidden, dtype, device, quant)
 
     def forward(self, x):
-        return self.down_proj(ops.silu_and_mul(self.gate_up_proj(x)))
+        return self.down_proj(ops.silu_and_mul(self.gate_up_proj(x), self.down_proj.quant == "fp8"))
 
     def init_random(self, gen):
         self.gate_up_proj.init_random(gen)

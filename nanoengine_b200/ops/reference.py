@@ -18,7 +18,8 @@ FP8 = torch.float8_e4m3fn
 
 
 # ---- norms -------------------------------------------------------------------------------------
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False) -> torch.Tensor:
+    """`quant` is a hint for the CUDA body (also emit the block-quantised copy for an fp8 consumer); ignored here."""
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     return (y * w.float()).to(x.dtype)
@@ -144,11 +145,13 @@ def mla_kv_store(cache: torch.Tensor, slot_mapping: torch.Tensor, ckv: torch.Ten
     (reference triton/hopper/fp8_utils.py:275-281)."""
     row = torch.cat([ckv, k_pe], -1)
     flat = cache.view(-1, cache.shape[-1])
+    keep = slot_mapping >= 0                     # padded tokens carry slot -1 and write nothing
+    slots, row = slot_mapping[keep].long(), row[keep]
     if cache.dtype == FP8:
         row = row.float().clamp(-FP8_MAX, FP8_MAX).to(FP8)
-        flat.view(torch.uint8)[slot_mapping.long()] = row.view(torch.uint8)
+        flat.view(torch.uint8)[slots] = row.view(torch.uint8)
     else:
-        flat[slot_mapping.long()] = row.to(cache.dtype)
+        flat[slots] = row.to(cache.dtype)
 
 
 def gqa_kv_store(k_cache, v_cache, slot_mapping, k, v) -> None:
@@ -264,7 +267,8 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_
     return idx.to(torch.int32), (w * routed_scaling_factor).float()
 
 
-def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+def silu_and_mul(x: torch.Tensor, quant: bool = False) -> torch.Tensor:
+    """`quant` is a hint for the CUDA body (emit only the block-quantised form for an fp8 consumer); ignored here."""
     a, b = x.float().chunk(2, -1)
     return (F.silu(a) * b).to(x.dtype)
 
@@ -364,6 +368,22 @@ def bmm_absorb(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, nope: int) -> torch.Tensor:
     """Absorbed MLA query [q_nope @ W_UK | rope(q_pe)]: q [T, H, nope + rope], kc [H, nope, R] -> [T, H, R + rope]."""
     return torch.cat([bmm_absorb(q[..., :nope], kc), apply_rope(q[..., nope:], positions, cache, True)], -1)
+
+
+def mla_query(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, rope_cache: torch.Tensor, nope: int, kv_cache: torch.Tensor,
+              dense: bool = True) -> torch.Tensor:
+    """Absorbed MLA query as the attention operator wants it.  The CUDA body may hand back e4m3 (clamped cast, no scale)
+    when `kv_cache` is fp8 and the dense fp8 attention kernel will consume it; this statement always returns q's dtype."""
+    return mla_absorb_rope(q, kc, positions, rope_cache, nope)
+
+
+def mla_kv_prepare(kv_a: torch.Tensor, norm_w: torch.Tensor, eps: float, positions: torch.Tensor, rope_cache: torch.Tensor,
+                   kv_cache: torch.Tensor, slot_mapping: torch.Tensor, R: int) -> None:
+    """MLA key path: kv_a [T, R + rope] -> cache rows [RMSNorm(kv_a[:, :R]) | rope(kv_a[:, R:])] at `slot_mapping`
+    (reference models/deepseek_v2/deepseek_v2.py:1139-1164 key half, then the KV write of T5)."""
+    ckv = rmsnorm(kv_a[:, :R], norm_w, eps)
+    k_pe = apply_rope(kv_a[:, R:], positions, rope_cache, True)
+    mla_kv_store(kv_cache, slot_mapping, ckv, k_pe)
 
 
 def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

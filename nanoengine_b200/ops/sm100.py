@@ -90,8 +90,25 @@ def _as_bf16_2d(x):
     return x2
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, bias=None, out_fp32: bool = False) -> torch.Tensor:
+class PrequantizedActivation:
+    """An activation that exists only in its 1x128 block-quantised form: e4m3 [T, K] and scales [K/128, T], as left by a
+    fused producer (SwiGLU + quant).  `linear` with an fp8 weight consumes it directly.
+    Parity: reference layers/base_backend.py:14-26."""
+    __slots__ = ("q", "scales", "shape", "device")
+
+    def __init__(self, q: torch.Tensor, scales: torch.Tensor):
+        self.q, self.scales, self.shape, self.device = q, scales, q.shape, q.device
+
+
+def linear(x, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, bias=None, out_fp32: bool = False) -> torch.Tensor:
     N, K = w.shape
+    if isinstance(x, PrequantizedActivation):
+        assert w.dtype == FP8 and x.shape[-1] == K, "a pre-quantised activation feeds fp8 linears only"
+        T = x.shape[0]
+        out = torch.empty(T, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+        if T > 0:
+            _gemm(x.q, K, 0, w, out, N, 0, T, N, K, 1, None, None, True, x.scales, T, 0, w_scale, out_fp32)
+        return out if bias is None else out + bias
     pre = getattr(x, "_ne_q", None)          # (e4m3 [T, K], scales [K/128, T]) left by a fused norm + quant kernel
     x2 = _as_bf16_2d(x)
     T = x2.shape[0]
@@ -180,10 +197,11 @@ def _rmsnorm(x, res_in, w, eps, want_res, quant=False):
     return out, res_out
 
 
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False) -> torch.Tensor:
+    """`quant`: also leave the e4m3 1x128 copy for an fp8 linear that consumes the result (picked up by `linear`)."""
     if x.stride(0) % 8 or x.data_ptr() % 16:
         x = x.contiguous()
-    return _rmsnorm(x, None, w, eps, False)[0]
+    return _rmsnorm(x, None, w, eps, False, quant and x.shape[1] % 128 == 0)[0]
 
 
 def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float):
@@ -198,10 +216,17 @@ def layernorm(x, w, b, eps):
     return ref.layernorm(x, w, b, eps)
 
 
-def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+def silu_and_mul(x: torch.Tensor, quant: bool = False):
+    """SwiGLU of [gate | up].  `quant`: return only the 1x128 block-quantised result (for an fp8 down projection)."""
     T, I2 = x.shape
     I = I2 // 2
     x = x.contiguous()
+    if quant and I % 128 == 0 and T > 0:
+        q = torch.empty(T, I, dtype=FP8, device=x.device)
+        sc = torch.empty(I // 128, T, dtype=torch.float32, device=x.device)
+        _ck(lib().ne_silu_mul(_p(x), _p(None), _p(q), _p(sc), _c.c_int(T), _c.c_longlong(0), _p(None), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I),
+                              _st()), "ne_silu_mul")
+        return PrequantizedActivation(q, sc)
     y = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
     _ck(lib().ne_silu_mul(_p(x), _p(y), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(None), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I), _st()), "ne_silu_mul")
     return y
@@ -232,6 +257,39 @@ def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, 
     bmm_absorb(q[..., :nope], kc, out=out[..., :R])
     apply_rope(q[..., nope:], positions, cache, True, out=out[..., R:])
     return out
+
+
+def mla_query(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, rope_cache: torch.Tensor, nope: int, kv_cache: torch.Tensor,
+              dense: bool = True) -> torch.Tensor:
+    """Absorbed MLA query.  For the dense fp8 attention kernel (fp8 cache of 64-token pages, 512 + 64 wide rows, at most
+    128 heads) the result is e4m3 [T, H, 576]: the latent product lands in a bf16 scratch and one kernel applies RoPE to
+    the tail and casts both parts, instead of a RoPE pass into a bf16 query followed by a cast pass over all of it."""
+    T, H, _ = q.shape
+    R = kc.shape[2]
+    rope = q.shape[2] - nope
+    if not (dense and kv_cache.dtype == FP8 and R == 512 and rope == 64 and kv_cache.shape[1] == 64 and H <= 128 and T > 0):
+        return mla_absorb_rope(q, kc, positions, rope_cache, nope)
+    q_lat = torch.empty(T, H, R, dtype=torch.bfloat16, device=q.device)
+    bmm_absorb(q[..., :nope], kc, out=q_lat)
+    q8 = torch.empty(T, H, R + rope, dtype=torch.uint8, device=q.device)
+    pe = q[..., nope:]
+    pos = positions if positions.dtype == torch.int64 else positions.long()
+    _ck(lib().ne_mla_q_finalize(_p(q_lat), _p(pe), _c.c_longlong(pe.stride(0)), _c.c_int(pe.stride(1)), _p(pos), _p(rope_cache), _p(q8),
+                                _c.c_int(T), _c.c_int(H), _c.c_int(R), _c.c_int(rope), _st()), "ne_mla_q_finalize")
+    return q8.view(FP8)
+
+
+def mla_kv_prepare(kv_a: torch.Tensor, norm_w: torch.Tensor, eps: float, positions: torch.Tensor, rope_cache: torch.Tensor,
+                   kv_cache: torch.Tensor, slot_mapping: torch.Tensor, R: int) -> None:
+    """RMSNorm of the compressed KV, RoPE of the key tail and the cache write in one kernel (one warp per token)."""
+    T = kv_a.shape[0]
+    rope = kv_a.shape[1] - R
+    fp8 = kv_cache.dtype == FP8
+    assert kv_a.dtype == torch.bfloat16 and kv_a.stride(1) == 1 and (fp8 or kv_cache.dtype == torch.bfloat16)
+    assert kv_cache.shape[-1] == R + rope and norm_w.dtype == torch.bfloat16
+    pos = positions if positions.dtype == torch.int64 else positions.long()
+    _ck(lib().ne_mla_kv_prepare(_p(kv_a), _c.c_longlong(kv_a.stride(0)), _p(norm_w), _c.c_float(eps), _p(pos), _p(rope_cache), _p(kv_cache),
+                                _p(slot_mapping), _c.c_int(T), _c.c_int(R), _c.c_int(rope), _c.c_int(1 if fp8 else 0), _st()), "ne_mla_kv_prepare")
 
 
 def mla_kv_store(cache: torch.Tensor, slot_mapping: torch.Tensor, ckv: torch.Tensor, k_pe: torch.Tensor) -> None:
@@ -277,7 +335,7 @@ def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, exp
         return out
     R = T * K + E * 127
     R = (R + 127) // 128 * 128
-    meta = torch.zeros(E + (E + 1) + 2 * T * K, dtype=torch.int32, device=dev)
+    meta = torch.empty(E + (E + 1) + 2 * T * K, dtype=torch.int32, device=dev)      # every entry is written by the dispatch kernels
     counts, row_start = meta[:E], meta[E:2 * E + 1]
     slot, pos = meta[2 * E + 1:2 * E + 1 + T * K], meta[2 * E + 1 + T * K:]
     idx = topk_idx.to(torch.int32).contiguous()

@@ -45,11 +45,17 @@ def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scal
     out = torch.empty(T, H, R, dtype=torch.bfloat16, device=q.device)
     if T == 0:
         return out
-    q = q if (q.dtype == torch.bfloat16 and q.is_contiguous()) else q.to(torch.bfloat16).contiguous()
     fast = (cache.dtype == FP8 and Dk == 576 and R == 512 and cache.shape[1] == 64 and H <= 128 and sparse_indices is None)
+    if q.dtype == FP8:
+        assert fast and q.is_contiguous(), "an e4m3 query is only produced for the dense fp8 attention kernel"
+    else:
+        q = q if (q.dtype == torch.bfloat16 and q.is_contiguous()) else q.to(torch.bfloat16).contiguous()
     if fast:
-        q8 = torch.empty(T * H, Dk, dtype=torch.uint8, device=q.device)
-        _k._ck(lib.ne_cast_e4m3(_k._p(q), _k._p(q8), _c.c_longlong(T * H * Dk), _k._st()), "ne_cast_e4m3")
+        if q.dtype == FP8:
+            q8 = q
+        else:
+            q8 = torch.empty(T * H, Dk, dtype=torch.uint8, device=q.device)
+            _k._ck(lib.ne_cast_e4m3(_k._p(q), _k._p(q8), _c.c_longlong(T * H * Dk), _k._st()), "ne_cast_e4m3")
         S = splits if splits is not None else mla_splits(T, bt.shape[1])
         part = lse2 = None
         if S > 1:

@@ -148,6 +148,66 @@ def test_mla_kv_store(k, fp8):
     assert torch.equal(c1.view(torch.uint8), c2.view(torch.uint8))
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+def test_mla_kv_prepare_fuses_norm_rope_and_store(k, fp8):
+    """One kernel for RMSNorm(ckv) + RoPE(k_pe) + cache write against the three separate reference steps."""
+    torch.manual_seed(71)
+    T, R, rope, nb, bs = 77, 512, 64, 8, 64
+    a = torch.randn(T, 1536 + R + rope, device="cuda", dtype=torch.bfloat16)       # kv_a is a strided view of the fused projection
+    kv_a = a[:, 1536:]
+    w = (1 + 0.1 * torch.randn(R, device="cuda")).to(torch.bfloat16)
+    cache_cs = ref.rope_cos_sin_cache(rope, 4096, 10000.0).cuda()
+    pos = torch.randint(0, 4096, (T,), device="cuda")
+    slots = torch.randperm(nb * bs, device="cuda")[:T]
+    slots[3] = -1                                                                 # a padded token writes nothing
+    c1 = torch.zeros(nb, bs, R + rope, device="cuda", dtype=torch.uint8 if fp8 else torch.bfloat16)
+    c1 = c1.view(FP8) if fp8 else c1
+    c2 = c1.clone()
+    k.mla_kv_prepare(kv_a, w, 1e-6, pos, cache_cs, c1, slots, R)
+    ref.mla_kv_prepare(kv_a.clone(), w, 1e-6, pos, cache_cs, c2, slots, R)
+    f1, f2 = c1.float().view(-1, R + rope), c2.float().view(-1, R + rope)
+    assert _rel(f1, f2) < (7e-2 if fp8 else 5e-3)          # a bf16 ulp of difference before the e4m3 cast can flip a code
+    if fp8:
+        assert (c1.view(torch.uint8) != c2.view(torch.uint8)).float().mean() < 0.02
+    assert torch.equal(f1[(f2.abs().sum(-1) == 0)], f2[(f2.abs().sum(-1) == 0)])    # untouched rows stay zero
+
+
+def test_mla_query_emits_e4m3_for_the_dense_fp8_kernel(k):
+    torch.manual_seed(72)
+    T, H, nope, rope, R = 9, 128, 128, 64, 512
+    q = torch.randn(T, H, nope + rope, device="cuda", dtype=torch.bfloat16) * 0.5
+    kc = (torch.randn(H, nope, R, device="cuda") * 0.05).to(torch.bfloat16)
+    cache_cs = ref.rope_cos_sin_cache(rope, 4096, 10000.0).cuda()
+    pos = torch.randint(0, 4096, (T,), device="cuda")
+    kv_cache = torch.zeros(4, 64, R + rope, device="cuda", dtype=torch.uint8).view(FP8)
+    got = k.mla_query(q, kc, pos, cache_cs, nope, kv_cache, True)
+    assert got.dtype == FP8 and got.shape == (T, H, R + rope)
+    want = ref.mla_absorb_rope(q.clone(), kc, pos, cache_cs, nope)
+    assert _rel(got.float(), want.float().clamp(-448, 448)) < 4e-2
+    # sparse attention and bf16 caches keep the bf16 query
+    assert k.mla_query(q, kc, pos, cache_cs, nope, kv_cache, False).dtype == torch.bfloat16
+    assert k.mla_query(q, kc, pos, cache_cs, nope, kv_cache.view(torch.uint8).to(torch.bfloat16), True).dtype == torch.bfloat16
+
+
+def test_swiglu_quant_feeds_fp8_linear(k):
+    torch.manual_seed(73)
+    T, I, N = 45, 2048, 1024
+    gu = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, I, device="cuda") * 0.05
+    wq, ws = ref.quant_fp8_block(w)
+    pre = k.silu_and_mul(gu, True)
+    assert isinstance(pre, k.PrequantizedActivation) and pre.shape == (T, I)
+    got = k.linear(pre, wq, ws)
+    want = ref.linear(ref.silu_and_mul(gu), wq, ws)
+    assert _rel(got, want) < 6e-3
+    # the norm + quant variant leaves the same quantised copy the separate kernel would
+    x = torch.randn(T, 1536, device="cuda", dtype=torch.bfloat16)
+    wn = torch.ones(1536, device="cuda", dtype=torch.bfloat16)
+    y = k.rmsnorm(x, wn, 1e-6, True)
+    q2, s2 = k.quant_fp8_1x128(k.rmsnorm(x, wn, 1e-6))
+    assert torch.equal(y._ne_q[0].view(torch.uint8), q2.view(torch.uint8))
+
+
 @pytest.mark.parametrize("E,topk,ng,tg,scoring", [(256, 8, 8, 4, "sigmoid"), (128, 8, 1, 1, "softmax"), (8, 2, 1, 1, "sigmoid"), (64, 6, 4, 2, "sigmoid")])
 @pytest.mark.parametrize("T", [1, 16, 513])
 def test_moe_route(k, T, E, topk, ng, tg, scoring):
