@@ -21,7 +21,7 @@ from .. import ops
 from ..ops import reference as ref
 from ..parallel.dist import get_dist_context
 from ..parallel.ep import ep_moe_forward
-from ..parallel.tp import tp_all_gather, tp_reduce_scatter
+from ..parallel.tp import tp_all_gather, tp_linear_reduce_scatter, tp_reduce_scatter
 from ..runtime.context import ForwardContext
 from .config import ModelConfig
 from .layers import QLinear, RMSNorm, RoutedExperts, SwiGLUMLP
@@ -60,8 +60,8 @@ class Qwen3Attention(nn.Module):
         kc, vc = ctx.kv_caches[self.layer_idx]
         ops.gqa_kv_store(kc, vc, ctx.slot_mapping, k, v)
         o = ops.gqa_attention_paged(q, kc, vc, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale)
-        out = self.o_proj(o.reshape(T, self.hq * self.hd))
-        return tp_reduce_scatter(out) if self.tp > 1 else out
+        o = o.reshape(T, self.hq * self.hd)
+        return tp_linear_reduce_scatter(o, self.o_proj) if self.tp > 1 else self.o_proj(o)
 
 
 class Qwen3MoE(nn.Module):

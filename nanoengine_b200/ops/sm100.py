@@ -81,6 +81,15 @@ def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False):
     return q, s.t()
 
 
+def quant_fp8_1x128_raw(x: torch.Tensor):
+    """bf16 [T, K] -> (e4m3 [T, K], scales [K/128, T]) exactly as the block-scaled GEMM reads them."""
+    T, K = x.shape
+    q = torch.empty(T, K, dtype=FP8, device=x.device)
+    s = torch.empty(K // 128, T, dtype=torch.float32, device=x.device)
+    _ck(lib().ne_quant_1x128(_p(x), _c.c_longlong(x.stride(0)), _p(q), _p(s), _c.c_int(T), _c.c_int(T), _c.c_int(K), _st()), "ne_quant_1x128")
+    return q, s
+
+
 def _as_bf16_2d(x):
     x2 = x.reshape(-1, x.shape[-1])
     if x2.dtype != torch.bfloat16:

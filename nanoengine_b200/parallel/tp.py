@@ -86,6 +86,15 @@ def tp_all_gather(x: torch.Tensor, total_rows: Optional[int] = None, axis: str =
     return out if total_rows is None else out[:total_rows]
 
 
+def tp_linear_reduce_scatter(x: torch.Tensor, proj, axis: str = "attn_tp") -> torch.Tensor:
+    """Row-parallel projection followed by the reduce-scatter over the TP group: [T, K_local] -> [ceil(T/tp), N].
+    With the fused backend the GEMM's epilogue stores each tile straight into the owning rank's staging buffer."""
+    d = get_dist_context()
+    if d.group(axis) is not None and x.is_cuda and _FUSED_TP is not None and _FUSED_TP.axis == axis and proj.bias is None:
+        return _FUSED_TP.gemm_reduce_scatter(x, proj.weight, proj.weight_scale_inv)
+    return tp_reduce_scatter(proj(x), axis)
+
+
 def attn_to_ffn(x_partial: torch.Tensor) -> torch.Tensor:
     """After a row-parallel o_proj whose output is still a per-rank partial sum: reduce-scatter so every rank continues
     with its own slice of the tokens (what the EP experts want), instead of all-reduce + chunk."""

@@ -117,6 +117,9 @@ class ModelRunner:
         if self.device.type == "cuda" and self.dist.ep_size > 1:
             from ..parallel import fused_moe
             fused_moe.install(self.config, self.dist)
+        if self.device.type == "cuda" and self.dist.attn_tp_size > 1:
+            from ..parallel import fused_tp
+            fused_tp.install(self.config, self.dist, "attn_tp")
 
     def load_weights(self, it) -> int:
         if self.mtp is not None:
