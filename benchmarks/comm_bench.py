@@ -2,8 +2,9 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29533 benchmarks/comm_bench.py
 
-For every token count it times, with CUDA events on the launching stream (max over ranks, median of --iters, 3 warm-up
-runs, an L2-sized buffer rewritten between runs):
+For every token count it times a CUDA-graph replay of each sequence (as the decode step runs them; --eager times plain
+launches), with CUDA events on the launching stream (max over ranks, median of --iters, 3 warm-up runs, an L2-sized
+buffer rewritten between runs):
   gemm_rs   row-parallel fp8 GEMM (K split over the group) + reduce-scatter: fused scatter epilogue vs GEMM then NCCL
   ag        all-gather of [T / world, H] bf16: peer-store push vs NCCL
   ar        all-reduce of [T, H] bf16: push + reduce + push vs NCCL
@@ -27,6 +28,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=7168)
     ap.add_argument("--k-total", type=int, default=16384, help="contraction size of the row-parallel GEMM before sharding")
     ap.add_argument("--tokens", default="128,512,2048,8192")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -43,6 +45,14 @@ def main():
     def timeit(fn):
         for _ in range(3):
             fn()
+        if not args.eager:
+            # the decode path replays these sequences from a CUDA graph: time the replay, not the host-side launches
+            torch.cuda.synchronize(); dist.barrier()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            fn = gr.replay
+            fn(); torch.cuda.synchronize(); dist.barrier()
         ts = []
         for _ in range(args.iters):
             flush.fill_(1)

@@ -57,7 +57,8 @@ __global__ void tp_signal_kernel(const TpLayout L, int which, const int* __restr
 }
 
 // mode 0 (all-gather): row i of x -> gather[rank * rpr + i] of EVERY rank.  mode 1 (reduce-scatter): row i of x (i over all
-// world * rpr rows) -> stage slot [rank] of owner i / rpr.  The last CTA to finish raises the flag at every peer.
+// world * rpr rows) -> stage slot [rank] of owner i / rpr.  mode 2 (one-shot all-reduce of few rows): row i of x -> stage
+// slot [rank] of EVERY rank, which then adds all slots itself.  The last CTA to finish raises the flag at every peer.
 __global__ void __launch_bounds__(256) tp_push_kernel(const TpLayout L, const __nv_bfloat16* __restrict__ x, int rows, int rpr, int mode,
                                                      const int* __restrict__ epoch_ptr, int* __restrict__ cta_counter) {
   const int epoch = *epoch_ptr + 1, parity = epoch & 1;
@@ -72,9 +73,12 @@ __global__ void __launch_bounds__(256) tp_push_kernel(const TpLayout L, const __
         const int r = (L.rank + p) % L.world;              // start with the own copy, stagger the peers
         *reinterpret_cast<uint4*>(tp_ptr(L, r, off)) = v;
       }
-    } else {
+    } else if (mode == 1) {
       const int owner = row / rpr;
       *reinterpret_cast<uint4*>(tp_ptr(L, owner, stage_off(L, parity, L.rank, row % rpr) + c * 16)) = v;
+    } else {
+      const long long off = stage_off(L, parity, L.rank, row) + c * 16;
+      for (int p = 0; p < L.world; p++) *reinterpret_cast<uint4*>(tp_ptr(L, (L.rank + p) % L.world, off)) = v;
     }
   }
   __threadfence_system();
@@ -160,7 +164,7 @@ extern "C" int ne_tp_signal(const TpLayout* L, int which, const int* epoch_ptr, 
 
 extern "C" int ne_tp_push(const TpLayout* L, const void* x, int rows, int rpr, int mode, const int* epoch_ptr, int* cta_counter, cudaStream_t st) {
   if (int rc = tp_check(L, rpr)) return rc;
-  if (rows < 0 || (mode == 0 && rows > rpr) || (mode == 1 && rows > L->world * rpr)) return 1001;
+  if (rows < 0 || mode < 0 || mode > 2 || (mode != 1 && rows > rpr) || (mode == 1 && rows > L->world * rpr)) return 1001;
   if (rows == 0) return ne_tp_signal(L, mode == 0 ? 1 : 0, epoch_ptr, st);
   long long items = (long long)rows * (L->H / 8);
   int blocks = (int)((items + 255) / 256);

@@ -131,6 +131,16 @@ class FusedTP:
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
+        if 0 < T <= self.rpr_cap:
+            # few rows: every rank stores its partial into every peer's stage and adds the slots itself (one hop)
+            lib = _k.lib()
+            x = _k._as_bf16_2d(x).contiguous()
+            L, epoch, ctr, st = self._args()
+            _k._ck(lib.ne_tp_push(L, _k._p(x), _c.c_int(T), _c.c_int(T), _c.c_int(2), epoch, ctr, st), "ne_tp_push")
+            out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
+            _k._ck(lib.ne_tp_reduce(L, _k._p(None), _k._p(out), _c.c_int(T), epoch, _c.c_int(self.spin_limit), st), "ne_tp_reduce")
+            self._advance()
+            return out
         pad = (-T) % self.world
         xp = x if pad == 0 else torch.cat([x, x.new_zeros(pad, x.shape[1])], 0)
         return self.all_gather(self.reduce_scatter(xp))[:T].clone()
