@@ -120,6 +120,19 @@ class KVCache:
             return
         bdim = 1 if self.plan.mla else 2
         dev = self.kv.view(torch.uint8) if self.kv.dtype == torch.float8_e4m3fn else self.kv
+        if self.device.type == "cuda" and self.host_kv.is_pinned():
+            # one kernel copies every (layer, block) pair straight between the pinned host tier and the device cache
+            from ..ops import sm100 as _k
+            import ctypes as _c
+            planes = self.kv.shape[0] if self.plan.mla else self.kv.shape[0] * self.kv.shape[1]
+            blk = dev[0, 0].numel() * dev.element_size() if self.plan.mla else dev[0, 0, 0].numel() * dev.element_size()
+            d_stride, h_stride = blk * dev.shape[bdim], blk * self.host_kv.shape[bdim]
+            si = torch.tensor(src, dtype=torch.int32).to(self.device, non_blocking=True)
+            di = torch.tensor(dst, dtype=torch.int32).to(self.device, non_blocking=True)
+            dst_t, src_t, ds, ss = (self.host_kv, dev, h_stride, d_stride) if to_host else (dev, self.host_kv, d_stride, h_stride)
+            _k._ck(_k.lib().ne_kv_swap(_c.c_void_p(dst_t.data_ptr()), _c.c_void_p(src_t.data_ptr()), _k._p(si), _k._p(di), _c.c_int(len(src)),
+                                       _c.c_int(planes), _c.c_longlong(blk), _c.c_longlong(ds), _c.c_longlong(ss), _k._st()), "ne_kv_swap")
+            return      # stream order is enough: later kernels that reuse the blocks run behind this copy
         s = torch.as_tensor(src, dtype=torch.long)
         d = torch.as_tensor(dst, dtype=torch.long)
         if to_host:

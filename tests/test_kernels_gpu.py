@@ -276,3 +276,24 @@ def test_moe_experts_local(k, T, E, topk, fp8):
         got2 = k.moe_experts(x, idx, w, w13q[half:].contiguous(), w2q[half:].contiguous(), s13[half:].contiguous(), s2[half:].contiguous(), half)
         want2 = ref.moe_experts(x, idx, w, w13q[half:], w2q[half:], s13[half:], s2[half:], half)
         assert _rel(got2, want2) < 2e-2
+
+
+@pytest.mark.parametrize("model,kv", [("tiny-deepseek-v3", "fp8"), ("tiny-deepseek-v3", "bfloat16"), ("qwen3-235b-a22b", "bfloat16")])
+def test_kv_swap_kernel_round_trip(k, model, kv):
+    """Blocks leave for the pinned host tier and come back (to other block ids) bit-exact, all layers in one launch each way."""
+    from nanoengine_b200.models.config import PRESETS
+    from nanoengine_b200.runtime.cache import KVCache, make_cache_plan
+    plan = make_cache_plan(PRESETS[model](num_hidden_layers=3), kv, 16)
+    c = KVCache(plan, 12, "cuda")
+    c.allocate_host(6)
+    flat = c.kv.view(torch.uint8)
+    flat.copy_(torch.randint(0, 255, flat.shape, device="cuda", dtype=torch.uint8))
+    want = [v.clone() for b in (3, 7, 1) for v in c.block_views(b)]
+    c.swap([3, 7, 1], [0, 5, 2], to_host=True)
+    for b in (3, 7, 1):
+        for v in c.block_views(b):
+            v.zero_()
+    c.swap([0, 5, 2], [9, 10, 11], to_host=False)
+    torch.cuda.synchronize()
+    got = [v for b in (9, 10, 11) for v in c.block_views(b)]
+    assert all(torch.equal(a.view(torch.uint8), b.view(torch.uint8)) for a, b in zip(got, want))
