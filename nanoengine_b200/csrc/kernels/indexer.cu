@@ -1,0 +1,385 @@
+// DSA lightning indexer: query / key preparation, fp8 logits on the tensor cores, radix top-k with page translation.
+//
+//   indexer_prep    one warp per 128-wide row: [LayerNorm] -> RoPE on the first `rope` dims (pairs (i, i + rope/2)) ->
+//                   128-point Hadamard -> one power-of-two scale per row -> e4m3; keys go straight into their cache page
+//                   (page = [bs x 128 B keys | bs x fp32 scales]), queries into a dense [rows, 128] buffer + scales.
+//   indexer_logits  logits[t, j] = k_scale[j] * sum_h w[t, h] * relu(q8[t, h, :] . k8[j, :]) for the keys j the token may see.
+//                   One CTA per (token, key split): Q (heads x 128 B) stays in shared memory, key tiles of 128 keys (two pages)
+//                   stream through a TMA ring, S = Q K^T is one group of four tcgen05 MMAs (M = 128, N = 128, K = 32) into a
+//                   double-buffered TMEM accumulator; two epilogue warps apply relu and the head weights and add the 64 head
+//                   rows of every key column with a register transpose-reduce (124 shuffles per 128 columns).
+//   indexer_topk    per token: 3-pass radix select (11 + 11 + 10 bits) of the k largest logits among the visible keys, written
+//                   as physical slot ids (block_table[idx / bs] * bs + idx % bs), -1 padded.
+//
+// Replaces in the reference: deep_gemm.fp8_mqa_logits / fp8_paged_mqa_logits (layers/backends/dsa/indexer/lightning.py:
+// 1081-1492), kernel/jit/sgl/csrc/deepseek_v4/{indexer_q.cuh, topk.cuh, topk_v2.cuh}, fast-hadamard-transform/hadamard_jit.cuh
+// and the Triton key path (triton/generic/indexer_transform.py, fp8_ue8m0_quant.py:370).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <math.h>
+
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace ne {
+
+constexpr int kKernelIdx = 6;
+constexpr int kIdxD = 128;                 // index head dim: one 128-byte swizzle row of e4m3
+constexpr int kIdxPage = 64;               // keys per cache page
+constexpr int kIdxTile = 128;              // keys per MMA tile (two pages)
+constexpr int kIdxStages = 4;
+constexpr int kIdxQBytes = 128 * 128;      // Q tile slot (only the first `heads` rows are fetched)
+constexpr int kIdxKBytes = kIdxTile * 128;
+constexpr int kIdxSmem = kIdxQBytes + kIdxStages * kIdxKBytes + 1024 + 256 + 2 * 128 * 4;
+constexpr int kIdxThreads = 192;
+
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+// x: rows of 128 bf16 (row r at x + r * x_ld).  heads = rows per token (positions / slots are per token).
+__global__ void __launch_bounds__(256) indexer_prep_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int rows, int heads,
+                                                          const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b, float eps,
+                                                          const long long* __restrict__ positions, const float* __restrict__ rope_cache, int rope,
+                                                          uint8_t* __restrict__ q_out, float* __restrict__ s_out,
+                                                          uint8_t* __restrict__ cache, const long long* __restrict__ slots, int bs, long long page_bytes) {
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const int t = r / heads;
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + (long long)r * x_ld + lane * 4);
+  const float2 p0 = unpack_bf16x2(raw.x), p1 = unpack_bf16x2(raw.y);
+  float v[4] = {p0.x, p0.y, p1.x, p1.y};
+  if (ln_w) {
+    float s = warp_sum(v[0] + v[1] + v[2] + v[3]);
+    const float mean = s * (1.f / kIdxD);
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) q += (v[j] - mean) * (v[j] - mean);
+    const float inv = rsqrtf(warp_sum(q) * (1.f / kIdxD) + eps);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int e = lane * 4 + j;
+      v[j] = bf16_round((v[j] - mean) * inv * __bfloat162float(ln_w[e]) + (ln_b ? __bfloat162float(ln_b[e]) : 0.f));
+    }
+  }
+  // RoPE on elements [0, rope): pairs (i, i + rope/2).  With rope = 64 the partner of lane l (l < 16) is lane l ^ 8.
+  {
+    const int half = rope / 2, hl = half / 4;                 // lanes per half
+    const float* cs = rope_cache + positions[t] * rope;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], hl);
+      const int e = lane * 4 + j;
+      if (e < rope) {
+        const int i = e % half;
+        const float c = cs[i], sn = cs[half + i];
+        v[j] = bf16_round(e < half ? v[j] * c - other * sn : v[j] * c + other * sn);
+      }
+    }
+  }
+  // 128-point Walsh-Hadamard (Sylvester order): strides 1, 2 inside the lane, 4 .. 64 across lanes
+  {
+    float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+    v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
+        v[j] = (lane & m) ? o - v[j] : v[j] + o;
+      }
+    }
+    const float nrm = 0.08838834764831845f;                   // 128^-1/2
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = bf16_round(v[j] * nrm);
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  amax = fmaxf(warp_max(amax), 1e-4f);
+  const float sc = exp2f(ceilf(log2f(amax / 448.f)));
+  const float is = 1.f / sc;
+  const uint32_t packed = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
+  if (cache) {
+    const long long slot = slots[t];
+    if (slot < 0) return;
+    uint8_t* page = cache + (slot / bs) * page_bytes;
+    const int off = (int)(slot % bs);
+    *reinterpret_cast<uint32_t*>(page + (long long)off * kIdxD + lane * 4) = packed;
+    if (lane == 0) *reinterpret_cast<float*>(page + (long long)bs * kIdxD + off * 4) = sc;
+  } else {
+    *reinterpret_cast<uint32_t*>(q_out + (long long)r * kIdxD + lane * 4) = packed;
+    if (lane == 0) s_out[r] = sc;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+struct IdxArgs {
+  const float* head_w; const float* q_scale;        // [T, heads] each
+  const uint8_t* cache; long long page_bytes;       // indexer cache, for the key scales
+  const int* block_tables; int bt_stride;
+  const int* cu_seqlens_q; const int* context_lens; int num_seqs;
+  int T, heads, splits;
+  float* logits; long long ld;                      // [T, ld] fp32
+};
+
+__global__ void __launch_bounds__(kIdxThreads, 1)
+indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const IdxArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kIdxQBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sK + kIdxStages * kIdxKBytes);
+  // q_full | k_full[4] | k_empty[4] | s_full[2] | s_empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);        // [2 tile parities][128 columns]
+  const uint32_t b_qfull = smem_u32(bars), b_kfull = smem_u32(bars + 1), b_kempty = smem_u32(bars + 5);
+  const uint32_t b_sfull = smem_u32(bars + 9), b_sempty = smem_u32(bars + 11);
+  const int warp = threadIdx.x >> 5;
+  const int t = blockIdx.x, split = blockIdx.y;
+
+  int lo = 0, hi = a.num_seqs;
+  while (lo + 1 < hi) { int mid = (lo + hi) >> 1; if (a.cu_seqlens_q[mid] <= t) lo = mid; else hi = mid; }
+  const int seq = lo;
+  const int q_len = a.cu_seqlens_q[seq + 1] - a.cu_seqlens_q[seq];
+  const int limit = a.context_lens[seq] - q_len + (t - a.cu_seqlens_q[seq]);     // last visible key position
+  const int total_tiles = limit >= 0 ? limit / kIdxTile + 1 : 0;
+  const int per_split = (total_tiles + a.splits - 1) / a.splits;
+  const int tile_begin = split * per_split;
+  const int n_tiles = max(0, min(total_tiles, tile_begin + per_split) - tile_begin);
+  const int* bt = a.block_tables + (long long)seq * a.bt_stride;
+
+  if (threadIdx.x == 0) {
+    mbar_init(b_qfull, 1);
+    for (int i = 0; i < kIdxStages; i++) { mbar_init(b_kfull + 8 * i, 1); mbar_init(b_kempty + 8 * i, 1); }
+    for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 2); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tq); tma_prefetch_desc(&tk);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (n_tiles > 0 && elect_one()) {
+      mbar_expect_tx(b_qfull, 64 * 128);
+      tma_load_2d(smem_u32(sQ), &tq, b_qfull, 0, t * a.heads);
+      for (int i = 0; i < n_tiles; i++) {
+        const int s = i % kIdxStages;
+        if (!mbar_wait(b_kempty + 8 * s, ((i / kIdxStages) & 1) ^ 1, abort_flag, kKernelIdx, 100 + s)) break;
+        const int pg = (tile_begin + i) * 2;                       // first of the tile's two pages
+        const bool two = (long long)(pg + 1) * kIdxPage <= limit;  // the second page holds at least one visible key
+        mbar_expect_tx(b_kfull + 8 * s, two ? kIdxKBytes : kIdxKBytes / 2);
+        tma_load_3d(smem_u32(sK + s * kIdxKBytes), &tk, b_kfull + 8 * s, 0, 0, bt[pg]);
+        if (two) tma_load_3d(smem_u32(sK + s * kIdxKBytes + kIdxKBytes / 2), &tk, b_kfull + 8 * s, 0, 0, bt[pg + 1]);
+      }
+    }
+  } else if (warp == 1) {
+    if (n_tiles > 0 && elect_one()) {
+      constexpr uint32_t kIdesc = make_idesc(FMT_E4M3, FMT_E4M3, 128, kIdxTile);
+      bool ok = mbar_wait(b_qfull, 0, abort_flag, kKernelIdx, 200);
+      for (int i = 0; ok && i < n_tiles; i++) {
+        const int sb = i & 1, s = i % kIdxStages;
+        if (!mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelIdx, 210 + sb)) break;
+        if (!mbar_wait(b_kfull + 8 * s, (i / kIdxStages) & 1, abort_flag, kKernelIdx, 220 + s)) break;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * kIdxKBytes);
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+          uint64_t adesc = make_smem_desc(qa + ks * 32, 16, 1024, SW_128B);
+          uint64_t bdesc = make_smem_desc(ka + ks * 32, 16, 1024, SW_128B);
+          umma_f8(tmem_base + sb * kIdxTile, adesc, bdesc, kIdesc, ks != 0);
+        }
+        tc_commit(b_kempty + 8 * s);
+        tc_commit(b_sfull + 8 * sb);
+      }
+    }
+  } else if (warp >= 4) {
+    // rows 0..63 of the accumulator (TMEM lane quadrants 0 and 1) are the heads of this token
+    const int wq = warp & 3;                                  // 0 or 1
+    const int lane = (int)lane_id();
+    const int row = wq * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const float rw = row < a.heads ? a.head_w[(long long)t * a.heads + row] * a.q_scale[(long long)t * a.heads + row] : 0.f;
+    // after the transpose-reduce lane l holds the sums of columns cbase .. cbase + 3
+    const int cbase = ((lane >> 4) & 1) * 64 + ((lane >> 3) & 1) * 32 + ((lane >> 2) & 1) * 16 + ((lane >> 1) & 1) * 8 + (lane & 1) * 4;
+    float* out_row = a.logits + (long long)t * a.ld;
+    bool ok = true;
+    for (int i = 0; i < n_tiles; i++) {
+      const int sb = i & 1;
+      float v[128];
+      if (ok && !mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelIdx, 300 + sb)) ok = false;
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * kIdxTile + c * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[c * 32 + j] = row < a.heads ? fmaxf(__uint_as_float(r[j]), 0.f) * rw : 0.f;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(b_sempty + 8 * sb);
+        // transpose-reduce over the 32 lanes: every step halves the columns a lane keeps and doubles the rows they cover
+#pragma unroll
+        for (int w = 64, m = 16; w >= 4; w >>= 1, m >>= 1) {
+#pragma unroll
+          for (int j = 0; j < w; j++) {
+            const bool up = (lane & m) != 0;
+            const float send = up ? v[j] : v[j + w];
+            const float keep = up ? v[j + w] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, m);
+          }
+        }
+        if (wq == 1) *reinterpret_cast<float4*>(s_part + sb * 128 + cbase) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+      asm volatile("bar.sync 2, 64;" ::: "memory");           // the two epilogue warps; executed once per tile whatever happened
+      if (ok && wq == 0) {
+        const float4 o = *reinterpret_cast<const float4*>(s_part + sb * 128 + cbase);
+        const int key0 = (tile_begin + i) * kIdxTile + cbase;
+        const int pg = key0 / kIdxPage;
+        float ks[4] = {0.f, 0.f, 0.f, 0.f};
+        if (key0 <= limit) {
+          const float4 kv = *reinterpret_cast<const float4*>(a.cache + (long long)bt[pg] * a.page_bytes + kIdxPage * kIdxD + (key0 % kIdxPage) * 4);
+          ks[0] = kv.x; ks[1] = kv.y; ks[2] = kv.z; ks[3] = kv.w;
+        }
+        float res[4] = {(v[0] + o.x) * ks[0], (v[1] + o.y) * ks[1], (v[2] + o.z) * ks[2], (v[3] + o.w) * ks[3]};
+#pragma unroll
+        for (int j = 0; j < 4; j++) if (key0 + j > limit) res[j] = -INFINITY;
+        if (key0 < a.ld) *reinterpret_cast<float4*>(out_row + key0) = make_float4(res[0], res[1], res[2], res[3]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) for (int i = 0; i < 2000; i++) __nanosleep(1000);
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t float_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);          // larger float <=> larger key
+}
+
+// One CTA per token.  out [T, k] int32: physical slot ids of the k best visible keys (any order), -1 padded.
+__global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restrict__ logits, long long ld, const int* __restrict__ cu_seqlens_q,
+                                                           const int* __restrict__ context_lens, int num_seqs, const int* __restrict__ block_tables,
+                                                           int bt_stride, int bs, int k, int* __restrict__ out) {
+  __shared__ int hist[2048];
+  __shared__ uint32_t s_prefix; __shared__ int s_remaining, s_cnt_gt, s_cnt_eq;
+  const int t = blockIdx.x;
+  int lo = 0, hi = num_seqs;
+  while (lo + 1 < hi) { int mid = (lo + hi) >> 1; if (cu_seqlens_q[mid] <= t) lo = mid; else hi = mid; }
+  const int seq = lo;
+  const int q_len = cu_seqlens_q[seq + 1] - cu_seqlens_q[seq];
+  const int n = context_lens[seq] - q_len + (t - cu_seqlens_q[seq]) + 1;          // visible keys
+  const float* row = logits + (long long)t * ld;
+  const int* bt = block_tables ? block_tables + (long long)seq * bt_stride : nullptr;
+  int* o = out + (long long)t * k;
+  auto phys = [&](int idx) { return bt ? bt[idx / bs] * bs + idx % bs : idx; };
+  if (n <= k) {
+    for (int i = threadIdx.x; i < k; i += blockDim.x) o[i] = i < n ? phys(i) : -1;
+    return;
+  }
+  if (threadIdx.x == 0) { s_prefix = 0; s_remaining = k; }
+  // three digit passes: bits [31:21], [20:10], [9:0]
+  const int shifts[3] = {21, 10, 0}, widths[3] = {11, 11, 10};
+  uint32_t known_mask = 0;
+  for (int p = 0; p < 3; p++) {
+    for (int i = threadIdx.x; i < 2048; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    const int sh = shifts[p];
+    const uint32_t dm = (1u << widths[p]) - 1;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const uint32_t key = float_key(row[i]);
+      if ((key & known_mask) == prefix) atomicAdd(&hist[(key >> sh) & dm], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int rem = s_remaining, b = (int)dm;
+      for (; b > 0; b--) { if (hist[b] >= rem) break; rem -= hist[b]; }
+      s_prefix = prefix | ((uint32_t)b << sh);
+      s_remaining = rem;                                    // how many to take from the chosen digit's bucket
+    }
+    known_mask |= dm << sh;
+    __syncthreads();
+  }
+  const uint32_t thr = s_prefix;                            // the k-th largest key; s_remaining of its copies are taken
+  const int need_eq = s_remaining;
+  if (threadIdx.x == 0) { s_cnt_gt = 0; s_cnt_eq = 0; }
+  __syncthreads();
+  const int n_gt = k - need_eq;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint32_t key = float_key(row[i]);
+    if (key > thr) {
+      const int pos = atomicAdd(&s_cnt_gt, 1);
+      if (pos < n_gt) o[pos] = phys(i);
+    } else if (key == thr) {
+      const int pos = atomicAdd(&s_cnt_eq, 1);
+      if (pos < need_eq) o[n_gt + pos] = phys(i);
+    }
+  }
+}
+
+}  // namespace ne
+
+using namespace ne;
+
+// x [rows, 128] bf16 (row stride x_ld elements), heads = rows per token.  Keys: cache + slots given (q_out / s_out unused).
+// Queries: q_out [rows, 128] e4m3 + s_out [rows].
+extern "C" int ne_indexer_prep(const void* x, long long x_ld, int rows, int heads, const void* ln_w, const void* ln_b, float eps,
+                               const long long* positions, const float* rope_cache, int rope, void* q_out, float* s_out, void* cache,
+                               const long long* slots, int bs, long long page_bytes, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (heads < 1 || rows % heads || rope < 8 || rope > kIdxD || (rope & (rope - 1)) || x_ld % 4) return 1001;
+  if (!cache && (!q_out || !s_out)) return 1002;
+  indexer_prep_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, x_ld, rows, heads, (const __nv_bfloat16*)ln_w, (const __nv_bfloat16*)ln_b, eps,
+                                                      positions, rope_cache, rope, (uint8_t*)q_out, s_out, (uint8_t*)cache, slots, bs, page_bytes);
+  return (int)cudaGetLastError();
+}
+
+// q8 [T * heads, 128] e4m3; cache [num_blocks, page_bytes] with page = [64 x 128 B keys | 64 fp32 scales]; logits [T, ld] fp32
+// (ld a multiple of 4, at least the largest context rounded up to 128).  Columns past a token's causal limit inside its last
+// tile are written as -inf; columns in later tiles are left untouched.
+extern "C" int ne_indexer_logits(const void* q8, const float* q_scale, const float* head_w, const void* cache, int num_blocks, long long page_bytes,
+                                 const int* block_tables, int bt_stride, const int* cu_seqlens_q, const int* context_lens, int num_seqs,
+                                 int T, int heads, int splits, float* logits, long long ld, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (heads < 1 || heads > 64 || splits < 1 || page_bytes != kIdxPage * (kIdxD + 4) || ld % 4) return 1001;
+  CUtensorMap tq, tk;
+  {
+    uint64_t dims[2] = {kIdxD, (uint64_t)T * heads}; uint64_t strides[1] = {kIdxD}; uint32_t box[2] = {kIdxD, 64};
+    int rc = make_tmap(&tq, q8, TMA_U8, 2, dims, strides, box, TMA_SW_128); if (rc) return 2000 + rc;
+  }
+  {
+    uint64_t dims[3] = {kIdxD, kIdxPage, (uint64_t)num_blocks}; uint64_t strides[2] = {kIdxD, (uint64_t)page_bytes}; uint32_t box[3] = {kIdxD, kIdxPage, 1};
+    int rc = make_tmap(&tk, cache, TMA_U8, 3, dims, strides, box, TMA_SW_128); if (rc) return 2100 + rc;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(indexer_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIdxSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  IdxArgs a;
+  a.head_w = head_w; a.q_scale = q_scale; a.cache = (const uint8_t*)cache; a.page_bytes = page_bytes; a.block_tables = block_tables;
+  a.bt_stride = bt_stride; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs; a.T = T; a.heads = heads;
+  a.splits = splits; a.logits = logits; a.ld = ld;
+  indexer_logits_kernel<<<dim3((unsigned)T, (unsigned)splits), kIdxThreads, kIdxSmem, st>>>(tq, tk, a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_indexer_topk(const float* logits, long long ld, const int* cu_seqlens_q, const int* context_lens, int num_seqs,
+                               const int* block_tables, int bt_stride, int bs, int k, int T, int* out, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (k < 1 || bs < 1) return 1001;
+  indexer_topk_kernel<<<T, 1024, 0, st>>>(logits, ld, cu_seqlens_q, context_lens, num_seqs, block_tables, bt_stride, bs, k, out);
+  return (int)cudaGetLastError();
+}

@@ -8,8 +8,8 @@
 When a sequence's context is not longer than top-k the selection is the identity, and the layer runs the dense kernel.
 
 Parity: reference layers/backends/dsa/indexer/lightning.py:116-162 (scoring), :408-535 (IndexerCache), :538-1492
-(Indexer: projections, store, prefill and decode top-k); kernels K3/K5/K9/T11/X5 of the survey are restated here as
-operators (`ops.hadamard`, `ops.quant_fp8_per_token_pow2`, `ops.indexer_logits`, `ops.indexer_topk`).
+(Indexer: projections, store, prefill and decode top-k).  The work is three operators: `ops.indexer_k_store` (key path
+into the cache), `ops.indexer_q_prep` (query path) and `ops.indexer_select` (fp8 logits + top-k + page translation).
 """
 from __future__ import annotations
 
@@ -55,55 +55,20 @@ class LightningIndexer(nn.Module):
         elif leaf == "k_norm.bias":
             self.k_norm_bias.copy_(w.to(self.k_norm_bias.dtype))
 
-    # ---- cache -------------------------------------------------------------------------------
-    def _store(self, cache: torch.Tensor, slots: torch.Tensor, k8: torch.Tensor, ks: torch.Tensor):
-        """cache [blocks, bs*(D+4)] uint8.  Key row `off` of a page sits at off*D, its scale at bs*D + off*4."""
-        bs = cache.shape[1] // (self.D + 4)
-        blk, off = (slots // bs).long(), (slots % bs).long()
-        flat = cache.view(-1)
-        page = cache.shape[1]
-        kidx = (blk * page + off * self.D).unsqueeze(1) + torch.arange(self.D, device=cache.device)
-        flat[kidx.reshape(-1)] = k8.view(torch.uint8).reshape(-1)
-        sidx = (blk * page + bs * self.D + off * 4).unsqueeze(1) + torch.arange(4, device=cache.device)
-        flat[sidx.reshape(-1)] = ks.float().contiguous().view(torch.uint8).reshape(-1)
-
-    def _gather(self, cache: torch.Tensor, block_table: torch.Tensor, n: int):
-        bs = cache.shape[1] // (self.D + 4)
-        nb = (n + bs - 1) // bs
-        pages = cache[block_table[:nb].long()]                                      # [nb, bs*(D+4)]
-        keys = pages[:, : bs * self.D].reshape(nb * bs, self.D).view(FP8)[:n]
-        scales = pages[:, bs * self.D:].contiguous().view(torch.float32).reshape(nb * bs)[:n]
-        return keys, scales
-
     # ---- forward -----------------------------------------------------------------------------
     def forward(self, hidden: torch.Tensor, q_in: torch.Tensor, positions: torch.Tensor, ctx: ForwardContext, rope_cache: torch.Tensor
                 ) -> Optional[torch.Tensor]:
         T = hidden.shape[0]
-        q = self.wq_b(q_in).view(T, self.Hi, self.D)
-        k = ops.layernorm(self.wk(hidden), self.k_norm_weight, self.k_norm_bias, 1e-6)
         rd = self.rope_dim
-        q = torch.cat([ref.apply_rope(q[..., :rd], positions, rope_cache, False), q[..., rd:]], -1)
-        k = torch.cat([ref.apply_rope(k[..., :rd], positions, rope_cache, False), k[..., rd:]], -1)
-        q, k = ops.hadamard(q), ops.hadamard(k)
-        k8, ks = ops.quant_fp8_per_token_pow2(k)
+        q = self.wq_b(q_in).view(T, self.Hi, self.D)
         cache = ctx.indexer_caches[self.layer_idx]
-        self._store(cache, ctx.slot_mapping, k8, ks)
+        ops.indexer_k_store(self.wk(hidden), self.k_norm_weight, self.k_norm_bias, 1e-6, positions, rope_cache, rd, cache, ctx.slot_mapping)
         if max(ctx.context_lens_host or [ctx.max_seqlen_k]) <= self.topk:
             return None                                   # every key is selected anyway: dense attention
-        q8, qs = ops.quant_fp8_per_token_pow2(q.reshape(T * self.Hi, self.D))
-        q8, qs = q8.view(T, self.Hi, self.D), qs.view(T, self.Hi)
+        q8, qs = ops.indexer_q_prep(q, positions, rope_cache, rd)
         w = self.weights_proj(hidden).float() * (self.Hi ** -0.5) * self.softmax_scale
-        out = torch.full((T, self.topk), -1, dtype=torch.int32, device=hidden.device)
-        cu, cl = ctx.cu_seqlens_q_host, ctx.context_lens_host
-        bs = cache.shape[1] // (self.D + 4)
-        for i in range(ctx.num_seqs):
-            lo, hi = cu[i], cu[i + 1]
-            if hi == lo:
-                continue
-            n = cl[i]
-            keys, kscale = self._gather(cache, ctx.block_tables[i], n)
-            logits = ops.indexer_logits(q8[lo:hi], qs[lo:hi], w[lo:hi], keys, kscale)          # [q, n]
-            valid = torch.arange(n - (hi - lo) + 1, n + 1, device=hidden.device)               # causal: keys visible to each row
-            idx = ops.indexer_topk(logits, valid, self.topk)
-            out[lo:hi] = ops.logical_to_physical(idx, ctx.block_tables[i:i + 1].expand(hi - lo, -1), bs)
-        return out
+        cu = ctx.cu_seqlens_q_host if ctx.cu_seqlens_q_host is not None else ctx.cu_seqlens_q
+        cl = ctx.context_lens_host if ctx.context_lens_host is not None else ctx.context_lens
+        if hidden.is_cuda:
+            cu, cl = ctx.cu_seqlens_q, ctx.context_lens       # device tables: no host round trip inside a captured graph
+        return ops.indexer_select(q8, qs, w, cache, ctx.block_tables, cu, cl, self.topk)

@@ -359,6 +359,66 @@ def logical_to_physical(idx: torch.Tensor, block_table_rows: torch.Tensor, block
     return torch.where(idx >= 0, phys, torch.full_like(phys, -1)).to(torch.int32)
 
 
+def indexer_k_store(k: torch.Tensor, ln_w: torch.Tensor, ln_b: Optional[torch.Tensor], eps: float, positions: torch.Tensor,
+                    rope_cache: torch.Tensor, rope_dim: int, cache: torch.Tensor, slots: torch.Tensor) -> None:
+    """Indexer key path: LayerNorm -> RoPE on the first rope_dim dims (half-split pairs) -> Hadamard -> one power-of-two
+    scale per token -> e4m3, written into the indexer cache.  cache [blocks, bs*(D+4)] uint8: key row `off` of a page
+    sits at off*D, its fp32 scale at bs*D + off*4 (reference dsa/indexer/lightning.py:408-535, IndexerCache)."""
+    D = k.shape[-1]
+    k = layernorm(k, ln_w, ln_b, eps)
+    k = torch.cat([apply_rope(k[..., :rope_dim], positions, rope_cache, False), k[..., rope_dim:]], -1)
+    k8, ks = quant_fp8_per_token_pow2(hadamard(k))
+    keep = slots >= 0
+    slots, k8, ks = slots[keep], k8[keep], ks[keep]
+    bs = cache.shape[1] // (D + 4)
+    blk, off = (slots // bs).long(), (slots % bs).long()
+    flat, page = cache.view(-1), cache.shape[1]
+    kidx = (blk * page + off * D).unsqueeze(1) + torch.arange(D, device=cache.device)
+    flat[kidx.reshape(-1)] = k8.view(torch.uint8).reshape(-1)
+    sidx = (blk * page + bs * D + off * 4).unsqueeze(1) + torch.arange(4, device=cache.device)
+    flat[sidx.reshape(-1)] = ks.float().contiguous().view(torch.uint8).reshape(-1)
+
+
+def indexer_q_prep(q: torch.Tensor, positions: torch.Tensor, rope_cache: torch.Tensor, rope_dim: int):
+    """Indexer query path: q [T, Hi, D] -> RoPE (first rope_dim dims) -> Hadamard -> per-(token, head) power-of-two scale
+    -> (e4m3 [T, Hi, D], scales [T, Hi])."""
+    T, Hi, D = q.shape
+    q = torch.cat([apply_rope(q[..., :rope_dim], positions, rope_cache, False), q[..., rope_dim:]], -1)
+    q8, qs = quant_fp8_per_token_pow2(hadamard(q).reshape(T * Hi, D))
+    return q8.view(T, Hi, D), qs.view(T, Hi)
+
+
+def indexer_gather(cache: torch.Tensor, block_table: torch.Tensor, n: int, D: int):
+    bs = cache.shape[1] // (D + 4)
+    nb = (n + bs - 1) // bs
+    pages = cache[block_table[:nb].long()]
+    keys = pages[:, : bs * D].reshape(nb * bs, D).view(FP8)[:n]
+    scales = pages[:, bs * D:].contiguous().view(torch.float32).reshape(nb * bs)[:n]
+    return keys, scales
+
+
+def indexer_select(q8: torch.Tensor, q_scale: torch.Tensor, head_w: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
+                   cu_seqlens_q, context_lens, topk: int) -> torch.Tensor:
+    """Per token: physical slots of the `topk` visible keys with the largest indexer score, -1 padded ([T, topk] int32).
+    cu_seqlens_q / context_lens: host lists or tensors."""
+    T, Hi, D = q8.shape
+    cu = cu_seqlens_q.tolist() if isinstance(cu_seqlens_q, torch.Tensor) else list(cu_seqlens_q)
+    cl = context_lens.tolist() if isinstance(context_lens, torch.Tensor) else list(context_lens)
+    bs = cache.shape[1] // (D + 4)
+    out = torch.full((T, topk), -1, dtype=torch.int32, device=q8.device)
+    for i in range(len(cl)):
+        lo, hi = cu[i], cu[i + 1]
+        if hi == lo:
+            continue
+        n = cl[i]
+        keys, kscale = indexer_gather(cache, block_tables[i], n, D)
+        logits = indexer_logits(q8[lo:hi], q_scale[lo:hi], head_w[lo:hi], keys, kscale)
+        valid = torch.arange(n - (hi - lo) + 1, n + 1, device=q8.device)
+        idx = indexer_topk(logits, valid, topk)
+        out[lo:hi] = logical_to_physical(idx, block_tables[i:i + 1].expand(hi - lo, -1), bs)
+    return out
+
+
 # ---- small GEMM-shaped helpers -------------------------------------------------------------------
 def bmm_absorb(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """Per-head matmul of MLA weight absorption: x [T, H, A], w [H, A, B] -> [T, H, B]."""

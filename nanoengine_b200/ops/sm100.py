@@ -404,9 +404,71 @@ def merge_attention_states(o1, lse1, o2, lse2):
     return ref.merge_attention_states(o1, lse1, o2, lse2)
 
 
-hadamard = ref.hadamard
+# ---- DSA lightning indexer --------------------------------------------------------------------------
+hadamard = ref.hadamard                                     # building blocks of the oracle; the fused kernels below are what runs
 quant_fp8_per_token_pow2 = ref.quant_fp8_per_token_pow2
 indexer_logits = ref.indexer_logits
 indexer_topk = ref.indexer_topk
 logical_to_physical = ref.logical_to_physical
+indexer_gather = ref.indexer_gather
+
+
+def _i64(t):
+    return t if t.dtype == torch.int64 else t.long()
+
+
+def indexer_k_store(k, ln_w, ln_b, eps, positions, rope_cache, rope_dim, cache, slots) -> None:
+    T, D = k.shape
+    assert D == 128 and k.dtype == torch.bfloat16 and k.stride(1) == 1 and cache.dtype == torch.uint8 and cache.is_contiguous()
+    bs = cache.shape[1] // (D + 4)
+    _ck(lib().ne_indexer_prep(_p(k), _c.c_longlong(k.stride(0)), _c.c_int(T), _c.c_int(1), _p(ln_w), _p(ln_b), _c.c_float(eps), _p(_i64(positions)),
+                              _p(rope_cache), _c.c_int(rope_dim), _p(None), _p(None), _p(cache), _p(_i64(slots)), _c.c_int(bs),
+                              _c.c_longlong(cache.shape[1]), _st()), "ne_indexer_prep")
+
+
+def indexer_q_prep(q, positions, rope_cache, rope_dim):
+    T, Hi, D = q.shape
+    assert D == 128
+    q = q if (q.dtype == torch.bfloat16 and q.is_contiguous()) else q.to(torch.bfloat16).contiguous()
+    q8 = torch.empty(T, Hi, D, dtype=torch.uint8, device=q.device)
+    qs = torch.empty(T, Hi, dtype=torch.float32, device=q.device)
+    _ck(lib().ne_indexer_prep(_p(q), _c.c_longlong(D), _c.c_int(T * Hi), _c.c_int(Hi), _p(None), _p(None), _c.c_float(0.0), _p(_i64(positions)),
+                              _p(rope_cache), _c.c_int(rope_dim), _p(q8), _p(qs), _p(None), _p(None), _c.c_int(1), _c.c_longlong(0), _st()),
+        "ne_indexer_prep")
+    return q8.view(FP8), qs
+
+
+INDEXER_LOGITS_BYTES = 1 << 30          # query tokens are processed in chunks whose logits fit this budget
+
+
+def indexer_select(q8, q_scale, head_w, cache, block_tables, cu_seqlens_q, context_lens, topk: int) -> torch.Tensor:
+    """fp8 logits on the tensor cores (one CTA per token and key split) followed by the radix top-k with page translation."""
+    T, Hi, D = q8.shape
+    dev = q8.device
+    bs = cache.shape[1] // (D + 4)
+    assert D == 128 and bs == 64 and Hi <= 64, "the indexer kernels take 128-wide heads, 64-key pages and at most 64 heads"
+    cu = cu_seqlens_q if isinstance(cu_seqlens_q, torch.Tensor) else torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
+    cl = context_lens if isinstance(context_lens, torch.Tensor) else torch.tensor(list(context_lens), dtype=torch.int32)
+    cu, cl = cu.to(dev, torch.int32), cl.to(dev, torch.int32)
+    bt = block_tables.to(torch.int32).contiguous()
+    B = cl.numel()
+    ld = (bt.shape[1] * bs + 127) // 128 * 128
+    out = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    w = head_w.float().contiguous()
+    qs = q_scale.float().contiguous()
+    q8c = q8.contiguous()
+    chunk = max(1, min(T, INDEXER_LOGITS_BYTES // (ld * 4)))
+    logits = torch.empty(chunk, ld, dtype=torch.float32, device=dev)
+    l = lib()
+    for t0 in range(0, T, chunk):
+        n = min(chunk, T - t0)
+        # the kernels find a token's sequence from cu_seqlens_q, so a chunk sees the table shifted by its first token
+        cu_c = (cu - t0).clamp_(min=-(1 << 30))
+        splits = max(1, min(16, 148 // max(n, 1)))
+        _ck(l.ne_indexer_logits(_c.c_void_p(q8c.data_ptr() + t0 * Hi * D), _c.c_void_p(qs.data_ptr() + t0 * Hi * 4), _c.c_void_p(w.data_ptr() + t0 * Hi * 4),
+                                _p(cache), _c.c_int(cache.shape[0]), _c.c_longlong(cache.shape[1]), _p(bt), _c.c_int(bt.stride(0)), _p(cu_c), _p(cl),
+                                _c.c_int(B), _c.c_int(n), _c.c_int(Hi), _c.c_int(splits), _p(logits), _c.c_longlong(ld), _st()), "ne_indexer_logits")
+        _ck(l.ne_indexer_topk(_p(logits), _c.c_longlong(ld), _p(cu_c), _p(cl), _c.c_int(B), _p(bt), _c.c_int(bt.stride(0)), _c.c_int(bs),
+                              _c.c_int(topk), _c.c_int(n), _c.c_void_p(out.data_ptr() + t0 * topk * 4), _st()), "ne_indexer_topk")
+    return out
 dequant_fp8_1x128 = ref.dequant_fp8_1x128

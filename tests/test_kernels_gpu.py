@@ -297,3 +297,70 @@ def test_kv_swap_kernel_round_trip(k, model, kv):
     torch.cuda.synchronize()
     got = [v for b in (9, 10, 11) for v in c.block_views(b)]
     assert all(torch.equal(a.view(torch.uint8), b.view(torch.uint8)) for a, b in zip(got, want))
+
+
+def _indexer_setup(T_per_seq, ctxs, Hi=64, D=128, bs=64, seed=31):
+    torch.manual_seed(seed)
+    B = len(ctxs)
+    nb_per = [(c + bs - 1) // bs for c in ctxs]
+    max_nb = max(nb_per)
+    num_blocks = sum(nb_per) + 2
+    perm = torch.randperm(num_blocks - 1, device="cuda")[: sum(nb_per)].to(torch.int32) + 1
+    bt = torch.zeros(B, max_nb, dtype=torch.int32, device="cuda")
+    o = 0
+    for i, n in enumerate(nb_per):
+        bt[i, :n] = perm[o:o + n]; o += n
+    cache = torch.zeros(num_blocks, bs * (D + 4), dtype=torch.uint8, device="cuda")
+    rope_cache = ref.rope_cos_sin_cache(64, 1 << 17, 10000.0).cuda()
+    return B, bt, cache, rope_cache
+
+
+def test_indexer_prep_matches_reference_key_and_query_paths(k):
+    B, bt, cache, rope_cache = _indexer_setup(None, [300, 70])
+    T, D, Hi = 200, 128, 64
+    kx = torch.randn(T, D, device="cuda", dtype=torch.bfloat16) * 2
+    ln_w = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16)
+    ln_b = (0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16)
+    pos = torch.randint(0, 60000, (T,), device="cuda")
+    slots = (bt[0, :4].long().repeat_interleave(64) * 64 + torch.arange(256, device="cuda") % 64)[:T]
+    slots[5] = -1
+    c1, c2 = cache.clone(), cache.clone()
+    k.indexer_k_store(kx, ln_w, ln_b, 1e-6, pos, rope_cache, 64, c1, slots)
+    ref.indexer_k_store(kx, ln_w, ln_b, 1e-6, pos, rope_cache, 64, c2, slots)
+    k1, s1 = ref.indexer_gather(c1, bt[0], 256, D)
+    k2, s2 = ref.indexer_gather(c2, bt[0], 256, D)
+    d1, d2 = k1.float() * s1.unsqueeze(1), k2.float() * s2.unsqueeze(1)
+    assert _rel(d1, d2) < 4e-2
+    assert (s1 == s2).float().mean() > 0.97                   # power-of-two scales: identical except at rounding edges
+    q = torch.randn(T, Hi, D, device="cuda", dtype=torch.bfloat16)
+    q8, qs = k.indexer_q_prep(q, pos, rope_cache, 64)
+    r8, rs = ref.indexer_q_prep(q, pos, rope_cache, 64)
+    assert _rel(q8.float() * qs.unsqueeze(-1), r8.float() * rs.unsqueeze(-1)) < 4e-2
+
+
+@pytest.mark.parametrize("ctxs,q_lens", [([3000, 2500, 2049], [1, 1, 1]), ([2600], [300]), ([4100, 130], [2, 1])])
+def test_indexer_select_matches_reference_topk_sets(k, ctxs, q_lens):
+    """fp8 logits + radix top-k + page translation against the fp32 statement: the selected key sets must agree except
+    for near-ties at the k-th score."""
+    Hi, D, bs, topk = 64, 128, 64, 2048
+    B, bt, cache, rope_cache = _indexer_setup(None, ctxs)
+    # fill the cache with random e4m3 keys and power-of-two scales
+    cache.copy_(torch.randint(0, 255, cache.shape, device="cuda", dtype=torch.uint8))
+    pages = cache.view(cache.shape[0], -1)
+    keys = pages[:, : bs * D]
+    keys[(keys & 0x7F) == 0x7F] = 0x30                                        # no NaN codes
+    sc = torch.exp2(torch.randint(-6, 2, (cache.shape[0], bs), device="cuda").float())
+    pages[:, bs * D:] = sc.contiguous().view(torch.uint8).view(cache.shape[0], bs * 4)
+    T = sum(q_lens)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    cl = torch.tensor(ctxs, dtype=torch.int32, device="cuda")
+    q8 = (torch.randn(T, Hi, D, device="cuda") * 2).to(FP8)
+    qs = torch.exp2(torch.randint(-4, 1, (T, Hi), device="cuda").float())
+    w = torch.randn(T, Hi, device="cuda") * 0.1
+    got = k.indexer_select(q8, qs, w, cache, bt, cu, cl, topk)
+    want = ref.indexer_select(q8, qs, w, cache, bt, cu, cl, topk)
+    assert got.shape == want.shape == (T, topk)
+    for t in range(T):
+        a, b = set(got[t].tolist()) - {-1}, set(want[t].tolist()) - {-1}
+        assert len(a) == len(b)
+        assert len(a & b) >= len(b) - 4, (t, len(a & b), len(b))
