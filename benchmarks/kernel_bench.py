@@ -121,6 +121,22 @@ def case_silu_masked(E=32, rows=32, cap=512, I=2048):
     return fn, E * rows * I * 5, 0.0
 
 
+def case_indexer(B, ctx, q_len=1, Hi=64, D=128, bs=64, topk=2048):
+    """DSA indexer selection: fp8 logits of every visible key + top-2048 + page translation (decode: one token per sequence)."""
+    nb = (ctx + bs - 1) // bs
+    cache = torch.randint(0, 127, (B * nb + 1, bs * (D + 4)), device="cuda", dtype=torch.uint8)
+    cache[:, bs * D:] = torch.ones(B * nb + 1, bs, device="cuda").view(torch.uint8).view(B * nb + 1, bs * 4)
+    bt = torch.arange(B * nb, device="cuda", dtype=torch.int32).view(B, nb)
+    T = B * q_len
+    cu = (torch.arange(B + 1, device="cuda") * q_len).to(torch.int32)
+    cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    q8 = (torch.randn(T, Hi, D, device="cuda")).to(FP8)
+    qs = torch.ones(T, Hi, device="cuda")
+    w = torch.randn(T, Hi, device="cuda")
+    fn = lambda: sm100.indexer_select(q8, qs, w, cache, bt, cu, cl, topk)
+    return fn, B * ctx * (D + 4) + T * ctx * 4 * 2, 2.0 * T * Hi * ctx * D
+
+
 def case_moe_layer(T, E, topk=8, H=7168, I=2048):
     x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
     w13, w2 = rand_fp8(E, 2 * I, H), rand_fp8(E, H, I)
@@ -179,6 +195,9 @@ def build_cases(args):
         "rmsnorm_then_quant": lambda: case_small("rmsnorm_then_quant"),
         "moe_route": lambda: case_small("moe_route"),
         "sample": lambda: case_small("sample"),
+        "indexer_decode_16k": lambda: case_indexer(128, 16384),
+        "indexer_decode_64k": lambda: case_indexer(32, 65536),
+        "indexer_prefill_4k": lambda: case_indexer(1, 8192, q_len=4096),
         "mla_decode": lambda: case_mla(128, args.ctx),
         "mla_decode_small_batch": lambda: case_mla(8, 8192),
         # prefill, 16384 tokens

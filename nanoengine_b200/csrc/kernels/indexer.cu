@@ -5,9 +5,10 @@
 //                   (page = [bs x 128 B keys | bs x fp32 scales]), queries into a dense [rows, 128] buffer + scales.
 //   indexer_logits  logits[t, j] = k_scale[j] * sum_h w[t, h] * relu(q8[t, h, :] . k8[j, :]) for the keys j the token may see.
 //                   One CTA per (token, key split): Q (heads x 128 B) stays in shared memory, key tiles of 128 keys (two pages)
-//                   stream through a TMA ring, S = Q K^T is one group of four tcgen05 MMAs (M = 128, N = 128, K = 32) into a
-//                   double-buffered TMEM accumulator; two epilogue warps apply relu and the head weights and add the 64 head
-//                   rows of every key column with a register transpose-reduce (124 shuffles per 128 columns).
+//                   stream through a TMA ring, S^T = K Q^T is one group of four tcgen05 MMAs (M = 128 keys, N = 64 heads,
+//                   K = 32) into a double-buffered TMEM accumulator.  Keys are the accumulator's rows, so each of the 128
+//                   epilogue threads owns one key, reads its 64 head scores from TMEM and folds relu, head weight and the
+//                   head sum in registers: no cross-lane reduction.
 //   indexer_topk    per token: 3-pass radix select (11 + 11 + 10 bits) of the k largest logits among the visible keys, written
 //                   as physical slot ids (block_table[idx / bs] * bs + idx % bs), -1 padded.
 //
@@ -30,7 +31,7 @@ constexpr int kIdxTile = 128;              // keys per MMA tile (two pages)
 constexpr int kIdxStages = 4;
 constexpr int kIdxQBytes = 128 * 128;      // Q tile slot (only the first `heads` rows are fetched)
 constexpr int kIdxKBytes = kIdxTile * 128;
-constexpr int kIdxSmem = kIdxQBytes + kIdxStages * kIdxKBytes + 1024 + 256 + 2 * 128 * 4;
+constexpr int kIdxSmem = kIdxQBytes + kIdxStages * kIdxKBytes + 1024 + 256 + 64 * 4;
 constexpr int kIdxThreads = 192;
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -130,7 +131,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
   // q_full | k_full[4] | k_empty[4] | s_full[2] | s_empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);        // [2 tile parities][128 columns]
+  float* s_rw = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);          // [64] head weight x query scale
   const uint32_t b_qfull = smem_u32(bars), b_kfull = smem_u32(bars + 1), b_kempty = smem_u32(bars + 5);
   const uint32_t b_sfull = smem_u32(bars + 9), b_sempty = smem_u32(bars + 11);
   const int warp = threadIdx.x >> 5;
@@ -150,12 +151,13 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
   if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
     for (int i = 0; i < kIdxStages; i++) { mbar_init(b_kfull + 8 * i, 1); mbar_init(b_kempty + 8 * i, 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 2); }
+    for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 4); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tq); tma_prefetch_desc(&tk);
   }
-  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 256); tmem_relinquish(); }
+  if (threadIdx.x < 64) s_rw[threadIdx.x] = (int)threadIdx.x < a.heads ? a.head_w[(long long)t * a.heads + threadIdx.x] * a.q_scale[(long long)t * a.heads + threadIdx.x] : 0.f;
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 128); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -177,7 +179,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
     }
   } else if (warp == 1) {
     if (n_tiles > 0 && elect_one()) {
-      constexpr uint32_t kIdesc = make_idesc(FMT_E4M3, FMT_E4M3, 128, kIdxTile);
+      constexpr uint32_t kIdesc = make_idesc(FMT_E4M3, FMT_E4M3, 128, 64);        // M = 128 keys, N = 64 heads
       bool ok = mbar_wait(b_qfull, 0, abort_flag, kKernelIdx, 200);
       for (int i = 0; ok && i < n_tiles; i++) {
         const int sb = i & 1, s = i % kIdxStages;
@@ -187,69 +189,46 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
         const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * kIdxKBytes);
 #pragma unroll
         for (int ks = 0; ks < 4; ks++) {
-          uint64_t adesc = make_smem_desc(qa + ks * 32, 16, 1024, SW_128B);
-          uint64_t bdesc = make_smem_desc(ka + ks * 32, 16, 1024, SW_128B);
-          umma_f8(tmem_base + sb * kIdxTile, adesc, bdesc, kIdesc, ks != 0);
+          uint64_t adesc = make_smem_desc(ka + ks * 32, 16, 1024, SW_128B);
+          uint64_t bdesc = make_smem_desc(qa + ks * 32, 16, 1024, SW_128B);
+          umma_f8(tmem_base + sb * 64, adesc, bdesc, kIdesc, ks != 0);
         }
         tc_commit(b_kempty + 8 * s);
         tc_commit(b_sfull + 8 * sb);
       }
     }
-  } else if (warp >= 4) {
-    // rows 0..63 of the accumulator (TMEM lane quadrants 0 and 1) are the heads of this token
-    const int wq = warp & 3;                                  // 0 or 1
-    const int lane = (int)lane_id();
-    const int row = wq * 32 + lane;
+  } else {
+    // thread = key: TMEM lane quadrant (warp % 4) x lane
+    const int wq = warp & 3, lane = (int)lane_id();
+    const int krow = wq * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    const float rw = row < a.heads ? a.head_w[(long long)t * a.heads + row] * a.q_scale[(long long)t * a.heads + row] : 0.f;
-    // after the transpose-reduce lane l holds the sums of columns cbase .. cbase + 3
-    const int cbase = ((lane >> 4) & 1) * 64 + ((lane >> 3) & 1) * 32 + ((lane >> 2) & 1) * 16 + ((lane >> 1) & 1) * 8 + (lane & 1) * 4;
+    float rw[64];
+#pragma unroll
+    for (int h = 0; h < 64; h++) rw[h] = s_rw[h];
     float* out_row = a.logits + (long long)t * a.ld;
-    bool ok = true;
     for (int i = 0; i < n_tiles; i++) {
       const int sb = i & 1;
-      float v[128];
-      if (ok && !mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelIdx, 300 + sb)) ok = false;
-      if (ok) {
-        tc_fence_after();
+      if (!mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelIdx, 300 + sb)) break;
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * 64, r0);
+      tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * 64 + 32, r1);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b_sempty + 8 * sb);
+      float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * kIdxTile + c * 32, r);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; j++) v[c * 32 + j] = row < a.heads ? fmaxf(__uint_as_float(r[j]), 0.f) * rw : 0.f;
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(b_sempty + 8 * sb);
-        // transpose-reduce over the 32 lanes: every step halves the columns a lane keeps and doubles the rows they cover
-#pragma unroll
-        for (int w = 64, m = 16; w >= 4; w >>= 1, m >>= 1) {
-#pragma unroll
-          for (int j = 0; j < w; j++) {
-            const bool up = (lane & m) != 0;
-            const float send = up ? v[j] : v[j + w];
-            const float keep = up ? v[j + w] : v[j];
-            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, m);
-          }
-        }
-        if (wq == 1) *reinterpret_cast<float4*>(s_part + sb * 128 + cbase) = make_float4(v[0], v[1], v[2], v[3]);
+      for (int h = 0; h < 32; h++) {
+        acc0 = fmaf(fmaxf(__uint_as_float(r0[h]), 0.f), rw[h], acc0);
+        acc1 = fmaf(fmaxf(__uint_as_float(r1[h]), 0.f), rw[32 + h], acc1);
       }
-      asm volatile("bar.sync 2, 64;" ::: "memory");           // the two epilogue warps; executed once per tile whatever happened
-      if (ok && wq == 0) {
-        const float4 o = *reinterpret_cast<const float4*>(s_part + sb * 128 + cbase);
-        const int key0 = (tile_begin + i) * kIdxTile + cbase;
-        const int pg = key0 / kIdxPage;
-        float ks[4] = {0.f, 0.f, 0.f, 0.f};
-        if (key0 <= limit) {
-          const float4 kv = *reinterpret_cast<const float4*>(a.cache + (long long)bt[pg] * a.page_bytes + kIdxPage * kIdxD + (key0 % kIdxPage) * 4);
-          ks[0] = kv.x; ks[1] = kv.y; ks[2] = kv.z; ks[3] = kv.w;
-        }
-        float res[4] = {(v[0] + o.x) * ks[0], (v[1] + o.y) * ks[1], (v[2] + o.z) * ks[2], (v[3] + o.w) * ks[3]};
-#pragma unroll
-        for (int j = 0; j < 4; j++) if (key0 + j > limit) res[j] = -INFINITY;
-        if (key0 < a.ld) *reinterpret_cast<float4*>(out_row + key0) = make_float4(res[0], res[1], res[2], res[3]);
+      const int key = (tile_begin + i) * kIdxTile + krow;
+      if (key < a.ld) {
+        float res = -INFINITY;
+        if (key <= limit)
+          res = (acc0 + acc1) * *reinterpret_cast<const float*>(a.cache + (long long)bt[key / kIdxPage] * a.page_bytes + kIdxPage * kIdxD + (key % kIdxPage) * 4);
+        out_row[key] = res;
       }
     }
   }
@@ -258,7 +237,7 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
   __syncthreads();
   if (*abort_flag && threadIdx.x == 0) for (int i = 0; i < 2000; i++) __nanosleep(1000);
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
