@@ -74,6 +74,7 @@ def main():
     ap.add_argument("--experts-per-gpu", type=int, default=32)
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the device-timed decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
+    ap.add_argument("--profile-prefill", action="store_true", help="bracket the second prompt step instead")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -128,11 +129,16 @@ def main():
     first = True
     while llm.engine.scheduler.num_waiting() > 0 or llm.engine.scheduler.num_prefilling(0) > 0:
         sync()
+        prof = args.profile_prefill and not first and prefill_tok == 0
+        if prof:
+            torch.cuda.profiler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         llm.step()
         e1.record()
         e1.synchronize()
+        if prof:
+            torch.cuda.profiler.stop()
         ntok = llm.engine.scheduler.metrics_summary()["prompt_tokens"]
         if not first:
             prefill_ms += e0.elapsed_time(e1)
