@@ -137,6 +137,20 @@ def case_indexer(B, ctx, q_len=1, Hi=64, D=128, bs=64, topk=2048):
     return fn, B * ctx * (D + 4) + T * ctx * 4 * 2, 2.0 * T * Hi * ctx * D
 
 
+def case_gqa(B, ctx, q_len, Hq, Hkv, D=128, bs=64):
+    nb = (ctx + bs - 1) // bs
+    kc = torch.randn(B * nb + 1, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(B * nb + 1, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    bt = torch.arange(B * nb, device="cuda", dtype=torch.int32).view(B, nb)
+    T = B * q_len
+    q = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    cu = (torch.arange(B + 1, device="cuda") * q_len).to(torch.int32)
+    cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    fn = lambda: sm100_attn.gqa_attention_paged(q, kc, vc, bt, cu, cl, D ** -0.5)
+    causal = ctx - (q_len - 1) / 2.0
+    return fn, B * ctx * Hkv * D * 4 + T * Hq * D * 4, 4.0 * T * Hq * causal * D
+
+
 def case_moe_layer(T, E, topk=8, H=7168, I=2048):
     x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
     w13, w2 = rand_fp8(E, 2 * I, H), rand_fp8(E, H, I)
@@ -198,6 +212,9 @@ def build_cases(args):
         "indexer_decode_16k": lambda: case_indexer(128, 16384),
         "indexer_decode_64k": lambda: case_indexer(32, 65536),
         "indexer_prefill_4k": lambda: case_indexer(1, 8192, q_len=4096),
+        "gqa_decode_tp8": lambda: case_gqa(256, 4352, 1, 8, 1),          # Qwen3-235B per rank at TP8: 8 q heads, 1 kv head
+        "gqa_decode_tp1": lambda: case_gqa(64, 4352, 1, 64, 4),
+        "gqa_prefill_tp8": lambda: case_gqa(4, 4096, 4096, 8, 1),
         "mla_decode": lambda: case_mla(128, args.ctx),
         "mla_decode_small_batch": lambda: case_mla(8, 8192),
         # prefill, 16384 tokens

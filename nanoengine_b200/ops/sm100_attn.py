@@ -89,6 +89,27 @@ def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context
     if T == 0:
         return out
     group = Hq // Hkv
+    if (D == 128 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16 and k_cache.shape[1] == 64 and Hq % Hkv == 0
+            and group <= 128 and group & (group - 1) == 0 and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        # tcgen05 kernel: one CTA per (kv head, tile of 128 (token, head) rows, key slice)
+        q = q.contiguous()
+        tq = 128 // group
+        B = cl.numel()
+        max_tiles = min(T, T // tq + B)
+        S = 1
+        if max_tiles * Hkv < 74:                       # few CTAs (small decode batches): slice the keys
+            S = max(1, min(148 // (max_tiles * Hkv), max(1, bt.shape[1] // 4), 16))
+        part = lse2 = None
+        if S > 1:
+            part = torch.empty(S, T, Hq, D, dtype=torch.float32, device=q.device)
+            lse2 = torch.empty(S, T, Hq, dtype=torch.float32, device=q.device)
+        _k._ck(lib.ne_gqa_bf16(_k._p(q), _k._p(k_cache), _k._p(v_cache), _c.c_int(k_cache.shape[0]), _k._p(bt), _c.c_int(bt.stride(0)), _k._p(cu),
+                               _k._p(cl), _c.c_int(B), _c.c_int(T), _c.c_int(Hq), _c.c_int(Hkv), _c.c_int(max_tiles), _c.c_int(S), _c.c_float(scale),
+                               _k._p(out), _k._p(part), _k._p(lse2), _k._st()), "ne_gqa_bf16")
+        if S > 1:
+            _k._ck(lib.ne_attn_merge(_k._p(part), _k._p(lse2), _k._p(out), _c.c_int(S), _c.c_longlong(T * Hq), _c.c_int(D), _c.c_int(D), _k._st()),
+                   "ne_attn_merge")
+        return out
     assert group % 4 == 0 or group == 1 and Hq % 4 == 0 or Hkv == Hq, "query heads per kv head must be a multiple of 4"
     _k._ck(lib.ne_attn_generic(_k._p(q), _c.c_longlong(q.stride(0)), _c.c_int(q.stride(1)), _k._p(k_cache), _k._p(v_cache),
                                _c.c_longlong(Hkv * D), _c.c_int(D), _c.c_int(group), _k._p(bt), _c.c_int(bt.stride(0)), _c.c_int(k_cache.shape[1]),

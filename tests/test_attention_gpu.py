@@ -89,6 +89,32 @@ def test_gqa_attention(k):
     assert _rel(got, want) < 1e-2
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(16, 1), (8, 1), (64, 4), (4, 4), (32, 2)])
+@pytest.mark.parametrize("q_lens,ctx_lens", [([1], [64]), ([1, 1, 1], [1, 65, 700]), ([2, 3], [130, 257]), ([40, 9, 1], [40, 200, 64]), ([300], [420]), ([1], [2000]), ([1, 2], [3000, 1500])])
+def test_gqa_bf16_tcgen05(k, Hq, Hkv, q_lens, ctx_lens):
+    """The tensor-core GQA kernel (64-token pages, head dim 128) against the fp32 statement: decode, multi-token verify,
+    prefill and chunked prefill, tiles that span several tokens of a sequence, per-row causal limits."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    D, bs = 128, 64
+    B = len(q_lens)
+    nb = [(c + bs - 1) // bs for c in ctx_lens]
+    nblk = sum(nb) + 2
+    kc = torch.randn(nblk, bs, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    vc = torch.randn(nblk, bs, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    perm = (torch.randperm(nblk - 1, device="cuda", generator=g)[: sum(nb)] + 1).to(torch.int32)
+    bt = torch.zeros(B, max(nb), dtype=torch.int32, device="cuda")
+    o = 0
+    for i, n in enumerate(nb):
+        bt[i, :n] = perm[o:o + n]; o += n
+    T = sum(q_lens)
+    q = torch.randn(T, Hq, D, device="cuda", generator=g).to(torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    cl = torch.tensor(ctx_lens, dtype=torch.int32, device="cuda")
+    got = k.gqa_attention_paged(q, kc, vc, bt, cu, cl, D ** -0.5)
+    want = ref.gqa_attention_paged(q, kc, vc, bt, cu, cl, D ** -0.5)
+    assert _rel(got, want) < 1.5e-2, _rel(got, want)
+
+
 def test_sampler(k):
     torch.manual_seed(0)
     logits = torch.randn(6, 129280, device="cuda")
