@@ -58,6 +58,8 @@ class Config:
     cuda_graph_max_bs: int = 256
     executor_backend: str = "auto"           # auto | inproc | mp | spmd (one engine per torchrun rank)
     use_fused_comm: bool = True              # fused compute+collective kernels when peers are reachable
+    peer_timeout_s: float = 120.0            # SPMD: how long the per-step host rendezvous waits for a silent peer
+    kernel_status_every: int = 32            # worker: read the kernels' status words every this many steps (0 = never)
     dummy_eplb: bool = False
     # observability
     log_level: str = "INFO"

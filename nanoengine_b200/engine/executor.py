@@ -24,6 +24,9 @@ class ExecutorError(RuntimeError):
     pass
 
 
+_LEFT_KEY = "nanoengine/ranks_left"
+
+
 class InprocExecutor:
     def __init__(self, config: Config):
         from ..runtime.model_runner import ModelRunner
@@ -204,8 +207,15 @@ class SpmdExecutor:
                 dist.init_process_group("gloo", rank=self.rank, world_size=self.world_size)
         self.runner = ModelRunner(config, self.rank, self.world_size, device=f"cuda:{local}" if use_cuda else "cpu")
         self._host_group = None
+        self._store = None
         if self.world_size > 1:
-            self._host_group = dist.new_group(list(range(self.world_size)), backend="gloo")
+            import datetime
+            self._host_group = dist.new_group(list(range(self.world_size)), backend="gloo",
+                                              timeout=datetime.timedelta(seconds=config.peer_timeout_s))
+            try:
+                self._store = dist.distributed_c10d._get_default_store()
+            except Exception:
+                self._store = None
 
     def collective_rpc(self, method: str, *args, **kw) -> List[Any]:
         return [getattr(self.runner, method)(*args, **kw)]
@@ -215,8 +225,18 @@ class SpmdExecutor:
         if self.world_size == 1:
             return has_work, is_prefill
         import torch.distributed as dist
-        t = torch.tensor([int(has_work), int(is_prefill)], dtype=torch.int32)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self._host_group)
+        # Failure detection happens here, on the host and before anything is launched: a rank that left announced it in the
+        # job's store; one that died silently makes the rendezvous fail or run into the group's timeout.  Either way this
+        # rank stops stepping with an error instead of entering device collectives its peer will never join.
+        try:
+            if self._store is not None and int(self._store.add(_LEFT_KEY, 0)) > 0:
+                raise ExecutorError("a peer rank has left the job")
+            t = torch.tensor([int(has_work), int(is_prefill)], dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self._host_group)
+        except ExecutorError:
+            raise
+        except Exception as e:
+            raise ExecutorError(f"a peer rank stopped answering the per-step rendezvous: {e}") from e
         return bool(t[0]), bool(t[1])
 
     def min_over_ranks(self, v: int) -> int:
@@ -231,6 +251,14 @@ class SpmdExecutor:
         return [self.runner.run_from_bytes(blobs[0])]
 
     def shutdown(self):
+        """Leaves between steps (nothing of this rank is in flight) and says so, so the peers stop at their next rendezvous."""
+        if self.runner is not None and self._store is not None:
+            try:
+                if torch.cuda.is_available() and self.runner.device.type == "cuda":
+                    torch.cuda.synchronize(self.runner.device)
+                self._store.add(_LEFT_KEY, 1)
+            except Exception:
+                pass
         self.runner = None
 
 

@@ -264,6 +264,21 @@ class ModelRunner:
         pp_send(h, res, d.pp_neighbor(+1))
         return None
 
+    def _check_kernel_status(self) -> None:
+        """Every bounded device wait that gives up (a flag nobody raised, an mbarrier that never completed) leaves a code in
+        the kernels' status words.  They are read here, right after the step's token copy already synchronised the stream,
+        every `kernel_status_every` steps; a non-zero code stops the worker with an error instead of serving wrong tokens."""
+        every = self.config.kernel_status_every
+        if self.device.type != "cuda" or every <= 0:
+            return
+        self._status_steps = getattr(self, "_status_steps", 0) + 1
+        if self._status_steps % every:
+            return
+        from ..ops import sm100
+        st = sm100.kernel_status()
+        if st[0] != 0:
+            raise RuntimeError(f"a device wait timed out (kernel status {list(st)}): a peer GPU stopped answering or a kernel lost a hand-shake")
+
     # ---- file-backed KV tier (one store per worker: every rank persists its own shard of a block) ----
     def l3_open(self, root: str, capacity_blocks: int = 0) -> int:
         from .l3_store import L3Store
@@ -321,6 +336,7 @@ class ModelRunner:
         lps = lp.tolist() if lp is not None else None
         self.d2h_bytes += tok.numel() * tok.element_size() + (lp.numel() * 4 if lp is not None else 0)
         self.timer.stop()
+        self._check_kernel_status()
         if not ctx.is_prefill:
             self._last_decode = (ctx, temps)
         ids = [s for s, m in zip(b.seq_ids, mask) if m]

@@ -80,3 +80,57 @@ def test_pp2_prefill_pipeline_matches_single_stage():
             llm.shutdown()
 
     assert firsts(Config(**base, pp=2)) == firsts(Config(**base))
+
+
+def _spmd_peer(rank, world, port, mode, q):
+    """One SPMD rank on CPU (gloo).  Rank 1 leaves after two steps: politely (mode 'leave') or by dying ('die')."""
+    import os
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    try:
+        from nanoengine_b200.engine.executor import ExecutorError
+        cfg = Config(model="tiny-deepseek-v3", dtype="float32", device="cpu", kvcache_block_size=16, max_num_seqs=4, num_kvcache_blocks=64,
+                     attention_dp=world, ffn_ep=world, executor_backend="spmd", peer_timeout_s=8.0, seed=rank)
+        llm = LLM(cfg)
+        llm.add_request(_prompts(1, 12, 5 + rank, 1024)[0], SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True))
+        steps = 0
+        try:
+            while steps < 40:
+                llm.step()
+                steps += 1
+                if rank == 1 and steps == 2:
+                    if mode == "die":
+                        os._exit(0)                   # no goodbye: the peer has to notice by itself
+                    llm.shutdown()                    # between steps, nothing in flight: announce and go
+                    q.put((rank, "left", steps))
+                    return
+            q.put((rank, "finished", steps))
+        except ExecutorError as e:
+            q.put((rank, "peer-lost", steps, str(e)))
+    except Exception as e:
+        import traceback
+        q.put((rank, "error", f"{e}\n{traceback.format_exc()}"))
+
+
+@pytest.mark.parametrize("mode", ["leave", "die"])
+def test_spmd_rank_loss_is_detected_on_the_host(mode):
+    """Failure detection without touching a GPU: the surviving rank must stop with an error at its next per-step
+    rendezvous (announced departure: at once; silent death: connection error or the rendezvous timeout), never hang."""
+    import socket
+    import time
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_spmd_peer, args=(r, 2, port, mode, q)) for r in range(2)]
+    t0 = time.time()
+    for p in ps:
+        p.start()
+    want = 2 if mode == "leave" else 1
+    res = [q.get(timeout=120) for _ in range(want)]
+    for p in ps:
+        p.join(timeout=60)
+    by_rank = {r[0]: r for r in res}
+    assert by_rank[0][1] == "peer-lost", by_rank
+    assert 2 <= by_rank[0][2] <= 4                       # it noticed within a step or two
+    assert time.time() - t0 < 100
