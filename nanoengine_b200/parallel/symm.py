@@ -34,6 +34,10 @@ class SymmetricHeap:
     """Collective constructor: every rank of `group` must create the heap with the same size, in the same order."""
 
     def __init__(self, nbytes: int, group=None, device=None):
+        import os
+        # This package only issues plain peer loads / stores, never multimem instructions, so the heap is not bound to an
+        # NVLink multicast object: a rank that goes away while bound to one disturbs the GPUs of the ranks that stay.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())

@@ -55,3 +55,42 @@ def summarize_kernels(path: str, top: int = 30) -> List[tuple]:
             tot[e["name"]] += e.get("dur", 0.0)
             cnt[e["name"]] += 1
     return sorted(((n, cnt[n], t) for n, t in tot.items()), key=lambda x: -x[2])[:top]
+
+
+def compact_stream_lanes(path: str, out_path: str, min_group: int = 4) -> int:
+    """Fold the stream lanes a CUDA-graph replay produces into one lane per role.
+
+    A replayed graph with fork / join branches (the shared-expert side stream of every MoE layer) shows up in a profiler
+    trace as one stream lane per branch instance.  Lanes of one process whose kernels have the same name histogram are
+    copies of the same branch; when at least `min_group` lanes share a histogram their events are mapped onto the
+    lowest-numbered lane of the group.  Returns the number of lanes removed.
+    Parity: reference utils/trace_compactor.py:9-85 (StreamLaneCompactor)."""
+    data = _load(path)
+    evs = data.get("traceEvents", [])
+    hist: Dict[tuple, Dict[str, int]] = defaultdict(lambda: defaultdict(int))
+    for e in evs:
+        if e.get("cat") == "kernel" and e.get("ph") == "X" and "pid" in e and "tid" in e:
+            hist[(e["pid"], e["tid"])][str(e.get("name", ""))] += 1
+    groups: Dict[tuple, list] = defaultdict(list)
+    for (pid, tid), h in hist.items():
+        groups[(pid, tuple(sorted(h.items())))].append(tid)
+    remap, removed = {}, 0
+    for (pid, _), tids in groups.items():
+        if len(tids) < min_group:
+            continue
+        keep = min(tids, key=lambda t: (str(type(t)), t))
+        for t in tids:
+            if t != keep:
+                remap[(pid, t)] = keep
+                removed += 1
+    out = []
+    for e in evs:
+        key = (e.get("pid"), e.get("tid"))
+        if key in remap:
+            if e.get("ph") == "M":
+                continue                     # metadata of a folded lane
+            e = dict(e, tid=remap[key])
+        out.append(e)
+    with open(out_path, "w") as f:
+        json.dump({**{k: v for k, v in data.items() if k != "traceEvents"}, "traceEvents": out}, f)
+    return removed

@@ -81,3 +81,19 @@ def test_checkpoint_roundtrip_bf16_and_fp8_and_weight_update(tmp_path):
     other = LLM(Config(model=str(ck2), **base))
     assert from_disk.update_weights(str(ck2)) > 0
     assert _gen(from_disk, prompt) == _gen(other, prompt)
+
+
+def test_graph_branch_lanes_are_folded(tmp_path):
+    from nanoengine_b200.utils.trace_merger import compact_stream_lanes
+    evs = [{"ph": "M", "name": "thread_name", "pid": 1, "tid": t, "args": {"name": f"stream {t}"}} for t in range(7, 13)]
+    for t in range(7, 12):                               # five copies of the same branch: gate_up GEMM, SwiGLU, down GEMM
+        for i, n in enumerate(["gemm", "silu", "gemm"]):
+            evs.append({"ph": "X", "cat": "kernel", "name": n, "pid": 1, "tid": t, "ts": 100 * t + 10 * i, "dur": 5})
+    evs.append({"ph": "X", "cat": "kernel", "name": "mla", "pid": 1, "tid": 12, "ts": 5, "dur": 50})      # the main stream
+    src, dst = tmp_path / "t.json", tmp_path / "c.json"
+    src.write_text(json.dumps({"traceEvents": evs}))
+    assert compact_stream_lanes(str(src), str(dst)) == 4
+    out = json.load(open(dst))["traceEvents"]
+    kernels = [e for e in out if e.get("ph") == "X"]
+    assert len(kernels) == 16 and {e["tid"] for e in kernels} == {7, 12}
+    assert sum(1 for e in out if e.get("ph") == "M") == 2
