@@ -218,26 +218,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab);
       int stage = 0; uint32_t phase = 0; int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
       bool ok = true;
+      // A test of an mbarrier costs ~150 cycles even when the phase has long completed, and this thread is the serial
+      // resource of the CTA.  So the barriers of the NEXT K block are tested before the MMAs of the current one are issued
+      // (the issue blocks for about as long as the MMAs run, which hides the test); only a failed test falls back to waiting.
+      bool pre_full = mbar_test(full0 + 8 * stage, phase);
+      bool pre_te = mbar_test(tempty0 + 8 * buf, bphase ^ 1);
       for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
         if (!kBlockScaled) {
-          if (!mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 200 + buf)) { ok = false; break; }
+          if (!pre_te && !mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 200 + buf)) { ok = false; break; }
           tc_fence_after();
         }
         // the activation box of this tile (see the producer): its K blocks sit a_kstride apart inside the stage
         const int rows_here = sched.rows(grp) - mb * kBlockM;
         const uint32_t a_kstride = rows_here <= 32 ? 32 * kKBytes : (rows_here <= 64 ? 64 * kKBytes : S::kABytes);
         for (int st = 0; st < num_st && ok; st++) {
-          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, kKernelGemm, 300 + stage)) { ok = false; break; }
+          if (!pre_full && !mbar_wait(full0 + 8 * stage, phase, abort_flag, kKernelGemm, 300 + stage)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = smem_base + stage * S::kStageBytes, b_base = a_base + kG * S::kABytes;
+          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
+          const uint32_t nphase = stage + 1 == kStages ? phase ^ 1 : phase;
 #pragma unroll
           for (int g = 0; g < kG; g++) {
             const int kb = st * kG + g;
             if (kb >= num_kb) break;
             if (kBlockScaled) {
-              if (!mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 210 + buf)) { ok = false; break; }
+              if (!pre_te && !mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 210 + buf)) { ok = false; break; }
               tc_fence_after();
             }
+            // tests for what comes next, issued ahead of this K block's MMAs
+            if (kBlockScaled) {
+              const int nbuf = buf + 1 == kAcc ? 0 : buf + 1;
+              pre_te = mbar_test(tempty0 + 8 * nbuf, (buf + 1 == kAcc ? bphase ^ 1 : bphase) ^ 1);
+            }
+            if (g == kG - 1 || kb + 1 >= num_kb) pre_full = mbar_test(full0 + 8 * nstage, nphase);
             uint64_t adesc = make_smem_desc(a_base + g * a_kstride, 16, 1024, SW_128B);
             uint64_t bdesc = make_smem_desc(b_base + g * S::kBBytes, 16, 1024, SW_128B);
             uint32_t d = tmem_base + buf * BLOCK_N;
@@ -254,7 +267,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        if (!kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == kAcc) { buf = 0; bphase ^= 1; } }
+        if (!kBlockScaled) {
+          tc_commit(tfull0 + 8 * buf);
+          if (++buf == kAcc) { buf = 0; bphase ^= 1; }
+          pre_te = mbar_test(tempty0 + 8 * buf, bphase ^ 1);
+        }
       }
     }
   } else {
@@ -266,6 +283,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab);
     int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
     bool ok = true;
+    bool pre_tf = false;                               // result of an early test of the next accumulator's "full" barrier
     for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
       const bool row_ok = mb * kBlockM + row_in_tile < sched.rows(grp);
       const int row = sched.row0(grp) + mb * kBlockM + row_in_tile;      // row inside the group's (or the flat) matrix
@@ -293,7 +311,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         for (int jj = 0; jj < kPf; jj++) {
           if (kb0 + jj >= num_kb || !ok) break;
           const float s = cur[jj];
-          if (!mbar_wait(tfull0 + 8 * buf, bphase, abort_flag, kKernelGemm, 400 + buf)) { ok = false; break; }
+          if (!pre_tf && !mbar_wait(tfull0 + 8 * buf, bphase, abort_flag, kKernelGemm, 400 + buf)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < kCols / 32; c += 2) {
@@ -301,6 +319,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t r0[32], r1[32];
             tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + cbase + c * 32, r0);
             if (c + 1 < kCols / 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + cbase + (c + 1) * 32, r1);
+            // the next accumulator's barrier is tested while the loads and the promotion of this one are in flight
+            if (c == 0) pre_tf = mbar_test(tfull0 + 8 * (buf + 1 == kAcc ? 0 : buf + 1), buf + 1 == kAcc ? bphase ^ 1 : bphase);
             tc_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; j++) acc[c * 32 + j] = fmaf(s, __uint_as_float(r0[j]), acc[c * 32 + j]);

@@ -134,10 +134,15 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
         tc_commit(b_pempty + 8 * (j & 1));
         return true;
       };
+      // the barriers that gate S(i+1) are tested before the MMAs of S(i) are issued: a test costs ~150 cycles even when the
+      // phase completed long ago, and issuing MMAs blocks for about as long as they run, which hides it
+      bool pre_se = true, pre_kv = mbar_test(b_kvfull, 0);
       for (int i = 0; ok && i < n_tiles; i++) {
         const int sb = i & 1, s = i % kGStages;
-        if (!mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelGqa, 210 + sb)) { ok = false; break; }
-        if (!mbar_wait(b_kvfull + 8 * s, (i / kGStages) & 1, abort_flag, kKernelGqa, 220 + s)) { ok = false; break; }
+        if (!pre_se && !mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelGqa, 210 + sb)) { ok = false; break; }
+        if (!pre_kv && !mbar_wait(b_kvfull + 8 * s, (i / kGStages) & 1, abort_flag, kKernelGqa, 220 + s)) { ok = false; break; }
+        pre_se = mbar_test(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1);
+        pre_kv = mbar_test(b_kvfull + 8 * ((i + 1) % kGStages), ((i + 1) / kGStages) & 1);
         tc_fence_after();
         const uint32_t kt = smem_u32(sKV + s * 2 * kGKBytes);
         const uint32_t d = tmem_base + sb * kGPage;
@@ -164,9 +169,10 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
     const int limit = row_ok ? base_limit + tl : -1;          // this row's last visible key
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+    bool s_ready = false;                            // early test of the next page's S buffer
     for (int i = 0; ok && i < n_tiles; i++) {
       const int sb = i & 1;
-      if (!mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelGqa, 300 + sb)) { ok = false; break; }
+      if (!s_ready && !mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelGqa, 300 + sb)) { ok = false; break; }
       tc_fence_after();
       uint32_t r0[32], r1[32];
       tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * kGPage, r0);
@@ -176,6 +182,7 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
       __syncwarp();
       if (lane_id() == 0) mbar_arrive(b_sempty + 8 * sb);
       const int key0 = (pg_begin + i) * kGPage;
+      const bool p_free = i < 2 || mbar_test(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1);     // needed only after the math
       if (key0 + kGPage - 1 > limit) {
 #pragma unroll
         for (int j = 0; j < 32; j++) {
@@ -183,10 +190,13 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
           if (key0 + 32 + j > limit) r1[j] = 0xff800000u;
         }
       }
-      float m_tile = -INFINITY;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int j = 0; j < 32; j++) m_tile = fmaxf(m_tile, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
-      m_tile *= a.scale_log2;
+      for (int j = 0; j < 32; j += 2) {
+        mx[0] = fmaxf(mx[0], __uint_as_float(r0[j])); mx[1] = fmaxf(mx[1], __uint_as_float(r0[j + 1]));
+        mx[2] = fmaxf(mx[2], __uint_as_float(r1[j])); mx[3] = fmaxf(mx[3], __uint_as_float(r1[j + 1]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;
       // lazy rescaling: the reference maximum only moves when the page's maximum exceeds it by more than 2^8
       const bool first_valid = (m_run == -INFINITY);
       const float m_new = (first_valid || m_tile > m_run + 8.f) ? fmaxf(m_run, m_tile) : m_run;
@@ -220,7 +230,8 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
         }
         tc_wait_st();
       }
-      if (i > 1 && !mbar_wait(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1, abort_flag, kKernelGqa, 311)) { ok = false; break; }
+      if (!p_free && !mbar_wait(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1, abort_flag, kKernelGqa, 311)) { ok = false; break; }
+      s_ready = mbar_test(b_sfull + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1);
       // P row (64 bf16 = 8 chunks of 16 bytes) into the 128B-swizzled K-major layout the MMA reads
       {
         uint8_t* prow = sP + (i & 1) * kGPBytes + row * 128;

@@ -181,10 +181,15 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
     if (n_tiles > 0 && elect_one()) {
       constexpr uint32_t kIdesc = make_idesc(FMT_E4M3, FMT_E4M3, 128, 64);        // M = 128 keys, N = 64 heads
       bool ok = mbar_wait(b_qfull, 0, abort_flag, kKernelIdx, 200);
+      // the next tile's barriers are tested before this tile's MMAs are issued (a test costs ~150 cycles even when the phase
+      // completed long ago; the blocking MMA issue hides it)
+      bool pre_se = true, pre_k = mbar_test(b_kfull, 0);
       for (int i = 0; ok && i < n_tiles; i++) {
         const int sb = i & 1, s = i % kIdxStages;
-        if (!mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelIdx, 210 + sb)) break;
-        if (!mbar_wait(b_kfull + 8 * s, (i / kIdxStages) & 1, abort_flag, kKernelIdx, 220 + s)) break;
+        if (!pre_se && !mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelIdx, 210 + sb)) break;
+        if (!pre_k && !mbar_wait(b_kfull + 8 * s, (i / kIdxStages) & 1, abort_flag, kKernelIdx, 220 + s)) break;
+        pre_se = mbar_test(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1);
+        pre_k = mbar_test(b_kfull + 8 * ((i + 1) % kIdxStages), ((i + 1) / kIdxStages) & 1);
         tc_fence_after();
         const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * kIdxKBytes);
 #pragma unroll
@@ -206,13 +211,15 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
 #pragma unroll
     for (int h = 0; h < 64; h++) rw[h] = s_rw[h];
     float* out_row = a.logits + (long long)t * a.ld;
+    bool s_ready = false;
     for (int i = 0; i < n_tiles; i++) {
       const int sb = i & 1;
-      if (!mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelIdx, 300 + sb)) break;
+      if (!s_ready && !mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelIdx, 300 + sb)) break;
       tc_fence_after();
       uint32_t r0[32], r1[32];
       tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * 64, r0);
       tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * 64 + 32, r1);
+      s_ready = mbar_test(b_sfull + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1);      // answer wanted at the next loop top
       tc_wait_ld();
       tc_fence_before();
       __syncwarp();

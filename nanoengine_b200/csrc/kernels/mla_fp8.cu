@@ -7,7 +7,7 @@
 // Per 64-token page:  S = Q K^T   (18 x tcgen05.mma kind::f8f6f4, M=128 N=64 K=32, both operands K-major in smem)
 //                     online softmax by 128 threads (one per head) reading S from TMEM; P -> e4m3 -> smem
 //                     O += P V    (2 x tcgen05.mma, V is the same page tile read MN-major, N=256)
-// TMEM: S double-buffered (2 x 64 columns) + O (256 columns).  Shared memory: Q 72 KB, 4-page ring 144 KB, P 8 KB.
+// TMEM: S double-buffered (2 x 64 columns) + O (256 columns).  Shared memory: Q 72 KB, 3-page ring 108 KB, P 2 x 8 KB.
 // Warp 0: TMA producer; warp 1: MMA issuer; warps 2-5: softmax / rescale / epilogue.  All waits are bounded.
 // With more than one key slice the CTA writes a normalised partial result and its log2-sum-exp; ne_attn_merge folds them.
 //
@@ -122,10 +122,16 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
         tc_commit(b_pempty + 8 * (j & 1));
         return true;
       };
+      // An mbarrier test costs ~150 cycles even when the phase completed long ago and this thread is the serial resource of
+      // the CTA, so the two barriers that gate S(i+1) are tested before the MMAs of P V(i-1) / S(i) are issued (issuing blocks
+      // for about as long as the MMAs run); only a failed test falls back to waiting.
+      bool pre_se = true, pre_pg = mbar_test(b_pgfull, 0);
       for (int i = 0; ok && i < n_tiles; i++) {
         const int sb = i & 1, s = i % kPgStages;
-        if (!mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelMla, 210 + sb)) { ok = false; break; }
-        if (!mbar_wait(b_pgfull + 8 * s, (i / kPgStages) & 1, abort_flag, kKernelMla, 220 + s)) { ok = false; break; }
+        if (!pre_se && !mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelMla, 210 + sb)) { ok = false; break; }
+        if (!pre_pg && !mbar_wait(b_pgfull + 8 * s, (i / kPgStages) & 1, abort_flag, kKernelMla, 220 + s)) { ok = false; break; }
+        pre_se = mbar_test(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1);
+        pre_pg = mbar_test(b_pgfull + 8 * ((i + 1) % kPgStages), ((i + 1) / kPgStages) & 1);
         tc_fence_after();
         const uint32_t pg = smem_u32(sPg + s * kPgBytes);
         const uint32_t d = tmem_base + sb * kPage;
@@ -156,9 +162,10 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
     const bool row_ok = row < a.H;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+    bool s_ready = false;                            // early test of the next page's S buffer (see below)
     for (int i = 0; ok && i < n_tiles; i++) {
       const int sb = i & 1;
-      if (!mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelMla, 300 + sb)) { ok = false; break; }
+      if (!s_ready && !mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelMla, 300 + sb)) { ok = false; break; }
       tc_fence_after();
       uint32_t r0[32], r1[32];
       tmem_ld_32x32b_x32(tmem_base + lane_addr + sb * kPage, r0);
@@ -168,30 +175,44 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
       __syncwarp();
       if (lane_id() == 0) mbar_arrive(b_sempty + 8 * sb);
       const int key0 = (pg_begin + i) * kPage;
-      float tl[64];
-      float m_tile = -INFINITY;
+      // this page's P buffer was last read by the P V product of page i-2: tested here, long before the answer is needed
+      // (an mbarrier test costs ~150 cycles even when the phase completed long ago)
+      const bool p_free = i < 2 || mbar_test(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1);
+      if (!row_ok || key0 + kPage - 1 > limit) {                 // only the page that straddles the causal limit needs masking
 #pragma unroll
-      for (int j = 0; j < 64; j++) {
-        float s = __uint_as_float(j < 32 ? r0[j] : r1[j - 32]) * a.scale_log2;
-        tl[j] = (row_ok && key0 + j <= limit) ? s : -INFINITY;
-        m_tile = fmaxf(m_tile, tl[j]);
+        for (int j = 0; j < 32; j++) {
+          if (!row_ok || key0 + j > limit) r0[j] = 0xff800000u;
+          if (!row_ok || key0 + 32 + j > limit) r1[j] = 0xff800000u;
+        }
       }
+      // four independent chains for the maximum; the (positive) scale is applied once at the end
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        mx[0] = fmaxf(mx[0], __uint_as_float(r0[j])); mx[1] = fmaxf(mx[1], __uint_as_float(r0[j + 1]));
+        mx[2] = fmaxf(mx[2], __uint_as_float(r1[j])); mx[3] = fmaxf(mx[3], __uint_as_float(r1[j + 1]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;
       // Lazy rescaling: the reference maximum only moves when the page's maximum exceeds it by more than 2^8.  Until then
       // probabilities may be as large as 256 (inside e4m3's range, same relative precision) and O needs no correction;
       // the result is exact because l_run is accumulated against the same reference.
       const bool first_valid = (m_run == -INFINITY);
       const float m_new = (first_valid || m_tile > m_run + 8.f) ? fmaxf(m_run, m_tile) : m_run;
       const float alpha = (m_new == -INFINITY || first_valid) ? 1.f : exp2f(m_run - m_new);
-      float psum = 0.f;
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;      // masked scores are -inf and come out as 0 either way
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[16];
 #pragma unroll
-      for (int j = 0; j < 16; j++) {
-        float p0 = (m_new == -INFINITY) ? 0.f : exp2f(tl[4 * j] - m_new), p1 = (m_new == -INFINITY) ? 0.f : exp2f(tl[4 * j + 1] - m_new);
-        float p2 = (m_new == -INFINITY) ? 0.f : exp2f(tl[4 * j + 2] - m_new), p3 = (m_new == -INFINITY) ? 0.f : exp2f(tl[4 * j + 3] - m_new);
-        psum += (p0 + p1) + (p2 + p3);
+      for (int j = 0; j < 8; j++) {
+        const float p0 = exp2f(fmaf(__uint_as_float(r0[4 * j]), a.scale_log2, neg_m)), p1 = exp2f(fmaf(__uint_as_float(r0[4 * j + 1]), a.scale_log2, neg_m));
+        const float p2 = exp2f(fmaf(__uint_as_float(r0[4 * j + 2]), a.scale_log2, neg_m)), p3 = exp2f(fmaf(__uint_as_float(r0[4 * j + 3]), a.scale_log2, neg_m));
+        const float q0 = exp2f(fmaf(__uint_as_float(r1[4 * j]), a.scale_log2, neg_m)), q1 = exp2f(fmaf(__uint_as_float(r1[4 * j + 1]), a.scale_log2, neg_m));
+        const float q2 = exp2f(fmaf(__uint_as_float(r1[4 * j + 2]), a.scale_log2, neg_m)), q3 = exp2f(fmaf(__uint_as_float(r1[4 * j + 3]), a.scale_log2, neg_m));
+        ps[0] += p0 + p1; ps[1] += p2 + p3; ps[2] += q0 + q1; ps[3] += q2 + q3;
         pk[j] = pack_e4m3x4(p0, p1, p2, p3);
+        pk[8 + j] = pack_e4m3x4(q0, q1, q2, q3);
       }
-      l_run = l_run * alpha + psum;
+      l_run = l_run * alpha + ((ps[0] + ps[1]) + (ps[2] + ps[3]));
       m_run = m_new;
       // O may only be rescaled once the previous page's P V product has retired; that is rare with lazy rescaling
       if (i > 0 && __any_sync(0xffffffffu, alpha < 1.f)) {
@@ -209,7 +230,9 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
         tc_wait_st();
       }
       // this page's P buffer was last read by the P V product of page i-2
-      if (i > 1 && !mbar_wait(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1, abort_flag, kKernelMla, 311)) { ok = false; break; }
+      if (!p_free && !mbar_wait(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1, abort_flag, kKernelMla, 311)) { ok = false; break; }
+      // S of the next page is usually complete by now: test it before the stores so the answer is there at the loop top
+      s_ready = mbar_test(b_sfull + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1);
       // P row (64 e4m3 = 4 chunks of 16 bytes) into the 64B-swizzled K-major layout the MMA reads
       {
         uint8_t* prow = sP + (i & 1) * kPBytes + row * 64;

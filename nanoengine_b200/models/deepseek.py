@@ -90,6 +90,17 @@ class MLAAttention(nn.Module):
         return self.o_proj(o.reshape(T, H * self.v))
 
 
+OVERLAP_SHARED_EXPERTS = True
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device):
+    key = torch.device(device).index
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
 class MoEGate(nn.Module):
     def __init__(self, cfg: ModelConfig, device):
         super().__init__()
@@ -118,9 +129,32 @@ class DeepseekMoE(nn.Module):
 
     def forward(self, x, ctx: ForwardContext):
         from ..parallel.ep import ep_moe_forward
+        if self.shared_experts is None:
+            idx, w = self.gate(x)
+            return ep_moe_forward(self.experts, x, idx, w, ctx, add_in=None)
+        if not (x.is_cuda and OVERLAP_SHARED_EXPERTS):
+            idx, w = self.gate(x)
+            return ep_moe_forward(self.experts, x, idx, w, ctx, add_in=self.shared_experts(x))
+        # The shared expert runs on a side stream next to routing, dispatch and the routed GEMMs (its two small GEMMs leave
+        # most SMs idle, and so do the routing kernels); the main stream joins it right before the combine adds its output.
+        # Works the same eagerly and under CUDA-graph capture (the fork / join become graph edges).
+        # Parity: reference models/deepseek_v2/deepseek_v2.py:560-591 (shared-expert overlap on a side stream).
+        main = torch.cuda.current_stream(x.device)
+        side = _side_stream(x.device)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            shared = self.shared_experts(x)
+            done = torch.cuda.Event()
+            done.record(side)
+
+        def join():
+            main.wait_event(done)
+            return shared
+
         idx, w = self.gate(x)
-        shared = self.shared_experts(x) if self.shared_experts is not None else None
-        return ep_moe_forward(self.experts, x, idx, w, ctx, add_in=shared)
+        return ep_moe_forward(self.experts, x, idx, w, ctx, add_in=join)
 
 
 class DeepseekDecoderLayer(nn.Module):

@@ -276,6 +276,8 @@ def silu_and_mul(x: torch.Tensor, quant: bool = False) -> torch.Tensor:
 def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0, add_in=None) -> torch.Tensor:
     """Routed experts held locally: ids [expert_offset, expert_offset + E_local).  w13 [E, 2I, H], w2 [E, H, I].
     Returns the weighted sum over the local experts of each token (zeros where none is local)."""
+    if callable(add_in):
+        add_in = add_in()
     T, H = x.shape
     E = w13.shape[0]
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)

@@ -372,6 +372,8 @@ def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, exp
         h = torch.empty(R, I, dtype=torch.bfloat16, device=dev)
         _ck(lib().ne_silu_mul(_p(g), _p(h), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(counts), _p(row_start), _c.c_int(E), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
         _gemm(h, I, 0, w2, y, H, 0, R, H, I, E, counts, row_start, False, None, 0, 0, None, False)
+    if callable(add_in):
+        add_in = add_in()          # produced on another stream: the callable joins that stream as late as possible
     _ck(lib().ne_moe_combine_local(_p(y), _p(pos), _p(w), _p(add_in), _p(out), _c.c_int(T), _c.c_int(K), _c.c_int(H), _st()), "ne_moe_combine_local")
     return out
 

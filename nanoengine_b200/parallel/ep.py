@@ -65,4 +65,6 @@ def ep_moe_forward(experts, x, topk_idx, topk_w, ctx=None, add_in=None):
     if x.is_cuda and _FUSED is not None:
         return _FUSED.forward(experts, x, topk_idx, topk_w, ctx, add_in)
     out = ep_moe_allgather(experts, x, topk_idx, topk_w, d.group("ffn_ep"), d.ep_size, d.ep_rank)
+    if callable(add_in):
+        add_in = add_in()
     return out if add_in is None else out + add_in

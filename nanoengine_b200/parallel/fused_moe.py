@@ -119,6 +119,8 @@ class FusedEP:
             _k._gemm(self.h, I, C * I, experts.down_proj, ret_dummy, H, 0, C, H, I, E, self.counts, None, False, None, 0, 0, None, False,
                      row_dst=self.row_dst)
         _k._ck(lib.ne_ep_signal(L, epoch, st), "ne_ep_signal")
+        if callable(add_in):
+            add_in = add_in()      # shared-expert output from the side stream: joined right before it is consumed
         _k._ck(lib.ne_ep_reduce(L, _k._p(self.pair_ok), _k._p(w), _k._p(add_in), _k._p(out), _c.c_int(T), epoch, _c.c_int(self.spin_limit), st),
                "ne_ep_reduce")
         _k._ck(lib.ne_ep_advance(epoch, st), "ne_ep_advance")
