@@ -149,12 +149,19 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const EpLayout L, const 
   for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (s_ok) {
-      for (int k = 0; k < K; k++) {
-        if (!s_use[k]) continue;
-        uint4 v = *reinterpret_cast<const uint4*>(ret + ((long long)t * K + k) * H + c);
-        uint32_t u[4] = {v.x, v.y, v.z, v.w};
+      // eight returned rows are fetched before any is used: the loads are independent and the kernel is latency-bound
+      for (int k0 = 0; k0 < K; k0 += 8) {
+        uint4 v[8];
 #pragma unroll
-        for (int j = 0; j < 4; j++) { float2 f = unpack_bf16x2(u[j]); acc[2 * j] += s_w[k] * f.x; acc[2 * j + 1] += s_w[k] * f.y; }
+        for (int q = 0; q < 8; q++)
+          v[q] = (k0 + q < K && s_use[k0 + q]) ? *reinterpret_cast<const uint4*>(ret + ((long long)t * K + k0 + q) * H + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+          const float wk = (k0 + q < K && s_use[k0 + q]) ? s_w[k0 + q] : 0.f;
+          const uint32_t u[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) { float2 f = unpack_bf16x2(u[j]); acc[2 * j] += wk * f.x; acc[2 * j + 1] += wk * f.y; }
+        }
       }
     }
     if (add_in) {

@@ -118,11 +118,19 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpLayout L, const 
   for (int c = threadIdx.x * 8; c < L.H; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (s_ok) {
-      for (int s = 0; s < L.world; s++) {
-        const uint4 v = *reinterpret_cast<const uint4*>(tp_ptr(L, L.rank, stage_off(L, parity, s, row) + (long long)c * 2));
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+      // the partials of eight sources are fetched before any is added: independent loads, latency-bound kernel
+      for (int s0 = 0; s0 < L.world; s0 += 8) {
+        uint4 v[8];
 #pragma unroll
-        for (int j = 0; j < 4; j++) { const float2 f = unpack_bf16x2(u[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        for (int q = 0; q < 8; q++)
+          v[q] = s0 + q < L.world ? *reinterpret_cast<const uint4*>(tp_ptr(L, L.rank, stage_off(L, parity, s0 + q, row) + (long long)c * 2))
+                                  : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+          const uint32_t u[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) { const float2 f = unpack_bf16x2(u[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        }
       }
     }
     if (add_in) {

@@ -41,6 +41,7 @@ struct GemmArgs {
   const int* row_start;                 // contiguous mode: group g owns rows [row_start[g], row_start[g] + masked_m[g]) of one
                                         // flat [M, K] activation matrix (starts are multiples of 128); nullptr = [groups, M, K]
   int a_group_inner;                    // A is stored [rows, groups, K]: TMA coordinates are (k, group, row)
+  int k_flat;                           // K in bytes is not a multiple of 128: K stays the maps' innermost dimension (zero-filled tail), one TMA per K block
   void* D; long long ldd; long long d_group_stride;   // in elements
   const float* sa; int sa_ld; long long sa_group_stride;   // activation scales [groups][K/128][sa_ld]
   const float* sb; long long sb_group_stride;              // weight scales [groups][ceil(N/128)][K/128]
@@ -205,9 +206,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint32_t a_dst = smem_base + stage * S::kStageBytes, b_dst = a_dst + kG * S::kABytes;
           mbar_expect_tx(full0 + 8 * stage, kG * (a_bytes + S::kBBytes));      // chunks past the end of K arrive as zeros
           const int kc = kb_begin + st * kG;
-          if (args.a_group_inner) tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, grp, mb * kBlockM, kc);
-          else tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, kc);
-          tma_load_4d(b_dst, &tmap_b, full0 + 8 * stage, 0, nb * BLOCK_N, grp, kc);
+          if (!args.k_flat) {
+            if (args.a_group_inner) tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, grp, mb * kBlockM, kc);
+            else tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, kc);
+            tma_load_4d(b_dst, &tmap_b, full0 + 8 * stage, 0, nb * BLOCK_N, grp, kc);
+          } else {
+#pragma unroll
+            for (int g = 0; g < kG; g++) {
+              const int kx = (kc + g) * kElemsPerStageK;           // past the end of K: the whole box is zero-filled
+              if (args.a_group_inner) tma_load_4d(a_dst + g * a_bytes, ta, full0 + 8 * stage, kx, grp, mb * kBlockM, 0);
+              else tma_load_4d(a_dst + g * a_bytes, ta, full0 + 8 * stage, kx, sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, 0);
+              tma_load_4d(b_dst + g * S::kBBytes, &tmap_b, full0 + 8 * stage, kx, nb * BLOCK_N, grp, 0);
+            }
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -472,14 +483,16 @@ struct TmapKeyHash {
 // stride, which the encoder accepts.
 static int get_tmap_kmajor(CUtensorMap* out, const void* base, bool fp8, uint64_t K, uint64_t rows, uint64_t groups,
                            uint64_t row_stride_elems, uint64_t group_stride_elems, uint32_t box_rows, int kg) {
+  const bool flat = (K * (fp8 ? 1 : 2)) % kKBytes != 0;       // see GemmArgs::k_flat
+  if (flat) kg = 1;
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   const uint64_t es = fp8 ? 1 : 2;
-  TmapKey key{base, K, rows, groups, row_stride_elems * es, group_stride_elems * es, (uint32_t)(kKBytes / es), box_rows | ((uint32_t)kg << 16), fp8 ? TMA_U8 : TMA_BF16};
+  TmapKey key{base, K, rows, groups, row_stride_elems * es, group_stride_elems * es, (uint32_t)(kKBytes / es), box_rows | ((uint32_t)kg << 16) | (flat ? 1u << 24 : 0u), fp8 ? TMA_U8 : TMA_BF16};
   std::lock_guard<std::mutex> lk(mu);
   auto it = cache.find(key);
   if (it != cache.end()) { *out = it->second; return 0; }
-  uint64_t dims[4] = {kKBytes / es, rows, groups, K * es / kKBytes};
+  uint64_t dims[4] = {flat ? K : kKBytes / es, rows, groups, flat ? 1 : K * es / kKBytes};
   uint64_t strides[3] = {row_stride_elems * es, group_stride_elems * es, (uint64_t)kKBytes};
   uint32_t box[4] = {(uint32_t)(kKBytes / es), box_rows, 1, (uint32_t)kg};
   if (groups > 1 && group_stride_elems < row_stride_elems) {
@@ -572,7 +585,7 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
                        long long sa_gs, const float* sb, int out_fp32, int block_n_hint, const long long* row_dst, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
   const bool fp8 = dtype == 1;
-  if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % kKBytes != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
+  if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % 16 != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
   if (fp8 && (K % 128 != 0 || !sa || !sb)) return 1002;
   if ((ldd * (out_fp32 ? 4 : 2)) % 16 != 0) return 1003;
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
@@ -618,6 +631,7 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
   if (rc) return 3000 + rc;
   GemmArgs a;
   a.a_group_inner = (!row_start && groups > 1 && a_gs < lda) ? 1 : 0;
+  a.k_flat = (K * (fp8 ? 1 : 2)) % kKBytes != 0 ? 1 : 0;
   a.M = M; a.N = N; a.K = K; a.groups = groups; a.masked_m = masked_m; a.row_start = row_start; a.D = D; a.ldd = ldd; a.d_group_stride = d_gs;
   if (row_start) { a.d_group_stride = 0; sa_gs = 0; if (!masked_m) return 1004; }
   a.sa = sa; a.sa_ld = sa_ld; a.sa_group_stride = sa_gs; a.sb = sb;

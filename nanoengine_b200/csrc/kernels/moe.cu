@@ -237,13 +237,21 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
   __syncthreads();
   for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int k = 0; k < top_k; k++) {
-      int r = s_pos[k];
-      if (r < 0) continue;
-      uint4 v = *reinterpret_cast<const uint4*>(y + (long long)r * H + c);
-      uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    // eight expert rows are fetched before any is used: the loads are independent and the kernel is latency-bound
+    for (int k0 = 0; k0 < top_k; k0 += 8) {
+      uint4 v[8];
 #pragma unroll
-      for (int j = 0; j < 4; j++) { float2 f = unpack_bf16x2(u[j]); acc[2 * j] += s_w[k] * f.x; acc[2 * j + 1] += s_w[k] * f.y; }
+      for (int q = 0; q < 8; q++) {
+        const int r = k0 + q < top_k ? s_pos[k0 + q] : -1;
+        v[q] = r >= 0 ? *reinterpret_cast<const uint4*>(y + (long long)r * H + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        const float wk = k0 + q < top_k ? s_w[k0 + q] : 0.f;
+        const uint32_t u[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) { float2 f = unpack_bf16x2(u[j]); acc[2 * j] += wk * f.x; acc[2 * j + 1] += wk * f.y; }
+      }
     }
     if (add_in) {
       // the routed sum is rounded to bf16 before the shared-expert output is added, as in the unfused form

@@ -21,7 +21,8 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (7, 576, 512), (128, 2112, 7168), (300, 7168, 2048), (1000, 1536, 1536), (4096, 4096, 4096)])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (7, 576, 512), (128, 2112, 7168), (300, 7168, 2048), (1000, 1536, 1536), (4096, 4096, 4096),
+                                   (7, 64, 32), (100, 256, 96), (130, 128, 200)])     # the last three: K not a multiple of 128 bytes
 def test_gemm_bf16(k, M, N, K):
     torch.manual_seed(0)
     x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
