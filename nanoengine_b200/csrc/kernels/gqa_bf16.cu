@@ -141,8 +141,8 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
         const int sb = i & 1, s = i % kGStages;
         if (!pre_se && !mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelGqa, 210 + sb)) { ok = false; break; }
         if (!pre_kv && !mbar_wait(b_kvfull + 8 * s, (i / kGStages) & 1, abort_flag, kKernelGqa, 220 + s)) { ok = false; break; }
-        pre_se = mbar_test(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1);
-        pre_kv = mbar_test(b_kvfull + 8 * ((i + 1) % kGStages), ((i + 1) / kGStages) & 1);
+        mbar_test2(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1, b_kvfull + 8 * ((i + 1) % kGStages), ((i + 1) / kGStages) & 1,
+                   pre_se, pre_kv);
         tc_fence_after();
         const uint32_t kt = smem_u32(sKV + s * 2 * kGKBytes);
         const uint32_t d = tmem_base + sb * kGPage;

@@ -188,8 +188,8 @@ indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
         const int sb = i & 1, s = i % kIdxStages;
         if (!pre_se && !mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelIdx, 210 + sb)) break;
         if (!pre_k && !mbar_wait(b_kfull + 8 * s, (i / kIdxStages) & 1, abort_flag, kKernelIdx, 220 + s)) break;
-        pre_se = mbar_test(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1);
-        pre_k = mbar_test(b_kfull + 8 * ((i + 1) % kIdxStages), ((i + 1) / kIdxStages) & 1);
+        mbar_test2(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1, b_kfull + 8 * ((i + 1) % kIdxStages), ((i + 1) / kIdxStages) & 1,
+                   pre_se, pre_k);
         tc_fence_after();
         const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * kIdxKBytes);
 #pragma unroll

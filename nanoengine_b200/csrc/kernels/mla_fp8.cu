@@ -130,8 +130,8 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
         const int sb = i & 1, s = i % kPgStages;
         if (!pre_se && !mbar_wait(b_sempty + 8 * sb, ((i >> 1) & 1) ^ 1, abort_flag, kKernelMla, 210 + sb)) { ok = false; break; }
         if (!pre_pg && !mbar_wait(b_pgfull + 8 * s, (i / kPgStages) & 1, abort_flag, kKernelMla, 220 + s)) { ok = false; break; }
-        pre_se = mbar_test(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1);
-        pre_pg = mbar_test(b_pgfull + 8 * ((i + 1) % kPgStages), ((i + 1) / kPgStages) & 1);
+        mbar_test2(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1, b_pgfull + 8 * ((i + 1) % kPgStages), ((i + 1) / kPgStages) & 1,
+                   pre_se, pre_pg);
         tc_fence_after();
         const uint32_t pg = smem_u32(sPg + s * kPgBytes);
         const uint32_t d = tmem_base + sb * kPage;

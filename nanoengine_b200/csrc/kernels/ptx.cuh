@@ -50,6 +50,14 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// Two tests for the price of one: both are in flight before either result is consumed.
+__device__ __forceinline__ void mbar_test2(uint32_t barA, uint32_t parA, uint32_t barB, uint32_t parB, bool& okA, bool& okB) {
+  uint32_t a, b;
+  asm volatile("{\n .reg .pred pa, pb;\n mbarrier.test_wait.parity.shared::cta.b64 pa, [%2], %3;\n"
+               " mbarrier.test_wait.parity.shared::cta.b64 pb, [%4], %5;\n selp.u32 %0, 1, 0, pa;\n selp.u32 %1, 1, 0, pb;\n}\n"
+               : "=r"(a), "=r"(b) : "r"(barA), "r"(parA), "r"(barB), "r"(parB) : "memory");
+  okA = a != 0; okB = b != 0;
+}
 // Hardware-suspended wait: the thread sleeps inside the barrier unit until the phase completes or `hint_ns` elapses.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;

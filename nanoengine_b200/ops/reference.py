@@ -456,3 +456,139 @@ def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def lm_head(hidden: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """Vocabulary projection; logits are returned in fp32."""
     return F.linear(hidden, w).float()
+
+
+# ---- gated delta-net linear attention (Qwen3.5 family) -----------------------------------------------------
+#
+# Parity: reference runtime/layers/backends/delta_net/generic.py:170-329 (layer orchestration),
+# components/conv.py (causal depthwise convolution with a carried window), components/recurrence.py:100-200
+# (the delta rule, state [.., V, K]), components/output.py:17-62 (gated RMSNorm).
+
+def gdn_conv(x: torch.Tensor, weight: torch.Tensor, conv_state: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor,
+             fresh: torch.Tensor) -> torch.Tensor:
+    """Causal depthwise convolution + SiLU over ragged sequences, carrying a window of the last K-1 inputs per sequence.
+
+    x [T, C]; weight [C, K]; conv_state [S, K-1, C] (this layer's pool, oldest input first); slots [B]; cu_seqlens [B+1];
+    fresh [B] non-zero where the sequence starts here (its window is taken as zeros).  Returns y [T, C] in x's dtype and
+    writes each sequence's new window back to its slot."""
+    K = weight.shape[1]
+    y = torch.empty_like(x)
+    cu = cu_seqlens.tolist()
+    w = weight.float()
+    for i in range(len(cu) - 1):
+        s, e = cu[i], cu[i + 1]
+        if e <= s:
+            continue
+        slot = int(slots[i])
+        win = conv_state[slot].float()
+        if int(fresh[i]):
+            win = torch.zeros_like(win)
+        full = torch.cat([win, x[s:e].float()], 0)                     # [K-1 + n, C]
+        acc = torch.zeros(e - s, x.shape[1], dtype=torch.float32, device=x.device)
+        for j in range(K):
+            acc += full[j: j + (e - s)] * w[:, j]
+        y[s:e] = torch.nn.functional.silu(acc).to(x.dtype)
+        conv_state[slot] = full[-(K - 1):].to(conv_state.dtype)
+    return y
+
+
+def gdn_gates(a: torch.Tensor, b: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor):
+    """log-decay g = -exp(A_log) * softplus(a + dt_bias) and write strength beta = sigmoid(b), both fp32 [T, Hv]."""
+    g = -A_log.float().exp() * torch.nn.functional.softplus(a.float() + dt_bias.float())
+    return g, b.float().sigmoid()
+
+
+def _l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+def gdn_scan(q, k, v, g, beta, S):
+    """Token-by-token delta rule for one sequence.  q, k [n, H, Dk] (normalised, q scaled); v [n, H, Dv]; g, beta [n, H];
+    S [H, Dv, Dk] fp32.  Returns (o [n, H, Dv] fp32, S)."""
+    out = []
+    for t in range(q.shape[0]):
+        S = S * g[t].exp()[:, None, None]
+        Sk = torch.einsum("hvk,hk->hv", S, k[t])
+        S = S + (beta[t][:, None] * (v[t] - Sk))[:, :, None] * k[t][:, None, :]
+        out.append(torch.einsum("hvk,hk->hv", S, q[t]))
+    return torch.stack(out, 0), S
+
+
+def gdn_chunked(q, k, v, g, beta, S, chunk: int = 64):
+    """The same recurrence evaluated chunk by chunk with matrix products (what a tensor-core prefill does).
+
+    Inside a chunk with cumulative log-decay G_t, the per-token writes u_t solve the unit-lower-triangular system
+    (I + A) U = beta * (V - exp(G) * K S0^T) with A[t, i] = beta_t exp(G_t - G_i) k_t.k_i for i < t; then
+    o_t = exp(G_t) S0 q_t + sum_{i<=t} exp(G_t - G_i) (k_i.q_t) u_i and S_C = exp(G_C) S0 + sum_i exp(G_C - G_i) u_i k_i^T."""
+    n, H, Dk = q.shape
+    Dv = v.shape[-1]
+    pad = (-n) % chunk
+    if pad:
+        z = lambda t: torch.cat([t, t.new_zeros(pad, *t.shape[1:])], 0)
+        q, k, v, g, beta = z(q), z(k), z(v), z(g), z(beta)      # padded tokens: g = 0 (no decay), beta = 0 (no write)
+    nc = (n + pad) // chunk
+    # [H, nc, C, *]
+    rs = lambda t: t.reshape(nc, chunk, H, -1).permute(2, 0, 1, 3)
+    qc, kc, vc = rs(q), rs(k), rs(v)
+    gc, bc = rs(g).squeeze(-1), rs(beta).squeeze(-1)             # [H, nc, C]
+    G = gc.cumsum(-1)
+    diff = G[..., :, None] - G[..., None, :]                     # G_t - G_i
+    tril = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device).tril()
+    decay = torch.where(tril, diff, torch.full_like(diff, float("-inf"))).exp()          # i <= t
+    kk = kc @ kc.transpose(-1, -2)
+    A = (bc[..., :, None] * decay * kk).masked_fill(~tril.tril(-1), 0.0)
+    eye = torch.eye(chunk, dtype=q.dtype, device=q.device)
+    Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A).contiguous(), upper=False)
+    W = Tm @ (bc[..., None] * G.exp()[..., None] * kc)          # [H, nc, C, Dk]
+    U0 = Tm @ (bc[..., None] * vc)                              # [H, nc, C, Dv]
+    qk = (qc @ kc.transpose(-1, -2)) * decay                     # [H, nc, C(t), C(i)]
+    eG = G.exp()[..., None]
+    gl = G[..., -1]                                              # [H, nc]
+    kdec = (gl[..., None] - G).exp()[..., None] * kc             # exp(G_C - G_i) k_i
+    out = torch.empty(H, nc, chunk, Dv, dtype=q.dtype, device=q.device)
+    for c in range(nc):
+        St = S.transpose(-1, -2)                                 # [H, Dk, Dv]
+        U = U0[:, c] - W[:, c] @ St
+        out[:, c] = eG[:, c] * (qc[:, c] @ St) + qk[:, c] @ U
+        S = gl[:, c].exp()[:, None, None] * S + U.transpose(-1, -2) @ kdec[:, c]
+    o = out.permute(1, 2, 0, 3).reshape(nc * chunk, H, Dv)[:n]
+    return o, S
+
+
+def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """w * rmsnorm(x) * silu(z) over the last dimension; result in z's dtype."""
+    xf = x.float()
+    xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(z.dtype)
+    return (w.to(z.dtype) * xn) * torch.nn.functional.silu(z.float()).to(z.dtype)
+
+
+GDN_CHUNK_MIN_TOKENS = 64      # sequences at least this long go through the chunked form
+
+
+def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh, z, norm_w, eps: float) -> torch.Tensor:
+    """Gated delta rule over ragged sequences with a per-sequence state, followed by the gated RMSNorm.
+
+    q, k [T, Hk, Dk] and v [T, Hv, Dv] are the convolved projections (Hv a multiple of Hk: value head h reads key head
+    h // (Hv/Hk)); a, b [T, Hv]; state [S, Hv, Dv, Dk] fp32 (this layer's pool); slots [B]; cu_seqlens [B+1]; fresh [B];
+    z [T, Hv, Dv] the output gate.  Returns [T, Hv*Dv] in v's dtype."""
+    T, Hk, Dk = q.shape
+    Hv, Dv = v.shape[1], v.shape[2]
+    rep = Hv // Hk
+    g, beta = gdn_gates(a, b, A_log, dt_bias)
+    qn = _l2norm(q.float()).repeat_interleave(rep, 1) * (Dk ** -0.5)
+    kn = _l2norm(k.float()).repeat_interleave(rep, 1)
+    vf = v.float()
+    o = torch.empty(T, Hv, Dv, dtype=torch.float32, device=v.device)
+    cu = cu_seqlens.tolist()
+    for i in range(len(cu) - 1):
+        s, e = cu[i], cu[i + 1]
+        if e <= s:
+            continue
+        slot = int(slots[i])
+        S = torch.zeros_like(state[slot]) if int(fresh[i]) else state[slot].clone()
+        if e - s >= GDN_CHUNK_MIN_TOKENS:
+            o[s:e], S = gdn_chunked(qn[s:e], kn[s:e], vf[s:e], g[s:e], beta[s:e], S)
+        else:
+            o[s:e], S = gdn_scan(qn[s:e], kn[s:e], vf[s:e], g[s:e], beta[s:e], S)
+        state[slot] = S
+    return rmsnorm_gated(o, z, norm_w, eps).reshape(T, Hv * Dv)
