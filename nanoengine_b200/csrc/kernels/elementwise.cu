@@ -31,7 +31,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, const __nv_bfloat16* __restrict__ res_in,
                                                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long out_ld,
                                                      __nv_bfloat16* __restrict__ res_out, uint8_t* __restrict__ q, float* __restrict__ sc, int sc_ld,
-                                                     int H, float eps) {
+                                                     int H, float eps, float w_off) {
   extern __shared__ float srow[];            // H floats
   __shared__ float red[32];
   const int row = blockIdx.x;
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         float2 t = unpack_bf16x2(wu[j]);
-        o[j] = pack_bf16x2(srow[i + 2 * j] * inv * t.x, srow[i + 2 * j + 1] * inv * t.y);
+        o[j] = pack_bf16x2(srow[i + 2 * j] * inv * (t.x + w_off), srow[i + 2 * j + 1] * inv * (t.y + w_off));
       }
       *reinterpret_cast<uint4*>(out + (long long)row * out_ld + i) = make_uint4(o[0], o[1], o[2], o[3]);
     }
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
       float amax = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; j++) {
-        v[j] = __bfloat162float(__float2bfloat16(srow[c + j] * inv * __bfloat162float(w[c + j])));
+        v[j] = __bfloat162float(__float2bfloat16(srow[c + j] * inv * (__bfloat162float(w[c + j]) + w_off)));
         amax = fmaxf(amax, fabsf(v[j]));
       }
       amax = fmaxf(warp_max(amax), 1e-10f);
@@ -302,7 +302,7 @@ __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_
 using namespace ne;
 
 extern "C" int ne_rmsnorm(const void* x, long long x_ld, const void* res_in, const void* w, void* out, long long out_ld, void* res_out,
-                          void* q, float* sc, int sc_ld, int T, int H, float eps, cudaStream_t st) {
+                          void* q, float* sc, int sc_ld, int T, int H, float eps, float w_off, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8 != 0 || (q && H % 128 != 0) || x_ld % 8 != 0) return 1001;
   size_t smem = (size_t)H * sizeof(float);
@@ -311,7 +311,7 @@ extern "C" int ne_rmsnorm(const void* x, long long x_ld, const void* res_in, con
     if (!done) { cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); done = true; }
   }
   rmsnorm_kernel<<<T, 256, smem, st>>>((const __nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)res_in, (const __nv_bfloat16*)w,
-                                       (__nv_bfloat16*)out, out_ld, (__nv_bfloat16*)res_out, (uint8_t*)q, sc, sc_ld, H, eps);
+                                       (__nv_bfloat16*)out, out_ld, (__nv_bfloat16*)res_out, (uint8_t*)q, sc, sc_ld, H, eps, w_off);
   return (int)cudaGetLastError();
 }
 

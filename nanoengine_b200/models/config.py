@@ -54,6 +54,18 @@ class ModelConfig:
     index_n_heads: int = 0
     index_head_dim: int = 128
     index_topk: int = 2048
+    # hybrid linear attention (Qwen3.5): gated delta-net layers between full-attention layers
+    layer_types: Optional[List[str]] = None  # per layer "linear_attention" | "full_attention"; None = all full attention
+    full_attention_interval: int = 0         # used when layer_types is absent: every n-th layer is full attention
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_conv_kernel_dim: int = 4
+    partial_rotary_factor: float = 1.0       # fraction of each head that is rotated
+    attn_output_gate: bool = False           # q projection carries a per-head sigmoid gate for the attention output
+    norm_unit_offset: bool = False           # RMSNorm weights are stored as the deviation from one
+    shared_expert_intermediate_size: int = 0 # Qwen3.5-MoE: one always-on expert behind a sigmoid gate
     # MTP
     num_nextn_predict_layers: int = 0
     # quantisation of linear / expert weights: None (use dtype) or "fp8" (e4m3, 128x128 block scales)
@@ -67,6 +79,25 @@ class ModelConfig:
     def is_mla(self) -> bool:
         return self.architecture in ("DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM",
                                      "GlmMoeDsaForCausalLM", "KimiK2ForCausalLM")
+
+    @property
+    def is_hybrid_gdn(self) -> bool:
+        return self.linear_num_value_heads > 0
+
+    def layer_type(self, layer_idx: int) -> str:
+        if not self.is_hybrid_gdn:
+            return "full_attention"
+        if self.layer_types and layer_idx < len(self.layer_types):
+            return self.layer_types[layer_idx]
+        n = self.full_attention_interval
+        return "full_attention" if n > 0 and (layer_idx + 1) % n == 0 else "linear_attention"
+
+    def num_layers_of(self, kind: str, upto: Optional[int] = None) -> int:
+        return sum(1 for i in range(self.num_hidden_layers if upto is None else upto) if self.layer_type(i) == kind)
+
+    @property
+    def gdn_conv_dim(self) -> int:
+        return 2 * self.linear_num_key_heads * self.linear_key_head_dim + self.linear_num_value_heads * self.linear_value_head_dim
 
     @property
     def has_indexer(self) -> bool:
@@ -94,6 +125,17 @@ class ModelConfig:
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "ModelConfig":
         d = dict(d)
+        if isinstance(d.get("text_config"), dict):        # multimodal wrappers keep the language model's fields one level down
+            inner = dict(d.pop("text_config"))
+            inner.setdefault("architectures", d.get("architectures"))
+            for k in ("quantization_config", "eos_token_id", "bos_token_id", "tie_word_embeddings"):
+                if k in d and k not in inner:
+                    inner[k] = d[k]
+            d = inner
+        rp = d.pop("rope_parameters", None)
+        if isinstance(rp, dict):
+            d.setdefault("rope_theta", rp.get("rope_theta", 10000000.0))
+            d.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 1.0))
         archs = d.pop("architectures", None)
         if archs and "architecture" not in d:
             d["architecture"] = archs[0]
@@ -111,6 +153,12 @@ class ModelConfig:
             d.setdefault("topk_group", 1)
             d.setdefault("routed_scaling_factor", 1.0)
             d.setdefault("qk_norm", True)
+        if d.get("architecture", "").startswith("Qwen3_5"):
+            d.setdefault("qk_norm", True)
+            d.setdefault("attn_output_gate", True)
+            d.setdefault("norm_unit_offset", True)
+            d.setdefault("n_shared_experts", 0)
+            d.setdefault("first_k_dense_replace", 0)
         if d.get("architecture", "").startswith("Qwen3") and "n_routed_experts" not in d:
             d.setdefault("n_routed_experts", 0)
             d.setdefault("qk_norm", True)
@@ -172,5 +220,35 @@ def qwen3_235b(**over) -> ModelConfig:
     return c
 
 
+def tiny_qwen3_5(moe: bool = False, **over) -> ModelConfig:
+    """CPU plumbing shape of the hybrid family: 4 layers (three gated delta-net, one gated full attention), hidden 128."""
+    c = ModelConfig(architecture="Qwen3_5MoeForConditionalGeneration" if moe else "Qwen3_5ForConditionalGeneration", vocab_size=512,
+                    hidden_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32, rope_theta=1e6,
+                    max_position_embeddings=4096, intermediate_size=256, q_lora_rank=None, n_routed_experts=8 if moe else 0,
+                    n_shared_experts=0, num_experts_per_tok=2, moe_intermediate_size=64, first_k_dense_replace=0, n_group=1,
+                    topk_group=1, norm_topk_prob=True, routed_scaling_factor=1.0, scoring_func="softmax", qk_norm=True,
+                    full_attention_interval=4, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
+                    linear_value_head_dim=32, linear_conv_kernel_dim=4, partial_rotary_factor=0.25, attn_output_gate=True,
+                    norm_unit_offset=True, shared_expert_intermediate_size=64 if moe else 0, eos_token_id=None)
+    for k, v in over.items():
+        setattr(c, k, v)
+    return c
+
+
+def qwen3_5_80b(**over) -> ModelConfig:
+    """Qwen3.5-MoE shape of the 80B-A3B class: 48 layers (3 gated delta-net : 1 full attention), 512 experts top-10 + gated shared expert."""
+    c = ModelConfig(architecture="Qwen3_5MoeForConditionalGeneration", vocab_size=151936, hidden_size=2048, num_hidden_layers=48,
+                    num_attention_heads=16, num_key_value_heads=2, head_dim=256, rope_theta=1e7, max_position_embeddings=262144,
+                    intermediate_size=5120, q_lora_rank=None, n_routed_experts=512, n_shared_experts=0, num_experts_per_tok=10,
+                    moe_intermediate_size=512, first_k_dense_replace=0, n_group=1, topk_group=1, norm_topk_prob=True,
+                    routed_scaling_factor=1.0, scoring_func="softmax", qk_norm=True, full_attention_interval=4,
+                    linear_num_key_heads=16, linear_num_value_heads=32, linear_key_head_dim=128, linear_value_head_dim=128,
+                    linear_conv_kernel_dim=4, partial_rotary_factor=0.25, attn_output_gate=True, norm_unit_offset=True,
+                    shared_expert_intermediate_size=512, eos_token_id=151645)
+    for k, v in over.items():
+        setattr(c, k, v)
+    return c
+
+
 PRESETS = {"tiny-deepseek-v3": tiny_deepseek_v3, "deepseek-v3": deepseek_v3, "deepseek-v3.2": deepseek_v32,
-           "qwen3-235b-a22b": qwen3_235b}
+           "qwen3-235b-a22b": qwen3_235b, "tiny-qwen3.5": tiny_qwen3_5, "qwen3.5-80b-a3b": qwen3_5_80b}

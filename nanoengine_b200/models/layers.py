@@ -64,17 +64,18 @@ class QLinear(nn.Module):
 
 
 class RMSNorm(nn.Module):
-    def __init__(self, dim: int, eps: float, dtype, device, quant_out: bool = False):
+    def __init__(self, dim: int, eps: float, dtype, device, quant_out: bool = False, unit_offset: bool = False):
         super().__init__()
-        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device), requires_grad=False)
+        self.unit_offset = unit_offset  # stored weight is the deviation from one; the kernels apply (1 + w) in fp32
+        self.weight = nn.Parameter((torch.zeros if unit_offset else torch.ones)(dim, dtype=dtype, device=device), requires_grad=False)
         self.eps = eps
         self.quant_out = quant_out      # the only consumer is an fp8 linear: let the kernel emit its quantised input too
 
     def forward(self, x, residual=None):
         """Without residual: y.  With residual: (y, x + residual) - the fused add + norm used between blocks."""
         if residual is None:
-            return ops.rmsnorm(x, self.weight, self.eps, self.quant_out)
-        return ops.add_rmsnorm(x, residual, self.weight, self.eps)
+            return ops.rmsnorm(x, self.weight, self.eps, self.quant_out, self.unit_offset)
+        return ops.add_rmsnorm(x, residual, self.weight, self.eps, self.unit_offset)
 
 
 class SwiGLUMLP(nn.Module):

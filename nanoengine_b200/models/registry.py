@@ -24,10 +24,16 @@ def _qwen3_moe():
     return Qwen3MoeForCausalLM
 
 
+def _qwen3_5():
+    from .qwen3_5 import Qwen35ForCausalLM
+    return Qwen35ForCausalLM
+
+
 _LAZY = {
     "DeepseekV2ForCausalLM": _deepseek, "DeepseekV3ForCausalLM": _deepseek, "DeepseekV32ForCausalLM": _deepseek,
     "GlmMoeDsaForCausalLM": _deepseek, "KimiK2ForCausalLM": _deepseek,
     "Qwen3MoeForCausalLM": _qwen3_moe, "Qwen3ForCausalLM": _qwen3_moe,
+    "Qwen3_5ForConditionalGeneration": _qwen3_5, "Qwen3_5MoeForConditionalGeneration": _qwen3_5,
 }
 
 

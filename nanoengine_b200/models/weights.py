@@ -78,7 +78,7 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
                 out[p + "indexer.weights_proj.weight"] = (cfg.index_n_heads, H)
         else:
             hd = cfg.head_dim
-            out[p + "q_proj.weight"] = (cfg.num_attention_heads * hd, H)
+            out[p + "q_proj.weight"] = (cfg.num_attention_heads * hd * (2 if cfg.attn_output_gate else 1), H)
             out[p + "k_proj.weight"] = (cfg.num_key_value_heads * hd, H)
             out[p + "v_proj.weight"] = (cfg.num_key_value_heads * hd, H)
             out[p + "o_proj.weight"] = (H, cfg.num_attention_heads * hd)
@@ -86,11 +86,26 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
                 out[p + "q_norm.weight"] = (hd,)
                 out[p + "k_norm.weight"] = (hd,)
 
+    def linear_attn(p):
+        Hk, Hv, Dk, Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        out[p + "in_proj_qkv.weight"] = (cfg.gdn_conv_dim, H)
+        out[p + "in_proj_z.weight"] = (Hv * Dv, H)
+        out[p + "in_proj_a.weight"] = (Hv, H)
+        out[p + "in_proj_b.weight"] = (Hv, H)
+        out[p + "conv1d.weight"] = (cfg.gdn_conv_dim, 1, cfg.linear_conv_kernel_dim)
+        out[p + "dt_bias"] = (Hv,)
+        out[p + "A_log"] = (Hv,)
+        out[p + "norm.weight"] = (Dv,)
+        out[p + "out_proj.weight"] = (H, Hv * Dv)
+
     def layer(i, moe):
         p = f"model.layers.{i}."
         out[p + "input_layernorm.weight"] = (H,)
         out[p + "post_attention_layernorm.weight"] = (H,)
-        attn(p + "self_attn.")
+        if cfg.layer_type(i) == "linear_attention":
+            linear_attn(p + "linear_attn.")
+        else:
+            attn(p + "self_attn.")
         if moe:
             I = cfg.moe_intermediate_size
             out[p + "mlp.gate.weight"] = (cfg.n_routed_experts, H)
@@ -100,6 +115,12 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
                 out[p + f"mlp.experts.{e}.gate_proj.weight"] = (I, H)
                 out[p + f"mlp.experts.{e}.up_proj.weight"] = (I, H)
                 out[p + f"mlp.experts.{e}.down_proj.weight"] = (H, I)
+            if cfg.shared_expert_intermediate_size:
+                Is = cfg.shared_expert_intermediate_size
+                out[p + "mlp.shared_expert.gate_proj.weight"] = (Is, H)
+                out[p + "mlp.shared_expert.up_proj.weight"] = (Is, H)
+                out[p + "mlp.shared_expert.down_proj.weight"] = (H, Is)
+                out[p + "mlp.shared_expert_gate.weight"] = (1, H)
             if cfg.n_shared_experts:
                 Is = I * cfg.n_shared_experts
                 out[p + "mlp.shared_experts.gate_proj.weight"] = (Is, H)
@@ -135,7 +156,15 @@ def random_hf_weights(cfg: ModelConfig, seed: int = 0, device="cpu", keep: Optio
             continue
         g = torch.Generator(device=dev)
         g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFF)
-        if name.endswith("norm.weight") and "k_norm" not in name or name.endswith("layernorm.weight"):
+        if name.endswith("A_log"):
+            t = torch.log(1.0 + 3.0 * torch.rand(shape, generator=g, device=dev, dtype=torch.float32))
+        elif name.endswith("dt_bias"):
+            t = 0.5 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        elif name.endswith("conv1d.weight"):
+            t = 0.3 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        elif cfg.norm_unit_offset and name.endswith("norm.weight") and "linear_attn" not in name:
+            t = 0.1 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)      # stored as the deviation from one
+        elif name.endswith("norm.weight") and "k_norm" not in name or name.endswith("layernorm.weight"):
             t = 1.0 + 0.1 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
         elif name.endswith("e_score_correction_bias") or name.endswith(".bias"):
             t = 0.01 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)

@@ -18,18 +18,20 @@ FP8 = torch.float8_e4m3fn
 
 
 # ---- norms -------------------------------------------------------------------------------------
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False) -> torch.Tensor:
-    """`quant` is a hint for the CUDA body (also emit the block-quantised copy for an fp8 consumer); ignored here."""
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False, unit_offset: bool = False) -> torch.Tensor:
+    """`quant` is a hint for the CUDA body (also emit the block-quantised copy for an fp8 consumer); ignored here.
+    `unit_offset`: the stored weight is the deviation from one (Qwen3.5 / Gemma convention), applied as (1 + w) in fp32."""
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
-    return (y * w.float()).to(x.dtype)
+    wf = w.float() + 1.0 if unit_offset else w.float()
+    return (y * wf).to(x.dtype)
 
 
-def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float):
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float, unit_offset: bool = False):
     """residual_out = x + residual (in the activation dtype); y = rmsnorm(residual_out)."""
     if residual is not None:
         x = (x.float() + residual.float()).to(x.dtype)
-    return rmsnorm(x, w, eps), x
+    return rmsnorm(x, w, eps, False, unit_offset), x
 
 
 def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float) -> torch.Tensor:
@@ -465,7 +467,7 @@ def lm_head(hidden: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 # (the delta rule, state [.., V, K]), components/output.py:17-62 (gated RMSNorm).
 
 def gdn_conv(x: torch.Tensor, weight: torch.Tensor, conv_state: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor,
-             fresh: torch.Tensor) -> torch.Tensor:
+             fresh: torch.Tensor, uniform_one: bool = False) -> torch.Tensor:
     """Causal depthwise convolution + SiLU over ragged sequences, carrying a window of the last K-1 inputs per sequence.
 
     x [T, C]; weight [C, K]; conv_state [S, K-1, C] (this layer's pool, oldest input first); slots [B]; cu_seqlens [B+1];
@@ -555,17 +557,27 @@ def gdn_chunked(q, k, v, g, beta, S, chunk: int = 64):
     return o, S
 
 
-def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """w * rmsnorm(x) * silu(z) over the last dimension; result in z's dtype."""
     xf = x.float()
     xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(z.dtype)
-    return (w.to(z.dtype) * xn) * torch.nn.functional.silu(z.float()).to(z.dtype)
+    y = (w.to(z.dtype) * xn) * torch.nn.functional.silu(z.float()).to(z.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """o * sigmoid(gate), the output gate of the hybrid family's full-attention layers (gate may be a strided view)."""
+    return (o.float() * torch.sigmoid(gate.float())).to(o.dtype)
 
 
 GDN_CHUNK_MIN_TOKENS = 64      # sequences at least this long go through the chunked form
 
 
-def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh, z, norm_w, eps: float) -> torch.Tensor:
+def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh, z, norm_w, eps: float, max_q_len: int = 1,
+                  cu_host=None) -> torch.Tensor:
     """Gated delta rule over ragged sequences with a per-sequence state, followed by the gated RMSNorm.
 
     q, k [T, Hk, Dk] and v [T, Hv, Dv] are the convolved projections (Hv a multiple of Hk: value head h reads key head

@@ -188,7 +188,7 @@ def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = N
 QUANT_AFTER_NORM = True      # block-level norms also emit the e4m3 1x128 copy their fp8 consumers need
 
 
-def _rmsnorm(x, res_in, w, eps, want_res, quant=False):
+def _rmsnorm(x, res_in, w, eps, want_res, quant=False, unit_offset=False):
     T, H = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1
     out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
@@ -200,25 +200,25 @@ def _rmsnorm(x, res_in, w, eps, want_res, quant=False):
         q = torch.empty(T, H, dtype=FP8, device=x.device)
         sc = torch.empty(H // 128, T, dtype=torch.float32, device=x.device)
     _ck(lib().ne_rmsnorm(_p(x), _c.c_longlong(x.stride(0)), _p(res_in), _p(w), _p(out), _c.c_longlong(H), _p(res_out), _p(q), _p(sc),
-                         _c.c_int(T), _c.c_int(T), _c.c_int(H), _c.c_float(eps), _st()), "ne_rmsnorm")
+                         _c.c_int(T), _c.c_int(T), _c.c_int(H), _c.c_float(eps), _c.c_float(1.0 if unit_offset else 0.0), _st()), "ne_rmsnorm")
     if q is not None:
         out._ne_q = (q, sc)
     return out, res_out
 
 
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False) -> torch.Tensor:
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False, unit_offset: bool = False) -> torch.Tensor:
     """`quant`: also leave the e4m3 1x128 copy for an fp8 linear that consumes the result (picked up by `linear`)."""
     if x.stride(0) % 8 or x.data_ptr() % 16:
         x = x.contiguous()
-    return _rmsnorm(x, None, w, eps, False, quant and x.shape[1] % 128 == 0)[0]
+    return _rmsnorm(x, None, w, eps, False, quant and x.shape[1] % 128 == 0, unit_offset)[0]
 
 
-def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float):
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float, unit_offset: bool = False):
     if x.stride(0) % 8 or x.data_ptr() % 16:
         x = x.contiguous()
     if residual is None:
-        return _rmsnorm(x, None, w, eps, False, QUANT_AFTER_NORM)[0], x
-    return _rmsnorm(x, residual, w, eps, True, QUANT_AFTER_NORM)
+        return _rmsnorm(x, None, w, eps, False, QUANT_AFTER_NORM, unit_offset)[0], x
+    return _rmsnorm(x, residual, w, eps, True, QUANT_AFTER_NORM, unit_offset)
 
 
 def layernorm(x, w, b, eps):
@@ -474,3 +474,88 @@ def indexer_select(q8, q_scale, head_w, cache, block_tables, cu_seqlens_q, conte
                               _c.c_int(topk), _c.c_int(n), _c.c_void_p(out.data_ptr() + t0 * topk * 4), _st()), "ne_indexer_topk")
     return out
 dequant_fp8_1x128 = ref.dequant_fp8_1x128
+
+
+# ---- gated delta-net linear attention ---------------------------------------------------------------
+def _i32(t):
+    return t if t.dtype == torch.int32 else t.int()
+
+
+def gdn_conv(x: torch.Tensor, weight: torch.Tensor, conv_state: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor,
+             fresh: torch.Tensor, uniform_one: bool = False) -> torch.Tensor:
+    """Causal depthwise convolution + SiLU with the carried window updated in place.  `uniform_one`: every sequence
+    contributes exactly one token, so the window shift is done by the same kernel."""
+    T, C = x.shape
+    K = weight.shape[1]
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+    assert conv_state.dtype == torch.bfloat16 and conv_state.is_contiguous() and conv_state.shape[1:] == (K - 1, C)
+    y = torch.empty(T, C, dtype=torch.bfloat16, device=x.device)
+    B = cu_seqlens.numel() - 1
+    _ck(lib().ne_gdn_conv(_p(x), _c.c_longlong(x.stride(0)), _p(weight), _p(conv_state), _p(_i32(slots)), _p(_i32(cu_seqlens)), _p(_i32(fresh)),
+                          _p(y), _c.c_longlong(C), _c.c_int(T), _c.c_int(B), _c.c_int(C), _c.c_int(K), _c.c_int(1 if uniform_one else 0), _st()),
+        "ne_gdn_conv")
+    if not uniform_one:
+        LAUNCHES[0] += 1
+    return y
+
+
+def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """w * rmsnorm(x) * silu(z) per head; x [T, H, D] fp32, z [T, H, D] bf16 (rows may be strided)."""
+    T, H, D = x.shape
+    x = x.float().contiguous()
+    assert z.dtype == torch.bfloat16 and z.stride(2) == 1 and z.stride(1) == D and w.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty(T, H, D, dtype=torch.bfloat16, device=x.device)
+    assert out.stride(2) == 1 and out.stride(1) == D
+    _ck(lib().ne_rmsnorm_gated(_p(x), _p(z), _c.c_longlong(z.stride(0)), _p(w), _c.c_float(eps), _p(out), _c.c_longlong(out.stride(0)),
+                               _c.c_longlong(T), _c.c_int(H), _c.c_int(D), _st()), "ne_rmsnorm_gated")
+    return out
+
+
+def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh, z, norm_w, eps: float, max_q_len: int = 1,
+                  cu_host=None) -> torch.Tensor:
+    """Gated delta rule + gated RMSNorm.  Sequences shorter than `ref.GDN_CHUNK_MIN_TOKENS` new tokens (decode, verification,
+    short chunks) run in the recurrent kernel that keeps the state in registers; longer ones take the chunked form, whose
+    work is batched matrix products, and need the host copy of the sequence boundaries (`cu_host`)."""
+    T, Hk, Dk = q.shape
+    Hv, Dv = v.shape[1], v.shape[2]
+    for t in (q, k, v, z):
+        assert t.dtype == torch.bfloat16 and t.stride(2) == 1 and t.stride(1) == t.shape[2]
+    assert q.stride(0) == k.stride(0) and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(0) == b.stride(0)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (Hv, Dv, Dk)
+    assert A_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and norm_w.dtype == torch.bfloat16
+    out = torch.empty(T, Hv, Dv, dtype=torch.bfloat16, device=q.device)
+    slots, cu, fresh = _i32(slots), _i32(cu_seqlens), _i32(fresh)
+    skip = 1 << 30
+    if max_q_len >= ref.GDN_CHUNK_MIN_TOKENS:
+        assert cu_host is not None, "the chunked prefill form needs the sequence boundaries on the host"
+        skip = ref.GDN_CHUNK_MIN_TOKENS
+        rep = Hv // Hk
+        g, beta = ref.gdn_gates(a, b, A_log, dt_bias)
+        for i in range(len(cu_host) - 1):
+            s, e = cu_host[i], cu_host[i + 1]
+            if e - s < skip:
+                continue
+            qn = ref._l2norm(q[s:e].float()).repeat_interleave(rep, 1) * (Dk ** -0.5)
+            kn = ref._l2norm(k[s:e].float()).repeat_interleave(rep, 1)
+            sl = slots[i: i + 1].long()
+            S0 = state.index_select(0, sl)[0] * (1 - fresh[i]).float()
+            o, S = ref.gdn_chunked(qn, kn, v[s:e].float(), g[s:e], beta[s:e], S0)
+            state.index_copy_(0, sl, S[None])
+            rmsnorm_gated(o, z[s:e], norm_w, eps, out[s:e])
+    _ck(lib().ne_gdn_step(_p(q), _p(k), _p(v), _c.c_longlong(q.stride(0)), _c.c_longlong(v.stride(0)), _p(a), _p(b), _c.c_longlong(a.stride(0)),
+                          _p(A_log), _p(dt_bias), _p(state), _p(slots), _p(cu), _p(fresh), _p(z), _c.c_longlong(z.stride(0)), _p(norm_w),
+                          _c.c_float(eps), _p(out), _c.c_longlong(out.stride(0)), _c.c_int(cu.numel() - 1), _c.c_int(Hk), _c.c_int(Hv), _c.c_int(Dk),
+                          _c.c_int(Dv), _c.c_int(skip), _st()), "ne_gdn_step")
+    return out.view(T, Hv * Dv)
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """o * sigmoid(gate) for o [T, heads, D] contiguous and gate a (possibly strided) view of the same shape."""
+    T, Hh, D = o.shape
+    o = o.contiguous()
+    assert o.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and gate.stride(2) == 1 and D % 2 == 0
+    out = torch.empty_like(o)
+    _ck(lib().ne_sigmoid_gate(_p(o), _p(gate), _c.c_longlong(gate.stride(0)), _c.c_longlong(gate.stride(1)), _p(out), _c.c_longlong(T), _c.c_int(Hh),
+                              _c.c_int(D), _st()), "ne_sigmoid_gate")
+    return out

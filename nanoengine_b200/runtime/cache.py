@@ -4,6 +4,9 @@ MLA latent cache   [L, blocks, block_size, R + rope]   bf16/fp32, or fp8 e4m3 ra
                                                         for DeepSeek-V3: clamped cast, no scales)
 indexer key cache  [L, blocks, block_size * (D + 4)] u8 per page: block_size fp8 keys, then block_size fp32 scales
 GQA cache          [2, L, blocks, block_size, kv_heads_local, head_dim]
+recurrent state    hybrid models with gated delta-net layers keep, per sequence slot and linear layer, the delta-rule state
+                   [Hv, Dv, Dk] fp32 and the convolution window [K-1, conv_dim]; the paged GQA cache then covers only the
+                   full-attention layers.  Slot `state_slots` (one past the scheduler-visible range) is scratch.
 
 One extra block past the scheduler-visible range is reserved as the scratch page that dummy batches of idle
 DP ranks write into.
@@ -36,6 +39,27 @@ class CachePlan:
     row_dim: int               # MLA: R + rope ; GQA: head_dim
     kv_heads_local: int = 1
     index_dim: int = 0
+    # recurrent-state layers (gated delta-net)
+    gdn: bool = False
+    gdn_layers: int = 0
+    state_slots: int = 0
+    conv_dim: int = 0
+    conv_k: int = 0
+    gdn_heads: int = 0
+    gdn_dv: int = 0
+    gdn_dk: int = 0
+
+    @property
+    def state_slot_bytes(self) -> int:
+        """Bytes one sequence slot takes over all linear-attention layers."""
+        if not self.gdn:
+            return 0
+        e = 2 if self.kv_dtype in (torch.bfloat16, torch.float16, torch.float8_e4m3fn) else 4
+        return self.gdn_layers * (self.gdn_heads * self.gdn_dv * self.gdn_dk * 4 + (self.conv_k - 1) * self.conv_dim * e)
+
+    @property
+    def state_bytes(self) -> int:
+        return (self.state_slots + 1) * self.state_slot_bytes
 
     @property
     def kv_block_bytes(self) -> int:
@@ -57,13 +81,20 @@ class CachePlan:
         bits = C.PLAN_MLA if self.mla else C.PLAN_GQA
         if self.indexer:
             bits |= C.PLAN_INDEXER
+        if self.gdn:
+            bits |= C.PLAN_GDN
         return bits
 
 
 def make_cache_plan(mc: ModelConfig, kv_dtype_name: str, block_size: int, attn_tp: int = 1, num_mtp_layers: int = 0,
-                    use_indexer: bool = True, num_layers: Optional[int] = None) -> CachePlan:
+                    use_indexer: bool = True, num_layers: Optional[int] = None, state_slots: int = 0) -> CachePlan:
     L = (num_layers if num_layers is not None else mc.num_hidden_layers) + num_mtp_layers
     dt = torch_dtype(kv_dtype_name)
+    if mc.is_hybrid_gdn:
+        return CachePlan(False, True, False, mc.num_layers_of("full_attention"), block_size, dt, mc.head_dim,
+                         kv_heads_local=max(1, mc.num_key_value_heads // attn_tp), gdn=True, gdn_layers=mc.num_layers_of("linear_attention"),
+                         state_slots=state_slots, conv_dim=mc.gdn_conv_dim, conv_k=mc.linear_conv_kernel_dim,
+                         gdn_heads=mc.linear_num_value_heads, gdn_dv=mc.linear_value_head_dim, gdn_dk=mc.linear_key_head_dim)
     if mc.is_mla:
         return CachePlan(True, False, mc.has_indexer and use_indexer, L, block_size, dt, mc.mla_cache_dim,
                          index_dim=mc.index_head_dim)
@@ -95,6 +126,15 @@ class KVCache:
             self.indexer = torch.zeros(plan.num_layers, nb, plan.block_size * (plan.index_dim + 4), dtype=torch.uint8, device=device)
             self.indexer_layers = [self.indexer[l] for l in range(plan.num_layers)]
         self.host_kv = None
+        self.rec_states = self.conv_states = None
+        self.scratch_slot = plan.state_slots
+        if plan.gdn:
+            ns = plan.state_slots + 1   # + scratch slot for padded graph rows and dummy batches
+            cdt = torch.bfloat16 if plan.kv_dtype == torch.float8_e4m3fn else plan.kv_dtype
+            self.rec = torch.zeros(plan.gdn_layers, ns, plan.gdn_heads, plan.gdn_dv, plan.gdn_dk, dtype=torch.float32, device=device)
+            self.conv = torch.zeros(plan.gdn_layers, ns, plan.conv_k - 1, plan.conv_dim, dtype=cdt, device=device)
+            self.rec_states = [self.rec[l] for l in range(plan.gdn_layers)]
+            self.conv_states = [self.conv[l] for l in range(plan.gdn_layers)]
 
     def allocate_host(self, num_host_blocks: int):
         """Pinned host tier used by preemption swap."""

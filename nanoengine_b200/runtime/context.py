@@ -29,6 +29,11 @@ class ForwardContext:
     is_dummy: bool = False
     kv_caches: Optional[List[Any]] = None  # per-layer cache tensors (MLA: [blocks, bs, D]; GQA: (k, v))
     indexer_caches: Optional[List[Any]] = None
+    # recurrent-state layers: slot of each sequence in the state pools, whether the sequence starts in this step, the pools
+    state_slots: Optional[torch.Tensor] = None      # int32 [B]
+    seq_fresh: Optional[torch.Tensor] = None        # int32 [B], 1 = no state carried in (first chunk of the prompt)
+    conv_states: Optional[List[Any]] = None         # per linear layer [slots, K-1, conv_dim]
+    rec_states: Optional[List[Any]] = None          # per linear layer [slots, Hv, Dv, Dk] fp32
     extras: Dict[str, Any] = field(default_factory=dict)   # per-forward scratch shared by layers (e.g. DSA top-k reuse)
     # host copies for the CPU reference path and for planning
     cu_seqlens_q_host: Optional[List[int]] = None

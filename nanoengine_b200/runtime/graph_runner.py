@@ -42,6 +42,10 @@ class DecodeGraphRunner:
         self.context_lens = torch.ones(self.max_bs, dtype=torch.int32, device=dev)
         self.block_tables = torch.zeros(self.max_bs, self.max_blocks, dtype=torch.int32, device=dev)
         self.cu_seqlens_q = (torch.arange(self.max_bs + 1, dtype=torch.int32, device=dev) * q_len)
+        # recurrent-state models: slot of every row (padding rows and capture warm-ups use the scratch slot)
+        self.gdn = runner.plan.gdn
+        self.state_slots = torch.full((self.max_bs,), runner.cache.scratch_slot, dtype=torch.int32, device=dev)
+        self.seq_fresh = torch.zeros(self.max_bs, dtype=torch.int32, device=dev)
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.outputs: Dict[int, torch.Tensor] = {}
         self.pool = None
@@ -62,7 +66,9 @@ class DecodeGraphRunner:
             is_prefill=False, num_seqs=b, num_tokens=b * q, cu_seqlens_q=self.cu_seqlens_q[: b + 1], context_lens=self.context_lens[:b],
             slot_mapping=self.slot_mapping[: b * q], block_tables=self.block_tables[:b], max_seqlen_q=q,
             max_seqlen_k=self.r.config.max_model_len, last_token_indices=None, q_len_uniform=q,
-            kv_caches=self.r.cache.layers, indexer_caches=self.r.cache.indexer_layers)
+            kv_caches=self.r.cache.layers, indexer_caches=self.r.cache.indexer_layers,
+            state_slots=self.state_slots[:b] if self.gdn else None, seq_fresh=self.seq_fresh[:b] if self.gdn else None,
+            conv_states=self.r.cache.conv_states, rec_states=self.r.cache.rec_states)
 
     def _fill(self, ids, pos, ctx: ForwardContext, b: int):
         n, q = ctx.num_seqs, self.q_len
@@ -73,6 +79,10 @@ class DecodeGraphRunner:
         self.context_lens[:n].copy_(ctx.context_lens)
         w = ctx.block_tables.shape[1]
         self.block_tables[:n, :w].copy_(ctx.block_tables)
+        if self.gdn:
+            self.state_slots[:n].copy_(ctx.state_slots)
+            self.seq_fresh[:n].copy_(ctx.seq_fresh)
+            self.state_slots[n:b].fill_(self.r.cache.scratch_slot)
         if n < b:
             # padding rows: q_len tokens of a one-page sequence on the scratch page
             self.input_ids[n * q: b * q].zero_()
@@ -85,6 +95,10 @@ class DecodeGraphRunner:
         sctx = self._static_ctx(b)
         q = self.q_len
         ids, pos = self.input_ids[: b * q], self.positions[: b * q]
+        if self.gdn:
+            # the warm-up runs execute real steps: point every row at the scratch slot so no live sequence's state advances
+            # (rows sharing one slot race on it, which is harmless for scratch data); run() refills the live slots afterwards
+            self.state_slots[:b].fill_(self.r.cache.scratch_slot)
         # eager warm-up on the side stream: sets kernel attributes, fills caches of derived weights, sizes the allocator
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())

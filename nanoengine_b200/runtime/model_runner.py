@@ -85,7 +85,7 @@ class ModelRunner:
         self.d2h_bytes = 0          # bytes read back (sampled tokens, log-probabilities)
         self._last_decode = None
         self.plan = make_cache_plan(self.mc, config.resolved_kv_dtype(), config.kvcache_block_size, config.attention_tp,
-                                    num_mtp_layers=self._num_mtp_layers(), use_indexer=config.use_nsa())
+                                    num_mtp_layers=self._num_mtp_layers(), use_indexer=config.use_nsa(), state_slots=config.max_num_seqs)
 
     def _num_mtp_layers(self) -> int:
         return max(1, self.mc.num_nextn_predict_layers) if self.config.num_speculative_tokens > 0 else 0
@@ -158,12 +158,13 @@ class ModelRunner:
         peak = torch.cuda.max_memory_allocated()
         used = total - free
         torch.cuda.empty_cache()
-        return kv_budget_blocks(self.plan, total, self.config.gpu_memory_utilization, used, peak, current)
+        return kv_budget_blocks(self.plan, total, self.config.gpu_memory_utilization, used, peak, current, reserved=self.plan.state_bytes)
 
     def _warmup_prefill(self, tokens: int) -> None:
         bs = self.plan.block_size
         nb = (tokens + bs - 1) // bs
-        tmp = KVCache(self.plan, nb, self.device)
+        import dataclasses
+        tmp = KVCache(dataclasses.replace(self.plan, state_slots=0), nb, self.device)   # the scratch state slot is enough here
         b = C.RunnerIn()
         b.is_prefill = True
         b.seq_ids = [0]
@@ -220,6 +221,12 @@ class ModelRunner:
             cu_seqlens_q_host=d["cu_seqlens_q"].tolist(), context_lens_host=d["context_lens"].tolist())
         ctx.extras["input_ids"] = self._to_dev(d["input_ids"]).long()
         ctx.extras["positions"] = self._to_dev(d["positions"]).long()
+        if self.plan.gdn:
+            # a sequence whose whole context arrives in this step carries no state in; unassigned slots go to the scratch slot
+            slots = np.asarray([s if s >= 0 else self.cache.scratch_slot for s in b.state_slots], dtype=np.int32)
+            fresh = (np.asarray(d["context_lens"]) == np.asarray(q_lens)).astype(np.int32)
+            ctx.state_slots, ctx.seq_fresh = self._to_dev(slots), self._to_dev(fresh)
+            ctx.conv_states, ctx.rec_states = self.cache.conv_states, self.cache.rec_states
         return ctx
 
     def _dummy_context(self, is_prefill: bool) -> ForwardContext:
@@ -235,6 +242,10 @@ class ModelRunner:
             kv_caches=self.cache.layers, indexer_caches=self.cache.indexer_layers, cu_seqlens_q_host=[0, 1], context_lens_host=[1])
         ctx.extras["input_ids"] = torch.zeros(1, dtype=torch.long, device=dev)
         ctx.extras["positions"] = torch.zeros(1, dtype=torch.long, device=dev)
+        if self.plan.gdn:
+            ctx.state_slots = torch.tensor([self.cache.scratch_slot], dtype=torch.int32, device=dev)
+            ctx.seq_fresh = torch.ones(1, dtype=torch.int32, device=dev)
+            ctx.conv_states, ctx.rec_states = self.cache.conv_states, self.cache.rec_states
         return ctx
 
     # ---- execution -----------------------------------------------------------------------------
