@@ -8,6 +8,8 @@ buffer rewritten between runs):
   gemm_rs   row-parallel fp8 GEMM (K split over the group) + reduce-scatter: fused scatter epilogue vs GEMM then NCCL
   ag        all-gather of [T / world, H] bf16: peer-store push vs NCCL
   ar        all-reduce of [T, H] bf16: push + reduce + push vs NCCL
+  cp        (--decode-cp) MLA decode of a few long sequences: all pages on one GPU vs pages dealt over the group, partials
+            pushed to every peer and merged by log-sum-exp
 and prints one table from rank 0.  The roofline for the collectives is bytes crossing NVLink per GPU / 770 GB/s.
 """
 from __future__ import annotations
@@ -29,6 +31,9 @@ def main():
     ap.add_argument("--k-total", type=int, default=16384, help="contraction size of the row-parallel GEMM before sharding")
     ap.add_argument("--tokens", default="128,512,2048,8192")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
+    ap.add_argument("--decode-cp", action="store_true", help="also time context-parallel MLA decode")
+    ap.add_argument("--cp-batch", type=int, default=8)
+    ap.add_argument("--cp-ctx", type=int, default=65536)
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -91,6 +96,26 @@ def main():
         t_f = timeit(lambda: be.all_reduce(y))
         t_n = timeit(lambda: dist.all_reduce(y.clone()))
         rows.append(("ar", T, t_f, t_n, f"link floor {2 * nbytes / 770e9 * 1e6:6.1f}"))
+    if args.decode_cp:
+        from nanoengine_b200.ops import sm100_attn
+        from nanoengine_b200.parallel.decode_cp import DecodeCP, shard_pages
+        B, ctx, Hh, bs = args.cp_batch, args.cp_ctx, 128, 64
+        npg = -(-ctx // bs)
+        cache = (torch.randn(B * npg + 1, bs, 576, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+        tables = [list(range(b * npg, (b + 1) * npg)) for b in range(B)]
+        bt_full = torch.tensor(tables, dtype=torch.int32, device="cuda")
+        cl_full = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        loc = [shard_pages(t, ctx, bs, world, rank) for t in tables]
+        lw = max(len(p) for p, _ in loc)
+        bt_loc = torch.tensor([p + [0] * (lw - len(p)) for p, _ in loc], dtype=torch.int32, device="cuda")
+        cl_loc = torch.tensor([n for _, n in loc], dtype=torch.int32, device="cuda")
+        cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        q = torch.randn(B, Hh, 576, device="cuda").to(torch.bfloat16)
+        cp = DecodeCP(dist.group.WORLD, Hh, 512, max_tokens=B, local_splits=max(2, 16 // world))
+        sc = 576 ** -0.5
+        t_full = timeit(lambda: sm100_attn.mla_attention_paged(q, cache, bt_full, cu, cl_full, sc, 512))
+        t_cp = timeit(lambda: cp.attention(q, cache, bt_loc, cu, cl_loc, sc))
+        rows.append(("cp", B, t_cp, t_full, f"ctx {ctx}; 'nccl' column = all pages on one GPU"))
     if rank == 0:
         print(f"world={world} hidden={H} K/rank={Kl}; times in us (max over ranks)")
         print(f"{'op':8s} {'tokens':>7s} {'fused':>9s} {'nccl':>9s} {'speedup':>8s}   note")

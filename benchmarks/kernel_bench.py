@@ -137,6 +137,48 @@ def case_indexer(B, ctx, q_len=1, Hi=64, D=128, bs=64, topk=2048):
     return fn, B * ctx * (D + 4) + T * ctx * 4 * 2, 2.0 * T * Hi * ctx * D
 
 
+def case_absorb(T, which, H=128, nope=128, rope=64, R=512, v=128):
+    """The two per-head products around absorbed MLA: q_nope @ W_UK ([T, H, 128] -> [T, H, 512], read out of the q_b output) and
+    the latent attention output @ W_UV ([T, H, 512] -> [T, H, 128]); one GEMM group per head."""
+    if which == "k":
+        q = torch.randn(T, H, nope + rope, device="cuda", dtype=torch.bfloat16)
+        x, w = q[..., :nope], (torch.randn(H, nope, R, device="cuda") * 0.05).to(torch.bfloat16)
+    else:
+        x, w = torch.randn(T, H, R, device="cuda", dtype=torch.bfloat16), (torch.randn(H, R, v, device="cuda") * 0.05).to(torch.bfloat16)
+    out = torch.empty(T, H, w.shape[2], device="cuda", dtype=torch.bfloat16)
+    fn = lambda: sm100.bmm_absorb(x, w, out)
+    return fn, w.numel() * 2 + T * H * (w.shape[1] + w.shape[2]) * 2, 2.0 * T * H * w.shape[1] * w.shape[2]
+
+
+def case_gdn(B, q_len=1, Hk=16, Hv=32, Dk=128, Dv=128, K=4):
+    """Gated delta-net layer core at the Qwen3.5-MoE shape: conv over [q|k|v] with window shift, then the recurrent step with the gated
+    norm.  The floor is one read and one write of every sequence's fp32 state."""
+    T = B * q_len
+    C = 2 * Hk * Dk + Hv * Dv
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    proj = torch.randn(T, C + Hv * Dv, **bf)
+    qkv, z = proj[:, :C], proj[:, C:].reshape(T, Hv, Dv)
+    ab = torch.randn(T, 2 * Hv, **bf)
+    w = (torch.randn(C, K, device="cuda") * 0.3).to(torch.bfloat16)
+    conv = torch.zeros(B + 1, K - 1, C, **bf)
+    state = torch.randn(B + 1, Hv, Dv, Dk, device="cuda") * 0.1
+    slots = torch.arange(B, device="cuda", dtype=torch.int32)
+    cu = (torch.arange(B + 1, device="cuda") * q_len).to(torch.int32)
+    fresh = torch.zeros(B, dtype=torch.int32, device="cuda")
+    A_log, dtb = torch.rand(Hv, device="cuda"), torch.randn(Hv, device="cuda")
+    nw = torch.ones(Dv, **bf)
+
+    def fn():
+        y = sm100.gdn_conv(qkv, w, conv, slots, cu, fresh, q_len == 1)
+        q = y[:, : Hk * Dk].view(T, Hk, Dk)
+        k = y[:, Hk * Dk: 2 * Hk * Dk].view(T, Hk, Dk)
+        v = y[:, 2 * Hk * Dk:].view(T, Hv, Dv)
+        return sm100.gdn_recurrent(q, k, v, ab[:, :Hv], ab[:, Hv:], A_log, dtb, state, slots, cu, fresh, z, nw, 1e-6, q_len, None)
+
+    nbytes = B * Hv * Dv * Dk * 4 * 2 + T * (C * 2 * 3 + Hv * Dv * 2 * 2) + B * (K - 1) * C * 2 * 2
+    return fn, nbytes, 2.0 * T * Hv * Dv * Dk * 3
+
+
 def case_gqa(B, ctx, q_len, Hq, Hkv, D=128, bs=64):
     nb = (ctx + bs - 1) // bs
     kc = torch.randn(B * nb + 1, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
@@ -215,6 +257,10 @@ def build_cases(args):
         "gqa_decode_tp8": lambda: case_gqa(256, 4352, 1, 8, 1),          # Qwen3-235B per rank at TP8: 8 q heads, 1 kv head
         "gqa_decode_tp1": lambda: case_gqa(64, 4352, 1, 64, 4),
         "gqa_prefill_tp8": lambda: case_gqa(4, 4096, 4096, 8, 1),
+        "absorb_k_decode": lambda: case_absorb(128, "k"),
+        "absorb_v_decode": lambda: case_absorb(128, "v"),
+        "gdn_decode": lambda: case_gdn(128),
+        "gdn_verify2": lambda: case_gdn(128, q_len=2),
         "mla_decode": lambda: case_mla(128, args.ctx),
         "mla_decode_small_batch": lambda: case_mla(8, 8192),
         # prefill, 16384 tokens

@@ -36,6 +36,29 @@ def mla_splits(T: int, max_pages: int) -> int:
     return max(1, min(want, max(1, max_pages // 4), 32))
 
 
+def mla_partials(q, cache, block_tables, cu_seqlens_q, context_lens, scale, kv_lora_rank, splits: int):
+    """Un-merged split-KV results of the fp8 tcgen05 kernel: part [splits, T, H, R] fp32 (each slice normalised on its own) and
+    lse2 [splits, T, H] fp32 (log2-sum-exp of the slice, -inf where a slice saw no key).  `ne_attn_merge` folds any stack of
+    such slices, including slices computed on other GPUs."""
+    T, H, Dk = q.shape
+    R = kv_lora_rank
+    assert splits >= 2 and cache.dtype == FP8 and Dk == 576 and R == 512 and cache.shape[1] == 64 and H <= 128
+    lib = _k.lib()
+    bt, cu, cl = _i32(block_tables), _i32(cu_seqlens_q), _i32(context_lens)
+    if q.dtype == FP8:
+        q8 = q.contiguous()
+    else:
+        q = q if (q.dtype == torch.bfloat16 and q.is_contiguous()) else q.to(torch.bfloat16).contiguous()
+        q8 = torch.empty(T * H, Dk, dtype=torch.uint8, device=q.device)
+        _k._ck(lib.ne_cast_e4m3(_k._p(q), _k._p(q8), _c.c_longlong(T * H * Dk), _k._st()), "ne_cast_e4m3")
+    part = torch.empty(splits, T, H, R, dtype=torch.float32, device=q.device)
+    lse2 = torch.empty(splits, T, H, dtype=torch.float32, device=q.device)
+    _k._ck(lib.ne_mla_fp8(_k._p(q8), _k._p(cache), _c.c_int(cache.shape[0]), _k._p(bt), _c.c_int(bt.stride(0)), _k._p(cu), _k._p(cl),
+                          _c.c_int(cl.numel()), _c.c_int(T), _c.c_int(H), _c.c_int(splits), _c.c_float(scale), _k._p(None), _k._p(part), _k._p(lse2),
+                          _k._st()), "ne_mla_fp8")
+    return part, lse2
+
+
 def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scale, kv_lora_rank, sparse_indices=None, splits=None):
     T, H, Dk = q.shape
     R = kv_lora_rank
