@@ -2,6 +2,7 @@
 
     python benchmarks/kernel_bench.py                       # all cases, table on stdout
     python benchmarks/kernel_bench.py --case moe_gemm1 --experts 8 --iters 3   # one small case (what the ncu captures run)
+    python benchmarks/kernel_bench.py --case absorb_k_decode --graph           # short kernels: time a graph replay
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, a buffer larger than L2 is rewritten between timed
 runs, the median of `--iters` runs is reported.  Fractions are against MEASURED_PEAKS.json (copy bandwidth and cuBLAS
@@ -42,8 +43,16 @@ def flush_l2():
     _flush.fill_(1)
 
 
-def timeit(fn, iters):
+def timeit(fn, iters, graph=False):
     for _ in range(3):
+        fn()
+    if graph:
+        # a kernel of a few microseconds is shorter than its own launch path: replay it from a CUDA graph, as the decode step does
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        fn = g.replay
         fn()
     ts = []
     for _ in range(iters):
@@ -280,6 +289,7 @@ def main():
     ap.add_argument("--rows", type=int, default=32, help="rows per expert for the grouped GEMM cases")
     ap.add_argument("--ctx", type=int, default=2560)
     ap.add_argument("--prefill-tokens", type=int, default=16384)
+    ap.add_argument("--graph", action="store_true", help="time a CUDA-graph replay of the case (removes the host launch path from short kernels)")
     args = ap.parse_args()
     sm100.lib()
     bw, fl, src = peaks()
@@ -288,7 +298,7 @@ def main():
     print(f"{'case':26s} {'time_us':>10s} {'GB/s':>9s} {'frac_bw':>8s} {'TFLOP/s':>9s} {'frac_bf16':>9s}   (fractions of {src} peaks)")
     for n in names:
         fn, nbytes, flops = cases[n]()
-        t = timeit(fn, args.iters)
+        t = timeit(fn, args.iters, args.graph)
         print(f"{n:26s} {t * 1e6:10.1f} {nbytes / t / 1e9:9.0f} {nbytes / t / bw:8.2f} {flops / t / 1e12:9.1f} {flops / t / fl:9.2f}")
         del fn
         torch.cuda.empty_cache()

@@ -151,7 +151,9 @@ def _step_logits(runner, C, seqs, new_tokens, state_slots, is_prefill):
 
 @pytest.mark.parametrize("moe", [False, True])
 def test_hybrid_model_logits_match_fp32_cpu_model(moe):
-    """The bf16 CUDA model against the fp32 CPU model on identical (bf16-rounded) weights: a ragged prefill, then decode steps."""
+    """The bf16 CUDA model against the fp32 CPU model on identical (bf16-rounded) weights: a ragged prefill, then decode steps.
+    The routed variant selects every expert (top-8 of 8), so no near-tie in a bf16 router can send a token to another expert
+    and the comparison stays a smooth function of the rounding error."""
     from nanoengine_b200 import Config
     from nanoengine_b200._native import _core as C
     from nanoengine_b200.models.config import tiny_qwen3_5
@@ -159,7 +161,7 @@ def test_hybrid_model_logits_match_fp32_cpu_model(moe):
     from nanoengine_b200.runtime.model_runner import ModelRunner
     mc = tiny_qwen3_5(moe=moe, hidden_size=256, head_dim=128, num_attention_heads=4, num_key_value_heads=2, linear_key_head_dim=64,
                       linear_value_head_dim=64, intermediate_size=512, moe_intermediate_size=128,
-                      shared_expert_intermediate_size=128 if moe else 0)
+                      shared_expert_intermediate_size=128 if moe else 0, num_experts_per_tok=8 if moe else 2)
     W = [(n, t.to(torch.bfloat16).float()) for n, t in random_hf_weights(mc, seed=5, std=0.05)]
     g = torch.Generator().manual_seed(6)
     seqs = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (100, 9, 70)]
@@ -177,7 +179,6 @@ def test_hybrid_model_logits_match_fp32_cpu_model(moe):
         new = [len(s) for s in cur] if step == 0 else [1] * len(cur)
         lc = _step_logits(runners["cpu"], C, cur, new, slots, step == 0)
         lg = _step_logits(runners["cuda"], C, cur, new, slots, step == 0)
-        # with routed experts a bf16 router can pick another expert for a near-tie token, which moves that token's logits as a whole
-        assert _rel(lg, lc) < (0.12 if moe else 5e-2), f"step {step}: {_rel(lg, lc)}"
+        assert _rel(lg, lc) < 5e-2, f"step {step}: {_rel(lg, lc)}"
         nxt = lc.argmax(-1).tolist()                       # both models continue with the fp32 model's tokens
         cur = [s + [t] for s, t in zip(cur, nxt)]
