@@ -56,30 +56,57 @@ template <int BLOCK_N> struct Smem {
   static constexpr int kG = KGroup<BLOCK_N>::value;
   static constexpr int kStageBytes = kG * (kABytes + kBBytes);
   static constexpr int kStaging = 8 * 32 * 80;      // per-warp epilogue staging for up to 8 epilogue warps
-  static constexpr int kBudget = 232448 - 1024 - 256 - kStaging;
+  static constexpr int kStaticTables = 6400;       // the kernel's static shared memory: three per-group tables of kSchedCache ints + small
+  static constexpr int kBudget = 232448 - 1024 - 256 - kStaging - kStaticTables;
   static constexpr int kStages = (kBudget / kStageBytes) > 10 ? 10 : (kBudget / kStageBytes);
   static constexpr int kBytes = kStages * kStageBytes + kStaging + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 constexpr int kSchedCache = 512;        // group tables up to this many groups are staged in shared memory
 
+// Maps a linear tile index to (group, row block, column block).  Three roles of a CTA (producer, MMA issuer, epilogue) each walk
+// their own copy, and the lookup sits on the producer's critical path at every tile switch, so it must not scan: a step of a
+// linear walk over the groups costs ~300 cycles in one thread (measured: 20k cycles to reach group 94 of a 128-head batched
+// GEMM, most of that kernel's run time).  Uniform groups use a division; ragged groups use the table of first-tile indices
+// that the CTA builds once in shared memory (`base`, groups + 1 entries) and a binary search.  Only group counts beyond the
+// shared-memory table fall back to the incremental walk.
 struct TileSched {
   int groups, M, n_blocks;
   const int* masked_m;                  // global or shared memory
   const int* row_start;
-  int g = 0, base = 0;
-  __device__ TileSched(int groups_, int M_, int nb, const int* mm, const int* rs) : groups(groups_), M(M_), n_blocks(nb), masked_m(mm), row_start(rs) {}
+  const int* base;                      // shared memory: first tile of every group, total at [groups]; null = none built
+  int g = 0, walked = 0;
+  __device__ TileSched(int groups_, int M_, int nb, const int* mm, const int* rs, const int* base_)
+      : groups(groups_), M(M_), n_blocks(nb), masked_m(mm), row_start(rs), base(base_) {}
   __device__ int row0(int grp) const { return row_start ? row_start[grp] : 0; }
   __device__ int rows(int grp) const {
     int r = masked_m ? masked_m[grp] : M;
     int cap = row_start ? M - row_start[grp] : M;      // never step outside the buffer, whatever the counts say
     return r < cap ? r : (cap > 0 ? cap : 0);
   }
+  __device__ int tiles_of(int grp) const { return ((rows(grp) + kBlockM - 1) / kBlockM) * n_blocks; }
   __device__ bool get(int tile, int& grp, int& mb, int& nb) {
+    if (!masked_m && !row_start) {                      // every group has the same shape
+      const int per = ((M + kBlockM - 1) / kBlockM) * n_blocks;
+      if (tile >= per * groups) return false;
+      grp = tile / per;
+      const int l = tile - grp * per;
+      mb = l / n_blocks; nb = l - mb * n_blocks;
+      return true;
+    }
+    if (base) {
+      if (tile >= base[groups]) return false;
+      int lo = g, hi = groups - 1;                      // tiles only move forward: the answer is never before the last one
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (base[mid] <= tile) lo = mid; else hi = mid - 1; }
+      g = grp = lo;
+      const int l = tile - base[lo];
+      mb = l / n_blocks; nb = l - mb * n_blocks;
+      return true;
+    }
     while (g < groups) {
-      int cnt = ((rows(g) + kBlockM - 1) / kBlockM) * n_blocks;
-      if (tile < base + cnt) { int l = tile - base; grp = g; mb = l / n_blocks; nb = l % n_blocks; return true; }
-      base += cnt; g++;
+      const int cnt = tiles_of(g);
+      if (tile < walked + cnt) { const int l = tile - walked; grp = g; mb = l / n_blocks; nb = l % n_blocks; return true; }
+      walked += cnt; g++;
     }
     return false;
   }
@@ -91,7 +118,22 @@ struct TileSched {
 // are scattered to peer GPUs by the MoE combine.
 constexpr int kStgPitch = 80;                       // 64 bytes of data + 16 of padding: conflict-free for 16-byte accesses
 constexpr int kStgWarpBytes = 32 * kStgPitch;
-__device__ __forceinline__ void epi_store32_bf16(uint8_t* stg, const float (&v)[32], bool row_ok, __nv_bfloat16* drow, int ncols_left) {
+// Which rows a lane serves in the four store rounds of a 32-column chunk, fetched from their owner lanes once per tile
+// (the shuffles cost as much as the stores when repeated per chunk).
+struct EpiRows { unsigned long long dp[4]; bool ok[4]; };
+__device__ __forceinline__ EpiRows epi_rows(bool row_ok, __nv_bfloat16* drow) {
+  EpiRows r;
+  const int lane = (int)lane_id();
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int rr = i * 8 + (lane >> 2);
+    r.ok[i] = __shfl_sync(0xffffffffu, (int)row_ok, rr) != 0;
+    r.dp[i] = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(drow), rr);
+  }
+  return r;
+}
+// `col` = first column of the chunk relative to the row pointers in `rows`.
+__device__ __forceinline__ void epi_store32_bf16(uint8_t* stg, const float (&v)[32], const EpiRows& rows, int col, int ncols_left) {
   const int lane = (int)lane_id();
   uint8_t* mine = stg + lane * kStgPitch;
 #pragma unroll
@@ -101,12 +143,10 @@ __device__ __forceinline__ void epi_store32_bf16(uint8_t* stg, const float (&v)[
   __syncwarp();
   const int ch = lane & 3;
 #pragma unroll
-  for (int r0 = 0; r0 < 32; r0 += 8) {
-    const int rr = r0 + (lane >> 2);
-    const bool okr = __shfl_sync(0xffffffffu, (int)row_ok, rr) != 0;
-    const unsigned long long dp = __shfl_sync(0xffffffffu, (unsigned long long)reinterpret_cast<uintptr_t>(drow), rr);
-    if (okr && ch * 8 < ncols_left)
-      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dp) + ch * 8) = *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + ch * 16);
+  for (int i = 0; i < 4; i++) {
+    const int rr = i * 8 + (lane >> 2);
+    if (rows.ok[i] && ch * 8 < ncols_left)
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(rows.dp[i]) + col + ch * 8) = *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + ch * 16);
   }
   __syncwarp();
 }
@@ -176,6 +216,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
   const int* mm_tab = args.masked_m ? (cache_tables ? s_mm : args.masked_m) : nullptr;
   const int* rs_tab = args.row_start ? (cache_tables ? s_rs : args.row_start) : nullptr;
+  // first tile of every ragged group: counts by all threads, then one warp turns them into running sums
+  __shared__ int s_base[kSchedCache + 1];
+  static_assert((3 * kSchedCache + 1) * (int)sizeof(int) + 128 <= S::kStaticTables, "the stage budget must leave room for the static tables");
+  const bool ragged = args.masked_m || args.row_start;
+  const int* base_tab = (ragged && cache_tables) ? s_base : nullptr;
+  if (base_tab) {
+    __syncthreads();                                   // the row tables above are complete
+    TileSched cnt(args.groups, args.M, n_blocks, mm_tab, rs_tab, nullptr);
+    for (int i = threadIdx.x; i < args.groups; i += blockDim.x) s_base[i + 1] = cnt.tiles_of(i);
+    __syncthreads();
+    if (warp == 2) {
+      const int lane = (int)lane_id();
+      const int per = (args.groups + 31) / 32, lo = lane * per, hi = min(lo + per, args.groups);
+      int sum = 0;
+      for (int i = lo; i < hi; i++) sum += s_base[i + 1];
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+      int run = incl - sum;                            // tiles before this lane's first group
+      if (lane == 0) s_base[0] = 0;
+      for (int i = lo; i < hi; i++) { run += s_base[i + 1]; s_base[i + 1] = run; }
+    }
+    // the __syncthreads that ends the prologue publishes the table
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
     for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4 * kEpi); }
@@ -192,7 +256,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (elect_one()) {
-      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab);
+      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab);
       int stage = 0; uint32_t phase = 0; int grp, mb, nb;
       bool ok = true;
       for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
@@ -226,7 +290,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab);
+      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab);
       int stage = 0; uint32_t phase = 0; int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
       bool ok = true;
       // A test of an mbarrier costs ~150 cycles even when the phase has long completed, and this thread is the serial
@@ -291,7 +355,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int cbase = ((warp - 2) >> 2) * kCols;   // column offset of this warp's group inside the tile
     const int row_in_tile = wq * 32 + (int)lane_id();
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab);
+    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab);
     int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
     bool ok = true;
     bool pre_tf = false;                               // result of an early test of the next accumulator's "full" barrier
@@ -374,12 +438,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0 + cbase
                 : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
             uint8_t* stg = staging + (warp - 2) * kStgWarpBytes;
+            const EpiRows erows = epi_rows(row_ok, dbf);
 #pragma unroll
             for (int cc = 0; cc < kCols / 32; cc++) {
               float v[32];
 #pragma unroll
               for (int j = 0; j < 32; j++) v[j] = acc[cc * 32 + j];
-              epi_store32_bf16(stg, v, row_ok, dbf + cc * 32, args.N - (n0 + cbase + cc * 32));
+              epi_store32_bf16(stg, v, erows, cc * 32, args.N - (n0 + cbase + cc * 32));
             }
           }
         }
@@ -389,6 +454,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0;
         __nv_bfloat16* dbf = (args.row_dst && row_ok) ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0
                                                       : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
+        EpiRows erows;
+        if (!kSplit && !args.out_fp32) erows = epi_rows(row_ok, dbf);
 #pragma unroll
         for (int c = 0; c < BLOCK_N / 32; c++) {
           uint32_t r[32];
@@ -415,7 +482,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-            epi_store32_bf16(staging + (warp - 2) * kStgWarpBytes, v, row_ok, dbf + c * 32, args.N - (n0 + c * 32));
+            epi_store32_bf16(staging + (warp - 2) * kStgWarpBytes, v, erows, c * 32, args.N - (n0 + c * 32));
           }
         }
         tc_fence_before();
