@@ -114,6 +114,27 @@ __global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, long lon
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
+// One (row, 128-column block) item of SwiGLU: 4 columns per lane; bf16 out, or e4m3 with the block's scale at sc[c * sc_ld + row].
+__device__ __forceinline__ void silu_item(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q,
+                                          float* __restrict__ sc, int sc_ld, long long mrow, int row, int c, int I, int lane) {
+  const __nv_bfloat16* xr = x + mrow * 2 * I + c * 128 + lane * 4;
+  uint2 gv = *reinterpret_cast<const uint2*>(xr), uv = *reinterpret_cast<const uint2*>(xr + I);
+  float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), u0 = unpack_bf16x2(uv.x), u1 = unpack_bf16x2(uv.y);
+  float v[4] = {silu(g0.x) * u0.x, silu(g0.y) * u0.y, silu(g1.x) * u1.x, silu(g1.y) * u1.y};
+  const long long o = mrow * I + c * 128 + lane * 4;
+  if (!q) {
+    *reinterpret_cast<uint2*>(y + o) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+    return;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; j++) { v[j] = __bfloat162float(__float2bfloat16(v[j])); amax = fmaxf(amax, fabsf(v[j])); }
+  amax = fmaxf(warp_max(amax), 1e-10f);
+  const float is = kFp8Max / amax;
+  *reinterpret_cast<uint32_t*>(q + o) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
+  if (lane == 0) sc[(long long)c * sc_ld + row] = amax / kFp8Max;
+}
+
 // x [groups, rows, 2I] -> y.  One warp per (row, 128 output columns).  rows_valid[g] masks rows (nullptr = all).
 // Output bf16 (q == nullptr) or e4m3 + scales sc[g][(col/128) * sc_ld + row].
 constexpr int kSiluMaxGroups = 1024;
@@ -121,28 +142,56 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
                                 int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, const int* __restrict__ row_start, int groups,
                                 int rows, int I) {
   // warps stride over the concatenation of all groups' (valid row, 128-column block) items, so a sparsely filled masked
-  // layout costs only its valid rows and every warp gets an equal share whatever the split between groups.  The two group
-  // tables are staged in shared memory first: read from global memory inside the loop they put one L2 round trip per
-  // group on every warp's critical path (32 groups = ~30 us for a kernel that moves 10 MB).
-  __shared__ int s_cnt[kSiluMaxGroups], s_rs[kSiluMaxGroups];
-  const bool staged = groups <= kSiluMaxGroups;
-  if (staged) {
+  // layout costs only its valid rows and every warp gets an equal share whatever the split between groups.  The item index
+  // is mapped back to its group through a table of first-item indices built once per CTA in shared memory and a binary
+  // search: walking the groups in every warp (with a global load and 64-bit modulo arithmetic per group) made a kernel
+  // that moves 10 MB take 30 us.
+  __shared__ int s_first[kSiluMaxGroups + 1], s_rs[kSiluMaxGroups];
+  const int cg = I / 128, lane = threadIdx.x & 31;
+  if (groups <= kSiluMaxGroups) {
     for (int g = threadIdx.x; g < groups; g += blockDim.x) {
-      s_cnt[g] = rows_valid ? rows_valid[g] : rows;
+      int n = rows_valid ? rows_valid[g] : rows;
+      n = n < rows ? n : rows;
+      s_first[g + 1] = (n > 0 ? n : 0) * cg;
       s_rs[g] = row_start ? row_start[g] : 0;
     }
     __syncthreads();
+    if (threadIdx.x < 32) {
+      const int per = (groups + 31) / 32, lo = lane * per, hi = lo + per < groups ? lo + per : groups;
+      int sum = 0;
+      for (int i = lo; i < hi; i++) sum += s_first[i + 1];
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+      int run = incl - sum;
+      if (lane == 0) s_first[0] = 0;
+      for (int i = lo; i < hi; i++) { run += s_first[i + 1]; s_first[i + 1] = run; }
+    }
+    __syncthreads();
+    const int total = s_first[groups];
+    const int w0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nw = gridDim.x * (blockDim.x >> 5);
+    int g = 0;
+    for (int it = w0; it < total; it += nw) {
+      int hi = groups - 1;                              // items only move forward: search from the last group found
+      while (g < hi) { const int mid = (g + hi + 1) >> 1; if (s_first[mid] <= it) g = mid; else hi = mid - 1; }
+      const int l = it - s_first[g];
+      const int ri = l / cg, c = l - ri * cg;
+      const int row = s_rs[g] + ri;
+      if (row >= rows && row_start) continue;
+      const long long gbase = row_start ? 0 : (long long)g * rows;
+      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane);
+    }
+    return;
   }
-  const int cg = I / 128, lane = threadIdx.x & 31;
+  // more groups than the table holds: walk them
   const long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nw = (long long)gridDim.x * (blockDim.x >> 5);
   long long base = 0;                      // items of the groups before g, modulo nw
   for (int g = 0; g < groups; g++) {
-    int nrows = staged ? s_cnt[g] : (rows_valid ? rows_valid[g] : rows);
+    int nrows = rows_valid ? rows_valid[g] : rows;
     nrows = nrows < rows ? nrows : rows;
-    // contiguous grouped layout: group g owns rows [row_start[g], +rows_valid[g]) of one flat matrix; otherwise [groups, rows, *]
     const long long gbase = row_start ? 0 : (long long)g * rows;
-    const int r0 = row_start ? (staged ? s_rs[g] : row_start[g]) : 0;
+    const int r0 = row_start ? row_start[g] : 0;
     const long long items = (long long)nrows * cg;
     long long first = w0 - base;
     if (first < 0) first += nw;
@@ -150,22 +199,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
     for (long long it = first; it < items; it += nw) {
       const int row = r0 + (int)(it / cg), c = (int)(it % cg);
       if (row >= rows && row_start) continue;
-      const __nv_bfloat16* xr = x + (gbase + row) * 2 * I + c * 128 + lane * 4;
-      uint2 gv = *reinterpret_cast<const uint2*>(xr), uv = *reinterpret_cast<const uint2*>(xr + I);
-      float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), u0 = unpack_bf16x2(uv.x), u1 = unpack_bf16x2(uv.y);
-      float v[4] = {silu(g0.x) * u0.x, silu(g0.y) * u0.y, silu(g1.x) * u1.x, silu(g1.y) * u1.y};
-      const long long o = (gbase + row) * I + c * 128 + lane * 4;
-      if (!q) {
-        *reinterpret_cast<uint2*>(y + o) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
-        continue;
-      }
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; j++) { v[j] = __bfloat162float(__float2bfloat16(v[j])); amax = fmaxf(amax, fabsf(v[j])); }
-      amax = fmaxf(warp_max(amax), 1e-10f);
-      const float is = kFp8Max / amax;
-      *reinterpret_cast<uint32_t*>(q + o) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
-      if (lane == 0) sc[(row_start ? 0 : (long long)g * sc_gs) + (long long)c * sc_ld + row] = amax / kFp8Max;
+      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane);
     }
   }
 }

@@ -59,15 +59,31 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
   const int hkv = blockIdx.y, split = blockIdx.z;
 
   // which sequence and which of its token tiles is this CTA?  Tiles never straddle sequences.
-  if (threadIdx.x == 0) {
+  // (warp 0 searches 32 sequences per round with a prefix sum of their tile counts: one thread walking the sequences
+  // delays the CTAs of the last sequences of a 256-sequence decode batch by several microseconds)
+  if (warp == 0) {
+    const int lane = (int)lane_id();
     int rem = blockIdx.x, seq = -1, tok0 = 0;
-    for (int s = 0; s < a.num_seqs; s++) {
-      const int ql = a.cu_seqlens_q[s + 1] - a.cu_seqlens_q[s];
-      const int nt = (ql + a.tq - 1) / a.tq;
-      if (rem < nt) { seq = s; tok0 = a.cu_seqlens_q[s] + rem * a.tq; break; }
-      rem -= nt;
+    for (int s0 = 0; s0 < a.num_seqs && seq < 0; s0 += 32) {
+      const int s = s0 + lane;
+      int q0 = 0, nt = 0;
+      if (s < a.num_seqs) { q0 = a.cu_seqlens_q[s]; nt = (a.cu_seqlens_q[s + 1] - q0 + a.tq - 1) / a.tq; }
+      int incl = nt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+      const unsigned hit = __ballot_sync(0xffffffffu, rem < incl);        // lanes whose running count passes the tile index
+      if (hit) {
+        const int l = __ffs(hit) - 1;
+        const int before = __shfl_sync(0xffffffffu, incl - nt, l);
+        seq = s0 + l;
+        tok0 = __shfl_sync(0xffffffffu, q0, l) + (rem - before) * a.tq;
+      } else {
+        rem -= __shfl_sync(0xffffffffu, incl, 31);
+      }
     }
-    s_tile[0] = seq; s_tile[1] = tok0;
+    if (lane == 0) { s_tile[0] = seq; s_tile[1] = tok0; }
+  }
+  if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
     for (int i = 0; i < kGStages; i++) { mbar_init(b_kvfull + 8 * i, 1); mbar_init(b_kvempty + 8 * i, 1); }
     for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 4); }

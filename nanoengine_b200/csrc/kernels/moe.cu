@@ -235,7 +235,11 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
   __shared__ int s_pos[64]; __shared__ float s_w[64];
   if (threadIdx.x < top_k) { s_pos[threadIdx.x] = pos[(long long)t * top_k + threadIdx.x]; s_w[threadIdx.x] = w[(long long)t * top_k + threadIdx.x]; }
   __syncthreads();
-  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+  // blockIdx.y splits the row into column slices: with one CTA per token a decode batch would occupy fewer CTAs than there
+  // are SMs, each with 32 KB of loads in flight, a fraction of what it takes to keep HBM busy
+  const int slice = (((H + 7) / 8 + gridDim.y - 1) / gridDim.y) * 8;
+  const int c_end = min(H, ((int)blockIdx.y + 1) * slice);
+  for (int c = blockIdx.y * slice + threadIdx.x * 8; c < c_end; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     // eight expert rows are fetched before any is used: the loads are independent and the kernel is latency-bound
     for (int k0 = 0; k0 < top_k; k0 += 8) {
@@ -299,7 +303,8 @@ extern "C" int ne_moe_combine_local(const void* y, const int* pos, const float* 
                                     cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8 || top_k > 64) return 1001;
-  moe_combine_kernel<<<T, 256, 0, st>>>((const __nv_bfloat16*)y, pos, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, top_k, H);
+  const int slices = T >= 2048 ? 1 : (T >= 512 ? 2 : 4);      // enough CTAs per SM at decode sizes, one pass over the tables per token otherwise
+  moe_combine_kernel<<<dim3(T, slices), 256, 0, st>>>((const __nv_bfloat16*)y, pos, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, top_k, H);
   return (int)cudaGetLastError();
 }
 
