@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(const AttnArgs a) {
 // out = sum_s softmax_s(lse) * part_s  for split-KV attention.  part [S, rows, D] fp32 (already normalised), lse2 [S, rows] (log2 domain).
 __global__ void attn_merge_kernel(const float* __restrict__ part, const float* __restrict__ lse2, __nv_bfloat16* __restrict__ out,
                                   int splits, long long rows, int D, int out_row_stride) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   long long row = blockIdx.x;
   float m = -INFINITY;
   for (int s = 0; s < splits; s++) m = fmaxf(m, lse2[(long long)s * rows + row]);
@@ -154,6 +155,7 @@ __device__ __forceinline__ uint32_t hash32(uint32_t x) {
 // counter-based hash of (seed, row, column).  Optionally the log-probability of the chosen token under softmax(logits).
 __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ logits, const float* __restrict__ temps, long long* __restrict__ tok,
                                                      float* __restrict__ logprob, int V, uint64_t seed) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   __shared__ float s_val[32]; __shared__ int s_idx[32]; __shared__ float s_m[32]; __shared__ float s_s[32];
   const int row = blockIdx.x;
   const float* lr = logits + (long long)row * V;
@@ -232,13 +234,11 @@ extern "C" int ne_attn_generic(const void* q, long long q_tok_stride, int q_head
 
 extern "C" int ne_attn_merge(const float* part, const float* lse2, void* out, int splits, long long rows, int D, int out_row_stride, cudaStream_t st) {
   if (rows <= 0) return 0;
-  attn_merge_kernel<<<(unsigned)rows, 128, 0, st>>>(part, lse2, (__nv_bfloat16*)out, splits, rows, D, out_row_stride);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(attn_merge_kernel, dim3((unsigned)rows), dim3(128), 0, st, part, lse2, (__nv_bfloat16*)out, splits, rows, D, out_row_stride);
 }
 
 extern "C" int ne_sample(const float* logits, const float* temps, long long* tok, float* logprob, int rows, int V, unsigned long long seed,
                          cudaStream_t st) {
   if (rows <= 0) return 0;
-  sample_kernel<<<rows, 1024, 0, st>>>(logits, temps, tok, logprob, V, seed);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(sample_kernel, dim3(rows), dim3(1024), 0, st, logits, temps, tok, logprob, V, (uint64_t)seed);
 }

@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
                                                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long out_ld,
                                                      __nv_bfloat16* __restrict__ res_out, uint8_t* __restrict__ q, float* __restrict__ sc, int sc_ld,
                                                      int H, float eps, float w_off) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   extern __shared__ float srow[];            // H floats
   __shared__ float red[32];
   const int row = blockIdx.x;
@@ -99,6 +100,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 // bf16 [T, K] (row stride x_ld) -> e4m3 [T, K] + scales sc[(k/128) * sc_ld + t].  One warp per (row, group).
 __global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, uint8_t* __restrict__ q, float* __restrict__ sc,
                                    int sc_ld, int T, int K) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const int groups = K / 128;
   long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (gw >= (long long)T * groups) return;
@@ -141,6 +143,7 @@ constexpr int kSiluMaxGroups = 1024;
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ sc,
                                 int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, const int* __restrict__ row_start, int groups,
                                 int rows, int I) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   // warps stride over the concatenation of all groups' (valid row, 128-column block) items, so a sparsely filled masked
   // layout costs only its valid rows and every warp gets an equal share whatever the split between groups.  The item index
   // is mapped back to its group through a table of first-item indices built once per CTA in shared memory and a binary
@@ -231,6 +234,7 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, long long row_s
 __global__ void __launch_bounds__(256) mla_kv_prepare_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_ld, const __nv_bfloat16* __restrict__ w,
                                                             float eps, const long long* __restrict__ positions, const float* __restrict__ rope_cache,
                                                             void* __restrict__ cache, const long long* __restrict__ slots, int T, int R, int rope, int fp8) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   const long long slot = slots[t];
@@ -276,6 +280,7 @@ __global__ void __launch_bounds__(256) mla_kv_prepare_kernel(const __nv_bfloat16
 __global__ void __launch_bounds__(256) mla_q_finalize_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q_pe,
                                                             long long pe_row_stride, int pe_head_stride, const long long* __restrict__ positions,
                                                             const float* __restrict__ rope_cache, uint8_t* __restrict__ q8, int T, int H, int R, int rope) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)T * H) return;
@@ -344,9 +349,8 @@ extern "C" int ne_rmsnorm(const void* x, long long x_ld, const void* res_in, con
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); done = true; }
   }
-  rmsnorm_kernel<<<T, 256, smem, st>>>((const __nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)res_in, (const __nv_bfloat16*)w,
+  return (int)launch_pdl(rmsnorm_kernel, dim3(T), dim3(256), smem, st, (const __nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)res_in, (const __nv_bfloat16*)w,
                                        (__nv_bfloat16*)out, out_ld, (__nv_bfloat16*)res_out, (uint8_t*)q, sc, sc_ld, H, eps, w_off);
-  return (int)cudaGetLastError();
 }
 
 extern "C" int ne_quant_1x128(const void* x, long long x_ld, void* q, float* sc, int sc_ld, int T, int K, cudaStream_t st) {
@@ -354,8 +358,7 @@ extern "C" int ne_quant_1x128(const void* x, long long x_ld, void* q, float* sc,
   if (K % 128 != 0 || x_ld % 4 != 0) return 1001;
   long long warps = (long long)T * (K / 128);
   int blocks = (int)((warps + 7) / 8);
-  quant_1x128_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, x_ld, (uint8_t*)q, sc, sc_ld, T, K);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(quant_1x128_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, x_ld, (uint8_t*)q, sc, sc_ld, T, K);
 }
 
 extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, const int* row_start,
@@ -365,8 +368,7 @@ extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld
   long long warps = (long long)groups * rows * (I / 128);
   long long want = (warps + 7) / 8;
   int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
-  silu_mul_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, row_start, groups, rows, I);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, row_start, groups, rows, I);
 }
 
 extern "C" int ne_rope(const void* x, long long row_stride, int head_stride, void* y, long long y_row_stride, int y_head_stride, int heads,
@@ -390,9 +392,8 @@ extern "C" int ne_mla_kv_prepare(const void* kv, long long kv_ld, const void* w,
                                  void* cache, const long long* slots, int T, int R, int rope, int fp8, cudaStream_t st) {
   if (T <= 0) return 0;
   if (R % 2 || rope % 2 || kv_ld % 2) return 1001;
-  mla_kv_prepare_kernel<<<(T + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)kv, kv_ld, (const __nv_bfloat16*)w, eps, positions, rope_cache, cache, slots,
+  return (int)launch_pdl(mla_kv_prepare_kernel, dim3((T + 7) / 8), dim3(256), 0, st, (const __nv_bfloat16*)kv, kv_ld, (const __nv_bfloat16*)w, eps, positions, rope_cache, cache, slots,
                                                      T, R, rope, fp8);
-  return (int)cudaGetLastError();
 }
 
 extern "C" int ne_mla_q_finalize(const void* q_lat, const void* q_pe, long long pe_row_stride, int pe_head_stride, const long long* positions,
@@ -400,9 +401,8 @@ extern "C" int ne_mla_q_finalize(const void* q_lat, const void* q_pe, long long 
   if (T <= 0) return 0;
   if (R % 8 || rope % 2 || pe_row_stride % 2 || pe_head_stride % 2) return 1001;
   long long warps = (long long)T * H;
-  mla_q_finalize_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>((const __nv_bfloat16*)q_lat, (const __nv_bfloat16*)q_pe, pe_row_stride, pe_head_stride,
+  return (int)launch_pdl(mla_q_finalize_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, st, (const __nv_bfloat16*)q_lat, (const __nv_bfloat16*)q_pe, pe_row_stride, pe_head_stride,
                                                                      positions, rope_cache, (uint8_t*)q8, T, H, R, rope);
-  return (int)cudaGetLastError();
 }
 
 extern "C" int ne_add(const void* a, const void* b, void* y, long long n, cudaStream_t st) {

@@ -73,27 +73,31 @@ __global__ void __launch_bounds__(256) gdn_conv_state_kernel(const __nv_bfloat16
   }
 }
 
-// grid = (Hv, B), 256 threads = 8 warps.  Warp w owns state rows [w*R, (w+1)*R) of the [Dv = 8R, Dk = 32E] state; a lane holds
-// elements {e*32 + lane} of each row.  Per token: S *= exp(g); u = beta * (v - S k); S += u k^T; o = S q, evaluated from the two
+// grid = (Hv * (Dv / (NW * R)), B), NW warps.  Warp w of a CTA owns R rows of the [Dv, Dk = 32E] state; a lane holds elements
+// {e*32 + lane} of each row.  Per token: S *= exp(g); u = beta * (v - S k); S += u k^T; o = S q, evaluated from the two
 // dot products S_old.k and S_old.q taken in one pass (o = exp(g) S_old.q + u (k.q)).  Sequences of at least `skip_len` new tokens
-// are left to the chunked form.
-template <int E, int R>
-__global__ void __launch_bounds__(256) gdn_step_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
-                                                      const __nv_bfloat16* __restrict__ v, long long qk_ld, long long v_ld,
-                                                      const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b, long long ab_ld,
-                                                      const float* __restrict__ A_log, const float* __restrict__ dt_bias,
-                                                      float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
-                                                      const int* __restrict__ fresh, const __nv_bfloat16* __restrict__ z, long long z_ld,
-                                                      const __nv_bfloat16* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ out,
-                                                      long long out_ld, int Hv, int rep, int skip_len) {
-  constexpr int Dk = 32 * E, Dv = 8 * R;
-  __shared__ float s_o[Dv];
-  __shared__ float s_red[8];
-  const int h = blockIdx.x, seq = blockIdx.y, hk = h / rep;
+// are left to the chunked form.  kFuseNorm (the CTA holds the whole head): the gated RMSNorm is applied here and `out` is
+// bf16; otherwise several small CTAs share a head - more CTAs per SM overlap their load / compute / store phases better at
+// the 128 x 128 state size - and `out` receives the raw fp32 rows for the separate gated norm kernel.
+template <int E, int R, int NW, bool kFuseNorm>
+__global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                         const __nv_bfloat16* __restrict__ v, long long qk_ld, long long v_ld,
+                                                         const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b, long long ab_ld,
+                                                         const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                         float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
+                                                         const int* __restrict__ fresh, const __nv_bfloat16* __restrict__ z, long long z_ld,
+                                                         const __nv_bfloat16* __restrict__ norm_w, float eps, void* __restrict__ out,
+                                                         long long out_ld, int Hv, int Dv, int rep, int skip_len) {
+  constexpr int Dk = 32 * E, kRowsPerCta = NW * R;
+  __shared__ float s_o[kFuseNorm ? kRowsPerCta : 1];
+  __shared__ float s_red[NW];
+  const int bph = Dv / kRowsPerCta;                    // CTAs per head
+  const int h = blockIdx.x / bph, seq = blockIdx.y, hk = h / rep;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = (blockIdx.x % bph) * kRowsPerCta + warp * R;
   const int start = cu[seq], n = cu[seq + 1] - start;
   if (n <= 0 || n >= skip_len) return;
-  float* S_g = state + (((long long)slots[seq] * Hv + h) * Dv + warp * R) * Dk;
+  float* S_g = state + (((long long)slots[seq] * Hv + h) * Dv + row0) * Dk;
   float S[R][E];
   if (fresh[seq]) {
 #pragma unroll
@@ -133,31 +137,39 @@ __global__ void __launch_bounds__(256) gdn_step_kernel(const __nv_bfloat16* __re
 #pragma unroll
       for (int e = 0; e < E; e++) { pk += S[r][e] * kf[e]; pq += S[r][e] * qf[e]; }
       pk = warp_sum(pk); pq = warp_sum(pq);
-      const float vr = __bfloat162float(v[t * v_ld + h * Dv + warp * R + r]);
+      const float vr = __bfloat162float(v[t * v_ld + h * Dv + row0 + r]);
       const float u = beta * (vr - decay * pk);
 #pragma unroll
       for (int e = 0; e < E; e++) S[r][e] = decay * S[r][e] + u * kf[e];
       o[r] = decay * pq + u * kq;
+    }
+    if (!kFuseNorm) {
+      float* orow = reinterpret_cast<float*>(out) + t * out_ld + h * Dv + row0;
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < R; r++) orow[r] = o[r];
+      }
+      continue;
     }
     if (lane == 0) {
 #pragma unroll
       for (int r = 0; r < R; r++) s_o[warp * R + r] = o[r];
     }
     __syncthreads();
-    // gated RMSNorm over the head's Dv outputs
-    float val = threadIdx.x < Dv ? s_o[threadIdx.x] : 0.f;
+    // gated RMSNorm over the head's Dv outputs (the CTA holds them all: kRowsPerCta == Dv <= blockDim.x)
+    float val = (int)threadIdx.x < Dv ? s_o[threadIdx.x] : 0.f;
     float ss = warp_sum(val * val);
     if (lane == 0) s_red[warp] = ss;
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int wv = 0; wv < 8; wv++) tot += s_red[wv];
-    if (threadIdx.x < Dv) {
+    for (int wv = 0; wv < NW; wv++) tot += s_red[wv];
+    if ((int)threadIdx.x < Dv) {
       const int d = threadIdx.x;
       float xn = __bfloat162float(__float2bfloat16(val * rsqrtf(tot / (float)Dv + eps)));
       float y = __bfloat162float(__float2bfloat16(__bfloat162float(norm_w[d]) * xn));
       float zg = __bfloat162float(__float2bfloat16(silu_f(__bfloat162float(z[t * z_ld + h * Dv + d]))));
-      out[t * out_ld + h * Dv + d] = __float2bfloat16(y * zg);
+      reinterpret_cast<__nv_bfloat16*>(out)[t * out_ld + h * Dv + d] = __float2bfloat16(y * zg);
     }
     __syncthreads();
   }
@@ -231,22 +243,26 @@ extern "C" int ne_gdn_conv(const void* x, long long x_ld, const void* w, void* w
   return (int)cudaGetLastError();
 }
 
+// raw_out != 0: `out` is fp32 [T, Hv, Dv] without the gated norm (the caller runs ne_rmsnorm_gated); the 128 x 128 state size
+// always takes that form.  Returns 0, an argument error, or 1 when the caller asked for the fused form at a size that has none.
+extern "C" int ne_gdn_step_raw_only(int Dk, int Dv) { return (Dk == 128 && Dv == 128) ? 1 : 0; }
 extern "C" int ne_gdn_step(const void* q, const void* k, const void* v, long long qk_ld, long long v_ld, const void* a, const void* b, long long ab_ld,
                            const float* A_log, const float* dt_bias, float* state, const int* slots, const int* cu, const int* fresh,
                            const void* z, long long z_ld, const void* norm_w, float eps, void* out, long long out_ld, int B, int Hk, int Hv,
-                           int Dk, int Dv, int skip_len, cudaStream_t st) {
+                           int Dk, int Dv, int skip_len, int raw_out, cudaStream_t st) {
   if (B <= 0) return 0;
   if (Hv % Hk) return 1001;
   const int rep = Hv / Hk;
-#define NE_GDN_LAUNCH(E_, R_)                                                                                                              \
-  gdn_step_kernel<E_, R_><<<dim3(Hv, B), 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, qk_ld, v_ld, \
-                                                       (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, ab_ld, A_log, dt_bias, state, slots, cu, \
-                                                       fresh, (const __nv_bfloat16*)z, z_ld, (const __nv_bfloat16*)norm_w, eps,              \
-                                                       (__nv_bfloat16*)out, out_ld, Hv, rep, skip_len)
-  if (Dk == 128 && Dv == 128) NE_GDN_LAUNCH(4, 16);
-  else if (Dk == 128 && Dv == 64) NE_GDN_LAUNCH(4, 8);
-  else if (Dk == 64 && Dv == 64) NE_GDN_LAUNCH(2, 8);
-  else if (Dk == 32 && Dv == 32) NE_GDN_LAUNCH(1, 4);
+#define NE_GDN_LAUNCH(E_, R_, NW_, FUSE_)                                                                                                   \
+  gdn_step_kernel<E_, R_, NW_, FUSE_><<<dim3(Hv * (Dv / (NW_ * R_)), B), 32 * NW_, 0, st>>>(                                                 \
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, qk_ld, v_ld, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, \
+      ab_ld, A_log, dt_bias, state, slots, cu, fresh, (const __nv_bfloat16*)z, z_ld, (const __nv_bfloat16*)norm_w, eps, out, out_ld, Hv, Dv, rep, \
+      skip_len)
+  if (Dk == 128 && Dv == 128) { if (!raw_out) return 1001; NE_GDN_LAUNCH(4, 8, 4, false); }
+  else if (raw_out) return 1001;
+  else if (Dk == 128 && Dv == 64) NE_GDN_LAUNCH(4, 8, 8, true);
+  else if (Dk == 64 && Dv == 64) NE_GDN_LAUNCH(2, 8, 8, true);
+  else if (Dk == 32 && Dv == 32) NE_GDN_LAUNCH(1, 4, 8, true);
   else return 1001;
 #undef NE_GDN_LAUNCH
   return (int)cudaGetLastError();

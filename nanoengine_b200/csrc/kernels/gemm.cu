@@ -204,6 +204,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int tile0 = kSplit ? (int)blockIdx.x / split : (int)blockIdx.x;
   const int tile_stride = kSplit ? (int)gridDim.x / split : (int)gridDim.x;
 
+  // set-up that touches no global memory comes first: under a programmatic dependent launch it overlaps the previous kernel's tail
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
+    for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4 * kEpi); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_a64); tma_prefetch_desc(&tmap_a32); tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
+  pdl_wait();                                          // from here on the previous kernel's results may be read, and ours written
+  pdl_trigger();
   // the per-group row tables are read once per tile by three roles: keep them in shared memory, a global load per
   // lookup sits on the producer's critical path at every tile switch
   __shared__ int s_mm[kSchedCache], s_rs[kSchedCache];
@@ -240,14 +251,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     // the __syncthreads that ends the prologue publishes the table
   }
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
-    for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4 * kEpi); }
-    *abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_a64); tma_prefetch_desc(&tmap_a32); tma_prefetch_desc(&tmap_b);
-  }
-  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -590,8 +593,7 @@ static int launch(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs&
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, EpiCfg<BLOCK_N, kBS>::kThreads, Smem<BLOCK_N>::kBytes, st>>>(tas[0], tas[1], tas[2], tb, a);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(kern, dim3((unsigned)grid), dim3(EpiCfg<BLOCK_N, kBS>::kThreads), Smem<BLOCK_N>::kBytes, st, tas[0], tas[1], tas[2], tb, a);
 }
 
 // split-K form: `tiles` clusters of `split` CTAs
@@ -609,10 +611,10 @@ static int launch_split(const CUtensorMap* tas, const CUtensorMap& tb, const Gem
   cfg.blockDim = dim3(EpiCfg<BLOCK_N, kBS>::kThreads, 1, 1);
   cfg.dynamicSmemBytes = Smem<BLOCK_N>::kBytes;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  pdl_attr(cfg, attr, 1);
   return (int)cudaLaunchKernelEx(&cfg, kern, tas[0], tas[1], tas[2], tb, a);
 }
 

@@ -57,6 +57,17 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
   // the two output halves of a token sit in adjacent CTAs so the second reader of every KV page hits L2
   const int t = blockIdx.x >> 1, vhalf = blockIdx.x & 1, split = blockIdx.y;
 
+  if (threadIdx.x == 0) {
+    mbar_init(b_qfull, 1);
+    for (int i = 0; i < kPgStages; i++) { mbar_init(b_pgfull + 8 * i, 1); mbar_init(b_pgempty + 8 * i, 1); }
+    for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 4); }
+    for (int i = 0; i < 2; i++) { mbar_init(b_pfull + 8 * i, 4); mbar_init(b_pempty + 8 * i, 1); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+  pdl_wait(); pdl_trigger();      // dependent launch: the set-up above touches no global memory
+
   // sequence of this token, causal limit, page range of this split (uniform over the CTA)
   int lo = 0, hi = a.num_seqs;
   while (lo + 1 < hi) { int mid = (lo + hi) >> 1; if (a.cu_seqlens_q[mid] <= t) lo = mid; else hi = mid; }
@@ -70,15 +81,6 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
   const int n_tiles = max(0, pg_end - pg_begin);
   const int* bt = a.block_tables + (long long)seq * a.bt_stride;
 
-  if (threadIdx.x == 0) {
-    mbar_init(b_qfull, 1);
-    for (int i = 0; i < kPgStages; i++) { mbar_init(b_pgfull + 8 * i, 1); mbar_init(b_pgempty + 8 * i, 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 4); }
-    for (int i = 0; i < 2; i++) { mbar_init(b_pfull + 8 * i, 4); mbar_init(b_pempty + 8 * i, 1); }
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -343,8 +345,7 @@ extern "C" int ne_mla_fp8(const void* q8, const void* cache, int num_blocks, con
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs;
   a.T = T; a.H = H; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f; a.out = (__nv_bfloat16*)out; a.part = part; a.lse2 = lse2;
   dim3 grid(2 * T, splits, 1);
-  mla_fp8_kernel<<<grid, kMlaThreads, kMlaSmem, st>>>(tq128, tq64, tk128, tk64, a);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(mla_fp8_kernel, grid, dim3(kMlaThreads), kMlaSmem, st, tq128, tq64, tk128, tk64, a);
 }
 
 // ---- allocation-free entry point ----------------------------------------------------------------------

@@ -19,6 +19,7 @@ constexpr int kMaxExperts = 1024;
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx_out,
                                                        float* __restrict__ w_out, int T, int E, int top_k, int n_group, int topk_group,
                                                        int norm, float scale, int softmax, int planes) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   __shared__ float s_choice[4][kMaxExperts];
   __shared__ float s_score[4][kMaxExperts];
   __shared__ float s_group[4][64];
@@ -110,6 +111,7 @@ __global__ void moe_scan_kernel(const int* __restrict__ counts, int* __restrict_
 // of microseconds, a small cost against saving two launches and a memset per MoE layer in every decode step.
 __global__ void __launch_bounds__(1024) moe_count_scan_kernel(const int* __restrict__ idx, int* __restrict__ counts, int* __restrict__ slot,
                                                              int* __restrict__ row_start, int n_pairs, int expert_offset, int E, int align) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   __shared__ int s_cnt[kMaxExperts + 1];
   for (int e = threadIdx.x; e <= E; e += blockDim.x) s_cnt[e] = 0;
   __syncthreads();
@@ -142,6 +144,7 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* _
                                    const int* __restrict__ row_start, int* __restrict__ pos, __nv_bfloat16* __restrict__ a_bf16,
                                    uint8_t* __restrict__ a_q, float* __restrict__ a_s, int s_ld, int top_k, int H,
                                    int expert_offset, int E_local, int max_rows) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   extern __shared__ uint8_t s_raw[];
   uint32_t* s_q = reinterpret_cast<uint32_t*>(s_raw);                 // H bytes of e4m3
   float* s_sc = reinterpret_cast<float*>(s_raw + H);                  // H/128 scales
@@ -188,6 +191,7 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* _
 constexpr int kRouterCols = 1024;
 __global__ void __launch_bounds__(256) router_gemv_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, float* __restrict__ planes,
                                                          int T, int E, int H) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   __shared__ __align__(16) __nv_bfloat16 s_x[8][kRouterCols];
   const int t0 = blockIdx.x * 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h0 = blockIdx.z * kRouterCols;
@@ -231,6 +235,7 @@ __global__ void __launch_bounds__(256) router_gemv_kernel(const __nv_bfloat16* _
 // one CTA per token
 __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ add_in, __nv_bfloat16* __restrict__ out, int top_k, int H) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const int t = blockIdx.x;
   __shared__ int s_pos[64]; __shared__ float s_w[64];
   if (threadIdx.x < top_k) { s_pos[threadIdx.x] = pos[(long long)t * top_k + threadIdx.x]; s_w[threadIdx.x] = w[(long long)t * top_k + threadIdx.x]; }
@@ -280,8 +285,7 @@ extern "C" int ne_moe_route(const float* logits, const float* bias, int* idx, fl
                             int topk_group, int norm, float scale, int softmax, int planes, cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > kMaxExperts || top_k > 64 || n_group > 64 || (n_group > 1 && E % n_group) || planes < 1) return 1001;
-  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, bias, idx, w, T, E, top_k, n_group, topk_group, norm, scale, softmax, planes);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, st, logits, bias, idx, w, T, E, top_k, n_group, topk_group, norm, scale, softmax, planes);
 }
 
 // Outputs: counts [E_local], slot [T*K] (scratch), row_start [E_local+1], pos [T*K], and the
@@ -293,10 +297,10 @@ extern "C" int ne_moe_dispatch_local(const void* x, const int* idx, int* counts,
   if (E_local > kMaxExperts || H % 128) return 1001;
   int n = T * top_k;
   if (top_k > 64) return 1001;
-  moe_count_scan_kernel<<<1, 1024, 0, st>>>(idx, counts, slot, row_start, n, expert_offset, E_local, align);
-  moe_scatter_kernel<<<T, 256, (size_t)H + (H / 128) * 4, st>>>((const __nv_bfloat16*)x, idx, slot, row_start, pos, (__nv_bfloat16*)a_bf16,
-                                                                (uint8_t*)a_q, a_s, s_ld, top_k, H, expert_offset, E_local, max_rows);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(moe_count_scan_kernel, dim3(1), dim3(1024), 0, st, idx, counts, slot, row_start, n, expert_offset, E_local, align);
+  if (e != cudaSuccess) return (int)e;
+  return (int)launch_pdl(moe_scatter_kernel, dim3(T), dim3(256), (size_t)H + (H / 128) * 4, st, (const __nv_bfloat16*)x, idx, slot, row_start, pos,
+                         (__nv_bfloat16*)a_bf16, (uint8_t*)a_q, a_s, s_ld, top_k, H, expert_offset, E_local, max_rows);
 }
 
 extern "C" int ne_moe_combine_local(const void* y, const int* pos, const float* w, const void* add_in, void* out, int T, int top_k, int H,
@@ -304,8 +308,7 @@ extern "C" int ne_moe_combine_local(const void* y, const int* pos, const float* 
   if (T <= 0) return 0;
   if (H % 8 || top_k > 64) return 1001;
   const int slices = T >= 2048 ? 1 : (T >= 512 ? 2 : 4);      // enough CTAs per SM at decode sizes, one pass over the tables per token otherwise
-  moe_combine_kernel<<<dim3(T, slices), 256, 0, st>>>((const __nv_bfloat16*)y, pos, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, top_k, H);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(moe_combine_kernel, dim3(dim3(T, slices)), dim3(256), 0, st, (const __nv_bfloat16*)y, pos, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, top_k, H);
 }
 
 // x bf16 [T, H], w fp32 [E, H] -> partial logits fp32 [ne_router_planes(H), T, E]; their sum over the first axis is x . w^T
@@ -313,6 +316,5 @@ extern "C" int ne_router_planes(int H) { return (H + kRouterCols - 1) / kRouterC
 extern "C" int ne_router_gemv(const void* x, const float* w, float* planes, int T, int E, int H, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 128) return 1001;
-  router_gemv_kernel<<<dim3((T + 7) / 8, (E + 31) / 32, ne_router_planes(H)), 256, 0, st>>>((const __nv_bfloat16*)x, w, planes, T, E, H);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(router_gemv_kernel, dim3(dim3((T + 7) / 8, (E + 31) / 32, ne_router_planes(H))), dim3(256), 0, st, (const __nv_bfloat16*)x, w, planes, T, E, H);
 }

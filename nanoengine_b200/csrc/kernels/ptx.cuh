@@ -245,4 +245,39 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched with `launch_pdl` may be scheduled while the kernel before it in the stream is still draining; it runs its
+// own set-up (barrier init, TMEM allocation, descriptor prefetch: nothing that touches global memory), then `pdl_wait()`
+// blocks until the previous kernel has completed and its writes are visible, and `pdl_trigger()` right after lets the next
+// kernel do the same behind this one.  Triggering only after the wait keeps at most one waiting grid resident.  Both are
+// no-ops in a kernel launched the ordinary way, and an ordinary launch next in the stream still waits for full completion.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+}  // namespace ne
+
+#include <cstdlib>
+namespace ne {
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("NE_PDL"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v != 0;
+}
+// extra launch attributes (a cluster dimension) go first in `attrs`, which must have room for one more entry
+inline void pdl_attr(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attrs, unsigned n_before) {
+  if (pdl_enabled()) {
+    attrs[n_before].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_before].val.programmaticStreamSerializationAllowed = 1;
+    n_before++;
+  }
+  cfg.attrs = attrs; cfg.numAttrs = n_before;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attrs[1];
+  pdl_attr(cfg, attrs, 0);
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 }  // namespace ne

@@ -543,10 +543,26 @@ def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh
             o, S = ref.gdn_chunked(qn, kn, v[s:e].float(), g[s:e], beta[s:e], S0)
             state.index_copy_(0, sl, S[None])
             rmsnorm_gated(o, z[s:e], norm_w, eps, out[s:e])
+    raw = bool(lib().ne_gdn_step_raw_only(_c.c_int(Dk), _c.c_int(Dv)))     # large states: several CTAs per head, norm in its own kernel
+    if raw and max_q_len >= ref.GDN_CHUNK_MIN_TOKENS:
+        # rows of the long sequences were already normalised into `out`; the recurrent kernel's raw rows go to their own buffer
+        dst = torch.zeros(T, Hv, Dv, dtype=torch.float32, device=q.device)
+    else:
+        dst = torch.empty(T, Hv, Dv, dtype=torch.float32, device=q.device) if raw else out
     _ck(lib().ne_gdn_step(_p(q), _p(k), _p(v), _c.c_longlong(q.stride(0)), _c.c_longlong(v.stride(0)), _p(a), _p(b), _c.c_longlong(a.stride(0)),
                           _p(A_log), _p(dt_bias), _p(state), _p(slots), _p(cu), _p(fresh), _p(z), _c.c_longlong(z.stride(0)), _p(norm_w),
-                          _c.c_float(eps), _p(out), _c.c_longlong(out.stride(0)), _c.c_int(cu.numel() - 1), _c.c_int(Hk), _c.c_int(Hv), _c.c_int(Dk),
-                          _c.c_int(Dv), _c.c_int(skip), _st()), "ne_gdn_step")
+                          _c.c_float(eps), _p(dst), _c.c_longlong(dst.stride(0)), _c.c_int(cu.numel() - 1), _c.c_int(Hk), _c.c_int(Hv), _c.c_int(Dk),
+                          _c.c_int(Dv), _c.c_int(skip), _c.c_int(1 if raw else 0), _st()), "ne_gdn_step")
+    if raw:
+        if max_q_len >= ref.GDN_CHUNK_MIN_TOKENS:
+            short = torch.ones(T, dtype=torch.bool, device=q.device)
+            for i in range(len(cu_host) - 1):
+                if cu_host[i + 1] - cu_host[i] >= skip:
+                    short[cu_host[i]: cu_host[i + 1]] = False
+            normed = rmsnorm_gated(dst, z, norm_w, eps)
+            out[short] = normed[short]
+        else:
+            rmsnorm_gated(dst, z, norm_w, eps, out)
     return out.view(T, Hv * Dv)
 
 
