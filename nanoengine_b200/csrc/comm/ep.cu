@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpLayout L, cons
     if (L.fp8) {
       uint8_t* aq = peer_ptr(L, dst, L.off_aq) + row * H;
       float* as = reinterpret_cast<float*>(peer_ptr(L, dst, L.off_as)) + (long long)el * (H / 128) * cap + slot;
+#pragma unroll 4
       for (int g = 0; g < H / 128; g++) {
         uint2 v = *reinterpret_cast<const uint2*>(xr + g * 128 + lane * 4);
         float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
@@ -114,13 +115,21 @@ __global__ void __launch_bounds__(1024) ep_wait_build_kernel(const EpLayout L, i
     s_cnt[e] = c; counts[e] = c; cnt[e] = 0;
   }
   __syncthreads();
+  // one flat loop over (expert, slot) up to the fullest expert's count: a loop per expert puts one dependent global load per
+  // expert on the critical path of this single CTA (32 experts = ~10 us)
+  __shared__ int s_max;
+  if (threadIdx.x == 0) s_max = 0;
+  __syncthreads();
+  for (int e = threadIdx.x; e < L.E_local; e += blockDim.x) atomicMax(&s_max, s_cnt[e]);
+  __syncthreads();
+  const int width = s_max;
   const long long* info = reinterpret_cast<const long long*>(peer_ptr(L, L.rank, L.off_info));
-  for (int e = 0; e < L.E_local; e++) {
-    for (int s = threadIdx.x; s < s_cnt[e]; s += blockDim.x) {
-      const long long v = info[(long long)e * L.cap + s];
-      const int src = (int)(v >> 32); const long long pair = v & 0xffffffffll;
-      row_dst[(long long)e * L.cap + s] = (long long)(L.peer_base[src] + L.off_ret + pair * L.H * 2);
-    }
+  for (int i = threadIdx.x; i < L.E_local * width; i += blockDim.x) {
+    const int e = i / width, sl = i - e * width;
+    if (sl >= s_cnt[e]) continue;
+    const long long v = info[(long long)e * L.cap + sl];
+    const int src = (int)(v >> 32); const long long pair = v & 0xffffffffll;
+    row_dst[(long long)e * L.cap + sl] = (long long)(L.peer_base[src] + L.off_ret + pair * L.H * 2);
   }
 }
 
@@ -146,7 +155,11 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const EpLayout L, const 
   if ((int)threadIdx.x < K) { s_use[threadIdx.x] = pair_ok[(long long)t * K + threadIdx.x]; s_w[threadIdx.x] = w[(long long)t * K + threadIdx.x]; }
   __syncthreads();
   const __nv_bfloat16* ret = reinterpret_cast<const __nv_bfloat16*>(peer_ptr(L, L.rank, L.off_ret));
-  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+  // blockIdx.y splits the row into column slices so a decode batch fills the SMs (one CTA per token would leave some idle and
+  // keep too few loads in flight on the others)
+  const int slice = (((H + 7) / 8 + gridDim.y - 1) / gridDim.y) * 8;
+  const int c_end = min(H, ((int)blockIdx.y + 1) * slice);
+  for (int c = blockIdx.y * slice + threadIdx.x * 8; c < c_end; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (s_ok) {
       // eight returned rows are fetched before any is used: the loads are independent and the kernel is latency-bound
@@ -215,7 +228,8 @@ extern "C" int ne_ep_reduce(const EpLayout* L, const int* pair_ok, const float* 
                             int spin_limit, cudaStream_t st) {
   if (T > 0) {
     if (L->top_k > 64 || L->H % 8) return 1001;
-    ep_reduce_kernel<<<T, 256, 0, st>>>(*L, pair_ok, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, epoch_ptr, spin_limit);
+    const int slices = T >= 2048 ? 1 : (T >= 512 ? 2 : 4);
+    ep_reduce_kernel<<<dim3(T, slices), 256, 0, st>>>(*L, pair_ok, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, epoch_ptr, spin_limit);
   }
   return (int)cudaGetLastError();
 }
