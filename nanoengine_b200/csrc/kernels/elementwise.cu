@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(256) mla_q_finalize_kernel(const __nv_bfloat16
   const int D = R + rope;
   const __nv_bfloat16* src = q_lat + wid * R;
   uint8_t* dst = q8 + wid * D;
-  for (int c = lane * 8; c < R; c += 256) {
+  for (int c = lane * 8; q_lat && c < R; c += 256) {        // q_lat == nullptr: the producing GEMM already wrote the e4m3 latent part
     const uint4 v = *reinterpret_cast<const uint4*>(src + c);
     const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c2 = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
     *reinterpret_cast<uint2*>(dst + c) = make_uint2(pack_e4m3x4(a.x, a.y, b.x, b.y), pack_e4m3x4(c2.x, c2.y, d.x, d.y));

@@ -45,7 +45,7 @@ struct GemmArgs {
   void* D; long long ldd; long long d_group_stride;   // in elements
   const float* sa; int sa_ld; long long sa_group_stride;   // activation scales [groups][K/128][sa_ld]
   const float* sb; long long sb_group_stride;              // weight scales [groups][ceil(N/128)][K/128]
-  int out_fp32;
+  int out_fp32;                         // 0: bf16 output, 1: fp32, 2: e4m3 (clamped cast, no scale; plain bf16 GEMMs only)
   const long long* row_dst;             // optional scatter epilogue: absolute address of every output row (bf16, may be peer memory),
   long long rd_group_stride;            // indexed [group * rd_group_stride + row]; used by the MoE combine
 };
@@ -458,7 +458,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __nv_bfloat16* dbf = (args.row_dst && row_ok) ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0
                                                       : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
         EpiRows erows;
-        if (!kSplit && !args.out_fp32) erows = epi_rows(row_ok, dbf);
+        if (!kSplit && args.out_fp32 == 0) erows = epi_rows(row_ok, dbf);
 #pragma unroll
         for (int c = 0; c < BLOCK_N / 32; c++) {
           uint32_t r[32];
@@ -470,6 +470,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int q = 0; q < 8; q++)
               P[row_in_tile * (BLOCK_N / 4) + ((c * 8 + q) ^ (row_in_tile & 7))] =
                   make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
+          } else if (args.out_fp32 == 2) {
+            // 32 columns = 32 bytes of this thread's row: one full sector, written straight from registers
+            if (row_ok && n0 + c * 32 < args.N) {
+              uint4* p = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(args.D) + off + c * 32);
+              uint32_t w[8];
+#pragma unroll
+              for (int q = 0; q < 8; q++)
+                w[q] = pack_e4m3x4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
+              p[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              p[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
           } else if (args.out_fp32) {
             if (row_ok) {
 #pragma unroll
@@ -656,14 +667,15 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
   const bool fp8 = dtype == 1;
   if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % 16 != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
   if (fp8 && (K % 128 != 0 || !sa || !sb)) return 1002;
-  if ((ldd * (out_fp32 ? 4 : 2)) % 16 != 0) return 1003;
+  if ((ldd * (out_fp32 == 1 ? 4 : (out_fp32 == 2 ? 1 : 2))) % 16 != 0) return 1003;
+  if (out_fp32 == 2 && (dtype == 1 || N % 32 != 0)) return 1006;      // e4m3 output: plain bf16 GEMMs, whole 32-column chunks
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
   // pick the widest N tile that still yields about one tile per SM; fp8 promotion keeps BLOCK_N accumulators in registers
   int bn = block_n_hint;
   int split = 1;
   const int num_kb_host = (K * (fp8 ? 1 : 2) + kKBytes - 1) / kKBytes;
   const bool can_split = groups == 1 && !row_start && !masked_m && !row_dst && m_blocks == 1 && N % 4 == 0 &&
-                         (K * (fp8 ? 1 : 2)) % kKBytes == 0 && g_split_k_enabled;
+                         (K * (fp8 ? 1 : 2)) % kKBytes == 0 && g_split_k_enabled && out_fp32 != 2;
   if (bn == 0 && can_split) {
     plan_small_m(N, num_kb_host, fp8, &bn, &split);
   } else if (bn == 0) {

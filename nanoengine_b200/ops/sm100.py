@@ -65,7 +65,7 @@ def clear_kernel_status():
 def _gemm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, row_start, fp8, sa, sa_ld, sa_gs, sb, out_fp32, bn=0, row_dst=None):
     rc = lib().ne_gemm(_p(A), _c.c_longlong(lda), _c.c_longlong(a_gs), _p(B), _p(D), _c.c_longlong(ldd), _c.c_longlong(d_gs),
                        _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), _p(masked_m), _p(row_start), _c.c_int(1 if fp8 else 0),
-                       _p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(1 if out_fp32 else 0), _c.c_int(bn), _p(row_dst), _st())
+                       _p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(int(out_fp32)), _c.c_int(bn), _p(row_dst), _st())     # output: 0 bf16, 1 fp32, 2 e4m3
     _ck(rc, "ne_gemm")
 
 
@@ -170,7 +170,8 @@ def lm_head(hidden: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x [T, H, A] (any row/head strides, unit inner stride), w [H, A, B] -> [T, H, B]: a grouped GEMM with one group per head."""
+    """x [T, H, A] (any row/head strides, unit inner stride), w [H, A, B] -> [T, H, B]: a grouped GEMM with one group per head.
+    `out` may be a strided view; a one-byte `out` (uint8 / e4m3) makes the epilogue write clamped e4m3 instead of bf16."""
     T, H, A = x.shape
     Bd = w.shape[2]
     wt = _cached(w, "t", lambda t: t.to(torch.bfloat16).transpose(1, 2).contiguous())      # [H, B, A], K-major
@@ -178,9 +179,11 @@ def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = N
         x = x.to(torch.bfloat16).contiguous()
     if out is None:
         out = torch.empty(T, H, Bd, dtype=torch.bfloat16, device=x.device)
-    assert out.stride(2) == 1 and (out.stride(0) * 2) % 16 == 0 and (out.stride(1) * 2) % 16 == 0 and out.data_ptr() % 16 == 0
+    es = out.element_size()
+    assert es in (1, 2) and out.stride(2) == 1 and (out.stride(0) * es) % 16 == 0 and (out.stride(1) * es) % 16 == 0 and out.data_ptr() % 16 == 0
     if T > 0:
-        _gemm(x, x.stride(0), x.stride(1), wt, out, out.stride(0), out.stride(1), T, Bd, A, H, None, None, False, None, 0, 0, None, False)
+        _gemm(x, x.stride(0), x.stride(1), wt, out, out.stride(0), out.stride(1), T, Bd, A, H, None, None, False, None, 0, 0, None,
+              2 if es == 1 else 0)
     return out
 
 
@@ -271,19 +274,18 @@ def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, 
 def mla_query(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, rope_cache: torch.Tensor, nope: int, kv_cache: torch.Tensor,
               dense: bool = True) -> torch.Tensor:
     """Absorbed MLA query.  For the dense fp8 attention kernel (fp8 cache of 64-token pages, 512 + 64 wide rows, at most
-    128 heads) the result is e4m3 [T, H, 576]: the latent product lands in a bf16 scratch and one kernel applies RoPE to
-    the tail and casts both parts, instead of a RoPE pass into a bf16 query followed by a cast pass over all of it."""
+    128 heads) the result is e4m3 [T, H, 576]: the per-head GEMM's epilogue writes the latent part as e4m3 straight into it
+    and one small kernel rotates and casts the 64-wide tail, instead of a bf16 latent query, a RoPE pass and a cast pass."""
     T, H, _ = q.shape
     R = kc.shape[2]
     rope = q.shape[2] - nope
     if not (dense and kv_cache.dtype == FP8 and R == 512 and rope == 64 and kv_cache.shape[1] == 64 and H <= 128 and T > 0):
         return mla_absorb_rope(q, kc, positions, rope_cache, nope)
-    q_lat = torch.empty(T, H, R, dtype=torch.bfloat16, device=q.device)
-    bmm_absorb(q[..., :nope], kc, out=q_lat)
     q8 = torch.empty(T, H, R + rope, dtype=torch.uint8, device=q.device)
+    bmm_absorb(q[..., :nope], kc, out=q8[..., :R])
     pe = q[..., nope:]
     pos = positions if positions.dtype == torch.int64 else positions.long()
-    _ck(lib().ne_mla_q_finalize(_p(q_lat), _p(pe), _c.c_longlong(pe.stride(0)), _c.c_int(pe.stride(1)), _p(pos), _p(rope_cache), _p(q8),
+    _ck(lib().ne_mla_q_finalize(_p(None), _p(pe), _c.c_longlong(pe.stride(0)), _c.c_int(pe.stride(1)), _p(pos), _p(rope_cache), _p(q8),
                                 _c.c_int(T), _c.c_int(H), _c.c_int(R), _c.c_int(rope), _st()), "ne_mla_q_finalize")
     return q8.view(FP8)
 

@@ -252,6 +252,22 @@ def test_bmm_absorb_on_strided_heads(k):
     assert _rel(k.bmm_absorb(o, vc), ref.bmm_absorb(o, vc)) < 5e-3
 
 
+@pytest.mark.parametrize("T", [3, 128, 300])
+def test_bmm_absorb_writes_e4m3_into_a_strided_view(k, T):
+    """The e4m3 epilogue: clamped cast of the fp32 accumulator into the first 512 bytes of 576-byte rows; the tail is untouched."""
+    torch.manual_seed(11)
+    H = 16
+    q = torch.randn(T, H, 192, device="cuda", dtype=torch.bfloat16) * 2
+    kc = (torch.randn(H, 128, 512, device="cuda") * 0.3).to(torch.bfloat16)
+    q8 = torch.full((T, H, 576), 0x55, dtype=torch.uint8, device="cuda")
+    k.bmm_absorb(q[..., :128], kc, out=q8[..., :512])
+    want = ref.bmm_absorb(q[..., :128], kc).float().clamp(-448, 448).to(FP8).float()
+    got = q8[..., :512].contiguous().view(FP8).float()
+    assert _rel(got, want) < 3e-2                          # one e4m3 step where bf16 rounding first lands on the other side of a tie
+    assert (got - want).abs().max() <= want.abs().max() * 0.13
+    assert bool((q8[..., 512:] == 0x55).all())
+
+
 @pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("T,E,topk", [(1, 8, 2), (64, 32, 8), (700, 16, 4)])
 def test_moe_experts_local(k, T, E, topk, fp8):
