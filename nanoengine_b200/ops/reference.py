@@ -582,7 +582,8 @@ def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh
 
     q, k [T, Hk, Dk] and v [T, Hv, Dv] are the convolved projections (Hv a multiple of Hk: value head h reads key head
     h // (Hv/Hk)); a, b [T, Hv]; state [S, Hv, Dv, Dk] fp32 (this layer's pool); slots [B]; cu_seqlens [B+1]; fresh [B];
-    z [T, Hv, Dv] the output gate.  Returns [T, Hv*Dv] in v's dtype."""
+    z [T, Hv, Dv] the output gate.  Returns [T, Hv*Dv] in v's dtype.  `max_q_len` and `cu_host` are planning hints for the
+    CUDA body (which form to run, sequence boundaries without a device read-back); unused here."""
     T, Hk, Dk = q.shape
     Hv, Dv = v.shape[1], v.shape[2]
     rep = Hv // Hk
