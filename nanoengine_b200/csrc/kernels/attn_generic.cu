@@ -35,6 +35,7 @@ __device__ __forceinline__ float load_kv(const void* base, long long idx, int fp
 }
 
 __global__ void __launch_bounds__(128) attn_generic_kernel(const AttnArgs a) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   extern __shared__ float sm[];
   // layout: q [4][Dk] | ktile [32][Dk+1] | vtile [32][Dv+1] (only when V is separate)
   const int Dk = a.Dk, Dv = a.Dv;
@@ -228,8 +229,7 @@ extern "C" int ne_attn_generic(const void* q, long long q_tok_stride, int q_head
     configured = smem;
   }
   dim3 grid(T, (H + kHeadsPerCta - 1) / kHeadsPerCta);
-  attn_generic_kernel<<<grid, 128, smem, st>>>(a);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(attn_generic_kernel, dim3(grid), dim3(128), smem, st, a);
 }
 
 extern "C" int ne_attn_merge(const float* part, const float* lse2, void* out, int splits, long long rows, int D, int out_row_stride, cudaStream_t st) {

@@ -213,6 +213,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
 __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, long long row_stride, int head_stride, __nv_bfloat16* __restrict__ y,
                             long long y_row_stride, int y_head_stride, int heads, int off, int D,
                             const long long* __restrict__ positions, const float* __restrict__ cache, int interleaved, int T) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   int half = D / 2;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long total = (long long)T * heads * half;
@@ -327,6 +328,7 @@ __global__ void mla_kv_store_kernel(const __nv_bfloat16* __restrict__ ckv, long 
 
 // y[t, :] = a[t, :] + b[t, :] (bf16), used where a fused epilogue is not available
 __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* y, long long n) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
   uint4 av = *reinterpret_cast<const uint4*>(a + i), bv = *reinterpret_cast<const uint4*>(b + i);
@@ -375,9 +377,8 @@ extern "C" int ne_rope(const void* x, long long row_stride, int head_stride, voi
                        int off, int D, const long long* positions, const float* cache, int interleaved, int T, cudaStream_t st) {
   if (T <= 0) return 0;
   long long total = (long long)T * heads * (D / 2);
-  rope_kernel<<<(int)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, row_stride, head_stride, (__nv_bfloat16*)y, y_row_stride,
+  return (int)launch_pdl(rope_kernel, dim3((int)((total + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)x, row_stride, head_stride, (__nv_bfloat16*)y, y_row_stride,
                                                           y_head_stride, heads, off, D, positions, cache, interleaved, T);
-  return (int)cudaGetLastError();
 }
 
 extern "C" int ne_mla_kv_store(const void* ckv, long long ckv_ld, const void* kpe, long long kpe_ld, void* cache, const long long* slots,
@@ -408,6 +409,5 @@ extern "C" int ne_mla_q_finalize(const void* q_lat, const void* q_pe, long long 
 extern "C" int ne_add(const void* a, const void* b, void* y, long long n, cudaStream_t st) {
   if (n <= 0) return 0;
   if (n % 8) return 1001;
-  add_kernel<<<(int)((n / 8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(add_kernel, dim3((int)((n / 8 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n);
 }

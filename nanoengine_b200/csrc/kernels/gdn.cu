@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(256) gdn_conv_kernel(const __nv_bfloat16* __re
                                                       __nv_bfloat16* __restrict__ window, const int* __restrict__ slots,
                                                       const int* __restrict__ cu, const int* __restrict__ fresh, __nv_bfloat16* __restrict__ y,
                                                       long long y_ld, int B, int C, int K, int fused_state) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   __shared__ int s_seq;
   const int t = blockIdx.x;
   if (threadIdx.x == 0) {
@@ -55,6 +56,7 @@ __global__ void __launch_bounds__(256) gdn_conv_kernel(const __nv_bfloat16* __re
 __global__ void __launch_bounds__(256) gdn_conv_state_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, __nv_bfloat16* __restrict__ window,
                                                             const int* __restrict__ slots, const int* __restrict__ cu,
                                                             const int* __restrict__ fresh, int C, int K) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const int seq = blockIdx.x;
   const int start = cu[seq], n = cu[seq + 1] - start;
   if (n <= 0) return;
@@ -88,6 +90,7 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
                                                          const int* __restrict__ fresh, const __nv_bfloat16* __restrict__ z, long long z_ld,
                                                          const __nv_bfloat16* __restrict__ norm_w, float eps, void* __restrict__ out,
                                                          long long out_ld, int Hv, int Dv, int rep, int skip_len) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   constexpr int Dk = 32 * E, kRowsPerCta = NW * R;
   __shared__ float s_o[kFuseNorm ? kRowsPerCta : 1];
   __shared__ float s_red[NW];
@@ -183,6 +186,7 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
 __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ z, long long z_ld,
                                                            const __nv_bfloat16* __restrict__ w, float eps, __nv_bfloat16* __restrict__ out,
                                                            long long out_ld, long long rows, int heads, int D) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -204,6 +208,7 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const float* __restr
 // out = o * sigmoid(gate); o, out [T, heads, D] contiguous, gate a strided view (row and head strides in elements); two columns per thread
 __global__ void __launch_bounds__(256) sigmoid_gate_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ gate, long long g_row,
                                                           long long g_head, __nv_bfloat16* __restrict__ out, long long pairs, int heads, int D) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= pairs) return;
   const int half = D / 2;
@@ -225,9 +230,8 @@ extern "C" int ne_sigmoid_gate(const void* o, const void* gate, long long g_row,
   long long pairs = T * heads * (D / 2);
   if (pairs <= 0) return 0;
   if (D % 2) return 1001;
-  sigmoid_gate_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)gate, g_row, g_head,
+  return (int)launch_pdl(sigmoid_gate_kernel, dim3((unsigned)((pairs + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)o, (const __nv_bfloat16*)gate, g_row, g_head,
                                                                       (__nv_bfloat16*)out, pairs, heads, D);
-  return (int)cudaGetLastError();
 }
 
 extern "C" int ne_gdn_conv(const void* x, long long x_ld, const void* w, void* window, const int* slots, const int* cu, const int* fresh, void* y,
@@ -236,11 +240,12 @@ extern "C" int ne_gdn_conv(const void* x, long long x_ld, const void* w, void* w
   if (C % 2 || x_ld % 2 || y_ld % 2 || K < 2 || K > 8) return 1001;
   int gy = (C / 2 + 255) / 256;
   if (gy > 8) gy = 8;
-  gdn_conv_kernel<<<dim3(T, gy), 256, 0, st>>>((const __nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)w, (__nv_bfloat16*)window, slots, cu, fresh,
-                                               (__nv_bfloat16*)y, y_ld, B, C, K, uniform_one);
-  if (!uniform_one)
-    gdn_conv_state_kernel<<<dim3(B, gy), 256, 0, st>>>((const __nv_bfloat16*)x, x_ld, (__nv_bfloat16*)window, slots, cu, fresh, C, K);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(gdn_conv_kernel, dim3(T, gy), dim3(256), 0, st, (const __nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)w,
+                             (__nv_bfloat16*)window, slots, cu, fresh, (__nv_bfloat16*)y, y_ld, B, C, K, uniform_one);
+  if (e != cudaSuccess || uniform_one) return (int)e;
+  // the window update starts only after the convolution above has read the old window: its writes follow its own dependency wait
+  return (int)launch_pdl(gdn_conv_state_kernel, dim3(B, gy), dim3(256), 0, st, (const __nv_bfloat16*)x, x_ld, (__nv_bfloat16*)window, slots, cu,
+                         fresh, C, K);
 }
 
 // raw_out != 0: `out` is fp32 [T, Hv, Dv] without the gated norm (the caller runs ne_rmsnorm_gated); the 128 x 128 state size
@@ -254,7 +259,7 @@ extern "C" int ne_gdn_step(const void* q, const void* k, const void* v, long lon
   if (Hv % Hk) return 1001;
   const int rep = Hv / Hk;
 #define NE_GDN_LAUNCH(E_, R_, NW_, FUSE_)                                                                                                   \
-  gdn_step_kernel<E_, R_, NW_, FUSE_><<<dim3(Hv * (Dv / (NW_ * R_)), B), 32 * NW_, 0, st>>>(                                                 \
+  launch_pdl(gdn_step_kernel<E_, R_, NW_, FUSE_>, dim3(Hv * (Dv / (NW_ * R_)), B), dim3(32 * NW_), 0, st,                                \
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, qk_ld, v_ld, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, \
       ab_ld, A_log, dt_bias, state, slots, cu, fresh, (const __nv_bfloat16*)z, z_ld, (const __nv_bfloat16*)norm_w, eps, out, out_ld, Hv, Dv, rep, \
       skip_len)
@@ -272,7 +277,6 @@ extern "C" int ne_rmsnorm_gated(const float* x, const void* z, long long z_ld, c
                                 int heads, int D, cudaStream_t st) {
   long long rows = tokens * heads;
   if (rows <= 0) return 0;
-  rmsnorm_gated_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(x, (const __nv_bfloat16*)z, z_ld, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out,
+  return (int)launch_pdl(rmsnorm_gated_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, st, x, (const __nv_bfloat16*)z, z_ld, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out,
                                                                   out_ld, rows, heads, D);
-  return (int)cudaGetLastError();
 }

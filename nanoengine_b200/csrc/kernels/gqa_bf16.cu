@@ -42,6 +42,7 @@ struct GqaArgs {
 __global__ void __launch_bounds__(kGqaThreads, 1)
 gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constant__ CUtensorMap tk_map, const __grid_constant__ CUtensorMap tv_map,
                 const GqaArgs a) {
+  pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -348,6 +349,5 @@ extern "C" int ne_gqa_bf16(const void* q, const void* k_cache, const void* v_cac
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs;
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.g = g; a.tq = tq; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f;
   a.out = (__nv_bfloat16*)out; a.part = part; a.lse2 = lse2;
-  gqa_bf16_kernel<<<dim3((unsigned)max_tiles, (unsigned)Hkv, (unsigned)splits), kGqaThreads, kGqaSmem, st>>>(mq, mk, mv, a);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(gqa_bf16_kernel, dim3(dim3((unsigned)max_tiles, (unsigned)Hkv, (unsigned)splits)), dim3(kGqaThreads), kGqaSmem, st, mq, mk, mv, a);
 }
