@@ -78,6 +78,8 @@ def _llm(mc, **kw):
     base = dict(model="tiny-qwen3.5", model_config=mc, dummy_weight=True, dtype="float32", device="cpu", kvcache_block_size=16,
                 num_kvcache_blocks=64, max_num_seqs=8)
     base.update(kw)
+    if mc is None:
+        base.pop("model_config"); base.pop("dummy_weight")
     return LLM(Config(**base))
 
 
@@ -118,3 +120,17 @@ def test_hf_config_of_the_hybrid_family_is_understood():
     assert c.is_hybrid_gdn and not c.is_mla and c.n_routed_experts == 4 and c.rope_theta == 1e7 and c.partial_rotary_factor == 0.25
     assert [c.layer_type(i) for i in range(8)].count("full_attention") == 2 and c.layer_type(3) == "full_attention"
     assert c.norm_unit_offset and c.attn_output_gate and c.qk_norm
+
+
+def test_hybrid_checkpoint_round_trip(tmp_path):
+    """A checkpoint directory of the hybrid family (config.json + safetensors, with the non-`.weight` tensors A_log and dt_bias)
+    loads into the same model as the tensors fed directly."""
+    from nanoengine_b200.models.weights import random_hf_weights, save_hf_checkpoint
+    mc = tiny_qwen3_5(moe=True)
+    save_hf_checkpoint(str(tmp_path), mc, random_hf_weights(mc, seed=3))
+    from_disk = _llm(None, model=str(tmp_path))
+    direct = _llm(mc)
+    direct.engine.executor.runner.load_weights(random_hf_weights(mc, seed=3))
+    prompts = [list(range(5, 40))]
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    assert from_disk.generate(prompts, sp)[0]["token_ids"] == direct.generate(prompts, sp)[0]["token_ids"]
