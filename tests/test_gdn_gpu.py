@@ -182,3 +182,22 @@ def test_hybrid_model_logits_match_fp32_cpu_model(moe):
         assert _rel(lg, lc) < (8e-2 if moe else 5e-2), f"step {step}: {_rel(lg, lc)}"      # eight bf16 experts per token add their rounding
         nxt = lc.argmax(-1).tolist()                       # both models continue with the fp32 model's tokens
         cur = [s + [t] for s, t in zip(cur, nxt)]
+
+
+def test_hybrid_model_with_fp8_weights_runs_graph_and_eager():
+    """fp8 block-scaled projections and experts under the delta-net and gated-attention layers (pre-quantised activations from the
+    fused norms included): graph replay and eager launches must produce the same tokens."""
+    from nanoengine_b200 import Config, LLM, SamplingParams
+    from nanoengine_b200.models.config import tiny_qwen3_5
+    mc = tiny_qwen3_5(moe=True, hidden_size=256, head_dim=128, num_attention_heads=4, num_key_value_heads=2, linear_key_head_dim=64,
+                      linear_value_head_dim=64, intermediate_size=512, moe_intermediate_size=128, shared_expert_intermediate_size=128,
+                      quant="fp8")
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (70, 12)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = []
+    for eager in (True, False):
+        llm = LLM(Config(model="tiny-qwen3.5", model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kvcache_block_size=64,
+                         num_kvcache_blocks=32, max_num_seqs=4, enforce_eager=eager))
+        outs.append([o["token_ids"] for o in llm.generate(prompts, sp)])
+    assert outs[0] == outs[1] and all(len(o) == 6 for o in outs[0])
