@@ -33,6 +33,19 @@ def test_dp2_ep2_matches_single_rank():
     assert got == want
 
 
+def test_dp2_ep2_hybrid_delta_net_moe_matches_single_rank():
+    """The hybrid family under attention-DP + EP: every rank keeps its own recurrent-state pool; a rank without work runs a dummy
+    batch on the scratch state slot."""
+    from nanoengine_b200.models.config import tiny_qwen3_5
+    base = dict(model="tiny-qwen3.5", model_config=tiny_qwen3_5(moe=True), dummy_weight=True, dtype="float32", device="cpu",
+                kvcache_block_size=16, max_num_seqs=8, num_kvcache_blocks=64)
+    prompts = _prompts(3, 40, 2, 512)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = _run(Config(**base), prompts, sp)
+    got = _run(Config(**base, attention_dp=2, ffn_ep=2), prompts, sp)
+    assert got == want
+
+
 def _qwen_cfg():
     return ModelConfig(architecture="Qwen3MoeForCausalLM", vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=8,
                        num_key_value_heads=2, head_dim=16, rope_theta=1e6, max_position_embeddings=1024, intermediate_size=256,
