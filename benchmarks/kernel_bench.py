@@ -155,7 +155,8 @@ def case_absorb(T, which, H=128, nope=128, rope=64, R=512, v=128):
     else:
         x, w = torch.randn(T, H, R, device="cuda", dtype=torch.bfloat16), (torch.randn(H, R, v, device="cuda") * 0.05).to(torch.bfloat16)
     out = torch.empty(T, H, w.shape[2], device="cuda", dtype=torch.bfloat16)
-    fn = lambda: sm100.bmm_absorb(x, w, out)
+    wt = sm100.kmajor(w)
+    fn = lambda: sm100.bmm_absorb(x, w, out, wt=wt)
     return fn, w.numel() * 2 + T * H * (w.shape[1] + w.shape[2]) * 2, 2.0 * T * H * w.shape[1] * w.shape[2]
 
 

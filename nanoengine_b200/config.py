@@ -23,7 +23,7 @@ class Config:
     device: str = "auto"                     # "auto" | "cuda" | "cpu"
     seed: int = 0
     dummy_weight: bool = False               # random-init weights in the HF layout
-    dummy_prefill: bool = False              # decode engine fabricates KV for arriving prompts (no prefill peer)
+    dummy_prefill: bool = False              # HiSparse decode engines only: fabricate KV for arriving prompts (no prefill peer)
     # scheduling
     max_num_batched_tokens: int = 16384
     max_num_seqs: int = 16
@@ -59,8 +59,8 @@ class Config:
     executor_backend: str = "auto"           # auto | inproc | mp | spmd (one engine per torchrun rank)
     use_fused_comm: bool = True              # fused compute+collective kernels when peers are reachable
     peer_timeout_s: float = 120.0            # SPMD: how long the per-step host rendezvous waits for a silent peer
-    kernel_status_every: int = 32            # worker: read the kernels' status words every this many steps (0 = never)
-    dummy_eplb: bool = False
+    kernel_status_every: int = 1             # worker: read the kernels' status words every this many steps (0 = never)
+    dummy_eplb: bool = False                 # routers deal expert ids evenly over the EP ranks (capacity runs with random-init routers)
     # observability
     log_level: str = "INFO"
     step_timing: bool = False
@@ -126,6 +126,12 @@ class Config:
             self.enforce_eager = True
         if self.enable_hisparse and not mc.has_indexer:
             raise ValueError("enable_hisparse needs a DSA model (lightning indexer)")
+        if self.enable_hisparse:
+            raise ValueError("enable_hisparse: the hot/cold sparse-KV tier is not available in this build")
+        if self.dummy_prefill and not self.enable_hisparse:
+            raise ValueError("dummy_prefill only applies to a HiSparse decode engine (enable_hisparse=True)")
+        if self.ffn_tp != 1 or self.ffn_dp != 1:
+            raise ValueError("ffn_tp / ffn_dp > 1 are not supported: experts are sharded by ffn_ep only")
         if self.max_model_len is None:
             self.max_model_len = mc.max_position_embeddings
         if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1:

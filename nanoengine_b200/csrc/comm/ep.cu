@@ -9,14 +9,16 @@
 //   ret   bf16  [T_max*K, H]                  expert outputs coming back, written by the down-proj GEMM EPILOGUE of the owners
 //   arrive/done flags int32 [world] each, epoch-tagged
 //
-// One MoE layer is the stream-ordered sequence
+// One MoE layer is five launches in stream order:
 //   ep_dispatch   (sender)   slot = remote atomicAdd(cnt[e]); quantise + peer-store row, scales, info; last CTA raises `arrive` at all peers
-//   ep_wait_build (owner)    bounded wait for every peer's `arrive`; counts -> masked_m, reset cnt; info -> per-row return addresses
-//   grouped GEMM gate_up -> SwiGLU + requant -> grouped GEMM down whose epilogue stores each output row straight into the source
-//                            GPU's `ret` buffer (row_dst table), i.e. the combine "send" costs no extra pass
-//   ep_signal     (owner)    raises `done` at all peers
-//   ep_reduce     (sender)   bounded wait for every peer's `done`; out[t] = sum_k w[t,k] * ret[t*K+k] (+ shared expert output)
-//   ep_advance               epoch += 1
+//   grouped GEMM gate_up     (owner) every CTA's prologue waits (bounded) for all peers' `arrive`, then takes `cnt` as the per-expert row counts
+//   SwiGLU + requant
+//   grouped GEMM down        its epilogue stores each output row straight into the source GPU's `ret` buffer, addressed from the row's
+//                            `info` record (the combine "send" costs no extra pass); the last CTA to finish zeroes `cnt` and raises
+//                            `done` at all peers
+//   ep_reduce     (sender)   bounded wait for every peer's `done`; out[t] = sum_k w[t,k] * ret[t*K+k] (+ shared expert output); the last
+//                            CTA advances the epoch
+// (the wait, the address table and the two signals used to be kernels of their own: ep_wait_build, ep_signal, ep_advance)
 // The epoch lives in device memory so a captured CUDA graph replays with fresh tags.  Nothing here uses multicast loads;
 // all remote traffic is plain stores, one atomic per routed pair and flag words.
 //
@@ -95,54 +97,10 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpLayout L, cons
   }
 }
 
-// single CTA on the expert owner
-__global__ void __launch_bounds__(1024) ep_wait_build_kernel(const EpLayout L, int* __restrict__ counts, long long* __restrict__ row_dst,
-                                                            const int* __restrict__ epoch_ptr, int spin_limit) {
-  __shared__ int s_ok;
-  __shared__ int s_cnt[1024];
-  const int epoch = *epoch_ptr + 1;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if ((int)threadIdx.x < L.world) {
-    const int* f = reinterpret_cast<const int*>(peer_ptr(L, L.rank, L.off_arrive)) + threadIdx.x;
-    if (!wait_flag_ge(f, epoch, kKernelEp, 100 + threadIdx.x, (uint32_t)spin_limit)) s_ok = 0;
-  }
-  __syncthreads();
-  int* cnt = reinterpret_cast<int*>(peer_ptr(L, L.rank, L.off_cnt));
-  for (int e = threadIdx.x; e < L.E_local; e += blockDim.x) {
-    int c = s_ok ? cnt[e] : 0;              // a peer that never arrived: run no expert rather than half a batch
-    c = c < L.cap ? c : L.cap;
-    s_cnt[e] = c; counts[e] = c; cnt[e] = 0;
-  }
-  __syncthreads();
-  // one flat loop over (expert, slot) up to the fullest expert's count: a loop per expert puts one dependent global load per
-  // expert on the critical path of this single CTA (32 experts = ~10 us)
-  __shared__ int s_max;
-  if (threadIdx.x == 0) s_max = 0;
-  __syncthreads();
-  for (int e = threadIdx.x; e < L.E_local; e += blockDim.x) atomicMax(&s_max, s_cnt[e]);
-  __syncthreads();
-  const int width = s_max;
-  const long long* info = reinterpret_cast<const long long*>(peer_ptr(L, L.rank, L.off_info));
-  for (int i = threadIdx.x; i < L.E_local * width; i += blockDim.x) {
-    const int e = i / width, sl = i - e * width;
-    if (sl >= s_cnt[e]) continue;
-    const long long v = info[(long long)e * L.cap + sl];
-    const int src = (int)(v >> 32); const long long pair = v & 0xffffffffll;
-    row_dst[(long long)e * L.cap + sl] = (long long)(L.peer_base[src] + L.off_ret + pair * L.H * 2);
-  }
-}
-
-__global__ void ep_signal_kernel(const EpLayout L, const int* __restrict__ epoch_ptr) {
-  const int epoch = *epoch_ptr + 1;
-  __threadfence_system();
-  if ((int)threadIdx.x < L.world) st_release_sys(reinterpret_cast<int*>(peer_ptr(L, threadIdx.x, L.off_done)) + L.rank, epoch);
-}
-
 // one CTA per token
 __global__ void __launch_bounds__(256) ep_reduce_kernel(const EpLayout L, const int* __restrict__ pair_ok, const float* __restrict__ w,
                                                        const __nv_bfloat16* __restrict__ add_in, __nv_bfloat16* __restrict__ out,
-                                                       const int* __restrict__ epoch_ptr, int spin_limit) {
+                                                       int* __restrict__ epoch_ptr, int spin_limit, int* __restrict__ cta_counter) {
   __shared__ int s_ok; __shared__ int s_use[64]; __shared__ float s_w[64];
   const int epoch = *epoch_ptr + 1;
   const int t = blockIdx.x, K = L.top_k, H = L.H;
@@ -189,6 +147,12 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const EpLayout L, const 
     *reinterpret_cast<uint4*>(out + (long long)t * H + c) =
         make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
   }
+  // the layer is over for this rank once every CTA has read the epoch and its rows: the last one moves the epoch on
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(cta_counter, 1) == (int)(gridDim.x * gridDim.y) - 1) {
+    *cta_counter = 0;
+    *epoch_ptr = epoch;
+  }
 }
 
 __global__ void ep_advance_kernel(int* epoch_ptr) { *epoch_ptr += 1; }
@@ -213,23 +177,16 @@ extern "C" int ne_ep_dispatch(const EpLayout* L, const void* x, const int* idx, 
   return (int)cudaGetLastError();
 }
 
-extern "C" int ne_ep_wait_build(const EpLayout* L, int* counts, long long* row_dst, const int* epoch_ptr, int spin_limit, cudaStream_t st) {
-  if (L->E_local > 1024) return 1001;
-  ep_wait_build_kernel<<<1, 1024, 0, st>>>(*L, counts, row_dst, epoch_ptr, spin_limit);
-  return (int)cudaGetLastError();
-}
-
-extern "C" int ne_ep_signal(const EpLayout* L, const int* epoch_ptr, cudaStream_t st) {
-  ep_signal_kernel<<<1, 32, 0, st>>>(*L, epoch_ptr);
-  return (int)cudaGetLastError();
-}
-
-extern "C" int ne_ep_reduce(const EpLayout* L, const int* pair_ok, const float* w, const void* add_in, void* out, int T, const int* epoch_ptr,
-                            int spin_limit, cudaStream_t st) {
+// `cta_counter`: a zeroed device int owned by the caller (the kernel leaves it zero).  With no tokens the epoch still advances.
+extern "C" int ne_ep_reduce(const EpLayout* L, const int* pair_ok, const float* w, const void* add_in, void* out, int T, int* epoch_ptr,
+                            int spin_limit, int* cta_counter, cudaStream_t st) {
   if (T > 0) {
     if (L->top_k > 64 || L->H % 8) return 1001;
     const int slices = T >= 2048 ? 1 : (T >= 512 ? 2 : 4);
-    ep_reduce_kernel<<<dim3(T, slices), 256, 0, st>>>(*L, pair_ok, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, epoch_ptr, spin_limit);
+    ep_reduce_kernel<<<dim3(T, slices), 256, 0, st>>>(*L, pair_ok, w, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, epoch_ptr, spin_limit,
+                                                      cta_counter);
+  } else {
+    ep_advance_kernel<<<1, 1, 0, st>>>(epoch_ptr);
   }
   return (int)cudaGetLastError();
 }

@@ -5,14 +5,17 @@
 //   gather bf16 [2][world * rows_per_rank][H]  rows arriving from their owners, double-buffered by call parity
 //   flags  int32 [2][world]                    epoch-tagged: [0] = "my partials are in your stage", [1] = "my rows are in your gather"
 //
-// GEMM -> reduce-scatter (row-parallel o_proj / down_proj): the GEMM's scatter epilogue (`row_dst` of ne_gemm) stores
-// every output row of the local partial product straight into the stage slot of the rank that owns the row, tile by tile
-// while the other tiles are still being computed; tp_signal then raises the flag at every peer and tp_reduce, on the owner,
-// waits (bounded) for all sources and adds the `world` partials in rank order.  tp_row_dst fills the address table.
-// all-gather -> GEMM (column-parallel qkv / gate_up): tp_push stores this rank's rows into every peer's gather buffer and
-// raises the flag from its last CTA; tp_wait (bounded) precedes the consuming GEMM, which reads its own memory.
+// GEMM -> reduce-scatter (row-parallel o_proj / down_proj), two launches: the GEMM's scatter epilogue (GemmComm mode 3 of
+// ne_gemm_comm) stores every output row of the local partial product straight into the stage slot of the rank that owns the
+// row, tile by tile while the other tiles are still being computed, and the GEMM's last CTA raises the flag at every peer;
+// tp_reduce, on the owner, waits (bounded) for all sources, adds the `world` partials in rank order and advances the epoch.
+// all-gather -> GEMM (column-parallel qkv / gate_up), two launches: tp_push stores this rank's rows into every peer's gather
+// buffer and raises the flag from its last CTA; the consuming GEMM reads the gather buffer through its gated A operand (its
+// producer warp waits, bounded, for the source ranks of the row block it is about to load, own rows first) and its last CTA
+// advances the epoch.  The stand-alone all-gather (tp_wait_copy) copies the gathered rows out of the double buffer, so its
+// result does not depend on which half a call used.
 // tp_push also serves the plain reduce-scatter (mode 1: row i goes to its owner's stage slot), so an all-reduce is
-// push + reduce + push + wait.  Two calls may be in flight on different ranks, never three: a rank cannot pass the wait
+// push + reduce + push + wait_copy.  Two calls may be in flight on different ranks, never three: a rank cannot pass the wait
 // of call n+1 before every peer has finished call n, which is why two buffers per kind are enough.  The epoch lives in
 // device memory so captured CUDA graphs replay with fresh tags.  All remote traffic is plain stores; no multicast loads.
 //
@@ -38,15 +41,6 @@ __device__ __forceinline__ long long stage_off(const TpLayout& L, int parity, in
 }
 __device__ __forceinline__ long long gather_off(const TpLayout& L, int parity, long long row) {
   return L.off_gather + ((long long)parity * L.world * L.rows_per_rank + row) * L.H * 2;
-}
-
-// row_dst[i] = address of row (i % rpr) of this rank's slot in the stage of owner i / rpr, for i < world * rpr
-__global__ void tp_row_dst_kernel(const TpLayout L, long long* __restrict__ row_dst, int rpr, const int* __restrict__ epoch_ptr) {
-  const int parity = (*epoch_ptr + 1) & 1;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= L.world * rpr) return;
-  const int owner = i / rpr;
-  row_dst[i] = (long long)(L.peer_base[owner] + stage_off(L, parity, L.rank, i % rpr));
 }
 
 __global__ void tp_signal_kernel(const TpLayout L, int which, const int* __restrict__ epoch_ptr) {
@@ -93,17 +87,31 @@ __global__ void __launch_bounds__(256) tp_push_kernel(const TpLayout L, const __
   }
 }
 
-__global__ void tp_wait_kernel(const TpLayout L, int which, const int* __restrict__ epoch_ptr, int spin_limit) {
-  const int epoch = *epoch_ptr + 1;
+// Stand-alone all-gather, receiving side: wait (bounded) for every source, then copy the `rows` gathered rows of the half
+// this call used into `out`.  The last CTA advances the epoch.
+__global__ void __launch_bounds__(256) tp_wait_copy_kernel(const TpLayout L, __nv_bfloat16* __restrict__ out, int rows, int* __restrict__ epoch_ptr,
+                                                          int spin_limit, int* __restrict__ cta_counter) {
+  __shared__ int s_ok;
+  const int epoch = *epoch_ptr + 1, parity = epoch & 1;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
   if ((int)threadIdx.x < L.world) {
-    const int* f = reinterpret_cast<const int*>(tp_ptr(L, L.rank, L.off_flags)) + which * L.world + threadIdx.x;
-    wait_flag_ge(f, epoch, kKernelTp, 100 * (which + 1) + threadIdx.x, (uint32_t)spin_limit);
+    const int* f = reinterpret_cast<const int*>(tp_ptr(L, L.rank, L.off_flags)) + L.world + threadIdx.x;
+    if (!wait_flag_ge(f, epoch, kKernelTp, 200 + threadIdx.x, (uint32_t)spin_limit)) s_ok = 0;
   }
+  __syncthreads();
+  const uint4* src = reinterpret_cast<const uint4*>(tp_ptr(L, L.rank, gather_off(L, parity, 0)));
+  uint4* dst = reinterpret_cast<uint4*>(out);
+  const long long total = (long long)rows * (L.H / 8);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = s_ok ? src[i] : make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(cta_counter, 1) == (int)gridDim.x - 1) { *cta_counter = 0; *epoch_ptr = epoch; }
 }
 
 // out[row] = sum over sources (rank order, fp32) of stage[src][row]  (+ add_in[row]); one CTA per row.
 __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpLayout L, const __nv_bfloat16* __restrict__ add_in, __nv_bfloat16* __restrict__ out,
-                                                       int rows, const int* __restrict__ epoch_ptr, int spin_limit) {
+                                                       int rows, int* __restrict__ epoch_ptr, int spin_limit, int* __restrict__ cta_counter) {
   __shared__ int s_ok;
   const int epoch = *epoch_ptr + 1, parity = epoch & 1;
   if (threadIdx.x == 0) s_ok = 1;
@@ -114,8 +122,7 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpLayout L, const 
   }
   __syncthreads();
   const int row = blockIdx.x;
-  if (row >= rows) return;
-  for (int c = threadIdx.x * 8; c < L.H; c += blockDim.x * 8) {
+  for (int c = threadIdx.x * 8; row < rows && c < L.H; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (s_ok) {
       // the partials of eight sources are fetched before any is added: independent loads, latency-bound kernel
@@ -142,6 +149,9 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpLayout L, const 
     *reinterpret_cast<uint4*>(out + (long long)row * L.H + c) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
                                                                          pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
   }
+  // every CTA has read the epoch and its row by now: the last one to get here closes the call
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(cta_counter, 1) == (int)gridDim.x - 1) { *cta_counter = 0; *epoch_ptr = epoch; }
 }
 
 __global__ void tp_advance_kernel(int* epoch_ptr) { *epoch_ptr += 1; }
@@ -155,13 +165,6 @@ extern "C" int ne_tp_layout_size() { return (int)sizeof(TpLayout); }
 static int tp_check(const TpLayout* L, int rpr) {
   if (L->world > kTpMaxWorld || L->world < 1 || L->H % 8 || rpr < 1 || rpr > L->rows_per_rank) return 1001;
   return 0;
-}
-
-extern "C" int ne_tp_row_dst(const TpLayout* L, long long* row_dst, int rpr, const int* epoch_ptr, cudaStream_t st) {
-  if (int rc = tp_check(L, rpr)) return rc;
-  const int n = L->world * rpr;
-  tp_row_dst_kernel<<<(n + 255) / 256, 256, 0, st>>>(*L, row_dst, rpr, epoch_ptr);
-  return (int)cudaGetLastError();
 }
 
 // which: 0 = partials delivered (after a scatter-epilogue GEMM), 1 = rows delivered
@@ -181,14 +184,20 @@ extern "C" int ne_tp_push(const TpLayout* L, const void* x, int rows, int rpr, i
   return (int)cudaGetLastError();
 }
 
-extern "C" int ne_tp_wait(const TpLayout* L, int which, const int* epoch_ptr, int spin_limit, cudaStream_t st) {
-  tp_wait_kernel<<<1, 32, 0, st>>>(*L, which, epoch_ptr, spin_limit);
+// `cta_counter`: a zeroed device int owned by the caller (left zero).  `rows` = gathered rows (world * rows per rank).
+extern "C" int ne_tp_wait_copy(const TpLayout* L, void* out, int rows, int* epoch_ptr, int spin_limit, int* cta_counter, cudaStream_t st) {
+  if (rows < 0 || rows > L->world * L->rows_per_rank) return 1001;
+  long long items = (long long)rows * (L->H / 8);
+  int blocks = (int)((items + 255) / 256);
+  blocks = blocks < 1 ? 1 : (blocks > 592 ? 592 : blocks);
+  tp_wait_copy_kernel<<<blocks, 256, 0, st>>>(*L, (__nv_bfloat16*)out, rows, epoch_ptr, spin_limit, cta_counter);
   return (int)cudaGetLastError();
 }
 
-extern "C" int ne_tp_reduce(const TpLayout* L, const void* add_in, void* out, int rows, const int* epoch_ptr, int spin_limit, cudaStream_t st) {
+extern "C" int ne_tp_reduce(const TpLayout* L, const void* add_in, void* out, int rows, int* epoch_ptr, int spin_limit, int* cta_counter,
+                            cudaStream_t st) {
   if (int rc = tp_check(L, rows > 0 ? rows : 1)) return rc;
-  tp_reduce_kernel<<<rows > 0 ? rows : 1, 256, 0, st>>>(*L, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, rows, epoch_ptr, spin_limit);
+  tp_reduce_kernel<<<rows > 0 ? rows : 1, 256, 0, st>>>(*L, (const __nv_bfloat16*)add_in, (__nv_bfloat16*)out, rows, epoch_ptr, spin_limit, cta_counter);
   return (int)cudaGetLastError();
 }
 

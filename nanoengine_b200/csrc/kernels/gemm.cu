@@ -15,6 +15,7 @@
 // Replaces in the reference: deep_gemm.fp8_gemm_nt / m_grouped_fp8_gemm_nt_masked call sites
 // (layers/backends/linear/deep_gemm.py, layers/backends/experts/deep_gemm.py:498-837), the CuTe-DSL small-M bf16
 // GEMM (kernel/cutedsl_bf16_gemm.py) and cuBLAS F.linear (layers/backends/linear/generic.py:103-315).
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -35,6 +36,28 @@ template <int BLOCK_N> struct KGroup { static constexpr int value = BLOCK_N >= 2
 constexpr int kGemmThreads = 192;
 constexpr int kKernelGemm = 1;
 
+// Communication fused into a GEMM launch.  Every pointer is optional; epochs live in device memory so a captured CUDA
+// graph replays with fresh tags, and every wait is bounded (status word + no tiles run on expiry).
+struct GemmComm {
+  // (1) wait prologue (EP dispatch -> grouped GEMM): no tile starts before wait_flags[0 .. wait_world) >= *wait_epoch + 1.
+  const int* wait_epoch; const int* wait_flags; int wait_world; unsigned wait_spin;
+  // (2) gated A operand (all-gather -> GEMM): rows [s * gate_rpr, (s + 1) * gate_rpr) of A are delivered by source rank s,
+  //     which then raises gate_flags[s] to *gate_epoch + 1; the producer warp waits for the sources of the tile it is about
+  //     to load, so tiles of rows that have arrived (this rank's own first: mb_rot) run while others are in flight.  The
+  //     double-buffered gather area is one tensor map; the half in use is (epoch + 1) & 1, gate_parity_rows rows apart.
+  const int* gate_epoch; const int* gate_flags; int gate_rpr, gate_world, gate_parity_rows, mb_rot; unsigned gate_spin;
+  // (3) scatter epilogue without an address table.  mode 2 (MoE combine): row r of group g goes to
+  //     scatter_base[info >> 32] + (info & 0xffffffff) * ldd * 2 with info = row_info[g * rd_group_stride + r].
+  //     mode 3 (GEMM -> reduce-scatter): row r goes to scatter_base[r / scatter_rpr] + parity * scatter_parity_bytes +
+  //     (r % scatter_rpr) * ldd * 2, parity = (*scatter_epoch + 1) & 1.
+  int scatter_mode; const long long* row_info; unsigned long long scatter_base[16]; int scatter_rpr; long long scatter_parity_bytes;
+  const int* scatter_epoch;
+  // (4) tail: the last CTA of the grid to finish zeroes tail_clear[0 .. tail_clear_n), stores *tail_epoch + 1 (release, system
+  //     scope) to tail_flag[0 .. tail_world) and, if tail_advance is set, increments *tail_advance.
+  int* tail_counter; const int* tail_epoch; unsigned long long tail_flag[16]; int tail_world; int* tail_clear; int tail_clear_n;
+  int* tail_advance;
+};
+
 struct GemmArgs {
   int M, N, K, groups;
   const int* masked_m;                  // [groups] valid rows per group, or nullptr (all M rows valid)
@@ -48,6 +71,7 @@ struct GemmArgs {
   int out_fp32;                         // 0: bf16 output, 1: fp32, 2: e4m3 (clamped cast, no scale; plain bf16 GEMMs only)
   const long long* row_dst;             // optional scatter epilogue: absolute address of every output row (bf16, may be peer memory),
   long long rd_group_stride;            // indexed [group * rd_group_stride + row]; used by the MoE combine
+  GemmComm comm;                        // hooks that fuse a collective into this GEMM (all null / zero for a plain GEMM)
 };
 
 template <int BLOCK_N> struct Smem {
@@ -76,8 +100,9 @@ struct TileSched {
   const int* row_start;
   const int* base;                      // shared memory: first tile of every group, total at [groups]; null = none built
   int g = 0, walked = 0;
-  __device__ TileSched(int groups_, int M_, int nb, const int* mm, const int* rs, const int* base_)
-      : groups(groups_), M(M_), n_blocks(nb), masked_m(mm), row_start(rs), base(base_) {}
+  int mb_rot = 0;                       // dense single-group GEMMs only: row blocks are visited starting at this one
+  __device__ TileSched(int groups_, int M_, int nb, const int* mm, const int* rs, const int* base_, int rot = 0)
+      : groups(groups_), M(M_), n_blocks(nb), masked_m(mm), row_start(rs), base(base_), mb_rot(rot) {}
   __device__ int row0(int grp) const { return row_start ? row_start[grp] : 0; }
   __device__ int rows(int grp) const {
     int r = masked_m ? masked_m[grp] : M;
@@ -92,6 +117,7 @@ struct TileSched {
       grp = tile / per;
       const int l = tile - grp * per;
       mb = l / n_blocks; nb = l - mb * n_blocks;
+      if (mb_rot) { const int mbs = (M + kBlockM - 1) / kBlockM; mb += mb_rot; if (mb >= mbs) mb -= mbs; }
       return true;
     }
     if (base) {
@@ -149,6 +175,22 @@ __device__ __forceinline__ void epi_store32_bf16(uint8_t* stg, const float (&v)[
       *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(rows.dp[i]) + col + ch * 8) = *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + ch * 16);
   }
   __syncwarp();
+}
+
+// First element of an output row: the plain [group, row] position, or where the fused collective wants the row (GemmComm (3)).
+__device__ __forceinline__ __nv_bfloat16* scatter_row(const GemmArgs& a, int grp, int row, bool row_ok, int parity, __nv_bfloat16* plain) {
+  if (!row_ok) return plain;
+  if (a.row_dst) return reinterpret_cast<__nv_bfloat16*>(a.row_dst[(long long)grp * a.rd_group_stride + row]);
+  const GemmComm& cm = a.comm;
+  if (cm.scatter_mode == 2) {
+    const long long info = cm.row_info[(long long)grp * a.rd_group_stride + row];
+    return reinterpret_cast<__nv_bfloat16*>(cm.scatter_base[(int)(info >> 32) & 15]) + (info & 0xffffffffll) * a.ldd;
+  }
+  if (cm.scatter_mode == 3) {
+    const int owner = row / cm.scatter_rpr;
+    return reinterpret_cast<__nv_bfloat16*>(cm.scatter_base[owner & 15] + (long long)parity * cm.scatter_parity_bytes) + (long long)(row - owner * cm.scatter_rpr) * a.ldd;
+  }
+  return plain;
 }
 
 // Block-scaled tiles at least 64 wide use two epilogue warpgroups that split the tile's columns, halving the
@@ -215,13 +257,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
   pdl_wait();                                          // from here on the previous kernel's results may be read, and ours written
   pdl_trigger();
+  const GemmComm& cm = args.comm;
+  // wait prologue: the operands of this GEMM (and its row counts) are being written by peer GPUs; their arrival flags are
+  // local memory, polled by one thread each.  On expiry the status word is set and the row counts read as zero.
+  __shared__ int s_wait_failed;
+  if (cm.wait_flags) {
+    if (threadIdx.x == 0) s_wait_failed = 0;
+    __syncthreads();
+    if ((int)threadIdx.x < cm.wait_world &&
+        !wait_flag_ge(cm.wait_flags + threadIdx.x, *cm.wait_epoch + 1, kKernelGemm, 600 + (int)threadIdx.x, cm.wait_spin))
+      s_wait_failed = 1;
+    __syncthreads();
+  }
+  const bool wait_failed = cm.wait_flags && s_wait_failed;
+  const int sc_parity = cm.scatter_epoch ? ((*cm.scatter_epoch + 1) & 1) : 0;
   // the per-group row tables are read once per tile by three roles: keep them in shared memory, a global load per
   // lookup sits on the producer's critical path at every tile switch
   __shared__ int s_mm[kSchedCache], s_rs[kSchedCache];
   const bool cache_tables = args.groups <= kSchedCache;
   if (cache_tables) {
     for (int i = threadIdx.x; i < args.groups; i += blockDim.x) {
-      if (args.masked_m) s_mm[i] = args.masked_m[i];
+      if (args.masked_m) s_mm[i] = wait_failed ? 0 : args.masked_m[i];
       if (args.row_start) s_rs[i] = args.row_start[i];
     }
   }
@@ -229,7 +285,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int* rs_tab = args.row_start ? (cache_tables ? s_rs : args.row_start) : nullptr;
   // first tile of every ragged group: counts by all threads, then one warp turns them into running sums
   __shared__ int s_base[kSchedCache + 1];
-  static_assert((3 * kSchedCache + 1) * (int)sizeof(int) + 128 <= S::kStaticTables, "the stage budget must leave room for the static tables");
+  static_assert((3 * kSchedCache + 4) * (int)sizeof(int) + 128 <= S::kStaticTables, "the stage budget must leave room for the static tables");
   const bool ragged = args.masked_m || args.row_start;
   const int* base_tab = (ragged && cache_tables) ? s_base : nullptr;
   if (base_tab) {
@@ -259,10 +315,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (elect_one()) {
-      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab);
+      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
       int stage = 0; uint32_t phase = 0; int grp, mb, nb;
       bool ok = true;
+      const int gate_ep = cm.gate_flags ? *cm.gate_epoch + 1 : 0;
+      const int a_row_off = cm.gate_flags ? (gate_ep & 1) * cm.gate_parity_rows : 0;
+      unsigned gate_seen = 0;
+      if (cm.wait_flags) fence_proxy_async_all();      // peers' stores, observed through the flags, before the first TMA read
       for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
+        if (cm.gate_flags) {
+          // sources whose rows this tile reads; each is waited for once per CTA
+          const int r_lo = mb * kBlockM, r_hi = min(r_lo + kBlockM, args.M) - 1;
+          for (int sr = r_lo / cm.gate_rpr; sr <= r_hi / cm.gate_rpr && sr < cm.gate_world && ok; sr++) {
+            if (gate_seen >> sr & 1u) continue;
+            if (!wait_flag_ge(cm.gate_flags + sr, gate_ep, kKernelGemm, 700 + sr, cm.gate_spin)) { *abort_flag = 1; ok = false; break; }
+            gate_seen |= 1u << sr;
+            fence_proxy_async_all();
+          }
+          if (!ok) break;
+        }
         // a tile with few valid rows (decode: a handful of tokens per expert) fetches only the first 32 or 64 rows of
         // the activation block; the MMA still spans 128 rows, whose stale remainder lands in output rows nobody stores
         const int rows_here = sched.rows(grp) - mb * kBlockM;
@@ -275,14 +346,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int kc = kb_begin + st * kG;
           if (!args.k_flat) {
             if (args.a_group_inner) tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, grp, mb * kBlockM, kc);
-            else tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, kc);
+            else tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, a_row_off + sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, kc);
             tma_load_4d(b_dst, &tmap_b, full0 + 8 * stage, 0, nb * BLOCK_N, grp, kc);
           } else {
 #pragma unroll
             for (int g = 0; g < kG; g++) {
               const int kx = (kc + g) * kElemsPerStageK;           // past the end of K: the whole box is zero-filled
               if (args.a_group_inner) tma_load_4d(a_dst + g * a_bytes, ta, full0 + 8 * stage, kx, grp, mb * kBlockM, 0);
-              else tma_load_4d(a_dst + g * a_bytes, ta, full0 + 8 * stage, kx, sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, 0);
+              else tma_load_4d(a_dst + g * a_bytes, ta, full0 + 8 * stage, kx, a_row_off + sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, 0);
               tma_load_4d(b_dst + g * S::kBBytes, &tmap_b, full0 + 8 * stage, kx, nb * BLOCK_N, grp, 0);
             }
           }
@@ -293,7 +364,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab);
+      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
       int stage = 0; uint32_t phase = 0; int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
       bool ok = true;
       // A test of an mbarrier costs ~150 cycles even when the phase has long completed, and this thread is the serial
@@ -358,7 +429,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int cbase = ((warp - 2) >> 2) * kCols;   // column offset of this warp's group inside the tile
     const int row_in_tile = wq * 32 + (int)lane_id();
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab);
+    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
     int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
     bool ok = true;
     bool pre_tf = false;                               // result of an early test of the next accumulator's "full" barrier
@@ -437,9 +508,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               }
             }
           } else {
-            __nv_bfloat16* dbf = (args.row_dst && row_ok)
-                ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0 + cbase
-                : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
+            __nv_bfloat16* dbf = scatter_row(args, grp, row, row_ok, sc_parity, reinterpret_cast<__nv_bfloat16*>(args.D) + off - n0 - cbase) + n0 + cbase;
             uint8_t* stg = staging + (warp - 2) * kStgWarpBytes;
             const EpiRows erows = epi_rows(row_ok, dbf);
 #pragma unroll
@@ -455,8 +524,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (!mbar_wait(tfull0 + 8 * buf, bphase, abort_flag, kKernelGemm, 410 + buf)) { ok = false; break; }
         tc_fence_after();
         long long off = (long long)grp * args.d_group_stride + (long long)row * args.ldd + n0;
-        __nv_bfloat16* dbf = (args.row_dst && row_ok) ? reinterpret_cast<__nv_bfloat16*>(args.row_dst[(long long)grp * args.rd_group_stride + row]) + n0
-                                                      : reinterpret_cast<__nv_bfloat16*>(args.D) + off;
+        __nv_bfloat16* dbf = scatter_row(args, grp, row, row_ok, sc_parity, reinterpret_cast<__nv_bfloat16*>(args.D) + off - n0) + n0;
         EpiRows erows;
         if (!kSplit && args.out_fp32 == 0) erows = epi_rows(row_ok, dbf);
 #pragma unroll
@@ -511,7 +579,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ---------------- cross-CTA reduction of the partial tiles ----------------
     cluster_sync_all();
     if (warp >= 2) {
-      const int mb = tile0 / n_blocks, nb = tile0 % n_blocks;
+      const int mb = tile0 / n_blocks, nb = tile0 % n_blocks;      // split-K runs single-row-block GEMMs: no rotation to apply
       const int R = (kBlockM + split - 1) / split;
       constexpr int kChunks = BLOCK_N / 4;
       const int nthr = 128 * kEpi, te = (int)threadIdx.x - 64;
@@ -527,7 +595,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         const long long off = (long long)grow * args.ldd + n;
         if (args.out_fp32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(args.D) + off) = s4;
-        else *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(args.D) + off) = make_uint2(pack_bf16x2(s4.x, s4.y), pack_bf16x2(s4.z, s4.w));
+        else *reinterpret_cast<uint2*>(scatter_row(args, 0, grow, true, sc_parity, reinterpret_cast<__nv_bfloat16*>(args.D) + (long long)grow * args.ldd) + n) =
+            make_uint2(pack_bf16x2(s4.x, s4.y), pack_bf16x2(s4.z, s4.w));
       }
     }
     cluster_sync_all();           // nobody leaves while a peer may still read its partial tile
@@ -542,6 +611,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+  if (cm.tail_counter) {
+    // every thread orders its own (possibly peer-memory) stores before the count; the CTA that counts last speaks for the grid
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_last;
+    if (threadIdx.x == 0) s_last = (atomicAdd(cm.tail_counter, 1) == (int)gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (s_last) {
+      const int ep = *cm.tail_epoch + 1;
+      for (int i = threadIdx.x; i < cm.tail_clear_n; i += blockDim.x) cm.tail_clear[i] = 0;
+      __threadfence_system();
+      __syncthreads();
+      if ((int)threadIdx.x < cm.tail_world) st_release_sys(reinterpret_cast<int*>(cm.tail_flag[threadIdx.x]), ep);
+      if (threadIdx.x == 0) { *cm.tail_counter = 0; if (cm.tail_advance) *cm.tail_advance += 1; }
+    }
+  }
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -660,10 +745,18 @@ using namespace ne;
 // masked_m: device int32 [groups] or null.  row_start: device int32 [groups] for the contiguous grouped layout (A and D
 // are then flat [M, *] matrices and masked_m holds the per-group row counts) or null.
 // Returns 0 or a CUDA / argument error code.
-extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void* B, void* D, long long ldd, long long d_gs,
-                       int M, int N, int K, int groups, const int* masked_m, const int* row_start, int dtype, const float* sa, int sa_ld,
-                       long long sa_gs, const float* sb, int out_fp32, int block_n_hint, const long long* row_dst, cudaStream_t stream) {
+static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B, void* D, long long ldd, long long d_gs,
+                     int M, int N, int K, int groups, const int* masked_m, const int* row_start, int dtype, const float* sa, int sa_ld,
+                     long long sa_gs, const float* sb, int out_fp32, int block_n_hint, const long long* row_dst, const GemmComm* comm,
+                     int a_rows_total, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
+  if (comm) {
+    if (comm->wait_flags && (groups > kSchedCache || comm->wait_world > 16 || !masked_m)) return 1007;
+    if (comm->gate_flags && (groups != 1 || row_start || masked_m || comm->gate_world > 16 || comm->gate_rpr < 1)) return 1008;
+    if (comm->scatter_mode && (out_fp32 || row_dst)) return 1005;
+    if (comm->scatter_mode == 3 && (groups != 1 || comm->scatter_rpr < 1)) return 1009;
+    if (comm->tail_counter && comm->tail_world > 16) return 1010;
+  }
   const bool fp8 = dtype == 1;
   if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % 16 != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
   if (fp8 && (K % 128 != 0 || !sa || !sb)) return 1002;
@@ -675,7 +768,8 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
   int split = 1;
   const int num_kb_host = (K * (fp8 ? 1 : 2) + kKBytes - 1) / kKBytes;
   const bool can_split = groups == 1 && !row_start && !masked_m && !row_dst && m_blocks == 1 && N % 4 == 0 &&
-                         (K * (fp8 ? 1 : 2)) % kKBytes == 0 && g_split_k_enabled && out_fp32 != 2;
+                         (K * (fp8 ? 1 : 2)) % kKBytes == 0 && g_split_k_enabled && out_fp32 != 2 &&
+                         (!comm || (comm->scatter_mode != 2 && !comm->wait_flags));
   if (bn == 0 && can_split) {
     plan_small_m(N, num_kb_host, fp8, &bn, &split);
   } else if (bn == 0) {
@@ -703,10 +797,11 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
   if (fp8 && bn > 128) bn = 128;
   const int kg = bn >= 256 ? 1 : 2;      // KGroup<bn>::value
   CUtensorMap ta[3], tb;       // activation maps with 128-, 64- and 32-row boxes
-  if (row_start || groups == 1) a_gs = (long long)M * lda;
+  if (row_start || groups == 1) a_gs = (long long)(a_rows_total > 0 ? a_rows_total : M) * lda;
   int rc = 0;
   for (int i = 0; i < 3 && !rc; i++)
-    rc = get_tmap_kmajor(&ta[i], A, fp8, (uint64_t)K, (uint64_t)M, (uint64_t)(row_start ? 1 : groups), (uint64_t)lda, (uint64_t)a_gs, kBlockM >> i, kg);
+    rc = get_tmap_kmajor(&ta[i], A, fp8, (uint64_t)K, (uint64_t)(a_rows_total > 0 ? a_rows_total : M), (uint64_t)(row_start ? 1 : groups), (uint64_t)lda,
+                         (uint64_t)a_gs, kBlockM >> i, kg);
   if (rc) return 2000 + rc;
   rc = get_tmap_kmajor(&tb, B, fp8, (uint64_t)K, (uint64_t)N, (uint64_t)groups, (uint64_t)K, (uint64_t)N * K, (uint32_t)bn, kg);
   if (rc) return 3000 + rc;
@@ -719,6 +814,8 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
   a.sb_group_stride = (long long)((N + 127) / 128) * (K / 128); a.out_fp32 = out_fp32;
   a.row_dst = row_dst; a.rd_group_stride = row_start ? 0 : M;
   if (row_dst && out_fp32) return 1005;
+  if (comm) { a.comm = *comm; if (m_blocks <= 1 || groups != 1) a.comm.mb_rot = 0; else a.comm.mb_rot %= m_blocks; }
+  else memset(&a.comm, 0, sizeof(a.comm));
   long long tiles = (long long)groups * m_blocks * ((N + bn - 1) / bn);
   int grid = (int)(tiles < num_sms() ? tiles : num_sms());
   if (split > 1) {
@@ -749,6 +846,24 @@ extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void*
     default: return launch<32, false, false>(ta, tb, a, grid, stream);
   }
 }
+
+extern "C" int ne_gemm(const void* A, long long lda, long long a_gs, const void* B, void* D, long long ldd, long long d_gs,
+                       int M, int N, int K, int groups, const int* masked_m, const int* row_start, int dtype, const float* sa, int sa_ld,
+                       long long sa_gs, const float* sb, int out_fp32, int block_n_hint, const long long* row_dst, cudaStream_t stream) {
+  return gemm_impl(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, row_start, dtype, sa, sa_ld, sa_gs, sb, out_fp32, block_n_hint, row_dst,
+                   nullptr, 0, stream);
+}
+
+// The same GEMM with a collective fused in (see GemmComm).  `a_rows_total` > 0 gives the number of rows the A tensor map must
+// cover when that is more than M (the double-buffered gather area of the gated form).
+extern "C" int ne_gemm_comm(const void* A, long long lda, long long a_gs, const void* B, void* D, long long ldd, long long d_gs,
+                            int M, int N, int K, int groups, const int* masked_m, const int* row_start, int dtype, const float* sa, int sa_ld,
+                            long long sa_gs, const float* sb, int out_fp32, int block_n_hint, const GemmComm* comm, int a_rows_total,
+                            cudaStream_t stream) {
+  return gemm_impl(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, row_start, dtype, sa, sa_ld, sa_gs, sb, out_fp32, block_n_hint, nullptr,
+                   comm, a_rows_total, stream);
+}
+extern "C" int ne_gemm_comm_size() { return (int)sizeof(GemmComm); }
 
 // Turn the cluster split-K plan of small-M dense GEMMs on or off (on by default); returns the previous setting.
 extern "C" int ne_gemm_set_split_k(int on) { int was = g_split_k_enabled ? 1 : 0; g_split_k_enabled = on != 0; return was; }

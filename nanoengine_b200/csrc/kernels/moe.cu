@@ -18,7 +18,8 @@ constexpr int kMaxExperts = 1024;
 // one warp per token
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx_out,
                                                        float* __restrict__ w_out, int T, int E, int top_k, int n_group, int topk_group,
-                                                       int norm, float scale, int softmax, int planes) {
+                                                       int norm, float scale, int softmax, int planes, int balance_ranks,
+                                                       const int* __restrict__ log2phy, const int* __restrict__ logcnt, int max_rep) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   __shared__ float s_choice[4][kMaxExperts];
   __shared__ float s_score[4][kMaxExperts];
@@ -75,7 +76,19 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     if (bi >= E) bi = 0;   // every remaining choice is -inf (cannot happen with valid arguments)
     float sv = score[bi];
     wsum += sv;
-    if (lane == 0) { idx_out[(long long)t * top_k + k] = bi; w_out[(long long)t * top_k + k] = sv; choice[bi] = -INFINITY; }
+    if (lane == 0) {
+      int phys = bi;
+      if (balance_ranks > 0) {
+        // load-balance stand-in for random-init routers: expert ids dealt round-robin over the EP ranks, weights kept
+        const int i = t * top_k + k, step = E / balance_ranks;
+        phys = ((i / balance_ranks) % step + (i % balance_ranks) * step) % E;
+      } else if (log2phy) {
+        // EPLB: logical expert -> one of its physical replicas, chosen by token so that replicas share the load
+        const int cnt = logcnt[bi];
+        phys = log2phy[bi * max_rep + (cnt > 1 ? (int)(((unsigned)t * 2654435761u + (unsigned)k * 40503u) >> 8) % cnt : 0)];
+      }
+      idx_out[(long long)t * top_k + k] = phys; w_out[(long long)t * top_k + k] = sv; choice[bi] = -INFINITY;
+    }
     __syncwarp();
   }
   if (lane == 0) {
@@ -281,11 +294,16 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
 
 using namespace ne;
 
+// balance_ranks > 0: replace the chosen ids by ids dealt evenly over that many EP ranks (weights kept).  log2phy [E, max_rep] /
+// logcnt [E] (device int32, optional): remap every logical id to one of its physical replicas.
 extern "C" int ne_moe_route(const float* logits, const float* bias, int* idx, float* w, int T, int E, int top_k, int n_group,
-                            int topk_group, int norm, float scale, int softmax, int planes, cudaStream_t st) {
+                            int topk_group, int norm, float scale, int softmax, int planes, int balance_ranks, const int* log2phy,
+                            const int* logcnt, int max_rep, cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > kMaxExperts || top_k > 64 || n_group > 64 || (n_group > 1 && E % n_group) || planes < 1) return 1001;
-  return (int)launch_pdl(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, st, logits, bias, idx, w, T, E, top_k, n_group, topk_group, norm, scale, softmax, planes);
+  if (balance_ranks < 0 || (balance_ranks > 0 && E % balance_ranks) || (log2phy && (!logcnt || max_rep < 1))) return 1001;
+  return (int)launch_pdl(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, st, logits, bias, idx, w, T, E, top_k, n_group, topk_group, norm, scale, softmax,
+                         planes, balance_ranks, log2phy, logcnt, max_rep);
 }
 
 // Outputs: counts [E_local], slot [T*K] (scratch), row_start [E_local+1], pos [T*K], and the

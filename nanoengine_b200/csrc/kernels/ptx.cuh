@@ -121,6 +121,8 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, uint
 }
 // generic-proxy writes to smem -> visible to the async proxy (UMMA / TMA reads)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// generic-proxy observations (a flag acquired from a peer GPU) ordered before later async-proxy (TMA) reads of global memory
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // ---- tcgen05 ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {  // whole warp

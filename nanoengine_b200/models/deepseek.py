@@ -46,6 +46,9 @@ class MLAAttention(nn.Module):
         # absorbed halves of kv_b_proj
         self.kc = nn.Parameter(torch.empty(H, nope, R, dtype=dtype, device=device), requires_grad=False)   # W_UK
         self.vc = nn.Parameter(torch.empty(H, R, v, dtype=dtype, device=device), requires_grad=False)      # W_UV^T
+        # K-major bf16 copies of kc / vc for the per-head tensor-core GEMMs: built by `refresh_absorbed` whenever the weights are set
+        self.kc_t: Optional[torch.Tensor] = None
+        self.vc_t: Optional[torch.Tensor] = None
         self.o_proj = QLinear(H * v, cfg.hidden_size, dtype, device, q)
         self.scale = (nope + rope) ** -0.5
         sc = cfg.rope_scaling
@@ -64,6 +67,20 @@ class MLAAttention(nn.Module):
         w = w.view(self.H, self.nope + self.v, self.R)
         self.kc.copy_(w[:, : self.nope].to(self.kc.dtype))
         self.vc.copy_(w[:, self.nope:].transpose(1, 2).to(self.vc.dtype))
+        self.refresh_absorbed()
+
+    def refresh_absorbed(self):
+        """Rebuild the operand copies derived from kc / vc.  Called by `set_kv_b`; call it again after writing kc / vc directly.
+        Parity: reference models/deepseek_v2/deepseek_v2_loader.py:36-121 transforms kv_b_proj once at load."""
+        if self.kc.is_cuda:
+            if self.kc_t is not None and self.kc_t.device == self.kc.device:
+                # same storage: CUDA graphs that captured these addresses stay valid
+                self.kc_t.copy_(ops.kmajor(self.kc))
+                self.vc_t.copy_(ops.kmajor(self.vc))
+            else:
+                self.kc_t, self.vc_t = ops.kmajor(self.kc), ops.kmajor(self.vc)
+        else:
+            self.kc_t = self.vc_t = None
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor, ctx: ForwardContext, rope_cache: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
@@ -83,10 +100,10 @@ class MLAAttention(nn.Module):
         sparse = None
         if self.indexer is not None:
             sparse = self.indexer(x, q_c if q_c is not None else x, positions, ctx, rope_cache)
-        q_full = ops.mla_query(q, self.kc, positions, rope_cache, nope, cache, sparse is None)   # [T, H, R + rope]
+        q_full = ops.mla_query(q, self.kc, positions, rope_cache, nope, cache, sparse is None, kc_t=self.kc_t)   # [T, H, R + rope]
         o_lat = ops.mla_attention_paged(q_full, cache, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale, R,
                                         sparse_indices=sparse)
-        o = ops.bmm_absorb(o_lat, self.vc)                                   # [T, H, v]
+        o = ops.bmm_absorb(o_lat, self.vc, wt=self.vc_t)                                   # [T, H, v]
         return self.o_proj(o.reshape(T, H * self.v))
 
 
@@ -112,9 +129,10 @@ class MoEGate(nn.Module):
 
     def forward(self, x):
         c = self.cfg
+        from ..parallel.ep import routing_options
         logits = ops.router_logits(x, self.weight)
         return ops.moe_route(logits, self.e_score_correction_bias, c.num_experts_per_tok, c.n_group, c.topk_group,
-                             c.norm_topk_prob, c.routed_scaling_factor, c.scoring_func)
+                             c.norm_topk_prob, c.routed_scaling_factor, c.scoring_func, **routing_options())
 
 
 class DeepseekMoE(nn.Module):

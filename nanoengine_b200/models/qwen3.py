@@ -21,7 +21,7 @@ from .. import ops
 from ..ops import reference as ref
 from ..parallel.dist import get_dist_context
 from ..parallel.ep import ep_moe_forward
-from ..parallel.tp import tp_all_gather, tp_linear_reduce_scatter, tp_reduce_scatter
+from ..parallel.tp import tp_all_gather, tp_all_gather_linear, tp_linear_reduce_scatter, tp_reduce_scatter
 from ..runtime.context import ForwardContext
 from .config import ModelConfig
 from .layers import QLinear, RMSNorm, RoutedExperts, SwiGLUMLP
@@ -47,9 +47,8 @@ class Qwen3Attention(nn.Module):
         self.scale = self.hd ** -0.5
 
     def forward(self, x_slice, positions, ctx: ForwardContext, rope_cache, total_rows: int):
-        x = tp_all_gather(x_slice, total_rows) if self.tp > 1 else x_slice
-        T = x.shape[0]
-        qkv = self.qkv_proj(x)
+        qkv = tp_all_gather_linear(x_slice, total_rows, self.qkv_proj) if self.tp > 1 else self.qkv_proj(x_slice)
+        T = qkv.shape[0]
         q, k, v = qkv.split([self.hq * self.hd, self.hkv * self.hd, self.hkv * self.hd], -1)
         q, k, v = q.reshape(T, self.hq, self.hd), k.reshape(T, self.hkv, self.hd), v.reshape(T, self.hkv, self.hd)
         if self.q_norm is not None:
@@ -74,7 +73,8 @@ class Qwen3MoE(nn.Module):
     def forward(self, x, ctx):
         c = self.cfg
         logits = ops.router_logits(x, self.gate_weight)
-        idx, w = ops.moe_route(logits, None, c.num_experts_per_tok, 1, 1, c.norm_topk_prob, 1.0, "softmax")
+        from ..parallel.ep import routing_options
+        idx, w = ops.moe_route(logits, None, c.num_experts_per_tok, 1, 1, c.norm_topk_prob, 1.0, "softmax", **routing_options())
         return ep_moe_forward(self.experts, x, idx, w, ctx)
 
 

@@ -242,13 +242,19 @@ def merge_attention_states(o1, lse1, o2, lse2):
 
 # ---- MoE -----------------------------------------------------------------------------------------
 def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_group: int = 1, topk_group: int = 1,
-              norm_topk_prob: bool = True, routed_scaling_factor: float = 1.0, scoring: str = "sigmoid"):
+              norm_topk_prob: bool = True, routed_scaling_factor: float = 1.0, scoring: str = "sigmoid",
+              balance_ranks: int = 0, log2phy: Optional[torch.Tensor] = None, logcnt: Optional[torch.Tensor] = None):
     """DeepSeek ``noaux_tc`` routing and Qwen3 softmax routing.
 
     scores = sigmoid|softmax(logits fp32); choice = scores + bias; with n_group > 1 only the
     topk_group groups with the largest sum of their top-2 choices stay eligible; idx = top_k of
     choice; weights are the un-biased scores, renormalised and scaled
     (reference models/deepseek_v2/deepseek_v2.py:478-543, models/qwen3_moe/qwen3_moe.py:283-297).
+
+    Two optional post-steps on the ids (the weights stay those of the chosen experts): `balance_ranks` > 0 replaces them by
+    ids dealt evenly over that many expert-parallel ranks (a load-balance stand-in for random-init routers, reference
+    layers/backends/experts/deep_gemm.py:47-67); `log2phy [E, R]` / `logcnt [E]` map every logical id to one of its
+    physical replicas, picked by (row, k) hash so replicas share the load (reference experts/eplb.py, triton/generic/moe.py:561).
     """
     lf = logits.float()
     if lf.dim() == 3:          # partial sums of a split-K router product
@@ -266,6 +272,16 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_
     w = scores.gather(1, idx)
     if norm_topk_prob:
         w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    if balance_ranks > 0:
+        i = torch.arange(T * top_k, device=idx.device).view(T, top_k)
+        step = E // balance_ranks
+        idx = ((i // balance_ranks) % step + (i % balance_ranks) * step) % E
+    elif log2phy is not None:
+        cnt = logcnt.to(idx.device).long()[idx]
+        t = torch.arange(T, device=idx.device).view(T, 1)
+        k = torch.arange(top_k, device=idx.device).view(1, top_k)
+        h = (((t * 2654435761 + k * 40503) & 0xFFFFFFFF) >> 8) % cnt
+        idx = log2phy.to(idx.device).long()[idx, h]
     return idx.to(torch.int32), (w * routed_scaling_factor).float()
 
 
@@ -424,18 +440,28 @@ def indexer_select(q8: torch.Tensor, q_scale: torch.Tensor, head_w: torch.Tensor
 
 
 # ---- small GEMM-shaped helpers -------------------------------------------------------------------
-def bmm_absorb(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """Per-head matmul of MLA weight absorption: x [T, H, A], w [H, A, B] -> [T, H, B]."""
-    return torch.einsum("tha,hab->thb", x.float(), w.float()).to(x.dtype)
+def kmajor(w: torch.Tensor) -> torch.Tensor:
+    """w [H, A, B] -> [H, B, A] contiguous, the operand layout the CUDA body of `bmm_absorb` multiplies with."""
+    return w.transpose(1, 2).contiguous()
 
 
-def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, nope: int) -> torch.Tensor:
+def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out=None, wt=None) -> torch.Tensor:
+    """Per-head matmul of MLA weight absorption: x [T, H, A], w [H, A, B] -> [T, H, B].  `wt` (the K-major copy of `w` that
+    the weight's owner keeps for the CUDA body) is not needed here."""
+    r = torch.einsum("tha,hab->thb", x.float(), w.float()).to(x.dtype)
+    if out is not None:
+        out.copy_(r)
+        return out
+    return r
+
+
+def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, nope: int, kc_t=None) -> torch.Tensor:
     """Absorbed MLA query [q_nope @ W_UK | rope(q_pe)]: q [T, H, nope + rope], kc [H, nope, R] -> [T, H, R + rope]."""
     return torch.cat([bmm_absorb(q[..., :nope], kc), apply_rope(q[..., nope:], positions, cache, True)], -1)
 
 
 def mla_query(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, rope_cache: torch.Tensor, nope: int, kv_cache: torch.Tensor,
-              dense: bool = True) -> torch.Tensor:
+              dense: bool = True, kc_t=None) -> torch.Tensor:
     """Absorbed MLA query as the attention operator wants it.  The CUDA body may hand back e4m3 (clamped cast, no scale)
     when `kv_cache` is fp8 and the dense fp8 attention kernel will consume it; this statement always returns q's dtype."""
     return mla_absorb_rope(q, kc, positions, rope_cache, nope)

@@ -27,8 +27,6 @@ def lib():
         if not os.path.exists(path):
             raise RuntimeError(f"CUDA kernel library missing: {path}; run `python -m nanoengine_b200.build_native`")
         _LIB = ctypes.CDLL(path)
-        for name in dir(_LIB):
-            pass
     return _LIB
 
 
@@ -67,6 +65,31 @@ def _gemm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, row_start, f
                        _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), _p(masked_m), _p(row_start), _c.c_int(1 if fp8 else 0),
                        _p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(int(out_fp32)), _c.c_int(bn), _p(row_dst), _st())     # output: 0 bf16, 1 fp32, 2 e4m3
     _ck(rc, "ne_gemm")
+
+
+class GemmComm(_c.Structure):
+    """Mirror of `ne::GemmComm` (csrc/kernels/gemm.cu): the collective hooks of one GEMM launch."""
+    _fields_ = [("wait_epoch", _c.c_void_p), ("wait_flags", _c.c_void_p), ("wait_world", _c.c_int), ("wait_spin", _c.c_uint),
+                ("gate_epoch", _c.c_void_p), ("gate_flags", _c.c_void_p), ("gate_rpr", _c.c_int), ("gate_world", _c.c_int),
+                ("gate_parity_rows", _c.c_int), ("mb_rot", _c.c_int), ("gate_spin", _c.c_uint),
+                ("scatter_mode", _c.c_int), ("row_info", _c.c_void_p), ("scatter_base", _c.c_ulonglong * 16), ("scatter_rpr", _c.c_int),
+                ("scatter_parity_bytes", _c.c_longlong), ("scatter_epoch", _c.c_void_p),
+                ("tail_counter", _c.c_void_p), ("tail_epoch", _c.c_void_p), ("tail_flag", _c.c_ulonglong * 16), ("tail_world", _c.c_int),
+                ("tail_clear", _c.c_void_p), ("tail_clear_n", _c.c_int), ("tail_advance", _c.c_void_p)]
+
+
+def _gemm_comm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, fp8, sa, sa_ld, sa_gs, sb, comm: GemmComm, a_rows_total=0, bn=0):
+    """`_gemm` with a fused collective; `masked_m` may be a raw device address (an int) inside a symmetric region."""
+    l = lib()
+    if not getattr(l, "_comm_checked", False):
+        assert l.ne_gemm_comm_size() == _c.sizeof(GemmComm), "GemmComm mismatch between Python and the kernel library"
+        l._comm_checked = True
+    mm = _c.c_void_p(masked_m) if isinstance(masked_m, int) else _p(masked_m)
+    rc = l.ne_gemm_comm(_p(A) if not isinstance(A, int) else _c.c_void_p(A), _c.c_longlong(lda), _c.c_longlong(a_gs), _p(B), _p(D), _c.c_longlong(ldd),
+                        _c.c_longlong(d_gs), _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), mm, _p(None), _c.c_int(1 if fp8 else 0),
+                        _p(sa) if not isinstance(sa, int) else _c.c_void_p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(0), _c.c_int(bn),
+                        _c.byref(comm), _c.c_int(a_rows_total), _st())
+    _ck(rc, "ne_gemm_comm")
 
 
 def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False):
@@ -139,16 +162,10 @@ def linear(x, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, bias=None
     return out.view(*x.shape[:-1], N)
 
 
-_BF16_CACHE = {}
-
-
-def _cached(key_t: torch.Tensor, tag: str, fn):
-    key = (key_t.data_ptr(), tuple(key_t.shape), tag)
-    v = _BF16_CACHE.get(key)
-    if v is None:
-        v = fn(key_t)
-        _BF16_CACHE[key] = v
-    return v
+def kmajor(w: torch.Tensor) -> torch.Tensor:
+    """w [H, A, B] -> bf16 [H, B, A] contiguous: the K-major operand `bmm_absorb` multiplies with.  Owners of a weight build
+    this once when the weight is set (and again after an in-place update) and pass it as `wt`."""
+    return w.to(torch.bfloat16).transpose(1, 2).contiguous()
 
 
 def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -169,12 +186,16 @@ def lm_head(hidden: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return linear(hidden, w, out_fp32=True)
 
 
-def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, wt: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [T, H, A] (any row/head strides, unit inner stride), w [H, A, B] -> [T, H, B]: a grouped GEMM with one group per head.
-    `out` may be a strided view; a one-byte `out` (uint8 / e4m3) makes the epilogue write clamped e4m3 instead of bf16."""
+    `out` may be a strided view; a one-byte `out` (uint8 / e4m3) makes the epilogue write clamped e4m3 instead of bf16.
+    `wt` is `kmajor(w)` kept by the weight's owner; without it the transposed copy is made on every call (nothing is cached
+    here: a cache keyed on the weight's address would outlive the weight)."""
     T, H, A = x.shape
     Bd = w.shape[2]
-    wt = _cached(w, "t", lambda t: t.to(torch.bfloat16).transpose(1, 2).contiguous())      # [H, B, A], K-major
+    if wt is None:
+        wt = kmajor(w)                                                                     # [H, B, A], K-major
+    assert wt.shape == (H, Bd, A) and wt.dtype == torch.bfloat16 and wt.is_contiguous()
     if x.dtype != torch.bfloat16 or x.stride(2) != 1 or (x.stride(0) * 2) % 16 or (x.stride(1) * 2) % 16 or x.data_ptr() % 16:
         x = x.to(torch.bfloat16).contiguous()
     if out is None:
@@ -258,7 +279,7 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, in
     return y
 
 
-def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, nope: int) -> torch.Tensor:
+def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, nope: int, kc_t=None) -> torch.Tensor:
     """Absorbed query of MLA in one buffer: [q_nope @ W_UK | rope(q_pe)] -> [T, H, R + rope], no concatenation pass."""
     T, H, _ = q.shape
     R = kc.shape[2]
@@ -266,13 +287,13 @@ def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, 
     out = torch.empty(T, H, R + rope, dtype=torch.bfloat16, device=q.device)
     if T == 0:
         return out
-    bmm_absorb(q[..., :nope], kc, out=out[..., :R])
+    bmm_absorb(q[..., :nope], kc, out=out[..., :R], wt=kc_t)
     apply_rope(q[..., nope:], positions, cache, True, out=out[..., R:])
     return out
 
 
 def mla_query(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, rope_cache: torch.Tensor, nope: int, kv_cache: torch.Tensor,
-              dense: bool = True) -> torch.Tensor:
+              dense: bool = True, kc_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Absorbed MLA query.  For the dense fp8 attention kernel (fp8 cache of 64-token pages, 512 + 64 wide rows, at most
     128 heads) the result is e4m3 [T, H, 576]: the per-head GEMM's epilogue writes the latent part as e4m3 straight into it
     and one small kernel rotates and casts the 64-wide tail, instead of a bf16 latent query, a RoPE pass and a cast pass."""
@@ -280,9 +301,9 @@ def mla_query(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, rope_c
     R = kc.shape[2]
     rope = q.shape[2] - nope
     if not (dense and kv_cache.dtype == FP8 and R == 512 and rope == 64 and kv_cache.shape[1] == 64 and H <= 128 and T > 0):
-        return mla_absorb_rope(q, kc, positions, rope_cache, nope)
+        return mla_absorb_rope(q, kc, positions, rope_cache, nope, kc_t)
     q8 = torch.empty(T, H, R + rope, dtype=torch.uint8, device=q.device)
-    bmm_absorb(q[..., :nope], kc, out=q8[..., :R])
+    bmm_absorb(q[..., :nope], kc, out=q8[..., :R], wt=kc_t)
     pe = q[..., nope:]
     pos = positions if positions.dtype == torch.int64 else positions.long()
     _ck(lib().ne_mla_q_finalize(_p(None), _p(pe), _c.c_longlong(pe.stride(0)), _c.c_int(pe.stride(1)), _p(pos), _p(rope_cache), _p(q8),
@@ -318,15 +339,19 @@ def gqa_kv_store(k_cache, v_cache, slot_mapping, k, v):
 
 
 # ---- MoE -----------------------------------------------------------------------------------------
-def moe_route(logits, bias, top_k, n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=1.0, scoring="sigmoid"):
+def moe_route(logits, bias, top_k, n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=1.0, scoring="sigmoid",
+              balance_ranks: int = 0, log2phy: Optional[torch.Tensor] = None, logcnt: Optional[torch.Tensor] = None):
+    """`balance_ranks`, `log2phy` / `logcnt` (int32 device tables [E, R] / [E]): see `reference.moe_route`."""
     planes = logits.shape[0] if logits.dim() == 3 else 1
     T, E = logits.shape[-2:]
     logits = logits.float().contiguous()
     idx = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
     w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    if log2phy is not None:
+        assert log2phy.dtype == torch.int32 and logcnt.dtype == torch.int32 and log2phy.is_contiguous() and log2phy.shape[0] == E
     _ck(lib().ne_moe_route(_p(logits), _p(bias), _p(idx), _p(w), _c.c_int(T), _c.c_int(E), _c.c_int(top_k), _c.c_int(n_group), _c.c_int(topk_group),
                            _c.c_int(1 if norm_topk_prob else 0), _c.c_float(routed_scaling_factor), _c.c_int(0 if scoring == "sigmoid" else 1),
-                           _c.c_int(planes), _st()),
+                           _c.c_int(planes), _c.c_int(balance_ranks), _p(log2phy), _p(logcnt), _c.c_int(0 if log2phy is None else log2phy.shape[1]), _st()),
         "ne_moe_route")
     return idx, w
 

@@ -24,6 +24,18 @@ from .dist import get_dist_context
 
 _FUSED = None  # set by parallel.fused_moe.install() when a symmetric heap is available
 
+# Post-steps the routers apply to the expert ids they pick (see ops.reference.moe_route): set once per worker from the
+# engine configuration.  `balance_ranks` > 0 is the `dummy_eplb` switch.
+_ROUTING = {"balance_ranks": 0}
+
+
+def set_routing_options(balance_ranks: int = 0) -> None:
+    _ROUTING["balance_ranks"] = int(balance_ranks)
+
+
+def routing_options() -> dict:
+    return dict(_ROUTING)
+
 
 def set_fused_backend(obj) -> None:
     global _FUSED

@@ -1,7 +1,8 @@
 """Fused expert-parallel MoE: dispatch, grouped GEMMs and combine over NVLink peer memory (kernels in csrc/comm/ep.cu).
 
-``FusedEP`` owns the symmetric receive buffers of one EP group and runs one MoE layer as a fixed kernel sequence with
-no host synchronisation, so it can be captured in the decode CUDA graph.  Capacity per local expert (`cap`) bounds the
+``FusedEP`` owns the symmetric receive buffers of one EP group and runs one MoE layer as five launches (dispatch, gate_up
+GEMM whose prologue waits for the peers, SwiGLU + requant, down GEMM whose epilogue is the combine send and whose last
+CTA signals the peers, weighted reduce) with no host synchronisation, so it can be captured in the decode CUDA graph.  Capacity per local expert (`cap`) bounds the
 rows an expert can receive in one layer; a pair that finds its expert full is dropped and reported through the kernel
 status words (size `cap` from the token budget: the default is four times the balanced load, never less than 256).
 
@@ -74,9 +75,8 @@ class FusedEP:
         L.rank, L.world, L.E_local, L.cap, L.H, L.top_k, L.fp8 = ep_rank, ep_size, E, C, H, top_k, int(fp8)
         self.layout = L
         dev = hp.device
-        self.state = torch.zeros(4, dtype=torch.int32, device=dev)       # [epoch, dispatch CTA counter, -, -]
-        self.counts = torch.zeros(E, dtype=torch.int32, device=dev)
-        self.row_dst = torch.zeros(E * C, dtype=torch.int64, device=dev)
+        self.state = torch.zeros(4, dtype=torch.int32, device=dev)       # [epoch, dispatch / down-GEMM / reduce CTA counters]
+        self._comm1 = self._comm2 = None
         self.g = torch.empty(E, C, 2 * inter, dtype=torch.bfloat16, device=dev)
         if fp8:
             self.h_q = torch.empty(E, C, inter, dtype=FP8, device=dev)
@@ -85,6 +85,24 @@ class FusedEP:
             self.h = torch.empty(E, C, inter, dtype=torch.bfloat16, device=dev)
         self.pair_ok = torch.zeros(max_tokens * top_k, dtype=torch.int32, device=dev)
         hp.barrier()
+
+    def _comms(self):
+        """The two GemmComm records of a layer (built once: they hold addresses only, the epoch is read on the device)."""
+        if self._comm1 is None:
+            L, hp = self.layout, self.heap
+            me = hp.peer_ptrs[L.rank]
+            epoch = self.state.data_ptr()
+            c1 = _k.GemmComm()
+            c1.wait_epoch, c1.wait_flags, c1.wait_world, c1.wait_spin = epoch, me + L.off_arrive, L.world, self.spin_limit
+            c2 = _k.GemmComm()
+            c2.scatter_mode, c2.row_info = 2, me + L.off_info
+            for r in range(L.world):
+                c2.scatter_base[r] = hp.peer_ptrs[r] + L.off_ret
+                c2.tail_flag[r] = hp.peer_ptrs[r] + L.off_done + 4 * L.rank
+            c2.tail_counter, c2.tail_epoch, c2.tail_world = self.state.data_ptr() + 8, epoch, L.world
+            c2.tail_clear, c2.tail_clear_n = me + L.off_cnt, self.E_local
+            self._comm1, self._comm2 = c1, c2
+        return self._comm1, self._comm2
 
     def forward(self, experts, x, topk_idx, topk_w, ctx=None, add_in=None):
         lib = _k.lib()
@@ -99,31 +117,28 @@ class FusedEP:
         L = _c.byref(self.layout)
         epoch, ctr = _k._p(self.state), _c.c_void_p(self.state.data_ptr() + 4)
         st = _k._st()
+        c1, c2 = self._comms()
+        cnt = self.heap.peer_ptrs[self.layout.rank] + self.layout.off_cnt       # per-expert row counts, filled by the senders' atomics
         _k._ck(lib.ne_ep_dispatch(L, _k._p(x), _k._p(idx), _k._p(self.pair_ok), _c.c_int(T * K), epoch, ctr, st), "ne_ep_dispatch")
-        _k._ck(lib.ne_ep_wait_build(L, _k._p(self.counts), _k._p(self.row_dst), epoch, _c.c_int(self.spin_limit), st), "ne_ep_wait_build")
-        ret_dummy = self.g          # D pointer is unused when every row has an explicit destination
         if self.fp8:
             aq = self.b_aq.view(FP8, (E, C, H))
             a_s = self.b_as.view(torch.float32, (E, H // 128, C))
-            _k._gemm(aq, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, self.counts, None, True, a_s, C,
-                     (H // 128) * C, experts.gate_up_scale, False)
+            _k._gemm_comm(aq, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, cnt, True, a_s, C,
+                          (H // 128) * C, experts.gate_up_scale, c1)
             _k._ck(lib.ne_silu_mul(_k._p(self.g), _k._p(None), _k._p(self.h_q), _k._p(self.h_s), _c.c_int(C), _c.c_longlong((I // 128) * C),
-                                   _k._p(self.counts), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
-            _k._gemm(self.h_q, I, C * I, experts.down_proj, ret_dummy, H, 0, C, H, I, E, self.counts, None, True, self.h_s, C,
-                     (I // 128) * C, experts.down_scale, False, row_dst=self.row_dst)
+                                   _c.c_void_p(cnt), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
+            _k._gemm_comm(self.h_q, I, C * I, experts.down_proj, self.g, H, 0, C, H, I, E, cnt, True, self.h_s, C,
+                          (I // 128) * C, experts.down_scale, c2)
         else:
             ab = self.b_abf.view(torch.bfloat16, (E, C, H))
-            _k._gemm(ab, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, self.counts, None, False, None, 0, 0, None, False)
+            _k._gemm_comm(ab, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, cnt, False, None, 0, 0, None, c1)
             _k._ck(lib.ne_silu_mul(_k._p(self.g), _k._p(self.h), _k._p(None), _k._p(None), _c.c_int(0), _c.c_longlong(0),
-                                   _k._p(self.counts), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
-            _k._gemm(self.h, I, C * I, experts.down_proj, ret_dummy, H, 0, C, H, I, E, self.counts, None, False, None, 0, 0, None, False,
-                     row_dst=self.row_dst)
-        _k._ck(lib.ne_ep_signal(L, epoch, st), "ne_ep_signal")
+                                   _c.c_void_p(cnt), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
+            _k._gemm_comm(self.h, I, C * I, experts.down_proj, self.g, H, 0, C, H, I, E, cnt, False, None, 0, 0, None, c2)
         if callable(add_in):
             add_in = add_in()      # shared-expert output from the side stream: joined right before it is consumed
-        _k._ck(lib.ne_ep_reduce(L, _k._p(self.pair_ok), _k._p(w), _k._p(add_in), _k._p(out), _c.c_int(T), epoch, _c.c_int(self.spin_limit), st),
-               "ne_ep_reduce")
-        _k._ck(lib.ne_ep_advance(epoch, st), "ne_ep_advance")
+        _k._ck(lib.ne_ep_reduce(L, _k._p(self.pair_ok), _k._p(w), _k._p(add_in), _k._p(out), _c.c_int(T), epoch, _c.c_int(self.spin_limit),
+                                _c.c_void_p(self.state.data_ptr() + 12), st), "ne_ep_reduce")
         return out
 
 

@@ -2,8 +2,8 @@
 
 ``FusedTP`` owns the symmetric staging buffers of one TP group.  ``gemm_reduce_scatter`` runs the row-parallel GEMM with
 its scatter epilogue, so each tile of the local partial product is stored into the owning rank's stage while later tiles
-are still being computed, and the owner adds the partials; ``all_gather`` pushes this rank's rows into every peer and
-returns the gathered rows as a view of local memory for the consuming GEMM.  Every step is a kernel on the caller's
+are still being computed, and the owner adds the partials; ``all_gather_gemm`` pushes this rank's rows into every peer and
+runs the consuming GEMM straight on the receive buffer, its producer warp gated per source rank.  Every step is a kernel on the caller's
 stream (no host synchronisation), so the sequence can be captured in a CUDA graph.  Waits are bounded and report through
 the kernel status words.
 
@@ -53,19 +53,16 @@ class FusedTP:
         L.rank, L.world, L.rows_per_rank, L.H = self.rank, self.world, self.rpr_cap, hidden
         self.layout = L
         dev = hp.device
-        self.state = torch.zeros(4, dtype=torch.int32, device=dev)        # [epoch, push CTA counter, -, -]
-        self.row_dst = torch.zeros(self.world * self.rpr_cap, dtype=torch.int64, device=dev)
-        self.gather_view = self.b_gather.view(torch.bfloat16, (2, self.world * self.rpr_cap, hidden))
-        self._epoch_host = 0                                              # mirrors the device epoch for buffer parity of views
+        self.state = torch.zeros(4, dtype=torch.int32, device=dev)        # [epoch, push / GEMM-tail / reduce CTA counters]
+        self._comm_rs = None
         hp.barrier()
 
     # ---- helpers ----
     def _args(self):
         return _c.byref(self.layout), _k._p(self.state), _c.c_void_p(self.state.data_ptr() + 4), _k._st()
 
-    def _advance(self):
-        _k._ck(_k.lib().ne_tp_advance(_k._p(self.state), _k._st()), "ne_tp_advance")
-        self._epoch_host += 1
+    def _ctr(self, i: int):
+        return _c.c_void_p(self.state.data_ptr() + 4 * i)
 
     def _rpr(self, total_rows: int) -> int:
         rpr = -(-total_rows // self.world)
@@ -73,10 +70,14 @@ class FusedTP:
             raise ValueError(f"{total_rows} rows exceed the TP staging capacity {self.rpr_cap * self.world}")
         return rpr
 
+    def _stage_slot_bytes(self) -> int:
+        return self.rpr_cap * self.H * 2
+
     # ---- GEMM -> reduce-scatter ----
     def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, add_in=None) -> torch.Tensor:
         """x [T, K_local] @ w[N, K_local]^T summed over the group; returns this rank's rows [ceil(T / world), N]
-        (rows past T are zero-padding sums and must be ignored by the caller)."""
+        (rows past T are zero-padding sums and must be ignored by the caller).  Two launches: the GEMM, whose epilogue stores
+        every row into its owner's stage and whose last CTA raises the flags, and the owner-side reduce."""
         lib = _k.lib()
         N, K = w.shape
         assert N == self.H
@@ -85,19 +86,49 @@ class FusedTP:
         if x.shape[0] != T:               # pad to a multiple of the group size: the extra rows produce zeros in their owners' slots
             x = torch.cat([x, x.new_zeros(T - x.shape[0], x.shape[1])], 0)
         L, epoch, ctr, st = self._args()
-        _k._ck(lib.ne_tp_row_dst(L, _k._p(self.row_dst), _c.c_int(rpr), epoch, st), "ne_tp_row_dst")
-        dummy = self.row_dst            # D is unused: every row has an explicit destination
+        hp, Ly = self.heap, self.layout
+        cm = _k.GemmComm()
+        cm.scatter_mode, cm.scatter_rpr, cm.scatter_epoch = 3, rpr, self.state.data_ptr()
+        cm.scatter_parity_bytes = self.world * self._stage_slot_bytes()
+        for r in range(self.world):
+            cm.scatter_base[r] = hp.peer_ptrs[r] + Ly.off_stage + self.rank * self._stage_slot_bytes()      # my slot in r's stage
+            cm.tail_flag[r] = hp.peer_ptrs[r] + Ly.off_flags + 4 * self.rank                               # flags[0][me] at r
+        cm.tail_counter, cm.tail_epoch, cm.tail_world = self.state.data_ptr() + 8, self.state.data_ptr(), self.world
         x2 = _k._as_bf16_2d(x)
+        dummy = self.state               # D is unused: every row has a destination in some rank's stage
         if w.dtype == FP8:
-            pre = getattr(x, "_ne_q", None)
-            q, s = pre if (pre is not None and pre[0].shape == (T, K)) else _k.quant_fp8_1x128_raw(x2)
-            _k._gemm(q, K, 0, w, dummy, N, 0, T, N, K, 1, None, None, True, s, T, 0, w_scale, False, row_dst=self.row_dst)
+            q, s = _k.quant_fp8_1x128_raw(x2)
+            _k._gemm_comm(q, K, 0, w, dummy, N, 0, T, N, K, 1, None, True, s, T, 0, w_scale, cm)
         else:
-            _k._gemm(x2, x2.stride(0), 0, w, dummy, N, 0, T, N, K, 1, None, None, False, None, 0, 0, None, False, row_dst=self.row_dst)
-        _k._ck(lib.ne_tp_signal(L, _c.c_int(0), epoch, st), "ne_tp_signal")
+            _k._gemm_comm(x2, x2.stride(0), 0, w, dummy, N, 0, T, N, K, 1, None, False, None, 0, 0, None, cm)
         out = torch.empty(rpr, N, dtype=torch.bfloat16, device=x.device)
-        _k._ck(lib.ne_tp_reduce(L, _k._p(add_in), _k._p(out), _c.c_int(rpr), epoch, _c.c_int(self.spin_limit), st), "ne_tp_reduce")
-        self._advance()
+        _k._ck(lib.ne_tp_reduce(L, _k._p(add_in), _k._p(out), _c.c_int(rpr), epoch, _c.c_int(self.spin_limit), self._ctr(3), st), "ne_tp_reduce")
+        return out
+
+    # ---- all-gather -> GEMM ----
+    def all_gather_gemm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """x [rpr, H] on every rank, w [N, H] bf16 -> gathered rows times w^T: [world * rpr, N].  Two launches: the push of this
+        rank's rows into every peer's gather buffer, and the GEMM whose producer warp waits (bounded) for the source ranks of
+        each row block right before loading it - this rank's own rows first - so the product starts while peers' rows are still
+        arriving.  The GEMM's last CTA advances the epoch."""
+        lib = _k.lib()
+        rpr = x.shape[0]
+        N, K = w.shape
+        assert K == self.H and x.shape[1] == self.H and 1 <= rpr <= self.rpr_cap and w.dtype == torch.bfloat16
+        x = _k._as_bf16_2d(x).contiguous()
+        L, epoch, ctr, st = self._args()
+        _k._ck(lib.ne_tp_push(L, _k._p(x), _c.c_int(rpr), _c.c_int(rpr), _c.c_int(0), epoch, ctr, st), "ne_tp_push")
+        hp, Ly = self.heap, self.layout
+        me = hp.peer_ptrs[self.rank]
+        cm = _k.GemmComm()
+        cm.gate_epoch, cm.gate_flags = self.state.data_ptr(), me + Ly.off_flags + 4 * self.world
+        cm.gate_rpr, cm.gate_world, cm.gate_parity_rows, cm.gate_spin = rpr, self.world, self.world * self.rpr_cap, self.spin_limit
+        cm.mb_rot = (self.rank * rpr) // 128 if rpr % 128 == 0 else 0
+        cm.tail_counter, cm.tail_epoch, cm.tail_world, cm.tail_advance = self.state.data_ptr() + 8, self.state.data_ptr(), 0, self.state.data_ptr()
+        T = self.world * rpr
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+        _k._gemm_comm(me + Ly.off_gather, self.H, 0, w, out, N, 0, T, N, K, 1, None, False, None, 0, 0, None, cm,
+                      a_rows_total=2 * self.world * self.rpr_cap)
         return out
 
     # ---- plain collectives ----
@@ -111,23 +142,21 @@ class FusedTP:
         L, epoch, ctr, st = self._args()
         _k._ck(lib.ne_tp_push(L, _k._p(xp), _c.c_int(rows), _c.c_int(rpr), _c.c_int(1), epoch, ctr, st), "ne_tp_push")
         out = torch.empty(rpr, self.H, dtype=torch.bfloat16, device=xp.device)
-        _k._ck(lib.ne_tp_reduce(L, _k._p(None), _k._p(out), _c.c_int(rpr), epoch, _c.c_int(self.spin_limit), st), "ne_tp_reduce")
-        self._advance()
+        _k._ck(lib.ne_tp_reduce(L, _k._p(None), _k._p(out), _c.c_int(rpr), epoch, _c.c_int(self.spin_limit), self._ctr(3), st), "ne_tp_reduce")
         return out
 
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
-        """x [rpr, H] on every rank -> [world * rpr, H]: a view of this rank's gather buffer, valid until the second
-        next collective of this object."""
+        """x [rpr, H] on every rank -> [world * rpr, H] in a tensor of its own (copied out of the receive buffer by the
+        waiting kernel, so the result does not depend on the parity of the call and stays valid for as long as it is held)."""
         lib = _k.lib()
         rpr = x.shape[0]
         assert x.shape[1] == self.H and rpr <= self.rpr_cap
         x = _k._as_bf16_2d(x).contiguous()
         L, epoch, ctr, st = self._args()
-        parity = (self._epoch_host + 1) & 1
         _k._ck(lib.ne_tp_push(L, _k._p(x), _c.c_int(rpr), _c.c_int(max(rpr, 1)), _c.c_int(0), epoch, ctr, st), "ne_tp_push")
-        _k._ck(lib.ne_tp_wait(L, _c.c_int(1), epoch, _c.c_int(self.spin_limit), st), "ne_tp_wait")
-        self._advance()
-        return self.gather_view[parity, : self.world * rpr]
+        out = torch.empty(self.world * rpr, self.H, dtype=torch.bfloat16, device=x.device)
+        _k._ck(lib.ne_tp_wait_copy(L, _k._p(out), _c.c_int(self.world * rpr), epoch, _c.c_int(self.spin_limit), self._ctr(3), st), "ne_tp_wait_copy")
+        return out
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
@@ -138,12 +167,11 @@ class FusedTP:
             L, epoch, ctr, st = self._args()
             _k._ck(lib.ne_tp_push(L, _k._p(x), _c.c_int(T), _c.c_int(T), _c.c_int(2), epoch, ctr, st), "ne_tp_push")
             out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
-            _k._ck(lib.ne_tp_reduce(L, _k._p(None), _k._p(out), _c.c_int(T), epoch, _c.c_int(self.spin_limit), st), "ne_tp_reduce")
-            self._advance()
+            _k._ck(lib.ne_tp_reduce(L, _k._p(None), _k._p(out), _c.c_int(T), epoch, _c.c_int(self.spin_limit), self._ctr(3), st), "ne_tp_reduce")
             return out
         pad = (-T) % self.world
         xp = x if pad == 0 else torch.cat([x, x.new_zeros(pad, x.shape[1])], 0)
-        return self.all_gather(self.reduce_scatter(xp))[:T].clone()
+        return self.all_gather(self.reduce_scatter(xp))[:T]
 
 
 def install(config, dist_ctx, axis: str = "attn_tp") -> Optional[FusedTP]:

@@ -95,6 +95,18 @@ def tp_linear_reduce_scatter(x: torch.Tensor, proj, axis: str = "attn_tp") -> to
     return tp_reduce_scatter(proj(x), axis)
 
 
+def tp_all_gather_linear(x_slice: torch.Tensor, total_rows: int, proj, axis: str = "attn_tp") -> torch.Tensor:
+    """All-gather of the token slices followed by a column-parallel projection: [T/tp, H] per rank -> [T, N_local].
+    With the fused backend (bf16 weight, no bias) the GEMM reads the receive buffer directly and its producer warp waits per
+    source rank, so the product overlaps the arrival of the peers' rows; otherwise gather, then project."""
+    d = get_dist_context()
+    f = _FUSED_TP
+    if (d.group(axis) is not None and x_slice.is_cuda and f is not None and f.axis == axis and proj.bias is None
+            and proj.weight.dtype == torch.bfloat16 and 1 <= x_slice.shape[0] <= f.rpr_cap):
+        return f.all_gather_gemm(x_slice, proj.weight)[:total_rows]
+    return proj(tp_all_gather(x_slice, total_rows, axis))
+
+
 def attn_to_ffn(x_partial: torch.Tensor) -> torch.Tensor:
     """After a row-parallel o_proj whose output is still a per-rank partial sum: reduce-scatter so every rank continues
     with its own slice of the tokens (what the EP experts want), instead of all-reduce + chunk."""

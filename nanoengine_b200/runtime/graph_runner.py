@@ -1,9 +1,14 @@
 """CUDA-graph replay of the decode forward pass.
 
-One graph per batch-size bucket (1, 2, 4, 8, then multiples of 16 up to ``cuda_graph_max_bs``), captured lazily
-after an eager warm-up of the same shape, all sharing one memory pool and one set of persistent input buffers.
+One graph per batch-size bucket (1, 2, 4, 8, then multiples of 16 up to ``cuda_graph_max_bs``), captured after an
+eager warm-up of the same shape, all sharing one memory pool and one set of persistent input buffers.
 Rows beyond the live batch point at the scratch page with context length 1, so a padded replay is valid work
 that touches no live sequence.
+
+When the forward pass contains collectives (expert- or tensor-parallel groups), every bucket is captured up front by
+``capture_all`` - all ranks run it at start-up in the same order, so the warm-up passes and the captures, each of which
+executes the collectives for real, stay matched across ranks.  A rank must never capture on its own later: its peers
+would be replaying one round of collectives against its three.  Without collectives, buckets are captured on first use.
 
 Parity: reference runtime/runner/graph_runner.py:55 (_make_bs_list), :65-540 (DecodeGraphRunner: persistent
 buffers, shared pool, capture per size, run).
@@ -114,11 +119,38 @@ class DecodeGraphRunner:
             self.pool = g.pool()
         self.graphs[b], self.outputs[b] = g, out
 
+    def _fill_padding_only(self, b: int):
+        """Every row of bucket `b` becomes a padding row: q_len tokens of a one-page sequence on the scratch page."""
+        q = self.q_len
+        sb = self.r.cache.scratch_block
+        dev = self.input_ids.device
+        self.input_ids[: b * q].zero_()
+        self.positions[: b * q].copy_(torch.arange(q, device=dev).repeat(b))
+        self.slot_mapping[: b * q].copy_(sb * self.r.plan.block_size + torch.arange(q, device=dev).repeat(b))
+        self.context_lens[:b].fill_(q)
+        self.block_tables[:b].fill_(sb)
+        if self.gdn:
+            self.state_slots[:b].fill_(self.r.cache.scratch_slot)
+            self.seq_fresh[:b].fill_(1)
+
+    def capture_all(self) -> None:
+        """Capture every bucket now, largest first (the pool is sized once), on dummy rows.  Collective: all ranks of the
+        model's EP / TP groups must call this at the same point.
+        Parity: reference runtime/runner/graph_runner.py:298-455 (capture loop with a barrier per size)."""
+        for b in sorted(self.bs_list, reverse=True):
+            if b in self.graphs:
+                continue
+            self._fill_padding_only(b)
+            self._capture(b)
+
     def run(self, ids, pos, ctx: ForwardContext) -> torch.Tensor:
         b = self.bucket(ctx.num_seqs)
         # the padding rows must be in place before a capture too: the warm-up runs on them
         self._fill(ids, pos, ctx, b)
         if b not in self.graphs:
+            if self.r.has_collectives():
+                raise RuntimeError(f"decode graph for batch bucket {b} was not captured at start-up; a rank of a parallel group "
+                                   "must not capture on its own (its peers would not run the matching collectives)")
             self._capture(b)
             self._fill(ids, pos, ctx, b)
         self.graphs[b].replay()

@@ -100,6 +100,8 @@ class ModelRunner:
 
     def init_model(self) -> None:
         cls = get_model_class(self.mc.architecture)
+        from ..parallel.ep import set_routing_options
+        set_routing_options(balance_ranks=self.dist.ep_size if self.config.dummy_eplb else 0)
         torch.manual_seed(self.config.seed)
         lr = self.layer_range()
         self.model = cls(self.mc, dtype=self.dtype, device=self.device, layer_range=lr if self.config.pp > 1 else None)
@@ -128,15 +130,19 @@ class ModelRunner:
         return self.model.load_weights(it)
 
     def update_weights(self, src) -> int:
-        """Replace the weights in place from a checkpoint directory or an iterable of (name, tensor).  Derived copies that
-        kernels cache (transposed / bf16 forms) are dropped so they are rebuilt from the new values."""
+        """Replace the weights in place from a checkpoint directory or an iterable of (name, tensor).  Copies derived from a
+        weight (the K-major forms of the absorbed MLA matrices) are rebuilt by the modules that own them, and the decode
+        graphs, which captured the old copies' addresses, are re-created."""
         keep = expert_owner_filter(self.mc, self.dist.ep_size, self.dist.ep_rank, None)
         it = iterate_safetensors(src, keep, self.device) if isinstance(src, str) else ((n, t) for n, t in src if keep(n))
         n = self.load_weights(it)
-        if self.device.type == "cuda":
-            from ..ops import sm100
-            sm100._BF16_CACHE.clear()
-            self.graphs = None if self.graphs is None else type(self.graphs)(self)
+        for m in list(self.model.modules()) + (list(self.mtp.modules()) if self.mtp is not None else []):
+            if hasattr(m, "refresh_absorbed"):
+                m.refresh_absorbed()
+        if self.device.type == "cuda" and self.graphs is not None:
+            self.graphs = type(self.graphs)(self)
+            if self.has_collectives():
+                self.graphs.capture_all()
         return n
 
     # ---- cache -------------------------------------------------------------------------------
@@ -193,6 +199,13 @@ class ModelRunner:
         if self.device.type == "cuda" and not self.config.enforce_eager and ep_capturable:
             from .graph_runner import DecodeGraphRunner
             self.graphs = DecodeGraphRunner(self)
+            if self.has_collectives():
+                self.graphs.capture_all()
+
+    def has_collectives(self) -> bool:
+        """True when a forward pass talks to other ranks (expert- or tensor-parallel groups), i.e. when every rank has to run
+        the same sequence of forward passes."""
+        return self.dist.ep_size > 1 or self.dist.attn_tp_size > 1
 
     # ---- input preparation ---------------------------------------------------------------------
     def _to_dev(self, arr: np.ndarray, dtype=None) -> torch.Tensor:

@@ -47,6 +47,12 @@ def _worker(rank, world, port, fp8, q):
             full = be.all_gather(got)
             torch.cuda.synchronize()
             worst = max(worst, rel(full[:T], part[:T]))
+            # all-gather -> GEMM with the gated operand (bf16 weights): every rank multiplies the gathered slices
+            if not fp8:
+                wcol = (torch.randn(384, H, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+                prod = be.all_gather_gemm(got, wcol)
+                torch.cuda.synchronize()
+                worst = max(worst, rel(prod[:T], part[:T].to(torch.bfloat16).float() @ wcol.float().t()))
             # stand-alone all-reduce
             y = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
             wanty = y.float().clone()
@@ -67,6 +73,30 @@ def _worker(rank, world, port, fp8, q):
             gr.replay()
             torch.cuda.synchronize()
             worst = max(worst, rel(yg[:T], part))
+        # an ODD number of collectives per graph, replayed an even and an odd number of times, with eager calls in between:
+        # the receive buffers alternate per call on the device, so nothing the host fixed at capture may depend on the parity
+        if not fp8:
+            wcol = (torch.randn(256, H, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+            warm = be.gemm_reduce_scatter(xs, wq, ws)
+            be.all_gather_gemm(warm, wcol)
+            be.all_gather(warm)
+            torch.cuda.synchronize(); dist.barrier()
+            g3 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g3):
+                mine = be.gemm_reduce_scatter(xs, wq, ws)              # 1
+                y3 = be.all_gather_gemm(mine, wcol)                     # 2
+                z3 = be.all_gather(mine)                                # 3
+            for rep in range(5):
+                xs.copy_(torch.randn(T, Kl, device="cuda", generator=g).to(torch.bfloat16))
+                part = ref.linear(xs, wq, ws).float()
+                dist.all_reduce(part)
+                g3.replay()
+                torch.cuda.synchronize()
+                worst = max(worst, rel(z3[:T], part), rel(y3[:T], part.to(torch.bfloat16).float() @ wcol.float().t()))
+                if rep % 2 == 0:                                        # an eager collective between replays shifts the parity again
+                    e = be.all_gather(mine.clone())
+                    torch.cuda.synchronize()
+                    worst = max(worst, rel(e[:T], part))
         st = sm100.kernel_status()
         dist.barrier()
         q.put((rank, worst, st[0]))

@@ -252,6 +252,24 @@ def test_bmm_absorb_on_strided_heads(k):
     assert _rel(k.bmm_absorb(o, vc), ref.bmm_absorb(o, vc)) < 5e-3
 
 
+def test_bmm_absorb_follows_a_weight_reallocated_at_the_same_address(k):
+    """Two weights of one shape, created and freed in turn (the caching allocator tends to hand the second one the first
+    one's address): each product must use the weight it was given, with and without the owner's K-major copy."""
+    torch.manual_seed(10)
+    T, H = 40, 16
+    x = torch.randn(T, H, 128, device="cuda", dtype=torch.bfloat16)
+    ptrs = []
+    for scale in (0.05, 0.3, 0.01):
+        w = (torch.randn(H, 128, 512, device="cuda") * scale).to(torch.bfloat16)
+        ptrs.append(w.data_ptr())
+        want = ref.bmm_absorb(x, w)
+        assert _rel(k.bmm_absorb(x, w), want) < 5e-3
+        assert _rel(k.bmm_absorb(x, w, wt=k.kmajor(w)), want) < 5e-3
+        del w, want
+    # not an assertion on the allocator, only a note for whoever reads a failure: the case is sharpest when addresses repeat
+    print("weight addresses", ptrs)
+
+
 @pytest.mark.parametrize("T", [3, 128, 300])
 def test_bmm_absorb_writes_e4m3_into_a_strided_view(k, T):
     """The e4m3 epilogue: clamped cast of the fp32 accumulator into the first 512 bytes of 576-byte rows; the tail is untouched."""
