@@ -326,6 +326,8 @@ PYBIND11_MODULE(_core, m) {
       .def("allocate", [](BlockPool& p, int n) -> py::object {
         std::vector<int32_t> out; if (!p.allocate(n, &out)) return py::none(); return py::cast(out); })
       .def("commit", &BlockPool::commit)
+      .def("begin_import", &BlockPool::begin_import)
+      .def("finish_import", &BlockPool::finish_import, py::arg("hashes"), py::arg("ids"), py::arg("ok") = true)
       .def("release", &BlockPool::release);
   m.def("chain_hash", [](uint64_t prev, const std::vector<int32_t>& tok) { return chain_hash(prev, tok.data(), (int)tok.size()); });
 

@@ -123,7 +123,15 @@ class BlockPool {
   std::vector<int32_t> begin_import(const std::vector<uint64_t>& hashes) {
     std::vector<int32_t> out;
     for (uint64_t h : hashes) {
-      if (by_hash_.count(h)) { out.push_back(-1); continue; }
+      auto it = by_hash_.find(h);
+      if (it != by_hash_.end()) {
+        // already cached: hold it until finish_import, or a later allocation of this same import could evict the block the
+        // chain being imported hangs on
+        acquire(it->second);
+        import_held_.push_back(it->second);
+        out.push_back(-1);
+        continue;
+      }
       std::vector<int32_t> one;
       if (!allocate(1, &one)) break;
       out.push_back(one[0]);
@@ -139,6 +147,8 @@ class BlockPool {
       release_one(ids[i]);
     }
     log_commits_ = was;
+    for (int32_t id : import_held_) release_one(id);
+    import_held_.clear();
   }
 
   void mark_ready(int id) { blocks_.at(id).state = BLOCK_READY; }
@@ -180,6 +190,7 @@ class BlockPool {
     if (b.ref == 0 && b.in_lru) { lru_.erase(b.lru_it); b.in_lru = false; }
     b.ref++;
   }
+  std::vector<int32_t> import_held_;          // cached blocks referenced by the import in progress
   int block_size_ = 64;
   bool prefix_cache_ = true;
   std::vector<Block> blocks_;

@@ -108,7 +108,10 @@ class Scheduler {
 
   void reset_prefix_cache() {
     for (auto& p : pools_) p.clear_cache();
-    for (auto& kv : seqs_) { kv.second->commit_cursor = (int)kv.second->block_table.size(); }   // live sequences publish nothing stale
+    // Live sequences hold KV that is stale in part: they publish nothing from now on.  (Moving the cursor past the blocks
+    // held now would not do: a later block would be hashed from the old chain value, skipping the tokens in between, and a
+    // different prompt could reproduce that hash.)  A preempted sequence starts over at cursor 0 and publishes again.
+    for (auto& kv : seqs_) kv.second->commit_cursor = INT32_MAX;
   }
 
   // ---- scheduling ------------------------------------------------------------------------

@@ -1,7 +1,9 @@
 """Third KV tier: one file per KV block on a shared or local file system, keyed by the block's chained token hash.
 
 A block file holds the block's bytes of every cache family of every layer (``KVCache.block_views``), preceded by a 32-byte
-header that names the layout, so a file written under another cache plan is rejected instead of silently corrupting KV.
+header that names the layout AND the weights the KV was computed with (a model tag plus a generation counter that every
+live weight update bumps), so a file written under another cache plan, another checkpoint of the same shape or an older
+weight version is rejected instead of being served as a prefix hit.
 Files are written to a temporary name and renamed, so a reader never sees a partial block.  The native ``L3Index`` keeps
 the set of stored hashes in LRU order; with a capacity it reports the hash to drop and the store deletes its file.
 
@@ -28,8 +30,23 @@ from .._native import _core as C
 _MAGIC = b"NEL3BLK1"
 
 
+def model_tag(config) -> str:
+    """Identity of the weights an engine serves, for the block-file header: the checkpoint directory with the names, sizes and
+    modification times of its weight files, or (random-init runs) the model shape and the seed."""
+    import json
+    if getattr(config, "dummy_weight", False) or not os.path.isdir(str(config.model)):
+        return "dummy:" + json.dumps(config.model_config.to_dict(), sort_keys=True, default=str) + f":seed{config.seed}"
+    root = os.path.abspath(config.model)
+    files = []
+    for name in sorted(os.listdir(root)):
+        if name.endswith((".safetensors", ".json")):
+            st = os.stat(os.path.join(root, name))
+            files.append((name, st.st_size, st.st_mtime_ns))
+    return f"ckpt:{root}:{files!r}"
+
+
 class L3Store:
-    def __init__(self, cache, root: str, rank: int = 0, capacity_blocks: int = 0):
+    def __init__(self, cache, root: str, rank: int = 0, capacity_blocks: int = 0, tag: str = ""):
         self.cache = cache
         self.dir = os.path.join(root, f"rank{rank}")
         os.makedirs(self.dir, exist_ok=True)
@@ -37,16 +54,63 @@ class L3Store:
         probe = self.views(0)
         self.segments = [int(v.numel() * v.element_size()) for v in probe]
         self.block_nbytes = sum(self.segments)
-        desc = repr([(tuple(v.shape), str(v.dtype)) for v in probe]).encode()
-        self.fingerprint = hashlib.sha256(desc).digest()[:16]
-        self.header = _MAGIC + struct.pack("<Q", self.block_nbytes) + self.fingerprint
+        self._desc = repr([(tuple(v.shape), str(v.dtype)) for v in probe]).encode()
+        self._tag = tag.encode()
+        self.generation = self._read_generation()
+        if self.generation > 0:
+            # blocks left by a previous process after a live weight update: those weights existed only in that process' memory,
+            # this one loaded the checkpoint again, so they match nothing that can be served now
+            self._purge_files()
+            self._write_generation(0)
+        self._set_header()
         pin = cache.device.type == "cuda"
         self.staging = torch.empty(self.block_nbytes, dtype=torch.uint8, pin_memory=pin)
+        self._capacity = capacity_blocks
         self.index = C.L3Index(capacity_blocks)
         self.bytes_stored = self.bytes_loaded = 0
         self.n_store = self.n_load = self.n_evicted = 0
         self.t_store = self.t_load = 0.0
         self._recover()
+
+    # ---- identity of the stored KV ----
+    def _gen_path(self) -> str:
+        return os.path.join(self.dir, "GENERATION")
+
+    def _read_generation(self) -> int:
+        try:
+            with open(self._gen_path()) as f:
+                return int(f.read().strip() or 0)
+        except (OSError, ValueError):
+            return 0
+
+    def _set_header(self):
+        self.fingerprint = hashlib.sha256(self._desc + b"|" + self._tag + b"|" + str(self.generation).encode()).digest()[:16]
+        self.header = _MAGIC + struct.pack("<Q", self.block_nbytes) + self.fingerprint
+
+    def bump_generation(self) -> int:
+        """The weights changed in place: every stored block is stale.  Moves to the next generation (persisted: a later process
+        that finds a non-zero generation knows the directory holds blocks of weights it cannot have), forgets the index and
+        deletes the block files."""
+        self._write_generation(self.generation + 1)
+        self._set_header()
+        self.index = C.L3Index(self._capacity)
+        self._purge_files()
+        return self.generation
+
+    def _write_generation(self, g: int):
+        self.generation = g
+        tmp = self._gen_path() + f".tmp{os.getpid()}"
+        with open(tmp, "w") as f:
+            f.write(str(g))
+        os.replace(tmp, self._gen_path())
+
+    def _purge_files(self):
+        for name in os.listdir(self.dir):
+            if name.endswith(".kv"):
+                try:
+                    os.unlink(os.path.join(self.dir, name))
+                except OSError:
+                    pass
 
     # ---- layout ----
     def _path(self, h: int) -> str:
@@ -138,7 +202,7 @@ class L3Store:
                 raise FileNotFoundError(f"L3 block {h:#018x} is not at {p}")
             try:
                 if os.pread(fd, len(self.header), 0) != self.header:
-                    raise ValueError(f"L3 block {p} was written under another cache layout")
+                    raise ValueError(f"L3 block {p} was written under another cache layout or with other weights")
                 buf = memoryview(self.staging.numpy())
                 pos = 0
                 while pos < self.block_nbytes:

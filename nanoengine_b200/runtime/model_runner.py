@@ -139,6 +139,8 @@ class ModelRunner:
         for m in list(self.model.modules()) + (list(self.mtp.modules()) if self.mtp is not None else []):
             if hasattr(m, "refresh_absorbed"):
                 m.refresh_absorbed()
+        if getattr(self, "l3", None) is not None:
+            self.l3.bump_generation()            # blocks on disk were computed with the old weights
         if self.device.type == "cuda" and self.graphs is not None:
             self.graphs = type(self.graphs)(self)
             if self.has_collectives():
@@ -305,8 +307,9 @@ class ModelRunner:
 
     # ---- file-backed KV tier (one store per worker: every rank persists its own shard of a block) ----
     def l3_open(self, root: str, capacity_blocks: int = 0) -> int:
-        from .l3_store import L3Store
-        self.l3 = L3Store(self.cache, root, rank=self.dist.rank if self.dist is not None else 0, capacity_blocks=capacity_blocks)
+        from .l3_store import L3Store, model_tag
+        self.l3 = L3Store(self.cache, root, rank=self.dist.rank if self.dist is not None else 0, capacity_blocks=capacity_blocks,
+                          tag=model_tag(self.config))
         return len(self.l3)
 
     def l3_exists(self, hashes: List[int]) -> List[int]:

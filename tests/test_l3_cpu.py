@@ -107,3 +107,37 @@ def test_engine_survives_a_vanished_block_file(tmp_path):
     free_before = a.engine.scheduler.num_free_blocks(0)
     assert a.generate([prompt], sp)[0]["token_ids"] == want        # falls back to recomputing
     assert a.engine.scheduler.num_free_blocks(0) == free_before    # and the reserved blocks were returned
+
+
+def test_blocks_of_other_weights_are_not_adopted(tmp_path):
+    """Same cache layout, other model tag (another checkpoint of the same shape) or an older weight generation: the files stay
+    on disk unread; after a generation bump the old files are gone and the directory remembers the generation."""
+    c = _cache()
+    a = L3Store(c, str(tmp_path), tag="model-A")
+    a.store([(7, 1), (8, 2)])
+    assert len(L3Store(c, str(tmp_path), tag="model-A")) == 2
+    assert len(L3Store(c, str(tmp_path), tag="model-B")) == 0
+    assert a.bump_generation() == 1 and len(a) == 0
+    assert not [n for n in os.listdir(os.path.join(str(tmp_path), "rank0")) if n.endswith(".kv")]
+    a.store([(9, 3)])
+    again = L3Store(c, str(tmp_path), tag="model-A")               # a restart cannot have the updated weights: it starts clean
+    assert again.generation == 0 and len(again) == 0
+
+
+def test_live_weight_update_drops_the_file_tier(tmp_path):
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 1024, (70,), generator=g).tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    a = _llm(tmp_path)
+    a.generate([prompt], sp)
+    store = a.engine.executor.runner.l3
+    assert len(store) == 4
+    # new weights: scale one norm weight so the KV of the same prompt changes
+    name, w = next((n, p) for n, p in a.engine.executor.runner.model.named_parameters() if n.endswith("layers.0.input_layernorm.weight"))
+    a.update_weights([("model." + name.split("model.", 1)[1] if not name.startswith("model.") else name, w.detach() * 1.5)])
+    assert len(store) == 0 and store.generation == 1
+    want = a.generate([prompt], sp)[0]["token_ids"]
+    assert store.n_load == 0                                         # nothing stale was imported
+    b = _llm(tmp_path)
+    assert len(b.engine.executor.runner.l3) == 0                     # a fresh engine has the checkpoint's weights, not the updated ones
+    assert want is not None

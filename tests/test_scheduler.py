@@ -344,3 +344,81 @@ def test_block_pool_states_and_l3_index():
     assert l3.lookup(1) == 10
     assert l3.insert(3, 30) == 2  # LRU entry evicted
     assert l3.match([1, 3, 9]) == 2 and len(l3) == 2
+
+
+def test_exhausted_mtp_handoff_slot_keeps_request_waiting():
+    """Mirror of the reference scenario exhausted_mtp_handoff_slot_keeps_request_waiting (rust/src/scheduler/tests.rs:288)."""
+    s = make(num_speculative_tokens=1, num_handoff_slots=1)
+    add(s, 1, [4] * 5, max_tokens=3)
+    add(s, 2, [4] * 5, max_tokens=3)
+    r, _ = step(s)
+    assert r.batches[0].seq_ids == [1] and s.num_waiting() == 1 and s.num_free_handoff_slots() == 0
+    done = run_all(s)
+    assert set(done) == {1, 2} and s.num_free_handoff_slots() == 1
+
+
+def test_prefix_cache_survives_decode_growth_and_release():
+    """Blocks published during prefill stay valid while the sequence grows by decode and after it is released
+    (rust/src/scheduler/tests.rs:540)."""
+    s = make()
+    prompt = list(range(100, 109))                  # two full blocks + 1
+    add(s, 1, prompt, max_tokens=6)
+    step(s)
+    assert s.num_cached_blocks() == 2
+    run_all(s)                                       # grows to 15 tokens: the third block fills during decode
+    assert s.num_cached_blocks() >= 2
+    add(s, 2, prompt + [7, 7, 7], max_tokens=1)
+    r, _ = step(s)
+    assert r.prefix_hit_tokens >= 8
+
+
+def test_step_reports_prefix_hits_per_dp_rank():
+    """Per-rank hit accounting (rust/src/scheduler/tests.rs:604): the rank that served the prompt before reports the hit."""
+    s = make(attention_dp=2)
+    prompt = list(range(30, 39))
+    add(s, 1, prompt, max_tokens=1)                  # rank 0
+    run_all(s)
+    add(s, 2, [1] * 9, max_tokens=1)                 # rank 1
+    add(s, 3, prompt, max_tokens=1)                  # rank 0 again: hits
+    r, _ = step(s)
+    assert r.prefix_hit_tokens == 8
+    text = s.metrics_prometheus()
+    assert "dlengine_prefix_cache_hit_rate_per_dp" in text
+
+
+def test_reset_prefix_cache_stops_live_sequences_from_publishing():
+    """After the cached prefixes are dropped (weights changed), a sequence that was already running holds KV that is stale in
+    part: nothing it fills later may be published - in particular not under a hash chained from before the reset, which
+    would skip the tokens in between."""
+    s = make()
+    add(s, 1, list(range(200, 206)), max_tokens=12)          # 6 tokens: one full block published, second block half full
+    step(s)
+    assert s.num_cached_blocks() == 1
+    s.reset_prefix_cache()
+    assert s.num_cached_blocks() == 0
+    run_all(s)                                               # fills blocks 2..4 while decoding
+    assert s.num_cached_blocks() == 0
+    add(s, 2, list(range(200, 206)), max_tokens=1)           # a fresh request publishes again
+    run_all(s)
+    assert s.num_cached_blocks() == 1
+
+
+def test_import_holds_the_cached_head_of_its_chain():
+    """begin_import over [cached, missing, missing] with a pool that has to evict to make room: the cached head must not be
+    the block that gets evicted for its own tail."""
+    p = C.BlockPool(3, 4, True)
+    h = [C.chain_hash(0, [1, 2, 3, 4])]
+    h.append(C.chain_hash(h[0], [5, 6, 7, 8]))
+    h.append(C.chain_hash(h[1], [9, 9, 9, 9]))
+    ids = p.allocate(3)
+    p.commit(ids[0], h[0])
+    p.release(ids)                                           # block ids[0] is cached and unreferenced (LRU), two are free
+    spare = p.allocate(1)                                    # leaves one free block: the import of two needs an eviction
+    got = p.begin_import(h)
+    assert got[0] == -1 and len(got) == 2 and got[1] >= 0    # the pool ran dry instead of evicting the head
+    assert p.refcount(ids[0]) == 1
+    p.finish_import(h[: len(got)], got, True)
+    assert p.refcount(ids[0]) == 0 and p.num_cached() == 2
+    m, last = p.match_prefix([1, 2, 3, 4, 5, 6, 7, 8, 0])
+    assert len(m) == 2 and last == h[1]
+    p.release(spare)
