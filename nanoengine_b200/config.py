@@ -84,6 +84,8 @@ class Config:
                 self.model_config = ModelConfig.from_pretrained(self.model)
             else:
                 raise ValueError(f"model '{self.model}' is neither a checkpoint directory nor a preset {sorted(PRESETS)}")
+        elif not os.path.isdir(self.model):
+            self.dummy_weight = True          # a model_config without a checkpoint directory can only be random-init
         for k, v in self.hf_overrides.items():
             if not hasattr(self.model_config, k):
                 raise ValueError(f"unknown model field in hf_overrides: {k}")

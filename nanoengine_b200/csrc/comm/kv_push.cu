@@ -1,7 +1,9 @@
 // PD disaggregation data path: the prefill GPU pushes the KV pages of finished prompts straight into the decode GPU's
 // paged pool with peer stores, translating page ids on the way (prefill page ids differ from decode page ids), then raises
-// a per-request completion flag the decode side polls.  One CTA copies one (layer, page) pair; the last CTA to finish
-// publishes the flags after a system-scope fence, so a flag never overtakes its data.
+// a per-request completion flag the decode side polls.  One CTA copies one (plane, page) pair - a plane is one layer's
+// array of pages in a cache family (MLA latent rows, K or V of a GQA layer, indexer keys) - and the last CTA to finish
+// publishes the flags after a system-scope fence, so a flag never overtakes its data.  A request whose pages live in
+// several families is several launches on one stream; only the last one carries the flag.
 //
 // Replaces in the reference: the decode-side pull of runtime/disagg/p2p/cache_transfer.py:648-1142 (coalesced one-sided
 // reads followed by a device synchronise) and the byte-stride bookkeeping of disagg/p2p/cache_layout.py:14-240.
@@ -44,6 +46,21 @@ __global__ void kv_wait_kernel(const int* flags, const int* idx, int n, int want
   out[i] = wait_flag_ge(flags + idx[i], want, 4, i, (uint32_t)spin_limit) ? 1 : 0;
 }
 
+// The same wait with one expected value per flag, for tickets issued at different times.  A flag that never arrives is an
+// answer here (out[i] = 0: that request's push did not happen), not a fault of this GPU, so nothing goes to the status words.
+__global__ void kv_wait_each_kernel(const int* flags, const int* idx, const int* want, int n, int* out, int spin_limit) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int* p = flags + idx[i];
+  const int w = want[i];
+  int ok = 0;
+  for (int it = 0; it < spin_limit; ++it) {
+    if (ld_acquire_sys(p) >= w) { ok = 1; break; }
+    if (it > 16) __nanosleep(it > 1024 ? 512 : 64);
+  }
+  out[i] = ok;
+}
+
 }  // namespace ne
 
 using namespace ne;
@@ -62,5 +79,11 @@ extern "C" int ne_kv_push(const void* src, void* dst, long long src_layer_stride
 extern "C" int ne_kv_wait(const int* flags, const int* idx, int n, int want, int* out, int spin_limit, cudaStream_t st) {
   if (n <= 0) return 0;
   kv_wait_kernel<<<(n + 127) / 128, 128, 0, st>>>(flags, idx, n, want, out, spin_limit);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ne_kv_wait_each(const int* flags, const int* idx, const int* want, int n, int* out, int spin_limit, cudaStream_t st) {
+  if (n <= 0) return 0;
+  kv_wait_each_kernel<<<(n + 127) / 128, 128, 0, st>>>(flags, idx, want, n, out, spin_limit);
   return (int)cudaGetLastError();
 }

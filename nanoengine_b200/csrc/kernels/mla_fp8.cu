@@ -13,6 +13,8 @@
 //
 // fp8 contract (reference layers/backends/mla/trtllm.py:93-204): the query is clamped to +-448 and cast to e4m3 without
 // a scale, cache rows are clamped-cast e4m3, softmax scale is applied to the fp32 logits.
+#include <atomic>
+
 #include "ptx.cuh"
 #include "tma_host.h"
 
@@ -375,7 +377,9 @@ extern "C" int ne_attn_merge(const float* part, const float* lse2, void* out, in
 extern "C" int ne_mla_fp8_noalloc(const void* q8, const void* cache, int num_blocks, const int* block_tables, int bt_stride,
                                   const int* cu_seqlens_q, const int* context_lens, int num_seqs, int T, int H, int splits, float scale,
                                   void* out, cudaStream_t st) {
-  static unsigned char* scratch_of_device[64] = {nullptr};
+  // per-device address of the scratch array; atomics because host threads may make their first calls at the same time
+  // (they would all resolve the same address, so the last store wins harmlessly)
+  static std::atomic<unsigned char*> scratch_of_device[64];
   if (T <= 0) return 0;
   if (splits < 1 || H < 1 || H > 128) return 1001;
   const long long slice_rows = (long long)splits * T * H;
@@ -384,16 +388,18 @@ extern "C" int ne_mla_fp8_noalloc(const void* q8, const void* cache, int num_blo
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= 64) return 1102;
-  if (!scratch_of_device[dev]) {
+  unsigned char* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     // in host code the array's name is only a handle; the kernels need its address in this device's memory
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return (int)e;
-    scratch_of_device[dev] = static_cast<unsigned char*>(p);
+    scratch = static_cast<unsigned char*>(p);
+    scratch_of_device[dev].store(scratch, std::memory_order_release);
   }
   if (splits == 1)
     return ne_mla_fp8(q8, cache, num_blocks, block_tables, bt_stride, cu_seqlens_q, context_lens, num_seqs, T, H, 1, scale, out, nullptr, nullptr, st);
-  float* part = reinterpret_cast<float*>(scratch_of_device[dev]);
+  float* part = reinterpret_cast<float*>(scratch);
   float* lse2 = part + slice_rows * kDv;
   int rc = ne_mla_fp8(q8, cache, num_blocks, block_tables, bt_stride, cu_seqlens_q, context_lens, num_seqs, T, H, splits, scale, out, part, lse2, st);
   if (rc) return rc;

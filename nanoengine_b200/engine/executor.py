@@ -28,6 +28,8 @@ _LEFT_KEY = "nanoengine/ranks_left"
 
 
 class InprocExecutor:
+    in_process = True          # the workers' tensors are reachable from the controller's address space
+
     def __init__(self, config: Config):
         from ..runtime.model_runner import ModelRunner
         self.config = config
@@ -88,6 +90,8 @@ def _worker_main(rank: int, world_size: int, config_dict: dict, port: int, conn,
 
 
 class MultiprocExecutor:
+    in_process = False
+
     def __init__(self, config: Config, timeout_s: float = 600.0):
         import torch.multiprocessing as mp
         self.config = config
@@ -187,6 +191,8 @@ class SpmdExecutor:
     """One engine per rank, launched by torchrun (one process per GPU).  Every rank schedules the requests of its own
     attention-DP shard; ranks only meet inside the model's collectives, so before each step they agree (one tiny host
     all-reduce) whether anybody has work - a rank without work then runs a dummy batch to keep the collectives matched."""
+
+    in_process = True
 
     def __init__(self, config: Config):
         import torch.distributed as dist

@@ -45,7 +45,10 @@ def expert_owner_filter(cfg: ModelConfig, ep_size: int, ep_rank: int, layer_rang
 def iterate_safetensors(path: str, keep: Optional[Callable[[str], bool]] = None, device="cpu") -> Iterator[Tuple[str, torch.Tensor]]:
     """Yield (name, tensor) from every *.safetensors shard; `keep` is consulted before a tensor is read."""
     from safetensors import safe_open
-    for f in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
+    shards = sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    if not shards:
+        raise FileNotFoundError(f"no *.safetensors shards under {path!r}")
+    for f in shards:
         with safe_open(f, framework="pt", device=str(device)) as sf:
             for name in sf.keys():
                 if keep is None or keep(name):

@@ -3,26 +3,38 @@
 The decode scheduler admits a migrated request by allocating local pages and emitting a ``MigrationIn`` (which remote
 pages land in which local pages).  A ``KVMigrator`` turns that into data movement through a transport:
 
-* ``LocalTransport``   both caches are reachable as tensors in this process (CPU tests, one-GPU PD): indexed page copies.
-* ``PeerPushTransport`` the prefill GPU maps the decode GPU's pool (CUDA IPC) and runs ``ne_kv_push``: peer stores of every
-  (layer, page) plus a completion flag per request, which the decode side checks with a bounded wait.
+* ``LocalTransport``    both caches are reachable as tensors in this process and nothing needs a GPU kernel (CPU engines):
+  indexed page copies.
+* ``PeerPushTransport`` the north-star path: every PREFILL worker has the DECODE workers' pools mapped into its address space
+  (the same process: the tensors themselves; another process: CUDA IPC handles opened once at connect time) and, asked by
+  the decode engine, runs ``ne_kv_push`` - peer stores of every (plane, page) of every cache family into the decode pool's
+  pages, then one completion flag per request in the decode GPU's memory.  The decode worker checks the flags with a
+  bounded device wait; a request whose flag never comes is failed on its own, the engine keeps serving.
+
+  The control path is one message per batch of requests from the decode engine to the prefill engine (``pusher``): a direct
+  call when both engines live in one process, the engine server's ``ACT_PD_PUSH`` packet otherwise.
 
 Before moving anything the two engines' layouts are checked for compatibility (architecture, page size, cache dtype,
-layer count, MTP layers): a mismatch fails the request instead of corrupting the pool.
+layer count, MTP layers; then every cache family's plane count and page bytes): a mismatch fails at connect time instead
+of corrupting the pool.  Page ids are validated against both pools before submission.
 
 Parity: reference runtime/disagg/p2p/cache_transfer.py:1144-1756 (migrate_from_bytes: validation :1180-1200, per
-(layer, block) ops, MTP hand-off restore), :81-108 (bounds validation before submission), cache_layout.py:14-240.
+(layer, block) ops, MTP hand-off restore), :81-108 (bounds validation before submission), :203-425 (memory registration),
+cache_layout.py:14-240.  The reference's decode side READS from the prefill pool (RDMA / NVLink through dlslime); here the
+prefill side WRITES, which posts stores over NVLink instead of waiting for load round trips.
 """
 from __future__ import annotations
 
-import ctypes as _c
-from typing import Dict, List, Optional, Sequence, Tuple
+import pickle
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from .._native import _core as C
 
 _COMPAT_KEYS = ("architecture", "block_size", "kv_cache_dtype", "num_hidden_layers", "mtp_num_kv_layers")
+PD_FLAGS_PER_SOURCE = 64           # completion-flag words a decode worker keeps per prefill rank
+PD_MAX_SOURCES = 16
 
 
 def check_compatible(local_info: Dict, remote_info: Dict) -> None:
@@ -31,12 +43,39 @@ def check_compatible(local_info: Dict, remote_info: Dict) -> None:
         raise ValueError("PD engines are not compatible: " + ", ".join(f"{k}: {local_info.get(k)} != {remote_info.get(k)}" for k in bad))
     if local_info.get("attention_sp", 1) != 1 or remote_info.get("attention_sp", 1) != 1:
         raise ValueError("PD migration requires attention_sp == 1 on both sides")
+    if local_info.get("attention_tp", 1) != remote_info.get("attention_tp", 1):
+        raise ValueError("PD migration requires the same attention_tp on both sides (KV heads are sharded by it)")
 
 
 def validate_blocks(blocks: Sequence[int], num_blocks: int, what: str) -> None:
     for b in blocks:
         if not (0 <= b < num_blocks):
             raise ValueError(f"{what} page id {b} outside the pool of {num_blocks} pages")
+
+
+# ---- pool descriptors: what a decode worker publishes and a prefill worker opens ----------------------------------------
+def export_tensor(t: torch.Tensor, direct: bool):
+    """`direct`: the tensor itself (same process).  Otherwise bytes that rebuild a view of the same device memory in another
+    process on this machine (CUDA IPC through torch's tensor reduction)."""
+    if direct or not t.is_cuda:
+        return t
+    from torch.multiprocessing.reductions import reduce_tensor
+    fn, args = reduce_tensor(t)
+    return pickle.dumps((fn, args))
+
+
+def open_tensor(h) -> torch.Tensor:
+    if isinstance(h, torch.Tensor):
+        return h
+    fn, args = pickle.loads(h)
+    return fn(*args)
+
+
+def check_families(mine: List[dict], theirs: List[dict]) -> None:
+    a = [(f["name"], f["planes"], f["page_bytes"]) for f in mine]
+    b = [(f["name"], f["planes"], f["page_bytes"]) for f in theirs]
+    if a != b:
+        raise ValueError(f"PD cache layouts differ: prefill {a} vs decode {b}")
 
 
 class LocalTransport:
@@ -62,36 +101,58 @@ class LocalTransport:
             d.mtp_runner.restore_handoff(dst_slot, s.mtp_runner.publish_handoff(src_slot))
         return n
 
+    # ticket interface used by KVMigrator: a local copy is complete when it returns
+    def submit(self, src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot):
+        return ("done", self.copy(src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot))
+
+    def finish(self, tickets) -> List[bool]:
+        return [True] * len(tickets)
+
 
 class PeerPushTransport:
-    """One prefill GPU pushing into one decode GPU's pool through a peer mapping of that pool."""
+    """Decode-engine side of the push protocol.
 
-    def __init__(self, src_cache, dst_kv_peer: torch.Tensor, dst_flags_peer: torch.Tensor):
-        from ..ops import sm100
-        self.k = sm100
-        self.src_cache = src_cache
-        self.dst_kv = dst_kv_peer            # tensor view of the remote pool (opened from a CUDA IPC handle)
-        self.flags = dst_flags_peer          # int32 flag words in the remote GPU's memory
-        self.counter = torch.zeros(1, dtype=torch.int32, device=src_cache.kv.device)
+    `pusher(requests)`  asks the prefill engine to push; `requests` is a list of dicts {src_dp, dst_dp, src_blocks,
+                        dst_blocks, src_slot, dst_slot, flag, epoch}.  Returns the bytes each request will move (the pushes
+                        are queued on the prefill GPUs' streams when it returns, not necessarily finished).
+    `waiter(dst_dp, flags, epochs)`  bounded device wait on the decode worker `dst_dp`; returns one bool per flag.
+    """
+
+    def __init__(self, pusher: Callable[[List[dict]], List[int]], waiter: Callable[[int, List[int], List[int]], List[bool]]):
+        self.pusher, self.waiter = pusher, waiter
         self.epoch = 0
+        self._next_flag: Dict[int, int] = {}
+        self._pending: List[dict] = []
 
-    def push(self, src_blocks: List[int], dst_blocks: List[int], flag_slots: List[int]) -> int:
-        kv = self.src_cache.kv
-        plan = self.src_cache.plan
-        assert plan.mla, "the push kernel moves MLA latent pages"
-        dev = kv.device
-        layers = kv.shape[0]
-        page_bytes = kv.shape[2] * kv.shape[3] * kv.element_size()
-        sb = torch.tensor(src_blocks, dtype=torch.int32, device=dev)
-        db = torch.tensor(dst_blocks, dtype=torch.int32, device=dev)
-        fi = torch.tensor(flag_slots, dtype=torch.int32, device=dev)
+    def submit(self, src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot):
+        if not (0 <= src_dp < PD_MAX_SOURCES):
+            raise ValueError(f"prefill rank {src_dp} outside the flag table")
         self.epoch += 1
-        k = self.k
-        k._ck(k.lib().ne_kv_push(k._p(kv), k._p(self.dst_kv), _c.c_longlong(kv.stride(0) * kv.element_size()),
-                                 _c.c_longlong(self.dst_kv.stride(0) * self.dst_kv.element_size()), _c.c_int(page_bytes), k._p(sb), k._p(db),
-                                 _c.c_int(len(src_blocks)), _c.c_int(layers), k._p(self.flags), k._p(fi), _c.c_int(len(flag_slots)),
-                                 _c.c_int(self.epoch), k._p(self.counter), k._st()), "ne_kv_push")
-        return len(src_blocks) * layers * page_bytes
+        k = self._next_flag.get(src_dp, 0)
+        self._next_flag[src_dp] = (k + 1) % PD_FLAGS_PER_SOURCE
+        req = {"src_dp": int(src_dp), "dst_dp": int(dst_dp), "src_blocks": list(map(int, src_blocks)), "dst_blocks": list(map(int, dst_blocks)),
+               "src_slot": int(src_slot), "dst_slot": int(dst_slot), "flag": src_dp * PD_FLAGS_PER_SOURCE + k, "epoch": self.epoch}
+        self._pending.append(req)
+        return req
+
+    def finish(self, tickets) -> List[bool]:
+        """Send every submitted request to the prefill engine in one message, then wait for the flags."""
+        reqs, self._pending = self._pending, []
+        try:
+            sizes = self.pusher(reqs)
+        except Exception:
+            return [False] * len(tickets)
+        for r, n in zip(reqs, sizes):
+            r["nbytes"] = n
+        ok = {}
+        by_dst: Dict[int, List[dict]] = {}
+        for r in reqs:
+            by_dst.setdefault(r["dst_dp"], []).append(r)
+        for dst, lst in by_dst.items():
+            got = self.waiter(dst, [r["flag"] for r in lst], [r["epoch"] for r in lst])
+            for r, g in zip(lst, got):
+                ok[r["epoch"]] = bool(g)
+        return [ok.get(t["epoch"], False) for t in tickets]
 
 
 class KVMigrator:
@@ -106,6 +167,7 @@ class KVMigrator:
 
     def pull(self, blobs: Sequence[bytes]) -> Tuple[List[int], List[int], int]:
         ok, bad, nbytes = [], [], 0
+        sids, tickets = [], []
         for blob in blobs:
             m = C.MigrationIn.from_bytes(blob)
             for i, sid in enumerate(m.seq_ids):
@@ -117,8 +179,37 @@ class KVMigrator:
                         raise ConnectionError("prefill peer disappeared before the push")
                     validate_blocks(src, self.remote_blocks, "remote")
                     validate_blocks(dst, self.local_blocks, "local")
-                    nbytes += self.transport.copy(m.remote_dp_idx[i], m.dp_idx, src, dst, m.remote_handoff_slots[i], m.local_handoff_slots[i])
-                    ok.append(sid)
+                    tickets.append(self.transport.submit(m.remote_dp_idx[i], m.dp_idx, src, dst, m.remote_handoff_slots[i], m.local_handoff_slots[i]))
+                    sids.append(sid)
                 except Exception:
                     bad.append(sid)
+        for sid, t, good in zip(sids, tickets, self.transport.finish(tickets) if tickets else []):
+            if good:
+                ok.append(sid)
+                nbytes += t[1] if isinstance(t, tuple) else int(t.get("nbytes", 0))
+            else:
+                bad.append(sid)
         return ok, bad, nbytes
+
+
+# ---- wiring ----------------------------------------------------------------------------------------------------------------
+def connect_inproc(prefill_engine, decode_engine) -> KVMigrator:
+    """Both engines live in this process (their executors may still own worker processes): the decode workers publish their
+    pools, the prefill workers open them, and the decode engine gets a migrator that pushes through direct calls."""
+    direct = prefill_engine.executor.in_process and decode_engine.executor.in_process
+    pools = decode_engine.executor.collective_rpc("pd_export_pool", direct)
+    key = decode_engine.config.engine_id
+    prefill_engine.executor.collective_rpc("pd_open_pool", key, pools)
+
+    def pusher(reqs):
+        # every prefill worker sees the batch and serves the requests of its own attention-DP rank (all TP ranks of it)
+        per_worker = prefill_engine.executor.collective_rpc("pd_push", key, reqs)
+        return [max(col) for col in zip(*per_worker)] if reqs else []
+
+    def waiter(dst_dp, flags, epochs):
+        per_worker = [r for r in decode_engine.executor.collective_rpc("pd_wait", dst_dp, flags, epochs) if r is not None]
+        return [all(col) for col in zip(*per_worker)] if per_worker else [False] * len(flags)
+
+    mig = KVMigrator(PeerPushTransport(pusher, waiter), decode_engine.engine_info(), prefill_engine.engine_info())
+    decode_engine.migrator = mig
+    return mig

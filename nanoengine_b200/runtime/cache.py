@@ -136,6 +136,33 @@ class KVCache:
             self.rec_states = [self.rec[l] for l in range(plan.gdn_layers)]
             self.conv_states = [self.conv[l] for l in range(plan.gdn_layers)]
 
+    # ---- byte layout of the per-page cache families (what a PD transfer or any other page mover needs to know) ----
+    def page_families(self) -> List[dict]:
+        """One entry per cache family that is indexed by page id: `tensor` (the whole family), `planes` (how many
+        [pages, page_bytes] arrays it is made of: layers, or 2 x layers for separate K and V), `plane_stride` and `page_bytes`
+        in bytes.  Page `p` of plane `i` starts at byte `i * plane_stride + p * page_bytes` of the family.
+        Parity: reference runtime/disagg/p2p/cache_layout.py:14-240 (strides of the KV, indexer and state families)."""
+        def fam(name, t, planes):
+            es = t.element_size()
+            per_plane = t.numel() * es // planes
+            pages = self.num_blocks + 1
+            return {"name": name, "tensor": t, "planes": planes, "plane_stride": per_plane, "page_bytes": per_plane // pages}
+        out = [fam("mla_kv" if self.plan.mla else "gqa_kv", self.kv, self.kv.shape[0] if self.plan.mla else 2 * self.kv.shape[1])]
+        if self.indexer is not None:
+            out.append(fam("indexer", self.indexer, self.indexer.shape[0]))
+        return out
+
+    def slot_families(self) -> List[dict]:
+        """Cache families indexed by a per-sequence state slot instead of a page id (gated delta-net state and convolution
+        window): same description, with `slot_bytes` in place of `page_bytes`."""
+        out = []
+        if self.plan.gdn:
+            for name, t in (("gdn_state", self.rec), ("gdn_conv", self.conv)):
+                planes = t.shape[0]
+                per_plane = t.numel() * t.element_size() // planes
+                out.append({"name": name, "tensor": t, "planes": planes, "plane_stride": per_plane, "slot_bytes": per_plane // t.shape[1]})
+        return out
+
     def allocate_host(self, num_host_blocks: int):
         """Pinned host tier used by preemption swap."""
         if num_host_blocks <= 0:

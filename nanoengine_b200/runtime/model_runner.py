@@ -324,6 +324,117 @@ class ModelRunner:
     def l3_stats(self) -> dict:
         return self.l3.stats()
 
+    # ---- prefill -> decode KV push (see parallel/kv_transfer.py) -------------------------------------------------
+    def pd_export_pool(self, direct: bool = False) -> dict:
+        """Decode side: describe this worker's page pools, completion flags and MTP hand-off table so that a prefill worker on
+        this machine can map them (`direct`: hand over the tensors themselves, for a prefill engine in the same process)."""
+        from ..parallel.kv_transfer import PD_FLAGS_PER_SOURCE, PD_MAX_SOURCES, export_tensor
+        if getattr(self, "pd_flags", None) is None:
+            self.pd_flags = torch.zeros(PD_MAX_SOURCES * PD_FLAGS_PER_SOURCE, dtype=torch.int32, device=self.device)
+        fams = []
+        for f in self.cache.page_families():
+            t = f["tensor"]
+            flat = (t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).reshape(-1)
+            fams.append({"name": f["name"], "planes": f["planes"], "plane_stride": f["plane_stride"], "page_bytes": f["page_bytes"],
+                         "tensor": export_tensor(flat, direct)})
+        return {"dp": self.dist.attn_dp_rank, "tp": self.dist.attn_tp_rank, "num_blocks": self.cache.num_blocks, "families": fams,
+                "flags": export_tensor(self.pd_flags, direct),
+                "handoff": export_tensor(self.mtp_runner.handoff, direct) if self.mtp_runner is not None else None}
+
+    def pd_open_pool(self, key: str, pools: List[dict]) -> int:
+        """Prefill side: map the pools of the decode engine `key` (those of this worker's TP rank) and check that every cache
+        family has the layout of the local one.  Returns how many pools are mapped."""
+        from ..parallel.kv_transfer import check_families, open_tensor
+        mine = self.cache.page_families()
+        peers = getattr(self, "_pd_peers", None)
+        if peers is None:
+            peers = self._pd_peers = {}
+        n = 0
+        for p in pools:
+            if p["tp"] != self.dist.attn_tp_rank:
+                continue
+            check_families(mine, p["families"])
+            q = dict(p)
+            q["families"] = [dict(f, tensor=open_tensor(f["tensor"])) for f in p["families"]]
+            q["flags"] = open_tensor(p["flags"])
+            q["handoff"] = open_tensor(p["handoff"]) if p.get("handoff") is not None else None
+            peers[(key, p["dp"])] = q
+            n += 1
+        if self.device.type == "cuda":
+            self._pd_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+            for q in peers.values():                 # one small cross-device copy makes the runtime enable peer access both ways
+                if q["flags"].device != self.device:
+                    q["flags"][-1:].copy_(torch.zeros(1, dtype=torch.int32, device=self.device))
+            torch.cuda.synchronize(self.device)
+        return n
+
+    def pd_push(self, key: str, reqs: List[dict]) -> List[int]:
+        """Prefill side: queue the push of every request in `reqs` that this worker's attention-DP rank prefilled.  Per request:
+        the MTP hand-off row, then one `ne_kv_push` per cache family; the last launch raises the request's flag (value
+        `epoch`) in the decode GPU's memory.  Returns the bytes queued per request (0 for requests of other ranks)."""
+        import ctypes as _c
+        sizes = []
+        for r in reqs:
+            if r["src_dp"] != self.dist.attn_dp_rank:
+                sizes.append(0)
+                continue
+            peer = self._pd_peers[(key, r["dst_dp"])]
+            sb, db = r["src_blocks"], r["dst_blocks"]
+            if len(sb) != len(db) or any(not (0 <= b < self.cache.num_blocks) for b in sb) or any(not (0 <= b < peer["num_blocks"]) for b in db):
+                raise ValueError("kv push: page ids outside the pools")        # never hand a bad index to the kernel
+            if peer["handoff"] is not None and self.mtp_runner is not None and r["src_slot"] >= 0 and r["dst_slot"] >= 0:
+                peer["handoff"][r["dst_slot"]].copy_(self.mtp_runner.handoff[r["src_slot"]])
+            fams = self.cache.page_families()
+            total = 0
+            if self.device.type != "cuda":
+                for f, pf in zip(fams, peer["families"]):
+                    src = (f["tensor"].view(torch.uint8) if f["tensor"].dtype == torch.float8_e4m3fn else f["tensor"]).reshape(-1).view(torch.uint8)
+                    dst = pf["tensor"].view(torch.uint8)
+                    for pl in range(f["planes"]):
+                        for s_, d_ in zip(sb, db):
+                            so, do = pl * f["plane_stride"] + s_ * f["page_bytes"], pl * pf["plane_stride"] + d_ * pf["page_bytes"]
+                            dst[do:do + f["page_bytes"]] = src[so:so + f["page_bytes"]]
+                    total += f["planes"] * len(sb) * f["page_bytes"]
+                peer["flags"][r["flag"]] = r["epoch"]
+                sizes.append(total)
+                continue
+            from ..ops import sm100 as k
+            dev = self.device
+            sbt = torch.tensor(sb, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            dbt = torch.tensor(db, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            fi = torch.tensor([r["flag"]], dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            for i, (f, pf) in enumerate(zip(fams, peer["families"])):
+                last = i == len(fams) - 1
+                k._ck(k.lib().ne_kv_push(_c.c_void_p(f["tensor"].data_ptr()), _c.c_void_p(pf["tensor"].data_ptr()),
+                                         _c.c_longlong(f["plane_stride"]), _c.c_longlong(pf["plane_stride"]), _c.c_int(f["page_bytes"]),
+                                         k._p(sbt), k._p(dbt), _c.c_int(len(sb)), _c.c_int(f["planes"]), _c.c_void_p(peer["flags"].data_ptr()),
+                                         k._p(fi), _c.c_int(1 if last else 0), _c.c_int(r["epoch"]), k._p(self._pd_counter), k._st()), "ne_kv_push")
+                total += f["planes"] * len(sb) * f["page_bytes"]
+            if not sb:                       # nothing to move (a prompt that fits no page yet): the flag still has to come
+                peer["flags"][r["flag"]] = r["epoch"]
+            sizes.append(total)
+        return sizes
+
+    def pd_wait(self, dst_dp: int, flags: List[int], epochs: List[int], spin_limit: int = 1 << 22):
+        """Decode side: bounded wait until flag `flags[i]` has reached `epochs[i]`; one bool per flag.  Workers of other
+        attention-DP ranks return None.  A flag that does not come within the limit is False - the device, the stream and the
+        kernels' status words are untouched."""
+        if dst_dp != self.dist.attn_dp_rank:
+            return None
+        if getattr(self, "pd_flags", None) is None:
+            return [False] * len(flags)
+        if self.device.type != "cuda":
+            return [int(self.pd_flags[f]) >= e for f, e in zip(flags, epochs)]
+        import ctypes as _c
+        from ..ops import sm100 as k
+        dev = self.device
+        fi = torch.tensor(flags, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+        want = torch.tensor(epochs, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+        out = torch.zeros(len(flags), dtype=torch.int32, device=dev)
+        k._ck(k.lib().ne_kv_wait_each(k._p(self.pd_flags), k._p(fi), k._p(want), _c.c_int(len(flags)), k._p(out), _c.c_int(spin_limit), k._st()),
+              "ne_kv_wait_each")
+        return [bool(v) for v in out.tolist()]
+
     @torch.inference_mode()
     def run_batch(self, b) -> "C.RunnerOut":
         self.timer.start("swap")

@@ -72,3 +72,71 @@ def test_incompatible_engines_and_vanished_peer():
     outs = decode.generate()
     assert len(outs) == 1                              # the failed request was dropped, the other one decoded
     assert decode.engine.scheduler.num_free_blocks() == 64
+
+
+def _push_pair(**kw):
+    from nanoengine_b200.parallel.kv_transfer import connect_inproc
+    prefill, decode = LLM(_cfg("prefill", engine_id="p0", **kw)), LLM(_cfg("decode", engine_id="d0", **kw))
+    connect_inproc(prefill.engine, decode.engine)
+    return prefill, decode
+
+
+def test_push_protocol_equals_hybrid():
+    """The push transport end to end on CPU engines: the decode workers publish their pools, the prefill worker maps them and
+    copies pages by the same (plane, page) arithmetic the GPU kernel uses, completion flags gate the admission."""
+    sp = SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True)
+    want = {o["seq_id"]: o["token_ids"] for o in LLM(_cfg("hybrid")).generate(_prompts(), sp)}
+    prefill, decode = _push_pair()
+    firsts = {}
+    for b in prefill.generate(_prompts(), sp, return_serialized=True):
+        sid, first = RequestMigrate.from_bytes(b).metadata
+        firsts[sid] = first
+        decode.add_request_payload(b)
+    outs = {o["seq_id"]: [firsts[o["seq_id"]]] + o["token_ids"] for o in decode.generate()}
+    assert outs == want
+    flags = decode.engine.executor.runner.pd_flags
+    assert sorted(int(v) for v in flags if int(v) > 0) == [1, 2, 3]        # one ticket per request, each raised once
+    summary = decode.engine.scheduler.metrics_summary()
+    assert summary.get("transfer_bytes", 1) > 0
+
+
+def test_push_with_mtp_and_indexer_pages():
+    """A DSA model with MTP: indexer key pages travel with the latent pages and the draft hand-off row lands in the decode
+    engine's table."""
+    from nanoengine_b200.models.config import tiny_deepseek_v3
+    mc = tiny_deepseek_v3(index_topk=8, index_n_heads=4, index_head_dim=128, num_nextn_predict_layers=1)
+    kw = dict(model_config=mc, num_speculative_tokens=2, dummy_weight=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = {o["seq_id"]: o["token_ids"] for o in LLM(_cfg("hybrid", **kw)).generate(_prompts()[:2], sp)}
+    prefill, decode = _push_pair(**kw)
+    assert [f["name"] for f in decode.engine.executor.runner.cache.page_families()] == ["mla_kv", "indexer"]
+    firsts = {}
+    for b in prefill.generate(_prompts()[:2], sp, return_serialized=True):
+        sid, first = RequestMigrate.from_bytes(b).metadata
+        firsts[sid] = first
+        decode.add_request_payload(b)
+    outs = {o["seq_id"]: [firsts[o["seq_id"]]] + o["token_ids"] for o in decode.generate()}
+    assert outs == want
+
+
+def test_push_whose_producer_never_runs_fails_only_that_request():
+    prefill, decode = _push_pair()
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    blobs = prefill.generate(_prompts()[:2], sp, return_serialized=True)
+    tr = decode.engine.migrator.transport
+    real = tr.pusher
+    tr.pusher = lambda reqs: [0] + real(reqs[1:])            # the first request's push is never queued: its flag never comes
+    for b in blobs:
+        decode.add_request_payload(b)
+    outs = decode.generate()
+    assert len(outs) == 1
+    assert decode.engine.scheduler.num_free_blocks() == 64
+
+
+def test_layout_mismatch_is_refused_at_connect_time():
+    from nanoengine_b200.parallel.kv_transfer import check_families
+    a = [{"name": "mla_kv", "planes": 2, "page_bytes": 1024}]
+    with pytest.raises(ValueError):
+        check_families(a, [{"name": "mla_kv", "planes": 2, "page_bytes": 2048}])
+    with pytest.raises(ValueError):
+        check_families(a, a + [{"name": "indexer", "planes": 2, "page_bytes": 64}])
