@@ -70,6 +70,7 @@ class Config:
     ctrl_address: Optional[str] = None
     host: str = "127.0.0.1"
     port: int = 8000
+    pd_peers: Dict[str, str] = field(default_factory=dict)   # decode engines: prefill engine id -> ZMQ endpoint of its engine process
 
     def __post_init__(self):
         self.validate()

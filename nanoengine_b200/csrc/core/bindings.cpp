@@ -70,6 +70,7 @@ PYBIND11_MODULE(_core, m) {
   m.attr("ACT_STEPOUT_BATCH") = (int)ACT_STEPOUT_BATCH; m.attr("ACT_ABORT") = (int)ACT_ABORT;
   m.attr("ACT_GET_METRICS") = (int)ACT_GET_METRICS; m.attr("ACT_START_PROFILER") = (int)ACT_START_PROFILER;
   m.attr("ACT_STOP_PROFILER") = (int)ACT_STOP_PROFILER;
+  m.attr("ACT_PD_OPEN") = (int)ACT_PD_OPEN; m.attr("ACT_PD_PUSH") = (int)ACT_PD_PUSH;
 
   py::class_<SamplingParams>(m, "SamplingParams")
       .def(py::init([](float temperature, int max_tokens, bool ignore_eos, bool return_completion_logprobs) {

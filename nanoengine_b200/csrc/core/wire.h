@@ -31,6 +31,8 @@ enum WireTag : uint8_t {
 enum WireAction : int32_t {
   ACT_ADD = 1, ACT_GET_INFO = 2, ACT_FREE = 3, ACT_STEPOUT_BATCH = 4, ACT_ABORT = 5,
   ACT_GET_METRICS = 6, ACT_START_PROFILER = 7, ACT_STOP_PROFILER = 8,
+  ACT_PD_OPEN = 9,    // decode engine -> prefill engine: map my workers' KV pools (reply: the prefill engine's info)
+  ACT_PD_PUSH = 10,   // decode engine -> prefill engine: push these pages into my pools (reply: bytes queued per request)
 };
 
 struct WireError : std::runtime_error { using std::runtime_error::runtime_error; };

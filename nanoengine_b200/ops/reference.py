@@ -631,3 +631,100 @@ def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh
             o[s:e], S = gdn_scan(qn[s:e], kn[s:e], vf[s:e], g[s:e], beta[s:e], S)
         state[slot] = S
     return rmsnorm_gated(o, z, norm_w, eps).reshape(T, Hv * Dv)
+
+
+# ---- MTP draft verification -------------------------------------------------------------------------------
+def mtp_greedy_verify(logits: torch.Tensor, drafts: torch.Tensor):
+    """logits [B, N+1, V], drafts [B, N].  Returns (num_accepted [B] in 0..N, next_token [B]): the longest prefix with
+    argmax(row_i) == d_{i+1}; the next token is the argmax of the first mismatching row, or of the bonus row
+    (reference runtime/runner/mtp_runner.py:190-208)."""
+    am = logits.argmax(-1)                                   # [B, N+1]
+    match = (am[:, :-1] == drafts).to(torch.int64)
+    acc = match.cumprod(1).sum(1)                            # [B]
+    nxt = am.gather(1, acc.unsqueeze(1)).squeeze(1)
+    return acc, nxt
+
+
+def mtp_rejection_sample(logits: torch.Tensor, drafts: torch.Tensor, temperatures: torch.Tensor,
+                         generator: Optional[torch.Generator] = None, uniforms: Optional[torch.Tensor] = None,
+                         have: Optional[torch.Tensor] = None):
+    """Speculative sampling for greedy (one-hot) drafts (reference runtime/runner/mtp_runner.py:111-187).
+
+    Draft d_{i+1} is accepted with probability p_target(d_{i+1} | row i), one uniform coin per position; the accepted count
+    is the length of the all-accepted prefix.  The next token is sampled from the target row at the first rejection with the
+    rejected draft masked out (from the bonus row, unmasked, when everything was accepted) - which preserves the target
+    distribution.  Rows with temperature < 1e-5 fall back to greedy verification.
+    Returns (num_accepted [B], next_token [B], logprob_of_next [B] under the unmasked target row).
+    """
+    B, N1, V = logits.shape
+    N = N1 - 1
+    greedy = temperatures < 1e-5
+    t = torch.where(greedy, torch.ones_like(temperatures), temperatures).view(B, 1, 1)
+    logp = torch.log_softmax(logits.float() / t, -1)          # [B, N+1, V]
+    p_draft = logp[:, :N].gather(2, drafts.long().unsqueeze(-1)).squeeze(-1).exp()    # [B, N]
+    if uniforms is None:
+        uniforms = torch.rand(B, N, generator=generator, device=logits.device, dtype=torch.float32)
+    accept = (uniforms < p_draft).to(torch.int64)
+    has = torch.ones(B, dtype=torch.bool, device=logits.device) if have is None else have.to(logits.device) != 0
+    accept = accept * has.view(B, 1).to(torch.int64)
+    acc = accept.cumprod(1).sum(1)
+    row = logp.gather(1, acc.view(B, 1, 1).expand(B, 1, V)).squeeze(1)               # target row at the stop position
+    masked = row.clone()
+    rejected = (acc < N) & has
+    if N > 0:
+        rej_tok = drafts.long().gather(1, acc.clamp_max(N - 1).unsqueeze(1)).squeeze(1)
+        masked[rejected, rej_tok[rejected]] = float("-inf")
+    u = torch.rand(B, V, generator=generator, device=logits.device, dtype=torch.float32).clamp_min(1e-20)
+    nxt = (masked - torch.log(-torch.log(u))).argmax(-1)
+    g_acc, g_nxt = mtp_greedy_verify(logits, drafts)
+    g_acc = torch.where(has, g_acc, torch.zeros_like(g_acc))
+    g_nxt = torch.where(has, g_nxt, logits[:, 0].argmax(-1))
+    acc = torch.where(greedy, g_acc, acc)
+    nxt = torch.where(greedy, g_nxt, nxt)
+    row = logp.gather(1, acc.view(B, 1, 1).expand(B, 1, V)).squeeze(1)
+    return acc, nxt, row.gather(1, nxt.unsqueeze(1)).squeeze(1)
+
+
+def mtp_verify(logits: torch.Tensor, drafts: torch.Tensor, temperatures: torch.Tensor, have: Optional[torch.Tensor] = None,
+               coins: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None, force_accept: Optional[int] = None,
+               want_logprob: bool = False, seed: Optional[int] = None, seed_buf: Optional[torch.Tensor] = None):
+    """One verify step for every sequence: logits [B, N+1, V] of rows [last token, d1..dN], drafts [B, N], temperatures [B],
+    `have` [B] (0 = the sequence carries no drafts: nothing is accepted), `coins` [B, N] uniforms of the acceptance test.
+    Returns (num_accepted int32 [B], next_token int64 [B], bundle int64 [B, N+1] = accepted drafts + next token, -1 beyond,
+    extend_tokens int64 [B, N+1] = the predictor's token inputs for the draft-extend pass, logprob fp32 [B] or None).
+    `force_accept` pins the accepted count and takes the arg-max of that row (benchmarks)."""
+    B, N1, V = logits.shape
+    N = N1 - 1
+    drafts = drafts.long()
+    lp = None
+    if force_accept is not None:
+        acc = torch.full((B,), min(force_accept, N), dtype=torch.int64, device=logits.device)
+        nxt = logits.argmax(-1).gather(1, acc.unsqueeze(1)).squeeze(1)
+    elif bool((temperatures < 1e-5).all()):
+        acc, nxt = mtp_greedy_verify(logits, drafts)
+        if have is not None:
+            keep = have.to(logits.device) != 0
+            acc = torch.where(keep, acc, torch.zeros_like(acc))
+            nxt = torch.where(keep, nxt, logits[:, 0].argmax(-1))
+    else:
+        acc, nxt, lp = mtp_rejection_sample(logits, drafts, temperatures, generator, coins, have)
+    if want_logprob or lp is not None:
+        t = torch.where(temperatures < 1e-5, torch.ones_like(temperatures), temperatures).view(B, 1)
+        row = logits.float().gather(1, acc.view(B, 1, 1).expand(B, 1, V)).squeeze(1) / t
+        lp = torch.log_softmax(row, -1).gather(1, nxt.unsqueeze(1)).squeeze(1)
+    idx = torch.arange(N1, device=logits.device).view(1, N1)
+    dpad = torch.cat([drafts, drafts.new_zeros(B, 1)], 1)
+    a = acc.view(B, 1)
+    bundle = torch.where(idx < a, dpad, torch.where(idx == a, nxt.view(B, 1), torch.full_like(dpad, -1)))
+    ext = torch.where(idx < a, dpad, nxt.view(B, 1).expand(B, N1))
+    return acc.to(torch.int32), nxt, bundle, ext, lp
+
+
+def mtp_chain_meta(base_len, num_accepted, block_tables, block_size: int, k: int, positions, slot_mapping, context_lens) -> None:
+    """Positions, cache slots and context lengths of chain step `k` of the draft predictor: the token drafted at step k sits at
+    position base_len + num_accepted + k - 1."""
+    pos = (base_len.long() + num_accepted.long() + (k - 1))
+    positions.copy_(pos)
+    context_lens.copy_((pos + 1).to(context_lens.dtype))
+    page = block_tables.long().gather(1, (pos // block_size).unsqueeze(1)).squeeze(1)
+    slot_mapping.copy_(page * block_size + pos % block_size)

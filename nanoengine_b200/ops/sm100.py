@@ -602,3 +602,47 @@ def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     _ck(lib().ne_sigmoid_gate(_p(o), _p(gate), _c.c_longlong(gate.stride(0)), _c.c_longlong(gate.stride(1)), _p(out), _c.c_longlong(T), _c.c_int(Hh),
                               _c.c_int(D), _st()), "ne_sigmoid_gate")
     return out
+
+
+# ---- MTP draft verification --------------------------------------------------------------------------------
+mtp_greedy_verify = ref.mtp_greedy_verify
+mtp_rejection_sample = ref.mtp_rejection_sample
+
+
+def mtp_verify(logits: torch.Tensor, drafts: torch.Tensor, temperatures: torch.Tensor, have: Optional[torch.Tensor] = None,
+               coins: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None, force_accept: Optional[int] = None,
+               want_logprob: bool = False, seed: Optional[int] = None, seed_buf: Optional[torch.Tensor] = None):
+    """Two kernels, no host synchronisation (see csrc/kernels/mtp.cu); same contract as `reference.mtp_verify`.  The sampled
+    rows draw from a counter-based hash of a seed: `seed_buf` (int64 [1] on the device, read at run time - what a captured
+    CUDA graph uses, with the caller bumping it every step), else `seed`, else one taken from `generator`."""
+    B, N1, V = logits.shape
+    N = N1 - 1
+    dev = logits.device
+    logits = logits.float().contiguous()
+    drafts = drafts.to(torch.int64).contiguous()
+    temps = temperatures.float().contiguous()
+    acc = torch.empty(B, dtype=torch.int32, device=dev)
+    nxt = torch.empty(B, dtype=torch.int64, device=dev)
+    bundle = torch.empty(B, N1, dtype=torch.int64, device=dev)
+    ext = torch.empty(B, N1, dtype=torch.int64, device=dev)
+    lp = torch.empty(B, dtype=torch.float32, device=dev) if want_logprob else None
+    stats = torch.empty(B * N1 * 4, dtype=torch.int32, device=dev)
+    if seed is None:
+        seed = int(torch.randint(0, 2 ** 62, (1,), generator=generator).item()) if generator is not None and generator.device.type == "cpu" else 0x5eed
+    hv = None if have is None else have.to(torch.int32).contiguous()
+    cn = None if coins is None else coins.float().contiguous()
+    _ck(lib().ne_mtp_verify(_p(logits), _p(drafts), _p(temps), _p(hv), _p(cn), _p(stats), _p(acc), _p(nxt), _p(bundle), _p(ext), _p(lp),
+                            _c.c_int(B), _c.c_int(N), _c.c_int(V), _c.c_int(-1 if force_accept is None else int(force_accept)),
+                            _c.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(seed_buf), _st()), "ne_mtp_verify")
+    LAUNCHES[0] += 1
+    return acc, nxt, bundle, ext, lp
+
+
+def mtp_chain_meta(base_len: torch.Tensor, num_accepted: torch.Tensor, block_tables: torch.Tensor, block_size: int, k: int,
+                   positions: torch.Tensor, slot_mapping: torch.Tensor, context_lens: torch.Tensor) -> None:
+    """Positions, cache slots and context lengths of chain step `k` of the draft predictor, from the accepted counts on the device."""
+    B = base_len.numel()
+    assert base_len.dtype == torch.int32 and num_accepted.dtype == torch.int32 and block_tables.dtype == torch.int32
+    assert positions.dtype == torch.int64 and slot_mapping.dtype == torch.int64 and context_lens.dtype == torch.int32
+    _ck(lib().ne_mtp_chain_meta(_p(base_len), _p(num_accepted), _p(block_tables), _c.c_int(block_tables.stride(0)), _c.c_int(block_size), _c.c_int(k),
+                                _c.c_int(B), _p(positions), _p(slot_mapping), _p(context_lens), _st()), "ne_mtp_chain_meta")

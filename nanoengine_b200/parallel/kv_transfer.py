@@ -156,20 +156,31 @@ class PeerPushTransport:
 
 
 class KVMigrator:
-    """Attached to a decode engine (``engine.migrator``).  `pull` is called with the serialized MigrationIn batches."""
+    """Attached to a decode engine (``engine.migrator``).  `pull` is called with the serialized MigrationIn batches.
+    One transport per prefill engine: `add_peer` registers further ones, requests are routed by the engine id they carry."""
 
     def __init__(self, transport, local_info: Dict, remote_info: Dict, remote_num_blocks: Optional[int] = None):
         check_compatible(local_info, remote_info)
         self.transport = transport
+        self.local_info = local_info
         self.local_blocks = local_info["num_blocks"]
         self.remote_blocks = remote_num_blocks if remote_num_blocks is not None else remote_info["num_blocks"]
+        self.peers: Dict[str, Tuple[object, int]] = {str(remote_info.get("id", "")): (transport, self.remote_blocks)}
         self.fail_next = False           # host-side fault injection for tests: pretend the peer vanished
+
+    def add_peer(self, transport, remote_info: Dict) -> None:
+        check_compatible(self.local_info, remote_info)
+        self.peers[str(remote_info.get("id", ""))] = (transport, remote_info["num_blocks"])
+
+    def _route(self, engine_id: str):
+        return self.peers.get(str(engine_id), (self.transport, self.remote_blocks))
 
     def pull(self, blobs: Sequence[bytes]) -> Tuple[List[int], List[int], int]:
         ok, bad, nbytes = [], [], 0
-        sids, tickets = [], []
+        batches: Dict[int, Tuple[object, List[int], list]] = {}          # per transport: sequence ids and their tickets
         for blob in blobs:
             m = C.MigrationIn.from_bytes(blob)
+            eids = list(getattr(m, "remote_engine_ids", []) or [])
             for i, sid in enumerate(m.seq_ids):
                 lo, hi = m.block_offsets[i], m.block_offsets[i + 1]
                 src, dst = list(m.remote_blocks[lo:hi]), list(m.local_blocks[lo:hi])
@@ -177,18 +188,21 @@ class KVMigrator:
                     if self.fail_next:
                         self.fail_next = False
                         raise ConnectionError("prefill peer disappeared before the push")
-                    validate_blocks(src, self.remote_blocks, "remote")
+                    tr, remote_blocks = self._route(eids[i] if i < len(eids) else "")
+                    validate_blocks(src, remote_blocks, "remote")
                     validate_blocks(dst, self.local_blocks, "local")
-                    tickets.append(self.transport.submit(m.remote_dp_idx[i], m.dp_idx, src, dst, m.remote_handoff_slots[i], m.local_handoff_slots[i]))
-                    sids.append(sid)
+                    t = tr.submit(m.remote_dp_idx[i], m.dp_idx, src, dst, m.remote_handoff_slots[i], m.local_handoff_slots[i])
+                    b = batches.setdefault(id(tr), (tr, [], []))
+                    b[1].append(sid); b[2].append(t)
                 except Exception:
                     bad.append(sid)
-        for sid, t, good in zip(sids, tickets, self.transport.finish(tickets) if tickets else []):
-            if good:
-                ok.append(sid)
-                nbytes += t[1] if isinstance(t, tuple) else int(t.get("nbytes", 0))
-            else:
-                bad.append(sid)
+        for tr, sids, tickets in batches.values():
+            for sid, t, good in zip(sids, tickets, tr.finish(tickets)):
+                if good:
+                    ok.append(sid)
+                    nbytes += t[1] if isinstance(t, tuple) else int(t.get("nbytes", 0))
+                else:
+                    bad.append(sid)
         return ok, bad, nbytes
 
 
@@ -213,3 +227,75 @@ def connect_inproc(prefill_engine, decode_engine) -> KVMigrator:
     mig = KVMigrator(PeerPushTransport(pusher, waiter), decode_engine.engine_info(), prefill_engine.engine_info())
     decode_engine.migrator = mig
     return mig
+
+
+# ---- the same protocol between two engine processes (ZMQ packets of the engine server) -------------------------------------
+def _hexify(pools: List[dict]) -> List[dict]:
+    def hx(v):
+        return v.hex() if isinstance(v, (bytes, bytearray)) else v
+    return [dict(p, families=[dict(f, tensor=hx(f["tensor"])) for f in p["families"]], flags=hx(p["flags"]), handoff=hx(p.get("handoff"))) for p in pools]
+
+
+def _unhexify(pools: List[dict]) -> List[dict]:
+    def ux(v):
+        return bytes.fromhex(v) if isinstance(v, str) else v
+    return [dict(p, families=[dict(f, tensor=ux(f["tensor"])) for f in p["families"]], flags=ux(p["flags"]), handoff=ux(p.get("handoff"))) for p in pools]
+
+
+def serve_pd_packet(engine, action: int, payload: bytes) -> bytes:
+    """Prefill engine process: answer one ACT_PD_OPEN / ACT_PD_PUSH packet (JSON both ways; the memory handles inside are the
+    pickled CUDA IPC descriptors torch uses between its own processes, so this channel is for engines of one deployment on
+    one machine - an `ipc://` endpoint - not for untrusted peers)."""
+    import json
+    msg = json.loads(payload)
+    if action == C.ACT_PD_OPEN:
+        n = sum(engine.executor.collective_rpc("pd_open_pool", msg["key"], _unhexify(msg["pools"])))
+        return json.dumps({"mapped": n, "info": engine.engine_info()}).encode()
+    per_worker = engine.executor.collective_rpc("pd_push", msg["key"], msg["reqs"])
+    return json.dumps({"sizes": [max(col) for col in zip(*per_worker)] if msg["reqs"] else []}).encode()
+
+
+class PdPeerClient:
+    """Decode engine process: blocking client of one prefill engine's socket."""
+
+    def __init__(self, endpoint: str, timeout_s: float = 30.0):
+        import zmq
+        self.ctx = zmq.Context.instance()
+        self.sock = self.ctx.socket(zmq.DEALER)
+        self.sock.setsockopt(zmq.LINGER, 0)
+        self.sock.connect(endpoint)
+        self.timeout_ms = int(timeout_s * 1000)
+
+    def call(self, action: int, obj: dict) -> dict:
+        import json
+        self.sock.send(C.WirePacket(action, json.dumps(obj).encode()).to_bytes())
+        if not self.sock.poll(self.timeout_ms):
+            raise TimeoutError("the prefill engine did not answer")
+        pkt = C.WirePacket.from_bytes(self.sock.recv())
+        out = json.loads(pkt.payload)
+        if "error" in out:
+            raise RuntimeError(f"prefill engine: {out['error']}")
+        return out
+
+
+def connect_remote(decode_engine, prefill_engine_id: str, endpoint: str) -> KVMigrator:
+    """Decode engine process: publish the workers' pools to the prefill engine behind `endpoint` and attach (or extend) the
+    migrator that asks it to push."""
+    cli = PdPeerClient(endpoint)
+    key = decode_engine.config.engine_id
+    pools = decode_engine.executor.collective_rpc("pd_export_pool", False)
+    rinfo = cli.call(C.ACT_PD_OPEN, {"key": key, "pools": _hexify(pools)})["info"]
+
+    def pusher(reqs):
+        return cli.call(C.ACT_PD_PUSH, {"key": key, "reqs": reqs})["sizes"]
+
+    def waiter(dst_dp, flags, epochs):
+        per_worker = [r for r in decode_engine.executor.collective_rpc("pd_wait", dst_dp, flags, epochs) if r is not None]
+        return [all(col) for col in zip(*per_worker)] if per_worker else [False] * len(flags)
+
+    tr = PeerPushTransport(pusher, waiter)
+    if decode_engine.migrator is None:
+        decode_engine.migrator = KVMigrator(tr, decode_engine.engine_info(), rinfo)
+    else:
+        decode_engine.migrator.add_peer(tr, rinfo)
+    return decode_engine.migrator

@@ -201,8 +201,13 @@ class ModelRunner:
         if self.device.type == "cuda" and not self.config.enforce_eager and ep_capturable:
             from .graph_runner import DecodeGraphRunner
             self.graphs = DecodeGraphRunner(self)
+            if self.mtp_runner is not None:
+                from .mtp_runner import MTPGraphRunner
+                self.mtp_runner.graphs = MTPGraphRunner(self, self.mtp_runner)
             if self.has_collectives():
                 self.graphs.capture_all()
+                if self.mtp_runner is not None:
+                    self.mtp_runner.graphs.capture_all()
 
     def has_collectives(self) -> bool:
         """True when a forward pass talks to other ranks (expert- or tensor-parallel groups), i.e. when every rank has to run

@@ -53,6 +53,9 @@ def run_engine_backend(config_dict: dict, endpoint: str, ready=None, engine_fact
         from ..engine.llm_engine import LLMEngine
         engine = LLMEngine(Config.from_dict(config_dict))
     owner: Dict[int, bytes] = {}       # seq_id -> client identity
+    for peer_id, peer_ep in (config_dict.get("pd_peers") or {}).items():
+        from ..parallel.kv_transfer import connect_remote
+        connect_remote(engine, peer_id, peer_ep)      # decode role: prefill engines that will push KV into this engine's pools
     if ready is not None:
         ready.set()
     running = True
@@ -97,6 +100,14 @@ def run_engine_backend(config_dict: dict, endpoint: str, ready=None, engine_fact
             elif a == C.ACT_STOP_PROFILER:
                 paths = engine.stop_profiler()
                 sock.send_multipart([ident, C.WirePacket(a, json.dumps(paths).encode()).to_bytes()])
+            elif a in (C.ACT_PD_OPEN, C.ACT_PD_PUSH):
+                # a decode engine on this machine asks this (prefill) engine to map its pools / push pages into them
+                from ..parallel.kv_transfer import serve_pd_packet
+                try:
+                    reply = serve_pd_packet(engine, a, pkt.payload)
+                    sock.send_multipart([ident, C.WirePacket(a, reply).to_bytes()])
+                except Exception as e:
+                    sock.send_multipart([ident, C.WirePacket(a, json.dumps({"error": str(e)}).encode()).to_bytes()])
             elif a == 99:   # shutdown
                 running = False
         if not running:

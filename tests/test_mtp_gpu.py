@@ -1,0 +1,131 @@
+"""MTP speculative decoding on the GPU: the verify kernels against the PyTorch statement, and the engine with fp8 weights -
+the captured verify pipeline (one CUDA graph per step, one device->host copy) against the same pipeline run eagerly and
+against plain greedy decoding."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def k():
+    from nanoengine_b200.ops import sm100
+    sm100.lib()
+    return sm100
+
+
+def _random_case(B, N, V, seed, match_prob=0.6):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    logits = torch.randn(B, N + 1, V, device="cuda", generator=g) * 3
+    am = logits.argmax(-1)
+    drafts = torch.where(torch.rand(B, N, device="cuda", generator=g) < match_prob, am[:, :N],
+                         torch.randint(0, V, (B, N), device="cuda", generator=g))
+    return logits, drafts
+
+
+@pytest.mark.parametrize("B,N,V", [(1, 1, 33), (7, 2, 1024), (64, 5, 5000), (128, 3, 129280)])
+def test_greedy_verify_matches_reference(k, B, N, V):
+    from nanoengine_b200.ops import reference as ref
+    logits, drafts = _random_case(B, N, V, 1)
+    have = (torch.arange(B, device="cuda") % 5 != 0).to(torch.int32)
+    temps = torch.zeros(B, device="cuda")
+    acc, nxt, bundle, ext, lp = k.mtp_verify(logits, drafts, temps, have, want_logprob=True)
+    racc, rnxt, rbundle, rext, rlp = ref.mtp_verify(logits, drafts, temps, have, want_logprob=True)
+    assert torch.equal(acc, racc) and torch.equal(nxt, rnxt) and torch.equal(bundle, rbundle) and torch.equal(ext, rext)
+    assert torch.allclose(lp, rlp, atol=2e-3)
+    assert int(acc.max()) > 0 and int((acc * (1 - have)).sum()) == 0
+    # pinned acceptance (benchmarks): the next token is the arg-max of that row
+    acc2, nxt2, *_ = k.mtp_verify(logits, drafts, temps, have, force_accept=1)
+    assert bool((acc2 == min(1, N)).all()) and torch.equal(nxt2, logits.argmax(-1)[:, min(1, N)])
+
+
+def test_rejection_sampling_on_the_device(k):
+    from nanoengine_b200.ops import reference as ref
+    B, N, V = 4096, 2, 6
+    p = torch.tensor([0.45, 0.25, 0.12, 0.1, 0.05, 0.03], device="cuda")
+    logits = torch.log(p).view(1, 1, V).repeat(B, N + 1, 1).contiguous()
+    drafts = torch.zeros(B, N, dtype=torch.long, device="cuda")            # the draft model always proposes token 0
+    temps = torch.ones(B, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    coins = torch.rand(B, N, device="cuda", generator=g)
+    acc, nxt, bundle, ext, lp = k.mtp_verify(logits, drafts, temps, None, coins, seed=1234, want_logprob=True)
+    racc, *_ = ref.mtp_verify(logits, drafts, temps, None, coins)
+    assert torch.equal(acc, racc)                                           # same coins, same acceptance
+    rejected = acc < N
+    assert bool((nxt[rejected] != 0).all())                                 # the rejected draft is never drawn again
+    # the token emitted at position 0 follows the target distribution
+    first = torch.where(acc >= 1, torch.zeros_like(nxt), nxt)
+    freq = torch.bincount(first, minlength=V).float() / B
+    assert torch.allclose(freq, p, atol=0.03), freq
+    assert torch.allclose(lp, torch.log(p)[nxt], atol=1e-3)
+    # another seed draws other tokens; the device-side seed buffer does the same for a captured graph
+    _, nxt_b, *_ = k.mtp_verify(logits, drafts, temps, None, coins, seed=99)
+    assert not torch.equal(nxt, nxt_b)
+    sb = torch.tensor([5], dtype=torch.int64, device="cuda")
+    _, n1, *_ = k.mtp_verify(logits, drafts, temps, None, coins, seed_buf=sb)
+    sb.add_(1)
+    _, n2, *_ = k.mtp_verify(logits, drafts, temps, None, coins, seed_buf=sb)
+    assert not torch.equal(n1, n2)
+
+
+def test_chain_metadata_kernel(k):
+    from nanoengine_b200.ops import reference as ref
+    B, bs = 9, 64
+    base = torch.tensor([1, 63, 64, 65, 127, 128, 200, 10, 5], dtype=torch.int32, device="cuda")
+    acc = torch.tensor([0, 1, 2, 0, 1, 2, 3, 0, 1], dtype=torch.int32, device="cuda")
+    bt = torch.randint(0, 50, (B, 6), dtype=torch.int32, device="cuda")
+    for kk in (1, 2):
+        out = [torch.empty(B, dtype=torch.int64, device="cuda"), torch.empty(B, dtype=torch.int64, device="cuda"),
+               torch.empty(B, dtype=torch.int32, device="cuda")]
+        want = [torch.empty_like(t) for t in out]
+        k.mtp_chain_meta(base, acc, bt, bs, kk, *out)
+        ref.mtp_chain_meta(base, acc, bt, bs, kk, *want)
+        for a, b in zip(out, want):
+            assert torch.equal(a, b)
+
+
+def _engine(**kw):
+    from nanoengine_b200 import Config, LLM
+    from nanoengine_b200.models.config import tiny_deepseek_v3
+    mc = tiny_deepseek_v3(hidden_size=512, moe_intermediate_size=256, intermediate_size=1024, q_lora_rank=256, kv_lora_rank=512,
+                          qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_attention_heads=16, quant="fp8",
+                          num_nextn_predict_layers=1)
+    base = dict(model="tiny-deepseek-v3", model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kv_cache_dtype="fp8",
+                kvcache_block_size=64, num_kvcache_blocks=64, max_num_seqs=8, seed=0)
+    base.update(kw)
+    return LLM(Config(**base))
+
+
+def test_speculative_engine_graph_equals_eager_and_plain_greedy():
+    from nanoengine_b200 import SamplingParams
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (48, 70, 5, 129, 33)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    plain = [o["token_ids"] for o in _engine().generate(prompts, sp)]
+    spec = _engine(num_speculative_tokens=2)
+    runner = spec.engine.executor.runner
+    assert runner.mtp_runner.graphs is not None
+    got = [o["token_ids"] for o in spec.generate(prompts, sp)]
+    assert runner.mtp_runner.graphs.graphs, "the verify step was not replayed from a graph"
+    eager = [o["token_ids"] for o in _engine(num_speculative_tokens=2, enforce_eager=True).generate(prompts, sp)]
+    assert got == eager                                   # same kernels, same shapes: the graph changes nothing
+    assert all(len(t) == 12 for t in got)
+    # against plain decoding the rows differ in shape (3 rows per sequence instead of 1), so a near-tie of two logits may fall
+    # the other way in bf16; sequences must agree on their first tokens and almost all must agree entirely
+    same = sum(a == b for a, b in zip(got, plain))
+    assert same >= len(prompts) - 1, (got, plain)
+    assert all(a[:3] == b[:3] for a, b in zip(got, plain))
+    from nanoengine_b200.ops import sm100
+    assert sm100.kernel_status()[0] == 0
+
+
+def test_forced_acceptance_emits_that_many_tokens_per_step():
+    from nanoengine_b200 import SamplingParams
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1024, (40,), generator=g).tolist() for _ in range(4)]
+    llm = _engine(num_speculative_tokens=2)
+    mr = llm.engine.executor.runner.mtp_runner
+    mr.force_accept = 2
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=13, ignore_eos=True))
+    assert all(len(o["token_ids"]) == 13 for o in outs)
+    assert mr.accepted_total == 2 * mr.verify_steps        # 1 + 4 steps x 3 tokens

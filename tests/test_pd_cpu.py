@@ -140,3 +140,63 @@ def test_layout_mismatch_is_refused_at_connect_time():
         check_families(a, [{"name": "mla_kv", "planes": 2, "page_bytes": 2048}])
     with pytest.raises(ValueError):
         check_families(a, a + [{"name": "indexer", "planes": 2, "page_bytes": 64}])
+
+
+def test_pd_packets_between_engine_processes_round_trip():
+    """The ACT_PD_OPEN / ACT_PD_PUSH envelopes: memory handles travel as hex inside JSON and reach every prefill worker as bytes;
+    a ZMQ DEALER/ROUTER pair carries them, errors come back as errors."""
+    import json
+    import threading
+    import zmq
+    from nanoengine_b200._native import _core as C
+    from nanoengine_b200.parallel.kv_transfer import PdPeerClient, _hexify, serve_pd_packet
+
+    class FakeExecutor:
+        def __init__(self):
+            self.calls = []
+
+        def collective_rpc(self, method, *args):
+            self.calls.append((method, args))
+            if method == "pd_open_pool":
+                return [1, 1]
+            if method == "pd_push":
+                return [[10, 0], [0, 20]]                      # two prefill workers, each served its own request
+            raise KeyError(method)
+
+    class FakeEngine:
+        executor = FakeExecutor()
+
+        def engine_info(self):
+            return {"id": "p0", "num_blocks": 9}
+
+    eng = FakeEngine()
+    ep = "inproc://pd-test"
+    ctx = zmq.Context.instance()
+    srv = ctx.socket(zmq.ROUTER)
+    srv.bind(ep)
+
+    def serve(n):
+        for _ in range(n):
+            ident, payload = srv.recv_multipart()
+            pkt = C.WirePacket.from_bytes(payload)
+            try:
+                reply = serve_pd_packet(eng, pkt.action, pkt.payload)
+            except Exception as e:
+                reply = json.dumps({"error": str(e)}).encode()
+            srv.send_multipart([ident, C.WirePacket(pkt.action, reply).to_bytes()])
+
+    th = threading.Thread(target=serve, args=(3,), daemon=True)
+    th.start()
+    cli = PdPeerClient(ep, timeout_s=5.0)
+    pools = [{"dp": 0, "tp": 0, "num_blocks": 4, "families": [{"name": "mla_kv", "planes": 2, "plane_stride": 64, "page_bytes": 16, "tensor": b"\\x01\\x02"}],
+              "flags": b"\\x03", "handoff": None}]
+    out = cli.call(C.ACT_PD_OPEN, {"key": "d0", "pools": _hexify(pools)})
+    assert out["mapped"] == 2 and out["info"]["id"] == "p0"
+    method, (key, got) = eng.executor.calls[0]
+    assert method == "pd_open_pool" and key == "d0" and got[0]["families"][0]["tensor"] == b"\\x01\\x02" and got[0]["flags"] == b"\\x03"
+    assert cli.call(C.ACT_PD_PUSH, {"key": "d0", "reqs": [{"src_dp": 0}, {"src_dp": 1}]})["sizes"] == [10, 20]
+    eng.executor.collective_rpc = lambda *a: (_ for _ in ()).throw(ValueError("kv push: page ids outside the pools"))
+    with pytest.raises(RuntimeError, match="outside the pools"):
+        cli.call(C.ACT_PD_PUSH, {"key": "d0", "reqs": [{"src_dp": 0}]})
+    th.join(timeout=5)
+    srv.close(0)

@@ -27,6 +27,13 @@ def _prompts():
     return [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (150, 70, 129)]
 
 
+def _recv(conn, timeout=180.0):
+    """A peer that failed never answers: give up instead of waiting for the test's own limit."""
+    if not conn.poll(timeout):
+        raise TimeoutError("the other PD process stopped answering")
+    return conn.recv()
+
+
 def _prefill_proc(conn, q):
     # both GPUs stay visible: mapping the decode GPU's memory needs that device in this process too
     os.environ.update(CUDA_VISIBLE_DEVICES="0,1", LOCAL_RANK="0", NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
@@ -35,7 +42,7 @@ def _prefill_proc(conn, q):
         from nanoengine_b200 import LLM, SamplingParams
         llm = LLM(_cfg("prefill", engine_id="p0"))
         runner = llm.engine.executor.runner
-        pools, dinfo = conn.recv()
+        pools, dinfo = _recv(conn)
         assert runner.pd_open_pool("d0", pools) == 1
         conn.send(llm.engine.engine_info())
         sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
@@ -43,7 +50,7 @@ def _prefill_proc(conn, q):
             blobs = llm.generate(_prompts(), sp, return_serialized=True)
             conn.send(blobs)
             while True:
-                msg = conn.recv()
+                msg = _recv(conn)
                 if msg[0] == "push":
                     reqs = msg[1]
                     drop = msg[2]                                   # host-side fault injection: requests the producer never runs
@@ -77,12 +84,12 @@ def _decode_proc(conn, q):
         llm = LLM(_cfg("decode", engine_id="d0"))
         runner = llm.engine.executor.runner
         conn.send(([runner.pd_export_pool(direct=False)], llm.engine.engine_info()))
-        pinfo = conn.recv()
+        pinfo = _recv(conn)
         drop = set()
 
         def pusher(reqs):
             conn.send(("push", reqs, drop))
-            return conn.recv()
+            return _recv(conn)
 
         def waiter(dst_dp, flags, epochs):
             return runner.pd_wait(dst_dp, flags, epochs, spin_limit=1 << 21)
@@ -94,7 +101,7 @@ def _decode_proc(conn, q):
             if round_ == 1:
                 drop.add(1)                                         # the second request of this round is never pushed
             firsts = {}
-            for b in conn.recv():
+            for b in _recv(conn):
                 sid, first = RequestMigrate.from_bytes(b).metadata
                 firsts[sid] = first
                 llm.add_request_payload(b)
@@ -118,7 +125,7 @@ def test_prefill_gpu_pushes_pages_into_the_decode_gpus_pool():
     ps = [ctx.Process(target=_prefill_proc, args=(a, q)), ctx.Process(target=_decode_proc, args=(b, q))]
     for p in ps:
         p.start()
-    res = dict((r[0], r) for r in (q.get(timeout=600) for _ in ps))
+    res = dict((r[0], r) for r in (q.get(timeout=420) for _ in ps))
     for p in ps:
         p.join(timeout=60)
     assert res["prefill"][2] == 0, res["prefill"][1]
