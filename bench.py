@@ -57,8 +57,9 @@ def _summarise_clocks(samples):
 
 
 def reference_arm(args):
-    print(json.dumps({"impl": "reference", "unavailable": "reference cannot be installed offline: its build backend (maturin + a Rust "
-                      "toolchain) is absent, and its kernels need deep_gemm / deep_ep / flash_mla / tvm_ffi wheels that are not in the wheelhouse"}))
+    print(json.dumps({"impl": "reference", "unavailable": "reference cannot be installed offline: its scheduler and wire protocol are the Rust "
+                      "extension dlengine._engine, whose build backend (maturin + a Rust toolchain) is absent, and its DeepSeek-V3 path imports "
+                      "deep_gemm, deep_ep and flash_mla, which are not in the image (tvm_ffi, flashinfer, flash_attn, triton and the CUTLASS DSL are)"}))
     return 0
 
 
@@ -75,6 +76,9 @@ def main():
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the device-timed decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     ap.add_argument("--profile-prefill", action="store_true", help="bracket the second prompt step instead")
+    ap.add_argument("--mtp", type=int, default=0, help="speculative decoding with this many draft tokens per step (1 MTP layer)")
+    ap.add_argument("--force-accept", type=int, default=-1, help="with --mtp: pin the number of accepted drafts per step (random-init "
+                    "predictors accept next to nothing on their own)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -94,16 +98,20 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
 
-    mc = deepseek_v3(n_routed_experts=args.experts_per_gpu * N, num_hidden_layers=args.layers, num_nextn_predict_layers=0)
+    mc = deepseek_v3(n_routed_experts=args.experts_per_gpu * N, num_hidden_layers=args.layers, num_nextn_predict_layers=1 if args.mtp else 0)
     S, P = args.seqs_per_gpu, args.prompt_len
-    total_new = args.warmup + args.steps + 8
+    per_step = (args.force_accept + 1) if (args.mtp and args.force_accept >= 0) else 1
+    total_new = (args.warmup + args.steps + 8) * per_step + 2 * args.mtp
     pages = (P + total_new + 63) // 64 + 1
     cfg = Config(model="deepseek-v3", model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kv_cache_dtype="fp8",
                  max_num_seqs=S, max_num_batched_tokens=16384, max_model_len=P + total_new + 64, num_kvcache_blocks=S * pages + 16,
-                 attention_dp=N, ffn_ep=N, executor_backend="spmd", enable_prefix_caching=False, cuda_graph_max_bs=S, seed=rank)
+                 attention_dp=N, ffn_ep=N, executor_backend="spmd", enable_prefix_caching=False, cuda_graph_max_bs=S, seed=rank,
+                 num_speculative_tokens=args.mtp)
     t_build = time.time()
     llm = LLM(cfg)
     runner = llm.engine.executor.runner
+    if args.mtp and args.force_accept >= 0:
+        runner.mtp_runner.force_accept = args.force_accept
     build_s = time.time() - t_build
 
     g = torch.Generator().manual_seed(1234 + rank)
@@ -159,7 +167,7 @@ def main():
     e0.record()
     for _ in range(args.steps):
         outs = llm.step()
-        assert len(outs) == S
+        assert len(outs) == S, len(outs)
     e1.record()
     e1.synchronize()
     sync()
@@ -168,8 +176,14 @@ def main():
 
     # ---- device-timed: replay the same decode step (graph + lm_head + sampling) K times on resident inputs.
     # Each step streams the full weight set (~100 GB), far beyond the 126 MB L2, so no cache flush is needed between steps.
-    launches = runner.count_step_launches()
-    step_fn = runner.make_resident_decode_step()
+    if args.mtp:
+        launches = runner.mtp_runner.count_step_launches()
+        step_fn = runner.mtp_runner.make_resident_step()
+        graph_ok = None
+    else:
+        graph_ok = runner.graph_step_equals_eager()      # outside the timed region: the replayed step samples what an eager step samples
+        launches = runner.count_step_launches()
+        step_fn = runner.make_resident_decode_step()
     for _ in range(3):
         step_fn()
     sync()
@@ -188,7 +202,7 @@ def main():
     th.join(timeout=2)
 
     if rank == 0:
-        tokens_per_step = S * N
+        tokens_per_step = S * N * per_step
         value = tokens_per_step / (dev_ms * 1e-3)
         out = {
             "metric": "decode out tok/s (whole job; per-GPU = value / n_gpus) at TPOT = ms_per_step; prefill tok/s beside it",
@@ -206,7 +220,9 @@ def main():
             "e2e": {"value": round(tokens_per_step / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 3),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches * args.steps), "launches_per_step": int(launches),
-            "clocks": _summarise_clocks(samples), "build_s": round(build_s, 1), "impl": "ours",
+            "clocks": _summarise_clocks(samples), "build_s": round(build_s, 1), "impl": "ours", "graph_equals_eager": graph_ok,
+            "mtp": None if not args.mtp else {"draft_tokens": args.mtp, "forced_accept": args.force_accept, "tokens_per_seq_per_step": per_step,
+                                             "accepted_per_verify": round(runner.mtp_runner.accepted_total / max(1, runner.mtp_runner.verify_steps), 3)},
         }
         print(json.dumps(out))
     if N > 1:

@@ -338,6 +338,113 @@ __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_
   *reinterpret_cast<uint4*>(y + i) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+
+// GQA front end in one pass over the qkv projection output: per-head RMSNorm of q and k (optional), rotary embedding of both
+// (pairs (i, i + D/2), the whole head rotated) and the store of k and v into their paged cache rows.  One warp per (token, head);
+// a lane owns the bf16 pairs at columns 2*lane + 64*j, so with D = 128 or 256 both halves of every rotation pair sit in the
+// same lane.  qkv [T, (Hq + 2*Hkv) * D] with row stride ld; q_out [T, Hq, D] contiguous; caches [slots, Hkv, D].
+// Replaces four launches (q norm, k norm, two rope passes) and an indexed copy.  Reference: triton/generic/kv_store.py:7,31,
+// kernel/jit/sgl/csrc/deepseek_v4/fused_norm_rope.cuh:42, models/qwen3_moe/qwen3_moe.py:58-146.
+template <int D>
+__global__ void __launch_bounds__(256) gqa_qkv_prepare_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, int Hq, int Hkv,
+                                                             const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw, float eps,
+                                                             float w_offset, const long long* __restrict__ positions,
+                                                             const float* __restrict__ rope_cache, __nv_bfloat16* __restrict__ q_out,
+                                                             __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                                             const long long* __restrict__ slots, int T) {
+  pdl_wait(); pdl_trigger();
+  constexpr int J = D / 64;                       // bf16 pairs per lane
+  const int heads = Hq + 2 * Hkv;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)T * heads) return;
+  const int t = (int)(w / heads), h = (int)(w - (long long)t * heads), lane = threadIdx.x & 31;
+  const __nv_bfloat16* src = qkv + (long long)t * ld + (long long)h * D;
+  float2 v[J];
+#pragma unroll
+  for (int j = 0; j < J; j++) v[j] = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(src + 2 * lane + 64 * j));
+  const bool is_q = h < Hq, is_k = !is_q && h < Hq + Hkv;
+  const long long slot = is_q ? 0 : slots[t];
+  if (!is_q && slot < 0) return;                  // padded token: nothing to store
+  if (is_q || is_k) {
+    const __nv_bfloat16* nw = is_q ? qw : kw;
+    if (nw) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < J; j++) ss += v[j].x * v[j].x + v[j].y * v[j].y;
+      const float r = rsqrtf(warp_sum(ss) / D + eps);
+#pragma unroll
+      for (int j = 0; j < J; j++) {
+        const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(nw + 2 * lane + 64 * j));
+        // the separate norm kernel rounds to bf16 before the rotation reads it: keep that rounding
+        v[j] = unpack_bf16x2(pack_bf16x2(v[j].x * r * (g.x + w_offset), v[j].y * r * (g.y + w_offset)));
+      }
+    }
+    const float* cs = rope_cache + positions[t] * D;      // [cos (D/2) | sin (D/2)]
+#pragma unroll
+    for (int j = 0; j < J / 2; j++) {
+      const int i = 2 * lane + 64 * j;                    // column of the first element of the pair's low half
+      const float2 c = *reinterpret_cast<const float2*>(cs + i), sn = *reinterpret_cast<const float2*>(cs + D / 2 + i);
+      const float2 a = v[j], b = v[j + J / 2];
+      v[j] = make_float2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+      v[j + J / 2] = make_float2(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
+    }
+  }
+  __nv_bfloat16* dst = is_q ? q_out + ((long long)t * Hq + h) * D
+                            : (is_k ? k_cache + (slot * Hkv + (h - Hq)) * D : v_cache + (slot * Hkv + (h - Hq - Hkv)) * D);
+#pragma unroll
+  for (int j = 0; j < J; j++) *reinterpret_cast<uint32_t*>(dst + 2 * lane + 64 * j) = pack_bf16x2(v[j].x, v[j].y);
+}
+
+// Stand-alone paged store of K and V rows ([T, Hkv, D] each, any row stride) for shapes the fused front end does not take.
+__global__ void __launch_bounds__(256) gqa_kv_store_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, long long k_ld,
+                                                          long long v_ld, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                                          const long long* __restrict__ slots, int T, int row_elems) {
+  pdl_wait(); pdl_trigger();
+  const int t = blockIdx.x;
+  const long long slot = slots[t];
+  if (slot < 0) return;
+  for (int c = threadIdx.x * 8; c < row_elems; c += blockDim.x * 8) {
+    *reinterpret_cast<uint4*>(k_cache + slot * row_elems + c) = *reinterpret_cast<const uint4*>(k + (long long)t * k_ld + c);
+    *reinterpret_cast<uint4*>(v_cache + slot * row_elems + c) = *reinterpret_cast<const uint4*>(v + (long long)t * v_ld + c);
+  }
+}
+
+// LayerNorm over the last dimension, one warp per row: y = (x - mean) / sqrt(var + eps) * w + b.
+__global__ void __launch_bounds__(256) layernorm_kernel(const __nv_bfloat16* __restrict__ x, long long ld, const __nv_bfloat16* __restrict__ w,
+                                                       const __nv_bfloat16* __restrict__ b, float eps, __nv_bfloat16* __restrict__ y, long long rows, int D) {
+  pdl_wait(); pdl_trigger();
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* xr = x + r * ld;
+  float s = 0.f, ss = 0.f;
+  for (int c = lane; c < D; c += 32) { const float f = __bfloat162float(xr[c]); s += f; ss += f * f; }
+  s = warp_sum(s); ss = warp_sum(ss);
+  const float mean = s / D, rstd = rsqrtf(fmaxf(ss / D - mean * mean, 0.f) + eps);
+  for (int c = lane; c < D; c += 32) {
+    const float f = (__bfloat162float(xr[c]) - mean) * rstd;
+    y[r * D + c] = __float2bfloat16(f * (w ? __bfloat162float(w[c]) : 1.f) + (b ? __bfloat162float(b[c]) : 0.f));
+  }
+}
+
+// Merge of two attention partials by their log-sum-exp: o = (e^{l1} o1 + e^{l2} o2) / (e^{l1} + e^{l2}), lse = log(e^{l1} + e^{l2}).
+// o1, o2, out [rows, D] bf16 (rows = tokens x heads); lse1, lse2, lse_out [rows] fp32 (natural log; -inf = empty partial).
+__global__ void __launch_bounds__(128) merge_states_kernel(const __nv_bfloat16* __restrict__ o1, const float* __restrict__ l1,
+                                                          const __nv_bfloat16* __restrict__ o2, const float* __restrict__ l2,
+                                                          __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out, int D) {
+  pdl_wait(); pdl_trigger();
+  const long long r = blockIdx.x;
+  const float a = l1[r], b = l2[r], m = fmaxf(a, b);
+  const float ea = (a == -INFINITY) ? 0.f : __expf(a - m), eb = (b == -INFINITY) ? 0.f : __expf(b - m);
+  const float den = ea + eb, wa = den > 0.f ? ea / den : 0.f, wb = den > 0.f ? eb / den : 0.f;
+  for (int c = threadIdx.x * 2; c < D; c += blockDim.x * 2) {
+    const float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o1 + r * D + c));
+    const float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o2 + r * D + c));
+    *reinterpret_cast<uint32_t*>(out + r * D + c) = pack_bf16x2(wa * x.x + wb * y.x, wa * x.y + wb * y.y);
+  }
+  if (threadIdx.x == 0) lse_out[r] = den > 0.f ? m + __logf(den) : -INFINITY;
+}
+
 }  // namespace ne
 
 using namespace ne;
@@ -410,4 +517,43 @@ extern "C" int ne_add(const void* a, const void* b, void* y, long long n, cudaSt
   if (n <= 0) return 0;
   if (n % 8) return 1001;
   return (int)launch_pdl(add_kernel, dim3((int)((n / 8 + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n);
+}
+
+
+extern "C" int ne_gqa_qkv_prepare(const void* qkv, long long ld, int Hq, int Hkv, int D, const void* qw, const void* kw, float eps, float w_offset,
+                                  const long long* positions, const float* rope_cache, void* q_out, void* k_cache, void* v_cache,
+                                  const long long* slots, int T, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if ((D != 128 && D != 256) || ld % 2) return 1001;
+  const long long warps = (long long)T * (Hq + 2 * Hkv);
+  const dim3 grid((unsigned)((warps + 7) / 8));
+  if (D == 128)
+    return (int)launch_pdl(gqa_qkv_prepare_kernel<128>, grid, dim3(256), 0, st, (const __nv_bfloat16*)qkv, ld, Hq, Hkv, (const __nv_bfloat16*)qw,
+                           (const __nv_bfloat16*)kw, eps, w_offset, positions, rope_cache, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+                           (__nv_bfloat16*)v_cache, slots, T);
+  return (int)launch_pdl(gqa_qkv_prepare_kernel<256>, grid, dim3(256), 0, st, (const __nv_bfloat16*)qkv, ld, Hq, Hkv, (const __nv_bfloat16*)qw,
+                         (const __nv_bfloat16*)kw, eps, w_offset, positions, rope_cache, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+                         (__nv_bfloat16*)v_cache, slots, T);
+}
+
+extern "C" int ne_gqa_kv_store(const void* k, const void* v, long long k_ld, long long v_ld, void* k_cache, void* v_cache, const long long* slots,
+                               int T, int row_elems, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (row_elems % 8 || k_ld % 8 || v_ld % 8) return 1001;
+  return (int)launch_pdl(gqa_kv_store_kernel, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, k_ld, v_ld,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slots, T, row_elems);
+}
+
+extern "C" int ne_layernorm(const void* x, long long ld, const void* w, const void* b, float eps, void* y, long long rows, int D, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  return (int)launch_pdl(layernorm_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, st, (const __nv_bfloat16*)x, ld, (const __nv_bfloat16*)w,
+                         (const __nv_bfloat16*)b, eps, (__nv_bfloat16*)y, rows, D);
+}
+
+extern "C" int ne_merge_states(const void* o1, const float* l1, const void* o2, const float* l2, void* out, float* lse_out, long long rows, int D,
+                               cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (D % 2) return 1001;
+  return (int)launch_pdl(merge_states_kernel, dim3((unsigned)rows), dim3(128), 0, st, (const __nv_bfloat16*)o1, l1, (const __nv_bfloat16*)o2, l2,
+                         (__nv_bfloat16*)out, lse_out, D);
 }

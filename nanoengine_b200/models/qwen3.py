@@ -49,15 +49,11 @@ class Qwen3Attention(nn.Module):
     def forward(self, x_slice, positions, ctx: ForwardContext, rope_cache, total_rows: int):
         qkv = tp_all_gather_linear(x_slice, total_rows, self.qkv_proj) if self.tp > 1 else self.qkv_proj(x_slice)
         T = qkv.shape[0]
-        q, k, v = qkv.split([self.hq * self.hd, self.hkv * self.hd, self.hkv * self.hd], -1)
-        q, k, v = q.reshape(T, self.hq, self.hd), k.reshape(T, self.hkv, self.hd), v.reshape(T, self.hkv, self.hd)
-        if self.q_norm is not None:
-            q = self.q_norm(q.reshape(-1, self.hd)).view(T, self.hq, self.hd)
-            k = self.k_norm(k.reshape(-1, self.hd)).view(T, self.hkv, self.hd)
-        q = ops.apply_rope(q.contiguous(), positions, rope_cache, False)
-        k = ops.apply_rope(k.contiguous(), positions, rope_cache, False)
         kc, vc = ctx.kv_caches[self.layer_idx]
-        ops.gqa_kv_store(kc, vc, ctx.slot_mapping, k, v)
+        # head split, q / k RMSNorm, rotary embedding and the paged K / V store in one pass over the projection output
+        q = ops.gqa_qkv_prepare(qkv, self.hq, self.hkv, self.hd, self.q_norm.weight if self.q_norm is not None else None,
+                                self.k_norm.weight if self.k_norm is not None else None, self.cfg.rms_norm_eps, False, positions, rope_cache,
+                                kc, vc, ctx.slot_mapping)
         o = ops.gqa_attention_paged(q, kc, vc, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale)
         o = o.reshape(T, self.hq * self.hd)
         return tp_linear_reduce_scatter(o, self.o_proj) if self.tp > 1 else self.o_proj(o)

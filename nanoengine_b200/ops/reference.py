@@ -162,6 +162,25 @@ def gqa_kv_store(k_cache, v_cache, slot_mapping, k, v) -> None:
     v_cache.view(-1, *v_cache.shape[2:])[slot_mapping.long()] = v.to(v_cache.dtype)
 
 
+def gqa_qkv_prepare(qkv: torch.Tensor, hq: int, hkv: int, hd: int, q_norm_w, k_norm_w, eps: float, unit_offset: bool, positions,
+                    rope_cache: torch.Tensor, k_cache, v_cache, slot_mapping) -> torch.Tensor:
+    """The GQA front end after the qkv projection: split [T, (hq + 2 hkv) * hd] into heads, per-head RMSNorm of q and k (when
+    the weights are given), rotary embedding of both over the whole head (pairs (i, i + hd/2)), K and V rows stored into their
+    paged cache slots.  Returns q [T, hq, hd] (reference models/qwen3_moe/qwen3_moe.py:58-146, triton/generic/kv_store.py:7)."""
+    T = qkv.shape[0]
+    q, k, v = qkv.split([hq * hd, hkv * hd, hkv * hd], -1)
+    q, k, v = q.reshape(T, hq, hd), k.reshape(T, hkv, hd), v.reshape(T, hkv, hd)
+    if q_norm_w is not None:
+        q = rmsnorm(q.reshape(-1, hd), q_norm_w, eps, False, unit_offset).view(T, hq, hd)
+    if k_norm_w is not None:
+        k = rmsnorm(k.reshape(-1, hd), k_norm_w, eps, False, unit_offset).view(T, hkv, hd)
+    q = apply_rope(q.contiguous(), positions, rope_cache, False)
+    k = apply_rope(k.contiguous(), positions, rope_cache, False)
+    keep = slot_mapping >= 0
+    gqa_kv_store(k_cache, v_cache, slot_mapping[keep], k[keep], v[keep])
+    return q
+
+
 def _gather_rows(cache: torch.Tensor, block_table: torch.Tensor, n: int) -> torch.Tensor:
     bs = cache.shape[1]
     nb = (n + bs - 1) // bs

@@ -246,7 +246,18 @@ def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tens
 
 
 def layernorm(x, w, b, eps):
-    return ref.layernorm(x, w, b, eps)
+    """One warp per row of the last dimension."""
+    shape = x.shape
+    D = shape[-1]
+    x2 = x.reshape(-1, D)
+    if x2.dtype != torch.bfloat16 or x2.stride(-1) != 1:
+        x2 = x2.to(torch.bfloat16).contiguous()
+    y = torch.empty(x2.shape[0], D, dtype=torch.bfloat16, device=x.device)
+    wb = None if w is None else w.to(torch.bfloat16).contiguous()
+    bb = None if b is None else b.to(torch.bfloat16).contiguous()
+    _ck(lib().ne_layernorm(_p(x2), _c.c_longlong(x2.stride(0)), _p(wb), _p(bb), _c.c_float(eps), _p(y), _c.c_longlong(x2.shape[0]), _c.c_int(D), _st()),
+        "ne_layernorm")
+    return y.view(shape).to(x.dtype)
 
 
 def silu_and_mul(x: torch.Tensor, quant: bool = False):
@@ -335,7 +346,51 @@ def mla_kv_store(cache: torch.Tensor, slot_mapping: torch.Tensor, ckv: torch.Ten
 
 
 def gqa_kv_store(k_cache, v_cache, slot_mapping, k, v):
-    return ref.gqa_kv_store(k_cache, v_cache, slot_mapping, k, v)
+    """k, v [T, Hkv, D] (row stride free) -> rows `slot_mapping` of the paged caches [blocks, block_size, Hkv, D]."""
+    T = k.shape[0]
+    row = k.shape[1] * k.shape[2]
+    ok = (k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+          and k_cache.is_contiguous() and v_cache.is_contiguous() and row % 8 == 0)
+    if not ok:
+        raise ValueError("gqa_kv_store: the CUDA path stores bf16 rows of a multiple of 8 elements into contiguous bf16 caches")
+    k2, v2 = k.reshape(T, row), v.reshape(T, row)
+    if k2.stride(1) != 1 or k2.stride(0) % 8 or k2.data_ptr() % 16:
+        k2 = k2.contiguous()
+    if v2.stride(1) != 1 or v2.stride(0) % 8 or v2.data_ptr() % 16:
+        v2 = v2.contiguous()
+    _ck(lib().ne_gqa_kv_store(_p(k2), _p(v2), _c.c_longlong(k2.stride(0)), _c.c_longlong(v2.stride(0)), _p(k_cache), _p(v_cache),
+                              _p(_i64c(slot_mapping)), _c.c_int(T), _c.c_int(row), _st()), "ne_gqa_kv_store")
+
+
+def _i64c(t):
+    return t if (t.dtype == torch.int64 and t.is_contiguous()) else t.long().contiguous()
+
+
+def gqa_qkv_prepare(qkv, hq, hkv, hd, q_norm_w, k_norm_w, eps, unit_offset, positions, rope_cache, k_cache, v_cache, slot_mapping):
+    """One kernel for head split, q / k RMSNorm, rotary embedding and the paged K / V store (head dim 128 or 256 with the whole
+    head rotated, bf16 caches); other shapes run the same steps as separate kernels."""
+    T = qkv.shape[0]
+    fused = (hd in (128, 256) and rope_cache.shape[1] == hd and qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.stride(0) % 2 == 0
+             and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+             and rope_cache.dtype == torch.float32 and rope_cache.is_contiguous())
+    if not fused:
+        q, k, v = qkv.split([hq * hd, hkv * hd, hkv * hd], -1)
+        q, k, v = q.reshape(T, hq, hd), k.reshape(T, hkv, hd), v.reshape(T, hkv, hd)
+        if q_norm_w is not None:
+            q = rmsnorm(q.reshape(-1, hd), q_norm_w, eps, False, unit_offset).view(T, hq, hd)
+        if k_norm_w is not None:
+            k = rmsnorm(k.reshape(-1, hd), k_norm_w, eps, False, unit_offset).view(T, hkv, hd)
+        q = apply_rope(q.contiguous(), positions, rope_cache, False)
+        k = apply_rope(k.contiguous(), positions, rope_cache, False)
+        gqa_kv_store(k_cache, v_cache, slot_mapping, k, v.contiguous())
+        return q
+    q = torch.empty(T, hq, hd, dtype=torch.bfloat16, device=qkv.device)
+    qw = None if q_norm_w is None else q_norm_w.to(torch.bfloat16).contiguous()
+    kw = None if k_norm_w is None else k_norm_w.to(torch.bfloat16).contiguous()
+    _ck(lib().ne_gqa_qkv_prepare(_p(qkv), _c.c_longlong(qkv.stride(0)), _c.c_int(hq), _c.c_int(hkv), _c.c_int(hd), _p(qw), _p(kw), _c.c_float(eps),
+                                 _c.c_float(1.0 if unit_offset else 0.0), _p(_i64c(positions)), _p(rope_cache), _p(q), _p(k_cache), _p(v_cache),
+                                 _p(_i64c(slot_mapping)), _c.c_int(T), _st()), "ne_gqa_qkv_prepare")
+    return q
 
 
 # ---- MoE -----------------------------------------------------------------------------------------
@@ -430,7 +485,15 @@ def quant_fp8_block(w, block=128):
 
 
 def merge_attention_states(o1, lse1, o2, lse2):
-    return ref.merge_attention_states(o1, lse1, o2, lse2)
+    """o1, o2 [..., D] bf16 partial attention outputs with their log-sum-exp values [...]; one CTA per row."""
+    D = o1.shape[-1]
+    a = o1.reshape(-1, D).to(torch.bfloat16).contiguous()
+    b = o2.reshape(-1, D).to(torch.bfloat16).contiguous()
+    l1, l2 = lse1.reshape(-1).float().contiguous(), lse2.reshape(-1).float().contiguous()
+    out = torch.empty_like(a)
+    lse = torch.empty_like(l1)
+    _ck(lib().ne_merge_states(_p(a), _p(l1), _p(b), _p(l2), _p(out), _p(lse), _c.c_longlong(a.shape[0]), _c.c_int(D), _st()), "ne_merge_states")
+    return out.view(o1.shape).to(o1.dtype), lse.view(lse1.shape)
 
 
 # ---- DSA lightning indexer --------------------------------------------------------------------------

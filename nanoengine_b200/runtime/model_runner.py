@@ -504,6 +504,19 @@ class ModelRunner:
         return step
 
     @torch.inference_mode()
+    def graph_step_equals_eager(self) -> bool:
+        """The most recent decode step once through the captured graph and once eagerly: the sampled tokens must be the same
+        (same kernels on the same inputs; a difference means the replay reads something stale)."""
+        if self._last_decode is None:
+            raise RuntimeError("run a decode step first")
+        ctx, temps = self._last_decode
+        ids, pos = ctx.extras["input_ids"], ctx.extras["positions"]
+        rows = ctx.last_token_indices.long()
+        a = self.sampler(self.model.compute_logits(self.forward(ctx)[rows]), torch.zeros_like(temps), False)[0]
+        b = self.sampler(self.model.compute_logits(self.model(ids, pos, ctx)[rows]), torch.zeros_like(temps), False)[0]
+        return bool(torch.equal(a, b))
+
+    @torch.inference_mode()
     def count_step_launches(self) -> int:
         """Kernels of this library launched by one decode step, counted on an eager (non-graph) run of the last step."""
         from ..ops import sm100

@@ -195,6 +195,7 @@ class MTPRunner:
         dev_i = r._to_dev(h2d)
         temps = r._to_dev(np.asarray(list(b.temperatures), dtype=np.float32))
         last, slots, base_len = dev_i[0], dev_i[1], dev_i[2].to(torch.int32)
+        self._last = (ctx, B, last, slots, temps, base_len)
         if self.graphs is not None and not want_lp and self.graphs.can_run(ctx):
             bundle, acc = self.graphs.run(ctx, last, slots, temps, base_len)
             lp = None
@@ -215,6 +216,33 @@ class MTPRunner:
         if lpl is not None:
             lps = [[0.0] * a + [lpl[i]] for i, a in enumerate(acc_l)]
         return C.RunnerOut(list(b.seq_ids), out_tokens, lps)
+
+
+    # ---- benchmark helpers ------------------------------------------------------------------------
+    @torch.inference_mode()
+    def make_resident_step(self):
+        """A closure that repeats the most recent verify step on inputs already on the device (the same rows are verified and
+        their KV rewritten every time, which costs what a fresh step costs)."""
+        if getattr(self, "_last", None) is None:
+            raise RuntimeError("run a verify step first")
+        ctx, B, last, slots, temps, base_len = self._last
+
+        @torch.inference_mode()
+        def step():
+            if self.graphs is not None and self.graphs.can_run(ctx):
+                return self.graphs.run(ctx, last, slots, temps, base_len)[0]
+            return self.device_step(ctx, B, last, slots, temps, base_len)[0]
+
+        return step
+
+    @torch.inference_mode()
+    def count_step_launches(self) -> int:
+        from ..ops import sm100
+        ctx, B, last, slots, temps, base_len = self._last
+        before = sm100.LAUNCHES[0]
+        self.device_step(ctx, B, last, slots, temps, base_len)
+        torch.cuda.synchronize()
+        return sm100.LAUNCHES[0] - before
 
 
 class MTPGraphRunner:

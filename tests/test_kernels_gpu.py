@@ -399,3 +399,43 @@ def test_indexer_select_matches_reference_topk_sets(k, ctxs, q_lens):
         a, b = set(got[t].tolist()) - {-1}, set(want[t].tolist()) - {-1}
         assert len(a) == len(b)
         assert len(a & b) >= len(b) - 4, (t, len(a & b), len(b))
+
+
+@pytest.mark.parametrize("hd,hq,hkv,norm", [(128, 8, 2, True), (128, 16, 1, False), (256, 4, 4, True), (64, 4, 2, True)])
+def test_gqa_front_end_norm_rope_and_paged_store(k, hd, hq, hkv, norm):
+    """Head split + q/k RMSNorm + rotary + K/V store: one kernel for head dims 128/256, the separate kernels otherwise."""
+    torch.manual_seed(21)
+    T, nb, bs = 37, 5, 64
+    qkv = torch.randn(T, (hq + 2 * hkv) * hd, device="cuda", dtype=torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(hd, device="cuda")).to(torch.bfloat16) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd, device="cuda")).to(torch.bfloat16) if norm else None
+    rope = ref.rope_cos_sin_cache(hd, 512, 1e6).cuda()
+    pos = torch.randint(0, 512, (T,), device="cuda")
+    slots = torch.randperm(nb * bs, device="cuda")[:T].long()
+    slots[5] = -1                                                     # a padded token stores nothing
+    caches = [torch.full((nb, bs, hkv, hd), 7.0, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+    q = k.gqa_qkv_prepare(qkv, hq, hkv, hd, qw, kw, 1e-6, False, pos, rope, caches[0], caches[1], slots)
+    qr = ref.gqa_qkv_prepare(qkv, hq, hkv, hd, qw, kw, 1e-6, False, pos, rope, caches[2], caches[3], slots)
+    assert _rel(q, qr) < 1e-2
+    for a, b in zip(caches[:2], caches[2:]):
+        assert _rel(a, b) < 1e-2
+        untouched = torch.ones(nb * bs, dtype=torch.bool, device="cuda")
+        untouched[slots[slots >= 0]] = False
+        assert bool((a.view(nb * bs, -1)[untouched] == 7.0).all())
+
+
+def test_layernorm_and_merge_of_attention_partials(k):
+    torch.manual_seed(22)
+    x = torch.randn(50, 3, 128, device="cuda", dtype=torch.bfloat16) * 3 + 1
+    w = torch.randn(128, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(128, device="cuda", dtype=torch.bfloat16)
+    assert _rel(k.layernorm(x, w, b, 1e-6), ref.layernorm(x, w, b, 1e-6)) < 1e-2
+    assert _rel(k.layernorm(x[:, 1], w, None, 1e-5), ref.layernorm(x[:, 1], w, None, 1e-5)) < 1e-2
+    o1 = torch.randn(40, 16, 128, device="cuda", dtype=torch.bfloat16)
+    o2 = torch.randn(40, 16, 128, device="cuda", dtype=torch.bfloat16)
+    l1, l2 = torch.randn(40, 16, device="cuda") * 3, torch.randn(40, 16, device="cuda") * 3
+    l2[3, 2] = float("-inf")                                          # an empty partial contributes nothing
+    o, l = k.merge_attention_states(o1, l1, o2, l2)
+    orf, lrf = ref.merge_attention_states(o1, l1, o2, l2)
+    assert _rel(o, orf) < 1e-2 and torch.allclose(l, lrf, atol=1e-4)
+    assert torch.equal(o[3, 2], o1[3, 2])
