@@ -61,6 +61,8 @@ class Config:
     peer_timeout_s: float = 120.0            # SPMD: how long the per-step host rendezvous waits for a silent peer
     kernel_status_every: int = 1             # worker: read the kernels' status words every this many steps (0 = never)
     dummy_eplb: bool = False                 # routers deal expert ids evenly over the EP ranks (capacity runs with random-init routers)
+    eplb_redundant_experts: int = 0          # extra physical expert slots (whole model); hot experts get replicas in them
+    eplb_load_path: Optional[str] = None     # torch file with the expert load [layers, experts] the plan balances (default: uniform)
     # observability
     log_level: str = "INFO"
     step_timing: bool = False
@@ -133,6 +135,11 @@ class Config:
             raise ValueError("enable_hisparse: the hot/cold sparse-KV tier is not available in this build")
         if self.dummy_prefill and not self.enable_hisparse:
             raise ValueError("dummy_prefill only applies to a HiSparse decode engine (enable_hisparse=True)")
+        if self.eplb_redundant_experts:
+            if not mc.n_routed_experts or mc.is_hybrid_gdn:
+                raise ValueError("eplb_redundant_experts needs a DeepSeek or Qwen3 MoE model")
+            if self.eplb_redundant_experts < 0 or (mc.n_routed_experts + self.eplb_redundant_experts) % self.ffn_ep:
+                raise ValueError("experts + eplb_redundant_experts must divide evenly over ffn_ep")
         if self.ffn_tp != 1 or self.ffn_dp != 1:
             raise ValueError("ffn_tp / ffn_dp > 1 are not supported: experts are sharded by ffn_ep only")
         if self.max_model_len is None:

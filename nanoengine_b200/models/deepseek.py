@@ -119,9 +119,9 @@ def _side_stream(device):
 
 
 class MoEGate(nn.Module):
-    def __init__(self, cfg: ModelConfig, device):
+    def __init__(self, cfg: ModelConfig, device, layer_idx: Optional[int] = None):
         super().__init__()
-        self.cfg = cfg
+        self.cfg, self.layer_idx = cfg, layer_idx
         self.weight = nn.Parameter(torch.empty(cfg.n_routed_experts, cfg.hidden_size, dtype=torch.float32, device=device), requires_grad=False)
         self.e_score_correction_bias = None
         if cfg.topk_method == "noaux_tc" and cfg.scoring_func == "sigmoid":
@@ -132,15 +132,15 @@ class MoEGate(nn.Module):
         from ..parallel.ep import routing_options
         logits = ops.router_logits(x, self.weight)
         return ops.moe_route(logits, self.e_score_correction_bias, c.num_experts_per_tok, c.n_group, c.topk_group,
-                             c.norm_topk_prob, c.routed_scaling_factor, c.scoring_func, **routing_options())
+                             c.norm_topk_prob, c.routed_scaling_factor, c.scoring_func, **routing_options(self.layer_idx, x.device))
 
 
 class DeepseekMoE(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    def __init__(self, cfg: ModelConfig, dtype, device, layer_idx: Optional[int] = None):
         super().__init__()
         self.cfg = cfg
-        self.gate = MoEGate(cfg, device)
-        self.experts = RoutedExperts(cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, dtype, device, cfg.quant)
+        self.gate = MoEGate(cfg, device, layer_idx)
+        self.experts = RoutedExperts(cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, dtype, device, cfg.quant, layer_idx)
         self.shared_experts = None
         if cfg.n_shared_experts > 0:
             self.shared_experts = SwiGLUMLP(cfg.hidden_size, cfg.moe_intermediate_size * cfg.n_shared_experts, dtype, device, cfg.quant)
@@ -183,7 +183,7 @@ class DeepseekDecoderLayer(nn.Module):
         self.self_attn = MLAAttention(cfg, layer_idx, dtype, device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         self.is_moe = cfg.is_moe_layer(layer_idx) and not force_dense
-        self.mlp = DeepseekMoE(cfg, dtype, device) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
+        self.mlp = DeepseekMoE(cfg, dtype, device, layer_idx) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
 
     def forward(self, h, residual, positions, ctx, rope_cache):
         x, residual = self.input_layernorm(h, residual) if residual is not None else (self.input_layernorm(h), h)

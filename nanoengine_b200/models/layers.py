@@ -97,9 +97,18 @@ class SwiGLUMLP(nn.Module):
 class RoutedExperts(nn.Module):
     """The experts this rank owns: ids [ep_rank*E_local, (ep_rank+1)*E_local), stacked for grouped GEMMs."""
 
-    def __init__(self, num_experts: int, hidden: int, inter: int, dtype, device, quant=None):
+    def __init__(self, num_experts: int, hidden: int, inter: int, dtype, device, quant=None, layer_idx: Optional[int] = None):
         super().__init__()
         d = get_dist_context()
+        # under an expert-load-balancing plan the stacked tensors hold PHYSICAL slots (a hot expert may fill several, on
+        # different ranks); `phy2log` names the logical expert behind each slot of this layer
+        from ..parallel.eplb import active_plan
+        plan = active_plan() if layer_idx is not None else None
+        self.phy2log = None
+        if plan is not None:
+            assert plan.num_logical == num_experts, "the EPLB plan was made for another expert count"
+            self.phy2log = plan.phy2log[layer_idx].tolist()
+            num_experts = plan.num_physical
         assert num_experts % d.ep_size == 0, "experts must divide evenly over the EP group"
         self.num_experts, self.hidden, self.inter, self.quant = num_experts, hidden, inter, quant
         self.num_local = num_experts // d.ep_size
@@ -115,7 +124,22 @@ class RoutedExperts(nn.Module):
             self.gate_up_scale = self.down_scale = None
 
     def owns(self, expert_id: int) -> bool:
-        return self.expert_offset <= expert_id < self.expert_offset + self.num_local
+        return bool(self.local_slots_of(expert_id))
+
+    def local_slots_of(self, logical_id: int):
+        """Local slot indices that hold logical expert `logical_id` on this rank (one without a plan, any number with one)."""
+        lo, hi = self.expert_offset, self.expert_offset + self.num_local
+        if self.phy2log is None:
+            return [logical_id - lo] if lo <= logical_id < hi else []
+        return [p - lo for p in range(lo, hi) if self.phy2log[p] == logical_id]
+
+    @torch.no_grad()
+    def load_expert(self, logical_id: int, which: str, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None) -> bool:
+        """Store one logical expert's matrix into every local slot that holds it; False when this rank holds none."""
+        slots = self.local_slots_of(logical_id)
+        for s in slots:
+            self.set_expert(s, which, w, scale_inv)
+        return bool(slots)
 
     def forward(self, x, topk_idx, topk_w, add_in=None):
         """Local part of the routed output for the tokens given (weights applied, zero rows where no expert is local);

@@ -60,17 +60,17 @@ class Qwen3Attention(nn.Module):
 
 
 class Qwen3MoE(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    def __init__(self, cfg: ModelConfig, dtype, device, layer_idx: Optional[int] = None):
         super().__init__()
-        self.cfg = cfg
+        self.cfg, self.layer_idx = cfg, layer_idx
         self.gate_weight = nn.Parameter(torch.empty(cfg.n_routed_experts, cfg.hidden_size, dtype=torch.float32, device=device), requires_grad=False)
-        self.experts = RoutedExperts(cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, dtype, device, cfg.quant)
+        self.experts = RoutedExperts(cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, dtype, device, cfg.quant, layer_idx)
 
     def forward(self, x, ctx):
         c = self.cfg
         logits = ops.router_logits(x, self.gate_weight)
         from ..parallel.ep import routing_options
-        idx, w = ops.moe_route(logits, None, c.num_experts_per_tok, 1, 1, c.norm_topk_prob, 1.0, "softmax", **routing_options())
+        idx, w = ops.moe_route(logits, None, c.num_experts_per_tok, 1, 1, c.norm_topk_prob, 1.0, "softmax", **routing_options(self.layer_idx, x.device))
         return ep_moe_forward(self.experts, x, idx, w, ctx)
 
 
@@ -81,7 +81,7 @@ class Qwen3DecoderLayer(nn.Module):
         self.self_attn = Qwen3Attention(cfg, layer_idx, dtype, device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         self.is_moe = cfg.is_moe_layer(layer_idx)
-        self.mlp = Qwen3MoE(cfg, dtype, device) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
+        self.mlp = Qwen3MoE(cfg, dtype, device, layer_idx) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
 
     def forward(self, h, residual, positions, ctx, rope_cache, total_rows):
         x, residual = self.input_layernorm(h, residual) if residual is not None else (self.input_layernorm(h), h)
@@ -185,9 +185,7 @@ class Qwen3MoeForCausalLM(nn.Module):
             if e:
                 eid, which = int(e.group(1)), e.group(2)[:-5]
                 ex = L.mlp.experts
-                if ex.owns(eid):
-                    ex.set_expert(eid - ex.expert_offset, which, w, s)
-                else:
+                if not ex.load_expert(eid, which, w, s):
                     n -= 1
                 return
             if rest in ("mlp.gate_proj", "mlp.up_proj"):

@@ -279,9 +279,7 @@ class Qwen35ForCausalLM(nn.Module):
             if e:
                 eid, which = int(e.group(1)), e.group(2)[:-5]
                 ex = L.mlp.experts
-                if ex.owns(eid):
-                    ex.set_expert(eid - ex.expert_offset, which, w, s)
-                else:
+                if not ex.load_expert(eid, which, w, s):
                     n -= 1
                 return
             sm = re.match(r"mlp\.(shared_expert\.)?(gate_proj|up_proj|down_proj)$", rest)

@@ -27,6 +27,9 @@ _LAYER_RE = re.compile(r"^model\.layers\.(\d+)\.")
 def expert_owner_filter(cfg: ModelConfig, ep_size: int, ep_rank: int, layer_range=None) -> Callable[[str], bool]:
     """True for tensors this rank must read: its own experts and (with PP) its own layers."""
     per = max(1, cfg.n_routed_experts // max(1, ep_size)) if cfg.n_routed_experts else 1
+    from ..parallel.eplb import active_plan
+    plan = active_plan()
+    per_phys = plan.num_physical // max(1, ep_size) if plan is not None else 0
 
     def keep(name: str) -> bool:
         m = _LAYER_RE.match(name)
@@ -36,6 +39,9 @@ def expert_owner_filter(cfg: ModelConfig, ep_size: int, ep_rank: int, layer_rang
                 return False
         e = _EXPERT_RE.search(name)
         if e is not None:
+            if plan is not None and m and int(m.group(1)) < plan.num_layers:
+                # under a load-balancing plan an expert is read by every rank that holds one of its physical replicas
+                return any(p // per_phys == ep_rank for p in plan.slots_of(int(m.group(1)), int(e.group(1))))
             return int(e.group(1)) // per == ep_rank
         return True
 
@@ -286,9 +292,7 @@ def load_deepseek_weights(model, weights: Iterable[Tuple[str, torch.Tensor]], mt
             if e:
                 eid, which = int(e.group(1)), e.group(2)[:-5]
                 ex = M.experts
-                if ex.owns(eid):
-                    ex.set_expert(eid - ex.expert_offset, which, w, s)
-                else:
+                if not ex.load_expert(eid, which, w, s):
                     n -= 1
                 return
             tgt = M.shared_experts if leaf.startswith("shared_experts.") else M

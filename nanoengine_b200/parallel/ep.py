@@ -33,8 +33,16 @@ def set_routing_options(balance_ranks: int = 0) -> None:
     _ROUTING["balance_ranks"] = int(balance_ranks)
 
 
-def routing_options() -> dict:
-    return dict(_ROUTING)
+def routing_options(layer_idx: Optional[int] = None, device=None) -> dict:
+    """Keyword arguments for `ops.moe_route`: the dummy-balance switch, and under an EPLB plan the logical -> physical tables
+    of the layer."""
+    out = dict(_ROUTING)
+    if layer_idx is not None and not out["balance_ranks"]:
+        from .eplb import active_plan
+        plan = active_plan()
+        if plan is not None:
+            out["log2phy"], out["logcnt"] = plan.router_tables(layer_idx, device)
+    return out
 
 
 def set_fused_backend(obj) -> None:

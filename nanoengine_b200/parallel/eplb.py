@@ -111,3 +111,47 @@ def dummy_balanced_topk(num_tokens: int, top_k: int, num_experts: int, device="c
     """Round-robin expert ids (perfectly balanced), for capacity benchmarks with random-init routers."""
     base = torch.arange(num_tokens * top_k, device=device) % num_experts
     return base.view(num_tokens, top_k).to(torch.int32)
+
+
+# ---- the plan a worker serves under ------------------------------------------------------------------------------------
+class EplbPlan:
+    """Physical expert layout of a model: `phy2log [L, P]` (which logical expert every physical slot holds; slots are dealt to
+    the EP ranks in contiguous runs of P / ep), `log2phy [L, E, R]` (-1 padded) and `logcnt [L, E]` for the routers.  Rows are
+    indexed by the model's layer index; dense layers carry an identity row nobody reads."""
+
+    def __init__(self, phy2log: torch.Tensor, log2phy: torch.Tensor, logcnt: torch.Tensor):
+        self.phy2log, self.log2phy, self.logcnt = phy2log.long(), log2phy.long(), logcnt.long()
+        self.num_layers, self.num_physical = self.phy2log.shape
+        self.num_logical = self.logcnt.shape[1]
+        self._dev = {}
+
+    @classmethod
+    def from_load(cls, load: torch.Tensor, num_redundant: int, ep_size: int, num_groups: int = 1) -> "EplbPlan":
+        L, E = load.shape
+        P = E + num_redundant
+        if P % ep_size:
+            raise ValueError(f"{E} experts + {num_redundant} redundant slots do not divide over {ep_size} EP ranks")
+        return cls(*rebalance_experts(load, P, ep_size, num_groups, 1))
+
+    def slots_of(self, layer: int, logical: int):
+        row = self.log2phy[layer, logical]
+        return [int(p) for p in row.tolist() if p >= 0]
+
+    def router_tables(self, layer: int, device):
+        """(log2phy [E, R] int32, logcnt [E] int32) of one layer on `device`, as the routing kernel reads them."""
+        key = (layer, str(device))
+        if key not in self._dev:
+            self._dev[key] = (self.log2phy[layer].to(torch.int32).contiguous().to(device), self.logcnt[layer].to(torch.int32).contiguous().to(device))
+        return self._dev[key]
+
+
+_ACTIVE = None
+
+
+def set_active_plan(plan) -> None:
+    global _ACTIVE
+    _ACTIVE = plan
+
+
+def active_plan():
+    return _ACTIVE

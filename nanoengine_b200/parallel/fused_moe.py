@@ -153,7 +153,9 @@ def install(config, dist_ctx) -> Optional[FusedEP]:
     if not peers_reachable(group):
         return None
     max_tokens = max(config.max_num_batched_tokens, config.max_num_seqs * (1 + config.num_speculative_tokens))
-    be = FusedEP(group, dist_ctx.ep_rank, dist_ctx.ep_size, mc.n_routed_experts, mc.hidden_size, mc.moe_intermediate_size,
+    from .eplb import active_plan
+    plan = active_plan()
+    be = FusedEP(group, dist_ctx.ep_rank, dist_ctx.ep_size, plan.num_physical if plan is not None else mc.n_routed_experts, mc.hidden_size, mc.moe_intermediate_size,
                  mc.num_experts_per_tok, max_tokens, mc.quant == "fp8")
     ep.set_fused_backend(be)
     return be

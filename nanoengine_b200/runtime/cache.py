@@ -126,6 +126,7 @@ class KVCache:
             self.indexer = torch.zeros(plan.num_layers, nb, plan.block_size * (plan.index_dim + 4), dtype=torch.uint8, device=device)
             self.indexer_layers = [self.indexer[l] for l in range(plan.num_layers)]
         self.host_kv = None
+        self.host_families = {}
         self.rec_states = self.conv_states = None
         self.scratch_slot = plan.state_slots
         if plan.gdn:
@@ -164,14 +165,16 @@ class KVCache:
         return out
 
     def allocate_host(self, num_host_blocks: int):
-        """Pinned host tier used by preemption swap."""
+        """Pinned host tier used by preemption swap: one host array per page family (KV and, for DSA models, the indexer keys),
+        so a swapped-in sequence finds every per-page cache it had.  Per-sequence state slots (gated delta-net) are not part
+        of it: a swapped-out sequence keeps its slot on the device."""
+        self.host_families = {}
         if num_host_blocks <= 0:
             return
-        shape = list(self.kv.shape)
-        bdim = 1 if self.plan.mla else 2
-        shape[bdim] = num_host_blocks
-        self.host_kv = torch.zeros(shape, dtype=self.kv.dtype if self.kv.dtype != torch.float8_e4m3fn else torch.uint8,
-                                   pin_memory=self.device.type == "cuda")
+        for f in self.page_families():
+            self.host_families[f["name"]] = torch.zeros(f["planes"], num_host_blocks, f["page_bytes"], dtype=torch.uint8,
+                                                        pin_memory=self.device.type == "cuda")
+        self.host_kv = self.host_families["mla_kv" if self.plan.mla else "gqa_kv"]
 
     def block_views(self, bid: int) -> List[torch.Tensor]:
         """Byte views of everything block `bid` holds (all layers of every cache family), for the file-backed tier."""
@@ -182,27 +185,28 @@ class KVCache:
         return out
 
     def swap(self, src: List[int], dst: List[int], to_host: bool):
-        """Copy whole blocks (all layers) between the device cache and the host tier."""
+        """Copy whole pages (all planes of every page family) between the device caches and the host tier."""
         if not src:
             return
-        bdim = 1 if self.plan.mla else 2
-        dev = self.kv.view(torch.uint8) if self.kv.dtype == torch.float8_e4m3fn else self.kv
-        if self.device.type == "cuda" and self.host_kv.is_pinned():
-            # one kernel copies every (layer, block) pair straight between the pinned host tier and the device cache
-            from ..ops import sm100 as _k
-            import ctypes as _c
-            planes = self.kv.shape[0] if self.plan.mla else self.kv.shape[0] * self.kv.shape[1]
-            blk = dev[0, 0].numel() * dev.element_size() if self.plan.mla else dev[0, 0, 0].numel() * dev.element_size()
-            d_stride, h_stride = blk * dev.shape[bdim], blk * self.host_kv.shape[bdim]
-            si = torch.tensor(src, dtype=torch.int32).to(self.device, non_blocking=True)
-            di = torch.tensor(dst, dtype=torch.int32).to(self.device, non_blocking=True)
-            dst_t, src_t, ds, ss = (self.host_kv, dev, h_stride, d_stride) if to_host else (dev, self.host_kv, d_stride, h_stride)
-            _k._ck(_k.lib().ne_kv_swap(_c.c_void_p(dst_t.data_ptr()), _c.c_void_p(src_t.data_ptr()), _k._p(si), _k._p(di), _c.c_int(len(src)),
-                                       _c.c_int(planes), _c.c_longlong(blk), _c.c_longlong(ds), _c.c_longlong(ss), _k._st()), "ne_kv_swap")
-            return      # stream order is enough: later kernels that reuse the blocks run behind this copy
-        s = torch.as_tensor(src, dtype=torch.long)
-        d = torch.as_tensor(dst, dtype=torch.long)
-        if to_host:
-            self.host_kv.index_copy_(bdim, d, dev.index_select(bdim, s.to(dev.device)).to("cpu"))
-        else:
-            dev.index_copy_(bdim, d.to(dev.device), self.host_kv.index_select(bdim, s).to(dev.device, non_blocking=True))
+        for f in self.page_families():
+            host = self.host_families[f["name"]]
+            t = f["tensor"]
+            dev = (t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).reshape(-1).view(torch.uint8).view(f["planes"], -1, f["page_bytes"])
+            if self.device.type == "cuda" and host.is_pinned():
+                # one kernel copies every (plane, page) pair straight between the pinned host tier and the device cache
+                from ..ops import sm100 as _k
+                import ctypes as _c
+                d_stride, h_stride = f["plane_stride"], host.shape[1] * f["page_bytes"]
+                si = torch.tensor(src, dtype=torch.int32).to(self.device, non_blocking=True)
+                di = torch.tensor(dst, dtype=torch.int32).to(self.device, non_blocking=True)
+                dst_t, src_t, ds, ss = (host, dev, h_stride, d_stride) if to_host else (dev, host, d_stride, h_stride)
+                _k._ck(_k.lib().ne_kv_swap(_c.c_void_p(dst_t.data_ptr()), _c.c_void_p(src_t.data_ptr()), _k._p(si), _k._p(di), _c.c_int(len(src)),
+                                           _c.c_int(f["planes"]), _c.c_longlong(f["page_bytes"]), _c.c_longlong(ds), _c.c_longlong(ss), _k._st()),
+                       "ne_kv_swap")
+                continue        # stream order is enough: later kernels that reuse the pages run behind this copy
+            s_ = torch.as_tensor(src, dtype=torch.long)
+            d_ = torch.as_tensor(dst, dtype=torch.long)
+            if to_host:
+                host.index_copy_(1, d_, dev.index_select(1, s_.to(dev.device)).to("cpu"))
+            else:
+                dev.index_copy_(1, d_.to(dev.device), host.index_select(1, s_).to(dev.device, non_blocking=True))

@@ -102,6 +102,18 @@ class ModelRunner:
         cls = get_model_class(self.mc.architecture)
         from ..parallel.ep import set_routing_options
         set_routing_options(balance_ranks=self.dist.ep_size if self.config.dummy_eplb else 0)
+        from ..parallel import eplb
+        plan = None
+        if self.config.eplb_redundant_experts > 0:
+            rows = self.mc.num_hidden_layers + max(1, self.mc.num_nextn_predict_layers)
+            if self.config.eplb_load_path:
+                load = torch.load(self.config.eplb_load_path, map_location="cpu").float()
+                if load.shape[0] < rows:                       # layers the measurement does not cover (MTP blocks): uniform
+                    load = torch.cat([load, torch.ones(rows - load.shape[0], load.shape[1])], 0)
+            else:
+                load = torch.ones(rows, self.mc.n_routed_experts)
+            plan = eplb.EplbPlan.from_load(load, self.config.eplb_redundant_experts, self.dist.ep_size, 1)
+        eplb.set_active_plan(plan)
         torch.manual_seed(self.config.seed)
         lr = self.layer_range()
         self.model = cls(self.mc, dtype=self.dtype, device=self.device, layer_range=lr if self.config.pp > 1 else None)

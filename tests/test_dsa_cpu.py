@@ -78,3 +78,27 @@ def test_indexer_scoring_formula_and_topk_translation():
     assert phys[1, 0].item() == bt[1, i // 16].item() * 16 + i % 16 and (phys[idx < 0] == -1).all()
     h = ref.hadamard(torch.eye(8))
     assert torch.allclose(h @ h.t(), torch.eye(8), atol=1e-6)           # orthonormal
+
+
+def test_host_swap_moves_indexer_pages_with_the_kv_pages():
+    """A preempted DSA sequence comes back from the host tier with its indexer keys, not only its latent KV rows."""
+    import torch
+    from nanoengine_b200.models.config import tiny_deepseek_v3
+    from nanoengine_b200.runtime.cache import KVCache, make_cache_plan
+    mc = tiny_deepseek_v3(index_topk=8, index_n_heads=4, index_head_dim=128)
+    plan = make_cache_plan(mc, "bfloat16", 16)
+    assert plan.indexer
+    c = KVCache(plan, 10, "cpu")
+    c.allocate_host(4)
+    assert sorted(c.host_families) == ["indexer", "mla_kv"]
+    g = torch.Generator().manual_seed(0)
+    c.kv.copy_(torch.randn(c.kv.shape, generator=g).to(c.kv.dtype))
+    c.indexer.copy_(torch.randint(0, 255, c.indexer.shape, generator=g, dtype=torch.uint8))
+    want = [v.clone() for b in (2, 5) for v in c.block_views(b)]
+    c.swap([2, 5], [1, 3], to_host=True)
+    for b in (2, 5):
+        for v in c.block_views(b):
+            v.zero_()
+    c.swap([1, 3], [7, 8], to_host=False)
+    got = [v for b in (7, 8) for v in c.block_views(b)]
+    assert len(got) == 4 and all(torch.equal(a, b) for a, b in zip(got, want))

@@ -51,12 +51,14 @@ def test_rank_leaving_between_steps_is_detected_before_the_next_launch():
         s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
+    ps = [ctx.Process(target=_rank, args=(r, 2, port, q), daemon=True) for r in range(2)]
     for p in ps:
         p.start()
     res = {r[0]: r for r in (q.get(timeout=300) for _ in ps)}
-    for p in ps:
+    for p in ps:                           # a rank left waiting for a failed peer must not outlive the test
         p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
     assert res[1][1] == "left", res
     assert res[0][1] == "peer-lost", res
     assert 3 <= res[0][2] <= 5 and res[0][3] == 2048.0 and res[0][4] == 0, res

@@ -70,12 +70,14 @@ def test_fused_ep_matches_allgather_oracle(fp8):
         s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_worker, args=(r, 2, port, fp8, q)) for r in range(2)]
+    ps = [ctx.Process(target=_worker, args=(r, 2, port, fp8, q), daemon=True) for r in range(2)]
     for p in ps:
         p.start()
     res = [q.get(timeout=300) for _ in ps]
-    for p in ps:
+    for p in ps:                           # a rank left waiting for a failed peer must not outlive the test
         p.join(timeout=60)
+        if p.is_alive():
+            p.terminate()
     for rank, worst, status in res:
         assert status == 0, f"rank {rank}: {worst}"
         assert worst < 2e-2, f"rank {rank}: relative error {worst}"

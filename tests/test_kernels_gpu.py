@@ -323,6 +323,8 @@ def test_kv_swap_kernel_round_trip(k, model, kv):
     c.allocate_host(6)
     flat = c.kv.view(torch.uint8)
     flat.copy_(torch.randint(0, 255, flat.shape, device="cuda", dtype=torch.uint8))
+    if c.indexer is not None:                     # DSA plans: the indexer key pages travel with the KV pages
+        c.indexer.copy_(torch.randint(0, 255, c.indexer.shape, device="cuda", dtype=torch.uint8))
     want = [v.clone() for b in (3, 7, 1) for v in c.block_views(b)]
     c.swap([3, 7, 1], [0, 5, 2], to_host=True)
     for b in (3, 7, 1):

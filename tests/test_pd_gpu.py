@@ -122,12 +122,16 @@ def test_prefill_gpu_pushes_pages_into_the_decode_gpus_pool():
     ctx = mp.get_context("spawn")
     a, b = ctx.Pipe()
     q = ctx.Queue()
-    ps = [ctx.Process(target=_prefill_proc, args=(a, q)), ctx.Process(target=_decode_proc, args=(b, q))]
+    ps = [ctx.Process(target=_prefill_proc, args=(a, q), daemon=True), ctx.Process(target=_decode_proc, args=(b, q), daemon=True)]
     for p in ps:
         p.start()
-    res = dict((r[0], r) for r in (q.get(timeout=420) for _ in ps))
-    for p in ps:
-        p.join(timeout=60)
+    try:
+        res = dict((r[0], r) for r in (q.get(timeout=420) for _ in ps))
+    finally:
+        for p in ps:                       # a child still blocked on its pipe must not keep the test process alive
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
     assert res["prefill"][2] == 0, res["prefill"][1]
     assert res["decode"][2] == 0, res["decode"][1]
     want, results, free = res["decode"][1]
