@@ -223,7 +223,7 @@ def case_small(kind, T=128, H=7168, E=32, K=8, I=2048):
         return fn, E * H * 4 + T * H * 2, 2.0 * T * E * H
     if kind == "add_rmsnorm_quant":
         r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16); w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
-        return (lambda: sm100.add_rmsnorm(x, r, w, 1e-6)), T * H * (2 + 2 + 2 + 2 + 1), 0.0
+        return (lambda: sm100.add_rmsnorm(x, r, w, 1e-6, False, True)), T * H * (2 + 2 + 2 + 2 + 1), 0.0
     if kind == "rmsnorm_then_quant":
         r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16); w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
         def fn():

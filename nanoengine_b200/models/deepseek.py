@@ -99,7 +99,8 @@ class MLAAttention(nn.Module):
         ops.mla_kv_prepare(kv_a, self.kv_a_layernorm.weight, self.kv_a_layernorm.eps, positions, rope_cache, cache, ctx.slot_mapping, R)
         sparse = None
         if self.indexer is not None:
-            sparse = self.indexer(x, q_c if q_c is not None else x, positions, ctx, rope_cache)
+            xd = ops.dense(x)
+            sparse = self.indexer(xd, ops.dense(q_c) if q_c is not None else xd, positions, ctx, rope_cache)
         q_full = ops.mla_query(q, self.kc, positions, rope_cache, nope, cache, sparse is None, kc_t=self.kc_t)   # [T, H, R + rope]
         o_lat = ops.mla_attention_paged(q_full, cache, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale, R,
                                         sparse_indices=sparse)
@@ -145,14 +146,16 @@ class DeepseekMoE(nn.Module):
         if cfg.n_shared_experts > 0:
             self.shared_experts = SwiGLUMLP(cfg.hidden_size, cfg.moe_intermediate_size * cfg.n_shared_experts, dtype, device, cfg.quant)
 
-    def forward(self, x, ctx: ForwardContext):
+    def forward(self, xq, ctx: ForwardContext):
+        """`xq`: the normalised hidden states, possibly with their block-quantised copy (ops.QAct) for the shared expert."""
         from ..parallel.ep import ep_moe_forward
+        x = ops.dense(xq)
         if self.shared_experts is None:
             idx, w = self.gate(x)
             return ep_moe_forward(self.experts, x, idx, w, ctx, add_in=None)
         if not (x.is_cuda and OVERLAP_SHARED_EXPERTS):
             idx, w = self.gate(x)
-            return ep_moe_forward(self.experts, x, idx, w, ctx, add_in=self.shared_experts(x))
+            return ep_moe_forward(self.experts, x, idx, w, ctx, add_in=self.shared_experts(xq))
         # The shared expert runs on a side stream next to routing, dispatch and the routed GEMMs (its two small GEMMs leave
         # most SMs idle, and so do the routing kernels); the main stream joins it right before the combine adds its output.
         # Works the same eagerly and under CUDA-graph capture (the fork / join become graph edges).
@@ -163,7 +166,7 @@ class DeepseekMoE(nn.Module):
         fork.record(main)
         side.wait_event(fork)
         with torch.cuda.stream(side):
-            shared = self.shared_experts(x)
+            shared = self.shared_experts(xq)
             done = torch.cuda.Event()
             done.record(side)
 
@@ -179,9 +182,10 @@ class DeepseekDecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device, force_dense: bool = False):
         super().__init__()
         self.layer_idx = layer_idx
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        fp8 = cfg.quant == "fp8"             # the norms feed fp8 linears: they also emit the block-quantised copy
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, quant_out=fp8)
         self.self_attn = MLAAttention(cfg, layer_idx, dtype, device)
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, quant_out=fp8)
         self.is_moe = cfg.is_moe_layer(layer_idx) and not force_dense
         self.mlp = DeepseekMoE(cfg, dtype, device, layer_idx) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
 

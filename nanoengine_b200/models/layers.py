@@ -69,13 +69,14 @@ class RMSNorm(nn.Module):
         self.unit_offset = unit_offset  # stored weight is the deviation from one; the kernels apply (1 + w) in fp32
         self.weight = nn.Parameter((torch.zeros if unit_offset else torch.ones)(dim, dtype=dtype, device=device), requires_grad=False)
         self.eps = eps
-        self.quant_out = quant_out      # the only consumer is an fp8 linear: let the kernel emit its quantised input too
+        self.quant_out = quant_out      # the consumers include fp8 linears: the kernel also emits their quantised input (ops.QAct)
 
     def forward(self, x, residual=None):
-        """Without residual: y.  With residual: (y, x + residual) - the fused add + norm used between blocks."""
+        """Without residual: y.  With residual: (y, x + residual) - the fused add + norm used between blocks.  With
+        `quant_out` y is an `ops.QAct`: hand it to QLinear as it is, take `ops.dense(y)` wherever rows are read."""
         if residual is None:
             return ops.rmsnorm(x, self.weight, self.eps, self.quant_out, self.unit_offset)
-        return ops.add_rmsnorm(x, residual, self.weight, self.eps, self.unit_offset)
+        return ops.add_rmsnorm(x, residual, self.weight, self.eps, self.unit_offset, self.quant_out)
 
 
 class SwiGLUMLP(nn.Module):

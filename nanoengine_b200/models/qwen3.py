@@ -47,7 +47,7 @@ class Qwen3Attention(nn.Module):
         self.scale = self.hd ** -0.5
 
     def forward(self, x_slice, positions, ctx: ForwardContext, rope_cache, total_rows: int):
-        qkv = tp_all_gather_linear(x_slice, total_rows, self.qkv_proj) if self.tp > 1 else self.qkv_proj(x_slice)
+        qkv = tp_all_gather_linear(ops.dense(x_slice), total_rows, self.qkv_proj) if self.tp > 1 else self.qkv_proj(x_slice)
         T = qkv.shape[0]
         kc, vc = ctx.kv_caches[self.layer_idx]
         # head split, q / k RMSNorm, rotary embedding and the paged K / V store in one pass over the projection output
@@ -68,6 +68,7 @@ class Qwen3MoE(nn.Module):
 
     def forward(self, x, ctx):
         c = self.cfg
+        x = ops.dense(x)
         logits = ops.router_logits(x, self.gate_weight)
         from ..parallel.ep import routing_options
         idx, w = ops.moe_route(logits, None, c.num_experts_per_tok, 1, 1, c.norm_topk_prob, 1.0, "softmax", **routing_options(self.layer_idx, x.device))
@@ -77,9 +78,10 @@ class Qwen3MoE(nn.Module):
 class Qwen3DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
         super().__init__()
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        fp8 = cfg.quant == "fp8"
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, quant_out=fp8)
         self.self_attn = Qwen3Attention(cfg, layer_idx, dtype, device)
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, quant_out=fp8)
         self.is_moe = cfg.is_moe_layer(layer_idx)
         self.mlp = Qwen3MoE(cfg, dtype, device, layer_idx) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
 

@@ -127,15 +127,16 @@ class Qwen35MoE(nn.Module):
             self.shared_expert = SwiGLUMLP(cfg.hidden_size, cfg.shared_expert_intermediate_size, dtype, device, cfg.quant)
             self.shared_gate_weight = nn.Parameter(torch.zeros(1, cfg.hidden_size, dtype=torch.float32, device=device), requires_grad=False)
 
-    def forward(self, x, ctx):
+    def forward(self, xq, ctx):
         c = self.cfg
+        x = ops.dense(xq)
         logits = ops.router_logits(x, self.gate_weight)
         idx, w = ops.moe_route(logits, None, c.num_experts_per_tok, 1, 1, c.norm_topk_prob, 1.0, "softmax")
         add_in = None
         if self.shared_expert is not None:
             lg = ops.router_logits(x, self.shared_gate_weight)
             g = torch.sigmoid(lg.sum(0) if lg.dim() == 3 else lg)                      # [T, 1] fp32 (the CUDA body returns split-K planes)
-            add_in = (self.shared_expert(x).float() * g).to(x.dtype)
+            add_in = (self.shared_expert(xq).float() * g).to(x.dtype)
         return ep_moe_forward(self.experts, x, idx, w, ctx, add_in)
 
 
@@ -144,8 +145,9 @@ class Qwen35DecoderLayer(nn.Module):
         super().__init__()
         uo = cfg.norm_unit_offset
         self.kind = cfg.layer_type(layer_idx)
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, unit_offset=uo)
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, unit_offset=uo)
+        fp8 = cfg.quant == "fp8"
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, unit_offset=uo, quant_out=fp8)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, unit_offset=uo, quant_out=fp8)
         if self.kind == "linear_attention":
             self.linear_attn = GatedDeltaNet(cfg, cfg.num_layers_of("linear_attention", layer_idx), dtype, device)
         elif self.kind == "full_attention":

@@ -34,8 +34,13 @@ def __getattr__(name):
     if ref_fn is None:
         raise AttributeError(name)
 
+    if isinstance(ref_fn, type) or name == "dense":
+        return ref_fn                      # value types and pure helpers are shared by both bodies
+
     def dispatch(*args, **kw):
         for a in args:
+            if isinstance(a, reference.QAct):
+                a = a.x
             if isinstance(a, torch.Tensor):
                 return getattr(impl(a), name)(*args, **kw)
         return ref_fn(*args, **kw)

@@ -18,20 +18,56 @@ FP8 = torch.float8_e4m3fn
 
 
 # ---- norms -------------------------------------------------------------------------------------
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False, unit_offset: bool = False) -> torch.Tensor:
-    """`quant` is a hint for the CUDA body (also emit the block-quantised copy for an fp8 consumer); ignored here.
+class QAct:
+    """A normalised activation in the two forms its consumers take: `x`, the bf16 (or fp32) rows that routers, gathers and
+    non-quantised linears read, and - when the producing kernel emitted it - the 1x128 block-quantised copy (`q` e4m3 [T, H],
+    `scales` fp32 [H/128, T]) that an fp8 linear multiplies directly.  Norms asked for `quant` return this object (the
+    PyTorch statement leaves `q` empty), `linear` accepts it, everything else takes `dense(a)`.  An explicit value instead of
+    an attribute riding on the tensor: a view or a cast cannot silently drop the quantised copy.
+    Parity: reference layers/base_backend.py:14-26 (PrequantizedActivation) and the shared input quant of
+    models/deepseek_v2/deepseek_v2.py:1139-1164."""
+    __slots__ = ("x", "q", "scales")
+
+    def __init__(self, x: torch.Tensor, q: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None):
+        self.x, self.q, self.scales = x, q, scales
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def device(self):
+        return self.x.device
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    @property
+    def is_cuda(self):
+        return self.x.is_cuda
+
+
+def dense(a):
+    """The plain tensor behind an activation, whatever form it travels in."""
+    return a.x if isinstance(a, QAct) else a
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False, unit_offset: bool = False):
+    """`quant`: the consumer is an fp8 linear - return a `QAct` (the CUDA body fills in the block-quantised copy).
     `unit_offset`: the stored weight is the deviation from one (Qwen3.5 / Gemma convention), applied as (1 + w) in fp32."""
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     wf = w.float() + 1.0 if unit_offset else w.float()
-    return (y * wf).to(x.dtype)
+    y = (y * wf).to(x.dtype)
+    return QAct(y) if quant else y
 
 
-def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float, unit_offset: bool = False):
-    """residual_out = x + residual (in the activation dtype); y = rmsnorm(residual_out)."""
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float, unit_offset: bool = False, quant: bool = False):
+    """residual_out = x + residual (in the activation dtype); y = rmsnorm(residual_out) (a `QAct` when `quant`)."""
     if residual is not None:
         x = (x.float() + residual.float()).to(x.dtype)
-    return rmsnorm(x, w, eps, False, unit_offset), x
+    return rmsnorm(x, w, eps, quant, unit_offset), x
 
 
 def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float) -> torch.Tensor:
@@ -79,6 +115,7 @@ def dequant_fp8_block(q: torch.Tensor, s: torch.Tensor, block: int = 128) -> tor
 
 def linear(x: torch.Tensor, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, bias=None) -> torch.Tensor:
     """y = x @ w^T.  fp8 weights follow the DeepSeek recipe: activations quantised 1x128, fp32 accumulate."""
+    x = dense(x)
     if w.dtype == FP8:
         xq, xs = quant_fp8_1x128(x.reshape(-1, x.shape[-1]))
         y = dequant_fp8_1x128(xq, xs) @ dequant_fp8_block(w, w_scale).t()

@@ -122,6 +122,9 @@ def _as_bf16_2d(x):
     return x2
 
 
+QAct, dense = ref.QAct, ref.dense
+
+
 class PrequantizedActivation:
     """An activation that exists only in its 1x128 block-quantised form: e4m3 [T, K] and scales [K/128, T], as left by a
     fused producer (SwiGLU + quant).  `linear` with an fp8 weight consumes it directly.
@@ -141,7 +144,10 @@ def linear(x, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None, bias=None
         if T > 0:
             _gemm(x.q, K, 0, w, out, N, 0, T, N, K, 1, None, None, True, x.scales, T, 0, w_scale, out_fp32)
         return out if bias is None else out + bias
-    pre = getattr(x, "_ne_q", None)          # (e4m3 [T, K], scales [K/128, T]) left by a fused norm + quant kernel
+    pre = None
+    if isinstance(x, QAct):                   # (e4m3 [T, K], scales [K/128, T]) left by a fused norm + quant kernel
+        pre = (x.q, x.scales) if x.q is not None else None
+        x = x.x
     x2 = _as_bf16_2d(x)
     T = x2.shape[0]
     out = torch.empty(T, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
@@ -209,9 +215,6 @@ def bmm_absorb(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = N
 
 
 # ---- norms / activation ----------------------------------------------------------------------------
-QUANT_AFTER_NORM = True      # block-level norms also emit the e4m3 1x128 copy their fp8 consumers need
-
-
 def _rmsnorm(x, res_in, w, eps, want_res, quant=False, unit_offset=False):
     T, H = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1
@@ -225,24 +228,25 @@ def _rmsnorm(x, res_in, w, eps, want_res, quant=False, unit_offset=False):
         sc = torch.empty(H // 128, T, dtype=torch.float32, device=x.device)
     _ck(lib().ne_rmsnorm(_p(x), _c.c_longlong(x.stride(0)), _p(res_in), _p(w), _p(out), _c.c_longlong(H), _p(res_out), _p(q), _p(sc),
                          _c.c_int(T), _c.c_int(T), _c.c_int(H), _c.c_float(eps), _c.c_float(1.0 if unit_offset else 0.0), _st()), "ne_rmsnorm")
-    if q is not None:
-        out._ne_q = (q, sc)
+    if quant:
+        out = QAct(out, q, sc)               # q stays None when the width is not a multiple of 128: the consumer quantises itself
     return out, res_out
 
 
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False, unit_offset: bool = False) -> torch.Tensor:
-    """`quant`: also leave the e4m3 1x128 copy for an fp8 linear that consumes the result (picked up by `linear`)."""
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, quant: bool = False, unit_offset: bool = False):
+    """`quant`: the same kernel also writes the e4m3 1x128 copy for the fp8 linear that consumes the result; both travel in a
+    `QAct`."""
     if x.stride(0) % 8 or x.data_ptr() % 16:
         x = x.contiguous()
-    return _rmsnorm(x, None, w, eps, False, quant and x.shape[1] % 128 == 0, unit_offset)[0]
+    return _rmsnorm(x, None, w, eps, False, quant, unit_offset)[0]
 
 
-def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float, unit_offset: bool = False):
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], w: torch.Tensor, eps: float, unit_offset: bool = False, quant: bool = False):
     if x.stride(0) % 8 or x.data_ptr() % 16:
         x = x.contiguous()
     if residual is None:
-        return _rmsnorm(x, None, w, eps, False, QUANT_AFTER_NORM, unit_offset)[0], x
-    return _rmsnorm(x, residual, w, eps, True, QUANT_AFTER_NORM, unit_offset)
+        return _rmsnorm(x, None, w, eps, False, quant, unit_offset)[0], x
+    return _rmsnorm(x, residual, w, eps, True, quant, unit_offset)
 
 
 def layernorm(x, w, b, eps):

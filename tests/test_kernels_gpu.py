@@ -206,7 +206,10 @@ def test_swiglu_quant_feeds_fp8_linear(k):
     wn = torch.ones(1536, device="cuda", dtype=torch.bfloat16)
     y = k.rmsnorm(x, wn, 1e-6, True)
     q2, s2 = k.quant_fp8_1x128(k.rmsnorm(x, wn, 1e-6))
-    assert torch.equal(y._ne_q[0].view(torch.uint8), q2.view(torch.uint8))
+    assert isinstance(y, k.QAct) and torch.equal(y.q.view(torch.uint8), q2.view(torch.uint8))
+    # an fp8 linear fed the pair multiplies the quantised copy it was handed: same product as quantising the dense rows again
+    wq2, ws2 = ref.quant_fp8_block(torch.randn(256, 1536, device="cuda") * 0.05)
+    assert torch.equal(k.linear(y, wq2, ws2), k.linear(k.dense(y), wq2, ws2))
 
 
 @pytest.mark.parametrize("E,topk,ng,tg,scoring", [(256, 8, 8, 4, "sigmoid"), (128, 8, 1, 1, "softmax"), (8, 2, 1, 1, "sigmoid"), (64, 6, 4, 2, "sigmoid")])
