@@ -125,6 +125,30 @@ def build_gateway(force=False) -> Path:
     return target
 
 
+def build_sanitized(kind: str = "address,undefined", force=False) -> dict:
+    """Sanitizer builds of the host-side C++ (nothing here runs on a GPU): the control-plane exerciser
+    `csrc/core/selftest.cpp` and the gateway, compiled with -fsanitize=<kind> into `_native/san/`.  `kind` is
+    "address,undefined" or "thread".  The CPU test suite builds and runs both kinds."""
+    tag = "tsan" if "thread" in kind else "asan"
+    out = OUT / "san"
+    out.mkdir(parents=True, exist_ok=True)
+    flags = ["-std=c++20", "-O1", "-g", f"-fsanitize={kind}", "-fno-omit-frame-pointer", "-pthread"]
+    core_srcs = sorted((CSRC / "core").glob("*.h")) + [CSRC / "core" / "selftest.cpp"]
+    selftest = out / f"core_selftest_{tag}"
+    st = _stamp(core_srcs, kind)
+    if _needs(selftest, st, force):
+        _run([CXX, *flags, str(CSRC / "core" / "selftest.cpp"), "-o", str(selftest)])
+        _mark(selftest, st)
+    gdir = REPO / "gateway"
+    gsrcs = sorted(gdir.glob("*.cpp")) + sorted(gdir.glob("*.h"))
+    gateway = out / f"ne-gateway-{tag}"
+    st = _stamp(gsrcs, kind)
+    if _needs(gateway, st, force):
+        _run([CXX, *flags, *map(str, sorted(gdir.glob("*.cpp"))), "-o", str(gateway)])
+        _mark(gateway, st)
+    return {"selftest": selftest, "gateway": gateway}
+
+
 def build_all(force=False):
     OUT.mkdir(parents=True, exist_ok=True)
     (OUT / "__init__.py").touch()

@@ -7,6 +7,10 @@
 //
 // Replaces in the reference: the decode-side pull of runtime/disagg/p2p/cache_transfer.py:648-1142 (coalesced one-sided
 // reads followed by a device synchronise) and the byte-stride bookkeeping of disagg/p2p/cache_layout.py:14-240.
+#include <cuda.h>
+
+#include <cstring>
+
 #include "ptx.cuh"
 
 namespace ne {
@@ -87,3 +91,38 @@ extern "C" int ne_kv_wait_each(const int* flags, const int* idx, const int* want
   kv_wait_each_kernel<<<(n + 127) / 128, 128, 0, st>>>(flags, idx, want, n, out, spin_limit);
   return (int)cudaGetLastError();
 }
+
+// ---- mapping another process' device memory ------------------------------------------------------------------------
+// A decode worker publishes (handle of the allocation that holds a buffer, byte offset of the buffer inside it); a prefill
+// worker on the same machine opens the handle WITH ITS OWN DEVICE CURRENT, which is what makes the mapping reachable from
+// kernels running on that device (the runtime enables peer access between the opening device and the exporting one).  An
+// allocation can be opened once per process: callers keep the returned base and reuse it for every buffer inside it.
+typedef CUresult (*AddrRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+extern "C" int ne_ipc_export(const void* ptr, void* handle64, long long* offset, long long* alloc_bytes) {
+  static AddrRangeFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return 1201;
+    fn = (AddrRangeFn)p;
+  }
+  CUdeviceptr base = 0; size_t size = 0;
+  if (fn(&base, &size, (CUdeviceptr)(uintptr_t)ptr) != CUDA_SUCCESS) return 1202;
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, (void*)(uintptr_t)base);
+  if (e != cudaSuccess) return (int)e;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+  memcpy(handle64, &h, 64);
+  *offset = (long long)((uintptr_t)ptr - (uintptr_t)base);
+  *alloc_bytes = (long long)size;
+  return 0;
+}
+
+extern "C" int ne_ipc_open(const void* handle64, void** base_out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  return (int)cudaIpcOpenMemHandle(base_out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+
+extern "C" int ne_ipc_close(void* base) { return (int)cudaIpcCloseMemHandle(base); }

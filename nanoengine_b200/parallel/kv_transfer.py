@@ -54,21 +54,56 @@ def validate_blocks(blocks: Sequence[int], num_blocks: int, what: str) -> None:
 
 
 # ---- pool descriptors: what a decode worker publishes and a prefill worker opens ----------------------------------------
+_DT = {"uint8": torch.uint8, "int32": torch.int32, "int64": torch.int64}
+_OPENED: Dict[bytes, int] = {}           # IPC handle -> base address of its mapping in this process (an allocation opens once)
+
+
+class _Alias:
+    """Lets torch wrap memory it did not allocate (a peer process' buffer mapped into this one)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3, "strides": None}
+
+
 def export_tensor(t: torch.Tensor, direct: bool):
-    """`direct`: the tensor itself (same process).  Otherwise bytes that rebuild a view of the same device memory in another
-    process on this machine (CUDA IPC through torch's tensor reduction)."""
+    """`direct`: the tensor itself (same process).  Otherwise a picklable / JSON-able description from which a worker process on
+    this machine can map the same device memory: the CUDA IPC handle of the allocation the tensor lives in, the tensor's
+    byte offset inside it, its element type and element count (the tensor must be contiguous)."""
     if direct or not t.is_cuda:
         return t
-    from torch.multiprocessing.reductions import reduce_tensor
-    fn, args = reduce_tensor(t)
-    return pickle.dumps((fn, args))
+    import ctypes as _c
+    from ..ops import sm100 as k
+    assert t.is_contiguous() and str(t.dtype).replace("torch.", "") in _DT
+    h = (_c.c_ubyte * 64)()
+    off, size = _c.c_longlong(0), _c.c_longlong(0)
+    with torch.cuda.device(t.device):
+        rc = k.lib().ne_ipc_export(_c.c_void_p(t.data_ptr()), h, _c.byref(off), _c.byref(size))
+    if rc != 0:
+        raise RuntimeError(f"cannot export device memory for another process (code {rc})")
+    return {"ipc": bytes(h).hex(), "offset": int(off.value), "numel": t.numel(), "dtype": str(t.dtype).replace("torch.", ""),
+            "device": t.device.index}
 
 
 def open_tensor(h) -> torch.Tensor:
+    """The tensor behind an `export_tensor` result.  The mapping of a peer buffer is opened with THIS process' current device
+    current (the device whose kernels will write to it), once per allocation; the tensor returned aliases it."""
     if isinstance(h, torch.Tensor):
         return h
-    fn, args = pickle.loads(h)
-    return fn(*args)
+    import ctypes as _c
+    from ..ops import sm100 as k
+    handle = bytes.fromhex(h["ipc"])
+    base = _OPENED.get(handle)
+    if base is None:
+        out = _c.c_void_p(0)
+        rc = k.lib().ne_ipc_open((_c.c_ubyte * 64).from_buffer_copy(handle), _c.byref(out))
+        if rc != 0:
+            raise RuntimeError(f"cannot map a peer process' device memory (code {rc}); both processes must see the exporting GPU")
+        base = _OPENED[handle] = int(out.value)
+    dt = _DT[h["dtype"]]
+    typestr = {"uint8": "|u1", "int32": "<i4", "int64": "<i8"}[h["dtype"]]
+    t = torch.as_tensor(_Alias(base + h["offset"], (h["numel"],), typestr))      # no `device=`: that could copy instead of aliasing
+    assert t.data_ptr() == base + h["offset"] and t.dtype == dt
+    return t
 
 
 def check_families(mine: List[dict], theirs: List[dict]) -> None:

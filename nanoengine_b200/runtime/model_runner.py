@@ -363,6 +363,8 @@ class ModelRunner:
         family has the layout of the local one.  Returns how many pools are mapped."""
         from ..parallel.kv_transfer import check_families, open_tensor
         mine = self.cache.page_families()
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)       # peer mappings are opened with the writing device current
         peers = getattr(self, "_pd_peers", None)
         if peers is None:
             peers = self._pd_peers = {}
@@ -379,10 +381,6 @@ class ModelRunner:
             n += 1
         if self.device.type == "cuda":
             self._pd_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
-            for q in peers.values():                 # one small cross-device copy makes the runtime enable peer access both ways
-                if q["flags"].device != self.device:
-                    q["flags"][-1:].copy_(torch.zeros(1, dtype=torch.int32, device=self.device))
-            torch.cuda.synchronize(self.device)
         return n
 
     def pd_push(self, key: str, reqs: List[dict]) -> List[int]:

@@ -12,7 +12,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-GATEWAY = os.path.join(ROOT, "nanoengine_b200", "_native", "ne-gateway")
+GATEWAY = os.environ.get("NE_GATEWAY_BIN") or os.path.join(ROOT, "nanoengine_b200", "_native", "ne-gateway")      # the variable lets the sanitizer run reuse these tests
 
 
 def _port():

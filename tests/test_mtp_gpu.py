@@ -33,7 +33,7 @@ def test_greedy_verify_matches_reference(k, B, N, V):
     racc, rnxt, rbundle, rext, rlp = ref.mtp_verify(logits, drafts, temps, have, want_logprob=True)
     assert torch.equal(acc, racc) and torch.equal(nxt, rnxt) and torch.equal(bundle, rbundle) and torch.equal(ext, rext)
     assert torch.allclose(lp, rlp, atol=2e-3)
-    assert int(acc.max()) > 0 and int((acc * (1 - have)).sum()) == 0
+    assert (B == 1 or int(acc.max()) > 0) and int((acc * (1 - have)).sum()) == 0
     # pinned acceptance (benchmarks): the next token is the arg-max of that row
     acc2, nxt2, *_ = k.mtp_verify(logits, drafts, temps, have, force_accept=1)
     assert bool((acc2 == min(1, N)).all()) and torch.equal(nxt2, logits.argmax(-1)[:, min(1, N)])

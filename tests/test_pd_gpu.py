@@ -132,8 +132,7 @@ def test_prefill_gpu_pushes_pages_into_the_decode_gpus_pool():
             p.join(timeout=30)
             if p.is_alive():
                 p.terminate()
-    assert res["prefill"][2] == 0, res["prefill"][1]
-    assert res["decode"][2] == 0, res["decode"][1]
+    assert res["prefill"][2] == 0 and res["decode"][2] == 0, f"prefill: {res['prefill'][1]}\ndecode: {res['decode'][1]}"
     want, results, free = res["decode"][1]
     ids = sorted(want)
     # round 1: every request decodes to the hybrid engine's tokens (sequence ids differ between engines, order does not)
