@@ -65,6 +65,13 @@ def _run(cmd, log: Path | None = None):
     return r
 
 
+def _quiet_run(cmd):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError((r.stdout + r.stderr)[-600:])
+    return r
+
+
 def build_core(force=False) -> Path:
     import pybind11
     suffix = sysconfig.get_config_var("EXT_SUFFIX")
@@ -133,18 +140,30 @@ def build_sanitized(kind: str = "address,undefined", force=False) -> dict:
     out = OUT / "san"
     out.mkdir(parents=True, exist_ok=True)
     flags = ["-std=c++20", "-O1", "-g", f"-fsanitize={kind}", "-fno-omit-frame-pointer", "-pthread"]
+
+    def compile_(srcs, target):
+        # the configured compiler may be a wrapper without the sanitizer runtimes: try the system ones before giving up
+        last = None
+        for cxx in dict.fromkeys([CXX, "/usr/bin/g++", "g++", "clang++"]):
+            try:
+                _quiet_run([cxx, *flags, *map(str, srcs), "-o", str(target)])
+                return
+            except (RuntimeError, FileNotFoundError) as e:
+                last = e
+        raise RuntimeError(f"no compiler here links -fsanitize={kind}: {last}")
+
     core_srcs = sorted((CSRC / "core").glob("*.h")) + [CSRC / "core" / "selftest.cpp"]
     selftest = out / f"core_selftest_{tag}"
     st = _stamp(core_srcs, kind)
     if _needs(selftest, st, force):
-        _run([CXX, *flags, str(CSRC / "core" / "selftest.cpp"), "-o", str(selftest)])
+        compile_([CSRC / "core" / "selftest.cpp"], selftest)
         _mark(selftest, st)
     gdir = REPO / "gateway"
     gsrcs = sorted(gdir.glob("*.cpp")) + sorted(gdir.glob("*.h"))
     gateway = out / f"ne-gateway-{tag}"
     st = _stamp(gsrcs, kind)
     if _needs(gateway, st, force):
-        _run([CXX, *flags, *map(str, sorted(gdir.glob("*.cpp"))), "-o", str(gateway)])
+        compile_(sorted(gdir.glob("*.cpp")), gateway)
         _mark(gateway, st)
     return {"selftest": selftest, "gateway": gateway}
 
