@@ -147,8 +147,7 @@ class MTPRunner:
         slots = torch.tensor(list(b.handoff_slots), dtype=torch.long, device=r.device)
         done = torch.from_numpy(mask).to(r.device)
         srow = torch.where(done & (slots >= 0), slots, torch.full_like(slots, self.scratch_row))
-        self.handoff[srow, 1:] = drafts
-        self.handoff[srow, 0] = 1
+        self.handoff.index_copy_(0, srow, torch.cat([torch.ones_like(drafts[:, :1]), drafts], 1))
         toks = tok.tolist()
         lps = lp.tolist() if lp is not None else None
         ids_out = [s for s, m in zip(b.seq_ids, mask) if m]
@@ -180,8 +179,9 @@ class MTPRunner:
         h_last = h_mtp.index_select(0, sel)
         d1 = self._argmax(r.mtp.compute_logits(h_last))
         nd = self._draft_chain(ctx, B, h_last, d1, base_len, acc, chain_bufs) if N > 1 else d1.unsqueeze(1)
-        self.handoff[srow, 1:] = nd
-        self.handoff[srow, 0] = 1
+        # one indexed row copy, every operand already on the device (a Python scalar here would be a host->device copy, which a
+        # stream capture refuses); rows without a slot all land on the scratch row
+        self.handoff.index_copy_(0, srow, torch.cat([torch.ones_like(nd[:, :1]), nd], 1))
         return bundle, acc, lp
 
     def _run_verify(self, b):
