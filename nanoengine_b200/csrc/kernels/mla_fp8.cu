@@ -11,6 +11,13 @@
 // Warp 0: TMA producer; warp 1: MMA issuer; warps 2-5: softmax / rescale / epilogue.  All waits are bounded.
 // With more than one key slice the CTA writes a normalised partial result and its log2-sum-exp; ne_attn_merge folds them.
 //
+// Sparse form (DSA): the keys of a token are not pages but a list of cache rows picked by the lightning indexer (top-k
+// physical slot ids, -1 = none).  The same pipeline runs over tiles of 64 listed rows; only the producer differs: warp 0
+// gathers the 64 rows (576 bytes each, 16 bytes per cp.async) into the swizzled layout TMA would have produced, zero-filling
+// rows without an id, and hands a tile over once its copies have landed and were fenced for the tensor-core proxy.  The
+// softmax warps mask the columns whose id is -1.  This is the tensor-core replacement for the CUDA-core gather path
+// (reference layers/backends/mla/trtllm.py:93-204 `sparse_mla_top_k`, layers/backends/mla/flash_mla.py:22-121).
+//
 // fp8 contract (reference layers/backends/mla/trtllm.py:93-204): the query is clamped to +-448 and cast to e4m3 without
 // a scale, cache rows are clamped-cast e4m3, softmax scale is applied to the fp32 logits.
 #include <atomic>
@@ -38,8 +45,18 @@ struct MlaArgs {
   float scale_log2;                  // softmax scale * log2(e)
   __nv_bfloat16* out;                // [T, H, 512] (splits == 1)
   float* part; float* lse2;          // [splits, T, H, 512], [splits, T, H] (splits > 1)
+  // sparse form
+  const int* sparse; int topk;       // [T, topk] cache row ids (block * 64 + offset), -1 = no key
+  const uint8_t* cache; long long cache_rows;
 };
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <bool kSparse>
 __global__ void __launch_bounds__(kMlaThreads, 1)
 mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant__ CUtensorMap tq64,
                const __grid_constant__ CUtensorMap tk128, const __grid_constant__ CUtensorMap tk64, const MlaArgs a) {
@@ -61,7 +78,7 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
-    for (int i = 0; i < kPgStages; i++) { mbar_init(b_pgfull + 8 * i, 1); mbar_init(b_pgempty + 8 * i, 1); }
+    for (int i = 0; i < kPgStages; i++) { mbar_init(b_pgfull + 8 * i, kSparse ? 32 : 1); mbar_init(b_pgempty + 8 * i, 1); }
     for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 4); }
     for (int i = 0; i < 2; i++) { mbar_init(b_pfull + 8 * i, 4); mbar_init(b_pempty + 8 * i, 1); }
     *abort_flag = 0;
@@ -71,17 +88,24 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
   pdl_wait(); pdl_trigger();      // dependent launch: the set-up above touches no global memory
 
   // sequence of this token, causal limit, page range of this split (uniform over the CTA)
-  int lo = 0, hi = a.num_seqs;
-  while (lo + 1 < hi) { int mid = (lo + hi) >> 1; if (a.cu_seqlens_q[mid] <= t) lo = mid; else hi = mid; }
-  const int seq = lo;
-  const int q_len = a.cu_seqlens_q[seq + 1] - a.cu_seqlens_q[seq];
-  const int limit = a.context_lens[seq] - q_len + (t - a.cu_seqlens_q[seq]);     // last visible key position
-  const int total_pages = limit >= 0 ? limit / kPage + 1 : 0;
+  int seq = 0, limit = 0x3fffffff, total_pages;
+  const int* bt = nullptr;
+  if (!kSparse) {
+    int lo = 0, hi = a.num_seqs;
+    while (lo + 1 < hi) { int mid = (lo + hi) >> 1; if (a.cu_seqlens_q[mid] <= t) lo = mid; else hi = mid; }
+    seq = lo;
+    const int q_len = a.cu_seqlens_q[seq + 1] - a.cu_seqlens_q[seq];
+    limit = a.context_lens[seq] - q_len + (t - a.cu_seqlens_q[seq]);     // last visible key position
+    total_pages = limit >= 0 ? limit / kPage + 1 : 0;
+    bt = a.block_tables + (long long)seq * a.bt_stride;
+  } else {
+    total_pages = (a.topk + kPage - 1) / kPage;                           // tiles of 64 listed rows; the list is already causal
+  }
   const int per_split = (total_pages + a.splits - 1) / a.splits;
   const int pg_begin = split * per_split;
   const int pg_end = min(total_pages, pg_begin + per_split);
   const int n_tiles = max(0, pg_end - pg_begin);
-  const int* bt = a.block_tables + (long long)seq * a.bt_stride;
+  const int* ids = kSparse ? a.sparse + (long long)t * a.topk : nullptr;
 
   tc_fence_before();
   __syncthreads();
@@ -89,7 +113,51 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 128;
 
-  if (warp == 0) {
+  if (warp == 0 && kSparse) {
+    if (n_tiles > 0) {
+      const int lane = (int)lane_id();
+      if (lane == 0) {
+        const int qrow = t * a.H;
+        mbar_expect_tx(b_qfull, kQBytes);
+        for (int p = 0; p < 4; p++) tma_load_2d(smem_u32(sQ + p * 128 * 128), &tq128, b_qfull, p * 128, qrow);
+        tma_load_2d(smem_u32(sQ + kQNope), &tq64, b_qfull, 512, qrow);
+      }
+      // One cp.async group per iteration (empty once the tiles run out), so "all but the newest kPgStages - 1 groups have
+      // landed" identifies tile i - (kPgStages - 1): it is fenced for the tensor-core proxy and handed over, which keeps two
+      // tiles in flight behind the one being consumed.
+      bool ok = true;
+      for (int i = 0; i < n_tiles + kPgStages - 1; i++) {
+        if (i < n_tiles && ok) {
+          const int s = i % kPgStages;
+          if (!mbar_wait(b_pgempty + 8 * s, ((i / kPgStages) & 1) ^ 1, abort_flag, kKernelMla, 100 + s)) ok = false;
+          if (ok) {
+            const int k0 = (pg_begin + i) * kPage;
+            const int id_lo = k0 + lane < a.topk ? ids[k0 + lane] : -1, id_hi = k0 + 32 + lane < a.topk ? ids[k0 + 32 + lane] : -1;
+            const uint32_t dst = smem_u32(sPg + s * kPgBytes);
+#pragma unroll 4
+            for (int c = lane; c < kPage * (kDk / 16); c += 32) {
+              const int row = c / (kDk / 16), ch = c - row * (kDk / 16);            // 36 chunks of 16 bytes per row
+              const int a_lo = __shfl_sync(0xffffffffu, id_lo, row & 31), a_hi = __shfl_sync(0xffffffffu, id_hi, row & 31);
+              const int id = row < 32 ? a_lo : a_hi;
+              const bool valid = id >= 0 && (long long)id < a.cache_rows;          // anything else is zero-filled, never dereferenced
+              const uint8_t* src = a.cache + (valid ? (long long)id * kDk + ch * 16 : 0);
+              const uint32_t d = ch < 32 ? dst + (ch >> 3) * (kPage * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4)
+                                         : dst + kPgNope + row * 64 + (((ch - 32) ^ ((row >> 1) & 3)) << 4);
+              cp_async16(d, src, valid ? 16u : 0u);
+            }
+          }
+        }
+        cp_async_commit();
+        const int j = i - (kPgStages - 1);
+        if (j >= 0) {
+          cp_async_wait<kPgStages - 1>();
+          fence_proxy_async_smem();
+          mbar_arrive(b_pgfull + 8 * (j % kPgStages));
+        }
+      }
+      cp_async_wait<0>();
+    }
+  } else if (warp == 0) {
     if (n_tiles > 0 && elect_one()) {
       const int qrow = t * a.H;
       mbar_expect_tx(b_qfull, kQBytes);
@@ -182,7 +250,19 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
       // this page's P buffer was last read by the P V product of page i-2: tested here, long before the answer is needed
       // (an mbarrier test costs ~150 cycles even when the phase completed long ago)
       const bool p_free = i < 2 || mbar_test(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1);
-      if (!row_ok || key0 + kPage - 1 > limit) {                 // only the page that straddles the causal limit needs masking
+      if (kSparse) {
+        // columns whose listed row id is -1 (or past the list) hold zero-filled keys: take them out of the softmax
+        const int l = (int)lane_id();
+        const unsigned v_lo = __ballot_sync(0xffffffffu, key0 + l < a.topk && ids[key0 + l] >= 0);
+        const unsigned v_hi = __ballot_sync(0xffffffffu, key0 + 32 + l < a.topk && ids[key0 + 32 + l] >= 0);
+        if (!row_ok || (v_lo & v_hi) != 0xffffffffu) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            if (!row_ok || !((v_lo >> j) & 1u)) r0[j] = 0xff800000u;
+            if (!row_ok || !((v_hi >> j) & 1u)) r1[j] = 0xff800000u;
+          }
+        }
+      } else if (!row_ok || key0 + kPage - 1 > limit) {                 // only the page that straddles the causal limit needs masking
 #pragma unroll
         for (int j = 0; j < 32; j++) {
           if (!row_ok || key0 + j > limit) r0[j] = 0xff800000u;
@@ -339,15 +419,43 @@ extern "C" int ne_mla_fp8(const void* q8, const void* cache, int num_blocks, con
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(mla_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem);
+    cudaError_t e = cudaFuncSetAttribute(mla_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   MlaArgs a;
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs;
   a.T = T; a.H = H; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f; a.out = (__nv_bfloat16*)out; a.part = part; a.lse2 = lse2;
+  a.sparse = nullptr; a.topk = 0; a.cache = nullptr; a.cache_rows = 0;
   dim3 grid(2 * T, splits, 1);
-  return (int)launch_pdl(mla_fp8_kernel, grid, dim3(kMlaThreads), kMlaSmem, st, tq128, tq64, tk128, tk64, a);
+  return (int)launch_pdl(mla_fp8_kernel<false>, grid, dim3(kMlaThreads), kMlaSmem, st, tq128, tq64, tk128, tk64, a);
+}
+
+// Sparse form: every query token attends the `topk` cache rows listed for it (sparse int32 [T, topk], row id = block * 64 +
+// offset, -1 = none; the list must already respect causality).  Same outputs as ne_mla_fp8.
+extern "C" int ne_mla_fp8_sparse(const void* q8, const void* cache, int num_blocks, const int* sparse, int topk, int T, int H, int splits,
+                                 float scale, void* out, float* part, float* lse2, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H > 128 || H < 1 || splits < 1 || topk < 1 || !sparse || (splits > 1 && (!part || !lse2))) return 1001;
+  CUtensorMap tq128, tq64;
+  {
+    uint64_t dims[2] = {(uint64_t)kDk, (uint64_t)T * H}; uint64_t strides[1] = {(uint64_t)kDk};
+    uint32_t b128[2] = {128, 128}, b64[2] = {64, 128};
+    int rc = make_tmap(&tq128, q8, TMA_U8, 2, dims, strides, b128, TMA_SW_128); if (rc) return 2000 + rc;
+    rc = make_tmap(&tq64, q8, TMA_U8, 2, dims, strides, b64, TMA_SW_64); if (rc) return 2100 + rc;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mla_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  MlaArgs a;
+  a.block_tables = nullptr; a.bt_stride = 0; a.cu_seqlens_q = nullptr; a.context_lens = nullptr; a.num_seqs = 0;
+  a.T = T; a.H = H; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f; a.out = (__nv_bfloat16*)out; a.part = part; a.lse2 = lse2;
+  a.sparse = sparse; a.topk = topk; a.cache = (const uint8_t*)cache; a.cache_rows = (long long)num_blocks * kPage;
+  dim3 grid(2 * T, splits, 1);
+  return (int)launch_pdl(mla_fp8_kernel<true>, grid, dim3(kMlaThreads), kMlaSmem, st, tq128, tq64, tq128, tq64, a);     // the key maps are unused here
 }
 
 // ---- allocation-free entry point ----------------------------------------------------------------------

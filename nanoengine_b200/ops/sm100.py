@@ -309,13 +309,13 @@ def mla_absorb_rope(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, 
 
 def mla_query(q: torch.Tensor, kc: torch.Tensor, positions: torch.Tensor, rope_cache: torch.Tensor, nope: int, kv_cache: torch.Tensor,
               dense: bool = True, kc_t: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Absorbed MLA query.  For the dense fp8 attention kernel (fp8 cache of 64-token pages, 512 + 64 wide rows, at most
-    128 heads) the result is e4m3 [T, H, 576]: the per-head GEMM's epilogue writes the latent part as e4m3 straight into it
+    """Absorbed MLA query.  For the fp8 tensor-core attention kernels, dense or sparse (fp8 cache of 64-token pages, 512 + 64
+    wide rows, at most 128 heads) the result is e4m3 [T, H, 576]: the per-head GEMM's epilogue writes the latent part as e4m3 straight into it
     and one small kernel rotates and casts the 64-wide tail, instead of a bf16 latent query, a RoPE pass and a cast pass."""
     T, H, _ = q.shape
     R = kc.shape[2]
     rope = q.shape[2] - nope
-    if not (dense and kv_cache.dtype == FP8 and R == 512 and rope == 64 and kv_cache.shape[1] == 64 and H <= 128 and T > 0):
+    if not (kv_cache.dtype == FP8 and R == 512 and rope == 64 and kv_cache.shape[1] == 64 and H <= 128 and T > 0):      # dense and sparse alike
         return mla_absorb_rope(q, kc, positions, rope_cache, nope, kc_t)
     q8 = torch.empty(T, H, R + rope, dtype=torch.uint8, device=q.device)
     bmm_absorb(q[..., :nope], kc, out=q8[..., :R], wt=kc_t)

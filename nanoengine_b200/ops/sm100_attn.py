@@ -1,7 +1,8 @@
 """CUDA bodies of attention and sampling.
 
 MLA over an fp8 latent cache with the DeepSeek-V3 geometry (576-value rows, 64-token pages, <= 128 heads) runs on the
-tcgen05 kernel; every other shape, the bf16 cache and DSA sparse key lists run on the shape-generic CUDA-core kernel.
+tcgen05 kernel, dense (paged) and DSA-sparse (listed rows gathered into the same pipeline) alike; every other shape and the
+bf16 cache run on the shape-generic CUDA-core kernel.
 """
 from __future__ import annotations
 
@@ -68,11 +69,33 @@ def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scal
     out = torch.empty(T, H, R, dtype=torch.bfloat16, device=q.device)
     if T == 0:
         return out
-    fast = (cache.dtype == FP8 and Dk == 576 and R == 512 and cache.shape[1] == 64 and H <= 128 and sparse_indices is None)
+    geom = cache.dtype == FP8 and Dk == 576 and R == 512 and cache.shape[1] == 64 and H <= 128
+    fast = geom and sparse_indices is None
     if q.dtype == FP8:
-        assert fast and q.is_contiguous(), "an e4m3 query is only produced for the dense fp8 attention kernel"
+        assert geom and q.is_contiguous(), "an e4m3 query is only produced for the fp8 tensor-core attention kernels"
     else:
         q = q if (q.dtype == torch.bfloat16 and q.is_contiguous()) else q.to(torch.bfloat16).contiguous()
+    if geom and sparse_indices is not None:
+        # DSA: the listed cache rows are gathered into the same tcgen05 pipeline (64 rows per tile)
+        if q.dtype == FP8:
+            q8 = q
+        else:
+            q8 = torch.empty(T * H, Dk, dtype=torch.uint8, device=q.device)
+            _k._ck(lib.ne_cast_e4m3(_k._p(q), _k._p(q8), _c.c_longlong(T * H * Dk), _k._st()), "ne_cast_e4m3")
+        sp = _i32(sparse_indices)
+        topk = sp.shape[1]
+        tiles = -(-topk // 64)
+        S = splits if splits is not None else max(1, min(-(-_sms() // (2 * T)) if 2 * T < _sms() else 1, max(1, tiles // 4), 32))
+        part = lse2 = None
+        if S > 1:
+            part = torch.empty(S, T, H, R, dtype=torch.float32, device=q.device)
+            lse2 = torch.empty(S, T, H, dtype=torch.float32, device=q.device)
+        _k._ck(lib.ne_mla_fp8_sparse(_k._p(q8), _k._p(cache), _c.c_int(cache.shape[0]), _k._p(sp), _c.c_int(topk), _c.c_int(T), _c.c_int(H),
+                                     _c.c_int(S), _c.c_float(scale), _k._p(out), _k._p(part), _k._p(lse2), _k._st()), "ne_mla_fp8_sparse")
+        if S > 1:
+            _k._ck(lib.ne_attn_merge(_k._p(part), _k._p(lse2), _k._p(out), _c.c_int(S), _c.c_longlong(T * H), _c.c_int(R), _c.c_int(R), _k._st()),
+                   "ne_attn_merge")
+        return out
     if fast:
         if q.dtype == FP8:
             q8 = q
