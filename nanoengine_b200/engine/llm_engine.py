@@ -48,6 +48,15 @@ def build_scheduler_config(config: Config, num_blocks: int, plan_bits: int) -> "
     return sc
 
 
+def _dummy_batch(is_prefill: bool):
+    """The batch an idle rank runs so that it joins every collective of the step: no sequences (the wire form wants the
+    offsets table of an empty batch, one zero), flagged so the worker substitutes one token on the scratch page."""
+    b = C.RunnerIn()
+    b.is_dummy, b.is_prefill = True, is_prefill
+    b.block_offsets = [0]
+    return b
+
+
 class LLMEngine:
     def __init__(self, config: Config, executor=None):
         self.config = config
@@ -138,9 +147,7 @@ class LLMEngine:
         if self.spmd:
             any_work, any_prefill = self.executor.agree(res.has_work, res.has_work and res.is_prefill)
             if any_work and not res.has_work:
-                dummy = C.RunnerIn()
-                dummy.is_dummy, dummy.is_prefill = True, any_prefill
-                self.executor.run_batches([dummy.to_bytes()])
+                self.executor.run_batches([_dummy_batch(any_prefill).to_bytes()])
                 return []
         if not res.has_work:
             return []
@@ -169,9 +176,7 @@ class LLMEngine:
                 if r < len(mbs):
                     wave.append(mbs[r].to_bytes())
                 else:
-                    dummy = C.RunnerIn()
-                    dummy.is_dummy, dummy.is_prefill = True, True
-                    wave.append(dummy.to_bytes())
+                    wave.append(_dummy_batch(True).to_bytes())
             waves.append(wave)
         results = self.executor.run_batches_pipelined(waves)
         merged = []

@@ -15,6 +15,7 @@ from . import sm100 as _k
 FP8 = torch.float8_e4m3fn
 _NUM_SMS = None
 _sample_calls = 0
+SPARSE_TC_CALLS = [0]        # launches of the sparse tensor-core MLA kernel (tests check that the DSA path really takes it)
 
 
 def _sms():
@@ -92,6 +93,7 @@ def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scal
             lse2 = torch.empty(S, T, H, dtype=torch.float32, device=q.device)
         _k._ck(lib.ne_mla_fp8_sparse(_k._p(q8), _k._p(cache), _c.c_int(cache.shape[0]), _k._p(sp), _c.c_int(topk), _c.c_int(T), _c.c_int(H),
                                      _c.c_int(S), _c.c_float(scale), _k._p(out), _k._p(part), _k._p(lse2), _k._st()), "ne_mla_fp8_sparse")
+        SPARSE_TC_CALLS[0] += 1
         if S > 1:
             _k._ck(lib.ne_attn_merge(_k._p(part), _k._p(lse2), _k._p(out), _c.c_int(S), _c.c_longlong(T * H), _c.c_int(R), _c.c_int(R), _k._st()),
                    "ne_attn_merge")

@@ -30,6 +30,61 @@ class TpLayout(_c.Structure):
                 ("rank", _c.c_int), ("world", _c.c_int), ("rows_per_rank", _c.c_int), ("H", _c.c_int)]
 
 
+class NvlsLayout(_c.Structure):
+    _fields_ = [("mc_base", _c.c_ulonglong), ("local_base", _c.c_ulonglong), ("off_buf", _c.c_longlong), ("off_out", _c.c_longlong),
+                ("off_flags", _c.c_longlong), ("rank", _c.c_int), ("world", _c.c_int), ("rows_cap", _c.c_int), ("H", _c.c_int)]
+
+
+class NvlsCollectives:
+    """All-reduce, reduce-scatter and all-gather of bf16 rows through the NVSwitch (multimem instructions over a multicast
+    mapping of a symmetric buffer; kernel in csrc/comm/nvls.cu).  Opt-in: needs NE_NVLS=1 in every rank's environment before
+    the first symmetric heap is created, and a fabric that offers a multicast object to the group - `available` says whether
+    both held.  One kernel per call, capturable in a CUDA graph, bounded waits."""
+
+    def __init__(self, group, hidden: int, max_rows: int, spin_limit: int = 1 << 22):
+        lib = _k.lib()
+        assert lib.ne_nvls_layout_size() == _c.sizeof(NvlsLayout), "NvlsLayout mismatch between Python and the kernel library"
+        import torch.distributed as dist
+        self.H, self.group = hidden, group
+        self.world = dist.get_world_size(group)
+        self.rows_cap = -(-max_rows // self.world) * self.world
+        self.spin_limit = spin_limit
+        nbytes = self.rows_cap * hidden * 2
+        self.heap = SymmetricHeap(2 * nbytes + 64 * 1024, group)
+        hp = self.heap
+        self.available = bool(hp.multicast_ptr)
+        self.b_flags = hp.alloc(64)
+        self.b_buf = hp.alloc(nbytes)
+        self.b_out = hp.alloc(nbytes)
+        L = NvlsLayout()
+        L.mc_base, L.local_base = hp.multicast_ptr, hp.peer_ptrs[hp.rank]
+        L.off_buf, L.off_out, L.off_flags = self.b_buf.offset, self.b_out.offset, self.b_flags.offset
+        L.rank, L.world, L.rows_cap, L.H = hp.rank, self.world, self.rows_cap, hidden
+        self.layout = L
+        self.state = torch.zeros(4, dtype=torch.int32, device=hp.device)
+        hp.barrier()
+
+    def _run(self, x: torch.Tensor, out: torch.Tensor, rows: int, mode: int):
+        if not self.available:
+            raise RuntimeError("no NVLink multicast object for this group (set NE_NVLS=1 on every rank; needs NVSwitch multicast support)")
+        _k._ck(_k.lib().ne_nvls_collective(_c.byref(self.layout), _k._p(x), _k._p(out), _c.c_int(rows), _c.c_int(mode), _k._p(self.state),
+                                           _c.c_int(self.spin_limit), _k._st()), "ne_nvls_collective")
+        return out
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        x = _k._as_bf16_2d(x).contiguous()
+        return self._run(x, torch.empty_like(x), x.shape[0], 0)
+
+    def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        x = _k._as_bf16_2d(x).contiguous()
+        assert x.shape[0] % self.world == 0
+        return self._run(x, torch.empty(x.shape[0] // self.world, self.H, dtype=torch.bfloat16, device=x.device), x.shape[0], 1)
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        x = _k._as_bf16_2d(x).contiguous()
+        return self._run(x, torch.empty(x.shape[0] * self.world, self.H, dtype=torch.bfloat16, device=x.device), x.shape[0], 2)
+
+
 class FusedTP:
     def __init__(self, group, axis: str, hidden: int, max_rows: int, spin_limit: int = 1 << 22):
         lib = _k.lib()
@@ -56,6 +111,12 @@ class FusedTP:
         self.state = torch.zeros(4, dtype=torch.int32, device=dev)        # [epoch, push / GEMM-tail / reduce CTA counters]
         self._comm_rs = None
         hp.barrier()
+        # in-switch variants of the stand-alone collectives, when the process opted in and the fabric offers multicast
+        import os
+        self.nvls = None
+        if os.environ.get("NE_NVLS", "0") == "1":
+            nv = NvlsCollectives(group, hidden, max_rows, spin_limit)
+            self.nvls = nv if nv.available else None
 
     # ---- helpers ----
     def _args(self):
@@ -134,6 +195,8 @@ class FusedTP:
     # ---- plain collectives ----
     def reduce_scatter(self, xp: torch.Tensor) -> torch.Tensor:
         """xp [world * rpr, H] partial sums -> this rank's [rpr, H] of the total."""
+        if self.nvls is not None and xp.shape[0] <= self.nvls.rows_cap:
+            return self.nvls.reduce_scatter(xp)
         lib = _k.lib()
         rows = xp.shape[0]
         assert rows % self.world == 0 and xp.shape[1] == self.H
@@ -148,6 +211,8 @@ class FusedTP:
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
         """x [rpr, H] on every rank -> [world * rpr, H] in a tensor of its own (copied out of the receive buffer by the
         waiting kernel, so the result does not depend on the parity of the call and stays valid for as long as it is held)."""
+        if self.nvls is not None and x.shape[0] * self.world <= self.nvls.rows_cap and x.shape[0] > 0:
+            return self.nvls.all_gather(x)
         lib = _k.lib()
         rpr = x.shape[0]
         assert x.shape[1] == self.H and rpr <= self.rpr_cap
@@ -160,6 +225,8 @@ class FusedTP:
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
+        if self.nvls is not None and 0 < T <= self.nvls.rows_cap:
+            return self.nvls.all_reduce(x)
         if 0 < T <= self.rpr_cap:
             # few rows: every rank stores its partial into every peer's stage and adds the slots itself (one hop)
             lib = _k.lib()

@@ -35,9 +35,11 @@ class SymmetricHeap:
 
     def __init__(self, nbytes: int, group=None, device=None):
         import os
-        # This package only issues plain peer loads / stores, never multimem instructions, so the heap is not bound to an
-        # NVLink multicast object: a rank that goes away while bound to one disturbs the GPUs of the ranks that stay.
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        # By default the heap is not bound to an NVLink multicast object (the kernels then use plain peer loads / stores): a
+        # rank that goes away while bound to one disturbs the GPUs of the ranks that stay.  NE_NVLS=1 opts in to the binding
+        # for the in-switch (multimem) collectives; the choice is per process and must be the same on every rank.
+        if os.environ.get("NE_NVLS", "0") != "1":
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())

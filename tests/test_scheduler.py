@@ -422,3 +422,11 @@ def test_import_holds_the_cached_head_of_its_chain():
     m, last = p.match_prefix([1, 2, 3, 4, 5, 6, 7, 8, 0])
     assert len(m) == 2 and last == h[1]
     p.release(spare)
+
+
+def test_dummy_batch_of_an_idle_rank_survives_the_wire():
+    """An idle SPMD rank runs a dummy batch through the same bytes path as a real one: it must parse."""
+    from nanoengine_b200.engine.llm_engine import _dummy_batch
+    for prefill in (False, True):
+        b = C.RunnerIn.from_bytes(_dummy_batch(prefill).to_bytes())
+        assert b.is_dummy and b.is_prefill == prefill and b.num_seqs == 0
