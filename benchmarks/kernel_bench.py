@@ -6,7 +6,7 @@
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, a buffer larger than L2 is rewritten between timed
 runs, the median of `--iters` runs is reported.  Fractions are against MEASURED_PEAKS.json (copy bandwidth and cuBLAS
-bf16 throughput of this pool's B200s) when that file exists, otherwise against the documented fallback figures.
+bf16 throughput of the machine's B200s) when that file exists, otherwise against the documented fallback figures.
 """
 from __future__ import annotations
 
@@ -115,6 +115,56 @@ def case_mla(B, ctx, H=128, q_len=1):
     cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
     fn = lambda: sm100_attn.mla_attention_paged(q, cache, bt, cu, cl, 0.07, 512)
     return fn, B * ctx * 576 + B * q_len * H * (576 + 512) * 2, 2.0 * B * q_len * H * ctx * (576 + 512)
+
+
+def case_mla_sparse(B, ctx, topk=2048, H=128):
+    """DSA decode attention: every token attends `topk` rows of its own ~ctx-token context, picked at random."""
+    bs = 64
+    nb = (ctx + bs - 1) // bs
+    cache = rand_fp8(B * nb + 1, bs, 576)
+    q = (torch.randn(B, H, 576, device="cuda") * 0.3).to(torch.bfloat16)
+    bt = torch.arange(B * nb, device="cuda", dtype=torch.int32).view(B, nb)
+    cu = torch.arange(B + 1, device="cuda", dtype=torch.int32)
+    cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    sp = torch.stack([torch.randperm(ctx, device="cuda")[:topk] + b * nb * bs for b in range(B)]).to(torch.int32)
+    fn = lambda: sm100_attn.mla_attention_paged(q, cache, bt, cu, cl, 0.07, 512, sparse_indices=sp)
+    return fn, B * topk * 576 + B * H * (576 + 512) * 2, 2.0 * B * H * topk * (576 + 512)
+
+
+# ---- the same shapes through the libraries the reference calls on Blackwell (bars, not product paths) ----
+def bar_mla_flashinfer(B, ctx, H=128):
+    """flashinfer's TRTLLM-GEN MLA decode, the kernel the reference selects on sm_100 (layers/backends/mla/trtllm.py:45-204)."""
+    from flashinfer.mla import trtllm_batch_decode_with_kv_cache_mla
+    bs = 64
+    nb = (ctx + bs - 1) // bs
+    cache = rand_fp8(B * nb + 1, 1, bs, 576)
+    bt = torch.arange(B * nb, device="cuda", dtype=torch.int32).view(B, nb)
+    q = (torch.randn(B, 1, H, 576, device="cuda") * 0.3).to(FP8)
+    sl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    ws = torch.zeros(128 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: trtllm_batch_decode_with_kv_cache_mla(q, cache, ws, 128, 512, 64, bt, sl, ctx, bmm1_scale=0.07, bmm2_scale=1.0)
+    return fn, B * ctx * 576 + B * H * (576 + 512) * 2, 2.0 * B * H * ctx * (576 + 512)
+
+
+def bar_gqa_flashinfer(B, ctx, Hq, Hkv, D=128, bs=64):
+    """flashinfer's TRTLLM-GEN GQA decode (reference layers/backends/attention/fa4.py:100-149)."""
+    from flashinfer.decode import trtllm_batch_decode_with_kv_cache
+    nb = (ctx + bs - 1) // bs
+    kv = torch.randn(B * nb + 1, 2, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+    bt = torch.arange(B * nb, device="cuda", dtype=torch.int32).view(B, nb)
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    sl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    ws = torch.zeros(128 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: trtllm_batch_decode_with_kv_cache(q, kv, ws, bt, sl, ctx, bmm1_scale=D ** -0.5, bmm2_scale=1.0, kv_layout="HND")
+    return fn, B * ctx * Hkv * D * 4 + B * Hq * D * 4, 4.0 * B * Hq * ctx * D
+
+
+def bar_matmul_bf16(M, N, K):
+    """torch.matmul (cuBLAS) on bf16 operands of the same M, N, K."""
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    fn = lambda: torch.nn.functional.linear(x, w)
+    return fn, N * K * 2 + M * (K + N) * 2, 2.0 * M * N * K
 
 
 def case_silu_masked(E=32, rows=32, cap=512, I=2048):
@@ -273,6 +323,14 @@ def build_cases(args):
         "gdn_verify2": lambda: case_gdn(128, q_len=2),
         "mla_decode": lambda: case_mla(128, args.ctx),
         "mla_decode_small_batch": lambda: case_mla(8, 8192),
+        "mla_sparse_decode_2048": lambda: case_mla_sparse(128, 8192),
+        "mla_sparse_decode_64k": lambda: case_mla_sparse(64, 65536),
+        # library bars at the same shapes (what the reference runs on this hardware); "unavailable" when the import or call fails
+        "bar:mla_decode_flashinfer": lambda: bar_mla_flashinfer(128, args.ctx),
+        "bar:gqa_decode_tp8_flashinfer": lambda: bar_gqa_flashinfer(256, 4352, 8, 1),
+        "bar:qkv_a_like_bf16_cublas": lambda: bar_matmul_bf16(128, 2112, 3584),
+        "bar:o_proj_like_bf16_cublas": lambda: bar_matmul_bf16(128, 7168, 8192),
+        "bar:bf16_square_cublas": lambda: bar_matmul_bf16(8192, 8192, 8192),
         # prefill, 16384 tokens
         "qkv_a_prefill": lambda: case_dense_fp8(args.prefill_tokens, 2112, 7168),
         "o_proj_prefill": lambda: case_dense_fp8(args.prefill_tokens, 7168, 16384),
@@ -298,6 +356,17 @@ def main():
     names = list(cases) if args.case == "all" else args.case.split(",")
     print(f"{'case':26s} {'time_us':>10s} {'GB/s':>9s} {'frac_bw':>8s} {'TFLOP/s':>9s} {'frac_bf16':>9s}   (fractions of {src} peaks)")
     for n in names:
+        if n.startswith("bar:"):
+            try:
+                fn, nbytes, flops = cases[n]()
+                t = timeit(fn, args.iters, args.graph)
+            except Exception as e:                 # a library that does not import or does not take this shape here
+                print(f"{n:26s} unavailable: {type(e).__name__}: {str(e).splitlines()[0][:120] if str(e) else ''}")
+                continue
+            print(f"{n:26s} {t * 1e6:10.1f} {nbytes / t / 1e9:9.0f} {nbytes / t / bw:8.2f} {flops / t / 1e12:9.1f} {flops / t / fl:9.2f}")
+            del fn
+            torch.cuda.empty_cache()
+            continue
         fn, nbytes, flops = cases[n]()
         t = timeit(fn, args.iters, args.graph)
         print(f"{n:26s} {t * 1e6:10.1f} {nbytes / t / 1e9:9.0f} {nbytes / t / bw:8.2f} {flops / t / 1e12:9.1f} {flops / t / fl:9.2f}")
