@@ -69,6 +69,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="deepseek-v3", choices=["deepseek-v3", "qwen3-235b"],
+                    help="deepseek-v3: the headline (fp8, attention-DP + EP); qwen3-235b: bf16 GQA MoE with tensor-parallel attention + EP "
+                         "(the batch is shared by the TP ranks: --seqs-per-gpu is then the size of the whole batch)")
     ap.add_argument("--seqs-per-gpu", type=int, default=128)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=61, help="debug only: anything but 61 marks the result invalid")
@@ -98,15 +101,24 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
 
-    mc = deepseek_v3(n_routed_experts=args.experts_per_gpu * N, num_hidden_layers=args.layers, num_nextn_predict_layers=1 if args.mtp else 0)
+    qwen = args.model == "qwen3-235b"
+    if qwen:
+        from nanoengine_b200.models.config import qwen3_235b
+        if args.experts_per_gpu == 32:
+            args.experts_per_gpu = 16                    # 128 experts over 8 GPUs
+        if args.layers == 61:
+            args.layers = 94
+        mc = qwen3_235b(n_routed_experts=args.experts_per_gpu * N, num_hidden_layers=args.layers)
+    else:
+        mc = deepseek_v3(n_routed_experts=args.experts_per_gpu * N, num_hidden_layers=args.layers, num_nextn_predict_layers=1 if args.mtp else 0)
     S, P = args.seqs_per_gpu, args.prompt_len
     per_step = (args.force_accept + 1) if (args.mtp and args.force_accept >= 0) else 1
     total_new = (args.warmup + args.steps + 8) * per_step + 2 * args.mtp
     pages = (P + total_new + 63) // 64 + 1
-    cfg = Config(model="deepseek-v3", model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kv_cache_dtype="fp8",
+    cfg = Config(model=args.model, model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kv_cache_dtype="bfloat16" if qwen else "fp8",
                  max_num_seqs=S, max_num_batched_tokens=16384, max_model_len=P + total_new + 64, num_kvcache_blocks=S * pages + 16,
-                 attention_dp=N, ffn_ep=N, executor_backend="spmd", enable_prefix_caching=False, cuda_graph_max_bs=S, seed=rank,
-                 num_speculative_tokens=args.mtp)
+                 attention_dp=1 if qwen else N, attention_tp=N if qwen else 1, ffn_ep=N, executor_backend="spmd", enable_prefix_caching=False,
+                 cuda_graph_max_bs=S, seed=0 if qwen else rank, num_speculative_tokens=args.mtp)
     t_build = time.time()
     llm = LLM(cfg)
     runner = llm.engine.executor.runner
@@ -114,7 +126,7 @@ def main():
         runner.mtp_runner.force_accept = args.force_accept
     build_s = time.time() - t_build
 
-    g = torch.Generator().manual_seed(1234 + rank)
+    g = torch.Generator().manual_seed(1234 + (0 if qwen else rank))        # tensor-parallel ranks serve the same requests
     sp = SamplingParams(temperature=0.0, max_tokens=total_new, ignore_eos=True)
     for i in range(S):
         llm.add_request(torch.randint(0, mc.vocab_size, (P,), generator=g).tolist(), sp)
@@ -202,21 +214,25 @@ def main():
     th.join(timeout=2)
 
     if rank == 0:
-        tokens_per_step = S * N * per_step
+        tokens_per_step = S * (1 if qwen else N) * per_step
         value = tokens_per_step / (dev_ms * 1e-3)
         out = {
             "metric": "decode out tok/s (whole job; per-GPU = value / n_gpus) at TPOT = ms_per_step; prefill tok/s beside it",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": N, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms, 3), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None if BASELINE_VALUE is None else value / BASELINE_VALUE, "dtype": "fp8 weights + fp8 KV, bf16 activations",
+            "vs_baseline": None if BASELINE_VALUE is None else value / BASELINE_VALUE,
+            "dtype": "bf16" if qwen else "fp8 weights + fp8 KV, bf16 activations",
             "data": "synthetic uniform-random token ids, random-init weights (HF layout)",
-            "config": {"model": f"DeepSeek-V3 shape: {args.layers} layers, hidden 7168, 128 MLA heads, {args.experts_per_gpu * N} routed experts "
-                                f"({args.experts_per_gpu}/GPU) top-8, 1 shared", "global_batch": tokens_per_step, "seq_len": P,
-                       "parallelism": f"dp{N} attention + ep{N} experts", "l2": "inputs (weights ~100 GB/step) exceed L2; no flush",
-                       "valid": args.layers == 61 and args.experts_per_gpu == 32 and S == 128},
+            "config": {"model": (f"Qwen3-235B-A22B shape: {args.layers} layers, hidden 4096, 64/4 GQA heads, {args.experts_per_gpu * N} experts "
+                                 f"({args.experts_per_gpu}/GPU) top-8, bf16") if qwen else
+                                (f"DeepSeek-V3 shape: {args.layers} layers, hidden 7168, 128 MLA heads, {args.experts_per_gpu * N} routed experts "
+                                 f"({args.experts_per_gpu}/GPU) top-8, 1 shared"), "global_batch": tokens_per_step, "seq_len": P,
+                       "parallelism": f"tp{N} attention + ep{N} experts" if qwen else f"dp{N} attention + ep{N} experts",
+                       "l2": "inputs (the weights streamed every step) exceed L2; no flush",
+                       "valid": (args.layers == 94 and args.experts_per_gpu == 16) if qwen else (args.layers == 61 and args.experts_per_gpu == 32 and S == 128)},
             "decode_tok_s_per_gpu": round(value / N, 1), "tpot_ms": round(dev_ms, 3), "tpot_slo_50ms_met": dev_ms <= 50.0,
-            "prefill_tok_s": round(prefill_tok * N / (prefill_ms * 1e-3), 1) if prefill_ms > 0 else None,
-            "prefill_tok_s_per_gpu": round(prefill_tok / (prefill_ms * 1e-3), 1) if prefill_ms > 0 else None,
+            "prefill_tok_s": round(prefill_tok * (1 if qwen else N) / (prefill_ms * 1e-3), 1) if prefill_ms > 0 else None,
+            "prefill_tok_s_per_gpu": round(prefill_tok / (N if qwen else 1) / (prefill_ms * 1e-3), 1) if prefill_ms > 0 else None,
             "e2e": {"value": round(tokens_per_step / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 3),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches * args.steps), "launches_per_step": int(launches),

@@ -122,11 +122,19 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
         for (int p = 0; p < 4; p++) tma_load_2d(smem_u32(sQ + p * 128 * 128), &tq128, b_qfull, p * 128, qrow);
         tma_load_2d(smem_u32(sQ + kQNope), &tq64, b_qfull, 512, qrow);
       }
-      // One cp.async group per iteration (empty once the tiles run out), so "all but the newest kPgStages - 1 groups have
-      // landed" identifies tile i - (kPgStages - 1): it is fenced for the tensor-core proxy and handed over, which keeps two
-      // tiles in flight behind the one being consumed.
+      // One cp.async group per iteration (empty once the tiles run out).  At the top of iteration i the groups 0 .. i-1 are
+      // committed, so "all but the newest one have landed" means tile i-2 is complete: it is fenced for the tensor-core proxy
+      // and handed over BEFORE this warp blocks on the slot tile i goes into - that slot is freed by the product that runs
+      // after the scores of tile i-2, so handing over after the wait would deadlock.  Two tiles stay in flight behind the
+      // one being consumed.
       bool ok = true;
-      for (int i = 0; i < n_tiles + kPgStages - 1; i++) {
+      for (int i = 0; i < n_tiles + 2; i++) {
+        const int j = i - 2;
+        if (j >= 0 && j < n_tiles) {
+          cp_async_wait<1>();
+          fence_proxy_async_smem();
+          mbar_arrive(b_pgfull + 8 * (j % kPgStages));
+        }
         if (i < n_tiles && ok) {
           const int s = i % kPgStages;
           if (!mbar_wait(b_pgempty + 8 * s, ((i / kPgStages) & 1) ^ 1, abort_flag, kKernelMla, 100 + s)) ok = false;
@@ -148,12 +156,6 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
           }
         }
         cp_async_commit();
-        const int j = i - (kPgStages - 1);
-        if (j >= 0) {
-          cp_async_wait<kPgStages - 1>();
-          fence_proxy_async_smem();
-          mbar_arrive(b_pgfull + 8 * (j % kPgStages));
-        }
       }
       cp_async_wait<0>();
     }
