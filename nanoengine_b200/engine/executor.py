@@ -39,6 +39,9 @@ class InprocExecutor:
     def collective_rpc(self, method: str, *args, **kw) -> List[Any]:
         return [getattr(self.runner, method)(*args, **kw)]
 
+    def rank_rpc(self, method: str, per_rank_arg: Sequence[Any]) -> List[Any]:
+        return [getattr(self.runner, method)(per_rank_arg[0])]
+
     def run_batches(self, blobs: Sequence[bytes]) -> List[bytes]:
         return [self.runner.run_from_bytes(blobs[0])]
 
@@ -139,6 +142,12 @@ class MultiprocExecutor:
     def collective_rpc(self, method: str, *args, **kw) -> List[Any]:
         for r in range(self.world_size):
             self._send(r, (method, args, kw))
+        return [self._recv(r) for r in range(self.world_size)]
+
+    def rank_rpc(self, method: str, per_rank_arg: Sequence[Any]) -> List[Any]:
+        """Like collective_rpc, with a different single argument for every worker."""
+        for r in range(self.world_size):
+            self._send(r, (method, (per_rank_arg[r],), {}))
         return [self._recv(r) for r in range(self.world_size)]
 
     def _batch_index(self, rank: int) -> int:

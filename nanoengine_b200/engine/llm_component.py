@@ -69,6 +69,12 @@ class LLM:
     def update_weights(self, src):
         return self.engine.update_weights(src)
 
+    def export_weights(self, direct: bool = False):
+        return self.engine.export_weights(direct)
+
+    def pull_weights(self, per_worker):
+        return self.engine.pull_weights(per_worker)
+
     def metrics(self) -> str:
         return self.engine.metrics_prometheus()
 

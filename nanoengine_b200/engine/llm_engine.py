@@ -222,6 +222,21 @@ class LLMEngine:
         self.scheduler.reset_prefix_cache()      # cached KV was computed with the old weights
         return n
 
+    def export_weights(self, direct: bool = False) -> List[Dict]:
+        """Per-worker descriptors of the weights this engine serves (see ModelRunner.export_weights)."""
+        return self.executor.collective_rpc("export_weights", direct)
+
+    def pull_weights(self, per_worker: List[Dict]) -> int:
+        """Live update from a peer engine with the same layout: worker i copies the tensors of the peer's worker i."""
+        if len(per_worker) != self.executor.world_size:
+            raise ValueError("the peer engine has a different number of workers")
+        if self.executor.world_size == 1:
+            n = self.executor.collective_rpc("pull_weights", per_worker[0])[0]
+        else:
+            n = min(self.executor.rank_rpc("pull_weights", per_worker))
+        self.scheduler.reset_prefix_cache()
+        return n
+
     def metrics_prometheus(self) -> str:
         return self.scheduler.metrics_prometheus()
 

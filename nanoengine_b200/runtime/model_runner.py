@@ -148,6 +148,10 @@ class ModelRunner:
         keep = expert_owner_filter(self.mc, self.dist.ep_size, self.dist.ep_rank, None)
         it = iterate_safetensors(src, keep, self.device) if isinstance(src, str) else ((n, t) for n, t in src if keep(n))
         n = self.load_weights(it)
+        self._after_weight_change()
+        return n
+
+    def _after_weight_change(self) -> None:
         for m in list(self.model.modules()) + (list(self.mtp.modules()) if self.mtp is not None else []):
             if hasattr(m, "refresh_absorbed"):
                 m.refresh_absorbed()
@@ -157,6 +161,58 @@ class ModelRunner:
             self.graphs = type(self.graphs)(self)
             if self.has_collectives():
                 self.graphs.capture_all()
+
+    def export_weights(self, direct: bool = False) -> Dict[str, object]:
+        """Descriptors of every parameter and buffer of this worker's shard, from which a worker process on the same machine
+        (a serving replica with the same parallel layout and rank) can map the tensors and copy them over NVLink.  `direct`:
+        the tensors themselves, for a replica in this process.
+        Parity: reference runtime/context/parameter.py:91-140 (named regions registered for one-sided weight reads)."""
+        from ..parallel.kv_transfer import export_tensor
+        out = {}
+        mods = [("", self.model)] + ([("mtp.", self.mtp)] if self.mtp is not None else [])
+        for prefix, mod in mods:
+            for n, p in list(mod.named_parameters()) + list(mod.named_buffers()):
+                t = p.detach()
+                if direct or not t.is_cuda:
+                    out[prefix + n] = t
+                else:
+                    flat = (t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).contiguous().view(-1).view(torch.uint8)
+                    assert flat.data_ptr() == t.data_ptr(), f"{n}: parameters must be contiguous to be exported"
+                    out[prefix + n] = {"desc": export_tensor(flat, False), "dtype": str(t.dtype), "shape": list(t.shape)}
+        return out
+
+    def pull_weights(self, peer: Dict[str, object]) -> int:
+        """Copy every tensor of `peer` (another worker's `export_weights()`) into this worker's parameters in place - one
+        device-to-device copy per tensor, over NVLink when the peer sits on another GPU - then rebuild what is derived from
+        the weights.  Names and shapes must match (same model, same parallel layout, same rank).
+        Parity: reference runtime/context/parameter.py:169-228 (pull + in-place apply), engine/weight_sync.py."""
+        from ..parallel.kv_transfer import open_tensor
+        mine = {}
+        mods = [("", self.model)] + ([("mtp.", self.mtp)] if self.mtp is not None else [])
+        for prefix, mod in mods:
+            for n, p in list(mod.named_parameters()) + list(mod.named_buffers()):
+                mine[prefix + n] = p
+        missing = sorted(set(mine) - set(peer))
+        if missing:
+            raise ValueError(f"the peer does not hold {len(missing)} of this worker's tensors, e.g. {missing[:3]}")
+        n = 0
+        with torch.no_grad():
+            for name, dst in mine.items():
+                src = peer[name]
+                if isinstance(src, dict):
+                    if list(dst.shape) != src["shape"] or str(dst.dtype) != src["dtype"]:
+                        raise ValueError(f"{name}: peer has {src['dtype']} {src['shape']}, this worker {dst.dtype} {list(dst.shape)}")
+                    raw = open_tensor(src["desc"])
+                    d8 = (dst.view(torch.uint8) if dst.dtype == torch.float8_e4m3fn else dst).view(-1).view(torch.uint8)
+                    d8.copy_(raw, non_blocking=True)
+                else:
+                    if dst.shape != src.shape or dst.dtype != src.dtype:
+                        raise ValueError(f"{name}: peer has {src.dtype} {list(src.shape)}, this worker {dst.dtype} {list(dst.shape)}")
+                    dst.copy_(src, non_blocking=True)
+                n += 1
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self._after_weight_change()
         return n
 
     # ---- cache -------------------------------------------------------------------------------

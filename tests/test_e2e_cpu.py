@@ -85,3 +85,26 @@ def test_sampling_temperature_is_seeded_and_logprobs_are_returned():
     a = _make().generate([p], sp)[0]
     b = _make().generate([p], sp)[0]
     assert a["token_ids"] == b["token_ids"] and len(a["logprobs"]) == 6 and all(x <= 0 for x in a["logprobs"])
+
+
+def test_weights_pulled_from_a_peer_engine_replace_the_local_ones():
+    """Live weight update from a serving replica: after the pull the engine generates what the peer generates, its prefix
+    cache is empty, and a shape mismatch is refused before anything is copied."""
+    import torch
+    from nanoengine_b200 import Config, LLM, SamplingParams
+    base = dict(model="tiny-deepseek-v3", dtype="float32", device="cpu", kvcache_block_size=16, max_num_seqs=4, num_kvcache_blocks=32)
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (18, 40)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    a, b = LLM(Config(**base, seed=0)), LLM(Config(**base, seed=7))
+    want = [o["token_ids"] for o in a.generate(prompts, sp)]
+    before = [o["token_ids"] for o in b.generate(prompts, sp)]
+    assert before != want
+    n = b.pull_weights(a.export_weights(direct=True))
+    assert n > 20 and b.engine.scheduler.num_cached_blocks(0) == 0
+    assert [o["token_ids"] for o in b.generate(prompts, sp)] == want
+    bad = a.export_weights(direct=True)
+    bad[0] = {k: (v[:1] if k.endswith("lm_head.weight") else v) for k, v in bad[0].items()}
+    import pytest
+    with pytest.raises(ValueError):
+        b.pull_weights(bad)
