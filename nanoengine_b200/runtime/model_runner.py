@@ -25,6 +25,7 @@ from ..parallel.dist import DistContext, ParallelSpec, get_dist_context, init_di
 from .cache import KVCache, kv_budget_blocks, make_cache_plan, torch_dtype
 from .context import ForwardContext
 from .sampler import Sampler
+from ..utils import nvtx
 
 
 class StepTimer:
@@ -515,12 +516,14 @@ class ModelRunner:
             self.cache.swap(list(b.swap_in_src), list(b.swap_in_dst), to_host=False)
         self.timer.stop()
         self.timer.start("prepare")
-        ctx = self.prepare(b)
+        with nvtx.range("step/prepare"):
+            ctx = self.prepare(b)
         self.timer.stop()
         if self.mtp_runner is not None and not ctx.is_dummy:
             return self.mtp_runner.run(b, ctx)
         self.timer.forward_begin()
-        hidden = self.forward(ctx)
+        with nvtx.range("step/prefill_forward" if ctx.is_prefill else "step/decode_forward"):
+            hidden = self.forward(ctx)
         if hidden is None:                      # an inner pipeline stage: nothing to sample here
             self.timer.forward_end()
             return C.RunnerOut([], [])
@@ -536,12 +539,14 @@ class ModelRunner:
         rows = ctx.last_token_indices.long()
         if not mask.all():
             rows = rows[torch.from_numpy(mask).to(rows.device)]
-        logits = self.model.compute_logits(hidden[rows])
-        temps = self._to_dev(np.asarray([t for t, m in zip(b.temperatures, mask) if m], dtype=np.float32))
-        tok, lp = self.sampler(logits, temps, b.any_return_logprobs)
+        with nvtx.range("step/lm_head_sample"):
+            logits = self.model.compute_logits(hidden[rows])
+            temps = self._to_dev(np.asarray([t for t, m in zip(b.temperatures, mask) if m], dtype=np.float32))
+            tok, lp = self.sampler(logits, temps, b.any_return_logprobs)
         self.timer.forward_end()
         self.timer.start("d2h")
-        toks = tok.tolist()
+        with nvtx.range("step/copy_back"):
+            toks = tok.tolist()
         lps = lp.tolist() if lp is not None else None
         self.d2h_bytes += tok.numel() * tok.element_size() + (lp.numel() * 4 if lp is not None else 0)
         self.timer.stop()

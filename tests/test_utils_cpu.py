@@ -97,3 +97,36 @@ def test_graph_branch_lanes_are_folded(tmp_path):
     kernels = [e for e in out if e.get("ph") == "X"]
     assert len(kernels) == 16 and {e["tid"] for e in kernels} == {7, 12}
     assert sum(1 for e in out if e.get("ph") == "M") == 2
+
+
+def test_trace_compactor_folds_short_repeats_and_drops_python_frames(tmp_path):
+    import json
+    from nanoengine_b200.utils.trace_compactor import compact_events, compact_file
+    ev = [{"ph": "X", "cat": "python_function", "name": "f", "pid": 1, "tid": 1, "ts": 0, "dur": 100}]
+    ev += [{"ph": "X", "cat": "kernel", "name": "tiny", "pid": 1, "tid": 7, "ts": 10 + 3 * i, "dur": 2} for i in range(50)]
+    ev += [{"ph": "X", "cat": "kernel", "name": "gemm", "pid": 1, "tid": 7, "ts": 200, "dur": 80},
+           {"ph": "X", "cat": "kernel", "name": "tiny", "pid": 1, "tid": 7, "ts": 300, "dur": 2},
+           {"ph": "s", "cat": "ac2g", "name": "flow", "pid": 1, "tid": 1, "ts": 5},
+           {"ph": "M", "name": "process_name", "pid": 1, "args": {"name": "rank0"}}]
+    out = list(compact_events(ev))
+    names = [(e["name"], e.get("args", {}).get("count", 1)) for e in out if e.get("ph") == "X"]
+    assert ("tiny", 50) in names and ("gemm", 1) in names and ("tiny", 1) in names and not any(n == "f" for n, _ in names)
+    folded = next(e for e in out if e.get("args", {}).get("count") == 50)
+    assert folded["ts"] == 10 and folded["ts"] + folded["dur"] == 10 + 3 * 49 + 2
+    assert any(e.get("ph") == "M" for e in out)
+    src, dst = tmp_path / "t.json", tmp_path / "c.json"
+    src.write_text(json.dumps({"traceEvents": ev, "displayTimeUnit": "ms"}))
+    st = compact_file(str(src), str(dst))
+    assert st["events_in"] == len(ev) and st["events_out"] == len(out)
+    assert json.loads(dst.read_text())["displayTimeUnit"] == "ms"
+
+
+def test_nvtx_ranges_are_free_when_off_and_harmless_without_a_gpu():
+    from nanoengine_b200.utils import nvtx
+    assert not nvtx.enabled()
+    with nvtx.range("x"):
+        pass
+    nvtx.enable(True)
+    with nvtx.range("y"):
+        pass
+    nvtx.enable(False)
