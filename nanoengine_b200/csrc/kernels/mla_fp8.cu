@@ -28,6 +28,7 @@
 namespace ne {
 
 constexpr int kMlaThreads = 192;
+constexpr int kMlaSparseThreads = 288;        // + three more gather warps
 constexpr int kKernelMla = 2;
 constexpr int kPage = 64, kDk = 576, kDv = 512, kVHalf = 256;
 constexpr int kQNope = 4 * 128 * 128;          // four 128-byte-wide panels of 128 rows
@@ -57,7 +58,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <bool kSparse>
-__global__ void __launch_bounds__(kMlaThreads, 1)
+__global__ void __launch_bounds__(kSparse ? kMlaSparseThreads : kMlaThreads, 1)
 mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant__ CUtensorMap tq64,
                const __grid_constant__ CUtensorMap tk128, const __grid_constant__ CUtensorMap tk64, const MlaArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -78,7 +79,7 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
-    for (int i = 0; i < kPgStages; i++) { mbar_init(b_pgfull + 8 * i, kSparse ? 32 : 1); mbar_init(b_pgempty + 8 * i, 1); }
+    for (int i = 0; i < kPgStages; i++) { mbar_init(b_pgfull + 8 * i, kSparse ? 128 : 1); mbar_init(b_pgempty + 8 * i, 1); }
     for (int i = 0; i < 2; i++) { mbar_init(b_sfull + 8 * i, 1); mbar_init(b_sempty + 8 * i, 4); }
     for (int i = 0; i < 2; i++) { mbar_init(b_pfull + 8 * i, 4); mbar_init(b_pempty + 8 * i, 1); }
     *abort_flag = 0;
@@ -113,20 +114,33 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 128;
 
-  if (warp == 0 && kSparse) {
+  if (kSparse && (warp == 0 || warp >= 6)) {
+    // Four gather warps (0, 6, 7, 8); each owns 16 of the 64 listed rows of every tile.  A row's 512 latent bytes are one
+    // warp-wide cp.async (lane = 16-byte chunk, fully coalesced); the 64 rope bytes of 8 rows share another.  Destinations
+    // follow the 128-byte / 64-byte swizzle the tensor-core descriptors expect.
     if (n_tiles > 0) {
       const int lane = (int)lane_id();
-      if (lane == 0) {
+      const int pw = warp == 0 ? 0 : warp - 5;
+      const int r_lo = pw * 16;
+      if (warp == 0 && lane == 0) {
         const int qrow = t * a.H;
         mbar_expect_tx(b_qfull, kQBytes);
         for (int p = 0; p < 4; p++) tma_load_2d(smem_u32(sQ + p * 128 * 128), &tq128, b_qfull, p * 128, qrow);
         tma_load_2d(smem_u32(sQ + kQNope), &tq64, b_qfull, 512, qrow);
       }
+      // listed row id of row r_lo + (lane & 15) of tile i; anything that is not a cache row becomes -1 (zero-filled, never read)
+      auto load_id = [&](int i) -> int {
+        const int k = (pg_begin + i) * kPage + r_lo + (lane & 15);
+        int id = -1;
+        if (i < n_tiles && k < a.topk) id = ids[k];
+        return (id >= 0 && (long long)id < a.cache_rows) ? id : -1;
+      };
+      int id_next = load_id(0);
       // One cp.async group per iteration (empty once the tiles run out).  At the top of iteration i the groups 0 .. i-1 are
-      // committed, so "all but the newest one have landed" means tile i-2 is complete: it is fenced for the tensor-core proxy
-      // and handed over BEFORE this warp blocks on the slot tile i goes into - that slot is freed by the product that runs
-      // after the scores of tile i-2, so handing over after the wait would deadlock.  Two tiles stay in flight behind the
-      // one being consumed.
+      // committed, so "all but the newest one have landed" means this lane's part of tile i-2 is complete: it is fenced for
+      // the tensor-core proxy and handed over BEFORE the warp blocks on the slot tile i goes into - that slot is freed by the
+      // product that runs after the scores of tile i-2, so handing over after the wait would deadlock.  Two tiles stay in
+      // flight behind the one being consumed, and the ids of tile i+1 are fetched while tile i is issued.
       bool ok = true;
       for (int i = 0; i < n_tiles + 2; i++) {
         const int j = i - 2;
@@ -137,21 +151,28 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
         }
         if (i < n_tiles && ok) {
           const int s = i % kPgStages;
-          if (!mbar_wait(b_pgempty + 8 * s, ((i / kPgStages) & 1) ^ 1, abort_flag, kKernelMla, 100 + s)) ok = false;
+          ok = mbar_wait(b_pgempty + 8 * s, ((i / kPgStages) & 1) ^ 1, abort_flag, kKernelMla, 100 + s);
+          ok = __all_sync(0xffffffffu, ok);
           if (ok) {
-            const int k0 = (pg_begin + i) * kPage;
-            const int id_lo = k0 + lane < a.topk ? ids[k0 + lane] : -1, id_hi = k0 + 32 + lane < a.topk ? ids[k0 + 32 + lane] : -1;
+            const int my_id = id_next;
+            id_next = load_id(i + 1);
             const uint32_t dst = smem_u32(sPg + s * kPgBytes);
-#pragma unroll 4
-            for (int c = lane; c < kPage * (kDk / 16); c += 32) {
-              const int row = c / (kDk / 16), ch = c - row * (kDk / 16);            // 36 chunks of 16 bytes per row
-              const int a_lo = __shfl_sync(0xffffffffu, id_lo, row & 31), a_hi = __shfl_sync(0xffffffffu, id_hi, row & 31);
-              const int id = row < 32 ? a_lo : a_hi;
-              const bool valid = id >= 0 && (long long)id < a.cache_rows;          // anything else is zero-filled, never dereferenced
-              const uint8_t* src = a.cache + (valid ? (long long)id * kDk + ch * 16 : 0);
-              const uint32_t d = ch < 32 ? dst + (ch >> 3) * (kPage * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4)
-                                         : dst + kPgNope + row * 64 + (((ch - 32) ^ ((row >> 1) & 3)) << 4);
-              cp_async16(d, src, valid ? 16u : 0u);
+            const uint32_t d_nope = dst + (lane >> 3) * (kPage * 128);
+            const uint8_t* src_nope = a.cache + lane * 16;
+#pragma unroll
+            for (int r = 0; r < 16; r++) {
+              const int row = r_lo + r;
+              const int id = __shfl_sync(0xffffffffu, my_id, r);
+              const bool valid = id >= 0;
+              cp_async16(d_nope + row * 128 + (((lane & 7) ^ (row & 7)) << 4), src_nope + (valid ? (long long)id * kDk : 0), valid ? 16u : 0u);
+            }
+#pragma unroll
+            for (int it = 0; it < 2; it++) {
+              const int rr = it * 8 + (lane >> 2), row = r_lo + rr, ch = lane & 3;
+              const int id = __shfl_sync(0xffffffffu, my_id, rr);
+              const bool valid = id >= 0;
+              cp_async16(dst + kPgNope + row * 64 + ((ch ^ ((row >> 1) & 3)) << 4),
+                         a.cache + (valid ? (long long)id * kDk + kDv + ch * 16 : 0), valid ? 16u : 0u);
             }
           }
         }
@@ -239,6 +260,14 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
     bool s_ready = false;                            // early test of the next page's S buffer (see below)
     for (int i = 0; ok && i < n_tiles; i++) {
       const int sb = i & 1;
+      const int key0 = (pg_begin + i) * kPage;
+      bool in_lo = true, in_hi = true;               // sparse: is the listed row a cache row (fetched before the wait, used after)
+      if (kSparse) {
+        const int l = key0 + (int)lane_id();
+        const int id_lo = l < a.topk ? ids[l] : -1, id_hi = l + 32 < a.topk ? ids[l + 32] : -1;
+        in_lo = id_lo >= 0 && (long long)id_lo < a.cache_rows;
+        in_hi = id_hi >= 0 && (long long)id_hi < a.cache_rows;
+      }
       if (!s_ready && !mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, abort_flag, kKernelMla, 300 + sb)) { ok = false; break; }
       tc_fence_after();
       uint32_t r0[32], r1[32];
@@ -248,15 +277,12 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane_id() == 0) mbar_arrive(b_sempty + 8 * sb);
-      const int key0 = (pg_begin + i) * kPage;
       // this page's P buffer was last read by the P V product of page i-2: tested here, long before the answer is needed
       // (an mbarrier test costs ~150 cycles even when the phase completed long ago)
       const bool p_free = i < 2 || mbar_test(b_pempty + 8 * (i & 1), ((i - 2) >> 1) & 1);
       if (kSparse) {
-        // columns whose listed row id is -1 (or past the list) hold zero-filled keys: take them out of the softmax
-        const int l = (int)lane_id();
-        const unsigned v_lo = __ballot_sync(0xffffffffu, key0 + l < a.topk && ids[key0 + l] >= 0);
-        const unsigned v_hi = __ballot_sync(0xffffffffu, key0 + 32 + l < a.topk && ids[key0 + 32 + l] >= 0);
+        // columns whose listed row id is not a cache row (-1, or past the list) hold zero-filled keys: take them out of the softmax
+        const unsigned v_lo = __ballot_sync(0xffffffffu, in_lo), v_hi = __ballot_sync(0xffffffffu, in_hi);
         if (!row_ok || (v_lo & v_hi) != 0xffffffffu) {
 #pragma unroll
           for (int j = 0; j < 32; j++) {
@@ -457,7 +483,7 @@ extern "C" int ne_mla_fp8_sparse(const void* q8, const void* cache, int num_bloc
   a.T = T; a.H = H; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f; a.out = (__nv_bfloat16*)out; a.part = part; a.lse2 = lse2;
   a.sparse = sparse; a.topk = topk; a.cache = (const uint8_t*)cache; a.cache_rows = (long long)num_blocks * kPage;
   dim3 grid(2 * T, splits, 1);
-  return (int)launch_pdl(mla_fp8_kernel<true>, grid, dim3(kMlaThreads), kMlaSmem, st, tq128, tq64, tq128, tq64, a);     // the key maps are unused here
+  return (int)launch_pdl(mla_fp8_kernel<true>, grid, dim3(kMlaSparseThreads), kMlaSmem, st, tq128, tq64, tq128, tq64, a);     // the key maps are unused here
 }
 
 // ---- allocation-free entry point ----------------------------------------------------------------------
