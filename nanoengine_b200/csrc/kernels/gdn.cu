@@ -81,7 +81,10 @@ __global__ void __launch_bounds__(256) gdn_conv_state_kernel(const __nv_bfloat16
 // are left to the chunked form.  kFuseNorm (the CTA holds the whole head): the gated RMSNorm is applied here and `out` is
 // bf16; otherwise several small CTAs share a head - more CTAs per SM overlap their load / compute / store phases better at
 // the 128 x 128 state size - and `out` receives the raw fp32 rows for the separate gated norm kernel.
-template <int E, int R, int NW, bool kFuseNorm>
+// kVecGate (Kimi delta attention, reference layers/backends/delta_net/kda.py:300-370): the log-decay is a vector over the key
+// dimension, `a` is [T, Hv * Dk] with `dt_bias` of the same width, and the gate is either -exp(A) softplus(a + bias) or, with a
+// lower bound L < 0, L * sigmoid(exp(A) (a + bias)).  Row r of the state then decays element by element.
+template <int E, int R, int NW, bool kFuseNorm, bool kVecGate>
 __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                                                          const __nv_bfloat16* __restrict__ v, long long qk_ld, long long v_ld,
                                                          const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b, long long ab_ld,
@@ -89,7 +92,7 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
                                                          float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
                                                          const int* __restrict__ fresh, const __nv_bfloat16* __restrict__ z, long long z_ld,
                                                          const __nv_bfloat16* __restrict__ norm_w, float eps, void* __restrict__ out,
-                                                         long long out_ld, int Hv, int Dv, int rep, int skip_len) {
+                                                         long long out_ld, int Hv, int Dv, int rep, int skip_len, float lower_bound) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   constexpr int Dk = 32 * E, kRowsPerCta = NW * R;
   __shared__ float s_o[kFuseNorm ? kRowsPerCta : 1];
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
 #pragma unroll
       for (int e = 0; e < E; e++) S[r][e] = S_g[r * Dk + e * 32 + lane];
   }
-  const float neg_A = -__expf(A_log[h]), dtb = dt_bias[h];
+  const float neg_A = -__expf(A_log[h]), dtb = kVecGate ? 0.f : dt_bias[h];
   const float qscale = rsqrtf((float)Dk);
   for (int i = 0; i < n; i++) {
     const long long t = start + i;
@@ -129,22 +132,47 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
 #pragma unroll
     for (int e = 0; e < E; e++) { kf[e] *= kn; qf[e] *= qn; kq += kf[e] * qf[e]; }
     kq = warp_sum(kq);
-    const float av = __bfloat162float(a[t * ab_ld + h]) + dtb;
-    const float sp = av > 20.f ? av : log1pf(__expf(av));
-    const float decay = __expf(neg_A * sp);
     const float beta = 1.f / (1.f + __expf(-__bfloat162float(b[t * ab_ld + h])));
     float o[R];
+    if (kVecGate) {
+      // `a` rows are Hv * Dk wide here and `b` rows Hv wide; ab_ld is the row stride of `b`, a's is Hv * Dk
+      float dec[E], kd[E], qd[E];
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-      float pk = 0.f, pq = 0.f;
+      for (int e = 0; e < E; e++) {
+        const int c = h * Dk + e * 32 + lane;
+        const float x = __bfloat162float(a[t * (long long)Hv * Dk + c]) + dt_bias[c];
+        const float gl = lower_bound < 0.f ? lower_bound / (1.f + __expf(neg_A * x))          // L * sigmoid(exp(A) x)
+                                           : neg_A * (x > 20.f ? x : log1pf(__expf(x)));
+        dec[e] = __expf(gl); kd[e] = dec[e] * kf[e]; qd[e] = dec[e] * qf[e];
+      }
 #pragma unroll
-      for (int e = 0; e < E; e++) { pk += S[r][e] * kf[e]; pq += S[r][e] * qf[e]; }
-      pk = warp_sum(pk); pq = warp_sum(pq);
-      const float vr = __bfloat162float(v[t * v_ld + h * Dv + row0 + r]);
-      const float u = beta * (vr - decay * pk);
+      for (int r = 0; r < R; r++) {
+        float pk = 0.f, pq = 0.f;
 #pragma unroll
-      for (int e = 0; e < E; e++) S[r][e] = decay * S[r][e] + u * kf[e];
-      o[r] = decay * pq + u * kq;
+        for (int e = 0; e < E; e++) { pk += S[r][e] * kd[e]; pq += S[r][e] * qd[e]; }
+        pk = warp_sum(pk); pq = warp_sum(pq);
+        const float vr = __bfloat162float(v[t * v_ld + h * Dv + row0 + r]);
+        const float u = beta * (vr - pk);
+#pragma unroll
+        for (int e = 0; e < E; e++) S[r][e] = dec[e] * S[r][e] + u * kf[e];
+        o[r] = pq + u * kq;
+      }
+    } else {
+      const float av = __bfloat162float(a[t * ab_ld + h]) + dtb;
+      const float sp = av > 20.f ? av : log1pf(__expf(av));
+      const float decay = __expf(neg_A * sp);
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        float pk = 0.f, pq = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; e++) { pk += S[r][e] * kf[e]; pq += S[r][e] * qf[e]; }
+        pk = warp_sum(pk); pq = warp_sum(pq);
+        const float vr = __bfloat162float(v[t * v_ld + h * Dv + row0 + r]);
+        const float u = beta * (vr - decay * pk);
+#pragma unroll
+        for (int e = 0; e < E; e++) S[r][e] = decay * S[r][e] + u * kf[e];
+        o[r] = decay * pq + u * kq;
+      }
     }
     if (!kFuseNorm) {
       float* orow = reinterpret_cast<float*>(out) + t * out_ld + h * Dv + row0;
@@ -185,7 +213,7 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
 // one warp per row: out = w * bf16(rmsnorm(x)) * bf16(silu(z)); rows listed by [row_begin, row_end) ranges are handled by the caller.
 __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ z, long long z_ld,
                                                            const __nv_bfloat16* __restrict__ w, float eps, __nv_bfloat16* __restrict__ out,
-                                                           long long out_ld, long long rows, int heads, int D) {
+                                                           long long out_ld, long long rows, int heads, int D, int sigmoid_fp32) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -197,6 +225,11 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_kernel(const float* __restr
   for (int d = lane; d < D; d += 32) { float f = xr[d]; ss += f * f; }
   ss = warp_sum(ss);
   const float rstd = rsqrtf(ss / (float)D + eps);
+  if (sigmoid_fp32) {        // x * rstd * w * sigmoid(z) in fp32, one rounding (reference kernel/triton/generic/k3_output_norm.py:40)
+    for (int d = lane; d < D; d += 32)
+      out[t * out_ld + h * D + d] = __float2bfloat16(xr[d] * rstd * __bfloat162float(w[d]) / (1.f + __expf(-__bfloat162float(z[t * z_ld + h * D + d]))));
+    return;
+  }
   for (int d = lane; d < D; d += 32) {
     float xn = __bfloat162float(__float2bfloat16(xr[d] * rstd));
     float y = __bfloat162float(__float2bfloat16(__bfloat162float(w[d]) * xn));
@@ -254,29 +287,30 @@ extern "C" int ne_gdn_step_raw_only(int Dk, int Dv) { return (Dk == 128 && Dv ==
 extern "C" int ne_gdn_step(const void* q, const void* k, const void* v, long long qk_ld, long long v_ld, const void* a, const void* b, long long ab_ld,
                            const float* A_log, const float* dt_bias, float* state, const int* slots, const int* cu, const int* fresh,
                            const void* z, long long z_ld, const void* norm_w, float eps, void* out, long long out_ld, int B, int Hk, int Hv,
-                           int Dk, int Dv, int skip_len, int raw_out, cudaStream_t st) {
+                           int Dk, int Dv, int skip_len, int raw_out, int vec_gate, float lower_bound, cudaStream_t st) {
   if (B <= 0) return 0;
   if (Hv % Hk) return 1001;
   const int rep = Hv / Hk;
-#define NE_GDN_LAUNCH(E_, R_, NW_, FUSE_)                                                                                                   \
-  launch_pdl(gdn_step_kernel<E_, R_, NW_, FUSE_>, dim3(Hv * (Dv / (NW_ * R_)), B), dim3(32 * NW_), 0, st,                                \
+  if (vec_gate && !(Dk == 128 && Dv == 128 && raw_out)) return 1001;
+#define NE_GDN_LAUNCH(E_, R_, NW_, FUSE_, VEC_)                                                                                                 \
+  launch_pdl(gdn_step_kernel<E_, R_, NW_, FUSE_, VEC_>, dim3(Hv * (Dv / (NW_ * R_)), B), dim3(32 * NW_), 0, st,                                \
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, qk_ld, v_ld, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, \
       ab_ld, A_log, dt_bias, state, slots, cu, fresh, (const __nv_bfloat16*)z, z_ld, (const __nv_bfloat16*)norm_w, eps, out, out_ld, Hv, Dv, rep, \
-      skip_len)
-  if (Dk == 128 && Dv == 128) { if (!raw_out) return 1001; NE_GDN_LAUNCH(4, 8, 4, false); }
+      skip_len, lower_bound)
+  if (Dk == 128 && Dv == 128) { if (!raw_out) return 1001; if (vec_gate) NE_GDN_LAUNCH(4, 8, 4, false, true); else NE_GDN_LAUNCH(4, 8, 4, false, false); }
   else if (raw_out) return 1001;
-  else if (Dk == 128 && Dv == 64) NE_GDN_LAUNCH(4, 8, 8, true);
-  else if (Dk == 64 && Dv == 64) NE_GDN_LAUNCH(2, 8, 8, true);
-  else if (Dk == 32 && Dv == 32) NE_GDN_LAUNCH(1, 4, 8, true);
+  else if (Dk == 128 && Dv == 64) NE_GDN_LAUNCH(4, 8, 8, true, false);
+  else if (Dk == 64 && Dv == 64) NE_GDN_LAUNCH(2, 8, 8, true, false);
+  else if (Dk == 32 && Dv == 32) NE_GDN_LAUNCH(1, 4, 8, true, false);
   else return 1001;
 #undef NE_GDN_LAUNCH
   return (int)cudaGetLastError();
 }
 
 extern "C" int ne_rmsnorm_gated(const float* x, const void* z, long long z_ld, const void* w, float eps, void* out, long long out_ld, long long tokens,
-                                int heads, int D, cudaStream_t st) {
+                                int heads, int D, int sigmoid_fp32, cudaStream_t st) {
   long long rows = tokens * heads;
   if (rows <= 0) return 0;
   return (int)launch_pdl(rmsnorm_gated_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, st, x, (const __nv_bfloat16*)z, z_ld, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out,
-                                                                  out_ld, rows, heads, D);
+                                                                  out_ld, rows, heads, D, sigmoid_fp32);
 }

@@ -639,15 +639,69 @@ def gdn_chunked(q, k, v, g, beta, S, chunk: int = 64):
     return o, S
 
 
-def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """w * rmsnorm(x) * silu(z) over the last dimension; result in z's dtype."""
+def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+                  sigmoid: bool = False) -> torch.Tensor:
+    """w * rmsnorm(x) * silu(z) over the last dimension; result in z's dtype.  `sigmoid`: x * rstd * w * sigmoid(z) in fp32."""
     xf = x.float()
+    if sigmoid:
+        y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float() * torch.sigmoid(z.float())).to(z.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
     xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(z.dtype)
     y = (w.to(z.dtype) * xn) * torch.nn.functional.silu(z.float()).to(z.dtype)
     if out is not None:
         out.copy_(y)
         return out
     return y
+
+
+def kda_gates(raw_g: torch.Tensor, b: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, lower_bound: Optional[float]):
+    """Kimi delta attention gates.  raw_g [T, H, Dk], b [T, H], A_log [H], dt_bias [H * Dk].  The log-decay per key channel is
+    L * sigmoid(exp(A) (raw_g + bias)) when a lower bound L < 0 is given, else -exp(A) softplus(raw_g + bias); the write
+    strength is sigmoid(b) (reference kernel/triton/fla/fused_recurrent.py:505-530)."""
+    T, H, Dk = raw_g.shape
+    x = raw_g.float() + dt_bias.float().view(1, H, Dk)
+    A = A_log.float().exp().view(1, H, 1)
+    g = lower_bound * torch.sigmoid(A * x) if lower_bound is not None and lower_bound < 0 else -A * torch.nn.functional.softplus(x)
+    return g, b.float().sigmoid()
+
+
+def kda_scan(q, k, v, g, beta, S):
+    """Token-by-token delta rule with a decay per key channel.  q, k [n, H, Dk]; v [n, H, Dv]; g [n, H, Dk]; beta [n, H];
+    S [H, Dv, Dk] fp32."""
+    out = []
+    for t in range(q.shape[0]):
+        S = S * g[t].exp()[:, None, :]
+        Sk = torch.einsum("hvk,hk->hv", S, k[t])
+        S = S + (beta[t][:, None] * (v[t] - Sk))[:, :, None] * k[t][:, None, :]
+        out.append(torch.einsum("hvk,hk->hv", S, q[t]))
+    return torch.stack(out, 0), S
+
+
+def kda_recurrent(q, k, v, raw_g, b, A_log, dt_bias, lower_bound, state, slots, cu_seqlens, fresh, gate, norm_w, eps: float) -> torch.Tensor:
+    """Kimi delta attention over ragged sequences with a per-sequence state, followed by the sigmoid-gated RMSNorm
+    x * rstd * w * sigmoid(gate) (reference layers/backends/delta_net/kda.py:300-377).  q, k [T, H, Dk], v and gate
+    [T, H, Dv]; state [S, H, Dv, Dk] fp32.  Returns [T, H * Dv] in v's dtype."""
+    T, H, Dk = q.shape
+    Dv = v.shape[2]
+    g, beta = kda_gates(raw_g.reshape(T, H, Dk), b, A_log, dt_bias, lower_bound)
+    qn = _l2norm(q.float()) * (Dk ** -0.5)
+    kn = _l2norm(k.float())
+    vf = v.float()
+    o = torch.empty(T, H, Dv, dtype=torch.float32, device=v.device)
+    cu = cu_seqlens.tolist()
+    for i in range(len(cu) - 1):
+        s, e = cu[i], cu[i + 1]
+        if e <= s:
+            continue
+        slot = int(slots[i])
+        S = torch.zeros_like(state[slot]) if int(fresh[i]) else state[slot].clone()
+        o[s:e], S = kda_scan(qn[s:e], kn[s:e], vf[s:e], g[s:e], beta[s:e], S)
+        state[slot] = S
+    y = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float() * torch.sigmoid(gate.float())
+    return y.to(v.dtype).reshape(T, H * Dv)
 
 
 def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:

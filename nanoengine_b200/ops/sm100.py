@@ -593,8 +593,10 @@ def gdn_conv(x: torch.Tensor, weight: torch.Tensor, conv_state: torch.Tensor, sl
     return y
 
 
-def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """w * rmsnorm(x) * silu(z) per head; x [T, H, D] fp32, z [T, H, D] bf16 (rows may be strided)."""
+def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+                  sigmoid: bool = False) -> torch.Tensor:
+    """w * rmsnorm(x) * silu(z) per head; x [T, H, D] fp32, z [T, H, D] bf16 (rows may be strided).  `sigmoid`: the gate is
+    sigmoid(z) and the whole product is taken in fp32 (the output norm of Kimi delta attention)."""
     T, H, D = x.shape
     x = x.float().contiguous()
     assert z.dtype == torch.bfloat16 and z.stride(2) == 1 and z.stride(1) == D and w.dtype == torch.bfloat16
@@ -602,7 +604,7 @@ def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float,
         out = torch.empty(T, H, D, dtype=torch.bfloat16, device=x.device)
     assert out.stride(2) == 1 and out.stride(1) == D
     _ck(lib().ne_rmsnorm_gated(_p(x), _p(z), _c.c_longlong(z.stride(0)), _p(w), _c.c_float(eps), _p(out), _c.c_longlong(out.stride(0)),
-                               _c.c_longlong(T), _c.c_int(H), _c.c_int(D), _st()), "ne_rmsnorm_gated")
+                               _c.c_longlong(T), _c.c_int(H), _c.c_int(D), _c.c_int(1 if sigmoid else 0), _st()), "ne_rmsnorm_gated")
     return out
 
 
@@ -646,7 +648,7 @@ def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh
     _ck(lib().ne_gdn_step(_p(q), _p(k), _p(v), _c.c_longlong(q.stride(0)), _c.c_longlong(v.stride(0)), _p(a), _p(b), _c.c_longlong(a.stride(0)),
                           _p(A_log), _p(dt_bias), _p(state), _p(slots), _p(cu), _p(fresh), _p(z), _c.c_longlong(z.stride(0)), _p(norm_w),
                           _c.c_float(eps), _p(dst), _c.c_longlong(dst.stride(0)), _c.c_int(cu.numel() - 1), _c.c_int(Hk), _c.c_int(Hv), _c.c_int(Dk),
-                          _c.c_int(Dv), _c.c_int(skip), _c.c_int(1 if raw else 0), _st()), "ne_gdn_step")
+                          _c.c_int(Dv), _c.c_int(skip), _c.c_int(1 if raw else 0), _c.c_int(0), _c.c_float(0.0), _st()), "ne_gdn_step")
     if raw:
         if max_q_len >= ref.GDN_CHUNK_MIN_TOKENS:
             short = torch.ones(T, dtype=torch.bool, device=q.device)
@@ -658,6 +660,29 @@ def gdn_recurrent(q, k, v, a, b, A_log, dt_bias, state, slots, cu_seqlens, fresh
         else:
             rmsnorm_gated(dst, z, norm_w, eps, out)
     return out.view(T, Hv * Dv)
+
+
+def kda_recurrent(q, k, v, raw_g, b, A_log, dt_bias, lower_bound, state, slots, cu_seqlens, fresh, gate, norm_w, eps: float) -> torch.Tensor:
+    """Kimi delta attention: the delta rule with a log-decay per key channel, then the sigmoid-gated RMSNorm.  Every sequence,
+    prompt chunks included, runs token by token in the kernel that keeps the 128 x 128 state in registers."""
+    T, H, Dk = q.shape
+    Dv = v.shape[2]
+    assert Dk == 128 and Dv == 128 and k.shape == q.shape and v.shape[1] == H, "the CUDA form covers 128 x 128 states"
+    for t in (q, k, v, gate):
+        assert t.dtype == torch.bfloat16 and t.stride(2) == 1 and t.stride(1) == t.shape[2]
+    raw_g = raw_g.reshape(T, H * Dk)
+    assert q.stride(0) == k.stride(0) and raw_g.dtype == torch.bfloat16 and raw_g.is_contiguous() and b.dtype == torch.bfloat16 and b.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, Dv, Dk)
+    assert A_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and dt_bias.numel() == H * Dk and norm_w.dtype == torch.bfloat16
+    slots, cu, fresh = _i32(slots), _i32(cu_seqlens), _i32(fresh)
+    raw = torch.empty(T, H, Dv, dtype=torch.float32, device=q.device)
+    _ck(lib().ne_gdn_step(_p(q), _p(k), _p(v), _c.c_longlong(q.stride(0)), _c.c_longlong(v.stride(0)), _p(raw_g), _p(b), _c.c_longlong(b.stride(0)),
+                          _p(A_log), _p(dt_bias), _p(state), _p(slots), _p(cu), _p(fresh), _p(gate), _c.c_longlong(gate.stride(0)), _p(norm_w),
+                          _c.c_float(eps), _p(raw), _c.c_longlong(raw.stride(0)), _c.c_int(cu.numel() - 1), _c.c_int(H), _c.c_int(H), _c.c_int(Dk),
+                          _c.c_int(Dv), _c.c_int(1 << 30), _c.c_int(1), _c.c_int(1), _c.c_float(float(lower_bound) if lower_bound is not None else 0.0),
+                          _st()), "ne_gdn_step")
+    w = norm_w.expand(Dv) if norm_w.numel() == Dv else norm_w
+    return rmsnorm_gated(raw, gate, w.contiguous(), eps, sigmoid=True).view(T, H * Dv)
 
 
 def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
