@@ -117,12 +117,25 @@ __global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, long lon
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
 // One (row, 128-column block) item of SwiGLU: 4 columns per lane; bf16 out, or e4m3 with the block's scale at sc[c * sc_ld + row].
+// Gated activation of one (gate, up) pair.  act 0: silu(g) u.  act 1 (clamped SwiGLU, limit p0): up in [-p0, p0], gate <= p0,
+// then silu(g) u (reference layers/activation.py:86-92).  act 2 (SiTU-GLU, p0 = beta, p1 = linear beta or 0):
+// beta tanh(g / beta) sigmoid(g) times p1 tanh(u / p1) (reference kernel/triton/generic/situ.py:24-27).
+__device__ __forceinline__ float glu_act(float g, float u, int act, float p0, float p1) {
+  if (act == 1) { u = fminf(fmaxf(u, -p0), p0); g = fminf(g, p0); }
+  else if (act == 2) {
+    if (p1 > 0.f) u = p1 * tanhf(u / p1);
+    return p0 * tanhf(g / p0) / (1.f + __expf(-g)) * u;
+  }
+  return silu(g) * u;
+}
+
 __device__ __forceinline__ void silu_item(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q,
-                                          float* __restrict__ sc, int sc_ld, long long mrow, int row, int c, int I, int lane) {
+                                          float* __restrict__ sc, int sc_ld, long long mrow, int row, int c, int I, int lane,
+                                          int act = 0, float p0 = 0.f, float p1 = 0.f) {
   const __nv_bfloat16* xr = x + mrow * 2 * I + c * 128 + lane * 4;
   uint2 gv = *reinterpret_cast<const uint2*>(xr), uv = *reinterpret_cast<const uint2*>(xr + I);
   float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), u0 = unpack_bf16x2(uv.x), u1 = unpack_bf16x2(uv.y);
-  float v[4] = {silu(g0.x) * u0.x, silu(g0.y) * u0.y, silu(g1.x) * u1.x, silu(g1.y) * u1.y};
+  float v[4] = {glu_act(g0.x, u0.x, act, p0, p1), glu_act(g0.y, u0.y, act, p0, p1), glu_act(g1.x, u1.x, act, p0, p1), glu_act(g1.y, u1.y, act, p0, p1)};
   const long long o = mrow * I + c * 128 + lane * 4;
   if (!q) {
     *reinterpret_cast<uint2*>(y + o) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
@@ -142,7 +155,7 @@ __device__ __forceinline__ void silu_item(const __nv_bfloat16* __restrict__ x, _
 constexpr int kSiluMaxGroups = 1024;
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ sc,
                                 int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, const int* __restrict__ row_start, int groups,
-                                int rows, int I) {
+                                int rows, int I, int act, float p0, float p1) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   // warps stride over the concatenation of all groups' (valid row, 128-column block) items, so a sparsely filled masked
   // layout costs only its valid rows and every warp gets an equal share whatever the split between groups.  The item index
@@ -182,7 +195,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
       const int row = s_rs[g] + ri;
       if (row >= rows && row_start) continue;
       const long long gbase = row_start ? 0 : (long long)g * rows;
-      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane);
+      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane, act, p0, p1);
     }
     return;
   }
@@ -202,7 +215,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
     for (long long it = first; it < items; it += nw) {
       const int row = r0 + (int)(it / cg), c = (int)(it % cg);
       if (row >= rows && row_start) continue;
-      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane);
+      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane, act, p0, p1);
     }
   }
 }
@@ -470,14 +483,22 @@ extern "C" int ne_quant_1x128(const void* x, long long x_ld, void* q, float* sc,
   return (int)launch_pdl(quant_1x128_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, x_ld, (uint8_t*)q, sc, sc_ld, T, K);
 }
 
+extern "C" int ne_act_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, const int* row_start,
+                          int groups, int rows, int I, int act, float p0, float p1, cudaStream_t st);
 extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, const int* row_start,
                            int groups, int rows, int I, cudaStream_t st) {
+  return ne_act_mul(x, y, q, sc, sc_ld, sc_gs, rows_valid, row_start, groups, rows, I, 0, 0.f, 0.f, st);
+}
+// the same kernel with the gated activation chosen by `act` (see glu_act)
+extern "C" int ne_act_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, const int* row_start,
+                          int groups, int rows, int I, int act, float p0, float p1, cudaStream_t st) {
   if (groups <= 0 || rows <= 0) return 0;
+  if (act < 0 || act > 2 || (act != 0 && !(p0 > 0.f))) return 1001;
   if (I % 128 != 0) return 1001;
   long long warps = (long long)groups * rows * (I / 128);
   long long want = (warps + 7) / 8;
   int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
-  return (int)launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, row_start, groups, rows, I);
+  return (int)launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, row_start, groups, rows, I, act, p0, p1);
 }
 
 extern "C" int ne_rope(const void* x, long long row_stride, int head_stride, void* y, long long y_row_stride, int y_head_stride, int heads,

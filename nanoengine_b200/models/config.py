@@ -66,6 +66,22 @@ class ModelConfig:
     attn_output_gate: bool = False           # q projection carries a per-head sigmoid gate for the attention output
     norm_unit_offset: bool = False           # RMSNorm weights are stored as the deviation from one
     shared_expert_intermediate_size: int = 0 # Qwen3.5-MoE: one always-on expert behind a sigmoid gate
+    # Kimi delta attention (GLM5-next, Kimi-K3): the linear layers decay per key channel and sit between MLA layers
+    linear_kind: str = "gdn"                 # "gdn" (scalar decay per head) | "kda" (decay per key channel)
+    kda_gate_lower_bound: Optional[float] = None   # L < 0: log-decay = L * sigmoid(exp(A) (g + bias)); None: -exp(A) softplus(g + bias)
+    mla_output_gate: bool = False            # MLA layers carry g_proj: the attention output is multiplied by sigmoid(g_proj(x))
+    mla_skip_rope: bool = False              # MLA layers without rotary embedding (the rope dims are plain dims)
+    # hyper-connections (GLM5-next): the hidden state is hc_mult parallel streams
+    hc_mult: int = 0
+    hc_sinkhorn_iters: int = 1
+    hc_eps: float = 1e-6
+    swiglu_limit: float = 0.0                # > 0: clamp up to [-L, L] and gate to <= L before silu(gate) * up
+    mlp_layer_types: Optional[List[str]] = None    # per layer "dense" | "sparse"; None = first_k_dense_replace / moe_layer_freq rule
+    # Kimi-K3: block attention residuals, latent experts, SiTU-GLU
+    attn_res_block_size: int = 0             # > 0: every this-many layers the running residual sum is frozen into the bank
+    routed_expert_hidden_size: int = 0       # > 0: routed experts work in a latent space of this width (down-proj, experts, norm, up-proj)
+    activation_situ_beta: float = 0.0        # > 0: the gated activation is SiTU-GLU with this beta
+    activation_situ_linear_beta: float = 0.0
     # MTP
     num_nextn_predict_layers: int = 0
     # quantisation of linear / expert weights: None (use dtype) or "fp8" (e4m3, 128x128 block scales)
@@ -78,7 +94,8 @@ class ModelConfig:
     @property
     def is_mla(self) -> bool:
         return self.architecture in ("DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM",
-                                     "GlmMoeDsaForCausalLM", "KimiK2ForCausalLM")
+                                     "GlmMoeDsaForCausalLM", "KimiK2ForCausalLM", "Glm5NextForConditionalGeneration",
+                                     "KimiK3ForConditionalGeneration")
 
     @property
     def is_hybrid_gdn(self) -> bool:
@@ -111,9 +128,20 @@ class ModelConfig:
     def mla_cache_dim(self) -> int:
         return self.kv_lora_rank + self.qk_rope_head_dim
 
+    @property
+    def glu_act(self):
+        """Gated activation of the MLPs and experts as the ops take it: None (SwiGLU), ("clamp", L) or ("situ", beta, linear_beta)."""
+        if self.activation_situ_beta > 0:
+            return ("situ", self.activation_situ_beta, self.activation_situ_linear_beta or None)
+        if self.swiglu_limit > 0:
+            return ("clamp", self.swiglu_limit)
+        return None
+
     def is_moe_layer(self, layer_idx: int) -> bool:
         if self.n_routed_experts <= 0:
             return False
+        if self.mlp_layer_types and layer_idx < len(self.mlp_layer_types):
+            return self.mlp_layer_types[layer_idx] != "dense"
         return layer_idx >= self.first_k_dense_replace and layer_idx % self.moe_layer_freq == 0
 
     def eos_ids(self) -> List[int]:
@@ -143,6 +171,39 @@ class ModelConfig:
         if q and q.get("quant_method") == "fp8":
             d["quant"] = "fp8"
             d["weight_block_size"] = list(q.get("weight_block_size", [128, 128]))
+        arch = d.get("architecture", "")
+        la = d.pop("linear_attn_config", None)
+        if isinstance(la, dict):                          # Kimi delta attention block of GLM5-next / Kimi-K3
+            d["linear_kind"] = "kda"
+            d["linear_num_key_heads"] = d["linear_num_value_heads"] = int(la["num_heads"])
+            d["linear_key_head_dim"] = int(la["head_dim"])
+            d["linear_value_head_dim"] = int(la.get("value_head_dim", la["head_dim"]))
+            d["linear_conv_kernel_dim"] = int(la["short_conv_kernel_size"])
+            d["kda_gate_lower_bound"] = float(la.get("gate_lower_bound", -5.0))
+        if isinstance(d.get("layer_types"), list):         # anything that is not a linear layer is a full-attention layer
+            d["layer_types"] = ["linear_attention" if t == "linear_attention" else "full_attention" for t in d["layer_types"]]
+        if arch.startswith("KimiK3"):
+            if "num_experts" in d:
+                d["n_routed_experts"] = d.pop("num_experts")
+            if "num_experts_per_token" in d:
+                d["num_experts_per_tok"] = d.pop("num_experts_per_token")
+            if "num_shared_experts" in d:
+                d["n_shared_experts"] = d.pop("num_shared_experts")
+            d.setdefault("scoring_func", "sigmoid")
+            d.setdefault("topk_method", "noaux_tc")
+            d.setdefault("n_group", 1)
+            d.setdefault("topk_group", 1)
+            d.setdefault("routed_scaling_factor", 1.0)
+            d["norm_topk_prob"] = float(d["routed_scaling_factor"]) == 1.0
+            d.setdefault("mla_output_gate", True)
+            d.setdefault("mla_skip_rope", True)
+            d.setdefault("activation_situ_beta", 4.0)
+            d.setdefault("activation_situ_linear_beta", 25.0)
+            if d.get("attn_res_block_size") is None:
+                d["attn_res_block_size"] = 0
+        if arch.startswith("Glm5Next"):
+            d.setdefault("swiglu_limit", 10.0)
+            d.setdefault("hc_mult", 4)
         # Qwen3-MoE spellings
         if "num_experts" in d:
             d["n_routed_experts"] = d.pop("num_experts")
@@ -252,3 +313,31 @@ def qwen3_5_80b(**over) -> ModelConfig:
 
 PRESETS = {"tiny-deepseek-v3": tiny_deepseek_v3, "deepseek-v3": deepseek_v3, "deepseek-v3.2": deepseek_v32,
            "qwen3-235b-a22b": qwen3_235b, "tiny-qwen3.5": tiny_qwen3_5, "qwen3.5-80b-a3b": qwen3_5_80b}
+
+
+def tiny_glm5_next(**over) -> ModelConfig:
+    """CPU-sized GLM5-next shape: delta-attention / sparse-attention layers alternating, 2 hyper-connection streams."""
+    base = dict(architecture="Glm5NextForConditionalGeneration", vocab_size=512, hidden_size=128, num_hidden_layers=4,
+                num_attention_heads=4, num_key_value_heads=4, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=16,
+                v_head_dim=16, intermediate_size=256, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, moe_intermediate_size=64,
+                first_k_dense_replace=1, n_group=2, topk_group=1, max_position_embeddings=4096,
+                layer_types=["linear_attention", "full_attention", "linear_attention", "full_attention"],
+                mlp_layer_types=["dense", "sparse", "sparse", "sparse"], linear_kind="kda", linear_num_key_heads=2, linear_num_value_heads=2,
+                linear_key_head_dim=32, linear_value_head_dim=32, linear_conv_kernel_dim=4, kda_gate_lower_bound=-5.0,
+                hc_mult=2, hc_sinkhorn_iters=3, swiglu_limit=10.0, index_n_heads=2, index_head_dim=32, index_topk=64)
+    base.update(over)
+    return ModelConfig(**base)
+
+
+def tiny_kimi_k3(**over) -> ModelConfig:
+    """CPU-sized Kimi-K3 shape: delta-attention layers with every third layer NoPE MLA, residual blocks of 2 layers, latent experts."""
+    base = dict(architecture="KimiK3ForConditionalGeneration", vocab_size=512, hidden_size=128, num_hidden_layers=5,
+                num_attention_heads=4, num_key_value_heads=4, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=16,
+                v_head_dim=16, intermediate_size=256, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, moe_intermediate_size=64,
+                first_k_dense_replace=1, n_group=1, topk_group=1, routed_scaling_factor=1.0, norm_topk_prob=True, max_position_embeddings=4096,
+                layer_types=["linear_attention", "linear_attention", "full_attention", "linear_attention", "full_attention"],
+                linear_kind="kda", linear_num_key_heads=2, linear_num_value_heads=2, linear_key_head_dim=32, linear_value_head_dim=32,
+                linear_conv_kernel_dim=4, kda_gate_lower_bound=-5.0, mla_output_gate=True, mla_skip_rope=True, attn_res_block_size=2,
+                routed_expert_hidden_size=64, activation_situ_beta=4.0, activation_situ_linear_beta=25.0)
+    base.update(over)
+    return ModelConfig(**base)

@@ -27,9 +27,14 @@ from .layers import QLinear, RMSNorm, RoutedExperts, SwiGLUMLP
 
 
 class MLAAttention(nn.Module):
-    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+    """`cache_idx`: which page family entry the layer uses (its rank among the full-attention layers in the hybrid families;
+    the layer index otherwise).  With `cfg.mla_output_gate` the heads' output is multiplied by sigmoid(g_proj(x)) before
+    o_proj (reference models/kimi_k3/kimi_k3.py:73-100)."""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device, cache_idx: Optional[int] = None):
         super().__init__()
         self.cfg, self.layer_idx = cfg, layer_idx
+        self.cache_idx = layer_idx if cache_idx is None else cache_idx
         H, R, rope, nope, v = cfg.num_attention_heads, cfg.kv_lora_rank, cfg.qk_rope_head_dim, cfg.qk_nope_head_dim, cfg.v_head_dim
         self.H, self.R, self.rope, self.nope, self.v = H, R, rope, nope, v
         self.q_lora = cfg.q_lora_rank
@@ -58,7 +63,8 @@ class MLAAttention(nn.Module):
         self.indexer = None
         if cfg.has_indexer:
             from .indexer import LightningIndexer
-            self.indexer = LightningIndexer(cfg, layer_idx, dtype, device)
+            self.indexer = LightningIndexer(cfg, self.cache_idx, dtype, device)
+        self.g_proj = QLinear(cfg.hidden_size, H * v, dtype, device, None) if cfg.mla_output_gate else None
 
     def set_kv_b(self, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None):
         """kv_b_proj.weight [H*(nope+v), R] -> kc [H, nope, R], vc [H, R, v]."""
@@ -95,7 +101,7 @@ class MLAAttention(nn.Module):
             q = self.q_proj(x)
             kv_a = self.kv_a_proj_with_mqa(x)
         q = q.view(T, H, nope + rope)
-        cache = ctx.kv_caches[self.layer_idx]
+        cache = ctx.kv_caches[self.cache_idx]
         ops.mla_kv_prepare(kv_a, self.kv_a_layernorm.weight, self.kv_a_layernorm.eps, positions, rope_cache, cache, ctx.slot_mapping, R)
         sparse = None
         if self.indexer is not None:
@@ -104,8 +110,10 @@ class MLAAttention(nn.Module):
         q_full = ops.mla_query(q, self.kc, positions, rope_cache, nope, cache, sparse is None, kc_t=self.kc_t)   # [T, H, R + rope]
         o_lat = ops.mla_attention_paged(q_full, cache, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale, R,
                                         sparse_indices=sparse)
-        o = ops.bmm_absorb(o_lat, self.vc, wt=self.vc_t)                                   # [T, H, v]
-        return self.o_proj(o.reshape(T, H * self.v))
+        o = ops.bmm_absorb(o_lat, self.vc, wt=self.vc_t).reshape(T, H * self.v)           # [T, H * v]
+        if self.g_proj is not None:
+            o = ops.sigmoid_mul(o, self.g_proj(ops.dense(x)))
+        return self.o_proj(o)
 
 
 OVERLAP_SHARED_EXPERTS = True
@@ -141,10 +149,12 @@ class DeepseekMoE(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.gate = MoEGate(cfg, device, layer_idx)
-        self.experts = RoutedExperts(cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, dtype, device, cfg.quant, layer_idx)
+        self.experts = RoutedExperts(cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, dtype, device, cfg.quant, layer_idx,
+                                     act=cfg.glu_act)
         self.shared_experts = None
         if cfg.n_shared_experts > 0:
-            self.shared_experts = SwiGLUMLP(cfg.hidden_size, cfg.moe_intermediate_size * cfg.n_shared_experts, dtype, device, cfg.quant)
+            self.shared_experts = SwiGLUMLP(cfg.hidden_size, cfg.moe_intermediate_size * cfg.n_shared_experts, dtype, device, cfg.quant,
+                                            act=cfg.glu_act)
 
     def forward(self, xq, ctx: ForwardContext):
         """`xq`: the normalised hidden states, possibly with their block-quantised copy (ops.QAct) for the shared expert."""
@@ -187,7 +197,7 @@ class DeepseekDecoderLayer(nn.Module):
         self.self_attn = MLAAttention(cfg, layer_idx, dtype, device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, quant_out=fp8)
         self.is_moe = cfg.is_moe_layer(layer_idx) and not force_dense
-        self.mlp = DeepseekMoE(cfg, dtype, device, layer_idx) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
+        self.mlp = DeepseekMoE(cfg, dtype, device, layer_idx) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant, act=cfg.glu_act)
 
     def forward(self, h, residual, positions, ctx, rope_cache):
         x, residual = self.input_layernorm(h, residual) if residual is not None else (self.input_layernorm(h), h)

@@ -82,13 +82,14 @@ class RMSNorm(nn.Module):
 class SwiGLUMLP(nn.Module):
     """Dense SwiGLU MLP with gate and up projections merged into one GEMM."""
 
-    def __init__(self, hidden: int, inter: int, dtype, device, quant=None):
+    def __init__(self, hidden: int, inter: int, dtype, device, quant=None, act=None):
         super().__init__()
         self.gate_up_proj = QLinear(hidden, 2 * inter, dtype, device, quant)
         self.down_proj = QLinear(inter, hidden, dtype, device, quant)
+        self.act = act          # gated activation other than SwiGLU: see ops.reference.glu_act
 
     def forward(self, x):
-        return self.down_proj(ops.silu_and_mul(self.gate_up_proj(x), self.down_proj.quant == "fp8"))
+        return self.down_proj(ops.silu_and_mul(self.gate_up_proj(x), self.down_proj.quant == "fp8", act=self.act))
 
     def init_random(self, gen):
         self.gate_up_proj.init_random(gen)
@@ -98,8 +99,9 @@ class SwiGLUMLP(nn.Module):
 class RoutedExperts(nn.Module):
     """The experts this rank owns: ids [ep_rank*E_local, (ep_rank+1)*E_local), stacked for grouped GEMMs."""
 
-    def __init__(self, num_experts: int, hidden: int, inter: int, dtype, device, quant=None, layer_idx: Optional[int] = None):
+    def __init__(self, num_experts: int, hidden: int, inter: int, dtype, device, quant=None, layer_idx: Optional[int] = None, act=None):
         super().__init__()
+        self.act = act          # gated activation other than SwiGLU: see ops.reference.glu_act
         d = get_dist_context()
         # under an expert-load-balancing plan the stacked tensors hold PHYSICAL slots (a hot expert may fill several, on
         # different ranks); `phy2log` names the logical expert behind each slot of this layer
@@ -146,7 +148,7 @@ class RoutedExperts(nn.Module):
         """Local part of the routed output for the tokens given (weights applied, zero rows where no expert is local);
         `add_in` (the shared-expert output) is summed in by the same gather pass."""
         return ops.moe_experts(x, topk_idx, topk_w, self.gate_up_proj, self.down_proj, self.gate_up_scale, self.down_scale,
-                               self.expert_offset, add_in)
+                               self.expert_offset, add_in, act=self.act)
 
     @torch.no_grad()
     def set_expert(self, local_idx: int, which: str, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None):

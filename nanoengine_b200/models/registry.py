@@ -29,7 +29,18 @@ def _qwen3_5():
     return Qwen35ForCausalLM
 
 
+def _glm5_next():
+    from .glm5_next import Glm5NextForConditionalGeneration
+    return Glm5NextForConditionalGeneration
+
+
+def _kimi_k3():
+    from .kimi_k3 import KimiK3ForConditionalGeneration
+    return KimiK3ForConditionalGeneration
+
+
 _LAZY = {
+    "Glm5NextForConditionalGeneration": _glm5_next, "KimiK3ForConditionalGeneration": _kimi_k3,
     "DeepseekV2ForCausalLM": _deepseek, "DeepseekV3ForCausalLM": _deepseek, "DeepseekV32ForCausalLM": _deepseek,
     "GlmMoeDsaForCausalLM": _deepseek, "KimiK2ForCausalLM": _deepseek,
     "Qwen3MoeForCausalLM": _qwen3_moe, "Qwen3ForCausalLM": _qwen3_moe,

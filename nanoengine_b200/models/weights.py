@@ -79,6 +79,8 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
             out[p + "kv_a_layernorm.weight"] = (R,)
             out[p + "kv_b_proj.weight"] = (nh * (nope + v), R)
             out[p + "o_proj.weight"] = (H, nh * v)
+            if cfg.mla_output_gate:
+                out[p + "g_proj.weight"] = (nh * v, H)
             if cfg.has_indexer:
                 out[p + "indexer.wq_b.weight"] = (cfg.index_n_heads * cfg.index_head_dim, cfg.q_lora_rank or H)
                 out[p + "indexer.wk.weight"] = (cfg.index_head_dim, H)
@@ -111,11 +113,39 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
         p = f"model.layers.{i}."
         out[p + "input_layernorm.weight"] = (H,)
         out[p + "post_attention_layernorm.weight"] = (H,)
-        if cfg.layer_type(i) == "linear_attention":
+        if cfg.layer_type(i) == "linear_attention" and cfg.linear_kind == "kda":
+            from .kda import kda_param_shapes
+            kda_param_shapes(cfg, p + "self_attn.", out, low_rank_gate=cfg.linear_key_head_dim if cfg.hc_mult else None)
+        elif cfg.layer_type(i) == "linear_attention":
             linear_attn(p + "linear_attn.")
         else:
             attn(p + "self_attn.")
-        if moe:
+        if cfg.hc_mult:
+            for site in ("hc_attn", "hc_ffn"):
+                out[p + site + "_fn"] = ((2 + cfg.hc_mult) * cfg.hc_mult, cfg.hc_mult * H)
+                out[p + site + "_base"] = ((2 + cfg.hc_mult) * cfg.hc_mult,)
+                out[p + site + "_scale"] = (3,)
+        if cfg.attn_res_block_size and i < cfg.num_hidden_layers:
+            for site in ("self_attention_res", "mlp_res"):
+                out[p + site + "_norm.weight"] = (H,)
+                out[p + site + "_proj.weight"] = (1, H)
+        if moe and cfg.routed_expert_hidden_size:
+            I, Z = cfg.moe_intermediate_size, cfg.routed_expert_hidden_size
+            out[p + "mlp.gate.weight"] = (cfg.n_routed_experts, H)
+            out[p + "mlp.gate.e_score_correction_bias"] = (cfg.n_routed_experts,)
+            out[p + "mlp.routed_expert_down_proj.weight"] = (Z, H)
+            out[p + "mlp.routed_expert_norm.weight"] = (Z,)
+            out[p + "mlp.routed_expert_up_proj.weight"] = (H, Z)
+            for e in range(cfg.n_routed_experts):
+                out[p + f"mlp.experts.{e}.w1.weight"] = (I, Z)
+                out[p + f"mlp.experts.{e}.w3.weight"] = (I, Z)
+                out[p + f"mlp.experts.{e}.w2.weight"] = (Z, I)
+            if cfg.n_shared_experts:
+                Is = I * cfg.n_shared_experts
+                out[p + "mlp.shared_experts.gate_proj.weight"] = (Is, H)
+                out[p + "mlp.shared_experts.up_proj.weight"] = (Is, H)
+                out[p + "mlp.shared_experts.down_proj.weight"] = (H, Is)
+        elif moe:
             I = cfg.moe_intermediate_size
             out[p + "mlp.gate.weight"] = (cfg.n_routed_experts, H)
             if cfg.topk_method == "noaux_tc" and cfg.scoring_func == "sigmoid":
@@ -143,6 +173,9 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
 
     for i in range(cfg.num_hidden_layers):
         layer(i, cfg.is_moe_layer(i))
+    if cfg.attn_res_block_size:
+        out["model.output_attn_res_norm.weight"] = (H,)
+        out["model.output_attn_res_proj.weight"] = (1, H)
     if include_mtp:
         for k in range(cfg.num_nextn_predict_layers):
             i = cfg.num_hidden_layers + k
@@ -167,6 +200,10 @@ def random_hf_weights(cfg: ModelConfig, seed: int = 0, device="cpu", keep: Optio
         g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFF)
         if name.endswith("A_log"):
             t = torch.log(1.0 + 3.0 * torch.rand(shape, generator=g, device=dev, dtype=torch.float32))
+        elif name.endswith(("_fn", "_base")):
+            t = 0.05 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        elif name.endswith("_scale") and len(shape) == 1 and shape[0] == 3:
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
         elif name.endswith("dt_bias"):
             t = 0.5 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
         elif name.endswith("conv1d.weight"):
@@ -272,6 +309,10 @@ def load_deepseek_weights(model, weights: Iterable[Tuple[str, torch.Tensor]], mt
                 getattr(A, leaf).weight.copy_(w.to(getattr(A, leaf).weight.dtype)); return
             if leaf == "kv_b_proj":
                 A.set_kv_b(w, s); return
+            if leaf == "g_proj":
+                if A.g_proj is not None:
+                    A.g_proj.set_weight(_deq(w, s))
+                return
             if leaf in ("q_b_proj", "o_proj", "q_proj") or (leaf == "kv_a_proj_with_mqa" and not A.q_lora):
                 getattr(A, leaf).set_weight(w, s); return
             if leaf in ("q_a_proj", "kv_a_proj_with_mqa"):

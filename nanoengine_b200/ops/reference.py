@@ -341,15 +341,61 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_
     return idx.to(torch.int32), (w * routed_scaling_factor).float()
 
 
-def silu_and_mul(x: torch.Tensor, quant: bool = False) -> torch.Tensor:
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def mxfp4_dequant(packed: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """OCP MXFP4 -> fp32.  packed [rows, cols / 2] uint8 holds two e2m1 values per byte (the even column in the low nibble);
+    scale [rows, cols / 32] uint8 holds one e8m0 exponent (2^(s - 127)) per 32 consecutive columns."""
+    p = packed.view(torch.uint8)
+    lut = torch.tensor(_E2M1 + tuple(-v for v in _E2M1), dtype=torch.float32, device=p.device)
+    lo, hi = lut[(p & 0xF).long()], lut[(p >> 4).long()]
+    w = torch.stack([lo, hi], -1).reshape(p.shape[0], p.shape[1] * 2)
+    sc = torch.exp2(scale.view(torch.uint8).float() - 127.0)
+    return (w.view(p.shape[0], -1, 32) * sc.unsqueeze(-1)).reshape(p.shape[0], -1)
+
+
+def mxfp4_quant(w: torch.Tensor):
+    """fp32 [rows, cols] (cols a multiple of 32) -> (packed uint8 [rows, cols / 2], e8m0 scales uint8 [rows, cols / 32]); the
+    inverse of `mxfp4_dequant` up to rounding (nearest e2m1 value, power-of-two scale that maps the block maximum to <= 6)."""
+    r, c = w.shape
+    blk = w.float().view(r, c // 32, 32)
+    amax = blk.abs().amax(-1).clamp_min(2.0 ** -126)
+    e = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+    q = blk / torch.exp2(e).unsqueeze(-1)
+    lut = torch.tensor(_E2M1, dtype=torch.float32, device=w.device)
+    mag = (q.abs().unsqueeze(-1) - lut).abs().argmin(-1)
+    code = (mag + (q < 0).long() * 8).view(r, c).to(torch.uint8)
+    packed = code[:, 0::2] | (code[:, 1::2] << 4)
+    return packed.contiguous(), (e + 127).to(torch.uint8).contiguous()
+
+
+def glu_act(a: torch.Tensor, b: torch.Tensor, act=None) -> torch.Tensor:
+    """Gated activation of (gate a, up b) in fp32.  act None: silu(a) b.  ("clamp", L): up in [-L, L], gate <= L, then
+    silu(a) b (reference layers/activation.py:86-92).  ("situ", beta, linear_beta): beta tanh(a / beta) sigmoid(a) times
+    linear_beta tanh(b / linear_beta) (no clamp of b when linear_beta is None; reference kernel/triton/generic/situ.py:24-27)."""
+    if act is None:
+        return F.silu(a) * b
+    if act[0] == "clamp":
+        L = float(act[1])
+        return F.silu(a.clamp(max=L)) * b.clamp(-L, L)
+    if act[0] == "situ":
+        beta, lb = float(act[1]), act[2]
+        if lb:
+            b = float(lb) * torch.tanh(b / float(lb))
+        return beta * torch.tanh(a / beta) * torch.sigmoid(a) * b
+    raise ValueError(f"unknown gated activation {act!r}")
+
+
+def silu_and_mul(x: torch.Tensor, quant: bool = False, act=None) -> torch.Tensor:
     """`quant` is a hint for the CUDA body (emit only the block-quantised form for an fp8 consumer); ignored here."""
     a, b = x.float().chunk(2, -1)
-    return (F.silu(a) * b).to(x.dtype)
+    return glu_act(a, b, act).to(x.dtype)
 
 
-def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0, add_in=None) -> torch.Tensor:
+def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0, add_in=None, act=None) -> torch.Tensor:
     """Routed experts held locally: ids [expert_offset, expert_offset + E_local).  w13 [E, 2I, H], w2 [E, H, I].
-    Returns the weighted sum over the local experts of each token (zeros where none is local)."""
+    Returns the weighted sum over the local experts of each token (zeros where none is local).  `act`: see `glu_act`."""
     if callable(add_in):
         add_in = add_in()
     T, H = x.shape
@@ -362,7 +408,7 @@ def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, exp
             continue
         xe = x[tok]
         h = linear(xe, w13[e], None if w13_scale is None else w13_scale[e])
-        h = silu_and_mul(h)
+        h = silu_and_mul(h, act=act)
         y = linear(h, w2[e], None if w2_scale is None else w2_scale[e])
         out.index_add_(0, tok, y.float() * topk_w[tok, slot].unsqueeze(-1))
     out = out.to(x.dtype)
@@ -702,6 +748,54 @@ def kda_recurrent(q, k, v, raw_g, b, A_log, dt_bias, lower_bound, state, slots, 
         state[slot] = S
     y = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float() * torch.sigmoid(gate.float())
     return y.to(v.dtype).reshape(T, H * Dv)
+
+
+def sigmoid_mul(o: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """o * sigmoid(g) over rows [T, W] (g may be a strided view)."""
+    return (o.float() * torch.sigmoid(g.float())).to(o.dtype)
+
+
+def attn_res_mix(prefix: torch.Tensor, bank: torch.Tensor, valid: int, w_score: torch.Tensor, w_out: torch.Tensor, eps: float,
+                 write_row: int = -1) -> torch.Tensor:
+    """Block attention residual.  prefix [T, D] is the running sum since the last block boundary, bank [T, rows, D] holds the
+    frozen block sums of which the first `valid` count.  Every candidate (bank rows, then the prefix) gets the score
+    (cand . w_score) * rsqrt(mean(cand^2) + eps); the softmax mixture of the candidates is rounded to the activation dtype
+    and RMS-normalised with `w_out`.  `write_row` >= 0 also stores the prefix into that bank row.
+    Parity: reference models/kimi_k3/kimi_k3.py:103-161, kernel/triton/kimi_k3/attn_residual.py:17-140."""
+    cand = torch.cat([bank[:, :valid], prefix[:, None]], 1).float()
+    sc = (cand * w_score.float()).sum(-1) * torch.rsqrt(cand.square().mean(-1) + eps)
+    mix = (sc.softmax(-1)[..., None] * cand).sum(1).to(prefix.dtype)
+    if write_row >= 0:
+        bank[:, write_row].copy_(prefix)
+    return rmsnorm(mix, w_out, eps)
+
+
+def mhc_pre(x: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, iters: int, eps: float):
+    """Hyper-connection pre-mix.  x [T, h, D] streams; fn [(2+h)h, h*D], base [(2+h)h], scale [3] fp32.  Returns the
+    contracted sub-layer input y [T, D] and the post weights [T, h] and stream-mixing matrix [T, h, h] for `mhc_post`.
+    Parity: reference models/glm5_next/glm5_next.py:27-70."""
+    T, h, D = x.shape
+    flat = x.flatten(1).float()
+    r = torch.rsqrt(flat.square().mean(-1, keepdim=True) + eps)
+    mixes = F.linear(flat, fn.float()) * r
+    pre = torch.sigmoid(mixes[:, :h] * scale[0] + base[:h]) + eps
+    post = 2 * torch.sigmoid(mixes[:, h: 2 * h] * scale[1] + base[h: 2 * h])
+    comb = mixes[:, 2 * h:].view(T, h, h) * scale[2] + base[2 * h:].view(h, h)
+    comb = comb.softmax(-1) + eps
+    comb = comb / (comb.sum(-2, keepdim=True) + eps)
+    for _ in range(max(0, iters - 1)):
+        comb = comb / (comb.sum(-1, keepdim=True) + eps)
+        comb = comb / (comb.sum(-2, keepdim=True) + eps)
+    pre = pre.to(x.dtype)
+    y = (pre.float().unsqueeze(-1) * x.float()).sum(1)
+    return y.to(x.dtype), post.to(x.dtype), comb.to(x.dtype)
+
+
+def mhc_post(x: torch.Tensor, res: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+    """Hyper-connection post-mix: out[t, i] = post[t, i] x[t] + sum_j comb[t, j, i] res[t, j]; x [T, D], res [T, h, D].
+    Parity: reference models/glm5_next/glm5_next.py:96-97."""
+    out = post.float().unsqueeze(-1) * x.float().unsqueeze(1) + torch.einsum("tji,tjd->tid", comb.float(), res.float())
+    return out.to(res.dtype)
 
 
 def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:

@@ -264,19 +264,32 @@ def layernorm(x, w, b, eps):
     return y.view(shape).to(x.dtype)
 
 
-def silu_and_mul(x: torch.Tensor, quant: bool = False):
-    """SwiGLU of [gate | up].  `quant`: return only the 1x128 block-quantised result (for an fp8 down projection)."""
+def _act_args(act):
+    """(mode, p0, p1) of the gated activation for ne_act_mul; see ops.reference.glu_act."""
+    if act is None:
+        return _c.c_int(0), _c.c_float(0.0), _c.c_float(0.0)
+    if act[0] == "clamp":
+        return _c.c_int(1), _c.c_float(float(act[1])), _c.c_float(0.0)
+    if act[0] == "situ":
+        return _c.c_int(2), _c.c_float(float(act[1])), _c.c_float(float(act[2] or 0.0))
+    raise ValueError(f"unknown gated activation {act!r}")
+
+
+def silu_and_mul(x: torch.Tensor, quant: bool = False, act=None):
+    """Gated activation of [gate | up] (SwiGLU unless `act` says otherwise).  `quant`: return only the 1x128 block-quantised
+    result (for an fp8 down projection)."""
     T, I2 = x.shape
     I = I2 // 2
     x = x.contiguous()
     if quant and I % 128 == 0 and T > 0:
         q = torch.empty(T, I, dtype=FP8, device=x.device)
         sc = torch.empty(I // 128, T, dtype=torch.float32, device=x.device)
-        _ck(lib().ne_silu_mul(_p(x), _p(None), _p(q), _p(sc), _c.c_int(T), _c.c_longlong(0), _p(None), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I),
-                              _st()), "ne_silu_mul")
+        _ck(lib().ne_act_mul(_p(x), _p(None), _p(q), _p(sc), _c.c_int(T), _c.c_longlong(0), _p(None), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I),
+                             *_act_args(act), _st()), "ne_act_mul")
         return PrequantizedActivation(q, sc)
     y = torch.empty(T, I, dtype=torch.bfloat16, device=x.device)
-    _ck(lib().ne_silu_mul(_p(x), _p(y), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(None), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I), _st()), "ne_silu_mul")
+    _ck(lib().ne_act_mul(_p(x), _p(y), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(None), _p(None), _c.c_int(1), _c.c_int(T), _c.c_int(I),
+                         *_act_args(act), _st()), "ne_act_mul")
     return y
 
 
@@ -415,7 +428,7 @@ def moe_route(logits, bias, top_k, n_group=1, topk_group=1, norm_topk_prob=True,
     return idx, w
 
 
-def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0, add_in=None) -> torch.Tensor:
+def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, expert_offset: int = 0, add_in=None, act=None) -> torch.Tensor:
     """Local routed experts over an expert-major, 128-row-aligned layout: scatter (+fp8 quant) -> grouped GEMM ->
     SwiGLU (+requant) -> grouped GEMM -> weighted gather.  `add_in` (e.g. the shared-expert output) is summed in the gather."""
     T, H = x.shape
@@ -451,12 +464,14 @@ def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, exp
         _gemm(a_q, H, 0, w13, g, I2, 0, R, I2, H, E, counts, row_start, True, a_s, R, 0, w13_scale, False)
         h_q = torch.empty(R, I, dtype=FP8, device=dev)
         h_s = torch.empty(I // 128, R, dtype=torch.float32, device=dev)
-        _ck(lib().ne_silu_mul(_p(g), _p(None), _p(h_q), _p(h_s), _c.c_int(R), _c.c_longlong(0), _p(counts), _p(row_start), _c.c_int(E), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
+        _ck(lib().ne_act_mul(_p(g), _p(None), _p(h_q), _p(h_s), _c.c_int(R), _c.c_longlong(0), _p(counts), _p(row_start), _c.c_int(E), _c.c_int(R), _c.c_int(I),
+                             *_act_args(act), _st()), "ne_act_mul")
         _gemm(h_q, I, 0, w2, y, H, 0, R, H, I, E, counts, row_start, True, h_s, R, 0, w2_scale, False)
     else:
         _gemm(a_b, H, 0, w13, g, I2, 0, R, I2, H, E, counts, row_start, False, None, 0, 0, None, False)
         h = torch.empty(R, I, dtype=torch.bfloat16, device=dev)
-        _ck(lib().ne_silu_mul(_p(g), _p(h), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(counts), _p(row_start), _c.c_int(E), _c.c_int(R), _c.c_int(I), _st()), "ne_silu_mul")
+        _ck(lib().ne_act_mul(_p(g), _p(h), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(counts), _p(row_start), _c.c_int(E), _c.c_int(R), _c.c_int(I),
+                             *_act_args(act), _st()), "ne_act_mul")
         _gemm(h, I, 0, w2, y, H, 0, R, H, I, E, counts, row_start, False, None, 0, 0, None, False)
     if callable(add_in):
         add_in = add_in()          # produced on another stream: the callable joins that stream as late as possible
@@ -683,6 +698,56 @@ def kda_recurrent(q, k, v, raw_g, b, A_log, dt_bias, lower_bound, state, slots, 
                           _st()), "ne_gdn_step")
     w = norm_w.expand(Dv) if norm_w.numel() == Dv else norm_w
     return rmsnorm_gated(raw, gate, w.contiguous(), eps, sigmoid=True).view(T, H * Dv)
+
+
+def sigmoid_mul(o: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """o * sigmoid(g) over rows [T, W]; g may have a row stride."""
+    T, W = o.shape
+    o = o.contiguous()
+    assert o.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and g.shape == o.shape and g.stride(1) == 1
+    out = torch.empty_like(o)
+    _ck(lib().ne_sigmoid_mul(_p(o), _p(g), _c.c_longlong(g.stride(0)), _p(out), _c.c_longlong(T), _c.c_int(W), _st()), "ne_sigmoid_mul")
+    return out
+
+
+def attn_res_mix(prefix: torch.Tensor, bank: torch.Tensor, valid: int, w_score: torch.Tensor, w_out: torch.Tensor, eps: float,
+                 write_row: int = -1) -> torch.Tensor:
+    """Block attention residual: softmax mixture of the first `valid` bank rows and the running prefix, then RMSNorm; one
+    kernel, one CTA per token.  `write_row` >= 0 also stores the prefix into that bank row."""
+    T, D = prefix.shape
+    assert prefix.dtype == torch.bfloat16 and bank.dtype == torch.bfloat16 and prefix.stride(1) == 1 and bank.stride(2) == 1
+    assert bank.shape[0] >= T and bank.shape[2] == D and w_score.dtype == torch.float32 and w_score.is_contiguous() and w_out.dtype == torch.bfloat16
+    out = torch.empty(T, D, dtype=torch.bfloat16, device=prefix.device)
+    _ck(lib().ne_attn_res(_p(prefix), _c.c_longlong(prefix.stride(0)), _p(bank), _c.c_longlong(bank.stride(0)), _c.c_longlong(bank.stride(1)),
+                          _c.c_int(valid), _p(w_score), _p(w_out), _c.c_float(eps), _p(out), _c.c_longlong(D), _c.c_int(T), _c.c_int(D),
+                          _c.c_int(write_row), _st()), "ne_attn_res")
+    return out
+
+
+def mhc_pre(x: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, iters: int, eps: float):
+    """Hyper-connection pre-mix in one kernel (coefficients, Sinkhorn normalisation and stream contraction)."""
+    T, h, D = x.shape
+    x = x.contiguous()
+    assert x.dtype == torch.bfloat16 and fn.dtype == torch.float32 and fn.is_contiguous() and fn.shape == ((2 + h) * h, h * D)
+    assert base.dtype == torch.float32 and scale.dtype == torch.float32
+    y = torch.empty(T, D, dtype=torch.bfloat16, device=x.device)
+    post = torch.empty(T, h, dtype=torch.bfloat16, device=x.device)
+    comb = torch.empty(T, h, h, dtype=torch.bfloat16, device=x.device)
+    _ck(lib().ne_mhc_pre(_p(x), _p(fn), _p(base), _p(scale), _p(y), _p(post), _p(comb), _c.c_int(T), _c.c_int(h), _c.c_int(D), _c.c_int(iters),
+                         _c.c_float(eps), _st()), "ne_mhc_pre")
+    return y, post, comb
+
+
+def mhc_post(x: torch.Tensor, res: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+    """Hyper-connection post-mix: out[t, i] = post[t, i] x[t] + sum_j comb[t, j, i] res[t, j]."""
+    T, h, D = res.shape
+    res = res.contiguous()
+    assert x.dtype == torch.bfloat16 and res.dtype == torch.bfloat16 and x.stride(1) == 1 and post.is_contiguous() and comb.is_contiguous()
+    assert post.dtype == torch.bfloat16 and comb.dtype == torch.bfloat16
+    out = torch.empty(T, h, D, dtype=torch.bfloat16, device=x.device)
+    _ck(lib().ne_mhc_post(_p(x), _c.c_longlong(x.stride(0)), _p(res), _p(post), _p(comb), _p(out), _c.c_longlong(T), _c.c_int(h), _c.c_int(D), _st()),
+        "ne_mhc_post")
+    return out
 
 
 def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:

@@ -118,6 +118,7 @@ class FusedEP:
         epoch, ctr = _k._p(self.state), _c.c_void_p(self.state.data_ptr() + 4)
         st = _k._st()
         c1, c2 = self._comms()
+        act = _k._act_args(getattr(experts, "act", None))
         cnt = self.heap.peer_ptrs[self.layout.rank] + self.layout.off_cnt       # per-expert row counts, filled by the senders' atomics
         _k._ck(lib.ne_ep_dispatch(L, _k._p(x), _k._p(idx), _k._p(self.pair_ok), _c.c_int(T * K), epoch, ctr, st), "ne_ep_dispatch")
         if self.fp8:
@@ -125,15 +126,15 @@ class FusedEP:
             a_s = self.b_as.view(torch.float32, (E, H // 128, C))
             _k._gemm_comm(aq, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, cnt, True, a_s, C,
                           (H // 128) * C, experts.gate_up_scale, c1)
-            _k._ck(lib.ne_silu_mul(_k._p(self.g), _k._p(None), _k._p(self.h_q), _k._p(self.h_s), _c.c_int(C), _c.c_longlong((I // 128) * C),
-                                   _c.c_void_p(cnt), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
+            _k._ck(lib.ne_act_mul(_k._p(self.g), _k._p(None), _k._p(self.h_q), _k._p(self.h_s), _c.c_int(C), _c.c_longlong((I // 128) * C),
+                                  _c.c_void_p(cnt), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), *act, st), "ne_act_mul")
             _k._gemm_comm(self.h_q, I, C * I, experts.down_proj, self.g, H, 0, C, H, I, E, cnt, True, self.h_s, C,
                           (I // 128) * C, experts.down_scale, c2)
         else:
             ab = self.b_abf.view(torch.bfloat16, (E, C, H))
             _k._gemm_comm(ab, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, cnt, False, None, 0, 0, None, c1)
-            _k._ck(lib.ne_silu_mul(_k._p(self.g), _k._p(self.h), _k._p(None), _k._p(None), _c.c_int(0), _c.c_longlong(0),
-                                   _c.c_void_p(cnt), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), st), "ne_silu_mul")
+            _k._ck(lib.ne_act_mul(_k._p(self.g), _k._p(self.h), _k._p(None), _k._p(None), _c.c_int(0), _c.c_longlong(0),
+                                  _c.c_void_p(cnt), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), *act, st), "ne_act_mul")
             _k._gemm_comm(self.h, I, C * I, experts.down_proj, self.g, H, 0, C, H, I, E, cnt, False, None, 0, 0, None, c2)
         if callable(add_in):
             add_in = add_in()      # shared-expert output from the side stream: joined right before it is consumed
@@ -155,7 +156,9 @@ def install(config, dist_ctx) -> Optional[FusedEP]:
     max_tokens = max(config.max_num_batched_tokens, config.max_num_seqs * (1 + config.num_speculative_tokens))
     from .eplb import active_plan
     plan = active_plan()
-    be = FusedEP(group, dist_ctx.ep_rank, dist_ctx.ep_size, plan.num_physical if plan is not None else mc.n_routed_experts, mc.hidden_size, mc.moe_intermediate_size,
+    be = FusedEP(group, dist_ctx.ep_rank, dist_ctx.ep_size, plan.num_physical if plan is not None else mc.n_routed_experts,
+                 mc.routed_expert_hidden_size or mc.hidden_size,      # latent experts exchange the down-projected rows
+                 mc.moe_intermediate_size,
                  mc.num_experts_per_tok, max_tokens, mc.quant == "fp8")
     ep.set_fused_backend(be)
     return be

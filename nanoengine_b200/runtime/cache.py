@@ -90,6 +90,13 @@ def make_cache_plan(mc: ModelConfig, kv_dtype_name: str, block_size: int, attn_t
                     use_indexer: bool = True, num_layers: Optional[int] = None, state_slots: int = 0) -> CachePlan:
     L = (num_layers if num_layers is not None else mc.num_hidden_layers) + num_mtp_layers
     dt = torch_dtype(kv_dtype_name)
+    if mc.is_hybrid_gdn and mc.is_mla:
+        # delta-attention layers between MLA layers (GLM5-next, Kimi-K3): latent pages for the full-attention layers (and the
+        # MTP layers), one state slot per sequence for the linear ones
+        return CachePlan(True, False, mc.has_indexer and use_indexer, mc.num_layers_of("full_attention") + num_mtp_layers, block_size, dt,
+                         mc.mla_cache_dim, index_dim=mc.index_head_dim, gdn=True, gdn_layers=mc.num_layers_of("linear_attention"),
+                         state_slots=state_slots, conv_dim=mc.gdn_conv_dim, conv_k=mc.linear_conv_kernel_dim,
+                         gdn_heads=mc.linear_num_value_heads, gdn_dv=mc.linear_value_head_dim, gdn_dk=mc.linear_key_head_dim)
     if mc.is_hybrid_gdn:
         return CachePlan(False, True, False, mc.num_layers_of("full_attention"), block_size, dt, mc.head_dim,
                          kv_heads_local=max(1, mc.num_key_value_heads // attn_tp), gdn=True, gdn_layers=mc.num_layers_of("linear_attention"),
