@@ -39,7 +39,9 @@ class KimiDeltaAttention(nn.Module):
         self.eps = cfg.rms_norm_eps
         H = cfg.hidden_size
         self.qkvg_proj = QLinear(H, self.conv_dim + self.value_dim, dtype, device, None)       # [q | k | v | output gate]
-        self.fa_b_proj = QLinear(H, self.dk + self.h, dtype, device, None)                     # [forget-gate bottleneck | beta logits]
+        # [forget-gate bottleneck | beta logits], rows padded to a multiple of 16 (the GEMM wants N % 8 == 0)
+        self.fab_rows = (self.dk + self.h + 15) // 16 * 16
+        self.fa_b_proj = QLinear(H, self.fab_rows, dtype, device, None)
         self.f_b_proj = QLinear(self.dk, self.key_dim, dtype, device, None)
         self.o_proj = QLinear(self.value_dim, H, dtype, device, None)
         self.conv_weight = nn.Parameter(torch.zeros(self.conv_dim, self.conv_k, dtype=dtype, device=device), requires_grad=False)
@@ -59,7 +61,7 @@ class KimiDeltaAttention(nn.Module):
         q = y[:, : self.key_dim].view(T, self.h, self.dk)
         k = y[:, self.key_dim: 2 * self.key_dim].view(T, self.h, self.dk)
         v = y[:, 2 * self.key_dim:].view(T, self.h, self.dv)
-        o = ops.kda_recurrent(q, k, v, raw_g, ab[:, self.dk:], self.A_log, self.dt_bias, self.lower_bound, ctx.rec_states[self.state_idx],
+        o = ops.kda_recurrent(q, k, v, raw_g, ab[:, self.dk: self.dk + self.h], self.A_log, self.dt_bias, self.lower_bound, ctx.rec_states[self.state_idx],
                               ctx.state_slots, ctx.cu_seqlens_q, ctx.seq_fresh, gate.view(T, self.h, self.dv), self.o_norm_weight, self.eps)
         return self.o_proj(o)
 
@@ -90,7 +92,9 @@ class KimiDeltaAttention(nn.Module):
                 P.pop("g_lr")
             return True
         if name in ("f_a_proj", "b_proj"):
-            return group("fab", name, ("f_a_proj", "b_proj"), self.fa_b_proj.set_weight)
+            def set_fab(m):
+                self.fa_b_proj.set_weight(torch.cat([m, m.new_zeros(self.fab_rows - m.shape[0], m.shape[1])], 0))
+            return group("fab", name, ("f_a_proj", "b_proj"), set_fab)
         if name == "f_b_proj":
             self.f_b_proj.set_weight(w); return True
         if name == "o_proj":

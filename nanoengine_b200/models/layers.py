@@ -33,12 +33,16 @@ class QLinear(nn.Module):
             self.weight_scale_inv = nn.Parameter(torch.ones(_ceil_div(out_features, 128), _ceil_div(in_features, 128),
                                                             dtype=torch.float32, device=device), requires_grad=False)
         else:
-            self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device), requires_grad=False)
+            # the tensor-core GEMM wants a multiple of 8 output columns: a narrower projection keeps zero rows below its own
+            rows = _ceil_div(out_features, 8) * 8 if not bias else out_features
+            self.weight = nn.Parameter((torch.zeros if rows != out_features else torch.empty)(rows, in_features, dtype=dtype, device=device),
+                                       requires_grad=False)
             self.weight_scale_inv = None
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device), requires_grad=False) if bias else None
 
     def forward(self, x):
-        return ops.linear(x, self.weight, self.weight_scale_inv, self.bias)
+        y = ops.linear(x, self.weight, self.weight_scale_inv, self.bias)
+        return y if y.shape[-1] == self.out_features else y[..., : self.out_features]
 
     @torch.no_grad()
     def init_random(self, gen: torch.Generator, std: float = 0.02):
@@ -60,7 +64,7 @@ class QLinear(nn.Module):
         else:
             if w.dtype == torch.float8_e4m3fn:
                 w = ref.dequant_fp8_block(w, scale_inv)
-            self.weight.copy_(w.to(self.weight.dtype))
+            self.weight[: self.out_features].copy_(w.to(self.weight.dtype))
 
 
 class RMSNorm(nn.Module):
