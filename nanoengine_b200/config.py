@@ -140,8 +140,18 @@ class Config:
                 raise ValueError("eplb_redundant_experts needs a DeepSeek or Qwen3 MoE model")
             if self.eplb_redundant_experts < 0 or (mc.n_routed_experts + self.eplb_redundant_experts) % self.ffn_ep:
                 raise ValueError("experts + eplb_redundant_experts must divide evenly over ffn_ep")
-        if self.ffn_tp != 1 or self.ffn_dp != 1:
-            raise ValueError("ffn_tp / ffn_dp > 1 are not supported: experts are sharded by ffn_ep only")
+        if self.ffn_dp != 1:
+            raise ValueError("ffn_dp > 1 is not supported: the FFN view is (ffn_ep, ffn_tp)")
+        if self.ffn_tp != 1:
+            # FFN tensor parallelism shares the attention-TP group: dense MLPs and every expert are split by intermediate columns
+            if mc.is_mla or mc.is_hybrid_gdn:
+                raise ValueError("ffn_tp > 1 is offered for the GQA families (Qwen3 dense / MoE) only")
+            if self.ffn_tp != self.attention_tp or self.ffn_ep != 1:
+                raise ValueError("ffn_tp must equal attention_tp with ffn_ep = 1 (the FFN shards reuse the attention-TP group)")
+            for what, size in (("intermediate_size", mc.intermediate_size if not mc.n_routed_experts or mc.first_k_dense_replace else 0),
+                               ("moe_intermediate_size", mc.moe_intermediate_size if mc.n_routed_experts else 0)):
+                if size and (size % self.ffn_tp or (mc.quant == "fp8" and (size // self.ffn_tp) % 128)):
+                    raise ValueError(f"{what} must split evenly over ffn_tp (in 128-wide blocks for fp8 weights)")
         if self.max_model_len is None:
             self.max_model_len = mc.max_position_embeddings
         if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1:

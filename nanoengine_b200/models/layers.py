@@ -100,6 +100,100 @@ class SwiGLUMLP(nn.Module):
         self.down_proj.init_random(gen)
 
 
+class TPSwiGLUMLP(nn.Module):
+    """Dense gated MLP sharded over the tensor-parallel group: gate / up column-parallel, down row-parallel.  Takes this
+    rank's slice of the tokens and returns its slice of the result: all-gather -> GEMM and GEMM -> reduce-scatter, each one
+    fused kernel pair on GPUs with peer access.
+    Parity: reference layers/backends/linear (column / row parallel linears on `ffn_tp_group`), models/kimi_k3/kimi_k3.py:34-70."""
+
+    def __init__(self, hidden: int, inter: int, dtype, device, quant=None, act=None, axis: str = "attn_tp"):
+        super().__init__()
+        d = get_dist_context()
+        self.tp, self.tp_rank, self.axis = d.ffn_tp_size, d.ffn_tp_rank, axis
+        assert inter % self.tp == 0 and (quant != "fp8" or (inter // self.tp) % 128 == 0), "intermediate size must split over ffn_tp (in 128-wide blocks for fp8)"
+        self.inter, self.inter_local = inter, inter // self.tp
+        self.gate_up_proj = QLinear(hidden, 2 * self.inter_local, dtype, device, quant)
+        self.down_proj = QLinear(self.inter_local, hidden, dtype, device, quant)
+        self.act = act
+
+    def forward(self, x_slice, total_rows: int):
+        from ..parallel.tp import tp_all_gather_linear, tp_linear_reduce_scatter
+        g = tp_all_gather_linear(ops.dense(x_slice), total_rows, self.gate_up_proj, self.axis)
+        return tp_linear_reduce_scatter(ops.silu_and_mul(g, act=self.act), self.down_proj, self.axis)
+
+    def shard_rows(self):
+        """Row range of gate_proj / up_proj (and column range of down_proj) this rank holds."""
+        return self.tp_rank * self.inter_local, (self.tp_rank + 1) * self.inter_local
+
+
+class VocabParallelEmbedding(nn.Module):
+    """Embedding table split by vocabulary rows over the tensor-parallel group: each rank looks up the ids it owns (zeros for
+    the rest) and the partial rows are summed.  `forward_scatter` returns this rank's slice of the tokens directly
+    (reduce-scatter), which is what the token-sliced residual stream wants.
+    Parity: reference layers/embed_head.py:49-94."""
+
+    def __init__(self, vocab: int, hidden: int, dtype, device, axis: str = "attn_tp"):
+        super().__init__()
+        d = get_dist_context()
+        self.tp, self.rank, self.axis = d.attn_tp_size, d.attn_tp_rank, axis
+        self.vocab = vocab
+        self.per = -(-vocab // self.tp)
+        self.lo = self.rank * self.per
+        self.weight = nn.Parameter(torch.zeros(self.per, hidden, dtype=dtype, device=device), requires_grad=False)
+
+    def _partial(self, ids):
+        local = ids - self.lo
+        ok = (local >= 0) & (local < self.per)
+        rows = self.weight[local.clamp(0, self.per - 1)]
+        return rows * ok.unsqueeze(-1).to(rows.dtype)
+
+    def forward(self, ids):
+        from ..parallel.tp import tp_all_reduce
+        return tp_all_reduce(self._partial(ids), self.axis)
+
+    def forward_scatter(self, ids):
+        from ..parallel.tp import tp_reduce_scatter
+        return tp_reduce_scatter(self._partial(ids), self.axis)
+
+    @torch.no_grad()
+    def load_full(self, w: torch.Tensor):
+        part = w[self.lo: self.lo + self.per]
+        self.weight.zero_()
+        self.weight[: part.shape[0]].copy_(part.to(self.weight.dtype))
+
+
+class ParallelLMHead(nn.Module):
+    """Output projection split by vocabulary rows: every rank computes the logits of its rows, the shards are gathered.
+    Parity: reference layers/embed_head.py:97-131."""
+
+    def __init__(self, vocab: int, hidden: int, dtype, device, axis: str = "attn_tp"):
+        super().__init__()
+        d = get_dist_context()
+        self.tp, self.rank, self.axis = d.attn_tp_size, d.attn_tp_rank, axis
+        self.vocab = vocab
+        self.per = -(-vocab // self.tp)
+        self.per = (self.per + 7) // 8 * 8
+        self.lo = self.rank * self.per
+        self.weight = nn.Parameter(torch.zeros(self.per, hidden, dtype=dtype, device=device), requires_grad=False)
+
+    def forward(self, hidden):
+        import torch.distributed as dist
+        local = ops.lm_head(hidden, self.weight)                                  # [B, per] fp32
+        g = get_dist_context().group(self.axis)
+        if g is None:
+            return local[:, : self.vocab]
+        B = local.shape[0]
+        out = local.new_empty(self.tp * B, self.per)                                # shard r occupies rows [r * B, (r + 1) * B)
+        dist.all_gather_into_tensor(out, local.contiguous(), group=g)
+        return out.view(self.tp, B, self.per).permute(1, 0, 2).reshape(B, self.tp * self.per)[:, : self.vocab]
+
+    @torch.no_grad()
+    def load_full(self, w: torch.Tensor):
+        part = w[self.lo: self.lo + self.per]
+        self.weight.zero_()
+        self.weight[: part.shape[0]].copy_(part.to(self.weight.dtype))
+
+
 class RoutedExperts(nn.Module):
     """The experts this rank owns: ids [ep_rank*E_local, (ep_rank+1)*E_local), stacked for grouped GEMMs."""
 
@@ -117,6 +211,12 @@ class RoutedExperts(nn.Module):
             self.phy2log = plan.phy2log[layer_idx].tolist()
             num_experts = plan.num_physical
         assert num_experts % d.ep_size == 0, "experts must divide evenly over the EP group"
+        # with ffn_tp > 1 every expert's intermediate dimension is split over the TP group (this rank holds rows
+        # [tp_rank * I/tp, (tp_rank + 1) * I/tp) of gate / up and the same columns of down); the caller sums the partial outputs
+        self.inter_full, self.ffn_tp, self.ffn_tp_rank = inter, d.ffn_tp_size, d.ffn_tp_rank
+        if self.ffn_tp > 1:
+            assert inter % self.ffn_tp == 0 and (quant != "fp8" or (inter // self.ffn_tp) % 128 == 0), "expert intermediate size must split over ffn_tp"
+            inter = inter // self.ffn_tp
         self.num_experts, self.hidden, self.inter, self.quant = num_experts, hidden, inter, quant
         self.num_local = num_experts // d.ep_size
         self.expert_offset = d.ep_rank * self.num_local
@@ -142,8 +242,19 @@ class RoutedExperts(nn.Module):
 
     @torch.no_grad()
     def load_expert(self, logical_id: int, which: str, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None) -> bool:
-        """Store one logical expert's matrix into every local slot that holds it; False when this rank holds none."""
+        """Store one logical expert's matrix into every local slot that holds it; False when this rank holds none.  A full-size
+        matrix is cut to this rank's ffn_tp shard first."""
         slots = self.local_slots_of(logical_id)
+        if slots and self.ffn_tp > 1:
+            lo, hi = self.ffn_tp_rank * self.inter, (self.ffn_tp_rank + 1) * self.inter
+            if which == "down" and w.shape[1] == self.inter_full:
+                w = w[:, lo:hi].contiguous()
+                if scale_inv is not None:
+                    scale_inv = scale_inv[:, lo // 128: hi // 128].contiguous()
+            elif which != "down" and w.shape[0] == self.inter_full:
+                w = w[lo:hi].contiguous()
+                if scale_inv is not None:
+                    scale_inv = scale_inv[lo // 128: hi // 128].contiguous()
         for s in slots:
             self.set_expert(s, which, w, scale_inv)
         return bool(slots)

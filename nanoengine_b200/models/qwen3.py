@@ -24,7 +24,10 @@ from ..parallel.ep import ep_moe_forward
 from ..parallel.tp import tp_all_gather, tp_all_gather_linear, tp_linear_reduce_scatter, tp_reduce_scatter
 from ..runtime.context import ForwardContext
 from .config import ModelConfig
-from .layers import QLinear, RMSNorm, RoutedExperts, SwiGLUMLP
+from .layers import ParallelLMHead, QLinear, RMSNorm, RoutedExperts, SwiGLUMLP, TPSwiGLUMLP, VocabParallelEmbedding
+
+
+VOCAB_PARALLEL = True     # split embed_tokens / lm_head by vocabulary rows whenever attention is tensor-parallel
 
 
 class Qwen3Attention(nn.Module):
@@ -66,13 +69,20 @@ class Qwen3MoE(nn.Module):
         self.gate_weight = nn.Parameter(torch.empty(cfg.n_routed_experts, cfg.hidden_size, dtype=torch.float32, device=device), requires_grad=False)
         self.experts = RoutedExperts(cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, dtype, device, cfg.quant, layer_idx)
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, total_rows: Optional[int] = None):
         c = self.cfg
         x = ops.dense(x)
+        ffn_tp = self.experts.ffn_tp > 1
+        if ffn_tp:
+            # experts split by intermediate columns over the TP group: every rank works on all tokens with its share of each
+            # expert and the partial outputs are reduce-scattered back to the token slices
+            from ..parallel.tp import tp_all_gather, tp_reduce_scatter
+            x = tp_all_gather(x, total_rows)
         logits = ops.router_logits(x, self.gate_weight)
         from ..parallel.ep import routing_options
         idx, w = ops.moe_route(logits, None, c.num_experts_per_tok, 1, 1, c.norm_topk_prob, 1.0, "softmax", **routing_options(self.layer_idx, x.device))
-        return ep_moe_forward(self.experts, x, idx, w, ctx)
+        out = ep_moe_forward(self.experts, x, idx, w, ctx)
+        return tp_reduce_scatter(out) if ffn_tp else out
 
 
 class Qwen3DecoderLayer(nn.Module):
@@ -83,13 +93,22 @@ class Qwen3DecoderLayer(nn.Module):
         self.self_attn = Qwen3Attention(cfg, layer_idx, dtype, device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, quant_out=fp8)
         self.is_moe = cfg.is_moe_layer(layer_idx)
-        self.mlp = Qwen3MoE(cfg, dtype, device, layer_idx) if self.is_moe else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
+        self.ffn_tp = get_dist_context().ffn_tp_size > 1
+        if self.is_moe:
+            self.mlp = Qwen3MoE(cfg, dtype, device, layer_idx)
+        elif self.ffn_tp:
+            self.mlp = TPSwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
+        else:
+            self.mlp = SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quant)
 
     def forward(self, h, residual, positions, ctx, rope_cache, total_rows):
         x, residual = self.input_layernorm(h, residual) if residual is not None else (self.input_layernorm(h), h)
         a = self.self_attn(x, positions, ctx, rope_cache, total_rows)
         x, residual = self.post_attention_layernorm(a, residual)
-        m = self.mlp(x, ctx) if self.is_moe else self.mlp(x)
+        if self.is_moe:
+            m = self.mlp(x, ctx, total_rows)
+        else:
+            m = self.mlp(x, total_rows) if self.ffn_tp else self.mlp(x)
         return m, residual
 
 
@@ -101,10 +120,16 @@ class Qwen3MoeForCausalLM(nn.Module):
         self.cfg, self.dtype = cfg, dtype
         d = get_dist_context()
         self.tp, self.tp_rank = d.attn_tp_size, d.attn_tp_rank
-        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+        # with tensor-parallel attention the embedding table and the output projection are split by vocabulary rows
+        self.vocab_parallel = self.tp > 1 and VOCAB_PARALLEL
+        if self.vocab_parallel:
+            self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, dtype, device)
+            self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, dtype, device)
+        else:
+            self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+            self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False, dtype=dtype, device=device)
         self.layers = nn.ModuleList([Qwen3DecoderLayer(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
-        self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False, dtype=dtype, device=device)
         rc = ref.rope_cos_sin_cache(cfg.head_dim, cfg.max_position_embeddings, cfg.rope_theta, cfg.rope_scaling)
         self.register_buffer("rope_cache", rc.to(device), persistent=False)
         for p in self.parameters():
@@ -115,9 +140,13 @@ class Qwen3MoeForCausalLM(nn.Module):
         return self.cfg.num_hidden_layers
 
     def forward(self, input_ids, positions, ctx: ForwardContext, inputs_embeds=None):
-        h = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
-        T = h.shape[0]
-        if self.tp > 1:
+        if self.vocab_parallel and inputs_embeds is None:
+            T = input_ids.shape[0]
+            h = self.embed_tokens.forward_scatter(input_ids)          # partial rows summed straight into the token slices
+        else:
+            h = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+            T = h.shape[0]
+        if self.tp > 1 and not (self.vocab_parallel and inputs_embeds is None):
             per = -(-T // self.tp)
             pad = per * self.tp - T
             if pad:
@@ -130,6 +159,8 @@ class Qwen3MoeForCausalLM(nn.Module):
         return tp_all_gather(h, T) if self.tp > 1 else h
 
     def compute_logits(self, hidden):
+        if self.vocab_parallel:
+            return self.lm_head(hidden)
         return ops.lm_head(hidden, self.lm_head.weight)
 
     # ---- weights ---------------------------------------------------------------------------
@@ -148,9 +179,9 @@ class Qwen3MoeForCausalLM(nn.Module):
             nonlocal n
             n += 1
             if base == "model.embed_tokens":
-                self.embed_tokens.weight.copy_(w.to(self.dtype)); return
+                (self.embed_tokens.load_full(w) if self.vocab_parallel else self.embed_tokens.weight.copy_(w.to(self.dtype))); return
             if base == "lm_head":
-                self.lm_head.weight.copy_(w.to(self.dtype)); return
+                (self.lm_head.load_full(w) if self.vocab_parallel else self.lm_head.weight.copy_(w.to(self.dtype))); return
             if base == "model.norm":
                 self.norm.weight.copy_(w.to(self.dtype)); return
             m = re.match(r"model\.layers\.(\d+)\.(.*)", base)
@@ -193,11 +224,18 @@ class Qwen3MoeForCausalLM(nn.Module):
             if rest in ("mlp.gate_proj", "mlp.up_proj"):
                 key = f"{m.group(1)}.gate_up"
                 g = pending.setdefault(key, {})
-                g[rest.split(".")[1]] = deq(w, s)
+                wf = deq(w, s)
+                if L.ffn_tp:
+                    lo, hi = L.mlp.shard_rows()
+                    wf = wf[lo:hi]
+                g[rest.split(".")[1]] = wf
                 if len(g) == 2:
                     L.mlp.gate_up_proj.set_weight(torch.cat([g["gate_proj"], g["up_proj"]], 0)); pending.pop(key)
                 return
             if rest == "mlp.down_proj":
+                if L.ffn_tp:
+                    lo, hi = L.mlp.shard_rows()
+                    L.mlp.down_proj.set_weight(deq(w, s)[:, lo:hi].contiguous()); return
                 L.mlp.down_proj.set_weight(w, s); return
 
         wbuf = {}

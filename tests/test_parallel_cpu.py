@@ -62,6 +62,23 @@ def test_tp2_ep2_qwen3_moe_matches_single_rank():
     assert got == want
 
 
+@pytest.mark.parametrize("moe", [False, True])
+def test_tp2_ffn_tp2_with_vocab_parallel_head_matches_single_rank(moe):
+    """Attention-TP 2 with the FFN split by intermediate columns over the same two ranks (dense MLP: all-gather -> GEMM and
+    GEMM -> reduce-scatter; experts: every rank holds half of every expert) and the embedding table / output projection split by
+    vocabulary rows (509 rows: the last shard is padded)."""
+    mc = _qwen_cfg()
+    mc.vocab_size = 509
+    if not moe:
+        mc.n_routed_experts = 0
+    base = dict(model="qwen3-tiny", dummy_weight=True, dtype="float32", device="cpu", kvcache_block_size=16, max_num_seqs=8, num_kvcache_blocks=64)
+    prompts = _prompts(3, 21, 2, 509)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = _run(Config(**base, model_config=mc), prompts, sp)
+    got = _run(Config(**base, model_config=mc, attention_tp=2, ffn_tp=2), prompts, sp)
+    assert got == want
+
+
 def test_dead_worker_is_reported():
     from nanoengine_b200.engine.executor import ExecutorError, MultiprocExecutor
     cfg = Config(model="tiny-deepseek-v3", dtype="float32", device="cpu", kvcache_block_size=16, num_kvcache_blocks=32, attention_dp=2, ffn_ep=2)

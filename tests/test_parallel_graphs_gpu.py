@@ -17,12 +17,16 @@ def _run(rank, world, port, case, eager, q):
         from nanoengine_b200 import Config, LLM, SamplingParams
         from nanoengine_b200.models.config import PRESETS
         from nanoengine_b200.ops import sm100
-        if case == "qwen3_tp2":
+        if case in ("qwen3_tp2", "qwen3_tp2_ffn_tp2", "qwen3_dense_tp2_ffn_tp2"):
+            ffn_tp = case != "qwen3_tp2"                                # experts / dense MLP split by intermediate columns, vocab-parallel head
             mc = PRESETS["qwen3-235b-a22b"](num_hidden_layers=3, hidden_size=1024, num_attention_heads=16, num_key_value_heads=4, head_dim=128,
                                             n_routed_experts=8, moe_intermediate_size=256, num_experts_per_tok=2, vocab_size=2048,
                                             max_position_embeddings=4096)
+            if case == "qwen3_dense_tp2_ffn_tp2":
+                mc.n_routed_experts, mc.intermediate_size = 0, 2048
             cfg = Config(model="qwen3-235b-a22b", model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kvcache_block_size=64,
-                         num_kvcache_blocks=64, max_num_seqs=8, attention_tp=world, ffn_ep=world, executor_backend="spmd", seed=0,
+                         num_kvcache_blocks=64, max_num_seqs=8, attention_tp=world, ffn_ep=1 if ffn_tp else world, ffn_tp=world if ffn_tp else 1,
+                         executor_backend="spmd", seed=0,
                          enforce_eager=eager, peer_timeout_s=60.0)
             prompts = [torch.randint(0, 2048, (n,), generator=torch.Generator().manual_seed(5 + i)).tolist() for i, n in enumerate((40, 70, 9))]
             late = [torch.randint(0, 2048, (33,), generator=torch.Generator().manual_seed(99)).tolist()]
@@ -76,7 +80,7 @@ def _launch(case, eager):
     return {rank: toks for rank, toks, _ in res}
 
 
-@pytest.mark.parametrize("case", ["qwen3_tp2", "deepseek_dp2_ep2_unequal"])
+@pytest.mark.parametrize("case", ["qwen3_tp2", "qwen3_tp2_ffn_tp2", "qwen3_dense_tp2_ffn_tp2", "deepseek_dp2_ep2_unequal"])
 def test_graphs_with_collectives_match_eager(case):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -86,5 +90,5 @@ def test_graphs_with_collectives_match_eager(case):
         assert len(a_all) == len(b_all) and all(len(a) == len(b) for a, b in zip(a_all, b_all))
         same = sum(a == b for a, b in zip(a_all, b_all))
         assert same >= len(a_all) - 1 and all(a[:3] == b[:3] for a, b in zip(a_all, b_all)), (rank, a_all, b_all)
-    if case == "qwen3_tp2":
+    if case.startswith("qwen3"):
         assert graph[0] == graph[1]                                     # TP ranks serve the same requests
