@@ -253,12 +253,13 @@ __device__ __forceinline__ uint32_t float_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);          // larger float <=> larger key
 }
 
-// One CTA per token.  out [T, k] int32: physical slot ids of the k best visible keys (any order), -1 padded.
+// One CTA per token.  out [T, k] int32: physical slot ids of the k best visible keys (keys above the k-th value in position order, then the
+// ties that fill the list, also in position order), -1 padded.
 __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restrict__ logits, long long ld, const int* __restrict__ cu_seqlens_q,
                                                            const int* __restrict__ context_lens, int num_seqs, const int* __restrict__ block_tables,
                                                            int bt_stride, int bs, int k, int* __restrict__ out) {
   __shared__ int hist[2048];
-  __shared__ uint32_t s_prefix; __shared__ int s_remaining, s_cnt_gt, s_cnt_eq;
+  __shared__ uint32_t s_prefix; __shared__ int s_remaining;
   const int t = blockIdx.x;
   int lo = 0, hi = num_seqs;
   while (lo + 1 < hi) { int mid = (lo + hi) >> 1; if (cu_seqlens_q[mid] <= t) lo = mid; else hi = mid; }
@@ -299,18 +300,40 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
   }
   const uint32_t thr = s_prefix;                            // the k-th largest key; s_remaining of its copies are taken
   const int need_eq = s_remaining;
-  if (threadIdx.x == 0) { s_cnt_gt = 0; s_cnt_eq = 0; }
-  __syncthreads();
   const int n_gt = k - need_eq;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const uint32_t key = float_key(row[i]);
-    if (key > thr) {
-      const int pos = atomicAdd(&s_cnt_gt, 1);
+  // Ordered compaction, 1024 keys at a time: keys above the threshold go to o[0, n_gt) and the first `need_eq` keys equal to
+  // it to o[n_gt, k), each group in ascending key position.  The list is the same in every run (slots handed out by atomics
+  // would list the keys in arrival order, and the attention that follows would sum its products in a different order).
+  int* s_wgt = hist;
+  int* s_weq = hist + 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned lt = (1u << lane) - 1u;
+  int base_gt = 0, base_eq = 0;
+  for (int i0 = 0; i0 < n && (base_gt < n_gt || base_eq < need_eq); i0 += 1024) {
+    const int i = i0 + (int)threadIdx.x;
+    const uint32_t key = i < n ? float_key(row[i]) : 0u;
+    const bool gt = i < n && key > thr, eq = i < n && key == thr;
+    const unsigned bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) { s_wgt[warp] = __popc(bg); s_weq[warp] = __popc(be); }
+    __syncthreads();
+    const int wg = s_wgt[lane], we = s_weq[lane];
+    int ig = wg, ie = we;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int vg = __shfl_up_sync(0xffffffffu, ig, d), ve = __shfl_up_sync(0xffffffffu, ie, d);
+      if (lane >= d) { ig += vg; ie += ve; }
+    }
+    const int tot_g = __shfl_sync(0xffffffffu, ig, 31), tot_e = __shfl_sync(0xffffffffu, ie, 31);
+    const int off_g = __shfl_sync(0xffffffffu, ig - wg, warp), off_e = __shfl_sync(0xffffffffu, ie - we, warp);
+    if (gt) {
+      const int pos = base_gt + off_g + __popc(bg & lt);
       if (pos < n_gt) o[pos] = phys(i);
-    } else if (key == thr) {
-      const int pos = atomicAdd(&s_cnt_eq, 1);
+    } else if (eq) {
+      const int pos = base_eq + off_e + __popc(be & lt);
       if (pos < need_eq) o[n_gt + pos] = phys(i);
     }
+    base_gt += tot_g; base_eq += tot_e;
+    __syncthreads();
   }
 }
 

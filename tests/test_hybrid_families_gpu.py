@@ -177,12 +177,7 @@ def test_family_on_gpu_graph_and_eager_agree(family):
                          kvcache_block_size=64, num_kvcache_blocks=32, max_num_seqs=4, enforce_eager=eager, seed=0))
         outs[eager] = [o["token_ids"] for o in llm.generate(prompts, sp)]
         again = [o["token_ids"] for o in llm.generate(prompts, sp)]
-        if family == "kimi_k3":
-            assert again == outs[eager]
-        else:
-            # the top-k selection lists its keys in the order its atomics hand out slots, so the fp8 products of two runs sum in
-            # different orders; with random weights that can flip a late near-tie, the first tokens must agree
-            assert all(a[:2] == b[:2] for a, b in zip(again, outs[eager])), (again, outs[eager])
+        assert again == outs[eager]        # also for the sparse layers: the top-k list comes out in the same order every run
         del llm
         torch.cuda.empty_cache()
     assert all(len(t) == 8 for t in outs[True])
