@@ -140,6 +140,11 @@ class Config:
                 raise ValueError("eplb_redundant_experts needs a DeepSeek or Qwen3 MoE model")
             if self.eplb_redundant_experts < 0 or (mc.n_routed_experts + self.eplb_redundant_experts) % self.ffn_ep:
                 raise ValueError("experts + eplb_redundant_experts must divide evenly over ffn_ep")
+        if mc.num_kv_shared_layers or mc.global_head_dim:
+            # cache layers of different head dims are packed at the front of equal slabs: the page movers (host swap, the L3 file
+            # tier, PD migration) assume one page size per family and are not offered for this family
+            if self.num_host_kvcache_blocks or self.l3_dir or self.mode != "hybrid" or self.attention_tp != 1 or self.pp != 1:
+                raise ValueError("models with per-layer head dims run as a hybrid engine with attention_tp = pp = 1 and no host / L3 tier")
         if self.ffn_dp != 1:
             raise ValueError("ffn_dp > 1 is not supported: the FFN view is (ffn_ep, ffn_tp)")
         if self.ffn_tp != 1:

@@ -28,6 +28,7 @@ struct AttnArgs {
   __nv_bfloat16* out; long long o_tok_stride; int o_head_stride;
   float* lse;                                     // optional [T, H] natural-log LSE
   int T, H, Dk, Dv; float scale; int fp8;
+  int window;                                     // > 0: a query sees only the last `window` key positions up to its own (sliding-window layers)
 };
 
 __device__ __forceinline__ float load_kv(const void* base, long long idx, int fp8) {
@@ -55,6 +56,7 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(const AttnArgs a) {
   const int ctx = a.context_lens[seq];
   const int limit = ctx - q_len + (t - a.cu_seqlens_q[seq]);   // last visible key position
   const int n_keys = a.sparse ? a.topk : limit + 1;
+  const int first_key = (a.window > 0 && !a.sparse) ? max(0, limit - a.window + 1) : 0;
 
   for (int i = threadIdx.x; i < kHeadsPerCta * Dk; i += blockDim.x) {
     int hh = h0 + i / Dk, d = i % Dk;
@@ -72,7 +74,7 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(const AttnArgs a) {
   const float c = a.scale * 1.4426950408889634f;
   const int* bt = a.block_tables + (long long)seq * a.bt_stride;
 
-  for (int k0 = 0; k0 < n_keys; k0 += kKeysPerTile) {
+  for (int k0 = first_key / kKeysPerTile * kKeysPerTile; k0 < n_keys; k0 += kKeysPerTile) {
     __syncthreads();
     // stage 32 key rows (and value rows) as fp32
     for (int r = warp; r < kKeysPerTile; r += 4) {
@@ -95,7 +97,7 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(const AttnArgs a) {
     const float* qr = sq + warp * Dk;
     float s = 0.f;
     for (int d = 0; d < Dk; d++) s = fmaf(qr[d], kr[d], s);
-    bool valid = (k0 + lane < n_keys) && kr[Dk] != 0.f;
+    bool valid = (k0 + lane < n_keys) && (k0 + lane >= first_key) && kr[Dk] != 0.f;
     float tl = valid ? s * c : -INFINITY;
     float m_new = fmaxf(m_run, warp_max(tl));
     if (m_new == -INFINITY) continue;
@@ -212,7 +214,7 @@ extern "C" int ne_attn_generic(const void* q, long long q_tok_stride, int q_head
                                long long kv_slot_stride, int kv_head_stride, int kv_group, const int* block_tables, int bt_stride,
                                int block_size, const int* cu_seqlens_q, const int* context_lens, int num_seqs, const int* sparse, int topk,
                                void* out, long long o_tok_stride, int o_head_stride, float* lse, int T, int H, int Dk, int Dv, float scale,
-                               int fp8, cudaStream_t st) {
+                               int fp8, int window, cudaStream_t st) {
   if (T <= 0) return 0;
   if (Dv > 640 || (kv_group > 1 && kv_group % kHeadsPerCta != 0)) return 1001;
   AttnArgs a;
@@ -220,7 +222,7 @@ extern "C" int ne_attn_generic(const void* q, long long q_tok_stride, int q_head
   a.kv_slot_stride = kv_slot_stride; a.kv_head_stride = kv_head_stride; a.kv_group = kv_group; a.block_tables = block_tables;
   a.bt_stride = bt_stride; a.block_size = block_size; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs;
   a.sparse = sparse; a.topk = topk; a.out = (__nv_bfloat16*)out; a.o_tok_stride = o_tok_stride; a.o_head_stride = o_head_stride; a.lse = lse;
-  a.T = T; a.H = H; a.Dk = Dk; a.Dv = Dv; a.scale = scale; a.fp8 = fp8;
+  a.T = T; a.H = H; a.Dk = Dk; a.Dv = Dv; a.scale = scale; a.fp8 = fp8; a.window = window;
   size_t smem = sizeof(float) * ((size_t)kHeadsPerCta * Dk + (size_t)kKeysPerTile * (Dk + 1) + (v_cache ? (size_t)kKeysPerTile * (Dv + 1) : 0));
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {

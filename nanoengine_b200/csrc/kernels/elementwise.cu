@@ -119,8 +119,10 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); 
 // One (row, 128-column block) item of SwiGLU: 4 columns per lane; bf16 out, or e4m3 with the block's scale at sc[c * sc_ld + row].
 // Gated activation of one (gate, up) pair.  act 0: silu(g) u.  act 1 (clamped SwiGLU, limit p0): up in [-p0, p0], gate <= p0,
 // then silu(g) u (reference layers/activation.py:86-92).  act 2 (SiTU-GLU, p0 = beta, p1 = linear beta or 0):
-// beta tanh(g / beta) sigmoid(g) times p1 tanh(u / p1) (reference kernel/triton/generic/situ.py:24-27).
+// beta tanh(g / beta) sigmoid(g) times p1 tanh(u / p1) (reference kernel/triton/generic/situ.py:24-27).  act 3: GELU(g) u with the
+// tanh approximation (reference models/gemma4/gemma4.py:27-36).
 __device__ __forceinline__ float glu_act(float g, float u, int act, float p0, float p1) {
+  if (act == 3) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;      // tanh-approximated GELU
   if (act == 1) { u = fminf(fmaxf(u, -p0), p0); g = fminf(g, p0); }
   else if (act == 2) {
     if (p1 > 0.f) u = p1 * tanhf(u / p1);
@@ -493,7 +495,7 @@ extern "C" int ne_silu_mul(const void* x, void* y, void* q, float* sc, int sc_ld
 extern "C" int ne_act_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, const int* row_start,
                           int groups, int rows, int I, int act, float p0, float p1, cudaStream_t st) {
   if (groups <= 0 || rows <= 0) return 0;
-  if (act < 0 || act > 2 || (act != 0 && !(p0 > 0.f))) return 1001;
+  if (act < 0 || act > 3 || (act != 0 && !(p0 > 0.f))) return 1001;
   if (I % 128 != 0) return 1001;
   long long warps = (long long)groups * rows * (I / 128);
   long long want = (warps + 7) / 8;

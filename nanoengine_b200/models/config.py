@@ -77,6 +77,17 @@ class ModelConfig:
     hc_eps: float = 1e-6
     swiglu_limit: float = 0.0                # > 0: clamp up to [-L, L] and gate to <= L before silu(gate) * up
     mlp_layer_types: Optional[List[str]] = None    # per layer "dense" | "sparse"; None = first_k_dense_replace / moe_layer_freq rule
+    # Gemma4: sliding-window / global attention layers with their own head dims and rotary tables, layers that reuse the
+    # keys and values of an earlier layer, GeGLU, sandwich norms, per-layer input embeddings, soft-capped logits
+    sliding_window: int = 0
+    global_head_dim: int = 0                 # head dim of the full-attention layers when it differs from head_dim
+    num_kv_shared_layers: int = 0            # the last this-many layers read the K / V of the last earlier layer of their type
+    use_double_wide_mlp: bool = False        # KV-sharing layers carry an MLP of twice the intermediate size
+    hidden_size_per_layer_input: int = 0
+    vocab_size_per_layer_input: int = 0
+    final_logit_softcapping: float = 0.0
+    hidden_activation: str = "silu"
+    rope_parameters_by_type: Optional[Dict[str, Any]] = None      # layer type -> {rope_theta, partial_rotary_factor, rope_type}
     # Kimi-K3: block attention residuals, latent experts, SiTU-GLU
     attn_res_block_size: int = 0             # > 0: every this-many layers the running residual sum is frozen into the bank
     routed_expert_hidden_size: int = 0       # > 0: routed experts work in a latent space of this width (down-proj, experts, norm, up-proj)
@@ -100,6 +111,31 @@ class ModelConfig:
     @property
     def is_hybrid_gdn(self) -> bool:
         return self.linear_num_value_heads > 0
+
+    def attn_layer_type(self, layer_idx: int) -> str:
+        """"sliding_attention" or "full_attention" for the families that mix window and global layers."""
+        if self.layer_types and layer_idx < len(self.layer_types) and self.layer_types[layer_idx] == "sliding_attention":
+            return "sliding_attention"
+        return "full_attention"
+
+    def attn_head_dim(self, layer_idx: int) -> int:
+        return self.global_head_dim if (self.global_head_dim and self.attn_layer_type(layer_idx) == "full_attention") else self.head_dim
+
+    @property
+    def first_kv_shared_layer(self) -> int:
+        return self.num_hidden_layers - self.num_kv_shared_layers if self.num_kv_shared_layers > 0 else self.num_hidden_layers
+
+    def kv_source_layer(self, layer_idx: int) -> int:
+        """The layer whose K / V cache layer `layer_idx` reads: itself, or for a KV-sharing layer the last earlier layer of the
+        same attention type that keeps its own."""
+        first = self.first_kv_shared_layer
+        if layer_idx < first:
+            return layer_idx
+        kind = self.attn_layer_type(layer_idx)
+        for j in range(first - 1, -1, -1):
+            if self.attn_layer_type(j) == kind:
+                return j
+        raise ValueError(f"no earlier {kind} layer to share keys and values with")
 
     def layer_type(self, layer_idx: int) -> str:
         if not self.is_hybrid_gdn:
@@ -135,6 +171,8 @@ class ModelConfig:
             return ("situ", self.activation_situ_beta, self.activation_situ_linear_beta or None)
         if self.swiglu_limit > 0:
             return ("clamp", self.swiglu_limit)
+        if self.hidden_activation.startswith("gelu"):
+            return ("gelu_tanh",)
         return None
 
     def is_moe_layer(self, layer_idx: int) -> bool:
@@ -161,6 +199,9 @@ class ModelConfig:
                     inner[k] = d[k]
             d = inner
         rp = d.pop("rope_parameters", None)
+        if isinstance(rp, dict) and rp and all(isinstance(v, dict) for v in rp.values()):
+            d["rope_parameters_by_type"] = rp                 # one table per layer type (Gemma4)
+            rp = None
         if isinstance(rp, dict):
             d.setdefault("rope_theta", rp.get("rope_theta", 10000000.0))
             d.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 1.0))
@@ -181,7 +222,7 @@ class ModelConfig:
             d["linear_conv_kernel_dim"] = int(la["short_conv_kernel_size"])
             d["kda_gate_lower_bound"] = float(la.get("gate_lower_bound", -5.0))
         if isinstance(d.get("layer_types"), list):         # anything that is not a linear layer is a full-attention layer
-            d["layer_types"] = ["linear_attention" if t == "linear_attention" else "full_attention" for t in d["layer_types"]]
+            d["layer_types"] = [t if t in ("linear_attention", "sliding_attention") else "full_attention" for t in d["layer_types"]]
         if arch.startswith("KimiK3"):
             if "num_experts" in d:
                 d["n_routed_experts"] = d.pop("num_experts")
@@ -201,6 +242,15 @@ class ModelConfig:
             d.setdefault("activation_situ_linear_beta", 25.0)
             if d.get("attn_res_block_size") is None:
                 d["attn_res_block_size"] = 0
+        if arch.startswith("Gemma4"):
+            d.setdefault("n_routed_experts", 0)
+            d.setdefault("hidden_activation", "gelu_pytorch_tanh")
+            d.setdefault("q_lora_rank", None)
+            d.setdefault("tie_word_embeddings", True)
+            for k in ("global_head_dim", "sliding_window", "num_kv_shared_layers", "hidden_size_per_layer_input", "vocab_size_per_layer_input",
+                      "final_logit_softcapping"):
+                if d.get(k) is None:
+                    d[k] = 0
         if arch.startswith("Glm5Next"):
             d.setdefault("swiglu_limit", 10.0)
             d.setdefault("hc_mult", 4)
@@ -339,5 +389,20 @@ def tiny_kimi_k3(**over) -> ModelConfig:
                 linear_kind="kda", linear_num_key_heads=2, linear_num_value_heads=2, linear_key_head_dim=32, linear_value_head_dim=32,
                 linear_conv_kernel_dim=4, kda_gate_lower_bound=-5.0, mla_output_gate=True, mla_skip_rope=True, attn_res_block_size=2,
                 routed_expert_hidden_size=64, activation_situ_beta=4.0, activation_situ_linear_beta=25.0)
+    base.update(over)
+    return ModelConfig(**base)
+
+
+def tiny_gemma4(**over) -> ModelConfig:
+    """CPU-sized Gemma4 shape: two sliding-window layers per global layer, the last two layers reading shared keys / values,
+    per-layer input embeddings, tied and soft-capped output."""
+    base = dict(architecture="Gemma4ForCausalLM", vocab_size=512, hidden_size=128, num_hidden_layers=6, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=32, global_head_dim=64, intermediate_size=256, n_routed_experts=0, q_lora_rank=None,
+                max_position_embeddings=4096, sliding_window=16, num_kv_shared_layers=2, use_double_wide_mlp=True,
+                layer_types=["sliding_attention", "sliding_attention", "full_attention", "sliding_attention", "sliding_attention", "full_attention"],
+                hidden_size_per_layer_input=16, vocab_size_per_layer_input=512, final_logit_softcapping=30.0,
+                hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True,
+                rope_parameters_by_type={"sliding_attention": {"rope_theta": 10000.0, "rope_type": "default"},
+                                         "full_attention": {"rope_theta": 1000000.0, "rope_type": "proportional", "partial_rotary_factor": 0.25}})
     base.update(over)
     return ModelConfig(**base)

@@ -39,7 +39,13 @@ def _kimi_k3():
     return KimiK3ForConditionalGeneration
 
 
+def _gemma4():
+    from .gemma4 import Gemma4ForCausalLM
+    return Gemma4ForCausalLM
+
+
 _LAZY = {
+    "Gemma4ForCausalLM": _gemma4, "Gemma4ForConditionalGeneration": _gemma4,
     "Glm5NextForConditionalGeneration": _glm5_next, "KimiK3ForConditionalGeneration": _kimi_k3,
     "DeepseekV2ForCausalLM": _deepseek, "DeepseekV3ForCausalLM": _deepseek, "DeepseekV32ForCausalLM": _deepseek,
     "GlmMoeDsaForCausalLM": _deepseek, "KimiK2ForCausalLM": _deepseek,

@@ -65,6 +65,8 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
     """Every tensor name of an HF-layout checkpoint of this architecture with its (high-precision) shape."""
     H, V = cfg.hidden_size, cfg.vocab_size
     out: Dict[str, Tuple[int, ...]] = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,), "lm_head.weight": (V, H)}
+    if cfg.architecture.startswith("Gemma4"):
+        return _gemma4_param_shapes(cfg, out)
 
     def attn(p):
         if cfg.is_mla:
@@ -188,6 +190,37 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
     return out
 
 
+def _gemma4_param_shapes(cfg: ModelConfig, out):
+    H, L, P = cfg.hidden_size, cfg.num_hidden_layers, cfg.hidden_size_per_layer_input
+    if cfg.tie_word_embeddings:
+        out.pop("lm_head.weight")
+    if P:
+        out["model.embed_tokens_per_layer.weight"] = (cfg.vocab_size_per_layer_input or cfg.vocab_size, L * P)
+        out["model.per_layer_model_projection.weight"] = (L * P, H)
+        out["model.per_layer_projection_norm.weight"] = (P,)
+    for i in range(L):
+        p = f"model.layers.{i}."
+        hd, shared = cfg.attn_head_dim(i), cfg.kv_source_layer(i) != i
+        out[p + "self_attn.q_proj.weight"] = (cfg.num_attention_heads * hd, H)
+        out[p + "self_attn.k_proj.weight"] = (cfg.num_key_value_heads * hd, H)      # kept by the checkpoints for every layer
+        out[p + "self_attn.v_proj.weight"] = (cfg.num_key_value_heads * hd, H)
+        out[p + "self_attn.o_proj.weight"] = (H, cfg.num_attention_heads * hd)
+        for nm in ("q_norm", "k_norm", "v_norm"):
+            out[p + f"self_attn.{nm}.weight"] = (hd,)
+        I = cfg.intermediate_size * (2 if (cfg.use_double_wide_mlp and shared) else 1)
+        out[p + "mlp.gate_proj.weight"] = (I, H)
+        out[p + "mlp.up_proj.weight"] = (I, H)
+        out[p + "mlp.down_proj.weight"] = (H, I)
+        for nm in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+            out[p + nm + ".weight"] = (H,)
+        out[p + "layer_scalar"] = (1,)
+        if P:
+            out[p + "per_layer_input_gate.weight"] = (P, H)
+            out[p + "per_layer_projection.weight"] = (H, P)
+            out[p + "post_per_layer_input_norm.weight"] = (H,)
+    return out
+
+
 def random_hf_weights(cfg: ModelConfig, seed: int = 0, device="cpu", keep: Optional[Callable[[str], bool]] = None,
                       include_mtp: bool = False, std: float = 0.02) -> Iterator[Tuple[str, torch.Tensor]]:
     """Random-init tensors under HF names.  Each tensor draws from its own generator seeded by (seed, name),
@@ -198,7 +231,9 @@ def random_hf_weights(cfg: ModelConfig, seed: int = 0, device="cpu", keep: Optio
             continue
         g = torch.Generator(device=dev)
         g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFF)
-        if name.endswith("A_log"):
+        if name.endswith("layer_scalar"):
+            t = 1.0 + 0.05 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        elif name.endswith("A_log"):
             t = torch.log(1.0 + 3.0 * torch.rand(shape, generator=g, device=dev, dtype=torch.float32))
         elif name.endswith(("_fn", "_base")):
             t = 0.05 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)

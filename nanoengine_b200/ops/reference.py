@@ -268,8 +268,9 @@ def mla_attention_paged(q: torch.Tensor, cache: torch.Tensor, block_tables: torc
     return out.to(q.dtype)
 
 
-def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale) -> torch.Tensor:
-    """q [T, Hq, D]; caches [blocks, block_size, Hkv, D]; causal; returns [T, Hq, D]."""
+def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale, window: int = 0) -> torch.Tensor:
+    """q [T, Hq, D]; caches [blocks, block_size, Hkv, D]; causal; returns [T, Hq, D].  `window` > 0: a query at position p sees
+    key positions (p - window, p] only (sliding-window layers, reference layers/backends/attention/base.py:527-707)."""
     T, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     out = torch.zeros(T, Hq, D, dtype=torch.float32, device=q.device)
@@ -283,7 +284,10 @@ def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context
         v = _gather_rows(v_cache, block_tables[i], n).repeat_interleave(Hq // Hkv, 1)
         s = torch.einsum("thd,nhd->thn", q[lo:hi].float(), k) * scale
         pos = torch.arange(n - ql, n, device=q.device).view(ql, 1, 1)
-        s = s.masked_fill(torch.arange(n, device=q.device).view(1, 1, n) > pos, float("-inf"))
+        keys = torch.arange(n, device=q.device).view(1, 1, n)
+        s = s.masked_fill(keys > pos, float("-inf"))
+        if window > 0:
+            s = s.masked_fill(keys <= pos - window, float("-inf"))
         out[lo:hi] = torch.einsum("thn,nhd->thd", torch.softmax(s, -1), v)
     return out.to(q.dtype)
 
@@ -371,7 +375,7 @@ def mxfp4_quant(w: torch.Tensor):
 
 
 def glu_act(a: torch.Tensor, b: torch.Tensor, act=None) -> torch.Tensor:
-    """Gated activation of (gate a, up b) in fp32.  act None: silu(a) b.  ("clamp", L): up in [-L, L], gate <= L, then
+    """Gated activation of (gate a, up b) in fp32.  act None: silu(a) b.  ("gelu_tanh",): tanh-approximated GELU(a) b.  ("clamp", L): up in [-L, L], gate <= L, then
     silu(a) b (reference layers/activation.py:86-92).  ("situ", beta, linear_beta): beta tanh(a / beta) sigmoid(a) times
     linear_beta tanh(b / linear_beta) (no clamp of b when linear_beta is None; reference kernel/triton/generic/situ.py:24-27)."""
     if act is None:
@@ -379,6 +383,8 @@ def glu_act(a: torch.Tensor, b: torch.Tensor, act=None) -> torch.Tensor:
     if act[0] == "clamp":
         L = float(act[1])
         return F.silu(a.clamp(max=L)) * b.clamp(-L, L)
+    if act[0] == "gelu_tanh":
+        return F.gelu(a, approximate="tanh") * b
     if act[0] == "situ":
         beta, lb = float(act[1]), act[2]
         if lb:

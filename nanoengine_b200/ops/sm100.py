@@ -272,6 +272,8 @@ def _act_args(act):
         return _c.c_int(1), _c.c_float(float(act[1])), _c.c_float(0.0)
     if act[0] == "situ":
         return _c.c_int(2), _c.c_float(float(act[1])), _c.c_float(float(act[2] or 0.0))
+    if act[0] == "gelu_tanh":
+        return _c.c_int(3), _c.c_float(1.0), _c.c_float(0.0)
     raise ValueError(f"unknown gated activation {act!r}")
 
 

@@ -123,11 +123,13 @@ def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scal
                                _c.c_longlong(cache.shape[-1]), _c.c_int(0), _c.c_int(0), _k._p(bt), _c.c_int(bt.stride(0)), _c.c_int(cache.shape[1]),
                                _k._p(cu), _k._p(cl), _c.c_int(B), _k._p(sp), _c.c_int(0 if sp is None else sp.shape[1]), _k._p(out),
                                _c.c_longlong(H * R), _c.c_int(R), _k._p(None), _c.c_int(T), _c.c_int(H), _c.c_int(Dk), _c.c_int(R),
-                               _c.c_float(scale), _c.c_int(1 if fp8 else 0), _k._st()), "ne_attn_generic")
+                               _c.c_float(scale), _c.c_int(1 if fp8 else 0), _c.c_int(0), _k._st()), "ne_attn_generic")
     return out
 
 
-def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale):
+def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale, window: int = 0):
+    """`window` > 0: every query sees only its last `window` key positions (sliding-window layers); those layers and head
+    dims other than 128 run on the generic kernel."""
     T, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     lib = _k.lib()
@@ -137,7 +139,7 @@ def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context
     if T == 0:
         return out
     group = Hq // Hkv
-    if (D == 128 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16 and k_cache.shape[1] == 64 and Hq % Hkv == 0
+    if (D == 128 and window <= 0 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16 and k_cache.shape[1] == 64 and Hq % Hkv == 0
             and group <= 128 and group & (group - 1) == 0 and k_cache.is_contiguous() and v_cache.is_contiguous()):
         # tcgen05 kernel: one CTA per (kv head, tile of 128 (token, head) rows, key slice)
         q = q.contiguous()
@@ -162,7 +164,7 @@ def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context
     _k._ck(lib.ne_attn_generic(_k._p(q), _c.c_longlong(q.stride(0)), _c.c_int(q.stride(1)), _k._p(k_cache), _k._p(v_cache),
                                _c.c_longlong(Hkv * D), _c.c_int(D), _c.c_int(group), _k._p(bt), _c.c_int(bt.stride(0)), _c.c_int(k_cache.shape[1]),
                                _k._p(cu), _k._p(cl), _c.c_int(cl.numel()), _k._p(None), _c.c_int(0), _k._p(out), _c.c_longlong(Hq * D), _c.c_int(D),
-                               _k._p(None), _c.c_int(T), _c.c_int(Hq), _c.c_int(D), _c.c_int(D), _c.c_float(scale), _c.c_int(0), _k._st()),
+                               _k._p(None), _c.c_int(T), _c.c_int(Hq), _c.c_int(D), _c.c_int(D), _c.c_float(scale), _c.c_int(0), _c.c_int(max(0, int(window))), _k._st()),
            "ne_attn_generic")
     return out
 

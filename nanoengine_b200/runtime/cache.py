@@ -48,6 +48,9 @@ class CachePlan:
     gdn_heads: int = 0
     gdn_dv: int = 0
     gdn_dk: int = 0
+    # GQA families whose layers have different head dims: the head dim of every cache layer (row_dim is their maximum; a
+    # layer with a smaller one uses the front of its slab)
+    layer_dims: Optional[List[int]] = None
 
     @property
     def state_slot_bytes(self) -> int:
@@ -105,6 +108,12 @@ def make_cache_plan(mc: ModelConfig, kv_dtype_name: str, block_size: int, attn_t
     if mc.is_mla:
         return CachePlan(True, False, mc.has_indexer and use_indexer, L, block_size, dt, mc.mla_cache_dim,
                          index_dim=mc.index_head_dim)
+    if mc.num_kv_shared_layers or mc.global_head_dim:
+        # window / global layers with their own head dims; KV-sharing layers own no cache layer
+        own = [i for i in range(mc.num_hidden_layers) if mc.kv_source_layer(i) == i]
+        dims = [mc.attn_head_dim(i) for i in own]
+        return CachePlan(False, True, False, len(own), block_size, dt, max(dims), kv_heads_local=max(1, mc.num_key_value_heads // attn_tp),
+                         layer_dims=dims)
     return CachePlan(False, True, False, L, block_size, dt, mc.head_dim, kv_heads_local=max(1, mc.num_key_value_heads // attn_tp))
 
 
@@ -127,6 +136,10 @@ class KVCache:
         else:
             self.kv = torch.zeros(2, plan.num_layers, nb, plan.block_size, plan.kv_heads_local, plan.row_dim, dtype=plan.kv_dtype, device=device)
             self.layers = [(self.kv[0, l], self.kv[1, l]) for l in range(plan.num_layers)]
+            if plan.layer_dims:
+                def front(t, d):          # a contiguous [blocks, block_size, heads, d] cache at the front of the layer's slab
+                    return t.reshape(-1)[: nb * plan.block_size * plan.kv_heads_local * d].view(nb, plan.block_size, plan.kv_heads_local, d)
+                self.layers = [(front(self.kv[0, l], d), front(self.kv[1, l], d)) for l, d in enumerate(plan.layer_dims)]
         self.indexer = None
         self.indexer_layers = None
         if plan.indexer:

@@ -184,3 +184,79 @@ def test_family_on_gpu_graph_and_eager_agree(family):
     same = sum(a == b for a, b in zip(outs[True], outs[False]))
     assert same >= 2 and all(a[:3] == b[:3] for a, b in zip(outs[True], outs[False])), outs
     assert sm100.kernel_status()[0] == 0
+
+
+# ---- Gemma4 -----------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("D,window", [(256, 40), (512, 0), (128, 100), (256, 1)])
+def test_windowed_gqa_attention_kernel(k, D, window):
+    from nanoengine_b200.ops import sm100_attn
+    torch.manual_seed(9)
+    Hq, Hkv, bs = 8, 2, 64
+    q_lens, ctx_lens = [1, 70, 5], [200, 70, 133]
+    nb = sum((c + bs - 1) // bs for c in ctx_lens)
+    kc = torch.randn(nb + 1, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(nb + 1, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    bt = torch.zeros(3, 4, dtype=torch.int32, device="cuda")
+    nxt = 0
+    for i, c in enumerate(ctx_lens):
+        n = (c + bs - 1) // bs
+        bt[i, :n] = torch.arange(nxt, nxt + n, dtype=torch.int32, device="cuda"); nxt += n
+    T = sum(q_lens)
+    q = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    cl = torch.tensor(ctx_lens, dtype=torch.int32, device="cuda")
+    want = ref.gqa_attention_paged(q.float(), kc.float(), vc.float(), bt, cu, cl, D ** -0.5, window)
+    got = sm100_attn.gqa_attention_paged(q, kc, vc, bt, cu, cl, D ** -0.5, window)
+    assert _rel(got, want) < 1e-2
+
+
+def _gemma_gpu_config():
+    from nanoengine_b200.models.config import tiny_gemma4
+    return tiny_gemma4(hidden_size=256, head_dim=256, global_head_dim=512, num_attention_heads=4, num_key_value_heads=1, intermediate_size=512,
+                       hidden_size_per_layer_input=128, sliding_window=48)
+
+
+def test_gemma4_logits_match_fp32_cpu_model():
+    from nanoengine_b200 import Config
+    from nanoengine_b200._native import _core as C
+    from nanoengine_b200.models.weights import random_hf_weights
+    from nanoengine_b200.runtime.model_runner import ModelRunner
+    mc = _gemma_gpu_config()
+    W = [(n, t.to(torch.bfloat16).float()) for n, t in random_hf_weights(mc, seed=5, std=0.05)]
+    g = torch.Generator().manual_seed(6)
+    seqs = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (100, 9, 70)]
+    runners = {}
+    for dev, dt in (("cpu", "float32"), ("cuda", "bfloat16")):
+        r = ModelRunner(Config(model="tiny", model_config=mc, dummy_weight=True, dtype=dt, device=dev, kvcache_block_size=64,
+                               num_kvcache_blocks=16, max_num_seqs=4, enforce_eager=True))
+        r.init_model()
+        r.load_weights(iter(W))
+        r.allocate_kvcache(16)
+        runners[dev] = r
+    cur = [list(s) for s in seqs]
+    for step in range(3):
+        new = [len(s) for s in cur] if step == 0 else [1] * len(cur)
+        lc = _step_logits(runners["cpu"], C, cur, new, [-1, -1, -1], step == 0)
+        lg = _step_logits(runners["cuda"], C, cur, new, [-1, -1, -1], step == 0)
+        assert _rel(lg, lc) < 5e-2, f"step {step}: {_rel(lg, lc)}"
+        cur = [s + [t] for s, t in zip(cur, lc.argmax(-1).tolist())]
+
+
+def test_gemma4_on_gpu_graph_and_eager_agree():
+    from nanoengine_b200 import Config, LLM, SamplingParams
+    from nanoengine_b200.ops import sm100
+    mc = _gemma_gpu_config()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (150, 9, 80)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    outs = {}
+    for eager in (True, False):
+        llm = LLM(Config(model="tiny", model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kvcache_block_size=64,
+                         num_kvcache_blocks=32, max_num_seqs=4, enforce_eager=eager, seed=0))
+        outs[eager] = [o["token_ids"] for o in llm.generate(prompts, sp)]
+        assert [o["token_ids"] for o in llm.generate(prompts, sp)] == outs[eager]
+        del llm
+        torch.cuda.empty_cache()
+    same = sum(a == b for a, b in zip(outs[True], outs[False]))
+    assert same >= 2 and all(a[:3] == b[:3] for a, b in zip(outs[True], outs[False])), outs
+    assert sm100.kernel_status()[0] == 0
