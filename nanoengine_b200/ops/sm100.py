@@ -487,9 +487,9 @@ def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scal
     return sm100_attn.mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scale, kv_lora_rank, sparse_indices)
 
 
-def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale):
+def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale, window: int = 0):
     from . import sm100_attn
-    return sm100_attn.gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale)
+    return sm100_attn.gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale, window)
 
 
 def sample(logits, temperatures, generator=None, return_logprobs=False):
