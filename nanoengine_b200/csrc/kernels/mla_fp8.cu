@@ -136,25 +136,6 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
         return (id >= 0 && (long long)id < a.cache_rows) ? id : -1;
       };
       int id_next = load_id(0);
-      // The listed rows are scattered over the whole cache, so a first touch pays DRAM and TLB latency that three stages of
-      // shared memory cannot cover: the lines of tile i + kAhead are pulled into L2 while tile i is issued (each warp its 16
-      // rows, six 128-byte-spaced touches per 576-byte row), and the cp.async that follows finds them there.
-      constexpr int kAhead = 6;
-      auto prefetch_tile = [&](int i) {
-        if (i >= n_tiles) return;
-        const int id = load_id(i);
-#pragma unroll
-        for (int it = 0; it < 3; it++) {
-          const int item = it * 32 + lane;                 // 16 rows x 6 touches
-          const int r = item / 6, part = item - r * 6;
-          const int rid = __shfl_sync(0xffffffffu, id, r);
-          if (rid >= 0) {
-            const uint8_t* ptr = a.cache + (long long)rid * kDk + (part < 5 ? part * 128 : kDk - 1);
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
-          }
-        }
-      };
-      for (int i = 0; i < kAhead; i++) prefetch_tile(i);
       // One cp.async group per iteration (empty once the tiles run out).  At the top of iteration i the groups 0 .. i-1 are
       // committed, so "all but the newest one have landed" means this lane's part of tile i-2 is complete: it is fenced for
       // the tensor-core proxy and handed over BEFORE the warp blocks on the slot tile i goes into - that slot is freed by the
@@ -175,7 +156,6 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
           if (ok) {
             const int my_id = id_next;
             id_next = load_id(i + 1);
-            prefetch_tile(i + kAhead);
             const uint32_t dst = smem_u32(sPg + s * kPgBytes);
             const uint32_t d_nope = dst + (lane >> 3) * (kPage * 128);
             const uint8_t* src_nope = a.cache + lane * 16;
