@@ -30,11 +30,13 @@ def _i32(t):
 
 
 def mla_splits(T: int, max_pages: int) -> int:
-    """Key slices per token so that small batches still fill the GPU: each slice keeps at least 4 pages."""
+    """Key slices per token so that small batches still fill the GPU: each slice keeps at least 4 pages.  Slicing is only worth
+    its price (every slice writes and the merge re-reads an fp32 [T, H, 512] partial result) when it raises the number of busy
+    SMs: with 2 T CTAs covering more than ~60 % of them a second slice just adds a second, half-empty wave."""
     ctas = 2 * T
-    if ctas >= _sms():
+    if ctas * 5 >= _sms() * 3:
         return 1
-    want = -(-_sms() // ctas)
+    want = _sms() // ctas                       # the largest count that still fits one wave
     return max(1, min(want, max(1, max_pages // 4), 32))
 
 
@@ -86,7 +88,7 @@ def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scal
         sp = _i32(sparse_indices)
         topk = sp.shape[1]
         tiles = -(-topk // 64)
-        S = splits if splits is not None else max(1, min(-(-_sms() // (2 * T)) if 2 * T < _sms() else 1, max(1, tiles // 4), 32))
+        S = splits if splits is not None else mla_splits(T, tiles)
         part = lse2 = None
         if S > 1:
             part = torch.empty(S, T, H, R, dtype=torch.float32, device=q.device)
