@@ -321,6 +321,12 @@ def build_cases(args):
         "absorb_v_decode": lambda: case_absorb(128, "v"),
         "gdn_decode": lambda: case_gdn(128),
         "gdn_verify2": lambda: case_gdn(128, q_len=2),
+        "kda_decode_256": lambda: case_kda(256),
+        "kda_prefill_2048": lambda: case_kda(8, q_len=2048),
+        "attn_res_decode": lambda: case_attn_res(128),
+        "attn_res_prefill": lambda: case_attn_res(16384),
+        "mhc_decode": lambda: case_mhc(128),
+        "mhc_prefill": lambda: case_mhc(8192),
         "mla_decode": lambda: case_mla(128, args.ctx),
         "mla_decode_small_batch": lambda: case_mla(8, 8192),
         "mla_sparse_decode_2048": lambda: case_mla_sparse(128, 8192),
@@ -338,6 +344,59 @@ def build_cases(args):
         "bf16_square": lambda: case_dense_bf16(8192, 8192, 8192),
     }
     return c
+
+
+def case_kda(B, q_len=1, H=64, D=128, K=4):
+    """Kimi delta attention layer core (convolution + recurrence with a decay per key channel + sigmoid-gated norm) at a 64-head
+    128 x 128 shape.  The floor is one read and one write of every sequence's fp32 state."""
+    T = B * q_len
+    C = 3 * H * D
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    proj = torch.randn(T, C + H * D, **bf)
+    qkv, gate = proj[:, :C], proj[:, C:].view(T, H, D)
+    raw_g = torch.randn(T, H * D, **bf)
+    b = torch.randn(T, H, **bf)
+    w = (torch.randn(C, K, device="cuda") * 0.3).to(torch.bfloat16)
+    conv = torch.zeros(B + 1, K - 1, C, **bf)
+    state = torch.randn(B + 1, H, D, D, device="cuda") * 0.1
+    slots = torch.arange(B, device="cuda", dtype=torch.int32)
+    cu = (torch.arange(B + 1, device="cuda") * q_len).to(torch.int32)
+    fresh = torch.zeros(B, dtype=torch.int32, device="cuda")
+    A_log, dtb = torch.rand(H, device="cuda") - 0.5, torch.randn(H * D, device="cuda") * 0.3
+    nw = torch.ones(D, **bf)
+
+    def fn():
+        y = sm100.gdn_conv(qkv, w, conv, slots, cu, fresh, q_len == 1)
+        q, k, v = y[:, : H * D].view(T, H, D), y[:, H * D: 2 * H * D].view(T, H, D), y[:, 2 * H * D:].view(T, H, D)
+        return sm100.kda_recurrent(q, k, v, raw_g, b, A_log, dtb, -5.0, state, slots, cu, fresh, gate, nw, 1e-6)
+
+    nbytes = B * H * D * D * 4 * 2 + T * (C * 2 * 3 + H * D * 2 * 3) + B * (K - 1) * C * 2 * 2
+    return fn, nbytes, 2.0 * T * H * D * D * 3
+
+
+def case_attn_res(T, D=7168, valid=8):
+    """Block attention residual of one layer: 9 candidate rows per token mixed and normalised."""
+    bank = torch.randn(T, valid + 1, D, device="cuda", dtype=torch.bfloat16)
+    prefix = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    ws = torch.randn(D, device="cuda") * 0.05
+    wo = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    fn = lambda: sm100.attn_res_mix(prefix, bank, valid, ws, wo, 1e-6, -1)
+    return fn, T * D * 2 * (valid + 2), 4.0 * T * D * (valid + 1)
+
+
+def case_mhc(T, h=4, D=6144):
+    """Hyper-connection pre-mix + post-mix around one sub-layer (4 streams)."""
+    x = torch.randn(T, h, D, device="cuda", dtype=torch.bfloat16)
+    fn_w = torch.randn((2 + h) * h, h * D, device="cuda") * 0.02
+    base = torch.zeros((2 + h) * h, device="cuda")
+    scale = torch.ones(3, device="cuda")
+    sub = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+
+    def fn():
+        y, post, comb = sm100.mhc_pre(x, fn_w, base, scale, 3, 1e-6)
+        return sm100.mhc_post(sub, x, post, comb)
+
+    return fn, T * h * D * 2 * 3 + T * D * 2 * 2 + fn_w.numel() * 4, 2.0 * T * (2 + h) * h * h * D
 
 
 def main():
