@@ -391,9 +391,10 @@ def case_mhc(T, h=4, D=6144):
     base = torch.zeros((2 + h) * h, device="cuda")
     scale = torch.ones(3, device="cuda")
     sub = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    split = sm100.mhc_split_weights(fn_w)
 
     def fn():
-        y, post, comb = sm100.mhc_pre(x, fn_w, base, scale, 3, 1e-6)
+        y, post, comb = sm100.mhc_pre(x, fn_w, base, scale, 3, 1e-6, split)
         return sm100.mhc_post(sub, x, post, comb)
 
     return fn, T * h * D * 2 * 3 + T * D * 2 * 2 + fn_w.numel() * 4, 2.0 * T * (2 + h) * h * h * D

@@ -9,7 +9,8 @@
 //  * mhc_pre_kernel / mhc_post_kernel: manifold-constrained hyper-connections (GLM5-next).  The hidden state is `h` parallel
 //    streams; before a sub-layer the streams are contracted with sigmoid weights, after it the sub-layer output is spread
 //    back with a second set of weights and the streams are mixed by a Sinkhorn-normalised h x h matrix.  All 2h + h*h
-//    coefficients of a token come from one fp32 product of the flattened streams with a [(2+h)h, h*D] matrix.
+//    coefficients of a token come from one product of the flattened streams with a [(2+h)h, h*D] matrix, which runs as a
+//    tensor-core GEMM in front of mhc_mix_kernel.
 //    Replaces in the reference: models/glm5_next/glm5_next.py:27-99 (PyTorch modules).
 #include "ptx.cuh"
 
@@ -112,69 +113,46 @@ __global__ void __launch_bounds__(256) attn_res_kernel(const __nv_bfloat16* __re
 }
 
 // ---- hyper-connections -------------------------------------------------------------------------------------------------
-constexpr int kHcTok = 4;       // tokens per CTA: the coefficient matrix is read once for all of them
 constexpr int kHcMaxM = 24;     // (2 + h) * h for h <= 4
 
-// x [T, h, D] bf16 contiguous; fn [(2+h)h, h*D] fp32; base [(2+h)h]; scale [3].
-// y [T, D] = sum_i pre_i x_i; post [T, h]; comb [T, h, h]  (all bf16, as the reference rounds them).
-__global__ void __launch_bounds__(256) mhc_pre_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ fn, const float* __restrict__ base,
-                                                     const float* __restrict__ scale, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ post,
-                                                     __nv_bfloat16* __restrict__ comb, int T, int h, int D, int iters, float eps) {
+// The coefficient product mixes[t, m] = x[t, :] . fn[m, :] over the h*D flattened streams runs on the tensor cores as one
+// bf16 GEMM: fn (fp32 in the checkpoint) is split into a bf16 head and a bf16 remainder, stacked as 2M weight rows, so the two
+// partial products add up to the fp32 product to ~2^-17 relative (x is bf16 already, accumulation is fp32).  This kernel takes
+// the GEMM's [T, ldm] fp32 output (columns [0, M) head, [M, 2M) remainder) and does everything else, one CTA per token: sum of
+// squares of the streams, sigmoid / softmax / Sinkhorn coefficients in one thread, stream contraction y = sum_i pre_i x_i
+// (the second pass over the token's h*D values hits L1 / L2).
+// x [T, h, D] bf16 contiguous; base [(2+h)h]; scale [3].  y [T, D], post [T, h], comb [T, h, h] bf16 (as the reference rounds them).
+__global__ void __launch_bounds__(256) mhc_mix_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mixes, int ldm,
+                                                     const float* __restrict__ base, const float* __restrict__ scale, __nv_bfloat16* __restrict__ y,
+                                                     __nv_bfloat16* __restrict__ post, __nv_bfloat16* __restrict__ comb, int h, int D, int iters,
+                                                     float eps) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
-  __shared__ float s_acc[8][kHcTok][kHcMaxM + 1];
-  __shared__ float s_pre[kHcTok][4];
+  __shared__ float s_red[8];
+  __shared__ float s_pre[4];
   const int M = (2 + h) * h, W = h * D;
-  const int t0 = blockIdx.x * kHcTok, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float acc[kHcTok][kHcMaxM], ssq[kHcTok];
+  const long long t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* xt = x + t * W;
+  float ss = 0.f;
+  for (int e = threadIdx.x * 8; e < W; e += 256 * 8) {
+    float f[8];
+    load8(xt + e, f);
 #pragma unroll
-  for (int k = 0; k < kHcTok; k++) {
-    ssq[k] = 0.f;
-#pragma unroll
-    for (int m = 0; m < kHcMaxM; m++) acc[k][m] = 0.f;
+    for (int j = 0; j < 8; j++) ss += f[j] * f[j];
   }
-  for (int e = threadIdx.x * 2; e < W; e += 512) {
-    float2 xv[kHcTok];
-#pragma unroll
-    for (int k = 0; k < kHcTok; k++) {
-      xv[k] = t0 + k < T ? unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + (long long)(t0 + k) * W + e)) : make_float2(0.f, 0.f);
-      ssq[k] += xv[k].x * xv[k].x + xv[k].y * xv[k].y;
-    }
-#pragma unroll
-    for (int m = 0; m < kHcMaxM; m++) {
-      if (m < M) {
-        const float2 f = *reinterpret_cast<const float2*>(fn + (long long)m * W + e);
-#pragma unroll
-        for (int k = 0; k < kHcTok; k++) acc[k][m] += xv[k].x * f.x + xv[k].y * f.y;
-      }
-    }
-  }
-#pragma unroll
-  for (int k = 0; k < kHcTok; k++) {
-    ssq[k] = warp_sum(ssq[k]);
-    if (lane == 0) s_acc[warp][k][kHcMaxM] = ssq[k];
-#pragma unroll
-    for (int m = 0; m < kHcMaxM; m++) {
-      if (m < M) {
-        const float v = warp_sum(acc[k][m]);
-        if (lane == 0) s_acc[warp][k][m] = v;
-      }
-    }
-  }
+  ss = warp_sum(ss);
+  if (lane == 0) s_red[warp] = ss;
   __syncthreads();
-  if (threadIdx.x < kHcTok && t0 + threadIdx.x < T) {
-    const int k = threadIdx.x;
-    const long long t = t0 + k;
-    float mix[kHcMaxM], ss = 0.f;
-    for (int w = 0; w < 8; w++) ss += s_acc[w][k][kHcMaxM];
-    const float r = rsqrtf(ss / (float)W + eps);
-    for (int m = 0; m < M; m++) {
-      float v = 0.f;
-      for (int w = 0; w < 8; w++) v += s_acc[w][k][m];
-      mix[m] = v * r;
-    }
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < 8; w++) tot += s_red[w];
+    const float r = rsqrtf(tot / (float)W + eps);
+    const float* mr = mixes + t * ldm;
+    float mix[kHcMaxM];
+    for (int m = 0; m < M; m++) mix[m] = (mr[m] + mr[M + m]) * r;
     for (int i = 0; i < h; i++) {
       const float pre = 1.f / (1.f + __expf(-(mix[i] * scale[0] + base[i]))) + eps;
-      s_pre[k][i] = __bfloat162float(__float2bfloat16(pre));
+      s_pre[i] = __bfloat162float(__float2bfloat16(pre));
       post[t * h + i] = __float2bfloat16(2.f / (1.f + __expf(-(mix[h + i] * scale[1] + base[h + i]))));
     }
     float c[4][4];
@@ -186,17 +164,17 @@ __global__ void __launch_bounds__(256) mhc_pre_kernel(const __nv_bfloat16* __res
     }
     auto cols = [&]() {
       for (int j = 0; j < h; j++) {
-        float s = 0.f;
-        for (int i = 0; i < h; i++) s += c[i][j];
-        for (int i = 0; i < h; i++) c[i][j] /= s + eps;
+        float sm = 0.f;
+        for (int i = 0; i < h; i++) sm += c[i][j];
+        for (int i = 0; i < h; i++) c[i][j] /= sm + eps;
       }
     };
     cols();
     for (int it = 1; it < iters; it++) {
       for (int i = 0; i < h; i++) {
-        float s = 0.f;
-        for (int j = 0; j < h; j++) s += c[i][j];
-        for (int j = 0; j < h; j++) c[i][j] /= s + eps;
+        float sm = 0.f;
+        for (int j = 0; j < h; j++) sm += c[i][j];
+        for (int j = 0; j < h; j++) c[i][j] /= sm + eps;
       }
       cols();
     }
@@ -204,16 +182,16 @@ __global__ void __launch_bounds__(256) mhc_pre_kernel(const __nv_bfloat16* __res
       for (int j = 0; j < h; j++) comb[(t * h + i) * h + j] = __float2bfloat16(c[i][j]);
   }
   __syncthreads();
-  for (int k = 0; k < kHcTok && t0 + k < T; k++) {
-    const long long t = t0 + k;
-    for (int d = threadIdx.x * 2; d < D; d += 512) {
-      float2 a = make_float2(0.f, 0.f);
-      for (int i = 0; i < h; i++) {
-        const float2 v = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + t * W + (long long)i * D + d));
-        a.x += s_pre[k][i] * v.x; a.y += s_pre[k][i] * v.y;
-      }
-      *reinterpret_cast<uint32_t*>(y + t * D + d) = pack_bf16x2(a.x, a.y);
+  for (int d = threadIdx.x * 8; d < D; d += 256 * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < h; i++) {
+      float f[8];
+      load8(xt + (long long)i * D + d, f);
+      const float p = s_pre[i];
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] += p * f[j];
     }
+    store8(y + t * D + d, acc);
   }
 }
 
@@ -273,12 +251,12 @@ extern "C" int ne_attn_res(const void* prefix, long long p_ld, void* bank, long 
                          (const __nv_bfloat16*)w_out, eps, (__nv_bfloat16*)out, o_ld, D, write_row);
 }
 
-extern "C" int ne_mhc_pre(const void* x, const float* fn, const float* base, const float* scale, void* y, void* post, void* comb, int T, int h, int D,
-                          int iters, float eps, cudaStream_t st) {
+extern "C" int ne_mhc_mix(const void* x, const float* mixes, int ldm, const float* base, const float* scale, void* y, void* post, void* comb, int T,
+                          int h, int D, int iters, float eps, cudaStream_t st) {
   if (T <= 0) return 0;
-  if (h < 1 || h > 4 || D % 2) return 1001;
-  return (int)launch_pdl(mhc_pre_kernel, dim3((T + kHcTok - 1) / kHcTok), dim3(256), 0, st, (const __nv_bfloat16*)x, fn, base, scale, (__nv_bfloat16*)y,
-                         (__nv_bfloat16*)post, (__nv_bfloat16*)comb, T, h, D, iters, eps);
+  if (h < 1 || h > 4 || D % 8 || ldm < 2 * (2 + h) * h) return 1001;
+  return (int)launch_pdl(mhc_mix_kernel, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)x, mixes, ldm, base, scale, (__nv_bfloat16*)y,
+                         (__nv_bfloat16*)post, (__nv_bfloat16*)comb, h, D, iters, eps);
 }
 
 extern "C" int ne_mhc_post(const void* x, long long x_ld, const void* res, const void* post, const void* comb, void* out, long long T, int h, int D,

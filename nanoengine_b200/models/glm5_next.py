@@ -37,9 +37,15 @@ class HyperConnection(nn.Module):
         self.fn = nn.Parameter(torch.zeros((2 + h) * h, h * D, dtype=torch.float32, device=device), requires_grad=False)
         self.base = nn.Parameter(torch.zeros((2 + h) * h, dtype=torch.float32, device=device), requires_grad=False)
         self.scale = nn.Parameter(torch.ones(3, dtype=torch.float32, device=device), requires_grad=False)
+        self._split = None          # bf16 head / remainder split of `fn` for the tensor-core product; rebuilt after a weight change
+
+    def refresh(self):
+        self._split = None
 
     def forward(self, streams):
-        return ops.mhc_pre(streams, self.fn, self.base, self.scale, self.iters, self.eps)
+        if streams.is_cuda and self._split is None:
+            self._split = ops.mhc_split_weights(self.fn)
+        return ops.mhc_pre(streams, self.fn, self.base, self.scale, self.iters, self.eps, self._split)
 
 
 class Glm5NextDecoderLayer(nn.Module):
@@ -140,6 +146,7 @@ class Glm5NextForConditionalGeneration(nn.Module):
             n += load_deepseek_weights(self, rest())
         for i in range(cfg.num_hidden_layers):
             L = self.model.layers[str(i)]
+            L.hc_attn.refresh(); L.hc_ffn.refresh()
             if L.kind == "linear_attention" and L.linear_attn.pending():
                 raise ValueError(f"incomplete checkpoint: layer {i} delta-attention parts {L.linear_attn.pending()}")
         return n

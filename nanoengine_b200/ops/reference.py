@@ -776,8 +776,21 @@ def attn_res_mix(prefix: torch.Tensor, bank: torch.Tensor, valid: int, w_score: 
     return rmsnorm(mix, w_out, eps)
 
 
-def mhc_pre(x: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, iters: int, eps: float):
-    """Hyper-connection pre-mix.  x [T, h, D] streams; fn [(2+h)h, h*D], base [(2+h)h], scale [3] fp32.  Returns the
+def mhc_split_weights(fn: torch.Tensor) -> torch.Tensor:
+    """fp32 coefficient matrix [M, W] -> bf16 [2M padded to a multiple of 8, W]: rows [0, M) its bf16 rounding, rows [M, 2M)
+    the bf16 rounding of what the first rows miss.  A bf16 product against both halves, added, equals the fp32 product to
+    ~2^-17 relative."""
+    hi = fn.float().to(torch.bfloat16)
+    lo = (fn.float() - hi.float()).to(torch.bfloat16)
+    rows = (2 * fn.shape[0] + 7) // 8 * 8
+    out = torch.zeros(rows, fn.shape[1], dtype=torch.bfloat16, device=fn.device)
+    out[: fn.shape[0]] = hi
+    out[fn.shape[0]: 2 * fn.shape[0]] = lo
+    return out
+
+
+def mhc_pre(x: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, iters: int, eps: float, fn_split=None):
+    """Hyper-connection pre-mix (`fn_split` is the CUDA body's prepared operand; unused here).  x [T, h, D] streams; fn [(2+h)h, h*D], base [(2+h)h], scale [3] fp32.  Returns the
     contracted sub-layer input y [T, D] and the post weights [T, h] and stream-mixing matrix [T, h, h] for `mhc_post`.
     Parity: reference models/glm5_next/glm5_next.py:27-70."""
     T, h, D = x.shape

@@ -726,17 +726,25 @@ def attn_res_mix(prefix: torch.Tensor, bank: torch.Tensor, valid: int, w_score: 
     return out
 
 
-def mhc_pre(x: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, iters: int, eps: float):
-    """Hyper-connection pre-mix in one kernel (coefficients, Sinkhorn normalisation and stream contraction)."""
+mhc_split_weights = ref.mhc_split_weights
+
+
+def mhc_pre(x: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, iters: int, eps: float, fn_split=None):
+    """Hyper-connection pre-mix: the coefficient product as a bf16 tensor-core GEMM against the head / remainder split of the
+    fp32 matrix (`mhc_split_weights`, pass it in to avoid rebuilding it every call), then one kernel for the sum of squares,
+    the sigmoid / softmax / Sinkhorn coefficients and the stream contraction."""
     T, h, D = x.shape
     x = x.contiguous()
-    assert x.dtype == torch.bfloat16 and fn.dtype == torch.float32 and fn.is_contiguous() and fn.shape == ((2 + h) * h, h * D)
-    assert base.dtype == torch.float32 and scale.dtype == torch.float32
+    assert x.dtype == torch.bfloat16 and base.dtype == torch.float32 and scale.dtype == torch.float32 and D % 8 == 0
+    if fn_split is None:
+        fn_split = mhc_split_weights(fn)
+    assert fn_split.dtype == torch.bfloat16 and fn_split.shape[1] == h * D and fn_split.shape[0] >= 2 * (2 + h) * h
+    mixes = linear(x.view(T, h * D), fn_split, out_fp32=True)                    # [T, >= 2M] fp32
     y = torch.empty(T, D, dtype=torch.bfloat16, device=x.device)
     post = torch.empty(T, h, dtype=torch.bfloat16, device=x.device)
     comb = torch.empty(T, h, h, dtype=torch.bfloat16, device=x.device)
-    _ck(lib().ne_mhc_pre(_p(x), _p(fn), _p(base), _p(scale), _p(y), _p(post), _p(comb), _c.c_int(T), _c.c_int(h), _c.c_int(D), _c.c_int(iters),
-                         _c.c_float(eps), _st()), "ne_mhc_pre")
+    _ck(lib().ne_mhc_mix(_p(x), _p(mixes), _c.c_int(mixes.stride(0)), _p(base), _p(scale), _p(y), _p(post), _p(comb), _c.c_int(T), _c.c_int(h),
+                         _c.c_int(D), _c.c_int(iters), _c.c_float(eps), _st()), "ne_mhc_mix")
     return y, post, comb
 
 

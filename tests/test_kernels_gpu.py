@@ -173,7 +173,7 @@ def test_mla_kv_prepare_fuses_norm_rope_and_store(k, fp8):
     assert torch.equal(f1[(f2.abs().sum(-1) == 0)], f2[(f2.abs().sum(-1) == 0)])    # untouched rows stay zero
 
 
-def test_mla_query_emits_e4m3_for_the_dense_fp8_kernel(k):
+def test_mla_query_emits_e4m3_for_the_fp8_kernels(k):
     torch.manual_seed(72)
     T, H, nope, rope, R = 9, 128, 128, 64, 512
     q = torch.randn(T, H, nope + rope, device="cuda", dtype=torch.bfloat16) * 0.5
@@ -185,8 +185,8 @@ def test_mla_query_emits_e4m3_for_the_dense_fp8_kernel(k):
     assert got.dtype == FP8 and got.shape == (T, H, R + rope)
     want = ref.mla_absorb_rope(q.clone(), kc, pos, cache_cs, nope)
     assert _rel(got.float(), want.float().clamp(-448, 448)) < 4e-2
-    # sparse attention and bf16 caches keep the bf16 query
-    assert k.mla_query(q, kc, pos, cache_cs, nope, kv_cache, False).dtype == torch.bfloat16
+    # the sparse tensor-core kernel reads the same e4m3 query; bf16 caches keep the bf16 query
+    assert k.mla_query(q, kc, pos, cache_cs, nope, kv_cache, False).dtype == FP8
     assert k.mla_query(q, kc, pos, cache_cs, nope, kv_cache.view(torch.uint8).to(torch.bfloat16), True).dtype == torch.bfloat16
 
 
