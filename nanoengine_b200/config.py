@@ -52,7 +52,9 @@ class Config:
     num_speculative_tokens: int = 0
     # sparse attention
     disable_nsa: bool = False
-    enable_hisparse: bool = False
+    enable_hisparse: bool = False            # DSA decode engines: latent cache in pinned host memory, top-k rows staged into a hot device buffer
+    hisparse_device_buffer_size: int = 4096  # hot rows per sequence and layer (a multiple of 64, at least index_topk + 64)
+    hisparse_host_gb: float = 16.0           # pinned host memory for the cold tier when num_kvcache_blocks is not given
     # execution
     enforce_eager: bool = False
     cuda_graph_max_bs: int = 256
@@ -132,7 +134,16 @@ class Config:
         if self.enable_hisparse and not mc.has_indexer:
             raise ValueError("enable_hisparse needs a DSA model (lightning indexer)")
         if self.enable_hisparse:
-            raise ValueError("enable_hisparse: the hot/cold sparse-KV tier is not available in this build")
+            # the hot / cold tier serves decode engines: prompts arrive by PD migration (or are fabricated with dummy_prefill)
+            if self.mode != "decode":
+                raise ValueError("enable_hisparse needs mode='decode' (prefill engines keep their cache on the device)")
+            if self.disable_nsa or self.resolved_kv_dtype() != "fp8" and self.device != "cpu":
+                raise ValueError("enable_hisparse needs the DSA indexer (disable_nsa=False) and kv_cache_dtype='fp8'")
+            if self.num_speculative_tokens or self.attention_sp != 1 or self.num_host_kvcache_blocks or self.l3_dir:
+                raise ValueError("enable_hisparse excludes speculative decoding, attention_sp > 1 and the host-swap / L3 tiers")
+            hb = self.hisparse_device_buffer_size
+            if hb % 64 or hb < mc.index_topk + 64:
+                raise ValueError("hisparse_device_buffer_size must be a multiple of 64 and at least index_topk + 64")
         if self.dummy_prefill and not self.enable_hisparse:
             raise ValueError("dummy_prefill only applies to a HiSparse decode engine (enable_hisparse=True)")
         if self.eplb_redundant_experts:

@@ -57,6 +57,16 @@ def _dummy_batch(is_prefill: bool):
     return b
 
 
+class _NoCopyMigrator:
+    """Migrator of a dummy-prefill decode engine: every import "succeeds" without moving a byte."""
+
+    def pull(self, blobs):
+        ids = []
+        for blob in blobs:
+            ids += list(C.MigrationIn.from_bytes(blob).seq_ids)
+        return ids, [], 0
+
+
 class LLMEngine:
     def __init__(self, config: Config, executor=None):
         self.config = config
@@ -71,7 +81,7 @@ class LLMEngine:
             raise RuntimeError("no memory left for the KV cache; lower gpu_memory_utilization or the model size")
         from ..runtime.cache import make_cache_plan
         plan = make_cache_plan(config.model_config, config.resolved_kv_dtype(), config.kvcache_block_size, config.attention_tp,
-                               use_indexer=config.use_nsa())
+                               use_indexer=config.use_nsa(), hisparse_rows=config.hisparse_device_buffer_size if config.enable_hisparse else 0)
         self.scheduler = C.Scheduler(build_scheduler_config(config, self.num_blocks, plan.plan_bits()))
         self.executor.collective_rpc("allocate_kvcache", self.num_blocks)
         self._next_seq_id = 1
@@ -95,6 +105,17 @@ class LLMEngine:
             seq_id = self._next_seq_id
         self._next_seq_id = max(self._next_seq_id, seq_id) + 1
         sp = sampling_params or C.SamplingParams()
+        if self.config.dummy_prefill:
+            # a decode engine without a prefill peer: the prompt arrives as if it had been migrated, its cache rows stay what
+            # the (zero-initialised) cold tier holds and its first token is made up; the serving flow, slot handling and graph
+            # replay are exercised, the text is meaningless (reference docs/hisparse-design.md, "Dummy-prefill flow")
+            m = C.RequestMigrate()
+            m.seq_id, m.token_ids, m.prompt_len = seq_id, list(prompt_token_ids) + [int(prompt_token_ids[-1])], len(prompt_token_ids)
+            m.num_computed, m.sampling_params, m.affinity_key = len(prompt_token_ids), sp, affinity_key
+            m.migrate_block_table, m.migrate_engine_id, m.block_size = [], "dummy-prefill", self.config.kvcache_block_size
+            if self.migrator is None:
+                self.migrator = _NoCopyMigrator()
+            return self.scheduler.add_request_bytes(m.to_bytes())
         if self.l3_enabled:
             self._l3_import(prompt_token_ids)
         return self.scheduler.add_request(C.RequestIn(seq_id, list(prompt_token_ids), sp, affinity_key))

@@ -101,6 +101,8 @@ class MLAAttention(nn.Module):
             q = self.q_proj(x)
             kv_a = self.kv_a_proj_with_mqa(x)
         q = q.view(T, H, nope + rope)
+        if ctx.hisparse is not None and not ctx.is_prefill and self.indexer is not None:
+            return self._forward_hot_cold(x, q, q_c, kv_a, positions, ctx, rope_cache)
         cache = ctx.kv_caches[self.cache_idx]
         ops.mla_kv_prepare(kv_a, self.kv_a_layernorm.weight, self.kv_a_layernorm.eps, positions, rope_cache, cache, ctx.slot_mapping, R)
         sparse = None
@@ -113,6 +115,30 @@ class MLAAttention(nn.Module):
         o = ops.bmm_absorb(o_lat, self.vc, wt=self.vc_t).reshape(T, H * self.v)           # [T, H * v]
         if self.g_proj is not None:
             o = ops.sigmoid_mul(o, self.g_proj(ops.dense(x)))
+        return self.o_proj(o)
+
+
+    def _forward_hot_cold(self, x, q, q_c, kv_a, positions, ctx: ForwardContext, rope_cache):
+        """Decode step under the hot / cold tier: the indexer lists key positions, the tier makes them resident in the
+        sequence's hot buffer (the new token's row included), the key path writes the new row there and copies it back to
+        the cold pages, and the sparse attention reads the hot buffer.
+        Parity: reference docs/hisparse-design.md "Model forward", runtime/context/cache/hisparse.py:294-316."""
+        T, H, R, nope = x.shape[0], self.H, self.R, self.nope
+        assert ctx.q_len_uniform == 1, "the hot / cold tier serves plain decode steps (one new token per sequence)"
+        tier = ctx.hisparse
+        L = tier.layer(self.cache_idx)
+        xd = ops.dense(x)
+        sel = self.indexer(xd, ops.dense(q_c) if q_c is not None else xd, positions, ctx, rope_cache, logical=True)
+        hot_ids, new_slot = ops.hisparse_stage(L, sel, ctx.hs_slots, ctx.context_lens, ctx.block_tables)
+        dt = ctx.kv_caches[self.cache_idx].dtype
+        hot = tier.hot_pages(self.cache_idx, dt)
+        ops.mla_kv_prepare(kv_a, self.kv_a_layernorm.weight, self.kv_a_layernorm.eps, positions, rope_cache, hot, new_slot, R)
+        ops.hisparse_writeback(L["hot"], L["cold"], new_slot, ctx.slot_mapping)
+        q_full = ops.mla_query(q, self.kc, positions, rope_cache, nope, hot, False, kc_t=self.kc_t)
+        o_lat = ops.mla_attention_paged(q_full, hot, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale, R, sparse_indices=hot_ids)
+        o = ops.bmm_absorb(o_lat, self.vc, wt=self.vc_t).reshape(T, H * self.v)
+        if self.g_proj is not None:
+            o = ops.sigmoid_mul(o, self.g_proj(xd))
         return self.o_proj(o)
 
 

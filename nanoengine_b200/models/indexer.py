@@ -56,14 +56,16 @@ class LightningIndexer(nn.Module):
             self.k_norm_bias.copy_(w.to(self.k_norm_bias.dtype))
 
     # ---- forward -----------------------------------------------------------------------------
-    def forward(self, hidden: torch.Tensor, q_in: torch.Tensor, positions: torch.Tensor, ctx: ForwardContext, rope_cache: torch.Tensor
-                ) -> Optional[torch.Tensor]:
+    def forward(self, hidden: torch.Tensor, q_in: torch.Tensor, positions: torch.Tensor, ctx: ForwardContext, rope_cache: torch.Tensor,
+                logical: bool = False) -> Optional[torch.Tensor]:
+        """Physical cache rows of the selected keys of every token ([T, topk], -1 padded), or None when every context fits the
+        list (dense attention).  `logical`: always select, and list key positions (the hot / cold tier maps them itself)."""
         T = hidden.shape[0]
         rd = self.rope_dim
         q = self.wq_b(q_in).view(T, self.Hi, self.D)
         cache = ctx.indexer_caches[self.layer_idx]
         ops.indexer_k_store(self.wk(hidden), self.k_norm_weight, self.k_norm_bias, 1e-6, positions, rope_cache, rd, cache, ctx.slot_mapping)
-        if max(ctx.context_lens_host or [ctx.max_seqlen_k]) <= self.topk:
+        if not logical and max(ctx.context_lens_host or [ctx.max_seqlen_k]) <= self.topk:
             return None                                   # every key is selected anyway: dense attention
         q8, qs = ops.indexer_q_prep(q, positions, rope_cache, rd)
         w = self.weights_proj(hidden).float() * (self.Hi ** -0.5) * self.softmax_scale
@@ -71,4 +73,4 @@ class LightningIndexer(nn.Module):
         cl = ctx.context_lens_host if ctx.context_lens_host is not None else ctx.context_lens
         if hidden.is_cuda:
             cu, cl = ctx.cu_seqlens_q, ctx.context_lens       # device tables: no host round trip inside a captured graph
-        return ops.indexer_select(q8, qs, w, cache, ctx.block_tables, cu, cl, self.topk)
+        return ops.indexer_select(q8, qs, w, cache, ctx.block_tables, cu, cl, self.topk, logical)

@@ -526,9 +526,10 @@ def indexer_gather(cache: torch.Tensor, block_table: torch.Tensor, n: int, D: in
 
 
 def indexer_select(q8: torch.Tensor, q_scale: torch.Tensor, head_w: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
-                   cu_seqlens_q, context_lens, topk: int) -> torch.Tensor:
+                   cu_seqlens_q, context_lens, topk: int, logical: bool = False) -> torch.Tensor:
     """Per token: physical slots of the `topk` visible keys with the largest indexer score, -1 padded ([T, topk] int32).
-    cu_seqlens_q / context_lens: host lists or tensors."""
+    cu_seqlens_q / context_lens: host lists or tensors.  `logical`: return key positions instead of physical slots (the
+    hot / cold tier maps them itself)."""
     T, Hi, D = q8.shape
     cu = cu_seqlens_q.tolist() if isinstance(cu_seqlens_q, torch.Tensor) else list(cu_seqlens_q)
     cl = context_lens.tolist() if isinstance(context_lens, torch.Tensor) else list(context_lens)
@@ -543,8 +544,91 @@ def indexer_select(q8: torch.Tensor, q_scale: torch.Tensor, head_w: torch.Tensor
         logits = indexer_logits(q8[lo:hi], q_scale[lo:hi], head_w[lo:hi], keys, kscale)
         valid = torch.arange(n - (hi - lo) + 1, n + 1, device=q8.device)
         idx = indexer_topk(logits, valid, topk)
-        out[lo:hi] = logical_to_physical(idx, block_tables[i:i + 1].expand(hi - lo, -1), bs)
+        out[lo:hi] = idx if logical else logical_to_physical(idx, block_tables[i:i + 1].expand(hi - lo, -1), bs)
     return out
+
+
+# ---- hot / cold tier of the sparse-attention cache --------------------------------------------------------------------------
+def hisparse_stage(L: dict, sel: torch.Tensor, slots: torch.Tensor, context_lens: torch.Tensor, block_tables: torch.Tensor):
+    """Make the listed key positions of every sequence resident in its hot buffer and return their hot row ids.
+
+    L: one layer's tier tensors (runtime/hisparse.py::HiSparseTier.layer).  sel [B, topk] key positions, -1 padded; the token
+    being decoded sits at position context_len - 1 and always gets a row (the key kernel writes it afterwards, nothing is
+    copied for it).  Positions already resident are stamped as used in this step; the others take, in ring order from the
+    slot's cursor, rows that were not used in this step, evict their occupants and are copied in from the cold pages.
+    Returns (hot_ids [B, topk] int32: slot * hot_rows + row, or -1; new_slot [B] int64: hot row id of the new token)."""
+    p2h, h2p, stamp, cursor, stepc, cold, hot = L["pos_to_hot"], L["hot_to_pos"], L["stamp"], L["cursor"], L["step"], L["cold"], L["hot"]
+    page_rows = L["page_rows"]
+    B, topk = sel.shape
+    hot_rows, max_ctx = h2p.shape[1], p2h.shape[1]
+    out = torch.full((B, topk), -1, dtype=torch.int32, device=sel.device)
+    new_slot = torch.zeros(B, dtype=torch.int64, device=sel.device)
+    step = int(stepc[0]) + 1
+    cold_rows = cold.reshape(-1, cold.shape[-1])
+    for b in range(B):
+        s = int(slots[b])
+        new_pos = int(context_lens[b]) - 1
+        row0 = s * hot_rows
+        misses, i_new = [], -1
+        for i, p in enumerate(sel[b].tolist()):
+            if p < 0 or p >= max_ctx:
+                continue
+            if p == new_pos:
+                i_new = i
+                continue
+            h = int(p2h[s, p])
+            if h >= 0:
+                stamp[s, h] = step
+                out[b, i] = row0 + h
+            else:
+                misses.append(i)
+        hn, need_new = -1, False
+        if 0 <= new_pos < max_ctx:
+            hn = int(p2h[s, new_pos])
+            if hn >= 0:
+                stamp[s, hn] = step
+            else:
+                need_new = True
+        need = len(misses) + int(need_new)
+        cur, victims, scanned = int(cursor[s]), [], 0
+        for j in range(hot_rows):
+            if len(victims) >= need:
+                break
+            h = (cur + j) % hot_rows
+            if int(stamp[s, h]) != step:
+                victims.append(h)
+                scanned = j + 1
+
+        def take(h, p):
+            old = int(h2p[s, h])
+            if old >= 0:
+                p2h[s, old] = -1
+            h2p[s, h] = p; p2h[s, p] = h; stamp[s, h] = step
+
+        if need_new and victims:
+            hn = victims[0]
+            take(hn, new_pos)
+        new_slot[b] = row0 + (hn if hn >= 0 else 0)
+        if i_new >= 0 and hn >= 0:
+            out[b, i_new] = row0 + hn
+        for m, i in enumerate(misses):
+            v = m + int(need_new)
+            if v >= len(victims):
+                continue                                  # hot buffer smaller than one step's demand: the key is dropped
+            p, h = int(sel[b, i]), victims[v]
+            take(h, p)
+            out[b, i] = row0 + h
+            page = int(block_tables[b, p // page_rows])
+            hot[row0 + h] = cold_rows[page * page_rows + p % page_rows].to(hot.device)
+        cursor[s] = (cur + scanned) % hot_rows
+    stepc[0] = step
+    return out, new_slot
+
+
+def hisparse_writeback(hot: torch.Tensor, cold: torch.Tensor, new_slot: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """Copy the row just written for every sequence from its hot row to its logical row of the cold pages."""
+    cold_rows = cold.reshape(-1, cold.shape[-1])
+    cold_rows[slot_mapping.long().to(cold.device)] = hot[new_slot.long()].to(cold.device)
 
 
 # ---- small GEMM-shaped helpers -------------------------------------------------------------------

@@ -554,8 +554,9 @@ def indexer_q_prep(q, positions, rope_cache, rope_dim):
 INDEXER_LOGITS_BYTES = 1 << 30          # query tokens are processed in chunks whose logits fit this budget
 
 
-def indexer_select(q8, q_scale, head_w, cache, block_tables, cu_seqlens_q, context_lens, topk: int) -> torch.Tensor:
-    """fp8 logits on the tensor cores (one CTA per token and key split) followed by the radix top-k with page translation."""
+def indexer_select(q8, q_scale, head_w, cache, block_tables, cu_seqlens_q, context_lens, topk: int, logical: bool = False) -> torch.Tensor:
+    """fp8 logits on the tensor cores (one CTA per token and key split) followed by the radix top-k with page translation
+    (`logical`: no translation, the list holds key positions)."""
     T, Hi, D = q8.shape
     dev = q8.device
     bs = cache.shape[1] // (D + 4)
@@ -581,10 +582,33 @@ def indexer_select(q8, q_scale, head_w, cache, block_tables, cu_seqlens_q, conte
         _ck(l.ne_indexer_logits(_c.c_void_p(q8c.data_ptr() + t0 * Hi * D), _c.c_void_p(qs.data_ptr() + t0 * Hi * 4), _c.c_void_p(w.data_ptr() + t0 * Hi * 4),
                                 _p(cache), _c.c_int(cache.shape[0]), _c.c_longlong(cache.shape[1]), _p(bt), _c.c_int(bt.stride(0)), _p(cu_c), _p(cl),
                                 _c.c_int(B), _c.c_int(n), _c.c_int(Hi), _c.c_int(splits), _p(logits), _c.c_longlong(ld), _st()), "ne_indexer_logits")
-        _ck(l.ne_indexer_topk(_p(logits), _c.c_longlong(ld), _p(cu_c), _p(cl), _c.c_int(B), _p(bt), _c.c_int(bt.stride(0)), _c.c_int(bs),
+        _ck(l.ne_indexer_topk(_p(logits), _c.c_longlong(ld), _p(cu_c), _p(cl), _c.c_int(B), _p(None if logical else bt), _c.c_int(bt.stride(0)), _c.c_int(bs),
                               _c.c_int(topk), _c.c_int(n), _c.c_void_p(out.data_ptr() + t0 * topk * 4), _st()), "ne_indexer_topk")
     return out
 dequant_fp8_1x128 = ref.dequant_fp8_1x128
+
+
+# ---- hot / cold tier of the sparse-attention cache ---------------------------------------------------------------------------
+def hisparse_stage(L: dict, sel: torch.Tensor, slots: torch.Tensor, context_lens: torch.Tensor, block_tables: torch.Tensor):
+    """One kernel, one CTA per sequence: stamps the resident positions, picks victims in ring order, copies the missing rows
+    from the cold pages (pinned host memory, read through the unified address space) and emits hot row ids."""
+    B, topk = sel.shape
+    hot, cold = L["hot"], L["cold"]
+    assert sel.dtype == torch.int32 and sel.is_contiguous() and hot.is_cuda and hot.is_contiguous() and cold.is_contiguous()
+    assert cold.is_pinned() or cold.is_cuda, "the cold pages must be pinned host memory (or device memory)"
+    bt = block_tables if (block_tables.dtype == torch.int32 and block_tables.stride(1) == 1) else block_tables.int().contiguous()
+    out = torch.empty(B, topk, dtype=torch.int32, device=sel.device)
+    new_slot = torch.empty(B, dtype=torch.int64, device=sel.device)
+    _ck(lib().ne_hisparse_stage(_p(L["pos_to_hot"]), _p(L["hot_to_pos"]), _p(L["stamp"]), _p(L["cursor"]), _p(L["step"]), _c.c_void_p(cold.data_ptr()),
+                                _p(hot), _p(sel), _c.c_int(topk), _p(_i32(slots)), _p(_i32(context_lens)), _p(bt), _c.c_int(bt.stride(0)), _p(out),
+                                _p(new_slot), _c.c_int(L["pos_to_hot"].shape[1]), _c.c_int(L["hot_to_pos"].shape[1]), _c.c_int(hot.shape[1]),
+                                _c.c_int(L["page_rows"]), _c.c_int(B), _st()), "ne_hisparse_stage")
+    return out, new_slot
+
+
+def hisparse_writeback(hot: torch.Tensor, cold: torch.Tensor, new_slot: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    _ck(lib().ne_hisparse_writeback(_p(hot), _c.c_void_p(cold.data_ptr()), _p(new_slot), _p(_i64c(slot_mapping)), _c.c_int(hot.shape[1]),
+                                    _c.c_int(new_slot.numel()), _st()), "ne_hisparse_writeback")
 
 
 # ---- gated delta-net linear attention ---------------------------------------------------------------

@@ -51,6 +51,12 @@ class CachePlan:
     # GQA families whose layers have different head dims: the head dim of every cache layer (row_dim is their maximum; a
     # layer with a smaller one uses the front of its slab)
     layer_dims: Optional[List[int]] = None
+    # hot / cold tier (DSA decode engines): the latent pages live in pinned host memory, `hot_rows` rows per sequence slot
+    # and layer on the device
+    hisparse: bool = False
+    hot_rows: int = 0
+    hs_slots: int = 0
+    max_ctx: int = 0
 
     @property
     def state_slot_bytes(self) -> int:
@@ -77,7 +83,15 @@ class CachePlan:
 
     @property
     def block_bytes(self) -> int:
-        return self.kv_block_bytes + self.indexer_block_bytes
+        """Device bytes one logical page costs (under the hot / cold tier only the indexer keys of a page are on the device)."""
+        return (0 if self.hisparse else self.kv_block_bytes) + self.indexer_block_bytes
+
+    @property
+    def hisparse_device_bytes(self) -> int:
+        if not self.hisparse:
+            return 0
+        n = self.hs_slots + 1
+        return self.num_layers * n * (self.hot_rows * (self.row_dim + 8) + self.max_ctx * 4 + 4)
 
     def plan_bits(self) -> int:
         from .._native import _core as C
@@ -86,11 +100,23 @@ class CachePlan:
             bits |= C.PLAN_INDEXER
         if self.gdn:
             bits |= C.PLAN_GDN
+        if self.hisparse:
+            bits |= C.PLAN_HISPARSE
         return bits
 
 
 def make_cache_plan(mc: ModelConfig, kv_dtype_name: str, block_size: int, attn_tp: int = 1, num_mtp_layers: int = 0,
-                    use_indexer: bool = True, num_layers: Optional[int] = None, state_slots: int = 0) -> CachePlan:
+                    use_indexer: bool = True, num_layers: Optional[int] = None, state_slots: int = 0, hisparse_rows: int = 0,
+                    max_ctx: int = 0) -> CachePlan:
+    plan = _make_cache_plan(mc, kv_dtype_name, block_size, attn_tp, num_mtp_layers, use_indexer, num_layers, state_slots)
+    if hisparse_rows:
+        assert plan.mla and plan.indexer, "the hot / cold tier needs an MLA cache with the DSA indexer"
+        plan.hisparse, plan.hot_rows, plan.hs_slots, plan.max_ctx = True, hisparse_rows, state_slots, max_ctx
+    return plan
+
+
+def _make_cache_plan(mc: ModelConfig, kv_dtype_name: str, block_size: int, attn_tp: int = 1, num_mtp_layers: int = 0,
+                     use_indexer: bool = True, num_layers: Optional[int] = None, state_slots: int = 0) -> CachePlan:
     L = (num_layers if num_layers is not None else mc.num_hidden_layers) + num_mtp_layers
     dt = torch_dtype(kv_dtype_name)
     if mc.is_hybrid_gdn and mc.is_mla:
@@ -128,8 +154,14 @@ class KVCache:
         self.plan, self.num_blocks, self.device = plan, num_blocks, torch.device(device)
         nb = num_blocks + 1   # + scratch page
         self.scratch_block = num_blocks
+        self.hisparse = None
         if plan.mla:
-            self.kv = torch.zeros(plan.num_layers, nb, plan.block_size, plan.row_dim, dtype=torch.uint8 if plan.kv_dtype == torch.float8_e4m3fn else plan.kv_dtype, device=device)
+            # under the hot / cold tier the logical pages are the cold tier: pinned host memory the staging kernel reads
+            # through the unified address space
+            kv_dev = "cpu" if plan.hisparse else device
+            self.kv = torch.zeros(plan.num_layers, nb, plan.block_size, plan.row_dim, dtype=torch.uint8 if plan.kv_dtype == torch.float8_e4m3fn else plan.kv_dtype, device=kv_dev)
+            if plan.hisparse and self.device.type == "cuda":
+                self.kv = self.kv.pin_memory()
             if plan.kv_dtype == torch.float8_e4m3fn:
                 self.kv = self.kv.view(torch.float8_e4m3fn)
             self.layers: List = [self.kv[l] for l in range(plan.num_layers)]
@@ -145,6 +177,11 @@ class KVCache:
         if plan.indexer:
             self.indexer = torch.zeros(plan.num_layers, nb, plan.block_size * (plan.index_dim + 4), dtype=torch.uint8, device=device)
             self.indexer_layers = [self.indexer[l] for l in range(plan.num_layers)]
+        if plan.hisparse:
+            from .hisparse import HiSparseTier
+            es = torch.empty(0, dtype=plan.kv_dtype).element_size()
+            self.hisparse = HiSparseTier(plan.num_layers, plan.hs_slots, plan.hot_rows, plan.max_ctx, plan.row_dim * es,
+                                         [self.kv[l] for l in range(plan.num_layers)], device)
         self.host_kv = None
         self.host_families = {}
         self.rec_states = self.conv_states = None

@@ -34,6 +34,9 @@ class ForwardContext:
     seq_fresh: Optional[torch.Tensor] = None        # int32 [B], 1 = no state carried in (first chunk of the prompt)
     conv_states: Optional[List[Any]] = None         # per linear layer [slots, K-1, conv_dim]
     rec_states: Optional[List[Any]] = None          # per linear layer [slots, Hv, Dv, Dk] fp32
+    # hot / cold tier of the sparse-attention cache: the tier object and the hot-buffer slot of each sequence
+    hisparse: Optional[Any] = None
+    hs_slots: Optional[torch.Tensor] = None         # int32 [B]
     extras: Dict[str, Any] = field(default_factory=dict)   # per-forward scratch shared by layers (e.g. DSA top-k reuse)
     # host copies for the CPU reference path and for planning
     cu_seqlens_q_host: Optional[List[int]] = None

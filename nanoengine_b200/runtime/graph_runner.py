@@ -51,6 +51,9 @@ class DecodeGraphRunner:
         self.gdn = runner.plan.gdn
         self.state_slots = torch.full((self.max_bs,), runner.cache.scratch_slot, dtype=torch.int32, device=dev)
         self.seq_fresh = torch.zeros(self.max_bs, dtype=torch.int32, device=dev)
+        # hot / cold tier: hot-buffer slot of every row (padding rows use the tier's scratch slot)
+        self.hs = runner.cache.hisparse
+        self.hs_slots = torch.full((self.max_bs,), self.hs.scratch_slot if self.hs is not None else 0, dtype=torch.int32, device=dev)
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.outputs: Dict[int, torch.Tensor] = {}
         self.pool = None
@@ -73,7 +76,8 @@ class DecodeGraphRunner:
             max_seqlen_k=self.r.config.max_model_len, last_token_indices=None, q_len_uniform=q,
             kv_caches=self.r.cache.layers, indexer_caches=self.r.cache.indexer_layers,
             state_slots=self.state_slots[:b] if self.gdn else None, seq_fresh=self.seq_fresh[:b] if self.gdn else None,
-            conv_states=self.r.cache.conv_states, rec_states=self.r.cache.rec_states)
+            conv_states=self.r.cache.conv_states, rec_states=self.r.cache.rec_states,
+            hisparse=self.hs, hs_slots=self.hs_slots[:b] if self.hs is not None else None)
 
     def _fill(self, ids, pos, ctx: ForwardContext, b: int):
         n, q = ctx.num_seqs, self.q_len
@@ -88,6 +92,9 @@ class DecodeGraphRunner:
             self.state_slots[:n].copy_(ctx.state_slots)
             self.seq_fresh[:n].copy_(ctx.seq_fresh)
             self.state_slots[n:b].fill_(self.r.cache.scratch_slot)
+        if self.hs is not None:
+            self.hs_slots[:n].copy_(ctx.hs_slots)
+            self.hs_slots[n:b].fill_(self.hs.scratch_slot)
         if n < b:
             # padding rows: q_len tokens of a one-page sequence on the scratch page
             self.input_ids[n * q: b * q].zero_()
@@ -104,6 +111,8 @@ class DecodeGraphRunner:
             # the warm-up runs execute real steps: point every row at the scratch slot so no live sequence's state advances
             # (rows sharing one slot race on it, which is harmless for scratch data); run() refills the live slots afterwards
             self.state_slots[:b].fill_(self.r.cache.scratch_slot)
+        if self.hs is not None:
+            self.hs_slots[:b].fill_(self.hs.scratch_slot)      # same for the hot buffers: the warm-ups stage into the scratch slot
         # eager warm-up on the side stream: sets kernel attributes, fills caches of derived weights, sizes the allocator
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
@@ -132,6 +141,8 @@ class DecodeGraphRunner:
         if self.gdn:
             self.state_slots[:b].fill_(self.r.cache.scratch_slot)
             self.seq_fresh[:b].fill_(1)
+        if self.hs is not None:
+            self.hs_slots[:b].fill_(self.hs.scratch_slot)
 
     def capture_all(self) -> None:
         """Capture every bucket now, largest first (the pool is sized once), on dummy rows.  Collective: all ranks of the

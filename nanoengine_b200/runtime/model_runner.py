@@ -86,7 +86,9 @@ class ModelRunner:
         self.d2h_bytes = 0          # bytes read back (sampled tokens, log-probabilities)
         self._last_decode = None
         self.plan = make_cache_plan(self.mc, config.resolved_kv_dtype(), config.kvcache_block_size, config.attention_tp,
-                                    num_mtp_layers=self._num_mtp_layers(), use_indexer=config.use_nsa(), state_slots=config.max_num_seqs)
+                                    num_mtp_layers=self._num_mtp_layers(), use_indexer=config.use_nsa(), state_slots=config.max_num_seqs,
+                                    hisparse_rows=config.hisparse_device_buffer_size if config.enable_hisparse else 0,
+                                    max_ctx=(config.max_model_len or self.mc.max_position_embeddings))
 
     def _num_mtp_layers(self) -> int:
         return max(1, self.mc.num_nextn_predict_layers) if self.config.num_speculative_tokens > 0 else 0
@@ -235,7 +237,11 @@ class ModelRunner:
         peak = torch.cuda.max_memory_allocated()
         used = total - free
         torch.cuda.empty_cache()
-        return kv_budget_blocks(self.plan, total, self.config.gpu_memory_utilization, used, peak, current, reserved=self.plan.state_bytes)
+        blocks = kv_budget_blocks(self.plan, total, self.config.gpu_memory_utilization, used, peak, current,
+                                  reserved=self.plan.state_bytes + self.plan.hisparse_device_bytes)
+        if self.plan.hisparse:      # the cold tier is bounded by the pinned host memory it may take
+            blocks = min(blocks, int(self.config.hisparse_host_gb * (1 << 30)) // max(1, self.plan.kv_block_bytes))
+        return blocks
 
     def _warmup_prefill(self, tokens: int) -> None:
         bs = self.plan.block_size
@@ -310,6 +316,12 @@ class ModelRunner:
             cu_seqlens_q_host=d["cu_seqlens_q"].tolist(), context_lens_host=d["context_lens"].tolist())
         ctx.extras["input_ids"] = self._to_dev(d["input_ids"]).long()
         ctx.extras["positions"] = self._to_dev(d["positions"]).long()
+        if self.cache.hisparse is not None:
+            tier = self.cache.hisparse
+            for s, sid in zip(b.hisparse_slots, b.seq_ids):
+                tier.assign(int(s), int(sid))
+            ctx.hisparse = tier
+            ctx.hs_slots = self._to_dev(np.asarray([s if s >= 0 else tier.scratch_slot for s in b.hisparse_slots], dtype=np.int32))
         if self.plan.gdn:
             # a sequence whose whole context arrives in this step carries no state in; unassigned slots go to the scratch slot
             slots = np.asarray([s if s >= 0 else self.cache.scratch_slot for s in b.state_slots], dtype=np.int32)
@@ -331,6 +343,9 @@ class ModelRunner:
             kv_caches=self.cache.layers, indexer_caches=self.cache.indexer_layers, cu_seqlens_q_host=[0, 1], context_lens_host=[1])
         ctx.extras["input_ids"] = torch.zeros(1, dtype=torch.long, device=dev)
         ctx.extras["positions"] = torch.zeros(1, dtype=torch.long, device=dev)
+        if self.cache.hisparse is not None:
+            ctx.hisparse = self.cache.hisparse
+            ctx.hs_slots = torch.tensor([self.cache.hisparse.scratch_slot], dtype=torch.int32, device=dev)
         if self.plan.gdn:
             ctx.state_slots = torch.tensor([self.cache.scratch_slot], dtype=torch.int32, device=dev)
             ctx.seq_fresh = torch.ones(1, dtype=torch.int32, device=dev)
