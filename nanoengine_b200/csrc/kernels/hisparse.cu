@@ -52,14 +52,30 @@ __global__ void __launch_bounds__(256) hisparse_stage_kernel(const HsArgs a) {
   const long long row0 = (long long)slot * a.hot_rows;
   if (tid == 0) { s_nmiss = 0; s_inew = -1; s_need_new = 0; s_hnew = -1; s_base = 0; s_scanned = 0; }
   __syncthreads();
-  // A: hits are stamped, misses are listed
-  for (int i = tid; i < a.topk; i += 256) {
-    const int p = sel[i];
-    if (p < 0 || p >= a.max_ctx) { out[i] = -1; continue; }
-    if (p == new_pos) { s_inew = i; continue; }
-    const int h = p2h[p];
-    if (h >= 0) { stp[h] = step; out[i] = (int)(row0 + h); }
-    else s_miss[atomicAdd(&s_nmiss, 1)] = i;
+  // A: hits are stamped, misses are listed in list order (ordered compaction: the same victims go to the same positions on
+  // every run, and the tables equal those of the plain PyTorch statement)
+  for (int i0 = 0; i0 < a.topk; i0 += 256) {
+    const int i = i0 + tid;
+    bool miss = false;
+    if (i < a.topk) {
+      const int p = sel[i];
+      if (p < 0 || p >= a.max_ctx) out[i] = -1;
+      else if (p == new_pos) s_inew = i;
+      else {
+        const int h = p2h[p];
+        if (h >= 0) { stp[h] = step; out[i] = (int)(row0 + h); }
+        else miss = true;
+      }
+    }
+    const unsigned bal = __ballot_sync(0xffffffffu, miss);
+    if (lane == 0) s_wcnt[warp] = __popc(bal);
+    __syncthreads();
+    int off = s_nmiss;
+    for (int w = 0; w < warp; w++) off += s_wcnt[w];
+    if (miss) s_miss[off + __popc(bal & ((1u << lane) - 1u))] = i;
+    __syncthreads();
+    if (tid == 0) { int t = 0; for (int w = 0; w < 8; w++) t += s_wcnt[w]; s_nmiss += t; }
+    __syncthreads();
   }
   if (tid == 0 && new_pos >= 0 && new_pos < a.max_ctx) {
     const int h = p2h[new_pos];
