@@ -63,15 +63,45 @@ def reference_arm(args):
     return 0
 
 
+def _fill_random_cache(cache):
+    """Random finite e4m3 bytes in the latent pages and the indexer keys, small positive key scales: what a prefill would have
+    left, as far as the cost of a decode step goes."""
+    import torch
+    dev = "cuda" if torch.cuda.is_available() else "cpu"           # generated on the GPU, also for pages that live in host memory
+    g = torch.Generator(device=dev).manual_seed(7)
+
+    def rnd_bytes(shape):
+        return (torch.randint(0, 0x70, shape, dtype=torch.uint8, generator=g, device=dev)
+                | (torch.randint(0, 2, shape, dtype=torch.uint8, generator=g, device=dev) << 7))
+
+    kv = cache.kv.view(torch.uint8)
+    for l in range(kv.shape[0]):                                   # layer by layer: the host-side generator buffers stay small
+        kv[l].copy_(rnd_bytes(tuple(kv[l].shape)))
+    if cache.indexer is not None:
+        L, nb, pb = cache.indexer.shape
+        D = pb // 64 - 4
+        for l in range(L):
+            page = torch.empty(nb, pb, dtype=torch.uint8, device=dev)
+            page[:, : 64 * D] = rnd_bytes((nb, 64 * D))
+            page[:, 64 * D:] = (torch.rand(nb, 64, generator=g, device=dev) * 0.01 + 0.001).view(torch.uint8)
+            cache.indexer[l].copy_(page)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--model", default="deepseek-v3", choices=["deepseek-v3", "qwen3-235b"],
-                    help="deepseek-v3: the headline (fp8, attention-DP + EP); qwen3-235b: bf16 GQA MoE with tensor-parallel attention + EP "
-                         "(the batch is shared by the TP ranks: --seqs-per-gpu is then the size of the whole batch)")
+    ap.add_argument("--model", default="deepseek-v3", choices=["deepseek-v3", "deepseek-v32", "qwen3-235b"],
+                    help="deepseek-v3: the headline (fp8, attention-DP + EP); deepseek-v32: the same body with the DSA indexer and sparse "
+                         "attention (long-context decode, see --synthetic-context); qwen3-235b: bf16 GQA MoE with tensor-parallel attention + "
+                         "EP (the batch is shared by the TP ranks: --seqs-per-gpu is then the size of the whole batch)")
+    ap.add_argument("--synthetic-context", action="store_true",
+                    help="decode-only: sequences are admitted with --prompt-len tokens of context whose cache rows are random bytes (no "
+                         "prefill pass; a 64 x 65,536-token prefill would take minutes).  The decode step does all of its work.")
+    ap.add_argument("--hisparse", type=int, default=0, help="with --synthetic-context: hot rows per sequence of the hot / cold cache tier "
+                    "(the latent cache then lives in pinned host memory)")
     ap.add_argument("--seqs-per-gpu", type=int, default=128)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=61, help="debug only: anything but 61 marks the result invalid")
@@ -109,6 +139,9 @@ def main():
         if args.layers == 61:
             args.layers = 94
         mc = qwen3_235b(n_routed_experts=args.experts_per_gpu * N, num_hidden_layers=args.layers)
+    elif args.model == "deepseek-v32":
+        from nanoengine_b200.models.config import deepseek_v32
+        mc = deepseek_v32(n_routed_experts=args.experts_per_gpu * N, num_hidden_layers=args.layers)
     else:
         mc = deepseek_v3(n_routed_experts=args.experts_per_gpu * N, num_hidden_layers=args.layers, num_nextn_predict_layers=1 if args.mtp else 0)
     S, P = args.seqs_per_gpu, args.prompt_len
@@ -118,10 +151,15 @@ def main():
     cfg = Config(model=args.model, model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kv_cache_dtype="bfloat16" if qwen else "fp8",
                  max_num_seqs=S, max_num_batched_tokens=16384, max_model_len=P + total_new + 64, num_kvcache_blocks=S * pages + 16,
                  attention_dp=1 if qwen else N, attention_tp=N if qwen else 1, ffn_ep=N, executor_backend="spmd", enable_prefix_caching=False,
-                 cuda_graph_max_bs=S, seed=0 if qwen else rank, num_speculative_tokens=args.mtp)
+                 cuda_graph_max_bs=S, seed=0 if qwen else rank, num_speculative_tokens=args.mtp,
+                 mode="decode" if args.synthetic_context else "hybrid", dummy_prefill=args.synthetic_context,
+                 enable_hisparse=args.hisparse > 0, hisparse_device_buffer_size=args.hisparse or 4096,
+                 hisparse_host_gb=(S * pages + 16) * 64 * 576 * args.layers / 2 ** 30 + 1)
     t_build = time.time()
     llm = LLM(cfg)
     runner = llm.engine.executor.runner
+    if args.synthetic_context:
+        _fill_random_cache(runner.cache)
     if args.mtp and args.force_accept >= 0:
         runner.mtp_runner.force_accept = args.force_accept
     build_s = time.time() - t_build
@@ -222,14 +260,15 @@ def main():
             "ms_per_step": round(dev_ms, 3), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None if BASELINE_VALUE is None else value / BASELINE_VALUE,
             "dtype": "bf16" if qwen else "fp8 weights + fp8 KV, bf16 activations",
-            "data": "synthetic uniform-random token ids, random-init weights (HF layout)",
+            "data": ("synthetic: random cache rows standing in for the prompts (no prefill pass), random-init weights (HF layout)"
+                     if args.synthetic_context else "synthetic uniform-random token ids, random-init weights (HF layout)"),
             "config": {"model": (f"Qwen3-235B-A22B shape: {args.layers} layers, hidden 4096, 64/4 GQA heads, {args.experts_per_gpu * N} experts "
                                  f"({args.experts_per_gpu}/GPU) top-8, bf16") if qwen else
-                                (f"DeepSeek-V3 shape: {args.layers} layers, hidden 7168, 128 MLA heads, {args.experts_per_gpu * N} routed experts "
+                                (f"DeepSeek-{'V3.2 (DSA top-2048' + (', hot / cold tier ' + str(args.hisparse) + ' rows' if args.hisparse else '') + ')' if args.model == 'deepseek-v32' else 'V3'} shape: {args.layers} layers, hidden 7168, 128 MLA heads, {args.experts_per_gpu * N} routed experts "
                                  f"({args.experts_per_gpu}/GPU) top-8, 1 shared"), "global_batch": tokens_per_step, "seq_len": P,
                        "parallelism": f"tp{N} attention + ep{N} experts" if qwen else f"dp{N} attention + ep{N} experts",
                        "l2": "inputs (the weights streamed every step) exceed L2; no flush",
-                       "valid": (args.layers == 94 and args.experts_per_gpu == 16) if qwen else (args.layers == 61 and args.experts_per_gpu == 32 and S == 128)},
+                       "valid": (args.layers == 94 and args.experts_per_gpu == 16) if qwen else (args.layers == 61 and args.experts_per_gpu == 32 and (S == 128 or args.model == "deepseek-v32"))},
             "decode_tok_s_per_gpu": round(value / N, 1), "tpot_ms": round(dev_ms, 3), "tpot_slo_50ms_met": dev_ms <= 50.0,
             "prefill_tok_s": round(prefill_tok * (1 if qwen else N) / (prefill_ms * 1e-3), 1) if prefill_ms > 0 else None,
             "prefill_tok_s_per_gpu": round(prefill_tok / (N if qwen else 1) / (prefill_ms * 1e-3), 1) if prefill_ms > 0 else None,

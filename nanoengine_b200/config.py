@@ -23,7 +23,7 @@ class Config:
     device: str = "auto"                     # "auto" | "cuda" | "cpu"
     seed: int = 0
     dummy_weight: bool = False               # random-init weights in the HF layout
-    dummy_prefill: bool = False              # HiSparse decode engines only: fabricate KV for arriving prompts (no prefill peer)
+    dummy_prefill: bool = False              # decode engines only: prompts arrive as if migrated, their cache rows are whatever the cache holds (no prefill peer)
     # scheduling
     max_num_batched_tokens: int = 16384
     max_num_seqs: int = 16
@@ -144,8 +144,8 @@ class Config:
             hb = self.hisparse_device_buffer_size
             if hb % 64 or hb < mc.index_topk + 64:
                 raise ValueError("hisparse_device_buffer_size must be a multiple of 64 and at least index_topk + 64")
-        if self.dummy_prefill and not self.enable_hisparse:
-            raise ValueError("dummy_prefill only applies to a HiSparse decode engine (enable_hisparse=True)")
+        if self.dummy_prefill and self.mode != "decode":
+            raise ValueError("dummy_prefill only applies to a decode engine (mode='decode'): prompts arrive as if migrated, with made-up cache rows")
         if self.eplb_redundant_experts:
             if not mc.n_routed_experts or mc.is_hybrid_gdn:
                 raise ValueError("eplb_redundant_experts needs a DeepSeek or Qwen3 MoE model")

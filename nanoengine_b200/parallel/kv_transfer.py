@@ -130,8 +130,10 @@ class LocalTransport:
         dkv.index_copy_(bdim, di, skv.index_select(bdim, si).to(dkv.device))
         n = skv.index_select(bdim, si).numel() * skv.element_size()
         if sc.indexer is not None and dc.indexer is not None:
-            dc.indexer.index_copy_(1, di, sc.indexer.index_select(1, si).to(dc.indexer.device))
-            n += sc.indexer.index_select(1, si).numel()
+            # the indexer keys may sit on another device than the latent pages (hot / cold tier: pages in host memory)
+            rows = sc.indexer.index_select(1, si.to(sc.indexer.device))
+            dc.indexer.index_copy_(1, di.to(dc.indexer.device), rows.to(dc.indexer.device))
+            n += rows.numel()
         if s.mtp_runner is not None and d.mtp_runner is not None and src_slot >= 0 and dst_slot >= 0:
             d.mtp_runner.restore_handoff(dst_slot, s.mtp_runner.publish_handoff(src_slot))
         return n

@@ -32,8 +32,7 @@ def test_stage_kernel_matches_the_reference_step_by_step():
         for b in range(B):
             n = min(topk, ctx[b])
             # a list that overlaps the previous step's (the same generator stream, drifting window) and contains the new position
-            cand = torch.randperm(ctx[b], generator=g)[:n]
-            cand[0] = ctx[b] - 1
+            cand = torch.cat([torch.tensor([ctx[b] - 1]), torch.randperm(ctx[b] - 1, generator=g)[: n - 1]])     # distinct positions
             sel[b, :n] = cand.int()
         cl = torch.tensor(ctx, dtype=torch.int32)
         want_ids, want_new = ref.hisparse_stage(cpu.layer(0), sel, slots, cl, bt)
