@@ -23,7 +23,7 @@ def test_stage_kernel_matches_the_reference_step_by_step():
     hot_rows, max_ctx, topk, row = 256, 1024, 128, 576
     gpu, cpu = _tiers(hot_rows, max_ctx, 48, row)
     B = 3
-    bt = torch.stack([torch.randperm(48)[:16] for _ in range(B)]).int()
+    bt = torch.randperm(48).view(B, 16).int()                                    # disjoint cold pages per sequence
     slots = torch.tensor([2, 0, 1], dtype=torch.int32)
     g = torch.Generator().manual_seed(4)
     ctx = [700, 90, 400]
