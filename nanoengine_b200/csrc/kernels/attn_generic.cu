@@ -29,6 +29,8 @@ struct AttnArgs {
   float* lse;                                     // optional [T, H] natural-log LSE
   int T, H, Dk, Dv; float scale; int fp8;
   int window;                                     // > 0: a query sees only the last `window` key positions up to its own (sliding-window layers)
+  int noncausal;                                  // 1: every query sees all keys of its sequence (vision encoder)
+  int heads_per_cta;                              // 4, or 1 when every query head has its own kv head (the CTA stages one kv head)
 };
 
 __device__ __forceinline__ float load_kv(const void* base, long long idx, int fp8) {
@@ -43,10 +45,10 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(const AttnArgs a) {
   float* sq = sm;
   float* sk = sq + kHeadsPerCta * Dk;
   float* sv = a.v_cache ? sk + kKeysPerTile * (Dk + 1) : nullptr;
-  const int t = blockIdx.x, h0 = blockIdx.y * kHeadsPerCta;
+  const int t = blockIdx.x, h0 = blockIdx.y * a.heads_per_cta;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = h0 + warp;
-  const bool head_ok = h < a.H;
+  const bool head_ok = h < a.H && warp < a.heads_per_cta;
 
   // which sequence owns token t
   int lo = 0, hi = a.num_seqs;
@@ -54,13 +56,13 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(const AttnArgs a) {
   const int seq = lo;
   const int q_len = a.cu_seqlens_q[seq + 1] - a.cu_seqlens_q[seq];
   const int ctx = a.context_lens[seq];
-  const int limit = ctx - q_len + (t - a.cu_seqlens_q[seq]);   // last visible key position
+  const int limit = a.noncausal ? ctx - 1 : ctx - q_len + (t - a.cu_seqlens_q[seq]);   // last visible key position
   const int n_keys = a.sparse ? a.topk : limit + 1;
   const int first_key = (a.window > 0 && !a.sparse) ? max(0, limit - a.window + 1) : 0;
 
   for (int i = threadIdx.x; i < kHeadsPerCta * Dk; i += blockDim.x) {
     int hh = h0 + i / Dk, d = i % Dk;
-    float v = hh < a.H ? __bfloat162float(a.q[(long long)t * a.q_tok_stride + (long long)hh * a.q_head_stride + d]) : 0.f;
+    float v = (hh < a.H && i / Dk < a.heads_per_cta) ? __bfloat162float(a.q[(long long)t * a.q_tok_stride + (long long)hh * a.q_head_stride + d]) : 0.f;
     if (a.fp8) v = e4m3_to_float(to_e4m3(fminf(fmaxf(v, -448.f), 448.f)));
     sq[i] = v;
   }
@@ -214,7 +216,7 @@ extern "C" int ne_attn_generic(const void* q, long long q_tok_stride, int q_head
                                long long kv_slot_stride, int kv_head_stride, int kv_group, const int* block_tables, int bt_stride,
                                int block_size, const int* cu_seqlens_q, const int* context_lens, int num_seqs, const int* sparse, int topk,
                                void* out, long long o_tok_stride, int o_head_stride, float* lse, int T, int H, int Dk, int Dv, float scale,
-                               int fp8, int window, cudaStream_t st) {
+                               int fp8, int window, int noncausal, cudaStream_t st) {
   if (T <= 0) return 0;
   if (Dv > 640 || (kv_group > 1 && kv_group % kHeadsPerCta != 0)) return 1001;
   AttnArgs a;
@@ -222,7 +224,10 @@ extern "C" int ne_attn_generic(const void* q, long long q_tok_stride, int q_head
   a.kv_slot_stride = kv_slot_stride; a.kv_head_stride = kv_head_stride; a.kv_group = kv_group; a.block_tables = block_tables;
   a.bt_stride = bt_stride; a.block_size = block_size; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs;
   a.sparse = sparse; a.topk = topk; a.out = (__nv_bfloat16*)out; a.o_tok_stride = o_tok_stride; a.o_head_stride = o_head_stride; a.lse = lse;
-  a.T = T; a.H = H; a.Dk = Dk; a.Dv = Dv; a.scale = scale; a.fp8 = fp8; a.window = window;
+  a.T = T; a.H = H; a.Dk = Dk; a.Dv = Dv; a.scale = scale; a.fp8 = fp8; a.window = window; a.noncausal = noncausal;
+  // multi-head attention proper (one kv head per query head, separate V): the four query heads of a CTA would need four
+  // different key tiles, so a CTA serves one head there
+  a.heads_per_cta = (kv_group == 1 && kv_head_stride != 0 && v_cache != nullptr) ? 1 : kHeadsPerCta;
   size_t smem = sizeof(float) * ((size_t)kHeadsPerCta * Dk + (size_t)kKeysPerTile * (Dk + 1) + (v_cache ? (size_t)kKeysPerTile * (Dv + 1) : 0));
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
@@ -230,7 +235,7 @@ extern "C" int ne_attn_generic(const void* q, long long q_tok_stride, int q_head
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  dim3 grid(T, (H + kHeadsPerCta - 1) / kHeadsPerCta);
+  dim3 grid(T, (H + a.heads_per_cta - 1) / a.heads_per_cta);
   return (int)launch_pdl(attn_generic_kernel, dim3(grid), dim3(128), smem, st, a);
 }
 

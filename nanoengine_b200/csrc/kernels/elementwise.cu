@@ -424,6 +424,24 @@ __global__ void __launch_bounds__(256) gqa_kv_store_kernel(const __nv_bfloat16* 
   }
 }
 
+// GELU over a flat bf16 array, 8 elements per thread: tanh approximation or the exact erf form
+__global__ void __launch_bounds__(256) gelu_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n, int tanh_form) {
+  pdl_wait(); pdl_trigger();
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  auto act = [&](float v) {
+    return tanh_form ? 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))) : 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
+  };
+  if (i + 8 <= n) {
+    const uint4 u = *reinterpret_cast<const uint4*>(x + i);
+    float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    *reinterpret_cast<uint4*>(y + i) = make_uint4(pack_bf16x2(act(a.x), act(a.y)), pack_bf16x2(act(b.x), act(b.y)), pack_bf16x2(act(c.x), act(c.y)),
+                                                  pack_bf16x2(act(d.x), act(d.y)));
+  } else {
+    for (long long j = i; j < n; j++) y[j] = __float2bfloat16(act(__bfloat162float(x[j])));
+  }
+}
+
 // LayerNorm over the last dimension, one warp per row: y = (x - mean) / sqrt(var + eps) * w + b.
 __global__ void __launch_bounds__(256) layernorm_kernel(const __nv_bfloat16* __restrict__ x, long long ld, const __nv_bfloat16* __restrict__ w,
                                                        const __nv_bfloat16* __restrict__ b, float eps, __nv_bfloat16* __restrict__ y, long long rows, int D) {
@@ -565,6 +583,11 @@ extern "C" int ne_gqa_kv_store(const void* k, const void* v, long long k_ld, lon
   if (row_elems % 8 || k_ld % 8 || v_ld % 8) return 1001;
   return (int)launch_pdl(gqa_kv_store_kernel, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, k_ld, v_ld,
                          (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slots, T, row_elems);
+}
+
+extern "C" int ne_gelu(const void* x, void* y, long long n, int tanh_form, cudaStream_t st) {
+  if (n <= 0) return 0;
+  return (int)launch_pdl(gelu_kernel, dim3((unsigned)((n + 2047) / 2048)), dim3(256), 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, tanh_form);
 }
 
 extern "C" int ne_layernorm(const void* x, long long ld, const void* w, const void* b, float eps, void* y, long long rows, int D, cudaStream_t st) {

@@ -120,6 +120,19 @@ class LLMEngine:
             self._l3_import(prompt_token_ids)
         return self.scheduler.add_request(C.RequestIn(seq_id, list(prompt_token_ids), sp, affinity_key))
 
+    def add_vision_request(self, prompt_token_ids: List[int], image_token_id: int, embeddings=None, vision_slot=None, pool_desc=None,
+                           sampling_params=None, seq_id: Optional[int] = None) -> int:
+        """A request whose `image_token_id` prompt tokens stand for image embeddings: given directly ([n, hidden]) or as a slot of
+        a vision encoder's pool (`vl.EncoderEngine.encode` + `engine_info()["pool"]`).  The workers splice the rows in during
+        prefill.  Parity: reference engine/llm_component.py:285-340 + runtime/runner/model_runner.py:1557-1573, :1886-1890."""
+        if seq_id is None:
+            seq_id = self._next_seq_id
+        slot, ntok = (int(vision_slot.slot), int(vision_slot.num_tokens)) if vision_slot is not None else (-1, 0)
+        self.executor.collective_rpc("register_vision", seq_id, list(prompt_token_ids), int(image_token_id), embeddings, pool_desc, slot, ntok)
+        self._next_seq_id = max(self._next_seq_id, seq_id) + 1
+        sp = sampling_params or C.SamplingParams()
+        return self.scheduler.add_request(C.RequestIn(seq_id, list(prompt_token_ids), sp, 0, [slot] if slot >= 0 else None))
+
     # ---- file-backed KV tier ------------------------------------------------------------------
     def _l3_import(self, prompt_token_ids: List[int]) -> int:
         """Bring the prompt's leading blocks that only the file tier still holds back into the device prefix cache."""

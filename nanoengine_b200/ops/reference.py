@@ -292,6 +292,27 @@ def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context
     return out.to(q.dtype)
 
 
+def attention_varlen(q, k, v, cu_seqlens, scale, causal: bool = False) -> torch.Tensor:
+    """Attention over ragged sequences: q, k, v [T, H, D]; sequence i owns rows [cu[i], cu[i+1]).  Non-causal by default (the
+    vision encoder, reference vl/vision/encoder.py:154-198)."""
+    out = torch.empty_like(q)
+    cu = cu_seqlens.tolist()
+    for i in range(len(cu) - 1):
+        lo, hi = cu[i], cu[i + 1]
+        if hi == lo:
+            continue
+        s = torch.einsum("thd,nhd->htn", q[lo:hi].float(), k[lo:hi].float()) * scale
+        if causal:
+            n = hi - lo
+            s = s.masked_fill(torch.ones(n, n, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+        out[lo:hi] = torch.einsum("htn,nhd->thd", torch.softmax(s, -1), v[lo:hi].float()).to(q.dtype)
+    return out
+
+
+def gelu(x: torch.Tensor, tanh: bool = True) -> torch.Tensor:
+    return F.gelu(x.float(), approximate="tanh" if tanh else "none").to(x.dtype)
+
+
 def merge_attention_states(o1, lse1, o2, lse2):
     """Combine two partial attention results over disjoint key sets (LSE-weighted)."""
     m = torch.maximum(lse1, lse2)

@@ -487,6 +487,20 @@ def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scal
     return sm100_attn.mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scale, kv_lora_rank, sparse_indices)
 
 
+def attention_varlen(q, k, v, cu_seqlens, scale, causal: bool = False):
+    from . import sm100_attn
+    return sm100_attn.attention_varlen(q, k, v, cu_seqlens, scale, causal)
+
+
+def gelu(x: torch.Tensor, tanh: bool = True) -> torch.Tensor:
+    """GELU (tanh approximation or exact) over a contiguous bf16 tensor."""
+    x = x.contiguous()
+    assert x.dtype == torch.bfloat16
+    y = torch.empty_like(x)
+    _ck(lib().ne_gelu(_p(x), _p(y), _c.c_longlong(x.numel()), _c.c_int(1 if tanh else 0), _st()), "ne_gelu")
+    return y
+
+
 def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale, window: int = 0):
     from . import sm100_attn
     return sm100_attn.gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context_lens, scale, window)

@@ -125,7 +125,7 @@ def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scal
                                _c.c_longlong(cache.shape[-1]), _c.c_int(0), _c.c_int(0), _k._p(bt), _c.c_int(bt.stride(0)), _c.c_int(cache.shape[1]),
                                _k._p(cu), _k._p(cl), _c.c_int(B), _k._p(sp), _c.c_int(0 if sp is None else sp.shape[1]), _k._p(out),
                                _c.c_longlong(H * R), _c.c_int(R), _k._p(None), _c.c_int(T), _c.c_int(H), _c.c_int(Dk), _c.c_int(R),
-                               _c.c_float(scale), _c.c_int(1 if fp8 else 0), _c.c_int(0), _k._st()), "ne_attn_generic")
+                               _c.c_float(scale), _c.c_int(1 if fp8 else 0), _c.c_int(0), _c.c_int(0), _k._st()), "ne_attn_generic")
     return out
 
 
@@ -166,8 +166,31 @@ def gqa_attention_paged(q, k_cache, v_cache, block_tables, cu_seqlens_q, context
     _k._ck(lib.ne_attn_generic(_k._p(q), _c.c_longlong(q.stride(0)), _c.c_int(q.stride(1)), _k._p(k_cache), _k._p(v_cache),
                                _c.c_longlong(Hkv * D), _c.c_int(D), _c.c_int(group), _k._p(bt), _c.c_int(bt.stride(0)), _c.c_int(k_cache.shape[1]),
                                _k._p(cu), _k._p(cl), _c.c_int(cl.numel()), _k._p(None), _c.c_int(0), _k._p(out), _c.c_longlong(Hq * D), _c.c_int(D),
-                               _k._p(None), _c.c_int(T), _c.c_int(Hq), _c.c_int(D), _c.c_int(D), _c.c_float(scale), _c.c_int(0), _c.c_int(max(0, int(window))), _k._st()),
+                               _k._p(None), _c.c_int(T), _c.c_int(Hq), _c.c_int(D), _c.c_int(D), _c.c_float(scale), _c.c_int(0), _c.c_int(max(0, int(window))), _c.c_int(0), _k._st()),
            "ne_attn_generic")
+    return out
+
+
+def attention_varlen(q, k, v, cu_seqlens, scale, causal: bool = False):
+    """Attention over ragged sequences without a paged cache: q, k, v [T, H, D] of the same tokens, sequence i owns rows
+    [cu[i], cu[i+1]).  Runs on the generic kernel, which addresses k / v as a one-row-per-page cache through a table of row
+    numbers (no copy); any head dim up to 640.  Used by the vision encoder (non-causal)."""
+    T, H, D = q.shape
+    q = q if (q.dtype == torch.bfloat16 and q.stride(-1) == 1) else q.to(torch.bfloat16).contiguous()
+    k, v = k.to(torch.bfloat16).contiguous(), v.to(torch.bfloat16).contiguous()
+    out = torch.empty(T, H, D, dtype=torch.bfloat16, device=q.device)
+    if T == 0:
+        return out
+    cu = _i32(cu_seqlens)
+    lens = (cu[1:] - cu[:-1])
+    B = lens.numel()
+    max_len = int(lens.max())
+    bt = (cu[:-1, None] + torch.arange(max_len, device=q.device, dtype=torch.int32)[None, :]).clamp_(max=T - 1).contiguous()
+    _k._ck(_k.lib().ne_attn_generic(_k._p(q), _c.c_longlong(q.stride(0)), _c.c_int(q.stride(1)), _k._p(k), _k._p(v), _c.c_longlong(H * D),
+                                    _c.c_int(D), _c.c_int(1), _k._p(bt), _c.c_int(bt.stride(0)), _c.c_int(1), _k._p(cu), _k._p(lens.contiguous()),
+                                    _c.c_int(B), _k._p(None), _c.c_int(0), _k._p(out), _c.c_longlong(H * D), _c.c_int(D), _k._p(None), _c.c_int(T),
+                                    _c.c_int(H), _c.c_int(D), _c.c_int(D), _c.c_float(scale), _c.c_int(0), _c.c_int(0),
+                                    _c.c_int(0 if causal else 1), _k._st()), "ne_attn_generic")
     return out
 
 

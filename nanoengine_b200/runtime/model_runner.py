@@ -353,9 +353,62 @@ class ModelRunner:
         return ctx
 
     # ---- execution -----------------------------------------------------------------------------
+    # ---- vision embeddings -----------------------------------------------------------------------
+    def register_vision(self, seq_id: int, prompt_token_ids, image_token_id: int, embeddings=None, pool_desc=None, slot: int = -1,
+                        num_tokens: int = 0) -> int:
+        """Attach the image embeddings of a request: the rows replace, in order, the embeddings of its `image_token_id`
+        prompt tokens during prefill (also when the prompt is prefetched in chunks).  `embeddings` [n, hidden] directly, or
+        a pool descriptor of a vision encoder (`vl.EmbeddingPool.export`) plus the slot to read.
+        Parity: reference runtime/runner/vision_embed.py:33-82 (masked scatter of image rows), :84-140 (one-sided fetch)."""
+        if embeddings is None:
+            from ..vl.embedding_pool import EmbeddingReader
+            key = id(pool_desc.get("tensor")) if isinstance(pool_desc.get("tensor"), torch.Tensor) else str(sorted(pool_desc.items(), key=str))[:256]
+            readers = self.__dict__.setdefault("_vision_readers", {})
+            if key not in readers:
+                readers[key] = EmbeddingReader(pool_desc, self.device)
+            embeddings = readers[key].fetch(slot, num_tokens, self.dtype)
+        ids = np.asarray(prompt_token_ids, dtype=np.int64)
+        is_img = ids == image_token_id
+        if int(is_img.sum()) != embeddings.shape[0]:
+            raise ValueError(f"request {seq_id}: {int(is_img.sum())} image tokens in the prompt but {embeddings.shape[0]} embedding rows")
+        if embeddings.shape[1] != self.mc.hidden_size:
+            raise ValueError("embedding width differs from the model's hidden size")
+        self.__dict__.setdefault("_vision", {})[int(seq_id)] = (np.concatenate([[0], np.cumsum(is_img)]), is_img,
+                                                                  embeddings.to(self.device, self.dtype))
+        return embeddings.shape[0]
+
+    def release_vision(self, seq_id: int) -> None:
+        self.__dict__.get("_vision", {}).pop(int(seq_id), None)
+
+    def _vision_inputs_embeds(self, b, ctx: ForwardContext):
+        """inputs_embeds of a prefill step when one of its sequences carries image embeddings, else None."""
+        reg = self.__dict__.get("_vision")
+        if not reg or not ctx.is_prefill or not any(int(s) in reg for s in b.seq_ids):
+            return None
+        embed = getattr(self.model, "embed_tokens", None) or self.model.model.embed_tokens
+        ids = ctx.extras["input_ids"]
+        x = embed(ids).clone()
+        row = 0
+        for sid, q, n in zip(b.seq_ids, b.q_lens, b.seq_lens):
+            ent = reg.get(int(sid))
+            if ent is not None:
+                prefix, is_img, emb = ent
+                lo, hi = n - q, min(n, len(is_img))                     # prompt positions covered by this chunk
+                if hi > lo:
+                    sel = np.nonzero(is_img[lo:hi])[0]
+                    if sel.size:
+                        rows = torch.from_numpy(sel + row).to(x.device)
+                        x.index_copy_(0, rows, emb[int(prefix[lo]): int(prefix[lo]) + sel.size])
+                if n >= len(is_img):
+                    reg.pop(int(sid))                                   # the whole prompt is in: the rows are no longer needed
+            row += q
+        return x
+
     @torch.inference_mode()
     def forward(self, ctx: ForwardContext) -> torch.Tensor:
         ids, pos = ctx.extras["input_ids"], ctx.extras["positions"]
+        if ctx.extras.get("inputs_embeds") is not None:
+            return self.model(ids, pos, ctx, inputs_embeds=ctx.extras["inputs_embeds"])
         if self.graphs is not None and not ctx.is_prefill and ctx.q_len_uniform == 1 and self.graphs.can_run(ctx):
             return self.graphs.run(ids, pos, ctx)
         if self.config.pp > 1:
@@ -533,6 +586,8 @@ class ModelRunner:
         self.timer.start("prepare")
         with nvtx.range("step/prepare"):
             ctx = self.prepare(b)
+            if not ctx.is_dummy:
+                ctx.extras["inputs_embeds"] = self._vision_inputs_embeds(b, ctx)
         self.timer.stop()
         if self.mtp_runner is not None and not ctx.is_dummy:
             return self.mtp_runner.run(b, ctx)

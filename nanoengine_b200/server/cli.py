@@ -94,7 +94,24 @@ def main(argv=None) -> int:
         from ..build_native import build_gateway
         build_gateway()
         return subprocess.call([gateway_binary(), *rest])
-    raise SystemExit(f"unknown command {cmd}; expected serve | monitor | router")
+    if cmd == "serve-encoder":
+        ap = argparse.ArgumentParser(prog="serve-encoder", description="vision encoder engine: ZMQ service and HTTP front")
+        ap.add_argument("--model", default="", help="checkpoint directory with vision_config and visual.* tensors ('' = random weights)")
+        ap.add_argument("--device", default="cuda")
+        ap.add_argument("--dtype", default="bfloat16")
+        ap.add_argument("--num-slots", type=int, default=64)
+        ap.add_argument("--max-tokens-per-slot", type=int, default=4096)
+        ap.add_argument("--endpoint", default="", help="ZMQ endpoint for the language-model engines, e.g. ipc:///tmp/encoder.sock")
+        ap.add_argument("--engine-id", default="encoder-0")
+        ap.add_argument("--host", default="0.0.0.0")
+        ap.add_argument("--port", type=int, default=8100)
+        a = ap.parse_args(rest)
+        from ..vl import EncoderConfig
+        from .vl_server import serve
+        serve(EncoderConfig(model=a.model, device=a.device, dtype=a.dtype, num_slots=a.num_slots, max_tokens_per_slot=a.max_tokens_per_slot,
+                            endpoint=a.endpoint, engine_id=a.engine_id), a.host, a.port)
+        return 0
+    raise SystemExit(f"unknown command {cmd}; expected serve | serve-encoder | monitor | router")
 
 
 if __name__ == "__main__":
