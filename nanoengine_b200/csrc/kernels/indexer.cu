@@ -253,14 +253,32 @@ __device__ __forceinline__ uint32_t float_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);          // larger float <=> larger key
 }
 
-// One CTA per token.  out [T, k] int32: physical slot ids of the k best visible keys (keys above the k-th value in position order, then the
-// ties that fill the list, also in position order), -1 padded.
+__device__ __forceinline__ int ld_dsmem_i32(uint32_t addr) {
+  int v;
+  asm volatile("ld.shared::cluster.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// A thread-block cluster of S CTAs (S = 1, 2, 4 or 8) per token; CTA r of the cluster owns positions [r * span, (r + 1) * span) of the
+// token's row.  out [T, k] int32: physical slot ids of the k best visible keys (keys above the k-th value in position order, then
+// the ties that fill the list, also in position order), -1 padded.
+//
+// Three radix passes over the order-preserving key of the logit (11 + 11 + 10 bits).  Per pass every CTA histograms its span in
+// shared memory, the cluster meets, every CTA adds up the S histograms through distributed shared memory and finds the digit
+// of the k-th largest key with a block-wide prefix sum (thread i owns bins 2i and 2i + 1; exactly one bin b has
+// count(bins > b) < remaining <= count(bins >= b)).  A serial walk down the 2048 bins by one thread took about as long as the
+// histogram itself.  The list is then written by ordered compaction: spans in rank order (their counts are exchanged through
+// distributed shared memory), 1024 positions at a time inside a span.
 __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restrict__ logits, long long ld, const int* __restrict__ cu_seqlens_q,
                                                            const int* __restrict__ context_lens, int num_seqs, const int* __restrict__ block_tables,
                                                            int bt_stride, int bs, int k, int* __restrict__ out) {
   __shared__ int hist[2048];
+  __shared__ int s_warp[32];
+  __shared__ int s_cnt[2];                                   // keys of this span above / equal to the threshold
   __shared__ uint32_t s_prefix; __shared__ int s_remaining;
-  const int t = blockIdx.x;
+  const int S = (int)cluster_nctarank(), rank = (int)cluster_ctarank();
+  const int t = blockIdx.x / S;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int lo = 0, hi = num_seqs;
   while (lo + 1 < hi) { int mid = (lo + hi) >> 1; if (cu_seqlens_q[mid] <= t) lo = mid; else hi = mid; }
   const int seq = lo;
@@ -270,49 +288,85 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
   const int* bt = block_tables ? block_tables + (long long)seq * bt_stride : nullptr;
   int* o = out + (long long)t * k;
   auto phys = [&](int idx) { return bt ? bt[idx / bs] * bs + idx % bs : idx; };
-  if (n <= k) {
-    for (int i = threadIdx.x; i < k; i += blockDim.x) o[i] = i < n ? phys(i) : -1;
+  if (n <= k) {                                               // uniform over the cluster: nobody waits at a cluster barrier below
+    for (int i = rank * 1024 + tid; i < k; i += S * 1024) o[i] = i < n ? phys(i) : -1;
     return;
   }
-  if (threadIdx.x == 0) { s_prefix = 0; s_remaining = k; }
-  // three digit passes: bits [31:21], [20:10], [9:0]
+  const int span = ((n + S - 1) / S + 3) & ~3;
+  const int begin = min(n, rank * span), end = min(n, begin + span);
+  const uint32_t hist_addr = smem_u32(hist);
+  if (tid == 0) { s_prefix = 0; s_remaining = k; }
   const int shifts[3] = {21, 10, 0}, widths[3] = {11, 11, 10};
   uint32_t known_mask = 0;
   for (int p = 0; p < 3; p++) {
-    for (int i = threadIdx.x; i < 2048; i += blockDim.x) hist[i] = 0;
+    for (int i = tid; i < 2048; i += 1024) hist[i] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix;
+    const int rem = s_remaining;
     const int sh = shifts[p];
     const uint32_t dm = (1u << widths[p]) - 1;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    for (int i = begin + tid; i < end; i += 1024) {
       const uint32_t key = float_key(row[i]);
       if ((key & known_mask) == prefix) atomicAdd(&hist[(key >> sh) & dm], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int rem = s_remaining, b = (int)dm;
-      for (; b > 0; b--) { if (hist[b] >= rem) break; rem -= hist[b]; }
-      s_prefix = prefix | ((uint32_t)b << sh);
-      s_remaining = rem;                                    // how many to take from the chosen digit's bucket
+    cluster_sync_all();                                       // every span's histogram is complete
+    int c0 = 0, c1 = 0;
+    for (int r = 0; r < S; r++) {
+      const uint32_t a = mapa_shared(hist_addr + 8u * tid, (uint32_t)r);
+      c0 += ld_dsmem_i32(a); c1 += ld_dsmem_i32(a + 4);
     }
+    // inclusive prefix sum of the pair sums over the 1024 threads
+    int incl = c0 + c1;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, d); if (lane >= d) incl += v; }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_up_sync(0xffffffffu, w, d); if (lane >= d) w += v; }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    const int total = s_warp[31];
+    incl += warp > 0 ? s_warp[warp - 1] : 0;
+    const int gt1 = total - incl, gt0 = gt1 + c1;             // keys in bins above 2i + 1 / above 2i
+    if (gt1 < rem && rem <= gt1 + c1) { s_prefix = prefix | ((uint32_t)(2 * tid + 1) << sh); s_remaining = rem - gt1; }
+    else if (gt0 < rem && rem <= gt0 + c0) { s_prefix = prefix | ((uint32_t)(2 * tid) << sh); s_remaining = rem - gt0; }
     known_mask |= dm << sh;
     __syncthreads();
+    cluster_sync_all();                                       // everybody has read the histograms: they may be cleared
   }
-  const uint32_t thr = s_prefix;                            // the k-th largest key; s_remaining of its copies are taken
+  const uint32_t thr = s_prefix;                              // the k-th largest key; s_remaining of its copies are taken
   const int need_eq = s_remaining;
   const int n_gt = k - need_eq;
-  // Ordered compaction, 1024 keys at a time: keys above the threshold go to o[0, n_gt) and the first `need_eq` keys equal to
-  // it to o[n_gt, k), each group in ascending key position.  The list is the same in every run (slots handed out by atomics
-  // would list the keys in arrival order, and the attention that follows would sum its products in a different order).
+  // keys above / equal to the threshold in this span, then the offsets of the span in the two output groups
+  int my_gt = 0, my_eq = 0;
+  for (int i = begin + tid; i < end; i += 1024) {
+    const uint32_t key = float_key(row[i]);
+    my_gt += key > thr; my_eq += key == thr;
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) { my_gt += __shfl_xor_sync(0xffffffffu, my_gt, d); my_eq += __shfl_xor_sync(0xffffffffu, my_eq, d); }
+  if (tid < 2) s_cnt[tid] = 0;
+  __syncthreads();
+  if (lane == 0) { atomicAdd(&s_cnt[0], my_gt); atomicAdd(&s_cnt[1], my_eq); }
+  __syncthreads();
+  cluster_sync_all();
+  int base_gt = 0, base_eq = 0;
+  const uint32_t cnt_addr = smem_u32(s_cnt);
+  for (int r = 0; r < rank; r++) {
+    const uint32_t a = mapa_shared(cnt_addr, (uint32_t)r);
+    base_gt += ld_dsmem_i32(a); base_eq += ld_dsmem_i32(a + 4);
+  }
   int* s_wgt = hist;
   int* s_weq = hist + 32;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned lt = (1u << lane) - 1u;
-  int base_gt = 0, base_eq = 0;
-  for (int i0 = 0; i0 < n && (base_gt < n_gt || base_eq < need_eq); i0 += 1024) {
-    const int i = i0 + (int)threadIdx.x;
-    const uint32_t key = i < n ? float_key(row[i]) : 0u;
-    const bool gt = i < n && key > thr, eq = i < n && key == thr;
+  for (int i0 = begin; i0 < end && (base_gt < n_gt || base_eq < need_eq); i0 += 1024) {
+    const int i = i0 + tid;
+    const uint32_t key = i < end ? float_key(row[i]) : 0u;
+    const bool gt = i < end && key > thr, eq = i < end && key == thr;
     const unsigned bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
     if (lane == 0) { s_wgt[warp] = __popc(bg); s_weq[warp] = __popc(be); }
     __syncthreads();
@@ -335,6 +389,7 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
     base_gt += tot_g; base_eq += tot_e;
     __syncthreads();
   }
+  cluster_sync_all();                                         // no CTA leaves while a peer may still read its counters
 }
 
 }  // namespace ne
@@ -389,6 +444,17 @@ extern "C" int ne_indexer_topk(const float* logits, long long ld, const int* cu_
                                const int* block_tables, int bt_stride, int bs, int k, int T, int* out, cudaStream_t st) {
   if (T <= 0) return 0;
   if (k < 1 || bs < 1) return 1001;
-  indexer_topk_kernel<<<T, 1024, 0, st>>>(logits, ld, cu_seqlens_q, context_lens, num_seqs, block_tables, bt_stride, bs, k, out);
-  return (int)cudaGetLastError();
+  // few tokens over long rows: several CTAs share a row (a cluster per token), as many as keeps every CTA at >= 8192 positions and
+  // the grid within one wave
+  int S = 1;
+  while (S < 8 && T * S * 2 <= 148 && ld / (S * 2) >= 8192) S *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(T * S), 1, 1);
+  cfg.blockDim = dim3(1024, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)S; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, indexer_topk_kernel, logits, ld, cu_seqlens_q, context_lens, num_seqs, block_tables, bt_stride, bs, k, out);
 }

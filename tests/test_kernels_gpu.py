@@ -406,6 +406,35 @@ def test_indexer_select_matches_reference_topk_sets(k, ctxs, q_lens):
         assert len(a & b) >= len(b) - 4, (t, len(a & b), len(b))
 
 
+@pytest.mark.parametrize("T,n,topk", [(3, 70000, 2048), (8, 65600, 2048), (40, 20000, 512), (130, 5000, 2048), (2, 3000, 4096)])
+def test_topk_kernel_exact_sets_order_and_ties(k, T, n, topk):
+    """The radix top-k on its own, on rows long enough that several CTAs (a cluster) share a token: the selected set equals
+    torch.topk's wherever the k-th value is unique, ties at the k-th value are taken in position order, and the list is
+    written as [keys above the threshold in position order | ties in position order]."""
+    import ctypes as c
+    torch.manual_seed(5)
+    ld = (n + 127) // 128 * 128
+    logits = torch.randn(T, ld, device="cuda")
+    logits[:, ::7] = logits[:, ::7].round()                      # many exact ties
+    logits[0, :n] = 0.25                                         # a row that is one big tie
+    cu = torch.arange(T + 1, dtype=torch.int32, device="cuda")
+    cl = torch.full((T,), n, dtype=torch.int32, device="cuda")
+    out = torch.full((T, topk), -7, dtype=torch.int32, device="cuda")
+    k._ck(k.lib().ne_indexer_topk(k._p(logits), c.c_longlong(ld), k._p(cu), k._p(cl), c.c_int(T), k._p(None), c.c_int(0), c.c_int(64), c.c_int(topk),
+                                  c.c_int(T), k._p(out), k._st()), "ne_indexer_topk")
+    torch.cuda.synchronize()
+    for t in range(T):
+        row = logits[t, :n]
+        kk = min(topk, n)
+        thr = torch.topk(row, kk).values[-1]
+        above = (row > thr).nonzero().flatten()
+        ties = (row == thr).nonzero().flatten()[: kk - above.numel()]
+        want = torch.cat([above, ties]).int()
+        got = out[t, :kk]
+        assert torch.equal(got, want), (t, (got != want).sum().item())
+        assert (out[t, kk:] == -1).all()
+
+
 @pytest.mark.parametrize("hd,hq,hkv,norm", [(128, 8, 2, True), (128, 16, 1, False), (256, 4, 4, True), (64, 4, 2, True)])
 def test_gqa_front_end_norm_rope_and_paged_store(k, hd, hq, hkv, norm):
     """Head split + q/k RMSNorm + rotary + K/V store: one kernel for head dims 128/256, the separate kernels otherwise."""
