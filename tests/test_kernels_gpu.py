@@ -429,7 +429,7 @@ def test_topk_kernel_exact_sets_order_and_ties(k, T, n, topk):
         thr = torch.topk(row, kk).values[-1]
         above = (row > thr).nonzero().flatten()
         ties = (row == thr).nonzero().flatten()[: kk - above.numel()]
-        want = torch.cat([above, ties]).int()
+        want = torch.cat([above, ties]).int() if n > topk else torch.arange(n, dtype=torch.int32, device="cuda")   # everything visible: position order
         got = out[t, :kk]
         assert torch.equal(got, want), (t, (got != want).sum().item())
         assert (out[t, kk:] == -1).all()
