@@ -118,29 +118,55 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
   }
   const float neg_A = -__expf(A_log[h]), dtb = kVecGate ? 0.f : dt_bias[h];
   const float qscale = rsqrtf((float)Dk);
-  for (int i = 0; i < n; i++) {
-    const long long t = start + i;
-    float kf[E], qf[E], kk = 0.f, qq = 0.f, kq = 0.f;
+  // Inputs of token i + 1 are fetched while token i is computed: a sequence's tokens are strictly serial, so an exposed global
+  // load per step (about a microsecond) would otherwise be most of a step of a long prompt chunk.
+  float dtv[kVecGate ? E : 1];
+  if (kVecGate) {
+#pragma unroll
+    for (int e = 0; e < E; e++) dtv[e] = dt_bias[h * Dk + e * 32 + lane];
+  }
+  __nv_bfloat16 rk[E], rq[E], ra[kVecGate ? E : 1], rv[R], rb;
+  auto fetch = [&](long long t) {
 #pragma unroll
     for (int e = 0; e < E; e++) {
-      kf[e] = __bfloat162float(k[t * qk_ld + hk * Dk + e * 32 + lane]);
-      qf[e] = __bfloat162float(q[t * qk_ld + hk * Dk + e * 32 + lane]);
+      rk[e] = k[t * qk_ld + hk * Dk + e * 32 + lane];
+      rq[e] = q[t * qk_ld + hk * Dk + e * 32 + lane];
+      if (kVecGate) ra[e] = a[t * (long long)Hv * Dk + h * Dk + e * 32 + lane];
+    }
+    if (!kVecGate) ra[0] = a[t * ab_ld + h];
+    rb = b[t * ab_ld + h];
+#pragma unroll
+    for (int r = 0; r < R; r++) rv[r] = v[t * v_ld + h * Dv + row0 + r];
+  };
+  fetch(start);
+  for (int i = 0; i < n; i++) {
+    const long long t = start + i;
+    float kf[E], qf[E], af[kVecGate ? E : 1], vf[R], kk = 0.f, qq = 0.f, kq = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; e++) {
+      kf[e] = __bfloat162float(rk[e]);
+      qf[e] = __bfloat162float(rq[e]);
+      if (kVecGate) af[e] = __bfloat162float(ra[e]);
       kk += kf[e] * kf[e]; qq += qf[e] * qf[e];
     }
+    if (!kVecGate) af[0] = __bfloat162float(ra[0]);
+    const float bf = __bfloat162float(rb);
+#pragma unroll
+    for (int r = 0; r < R; r++) vf[r] = __bfloat162float(rv[r]);
+    if (i + 1 < n) fetch(t + 1);
     kk = warp_sum(kk); qq = warp_sum(qq);
     const float kn = rsqrtf(kk + 1e-6f), qn = rsqrtf(qq + 1e-6f) * qscale;
 #pragma unroll
     for (int e = 0; e < E; e++) { kf[e] *= kn; qf[e] *= qn; kq += kf[e] * qf[e]; }
     kq = warp_sum(kq);
-    const float beta = 1.f / (1.f + __expf(-__bfloat162float(b[t * ab_ld + h])));
+    const float beta = 1.f / (1.f + __expf(-bf));
     float o[R];
     if (kVecGate) {
       // `a` rows are Hv * Dk wide here and `b` rows Hv wide; ab_ld is the row stride of `b`, a's is Hv * Dk
       float dec[E], kd[E], qd[E];
 #pragma unroll
       for (int e = 0; e < E; e++) {
-        const int c = h * Dk + e * 32 + lane;
-        const float x = __bfloat162float(a[t * (long long)Hv * Dk + c]) + dt_bias[c];
+        const float x = af[e] + dtv[e];
         const float gl = lower_bound < 0.f ? lower_bound / (1.f + __expf(neg_A * x))          // L * sigmoid(exp(A) x)
                                            : neg_A * (x > 20.f ? x : log1pf(__expf(x)));
         dec[e] = __expf(gl); kd[e] = dec[e] * kf[e]; qd[e] = dec[e] * qf[e];
@@ -151,14 +177,13 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
 #pragma unroll
         for (int e = 0; e < E; e++) { pk += S[r][e] * kd[e]; pq += S[r][e] * qd[e]; }
         pk = warp_sum(pk); pq = warp_sum(pq);
-        const float vr = __bfloat162float(v[t * v_ld + h * Dv + row0 + r]);
-        const float u = beta * (vr - pk);
+        const float u = beta * (vf[r] - pk);
 #pragma unroll
         for (int e = 0; e < E; e++) S[r][e] = dec[e] * S[r][e] + u * kf[e];
         o[r] = pq + u * kq;
       }
     } else {
-      const float av = __bfloat162float(a[t * ab_ld + h]) + dtb;
+      const float av = af[0] + dtb;
       const float sp = av > 20.f ? av : log1pf(__expf(av));
       const float decay = __expf(neg_A * sp);
 #pragma unroll
@@ -167,8 +192,7 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
 #pragma unroll
         for (int e = 0; e < E; e++) { pk += S[r][e] * kf[e]; pq += S[r][e] * qf[e]; }
         pk = warp_sum(pk); pq = warp_sum(pq);
-        const float vr = __bfloat162float(v[t * v_ld + h * Dv + row0 + r]);
-        const float u = beta * (vr - decay * pk);
+        const float u = beta * (vf[r] - decay * pk);
 #pragma unroll
         for (int e = 0; e < E; e++) S[r][e] = decay * S[r][e] + u * kf[e];
         o[r] = decay * pq + u * kq;
