@@ -87,8 +87,12 @@ def build_core(force=False) -> Path:
     return target
 
 
-def build_kernels(force=False) -> Path:
-    target = OUT / "libne_kernels.so"
+def build_kernels(force=False, debug_bounds=False) -> Path:
+    """`debug_bounds`: the same sources with -DNE_DEBUG_BOUNDS into libne_kernels_dbg.so (kernels compare the cache rows, pages,
+    state slots and expert ids they take from tables with the bounds the worker registers; loaded when NE_DEBUG_BOUNDS=1)."""
+    target = OUT / ("libne_kernels_dbg.so" if debug_bounds else "libne_kernels.so")
+    OBJ = OUT / ("obj_dbg" if debug_bounds else "obj")
+    NVCC_FLAGS = globals()["NVCC_FLAGS"] + (["-DNE_DEBUG_BOUNDS"] if debug_bounds else [])
     kdir = CSRC / "kernels"
     cus = sorted(kdir.glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu"))
     hdrs = sorted(kdir.glob("*.cuh")) + sorted(kdir.glob("*.h")) + sorted((CSRC / "comm").glob("*.cuh")) + sorted((CSRC / "comm").glob("*.h"))
@@ -176,5 +180,7 @@ def build_all(force=False):
 
 if __name__ == "__main__":
     res = build_all(force="--force" in sys.argv)
+    if "--debug-bounds" in sys.argv:
+        res["kernels (bounds-checked)"] = build_kernels("--force" in sys.argv, debug_bounds=True)
     for k, v in res.items():
         print(f"{k}: {v} ({'ok' if Path(v).exists() else 'absent'})")

@@ -84,7 +84,10 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(const AttnArgs a) {
       long long slot = -1;
       if (kidx < n_keys) {
         if (a.sparse) slot = a.sparse[(long long)t * a.topk + kidx];
-        else slot = (long long)bt[kidx / a.block_size] * a.block_size + kidx % a.block_size;
+        else {
+          const int page = bt[kidx / a.block_size];
+          slot = (a.block_size == 1 || NE_INDEX_OK(page, BK_CACHE_PAGES, 23, __LINE__)) ? (long long)page * a.block_size + kidx % a.block_size : -1;
+        }
       }
       for (int d = lane; d < Dk; d += 32)
         sk[r * (Dk + 1) + d] = slot >= 0 ? load_kv(a.k_cache, slot * a.kv_slot_stride + (long long)kvh * a.kv_head_stride + d, a.fp8) : 0.f;

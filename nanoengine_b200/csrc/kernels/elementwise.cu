@@ -254,6 +254,7 @@ __global__ void __launch_bounds__(256) mla_kv_prepare_kernel(const __nv_bfloat16
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   const long long slot = slots[t];
+  if (slot >= 0 && !NE_INDEX_OK(slot, BK_CACHE_ROWS, 20, __LINE__)) return;
   const __nv_bfloat16* row = kv + (long long)t * kv_ld;
   float ss = 0.f;
   for (int c = lane * 2; c < R; c += 64) {
@@ -326,6 +327,7 @@ __global__ void mla_kv_store_kernel(const __nv_bfloat16* __restrict__ ckv, long 
   int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   long long slot = slots[t];
+  if (slot >= 0 && !NE_INDEX_OK(slot, BK_CACHE_ROWS, 20, __LINE__)) return;
   if (slot < 0) return;
   int D = R + rope;
   for (int c = lane * 2; c < D; c += 64) {
@@ -379,6 +381,7 @@ __global__ void __launch_bounds__(256) gqa_qkv_prepare_kernel(const __nv_bfloat1
   for (int j = 0; j < J; j++) v[j] = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(src + 2 * lane + 64 * j));
   const bool is_q = h < Hq, is_k = !is_q && h < Hq + Hkv;
   const long long slot = is_q ? 0 : slots[t];
+  if (slot >= 0 && !NE_INDEX_OK(slot, BK_CACHE_ROWS, 20, __LINE__)) return;
   if (!is_q && slot < 0) return;                  // padded token: nothing to store
   if (is_q || is_k) {
     const __nv_bfloat16* nw = is_q ? qw : kw;
@@ -417,6 +420,7 @@ __global__ void __launch_bounds__(256) gqa_kv_store_kernel(const __nv_bfloat16* 
   pdl_wait(); pdl_trigger();
   const int t = blockIdx.x;
   const long long slot = slots[t];
+  if (slot >= 0 && !NE_INDEX_OK(slot, BK_CACHE_ROWS, 20, __LINE__)) return;
   if (slot < 0) return;
   for (int c = threadIdx.x * 8; c < row_elems; c += blockDim.x * 8) {
     *reinterpret_cast<uint4*>(k_cache + slot * row_elems + c) = *reinterpret_cast<const uint4*>(k + (long long)t * k_ld + c);

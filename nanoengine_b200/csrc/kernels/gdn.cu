@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(256) gdn_conv_kernel(const __nv_bfloat16* __re
   const int start = cu[seq], p = t - start;
   const bool is_fresh = fresh[seq] != 0;
   const int slot = slots[seq];
+  if (!NE_INDEX_OK(slot, BK_STATE_SLOTS, 21, __LINE__)) return;
   __nv_bfloat16* win = window + (long long)slot * (K - 1) * C;
   for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2; c < C; c += gridDim.y * blockDim.x * 2) {
     float acc0 = 0.f, acc1 = 0.f;
@@ -61,6 +62,7 @@ __global__ void __launch_bounds__(256) gdn_conv_state_kernel(const __nv_bfloat16
   const int start = cu[seq], n = cu[seq + 1] - start;
   if (n <= 0) return;
   const bool is_fresh = fresh[seq] != 0;
+  if (!NE_INDEX_OK(slots[seq], BK_STATE_SLOTS, 21, __LINE__)) return;
   __nv_bfloat16* win = window + (long long)slots[seq] * (K - 1) * C;
   for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2; c < C; c += gridDim.y * blockDim.x * 2) {
     uint32_t nw[8];
@@ -103,6 +105,7 @@ __global__ void __launch_bounds__(32 * NW) gdn_step_kernel(const __nv_bfloat16* 
   const int row0 = (blockIdx.x % bph) * kRowsPerCta + warp * R;
   const int start = cu[seq], n = cu[seq + 1] - start;
   if (n <= 0 || n >= skip_len) return;
+  if (!NE_INDEX_OK(slots[seq], BK_STATE_SLOTS, 21, __LINE__)) return;
   float* S_g = state + (((long long)slots[seq] * Hv + h) * Dv + row0) * Dk;
   float S[R][E];
   if (fresh[seq]) {

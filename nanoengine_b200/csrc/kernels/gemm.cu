@@ -25,6 +25,9 @@
 namespace ne {
 
 __device__ int g_status[8];
+#ifdef NE_DEBUG_BOUNDS
+__device__ long long g_bounds[BK_COUNT];
+#endif
 
 constexpr int kBlockM = 128;
 constexpr int kKBytes = 128;            // bytes of K per K block row: one 128B swizzle atom
@@ -867,6 +870,19 @@ extern "C" int ne_gemm_comm_size() { return (int)sizeof(GemmComm); }
 
 // Turn the cluster split-K plan of small-M dense GEMMs on or off (on by default); returns the previous setting.
 extern "C" int ne_gemm_set_split_k(int on) { int was = g_split_k_enabled ? 1 : 0; g_split_k_enabled = on != 0; return was; }
+
+// Debug build only: register the bounds the checked kernels compare their table entries with (0 = leave unchecked).  Returns 1 when
+// this library was built with the checks, 0 otherwise (the call is then a no-op).
+extern "C" int ne_debug_set_bounds(long long cache_rows, long long cache_pages, long long state_slots, long long experts) {
+#ifdef NE_DEBUG_BOUNDS
+  long long b[BK_COUNT] = {cache_rows, cache_pages, state_slots, experts};
+  cudaMemcpyToSymbol(g_bounds, b, sizeof(b));
+  return 1;
+#else
+  (void)cache_rows; (void)cache_pages; (void)state_slots; (void)experts;
+  return 0;
+#endif
+}
 
 extern "C" int ne_get_status(int* out8) {
   return (int)cudaMemcpyFromSymbol(out8, g_status, sizeof(int) * 8);

@@ -123,7 +123,8 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
       for (int i = 0; i < n_tiles; i++) {
         const int s = i % kGStages;
         if (!mbar_wait(b_kvempty + 8 * s, ((i / kGStages) & 1) ^ 1, abort_flag, kKernelGqa, 100 + s)) break;
-        const int block = bt[pg_begin + i];
+        int block = bt[pg_begin + i];
+        if (!NE_INDEX_OK(block, BK_CACHE_PAGES, 7, __LINE__)) block = 0;      // a bad page id reads page 0 instead of another allocation
         uint8_t* dst = sKV + s * 2 * kGKBytes;
         mbar_expect_tx(b_kvfull + 8 * s, 2 * kGKBytes);
         tma_load_5d(smem_u32(dst), &tk_map, b_kvfull + 8 * s, 0, 0, hkv, block, 0);

@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(256) indexer_prep_kernel(const __nv_bfloat16* 
   const uint32_t packed = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
   if (cache) {
     const long long slot = slots[t];
+    if (slot >= 0 && !NE_INDEX_OK(slot, BK_CACHE_ROWS, 22, __LINE__)) return;
     if (slot < 0) return;
     uint8_t* page = cache + (slot / bs) * page_bytes;
     const int off = (int)(slot % bs);

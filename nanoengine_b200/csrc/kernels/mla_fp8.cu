@@ -189,7 +189,8 @@ mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant_
       for (int i = 0; i < n_tiles; i++) {
         const int s = i % kPgStages;
         if (!mbar_wait(b_pgempty + 8 * s, ((i / kPgStages) & 1) ^ 1, abort_flag, kKernelMla, 100 + s)) break;
-        const int block = bt[pg_begin + i];
+        int block = bt[pg_begin + i];
+        if (!NE_INDEX_OK(block, BK_CACHE_PAGES, kKernelMla, __LINE__)) block = 0;      // a bad page id reads page 0 instead of another allocation
         uint8_t* dst = sPg + s * kPgBytes;
         mbar_expect_tx(b_pgfull + 8 * s, kPgBytes);
         for (int p = 0; p < 4; p++) tma_load_3d(smem_u32(dst + p * kPage * 128), &tk128, b_pgfull + 8 * s, p * 128, 0, block);

@@ -16,7 +16,7 @@ namespace ne {
 
 // ---- status buffer -----------------------------------------------------------------------------
 // word 0: first error code (0 = ok); 1: kernel id; 2: block; 3: detail a; 4: detail b.
-enum StatusCode : int { ST_OK = 0, ST_MBAR_TIMEOUT = 1, ST_FLAG_TIMEOUT = 2, ST_BAD_ARG = 3 };
+enum StatusCode : int { ST_OK = 0, ST_MBAR_TIMEOUT = 1, ST_FLAG_TIMEOUT = 2, ST_BAD_ARG = 3, ST_BAD_INDEX = 4 };
 extern __device__ int g_status[8];
 
 __device__ __forceinline__ void report(int code, int kernel_id, int a, int b) {
@@ -24,6 +24,25 @@ __device__ __forceinline__ void report(int code, int kernel_id, int a, int b) {
     g_status[1] = kernel_id; g_status[2] = (int)blockIdx.x; g_status[3] = a; g_status[4] = b;
   }
 }
+
+// ---- debug build: bounds on the indices the kernels take from tables ------------------------------------------------------
+// Compiled with -DNE_DEBUG_BOUNDS (python -m nanoengine_b200.build_native --debug-bounds; loaded with NE_DEBUG_BOUNDS=1), the
+// kernels that turn a table entry into an address (cache rows from a slot mapping, pages from a block table, state slots,
+// expert ids) compare it with the bound the host registered (ne_debug_set_bounds) before they use it; a bad entry is recorded in
+// the status words (ST_BAD_INDEX, kernel, site, value) and the access is skipped.  In the ordinary build the macro is `true`.
+enum BoundKind : int { BK_CACHE_ROWS = 0, BK_CACHE_PAGES = 1, BK_STATE_SLOTS = 2, BK_EXPERTS = 3, BK_COUNT = 4 };
+#ifdef NE_DEBUG_BOUNDS
+extern __device__ long long g_bounds[BK_COUNT];
+__device__ __forceinline__ bool ne_index_ok(long long idx, int kind, int kernel_id, int site) {
+  const long long n = g_bounds[kind];
+  if (n <= 0 || (idx >= 0 && idx < n)) return true;        // no bound registered: nothing to compare with
+  report(ST_BAD_INDEX, kernel_id, site, (int)idx);
+  return false;
+}
+#define NE_INDEX_OK(idx, kind, kernel_id, site) ne_index_ok((long long)(idx), kind, kernel_id, site)
+#else
+#define NE_INDEX_OK(idx, kind, kernel_id, site) true
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }

@@ -23,11 +23,18 @@ _c = ctypes
 def lib():
     global _LIB
     if _LIB is None:
-        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_native", "libne_kernels.so")
+        # NE_DEBUG_BOUNDS=1 selects the bounds-checked build of the same kernels (python -m nanoengine_b200.build_native --debug-bounds)
+        dbg = os.environ.get("NE_DEBUG_BOUNDS", "0") not in ("", "0")
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_native", "libne_kernels_dbg.so" if dbg else "libne_kernels.so")
         if not os.path.exists(path):
-            raise RuntimeError(f"CUDA kernel library missing: {path}; run `python -m nanoengine_b200.build_native`")
+            raise RuntimeError(f"CUDA kernel library missing: {path}; run `python -m nanoengine_b200.build_native{' --debug-bounds' if dbg else ''}`")
         _LIB = ctypes.CDLL(path)
     return _LIB
+
+
+def debug_set_bounds(cache_rows: int = 0, cache_pages: int = 0, state_slots: int = 0, experts: int = 0) -> bool:
+    """Register the bounds the bounds-checked build compares table entries with; False (and no effect) in the ordinary build."""
+    return bool(lib().ne_debug_set_bounds(_c.c_longlong(cache_rows), _c.c_longlong(cache_pages), _c.c_longlong(state_slots), _c.c_longlong(experts)))
 
 
 def _p(t: Optional[torch.Tensor]):

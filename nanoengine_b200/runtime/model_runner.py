@@ -266,6 +266,12 @@ class ModelRunner:
 
     def allocate_kvcache(self, num_blocks: int) -> None:
         self.cache = KVCache(self.plan, num_blocks, self.device)
+        if self.device.type == "cuda":
+            from ..ops import sm100
+            rows = (num_blocks + 1) * self.plan.block_size
+            if self.plan.hisparse:                      # the key path writes into the hot buffers there
+                rows = max(rows, (self.plan.hs_slots + 1) * self.plan.hot_rows)
+            sm100.debug_set_bounds(rows, num_blocks + 1, self.plan.state_slots + 1 if self.plan.gdn else 0, self.mc.n_routed_experts)
         self.cache.allocate_host(self.config.num_host_kvcache_blocks)
         if self.config.num_speculative_tokens > 0:
             from .mtp_runner import MTPRunner
