@@ -24,11 +24,17 @@ constexpr int kGqaThreads = 192;
 constexpr int kKernelGqa = 7;
 constexpr int kGD = 128;                     // head dim
 constexpr int kGPage = 64;                   // keys per page
-constexpr int kGQBytes = 128 * kGD * 2;      // 32 KB: two 64-element chunks of 128 rows
-constexpr int kGKBytes = kGPage * kGD * 2;   // 16 KB per K (or V) page tile
+constexpr int kGVBytes = kGPage * kGD * 2;   // 16 KB per V tile (and per K tile of a 128-wide head)
 constexpr int kGStages = 3;
 constexpr int kGPBytes = 128 * 128;          // P tile: 128 rows x 64 bf16
-constexpr int kGqaSmem = kGQBytes + kGStages * 2 * kGKBytes + 2 * kGPBytes + 1024 + 256;
+// kC = 64-element chunks of the query / key head dim: 2 (grouped-query models, head dim 128) or 3 (the non-absorbed form of MLA:
+// 128 no-position dims + 64 rotary dims = 192; values stay 128 wide)
+template <int kC> struct GqaSmem {
+  static constexpr int kQ = 128 * 64 * 2 * kC;        // Q tile: kC chunks of 128 rows x 128 B
+  static constexpr int kK = kGPage * 64 * 2 * kC;     // K tile: kC chunks of 64 keys x 128 B
+  static constexpr int kStage = kK + kGVBytes;
+  static constexpr int kBytes = kQ + kGStages * kStage + 2 * kGPBytes + 1024 + 256;
+};
 
 struct GqaArgs {
   const int* block_tables; int bt_stride;
@@ -39,15 +45,22 @@ struct GqaArgs {
   float* part; float* lse2;                  // [splits, T, Hq, 128], [splits, T, Hq] (splits > 1)
 };
 
+// kRagged: keys and values are not paged.  They are the rows of the same tokens as the queries (a prompt without a cached
+// prefix): K no-position part [T, H, 128] and V [T, H, 128] contiguous, the rotary part of the key [T, 64] shared by all heads.
+// "Page" i of a sequence is then its tokens [64 i, 64 i + 64), fetched by token coordinate; rows past the sequence's end belong
+// to the next sequence and are masked by the causal limit like any later key.
+
+template <int kC, bool kRagged>
 __global__ void __launch_bounds__(kGqaThreads, 1)
 gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constant__ CUtensorMap tk_map, const __grid_constant__ CUtensorMap tv_map,
-                const GqaArgs a) {
+                const __grid_constant__ CUtensorMap tr_map, const GqaArgs a) {
+  constexpr int kGQBytes = GqaSmem<kC>::kQ, kGKBytes = GqaSmem<kC>::kK, kStage = GqaSmem<kC>::kStage;
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + kGQBytes;                                     // per stage: [K 16 KB][V 16 KB]
-  uint8_t* sP = sKV + kGStages * 2 * kGKBytes;
+  uint8_t* sKV = sQ + kGQBytes;                                     // per stage: [K kC x 8 KB][V 16 KB]
+  uint8_t* sP = sKV + kGStages * kStage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kGPBytes);
   // q_full | kv_full[3] | kv_empty[3] | s_full[2] | s_empty[2] | p_full[2] | p_empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
@@ -118,17 +131,25 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
   if (warp == 0) {
     if (n_tiles > 0 && elect_one()) {
       mbar_expect_tx(b_qfull, kGQBytes);
-      // box {64 elems, g heads, tq tokens, 2 chunks}: lands as [chunk][token][head][128 B], i.e. row = token * g + head
+      // box {64 elems, g heads, tq tokens, kC chunks}: lands as [chunk][token][head][128 B], i.e. row = token * g + head
       tma_load_4d(smem_u32(sQ), &tq_map, b_qfull, 0, hkv * a.g, tok0, 0);
+      const int k_beg = kRagged ? a.cu_seqlens_q[seq] : 0;
       for (int i = 0; i < n_tiles; i++) {
         const int s = i % kGStages;
         if (!mbar_wait(b_kvempty + 8 * s, ((i / kGStages) & 1) ^ 1, abort_flag, kKernelGqa, 100 + s)) break;
-        int block = bt[pg_begin + i];
-        if (!NE_INDEX_OK(block, BK_CACHE_PAGES, 7, __LINE__)) block = 0;      // a bad page id reads page 0 instead of another allocation
-        uint8_t* dst = sKV + s * 2 * kGKBytes;
-        mbar_expect_tx(b_kvfull + 8 * s, 2 * kGKBytes);
-        tma_load_5d(smem_u32(dst), &tk_map, b_kvfull + 8 * s, 0, 0, hkv, block, 0);
-        tma_load_5d(smem_u32(dst + kGKBytes), &tv_map, b_kvfull + 8 * s, 0, 0, hkv, block, 0);
+        uint8_t* dst = sKV + s * kStage;
+        mbar_expect_tx(b_kvfull + 8 * s, kStage);
+        if (kRagged) {
+          const int tok = k_beg + (pg_begin + i) * kGPage;                 // rows past the tensor's end are zero-filled
+          tma_load_4d(smem_u32(dst), &tk_map, b_kvfull + 8 * s, 0, tok, hkv, 0);                    // no-position part: 2 chunks
+          tma_load_2d(smem_u32(dst + 2 * kGPage * 128), &tr_map, b_kvfull + 8 * s, 0, tok);         // rotary part: third chunk
+          tma_load_4d(smem_u32(dst + kGKBytes), &tv_map, b_kvfull + 8 * s, 0, tok, hkv, 0);
+        } else {
+          int block = bt[pg_begin + i];
+          if (!NE_INDEX_OK(block, BK_CACHE_PAGES, 7, __LINE__)) block = 0;      // a bad page id reads page 0 instead of another allocation
+          tma_load_5d(smem_u32(dst), &tk_map, b_kvfull + 8 * s, 0, 0, hkv, block, 0);
+          tma_load_5d(smem_u32(dst + kGKBytes), &tv_map, b_kvfull + 8 * s, 0, 0, hkv, block, 0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -141,7 +162,7 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
         if (!mbar_wait(b_pfull + 8 * (j & 1), (j >> 1) & 1, abort_flag, kKernelGqa, 230)) return false;
         tc_fence_after();
         const int s = j % kGStages;
-        const uint32_t vt = smem_u32(sKV + s * 2 * kGKBytes + kGKBytes);
+        const uint32_t vt = smem_u32(sKV + s * kStage + kGKBytes);
 #pragma unroll
         for (int ks = 0; ks < 4; ks++) {                     // 16 keys per MMA
           uint64_t adesc = make_smem_desc(p_addr + (j & 1) * kGPBytes + ks * 32, 16, 1024, SW_128B);
@@ -162,10 +183,10 @@ gqa_bf16_kernel(const __grid_constant__ CUtensorMap tq_map, const __grid_constan
         mbar_test2(b_sempty + 8 * ((i + 1) & 1), (((i + 1) >> 1) & 1) ^ 1, b_kvfull + 8 * ((i + 1) % kGStages), ((i + 1) / kGStages) & 1,
                    pre_se, pre_kv);
         tc_fence_after();
-        const uint32_t kt = smem_u32(sKV + s * 2 * kGKBytes);
+        const uint32_t kt = smem_u32(sKV + s * kStage);
         const uint32_t d = tmem_base + sb * kGPage;
 #pragma unroll
-        for (int c = 0; c < 2; c++) {                        // two 64-element chunks of the head dim
+        for (int c = 0; c < kC; c++) {                       // 64-element chunks of the query / key head dim
 #pragma unroll
           for (int ks = 0; ks < 4; ks++) {
             uint64_t adesc = make_smem_desc(q_addr + c * 128 * 128 + ks * 32, 16, 1024, SW_128B);
@@ -342,7 +363,7 @@ extern "C" int ne_gqa_bf16(const void* q, const void* k_cache, const void* v_cac
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gqa_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGqaSmem);
+    cudaError_t e = cudaFuncSetAttribute(gqa_bf16_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GqaSmem<2>::kBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -350,5 +371,45 @@ extern "C" int ne_gqa_bf16(const void* q, const void* k_cache, const void* v_cac
   a.block_tables = block_tables; a.bt_stride = bt_stride; a.cu_seqlens_q = cu_seqlens_q; a.context_lens = context_lens; a.num_seqs = num_seqs;
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.g = g; a.tq = tq; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f;
   a.out = (__nv_bfloat16*)out; a.part = part; a.lse2 = lse2;
-  return (int)launch_pdl(gqa_bf16_kernel, dim3(dim3((unsigned)max_tiles, (unsigned)Hkv, (unsigned)splits)), dim3(kGqaThreads), kGqaSmem, st, mq, mk, mv, a);
+  return (int)launch_pdl(gqa_bf16_kernel<2, false>, dim3(dim3((unsigned)max_tiles, (unsigned)Hkv, (unsigned)splits)), dim3(kGqaThreads), GqaSmem<2>::kBytes,
+                         st, mq, mk, mv, mk, a);
+}
+
+// Non-absorbed MLA attention of prompts without a cached prefix (causal, ragged): q bf16 [T, H, 192] (row stride q_ld elements; the last
+// 64 dims rotated), k_nope bf16 [T, H, 128] and v bf16 [T, H, 128] contiguous, k_rope bf16 [T, 64] (row stride kr_ld elements) shared by
+// the heads, cu_seqlens [num_seqs + 1] (queries and keys alike).  out bf16 [T, H, 128].  max_tiles >= sum of ceil(len / 128).
+// Replaces in the reference: the FA4 ragged prefill call of models/deepseek_v2/deepseek_v2.py:1792-1816.
+extern "C" int ne_mla_prefill_bf16(const void* q, long long q_ld, const void* k_nope, const void* k_rope, long long kr_ld, const void* v,
+                                   const int* cu_seqlens, const int* seq_lens, int num_seqs, int T, int H, int max_tiles, float scale, void* out,
+                                   cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H < 1 || q_ld % 8 || kr_ld % 8 || q_ld < (long long)H * 192) return 1001;
+  CUtensorMap mq, mk, mv, mr;
+  {
+    uint64_t dims[4] = {64, (uint64_t)H, (uint64_t)T, 3}; uint64_t strides[3] = {192 * 2, (uint64_t)q_ld * 2, 128};
+    uint32_t box[4] = {64, 1, 128, 3};
+    int rc = make_tmap(&mq, q, TMA_BF16, 4, dims, strides, box, TMA_SW_128); if (rc) return 2000 + rc;
+  }
+  for (int which = 0; which < 2; which++) {
+    // {64 elems, tokens, heads, 2 chunks}: a box of 64 tokens of one head lands as [chunk][token][128 B]
+    uint64_t dims[4] = {64, (uint64_t)T, (uint64_t)H, 2}; uint64_t strides[3] = {(uint64_t)H * 128 * 2, 128 * 2, 128};
+    uint32_t box[4] = {64, kGPage, 1, 2};
+    int rc = make_tmap(which ? &mv : &mk, which ? v : k_nope, TMA_BF16, 4, dims, strides, box, TMA_SW_128); if (rc) return 2100 + rc;
+  }
+  {
+    uint64_t dims[2] = {64, (uint64_t)T}; uint64_t strides[1] = {(uint64_t)kr_ld * 2}; uint32_t box[2] = {64, kGPage};
+    int rc = make_tmap(&mr, k_rope, TMA_BF16, 2, dims, strides, box, TMA_SW_128); if (rc) return 2200 + rc;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gqa_bf16_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GqaSmem<3>::kBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  GqaArgs a;
+  a.block_tables = nullptr; a.bt_stride = 0; a.cu_seqlens_q = cu_seqlens; a.context_lens = seq_lens; a.num_seqs = num_seqs;
+  a.T = T; a.Hq = H; a.Hkv = H; a.g = 1; a.tq = 128; a.splits = 1; a.scale_log2 = scale * 1.4426950408889634f;
+  a.out = (__nv_bfloat16*)out; a.part = nullptr; a.lse2 = nullptr;
+  return (int)launch_pdl(gqa_bf16_kernel<3, true>, dim3(dim3((unsigned)max_tiles, (unsigned)H, 1)), dim3(kGqaThreads), GqaSmem<3>::kBytes, st, mq, mk, mv,
+                         mr, a);
 }

@@ -109,6 +109,9 @@ class MLAAttention(nn.Module):
         if self.indexer is not None:
             xd = ops.dense(x)
             sparse = self.indexer(xd, ops.dense(q_c) if q_c is not None else xd, positions, ctx, rope_cache)
+        if (NONABSORBED_PREFILL and ctx.is_prefill and sparse is None and x.is_cuda and ctx.extras.get("no_prefix") and nope == 128
+                and rope == 64 and self.v == 128 and x.dtype == torch.bfloat16):
+            return self._prefill_nonabsorbed(x, q, kv_a, positions, ctx, rope_cache)
         q_full = ops.mla_query(q, self.kc, positions, rope_cache, nope, cache, sparse is None, kc_t=self.kc_t)   # [T, H, R + rope]
         o_lat = ops.mla_attention_paged(q_full, cache, ctx.block_tables, ctx.cu_seqlens_q, ctx.context_lens, self.scale, R,
                                         sparse_indices=sparse)
@@ -117,6 +120,24 @@ class MLAAttention(nn.Module):
             o = ops.sigmoid_mul(o, self.g_proj(ops.dense(x)))
         return self.o_proj(o)
 
+
+    def _prefill_nonabsorbed(self, x, q, kv_a, positions, ctx: ForwardContext, rope_cache):
+        """Prompts without a cached prefix: keys and values are expanded from the latent rows of the same tokens (two GEMMs against
+        W_UK / W_UV) and attended in their own 192 / 128-wide geometry, 128 query tokens per tile - about a third of the
+        multiply-adds of the absorbed 576 / 512-wide form and no re-read of the pages per query token.  The latent cache was
+        written just before (decode and later chunks read it).
+        Parity: reference models/deepseek_v2/deepseek_v2.py:1792-1816 (non-absorbed ragged prefill)."""
+        T, H, R, nope = x.shape[0], self.H, self.R, self.nope
+        ckv = ops.rmsnorm(kv_a[:, :R], self.kv_a_layernorm.weight, self.kv_a_layernorm.eps)
+        ckv = ops.dense(ckv)
+        k_pe = ops.apply_rope(kv_a[:, R:].contiguous().view(T, 1, self.rope), positions, rope_cache, True).view(T, self.rope)
+        ops.apply_rope(q[..., nope:], positions, rope_cache, True, q[..., nope:])           # in place on the strided view
+        k_nope = ops.linear(ckv, self.kc.view(H * nope, R)).view(T, H, nope)
+        v = ops.linear(ckv, self.vc_t.view(H * self.v, R)).view(T, H, self.v)
+        o = ops.mla_prefill_ragged(q, k_nope, k_pe, v, ctx.cu_seqlens_q, self.scale).reshape(T, H * self.v)
+        if self.g_proj is not None:
+            o = ops.sigmoid_mul(o, self.g_proj(ops.dense(x)))
+        return self.o_proj(o)
 
     def _forward_hot_cold(self, x, q, q_c, kv_a, positions, ctx: ForwardContext, rope_cache):
         """Decode step under the hot / cold tier: the indexer lists key positions, the tier makes them resident in the
@@ -142,6 +163,7 @@ class MLAAttention(nn.Module):
         return self.o_proj(o)
 
 
+NONABSORBED_PREFILL = True        # prompts without a cached prefix attend in the 192 / 128-wide geometry on the GPU
 OVERLAP_SHARED_EXPERTS = True
 _SIDE_STREAMS = {}
 

@@ -309,6 +309,25 @@ def attention_varlen(q, k, v, cu_seqlens, scale, causal: bool = False) -> torch.
     return out
 
 
+def mla_prefill_ragged(q: torch.Tensor, k_nope: torch.Tensor, k_rope: torch.Tensor, v: torch.Tensor, cu_seqlens, scale: float) -> torch.Tensor:
+    """Non-absorbed MLA attention of prompts without a cached prefix: q [T, H, nope + rope] (rotary part rotated), k_nope
+    [T, H, nope], k_rope [T, rope] shared by the heads, v [T, H, dv]; causal inside each sequence [cu[i], cu[i+1]).  Returns
+    [T, H, dv] (reference models/deepseek_v2/deepseek_v2.py:1792-1816)."""
+    T, H, _ = q.shape
+    k = torch.cat([k_nope.float(), k_rope.float()[:, None, :].expand(T, H, k_rope.shape[-1])], -1)
+    out = torch.empty(T, H, v.shape[-1], dtype=torch.float32, device=q.device)
+    cu = cu_seqlens.tolist() if isinstance(cu_seqlens, torch.Tensor) else list(cu_seqlens)
+    for i in range(len(cu) - 1):
+        lo, hi = cu[i], cu[i + 1]
+        if hi == lo:
+            continue
+        n = hi - lo
+        s = torch.einsum("thd,nhd->htn", q[lo:hi].float(), k[lo:hi]) * scale
+        s = s.masked_fill(torch.ones(n, n, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+        out[lo:hi] = torch.einsum("htn,nhd->thd", torch.softmax(s, -1), v[lo:hi].float())
+    return out.to(q.dtype)
+
+
 def gelu(x: torch.Tensor, tanh: bool = True) -> torch.Tensor:
     return F.gelu(x.float(), approximate="tanh" if tanh else "none").to(x.dtype)
 

@@ -499,6 +499,25 @@ def attention_varlen(q, k, v, cu_seqlens, scale, causal: bool = False):
     return sm100_attn.attention_varlen(q, k, v, cu_seqlens, scale, causal)
 
 
+def mla_prefill_ragged(q: torch.Tensor, k_nope: torch.Tensor, k_rope: torch.Tensor, v: torch.Tensor, cu_seqlens, scale: float) -> torch.Tensor:
+    """Non-absorbed MLA prefill attention on the tcgen05 kernel (128-query tiles per head, 64-key tiles fetched by token
+    coordinate, the shared rotary key part through its own tensor map): head dims 128 + 64 / 128 only."""
+    T, H, D = q.shape
+    assert D == 192 and k_nope.shape == (T, H, 128) and v.shape == (T, H, 128) and k_rope.shape == (T, 64)
+    for t in (q, k_nope, k_rope, v):
+        assert t.dtype == torch.bfloat16 and t.stride(-1) == 1
+    assert q.stride(1) == 192 and k_nope.is_contiguous() and v.is_contiguous() and q.data_ptr() % 16 == 0 and k_rope.data_ptr() % 16 == 0
+    cu = cu_seqlens if isinstance(cu_seqlens, torch.Tensor) else torch.tensor(list(cu_seqlens), dtype=torch.int32)
+    cu = cu.to(q.device, torch.int32)
+    lens = (cu[1:] - cu[:-1]).contiguous()
+    B = lens.numel()
+    out = torch.empty(T, H, 128, dtype=torch.bfloat16, device=q.device)
+    _ck(lib().ne_mla_prefill_bf16(_p(q), _c.c_longlong(q.stride(0)), _p(k_nope), _p(k_rope), _c.c_longlong(k_rope.stride(0)), _p(v), _p(cu), _p(lens),
+                                  _c.c_int(B), _c.c_int(T), _c.c_int(H), _c.c_int(T // 128 + B), _c.c_float(scale), _p(out), _st()),
+        "ne_mla_prefill_bf16")
+    return out
+
+
 def gelu(x: torch.Tensor, tanh: bool = True) -> torch.Tensor:
     """GELU (tanh approximation or exact) over a contiguous bf16 tensor."""
     x = x.contiguous()

@@ -322,6 +322,8 @@ class ModelRunner:
             cu_seqlens_q_host=d["cu_seqlens_q"].tolist(), context_lens_host=d["context_lens"].tolist())
         ctx.extras["input_ids"] = self._to_dev(d["input_ids"]).long()
         ctx.extras["positions"] = self._to_dev(d["positions"]).long()
+        # every sequence of the step brings its whole context with it (no cached prefix, no earlier chunk)
+        ctx.extras["no_prefix"] = bool(b.is_prefill and all(int(n) == int(q) for n, q in zip(b.seq_lens, q_lens)))
         if self.cache.hisparse is not None:
             tier = self.cache.hisparse
             for s, sid in zip(b.hisparse_slots, b.seq_ids):

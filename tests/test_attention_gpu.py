@@ -188,3 +188,45 @@ def test_dsa_model_end_to_end_takes_the_sparse_tensor_core_path():
     same = sum(a == b for a, b in zip(outs[True], outs[False]))
     assert same >= 2 and all(a[:3] == b[:3] for a, b in zip(outs[True], outs[False])), outs
     assert sm100.kernel_status()[0] == 0
+
+
+@pytest.mark.parametrize("H,lens", [(4, [300, 1, 64, 129]), (16, [2048]), (2, [128, 128, 5])])
+def test_mla_prefill_ragged_tcgen05(k, H, lens):
+    """Non-absorbed MLA prefill (192-wide queries / keys with a rotary key part shared by the heads, 128-wide values) against the
+    fp32 statement; q and the rotary keys are strided views, as the model passes them."""
+    torch.manual_seed(11)
+    T = sum(lens)
+    q = (torch.randn(T, H * 192 + 64, device="cuda") * 0.5).to(torch.bfloat16)[:, : H * 192].view(T, H, 192)
+    kn = (torch.randn(T, H, 128, device="cuda") * 0.5).to(torch.bfloat16)
+    kr = (torch.randn(T, 576, device="cuda") * 0.5).to(torch.bfloat16)[:, 512:]
+    v = torch.randn(T, H, 128, device="cuda").to(torch.bfloat16)
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    want = ref.mla_prefill_ragged(q.float(), kn.float(), kr.float(), v.float(), cu, 192 ** -0.5)
+    got = k.mla_prefill_ragged(q, kn, kr, v, cu, 192 ** -0.5)
+    assert _rel(got, want) < 1e-2
+
+
+def test_nonabsorbed_prefill_gives_the_absorbed_form_s_logits():
+    """The same prompts through the absorbed (576 / 512-wide, paged) and the non-absorbed (192 / 128-wide, ragged) prefill: the
+    logits of the first generated token agree, and so do the tokens that follow (the cache both leave is the same)."""
+    from nanoengine_b200 import Config, LLM, SamplingParams
+    from nanoengine_b200.models import deepseek
+    from nanoengine_b200.models.config import tiny_deepseek_v3
+    mc = tiny_deepseek_v3(hidden_size=512, moe_intermediate_size=256, intermediate_size=1024, q_lora_rank=256, kv_lora_rank=512,
+                          qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_attention_heads=16)
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (300, 70, 129)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = {}
+    for flag in (True, False):
+        deepseek.NONABSORBED_PREFILL = flag
+        try:
+            llm = LLM(Config(model="tiny-deepseek-v3", model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kvcache_block_size=64,
+                             num_kvcache_blocks=64, max_num_seqs=4, enforce_eager=True, seed=0, enable_prefix_caching=False))
+            outs[flag] = [o["token_ids"] for o in llm.generate(prompts, sp)]
+        finally:
+            deepseek.NONABSORBED_PREFILL = True
+        del llm
+        torch.cuda.empty_cache()
+    same = sum(a == b for a, b in zip(outs[True], outs[False]))
+    assert same >= 2 and all(a[:2] == b[:2] for a, b in zip(outs[True], outs[False])), outs
