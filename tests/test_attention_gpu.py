@@ -202,7 +202,8 @@ def test_mla_prefill_ragged_tcgen05(k, H, lens):
     v = torch.randn(T, H, 128, device="cuda").to(torch.bfloat16)
     cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
     want = ref.mla_prefill_ragged(q.float(), kn.float(), kr.float(), v.float(), cu, 192 ** -0.5)
-    got = k.mla_prefill_ragged(q, kn, kr, v, cu, 192 ** -0.5)
+    from nanoengine_b200.ops import sm100
+    got = sm100.mla_prefill_ragged(q, kn, kr, v, cu, 192 ** -0.5)
     assert _rel(got, want) < 1e-2
 
 
