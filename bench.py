@@ -102,6 +102,9 @@ def main():
                          "prefill pass; a 64 x 65,536-token prefill would take minutes).  The decode step does all of its work.")
     ap.add_argument("--hisparse", type=int, default=0, help="with --synthetic-context: hot rows per sequence of the hot / cold cache tier "
                     "(the latent cache then lives in pinned host memory)")
+    ap.add_argument("--scale-format", default="ue8m0", choices=["fp32", "ue8m0"],
+                    help="fp8 block scales of the DeepSeek shapes: ue8m0 (powers of two, as the V3.1 / V3.2 checkpoints ship them; the tensor cores "
+                         "apply them) or fp32 (the original V3 recipe; applied on the CUDA cores)")
     ap.add_argument("--seqs-per-gpu", type=int, default=128)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=61, help="debug only: anything but 61 marks the result invalid")
@@ -153,7 +156,7 @@ def main():
                  attention_dp=1 if qwen else N, attention_tp=N if qwen else 1, ffn_ep=N, executor_backend="spmd", enable_prefix_caching=False,
                  cuda_graph_max_bs=S, seed=0 if qwen else rank, num_speculative_tokens=args.mtp,
                  mode="decode" if args.synthetic_context else "hybrid", dummy_prefill=args.synthetic_context,
-                 enable_hisparse=args.hisparse > 0, hisparse_device_buffer_size=args.hisparse or 4096,
+                 fp8_scale_format=args.scale_format, enable_hisparse=args.hisparse > 0, hisparse_device_buffer_size=args.hisparse or 4096,
                  hisparse_host_gb=(S * pages + 16) * 64 * 576 * args.layers / 2 ** 30 + 1)
     t_build = time.time()
     llm = LLM(cfg)
@@ -267,6 +270,7 @@ def main():
                                 (f"DeepSeek-{'V3.2 (DSA top-2048' + (', hot / cold tier ' + str(args.hisparse) + ' rows' if args.hisparse else '') + ')' if args.model == 'deepseek-v32' else 'V3'} shape: {args.layers} layers, hidden 7168, 128 MLA heads, {args.experts_per_gpu * N} routed experts "
                                  f"({args.experts_per_gpu}/GPU) top-8, 1 shared"), "global_batch": tokens_per_step, "seq_len": P,
                        "parallelism": f"tp{N} attention + ep{N} experts" if qwen else f"dp{N} attention + ep{N} experts",
+                       "fp8_scale_format": None if qwen else args.scale_format,
                        "l2": "inputs (the weights streamed every step) exceed L2; no flush",
                        "valid": (args.layers == 94 and args.experts_per_gpu == 16) if qwen else (args.layers == 61 and args.experts_per_gpu == 32 and (S == 128 or args.model == "deepseek-v32"))},
             "decode_tok_s_per_gpu": round(value / N, 1), "tpot_ms": round(dev_ms, 3), "tpot_slo_50ms_met": dev_ms <= 50.0,

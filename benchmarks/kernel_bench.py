@@ -72,9 +72,16 @@ def rand_fp8(*shape):
     return (torch.randn(*shape, device="cuda") * 0.5).to(FP8)
 
 
+def rand_scales(*shape):
+    """Weight block scales in the process's scale format (powers of two under "ue8m0")."""
+    if sm100.scale_format() == "ue8m0":
+        return torch.exp2(torch.randint(-1, 2, shape, device="cuda").float())
+    return torch.rand(*shape, device="cuda") + 0.5
+
+
 def case_dense_fp8(M, N, K):
     x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
-    w, s = rand_fp8(N, K), torch.rand((N + 127) // 128, K // 128, device="cuda") + 0.5
+    w, s = rand_fp8(N, K), rand_scales((N + 127) // 128, K // 128)
     q = torch.empty(M, K, dtype=FP8, device="cuda")
     sc = torch.empty(K // 128, M, dtype=torch.float32, device="cuda")
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
@@ -97,7 +104,7 @@ def case_moe_gemm(E, rows_per_expert, N, K):
     a = rand_fp8(R, K)
     sa = torch.ones(K // 128, R, device="cuda")
     w = rand_fp8(E, N, K)
-    sb = torch.rand(E, (N + 127) // 128, K // 128, device="cuda") + 0.5
+    sb = rand_scales(E, (N + 127) // 128, K // 128)
     counts = torch.full((E,), rows_per_expert, dtype=torch.int32, device="cuda")
     row_start = (torch.arange(E + 1, device="cuda") * pad).to(torch.int32)
     out = torch.empty(R, N, dtype=torch.bfloat16, device="cuda")
@@ -409,8 +416,11 @@ def main():
     ap.add_argument("--ctx", type=int, default=2560)
     ap.add_argument("--prefill-tokens", type=int, default=16384)
     ap.add_argument("--graph", action="store_true", help="time a CUDA-graph replay of the case (removes the host launch path from short kernels)")
+    ap.add_argument("--scale-format", default="fp32", choices=["fp32", "ue8m0"],
+                    help="ue8m0: power-of-two fp8 block scales, applied by the tensor cores (tcgen05 block-scaled MMA) instead of the CUDA cores")
     args = ap.parse_args()
     sm100.lib()
+    sm100.set_scale_format(args.scale_format)
     bw, fl, src = peaks()
     cases = build_cases(args)
     names = list(cases) if args.case == "all" else args.case.split(",")

@@ -40,6 +40,10 @@ class Config:
     ffn_ep: int = 1
     ffn_tp: int = 1
     pp: int = 1
+    # fp8 block scales: auto (what the checkpoint's quantization_config.scale_fmt says) | fp32 | ue8m0.  ue8m0 rounds every
+    # activation scale up to a power of two (and re-quantises weights whose scales are not) so that the tensor cores apply
+    # the scales themselves; one setting per process.
+    fp8_scale_format: str = "auto"
     # cache
     kv_cache_dtype: str = "auto"             # auto | bfloat16 | fp8
     kvcache_block_size: int = 256
@@ -100,6 +104,8 @@ class Config:
             raise ValueError("mode must be hybrid, prefill or decode")
         if self.routing_strategy not in ("round_robin", "least_batch", "least_cache", "affinity"):
             raise ValueError(f"unknown routing_strategy {self.routing_strategy}")
+        if self.fp8_scale_format not in ("auto", "fp32", "ue8m0"):
+            raise ValueError("fp8_scale_format must be auto, fp32 or ue8m0")
         if self.kv_cache_dtype not in ("auto", "bfloat16", "float32", "fp8"):
             raise ValueError("kv_cache_dtype must be auto, bfloat16, float32 or fp8")
         if self.dtype not in ("bfloat16", "float16", "float32"):
@@ -182,6 +188,11 @@ class Config:
     @property
     def world_size(self) -> int:
         return self.parallel_spec().world_size
+
+    def resolved_scale_format(self) -> str:
+        if self.fp8_scale_format != "auto":
+            return self.fp8_scale_format
+        return "ue8m0" if self.model_config.scale_fmt == "ue8m0" else "fp32"
 
     def resolved_kv_dtype(self) -> str:
         if self.kv_cache_dtype != "auto":

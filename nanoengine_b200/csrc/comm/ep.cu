@@ -69,9 +69,9 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpLayout L, cons
         float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
         float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
         amax = fmaxf(warp_max(amax), 1e-10f);
-        const float is = 448.f / amax;
+        float is; const float sg = fp8_group_scale(amax, L.fp8 == 2, &is);
         *reinterpret_cast<uint32_t*>(aq + g * 128 + lane * 4) = pack_e4m3x4(a.x * is, a.y * is, b.x * is, b.y * is);
-        if (lane == 0) as[(long long)g * cap] = amax / 448.f;
+        if (lane == 0) as[(long long)g * cap] = sg;
       }
     } else {
       __nv_bfloat16* ab = reinterpret_cast<__nv_bfloat16*>(peer_ptr(L, dst, L.off_abf)) + row * H;
@@ -173,7 +173,9 @@ extern "C" int ne_ep_dispatch(const EpLayout* L, const void* x, const int* idx, 
   if (n_pairs <= 0) { ep_arrive_only_kernel<<<1, 32, 0, st>>>(*L, epoch_ptr); return (int)cudaGetLastError(); }
   int blocks = (n_pairs + 7) / 8;
   if (blocks > 1184) blocks = 1184;
-  ep_dispatch_kernel<<<blocks, 256, 0, st>>>(*L, (const __nv_bfloat16*)x, idx, pair_ok, n_pairs, epoch_ptr, cta_counter);
+  EpLayout Lq = *L;
+  if (Lq.fp8 && g_scale_pow2) Lq.fp8 = 2;               // fp8 == 2: group scales rounded up to powers of two
+  ep_dispatch_kernel<<<blocks, 256, 0, st>>>(Lq, (const __nv_bfloat16*)x, idx, pair_ok, n_pairs, epoch_ptr, cta_counter);
   return (int)cudaGetLastError();
 }
 

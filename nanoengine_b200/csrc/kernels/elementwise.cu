@@ -31,7 +31,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, const __nv_bfloat16* __restrict__ res_in,
                                                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long out_ld,
                                                      __nv_bfloat16* __restrict__ res_out, uint8_t* __restrict__ q, float* __restrict__ sc, int sc_ld,
-                                                     int H, float eps, float w_off) {
+                                                     int H, float eps, float w_off, int pow2) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   extern __shared__ float srow[];            // H floats
   __shared__ float red[32];
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
         amax = fmaxf(amax, fabsf(v[j]));
       }
       amax = fmaxf(warp_max(amax), 1e-10f);
-      float s = amax / kFp8Max, is = kFp8Max / amax;
+      float is; const float s = fp8_group_scale(amax, pow2, &is);
       *reinterpret_cast<uint32_t*>(q + (long long)row * H + c) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
       if (lane == 0) sc[(long long)g * sc_ld + row] = s;
     }
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 
 // bf16 [T, K] (row stride x_ld) -> e4m3 [T, K] + scales sc[(k/128) * sc_ld + t].  One warp per (row, group).
 __global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, uint8_t* __restrict__ q, float* __restrict__ sc,
-                                   int sc_ld, int T, int K) {
+                                   int sc_ld, int T, int K, int pow2) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   const int groups = K / 128;
   long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -109,9 +109,9 @@ __global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, long lon
   float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
   float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
   amax = fmaxf(warp_max(amax), 1e-10f);
-  float is = kFp8Max / amax;
+  float is; const float s = fp8_group_scale(amax, pow2, &is);
   *reinterpret_cast<uint32_t*>(q + (long long)row * K + g * 128 + lane * 4) = pack_e4m3x4(a.x * is, a.y * is, b.x * is, b.y * is);
-  if (lane == 0) sc[(long long)g * sc_ld + row] = amax / kFp8Max;
+  if (lane == 0) sc[(long long)g * sc_ld + row] = s;
 }
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -133,7 +133,7 @@ __device__ __forceinline__ float glu_act(float g, float u, int act, float p0, fl
 
 __device__ __forceinline__ void silu_item(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q,
                                           float* __restrict__ sc, int sc_ld, long long mrow, int row, int c, int I, int lane,
-                                          int act = 0, float p0 = 0.f, float p1 = 0.f) {
+                                          int act, float p0, float p1, int pow2) {
   const __nv_bfloat16* xr = x + mrow * 2 * I + c * 128 + lane * 4;
   uint2 gv = *reinterpret_cast<const uint2*>(xr), uv = *reinterpret_cast<const uint2*>(xr + I);
   float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), u0 = unpack_bf16x2(uv.x), u1 = unpack_bf16x2(uv.y);
@@ -147,9 +147,9 @@ __device__ __forceinline__ void silu_item(const __nv_bfloat16* __restrict__ x, _
 #pragma unroll
   for (int j = 0; j < 4; j++) { v[j] = __bfloat162float(__float2bfloat16(v[j])); amax = fmaxf(amax, fabsf(v[j])); }
   amax = fmaxf(warp_max(amax), 1e-10f);
-  const float is = kFp8Max / amax;
+  float is; const float s = fp8_group_scale(amax, pow2, &is);
   *reinterpret_cast<uint32_t*>(q + o) = pack_e4m3x4(v[0] * is, v[1] * is, v[2] * is, v[3] * is);
-  if (lane == 0) sc[(long long)c * sc_ld + row] = amax / kFp8Max;
+  if (lane == 0) sc[(long long)c * sc_ld + row] = s;
 }
 
 // x [groups, rows, 2I] -> y.  One warp per (row, 128 output columns).  rows_valid[g] masks rows (nullptr = all).
@@ -157,7 +157,7 @@ __device__ __forceinline__ void silu_item(const __nv_bfloat16* __restrict__ x, _
 constexpr int kSiluMaxGroups = 1024;
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ sc,
                                 int sc_ld, long long sc_gs, const int* __restrict__ rows_valid, const int* __restrict__ row_start, int groups,
-                                int rows, int I, int act, float p0, float p1) {
+                                int rows, int I, int act, float p0, float p1, int pow2) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   // warps stride over the concatenation of all groups' (valid row, 128-column block) items, so a sparsely filled masked
   // layout costs only its valid rows and every warp gets an equal share whatever the split between groups.  The item index
@@ -197,7 +197,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
       const int row = s_rs[g] + ri;
       if (row >= rows && row_start) continue;
       const long long gbase = row_start ? 0 : (long long)g * rows;
-      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane, act, p0, p1);
+      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane, act, p0, p1, pow2);
     }
     return;
   }
@@ -217,7 +217,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
     for (long long it = first; it < items; it += nw) {
       const int row = r0 + (int)(it / cg), c = (int)(it % cg);
       if (row >= rows && row_start) continue;
-      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane, act, p0, p1);
+      silu_item(x, y, q, sc + (row_start ? 0 : (long long)g * sc_gs), sc_ld, gbase + row, row, c, I, lane, act, p0, p1, pow2);
     }
   }
 }
@@ -496,7 +496,7 @@ extern "C" int ne_rmsnorm(const void* x, long long x_ld, const void* res_in, con
     if (!done) { cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); done = true; }
   }
   return (int)launch_pdl(rmsnorm_kernel, dim3(T), dim3(256), smem, st, (const __nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)res_in, (const __nv_bfloat16*)w,
-                                       (__nv_bfloat16*)out, out_ld, (__nv_bfloat16*)res_out, (uint8_t*)q, sc, sc_ld, H, eps, w_off);
+                                       (__nv_bfloat16*)out, out_ld, (__nv_bfloat16*)res_out, (uint8_t*)q, sc, sc_ld, H, eps, w_off, g_scale_pow2);
 }
 
 extern "C" int ne_quant_1x128(const void* x, long long x_ld, void* q, float* sc, int sc_ld, int T, int K, cudaStream_t st) {
@@ -504,7 +504,7 @@ extern "C" int ne_quant_1x128(const void* x, long long x_ld, void* q, float* sc,
   if (K % 128 != 0 || x_ld % 4 != 0) return 1001;
   long long warps = (long long)T * (K / 128);
   int blocks = (int)((warps + 7) / 8);
-  return (int)launch_pdl(quant_1x128_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, x_ld, (uint8_t*)q, sc, sc_ld, T, K);
+  return (int)launch_pdl(quant_1x128_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, x_ld, (uint8_t*)q, sc, sc_ld, T, K, g_scale_pow2);
 }
 
 extern "C" int ne_act_mul(const void* x, void* y, void* q, float* sc, int sc_ld, long long sc_gs, const int* rows_valid, const int* row_start,
@@ -522,7 +522,7 @@ extern "C" int ne_act_mul(const void* x, void* y, void* q, float* sc, int sc_ld,
   long long warps = (long long)groups * rows * (I / 128);
   long long want = (warps + 7) / 8;
   int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
-  return (int)launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, row_start, groups, rows, I, act, p0, p1);
+  return (int)launch_pdl(silu_mul_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)q, sc, sc_ld, sc_gs, rows_valid, row_start, groups, rows, I, act, p0, p1, g_scale_pow2);
 }
 
 extern "C" int ne_rope(const void* x, long long row_stride, int head_stride, void* y, long long y_row_stride, int y_head_stride, int heads,

@@ -24,6 +24,7 @@
 
 namespace ne {
 
+int g_scale_pow2 = 0;
 __device__ int g_status[8];
 #ifdef NE_DEBUG_BOUNDS
 __device__ long long g_bounds[BK_COUNT];
@@ -198,10 +199,24 @@ __device__ __forceinline__ __nv_bfloat16* scatter_row(const GemmArgs& a, int grp
 
 // Block-scaled tiles at least 64 wide use two epilogue warpgroups that split the tile's columns, halving the
 // promotion work per thread and per K block.
-template <int BLOCK_N, bool kBlockScaled> struct EpiCfg {
+template <int BLOCK_N, bool kBlockScaled, bool kHw = false> struct EpiCfg {
   static constexpr int kGroups = (kBlockScaled && BLOCK_N >= 64) ? 2 : 1;
-  static constexpr int kThreads = 64 + 128 * kGroups;
+  static constexpr int kThreads = 64 + 128 * kGroups + (kHw ? 128 : 0);      // kHw: four scale-factor warps after the epilogue warps
 };
+
+// kHw: fp8 operands whose block scales are powers of two, applied by the tensor cores themselves
+// (tcgen05.mma.kind::mxf8f6f4.block_scale, UE8M0 scale factors read from TMEM).  One accumulator per tile, as in a plain
+// GEMM: no promotion on the CUDA cores.  The instruction takes one scale byte per operand row and per 32 elements of K;
+// the DeepSeek granularity (one per 128 of K, and per 128 x 128 weight block) maps onto it as follows:
+//  * the scale factors of A for 4 consecutive K blocks of a 128-row tile are one TMEM word per row: byte j belongs to K
+//    block j, selected by the scale-factor id of the instruction descriptor, and all four K = 32 instructions of a K block
+//    use the same byte.  Row r + 32 g of the tile is held by lane r (of every 32-lane quarter) in column g.
+//  * a tile is at most 128 columns wide and never straddles a weight block, so the weight scale of a K block is one
+//    number per tile; it is folded into A's byte (exponents add) and B's scale factors are the constant 1.
+// Four extra warps, one per TMEM lane quarter, compute the bytes from the fp32 scale arrays and store them into TMEM
+// (tcgen05.st) a few chunks ahead of the MMA issuer.
+constexpr int kSfBufs = 8;          // TMEM ring of scale-factor chunks
+constexpr int kSfGroup = 4;         // chunks whose scales are fetched together
 
 // kSplit: split-K across a thread-block cluster.  The CTAs of a cluster work on the same output tile, each over its own
 // slice of K; every CTA parks its fp32 partial tile in its shared memory and, after a cluster barrier, CTA r adds up rows
@@ -209,8 +224,8 @@ template <int BLOCK_N, bool kBlockScaled> struct EpiCfg {
 // 128-token decode GEMM keep every SM pulling weights while using the 128-wide tile (a narrow tile re-reads the
 // activation operand once per tile and is bound by the SM's L2 read rate instead of HBM).  One tile per cluster,
 // dense operands only (groups = 1, no row tables).
-template <int BLOCK_N, bool kFP8, bool kBlockScaled, bool kSplit>
-__global__ void __launch_bounds__((EpiCfg<BLOCK_N, kBlockScaled>::kThreads), 1)
+template <int BLOCK_N, bool kFP8, bool kBlockScaled, bool kSplit, bool kHw = false>
+__global__ void __launch_bounds__((EpiCfg<BLOCK_N, kBlockScaled, kHw>::kThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64, const __grid_constant__ CUtensorMap tmap_a32,
             const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
   using S = Smem<BLOCK_N>;
@@ -222,8 +237,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   // TMEM accumulator ring: block-scaled GEMMs hand one accumulator per K block to the epilogue, so they use the
   // deepest ring 512 columns allow (up to 4); plain GEMMs hand over one per tile and need two.
   constexpr int kAcc = kBlockScaled ? ((512 / BLOCK_N) > 4 ? 4 : (512 / BLOCK_N)) : 2;
-  constexpr uint32_t kTmemCols = (kAcc * BLOCK_N) < 32 ? 32 : kAcc * BLOCK_N;
-  constexpr uint32_t kIdesc = make_idesc(kFP8 ? FMT_E4M3 : FMT_BF16, kFP8 ? FMT_E4M3 : FMT_BF16, kBlockM, BLOCK_N);
+  static_assert(!kHw || (kFP8 && !kBlockScaled && BLOCK_N <= 128), "hardware block scaling: fp8 operands, one accumulator per tile");
+  // kHw: the scale factors follow the accumulators: 4 columns of B's constant, then kSfBufs buffers of 4 columns for A
+  constexpr uint32_t kSfbCol = kAcc * BLOCK_N, kSfaCol = kSfbCol + 4;
+  constexpr uint32_t kColsUsed = kAcc * BLOCK_N + (kHw ? 4 + 4 * kSfBufs : 0);
+  constexpr uint32_t kTmemCols = kColsUsed <= 32 ? 32 : (kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512)));
+  constexpr uint32_t kIdesc = kHw ? make_idesc_block_scaled(FMT_E4M3, FMT_E4M3, kBlockM, BLOCK_N)
+                                  : make_idesc(kFP8 ? FMT_E4M3 : FMT_BF16, kFP8 ? FMT_E4M3 : FMT_BF16, kBlockM, BLOCK_N);
   constexpr int kEpi = EpiCfg<BLOCK_N, kBlockScaled>::kGroups;
   constexpr int kCols = BLOCK_N / kEpi;          // columns of the tile each epilogue thread owns
 
@@ -237,6 +257,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
   const uint32_t tfull0 = smem_u32(bars + 2 * kStages), tempty0 = smem_u32(bars + 2 * kStages + kAcc);
   const uint32_t smem_base = smem_u32(smem);
+  __shared__ uint64_t s_sfbar[2 * kSfBufs];            // kHw: scale-factor buffer filled (4 warps arrive) / drained (MMAs retired)
+  const uint32_t sffull0 = smem_u32(s_sfbar), sfempty0 = smem_u32(s_sfbar + kSfBufs);
 
   const int warp = threadIdx.x >> 5;
   const int total_kb = (args.K + kElemsPerStageK - 1) / kElemsPerStageK;
@@ -253,6 +275,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
     for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4 * kEpi); }
+    if (kHw) for (int i = 0; i < kSfBufs; i++) { mbar_init(sffull0 + 8 * i, 4); mbar_init(sfempty0 + 8 * i, 1); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_a64); tma_prefetch_desc(&tmap_a32); tma_prefetch_desc(&tmap_b);
@@ -288,7 +311,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int* rs_tab = args.row_start ? (cache_tables ? s_rs : args.row_start) : nullptr;
   // first tile of every ragged group: counts by all threads, then one warp turns them into running sums
   __shared__ int s_base[kSchedCache + 1];
-  static_assert((3 * kSchedCache + 4) * (int)sizeof(int) + 128 <= S::kStaticTables, "the stage budget must leave room for the static tables");
+  static_assert((3 * kSchedCache + 4) * (int)sizeof(int) + 16 * kSfBufs + 64 <= S::kStaticTables, "the stage budget must leave room for the static tables");
   const bool ragged = args.masked_m || args.row_start;
   const int* base_tab = (ragged && cache_tables) ? s_base : nullptr;
   if (base_tab) {
@@ -375,6 +398,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       // (the issue blocks for about as long as the MMAs run, which hides the test); only a failed test falls back to waiting.
       bool pre_full = mbar_test(full0 + 8 * stage, phase);
       bool pre_te = mbar_test(tempty0 + 8 * buf, bphase ^ 1);
+      int sfb = 0; uint32_t sfphase = 0;                // kHw: scale-factor buffer in use and its phase
+      bool pre_sf = false;
       for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
         if (!kBlockScaled) {
           if (!pre_te && !mbar_wait(tempty0 + 8 * buf, bphase ^ 1, abort_flag, kKernelGemm, 200 + buf)) { ok = false; break; }
@@ -403,6 +428,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               pre_te = mbar_test(tempty0 + 8 * nbuf, (buf + 1 == kAcc ? bphase ^ 1 : bphase) ^ 1);
             }
             if (g == kG - 1 || kb + 1 >= num_kb) pre_full = mbar_test(full0 + 8 * nstage, nphase);
+            if (kHw && (kb & 3) == 0) {
+              // a new chunk of four K blocks: its scale factors must be in TMEM
+              if (!pre_sf && !mbar_wait(sffull0 + 8 * sfb, sfphase, abort_flag, kKernelGemm, 500 + sfb)) { ok = false; break; }
+              tc_fence_after();
+            }
+            const bool chunk_end = kHw && ((kb & 3) == 3 || kb + 1 >= num_kb);
+            if (chunk_end) {
+              const int nsf = sfb + 1 == kSfBufs ? 0 : sfb + 1;
+              pre_sf = mbar_test(sffull0 + 8 * nsf, sfb + 1 == kSfBufs ? sfphase ^ 1 : sfphase);
+            }
             uint64_t adesc = make_smem_desc(a_base + g * a_kstride, 16, 1024, SW_128B);
             uint64_t bdesc = make_smem_desc(b_base + g * S::kBBytes, 16, 1024, SW_128B);
             uint32_t d = tmem_base + buf * BLOCK_N;
@@ -410,9 +445,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int k = 0; k < kMmasPerStage; k++) {
               uint32_t acc = kBlockScaled ? (k != 0) : ((kb | k) != 0);
               // advancing 32 bytes along K inside the 128B swizzle atom = +2 in the descriptor's 16-byte address units
-              if (kFP8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              if (kHw) umma_f8_block_scaled(d, adesc + 2 * k, bdesc + 2 * k, kIdesc | ((uint32_t)(kb & 3) << 29), acc,
+                                            tmem_base + kSfaCol + 4 * sfb, tmem_base + kSfbCol);
+              else if (kFP8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
               else umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
             }
+            if (chunk_end) { tc_commit(sfempty0 + 8 * sfb); if (++sfb == kSfBufs) { sfb = 0; sfphase ^= 1; } }
             if (kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == kAcc) { buf = 0; bphase ^= 1; } }
           }
           tc_commit(empty0 + 8 * stage);                // smem slot reusable once these MMAs retire
@@ -423,6 +461,80 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tc_commit(tfull0 + 8 * buf);
           if (++buf == kAcc) { buf = 0; bphase ^= 1; }
           pre_te = mbar_test(tempty0 + 8 * buf, bphase ^ 1);
+        }
+      }
+    }
+  } else if (kHw && warp >= 2 + 4 * kEpi) {
+    // ---------------- scale-factor warps: warp w fills TMEM lanes [32*(w%4), +32) ----------------
+    const int lane = (int)lane_id();
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
+    int sfb = 0; uint32_t sfphase = 0; int grp, mb, nb;
+    bool ok = true, first = true;
+    for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
+      if (first) {
+        // B's scale factors: the constant 1 (UE8M0 byte 127), written once
+        const uint32_t ones[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
+        tmem_st_32x32b_x4(tmem_base + lane_addr + kSfbCol, ones);
+        first = false;
+      }
+      // rows lane + 32 g of the tile; rows past the group's end read the tile's first row (their results are never stored)
+      const int rows_here = sched.rows(grp) - mb * kBlockM;
+      const float* sa = args.sa + (long long)grp * args.sa_group_stride + sched.row0(grp) + mb * kBlockM + (long long)kb_begin * args.sa_ld;
+      const float* sb = args.sb + (long long)grp * args.sb_group_stride + (long long)(nb * BLOCK_N / 128) * total_kb + kb_begin;
+      int roff[4];
+#pragma unroll
+      for (int g = 0; g < 4; g++) roff[g] = lane + 32 * g < rows_here ? lane + 32 * g : 0;
+      // The scale arrays are read kSfGroup chunks (16 K blocks) at a time, and the loads of the next batch are in flight while
+      // this one is converted and stored: a single chunk per round trip to L2 (about a microsecond) would feed the tensor
+      // pipe at half the rate it consumes them.
+      const int n_chunks = (num_kb + 3) >> 2;
+      uint32_t ra[kSfGroup][4][4], rb[kSfGroup][4];         // raw bits: [chunk][K block][row group], [chunk][K block]
+      auto fetch = [&](int c0) {
+#pragma unroll
+        for (int u = 0; u < kSfGroup; u++) {
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int kb = (c0 + u) * 4 + j;
+            const bool in = kb < num_kb;
+            rb[u][j] = in ? __float_as_uint(__ldg(sb + kb)) : 0u;
+#pragma unroll
+            for (int g = 0; g < 4; g++) ra[u][j][g] = in ? __float_as_uint(__ldg(sa + (long long)kb * args.sa_ld + roff[g])) : 0u;
+          }
+        }
+      };
+      fetch(0);
+      for (int c0 = 0; c0 < n_chunks && ok; c0 += kSfGroup) {
+        uint32_t w[kSfGroup][4];
+#pragma unroll
+        for (int u = 0; u < kSfGroup; u++) {
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            uint32_t word = 0u;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int e = (int)((ra[u][j][g] >> 23) & 0xffu) + (int)((rb[u][j] >> 23) & 0xffu) - 127;
+              word |= (uint32_t)min(max(e, 0), 254) << (8 * j);
+            }
+            w[u][g] = word;
+          }
+        }
+        if (c0 + kSfGroup < n_chunks) fetch(c0 + kSfGroup);
+#pragma unroll
+        for (int u = 0; u < kSfGroup; u++) {
+          if (c0 + u < n_chunks && ok) {
+            if (mbar_wait(sfempty0 + 8 * sfb, sfphase ^ 1, abort_flag, kKernelGemm, 510 + sfb)) {
+              tc_fence_after();
+              tmem_st_32x32b_x4(tmem_base + lane_addr + kSfaCol + 4 * sfb, w[u]);
+              tc_wait_st();
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(sffull0 + 8 * sfb);
+              if (++sfb == kSfBufs) { sfb = 0; sfphase ^= 1; }
+            } else {
+              ok = false;
+            }
+          }
         }
       }
     }
@@ -581,7 +693,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (kSplit) {
     // ---------------- cross-CTA reduction of the partial tiles ----------------
     cluster_sync_all();
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 2 + 4 * kEpi) {
       const int mb = tile0 / n_blocks, nb = tile0 % n_blocks;      // split-K runs single-row-block GEMMs: no rotation to apply
       const int R = (kBlockM + split - 1) / split;
       constexpr int kChunks = BLOCK_N / 4;
@@ -683,22 +795,22 @@ static int num_sms() {
   return n;
 }
 
-template <int BLOCK_N, bool kFP8, bool kBS>
+template <int BLOCK_N, bool kFP8, bool kBS, bool kHw = false>
 static int launch(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs& a, int grid, cudaStream_t st) {
-  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, false>;
+  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, false, kHw>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BLOCK_N>::kBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)launch_pdl(kern, dim3((unsigned)grid), dim3(EpiCfg<BLOCK_N, kBS>::kThreads), Smem<BLOCK_N>::kBytes, st, tas[0], tas[1], tas[2], tb, a);
+  return (int)launch_pdl(kern, dim3((unsigned)grid), dim3(EpiCfg<BLOCK_N, kBS, kHw>::kThreads), Smem<BLOCK_N>::kBytes, st, tas[0], tas[1], tas[2], tb, a);
 }
 
 // split-K form: `tiles` clusters of `split` CTAs
-template <int BLOCK_N, bool kFP8, bool kBS>
+template <int BLOCK_N, bool kFP8, bool kBS, bool kHw = false>
 static int launch_split(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs& a, int tiles, int split, cudaStream_t st) {
-  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, true>;
+  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, true, kHw>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BLOCK_N>::kBytes);
@@ -707,7 +819,7 @@ static int launch_split(const CUtensorMap* tas, const CUtensorMap& tb, const Gem
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(tiles * split), 1, 1);
-  cfg.blockDim = dim3(EpiCfg<BLOCK_N, kBS>::kThreads, 1, 1);
+  cfg.blockDim = dim3(EpiCfg<BLOCK_N, kBS, kHw>::kThreads, 1, 1);
   cfg.dynamicSmemBytes = Smem<BLOCK_N>::kBytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -743,7 +855,8 @@ static void plan_small_m(int N, int num_kb, bool fp8, int* bn_out, int* split_ou
 
 using namespace ne;
 
-// dtype: 0 = bf16 operands, 1 = fp8 e4m3 operands with block scales (sa/sb required).
+// dtype: 0 = bf16 operands, 1 = fp8 e4m3 operands with block scales (sa/sb required), 2 = the same with the promise that every
+// scale is a power of two: the tensor cores apply them (see kHw).
 // A [groups, M, K] (row stride lda, group stride a_gs), B [groups, N, K] (contiguous), D [groups, M, N] (row stride ldd).
 // masked_m: device int32 [groups] or null.  row_start: device int32 [groups] for the contiguous grouped layout (A and D
 // are then flat [M, *] matrices and masked_m holds the per-group row counts) or null.
@@ -760,11 +873,14 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
     if (comm->scatter_mode == 3 && (groups != 1 || comm->scatter_rpr < 1)) return 1009;
     if (comm->tail_counter && comm->tail_world > 16) return 1010;
   }
-  const bool fp8 = dtype == 1;
+  // Tensor-core scaling pays where tiles follow one another on an SM (prefill): it frees the CUDA cores but drains a whole
+  // accumulator at the end of every tile, and its scale fetch delays a CTA's first tile.  A GEMM of at most 128 rows per
+  // group is one wave of tiles bound by the weight stream, where the promotion path (which takes any scales) is faster.
+  const bool fp8 = dtype >= 1, hw = dtype == 2 && (row_start ? M / groups : M) > 128;
   if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % 16 != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
   if (fp8 && (K % 128 != 0 || !sa || !sb)) return 1002;
   if ((ldd * (out_fp32 == 1 ? 4 : (out_fp32 == 2 ? 1 : 2))) % 16 != 0) return 1003;
-  if (out_fp32 == 2 && (dtype == 1 || N % 32 != 0)) return 1006;      // e4m3 output: plain bf16 GEMMs, whole 32-column chunks
+  if (out_fp32 == 2 && (fp8 || N % 32 != 0)) return 1006;      // e4m3 output: plain bf16 GEMMs, whole 32-column chunks
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
   // pick the widest N tile that still yields about one tile per SM; fp8 promotion keeps BLOCK_N accumulators in registers
   int bn = block_n_hint;
@@ -776,7 +892,7 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
   if (bn == 0 && can_split) {
     plan_small_m(N, num_kb_host, fp8, &bn, &split);
   } else if (bn == 0) {
-    if (fp8 && !row_start && !masked_m) {
+    if (fp8 && !hw && !row_start && !masked_m) {
       // dense block-scaled GEMM: the serial K loop of a tile dominates at small M, so take the fewest waves of
       // tiles and, among equals, the narrowest tile (more SMs pulling weights at the same time)
       long long best_waves = 1ll << 60;
@@ -821,6 +937,13 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
   else memset(&a.comm, 0, sizeof(a.comm));
   long long tiles = (long long)groups * m_blocks * ((N + bn - 1) / bn);
   int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+  if (hw) {
+    switch (bn) {
+      case 128: return launch<128, true, false, true>(ta, tb, a, grid, stream);
+      case 64: return launch<64, true, false, true>(ta, tb, a, grid, stream);
+      default: return launch<32, true, false, true>(ta, tb, a, grid, stream);
+    }
+  }
   if (split > 1) {
     if (fp8) {
       switch (bn) {
@@ -867,6 +990,11 @@ extern "C" int ne_gemm_comm(const void* A, long long lda, long long a_gs, const 
                    comm, a_rows_total, stream);
 }
 extern "C" int ne_gemm_comm_size() { return (int)sizeof(GemmComm); }
+
+// 1: every fp8 activation quantiser of this library rounds its group scales up to powers of two (the form dtype 2 of
+// ne_gemm needs); 0: plain amax / 448.  Returns the previous setting.  Kernels captured in a CUDA graph keep the setting
+// they were captured with.
+extern "C" int ne_set_scale_pow2(int on) { int was = g_scale_pow2; g_scale_pow2 = on ? 1 : 0; return was; }
 
 // Turn the cluster split-K plan of small-M dense GEMMs on or off (on by default); returns the previous setting.
 extern "C" int ne_gemm_set_split_k(int on) { int was = g_split_k_enabled ? 1 : 0; g_split_k_enabled = on != 0; return was; }

@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(1024) moe_count_scan_kernel(const int* __restr
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx, const int* __restrict__ slot,
                                    const int* __restrict__ row_start, int* __restrict__ pos, __nv_bfloat16* __restrict__ a_bf16,
                                    uint8_t* __restrict__ a_q, float* __restrict__ a_s, int s_ld, int top_k, int H,
-                                   int expert_offset, int E_local, int max_rows) {
+                                   int expert_offset, int E_local, int max_rows, int pow2) {
   pdl_wait(); pdl_trigger();      // dependent launch: nothing above this line touches global memory
   extern __shared__ uint8_t s_raw[];
   uint32_t* s_q = reinterpret_cast<uint32_t*>(s_raw);                 // H bytes of e4m3
@@ -177,9 +177,9 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const __nv_bfloat16* _
       float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
       float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
       amax = fmaxf(warp_max(amax), 1e-10f);
-      const float is = 448.f / amax;
+      float is; const float sg = fp8_group_scale(amax, pow2, &is);
       s_q[g * 32 + lane] = pack_e4m3x4(a.x * is, a.y * is, b.x * is, b.y * is);
-      if (lane == 0) s_sc[g] = amax / 448.f;
+      if (lane == 0) s_sc[g] = sg;
     }
   }
   __syncthreads();
@@ -318,7 +318,7 @@ extern "C" int ne_moe_dispatch_local(const void* x, const int* idx, int* counts,
   cudaError_t e = launch_pdl(moe_count_scan_kernel, dim3(1), dim3(1024), 0, st, idx, counts, slot, row_start, n, expert_offset, E_local, align);
   if (e != cudaSuccess) return (int)e;
   return (int)launch_pdl(moe_scatter_kernel, dim3(T), dim3(256), (size_t)H + (H / 128) * 4, st, (const __nv_bfloat16*)x, idx, slot, row_start, pos,
-                         (__nv_bfloat16*)a_bf16, (uint8_t*)a_q, a_s, s_ld, top_k, H, expert_offset, E_local, max_rows);
+                         (__nv_bfloat16*)a_bf16, (uint8_t*)a_q, a_s, s_ld, top_k, H, expert_offset, E_local, max_rows, g_scale_pow2);
 }
 
 extern "C" int ne_moe_combine_local(const void* y, const int* pos, const float* w, const void* add_in, void* out, int T, int top_k, int H,

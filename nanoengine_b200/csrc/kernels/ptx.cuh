@@ -13,6 +13,8 @@
 #include <stdint.h>
 
 namespace ne {
+// host-side switch of the library: 1 = every fp8 activation quantiser rounds its group scales up to powers of two
+extern int g_scale_pow2;
 
 // ---- status buffer -----------------------------------------------------------------------------
 // word 0: first error code (0 = ok); 1: kernel id; 2: block; 3: detail a; 4: detail b.
@@ -170,6 +172,13 @@ __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t adesc, uint64_
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n"
                ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// e4m3 operands with UE8M0 block scales read from TMEM (one byte per row and per 32 elements of K; the byte of a 32-bit
+// scale-factor word is picked by the scale-factor id fields of the instruction descriptor).
+__device__ __forceinline__ void umma_f8_block_scaled(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                                                     uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
 // A operand from TMEM (e.g. softmax probabilities), B from smem.
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
@@ -195,6 +204,9 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
 __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -207,6 +219,11 @@ enum UmmaFmt : uint32_t { FMT_F16 = 0, FMT_BF16 = 1, FMT_E4M3 = 0, FMT_E5M2 = 1 
 // 32-bit instruction descriptor: fp32 accumulate, dense, no negate.  a_mn / b_mn = 1 selects an MN-major operand.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t M, uint32_t N, uint32_t a_mn = 0, uint32_t b_mn = 0) {
   return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+// Descriptor of the block-scaled kinds: no accumulator-format field (always fp32); bit 23 = UE8M0 scale factors; the
+// scale-factor ids (which byte of the 32-bit scale word) sit at bits [4,6) for B and [29,31) for A.
+__host__ __device__ constexpr uint32_t make_idesc_block_scaled(uint32_t a_fmt, uint32_t b_fmt, uint32_t M, uint32_t N) {
+  return (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24);
 }
 enum SwizzleMode : uint64_t { SW_NONE = 0, SW_128B = 2, SW_64B = 4, SW_32B = 6 };
 // 64-bit shared-memory matrix descriptor (Blackwell version field = 1).  Offsets are given in bytes.
@@ -249,6 +266,15 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
   uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
   return lo | (hi << 16);
+}
+// Scale of a 128-element group whose absolute maximum is amax: amax / 448, or (pow2) the next power of two at or above
+// it, the form the tensor cores' own block scaling takes.  *inv receives the factor that maps the group onto e4m3.
+__device__ __forceinline__ float fp8_group_scale(float amax, int pow2, float* inv) {
+  float s = amax / 448.f;
+  if (!pow2) { *inv = 448.f / amax; return s; }
+  const uint32_t b = (__float_as_uint(s) + 0x7fffffu) & 0x7f800000u;
+  *inv = __uint_as_float(0x7f000000u - b);
+  return __uint_as_float(b);
 }
 __device__ __forceinline__ float e4m3_to_float(uint8_t v) {
   __half_raw h = __nv_cvt_fp8_to_halfraw(v, __NV_E4M3);

@@ -98,6 +98,9 @@ class ModelConfig:
     # quantisation of linear / expert weights: None (use dtype) or "fp8" (e4m3, 128x128 block scales)
     quant: Optional[str] = None
     weight_block_size: List[int] = field(default_factory=lambda: [128, 128])
+    # "ue8m0": the checkpoint's block scales are powers of two and activations are quantised the same way (reference
+    # models/quant_config.py:39-44); None: plain fp32 scales
+    scale_fmt: Optional[str] = None
     eos_token_id: Any = None
     bos_token_id: Any = None
 
@@ -212,6 +215,8 @@ class ModelConfig:
         if q and q.get("quant_method") == "fp8":
             d["quant"] = "fp8"
             d["weight_block_size"] = list(q.get("weight_block_size", [128, 128]))
+            if q.get("scale_fmt"):
+                d["scale_fmt"] = q["scale_fmt"]
         arch = d.get("architecture", "")
         la = d.pop("linear_attn_config", None)
         if isinstance(la, dict):                          # Kimi delta attention block of GLM5-next / Kimi-K3
@@ -286,7 +291,10 @@ class ModelConfig:
         d["architectures"] = [d.pop("architecture")]
         if d.pop("quant") == "fp8":
             d["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": d["weight_block_size"]}
+            if d.get("scale_fmt"):
+                d["quantization_config"]["scale_fmt"] = d["scale_fmt"]
         d.pop("weight_block_size")
+        d.pop("scale_fmt", None)
         return d
 
 

@@ -55,6 +55,7 @@ class QLinear(nn.Module):
         """Accepts a high-precision weight (quantised here if needed) or an fp8 weight with its scales."""
         if self.quant == "fp8":
             if w.dtype == torch.float8_e4m3fn:
+                w, scale_inv = ref.fp8_block_for_format(w.to(self.weight.device), scale_inv.to(self.weight.device))
                 self.weight.copy_(w)
                 self.weight_scale_inv.copy_(scale_inv)
             else:
@@ -277,6 +278,8 @@ class RoutedExperts(nn.Module):
         if self.quant == "fp8":
             if w.dtype != torch.float8_e4m3fn:
                 w, scale_inv = ref.quant_fp8_block(w.to(tgt.device))
+            else:
+                w, scale_inv = ref.fp8_block_for_format(w.to(tgt.device), scale_inv.to(tgt.device))
             tgt[local_idx, rows].copy_(w)
             srows = slice(rows.start // 128, _ceil_div(rows.stop, 128))
             tscale[local_idx, srows].copy_(scale_inv)

@@ -75,15 +75,37 @@ def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: 
 
 
 # ---- fp8 block quantisation ----------------------------------------------------------------------
-def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Per-row, per-128-column groups: q = x / s (e4m3), s = amax/448 (optionally rounded up to 2^k)."""
+# Process-wide scale format of the fp8 block quantisers (reference models/quant_config.py:39-44, `scale_fmt`): "ue8m0" rounds
+# every group scale up to a power of two, the form the Blackwell tensor cores apply themselves.
+SCALE_POW2 = [False]
+
+
+def set_scale_format(fmt: Optional[str]) -> None:
+    assert fmt in (None, "fp32", "ue8m0"), fmt
+    SCALE_POW2[0] = fmt == "ue8m0"
+
+
+def scale_format() -> str:
+    return "ue8m0" if SCALE_POW2[0] else "fp32"
+
+
+def _ceil_pow2(s: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= s, computed on the bits (exact, and the same on every device)."""
+    b = s.float().contiguous().view(torch.int32)
+    return ((b + 0x7FFFFF) & 0x7F800000).view(torch.float32)
+
+
+def quant_fp8_1x128(x: torch.Tensor, ue8m0: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row, per-128-column groups: q = x / s (e4m3), s = amax/448 (rounded up to 2^k under the "ue8m0" scale format)."""
+    if ue8m0 is None:
+        ue8m0 = SCALE_POW2[0]
     T, K = x.shape
     assert K % 128 == 0
     g = x.float().view(T, K // 128, 128)
     amax = g.abs().amax(-1).clamp_min(1e-10)
     s = amax / FP8_MAX
     if ue8m0:
-        s = torch.exp2(torch.ceil(torch.log2(s)))
+        s = _ceil_pow2(s)
     q = (g / s.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(FP8).view(T, K)
     return q, s
 
@@ -93,8 +115,10 @@ def dequant_fp8_1x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     return (q.float().view(T, K // 128, 128) * s.unsqueeze(-1)).view(T, K)
 
 
-def quant_fp8_block(w: torch.Tensor, block: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+def quant_fp8_block(w: torch.Tensor, block: int = 128, ue8m0: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """128x128 weight blocks: returns (w_fp8, weight_scale_inv) with w ~= w_fp8 * scale_inv."""
+    if ue8m0 is None:
+        ue8m0 = SCALE_POW2[0]
     *lead, N, K = w.shape
     pn, pk = (-N) % block, (-K) % block
     wf = F.pad(w.float(), (0, pk, 0, pn))
@@ -102,9 +126,22 @@ def quant_fp8_block(w: torch.Tensor, block: int = 128) -> Tuple[torch.Tensor, to
     g = wf.view(*lead, Np // block, block, Kp // block, block)
     amax = g.abs().amax(dim=(-3, -1)).clamp_min(1e-10)
     s = amax / FP8_MAX
+    if ue8m0:
+        s = _ceil_pow2(s)
     q = (g / s.unsqueeze(-1).unsqueeze(-3)).clamp(-FP8_MAX, FP8_MAX).to(FP8)
     q = q.view(*lead, Np, Kp)[..., :N, :K].contiguous()
     return q, s
+
+
+def fp8_block_for_format(q: torch.Tensor, s: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """A checkpoint's fp8 weight and block scales in the process's scale format: unchanged unless the format is "ue8m0" and
+    some scale is not a power of two, in which case the weight is dequantised and quantised again with rounded-up scales."""
+    if not SCALE_POW2[0]:
+        return q, s
+    sf = s.float()
+    if bool(((sf.contiguous().view(torch.int32) & 0x7FFFFF) == 0).all()):
+        return q, sf
+    return quant_fp8_block(dequant_fp8_block(q, sf), ue8m0=True)
 
 
 def dequant_fp8_block(q: torch.Tensor, s: torch.Tensor, block: int = 128) -> torch.Tensor:

@@ -66,10 +66,32 @@ def clear_kernel_status():
     _ck(lib().ne_clear_status(), "ne_clear_status")
 
 
+# ---- scale format ----------------------------------------------------------------------------------
+def set_scale_format(fmt: Optional[str]) -> None:
+    """"ue8m0": every fp8 quantiser of the library rounds its group scales up to powers of two and the block-scaled GEMMs
+    hand them to the tensor cores (tcgen05.mma.kind::mxf8f6f4.block_scale); "fp32" (or None): plain amax / 448 scales, applied
+    on the CUDA cores between K blocks.  Weights must have been quantised (or re-quantised: `fp8_block_for_format`) under the
+    same setting.  CUDA graphs keep the setting they were captured with."""
+    ref.set_scale_format(fmt)
+    lib().ne_set_scale_pow2(_c.c_int(1 if ref.SCALE_POW2[0] else 0))
+
+
+scale_format = ref.scale_format
+
+
+def _fp8_dtype(fp8) -> int:
+    return (2 if ref.SCALE_POW2[0] else 1) if fp8 else 0
+
+
+TC_SCALED_GEMMS = [0]       # GEMM launches whose block scales the tensor cores applied (more than 128 rows per group, "ue8m0" format)
+
+
 # ---- GEMM ----------------------------------------------------------------------------------------
 def _gemm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, row_start, fp8, sa, sa_ld, sa_gs, sb, out_fp32, bn=0, row_dst=None):
+    if fp8 and ref.SCALE_POW2[0] and (M // groups if row_start is not None else M) > 128:
+        TC_SCALED_GEMMS[0] += 1
     rc = lib().ne_gemm(_p(A), _c.c_longlong(lda), _c.c_longlong(a_gs), _p(B), _p(D), _c.c_longlong(ldd), _c.c_longlong(d_gs),
-                       _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), _p(masked_m), _p(row_start), _c.c_int(1 if fp8 else 0),
+                       _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), _p(masked_m), _p(row_start), _c.c_int(_fp8_dtype(fp8)),
                        _p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(int(out_fp32)), _c.c_int(bn), _p(row_dst), _st())     # output: 0 bf16, 1 fp32, 2 e4m3
     _ck(rc, "ne_gemm")
 
@@ -93,16 +115,16 @@ def _gemm_comm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, fp8, sa
         l._comm_checked = True
     mm = _c.c_void_p(masked_m) if isinstance(masked_m, int) else _p(masked_m)
     rc = l.ne_gemm_comm(_p(A) if not isinstance(A, int) else _c.c_void_p(A), _c.c_longlong(lda), _c.c_longlong(a_gs), _p(B), _p(D), _c.c_longlong(ldd),
-                        _c.c_longlong(d_gs), _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), mm, _p(None), _c.c_int(1 if fp8 else 0),
+                        _c.c_longlong(d_gs), _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), mm, _p(None), _c.c_int(_fp8_dtype(fp8)),
                         _p(sa) if not isinstance(sa, int) else _c.c_void_p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(0), _c.c_int(bn),
                         _c.byref(comm), _c.c_int(a_rows_total), _st())
     _ck(rc, "ne_gemm_comm")
 
 
-def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False):
+def quant_fp8_1x128(x: torch.Tensor, ue8m0: Optional[bool] = None):
     """bf16 [T, K] -> (e4m3 [T, K], scales [T, K/128]).  The kernel writes scales column-major ([K/128, T]);
-    the returned view presents them in the reference's [T, K/128] orientation."""
-    assert not ue8m0, "UE8M0 scales are not produced by the CUDA path"
+    the returned view presents them in the reference's [T, K/128] orientation.  The scales follow the process's scale format."""
+    assert ue8m0 is None or bool(ue8m0) == ref.SCALE_POW2[0], "the CUDA quantisers follow set_scale_format()"
     T, K = x.shape
     x = x if x.stride(-1) == 1 else x.contiguous()
     q = torch.empty(T, K, dtype=FP8, device=x.device)
@@ -541,8 +563,11 @@ def dequant_fp8_block(q, s, block=128):
     return ref.dequant_fp8_block(q, s, block)
 
 
-def quant_fp8_block(w, block=128):
-    return ref.quant_fp8_block(w, block)
+def quant_fp8_block(w, block=128, ue8m0=None):
+    return ref.quant_fp8_block(w, block, ue8m0)
+
+
+fp8_block_for_format = ref.fp8_block_for_format
 
 
 def merge_attention_states(o1, lse1, o2, lse2):

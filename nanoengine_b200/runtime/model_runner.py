@@ -103,6 +103,10 @@ class ModelRunner:
 
     def init_model(self) -> None:
         cls = get_model_class(self.mc.architecture)
+        if self.mc.quant == "fp8":
+            # before any weight is quantised or loaded: the quantisers and the block-scaled GEMMs follow this setting
+            from .. import ops
+            (ops._get_sm100() if self.device.type == "cuda" else ops.reference).set_scale_format(self.config.resolved_scale_format())
         from ..parallel.ep import set_routing_options
         set_routing_options(balance_ranks=self.dist.ep_size if self.config.dummy_eplb else 0)
         from ..parallel import eplb
