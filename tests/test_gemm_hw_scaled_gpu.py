@@ -91,7 +91,9 @@ def test_gemm_fp8_hw_scaled_every_tile_width(k, bn):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 2112, 7168), (5, 4096, 7168), (77, 7168, 2048), (16, 520, 1024)])
-def test_gemm_fp8_hw_scaled_split_k(k, M, N, K):
+def test_small_m_gemms_keep_the_promotion_path_and_its_split_k(k, M, N, K):
+    """At most 128 rows: one wave of tiles bound by the weight stream, where the library keeps the CUDA-core promotion kernel (it
+    takes any scales, powers of two included) and its split-K form."""
     x, w = _ragged_magnitudes(M, K, N, 7)
     wq, ws = ref.quant_fp8_block(w)
     want = ref.linear(x, wq, ws)
