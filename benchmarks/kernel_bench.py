@@ -348,6 +348,7 @@ def build_cases(args):
         "qkv_a_prefill": lambda: case_dense_fp8(args.prefill_tokens, 2112, 7168),
         "o_proj_prefill": lambda: case_dense_fp8(args.prefill_tokens, 7168, 16384),
         "moe_gemm1_prefill": lambda: case_moe_gemm(E, args.prefill_tokens * 8 // 32, 4096, 7168),
+        "moe_gemm2_prefill": lambda: case_moe_gemm(E, args.prefill_tokens * 8 // 32, 7168, 2048),
         "bf16_square": lambda: case_dense_bf16(8192, 8192, 8192),
     }
     return c

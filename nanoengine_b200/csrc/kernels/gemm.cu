@@ -36,7 +36,7 @@ constexpr int kKBytes = 128;            // bytes of K per K block row: one 128B 
 // tensor maps carry the 128-byte K chunk index as their outermost dimension, so a box {128 B, rows, ..., kG} lands as kG
 // consecutive swizzled [rows x 128 B] tiles.  An SM retires roughly one TMA instruction per 0.2 us whatever its size, so
 // two instructions per K block cap a 128-wide tile well below both the tensor pipe and HBM; two per kG blocks do not.
-template <int BLOCK_N> struct KGroup { static constexpr int value = BLOCK_N >= 256 ? 1 : 2; };   // the 256-wide tile keeps 4 single-block stages
+template <int BLOCK_N> struct KGroup { static constexpr int value = BLOCK_N >= 192 ? 1 : 2; };   // the wide tiles keep 4 single-block stages
 constexpr int kGemmThreads = 192;
 constexpr int kKernelGemm = 1;
 
@@ -215,8 +215,11 @@ template <int BLOCK_N, bool kBlockScaled, bool kHw = false> struct EpiCfg {
 //    number per tile; it is folded into A's byte (exponents add) and B's scale factors are the constant 1.
 // Four extra warps, one per TMEM lane quarter, compute the bytes from the fp32 scale arrays and store them into TMEM
 // (tcgen05.st) a few chunks ahead of the MMA issuer.
-constexpr int kSfBufs = 8;          // TMEM ring of scale-factor chunks
-constexpr int kSfGroup = 4;         // chunks whose scales are fetched together
+// A tile wider than a weight block (BLOCK_N = 224: two accumulators and the scale factors just fit the 512 TMEM columns, and
+// 7168 = 32 x 224) cannot fold: B gets its own scale bytes, one per tile column and K block (column c + 32 g of the tile: lane
+// c, word g, byte = K block of the chunk), written next to A's in every ring entry.  The wide tile moves a fifth fewer operand
+// bytes per FLOP through the SM's fill path, which is what bounds these GEMMs.
+constexpr int kSfBufsMax = 8;
 
 // kSplit: split-K across a thread-block cluster.  The CTAs of a cluster work on the same output tile, each over its own
 // slice of K; every CTA parks its fp32 partial tile in its shared memory and, after a cluster barrier, CTA r adds up rows
@@ -237,10 +240,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   // TMEM accumulator ring: block-scaled GEMMs hand one accumulator per K block to the epilogue, so they use the
   // deepest ring 512 columns allow (up to 4); plain GEMMs hand over one per tile and need two.
   constexpr int kAcc = kBlockScaled ? ((512 / BLOCK_N) > 4 ? 4 : (512 / BLOCK_N)) : 2;
-  static_assert(!kHw || (kFP8 && !kBlockScaled && BLOCK_N <= 128), "hardware block scaling: fp8 operands, one accumulator per tile");
-  // kHw: the scale factors follow the accumulators: 4 columns of B's constant, then kSfBufs buffers of 4 columns for A
-  constexpr uint32_t kSfbCol = kAcc * BLOCK_N, kSfaCol = kSfbCol + 4;
-  constexpr uint32_t kColsUsed = kAcc * BLOCK_N + (kHw ? 4 + 4 * kSfBufs : 0);
+  static_assert(!kHw || (kFP8 && !kBlockScaled && BLOCK_N <= 224), "hardware block scaling: fp8 operands, one accumulator per tile");
+  // kHw: the scale factors follow the accumulators.  Folded form: 4 columns of B's constant, then a ring of 4-column entries
+  // for A.  Wide form: a ring of 12-column entries, 4 for A and 8 for B.
+  constexpr bool kFold = BLOCK_N <= 128;
+  constexpr int kSfBufs = kFold ? 8 : 5;               // ring entries (one chunk of 4 K blocks each)
+  constexpr int kSfGroup = kFold ? 4 : 2;              // chunks whose scales are fetched together
+  constexpr uint32_t kSfEntry = kFold ? 4 : 12;
+  constexpr uint32_t kSfbCol = kAcc * BLOCK_N, kSfaCol = kSfbCol + (kFold ? 4 : 0);
+  constexpr uint32_t kColsUsed = kAcc * BLOCK_N + (kHw ? (kFold ? 4 : 0) + kSfEntry * kSfBufs : 0);
+  static_assert(kColsUsed <= 512 && kSfBufs <= kSfBufsMax, "TMEM holds 512 columns");
   constexpr uint32_t kTmemCols = kColsUsed <= 32 ? 32 : (kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512)));
   constexpr uint32_t kIdesc = kHw ? make_idesc_block_scaled(FMT_E4M3, FMT_E4M3, kBlockM, BLOCK_N)
                                   : make_idesc(kFP8 ? FMT_E4M3 : FMT_BF16, kFP8 ? FMT_E4M3 : FMT_BF16, kBlockM, BLOCK_N);
@@ -257,7 +266,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
   const uint32_t tfull0 = smem_u32(bars + 2 * kStages), tempty0 = smem_u32(bars + 2 * kStages + kAcc);
   const uint32_t smem_base = smem_u32(smem);
-  __shared__ uint64_t s_sfbar[2 * kSfBufs];            // kHw: scale-factor buffer filled (4 warps arrive) / drained (MMAs retired)
+  __shared__ uint64_t s_sfbar[2 * kSfBufsMax];            // kHw: scale-factor buffer filled (4 warps arrive) / drained (MMAs retired)
   const uint32_t sffull0 = smem_u32(s_sfbar), sfempty0 = smem_u32(s_sfbar + kSfBufs);
 
   const int warp = threadIdx.x >> 5;
@@ -311,7 +320,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int* rs_tab = args.row_start ? (cache_tables ? s_rs : args.row_start) : nullptr;
   // first tile of every ragged group: counts by all threads, then one warp turns them into running sums
   __shared__ int s_base[kSchedCache + 1];
-  static_assert((3 * kSchedCache + 4) * (int)sizeof(int) + 16 * kSfBufs + 64 <= S::kStaticTables, "the stage budget must leave room for the static tables");
+  static_assert((3 * kSchedCache + 4) * (int)sizeof(int) + 16 * kSfBufsMax + 64 <= S::kStaticTables, "the stage budget must leave room for the static tables");
   const bool ragged = args.masked_m || args.row_start;
   const int* base_tab = (ragged && cache_tables) ? s_base : nullptr;
   if (base_tab) {
@@ -445,8 +454,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int k = 0; k < kMmasPerStage; k++) {
               uint32_t acc = kBlockScaled ? (k != 0) : ((kb | k) != 0);
               // advancing 32 bytes along K inside the 128B swizzle atom = +2 in the descriptor's 16-byte address units
-              if (kHw) umma_f8_block_scaled(d, adesc + 2 * k, bdesc + 2 * k, kIdesc | ((uint32_t)(kb & 3) << 29), acc,
-                                            tmem_base + kSfaCol + 4 * sfb, tmem_base + kSfbCol);
+              if (kHw) umma_f8_block_scaled(d, adesc + 2 * k, bdesc + 2 * k,
+                                            kIdesc | ((uint32_t)(kb & 3) << 29) | (kFold ? 0u : (uint32_t)(kb & 3) << 4), acc,
+                                            tmem_base + kSfaCol + kSfEntry * sfb, tmem_base + (kFold ? kSfbCol : kSfaCol + kSfEntry * sfb + 4));
               else if (kFP8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
               else umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
             }
@@ -472,24 +482,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int sfb = 0; uint32_t sfphase = 0; int grp, mb, nb;
     bool ok = true, first = true;
     for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
-      if (first) {
+      if (first && kFold) {
         // B's scale factors: the constant 1 (UE8M0 byte 127), written once
         const uint32_t ones[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
         tmem_st_32x32b_x4(tmem_base + lane_addr + kSfbCol, ones);
-        first = false;
       }
+      first = false;
       // rows lane + 32 g of the tile; rows past the group's end read the tile's first row (their results are never stored)
       const int rows_here = sched.rows(grp) - mb * kBlockM;
       const float* sa = args.sa + (long long)grp * args.sa_group_stride + sched.row0(grp) + mb * kBlockM + (long long)kb_begin * args.sa_ld;
-      const float* sb = args.sb + (long long)grp * args.sb_group_stride + (long long)(nb * BLOCK_N / 128) * total_kb + kb_begin;
-      int roff[4];
+      // weight blocks under the tile: one when folded, up to three under a wide tile
+      constexpr int kNB = kFold ? 1 : 3;
+      const int nblk = (args.N + 127) / 128, b0 = nb * BLOCK_N / 128;
+      const float* sb[kNB];
+#pragma unroll
+      for (int i = 0; i < kNB; i++)
+        sb[i] = args.sb + (long long)grp * args.sb_group_stride + (long long)min(b0 + i, nblk - 1) * total_kb + kb_begin;
+      int roff[4], bsel[8];
 #pragma unroll
       for (int g = 0; g < 4; g++) roff[g] = lane + 32 * g < rows_here ? lane + 32 * g : 0;
-      // The scale arrays are read kSfGroup chunks (16 K blocks) at a time, and the loads of the next batch are in flight while
-      // this one is converted and stored: a single chunk per round trip to L2 (about a microsecond) would feed the tensor
-      // pipe at half the rate it consumes them.
+#pragma unroll
+      for (int g = 0; g < 8; g++) bsel[g] = kFold ? 0 : min((nb * BLOCK_N + lane + 32 * g) / 128 - b0, kNB - 1);
+      // The scale arrays are read kSfGroup chunks at a time, and the loads of the next batch are in flight while this one is
+      // converted and stored: a single chunk per round trip to L2 (about a microsecond) would feed the tensor pipe at half
+      // the rate it consumes them.
       const int n_chunks = (num_kb + 3) >> 2;
-      uint32_t ra[kSfGroup][4][4], rb[kSfGroup][4];         // raw bits: [chunk][K block][row group], [chunk][K block]
+      uint32_t ra[kSfGroup][4][4], rb[kSfGroup][4][kNB];    // raw bits: [chunk][K block][row group], [chunk][K block][weight block]
       auto fetch = [&](int c0) {
 #pragma unroll
         for (int u = 0; u < kSfGroup; u++) {
@@ -497,7 +515,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int j = 0; j < 4; j++) {
             const int kb = (c0 + u) * 4 + j;
             const bool in = kb < num_kb;
-            rb[u][j] = in ? __float_as_uint(__ldg(sb + kb)) : 0u;
+#pragma unroll
+            for (int i = 0; i < kNB; i++) rb[u][j][i] = in ? __float_as_uint(__ldg(sb[i] + kb)) : 0u;
 #pragma unroll
             for (int g = 0; g < 4; g++) ra[u][j][g] = in ? __float_as_uint(__ldg(sa + (long long)kb * args.sa_ld + roff[g])) : 0u;
           }
@@ -505,7 +524,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       };
       fetch(0);
       for (int c0 = 0; c0 < n_chunks && ok; c0 += kSfGroup) {
-        uint32_t w[kSfGroup][4];
+        uint32_t w[kSfGroup][4], wb[kSfGroup][8];
 #pragma unroll
         for (int u = 0; u < kSfGroup; u++) {
 #pragma unroll
@@ -513,10 +532,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t word = 0u;
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-              const int e = (int)((ra[u][j][g] >> 23) & 0xffu) + (int)((rb[u][j] >> 23) & 0xffu) - 127;
+              const int e = (int)((ra[u][j][g] >> 23) & 0xffu) + (kFold ? (int)((rb[u][j][0] >> 23) & 0xffu) - 127 : 0);
               word |= (uint32_t)min(max(e, 0), 254) << (8 * j);
             }
             w[u][g] = word;
+          }
+          if (!kFold) {
+#pragma unroll
+            for (int g = 0; g < 8; g++) {
+              uint32_t word = 0u;
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                const uint32_t bits = bsel[g] == 0 ? rb[u][j][0] : (bsel[g] == 1 ? rb[u][j][kNB > 1 ? 1 : 0] : rb[u][j][kNB - 1]);
+                word |= min((bits >> 23) & 0xffu, 254u) << (8 * j);
+              }
+              wb[u][g] = word;
+            }
           }
         }
         if (c0 + kSfGroup < n_chunks) fetch(c0 + kSfGroup);
@@ -525,7 +556,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (c0 + u < n_chunks && ok) {
             if (mbar_wait(sfempty0 + 8 * sfb, sfphase ^ 1, abort_flag, kKernelGemm, 510 + sfb)) {
               tc_fence_after();
-              tmem_st_32x32b_x4(tmem_base + lane_addr + kSfaCol + 4 * sfb, w[u]);
+              tmem_st_32x32b_x4(tmem_base + lane_addr + kSfaCol + kSfEntry * sfb, w[u]);
+              if (!kFold) tmem_st_32x32b_x8(tmem_base + lane_addr + kSfaCol + kSfEntry * sfb + 4, wb[u]);
               tc_wait_st();
               tc_fence_before();
               __syncwarp();
@@ -913,8 +945,16 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
       if (!fp8 && bn == 256 && N % 256 != 0 && N < 2048) bn = 128;
     }
   }
-  if (fp8 && bn > 128) bn = 128;
-  const int kg = bn >= 256 ? 1 : 2;      // KGroup<bn>::value
+  if (hw && bn == 0) bn = 128;
+  if (hw && !block_n_hint) {
+    // Wide tile where it lowers the operand bytes an SM pulls through its fill path over the whole GEMM: waves of tiles times
+    // the bytes of one K block of a tile.
+    const long long gm = row_start ? m_blocks : (long long)groups * m_blocks;
+    auto cost = [&](int w) { const long long t = gm * ((N + w - 1) / w); return ((t + num_sms() - 1) / num_sms()) * (long long)(kBlockM + w); };
+    if (N >= 224 && cost(224) < cost(bn)) bn = 224;
+  }
+  if (fp8 && bn > 128 && !(hw && bn == 224)) bn = 128;
+  const int kg = bn >= 192 ? 1 : 2;      // KGroup<bn>::value
   CUtensorMap ta[3], tb;       // activation maps with 128-, 64- and 32-row boxes
   if (row_start || groups == 1) a_gs = (long long)(a_rows_total > 0 ? a_rows_total : M) * lda;
   int rc = 0;
@@ -939,6 +979,7 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
   int grid = (int)(tiles < num_sms() ? tiles : num_sms());
   if (hw) {
     switch (bn) {
+      case 224: return launch<224, true, false, true>(ta, tb, a, grid, stream);
       case 128: return launch<128, true, false, true>(ta, tb, a, grid, stream);
       case 64: return launch<64, true, false, true>(ta, tb, a, grid, stream);
       default: return launch<32, true, false, true>(ta, tb, a, grid, stream);

@@ -63,7 +63,9 @@ def test_quantisers_round_scales_up_to_powers_of_two(k):
 @pytest.mark.parametrize("M,N,K", [(1, 256, 128), (33, 2112, 7168), (128, 4096, 7168), (500, 7168, 2048), (2048, 2048, 2048),
                                    (300, 384, 640),        # five K blocks: the last scale chunk is partial
                                    (129, 1536, 4096),      # 8 chunks per tile: the scale-factor ring wraps twice
-                                   (70, 192, 1024)])       # N = 128 + 64: the last tile holds half a weight block
+                                   (70, 192, 1024),        # N = 128 + 64: the last tile holds half a weight block
+                                   (4096, 4096, 1024),     # the wide (224-column) tile is chosen; 4096 = 18 x 224 + 64
+                                   (1000, 7168, 640)])     # 7168 = 32 x 224
 def test_gemm_fp8_hw_scaled(k, M, N, K):
     x, w = _ragged_magnitudes(M, K, N, 2)
     wq, ws = ref.quant_fp8_block(w)
@@ -77,7 +79,7 @@ def test_gemm_fp8_hw_scaled(k, M, N, K):
     assert _rel(got, x.float() @ w.t()) < 7e-2
 
 
-@pytest.mark.parametrize("bn", [32, 64, 128])
+@pytest.mark.parametrize("bn", [32, 64, 128, 224])      # 224: tiles straddle up to three weight blocks, B's scale factors are per column
 def test_gemm_fp8_hw_scaled_every_tile_width(k, bn):
     M, N, K = 200, 768, 1536
     x, w = _ragged_magnitudes(M, K, N, 5)
