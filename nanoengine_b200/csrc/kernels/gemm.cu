@@ -908,7 +908,8 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
   // Tensor-core scaling pays where tiles follow one another on an SM (prefill): it frees the CUDA cores but drains a whole
   // accumulator at the end of every tile, and its scale fetch delays a CTA's first tile.  A GEMM of at most 128 rows per
   // group is one wave of tiles bound by the weight stream, where the promotion path (which takes any scales) is faster.
-  const bool fp8 = dtype >= 1, hw = dtype == 2 && (row_start ? M / groups : M) > 128;
+  // (Not with a gated A operand: the scale warps would read the scales of rows whose source rank has not delivered them yet.)
+  const bool fp8 = dtype >= 1, hw = dtype == 2 && (row_start ? M / groups : M) > 128 && !(comm && comm->gate_flags);
   if (N % 8 != 0 || (K * (fp8 ? 1 : 2)) % 16 != 0 || (lda * (fp8 ? 1 : 2)) % 16 != 0) return 1001;
   if (fp8 && (K % 128 != 0 || !sa || !sb)) return 1002;
   if ((ldd * (out_fp32 == 1 ? 4 : (out_fp32 == 2 ? 1 : 2))) % 16 != 0) return 1003;

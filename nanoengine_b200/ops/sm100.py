@@ -107,15 +107,17 @@ class GemmComm(_c.Structure):
                 ("tail_clear", _c.c_void_p), ("tail_clear_n", _c.c_int), ("tail_advance", _c.c_void_p)]
 
 
-def _gemm_comm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, fp8, sa, sa_ld, sa_gs, sb, comm: GemmComm, a_rows_total=0, bn=0):
-    """`_gemm` with a fused collective; `masked_m` may be a raw device address (an int) inside a symmetric region."""
+def _gemm_comm(A, lda, a_gs, B, D, ldd, d_gs, M, N, K, groups, masked_m, fp8, sa, sa_ld, sa_gs, sb, comm: GemmComm, a_rows_total=0, bn=0,
+               few_rows=False):
+    """`_gemm` with a fused collective; `masked_m` may be a raw device address (an int) inside a symmetric region.  `few_rows`:
+    the groups hold far fewer rows than `M` allows (a decode step through prefill-sized buffers): keep the CUDA-core scaling."""
     l = lib()
     if not getattr(l, "_comm_checked", False):
         assert l.ne_gemm_comm_size() == _c.sizeof(GemmComm), "GemmComm mismatch between Python and the kernel library"
         l._comm_checked = True
     mm = _c.c_void_p(masked_m) if isinstance(masked_m, int) else _p(masked_m)
     rc = l.ne_gemm_comm(_p(A) if not isinstance(A, int) else _c.c_void_p(A), _c.c_longlong(lda), _c.c_longlong(a_gs), _p(B), _p(D), _c.c_longlong(ldd),
-                        _c.c_longlong(d_gs), _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), mm, _p(None), _c.c_int(_fp8_dtype(fp8)),
+                        _c.c_longlong(d_gs), _c.c_int(M), _c.c_int(N), _c.c_int(K), _c.c_int(groups), mm, _p(None), _c.c_int(1 if (fp8 and few_rows) else _fp8_dtype(fp8)),
                         _p(sa) if not isinstance(sa, int) else _c.c_void_p(sa), _c.c_int(sa_ld), _c.c_longlong(sa_gs), _p(sb), _c.c_int(0), _c.c_int(bn),
                         _c.byref(comm), _c.c_int(a_rows_total), _st())
     _ck(rc, "ne_gemm_comm")

@@ -8,7 +8,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, fp8, q):
+def _worker(rank, world, port, fp8, q, fmt=None):
     try:
         import torch.distributed as dist
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -20,13 +20,16 @@ def _worker(rank, world, port, fp8, q):
         from nanoengine_b200.parallel.ep import ep_moe_allgather
         from nanoengine_b200.parallel.fused_moe import FusedEP
         d = init_dist_context(ParallelSpec(attention_dp=world, ffn_ep=world), rank, world, f"cuda:{rank}")
+        sm100.set_scale_format(fmt)          # before the weights are quantised
         H, I, E, K = 1024, 256, 16, 4
         ex = RoutedExperts(E, H, I, torch.bfloat16, f"cuda:{rank}", "fp8" if fp8 else None)
         g = torch.Generator(device=f"cuda:{rank}").manual_seed(100 + rank)
         ex.init_random(g, std=0.05)
-        be = FusedEP(d.group("ffn_ep"), d.ep_rank, world, E, H, I, K, max_tokens=64, fp8=fp8)
+        be = FusedEP(d.group("ffn_ep"), d.ep_rank, world, E, H, I, K, max_tokens=640 if fmt else 64, fp8=fp8)
         worst = 0.0
-        for it, T in enumerate([37 if rank == 0 else 5, 1, 64]):
+        # 64 tokens x top-4 x 2 ranks over 16 experts = 32 rows per expert (the CUDA-core scaling); 600 tokens = 300 rows per expert
+        # (under "ue8m0": the tensor-core-scaled kernel behind the wait prologue and in front of the scatter epilogue)
+        for it, T in enumerate([37 if rank == 0 else 5, 1, 64] + ([600] if fmt else [])):
             x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
             logits = torch.randn(T, E, device="cuda", generator=g)
             idx, w = ref.moe_route(logits, None, K, 1, 1, True, 1.0, "softmax")
@@ -60,8 +63,10 @@ def _worker(rank, world, port, fp8, q):
         q.put((rank, f"{e}\n{traceback.format_exc()}", -1))
 
 
-@pytest.mark.parametrize("fp8", [True, False])
+@pytest.mark.parametrize("fp8", [True, False, "ue8m0"])
 def test_fused_ep_matches_allgather_oracle(fp8):
+    fmt = "ue8m0" if fp8 == "ue8m0" else None
+    fp8 = bool(fp8)
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import socket
@@ -70,7 +75,7 @@ def test_fused_ep_matches_allgather_oracle(fp8):
         s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    ps = [ctx.Process(target=_worker, args=(r, 2, port, fp8, q), daemon=True) for r in range(2)]
+    ps = [ctx.Process(target=_worker, args=(r, 2, port, fp8, q, fmt), daemon=True) for r in range(2)]
     for p in ps:
         p.start()
     res = [q.get(timeout=300) for _ in ps]
