@@ -36,7 +36,7 @@ constexpr int kKBytes = 128;            // bytes of K per K block row: one 128B 
 // tensor maps carry the 128-byte K chunk index as their outermost dimension, so a box {128 B, rows, ..., kG} lands as kG
 // consecutive swizzled [rows x 128 B] tiles.  An SM retires roughly one TMA instruction per 0.2 us whatever its size, so
 // two instructions per K block cap a 128-wide tile well below both the tensor pipe and HBM; two per kG blocks do not.
-template <int BLOCK_N> struct KGroup { static constexpr int value = BLOCK_N >= 192 ? 1 : 2; };   // the wide tiles keep 4 single-block stages
+template <int BLOCK_N, bool kFp4 = false> struct KGroup { static constexpr int value = (BLOCK_N >= 192 || kFp4) ? 1 : 2; };   // the wide tiles keep 4 single-block stages
 constexpr int kGemmThreads = 192;
 constexpr int kKernelGemm = 1;
 
@@ -72,22 +72,25 @@ struct GemmArgs {
   void* D; long long ldd; long long d_group_stride;   // in elements
   const float* sa; int sa_ld; long long sa_group_stride;   // activation scales [groups][K/128][sa_ld]
   const float* sb; long long sb_group_stride;              // weight scales [groups][ceil(N/128)][K/128]
+  const float* alpha;                   // optional [groups]: the accumulator is multiplied by alpha[group] (plain and NVFP4 GEMMs)
   int out_fp32;                         // 0: bf16 output, 1: fp32, 2: e4m3 (clamped cast, no scale; plain bf16 GEMMs only)
   const long long* row_dst;             // optional scatter epilogue: absolute address of every output row (bf16, may be peer memory),
   long long rd_group_stride;            // indexed [group * rd_group_stride + row]; used by the MoE combine
   GemmComm comm;                        // hooks that fuse a collective into this GEMM (all null / zero for a plain GEMM)
 };
 
-template <int BLOCK_N> struct Smem {
+constexpr int kFp4SfSlots = 7;          // NVFP4: shared-memory ring of scale-factor tiles (one K block each, 4 KB), 6 in flight
+template <int BLOCK_N, bool kFp4 = false> struct Smem {
   static constexpr int kABytes = kBlockM * kKBytes;
   static constexpr int kBBytes = BLOCK_N * kKBytes;
-  static constexpr int kG = KGroup<BLOCK_N>::value;
+  static constexpr int kG = KGroup<BLOCK_N, kFp4>::value;
+  static constexpr int kSfRing = kFp4 ? kFp4SfSlots * 4096 : 0;
   static constexpr int kStageBytes = kG * (kABytes + kBBytes);
   static constexpr int kStaging = 8 * 32 * 80;      // per-warp epilogue staging for up to 8 epilogue warps
   static constexpr int kStaticTables = 6400;       // the kernel's static shared memory: three per-group tables of kSchedCache ints + small
-  static constexpr int kBudget = 232448 - 1024 - 256 - kStaging - kStaticTables;
+  static constexpr int kBudget = 232448 - 1024 - 256 - kStaging - kStaticTables - kSfRing;
   static constexpr int kStages = (kBudget / kStageBytes) > 10 ? 10 : (kBudget / kStageBytes);
-  static constexpr int kBytes = kStages * kStageBytes + kStaging + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kBytes = kStages * kStageBytes + kSfRing + kStaging + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 constexpr int kSchedCache = 512;        // group tables up to this many groups are staged in shared memory
@@ -227,11 +230,19 @@ constexpr int kSfBufsMax = 8;
 // 128-token decode GEMM keep every SM pulling weights while using the 128-wide tile (a narrow tile re-reads the
 // activation operand once per tile and is bound by the SM's L2 read rate instead of HBM).  One tile per cluster,
 // dense operands only (groups = 1, no row tables).
-template <int BLOCK_N, bool kFP8, bool kBlockScaled, bool kSplit, bool kHw = false>
-__global__ void __launch_bounds__((EpiCfg<BLOCK_N, kBlockScaled, kHw>::kThreads), 1)
+// kMode: 0 = scales (if any) on the CUDA cores, 1 = kHw (fp8, UE8M0 scales on the tensor cores), 2 = NVFP4: packed e2m1 operands
+// (kFP8's byte-wide plumbing: a 128-byte K block row holds 256 elements), one UE4M3 scale per 16 elements of either operand
+// ([rows, K / 16] bytes, row-major, as ModelOpt checkpoints and the activation quantiser write them), applied by
+// tcgen05.mma.kind::mxf4nvf4.block_scale, fp32 accumulator times alpha[group] in the epilogue.  A K block needs 16 scale bytes per
+// row of A and B: the four scale warps bring them in with 16-byte cp.async copies, six K blocks ahead, through a ring in shared
+// memory (each warp a quarter of the rows), and store them to TMEM as 16 + 16 columns per K block (column 4 i + g: instruction i of
+// the K block, rows 32 g .. 32 g + 31 of the tile).
+template <int BLOCK_N, bool kFP8, bool kBlockScaled, bool kSplit, int kMode = 0>
+__global__ void __launch_bounds__((EpiCfg<BLOCK_N, kBlockScaled, kMode != 0>::kThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64, const __grid_constant__ CUtensorMap tmap_a32,
             const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
-  using S = Smem<BLOCK_N>;
+  constexpr bool kHw = kMode != 0, kFp4 = kMode == 2;
+  using S = Smem<BLOCK_N, kFp4>;
   constexpr int kStages = S::kStages;
   constexpr int kG = S::kG;
   constexpr int kElemsPerStageK = kFP8 ? 128 : 64;
@@ -241,24 +252,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   // deepest ring 512 columns allow (up to 4); plain GEMMs hand over one per tile and need two.
   constexpr int kAcc = kBlockScaled ? ((512 / BLOCK_N) > 4 ? 4 : (512 / BLOCK_N)) : 2;
   static_assert(!kHw || (kFP8 && !kBlockScaled && BLOCK_N <= 224), "hardware block scaling: fp8 operands, one accumulator per tile");
+  static_assert(!kFp4 || BLOCK_N == 128, "NVFP4: 128-wide tiles");
   // kHw: the scale factors follow the accumulators.  Folded form: 4 columns of B's constant, then a ring of 4-column entries
   // for A.  Wide form: a ring of 12-column entries, 4 for A and 8 for B.
-  constexpr bool kFold = BLOCK_N <= 128;
-  constexpr int kSfBufs = kFold ? 8 : 5;               // ring entries (one chunk of 4 K blocks each)
+  constexpr bool kFold = BLOCK_N <= 128 && !kFp4;
+  constexpr int kSfBufs = kFp4 ? 8 : (kFold ? 8 : 5);  // ring entries (one chunk of 4 K blocks each; NVFP4: one K block each)
   constexpr int kSfGroup = kFold ? 4 : 2;              // chunks whose scales are fetched together
-  constexpr uint32_t kSfEntry = kFold ? 4 : 12;
+  constexpr uint32_t kSfEntry = kFp4 ? 32 : (kFold ? 4 : 12);
   constexpr uint32_t kSfbCol = kAcc * BLOCK_N, kSfaCol = kSfbCol + (kFold ? 4 : 0);
   constexpr uint32_t kColsUsed = kAcc * BLOCK_N + (kHw ? (kFold ? 4 : 0) + kSfEntry * kSfBufs : 0);
   static_assert(kColsUsed <= 512 && kSfBufs <= kSfBufsMax, "TMEM holds 512 columns");
   constexpr uint32_t kTmemCols = kColsUsed <= 32 ? 32 : (kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512)));
-  constexpr uint32_t kIdesc = kHw ? make_idesc_block_scaled(FMT_E4M3, FMT_E4M3, kBlockM, BLOCK_N)
+  constexpr uint32_t kIdesc = kFp4 ? make_idesc_block_scaled(FMT_E2M1_MXF4, FMT_E2M1_MXF4, kBlockM, BLOCK_N, 0)
+                              : kHw ? make_idesc_block_scaled(FMT_E4M3, FMT_E4M3, kBlockM, BLOCK_N)
                                   : make_idesc(kFP8 ? FMT_E4M3 : FMT_BF16, kFP8 ? FMT_E4M3 : FMT_BF16, kBlockM, BLOCK_N);
   constexpr int kEpi = EpiCfg<BLOCK_N, kBlockScaled>::kGroups;
   constexpr int kCols = BLOCK_N / kEpi;          // columns of the tile each epilogue thread owns
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* staging = smem + kStages * S::kStageBytes;
+  uint8_t* sf_ring = smem + kStages * S::kStageBytes;       // NVFP4 only (S::kSfRing bytes)
+  uint8_t* staging = sf_ring + S::kSfRing;
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + S::kStaging);
   // bars: full[kStages], empty[kStages], tmem_full[kAcc], tmem_empty[kAcc]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAcc);
@@ -437,12 +451,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               pre_te = mbar_test(tempty0 + 8 * nbuf, (buf + 1 == kAcc ? bphase ^ 1 : bphase) ^ 1);
             }
             if (g == kG - 1 || kb + 1 >= num_kb) pre_full = mbar_test(full0 + 8 * nstage, nphase);
-            if (kHw && (kb & 3) == 0) {
+            if (kHw && (kFp4 || (kb & 3) == 0)) {
               // a new chunk of four K blocks: its scale factors must be in TMEM
               if (!pre_sf && !mbar_wait(sffull0 + 8 * sfb, sfphase, abort_flag, kKernelGemm, 500 + sfb)) { ok = false; break; }
               tc_fence_after();
             }
-            const bool chunk_end = kHw && ((kb & 3) == 3 || kb + 1 >= num_kb);
+            const bool chunk_end = kHw && (kFp4 || (kb & 3) == 3 || kb + 1 >= num_kb);
             if (chunk_end) {
               const int nsf = sfb + 1 == kSfBufs ? 0 : sfb + 1;
               pre_sf = mbar_test(sffull0 + 8 * nsf, sfb + 1 == kSfBufs ? sfphase ^ 1 : sfphase);
@@ -454,7 +468,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int k = 0; k < kMmasPerStage; k++) {
               uint32_t acc = kBlockScaled ? (k != 0) : ((kb | k) != 0);
               // advancing 32 bytes along K inside the 128B swizzle atom = +2 in the descriptor's 16-byte address units
-              if (kHw) umma_f8_block_scaled(d, adesc + 2 * k, bdesc + 2 * k,
+              if (kFp4) umma_nvfp4_block_scaled(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc, tmem_base + kSfaCol + kSfEntry * sfb + 4 * k,
+                                                tmem_base + kSfaCol + kSfEntry * sfb + 16 + 4 * k);
+              else if (kHw) umma_f8_block_scaled(d, adesc + 2 * k, bdesc + 2 * k,
                                             kIdesc | ((uint32_t)(kb & 3) << 29) | (kFold ? 0u : (uint32_t)(kb & 3) << 4), acc,
                                             tmem_base + kSfaCol + kSfEntry * sfb, tmem_base + (kFold ? kSfbCol : kSfaCol + kSfEntry * sfb + 4));
               else if (kFP8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
@@ -473,6 +489,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           pre_te = mbar_test(tempty0 + 8 * buf, bphase ^ 1);
         }
       }
+    }
+  } else if (kFp4 && warp >= 2 + 4 * kEpi) {
+    // ---------------- NVFP4 scale-factor warps ----------------
+    const int lane = (int)lane_id(), wq = warp & 3;
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const uint32_t ring0 = smem_u32(sf_ring);
+    const long long sf_ld = args.K / 8;                 // scale bytes per operand row (args.K counts bytes of packed e2m1)
+    const uint8_t* sfa_all = reinterpret_cast<const uint8_t*>(args.sa);
+    const uint8_t* sfb_all = reinterpret_cast<const uint8_t*>(args.sb);
+    constexpr int kAhead = kFp4SfSlots - 1;
+    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
+    int sfb = 0; uint32_t sfphase = 0; int grp, mb, nb;
+    bool ok = true;
+    int slot_w = 0, slot_r = 0;                          // ring slots written (copies issued) / read
+    // (A wait that runs out clears `ok`; the warp keeps walking the tiles without touching TMEM, because its three peers count on it
+    // at the named barrier.)
+    for (int tile = tile0; sched.get(tile, grp, mb, nb); tile += tile_stride) {
+      // this warp copies rows / columns 32 wq + lane of the tile; rows past the end read the tile's first row, columns past N the last
+      const int rows_here = sched.rows(grp) - mb * kBlockM;
+      const int ar = 32 * wq + lane < rows_here ? 32 * wq + lane : 0;
+      const int bc = min(nb * BLOCK_N + 32 * wq + lane, args.N - 1);
+      const uint8_t* pa = sfa_all + ((long long)grp * args.sa_group_stride + sched.row0(grp) + mb * kBlockM + ar) * sf_ld + (long long)kb_begin * 16;
+      const uint8_t* pb = sfb_all + ((long long)grp * args.N + bc) * sf_ld + (long long)kb_begin * 16;
+      auto issue = [&](int kb) {
+        if (kb < num_kb) {
+          const uint32_t dst = ring0 + slot_w * 4096 + (wq * 32 + lane) * 16;
+          cp_async16(dst, pa + (long long)kb * 16, 16u);
+          cp_async16(dst + 2048, pb + (long long)kb * 16, 16u);
+          if (++slot_w == kFp4SfSlots) slot_w = 0;
+        }
+        cp_async_commit();                             // one group per K block, empty past the end: the wait below counts groups
+      };
+      for (int kb = 0; kb < kAhead; kb++) issue(kb);
+      for (int kb = 0; kb < num_kb; kb++) {
+        cp_async_wait<kAhead - 1>();                   // this warp's copies of K block kb have landed
+        named_bar_sync(1, 128);                        // ... and the other three warps'
+        uint32_t wa[16], wbq[16];
+        const uint4* src = reinterpret_cast<const uint4*>(sf_ring + slot_r * 4096) + lane;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+          const uint4 va = src[g * 32], vb = src[128 + g * 32];
+          wa[g] = va.x; wa[4 + g] = va.y; wa[8 + g] = va.z; wa[12 + g] = va.w;
+          wbq[g] = vb.x; wbq[4 + g] = vb.y; wbq[8 + g] = vb.z; wbq[12 + g] = vb.w;
+        }
+        if (++slot_r == kFp4SfSlots) slot_r = 0;
+        issue(kb + kAhead);                            // the slot it takes was read one barrier ago by every warp
+        if (ok && mbar_wait(sfempty0 + 8 * sfb, sfphase ^ 1, abort_flag, kKernelGemm, 520 + sfb)) {
+          tc_fence_after();
+          tmem_st_32x32b_x16(tmem_base + lane_addr + kSfaCol + kSfEntry * sfb, wa);
+          tmem_st_32x32b_x16(tmem_base + lane_addr + kSfaCol + kSfEntry * sfb + 16, wbq);
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sffull0 + 8 * sfb);
+          if (++sfb == kSfBufs) { sfb = 0; sfphase ^= 1; }
+        } else {
+          ok = false;
+        }
+      }
+      cp_async_wait<0>();
     }
   } else if (kHw && warp >= 2 + 4 * kEpi) {
     // ---------------- scale-factor warps: warp w fills TMEM lanes [32*(w%4), +32) ----------------
@@ -674,11 +750,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __nv_bfloat16* dbf = scatter_row(args, grp, row, row_ok, sc_parity, reinterpret_cast<__nv_bfloat16*>(args.D) + off - n0) + n0;
         EpiRows erows;
         if (!kSplit && args.out_fp32 == 0) erows = epi_rows(row_ok, dbf);
+        const float al = args.alpha ? __ldg(args.alpha + grp) : 1.f;
 #pragma unroll
         for (int c = 0; c < BLOCK_N / 32; c++) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + lane_addr + buf * BLOCK_N + c * 32, r);
           tc_wait_ld();
+          if (kFp4) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) * al);
+          }
           if (kSplit) {
             float4* P = reinterpret_cast<float4*>(smem);
 #pragma unroll
@@ -827,22 +908,25 @@ static int num_sms() {
   return n;
 }
 
-template <int BLOCK_N, bool kFP8, bool kBS, bool kHw = false>
+template <int BLOCK_N, bool kFP8, bool kBS, int kMode = 0>
 static int launch(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs& a, int grid, cudaStream_t st) {
-  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, false, kHw>;
+  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, false, kMode>;
+  using S = Smem<BLOCK_N, kMode == 2>;
+  constexpr bool kHw = kMode != 0;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BLOCK_N>::kBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)launch_pdl(kern, dim3((unsigned)grid), dim3(EpiCfg<BLOCK_N, kBS, kHw>::kThreads), Smem<BLOCK_N>::kBytes, st, tas[0], tas[1], tas[2], tb, a);
+  return (int)launch_pdl(kern, dim3((unsigned)grid), dim3(EpiCfg<BLOCK_N, kBS, kHw>::kThreads), S::kBytes, st, tas[0], tas[1], tas[2], tb, a);
 }
 
 // split-K form: `tiles` clusters of `split` CTAs
-template <int BLOCK_N, bool kFP8, bool kBS, bool kHw = false>
+template <int BLOCK_N, bool kFP8, bool kBS>
 static int launch_split(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs& a, int tiles, int split, cudaStream_t st) {
-  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, true, kHw>;
+  constexpr bool kHw = false;
+  auto kern = gemm_kernel<BLOCK_N, kFP8, kBS, true, 0>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BLOCK_N>::kBytes);
@@ -971,7 +1055,7 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
   a.M = M; a.N = N; a.K = K; a.groups = groups; a.masked_m = masked_m; a.row_start = row_start; a.D = D; a.ldd = ldd; a.d_group_stride = d_gs;
   if (row_start) { a.d_group_stride = 0; sa_gs = 0; if (!masked_m) return 1004; }
   a.sa = sa; a.sa_ld = sa_ld; a.sa_group_stride = sa_gs; a.sb = sb;
-  a.sb_group_stride = (long long)((N + 127) / 128) * (K / 128); a.out_fp32 = out_fp32;
+  a.sb_group_stride = (long long)((N + 127) / 128) * (K / 128); a.out_fp32 = out_fp32; a.alpha = nullptr;
   a.row_dst = row_dst; a.rd_group_stride = row_start ? 0 : M;
   if (row_dst && out_fp32) return 1005;
   if (comm) { a.comm = *comm; if (m_blocks <= 1 || groups != 1) a.comm.mb_rot = 0; else a.comm.mb_rot %= m_blocks; }
@@ -980,10 +1064,10 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
   int grid = (int)(tiles < num_sms() ? tiles : num_sms());
   if (hw) {
     switch (bn) {
-      case 224: return launch<224, true, false, true>(ta, tb, a, grid, stream);
-      case 128: return launch<128, true, false, true>(ta, tb, a, grid, stream);
-      case 64: return launch<64, true, false, true>(ta, tb, a, grid, stream);
-      default: return launch<32, true, false, true>(ta, tb, a, grid, stream);
+      case 224: return launch<224, true, false, 1>(ta, tb, a, grid, stream);
+      case 128: return launch<128, true, false, 1>(ta, tb, a, grid, stream);
+      case 64: return launch<64, true, false, 1>(ta, tb, a, grid, stream);
+      default: return launch<32, true, false, 1>(ta, tb, a, grid, stream);
     }
   }
   if (split > 1) {
@@ -1032,6 +1116,38 @@ extern "C" int ne_gemm_comm(const void* A, long long lda, long long a_gs, const 
                    comm, a_rows_total, stream);
 }
 extern "C" int ne_gemm_comm_size() { return (int)sizeof(GemmComm); }
+
+// NVFP4 GEMM (see kMode 2): A [rows, K] and B [groups, N, K] packed e2m1 (K / 2 bytes per row), SFA [rows, K / 16] and
+// SFB [groups, N, K / 16] e4m3 bytes, alpha [groups] fp32 (or null), D bf16 (out_fp32 = 1: fp32).  Layouts as ne_gemm: one dense
+// group, masked groups [groups, M, *] (masked_m) or the contiguous grouped form (row_start + masked_m over flat [M, *] matrices).
+extern "C" int ne_gemm_nvfp4(const void* A, const void* B, void* D, long long ldd, int M, int N, int K, int groups, const int* masked_m,
+                             const int* row_start, const void* sfa, const void* sfb, const float* alpha, int out_fp32, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
+  if (K % 256 != 0 || N % 8 != 0 || !sfa || !sfb || (row_start && !masked_m)) return 1001;
+  if ((ldd * (out_fp32 ? 4 : 2)) % 16 != 0) return 1003;
+  const int Kb = K / 2;                 // bytes per operand row: the kernel's unit of K
+  constexpr int bn = 128;
+  const int m_blocks = (M + kBlockM - 1) / kBlockM;
+  CUtensorMap ta[3], tb;
+  const long long a_gs = (row_start || groups == 1) ? (long long)M * Kb : (long long)M * Kb;
+  int rc = 0;
+  for (int i = 0; i < 3 && !rc; i++)
+    rc = get_tmap_kmajor(&ta[i], A, true, (uint64_t)Kb, (uint64_t)M, (uint64_t)(row_start ? 1 : groups), (uint64_t)Kb, (uint64_t)a_gs, kBlockM >> i, 1);
+  if (rc) return 2000 + rc;
+  rc = get_tmap_kmajor(&tb, B, true, (uint64_t)Kb, (uint64_t)N, (uint64_t)groups, (uint64_t)Kb, (uint64_t)N * Kb, (uint32_t)bn, 1);
+  if (rc) return 3000 + rc;
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.M = M; a.N = N; a.K = Kb; a.groups = groups; a.masked_m = masked_m; a.row_start = row_start; a.D = D; a.ldd = ldd;
+  a.d_group_stride = row_start ? 0 : (long long)M * ldd;
+  a.sa = reinterpret_cast<const float*>(sfa); a.sa_group_stride = row_start ? 0 : M;      // NVFP4: byte arrays; the stride counts rows
+  a.sb = reinterpret_cast<const float*>(sfb);
+  a.alpha = alpha; a.out_fp32 = out_fp32 ? 1 : 0;
+  a.rd_group_stride = row_start ? 0 : M;
+  const long long tiles = (row_start ? (long long)m_blocks + groups : (long long)groups * m_blocks) * ((N + bn - 1) / bn);
+  const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+  return launch<128, true, false, 2>(ta, tb, a, grid, stream);
+}
 
 // 1: every fp8 activation quantiser of this library rounds its group scales up to powers of two (the form dtype 2 of
 // ne_gemm needs); 0: plain amax / 448.  Returns the previous setting.  Kernels captured in a CUDA graph keep the setting

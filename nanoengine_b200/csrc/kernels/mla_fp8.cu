@@ -51,12 +51,6 @@ struct MlaArgs {
   const uint8_t* cache; long long cache_rows;
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 template <bool kSparse>
 __global__ void __launch_bounds__(kSparse ? kMlaSparseThreads : kMlaThreads, 1)
 mla_fp8_kernel(const __grid_constant__ CUtensorMap tq128, const __grid_constant__ CUtensorMap tq64,

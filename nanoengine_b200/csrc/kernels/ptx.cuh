@@ -179,6 +179,13 @@ __device__ __forceinline__ void umma_f8_block_scaled(uint32_t d_tmem, uint64_t a
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
                ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
 }
+// Packed e2m1 operands (two per byte, K-major), one UE4M3 scale per 16 elements: K = 64 per instruction, four scale bytes per
+// operand row = one 32-bit TMEM word (NVFP4).
+__device__ __forceinline__ void umma_nvfp4_block_scaled(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                                                        uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
 // A operand from TMEM (e.g. softmax probabilities), B from smem.
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
@@ -218,6 +225,15 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 
+// ---- asynchronous 16-byte copies global -> shared (src_bytes < 16 zero-fills the rest) ----
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// barrier among `count` threads of a CTA (a multiple of 32), ids 1..15
+__device__ __forceinline__ void named_bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
 // ---- descriptors -----------------------------------------------------------------------------------
 enum UmmaFmt : uint32_t { FMT_F16 = 0, FMT_BF16 = 1, FMT_E4M3 = 0, FMT_E5M2 = 1 };
 // 32-bit instruction descriptor: fp32 accumulate, dense, no negate.  a_mn / b_mn = 1 selects an MN-major operand.
@@ -226,9 +242,10 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
 }
 // Descriptor of the block-scaled kinds: no accumulator-format field (always fp32); bit 23 = UE8M0 scale factors; the
 // scale-factor ids (which byte of the 32-bit scale word) sit at bits [4,6) for B and [29,31) for A.
-__host__ __device__ constexpr uint32_t make_idesc_block_scaled(uint32_t a_fmt, uint32_t b_fmt, uint32_t M, uint32_t N) {
-  return (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_block_scaled(uint32_t a_fmt, uint32_t b_fmt, uint32_t M, uint32_t N, uint32_t ue8m0 = 1) {
+  return (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | (ue8m0 << 23) | ((M >> 4) << 24);
 }
+constexpr uint32_t FMT_E2M1_MXF4 = 1;      // operand format code of the packed-fp4 kinds
 enum SwizzleMode : uint64_t { SW_NONE = 0, SW_128B = 2, SW_64B = 4, SW_32B = 6 };
 // 64-bit shared-memory matrix descriptor (Blackwell version field = 1).  Offsets are given in bytes.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint64_t swizzle) {

@@ -498,6 +498,95 @@ def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, exp
     return out if add_in is None else out + add_in
 
 
+# ---- NVFP4 (packed e2m1 + one e4m3 scale per 16 elements + one fp32 scale per tensor) ---------------------------------
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def _e2m1_codes(v: torch.Tensor) -> torch.Tensor:
+    """Round to the nearest e2m1 value (ties to the even code, saturating at 6); returns 4-bit codes with the sign in bit 3."""
+    grid = torch.tensor(_E2M1, dtype=torch.float32, device=v.device)
+    d = (v.abs().unsqueeze(-1) - grid).abs() + torch.tensor([0.0, 1e-6] * 4, device=v.device)     # a tie goes to the even code
+    code = d.argmin(-1)
+    return (code | ((v < 0) & (code > 0)).long() << 3).to(torch.uint8)
+
+
+def nvfp4_quant(x: torch.Tensor, gscale: torch.Tensor, row_group: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """x [R, K] -> (packed e2m1 uint8 [R, K/2], e4m3 scales [R, K/16]) with x ~= q * sf / gscale.  `gscale` (= 1 / input_scale of
+    a ModelOpt checkpoint) is one number, or one per group with `row_group` [R] naming each row's group.
+    Parity: the flashinfer `fp4_quantize` recipe the reference calls (layers/backends/experts/nvfp4.py:318-326)."""
+    R, K = x.shape
+    assert K % 16 == 0
+    g = gscale.float().reshape(-1)
+    g = g[0].expand(R) if row_group is None else g[row_group.long()]
+    v = x.float().view(R, K // 16, 16)
+    sf = (g.view(R, 1) * v.abs().amax(-1) / 6.0).clamp(max=FP8_MAX).to(FP8)
+    sfv = sf.float()
+    os = torch.where(sfv != 0, g.view(R, 1) / sfv.clamp_min(1e-30), torch.zeros_like(sfv))
+    codes = _e2m1_codes(v * os.unsqueeze(-1)).view(R, K)
+    return (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous(), sf
+
+
+def nvfp4_unpack(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    """Packed e2m1 [..., K/2] and e4m3 scales [..., K/16] -> fp32 [..., K] (without the per-tensor scale)."""
+    grid = torch.tensor(_E2M1 + tuple(-a for a in _E2M1), dtype=torch.float32, device=q.device)
+    lo, hi = (q & 0xF).long(), (q >> 4).long()
+    v = torch.stack([grid[lo], grid[hi]], -1).flatten(-2)
+    return (v.view(*v.shape[:-1], -1, 16) * sf.float().unsqueeze(-1)).flatten(-2)
+
+
+def nvfp4_quant_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The ModelOpt NVFP4 weight format: (packed [..., N, K/2], weight_scale e4m3 [..., N, K/16], weight_scale_2 fp32 per matrix)
+    with w ~= e2m1 * weight_scale * weight_scale_2."""
+    *lead, N, K = w.shape
+    wf = w.float().reshape(-1, N, K)
+    s2 = (wf.abs().amax(dim=(1, 2)) / (6.0 * FP8_MAX)).clamp_min(1e-12)
+    qs, sfs = [], []
+    for m, s in zip(wf, s2):
+        q, sf = nvfp4_quant(m, (1.0 / s).reshape(1))
+        qs.append(q); sfs.append(sf)
+    return torch.stack(qs).view(*lead, N, K // 2), torch.stack(sfs).view(*lead, N, K // 16), s2.view(*lead) if lead else s2[0]
+
+
+def nvfp4_gemm(a_q, a_sf, b_q, b_sf, alpha, masked_m=None, row_start=None, out_fp32: bool = False) -> torch.Tensor:
+    """D = alpha[g] * (A_g B_g^T) over NVFP4 operands.  A [R, K/2] with B [G, N, K/2] in the contiguous grouped layout (row_start /
+    masked_m as in the fp8 grouped GEMM) or G = 1; rows outside every group's range come back as zeros."""
+    G, N = b_q.shape[0], b_q.shape[1]
+    A = nvfp4_unpack(a_q, a_sf)
+    out = torch.zeros(A.shape[0], N, dtype=torch.float32, device=A.device)
+    al = torch.ones(G, device=A.device) if alpha is None else alpha.float().reshape(-1)
+    for g in range(G):
+        lo = 0 if row_start is None else int(row_start[g])
+        n = A.shape[0] if masked_m is None else int(masked_m[g])
+        if n > 0:
+            out[lo:lo + n] = A[lo:lo + n] @ nvfp4_unpack(b_q[g], b_sf[g]).t() * al[g]
+    return out if out_fp32 else out.to(torch.bfloat16)
+
+
+def moe_experts_nvfp4(x, topk_idx, topk_w, w13_q, w13_sf, alpha1, a1_gscale, w2_q, w2_sf, alpha2, a2_gscale, expert_offset: int = 0,
+                      add_in=None, act=None) -> torch.Tensor:
+    """Routed experts with NVFP4 weights and activations (W4A4).  w13_q [E, 2I, H/2], w2_q [E, H, I/2] packed e2m1 with e4m3
+    block scales; `a1_gscale` (one number) and `a2_gscale` [E] are the reciprocals of the checkpoint's input scales, `alpha1` /
+    `alpha2` [E] = input_scale * weight_scale_2.  Parity: reference layers/backends/experts/nvfp4.py:143-160,205-220."""
+    if callable(add_in):
+        add_in = add_in()
+    T, H = x.shape
+    E = w13_q.shape[0]
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for e in range(E):
+        tok, slot = (topk_idx == e + expert_offset).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        xe = x[tok].to(torch.bfloat16)
+        aq, asf = nvfp4_quant(xe, a1_gscale.reshape(-1)[:1])
+        h = nvfp4_gemm(aq, asf, w13_q[e:e + 1], w13_sf[e:e + 1], alpha1[e:e + 1])
+        h = silu_and_mul(h, act=act)
+        hq, hsf = nvfp4_quant(h, a2_gscale.reshape(-1)[e:e + 1])
+        y = nvfp4_gemm(hq, hsf, w2_q[e:e + 1], w2_sf[e:e + 1], alpha2[e:e + 1])
+        out.index_add_(0, tok, y.float() * topk_w[tok, slot].unsqueeze(-1))
+    out = out.to(x.dtype)
+    return out if add_in is None else out + add_in
+
+
 # ---- sampling ------------------------------------------------------------------------------------
 def sample(logits: torch.Tensor, temperatures: torch.Tensor, generator: Optional[torch.Generator] = None,
            return_logprobs: bool = False):

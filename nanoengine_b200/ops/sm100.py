@@ -512,6 +512,84 @@ def moe_experts(x, topk_idx, topk_w, w13, w2, w13_scale=None, w2_scale=None, exp
     return out
 
 
+# ---- NVFP4 -------------------------------------------------------------------------------------------------------
+nvfp4_unpack, nvfp4_quant_weight = ref.nvfp4_unpack, ref.nvfp4_quant_weight
+
+
+def _nvfp4_quant_raw(x, gscale, row_start, counts, groups):
+    R, K = x.shape
+    q = torch.empty(R, K // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.zeros(R, K // 16, dtype=FP8, device=x.device) if row_start is not None else torch.empty(R, K // 16, dtype=FP8, device=x.device)
+    _ck(lib().ne_nvfp4_quant(_p(x), _c.c_longlong(x.stride(0)), _p(q), _p(sf), _p(gscale), _p(row_start), _p(counts), _c.c_int(groups), _c.c_int(R),
+                             _c.c_int(K), _st()), "ne_nvfp4_quant")
+    return q, sf
+
+
+def nvfp4_quant(x: torch.Tensor, gscale: torch.Tensor, row_group: Optional[torch.Tensor] = None):
+    """bf16 [R, K] -> (packed e2m1 [R, K/2], e4m3 scales [R, K/16]); see the reference body.  `row_group` must be sorted (rows of a
+    group adjacent), as the grouped layouts are."""
+    x = _as_bf16_2d(x)
+    g = gscale.float().reshape(-1).contiguous()
+    if row_group is None:
+        return _nvfp4_quant_raw(x, g, None, None, 1)
+    G = g.numel()
+    counts = torch.bincount(row_group.long(), minlength=G).to(torch.int32)
+    row_start = (counts.cumsum(0) - counts).to(torch.int32)
+    return _nvfp4_quant_raw(x, g, row_start, counts, G)
+
+
+def nvfp4_gemm(a_q, a_sf, b_q, b_sf, alpha, masked_m=None, row_start=None, out_fp32: bool = False) -> torch.Tensor:
+    """NVFP4 grouped GEMM on the tensor cores (tcgen05.mma.kind::mxf4nvf4.block_scale); layouts as the reference body."""
+    G, N, K2 = b_q.shape
+    R = a_q.shape[0]
+    assert a_q.shape[1] == K2 and a_q.is_contiguous() and b_q.is_contiguous() and a_sf.is_contiguous() and b_sf.is_contiguous()
+    out = torch.zeros(R, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=a_q.device)
+    if G > 1:
+        assert row_start is not None and masked_m is not None, "several groups: the contiguous grouped layout"
+    al = None if alpha is None else alpha.float().reshape(-1).contiguous()
+    _ck(lib().ne_gemm_nvfp4(_p(a_q), _p(b_q), _p(out), _c.c_longlong(N), _c.c_int(R), _c.c_int(N), _c.c_int(K2 * 2), _c.c_int(G),
+                            _p(None if masked_m is None else masked_m.to(torch.int32)), _p(None if row_start is None else row_start.to(torch.int32)),
+                            _p(a_sf), _p(b_sf), _p(al), _c.c_int(1 if out_fp32 else 0), _st()), "ne_gemm_nvfp4")
+    return out
+
+
+def moe_experts_nvfp4(x, topk_idx, topk_w, w13_q, w13_sf, alpha1, a1_gscale, w2_q, w2_sf, alpha2, a2_gscale, expert_offset: int = 0,
+                      add_in=None, act=None) -> torch.Tensor:
+    """Local routed experts, W4A4: dispatch into the contiguous grouped layout, quantise, NVFP4 GEMM, gated activation, quantise with
+    the expert's own scale, NVFP4 GEMM, weighted combine."""
+    T, H = x.shape
+    E, I2 = w13_q.shape[0], w13_q.shape[1]
+    I = I2 // 2
+    K = topk_idx.shape[1]
+    dev = x.device
+    x = _as_bf16_2d(x)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    if T == 0:
+        return out
+    R = (T * K + E * 127 + 127) // 128 * 128
+    meta = torch.empty(E + (E + 1) + 2 * T * K, dtype=torch.int32, device=dev)
+    counts, row_start = meta[:E], meta[E:2 * E + 1]
+    slot, pos = meta[2 * E + 1:2 * E + 1 + T * K], meta[2 * E + 1 + T * K:]
+    idx = topk_idx.to(torch.int32).contiguous()
+    w = topk_w.float().contiguous()
+    a_b = torch.empty(R, H, dtype=torch.bfloat16, device=dev)
+    _ck(lib().ne_moe_dispatch_local(_p(x), _p(idx), _p(counts), _p(slot), _p(row_start), _p(pos), _p(a_b), _p(None), _p(None), _c.c_int(R),
+                                    _c.c_int(T), _c.c_int(K), _c.c_int(H), _c.c_int(expert_offset), _c.c_int(E), _c.c_int(R), _c.c_int(128), _st()),
+        "ne_moe_dispatch_local")
+    g1 = a1_gscale.float().reshape(-1)[:1].expand(E).contiguous()
+    aq, asf = _nvfp4_quant_raw(a_b, g1, row_start, counts, E)
+    g = nvfp4_gemm(aq, asf, w13_q, w13_sf, alpha1, counts, row_start)
+    h = torch.empty(R, I, dtype=torch.bfloat16, device=dev)
+    _ck(lib().ne_act_mul(_p(g), _p(h), _p(None), _p(None), _c.c_int(0), _c.c_longlong(0), _p(counts), _p(row_start), _c.c_int(E), _c.c_int(R), _c.c_int(I),
+                         *_act_args(act), _st()), "ne_act_mul")
+    hq, hsf = _nvfp4_quant_raw(h, a2_gscale.float().reshape(-1).contiguous(), row_start, counts, E)
+    y = nvfp4_gemm(hq, hsf, w2_q, w2_sf, alpha2, counts, row_start)
+    if callable(add_in):
+        add_in = add_in()
+    _ck(lib().ne_moe_combine_local(_p(y), _p(pos), _p(w), _p(add_in), _p(out), _c.c_int(T), _c.c_int(K), _c.c_int(H), _st()), "ne_moe_combine_local")
+    return out
+
+
 # ---- attention / sampling: filled in by the dedicated kernel modules ---------------------------------
 def mla_attention_paged(q, cache, block_tables, cu_seqlens_q, context_lens, scale, kv_lora_rank, sparse_indices=None):
     from . import sm100_attn
