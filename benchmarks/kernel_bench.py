@@ -112,6 +112,26 @@ def case_moe_gemm(E, rows_per_expert, N, K):
     return fn, E * N * K + E * rows_per_expert * (K + 2 * N), 2.0 * E * rows_per_expert * N * K
 
 
+def case_moe_gemm_nvfp4(E, rows_per_expert, N, K):
+    """The same grouped GEMM with NVFP4 operands (packed e2m1, e4m3 scale per 16 elements), W4A4."""
+    pad = (rows_per_expert + 127) // 128 * 128
+    R = E * pad
+    a = torch.randint(0, 256, (R, K // 2), device="cuda", dtype=torch.int32).to(torch.uint8)
+    b = torch.randint(0, 256, (E, N, K // 2), device="cuda", dtype=torch.int32).to(torch.uint8)
+    sa = torch.ones(R, K // 16, device="cuda").to(FP8)
+    sb = torch.ones(E, N, K // 16, device="cuda").to(FP8)
+    alpha = torch.ones(E, device="cuda")
+    counts = torch.full((E,), rows_per_expert, dtype=torch.int32, device="cuda")
+    row_start = (torch.arange(E + 1, device="cuda") * pad).to(torch.int32)
+    out = torch.empty(R, N, dtype=torch.bfloat16, device="cuda")
+    lib = sm100.lib()
+    import ctypes as _c
+    p = sm100._p
+    fn = lambda: sm100._ck(lib.ne_gemm_nvfp4(p(a), p(b), p(out), _c.c_longlong(N), _c.c_int(R), _c.c_int(N), _c.c_int(K), _c.c_int(E), p(counts),
+                                             p(row_start), p(sa), p(sb), p(alpha), _c.c_int(0), sm100._st()), "ne_gemm_nvfp4")
+    return fn, E * N * K // 2 + E * N * K // 16 + E * rows_per_expert * (K // 2 + K // 16 + 2 * N), 2.0 * E * rows_per_expert * N * K
+
+
 def case_mla(B, ctx, H=128, q_len=1):
     bs = 64
     nb = (ctx + bs - 1) // bs
@@ -349,6 +369,10 @@ def build_cases(args):
         "o_proj_prefill": lambda: case_dense_fp8(args.prefill_tokens, 7168, 16384),
         "moe_gemm1_prefill": lambda: case_moe_gemm(E, args.prefill_tokens * 8 // 32, 4096, 7168),
         "moe_gemm2_prefill": lambda: case_moe_gemm(E, args.prefill_tokens * 8 // 32, 7168, 2048),
+        "nvfp4_moe_gemm1_prefill": lambda: case_moe_gemm_nvfp4(E, args.prefill_tokens * 8 // 32, 4096, 7168),
+        "nvfp4_moe_gemm2_prefill": lambda: case_moe_gemm_nvfp4(E, args.prefill_tokens * 8 // 32, 7168, 2048),
+        "nvfp4_moe_gemm1": lambda: case_moe_gemm_nvfp4(E, args.rows, 4096, 7168),
+        "nvfp4_moe_gemm2": lambda: case_moe_gemm_nvfp4(E, args.rows, 7168, 2048),
         "bf16_square": lambda: case_dense_bf16(8192, 8192, 8192),
     }
     return c

@@ -212,7 +212,10 @@ class ModelConfig:
         if archs and "architecture" not in d:
             d["architecture"] = archs[0]
         q = d.pop("quantization_config", None)
-        if q and q.get("quant_method") == "fp8":
+        if q and (str(q.get("quant_algo", "")).upper() == "NVFP4" or q.get("quant_method") in ("nvfp4", "modelopt_fp4")):
+            # ModelOpt NVFP4: routed experts (and any other linear the checkpoint quantised) as packed e2m1 with e4m3 block scales
+            d["quant"] = "nvfp4"
+        elif q and q.get("quant_method") == "fp8":
             d["quant"] = "fp8"
             d["weight_block_size"] = list(q.get("weight_block_size", [128, 128]))
             if q.get("scale_fmt"):
@@ -284,12 +287,22 @@ class ModelConfig:
     @classmethod
     def from_pretrained(cls, path: str) -> "ModelConfig":
         with open(os.path.join(path, "config.json")) as f:
-            return cls.from_dict(json.load(f))
+            d = json.load(f)
+        side = os.path.join(path, "hf_quant_config.json")          # where ModelOpt exports put the quantisation recipe
+        if "quantization_config" not in d and os.path.exists(side):
+            with open(side) as f:
+                q = json.load(f).get("quantization", {})
+            if q.get("quant_algo"):
+                d["quantization_config"] = {"quant_method": "modelopt", **q}
+        return cls.from_dict(d)
 
     def to_dict(self) -> Dict[str, Any]:
         d = {f.name: getattr(self, f.name) for f in fields(self)}
         d["architectures"] = [d.pop("architecture")]
-        if d.pop("quant") == "fp8":
+        quant = d.pop("quant")
+        if quant == "nvfp4":
+            d["quantization_config"] = {"quant_method": "modelopt", "quant_algo": "NVFP4", "group_size": 16}
+        if quant == "fp8":
             d["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": d["weight_block_size"]}
             if d.get("scale_fmt"):
                 d["quantization_config"]["scale_fmt"] = d["scale_fmt"]

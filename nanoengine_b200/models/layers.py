@@ -223,6 +223,9 @@ class RoutedExperts(nn.Module):
         self.expert_offset = d.ep_rank * self.num_local
         wdt = torch.float8_e4m3fn if quant == "fp8" else dtype
         E = self.num_local
+        if quant == "nvfp4":
+            self._init_nvfp4(E, hidden, inter, device)
+            return
         self.gate_up_proj = nn.Parameter(torch.empty(E, 2 * inter, hidden, dtype=wdt, device=device), requires_grad=False)
         self.down_proj = nn.Parameter(torch.empty(E, hidden, inter, dtype=wdt, device=device), requires_grad=False)
         if quant == "fp8":
@@ -230,6 +233,71 @@ class RoutedExperts(nn.Module):
             self.down_scale = nn.Parameter(torch.ones(E, _ceil_div(hidden, 128), _ceil_div(inter, 128), dtype=torch.float32, device=device), requires_grad=False)
         else:
             self.gate_up_scale = self.down_scale = None
+
+    # ---- NVFP4 (ModelOpt checkpoints: packed e2m1 weights, e4m3 scale per 16, fp32 scale per matrix, fp32 input scale) ----
+    # Parity: reference layers/backends/experts/nvfp4.py:75-160 (parameters, load_expert_weight, process_weights_after_loading).
+    NVFP4_DEFAULT_INPUT_SCALE = 32.0 / (6.0 * 448.0)       # weights quantised here (random init, bf16 checkpoints): activations up to 32
+
+    def _init_nvfp4(self, E, hidden, inter, device):
+        assert self.ffn_tp == 1, "NVFP4 experts are sharded over the expert-parallel axis only"
+        assert hidden % 256 == 0 and inter % 256 == 0, "NVFP4 GEMMs take K in multiples of 256"
+        u8, e4 = torch.uint8, torch.float8_e4m3fn
+        P = lambda *shape, dtype: nn.Parameter(torch.zeros(*shape, dtype=dtype, device=device), requires_grad=False)
+        self.gate_up_proj = P(E, 2 * inter, hidden // 2, dtype=u8)
+        self.down_proj = P(E, hidden, inter // 2, dtype=u8)
+        self.gate_up_scale = P(E, 2 * inter, hidden // 16, dtype=e4)
+        self.down_scale = P(E, hidden, inter // 16, dtype=e4)
+        self.gate_up_scale_2 = P(E, 2, dtype=torch.float32)            # [gate, up]
+        self.down_scale_2 = P(E, dtype=torch.float32)
+        self.gate_up_input_scale = P(E, 2, dtype=torch.float32)
+        self.down_input_scale = P(E, dtype=torch.float32)
+        self._nvfp4_ready = False
+
+    @torch.no_grad()
+    def load_expert_part(self, logical_id: int, which: str, kind: str, t: torch.Tensor) -> bool:
+        """One tensor of an NVFP4 checkpoint: `kind` in {weight, weight_scale, weight_scale_2, input_scale}."""
+        slots = self.local_slots_of(logical_id)
+        for sl in slots:
+            self._set_part(sl, which, kind, t)
+        return bool(slots)
+
+    @torch.no_grad()
+    def _set_part(self, sl: int, which: str, kind: str, t: torch.Tensor) -> None:
+        I = self.inter
+        if True:
+            if which == "down":
+                tgt = {"weight": self.down_proj[sl], "weight_scale": self.down_scale[sl], "weight_scale_2": self.down_scale_2[sl],
+                       "input_scale": self.down_input_scale[sl]}[kind]
+            else:
+                half = 0 if which == "gate" else 1
+                rows = slice(half * I, (half + 1) * I)
+                tgt = {"weight": self.gate_up_proj[sl, rows], "weight_scale": self.gate_up_scale[sl, rows],
+                       "weight_scale_2": self.gate_up_scale_2[sl, half], "input_scale": self.gate_up_input_scale[sl, half]}[kind]
+            src = t.to(tgt.device)
+            tgt.copy_(src.view(tgt.dtype).reshape(tgt.shape) if src.dtype in (torch.uint8, torch.float8_e4m3fn) else src.reshape(tgt.shape))
+        self._nvfp4_ready = False
+
+    @torch.no_grad()
+    def _prepare_nvfp4(self):
+        """Scales the kernels take: one activation scale for GEMM 1 (the largest over all experts, over all EP ranks), one per expert
+        for GEMM 2, and alpha = input_scale * weight_scale_2.  Gate and up halves whose weight_scale_2 differ are brought onto the
+        gate's by rescaling the up half's block scales."""
+        d = get_dist_context()
+        in1 = self.gate_up_input_scale.max().float().reshape(1)
+        if d.ep_size > 1:
+            import torch.distributed as dist
+            dist.all_reduce(in1, op=dist.ReduceOp.MAX, group=d.group("ffn_ep"))
+        ratio = self.gate_up_scale_2[:, 1] / self.gate_up_scale_2[:, 0].clamp_min(1e-30)
+        if bool(((ratio - 1).abs() > 1e-6).any()):
+            I = self.inter
+            up = self.gate_up_scale[:, I:].float() * ratio.view(-1, 1, 1)
+            self.gate_up_scale[:, I:].copy_(up.clamp(max=448.0).to(torch.float8_e4m3fn))
+            self.gate_up_scale_2[:, 1].copy_(self.gate_up_scale_2[:, 0])
+        self.a1_gscale = (1.0 / in1).float().contiguous()
+        self.alpha1 = (in1 * self.gate_up_scale_2[:, 0]).float().contiguous()
+        self.a2_gscale = (1.0 / self.down_input_scale).float().contiguous()
+        self.alpha2 = (self.down_input_scale * self.down_scale_2).float().contiguous()
+        self._nvfp4_ready = True
 
     def owns(self, expert_id: int) -> bool:
         return bool(self.local_slots_of(expert_id))
@@ -263,6 +331,11 @@ class RoutedExperts(nn.Module):
     def forward(self, x, topk_idx, topk_w, add_in=None):
         """Local part of the routed output for the tokens given (weights applied, zero rows where no expert is local);
         `add_in` (the shared-expert output) is summed in by the same gather pass."""
+        if self.quant == "nvfp4":
+            if not self._nvfp4_ready:
+                self._prepare_nvfp4()
+            return ops.moe_experts_nvfp4(x, topk_idx, topk_w, self.gate_up_proj, self.gate_up_scale, self.alpha1, self.a1_gscale, self.down_proj,
+                                         self.down_scale, self.alpha2, self.a2_gscale, self.expert_offset, add_in, act=self.act)
         return ops.moe_experts(x, topk_idx, topk_w, self.gate_up_proj, self.down_proj, self.gate_up_scale, self.down_scale,
                                self.expert_offset, add_in, act=self.act)
 
@@ -270,6 +343,15 @@ class RoutedExperts(nn.Module):
     def set_expert(self, local_idx: int, which: str, w: torch.Tensor, scale_inv: Optional[torch.Tensor] = None):
         """which in {gate, up, down}; w is one expert's HF-layout matrix (fp8 + scales, or high precision)."""
         I = self.inter
+        if self.quant == "nvfp4":
+            # a high-precision (or fp8) matrix: quantised here, with a nominal activation scale
+            if w.dtype == torch.float8_e4m3fn:
+                w = ref.dequant_fp8_block(w, scale_inv)
+            q, sf, s2 = ref.nvfp4_quant_weight(w.to(self.gate_up_proj.device).float())
+            for kind, t in (("weight", q), ("weight_scale", sf), ("weight_scale_2", s2),
+                            ("input_scale", torch.tensor(self.NVFP4_DEFAULT_INPUT_SCALE, device=q.device))):
+                self._set_part(local_idx, which, kind, t)
+            return
         tgt, tscale, rows = {
             "gate": (self.gate_up_proj, self.gate_up_scale, slice(0, I)),
             "up": (self.gate_up_proj, self.gate_up_scale, slice(I, 2 * I)),

@@ -271,6 +271,10 @@ class _Pending:
         return self.w.pop(key), self.s.pop(key, None)
 
 
+_NVFP4_PART = re.compile(r"(.*)\.(weight|weight_scale|weight_scale_2|input_scale)$")
+_NVFP4_EXPERT = re.compile(r"model\.layers\.(\d+)\.mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)$")
+
+
 def _deq(w, s):
     from ..ops import reference as ref
     return ref.dequant_fp8_block(w, s) if w.dtype == torch.float8_e4m3fn else w.float()
@@ -289,6 +293,7 @@ def load_deepseek_weights(model, weights: Iterable[Tuple[str, torch.Tensor]], mt
     wbuf: Dict[str, torch.Tensor] = {}
     sbuf: Dict[str, torch.Tensor] = {}
     groups: Dict[str, Dict[str, Tuple[torch.Tensor, Optional[torch.Tensor]]]] = {}
+    fbuf: Dict[str, Dict[str, torch.Tensor]] = {}
     quant_names = set()
 
     def layer_of(i):
@@ -395,6 +400,27 @@ def load_deepseek_weights(model, weights: Iterable[Tuple[str, torch.Tensor]], mt
                 if L is not None and L.self_attn.indexer is not None:
                     L.self_attn.indexer.load("k_norm.bias", t, None); n += 1
                 continue
+            part = _NVFP4_PART.match(name)
+            if part and (cfg.quant == "nvfp4") and (part.group(2) != "weight" or t.dtype == torch.uint8):
+                # ModelOpt NVFP4: routed experts keep the packed form; any other quantised linear is expanded once all three weight
+                # tensors are in (its input_scale is not needed: it runs in bf16)
+                base, kind = part.group(1), part.group(2)
+                em = _NVFP4_EXPERT.match(base)
+                L = layer_of(int(em.group(1))) if em else None
+                if em and L is not None and getattr(L.mlp, "experts", None) is not None and L.mlp.experts.quant == "nvfp4":
+                    if L.mlp.experts.load_expert_part(int(em.group(2)), em.group(3)[:-5], kind, t):
+                        n += 1
+                    continue
+                if em and L is None:
+                    continue
+                fb = fbuf.setdefault(base, {})
+                fb[kind] = t
+                if all(k in fb for k in ("weight", "weight_scale", "weight_scale_2")):
+                    from ..ops import reference as ref
+                    w = ref.nvfp4_unpack(fb["weight"].to(torch.uint8), fb["weight_scale"].view(torch.float8_e4m3fn)) * fb["weight_scale_2"].float()
+                    fbuf.pop(base)
+                    place(base, w.to(torch.bfloat16), None)
+                continue
             if name.endswith(".weight_scale_inv"):
                 base = name[: -len(".weight_scale_inv")]
                 if base in wbuf:
@@ -412,20 +438,25 @@ def load_deepseek_weights(model, weights: Iterable[Tuple[str, torch.Tensor]], mt
                     wbuf[base] = t
             else:
                 place(base, t, None)
-    if wbuf or groups:
-        raise ValueError(f"incomplete checkpoint: {list(wbuf)[:3]} {list(groups)[:3]}")
+    fbuf = {k: v for k, v in fbuf.items() if "weight" in v}          # a stray input_scale of a linear kept in bf16 is not an error
+    if wbuf or groups or fbuf:
+        raise ValueError(f"incomplete checkpoint: {list(wbuf)[:3]} {list(groups)[:3]} {list(fbuf)[:3]}")
     return n
 
 
 def save_hf_checkpoint(path: str, cfg: ModelConfig, weights: Iterable[Tuple[str, torch.Tensor]], quantize_fp8: bool = False,
-                       shard_bytes: int = 1 << 30) -> None:
-    """Write a small HF-layout checkpoint (config.json + safetensors shards); used by tests and examples."""
+                       shard_bytes: int = 1 << 30, quantize_nvfp4: bool = False, nvfp4_input_scale: float = 32.0 / (6.0 * 448.0)) -> None:
+    """Write a small HF-layout checkpoint (config.json + safetensors shards); used by tests and examples.  `quantize_nvfp4`: the
+    MLP / expert projections in the ModelOpt NVFP4 layout (`weight` packed e2m1, `weight_scale` e4m3 per 16, `weight_scale_2`,
+    `input_scale`), everything else in bf16."""
     from safetensors.torch import save_file
     from ..ops import reference as ref
     os.makedirs(path, exist_ok=True)
     cd = cfg.to_dict()
     if quantize_fp8:
         cd["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128]}
+    if quantize_nvfp4:
+        cd["quantization_config"] = {"quant_method": "modelopt", "quant_algo": "NVFP4", "group_size": 16}
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(cd, f, indent=1)
     shard, size, idx = {}, 0, 0
@@ -439,7 +470,13 @@ def save_hf_checkpoint(path: str, cfg: ModelConfig, weights: Iterable[Tuple[str,
     for name, t in weights:
         t = t.detach().cpu()
         big = t.dim() == 2 and name.endswith("proj.weight") and "indexer" not in name and "eh_proj" not in name
-        if quantize_fp8 and big:
+        if quantize_nvfp4 and big and ".mlp." in name and t.shape[1] % 16 == 0:
+            q, sf, s2 = ref.nvfp4_quant_weight(t.float())
+            base = name[: -len(".weight")]
+            shard[name] = q.contiguous(); shard[base + ".weight_scale"] = sf.contiguous()
+            shard[base + ".weight_scale_2"] = s2.reshape(()).clone(); shard[base + ".input_scale"] = torch.tensor(nvfp4_input_scale)
+            size += q.numel() + sf.numel()
+        elif quantize_fp8 and big:
             q, s = ref.quant_fp8_block(t)
             shard[name] = q.contiguous(); shard[name + "_scale_inv"] = s.contiguous()
             size += q.numel() + s.numel() * 4

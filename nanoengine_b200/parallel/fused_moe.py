@@ -153,6 +153,8 @@ def install(config, dist_ctx) -> Optional[FusedEP]:
     mc = config.model_config
     if dist_ctx.ep_size == 1 or not config.use_fused_comm or not torch.cuda.is_available():
         return None
+    if mc.quant == "nvfp4":
+        return None        # NVFP4 experts take the collective path (all-gather, local W4A4 experts, all-reduce): no fused form is built
     group = dist_ctx.group("ffn_ep")
     if not peers_reachable(group):
         return None

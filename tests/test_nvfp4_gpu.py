@@ -90,3 +90,34 @@ def test_moe_experts_nvfp4(k, T, E, topk):
     got = k.moe_experts_nvfp4(*args)
     want = ref.moe_experts_nvfp4(*args)
     assert _rel(got, want) < 3e-2            # the intermediate is re-quantised to 4 bits: a rounding tie moves a whole step
+
+
+def test_engine_with_nvfp4_experts_graph_equals_eager():
+    """A small DeepSeek-style model whose routed experts are NVFP4 (W4A4 on the tensor cores), the rest bf16: eager and CUDA-graph
+    execution give the same tokens, and the expert module on the GPU agrees with its PyTorch statement on the same weights."""
+    from nanoengine_b200 import Config, LLM, SamplingParams
+    from nanoengine_b200.models.config import tiny_deepseek_v3
+    from nanoengine_b200.ops import sm100
+    mc = tiny_deepseek_v3(hidden_size=512, moe_intermediate_size=256, intermediate_size=1024, q_lora_rank=256, kv_lora_rank=512,
+                          qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_attention_heads=16, quant="nvfp4")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (300, 150, 9)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    outs = {}
+    for eager in (True, False):
+        llm = LLM(Config(model="tiny-deepseek-v3", model_config=mc, dummy_weight=True, dtype="bfloat16", device="cuda", kvcache_block_size=64,
+                         num_kvcache_blocks=64, max_num_seqs=8, enforce_eager=eager, seed=0))
+        ex = llm.engine.executor.runner.model.model.layers["1"].mlp.experts
+        assert ex.quant == "nvfp4" and ex.gate_up_proj.dtype == torch.uint8
+        outs[eager] = [o["token_ids"] for o in llm.generate(prompts, sp)]
+        if eager:
+            x = torch.randn(50, 512, device="cuda", dtype=torch.bfloat16)
+            idx, w = ref.moe_route(torch.randn(50, mc.n_routed_experts, device="cuda"), None, 2, 1, 1, True, 1.0, "softmax")
+            args = (x, idx, w, ex.gate_up_proj, ex.gate_up_scale, ex.alpha1, ex.a1_gscale, ex.down_proj, ex.down_scale, ex.alpha2, ex.a2_gscale, 0)
+            assert _rel(sm100.moe_experts_nvfp4(*args), ref.moe_experts_nvfp4(*args)) < 3e-2
+        del llm
+        torch.cuda.empty_cache()
+    assert all(len(t) == 8 for t in outs[True])
+    same = sum(a == b for a, b in zip(outs[True], outs[False]))
+    assert same >= 2 and all(a[:3] == b[:3] for a, b in zip(outs[True], outs[False])), outs
+    assert sm100.kernel_status()[0] == 0
