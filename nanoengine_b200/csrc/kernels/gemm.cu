@@ -79,7 +79,7 @@ struct GemmArgs {
   GemmComm comm;                        // hooks that fuse a collective into this GEMM (all null / zero for a plain GEMM)
 };
 
-constexpr int kFp4SfSlots = 7;          // NVFP4: shared-memory ring of scale-factor tiles (one K block each, 4 KB), 6 in flight
+constexpr int kFp4SfSlots = 8;          // NVFP4: shared-memory ring of scale-factor tiles (one K block each, 4 KB), 6 in flight
 template <int BLOCK_N, bool kFp4 = false> struct Smem {
   static constexpr int kABytes = kBlockM * kKBytes;
   static constexpr int kBBytes = BLOCK_N * kKBytes;
@@ -256,9 +256,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   // kHw: the scale factors follow the accumulators.  Folded form: 4 columns of B's constant, then a ring of 4-column entries
   // for A.  Wide form: a ring of 12-column entries, 4 for A and 8 for B.
   constexpr bool kFold = BLOCK_N <= 128 && !kFp4;
-  constexpr int kSfBufs = kFp4 ? 8 : (kFold ? 8 : 5);  // ring entries (one chunk of 4 K blocks each; NVFP4: one K block each)
+  constexpr int kSfBufs = kFp4 ? 4 : (kFold ? 8 : 5);  // ring entries (one chunk of 4 K blocks each; NVFP4: a pair of K blocks each)
   constexpr int kSfGroup = kFold ? 4 : 2;              // chunks whose scales are fetched together
-  constexpr uint32_t kSfEntry = kFp4 ? 32 : (kFold ? 4 : 12);
+  constexpr uint32_t kSfEntry = kFp4 ? 64 : (kFold ? 4 : 12);
   constexpr uint32_t kSfbCol = kAcc * BLOCK_N, kSfaCol = kSfbCol + (kFold ? 4 : 0);
   constexpr uint32_t kColsUsed = kAcc * BLOCK_N + (kHw ? (kFold ? 4 : 0) + kSfEntry * kSfBufs : 0);
   static_assert(kColsUsed <= 512 && kSfBufs <= kSfBufsMax, "TMEM holds 512 columns");
@@ -451,12 +451,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               pre_te = mbar_test(tempty0 + 8 * nbuf, (buf + 1 == kAcc ? bphase ^ 1 : bphase) ^ 1);
             }
             if (g == kG - 1 || kb + 1 >= num_kb) pre_full = mbar_test(full0 + 8 * nstage, nphase);
-            if (kHw && (kFp4 || (kb & 3) == 0)) {
+            if (kHw && (kFp4 ? (kb & 1) == 0 : (kb & 3) == 0)) {
               // a new chunk of four K blocks: its scale factors must be in TMEM
               if (!pre_sf && !mbar_wait(sffull0 + 8 * sfb, sfphase, abort_flag, kKernelGemm, 500 + sfb)) { ok = false; break; }
               tc_fence_after();
             }
-            const bool chunk_end = kHw && (kFp4 || (kb & 3) == 3 || kb + 1 >= num_kb);
+            const bool chunk_end = kHw && ((kFp4 ? (kb & 1) == 1 : (kb & 3) == 3) || kb + 1 >= num_kb);
             if (chunk_end) {
               const int nsf = sfb + 1 == kSfBufs ? 0 : sfb + 1;
               pre_sf = mbar_test(sffull0 + 8 * nsf, sfb + 1 == kSfBufs ? sfphase ^ 1 : sfphase);
@@ -468,8 +468,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int k = 0; k < kMmasPerStage; k++) {
               uint32_t acc = kBlockScaled ? (k != 0) : ((kb | k) != 0);
               // advancing 32 bytes along K inside the 128B swizzle atom = +2 in the descriptor's 16-byte address units
-              if (kFp4) umma_nvfp4_block_scaled(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc, tmem_base + kSfaCol + kSfEntry * sfb + 4 * k,
-                                                tmem_base + kSfaCol + kSfEntry * sfb + 16 + 4 * k);
+              if (kFp4) umma_nvfp4_block_scaled(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc, tmem_base + kSfaCol + kSfEntry * sfb + 32 * (kb & 1) + 4 * k,
+                                                tmem_base + kSfaCol + kSfEntry * sfb + 32 * (kb & 1) + 16 + 4 * k);
               else if (kHw) umma_f8_block_scaled(d, adesc + 2 * k, bdesc + 2 * k,
                                             kIdesc | ((uint32_t)(kb & 3) << 29) | (kFold ? 0u : (uint32_t)(kb & 3) << 4), acc,
                                             tmem_base + kSfaCol + kSfEntry * sfb, tmem_base + (kFold ? kSfbCol : kSfaCol + kSfEntry * sfb + 4));
@@ -498,47 +498,79 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const long long sf_ld = args.K / 8;                 // scale bytes per operand row (args.K counts bytes of packed e2m1)
     const uint8_t* sfa_all = reinterpret_cast<const uint8_t*>(args.sa);
     const uint8_t* sfb_all = reinterpret_cast<const uint8_t*>(args.sb);
-    constexpr int kAhead = kFp4SfSlots - 1;
+    // The copies run kAhead K blocks ahead of the stores, across tile boundaries (a second tile walker); the stores go pair by
+    // pair of K blocks (one barrier among the four warps, one TMEM ring entry, one arrival per pair).  The ring has two slots
+    // more than are in flight: the slots a pair's copies take were read one barrier earlier by every warp.
+    constexpr int kAhead = kFp4SfSlots - 2;
     TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
+    TileSched sched_i(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
     int sfb = 0; uint32_t sfphase = 0; int grp, mb, nb;
-    bool ok = true;
+    bool ok = true;                                      // a wait that ran out clears it; the warp keeps walking (its peers count on it at the barrier)
     int slot_w = 0, slot_r = 0;                          // ring slots written (copies issued) / read
-    // (A wait that runs out clears `ok`; the warp keeps walking the tiles without touching TMEM, because its three peers count on it
-    // at the named barrier.)
-    for (int tile = tile0; sched.get(tile, grp, mb, nb); tile += tile_stride) {
+    int tile_i = tile0, kb_i = 0, grp_i, mb_i, nb_i;
+    bool live_i = sched_i.get(tile_i, grp_i, mb_i, nb_i);
+    const uint8_t *pa_i = nullptr, *pb_i = nullptr;
+    auto point = [&]() {
       // this warp copies rows / columns 32 wq + lane of the tile; rows past the end read the tile's first row, columns past N the last
-      const int rows_here = sched.rows(grp) - mb * kBlockM;
+      const int rows_here = sched_i.rows(grp_i) - mb_i * kBlockM;
       const int ar = 32 * wq + lane < rows_here ? 32 * wq + lane : 0;
-      const int bc = min(nb * BLOCK_N + 32 * wq + lane, args.N - 1);
-      const uint8_t* pa = sfa_all + ((long long)grp * args.sa_group_stride + sched.row0(grp) + mb * kBlockM + ar) * sf_ld + (long long)kb_begin * 16;
-      const uint8_t* pb = sfb_all + ((long long)grp * args.N + bc) * sf_ld + (long long)kb_begin * 16;
-      auto issue = [&](int kb) {
-        if (kb < num_kb) {
-          const uint32_t dst = ring0 + slot_w * 4096 + (wq * 32 + lane) * 16;
-          cp_async16(dst, pa + (long long)kb * 16, 16u);
-          cp_async16(dst + 2048, pb + (long long)kb * 16, 16u);
-          if (++slot_w == kFp4SfSlots) slot_w = 0;
+      const int bc = min(nb_i * BLOCK_N + 32 * wq + lane, args.N - 1);
+      pa_i = sfa_all + ((long long)grp_i * args.sa_group_stride + sched_i.row0(grp_i) + mb_i * kBlockM + ar) * sf_ld + (long long)kb_begin * 16;
+      pb_i = sfb_all + ((long long)grp_i * args.N + bc) * sf_ld + (long long)kb_begin * 16;
+    };
+    if (live_i) point();
+    auto issue = [&]() {
+      if (live_i) {
+        const uint32_t dst = ring0 + slot_w * 4096 + (wq * 32 + lane) * 16;
+        cp_async16(dst, pa_i + (long long)kb_i * 16, 16u);
+        cp_async16(dst + 2048, pb_i + (long long)kb_i * 16, 16u);
+        if (++slot_w == kFp4SfSlots) slot_w = 0;
+        if (++kb_i == num_kb) {
+          kb_i = 0; tile_i += tile_stride;
+          live_i = sched_i.get(tile_i, grp_i, mb_i, nb_i);
+          if (live_i) point();
         }
-        cp_async_commit();                             // one group per K block, empty past the end: the wait below counts groups
-      };
-      for (int kb = 0; kb < kAhead; kb++) issue(kb);
-      for (int kb = 0; kb < num_kb; kb++) {
-        cp_async_wait<kAhead - 1>();                   // this warp's copies of K block kb have landed
+      }
+      cp_async_commit();                               // one group per K block, empty past the last tile: the waits below count groups
+    };
+    for (int i = 0; i < kAhead; i++) issue();
+    for (int tile = tile0; sched.get(tile, grp, mb, nb); tile += tile_stride) {
+      for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
+        const bool two = kb0 + 1 < num_kb;
+        if (two) cp_async_wait<kAhead - 2>(); else cp_async_wait<kAhead - 1>();      // this warp's copies of the pair have landed
         named_bar_sync(1, 128);                        // ... and the other three warps'
-        uint32_t wa[16], wbq[16];
-        const uint4* src = reinterpret_cast<const uint4*>(sf_ring + slot_r * 4096) + lane;
+        uint32_t w0a[16], w0b[16], w1a[16], w1b[16];
+        {
+          const uint4* src = reinterpret_cast<const uint4*>(sf_ring + slot_r * 4096) + lane;
 #pragma unroll
-        for (int g = 0; g < 4; g++) {
-          const uint4 va = src[g * 32], vb = src[128 + g * 32];
-          wa[g] = va.x; wa[4 + g] = va.y; wa[8 + g] = va.z; wa[12 + g] = va.w;
-          wbq[g] = vb.x; wbq[4 + g] = vb.y; wbq[8 + g] = vb.z; wbq[12 + g] = vb.w;
+          for (int g = 0; g < 4; g++) {
+            const uint4 va = src[g * 32], vb = src[128 + g * 32];
+            w0a[g] = va.x; w0a[4 + g] = va.y; w0a[8 + g] = va.z; w0a[12 + g] = va.w;
+            w0b[g] = vb.x; w0b[4 + g] = vb.y; w0b[8 + g] = vb.z; w0b[12 + g] = vb.w;
+          }
+          if (++slot_r == kFp4SfSlots) slot_r = 0;
         }
-        if (++slot_r == kFp4SfSlots) slot_r = 0;
-        issue(kb + kAhead);                            // the slot it takes was read one barrier ago by every warp
+        if (two) {
+          const uint4* src = reinterpret_cast<const uint4*>(sf_ring + slot_r * 4096) + lane;
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            const uint4 va = src[g * 32], vb = src[128 + g * 32];
+            w1a[g] = va.x; w1a[4 + g] = va.y; w1a[8 + g] = va.z; w1a[12 + g] = va.w;
+            w1b[g] = vb.x; w1b[4 + g] = vb.y; w1b[8 + g] = vb.z; w1b[12 + g] = vb.w;
+          }
+          if (++slot_r == kFp4SfSlots) slot_r = 0;
+        }
+        issue();
+        if (two) issue();
         if (ok && mbar_wait(sfempty0 + 8 * sfb, sfphase ^ 1, abort_flag, kKernelGemm, 520 + sfb)) {
           tc_fence_after();
-          tmem_st_32x32b_x16(tmem_base + lane_addr + kSfaCol + kSfEntry * sfb, wa);
-          tmem_st_32x32b_x16(tmem_base + lane_addr + kSfaCol + kSfEntry * sfb + 16, wbq);
+          const uint32_t ent = tmem_base + lane_addr + kSfaCol + kSfEntry * sfb;
+          tmem_st_32x32b_x16(ent, w0a);
+          tmem_st_32x32b_x16(ent + 16, w0b);
+          if (two) {
+            tmem_st_32x32b_x16(ent + 32, w1a);
+            tmem_st_32x32b_x16(ent + 48, w1b);
+          }
           tc_wait_st();
           tc_fence_before();
           __syncwarp();
@@ -548,8 +580,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           ok = false;
         }
       }
-      cp_async_wait<0>();
     }
+    cp_async_wait<0>();
   } else if (kHw && warp >= 2 + 4 * kEpi) {
     // ---------------- scale-factor warps: warp w fills TMEM lanes [32*(w%4), +32) ----------------
     const int lane = (int)lane_id();
