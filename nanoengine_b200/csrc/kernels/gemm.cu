@@ -80,10 +80,10 @@ struct GemmArgs {
 };
 
 constexpr int kFp4SfSlots = 8;          // NVFP4: shared-memory ring of scale-factor tiles (one K block each, 4 KB), 6 in flight
-template <int BLOCK_N, bool kFp4 = false> struct Smem {
+template <int BLOCK_N, bool kFp4 = false, bool kPair = false> struct Smem {
   static constexpr int kABytes = kBlockM * kKBytes;
-  static constexpr int kBBytes = BLOCK_N * kKBytes;
-  static constexpr int kG = KGroup<BLOCK_N, kFp4>::value;
+  static constexpr int kBBytes = (kPair ? BLOCK_N / 2 : BLOCK_N) * kKBytes;      // a CTA of a pair holds half of B's rows
+  static constexpr int kG = kPair ? 2 : KGroup<BLOCK_N, kFp4>::value;
   static constexpr int kSfRing = kFp4 ? kFp4SfSlots * 4096 : 0;
   static constexpr int kStageBytes = kG * (kABytes + kBBytes);
   static constexpr int kStaging = 8 * 32 * 80;      // per-warp epilogue staging for up to 8 epilogue warps
@@ -108,23 +108,27 @@ struct TileSched {
   const int* base;                      // shared memory: first tile of every group, total at [groups]; null = none built
   int g = 0, walked = 0;
   int mb_rot = 0;                       // dense single-group GEMMs only: row blocks are visited starting at this one
-  __device__ TileSched(int groups_, int M_, int nb, const int* mm, const int* rs, const int* base_, int rot = 0)
-      : groups(groups_), M(M_), n_blocks(nb), masked_m(mm), row_start(rs), base(base_), mb_rot(rot) {}
+  int bm = kBlockM, sub = 0;            // CTA pairs: tiles are 256 rows tall, `sub` (0 / 1) is this CTA's 128-row block of the tile
+  __device__ TileSched(int groups_, int M_, int nb, const int* mm, const int* rs, const int* base_, int rot = 0, int bm_ = kBlockM, int sub_ = 0)
+      : groups(groups_), M(M_), n_blocks(nb), masked_m(mm), row_start(rs), base(base_), mb_rot(rot), bm(bm_), sub(sub_) {}
+  // the caller's row block index counts 128-row blocks
+  __device__ int blk(int mb) const { return bm == kBlockM ? mb : mb * 2 + sub; }
   __device__ int row0(int grp) const { return row_start ? row_start[grp] : 0; }
   __device__ int rows(int grp) const {
     int r = masked_m ? masked_m[grp] : M;
     int cap = row_start ? M - row_start[grp] : M;      // never step outside the buffer, whatever the counts say
     return r < cap ? r : (cap > 0 ? cap : 0);
   }
-  __device__ int tiles_of(int grp) const { return ((rows(grp) + kBlockM - 1) / kBlockM) * n_blocks; }
+  __device__ int tiles_of(int grp) const { return ((rows(grp) + bm - 1) / bm) * n_blocks; }
   __device__ bool get(int tile, int& grp, int& mb, int& nb) {
     if (!masked_m && !row_start) {                      // every group has the same shape
-      const int per = ((M + kBlockM - 1) / kBlockM) * n_blocks;
+      const int per = ((M + bm - 1) / bm) * n_blocks;
       if (tile >= per * groups) return false;
       grp = tile / per;
       const int l = tile - grp * per;
       mb = l / n_blocks; nb = l - mb * n_blocks;
-      if (mb_rot) { const int mbs = (M + kBlockM - 1) / kBlockM; mb += mb_rot; if (mb >= mbs) mb -= mbs; }
+      if (mb_rot) { const int mbs = (M + bm - 1) / bm; mb += mb_rot; if (mb >= mbs) mb -= mbs; }
+      mb = blk(mb);
       return true;
     }
     if (base) {
@@ -133,12 +137,12 @@ struct TileSched {
       while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (base[mid] <= tile) lo = mid; else hi = mid - 1; }
       g = grp = lo;
       const int l = tile - base[lo];
-      mb = l / n_blocks; nb = l - mb * n_blocks;
+      mb = blk(l / n_blocks); nb = l % n_blocks;
       return true;
     }
     while (g < groups) {
       const int cnt = tiles_of(g);
-      if (tile < walked + cnt) { const int l = tile - walked; grp = g; mb = l / n_blocks; nb = l % n_blocks; return true; }
+      if (tile < walked + cnt) { const int l = tile - walked; grp = g; mb = blk(l / n_blocks); nb = l % n_blocks; return true; }
       walked += cnt; g++;
     }
     return false;
@@ -237,12 +241,19 @@ constexpr int kSfBufsMax = 8;
 // row of A and B: the four scale warps bring them in with 16-byte cp.async copies, six K blocks ahead, through a ring in shared
 // memory (each warp a quarter of the rows), and store them to TMEM as 16 + 16 columns per K block (column 4 i + g: instruction i of
 // the K block, rows 32 g .. 32 g + 31 of the tile).
-template <int BLOCK_N, bool kFP8, bool kBlockScaled, bool kSplit, int kMode = 0>
+// kPair (with kMode 1): two CTAs of a cluster work on one 256-row tile with tcgen05.mma.cta_group::2.  Each holds its 128 rows of A
+// and half of B's rows in its own shared memory (a third less operand traffic per SM than two separate 128 x BLOCK_N tiles), its
+// 128 accumulator rows and scale factors in its own TMEM.  The pair's first CTA issues the MMAs once both CTAs' loads have landed
+// (both count their bytes on its "full" barrier), and commits to the barriers of both; the second CTA's epilogue and scale warps
+// report to the first CTA's barriers.
+template <int BLOCK_N, bool kFP8, bool kBlockScaled, bool kSplit, int kMode = 0, bool kPair = false>
 __global__ void __launch_bounds__((EpiCfg<BLOCK_N, kBlockScaled, kMode != 0>::kThreads), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a64, const __grid_constant__ CUtensorMap tmap_a32,
             const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
   constexpr bool kHw = kMode != 0, kFp4 = kMode == 2;
-  using S = Smem<BLOCK_N, kFp4>;
+  static_assert(!kPair || (kMode == 1 && !kSplit), "CTA pairs: the tensor-core-scaled fp8 GEMM");
+  using S = Smem<BLOCK_N, kFp4, kPair>;
+  constexpr int kTileM = kPair ? 2 * kBlockM : kBlockM;
   constexpr int kStages = S::kStages;
   constexpr int kG = S::kG;
   constexpr int kElemsPerStageK = kFP8 ? 128 : 64;
@@ -264,7 +275,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   static_assert(kColsUsed <= 512 && kSfBufs <= kSfBufsMax, "TMEM holds 512 columns");
   constexpr uint32_t kTmemCols = kColsUsed <= 32 ? 32 : (kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512)));
   constexpr uint32_t kIdesc = kFp4 ? make_idesc_block_scaled(FMT_E2M1_MXF4, FMT_E2M1_MXF4, kBlockM, BLOCK_N, 0)
-                              : kHw ? make_idesc_block_scaled(FMT_E4M3, FMT_E4M3, kBlockM, BLOCK_N)
+                              : kHw ? make_idesc_block_scaled(FMT_E4M3, FMT_E4M3, kTileM, BLOCK_N)
                                   : make_idesc(kFP8 ? FMT_E4M3 : FMT_BF16, kFP8 ? FMT_E4M3 : FMT_BF16, kBlockM, BLOCK_N);
   constexpr int kEpi = EpiCfg<BLOCK_N, kBlockScaled>::kGroups;
   constexpr int kCols = BLOCK_N / kEpi;          // columns of the tile each epilogue thread owns
@@ -291,19 +302,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int num_kb = total_kb / split;                 // the host picks a split that divides the K blocks
   const int num_st = (num_kb + kG - 1) / kG;           // pipeline stages' worth of K blocks per tile
   const int kb_begin = srank * num_kb;
-  const int tile0 = kSplit ? (int)blockIdx.x / split : (int)blockIdx.x;
-  const int tile_stride = kSplit ? (int)gridDim.x / split : (int)gridDim.x;
+  const int prank = kPair ? (int)cluster_ctarank() : 0;     // 0: the CTA of a pair that issues the MMAs
+  const int tile0 = kSplit ? (int)blockIdx.x / split : (kPair ? (int)blockIdx.x / 2 : (int)blockIdx.x);
+  const int tile_stride = kSplit ? (int)gridDim.x / split : (kPair ? (int)gridDim.x / 2 : (int)gridDim.x);
+  // a barrier of the pair's first CTA, as seen from this one; arrivals there from either CTA
+  auto lead = [&](uint32_t bar) { return kPair ? mapa_shared(bar, 0u) : bar; };
+  auto arrive_lead = [&](uint32_t bar) { if (kPair && prank != 0) mbar_arrive_cluster(mapa_shared(bar, 0u)); else mbar_arrive(bar); };
+  // completion of the MMAs issued so far, signalled to the same barrier of both CTAs
+  auto commit = [&](uint32_t bar) { if (kPair) { tc_commit_pair(bar); tc_commit_pair(mapa_shared(bar, 1u)); } else tc_commit(bar); };
 
   // set-up that touches no global memory comes first: under a programmatic dependent launch it overlaps the previous kernel's tail
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; i++) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
-    for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4 * kEpi); }
-    if (kHw) for (int i = 0; i < kSfBufs; i++) { mbar_init(sffull0 + 8 * i, 4); mbar_init(sfempty0 + 8 * i, 1); }
+    for (int i = 0; i < kAcc; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4 * kEpi * (kPair ? 2 : 1)); }
+    if (kHw) for (int i = 0; i < kSfBufs; i++) { mbar_init(sffull0 + 8 * i, kPair ? 8 : 4); mbar_init(sfempty0 + 8 * i, 1); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_a64); tma_prefetch_desc(&tmap_a32); tma_prefetch_desc(&tmap_b);
   }
-  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
+  if (warp == 1) {
+    if (kPair) { tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
+  }
   pdl_wait();                                          // from here on the previous kernel's results may be read, and ours written
   pdl_trigger();
   const GemmComm& cm = args.comm;
@@ -339,7 +359,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int* base_tab = (ragged && cache_tables) ? s_base : nullptr;
   if (base_tab) {
     __syncthreads();                                   // the row tables above are complete
-    TileSched cnt(args.groups, args.M, n_blocks, mm_tab, rs_tab, nullptr);
+    TileSched cnt(args.groups, args.M, n_blocks, mm_tab, rs_tab, nullptr, 0, kTileM, 0);
     for (int i = threadIdx.x; i < args.groups; i += blockDim.x) s_base[i + 1] = cnt.tiles_of(i);
     __syncthreads();
     if (warp == 2) {
@@ -358,13 +378,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();          // the peer's barriers are initialised before anything is signalled to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (elect_one()) {
-      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
+      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot, kTileM, prank);
       int stage = 0; uint32_t phase = 0; int grp, mb, nb;
       bool ok = true;
       const int gate_ep = cm.gate_flags ? *cm.gate_epoch + 1 : 0;
@@ -386,13 +407,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // a tile with few valid rows (decode: a handful of tokens per expert) fetches only the first 32 or 64 rows of
         // the activation block; the MMA still spans 128 rows, whose stale remainder lands in output rows nobody stores
         const int rows_here = sched.rows(grp) - mb * kBlockM;
-        const CUtensorMap* ta = rows_here <= 32 ? &tmap_a32 : (rows_here <= 64 ? &tmap_a64 : &tmap_a);
-        const uint32_t a_bytes = rows_here <= 32 ? 32 * kKBytes : (rows_here <= 64 ? 64 * kKBytes : S::kABytes);
+        const CUtensorMap* ta = kPair ? &tmap_a : (rows_here <= 32 ? &tmap_a32 : (rows_here <= 64 ? &tmap_a64 : &tmap_a));
+        const uint32_t a_bytes = kPair ? S::kABytes : (rows_here <= 32 ? 32 * kKBytes : (rows_here <= 64 ? 64 * kKBytes : S::kABytes));
         for (int st = 0; st < num_st; st++) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, kKernelGemm, 100 + stage)) { ok = false; break; }
           uint32_t a_dst = smem_base + stage * S::kStageBytes, b_dst = a_dst + kG * S::kABytes;
-          mbar_expect_tx(full0 + 8 * stage, kG * (a_bytes + S::kBBytes));      // chunks past the end of K arrive as zeros
           const int kc = kb_begin + st * kG;
+          if (kPair) {
+            // both CTAs' bytes are counted on the first CTA's barrier, which alone announces them
+            if (prank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * kG * (S::kABytes + S::kBBytes));
+            const uint32_t fb = lead(full0 + 8 * stage);
+            tma_load_4d_pair(a_dst, ta, fb, 0, a_row_off + sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, kc);
+            tma_load_4d_pair(b_dst, &tmap_b, fb, 0, nb * BLOCK_N + prank * (BLOCK_N / 2), grp, kc);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+            continue;
+          }
+          mbar_expect_tx(full0 + 8 * stage, kG * (a_bytes + S::kBBytes));      // chunks past the end of K arrive as zeros
           if (!args.k_flat) {
             if (args.a_group_inner) tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, grp, mb * kBlockM, kc);
             else tma_load_4d(a_dst, ta, full0 + 8 * stage, 0, a_row_off + sched.row0(grp) + mb * kBlockM, args.row_start ? 0 : grp, kc);
@@ -412,8 +442,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (elect_one()) {
-      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
+    if ((!kPair || prank == 0) && elect_one()) {
+      TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot, kTileM, prank);
       int stage = 0; uint32_t phase = 0; int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
       bool ok = true;
       // A test of an mbarrier costs ~150 cycles even when the phase has long completed, and this thread is the serial
@@ -430,7 +460,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         // the activation box of this tile (see the producer): its K blocks sit a_kstride apart inside the stage
         const int rows_here = sched.rows(grp) - mb * kBlockM;
-        const uint32_t a_kstride = rows_here <= 32 ? 32 * kKBytes : (rows_here <= 64 ? 64 * kKBytes : S::kABytes);
+        const uint32_t a_kstride = kPair ? S::kABytes : (rows_here <= 32 ? 32 * kKBytes : (rows_here <= 64 ? 64 * kKBytes : S::kABytes));
         for (int st = 0; st < num_st && ok; st++) {
           if (!pre_full && !mbar_wait(full0 + 8 * stage, phase, abort_flag, kKernelGemm, 300 + stage)) { ok = false; break; }
           tc_fence_after();
@@ -470,21 +500,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               // advancing 32 bytes along K inside the 128B swizzle atom = +2 in the descriptor's 16-byte address units
               if (kFp4) umma_nvfp4_block_scaled(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc, tmem_base + kSfaCol + kSfEntry * sfb + 32 * (kb & 1) + 4 * k,
                                                 tmem_base + kSfaCol + kSfEntry * sfb + 32 * (kb & 1) + 16 + 4 * k);
+              else if (kPair) umma_f8_block_scaled_pair(d, adesc + 2 * k, bdesc + 2 * k,
+                                            kIdesc | ((uint32_t)(kb & 3) << 29) | (kFold ? 0u : (uint32_t)(kb & 3) << 4), acc,
+                                            tmem_base + kSfaCol + kSfEntry * sfb, tmem_base + (kFold ? kSfbCol : kSfaCol + kSfEntry * sfb + 4));
               else if (kHw) umma_f8_block_scaled(d, adesc + 2 * k, bdesc + 2 * k,
                                             kIdesc | ((uint32_t)(kb & 3) << 29) | (kFold ? 0u : (uint32_t)(kb & 3) << 4), acc,
                                             tmem_base + kSfaCol + kSfEntry * sfb, tmem_base + (kFold ? kSfbCol : kSfaCol + kSfEntry * sfb + 4));
               else if (kFP8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
               else umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
             }
-            if (chunk_end) { tc_commit(sfempty0 + 8 * sfb); if (++sfb == kSfBufs) { sfb = 0; sfphase ^= 1; } }
+            if (chunk_end) { commit(sfempty0 + 8 * sfb); if (++sfb == kSfBufs) { sfb = 0; sfphase ^= 1; } }
             if (kBlockScaled) { tc_commit(tfull0 + 8 * buf); if (++buf == kAcc) { buf = 0; bphase ^= 1; } }
           }
-          tc_commit(empty0 + 8 * stage);                // smem slot reusable once these MMAs retire
+          commit(empty0 + 8 * stage);                   // smem slot reusable once these MMAs retire
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         if (!kBlockScaled) {
-          tc_commit(tfull0 + 8 * buf);
+          commit(tfull0 + 8 * buf);
           if (++buf == kAcc) { buf = 0; bphase ^= 1; }
           pre_te = mbar_test(tempty0 + 8 * buf, bphase ^ 1);
         }
@@ -502,8 +535,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // pair of K blocks (one barrier among the four warps, one TMEM ring entry, one arrival per pair).  The ring has two slots
     // more than are in flight: the slots a pair's copies take were read one barrier earlier by every warp.
     constexpr int kAhead = kFp4SfSlots - 2;
-    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
-    TileSched sched_i(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
+    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot, kTileM, prank);
+    TileSched sched_i(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot, kTileM, prank);
     int sfb = 0; uint32_t sfphase = 0; int grp, mb, nb;
     bool ok = true;                                      // a wait that ran out clears it; the warp keeps walking (its peers count on it at the barrier)
     int slot_w = 0, slot_r = 0;                          // ring slots written (copies issued) / read
@@ -586,7 +619,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ---------------- scale-factor warps: warp w fills TMEM lanes [32*(w%4), +32) ----------------
     const int lane = (int)lane_id();
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
+    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot, kTileM, prank);
     int sfb = 0; uint32_t sfphase = 0; int grp, mb, nb;
     bool ok = true, first = true;
     for (int tile = tile0; ok && sched.get(tile, grp, mb, nb); tile += tile_stride) {
@@ -598,7 +631,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       first = false;
       // rows lane + 32 g of the tile; rows past the group's end read the tile's first row (their results are never stored)
       const int rows_here = sched.rows(grp) - mb * kBlockM;
-      const float* sa = args.sa + (long long)grp * args.sa_group_stride + sched.row0(grp) + mb * kBlockM + (long long)kb_begin * args.sa_ld;
+      // (a pair's second CTA may stand past the group's last row: it reads the group's first row instead)
+      const float* sa = args.sa + (long long)grp * args.sa_group_stride + sched.row0(grp) + (rows_here > 0 ? mb * kBlockM : 0) + (long long)kb_begin * args.sa_ld;
       // weight blocks under the tile: one when folded, up to three under a wide tile
       constexpr int kNB = kFold ? 1 : 3;
       const int nblk = (args.N + 127) / 128, b0 = nb * BLOCK_N / 128;
@@ -669,7 +703,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               tc_wait_st();
               tc_fence_before();
               __syncwarp();
-              if (lane == 0) mbar_arrive(sffull0 + 8 * sfb);
+              if (lane == 0) arrive_lead(sffull0 + 8 * sfb);
               if (++sfb == kSfBufs) { sfb = 0; sfphase ^= 1; }
             } else {
               ok = false;
@@ -684,7 +718,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int cbase = ((warp - 2) >> 2) * kCols;   // column offset of this warp's group inside the tile
     const int row_in_tile = wq * 32 + (int)lane_id();
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot);
+    TileSched sched(args.groups, args.M, n_blocks, mm_tab, rs_tab, base_tab, cm.mb_rot, kTileM, prank);
     int buf = 0; uint32_t bphase = 0; int grp, mb, nb;
     bool ok = true;
     bool pre_tf = false;                               // result of an early test of the next accumulator's "full" barrier
@@ -829,7 +863,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         tc_fence_before();
         __syncwarp();
-        if (lane_id() == 0) mbar_arrive(tempty0 + 8 * buf);
+        if (lane_id() == 0) arrive_lead(tempty0 + 8 * buf);
         if (++buf == kAcc) { buf = 0; bphase ^= 1; }
       }
     }
@@ -870,7 +904,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int i = 0; i < 2000; i++) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+  if (kPair) cluster_sync_all();          // neither CTA frees its TMEM or leaves while the other may still signal it or read its tiles
+  if (warp == 1) {
+    tc_fence_after();
+    if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
+  }
   if (cm.tail_counter) {
     // every thread orders its own (possibly peer-memory) stores before the count; the CTA that counts last speaks for the grid
     __threadfence_system();
@@ -933,6 +971,7 @@ static int get_tmap_kmajor(CUtensorMap* out, const void* base, bool fp8, uint64_
 }
 
 static bool g_split_k_enabled = true;
+static bool g_pair_enabled = true;
 
 static int num_sms() {
   static int n = 0;
@@ -952,6 +991,38 @@ static int launch(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs&
     configured = true;
   }
   return (int)launch_pdl(kern, dim3((unsigned)grid), dim3(EpiCfg<BLOCK_N, kBS, kHw>::kThreads), S::kBytes, st, tas[0], tas[1], tas[2], tb, a);
+}
+
+// CTA-pair form of the tensor-core-scaled fp8 GEMM: clusters of two CTAs, one 256-row tile per pair
+template <int BLOCK_N>
+static int launch_pair(const CUtensorMap* tas, const CUtensorMap& tb, const GemmArgs& a, int pairs, cudaStream_t st) {
+  auto kern = gemm_kernel<BLOCK_N, true, false, false, 1, true>;
+  using S = Smem<BLOCK_N, false, true>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(pairs * 2), 1, 1);
+  cfg.blockDim = dim3(EpiCfg<BLOCK_N, false, true>::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  // one pair per two SMs that can host a cluster: asked of the driver once (74 on a B200; 72 if it does not say)
+  static int resident = 0;
+  if (!resident) {
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    resident = (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) ? n : (num_sms() / 16) * 8;
+  }
+  if (pairs > resident) pairs = resident;
+  cfg.gridDim = dim3((unsigned)(pairs * 2), 1, 1);
+  pdl_attr(cfg, attr, 1);
+  return (int)cudaLaunchKernelEx(&cfg, kern, tas[0], tas[1], tas[2], tb, a);
 }
 
 // split-K form: `tiles` clusters of `split` CTAs
@@ -1071,7 +1142,11 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
     if (N >= 224 && cost(224) < cost(bn)) bn = 224;
   }
   if (fp8 && bn > 128 && !(hw && bn == 224)) bn = 128;
-  const int kg = bn >= 192 ? 1 : 2;      // KGroup<bn>::value
+  // CTA pairs (256-row tiles) where every group has rows for several of them; not with a fused collective
+  // and a long K loop to spread the two-CTA hand-overs of a tile over (measured: +2 % at K = 7168 / 16384 with N >= 4096, -13 % at
+  // K = 2048)
+  const bool pair = hw && bn == 224 && g_pair_enabled && !comm && !row_dst && (row_start ? M / groups : M) >= 512 && K >= 4096 && N >= 4096;
+  const int kg = pair ? 2 : (bn >= 192 ? 1 : 2);      // KGroup<bn>::value
   CUtensorMap ta[3], tb;       // activation maps with 128-, 64- and 32-row boxes
   if (row_start || groups == 1) a_gs = (long long)(a_rows_total > 0 ? a_rows_total : M) * lda;
   int rc = 0;
@@ -1079,7 +1154,7 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
     rc = get_tmap_kmajor(&ta[i], A, fp8, (uint64_t)K, (uint64_t)(a_rows_total > 0 ? a_rows_total : M), (uint64_t)(row_start ? 1 : groups), (uint64_t)lda,
                          (uint64_t)a_gs, kBlockM >> i, kg);
   if (rc) return 2000 + rc;
-  rc = get_tmap_kmajor(&tb, B, fp8, (uint64_t)K, (uint64_t)N, (uint64_t)groups, (uint64_t)K, (uint64_t)N * K, (uint32_t)bn, kg);
+  rc = get_tmap_kmajor(&tb, B, fp8, (uint64_t)K, (uint64_t)N, (uint64_t)groups, (uint64_t)K, (uint64_t)N * K, (uint32_t)(pair ? bn / 2 : bn), kg);
   if (rc) return 3000 + rc;
   GemmArgs a;
   a.a_group_inner = (!row_start && groups > 1 && a_gs < lda) ? 1 : 0;
@@ -1094,6 +1169,10 @@ static int gemm_impl(const void* A, long long lda, long long a_gs, const void* B
   else memset(&a.comm, 0, sizeof(a.comm));
   long long tiles = (long long)groups * m_blocks * ((N + bn - 1) / bn);
   int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+  if (pair) {
+    const long long ptiles = (row_start ? (long long)(M + 255) / 256 + groups : (long long)groups * ((M + 255) / 256)) * ((N + bn - 1) / bn);
+    return launch_pair<224>(ta, tb, a, (int)(ptiles < 4096 ? ptiles : 4096), stream);      // capped at the resident pairs by the launcher
+  }
   if (hw) {
     switch (bn) {
       case 224: return launch<224, true, false, 1>(ta, tb, a, grid, stream);
@@ -1188,6 +1267,9 @@ extern "C" int ne_set_scale_pow2(int on) { int was = g_scale_pow2; g_scale_pow2 
 
 // Turn the cluster split-K plan of small-M dense GEMMs on or off (on by default); returns the previous setting.
 extern "C" int ne_gemm_set_split_k(int on) { int was = g_split_k_enabled ? 1 : 0; g_split_k_enabled = on != 0; return was; }
+
+// Turn the CTA-pair form of the tensor-core-scaled fp8 GEMM on or off (on by default); returns the previous setting.
+extern "C" int ne_gemm_set_pair(int on) { int was = g_pair_enabled ? 1 : 0; g_pair_enabled = on != 0; return was; }
 
 // Debug build only: register the bounds the checked kernels compare their table entries with (0 = leave unchecked).  Returns 1 when
 // this library was built with the checks, 0 otherwise (the call is then a no-op).

@@ -79,6 +79,54 @@ def test_gemm_fp8_hw_scaled(k, M, N, K):
     assert _rel(got, x.float() @ w.t()) < 7e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 4096), (1000, 7168, 4224), (640, 7168, 4096), (2047, 4256, 5120)])
+def test_gemm_fp8_cta_pairs_equal_single_ctas(k, M, N, K):
+    """256-row tiles worked on by two CTAs (tcgen05.mma.cta_group::2, each CTA half of B's rows) against the same GEMM on single
+    CTAs and against the fp32 statement; row counts that leave the second CTA of the last pair partly or wholly without rows."""
+    x, w = _ragged_magnitudes(M, K, N, 11)
+    wq, ws = ref.quant_fp8_block(w)
+    want = ref.linear(x, wq, ws)
+    xq, xs = k.quant_fp8_1x128_raw(x)
+    lib = k.lib()
+
+    def run():
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        k._gemm(xq, K, 0, wq, out, N, 0, M, N, K, 1, None, None, True, xs, M, 0, ws, False, bn=224)
+        return out
+
+    pair = run()
+    was = lib.ne_gemm_set_pair(0)
+    try:
+        single = run()
+    finally:
+        lib.ne_gemm_set_pair(was)
+    assert _rel(pair, want) < 5e-3 and _rel(single, want) < 5e-3
+    row_err = (pair.float() - want.float()).norm(dim=1) / want.float().norm(dim=1).clamp_min(1e-12)
+    assert row_err.max().item() < 2e-2, row_err.argmax().item()
+    assert torch.equal(pair, single)          # the same products summed in the same order
+
+
+def test_grouped_gemm_fp8_cta_pairs(k):
+    """Contiguous grouped layout with groups of 0, 130, 600 and 1000 rows: pair tiles that end inside the next group's rows store only
+    their own."""
+    gen = torch.Generator(device="cuda").manual_seed(12)
+    E, N, K = 4, 4480, 4096
+    counts = torch.tensor([600, 130, 0, 1000], dtype=torch.int32, device="cuda")
+    starts = torch.tensor([0, 640, 896, 896, 1920], dtype=torch.int32, device="cuda")
+    R = 2048
+    x = (torch.randn(R, K, device="cuda", generator=gen) * torch.exp2(torch.randint(-4, 5, (R, 1), device="cuda", generator=gen).float())).to(torch.bfloat16)
+    w = torch.randn(E, N, K, device="cuda", generator=gen) * 0.05
+    wq, ws = ref.quant_fp8_block(w)
+    xq, xs = k.quant_fp8_1x128_raw(x)
+    out = torch.full((R, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    k._gemm(xq, K, 0, wq, out, N, 0, R, N, K, E, counts, starts, True, xs, R, 0, ws, False, bn=224)
+    for e in range(E):
+        lo, n = int(starts[e]), int(counts[e])
+        if n:
+            assert _rel(out[lo:lo + n], ref.linear(x[lo:lo + n], wq[e], ws[e])) < 5e-3, e
+    assert bool((out[600:640] == 7.0).all()) and bool((out[770:896] == 7.0).all())          # rows between the groups stay untouched
+
+
 @pytest.mark.parametrize("bn", [32, 64, 128, 224])      # 224: tiles straddle up to three weight blocks, B's scale factors are per column
 def test_gemm_fp8_hw_scaled_every_tile_width(k, bn):
     M, N, K = 200, 768, 1536
