@@ -45,6 +45,7 @@ def main():
     ap.add_argument("--out-len", type=int, default=64)
     ap.add_argument("--max-num-seqs", type=int, default=128)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--scale-format", default="ue8m0", choices=["fp32", "ue8m0"], help="fp8 block scales (see bench.py)")
     args = ap.parse_args()
 
     import torch
@@ -69,7 +70,7 @@ def main():
     kw = dict(model=args.model, model_config=mc, dummy_weight=True, device=args.device, max_num_seqs=S,
               max_model_len=P + O + 64, enable_prefix_caching=False, seed=rank)
     if cuda:
-        kw.update(dtype="bfloat16", kv_cache_dtype="fp8", max_num_batched_tokens=16384, num_kvcache_blocks=S * pages + 16,
+        kw.update(dtype="bfloat16", kv_cache_dtype="fp8", fp8_scale_format=args.scale_format, max_num_batched_tokens=16384, num_kvcache_blocks=S * pages + 16,
                   attention_dp=N, ffn_ep=N, executor_backend="spmd" if N > 1 else "inproc", cuda_graph_max_bs=S)
     else:
         kw.update(dtype="float32", kvcache_block_size=16, num_kvcache_blocks=max(64, S * ((P + O) // 16 + 2)))

@@ -141,7 +141,7 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint
                ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 // CTA-pair form: the data lands in this CTA's shared memory, the bytes are counted on `bar`, which may belong to the other CTA of
-// the pair (its shared::cluster address).  No multicast: each CTA fetches its own tile.
+// the pair (its shared::cluster address).  Each CTA fetches its own tile.
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void* tmap, uint32_t bar, int x, int y, int z, int w) {
   asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
