@@ -135,10 +135,10 @@ def test_prefill_gpu_pushes_pages_into_the_decode_gpus_pool():
     assert res["prefill"][2] == 0 and res["decode"][2] == 0, f"prefill: {res['prefill'][1]}\ndecode: {res['decode'][1]}"
     want, results, free = res["decode"][1]
     ids = sorted(want)
-    # round 1: every request decodes to the hybrid engine's tokens (sequence ids differ between engines, order does not)
+    # first pass: every request decodes to the hybrid engine's tokens (sequence ids differ between engines, order does not)
     got0 = results[0]
     assert [got0[k] for k in sorted(got0)] == [want[k] for k in ids]
-    # round 2: the request whose push never ran is dropped, the others still match; its pages went back to the pool
+    # second pass: the request whose push never ran is dropped, the others still match; its pages went back to the pool
     got1 = results[1]
     assert len(got1) == 2
     assert [got1[k] for k in sorted(got1)] == [want[ids[0]], want[ids[2]]]
