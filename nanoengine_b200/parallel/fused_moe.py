@@ -124,15 +124,16 @@ class FusedEP:
         if self.fp8:
             aq = self.b_aq.view(FP8, (E, C, H))
             a_s = self.b_as.view(torch.float32, (E, H // 128, C))
-            # about 128 rows per local expert or fewer (decode): one wave of weight-bound tiles, where the kernel that applies the
-            # scales on the CUDA cores is the faster one under either scale format
+            # about 128 rows per local expert or fewer (decode): weight-bound tiles.  Measured on the DeepSeek-V3 shapes with 32 rows
+            # per expert: gate_up (N = 4096) 167 us with the scales on the CUDA cores against 170 us on the tensor cores, down
+            # (N = 7168 = 32 x 224) 99 us against 85 us; so only the first GEMM keeps the CUDA-core scaling
             few = T * K * self.layout.world <= 128 * E * self.layout.world
             _k._gemm_comm(aq, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, cnt, True, a_s, C,
                           (H // 128) * C, experts.gate_up_scale, c1, few_rows=few)
             _k._ck(lib.ne_act_mul(_k._p(self.g), _k._p(None), _k._p(self.h_q), _k._p(self.h_s), _c.c_int(C), _c.c_longlong((I // 128) * C),
                                   _c.c_void_p(cnt), _k._p(None), _c.c_int(E), _c.c_int(C), _c.c_int(I), *act, st), "ne_act_mul")
             _k._gemm_comm(self.h_q, I, C * I, experts.down_proj, self.g, H, 0, C, H, I, E, cnt, True, self.h_s, C,
-                          (I // 128) * C, experts.down_scale, c2, few_rows=few)
+                          (I // 128) * C, experts.down_scale, c2, few_rows=few and H % 224 != 0)
         else:
             ab = self.b_abf.view(torch.bfloat16, (E, C, H))
             _k._gemm_comm(ab, H, C * H, experts.gate_up_proj, self.g, 2 * I, C * 2 * I, C, 2 * I, H, E, cnt, False, None, 0, 0, None, c1)
