@@ -2,7 +2,12 @@
 Parity: reference dlengine/router.py (shim around the Rust `dlengine-router` binary)."""
 import sys
 
-from .server.cli import main
+from .server.cli import main as _cli_main
+
+
+def main(argv=None) -> int:
+    return _cli_main(["router", *(sys.argv[1:] if argv is None else argv)])
+
 
 if __name__ == "__main__":
-    sys.exit(main(["router", *sys.argv[1:]]))
+    sys.exit(main())
