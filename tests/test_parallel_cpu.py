@@ -33,6 +33,20 @@ def test_dp2_ep2_matches_single_rank():
     assert got == want
 
 
+def test_dp2_ep2_nvfp4_experts_match_single_rank():
+    """NVFP4 routed experts under attention-DP + EP: every rank holds half of the experts in the packed form, the GEMM-1 activation
+    scale is agreed on with a MAX over the EP group when the experts are first used, and the tokens equal the single-rank run."""
+    from nanoengine_b200.models.config import tiny_deepseek_v3
+    mc = tiny_deepseek_v3(moe_intermediate_size=256, intermediate_size=512, quant="nvfp4")
+    base = dict(model="tiny-deepseek-v3", model_config=mc, dummy_weight=True, dtype="float32", device="cpu", kvcache_block_size=16,
+                max_num_seqs=8, num_kvcache_blocks=64)
+    prompts = _prompts(3, 24, 4, 1024)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = _run(Config(**base), prompts, sp)
+    got = _run(Config(**base, attention_dp=2, ffn_ep=2), prompts, sp)
+    assert got == want
+
+
 def test_dp2_ep2_hybrid_delta_net_moe_matches_single_rank():
     """The hybrid family under attention-DP + EP: every rank keeps its own recurrent-state pool; a rank without work runs a dummy
     batch on the scratch state slot."""
