@@ -75,6 +75,7 @@ class Config:
     profiler_dir: Optional[str] = None
     # serving / PD
     engine_id: str = "engine-0"
+    engine_endpoint: Optional[str] = None    # ZMQ endpoint of the engine process behind the HTTP server (default: a fresh ipc:// path); what a decode engine's pd_peers names
     ctrl_address: Optional[str] = None
     host: str = "127.0.0.1"
     port: int = 8000

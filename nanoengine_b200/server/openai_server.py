@@ -377,7 +377,7 @@ def run_server(config, host: Optional[str] = None, port: Optional[int] = None, t
     """Spawn the engine process, then serve HTTP in this one."""
     import uvicorn
     from .engine_server import EngineClient, spawn_backend
-    proc, endpoint = spawn_backend(config)
+    proc, endpoint = spawn_backend(config, endpoint=getattr(config, "engine_endpoint", None))
     client = EngineClient(endpoint, proc)
     tok = load_tokenizer(config.model, config.model_config.vocab_size)
     app = create_app(client, tok, model_name=config.model, tool_format=tool_format, mode=config.mode)
