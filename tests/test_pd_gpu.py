@@ -143,3 +143,58 @@ def test_prefill_gpu_pushes_pages_into_the_decode_gpus_pool():
     assert len(got1) == 2
     assert [got1[k] for k in sorted(got1)] == [want[ids[0]], want[ids[2]]]
     assert free == 48
+
+
+def test_pd_between_serving_processes_named_by_pd_peers():
+    """The deployment form: a prefill engine process with a fixed ZMQ endpoint, a decode engine process whose `pd_peers` names it
+    (it publishes its pools to the prefill engine when it starts), each behind the HTTP app.  A request prefilled through one app
+    and continued through the other, the way the gateway forwards it, reads the same tokens as a hybrid engine."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import tempfile
+    from starlette.testclient import TestClient
+    from nanoengine_b200.server.engine_server import EngineClient, spawn_backend
+    from nanoengine_b200.server.openai_server import create_app
+    from nanoengine_b200.server.tokenizer import ByteTokenizer
+    os.environ.update(NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    ep_p = f"ipc://{tempfile.gettempdir()}/ne-test-pd-p0-{os.getpid()}.sock"
+    procs, clients = [], []
+
+    def start(cfg, mode, local_rank, endpoint=None):
+        old = os.environ.get("LOCAL_RANK")
+        os.environ["LOCAL_RANK"] = str(local_rank)
+        try:
+            proc, ep = spawn_backend(cfg, endpoint=endpoint)
+        finally:
+            if old is None:
+                os.environ.pop("LOCAL_RANK", None)
+            else:
+                os.environ["LOCAL_RANK"] = old
+        cli = EngineClient(ep, proc)
+        procs.append(proc); clients.append(cli)
+        return create_app(cli, ByteTokenizer(1024), "m", mode=mode)
+
+    try:
+        app_h = start(_cfg("hybrid", engine_id="h0"), "hybrid", 0)
+        app_p = start(_cfg("prefill", engine_id="p0", engine_endpoint=ep_p), "prefill", 0, ep_p)
+        app_d = start(_cfg("decode", engine_id="d0", pd_peers={"p0": ep_p}), "decode", 1)
+        prompt = _prompts()[0]
+        base = {"prompt": prompt, "max_tokens": 6, "temperature": 0.0, "ignore_eos": True, "logprobs": True}
+        with TestClient(app_h) as th, TestClient(app_p) as tp, TestClient(app_d) as td:
+            want = th.post("/v1/completions", json=base).json()["choices"][0]
+            r = tp.post("/v1/completions", json=dict(base, kv_transfer_params={"do_remote_decode": True})).json()
+            kv = r["kv_transfer_params"]
+            assert kv["migration"] and kv["first_token"] is not None and kv["engine_id"] == "p0"
+            got = td.post("/v1/completions", json=dict(base, kv_transfer_params={"migration": kv["migration"], "first_token": kv["first_token"]}))
+            assert got.status_code == 200, got.text
+            got = got.json()["choices"][0]
+            assert tp.post("/pd/free", json={"seq_ids": [kv["seq_id"]]}).json()["freed"] == 1
+        assert got["text"] == want["text"]
+        assert len(got["logprobs"]["tokens"]) >= 5 and got["logprobs"]["tokens"][-5:] == want["logprobs"]["tokens"][-5:]
+    finally:
+        for c in clients:
+            c.destroy()
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+            p.join(timeout=20)
