@@ -78,3 +78,34 @@ def test_engine_follows_the_configured_format():
             assert len(outs[fmt]) == 4
     finally:
         ref.set_scale_format(None)
+
+
+def test_fp8_checkpoint_with_plain_scales_loads_under_ue8m0(tmp_path):
+    """A checkpoint quantised with plain amax / 448 scales, served with fp8_scale_format="ue8m0": every block scale is re-quantised to
+    a power of two at load (experts, merged projections and single linears alike) and the first-token logits stay close to the
+    engine that keeps the checkpoint's own scales."""
+    from nanoengine_b200 import LLM
+    from nanoengine_b200.models.weights import random_hf_weights, save_hf_checkpoint
+    mc = tiny_deepseek_v3(quant="fp8")
+    save_hf_checkpoint(str(tmp_path), mc, random_hf_weights(mc, seed=5), quantize_fp8=True)
+    logits = {}
+    try:
+        for fmt in ("fp32", "ue8m0"):
+            llm = LLM(Config(model=str(tmp_path), device="cpu", dtype="float32", fp8_scale_format=fmt, max_num_seqs=2, max_num_batched_tokens=64,
+                             num_kvcache_blocks=16, kvcache_block_size=16, enable_prefix_caching=False))
+            model = llm.engine.executor.runner.model
+            scales = [m.weight_scale_inv for m in model.modules() if getattr(m, "weight_scale_inv", None) is not None]
+            scales += [s for m in model.modules() for s in (getattr(m, "gate_up_scale", None), getattr(m, "down_scale", None)) if s is not None]
+            assert len(scales) > 6
+            assert all(_is_pow2(s) for s in scales) == (fmt == "ue8m0")
+            got = {}
+            orig = model.compute_logits
+            model.compute_logits = lambda h, _o=orig, _g=got: _g.setdefault("l", _o(h))
+            from nanoengine_b200 import RequestIn, SamplingParams
+            llm.add_request_payload(RequestIn(1, list(range(3, 40)), SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)).to_bytes())
+            llm.generate()
+            logits[fmt] = got["l"].float()
+    finally:
+        ref.set_scale_format(None)
+    rel = ((logits["ue8m0"] - logits["fp32"]).norm() / logits["fp32"].norm()).item()
+    assert rel < 0.1, rel
