@@ -19,7 +19,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 
-from nanoengine_b200.ops import reference as ref
+
 from nanoengine_b200.ops import sm100, sm100_attn
 
 FP8 = torch.float8_e4m3fn

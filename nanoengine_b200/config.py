@@ -7,8 +7,8 @@ from __future__ import annotations
 
 import json
 import os
-from dataclasses import asdict, dataclass, field, fields
-from typing import Any, Dict, List, Optional
+from dataclasses import dataclass, field, fields
+from typing import Any, Dict, Optional
 
 from .models.config import PRESETS, ModelConfig
 from .parallel.dist import ParallelSpec

@@ -7,7 +7,6 @@ block), layers/layernorm.py:16-108, layers/activation.py:29-112.
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

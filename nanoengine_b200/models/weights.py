@@ -17,7 +17,7 @@ from typing import Callable, Dict, Iterable, Iterator, Optional, Tuple
 
 import torch
 
-from ..parallel.dist import get_dist_context
+
 from .config import ModelConfig
 
 _EXPERT_RE = re.compile(r"\.mlp\.experts\.(\d+)\.")
