@@ -1,7 +1,11 @@
 // ne-gateway: HTTP/1.1 gateway in front of a pool of engines, with prefill/decode (PD) routing and SSE pass-through.
 //
-//   ne-gateway --port 3001 [--host 0.0.0.0] [--ctrl-address http://h:p] [--hybrid URL,...] [--prefill URL,...] [--decode URL,...]
-//              [--model-alias alias=model ...] [--daemonize] [--pid-file PATH]
+//   ne-gateway [start|status|stop] --port 3001 [--host 0.0.0.0] [--ctrl-address http://h:p] [--ctrl-scope NAME] [--hybrid URL,...]
+//              [--prefill URL,...] [--decode URL,...] [--model-alias alias=model ...] [--daemonize] [--pid-file PATH]
+//
+// Without a sub-command the gateway serves in the foreground.  `start` runs it as a daemon and records its pid under the runtime
+// directory ($NANOENGINE_ROUTER_RUNTIME_DIR, default /tmp/nanoengine-router), `status` says whether that daemon is alive and prints
+// its /status page, `stop` ends it.
 //
 // Routing.  Hybrid pool: round-robin reverse proxy.  PD pools (both non-empty): (1) POST the body to a prefill engine with
 // stream=false and kv_transfer_params={"do_remote_decode":true}; (2) read kv_transfer_params.{migration,seq_id,first_token}
@@ -11,8 +15,11 @@
 // (5) POST {prefill}/pd/free with the seq_id.  Upstream failures map to 502.  Discovery: every 5 s POST
 // {ctrl}/list_entities; engines that appear are added to their role's pool, engines that vanish are removed.
 //
-// Parity: reference rust/src/router/mod.rs:36-133 (CLI, daemonize, pid file), engine_manager.rs:8-68,219-452 (pools,
-// discovery, stale removal, P/D pairing), http_server.rs:130-267 (PD forward), :475-483 (routes).
+// GET /status: uptime, engines per role, models, request counters, the control plane in use.  --ctrl-scope: only entities the
+// control plane lists under that scope are taken (the scope is sent with the query and checked on every entity that names one).
+//
+// Parity: reference rust/src/router/mod.rs:11-231 (CLI, start / status / stop, daemonize, pid file), engine_manager.rs:8-68,100-105,
+// 219-452 (pools, scope, discovery, stale removal, P/D pairing), http_server.rs:130-267 (PD forward), :475-483 (routes).
 #include <arpa/inet.h>
 #include <netdb.h>
 #include <netinet/in.h>
@@ -218,13 +225,18 @@ class Pools {
 static Pools g_pools;
 static std::map<std::string, std::string> g_alias;
 static std::atomic<bool> g_stop{false};
+static std::atomic<long long> g_requests{0}, g_pd_requests{0}, g_failed{0};
+static std::string g_ctrl, g_scope;
+static int g_listen_fd = -1;
+static const auto g_started = std::chrono::steady_clock::now();
 
 static void discovery_loop(std::string ctrl) {
   Url cu;
   if (!parse_url(ctrl, &cu)) return;
+  const std::string query = g_scope.empty() ? "{}" : "{\"scope\":" + jl::quote(g_scope) + "}";
   while (!g_stop) {
     HttpMsg r;
-    if (http_call(cu, "POST", "/list_entities", "{}", &r, 5) && r.status() == 200) {
+    if (http_call(cu, "POST", "/list_entities", query, &r, 5) && r.status() == 200) {
       // reply: {"entities":[{"id":..,"role":..,"host":..,"port":..,"model":..}, ...]}
       std::vector<Engine> seen;
       auto arr = jl::raw(r.body, "entities");
@@ -246,7 +258,9 @@ static void discovery_loop(std::string ctrl) {
           if (auto v = jl::raw(obj, "port")) port = atoi(v->c_str());
           if (auto v = jl::raw(obj, "url")) en.url = jl::unquote(*v); else en.url = "http://" + host + ":" + std::to_string(port);
           if (en.role.empty()) en.role = "hybrid";
-          if (port > 0 || !en.url.empty()) seen.push_back(en);
+          bool in_scope = true;
+          if (!g_scope.empty()) if (auto v = jl::raw(obj, "scope")) in_scope = jl::unquote(*v) == g_scope;
+          if (in_scope && (port > 0 || !en.url.empty())) seen.push_back(en);
           i = jl::skip_ws(a, e);
           if (i < a.size() && a[i] == ',') i++;
         }
@@ -315,6 +329,21 @@ static void handle(int cfd) {
   if (method == "GET" && path == "/health") {
     auto all = g_pools.all();
     respond(cfd, all.empty() ? 503 : 200, "{\"status\":\"" + std::string(all.empty() ? "no engines" : "ok") + "\",\"engines\":" + std::to_string(all.size()) + "}");
+  } else if (method == "GET" && path == "/status") {
+    int nh = 0, np = 0, nd = 0;
+    std::set<std::string> names;
+    for (auto& e : g_pools.all()) {
+      (e.role == "prefill" ? np : e.role == "decode" ? nd : nh)++;
+      if (!e.model.empty()) names.insert(e.model);
+    }
+    std::string models = "[";
+    for (auto& n : names) models += std::string(models.size() > 1 ? "," : "") + jl::quote(n);
+    const long long up = std::chrono::duration_cast<std::chrono::seconds>(std::chrono::steady_clock::now() - g_started).count();
+    respond(cfd, 200, "{\"status\":\"" + std::string(nh + np + nd ? "ok" : "no engines") + "\",\"pid\":" + std::to_string(getpid()) + ",\"uptime_s\":" +
+                          std::to_string(up) + ",\"engines\":{\"hybrid\":" + std::to_string(nh) + ",\"prefill\":" + std::to_string(np) + ",\"decode\":" +
+                          std::to_string(nd) + "},\"pd_routing\":" + (np && nd ? "true" : "false") + ",\"models\":" + models + "],\"requests\":{\"total\":" +
+                          std::to_string(g_requests.load()) + ",\"pd\":" + std::to_string(g_pd_requests.load()) + ",\"failed\":" +
+                          std::to_string(g_failed.load()) + "},\"ctrl_address\":" + jl::quote(g_ctrl) + ",\"ctrl_scope\":" + jl::quote(g_scope) + "}");
   } else if (method == "GET" && path == "/v1/models") {
     std::set<std::string> names;
     for (auto& e : g_pools.all()) if (!e.model.empty()) names.insert(e.model);
@@ -336,11 +365,12 @@ static void handle(int cfd) {
       if (a != g_alias.end()) { model = a->second; body = jl::with_member(body, "model", jl::quote(model)); }
     }
     const bool pd = g_pools.has("prefill") && g_pools.has("decode") && path != "/v1/messages/count_tokens";
-    if (pd) forward_pd(cfd, path, body, model);
+    g_requests++;
+    if (pd) { g_pd_requests++; forward_pd(cfd, path, body, model); }
     else {
       Engine e; Url u;
-      if (!g_pools.pick("hybrid", model, &e) && !g_pools.pick("decode", model, &e) && !g_pools.pick("prefill", model, &e)) respond_error(cfd, 503, "no engine available");
-      else if (!parse_url(e.url, &u) || !proxy_stream(cfd, u, path, body)) respond_error(cfd, 502, "engine unreachable: " + e.url);
+      if (!g_pools.pick("hybrid", model, &e) && !g_pools.pick("decode", model, &e) && !g_pools.pick("prefill", model, &e)) { g_failed++; respond_error(cfd, 503, "no engine available"); }
+      else if (!parse_url(e.url, &u) || !proxy_stream(cfd, u, path, body)) { g_failed++; respond_error(cfd, 502, "engine unreachable: " + e.url); }
     }
   } else {
     respond_error(cfd, 404, "unknown route " + method + " " + path);
@@ -355,31 +385,83 @@ static std::vector<std::string> split(const std::string& s, char c) {
   return out;
 }
 
+static std::string runtime_dir() {
+  const char* d = getenv("NANOENGINE_ROUTER_RUNTIME_DIR");
+  return d && *d ? d : "/tmp/nanoengine-router";
+}
+static long read_pid(const std::string& file) {
+  std::ifstream f(file);
+  long p = 0;
+  return (f >> p) && p > 0 ? p : 0;
+}
+static bool alive(long pid) { return pid > 0 && kill((pid_t)pid, 0) == 0; }
+static void on_term(int) {
+  g_stop = true;
+  if (g_listen_fd >= 0) shutdown(g_listen_fd, SHUT_RDWR);      // wakes the accept loop
+}
+
 int main(int argc, char** argv) {
-  std::string host = "0.0.0.0", ctrl, pid_file;
+  std::string host = "0.0.0.0", ctrl, pid_file, cmd;
   int port = 3001; bool daemonize = false;
   for (int i = 1; i < argc; i++) {
     std::string a = argv[i];
     auto next = [&]() -> std::string { return i + 1 < argc ? argv[++i] : ""; };
-    if (a == "--port") port = atoi(next().c_str());
+    if (i == 1 && (a == "start" || a == "status" || a == "stop")) cmd = a;
+    else if (a == "--port") port = atoi(next().c_str());
     else if (a == "--host") host = next();
     else if (a == "--ctrl-address") ctrl = next();
+    else if (a == "--ctrl-scope") g_scope = next();
     else if (a == "--hybrid" || a == "--prefill" || a == "--decode") { for (auto& u : split(next(), ',')) g_pools.add({"", u, a.substr(2), "", false}); }
     else if (a == "--model-alias") { auto kv = split(next(), '='); if (kv.size() == 2) g_alias[kv[0]] = kv[1]; }
     else if (a == "--daemonize") daemonize = true;
     else if (a == "--pid-file") pid_file = next();
-    else if (a == "--help") { printf("usage: ne-gateway --port P [--host H] [--ctrl-address URL] [--hybrid URLS] [--prefill URLS] [--decode URLS] [--model-alias a=b] [--daemonize] [--pid-file F]\n"); return 0; }
+    else if (a == "--help") { printf("usage: ne-gateway [start|status|stop] --port P [--host H] [--ctrl-address URL] [--ctrl-scope S] [--hybrid URLS] [--prefill URLS] [--decode URLS] [--model-alias a=b] [--daemonize] [--pid-file F]\n"); return 0; }
     else { fprintf(stderr, "unknown flag %s\n", a.c_str()); return 2; }
   }
+  g_ctrl = ctrl;
+  if (!cmd.empty()) {
+    mkdir(runtime_dir().c_str(), 0755);
+    if (pid_file.empty()) pid_file = runtime_dir() + "/ne-gateway.pid";
+    const long pid = read_pid(pid_file);
+    if (cmd == "status") {
+      if (!alive(pid)) { printf("ne-gateway is not running\n"); return 3; }
+      printf("ne-gateway is running (pid=%ld)\n", pid);
+      Url self; self.host = "127.0.0.1"; self.port = port;
+      HttpMsg r;
+      if (http_call(self, "GET", "/status", "", &r, 3) && r.status() == 200) printf("%s\n", r.body.c_str());
+      else printf("status page: unavailable on port %d\n", port);
+      return 0;
+    }
+    if (cmd == "stop") {
+      if (!alive(pid)) { printf("ne-gateway is not running\n"); unlink(pid_file.c_str()); return 0; }
+      kill((pid_t)pid, SIGTERM);
+      for (int k = 0; k < 50 && alive(pid); k++) usleep(100 * 1000);
+      if (alive(pid)) { printf("ne-gateway (pid=%ld) did not stop\n", pid); return 1; }
+      unlink(pid_file.c_str());
+      printf("ne-gateway stopped (pid=%ld)\n", pid);
+      return 0;
+    }
+    if (alive(pid)) { printf("ne-gateway is already running (pid=%ld)\n", pid); return 0; }
+    daemonize = true;                                     // start
+  }
   signal(SIGPIPE, SIG_IGN);
+  signal(SIGTERM, on_term);
+  signal(SIGINT, on_term);
   if (daemonize) {
     pid_t p = fork();
     if (p < 0) return 1;
-    if (p > 0) return 0;
+    if (p > 0) { if (cmd == "start") printf("ne-gateway started (pid=%d)\n", (int)p); return 0; }
     setsid();
+    if (cmd == "start") {
+      // the daemon keeps none of the caller's descriptors: its log goes to the runtime directory
+      FILE* n = freopen("/dev/null", "r", stdin); (void)n;
+      n = freopen("/dev/null", "w", stdout); (void)n;
+      n = freopen((runtime_dir() + "/ne-gateway.log").c_str(), "a", stderr); (void)n;
+    }
   }
   if (!pid_file.empty()) { std::ofstream f(pid_file); f << getpid() << "\n"; }
   int ls = socket(AF_INET, SOCK_STREAM, 0);
+  g_listen_fd = ls;
   int one = 1; setsockopt(ls, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
   sockaddr_in addr{}; addr.sin_family = AF_INET; addr.sin_port = htons((uint16_t)port);
   inet_pton(AF_INET, host.c_str(), &addr.sin_addr);
@@ -389,11 +471,12 @@ int main(int argc, char** argv) {
   if (!ctrl.empty()) disc = std::thread(discovery_loop, ctrl);
   while (!g_stop) {
     int cfd = accept(ls, nullptr, nullptr);
-    if (cfd < 0) { if (errno == EINTR) continue; break; }
+    if (cfd < 0) { if (errno == EINTR && !g_stop) continue; break; }
     int nd = 1; setsockopt(cfd, IPPROTO_TCP, TCP_NODELAY, &nd, sizeof nd);
     std::thread(handle, cfd).detach();
   }
   g_stop = true;
   if (disc.joinable()) disc.join();
+  if (!cmd.empty() && !pid_file.empty()) unlink(pid_file.c_str());
   return 0;
 }

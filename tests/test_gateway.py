@@ -169,3 +169,72 @@ def test_discovery_adds_and_removes_engines():
         assert _post(gw + "/v1/completions", {"prompt": "x"})[0] == 503
     finally:
         p.terminate(); ctrl.stop(); e.stop()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_status_page_counts_engines_and_requests():
+    pf, dc = FakeEngine("prefill"), FakeEngine("decode")
+    p, gw = _gateway("--prefill", pf.url, "--decode", dc.url)
+    try:
+        st = json.loads(urllib.request.urlopen(gw + "/status").read())
+        assert st["status"] == "ok" and st["engines"] == {"hybrid": 0, "prefill": 1, "decode": 1} and st["pd_routing"] is True
+        assert st["requests"] == {"total": 0, "pd": 0, "failed": 0} and st["pid"] == p.pid
+        assert _post(gw + "/v1/chat/completions", {"model": "m", "messages": []})[0] == 200
+        st = json.loads(urllib.request.urlopen(gw + "/status").read())
+        assert st["requests"]["total"] == 1 and st["requests"]["pd"] == 1 and st["uptime_s"] >= 0
+    finally:
+        p.terminate(); pf.stop(); dc.stop()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_ctrl_scope_filters_the_discovered_engines():
+    a, b, ctrl = FakeEngine("hybrid"), FakeEngine("hybrid"), FakeEngine("ctrl")
+    ctrl.entities = [{"id": "a", "role": "hybrid", "host": "127.0.0.1", "port": a.port, "model": "m", "scope": "blue"},
+                     {"id": "b", "role": "hybrid", "host": "127.0.0.1", "port": b.port, "model": "m", "scope": "green"}]
+    p, gw = _gateway("--ctrl-address", ctrl.url, "--ctrl-scope", "blue")
+    try:
+        for _ in range(100):
+            if json.loads(urllib.request.urlopen(gw + "/status").read())["engines"]["hybrid"]:
+                break
+            time.sleep(0.1)
+        st = json.loads(urllib.request.urlopen(gw + "/status").read())
+        assert st["engines"]["hybrid"] == 1 and st["ctrl_scope"] == "blue"
+        assert any(path == "/list_entities" and body.get("scope") == "blue" for path, body in ctrl.requests)
+        for _ in range(3):
+            assert _post(gw + "/v1/completions", {"prompt": "x"})[0] == 200
+        assert len([r for r in a.requests if r[0] == "/v1/completions"]) == 3 and not b.requests
+    finally:
+        p.terminate(); a.stop(); b.stop(); ctrl.stop()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_start_status_stop_run_the_gateway_as_a_daemon(tmp_path):
+    e = FakeEngine("hybrid")
+    port = _port()
+    env = dict(os.environ, NANOENGINE_ROUTER_RUNTIME_DIR=str(tmp_path / "rt"))
+    common = ["--port", str(port), "--host", "127.0.0.1"]
+
+    def run(*args):
+        return subprocess.run([GATEWAY, *args], env=env, capture_output=True, text=True, timeout=20)
+
+    try:
+        assert "not running" in run("status", *common).stdout
+        out = run("start", *common, "--hybrid", e.url)
+        assert out.returncode == 0 and "started (pid=" in out.stdout
+        pid = int(out.stdout.split("pid=")[1].split(")")[0])
+        for _ in range(100):
+            try:
+                socket.create_connection(("127.0.0.1", port), timeout=0.2).close()
+                break
+            except OSError:
+                time.sleep(0.05)
+        assert _post(f"http://127.0.0.1:{port}/v1/completions", {"prompt": "x"})[0] == 200
+        st = run("status", *common)
+        assert f"running (pid={pid})" in st.stdout and '"hybrid":1' in st.stdout and '"total":1' in st.stdout
+        assert "already running" in run("start", *common, "--hybrid", e.url).stdout
+        assert f"stopped (pid={pid})" in run("stop", *common).stdout
+        assert "not running" in run("status", *common).stdout
+        assert not (tmp_path / "rt" / "ne-gateway.pid").exists()
+    finally:
+        run("stop", *common)
+        e.stop()
