@@ -81,7 +81,10 @@ class Metrics {
   struct Gauges {
     std::vector<int32_t> running_per_dp, waiting_blocks_per_dp, used_blocks_per_dp, total_blocks_per_dp;
     std::vector<double> prefix_hit_rate_per_dp;
-    int32_t waiting = 0; double prefix_hit_rate = 0;
+    std::vector<int32_t> used_host_blocks_per_dp;        // host tier of the prefix cache (empty when there is none)
+    int32_t total_host_blocks_per_dp = 0;
+    int32_t used_hisparse_slots = 0, total_hisparse_slots = 0;      // hot / cold cache tier: sequences holding a hot buffer
+    int32_t waiting = 0, waiting_migration = 0; double prefix_hit_rate = 0;
   };
 
   std::string prometheus(const Gauges& g) const {
@@ -94,9 +97,10 @@ class Metrics {
     line("dlengine_uptime_seconds", "gauge", up);
     o += "# TYPE dlengine_requests gauge\n";
     snprintf(buf, sizeof buf, "dlengine_requests{state=\"total\"} %llu\ndlengine_requests{state=\"finished\"} %llu\n"
-             "dlengine_requests{state=\"aborted\"} %llu\ndlengine_requests{state=\"waiting\"} %d\n",
+             "dlengine_requests{state=\"aborted\"} %llu\ndlengine_requests{state=\"waiting\"} %d\n"
+             "dlengine_requests{state=\"waiting_migration\"} %d\n",
              (unsigned long long)requests_total_, (unsigned long long)requests_finished_,
-             (unsigned long long)requests_aborted_, g.waiting); o += buf;
+             (unsigned long long)requests_aborted_, g.waiting, g.waiting_migration); o += buf;
     o += "# TYPE dlengine_tokens counter\n";
     snprintf(buf, sizeof buf, "dlengine_tokens{kind=\"prompt\"} %llu\ndlengine_tokens{kind=\"generated\"} %llu\n",
              (unsigned long long)prompt_tokens_, (unsigned long long)generated_tokens_); o += buf;
@@ -130,6 +134,18 @@ class Metrics {
     for (size_t i = 0; i < g.used_blocks_per_dp.size(); i++) {
       snprintf(buf, sizeof buf, "dlengine_kv_blocks{dp=\"%zu\",state=\"used\"} %d\ndlengine_kv_blocks{dp=\"%zu\",state=\"total\"} %d\n",
                i, g.used_blocks_per_dp[i], i, g.total_blocks_per_dp[i]); o += buf;
+    }
+    if (g.total_host_blocks_per_dp > 0) {
+      o += "# TYPE dlengine_host_kv_blocks gauge\n";
+      for (size_t i = 0; i < g.used_host_blocks_per_dp.size(); i++) {
+        snprintf(buf, sizeof buf, "dlengine_host_kv_blocks{dp=\"%zu\",state=\"used\"} %d\ndlengine_host_kv_blocks{dp=\"%zu\",state=\"total\"} %d\n",
+                 i, g.used_host_blocks_per_dp[i], i, g.total_host_blocks_per_dp); o += buf;
+      }
+    }
+    if (g.total_hisparse_slots > 0) {
+      o += "# TYPE dlengine_hisparse_slots gauge\n";
+      snprintf(buf, sizeof buf, "dlengine_hisparse_slots{state=\"used\"} %d\ndlengine_hisparse_slots{state=\"total\"} %d\n",
+               g.used_hisparse_slots, g.total_hisparse_slots); o += buf;
     }
     return o;
   }

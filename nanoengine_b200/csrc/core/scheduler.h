@@ -383,6 +383,10 @@ class Scheduler {
       hit += pools_[d].hit_tokens(); look += pools_[d].lookup_tokens();
     }
     g.prefix_hit_rate = look ? (double)hit / (double)look : 0.0;
+    g.waiting_migration = (int)waiting_migration_.size();
+    g.total_host_blocks_per_dp = (int)cfg_.num_host_blocks;
+    for (size_t d = 0; d < host_pools_.size(); d++) g.used_host_blocks_per_dp.push_back((int)cfg_.num_host_blocks - host_pools_[d].num_free());
+    for (auto& sp : hisparse_slots_) { g.total_hisparse_slots += sp.total(); g.used_hisparse_slots += sp.total() - sp.num_free(); }
     return metrics_.prometheus(g);
   }
 

@@ -328,6 +328,19 @@ def test_metrics_prometheus_names():
         assert name in text
 
 
+def test_metrics_report_the_host_tier_hot_slots_and_waiting_migrations():
+    s = make()
+    text = s.metrics_prometheus()
+    assert 'dlengine_requests{state="waiting_migration"} 0' in text
+    assert "dlengine_host_kv_blocks" not in text and "dlengine_hisparse_slots" not in text        # tiers that do not exist are not listed
+    s = make(num_host_blocks=8, num_hisparse_slots=4, cache_plan=C.PLAN_HISPARSE)
+    add(s, 1, [3] * 9, max_tokens=4)
+    s.schedule()
+    text = s.metrics_prometheus()
+    assert 'dlengine_host_kv_blocks{dp="0",state="used"} 0' in text and 'dlengine_host_kv_blocks{dp="0",state="total"} 8' in text
+    assert 'dlengine_hisparse_slots{state="used"} 1' in text and 'dlengine_hisparse_slots{state="total"} 4' in text
+
+
 def test_block_pool_states_and_l3_index():
     p = C.BlockPool(4, 4, True)
     ids = p.allocate(2)
