@@ -71,6 +71,7 @@ class Config:
     eplb_load_path: Optional[str] = None     # torch file with the expert load [layers, experts] the plan balances (default: uniform)
     # observability
     log_level: str = "INFO"
+    status_log_interval_s: float = 10.0      # the engine logs one status line (requests, cache occupancy, throughput) this often; 0 = never
     step_timing: bool = False
     profiler_dir: Optional[str] = None
     # serving / PD

@@ -303,6 +303,7 @@ PYBIND11_MODULE(_core, m) {
       .def("num_free_handoff_slots", &Scheduler::num_free_handoff_slots, py::arg("dp") = 0)
       .def_property_readonly("step", &Scheduler::step)
       .def("metrics_prometheus", &Scheduler::metrics_prometheus)
+      .def("status_line", &Scheduler::status_line, py::arg("mode") = "hybrid")
       .def("metrics_summary", [](Scheduler& s) {
         auto v = s.metrics().summary(); py::dict d;
         d["ttft_p50"] = v[0]; d["ttft_p90"] = v[1]; d["ttft_p99"] = v[2]; d["tpot_p50"] = v[3]; d["tpot_p90"] = v[4];

@@ -150,6 +150,31 @@ class Metrics {
     return o;
   }
 
+  // One line for the engine's periodic log: running / waiting / migrating requests, cache occupancy per tier, recent prefill and
+  // decode throughput, finished requests.  Parity: reference rust/src/metrics/manager.rs:500-610 (the periodic status line).
+  std::string status_line(const Gauges& g, const std::string& engine_id, const std::string& mode) const {
+    std::string run, kv, host;
+    for (size_t i = 0; i < g.running_per_dp.size(); i++) run += (i ? "," : "") + std::to_string(g.running_per_dp[i]);
+    for (size_t i = 0; i < g.used_blocks_per_dp.size(); i++)
+      kv += (i ? "," : "") + std::to_string(g.used_blocks_per_dp[i]) + "/" + std::to_string(g.total_blocks_per_dp[i]);
+    for (size_t i = 0; i < g.used_host_blocks_per_dp.size(); i++) host += (i ? "," : "") + std::to_string(g.used_host_blocks_per_dp[i]);
+    double pf_ms = 0, pf_tok = 0, dc_ms = 0, dc_tok = 0;
+    int k = 0;
+    for (auto it = recent_.rbegin(); it != recent_.rend() && k < 256; ++it, ++k) {
+      if (it->is_prefill) { pf_ms += it->latency_ms; pf_tok += it->num_tokens; } else { dc_ms += it->latency_ms; dc_tok += it->num_tokens; }
+    }
+    char buf[640];
+    std::string o;
+    snprintf(buf, sizeof buf, "[engine %s %s] run=%s wait=%d mig=%d | kv=%s blk", engine_id.c_str(), mode.c_str(), run.c_str(),
+             g.waiting - g.waiting_migration, g.waiting_migration, kv.c_str());
+    o = buf;
+    if (g.total_host_blocks_per_dp > 0) { snprintf(buf, sizeof buf, " host=%s/%d blk", host.c_str(), g.total_host_blocks_per_dp); o += buf; }
+    if (g.total_hisparse_slots > 0) { snprintf(buf, sizeof buf, " hisparse_hot=%d/%d slot", g.used_hisparse_slots, g.total_hisparse_slots); o += buf; }
+    snprintf(buf, sizeof buf, " | tput pf=%.0f dec=%.0f tok/s (%.0fs) | prefix hit %.2f | done=%llu", pf_ms > 0 ? pf_tok / (pf_ms * 1e-3) : 0.0,
+             dc_ms > 0 ? dc_tok / (dc_ms * 1e-3) : 0.0, now_seconds() - t_start_, g.prefix_hit_rate, (unsigned long long)requests_finished_);
+    return o + buf;
+  }
+
   // Percentile summary used by the final report and the serving benchmark.
   std::vector<double> summary() const {
     return {percentile(ttft_samples_, 0.5), percentile(ttft_samples_, 0.9), percentile(ttft_samples_, 0.99),

@@ -371,7 +371,10 @@ class Scheduler {
   int64_t step() const { return step_; }
   BlockPool& pool(int dp) { return pools_.at(dp); }
 
-  std::string metrics_prometheus() const {
+  std::string metrics_prometheus() const { return metrics_.prometheus(gauges()); }
+  std::string status_line(const std::string& mode) const { return metrics_.status_line(gauges(), cfg_.engine_id, mode); }
+
+  Metrics::Gauges gauges() const {
     Metrics::Gauges g; g.waiting = (int)waiting_.size() + (int)waiting_migration_.size();
     uint64_t hit = 0, look = 0;
     for (int d = 0; d < cfg_.attention_dp; d++) {
@@ -387,7 +390,7 @@ class Scheduler {
     g.total_host_blocks_per_dp = (int)cfg_.num_host_blocks;
     for (size_t d = 0; d < host_pools_.size(); d++) g.used_host_blocks_per_dp.push_back((int)cfg_.num_host_blocks - host_pools_[d].num_free());
     for (auto& sp : hisparse_slots_) { g.total_hisparse_slots += sp.total(); g.used_hisparse_slots += sp.total() - sp.num_free(); }
-    return metrics_.prometheus(g);
+    return g;
   }
 
  private:

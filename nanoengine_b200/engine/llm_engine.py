@@ -194,6 +194,10 @@ class LLMEngine:
         step_outs = self.scheduler.postprocess_runner_out_bytes(outs, ms)
         if self.l3_enabled:
             self._l3_persist()
+        every = self.config.status_log_interval_s
+        if every > 0 and t0 - getattr(self, "_status_logged_at", 0.0) >= every:
+            self._status_logged_at = t0
+            logger.info(self.scheduler.status_line(self.config.mode))
         return step_outs
 
     def _run_static_pp_prefill_pipeline(self, res) -> List[bytes]:

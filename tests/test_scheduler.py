@@ -443,3 +443,13 @@ def test_dummy_batch_of_an_idle_rank_survives_the_wire():
     for prefill in (False, True):
         b = C.RunnerIn.from_bytes(_dummy_batch(prefill).to_bytes())
         assert b.is_dummy and b.is_prefill == prefill and b.num_seqs == 0
+
+
+def test_status_line_names_requests_cache_and_throughput():
+    s = make(num_host_blocks=8)
+    add(s, 1, [3] * 9, max_tokens=3)
+    run_all(s)
+    add(s, 2, [4] * 5, max_tokens=2)
+    line = s.status_line("hybrid")
+    assert line.startswith("[engine ") and " hybrid] run=0 wait=1 mig=0 | kv=" in line and "/64 blk host=0/8 blk" in line
+    assert "tput pf=" in line and "dec=" in line and line.rstrip().endswith("done=1")
