@@ -77,7 +77,9 @@ class Config:
     # serving / PD
     engine_id: str = "engine-0"
     engine_endpoint: Optional[str] = None    # ZMQ endpoint of the engine process behind the HTTP server (default: a fresh ipc:// path); what a decode engine's pd_peers names
-    ctrl_address: Optional[str] = None
+    ctrl_address: Optional[str] = None       # control plane the HTTP server registers with (`nanoengine ctrl`); the gateway discovers engines there
+    ctrl_scope: Optional[str] = None         # only gateways started with the same scope take this engine
+    served_model_name: Optional[str] = None  # model id in /v1/models and for routing (default: the last component of `model`)
     host: str = "127.0.0.1"
     port: int = 8000
     pd_peers: Dict[str, str] = field(default_factory=dict)   # decode engines: prefill engine id -> ZMQ endpoint of its engine process

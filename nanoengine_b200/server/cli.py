@@ -1,5 +1,6 @@
 """Command line: ``python -m nanoengine_b200.server.cli serve <model> [--flag value ...] [--config file.yaml]``,
-``... monitor --targets host:port,... --out DIR`` and ``... router --port P ...`` (the C++ gateway).
+``... monitor --targets host:port,... --out DIR``, ``... router --port P ...`` (the C++ gateway) and ``... ctrl --port P`` (the control
+plane engines register with and the gateway discovers them from).
 
 Every Config field is a flag (``--attention_dp 8 --ffn_ep 8 --num_speculative_tokens 2``); nested per-role overrides for PD
 launches use ``--prefill.<field>`` / ``--decode.<field>``.
@@ -78,6 +79,15 @@ def main(argv=None) -> int:
         cfg = Config(model=rest[0], **common)
         from .openai_server import run_server
         run_server(cfg, tool_format=tool_format)
+        return 0
+    if cmd == "ctrl":
+        ap = argparse.ArgumentParser(prog="ctrl", description="control plane: registry of engines for dynamic discovery by the gateway")
+        ap.add_argument("--host", default="0.0.0.0")
+        ap.add_argument("--port", type=int, default=4479)
+        ap.add_argument("--ttl", type=float, default=15.0, help="seconds after the last heartbeat before an engine is dropped")
+        a = ap.parse_args(rest)
+        from .ctrl import run_ctrl
+        run_ctrl(a.host, a.port, a.ttl)
         return 0
     if cmd == "monitor":
         ap = argparse.ArgumentParser(prog="monitor")

@@ -1,0 +1,183 @@
+"""Control plane for dynamic discovery: engines announce their HTTP endpoint (role, model, scope) and keep it alive with a
+heartbeat; the gateway polls the list and adds / drops engines as they come and go.
+
+    nanoengine ctrl --port 4479                       # the registry (in memory, entries expire `ttl` seconds after their last heartbeat)
+    nanoengine serve MODEL --ctrl_address http://host:4479 [--ctrl_scope blue]      # an engine that registers itself
+    nanoengine-router --ctrl-address http://host:4479 [--ctrl-scope blue]           # a gateway that discovers engines
+
+HTTP API (JSON bodies): POST /register {id, host, port, role, model, scope?, engine_id?}, POST /heartbeat {id} -> {found},
+POST /unregister {id}, POST /list_entities {scope?} -> {entities: [...]}, GET /health.
+
+Parity: the reference registers with an external control-plane service through its client library
+(server/openai_server.py:1748-1810 `register_with_ctrl`: entity id, endpoint, role / model metadata, heartbeat with
+re-registration when the entry is gone) and its router polls it (rust/src/router/engine_manager.rs:263-452); here the small
+service itself is part of the package."""
+from __future__ import annotations
+
+import json
+import threading
+import time
+import urllib.request
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import Callable, Dict, List, Optional
+
+
+class Registry:
+    """Entities by id; an entity not heard from for `ttl` seconds is gone."""
+
+    def __init__(self, ttl: float = 15.0, clock: Callable[[], float] = time.monotonic):
+        self.ttl, self.clock = ttl, clock
+        self._mu = threading.Lock()
+        self._ents: Dict[str, dict] = {}
+
+    def register(self, ent: dict) -> None:
+        if not ent.get("id") or not ent.get("port"):
+            raise ValueError("an entity needs an id and a port")
+        e = {"id": str(ent["id"]), "host": str(ent.get("host") or "127.0.0.1"), "port": int(ent["port"]), "role": str(ent.get("role") or "hybrid"),
+             "model": str(ent.get("model") or ""), "scope": str(ent.get("scope") or ""), "engine_id": str(ent.get("engine_id") or ""),
+             "seen": self.clock()}
+        if e["role"] not in ("hybrid", "prefill", "decode"):
+            raise ValueError(f"unknown role {e['role']!r}")
+        e["url"] = f"http://{e['host']}:{e['port']}"
+        with self._mu:
+            self._ents[e["id"]] = e
+
+    def heartbeat(self, ent_id: str) -> bool:
+        with self._mu:
+            e = self._ents.get(ent_id)
+            if e is None or self.clock() - e["seen"] > self.ttl:
+                self._ents.pop(ent_id, None)
+                return False
+            e["seen"] = self.clock()
+            return True
+
+    def unregister(self, ent_id: str) -> bool:
+        with self._mu:
+            return self._ents.pop(ent_id, None) is not None
+
+    def list(self, scope: Optional[str] = None) -> List[dict]:
+        now = self.clock()
+        with self._mu:
+            for k in [k for k, e in self._ents.items() if now - e["seen"] > self.ttl]:
+                del self._ents[k]
+            return [{k: v for k, v in e.items() if k != "seen"} for e in self._ents.values() if not scope or e["scope"] == scope]
+
+
+def make_server(host: str = "0.0.0.0", port: int = 4479, ttl: float = 15.0, registry: Optional[Registry] = None) -> ThreadingHTTPServer:
+    reg = registry or Registry(ttl)
+
+    class Handler(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def _reply(self, code: int, obj) -> None:
+            b = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(b)))
+            self.end_headers()
+            self.wfile.write(b)
+
+        def do_GET(self):
+            if self.path == "/health":
+                return self._reply(200, {"status": "ok", "entities": len(reg.list())})
+            self._reply(404, {"error": "unknown route"})
+
+        def do_POST(self):
+            try:
+                body = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0))) or b"{}")
+                if self.path == "/register":
+                    reg.register(body)
+                    return self._reply(200, {"ok": True})
+                if self.path == "/heartbeat":
+                    return self._reply(200, {"found": reg.heartbeat(str(body.get("id", "")))})
+                if self.path == "/unregister":
+                    return self._reply(200, {"removed": reg.unregister(str(body.get("id", "")))})
+                if self.path == "/list_entities":
+                    return self._reply(200, {"entities": reg.list(body.get("scope") or None)})
+            except (ValueError, KeyError, TypeError) as e:
+                return self._reply(400, {"error": str(e)})
+            self._reply(404, {"error": "unknown route"})
+
+    srv = ThreadingHTTPServer((host, port), Handler)
+    srv.registry = reg
+    return srv
+
+
+def run_ctrl(host: str = "0.0.0.0", port: int = 4479, ttl: float = 15.0) -> None:
+    srv = make_server(host, port, ttl)
+    try:
+        srv.serve_forever()
+    finally:
+        srv.server_close()
+
+
+class CtrlClient:
+    """An engine's side: register, then a heartbeat thread that registers again when the control plane has forgotten the entry
+    (it restarted, or the engine was silent for longer than the time to live)."""
+
+    def __init__(self, address: str, scope: Optional[str] = None, timeout: float = 3.0):
+        self.address, self.scope, self.timeout = address.rstrip("/"), scope or "", timeout
+        self._ent: Optional[dict] = None
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+
+    def _post(self, path: str, obj: dict) -> dict:
+        req = urllib.request.Request(self.address + path, json.dumps(obj).encode(), {"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=self.timeout) as r:
+            return json.loads(r.read() or b"{}")
+
+    def register(self, ent_id: str, host: str, port: int, role: str = "hybrid", model: str = "", engine_id: str = "") -> bool:
+        self._ent = {"id": ent_id, "host": host, "port": port, "role": role, "model": model, "scope": self.scope, "engine_id": engine_id}
+        try:
+            return bool(self._post("/register", self._ent).get("ok"))
+        except OSError:
+            return False
+
+    def list_entities(self) -> List[dict]:
+        return self._post("/list_entities", {"scope": self.scope} if self.scope else {}).get("entities", [])
+
+    def start_heartbeat(self, interval: float = 5.0) -> None:
+        def loop():
+            while not self._stop.wait(interval):
+                try:
+                    if not self._post("/heartbeat", {"id": self._ent["id"]}).get("found"):
+                        self._post("/register", self._ent)
+                except OSError:
+                    pass                      # the control plane is away: keep trying, the engine keeps serving
+
+        self._thread = threading.Thread(target=loop, name="ctrl-heartbeat", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        if self._ent is not None:
+            try:
+                self._post("/unregister", {"id": self._ent["id"]})
+            except OSError:
+                pass
+
+
+def advertise_host(host: str) -> str:
+    """The address other machines should use for a server bound to `host` (a wildcard bind is announced under this machine's
+    name resolved to an address, falling back to loopback)."""
+    if host not in ("0.0.0.0", "", "::"):
+        return host
+    import socket
+    try:
+        return socket.gethostbyname(socket.gethostname())
+    except OSError:
+        return "127.0.0.1"
+
+
+def register_with_ctrl(config, host: str, port: int, served_model_name: str) -> Optional[CtrlClient]:
+    """Announce this engine's HTTP endpoint and keep it alive; None when the control plane cannot be reached."""
+    adv = advertise_host(host)
+    cli = CtrlClient(config.ctrl_address, getattr(config, "ctrl_scope", None))
+    ent_id = f"nanoengine-{served_model_name}-{adv}:{port}"
+    if not cli.register(ent_id, adv, port, role=config.mode, model=served_model_name, engine_id=config.engine_id):
+        return None
+    cli.start_heartbeat()
+    return cli

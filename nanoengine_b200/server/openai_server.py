@@ -380,9 +380,19 @@ def run_server(config, host: Optional[str] = None, port: Optional[int] = None, t
     proc, endpoint = spawn_backend(config, endpoint=getattr(config, "engine_endpoint", None))
     client = EngineClient(endpoint, proc)
     tok = load_tokenizer(config.model, config.model_config.vocab_size)
-    app = create_app(client, tok, model_name=config.model, tool_format=tool_format, mode=config.mode)
+    import os
+    name = getattr(config, "served_model_name", None) or os.path.basename(str(config.model).rstrip("/")) or str(config.model)
+    app = create_app(client, tok, model_name=name, tool_format=tool_format, mode=config.mode)
+    ctrl = None
+    if config.ctrl_address:
+        from .ctrl import register_with_ctrl
+        ctrl = register_with_ctrl(config, host or config.host, port or config.port, name)
+        if ctrl is None:
+            print(f"control plane {config.ctrl_address} unreachable: this engine will not be discovered", flush=True)
     try:
         uvicorn.run(app, host=host or config.host, port=port or config.port, log_level=config.log_level.lower())
     finally:
+        if ctrl is not None:
+            ctrl.stop()
         if proc.is_alive():
             proc.terminate()

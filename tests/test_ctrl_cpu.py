@@ -1,0 +1,120 @@
+"""The control plane: registry with expiry and scopes, the engine-side client (heartbeat, re-registration after the registry forgot
+the entry), and the C++ gateway discovering and dropping engines through it."""
+import json
+import os
+import socket
+import subprocess
+import threading
+import time
+import urllib.request
+
+import pytest
+
+from nanoengine_b200.server.ctrl import CtrlClient, Registry, advertise_host, make_server
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GATEWAY = os.path.join(ROOT, "nanoengine_b200", "_native", "ne-gateway")
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _serve(ttl=15.0):
+    port = _port()
+    srv = make_server("127.0.0.1", port, ttl)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    return srv, f"http://127.0.0.1:{port}"
+
+
+def test_registry_expiry_scopes_and_validation():
+    t = [0.0]
+    reg = Registry(ttl=10.0, clock=lambda: t[0])
+    reg.register({"id": "a", "host": "h1", "port": 8000, "role": "prefill", "model": "m", "scope": "blue"})
+    reg.register({"id": "b", "port": 8001, "model": "m"})
+    assert {e["id"] for e in reg.list()} == {"a", "b"} and [e["id"] for e in reg.list("blue")] == ["a"]
+    assert reg.list("blue")[0]["url"] == "http://h1:8000" and reg.list()[1]["role"] == "hybrid"
+    t[0] = 8.0
+    assert reg.heartbeat("a") and not reg.heartbeat("nobody")
+    t[0] = 12.0                                   # b was last seen at 0: gone; a at 8: alive
+    assert [e["id"] for e in reg.list()] == ["a"]
+    t[0] = 30.0
+    assert not reg.heartbeat("a") and reg.list() == []
+    with pytest.raises(ValueError):
+        reg.register({"id": "x", "port": 1, "role": "router"})
+    with pytest.raises(ValueError):
+        reg.register({"host": "h"})
+    assert advertise_host("10.1.2.3") == "10.1.2.3" and advertise_host("0.0.0.0")
+
+
+def test_client_registers_heartbeats_and_comes_back_after_being_forgotten():
+    srv, url = _serve()
+    try:
+        cli = CtrlClient(url, scope="blue")
+        assert cli.register("e0", "127.0.0.1", 8000, role="decode", model="m", engine_id="d0")
+        ents = cli.list_entities()
+        assert len(ents) == 1 and ents[0]["role"] == "decode" and ents[0]["scope"] == "blue" and ents[0]["engine_id"] == "d0"
+        assert CtrlClient(url, scope="green").list_entities() == []
+        cli.start_heartbeat(interval=0.05)
+        srv.registry.unregister("e0")              # the registry lost the entry (a restart)
+        for _ in range(100):
+            if cli.list_entities():
+                break
+            time.sleep(0.02)
+        assert [e["id"] for e in cli.list_entities()] == ["e0"]
+        cli.stop()
+        assert cli.list_entities() == []
+        assert not CtrlClient("http://127.0.0.1:1", timeout=0.2).register("x", "h", 1)      # nobody listening: False, no exception
+        assert json.loads(urllib.request.urlopen(url + "/health").read())["status"] == "ok"
+    finally:
+        srv.shutdown()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_gateway_discovers_engines_through_the_control_plane():
+    from test_gateway import FakeEngine, _post
+    srv, url = _serve(ttl=0.6)
+    e = FakeEngine("hybrid")
+    port = _port()
+    gw = subprocess.Popen([GATEWAY, "--port", str(port), "--host", "127.0.0.1", "--ctrl-address", url], stderr=subprocess.DEVNULL)
+    cli = CtrlClient(url)
+    try:
+        assert cli.register("e0", "127.0.0.1", e.port, model="m")
+        cli.start_heartbeat(interval=0.1)
+        base = f"http://127.0.0.1:{port}"
+        for _ in range(100):
+            try:
+                if json.loads(urllib.request.urlopen(base + "/status").read())["engines"]["hybrid"]:
+                    break
+            except OSError:
+                pass
+            time.sleep(0.1)
+        assert _post(base + "/v1/completions", {"prompt": "x"})[0] == 200
+        cli._stop.set()                             # the engine falls silent (no unregister): its entry expires, the gateway drops it
+        for _ in range(120):
+            if not json.loads(urllib.request.urlopen(base + "/status").read())["engines"]["hybrid"]:
+                break
+            time.sleep(0.1)
+        assert _post(base + "/v1/completions", {"prompt": "x"})[0] == 503
+    finally:
+        gw.terminate(); e.stop(); srv.shutdown()
+
+
+def test_engine_registration_carries_role_model_scope_and_engine_id():
+    from nanoengine_b200 import Config
+    from nanoengine_b200.server.ctrl import register_with_ctrl
+    srv, url = _serve()
+    try:
+        cfg = Config(model="tiny-deepseek-v3", device="cpu", dtype="float32", mode="prefill", engine_id="p7", ctrl_address=url, ctrl_scope="blue",
+                     served_model_name="tiny")
+        cli = register_with_ctrl(cfg, "127.0.0.1", 8123, cfg.served_model_name)
+        assert cli is not None
+        (ent,) = CtrlClient(url, scope="blue").list_entities()
+        assert ent["role"] == "prefill" and ent["model"] == "tiny" and ent["engine_id"] == "p7" and ent["url"] == "http://127.0.0.1:8123"
+        cli.stop()
+        assert CtrlClient(url).list_entities() == []
+        assert register_with_ctrl(Config(model="tiny-deepseek-v3", device="cpu", dtype="float32", ctrl_address="http://127.0.0.1:1"), "127.0.0.1", 1, "m") is None
+    finally:
+        srv.shutdown()
