@@ -5,8 +5,10 @@ heartbeat; the gateway polls the list and adds / drops engines as they come and 
     nanoengine serve MODEL --ctrl_address http://host:4479 [--ctrl_scope blue]      # an engine that registers itself
     nanoengine-router --ctrl-address http://host:4479 [--ctrl-scope blue]           # a gateway that discovers engines
 
-HTTP API (JSON bodies): POST /register {id, host, port, role, model, scope?, engine_id?}, POST /heartbeat {id} -> {found},
-POST /unregister {id}, POST /list_entities {scope?} -> {entities: [...]}, GET /health.
+HTTP API (JSON bodies): POST /register {id, host, port, role, model, scope?, engine_id?}, POST /heartbeat {id} -> {found, unknown},
+POST /unregister {id}, POST /list_entities {scope?} -> {entities: [...]}, GET /health.  Engines also publish their own description
+(`LLMComponent`: block size, cache dtype, layer count, ... under the engine id) with POST /register_entity {id, ...}; a peer reads it
+back with POST /get_entity {id} -> {entity} to check compatibility before it accepts migrated sequences.
 
 Parity: the reference registers with an external control-plane service through its client library
 (server/openai_server.py:1748-1810 `register_with_ctrl`: entity id, endpoint, role / model metadata, heartbeat with
@@ -29,6 +31,7 @@ class Registry:
         self.ttl, self.clock = ttl, clock
         self._mu = threading.Lock()
         self._ents: Dict[str, dict] = {}
+        self._engines: Dict[str, dict] = {}          # engine descriptions by engine id: {"info": {...}, "seen": t}
 
     def register(self, ent: dict) -> None:
         if not ent.get("id") or not ent.get("port"):
@@ -44,16 +47,37 @@ class Registry:
 
     def heartbeat(self, ent_id: str) -> bool:
         with self._mu:
-            e = self._ents.get(ent_id)
+            found = False
+            for table in (self._ents, self._engines):
+                e = table.get(ent_id)
+                if e is None:
+                    continue
+                if self.clock() - e["seen"] > self.ttl:
+                    del table[ent_id]
+                else:
+                    e["seen"] = self.clock()
+                    found = True
+            return found
+
+    def register_engine(self, info: dict) -> None:
+        if not info.get("id"):
+            raise ValueError("an engine description needs an id")
+        with self._mu:
+            self._engines[str(info["id"])] = {"info": dict(info), "seen": self.clock()}
+
+    def get_engine(self, engine_id: str) -> Optional[dict]:
+        with self._mu:
+            e = self._engines.get(engine_id)
             if e is None or self.clock() - e["seen"] > self.ttl:
-                self._ents.pop(ent_id, None)
-                return False
-            e["seen"] = self.clock()
-            return True
+                self._engines.pop(engine_id, None)
+                return None
+            return dict(e["info"])
 
     def unregister(self, ent_id: str) -> bool:
         with self._mu:
-            return self._ents.pop(ent_id, None) is not None
+            a = self._ents.pop(ent_id, None) is not None
+            b = self._engines.pop(ent_id, None) is not None
+            return a or b
 
     def list(self, scope: Optional[str] = None) -> List[dict]:
         now = self.clock()
@@ -90,7 +114,13 @@ def make_server(host: str = "0.0.0.0", port: int = 4479, ttl: float = 15.0, regi
                     reg.register(body)
                     return self._reply(200, {"ok": True})
                 if self.path == "/heartbeat":
-                    return self._reply(200, {"found": reg.heartbeat(str(body.get("id", "")))})
+                    found = reg.heartbeat(str(body.get("id", "")))
+                    return self._reply(200, {"found": found, "unknown": not found})
+                if self.path == "/register_entity":
+                    reg.register_engine(body)
+                    return self._reply(200, {"ok": True})
+                if self.path == "/get_entity":
+                    return self._reply(200, {"entity": reg.get_engine(str(body.get("id", "")))})
                 if self.path == "/unregister":
                     return self._reply(200, {"removed": reg.unregister(str(body.get("id", "")))})
                 if self.path == "/list_entities":

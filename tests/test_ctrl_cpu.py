@@ -118,3 +118,29 @@ def test_engine_registration_carries_role_model_scope_and_engine_id():
         assert register_with_ctrl(Config(model="tiny-deepseek-v3", device="cpu", dtype="float32", ctrl_address="http://127.0.0.1:1"), "127.0.0.1", 1, "m") is None
     finally:
         srv.shutdown()
+
+
+def test_engine_component_publishes_its_description_and_peers_read_it_back():
+    """`LLMComponent` registers the engine's own description (what a peer checks before it accepts migrated sequences) and keeps it
+    alive; after the registry forgot it, the next heartbeat brings it back."""
+    from nanoengine_b200 import Config, LLMComponent
+    srv, url = _serve()
+    comp = None
+    try:
+        comp = LLMComponent(Config(model="tiny-deepseek-v3", device="cpu", dtype="float32", kvcache_block_size=16, num_kvcache_blocks=16,
+                                   max_num_seqs=2, engine_id="d3", mode="decode", ctrl_address=url))
+        assert comp.registered
+        req = urllib.request.Request(url + "/get_entity", json.dumps({"id": "d3"}).encode(), {"Content-Type": "application/json"})
+        ent = json.loads(urllib.request.urlopen(req).read())["entity"]
+        assert ent["id"] == "d3" and ent["block_size"] == 16 and ent == comp.engine_info()
+        srv.registry.unregister("d3")
+        for _ in range(100):
+            if srv.registry.get_engine("d3") is not None:
+                break
+            time.sleep(0.1)
+        assert srv.registry.get_engine("d3") is not None
+        assert CtrlClient(url).list_entities() == []              # an engine description is not an HTTP endpoint: gateways do not see it
+    finally:
+        if comp is not None:
+            comp.shutdown()
+        srv.shutdown()
