@@ -86,6 +86,9 @@ class LLMEngine:
         self.executor.collective_rpc("allocate_kvcache", self.num_blocks)
         self._next_seq_id = 1
         self.migrator = None   # set by the PD layer (disagg.KVMigrator)
+        self.endpoint = None   # ZMQ endpoint of the engine process serving this engine, once it has one (published with the description)
+        self._pd_connect = None        # connector of a prefill engine found through the control plane (tests substitute it)
+        self._pd_unresolved = set()
         # file-backed third KV tier: needs the prefix cache (blocks are found by their chained hash) and one block pool
         self.l3_enabled = False
         if config.l3_dir and config.enable_prefix_caching:
@@ -226,10 +229,35 @@ class LLMEngine:
             merged.append(C.RunnerOut(ids, toks).to_bytes())
         return merged
 
+    def _resolve_pd_peers(self, blobs) -> None:
+        """Decode engines: a sequence arrives from a prefill engine this engine has no connection to yet.  With a control plane
+        configured, look the engine's description up there (it names the ZMQ endpoint of its engine process) and connect: the
+        decode workers publish their pools to it, as they do at start-up for the peers `pd_peers` lists.
+        Parity: reference engine/llm_component.py `_fetch_peer_info_from_ctrl` / `set_peer_info`."""
+        if not self.config.ctrl_address:
+            return
+        eids = {str(e) for b in blobs for e in (getattr(C.MigrationIn.from_bytes(b), "remote_engine_ids", None) or [])}
+        for eid in sorted(eids):
+            known = self.migrator is not None and eid in getattr(self.migrator, "peers", {})
+            if known or not eid or eid in self._pd_unresolved:
+                continue
+            from ..server.ctrl import fetch_engine
+            info = fetch_engine(self.config.ctrl_address, eid)
+            if not info or not info.get("endpoint"):
+                self._pd_unresolved.add(eid)          # asked once: a request from it fails by itself, the engine keeps serving
+                logger.warning("prefill engine %s is not known to the control plane %s", eid, self.config.ctrl_address)
+                continue
+            connect = self._pd_connect
+            if connect is None:
+                from ..parallel.kv_transfer import connect_remote as connect
+            connect(self, eid, info["endpoint"])
+            logger.info("connected to prefill engine %s at %s", eid, info["endpoint"])
+
     def _run_migrations(self, res) -> None:
+        blobs = self.scheduler.serialize_migrate_batches()
+        self._resolve_pd_peers(blobs)
         if self.migrator is None:
             raise RuntimeError("received a migrated request but no KV migrator is attached to this engine")
-        blobs = self.scheduler.serialize_migrate_batches()
         t0 = time.perf_counter()
         ok_ids, bad_ids, nbytes = self.migrator.pull(blobs)
         self.scheduler.record_transfer((time.perf_counter() - t0) * 1e3, nbytes)
@@ -288,7 +316,8 @@ class LLMEngine:
                 "attention_sp": c.attention_sp, "attention_tp": c.attention_tp, "pp": c.pp,
                 "num_hidden_layers": c.model_config.num_hidden_layers, "block_size": c.kvcache_block_size,
                 "architecture": c.model_config.architecture, "kv_cache_dtype": c.resolved_kv_dtype(),
-                "mtp_num_kv_layers": max(1, c.model_config.num_nextn_predict_layers) if c.num_speculative_tokens else 0}
+                "mtp_num_kv_layers": max(1, c.model_config.num_nextn_predict_layers) if c.num_speculative_tokens else 0,
+                "endpoint": getattr(self, "endpoint", None) or c.engine_endpoint}
 
     def shutdown(self):
         self.executor.shutdown()

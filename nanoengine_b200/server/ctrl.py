@@ -190,6 +190,49 @@ class CtrlClient:
                 pass
 
 
+def fetch_engine(address: str, engine_id: str, timeout: float = 3.0) -> Optional[dict]:
+    """The description an engine published under its id (None: unknown, expired, or the control plane is away)."""
+    req = urllib.request.Request(address.rstrip("/") + "/get_entity", json.dumps({"id": engine_id}).encode(), {"Content-Type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=timeout) as r:
+            return json.loads(r.read() or b"{}").get("entity")
+    except OSError:
+        return None
+
+
+class EnginePublisher:
+    """Keeps an engine's description (`LLMEngine.engine_info()`: layout facts a peer checks, the engine process's endpoint) alive in
+    the control plane: publish, heartbeat, publish again when the registry has forgotten it."""
+
+    def __init__(self, address: str, info_fn: Callable[[], dict], interval: float = 5.0):
+        self.address, self.info_fn, self.interval = address.rstrip("/"), info_fn, interval
+        self._stop = threading.Event()
+        self.published = self._publish()
+        self._thread = threading.Thread(target=self._loop, name="ctrl-engine-heartbeat", daemon=True)
+        self._thread.start()
+
+    def _post(self, path: str, obj: dict) -> Optional[dict]:
+        req = urllib.request.Request(self.address + path, json.dumps(obj).encode(), {"Content-Type": "application/json"})
+        try:
+            with urllib.request.urlopen(req, timeout=3.0) as r:
+                return json.loads(r.read() or b"{}")
+        except OSError:
+            return None
+
+    def _publish(self) -> bool:
+        return self._post("/register_entity", self.info_fn()) is not None
+
+    def _loop(self):
+        while not self._stop.wait(self.interval):
+            r = self._post("/heartbeat", {"id": self.info_fn()["id"]})
+            self.published = self._publish() if (r is None or r.get("unknown")) else True
+
+    def stop(self):
+        self._stop.set()
+        self._thread.join(timeout=2)
+        self._post("/unregister", {"id": self.info_fn()["id"]})
+
+
 def advertise_host(host: str) -> str:
     """The address other machines should use for a server bound to `host` (a wildcard bind is announced under this machine's
     name resolved to an address, falling back to loopback)."""

@@ -53,6 +53,13 @@ def run_engine_backend(config_dict: dict, endpoint: str, ready=None, engine_fact
         from ..engine.llm_engine import LLMEngine
         engine = LLMEngine(Config.from_dict(config_dict))
     owner: Dict[int, bytes] = {}       # seq_id -> client identity
+    publisher = None
+    if engine_factory is None:
+        engine.endpoint = endpoint
+        if config_dict.get("ctrl_address"):
+            # peers find this engine process (a decode engine: the prefill engine that sent it a sequence) through the control plane
+            from .ctrl import EnginePublisher
+            publisher = EnginePublisher(config_dict["ctrl_address"], engine.engine_info)
     for peer_id, peer_ep in (config_dict.get("pd_peers") or {}).items():
         from ..parallel.kv_transfer import connect_remote
         connect_remote(engine, peer_id, peer_ep)      # decode role: prefill engines that will push KV into this engine's pools
@@ -125,6 +132,8 @@ def run_engine_backend(config_dict: dict, endpoint: str, ready=None, engine_fact
                 owner.pop(o.seq_id, None)
         for ident, lst in per_client.items():
             sock.send_multipart([ident, C.WirePacket(C.ACT_STEPOUT_BATCH, _pack_stepouts(lst)).to_bytes()])
+    if publisher is not None:
+        publisher.stop()
     try:
         engine.shutdown()
     except Exception:

@@ -144,3 +144,51 @@ def test_engine_component_publishes_its_description_and_peers_read_it_back():
         if comp is not None:
             comp.shutdown()
         srv.shutdown()
+
+
+def test_decode_engine_finds_its_prefill_peer_through_the_control_plane():
+    """No `pd_peers`: the first sequence migrated from an unknown prefill engine makes the decode engine look that engine up in the
+    control plane and connect to the endpoint its description names (the connector is substituted: CPU engines share memory, GPU
+    engines would map each other's pools).  The tokens equal the hybrid engine's; an engine the control plane does not know is asked
+    for once."""
+    import torch
+    from nanoengine_b200 import Config, LLM, RequestMigrate, SamplingParams
+    from nanoengine_b200.parallel.kv_transfer import KVMigrator, LocalTransport
+    from nanoengine_b200.server.ctrl import EnginePublisher
+    srv, url = _serve()
+    pub = None
+    try:
+        base = dict(model="tiny-deepseek-v3", dtype="float32", device="cpu", kvcache_block_size=16, max_num_seqs=8, num_kvcache_blocks=64)
+        g = torch.Generator().manual_seed(21)
+        prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (30, 17)]
+        sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+        want = {o["seq_id"]: o["token_ids"] for o in LLM(Config(**base)).generate(prompts, sp)}
+        prefill = LLM(Config(**base, mode="prefill", engine_id="p0", engine_endpoint="ipc:///tmp/ne-test-p0.sock"))
+        decode = LLM(Config(**base, mode="decode", engine_id="d0", ctrl_address=url))
+        pub = EnginePublisher(url, prefill.engine.engine_info, interval=0.2)
+        assert pub.published
+        calls = []
+
+        def connect(engine, eid, endpoint):
+            calls.append((eid, endpoint))
+            tr = LocalTransport([prefill.engine.executor.runner], [engine.executor.runner])
+            engine.migrator = KVMigrator(tr, engine.engine_info(), prefill.engine.engine_info())
+
+        decode.engine._pd_connect = connect
+        firsts = {}
+        for b in prefill.generate(prompts, sp, return_serialized=True):
+            sid, first = RequestMigrate.from_bytes(b).metadata
+            firsts[sid] = first
+            decode.add_request_payload(b)
+        outs = {o["seq_id"]: [firsts[o["seq_id"]]] + o["token_ids"] for o in decode.generate()}
+        assert outs == want and calls == [("p0", "ipc:///tmp/ne-test-p0.sock")]            # looked up and connected once
+        # a sequence from an engine nobody published
+        lone = LLM(Config(**base, mode="prefill", engine_id="ghost"))
+        blob = lone.generate(prompts[:1], sp, return_serialized=True)[0]
+        decode.add_request_payload(blob)
+        decode.generate()               # takes the migrator's default route; the lookup is made once and remembered as failed
+        assert "ghost" in decode.engine._pd_unresolved and len(calls) == 1
+    finally:
+        if pub is not None:
+            pub.stop()
+        srv.shutdown()
