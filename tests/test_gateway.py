@@ -238,3 +238,38 @@ def test_start_status_stop_run_the_gateway_as_a_daemon(tmp_path):
     finally:
         run("stop", *common)
         e.stop()
+
+
+@pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
+def test_malformed_requests_do_not_take_the_gateway_down():
+    e = FakeEngine("hybrid")
+    p, gw = _gateway("--hybrid", e.url)
+    port = int(gw.rsplit(":", 1)[1])
+
+    def raw(data: bytes):
+        with socket.create_connection(("127.0.0.1", port), timeout=3) as s:
+            s.sendall(data)
+            s.settimeout(3)
+            try:
+                return s.recv(4096)
+            except OSError:
+                return b""
+
+    try:
+        raw(b"\x00\xff\xfe garbage\r\n\r\n")
+        raw(b"POST /v1/completions HTTP/1.1\r\nContent-Length: 999999999999999999999\r\n\r\n{}")
+        raw(b"POST /v1/completions HTTP/1.1\r\nContent-Length: 5\r\n\r\n{\"a\"")
+        raw(b"GET /status HTTP/1.1\r\n" + b"X-Pad: " + b"a" * 70000 + b"\r\n\r\n")
+        for body in (b"", b"not json", b'{"model": ', b'{"model": {"nested": [1, 2, {"x": "\\u12"}]}}', b"[" * 2000, b'{"kv_transfer_params": 7, "stream": "yes"}'):
+            req = urllib.request.Request(gw + "/v1/chat/completions", body, {"Content-Type": "application/json"})
+            try:
+                urllib.request.urlopen(req, timeout=5).read()
+            except urllib.error.HTTPError:
+                pass
+            except OSError:
+                pass
+        assert p.poll() is None                                                     # still running
+        assert json.loads(urllib.request.urlopen(gw + "/health").read())["engines"] == 1
+        assert _post(gw + "/v1/completions", {"prompt": "x"})[0] == 200
+    finally:
+        p.terminate(); e.stop()
