@@ -192,3 +192,29 @@ def test_decode_engine_finds_its_prefill_peer_through_the_control_plane():
         if pub is not None:
             pub.stop()
         srv.shutdown()
+
+
+def test_ctrl_command_line_and_config_flags():
+    import sys
+    from nanoengine_b200.server.cli import parse_config_args
+    port = _port()
+    p = subprocess.Popen([sys.executable, "-m", "nanoengine_b200.server.cli", "ctrl", "--host", "127.0.0.1", "--port", str(port), "--ttl", "3"],
+                         cwd=ROOT, stderr=subprocess.DEVNULL)
+    try:
+        url = f"http://127.0.0.1:{port}"
+        for _ in range(100):
+            try:
+                if json.loads(urllib.request.urlopen(url + "/health", timeout=0.5).read())["status"] == "ok":
+                    break
+            except OSError:
+                time.sleep(0.1)
+        cli = CtrlClient(url)
+        assert cli.register("e0", "127.0.0.1", 8000, model="m") and len(cli.list_entities()) == 1
+    finally:
+        p.terminate()
+        p.wait(timeout=10)
+    common, roles = parse_config_args(["--ctrl_address", "http://h:4479", "--ctrl-scope", "blue", "--served_model_name", "m", "--engine_endpoint",
+                                       "ipc:///tmp/x.sock", "--pd_peers", '{"p0": "ipc:///tmp/p0.sock"}', "--status_log_interval_s", "0",
+                                       "--fp8_scale_format", "ue8m0", "--decode.max_num_seqs", "64"])
+    assert common["ctrl_scope"] == "blue" and common["pd_peers"] == {"p0": "ipc:///tmp/p0.sock"} and common["status_log_interval_s"] == 0.0
+    assert common["fp8_scale_format"] == "ue8m0" and common["engine_endpoint"] == "ipc:///tmp/x.sock" and roles["decode"] == {"max_num_seqs": 64}
