@@ -178,6 +178,15 @@ class Config:
                                ("moe_intermediate_size", mc.moe_intermediate_size if mc.n_routed_experts else 0)):
                 if size and (size % self.ffn_tp or (mc.quant == "fp8" and (size // self.ffn_tp) % 128)):
                     raise ValueError(f"{what} must split evenly over ffn_tp (in 128-wide blocks for fp8 weights)")
+        if mc.quant == "nvfp4":
+            # packed e2m1 experts: the tensor-core kernel takes K in multiples of 256; experts are sharded over ffn_ep only
+            if not mc.n_routed_experts:
+                raise ValueError("NVFP4 quantisation applies to routed experts; this model has none")
+            if self.ffn_tp != 1:
+                raise ValueError("NVFP4 experts are sharded over ffn_ep only (ffn_tp must be 1)")
+            width = getattr(mc, "routed_expert_hidden_size", None) or mc.hidden_size
+            if width % 256 or mc.moe_intermediate_size % 256:
+                raise ValueError("NVFP4 experts need hidden and moe_intermediate sizes in multiples of 256")
         if self.max_model_len is None:
             self.max_model_len = mc.max_position_embeddings
         if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1:

@@ -84,3 +84,14 @@ def test_modelopt_checkpoint_round_trip(tmp_path):
     assert dense.dtype == torch.float32 and _rel(dense[: want.shape[0]], want) < 0.13
     llm.add_request_payload(RequestIn(1, [5, 6, 7, 8], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)).to_bytes())
     assert len([o["token_ids"] for o in llm.generate()][0]) == 3
+
+
+def test_config_refuses_shapes_the_nvfp4_kernels_do_not_take():
+    import pytest
+    from nanoengine_b200 import Config
+    ok = tiny_deepseek_v3(moe_intermediate_size=256, intermediate_size=512, quant="nvfp4")
+    Config(model_config=ok, dummy_weight=True, device="cpu", dtype="float32")
+    with pytest.raises(ValueError, match="multiples of 256"):
+        Config(model_config=tiny_deepseek_v3(quant="nvfp4"), dummy_weight=True, device="cpu", dtype="float32")        # moe_intermediate_size 128
+    with pytest.raises(ValueError, match="routed experts"):
+        Config(model_config=tiny_deepseek_v3(quant="nvfp4", n_routed_experts=0, moe_intermediate_size=256), dummy_weight=True, device="cpu", dtype="float32")
