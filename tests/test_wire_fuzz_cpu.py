@@ -9,7 +9,7 @@ from nanoengine_b200._native import _core as C
 PARSERS = [C.RequestIn, C.RequestMigrate, C.MigrationIn, C.RunnerIn, C.RunnerOut, C.WirePacket]
 
 
-@settings(max_examples=200, deadline=None)
+@settings(derandomize=True, max_examples=200, deadline=None)
 @given(st.binary(max_size=256))
 def test_arbitrary_bytes_are_rejected_not_crashed_on(data):
     for cls in PARSERS:
@@ -19,7 +19,7 @@ def test_arbitrary_bytes_are_rejected_not_crashed_on(data):
             pass
 
 
-@settings(max_examples=150, deadline=None)
+@settings(derandomize=True, max_examples=150, deadline=None)
 @given(st.lists(st.integers(0, 2 ** 31 - 1), min_size=1, max_size=64), st.integers(1, 2 ** 40), st.floats(0, 4, allow_nan=False),
        st.integers(1, 4096), st.booleans(), st.integers(0, 2 ** 60), st.data())
 def test_request_round_trip_and_single_byte_mutations(tokens, seq_id, temp, max_tokens, ignore_eos, affinity, data):
@@ -41,7 +41,7 @@ def test_request_round_trip_and_single_byte_mutations(tokens, seq_id, temp, max_
         pass
 
 
-@settings(max_examples=40, deadline=None)
+@settings(derandomize=True, max_examples=40, deadline=None)
 @given(st.integers(0, 2 ** 32 - 1))
 def test_random_request_streams_leave_the_block_pool_balanced(seed):
     rng = random.Random(seed)
