@@ -75,7 +75,7 @@ def test_client_registers_heartbeats_and_comes_back_after_being_forgotten():
 @pytest.mark.skipif(not os.path.exists(GATEWAY), reason="gateway binary not built")
 def test_gateway_discovers_engines_through_the_control_plane():
     from test_gateway import FakeEngine, _post
-    srv, url = _serve(ttl=0.6)
+    srv, url = _serve(ttl=1.5)
     e = FakeEngine("hybrid")
     port = _port()
     gw = subprocess.Popen([GATEWAY, "--port", str(port), "--host", "127.0.0.1", "--ctrl-address", url], stderr=subprocess.DEVNULL)
