@@ -165,14 +165,11 @@ class MLAAttention(nn.Module):
 
 NONABSORBED_PREFILL = True        # prompts without a cached prefix attend in the 192 / 128-wide geometry on the GPU
 OVERLAP_SHARED_EXPERTS = True
-_SIDE_STREAMS = {}
 
 
 def _side_stream(device):
-    key = torch.device(device).index
-    if key not in _SIDE_STREAMS:
-        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
-    return _SIDE_STREAMS[key]
+    from ..runtime.stream_pool import get_cuda_stream
+    return get_cuda_stream("shared_expert", device)
 
 
 class MoEGate(nn.Module):
