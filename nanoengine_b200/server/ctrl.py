@@ -234,15 +234,10 @@ class EnginePublisher:
 
 
 def advertise_host(host: str) -> str:
-    """The address other machines should use for a server bound to `host` (a wildcard bind is announced under this machine's
-    name resolved to an address, falling back to loopback)."""
-    if host not in ("0.0.0.0", "", "::"):
-        return host
-    import socket
-    try:
-        return socket.gethostbyname(socket.gethostname())
-    except OSError:
-        return "127.0.0.1"
+    """The address other machines should use for a server bound to `host` (a wildcard bind is announced under this machine's own
+    address)."""
+    from ..utils.network import get_advertise_host
+    return get_advertise_host(host)
 
 
 def register_with_ctrl(config, host: str, port: int, served_model_name: str) -> Optional[CtrlClient]:
