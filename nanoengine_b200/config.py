@@ -132,6 +132,14 @@ class Config:
             raise ValueError("attention_tp must divide (or be a multiple of) num_key_value_heads")
         if self.num_speculative_tokens < 0:
             raise ValueError("num_speculative_tokens must be >= 0")
+        if mc.is_dsv4:
+            # the compressor and the window / pooled-row attention are stated in PyTorch ops that read host-side batch facts
+            if self.attention_tp != 1 or self.pp != 1 or self.num_speculative_tokens or self.enable_hisparse:
+                raise ValueError("DeepSeek-V4 runs with attention_tp = pp = 1, without speculative decoding or the hot / cold tier")
+            for r in mc.compress_ratios or []:
+                if r and self.kvcache_block_size % r and r % self.kvcache_block_size:
+                    raise ValueError("every compression ratio must divide kvcache_block_size or be a multiple of it")
+            self.enforce_eager = True
         if self.num_speculative_tokens > 0:
             if mc.num_nextn_predict_layers < 1:
                 raise ValueError("speculative decoding needs a model with MTP layers (num_nextn_predict_layers >= 1)")

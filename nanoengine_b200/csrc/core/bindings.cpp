@@ -207,6 +207,8 @@ PYBIND11_MODULE(_core, m) {
       .def_readwrite("local_handoff_slots", &MigrateBatch::local_handoff_slots)
       .def_readwrite("remote_handoff_slots", &MigrateBatch::remote_handoff_slots)
       .def_readwrite("remote_engine_ids", &MigrateBatch::remote_engine_ids)
+      .def_readwrite("local_state_slots", &MigrateBatch::local_state_slots)
+      .def_readwrite("remote_state_slots", &MigrateBatch::remote_state_slots)
       .def("to_bytes", [](const MigrateBatch& r) { return py::bytes(r.to_bytes()); })
       .def_static("from_bytes", [](const std::string& b) { return MigrateBatch::from_bytes(b); });
 

@@ -83,6 +83,7 @@ class Scheduler {
     s->sampling = m.sampling_params; s->logprobs = m.logprobs; s->affinity_key = m.affinity_key;
     s->pending_migration = false; s->remote_block_table = m.migrate_block_table; s->remote_dp_idx = m.migrate_dp_idx;
     s->remote_handoff_slot = m.migrate_handoff_slot; s->remote_engine_id = m.migrate_engine_id;
+    s->remote_state_slot = m.migrate_state_slot;
     s->t_arrival = now_seconds(); s->t_first_token = s->t_arrival; s->t_last_token = s->t_arrival;
     seqs_[m.seq_id] = std::move(s);
     waiting_migration_.push_back(m.seq_id);
@@ -580,6 +581,7 @@ class Scheduler {
         m.block_offsets.push_back((int)m.local_blocks.size());
         m.remote_dp_idx.push_back(s.remote_dp_idx); m.local_handoff_slots.push_back(s.handoff_slot);
         m.remote_handoff_slots.push_back(s.remote_handoff_slot); m.remote_engine_ids.push_back(s.remote_engine_id);
+        m.local_state_slots.push_back(s.state_slot); m.remote_state_slots.push_back(s.remote_state_slot);
         placed = true; break;
       }
       if (!placed) break;

@@ -103,6 +103,7 @@ struct Sequence {
   std::vector<int32_t> remote_block_table;
   int32_t remote_dp_idx = 0;
   int32_t remote_handoff_slot = -1;
+  int32_t remote_state_slot = -1;    // the prefill engine's state slot of a migrated sequence
   std::string remote_engine_id;
   // timing (seconds, steady clock)
   double t_arrival = 0, t_first_token = 0, t_last_token = 0, t_first_scheduled = 0;

@@ -268,10 +268,12 @@ struct MigrateBatch {
   std::vector<int32_t> remote_dp_idx;
   std::vector<int32_t> local_handoff_slots, remote_handoff_slots;
   std::vector<std::string> remote_engine_ids;
+  std::vector<int32_t> local_state_slots, remote_state_slots;  // per-sequence state (recurrent state, compressor carry); -1 = none
   std::string to_bytes() const {
     ByteWriter w; w.header(TAG_MIGRATE_BATCH); w.i32(dp_idx); w.vec(seq_ids); w.vec(local_blocks); w.vec(remote_blocks);
     w.vec(block_offsets); w.vec(remote_dp_idx); w.vec(local_handoff_slots); w.vec(remote_handoff_slots);
-    w.u32((uint32_t)remote_engine_ids.size()); for (auto& e : remote_engine_ids) w.str(e); return w.buf;
+    w.u32((uint32_t)remote_engine_ids.size()); for (auto& e : remote_engine_ids) w.str(e);
+    w.vec(local_state_slots); w.vec(remote_state_slots); return w.buf;
   }
   static MigrateBatch from_bytes(const std::string& s) {
     ByteReader r(s); r.header(TAG_MIGRATE_BATCH); MigrateBatch m; m.dp_idx = r.i32(); m.seq_ids = r.vec<uint64_t>();
@@ -280,6 +282,7 @@ struct MigrateBatch {
     m.remote_handoff_slots = r.vec<int32_t>();
     uint32_t n = r.u32(); if (n > r.remaining()) throw WireError("wire: bad engine id count");
     for (uint32_t i = 0; i < n; i++) m.remote_engine_ids.push_back(r.str());
+    m.local_state_slots = r.vec<int32_t>(); m.remote_state_slots = r.vec<int32_t>();
     if (!r.done()) throw WireError("wire: trailing bytes in MigrateBatch");
     return m;
   }

@@ -1,6 +1,6 @@
 // MoE routing and the token <-> expert-major layout transforms around the grouped GEMMs.
 //
-//   route    : sigmoid (+ correction bias, group-limited) or softmax top-k with renormalisation and scaling
+//   route    : sigmoid / sqrt-softplus (+ correction bias, group-limited) or softmax top-k with renormalisation and scaling
 //   count    : per-expert token counts and each (token, k) pair's slot inside its expert
 //   scan     : 128-aligned exclusive prefix over the counts -> row_start[e] (every expert's rows start a GEMM tile)
 //   scatter  : write each routed token row into the expert-major buffer, quantising to e4m3 1x128 on the way
@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     choice[e] = v;
   }
   const float* lr = choice;
-  if (softmax) {
+  if (softmax == 1) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, lr[e]);
     m = warp_max(m);
@@ -45,7 +45,12 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     float inv = 1.f / s;
     for (int e = lane; e < E; e += 32) { score[e] *= inv; choice[e] = score[e] + (bias ? bias[e] : 0.f); }
   } else {
-    for (int e = lane; e < E; e += 32) { float v = 1.f / (1.f + __expf(-lr[e])); score[e] = v; choice[e] = v + (bias ? bias[e] : 0.f); }
+    // softmax == 2: sqrt(softplus(x)) (DeepSeek-V4), else sigmoid
+    for (int e = lane; e < E; e += 32) {
+      const float x = lr[e];
+      float v = softmax == 2 ? sqrtf(x > 20.f ? x : log1pf(__expf(x))) : 1.f / (1.f + __expf(-x));
+      score[e] = v; choice[e] = v + (bias ? bias[e] : 0.f);
+    }
   }
   __syncwarp();
   if (n_group > 1) {

@@ -93,6 +93,15 @@ class ModelConfig:
     routed_expert_hidden_size: int = 0       # > 0: routed experts work in a latent space of this width (down-proj, experts, norm, up-proj)
     activation_situ_beta: float = 0.0        # > 0: the gated activation is SiTU-GLU with this beta
     activation_situ_linear_beta: float = 0.0
+    # DeepSeek-V4: one shared key / value row per token (head_dim wide, the last qk_rope_head_dim dims rotated), a sliding window of
+    # raw rows plus rows pooled over `compress_ratios[layer]` tokens (0 = window only), a sink logit per head, a grouped low-rank
+    # output projection, hash-routed first layers
+    window_size: int = 0
+    compress_ratios: Optional[List[int]] = None
+    compress_rope_theta: float = 0.0         # rotary base of the layers that compress (0: rope_theta)
+    o_lora_rank: int = 0
+    o_groups: int = 0
+    num_hash_layers: int = 0                 # the first this-many MoE layers pick experts from a token-id table
     # MTP
     num_nextn_predict_layers: int = 0
     # quantisation of linear / expert weights: None (use dtype) or "fp8" (e4m3, 128x128 block scales)
@@ -110,6 +119,14 @@ class ModelConfig:
         return self.architecture in ("DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM",
                                      "GlmMoeDsaForCausalLM", "KimiK2ForCausalLM", "Glm5NextForConditionalGeneration",
                                      "KimiK3ForConditionalGeneration")
+
+    @property
+    def is_dsv4(self) -> bool:
+        return self.architecture.startswith("DeepseekV4")
+
+    def compress_ratio(self, layer_idx: int) -> int:
+        r = self.compress_ratios or []
+        return int(r[layer_idx]) if layer_idx < len(r) else 0
 
     @property
     def is_hybrid_gdn(self) -> bool:
@@ -259,6 +276,22 @@ class ModelConfig:
                       "final_logit_softcapping"):
                 if d.get(k) is None:
                     d[k] = 0
+        if arch.startswith("DeepseekV4"):
+            # the release's own spellings (reference models/deepseek_v4/deepseek_v4.py:2894-2921)
+            for ours, theirs in (("hidden_size", "dim"), ("num_hidden_layers", "n_layers"), ("num_attention_heads", "n_heads"),
+                                 ("qk_rope_head_dim", "rope_head_dim"), ("moe_intermediate_size", "moe_inter_dim"),
+                                 ("num_experts_per_tok", "n_activated_experts"), ("rms_norm_eps", "norm_eps"),
+                                 ("num_hash_layers", "n_hash_layers"), ("scoring_func", "score_func"),
+                                 ("routed_scaling_factor", "route_scale"), ("max_position_embeddings", "max_seq_len")):
+                if ours not in d and theirs in d:
+                    d[ours] = d.pop(theirs)
+            for k, v in (("num_key_value_heads", 1), ("n_shared_experts", 1), ("hc_mult", 4), ("hc_sinkhorn_iters", 20), ("hc_eps", 1e-6),
+                         ("o_groups", 8), ("o_lora_rank", 1024), ("window_size", 128), ("index_topk", 512), ("scoring_func", "sqrtsoftplus"),
+                         ("first_k_dense_replace", 0), ("n_group", 1), ("topk_group", 1), ("norm_topk_prob", True), ("head_dim", 512),
+                         ("max_position_embeddings", 16384), ("routed_scaling_factor", 1.0)):
+                d.setdefault(k, v)
+            if d.get("swiglu_limit") is None:
+                d["swiglu_limit"] = 0.0
         if arch.startswith("Glm5Next"):
             d.setdefault("swiglu_limit", 10.0)
             d.setdefault("hc_mult", 4)
@@ -410,6 +443,19 @@ def tiny_kimi_k3(**over) -> ModelConfig:
                 linear_kind="kda", linear_num_key_heads=2, linear_num_value_heads=2, linear_key_head_dim=32, linear_value_head_dim=32,
                 linear_conv_kernel_dim=4, kda_gate_lower_bound=-5.0, mla_output_gate=True, mla_skip_rope=True, attn_res_block_size=2,
                 routed_expert_hidden_size=64, activation_situ_beta=4.0, activation_situ_linear_beta=25.0)
+    base.update(over)
+    return ModelConfig(**base)
+
+
+def tiny_deepseek_v4(**over) -> ModelConfig:
+    """CPU-sized DeepSeek-V4 shape: a window-only layer, a ratio-4 (overlapping) and a ratio-8 compressing layer, 2 hyper-connection
+    streams, the first MoE layer hash-routed."""
+    base = dict(architecture="DeepseekV4ForCausalLM", vocab_size=512, hidden_size=128, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=1, head_dim=64, qk_rope_head_dim=16, q_lora_rank=48, o_lora_rank=32, o_groups=2, window_size=8,
+                compress_ratios=[0, 4, 8], compress_rope_theta=40000.0, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
+                moe_intermediate_size=64, first_k_dense_replace=0, n_group=1, topk_group=1, routed_scaling_factor=1.5, norm_topk_prob=True,
+                scoring_func="sqrtsoftplus", num_hash_layers=1, hc_mult=2, hc_sinkhorn_iters=3, swiglu_limit=10.0,
+                max_position_embeddings=4096)
     base.update(over)
     return ModelConfig(**base)
 

@@ -39,6 +39,11 @@ def _kimi_k3():
     return KimiK3ForConditionalGeneration
 
 
+def _deepseek_v4():
+    from .deepseek_v4 import DeepseekV4ForCausalLM
+    return DeepseekV4ForCausalLM
+
+
 def _gemma4():
     from .gemma4 import Gemma4ForCausalLM
     return Gemma4ForCausalLM
@@ -47,6 +52,7 @@ def _gemma4():
 _LAZY = {
     "Gemma4ForCausalLM": _gemma4, "Gemma4ForConditionalGeneration": _gemma4,
     "Glm5NextForConditionalGeneration": _glm5_next, "KimiK3ForConditionalGeneration": _kimi_k3,
+    "DeepseekV4ForCausalLM": _deepseek_v4,
     "DeepseekV2ForCausalLM": _deepseek, "DeepseekV3ForCausalLM": _deepseek, "DeepseekV32ForCausalLM": _deepseek,
     "GlmMoeDsaForCausalLM": _deepseek, "KimiK2ForCausalLM": _deepseek,
     "Qwen3MoeForCausalLM": _qwen3_moe, "Qwen3ForCausalLM": _qwen3_moe,

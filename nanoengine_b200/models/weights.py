@@ -20,8 +20,8 @@ import torch
 
 from .config import ModelConfig
 
-_EXPERT_RE = re.compile(r"\.mlp\.experts\.(\d+)\.")
-_LAYER_RE = re.compile(r"^model\.layers\.(\d+)\.")
+_EXPERT_RE = re.compile(r"\.(?:mlp|ffn)\.experts\.(\d+)\.")
+_LAYER_RE = re.compile(r"^(?:model\.)?layers\.(\d+)\.")
 
 
 def expert_owner_filter(cfg: ModelConfig, ep_size: int, ep_rank: int, layer_range=None) -> Callable[[str], bool]:
@@ -67,6 +67,9 @@ def hf_param_shapes(cfg: ModelConfig, include_mtp: bool = False) -> Dict[str, Tu
     out: Dict[str, Tuple[int, ...]] = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,), "lm_head.weight": (V, H)}
     if cfg.architecture.startswith("Gemma4"):
         return _gemma4_param_shapes(cfg, out)
+    if cfg.is_dsv4:
+        from .deepseek_v4 import dsv4_param_shapes
+        return dsv4_param_shapes(cfg, out)
 
     def attn(p):
         if cfg.is_mla:
@@ -231,13 +234,17 @@ def random_hf_weights(cfg: ModelConfig, seed: int = 0, device="cpu", keep: Optio
             continue
         g = torch.Generator(device=dev)
         g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFF)
-        if name.endswith("layer_scalar"):
+        if name.endswith("tid2eid"):            # token id -> its experts: distinct ids per row
+            t = torch.rand(shape[0], cfg.n_routed_experts, generator=g, device=dev).argsort(-1)[:, : shape[1]].to(torch.int32)
+        elif name.endswith("attn_sink"):
+            t = 0.5 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        elif name.endswith("layer_scalar"):
             t = 1.0 + 0.05 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
         elif name.endswith("A_log"):
             t = torch.log(1.0 + 3.0 * torch.rand(shape, generator=g, device=dev, dtype=torch.float32))
         elif name.endswith(("_fn", "_base")):
             t = 0.05 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
-        elif name.endswith("_scale") and len(shape) == 1 and shape[0] == 3:
+        elif name.endswith("_scale") and len(shape) == 1 and shape[0] in (1, 3):
             t = 1.0 + 0.1 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
         elif name.endswith("dt_bias"):
             t = 0.5 * torch.randn(shape, generator=g, device=dev, dtype=torch.float32)

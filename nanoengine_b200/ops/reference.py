@@ -383,7 +383,7 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_
               balance_ranks: int = 0, log2phy: Optional[torch.Tensor] = None, logcnt: Optional[torch.Tensor] = None):
     """DeepSeek ``noaux_tc`` routing and Qwen3 softmax routing.
 
-    scores = sigmoid|softmax(logits fp32); choice = scores + bias; with n_group > 1 only the
+    scores = sigmoid|softmax|sqrt(softplus) (logits fp32; the last is DeepSeek-V4's, reference models/deepseek_v4/deepseek_v4.py:40-47); choice = scores + bias; with n_group > 1 only the
     topk_group groups with the largest sum of their top-2 choices stay eligible; idx = top_k of
     choice; weights are the un-biased scores, renormalised and scaled
     (reference models/deepseek_v2/deepseek_v2.py:478-543, models/qwen3_moe/qwen3_moe.py:283-297).
@@ -396,7 +396,7 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_
     lf = logits.float()
     if lf.dim() == 3:          # partial sums of a split-K router product
         lf = lf.sum(0)
-    scores = torch.sigmoid(lf) if scoring == "sigmoid" else torch.softmax(lf, -1)
+    scores = (torch.sigmoid(lf) if scoring == "sigmoid" else F.softplus(lf).sqrt() if scoring == "sqrtsoftplus" else torch.softmax(lf, -1))
     choice = scores + bias.float() if bias is not None else scores
     T, E = choice.shape
     if n_group > 1:
@@ -1201,3 +1201,98 @@ def mtp_chain_meta(base_len, num_accepted, block_tables, block_size: int, k: int
     context_lens.copy_((pos + 1).to(context_lens.dtype))
     page = block_tables.long().gather(1, (pos // block_size).unsqueeze(1)).squeeze(1)
     slot_mapping.copy_(page * block_size + pos % block_size)
+
+
+# ---- DeepSeek-V4: compressed KV + window attention with a sink -----------------------------------------------------------------
+def fp8_qdq_pow2(x: torch.Tensor, block: int = 64) -> torch.Tensor:
+    """Round-trip through e4m3 with one power-of-two scale per `block` values of the last dim (what a cache that stores the
+    rows as fp8 would return).  Parity: reference models/deepseek_v4/deepseek_v4.py:549-590."""
+    if x.numel() == 0:
+        return x
+    shape = x.shape
+    v = x.float().reshape(-1, shape[-1] // block, block)
+    amax = v.abs().amax(-1, keepdim=True).clamp(min=1e-4)
+    s = torch.exp2(torch.ceil(torch.log2(amax / 448.0)))
+    return ((v / s).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * s).reshape(shape).to(x.dtype)
+
+
+def dsv4_compress_extend(kv: torch.Tensor, score: torch.Tensor, kv_state: torch.Tensor, score_state: torch.Tensor, pos0: int, ratio: int,
+                         d: int) -> torch.Tensor:
+    """Feed `n` new tokens (positions pos0 .. pos0+n-1) of one sequence to a DeepSeek-V4 KV compressor and return the pooled
+    rows [nb, d] fp32 of every block of `ratio` tokens that the new tokens complete (block j of the result starts at position
+    (pos0 - pos0 % ratio) + j * ratio).
+
+    kv / score [n, c*d] fp32 are the token projections (score already carries the position-in-block bias); c = 2 for ratio 4
+    ("overlap": a block pools the second halves of its own rows together with the first halves of the previous block's rows),
+    else 1.  kv_state / score_state [c*ratio, c*d] fp32 carry the rows of the unfinished block (and, with overlap, of the
+    previous block) between calls and are updated in place; a fresh sequence starts from zeros / -inf.
+    Parity: reference models/deepseek_v4/deepseek_v4.py:979-1077 (whole-prompt form), :1079-1176 (one token)."""
+    overlap = kv.shape[1] == 2 * d
+    off = ratio if overlap else 0
+    m = pos0 % ratio
+    full_kv = torch.cat([kv_state[off: off + m], kv], 0)
+    full_sc = torch.cat([score_state[off: off + m], score], 0)
+    nb = full_kv.shape[0] // ratio
+    rem = full_kv.shape[0] - nb * ratio
+    pooled = kv.new_zeros(0, d)
+    if nb:
+        bk = full_kv[: nb * ratio].view(nb, ratio, -1)
+        bs = full_sc[: nb * ratio].view(nb, ratio, -1)
+        if overlap:
+            pk = torch.cat([kv_state[None, :ratio], bk[:-1]], 0)           # the block before each block
+            ps = torch.cat([score_state[None, :ratio], bs[:-1]], 0)
+            k2 = torch.cat([pk[..., :d], bk[..., d:]], 1)                  # [nb, 2r, d]
+            s2 = torch.cat([ps[..., :d], bs[..., d:]], 1)
+            pooled = (k2 * s2.softmax(1)).sum(1)
+            kv_state[:ratio] = bk[-1]
+            score_state[:ratio] = bs[-1]
+        else:
+            pooled = (bk * bs.softmax(1)).sum(1)
+    kv_state[off:] = 0
+    score_state[off:] = float("-inf")
+    if rem:
+        kv_state[off: off + rem] = full_kv[nb * ratio:]
+        score_state[off: off + rem] = full_sc[nb * ratio:]
+    return pooled
+
+
+def sink_attention(q: torch.Tensor, kv: torch.Tensor, mask: torch.Tensor, sink: torch.Tensor, scale: float) -> torch.Tensor:
+    """Multi-query attention whose keys are also its values, with one learned "sink" logit per head in the softmax denominator.
+    q [T, H, D]; kv [T, L, D] (per-token candidate rows) or [L, D] (shared); mask [T, L] bool (True = attend); sink [H] fp32.
+    A token with nothing to attend returns zeros.  Parity: reference models/deepseek_v4/deepseek_v4.py:1676-1704."""
+    qf, kf = q.float(), kv.float()
+    s = (torch.einsum("thd,tld->thl", qf, kf) if kv.dim() == 3 else torch.einsum("thd,ld->thl", qf, kf)) * scale
+    s = s.masked_fill(~mask.unsqueeze(1), float("-inf"))
+    mx = torch.maximum(s.amax(-1), sink.float().view(1, -1))
+    p = torch.exp(s - mx.unsqueeze(-1))
+    p = p / (p.sum(-1, keepdim=True) + torch.exp(sink.float().view(1, -1, 1) - mx.unsqueeze(-1)))
+    p = p.to(q.dtype).float()
+    return (torch.einsum("thl,tld->thd", p, kf) if kv.dim() == 3 else torch.einsum("thl,ld->thd", p, kf)).to(q.dtype)
+
+
+def dsv4_compress_decode(kv: torch.Tensor, score: torch.Tensor, kv_states: torch.Tensor, score_states: torch.Tensor, slots: torch.Tensor,
+                         positions: torch.Tensor, ratio: int, d: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """`dsv4_compress_extend` for one new token of each of B sequences at once, without a host read: kv / score [B, c*d],
+    the carry pools [slots, c*ratio, c*d] (updated in place at rows `slots`), positions [B].  Returns the pooled rows [B, d]
+    (zeros where the token does not finish a block) and the mask of sequences that finished one."""
+    overlap = kv.shape[1] == 2 * d
+    off = ratio if overlap else 0
+    slots, m = slots.long(), positions.long() % ratio
+    kv_states[slots, off + m] = kv
+    score_states[slots, off + m] = score
+    done = m == ratio - 1
+    dm = done.view(-1, 1, 1)
+    ks, ss = kv_states[slots], score_states[slots]
+    if overlap:
+        k2 = torch.cat([ks[:, :ratio, :d], ks[:, ratio:, d:]], 1)
+        s2 = torch.cat([ss[:, :ratio, :d], ss[:, ratio:, d:]], 1)
+    else:
+        k2, s2 = ks, ss
+    s2 = torch.where(dm, s2, torch.zeros_like(s2))                  # rows that pool nothing stay finite
+    pooled = torch.where(done.unsqueeze(1), (k2 * s2.softmax(1)).sum(1), torch.zeros_like(k2[:, 0]))
+    if overlap:                                                       # the finished block becomes the previous one
+        kv_states[slots, :ratio] = torch.where(dm, ks[:, ratio:], ks[:, :ratio])
+        score_states[slots, :ratio] = torch.where(dm, ss[:, ratio:], ss[:, :ratio])
+    kv_states[slots, off:] = torch.where(dm, torch.zeros_like(ks[:, off:]), ks[:, off:])
+    score_states[slots, off:] = torch.where(dm, torch.full_like(ss[:, off:], float("-inf")), ss[:, off:])
+    return pooled, done

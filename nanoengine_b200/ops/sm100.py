@@ -455,7 +455,7 @@ def moe_route(logits, bias, top_k, n_group=1, topk_group=1, norm_topk_prob=True,
     if log2phy is not None:
         assert log2phy.dtype == torch.int32 and logcnt.dtype == torch.int32 and log2phy.is_contiguous() and log2phy.shape[0] == E
     _ck(lib().ne_moe_route(_p(logits), _p(bias), _p(idx), _p(w), _c.c_int(T), _c.c_int(E), _c.c_int(top_k), _c.c_int(n_group), _c.c_int(topk_group),
-                           _c.c_int(1 if norm_topk_prob else 0), _c.c_float(routed_scaling_factor), _c.c_int(0 if scoring == "sigmoid" else 1),
+                           _c.c_int(1 if norm_topk_prob else 0), _c.c_float(routed_scaling_factor), _c.c_int({"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[scoring]),
                            _c.c_int(planes), _c.c_int(balance_ranks), _p(log2phy), _p(logcnt), _c.c_int(0 if log2phy is None else log2phy.shape[1]), _st()),
         "ne_moe_route")
     return idx, w

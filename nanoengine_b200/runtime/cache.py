@@ -8,11 +8,17 @@ recurrent state    hybrid models with gated delta-net layers keep, per sequence 
                    [Hv, Dv, Dk] fp32 and the convolution window [K-1, conv_dim]; the paged GQA cache then covers only the
                    full-attention layers.  Slot `state_slots` (one past the scheduler-visible range) is scratch.
 
+DeepSeek-V4        one shared key / value row per token and layer in the latent-cache layout [L, blocks, block_size, head_dim];
+                   every compressing layer adds pooled rows [blocks, max(1, block_size / ratio), head_dim] addressed through the
+                   same block table (pooled row b of a sequence sits in the page of token b * ratio) and, per sequence slot, the
+                   compressor's carry [c * ratio, c * head_dim] fp32 twice (values and scores; c = 2 for ratio 4).
+
 One extra block past the scheduler-visible range is reserved as the scratch page that dummy batches of idle
 DP ranks write into.
 
 Parity: reference runtime/context/cache/__init__.py:153-472 (budget :366-372, blocks :431-432),
-cache/mla.py:45-199 (formats and shapes), cache/indexer.py:45-77, cache/gqa.py:56-71.
+cache/mla.py:45-199 (formats and shapes), cache/indexer.py:45-77, cache/gqa.py:56-71, cache/hca.py and cache/csa.py (the
+compressed caches of DeepSeek-V4).
 """
 from __future__ import annotations
 
@@ -53,14 +59,29 @@ class CachePlan:
     layer_dims: Optional[List[int]] = None
     # hot / cold tier (DSA decode engines): the latent pages live in pinned host memory, `hot_rows` rows per sequence slot
     # and layer on the device
+    # DeepSeek-V4: compression ratio of every layer (0 = window only)
+    dsv4_ratios: Optional[List[int]] = None
     hisparse: bool = False
     hot_rows: int = 0
     hs_slots: int = 0
     max_ctx: int = 0
 
     @property
+    def dsv4(self) -> bool:
+        return self.dsv4_ratios is not None
+
+    @property
+    def needs_state_slots(self) -> bool:
+        return self.gdn or self.dsv4
+
+    def comp_entries_per_page(self, ratio: int) -> int:
+        return max(1, self.block_size // ratio)
+
+    @property
     def state_slot_bytes(self) -> int:
-        """Bytes one sequence slot takes over all linear-attention layers."""
+        """Bytes one sequence slot takes over all layers that keep per-sequence state."""
+        if self.dsv4:
+            return sum(2 * 4 * (2 if r == 4 else 1) ** 2 * r * self.row_dim for r in self.dsv4_ratios if r)
         if not self.gdn:
             return 0
         e = 2 if self.kv_dtype in (torch.bfloat16, torch.float16, torch.float8_e4m3fn) else 4
@@ -73,6 +94,8 @@ class CachePlan:
     @property
     def kv_block_bytes(self) -> int:
         e = torch.empty(0, dtype=self.kv_dtype).element_size()
+        if self.dsv4:
+            return (self.num_layers * self.block_size + sum(self.comp_entries_per_page(r) for r in self.dsv4_ratios if r)) * self.row_dim * e
         if self.mla:
             return self.num_layers * self.block_size * self.row_dim * e
         return 2 * self.num_layers * self.block_size * self.kv_heads_local * self.row_dim * e
@@ -98,8 +121,8 @@ class CachePlan:
         bits = C.PLAN_MLA if self.mla else C.PLAN_GQA
         if self.indexer:
             bits |= C.PLAN_INDEXER
-        if self.gdn:
-            bits |= C.PLAN_GDN
+        if self.needs_state_slots:
+            bits |= C.PLAN_GDN          # one state slot per running sequence; no prefix reuse
         if self.hisparse:
             bits |= C.PLAN_HISPARSE
         return bits
@@ -119,6 +142,12 @@ def _make_cache_plan(mc: ModelConfig, kv_dtype_name: str, block_size: int, attn_
                      use_indexer: bool = True, num_layers: Optional[int] = None, state_slots: int = 0) -> CachePlan:
     L = (num_layers if num_layers is not None else mc.num_hidden_layers) + num_mtp_layers
     dt = torch_dtype(kv_dtype_name)
+    if mc.is_dsv4:
+        for r in mc.compress_ratios or []:
+            assert r == 0 or block_size % r == 0 or r % block_size == 0, "a compression ratio must divide the page size or be a multiple of it"
+        # the rows are kept as the values an fp8 cache would return (quantise-dequantise at write), in a 16-bit container
+        return CachePlan(True, False, False, mc.num_hidden_layers, block_size, torch.bfloat16 if dt == torch.float8_e4m3fn else dt, mc.head_dim,
+                         state_slots=state_slots, dsv4_ratios=[mc.compress_ratio(i) for i in range(mc.num_hidden_layers)])
     if mc.is_hybrid_gdn and mc.is_mla:
         # delta-attention layers between MLA layers (GLM5-next, Kimi-K3): latent pages for the full-attention layers (and the
         # MTP layers), one state slot per sequence for the linear ones
@@ -184,6 +213,18 @@ class KVCache:
                                          [self.kv[l] for l in range(plan.num_layers)], device)
         self.host_kv = None
         self.host_families = {}
+        self.comp = self.comp_kv_state = self.comp_score_state = None
+        if plan.dsv4:
+            ns = plan.state_slots + 1
+            self.comp, self.comp_kv_state, self.comp_score_state = [], [], []
+            for r in plan.dsv4_ratios:
+                if not r:
+                    self.comp.append(None); self.comp_kv_state.append(None); self.comp_score_state.append(None)
+                    continue
+                c = 2 if r == 4 else 1
+                self.comp.append(torch.zeros(nb, plan.comp_entries_per_page(r), plan.row_dim, dtype=plan.kv_dtype, device=device))
+                self.comp_kv_state.append(torch.zeros(ns, c * r, c * plan.row_dim, dtype=torch.float32, device=device))
+                self.comp_score_state.append(torch.full((ns, c * r, c * plan.row_dim), float("-inf"), dtype=torch.float32, device=device))
         self.rec_states = self.conv_states = None
         self.scratch_slot = plan.state_slots
         if plan.gdn:
@@ -208,6 +249,9 @@ class KVCache:
         out = [fam("mla_kv" if self.plan.mla else "gqa_kv", self.kv, self.kv.shape[0] if self.plan.mla else 2 * self.kv.shape[1])]
         if self.indexer is not None:
             out.append(fam("indexer", self.indexer, self.indexer.shape[0]))
+        for l, t in enumerate(self.comp or []):
+            if t is not None:
+                out.append(fam(f"dsv4_pooled_{l}", t, 1))
         return out
 
     def slot_families(self) -> List[dict]:
@@ -219,6 +263,10 @@ class KVCache:
                 planes = t.shape[0]
                 per_plane = t.numel() * t.element_size() // planes
                 out.append({"name": name, "tensor": t, "planes": planes, "plane_stride": per_plane, "slot_bytes": per_plane // t.shape[1]})
+        for l, t in enumerate(self.comp_kv_state or []):
+            if t is not None:
+                for name, u in ((f"dsv4_carry_kv_{l}", t), (f"dsv4_carry_score_{l}", self.comp_score_state[l])):
+                    out.append({"name": name, "tensor": u, "planes": 1, "plane_stride": u.numel() * 4, "slot_bytes": u.numel() * 4 // u.shape[0]})
         return out
 
     def allocate_host(self, num_host_blocks: int):
@@ -239,6 +287,9 @@ class KVCache:
         out = [kv[:, bid] if self.plan.mla else kv[:, :, bid]]
         if self.indexer is not None:
             out.append(self.indexer[:, bid])
+        for t in self.comp or []:
+            if t is not None:
+                out.append(t[bid])
         return out
 
     def swap(self, src: List[int], dst: List[int], to_host: bool):

@@ -34,6 +34,10 @@ class ForwardContext:
     seq_fresh: Optional[torch.Tensor] = None        # int32 [B], 1 = no state carried in (first chunk of the prompt)
     conv_states: Optional[List[Any]] = None         # per linear layer [slots, K-1, conv_dim]
     rec_states: Optional[List[Any]] = None          # per linear layer [slots, Hv, Dv, Dk] fp32
+    # DeepSeek-V4 compressors: per layer (None for a window-only layer) the pooled-row pages and the two carry pools
+    comp_caches: Optional[List[Any]] = None         # [blocks, entries_per_page, head_dim]
+    comp_kv_states: Optional[List[Any]] = None      # [slots, c * ratio, c * head_dim] fp32
+    comp_score_states: Optional[List[Any]] = None
     # hot / cold tier of the sparse-attention cache: the tier object and the hot-buffer slot of each sequence
     hisparse: Optional[Any] = None
     hs_slots: Optional[torch.Tensor] = None         # int32 [B]

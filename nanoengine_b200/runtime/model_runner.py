@@ -334,12 +334,15 @@ class ModelRunner:
                 tier.assign(int(s), int(sid))
             ctx.hisparse = tier
             ctx.hs_slots = self._to_dev(np.asarray([s if s >= 0 else tier.scratch_slot for s in b.hisparse_slots], dtype=np.int32))
-        if self.plan.gdn:
+        if self.plan.needs_state_slots:
             # a sequence whose whole context arrives in this step carries no state in; unassigned slots go to the scratch slot
             slots = np.asarray([s if s >= 0 else self.cache.scratch_slot for s in b.state_slots], dtype=np.int32)
             fresh = (np.asarray(d["context_lens"]) == np.asarray(q_lens)).astype(np.int32)
             ctx.state_slots, ctx.seq_fresh = self._to_dev(slots), self._to_dev(fresh)
             ctx.conv_states, ctx.rec_states = self.cache.conv_states, self.cache.rec_states
+            ctx.comp_caches, ctx.comp_kv_states, ctx.comp_score_states = self.cache.comp, self.cache.comp_kv_state, self.cache.comp_score_state
+            ctx.extras["state_slots_host"] = slots.tolist()
+            ctx.extras["fresh_host"] = fresh.tolist()
         return ctx
 
     def _dummy_context(self, is_prefill: bool) -> ForwardContext:
@@ -358,10 +361,13 @@ class ModelRunner:
         if self.cache.hisparse is not None:
             ctx.hisparse = self.cache.hisparse
             ctx.hs_slots = torch.tensor([self.cache.hisparse.scratch_slot], dtype=torch.int32, device=dev)
-        if self.plan.gdn:
+        if self.plan.needs_state_slots:
             ctx.state_slots = torch.tensor([self.cache.scratch_slot], dtype=torch.int32, device=dev)
             ctx.seq_fresh = torch.ones(1, dtype=torch.int32, device=dev)
             ctx.conv_states, ctx.rec_states = self.cache.conv_states, self.cache.rec_states
+            ctx.comp_caches, ctx.comp_kv_states, ctx.comp_score_states = self.cache.comp, self.cache.comp_kv_state, self.cache.comp_score_state
+            ctx.extras["state_slots_host"] = [self.cache.scratch_slot]
+            ctx.extras["fresh_host"] = [1]
         return ctx
 
     # ---- execution -----------------------------------------------------------------------------

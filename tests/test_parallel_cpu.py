@@ -60,6 +60,19 @@ def test_dp2_ep2_hybrid_delta_net_moe_matches_single_rank():
     assert got == want
 
 
+def test_dp2_ep2_deepseek_v4_matches_single_rank():
+    """DeepSeek-V4 under attention-DP + EP: every rank keeps its own window / pooled-row pages and compressor carries; hash-routed
+    and score-routed layers both dispatch over the EP group; an idle rank's dummy batch uses the spare state slot."""
+    from nanoengine_b200.models.config import tiny_deepseek_v4
+    base = dict(model="tiny-dsv4", model_config=tiny_deepseek_v4(head_dim=80), dummy_weight=True, dtype="float32", device="cpu",
+                kvcache_block_size=16, max_num_seqs=8, num_kvcache_blocks=64)
+    prompts = _prompts(3, 40, 5, 512)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = _run(Config(**base), prompts, sp)
+    got = _run(Config(**base, attention_dp=2, ffn_ep=2), prompts, sp)
+    assert got == want
+
+
 def _qwen_cfg():
     return ModelConfig(architecture="Qwen3MoeForCausalLM", vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=8,
                        num_key_value_heads=2, head_dim=16, rope_theta=1e6, max_position_embeddings=1024, intermediate_size=256,
