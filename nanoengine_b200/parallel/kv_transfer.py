@@ -107,8 +107,8 @@ def open_tensor(h) -> torch.Tensor:
 
 
 def check_families(mine: List[dict], theirs: List[dict]) -> None:
-    a = [(f["name"], f["planes"], f["page_bytes"]) for f in mine]
-    b = [(f["name"], f["planes"], f["page_bytes"]) for f in theirs]
+    a = [(f["name"], f["planes"], f["page_bytes"], f.get("by", "page")) for f in mine]
+    b = [(f["name"], f["planes"], f["page_bytes"], f.get("by", "page")) for f in theirs]
     if a != b:
         raise ValueError(f"PD cache layouts differ: prefill {a} vs decode {b}")
 
@@ -119,7 +119,8 @@ class LocalTransport:
     def __init__(self, src_runners, dst_runners):
         self.src, self.dst = src_runners, dst_runners
 
-    def copy(self, src_dp: int, dst_dp: int, src_blocks: List[int], dst_blocks: List[int], src_slot: int, dst_slot: int) -> int:
+    def copy(self, src_dp: int, dst_dp: int, src_blocks: List[int], dst_blocks: List[int], src_slot: int, dst_slot: int,
+             src_state: int = -1, dst_state: int = -1) -> int:
         s, d = self.src[src_dp], self.dst[dst_dp]
         sc, dc = s.cache, d.cache
         si = torch.as_tensor(src_blocks, dtype=torch.long, device=sc.kv.device)
@@ -134,13 +135,25 @@ class LocalTransport:
             rows = sc.indexer.index_select(1, si.to(sc.indexer.device))
             dc.indexer.index_copy_(1, di.to(dc.indexer.device), rows.to(dc.indexer.device))
             n += rows.numel()
+        for t, u in zip(sc.comp or [], dc.comp or []):                    # pooled-row pages (DeepSeek-V4)
+            if t is not None:
+                u.index_copy_(0, di, t.index_select(0, si).to(u.device))
+                n += len(src_blocks) * t[0].numel() * t.element_size()
+        sfam, dfam = sc.slot_families(), dc.slot_families()
+        if sfam:
+            # per-sequence state: recurrent state and convolution window, compressor carries
+            if not (0 <= src_state < sc.plan.state_slots and 0 <= dst_state < dc.plan.state_slots):
+                raise ValueError("kv transfer: a family with per-sequence state needs the state slots of both sides")
+            for f, g in zip(sfam, dfam):
+                g["tensor"].select(g["slot_dim"], dst_state).copy_(f["tensor"].select(f["slot_dim"], src_state))
+                n += f["planes"] * f["slot_bytes"]
         if s.mtp_runner is not None and d.mtp_runner is not None and src_slot >= 0 and dst_slot >= 0:
             d.mtp_runner.restore_handoff(dst_slot, s.mtp_runner.publish_handoff(src_slot))
         return n
 
     # ticket interface used by KVMigrator: a local copy is complete when it returns
-    def submit(self, src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot):
-        return ("done", self.copy(src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot))
+    def submit(self, src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot, src_state=-1, dst_state=-1):
+        return ("done", self.copy(src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot, src_state, dst_state))
 
     def finish(self, tickets) -> List[bool]:
         return [True] * len(tickets)
@@ -161,14 +174,15 @@ class PeerPushTransport:
         self._next_flag: Dict[int, int] = {}
         self._pending: List[dict] = []
 
-    def submit(self, src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot):
+    def submit(self, src_dp, dst_dp, src_blocks, dst_blocks, src_slot, dst_slot, src_state=-1, dst_state=-1):
         if not (0 <= src_dp < PD_MAX_SOURCES):
             raise ValueError(f"prefill rank {src_dp} outside the flag table")
         self.epoch += 1
         k = self._next_flag.get(src_dp, 0)
         self._next_flag[src_dp] = (k + 1) % PD_FLAGS_PER_SOURCE
         req = {"src_dp": int(src_dp), "dst_dp": int(dst_dp), "src_blocks": list(map(int, src_blocks)), "dst_blocks": list(map(int, dst_blocks)),
-               "src_slot": int(src_slot), "dst_slot": int(dst_slot), "flag": src_dp * PD_FLAGS_PER_SOURCE + k, "epoch": self.epoch}
+               "src_slot": int(src_slot), "dst_slot": int(dst_slot), "src_state": int(src_state), "dst_state": int(dst_state),
+               "flag": src_dp * PD_FLAGS_PER_SOURCE + k, "epoch": self.epoch}
         self._pending.append(req)
         return req
 
@@ -228,7 +242,9 @@ class KVMigrator:
                     tr, remote_blocks = self._route(eids[i] if i < len(eids) else "")
                     validate_blocks(src, remote_blocks, "remote")
                     validate_blocks(dst, self.local_blocks, "local")
-                    t = tr.submit(m.remote_dp_idx[i], m.dp_idx, src, dst, m.remote_handoff_slots[i], m.local_handoff_slots[i])
+                    rs, ls = list(m.remote_state_slots), list(m.local_state_slots)
+                    t = tr.submit(m.remote_dp_idx[i], m.dp_idx, src, dst, m.remote_handoff_slots[i], m.local_handoff_slots[i],
+                                  rs[i] if i < len(rs) else -1, ls[i] if i < len(ls) else -1)
                     b = batches.setdefault(id(tr), (tr, [], []))
                     b[1].append(sid); b[2].append(t)
                 except Exception:

@@ -256,18 +256,25 @@ class KVCache:
 
     def slot_families(self) -> List[dict]:
         """Cache families indexed by a per-sequence state slot instead of a page id (gated delta-net state and convolution
-        window): same description, with `slot_bytes` in place of `page_bytes`."""
+        window, compressor carries): same description, with `slot_bytes` in place of `page_bytes` and `slot_dim`, the tensor dimension
+        the slot indexes."""
         out = []
         if self.plan.gdn:
             for name, t in (("gdn_state", self.rec), ("gdn_conv", self.conv)):
                 planes = t.shape[0]
                 per_plane = t.numel() * t.element_size() // planes
-                out.append({"name": name, "tensor": t, "planes": planes, "plane_stride": per_plane, "slot_bytes": per_plane // t.shape[1]})
+                out.append({"name": name, "tensor": t, "planes": planes, "plane_stride": per_plane, "slot_bytes": per_plane // t.shape[1], "slot_dim": 1})
         for l, t in enumerate(self.comp_kv_state or []):
             if t is not None:
                 for name, u in ((f"dsv4_carry_kv_{l}", t), (f"dsv4_carry_score_{l}", self.comp_score_state[l])):
-                    out.append({"name": name, "tensor": u, "planes": 1, "plane_stride": u.numel() * 4, "slot_bytes": u.numel() * 4 // u.shape[0]})
+                    out.append({"name": name, "tensor": u, "planes": 1, "plane_stride": u.numel() * 4, "slot_bytes": u.numel() * 4 // u.shape[0], "slot_dim": 0})
         return out
+
+    def transfer_families(self) -> List[dict]:
+        """Everything a sequence owns, for a PD transfer: the per-slot families first (`by` = "slot", `page_bytes` = bytes per
+        slot), then the per-page ones (`by` = "page")."""
+        slots = [dict(f, by="slot", page_bytes=f["slot_bytes"]) for f in self.slot_families()]
+        return slots + [dict(f, by="page") for f in self.page_families()]
 
     def allocate_host(self, num_host_blocks: int):
         """Pinned host tier used by preemption swap: one host array per page family (KV and, for DSA models, the indexer keys),

@@ -492,10 +492,10 @@ class ModelRunner:
         if getattr(self, "pd_flags", None) is None:
             self.pd_flags = torch.zeros(PD_MAX_SOURCES * PD_FLAGS_PER_SOURCE, dtype=torch.int32, device=self.device)
         fams = []
-        for f in self.cache.page_families():
+        for f in self.cache.transfer_families():
             t = f["tensor"]
             flat = (t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t).reshape(-1)
-            fams.append({"name": f["name"], "planes": f["planes"], "plane_stride": f["plane_stride"], "page_bytes": f["page_bytes"],
+            fams.append({"name": f["name"], "planes": f["planes"], "plane_stride": f["plane_stride"], "page_bytes": f["page_bytes"], "by": f["by"],
                          "tensor": export_tensor(flat, direct)})
         return {"dp": self.dist.attn_dp_rank, "tp": self.dist.attn_tp_rank, "num_blocks": self.cache.num_blocks, "families": fams,
                 "flags": export_tensor(self.pd_flags, direct),
@@ -505,7 +505,7 @@ class ModelRunner:
         """Prefill side: map the pools of the decode engine `key` (those of this worker's TP rank) and check that every cache
         family has the layout of the local one.  Returns how many pools are mapped."""
         from ..parallel.kv_transfer import check_families, open_tensor
-        mine = self.cache.page_families()
+        mine = self.cache.transfer_families()
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)       # peer mappings are opened with the writing device current
         peers = getattr(self, "_pd_peers", None)
@@ -542,17 +542,25 @@ class ModelRunner:
                 raise ValueError("kv push: page ids outside the pools")        # never hand a bad index to the kernel
             if peer["handoff"] is not None and self.mtp_runner is not None and r["src_slot"] >= 0 and r["dst_slot"] >= 0:
                 peer["handoff"][r["dst_slot"]].copy_(self.mtp_runner.handoff[r["src_slot"]])
-            fams = self.cache.page_families()
+            # per-sequence state (recurrent state, compressor carries) moves by state slot, everything else by page; the
+            # per-slot families come first, so the launch that raises the flag is still the last per-page one
+            fams = self.cache.transfer_families()
+            ss, ds = int(r.get("src_state", -1)), int(r.get("dst_state", -1))
+            if any(f["by"] == "slot" for f in fams):
+                n_slots = self.plan.state_slots
+                if not (0 <= ss < n_slots and 0 <= ds < n_slots):
+                    raise ValueError("kv push: a family with per-sequence state needs the state slots of both sides")
             total = 0
             if self.device.type != "cuda":
                 for f, pf in zip(fams, peer["families"]):
                     src = (f["tensor"].view(torch.uint8) if f["tensor"].dtype == torch.float8_e4m3fn else f["tensor"]).reshape(-1).view(torch.uint8)
-                    dst = pf["tensor"].view(torch.uint8)
+                    dst = pf["tensor"].view(torch.uint8) if pf["tensor"].dtype == torch.float8_e4m3fn else pf["tensor"].reshape(-1).view(torch.uint8)
+                    ids = ([ss], [ds]) if f["by"] == "slot" else (sb, db)
                     for pl in range(f["planes"]):
-                        for s_, d_ in zip(sb, db):
+                        for s_, d_ in zip(*ids):
                             so, do = pl * f["plane_stride"] + s_ * f["page_bytes"], pl * pf["plane_stride"] + d_ * pf["page_bytes"]
                             dst[do:do + f["page_bytes"]] = src[so:so + f["page_bytes"]]
-                    total += f["planes"] * len(sb) * f["page_bytes"]
+                    total += f["planes"] * len(ids[0]) * f["page_bytes"]
                 peer["flags"][r["flag"]] = r["epoch"]
                 sizes.append(total)
                 continue
@@ -560,14 +568,17 @@ class ModelRunner:
             dev = self.device
             sbt = torch.tensor(sb, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
             dbt = torch.tensor(db, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            sst = torch.tensor([max(ss, 0)], dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            dst_ = torch.tensor([max(ds, 0)], dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
             fi = torch.tensor([r["flag"]], dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
             for i, (f, pf) in enumerate(zip(fams, peer["families"])):
                 last = i == len(fams) - 1
+                src_ids, dst_ids, n_ids = (sst, dst_, 1) if f["by"] == "slot" else (sbt, dbt, len(sb))
                 k._ck(k.lib().ne_kv_push(_c.c_void_p(f["tensor"].data_ptr()), _c.c_void_p(pf["tensor"].data_ptr()),
                                          _c.c_longlong(f["plane_stride"]), _c.c_longlong(pf["plane_stride"]), _c.c_int(f["page_bytes"]),
-                                         k._p(sbt), k._p(dbt), _c.c_int(len(sb)), _c.c_int(f["planes"]), _c.c_void_p(peer["flags"].data_ptr()),
+                                         k._p(src_ids), k._p(dst_ids), _c.c_int(n_ids), _c.c_int(f["planes"]), _c.c_void_p(peer["flags"].data_ptr()),
                                          k._p(fi), _c.c_int(1 if last else 0), _c.c_int(r["epoch"]), k._p(self._pd_counter), k._st()), "ne_kv_push")
-                total += f["planes"] * len(sb) * f["page_bytes"]
+                total += f["planes"] * n_ids * f["page_bytes"]
             if not sb:                       # nothing to move (a prompt that fits no page yet): the flag still has to come
                 peer["flags"][r["flag"]] = r["epoch"]
             sizes.append(total)

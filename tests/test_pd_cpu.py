@@ -200,3 +200,37 @@ def test_pd_packets_between_engine_processes_round_trip():
         cli.call(C.ACT_PD_PUSH, {"key": "d0", "reqs": [{"src_dp": 0}]})
     th.join(timeout=5)
     srv.close(0)
+
+
+def _state_family_configs():
+    from nanoengine_b200.models.config import tiny_deepseek_v4, tiny_glm5_next, tiny_qwen3_5
+    return {"qwen3.5": (tiny_qwen3_5(moe=True), 512), "glm5-next": (tiny_glm5_next(), 512), "deepseek-v4": (tiny_deepseek_v4(head_dim=80), 512)}
+
+
+@pytest.mark.parametrize("family", ["qwen3.5", "glm5-next", "deepseek-v4"])
+@pytest.mark.parametrize("transport", ["local", "push"])
+def test_families_with_per_sequence_state_migrate_their_state(family, transport):
+    """A sequence of a family with per-sequence state (delta-rule state and convolution window; compressor carries and pooled-row
+    pages) decodes on the other engine exactly as on a hybrid engine: the state slot of the prefill side travels with the pages
+    into the slot the decode scheduler assigned, which differs from the source slot here."""
+    mc, vocab = _state_family_configs()[family]
+    kw = dict(model="tiny", model_config=mc, dummy_weight=True)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in (30, 17, 45)]
+    sp = SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True)
+    want = {o["seq_id"]: o["token_ids"] for o in LLM(_cfg("hybrid", **kw)).generate(prompts, sp)}
+    prefill, decode = LLM(_cfg("prefill", engine_id="p0", **kw)), LLM(_cfg("decode", engine_id="d0", **kw))
+    if transport == "local":
+        tr = LocalTransport([prefill.engine.executor.runner], [decode.engine.executor.runner])
+        decode.engine.migrator = KVMigrator(tr, decode.engine.engine_info(), prefill.engine.engine_info())
+    else:
+        from nanoengine_b200.parallel.kv_transfer import connect_inproc
+        connect_inproc(prefill.engine, decode.engine)
+    firsts = {}
+    blobs = prefill.generate(prompts, sp, return_serialized=True)
+    for b in reversed(blobs):                      # admitted in the other order: source and destination slots differ
+        sid, first = RequestMigrate.from_bytes(b).metadata
+        firsts[sid] = first
+        decode.add_request_payload(b)
+    outs = {o["seq_id"]: [firsts[o["seq_id"]]] + o["token_ids"] for o in decode.generate()}
+    assert outs == want
