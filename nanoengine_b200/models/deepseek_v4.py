@@ -16,8 +16,9 @@ How it runs here.  The linear layers, norms, hyper-connection mixes, router and 
 compressor, the window / pooled-row gather and the sink softmax are stated in PyTorch ops (`ops.reference.dsv4_*`,
 `sink_attention`) on either device: decode is one batched pass without host reads, prefill walks the sequences of the step in
 query tiles.  The engine therefore runs this family eagerly, with attention_tp = pp = 1 and without speculative decoding.
-Chunked prefill and preemption work (the compressor carries its unfinished block per sequence slot); prefix reuse is off, as for
-every family with per-sequence state.
+Chunked prefill, preemption and PD migration work (the compressor carries its unfinished block per sequence slot); prefix reuse is
+off, as for every family with per-sequence state.  With kv_cache_dtype = "fp8" the raw and the pooled rows are stored packed
+(e4m3 values with one power-of-two scale byte per 64, bf16 rotated dims: 584 bytes per 512-wide row), otherwise as plain values.
 """
 from __future__ import annotations
 
@@ -49,6 +50,16 @@ def rotate_tail(x: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor, r
     a, b = t[..., 0::2], t[..., 1::2]
     x[..., -rd:] = torch.stack([a * cos - b * sin, b * cos + a * sin], -1).flatten(-2).to(x.dtype)
     return x
+
+
+def cache_store(cache: torch.Tensor, page: torch.Tensor, off: torch.Tensor, rows: torch.Tensor, rd: int) -> None:
+    """Write rows [N, D] at (page, off) of a cache [blocks, rows_per_page, D] - or [blocks, rows_per_page, row_bytes] uint8, packed."""
+    cache[page, off] = ref.dsv4_pack_rows(rows, rd) if cache.dtype == torch.uint8 else rows.to(cache.dtype)
+
+
+def cache_load(cache: torch.Tensor, page: torch.Tensor, off: torch.Tensor, d: int, rd: int, dtype) -> torch.Tensor:
+    rows = cache[page, off]
+    return ref.dsv4_unpack_rows(rows, d, rd, dtype) if cache.dtype == torch.uint8 else rows
 
 
 class Compressor(nn.Module):
@@ -85,7 +96,7 @@ class Compressor(nn.Module):
             start = (positions.long() + 1 - r).clamp_min(0)
             rows = self._finish(pooled, start, rope_cache, x.dtype)
             page = torch.where(done, bt.gather(1, (start // bs).unsqueeze(1)).squeeze(1), torch.full_like(start, cache.shape[0] - 1))
-            cache[page, torch.where(done, (start % bs) // r, torch.zeros_like(start)).clamp_max(epp - 1)] = rows
+            cache_store(cache, page, torch.where(done, (start % bs) // r, torch.zeros_like(start)).clamp_max(epp - 1), rows, self.rd)
             return
         cu, cl = ctx.cu_seqlens_q_host, ctx.context_lens_host
         slots_h, fresh_h = ctx.extras["state_slots_host"], ctx.extras["fresh_host"]
@@ -98,7 +109,7 @@ class Compressor(nn.Module):
             pooled = ref.dsv4_compress_extend(kv[qs:qe], score[qs:qe], ks, ss, pos0, r, d)
             if pooled.shape[0]:
                 start = (pos0 - pos0 % r) + r * torch.arange(pooled.shape[0], device=x.device)
-                cache[bt[i][start // bs], (start % bs) // r] = self._finish(pooled, start, rope_cache, x.dtype)
+                cache_store(cache, bt[i][start // bs], (start % bs) // r, self._finish(pooled, start, rope_cache, x.dtype), self.rd)
 
 
 class V4Attention(nn.Module):
@@ -129,7 +140,7 @@ class V4Attention(nn.Module):
         widx = pos.unsqueeze(1) - (W - 1) + torch.arange(W, device=q.device)
         wmask = widx >= 0
         widx = widx.clamp_min(0)
-        kv = cache[bt.gather(1, widx // bs), widx % bs]                                   # [B, W, D]
+        kv = cache_load(cache, bt.gather(1, widx // bs), widx % bs, self.D, self.rd, q.dtype)      # [B, W, D]
         mask = wmask
         if r:
             comp = ctx.comp_caches[self.layer_idx]
@@ -138,7 +149,7 @@ class V4Attention(nn.Module):
                 b = torch.arange(n, device=q.device).unsqueeze(0).expand(q.shape[0], n)
                 cmask = b < ((pos + 1) // r).unsqueeze(1)
                 tok = torch.where(cmask, b * r, torch.zeros_like(b))
-                kv = torch.cat([kv, comp[bt.gather(1, tok // bs), (tok % bs) // r]], 1)
+                kv = torch.cat([kv, cache_load(comp, bt.gather(1, tok // bs), (tok % bs) // r, self.D, self.rd, q.dtype)], 1)
                 mask = torch.cat([mask, cmask], 1)
         return ref.sink_attention(q, kv, mask, self.attn_sink, self.scale)
 
@@ -154,12 +165,12 @@ class V4Attention(nn.Module):
             comp = None
             if r and n_ctx // r:
                 tok = torch.arange(n_ctx // r, device=q.device) * r
-                comp = ctx.comp_caches[self.layer_idx][bt[tok // bs], (tok % bs) // r]
+                comp = cache_load(ctx.comp_caches[self.layer_idx], bt[tok // bs], (tok % bs) // r, self.D, self.rd, q.dtype)
             for t0 in range(0, qe - qs, QUERY_TILE):
                 t1 = min(qe - qs, t0 + QUERY_TILE)
                 qpos = pos0 + torch.arange(t0, t1, device=q.device)
                 kpos = torch.arange(max(0, pos0 + t0 - W + 1), pos0 + t1, device=q.device)
-                kv = cache[bt[kpos // bs], kpos % bs]
+                kv = cache_load(cache, bt[kpos // bs], kpos % bs, self.D, self.rd, q.dtype)
                 mask = (kpos.unsqueeze(0) <= qpos.unsqueeze(1)) & (kpos.unsqueeze(0) > qpos.unsqueeze(1) - W)
                 if comp is not None:
                     kv = torch.cat([kv, comp], 0)
@@ -177,7 +188,8 @@ class V4Attention(nn.Module):
         q = (qf * torch.rsqrt(qf.square().mean(-1, keepdim=True) + self.eps)).to(q.dtype)
         rotate_tail(q, positions, rope_cache, rd)
         cache = ctx.kv_caches[self.layer_idx]
-        cache.view(-1, D)[ctx.slot_mapping.long()] = kv.to(cache.dtype)
+        slot, bs = ctx.slot_mapping.long(), cache.shape[1]
+        cache_store(cache, slot // bs, slot % bs, kv, rd)
         if self.compressor is not None:
             self.compressor(ops.dense(x), positions, ctx, self.layer_idx, rope_cache)
         o = self._attend_decode(q, positions, ctx) if (not ctx.is_prefill and ctx.q_len_uniform == 1) else self._attend_varlen(q, ctx)

@@ -1296,3 +1296,38 @@ def dsv4_compress_decode(kv: torch.Tensor, score: torch.Tensor, kv_states: torch
     kv_states[slots, off:] = torch.where(dm, torch.zeros_like(ks[:, off:]), ks[:, off:])
     score_states[slots, off:] = torch.where(dm, torch.full_like(ss[:, off:], float("-inf")), ss[:, off:])
     return pooled, done
+
+
+def dsv4_row_bytes(d: int, rd: int) -> int:
+    """Bytes of one packed DeepSeek-V4 cache row: (d - rd) e4m3 values, rd bf16 values, one e8m0 scale byte per 64 e4m3 values
+    padded (by at least one byte) to a multiple of 8.  584 for d = 512, rd = 64.
+    Parity: reference models/deepseek_v4/deepseek_v4.py:592-612 (448 + 128 + 8)."""
+    tiles = (d - rd) // 64
+    return (d - rd) + 2 * rd + ((tiles + 8) // 8) * 8
+
+
+def dsv4_pack_rows(kv: torch.Tensor, rd: int) -> torch.Tensor:
+    """kv [N, d] -> uint8 [N, dsv4_row_bytes(d, rd)]: [e4m3 values | bf16 rotated dims | e8m0 scale bytes, zero padded].  The
+    scale of a 64-value tile is the power of two fp8_qdq_pow2 uses, so rows that went through it are stored without loss."""
+    N, d = kv.shape
+    nope = d - rd
+    tiles = nope // 64
+    v = kv[:, :nope].float().reshape(N, tiles, 64)
+    e = torch.ceil(torch.log2(v.abs().amax(-1).clamp(min=1e-4) / 448.0))                       # [N, tiles]
+    q = (v / torch.exp2(e).unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8).reshape(N, nope)
+    rope = kv[:, nope:].to(torch.bfloat16).contiguous().view(torch.uint8).reshape(N, 2 * rd)
+    sc = torch.zeros(N, dsv4_row_bytes(d, rd) - nope - 2 * rd, dtype=torch.uint8, device=kv.device)
+    sc[:, :tiles] = (e + 127).clamp(0, 254).to(torch.uint8)
+    return torch.cat([q, rope, sc], 1)
+
+
+def dsv4_unpack_rows(rows: torch.Tensor, d: int, rd: int, dtype=torch.float32) -> torch.Tensor:
+    """uint8 [..., row_bytes] -> [..., d] in `dtype`."""
+    nope = d - rd
+    tiles = nope // 64
+    lead = rows.shape[:-1]
+    r = rows.reshape(-1, rows.shape[-1])
+    q = r[:, :nope].contiguous().view(torch.float8_e4m3fn).float().reshape(-1, tiles, 64)
+    s = torch.exp2(r[:, nope + 2 * rd: nope + 2 * rd + tiles].float() - 127.0).unsqueeze(-1)
+    rope = r[:, nope: nope + 2 * rd].contiguous().view(torch.bfloat16).float()
+    return torch.cat([(q * s).reshape(-1, nope), rope], 1).to(dtype).reshape(*lead, d)

@@ -11,7 +11,8 @@ recurrent state    hybrid models with gated delta-net layers keep, per sequence 
 DeepSeek-V4        one shared key / value row per token and layer in the latent-cache layout [L, blocks, block_size, head_dim];
                    every compressing layer adds pooled rows [blocks, max(1, block_size / ratio), head_dim] addressed through the
                    same block table (pooled row b of a sequence sits in the page of token b * ratio) and, per sequence slot, the
-                   compressor's carry [c * ratio, c * head_dim] fp32 twice (values and scores; c = 2 for ratio 4).
+                   compressor's carry [c * ratio, c * head_dim] fp32 twice (values and scores; c = 2 for ratio 4).  With an fp8 cache a row
+                   is 584 packed bytes (448 e4m3 values, 64 bf16 rotated dims, 7 scale bytes + pad) instead of head_dim values.
 
 One extra block past the scheduler-visible range is reserved as the scratch page that dummy batches of idle
 DP ranks write into.
@@ -59,8 +60,10 @@ class CachePlan:
     layer_dims: Optional[List[int]] = None
     # hot / cold tier (DSA decode engines): the latent pages live in pinned host memory, `hot_rows` rows per sequence slot
     # and layer on the device
-    # DeepSeek-V4: compression ratio of every layer (0 = window only)
+    # DeepSeek-V4: compression ratio of every layer (0 = window only); the width of a key / value row (row_dim is its stored size:
+    # the same number, or the bytes of a packed row when the cache keeps fp8 values)
     dsv4_ratios: Optional[List[int]] = None
+    dsv4_head_dim: int = 0
     hisparse: bool = False
     hot_rows: int = 0
     hs_slots: int = 0
@@ -81,7 +84,7 @@ class CachePlan:
     def state_slot_bytes(self) -> int:
         """Bytes one sequence slot takes over all layers that keep per-sequence state."""
         if self.dsv4:
-            return sum(2 * 4 * (2 if r == 4 else 1) ** 2 * r * self.row_dim for r in self.dsv4_ratios if r)
+            return sum(2 * 4 * (2 if r == 4 else 1) ** 2 * r * self.dsv4_head_dim for r in self.dsv4_ratios if r)
         if not self.gdn:
             return 0
         e = 2 if self.kv_dtype in (torch.bfloat16, torch.float16, torch.float8_e4m3fn) else 4
@@ -145,9 +148,13 @@ def _make_cache_plan(mc: ModelConfig, kv_dtype_name: str, block_size: int, attn_
     if mc.is_dsv4:
         for r in mc.compress_ratios or []:
             assert r == 0 or block_size % r == 0 or r % block_size == 0, "a compression ratio must divide the page size or be a multiple of it"
-        # the rows are kept as the values an fp8 cache would return (quantise-dequantise at write), in a 16-bit container
-        return CachePlan(True, False, False, mc.num_hidden_layers, block_size, torch.bfloat16 if dt == torch.float8_e4m3fn else dt, mc.head_dim,
-                         state_slots=state_slots, dsv4_ratios=[mc.compress_ratio(i) for i in range(mc.num_hidden_layers)])
+        # every row passes an e4m3 round trip with one power-of-two scale per 64 values before it is stored; an fp8 cache keeps
+        # it packed (e4m3 values, bf16 rotated dims, scale bytes: 584 bytes for 512 dims), any other dtype keeps the values
+        packed = dt == torch.float8_e4m3fn
+        from ..ops.reference import dsv4_row_bytes
+        return CachePlan(True, False, False, mc.num_hidden_layers, block_size, torch.uint8 if packed else dt,
+                         dsv4_row_bytes(mc.head_dim, mc.qk_rope_head_dim) if packed else mc.head_dim, state_slots=state_slots,
+                         dsv4_ratios=[mc.compress_ratio(i) for i in range(mc.num_hidden_layers)], dsv4_head_dim=mc.head_dim)
     if mc.is_hybrid_gdn and mc.is_mla:
         # delta-attention layers between MLA layers (GLM5-next, Kimi-K3): latent pages for the full-attention layers (and the
         # MTP layers), one state slot per sequence for the linear ones
@@ -223,8 +230,8 @@ class KVCache:
                     continue
                 c = 2 if r == 4 else 1
                 self.comp.append(torch.zeros(nb, plan.comp_entries_per_page(r), plan.row_dim, dtype=plan.kv_dtype, device=device))
-                self.comp_kv_state.append(torch.zeros(ns, c * r, c * plan.row_dim, dtype=torch.float32, device=device))
-                self.comp_score_state.append(torch.full((ns, c * r, c * plan.row_dim), float("-inf"), dtype=torch.float32, device=device))
+                self.comp_kv_state.append(torch.zeros(ns, c * r, c * plan.dsv4_head_dim, dtype=torch.float32, device=device))
+                self.comp_score_state.append(torch.full((ns, c * r, c * plan.dsv4_head_dim), float("-inf"), dtype=torch.float32, device=device))
         self.rec_states = self.conv_states = None
         self.scratch_slot = plan.state_slots
         if plan.gdn:

@@ -95,6 +95,29 @@ def test_fp8_round_trip_uses_power_of_two_scales_per_64():
     assert torch.equal(y.view(4, 2, 64), (v / s).to(torch.float8_e4m3fn).float() * s)
 
 
+def test_packed_cache_rows_keep_quantised_rows_exactly():
+    torch.manual_seed(5)
+    d, rd = 192, 64
+    kv = (torch.randn(9, d) * torch.logspace(-3, 2, 9).view(9, 1)).to(torch.bfloat16)
+    kv[:, :-rd] = ref.fp8_qdq_pow2(kv[:, :-rd], 64)
+    rows = ref.dsv4_pack_rows(kv, rd)
+    assert rows.dtype == torch.uint8 and rows.shape == (9, 128 + 128 + 8) and (rows[:, -6:] == 0).all()
+    assert torch.equal(ref.dsv4_unpack_rows(rows, d, rd, torch.bfloat16), kv)
+    assert torch.equal(ref.dsv4_unpack_rows(rows.view(3, 3, -1), d, rd, torch.bfloat16), kv.view(3, 3, d))
+
+
+def test_model_with_packed_fp8_cache_equals_the_plain_cache():
+    """In bf16 the packed rows hold exactly what the plain cache holds, so the tokens are the same."""
+    mc = tiny_deepseek_v4(head_dim=80)
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (41, 12)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    plain = _llm(mc, dtype="bfloat16")
+    packed = _llm(mc, dtype="bfloat16", kv_cache_dtype="fp8")
+    assert packed.engine.executor.runner.cache.kv.dtype == torch.uint8 and packed.engine.executor.runner.cache.kv.shape[-1] == 64 + 32 + 8
+    assert [o["token_ids"] for o in packed.generate(prompts, sp)] == [o["token_ids"] for o in plain.generate(prompts, sp)]
+
+
 def test_sqrt_softplus_routing():
     torch.manual_seed(4)
     logits, bias = torch.randn(6, 16) * 3, torch.randn(16) * 0.1
@@ -116,10 +139,13 @@ def test_config_reads_the_release_spellings_and_the_cache_plan_counts_pooled_row
     assert mc.glu_act == ("clamp", 10.0) and mc.num_hash_layers == 1 and mc.routed_scaling_factor == 1.5 and mc.max_position_embeddings == 8192
     assert [mc.compress_ratio(i) for i in range(4)] == [0, 4, 128, 0] and mc.is_moe_layer(0)
     from nanoengine_b200.runtime.cache import KVCache, make_cache_plan
-    plan = make_cache_plan(mc, "fp8", 64, state_slots=4)
+    plan = make_cache_plan(mc, "bfloat16", 64, state_slots=4)
     assert plan.dsv4 and plan.mla and plan.needs_state_slots and plan.kv_dtype == torch.bfloat16 and plan.row_dim == 128
     # 3 layers x 64 raw rows + 16 rows pooled over 4 + 1 row pooled over 128, two bytes each
     assert plan.block_bytes == (3 * 64 + 16 + 1) * 128 * 2
+    packed = make_cache_plan(mc, "fp8", 64, state_slots=4)          # 64 e4m3 + 64 bf16 + 8 scale bytes per row
+    assert packed.kv_dtype == torch.uint8 and packed.row_dim == 200 and packed.block_bytes == (3 * 64 + 16 + 1) * 200
+    assert packed.state_slot_bytes == plan.state_slot_bytes and ref.dsv4_row_bytes(512, 64) == 584
     assert plan.state_slot_bytes == 2 * 4 * (4 * 4 * 128 + 128 * 128)
     from nanoengine_b200._native import _core as C
     assert plan.plan_bits() == C.PLAN_MLA | C.PLAN_GDN
