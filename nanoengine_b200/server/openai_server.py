@@ -23,6 +23,7 @@ from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from .._native import _core as C
 from .tokenizer import load_tokenizer
+from .text_stream import ReasoningStream, StopStream, cut_at_stop, model_aliases, parse_stop, prompt_opens_thinking, resolve_request_model, split_reasoning
 from .tool_parser import StreamingToolParser, parse as parse_tools
 
 
@@ -83,9 +84,21 @@ def anthropic_to_chat(body: Dict[str, Any]) -> Dict[str, Any]:
     return out
 
 
-def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", mode: str = "hybrid", default_max_tokens: int = 256):
+def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", mode: str = "hybrid", default_max_tokens: int = 256,
+               model_path: Optional[str] = None, reasoning: bool = True):
+    """`model_path`: the checkpoint path, accepted as a request's `model` next to `model_name` (a request that names another
+    model gets 404; one that names none is served).  `reasoning`: route `<think>` blocks of chat answers to
+    `reasoning_content`."""
     app = FastAPI(title="nanoengine_b200")
     t_start = time.time()
+    aliases = model_aliases(model_name, model_path or model_name)
+
+    def _unknown_model(body: Dict[str, Any]):
+        req_model = body.get("model")
+        if req_model and resolve_request_model(req_model, model_name, aliases) is None:
+            return JSONResponse({"error": {"message": f"Model '{req_model}' not found. Use one of: {sorted(aliases)}",
+                                           "type": "invalid_request_error", "code": "model_not_found"}}, status_code=404)
+        return None
 
     @app.on_event("startup")
     async def _startup():
@@ -152,12 +165,24 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
         sid = await client.submit(prompt_ids, sp, affinity_key(body))
         return sid, []
 
-    async def _collect(sid: int, pre: List[int]):
+    async def _collect(sid: int, pre: List[int], stops: Optional[List[str]] = None):
+        """All tokens of the request.  With stop strings the text is decoded as it arrives and the request is aborted at the
+        first one (status FINISHED, the text is cut by the caller)."""
         toks, lps, status = list(pre), [], C.RUNNING
+        dec, text = (tokenizer.incremental_decoder(), "") if stops else (None, "")
+        if dec is not None:
+            for t in pre:
+                text += dec.add(t)
         async for o in client.stream(sid):
             toks.extend(o.token_ids)
             lps.extend(o.logprobs)
             status = o.status
+            if dec is not None:
+                for t in o.token_ids:
+                    text += dec.add(t)
+                if cut_at_stop(text, stops)[1]:
+                    await client.abort(sid)
+                    return toks, lps, C.FINISHED
         return toks, lps, status
 
     def _finish_reason(status: int, n: int, sp_max: int, has_calls: bool) -> str:
@@ -180,6 +205,9 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
     async def _chat_or_completion(body: Dict[str, Any], chat: bool):
         rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
         obj = "chat.completion" if chat else "text_completion"
+        bad = _unknown_model(body)
+        if bad is not None:
+            return bad
         try:
             prompt_ids = _prompt_ids(body, chat)
         except Exception as e:
@@ -192,7 +220,10 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
             sid, pre = await _start(body, prompt_ids)
         except Exception as e:
             return JSONResponse({"error": {"message": str(e), "type": "server_error"}}, status_code=503)
-        tools = body.get("tools")
+        tools = body.get("tools") if body.get("tool_choice") != "none" else None
+        stops = parse_stop(body)
+        think = chat and reasoning
+        think_open = think and prompt_opens_thinking(tokenizer.decode(prompt_ids[-64:]))
         created = int(time.time())
 
         if kv.get("do_remote_decode") and mode == "prefill":
@@ -207,16 +238,21 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
 
         if not body.get("stream"):
             try:
-                toks, lps, status = await _collect(sid, pre)
+                toks, lps, status = await _collect(sid, pre, stops)
             except Exception as e:
                 return JSONResponse({"error": {"message": str(e), "type": "server_error"}}, status_code=503)
-            text = tokenizer.decode(toks)
+            text, stopped = cut_at_stop(tokenizer.decode(toks), stops)
+            thought = None
+            if think:
+                thought, text = split_reasoning(text, think_open)
             calls = []
             if chat and tools:
                 text, calls = parse_tools(text, tool_format, tools)
-            choice: Dict[str, Any] = {"index": 0, "finish_reason": _finish_reason(status, len(toks), sp.max_tokens, bool(calls))}
+            choice: Dict[str, Any] = {"index": 0, "finish_reason": "stop" if stopped and not calls else _finish_reason(status, len(toks), sp.max_tokens, bool(calls))}
             if chat:
                 msg: Dict[str, Any] = {"role": "assistant", "content": text or None if calls else text}
+                if thought is not None:
+                    msg["reasoning_content"] = thought
                 if calls:
                     msg["tool_calls"] = [c.to_openai(i) for i, c in enumerate(calls)]
                 choice["message"] = msg
@@ -232,6 +268,8 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
         async def gen():
             dec = tokenizer.incremental_decoder()
             tp = StreamingToolParser(tool_format, tools) if (chat and tools) else None
+            ss = StopStream(stops) if stops else None
+            rs = ReasoningStream(think_open) if think else None
             n, ncalls = 0, 0
             chunk_obj = "chat.completion.chunk" if chat else "text_completion"
 
@@ -246,9 +284,19 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
             if chat:
                 yield chunk({"role": "assistant", "content": ""})
 
-            def emit(piece: str):
+            def emit(piece: str, last: bool = False):
+                """decoded text -> stop strings -> reasoning / content -> tool calls -> chunks"""
                 nonlocal ncalls
                 outs = []
+                if ss is not None:
+                    piece = ss.feed(piece)[0] + (ss.flush() if last else "")
+                if rs is not None:
+                    thought, piece = rs.feed(piece)
+                    if last:
+                        t2, p2 = rs.flush()
+                        thought, piece = thought + t2, piece + p2
+                    if thought:
+                        outs.append(chunk({"reasoning_content": thought}))
                 if tp is not None:
                     piece, calls = tp.feed(piece)
                     for c in calls:
@@ -265,10 +313,17 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
                         yield s
                 async for o in client.stream(sid):
                     for t in o.token_ids:
+                        if ss is not None and ss.hit:
+                            break
                         n += 1
                         for s in emit(dec.add(t)):
                             yield s
-                tail = dec.flush()
+                    if ss is not None and ss.hit:
+                        await client.abort(sid)
+                        break
+                for s in emit(dec.flush() or "", last=True):
+                    yield s
+                tail = ""
                 if tp is not None:
                     rest, calls = tp.flush()
                     tail = (tail or "") + rest if not calls else tail
@@ -277,7 +332,7 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
                         ncalls += 1
                 if tail:
                     yield chunk({"content": tail}) if chat else chunk(text=tail)
-                yield chunk(finish=_finish_reason(C.FINISHED, n, sp.max_tokens, ncalls > 0))
+                yield chunk(finish="stop" if (ss is not None and ss.hit and not ncalls) else _finish_reason(C.FINISHED, n, sp.max_tokens, ncalls > 0))
                 if include_usage:
                     yield "data: " + json.dumps({"id": rid, "object": chunk_obj, "created": created, "model": model_name, "choices": [],
                                                  "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": n, "total_tokens": len(prompt_ids) + n}}) + "\n\n"
@@ -306,6 +361,9 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
     @app.post("/v1/messages")
     async def messages(req: Request):
         raw = await _json(req)
+        bad = _unknown_model(raw)
+        if bad is not None:
+            return bad
         body = anthropic_to_chat(raw)
         mid = "msg_" + uuid.uuid4().hex[:24]
         prompt_ids = tokenizer.apply_chat_template(body["messages"], tools=body.get("tools"))
@@ -382,7 +440,8 @@ def run_server(config, host: Optional[str] = None, port: Optional[int] = None, t
     tok = load_tokenizer(config.model, config.model_config.vocab_size)
     import os
     name = getattr(config, "served_model_name", None) or os.path.basename(str(config.model).rstrip("/")) or str(config.model)
-    app = create_app(client, tok, model_name=name, tool_format=tool_format, mode=config.mode)
+    app = create_app(client, tok, model_name=name, tool_format=tool_format, mode=config.mode, model_path=str(config.model),
+                     reasoning=os.environ.get("NANOENGINE_REASONING", "1") != "0")
     ctrl = None
     if config.ctrl_address:
         from .ctrl import register_with_ctrl

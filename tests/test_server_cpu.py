@@ -18,6 +18,13 @@ def _cfg(**kw):
     return Config(**base)
 
 
+class LetterTokenizer(ByteTokenizer):
+    """Printable bytes as themselves, every other id as a letter: a random-weight model then answers in visible text."""
+
+    def decode(self, ids):
+        return "".join(chr(i) if 32 <= i < 127 else chr(97 + i % 26) for i in ids)
+
+
 @pytest.fixture(scope="module")
 def served():
     from starlette.testclient import TestClient
@@ -26,7 +33,7 @@ def served():
     cfg = _cfg()
     proc, endpoint = spawn_backend(cfg)
     client = EngineClient(endpoint, proc)
-    app = create_app(client, ByteTokenizer(1024), "tiny", tool_format="hermes")
+    app = create_app(client, LetterTokenizer(1024), "tiny", tool_format="hermes")
     with TestClient(app) as tc:
         yield tc, proc
     client.destroy()
@@ -81,6 +88,55 @@ def test_profiler_endpoints_guard_the_trace_name(served):
     assert tc.post("/start_profiler", json={"trace_name": "ok"}).json() == {"started": False}   # no profiler_dir configured
 
 
+def test_unknown_model_is_404_and_names_are_case_insensitive(served):
+    tc, _ = served
+    body = {"prompt": "hello", "max_tokens": 2, "temperature": 0, "ignore_eos": True}
+    assert tc.post("/v1/completions", json={**body, "model": "TINY"}).status_code == 200
+    r = tc.post("/v1/completions", json={**body, "model": "someone-else"})
+    assert r.status_code == 404 and r.json()["error"]["code"] == "model_not_found"
+    assert tc.post("/v1/chat/completions", json={"model": "nope", "messages": [{"role": "user", "content": "x"}]}).status_code == 404
+    assert tc.post("/v1/messages", json={"model": "nope", "max_tokens": 2, "messages": [{"role": "user", "content": "x"}]}).status_code == 404
+
+
+def test_stop_strings_cut_the_answer_plain_and_streamed(served):
+    tc, _ = served
+    body = {"prompt": "stop strings", "max_tokens": 24, "temperature": 0, "ignore_eos": True}
+    full = tc.post("/v1/completions", json=body).json()["choices"][0]["text"]
+    assert len(full) >= 12
+    stop = full[8:11]
+    want = full[: full.find(stop)]
+    r = tc.post("/v1/completions", json={**body, "stop": [stop, "\x00never"]}).json()
+    assert r["choices"][0]["text"] == want and r["choices"][0]["finish_reason"] == "stop" and r["usage"]["completion_tokens"] < 24
+    text, finish = "", None
+    with tc.stream("POST", "/v1/completions", json={**body, "stop": stop, "stream": True}) as resp:
+        for l in resp.iter_lines():
+            if l.startswith("data: ") and l != "data: [DONE]":
+                for c in json.loads(l[6:]).get("choices", []):
+                    text += c.get("text") or ""
+                    finish = c.get("finish_reason") or finish
+    assert text == want and finish == "stop"
+    # the engine is free again: the aborted requests left nothing behind
+    assert tc.post("/v1/completions", json=body).json()["choices"][0]["text"] == full
+
+
+def test_reasoning_goes_to_its_own_field_when_the_prompt_opens_the_block(served):
+    tc, _ = served
+    body = {"messages": [{"role": "user", "content": "solve <think>"}], "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+    msg = tc.post("/v1/chat/completions", json=body).json()["choices"][0]["message"]
+    assert msg["content"] == "" and len(msg["reasoning_content"]) > 0
+    thought = ""
+    with tc.stream("POST", "/v1/chat/completions", json={**body, "stream": True}) as resp:
+        for l in resp.iter_lines():
+            if l.startswith("data: ") and l != "data: [DONE]":
+                for c in json.loads(l[6:]).get("choices", []):
+                    d = c.get("delta") or {}
+                    assert not d.get("content")
+                    thought += d.get("reasoning_content") or ""
+    assert thought == msg["reasoning_content"]
+    plain = tc.post("/v1/chat/completions", json={**body, "messages": [{"role": "user", "content": "solve"}]}).json()["choices"][0]["message"]
+    assert "reasoning_content" not in plain and len(plain["content"]) > 0
+
+
 def test_backend_death_is_noticed(served):
     tc, proc = served
     proc.terminate()
@@ -129,3 +185,40 @@ def test_streaming_parser_holds_back_partial_tags():
     out.append(o); calls.extend(c)
     assert "".join(out) == "Hello  bye <b>" and len(calls) == 1 and calls[0].arguments == {"a": 1}
     assert out[0] == "Hello "     # the possible tag prefix was held back
+
+
+# ---- model names, stop strings, reasoning blocks ------------------------------------------------------------------------------
+def test_text_filters():
+    from nanoengine_b200.server.text_stream import (ReasoningStream, StopStream, cut_at_stop, model_aliases, parse_stop,
+                                                     prompt_opens_thinking, resolve_request_model, split_reasoning)
+    assert parse_stop({"stop": "x"}) == ["x"] and parse_stop({"stop": ["a", "", 3, "b"]}) == ["a", "b"] and parse_stop({}) == [] and parse_stop({"stop": 5}) == []
+    assert cut_at_stop("one two three", ["three", "two"]) == ("one ", True) and cut_at_stop("abc", ["x"]) == ("abc", False)
+    # streamed in any split, the stop filter gives the text before the first stop string and nothing of a half-seen one
+    text, stops = "alpha beta END gamma\n\ndelta", ["END", "\n\n"]
+    for cuts in ([3, 11, 12, 13, 20], list(range(1, len(text))), []):
+        s, out, hit = StopStream(stops), "", False
+        for a, b in zip([0] + cuts, cuts + [len(text)]):
+            piece, hit = s.feed(text[a:b])
+            out += piece
+            if hit:
+                break
+        assert out + s.flush() == "alpha beta " and hit
+    s = StopStream(["END"])
+    assert s.feed("the E")[0] == "the " and s.flush() == "E"               # a half-seen stop string is text after all
+    assert prompt_opens_thinking("...<|assistant|>\n<think>\n") and not prompt_opens_thinking("<think>\n\n</think>\n\n") and not prompt_opens_thinking("hi")
+    assert split_reasoning("<think>why</think>\n\nanswer", False) == ("why", "answer")
+    assert split_reasoning("why</think>answer", True) == ("why", "answer") and split_reasoning("<think>why</think>answer", True) == ("why", "answer")
+    assert split_reasoning("no block", False) == (None, "no block") and split_reasoning("never closed", True) == ("never closed", "")
+    full = "  <think>step 1\nstep 2</think>\nfinal <b>text</b>"
+    for n in (1, 2, 3, 7):
+        r, th, co = ReasoningStream(False), "", ""
+        for i in range(0, len(full), n):
+            a, b = r.feed(full[i: i + n])
+            th, co = th + a, co + b
+        a, b = r.flush()
+        assert (th + a, co + b) == ("step 1\nstep 2", "final <b>text</b>")
+    al = model_aliases("GLM-5.2-NVFP4", "/models/GLM-5.2-NVFP4/")
+    assert {"GLM-5.2-NVFP4", "/models/GLM-5.2-NVFP4"} <= al
+    assert resolve_request_model("glm-5.2-nvfp4", "GLM-5.2-NVFP4", al) == "GLM-5.2-NVFP4"
+    assert resolve_request_model("/models/glm-5.2-nvfp4", "GLM-5.2-NVFP4", al) == "GLM-5.2-NVFP4"
+    assert resolve_request_model("other", "GLM-5.2-NVFP4", al) is None and resolve_request_model(None, "x", al) is None
