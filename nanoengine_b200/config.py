@@ -106,6 +106,9 @@ class Config:
         mc = self.model_config
         if self.mode not in ("hybrid", "prefill", "decode"):
             raise ValueError("mode must be hybrid, prefill or decode")
+        # the reference's spellings (RoundRobin, LeastBatch, LeastCache, Affinity) are taken too
+        import re as _re
+        self.routing_strategy = _re.sub(r"(?<=[a-z])(?=[A-Z])", "_", str(self.routing_strategy)).lower().replace("-", "_")
         if self.routing_strategy not in ("round_robin", "least_batch", "least_cache", "affinity"):
             raise ValueError(f"unknown routing_strategy {self.routing_strategy}")
         if self.fp8_scale_format not in ("auto", "fp32", "ue8m0"):

@@ -130,3 +130,12 @@ def test_nvtx_ranges_are_free_when_off_and_harmless_without_a_gpu():
     with nvtx.range("y"):
         pass
     nvtx.enable(False)
+
+
+def test_routing_strategy_accepts_both_spellings():
+    from nanoengine_b200 import Config
+    for given, want in (("LeastBatch", "least_batch"), ("RoundRobin", "round_robin"), ("least_cache", "least_cache"), ("Affinity", "affinity")):
+        assert Config(model="tiny-deepseek-v3", device="cpu", routing_strategy=given).routing_strategy == want
+    import pytest
+    with pytest.raises(ValueError):
+        Config(model="tiny-deepseek-v3", device="cpu", routing_strategy="Random")
