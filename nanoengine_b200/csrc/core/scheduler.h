@@ -458,7 +458,7 @@ class Scheduler {
   }
 
   bool acquire_slots(Sequence& s, int d) {
-    bool need_state = (cfg_.cache_plan & PLAN_GDN) && cfg_.num_state_slots > 0;
+    bool need_state = cfg_.needs_state_slots();
     bool need_handoff = spec() > 0 && cfg_.num_handoff_slots > 0;
     bool need_hs = (cfg_.cache_plan & PLAN_HISPARSE) && cfg_.num_hisparse_slots > 0;
     if (need_state && s.state_slot < 0 && state_slots_[d].num_free() == 0) return false;

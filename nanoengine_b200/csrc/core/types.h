@@ -31,8 +31,8 @@ enum CachePlanBits : uint32_t {
   PLAN_GQA = 1u << 0,
   PLAN_MLA = 1u << 1,
   PLAN_GDN = 1u << 2,      // recurrent-state layers: needs a state slot, disables prefix caching
-  PLAN_HCA = 1u << 3,
-  PLAN_CSA = 1u << 4,
+  PLAN_HCA = 1u << 3,      // DeepSeek-V4 shared-row pages (window rows)
+  PLAN_CSA = 1u << 4,      // DeepSeek-V4 pooled-row pages + compressor carry: needs a state slot, disables prefix caching
   PLAN_INDEXER = 1u << 5,  // DSA lightning-indexer key pages share the main page table
   PLAN_HISPARSE = 1u << 6, // hot/cold tiering: needs a hot-buffer slot per sequence
 };
@@ -68,9 +68,11 @@ struct SchedulerConfig {
   std::string engine_id;
 
   bool prefix_cache_effective() const {
-    // recurrent-state plans cannot reuse KV prefixes (state is not per block)
-    return enable_prefix_caching && !(cache_plan & PLAN_GDN);
+    // plans with per-sequence state cannot reuse KV prefixes (state is not per block)
+    // (PLAN_GDN: recurrent state; PLAN_CSA: the compressor's unfinished block)
+    return enable_prefix_caching && !(cache_plan & (PLAN_GDN | PLAN_CSA));
   }
+  bool needs_state_slots() const { return (cache_plan & (PLAN_GDN | PLAN_CSA)) && num_state_slots > 0; }
 };
 
 struct Sequence {

@@ -42,7 +42,7 @@ def build_scheduler_config(config: Config, num_blocks: int, plan_bits: int) -> "
     sc.cache_plan = plan_bits
     sc.num_handoff_slots = config.max_num_seqs if config.num_speculative_tokens > 0 else 0
     sc.num_hisparse_slots = config.max_num_seqs if config.enable_hisparse else 0
-    sc.num_state_slots = config.max_num_seqs if (plan_bits & C.PLAN_GDN) else 0   # one recurrent-state slot per running sequence
+    sc.num_state_slots = config.max_num_seqs if (plan_bits & (C.PLAN_GDN | C.PLAN_CSA)) else 0   # one state slot per running sequence
     sc.eos_token_ids = config.model_config.eos_ids()
     sc.engine_id = config.engine_id
     return sc

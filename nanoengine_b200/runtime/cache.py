@@ -121,10 +121,12 @@ class CachePlan:
 
     def plan_bits(self) -> int:
         from .._native import _core as C
+        if self.dsv4:                    # shared-row pages + pooled-row pages with their per-sequence carry
+            return C.PLAN_HCA | C.PLAN_CSA
         bits = C.PLAN_MLA if self.mla else C.PLAN_GQA
         if self.indexer:
             bits |= C.PLAN_INDEXER
-        if self.needs_state_slots:
+        if self.gdn:
             bits |= C.PLAN_GDN          # one state slot per running sequence; no prefix reuse
         if self.hisparse:
             bits |= C.PLAN_HISPARSE

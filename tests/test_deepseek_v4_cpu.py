@@ -148,7 +148,7 @@ def test_config_reads_the_release_spellings_and_the_cache_plan_counts_pooled_row
     assert packed.state_slot_bytes == plan.state_slot_bytes and ref.dsv4_row_bytes(512, 64) == 584
     assert plan.state_slot_bytes == 2 * 4 * (4 * 4 * 128 + 128 * 128)
     from nanoengine_b200._native import _core as C
-    assert plan.plan_bits() == C.PLAN_MLA | C.PLAN_GDN
+    assert plan.plan_bits() == C.PLAN_HCA | C.PLAN_CSA
     kv = KVCache(plan, 5, "cpu")
     assert kv.comp[0] is None and kv.comp[1].shape == (6, 16, 128) and kv.comp[2].shape == (6, 1, 128)
     assert kv.comp_kv_state[1].shape == (5, 8, 256) and kv.comp_score_state[2].shape == (5, 128, 128) and kv.comp_score_state[2].isinf().all()
