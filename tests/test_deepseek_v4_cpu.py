@@ -277,3 +277,8 @@ def test_checkpoint_round_trip_and_preemption(tmp_path):
     tight = _llm(mc, num_kvcache_blocks=9)
     tight.engine.executor.runner.load_weights((n, t if t.dtype == torch.int32 else t.to(torch.bfloat16).float()) for n, t in random_hf_weights(mc, seed=3))
     assert [o["token_ids"] for o in tight.generate(prompts, sp)] == want
+    # the same pool with a host tier: preempted sequences swap their raw and pooled-row pages out and keep their state slot
+    swapping = _llm(mc, num_kvcache_blocks=9, num_host_kvcache_blocks=16)
+    swapping.engine.executor.runner.load_weights((n, t if t.dtype == torch.int32 else t.to(torch.bfloat16).float()) for n, t in random_hf_weights(mc, seed=3))
+    assert set(swapping.engine.executor.runner.cache.host_families) == {"mla_kv", "dsv4_pooled_1", "dsv4_pooled_2"}
+    assert [o["token_ids"] for o in swapping.generate(prompts, sp)] == want
