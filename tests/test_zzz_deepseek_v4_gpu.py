@@ -65,3 +65,20 @@ def test_deepseek_v4_logits_match_fp32_cpu_model(kv):
         assert _rel(lg, lc) < 1e-1, f"step {step}: {_rel(lg, lc)}"
         cur = [s + [t] for s, t in zip(cur, lc.argmax(-1).tolist())]
     assert sm100.kernel_status()[0] == 0
+
+
+def test_sqrt_softplus_routing_kernel():
+    """The routing kernel's third scoring mode against the PyTorch statement (scores sqrt(softplus(x)), bias only in the choice,
+    weights renormalised and scaled), including large logits where softplus(x) = x."""
+    from nanoengine_b200.ops import reference as ref
+    from nanoengine_b200.ops import sm100
+    sm100.lib()
+    torch.manual_seed(3)
+    logits = torch.randn(37, 256, device="cuda") * 4
+    logits[0, :8] = torch.tensor([25.0, 30.0, 41.0, 22.0, 60.0, 21.0, 35.0, 27.0], device="cuda")
+    bias = torch.randn(256, device="cuda") * 0.05
+    idx, w = sm100.moe_route(logits, bias, 6, 1, 1, True, 1.5, "sqrtsoftplus")
+    ridx, rw = ref.moe_route(logits.cpu(), bias.cpu(), 6, 1, 1, True, 1.5, "sqrtsoftplus")
+    order, rorder = idx.long().cpu().sort(-1), ridx.long().sort(-1)
+    assert torch.equal(order.values, rorder.values)
+    assert (w.cpu().gather(1, order.indices) - rw.gather(1, rorder.indices)).abs().max() < 1e-4
