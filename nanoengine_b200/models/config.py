@@ -451,13 +451,16 @@ def tiny_deepseek_v4(**over) -> ModelConfig:
     """CPU-sized DeepSeek-V4 shape: a window-only layer, a ratio-4 (overlapping) and a ratio-8 compressing layer, 2 hyper-connection
     streams, the first MoE layer hash-routed."""
     base = dict(architecture="DeepseekV4ForCausalLM", vocab_size=512, hidden_size=128, num_hidden_layers=3, num_attention_heads=4,
-                num_key_value_heads=1, head_dim=64, qk_rope_head_dim=16, q_lora_rank=48, o_lora_rank=32, o_groups=2, window_size=8,
+                num_key_value_heads=1, head_dim=80, qk_rope_head_dim=16, q_lora_rank=48, o_lora_rank=32, o_groups=2, window_size=8,
                 compress_ratios=[0, 4, 8], compress_rope_theta=40000.0, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
                 moe_intermediate_size=64, first_k_dense_replace=0, n_group=1, topk_group=1, routed_scaling_factor=1.5, norm_topk_prob=True,
                 scoring_func="sqrtsoftplus", num_hash_layers=1, hc_mult=2, hc_sinkhorn_iters=3, swiglu_limit=10.0,
                 max_position_embeddings=4096)
     base.update(over)
     return ModelConfig(**base)
+
+
+PRESETS["tiny-deepseek-v4"] = tiny_deepseek_v4
 
 
 def tiny_gemma4(**over) -> ModelConfig:
