@@ -370,20 +370,36 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
         sp = build_sampling_params(body, 1024)
         sid = await client.submit(prompt_ids, sp, affinity_key(raw))
         tools = body.get("tools")
+        stops = parse_stop({"stop": raw.get("stop_sequences")})
+        think_open = reasoning and prompt_opens_thinking(tokenizer.decode(prompt_ids[-64:]))
+
+        def which_stop(text: str):
+            """The stop sequence that ends `text` first, if any."""
+            hits = [(text.find(s_), s_) for s_ in stops if s_ in text]
+            return min(hits)[1] if hits else None
+
         if not body.get("stream"):
-            toks, _, status = await _collect(sid, [])
-            text = tokenizer.decode(toks)
+            toks, _, status = await _collect(sid, [], stops)
+            full = tokenizer.decode(toks)
+            matched = which_stop(full)
+            text = cut_at_stop(full, stops)[0]
+            thought = None
+            if reasoning:
+                thought, text = split_reasoning(text, think_open)
             calls = []
             if tools:
                 text, calls = parse_tools(text, tool_format, tools)
             content: List[Dict[str, Any]] = []
+            if thought:
+                content.append({"type": "thinking", "thinking": thought, "signature": ""})
             if text:
                 content.append({"type": "text", "text": text})
             for c in calls:
                 content.append({"type": "tool_use", "id": c.id.replace("call_", "toolu_"), "name": c.name, "input": c.arguments})
-            stop = "tool_use" if calls else ("max_tokens" if len(toks) >= sp.max_tokens else "end_turn")
+            stop = "tool_use" if calls else "stop_sequence" if matched else ("max_tokens" if len(toks) >= sp.max_tokens else "end_turn")
             return {"id": mid, "type": "message", "role": "assistant", "model": model_name, "content": content, "stop_reason": stop,
-                    "stop_sequence": None, "usage": {"input_tokens": len(prompt_ids), "output_tokens": len(toks)}}
+                    "stop_sequence": matched if stop == "stop_sequence" else None,
+                    "usage": {"input_tokens": len(prompt_ids), "output_tokens": len(toks)}}
 
         async def gen():
             def ev(name, data):
@@ -391,37 +407,86 @@ def create_app(client, tokenizer, model_name: str, tool_format: str = "hermes", 
             yield ev("message_start", {"type": "message_start", "message": {"id": mid, "type": "message", "role": "assistant", "model": model_name,
                                                                            "content": [], "stop_reason": None,
                                                                            "usage": {"input_tokens": len(prompt_ids), "output_tokens": 0}}})
-            yield ev("content_block_start", {"type": "content_block_start", "index": 0, "content_block": {"type": "text", "text": ""}})
             dec = tokenizer.incremental_decoder()
             tp = StreamingToolParser(tool_format, tools) if tools else None
-            n, calls_all = 0, []
+            ss = StopStream(stops) if stops else None
+            rs = ReasoningStream(think_open) if reasoning else None
+            n, calls_all, seen = 0, [], ""
+            block = {"index": -1, "kind": None}          # the content block that is open
+
+            def to_block(kind: str):
+                """Events that close the open block (if it is of another kind) and open one of `kind`."""
+                out = []
+                if block["kind"] == kind:
+                    return out
+                if block["kind"] is not None:
+                    out.append(ev("content_block_stop", {"type": "content_block_stop", "index": block["index"]}))
+                block["index"] += 1
+                block["kind"] = kind
+                start = {"type": "thinking", "thinking": ""} if kind == "thinking" else {"type": "text", "text": ""}
+                out.append(ev("content_block_start", {"type": "content_block_start", "index": block["index"], "content_block": start}))
+                return out
+
+            def emit(piece: str, last: bool = False):
+                nonlocal seen
+                outs = []
+                seen += piece
+                if ss is not None:
+                    piece = ss.feed(piece)[0] + (ss.flush() if last else "")
+                thought = ""
+                if rs is not None:
+                    thought, piece = rs.feed(piece)
+                    if last:
+                        t2, p2 = rs.flush()
+                        thought, piece = thought + t2, piece + p2
+                if thought:
+                    outs += to_block("thinking")
+                    outs.append(ev("content_block_delta", {"type": "content_block_delta", "index": block["index"],
+                                                           "delta": {"type": "thinking_delta", "thinking": thought}}))
+                if tp is not None:
+                    piece, calls = tp.feed(piece)
+                    calls_all.extend(calls)
+                    if last:
+                        rest, calls = tp.flush()
+                        calls_all.extend(calls)
+                        piece += "" if calls else rest
+                if piece:
+                    outs += to_block("text")
+                    outs.append(ev("content_block_delta", {"type": "content_block_delta", "index": block["index"], "delta": {"type": "text_delta", "text": piece}}))
+                return outs
+
             try:
                 async for o in client.stream(sid):
                     for t in o.token_ids:
+                        if ss is not None and ss.hit:
+                            break
                         n += 1
-                        piece = dec.add(t)
-                        if tp is not None:
-                            piece, calls = tp.feed(piece)
-                            calls_all.extend(calls)
-                        if piece:
-                            yield ev("content_block_delta", {"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": piece}})
+                        for e in emit(dec.add(t)):
+                            yield e
+                    if ss is not None and ss.hit:
+                        await client.abort(sid)
+                        break
             except asyncio.CancelledError:
                 await client.abort(sid)
                 raise
-            tail = dec.flush()
-            if tp is not None:
-                rest, calls = tp.flush()
-                calls_all.extend(calls)
-                tail = (tail or "") + ("" if calls else rest)
-            if tail:
-                yield ev("content_block_delta", {"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": tail}})
-            yield ev("content_block_stop", {"type": "content_block_stop", "index": 0})
+            for e in emit(dec.flush() or "", last=True):
+                yield e
+            if block["kind"] is None:                     # an answer without any text still carries one (empty) text block
+                for e in to_block("text"):
+                    yield e
+            yield ev("content_block_stop", {"type": "content_block_stop", "index": block["index"]})
+            base = block["index"] + 1
             for i, c in enumerate(calls_all):
-                yield ev("content_block_start", {"type": "content_block_start", "index": i + 1,
+                yield ev("content_block_start", {"type": "content_block_start", "index": base + i,
                                                  "content_block": {"type": "tool_use", "id": c.id.replace("call_", "toolu_"), "name": c.name, "input": {}}})
-                yield ev("content_block_delta", {"type": "content_block_delta", "index": i + 1,
+                yield ev("content_block_delta", {"type": "content_block_delta", "index": base + i,
                                                  "delta": {"type": "input_json_delta", "partial_json": json.dumps(c.arguments)}})
-                yield ev("content_block_stop", {"type": "content_block_stop", "index": i + 1})
+                yield ev("content_block_stop", {"type": "content_block_stop", "index": base + i})
+            matched = which_stop(seen) if (ss is not None and ss.hit) else None
+            if matched and not calls_all:
+                yield ev("message_delta", {"type": "message_delta", "delta": {"stop_reason": "stop_sequence", "stop_sequence": matched}, "usage": {"output_tokens": n}})
+                yield ev("message_stop", {"type": "message_stop"})
+                return
             stop = "tool_use" if calls_all else ("max_tokens" if n >= sp.max_tokens else "end_turn")
             yield ev("message_delta", {"type": "message_delta", "delta": {"stop_reason": stop, "stop_sequence": None}, "usage": {"output_tokens": n}})
             yield ev("message_stop", {"type": "message_stop"})

@@ -137,6 +137,42 @@ def test_reasoning_goes_to_its_own_field_when_the_prompt_opens_the_block(served)
     assert "reasoning_content" not in plain and len(plain["content"]) > 0
 
 
+def test_anthropic_stop_sequences_and_thinking_blocks(served):
+    tc, _ = served
+    body = {"model": "tiny", "max_tokens": 24, "temperature": 0, "ignore_eos": True, "messages": [{"role": "user", "content": "stop here"}]}
+    full = tc.post("/v1/messages", json=body).json()
+    text = full["content"][0]["text"]
+    assert full["stop_reason"] == "max_tokens" and len(text) >= 12
+    stop = text[8:11]
+    r = tc.post("/v1/messages", json={**body, "stop_sequences": [stop]}).json()
+    assert r["stop_reason"] == "stop_sequence" and r["stop_sequence"] == stop and r["usage"]["output_tokens"] < 24
+    assert "".join(b["text"] for b in r["content"] if b["type"] == "text") == text[: text.find(stop)]
+    got, reason = "", None
+    with tc.stream("POST", "/v1/messages", json={**body, "stop_sequences": [stop], "stream": True}) as resp:
+        for l in resp.iter_lines():
+            if l.startswith("data: "):
+                d = json.loads(l[6:])
+                if d["type"] == "content_block_delta":
+                    got += d["delta"].get("text", "")
+                if d["type"] == "message_delta":
+                    reason = (d["delta"]["stop_reason"], d["delta"]["stop_sequence"])
+    assert got == text[: text.find(stop)] and reason == ("stop_sequence", stop)
+    # a prompt that leaves a thinking block open: the answer is a thinking block, plain and streamed
+    think = {**body, "max_tokens": 6, "messages": [{"role": "user", "content": "solve <think>"}]}
+    r = tc.post("/v1/messages", json=think).json()
+    assert [b["type"] for b in r["content"]] == ["thinking"] and len(r["content"][0]["thinking"]) > 0
+    kinds, thought = [], ""
+    with tc.stream("POST", "/v1/messages", json={**think, "stream": True}) as resp:
+        for l in resp.iter_lines():
+            if l.startswith("data: "):
+                d = json.loads(l[6:])
+                if d["type"] == "content_block_start":
+                    kinds.append((d["index"], d["content_block"]["type"]))
+                if d["type"] == "content_block_delta":
+                    thought += d["delta"].get("thinking", "")
+    assert kinds == [(0, "thinking")] and thought == r["content"][0]["thinking"]
+
+
 def test_backend_death_is_noticed(served):
     tc, proc = served
     proc.terminate()
